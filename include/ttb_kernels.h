@@ -1,0 +1,250 @@
+/* C ABI of the sm_100a kernel library (libttb200.so): the lowest boundary of the backend.
+ *
+ * In tt-mlir every per-op executor under runtime/lib/ttnn/operations/ ends in one call into
+ * the tt-metal TTNN library (`::ttnn::matmul`, `::ttnn::quantize`, ...).  Each launcher below
+ * replaces one of those library calls with a hand-written CUDA kernel; the citation beside a
+ * declaration names the reference call site it stands in for.  The C++ runtime target in
+ * tt-mlir_b200/runtime/ is the only intended caller, but nothing here depends on it: plain
+ * pointers, sizes and enums only, no C++ or torch types.
+ *
+ * Conventions
+ *  - every function returns TTB_OK (0) or a TTB_ERR_* code; ttb_last_error() gives the text
+ *    of the calling thread's most recent failure.  Nothing throws, aborts or exits.
+ *  - `stream` is a cudaStream_t passed as void*; launches are asynchronous on it.
+ *  - pointers are device pointers on the current device unless a name says `host`.
+ *  - `dtype` arguments use the numeric values of tt::target::DataType
+ *    (include/ttmlir/Target/Common/types.fbs:19-42).
+ *  - tensors are dense row-major unless strides are passed explicitly.
+ */
+#ifndef TTB_KERNELS_H
+#define TTB_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TTB_API __attribute__((visibility("default")))
+
+enum {
+  TTB_OK = 0,
+  TTB_ERR_CUDA = 1,        /* a CUDA runtime / driver call failed */
+  TTB_ERR_INVALID = 2,     /* bad argument (shape, alignment, null pointer) */
+  TTB_ERR_UNSUPPORTED = 3, /* valid request this build has no kernel for */
+  TTB_ERR_NCCL = 4,        /* NCCL call failed or NCCL could not be loaded */
+  TTB_ERR_DEVICE = 5       /* a kernel reported a failure through its status word */
+};
+
+enum {
+  TTB_DTYPE_FLOAT32 = 0,
+  TTB_DTYPE_FLOAT16 = 1,
+  TTB_DTYPE_BFLOAT16 = 2,
+  TTB_DTYPE_UINT32 = 9,
+  TTB_DTYPE_UINT16 = 10,
+  TTB_DTYPE_UINT8 = 11,
+  TTB_DTYPE_INT32 = 12,
+  TTB_DTYPE_INT8 = 17
+};
+
+TTB_API const char *ttb_last_error(void);
+TTB_API size_t ttb_dtype_size(int dtype);
+
+/* ---- device, streams, memory, events ------------------------------------------------------
+ * Stand in for what MeshDevice / command queues / buffers provide to runtime/lib/ttnn
+ * (openMeshDevice runtime/lib/ttnn/runtime.cpp:582-624, toLayout/toHost :861-933). */
+TTB_API int ttb_device_count(int *count);
+TTB_API int ttb_set_device(int device);
+TTB_API int ttb_device_info(int device, int *sm_count, size_t *total_mem, int *cc_major, int *cc_minor);
+TTB_API int ttb_stream_create(void **stream);
+TTB_API int ttb_stream_destroy(void *stream);
+TTB_API int ttb_stream_sync(void *stream);
+TTB_API int ttb_device_sync(void);
+/* Stream-ordered allocation from the device's default memory pool (kept warm, never trimmed). */
+TTB_API int ttb_malloc(void **ptr, size_t bytes, void *stream);
+TTB_API int ttb_free(void *ptr, void *stream);
+TTB_API int ttb_host_alloc_pinned(void **ptr, size_t bytes);
+TTB_API int ttb_host_free_pinned(void *ptr);
+TTB_API int ttb_memcpy_h2d(void *dst, const void *host_src, size_t bytes, void *stream);
+TTB_API int ttb_memcpy_d2h(void *host_dst, const void *src, size_t bytes, void *stream);
+TTB_API int ttb_memcpy_d2d(void *dst, const void *src, size_t bytes, void *stream);
+TTB_API int ttb_memset(void *dst, int byte, size_t bytes, void *stream);
+TTB_API int ttb_event_create(void **event);
+TTB_API int ttb_event_destroy(void *event);
+TTB_API int ttb_event_record(void *event, void *stream);
+TTB_API int ttb_event_sync(void *event);
+TTB_API int ttb_stream_wait_event(void *stream, void *event);
+TTB_API int ttb_event_elapsed_ms(void *start, void *stop, float *ms);
+/* Number of kernels this library has launched in the calling process (all threads). */
+TTB_API uint64_t ttb_launch_count(void);
+
+/* ---- quantization: ::ttnn::quantize / dequantize / requantize
+ * (runtime/lib/ttnn/operations/eltwise/quantization/quantization.cpp:173-187).
+ * Arithmetic follows the torch goldens tools/golden/mapping.py:2534-2582:
+ *   quantize   q = clamp(rne(x * (1/scale)) + zp, qmin, qmax)      (f32, 1/scale rounded once)
+ *   dequantize x = float(q - zp) * scale
+ *   requantize q' = quantize(dequantize(q))
+ * qmin/qmax come from the output dtype: INT8 [-128,127], UINT8 [0,255], INT32 full range unless
+ * `clamp_i8` is set, in which case an INT32 container holds values clamped to [-128,127]
+ * (how tt-mlir stores quantized tensors, lib/Dialect/TTNN/Pipelines/TTNNPipelines.cpp:349-351).
+ * Per-axis variants take one scale / zero point per index of `axis`; the tensor is viewed as
+ * [outer, axis_len, inner]. */
+TTB_API int ttb_quantize(const void *in, int in_dtype, void *out, int out_dtype, size_t n,
+                         float scale, int32_t zero_point, int clamp_i8, void *stream);
+TTB_API int ttb_dequantize(const void *in, int in_dtype, void *out, int out_dtype, size_t n,
+                           float scale, int32_t zero_point, void *stream);
+TTB_API int ttb_requantize(const void *in, int in_dtype, void *out, int out_dtype, size_t n,
+                           float in_scale, int32_t in_zp, float out_scale, int32_t out_zp,
+                           int clamp_i8, void *stream);
+TTB_API int ttb_quantize_per_axis(const void *in, int in_dtype, void *out, int out_dtype,
+                                  size_t outer, size_t axis_len, size_t inner,
+                                  const float *scales, const int32_t *zero_points, int clamp_i8,
+                                  void *stream);
+TTB_API int ttb_dequantize_per_axis(const void *in, int in_dtype, void *out, int out_dtype,
+                                    size_t outer, size_t axis_len, size_t inner,
+                                    const float *scales, const int32_t *zero_points, void *stream);
+TTB_API int ttb_requantize_per_axis(const void *in, int in_dtype, void *out, int out_dtype,
+                                    size_t outer, size_t axis_len, size_t inner,
+                                    const float *in_scales, const int32_t *in_zps,
+                                    const float *out_scales, const int32_t *out_zps, int clamp_i8,
+                                    void *stream);
+/* quantize -> requantize -> dequantize in one pass over the data (per-tensor parameters).
+ * `q1` / `q2` may be null; when given, the intermediate integer tensors are written too. */
+TTB_API int ttb_quant_chain(const void *in, int in_dtype, void *q1, int q1_dtype, void *q2,
+                            int q2_dtype, void *out, int out_dtype, size_t n, float scale1,
+                            int32_t zp1, float scale2, int32_t zp2, int clamp_i8, void *stream);
+
+/* ---- elementwise: ::ttnn::relu/.../add/... (runtime/lib/ttnn/operations/eltwise/unary/unary.cpp:133-273,
+ * binary/binary.cpp:37-127, binary/binary_composite.cpp, ternary/where.cpp).
+ * `op` uses the flatbuffer enum values (EltwiseUnaryOpType / EltwiseBinaryOpType,
+ * include/ttmlir/Target/TTNN/operations/eltwise.fbs:11-26,133-166); composite binary ops
+ * are offset by TTB_BINARY_COMPOSITE_BASE.  Math is done in f32 (i32 for integer inputs of
+ * integer ops) and rounded once to the output dtype. */
+#define TTB_BINARY_COMPOSITE_BASE 100
+TTB_API int ttb_eltwise_unary(int op, const void *in, int in_dtype, void *out, int out_dtype,
+                              size_t n, float param, void *stream);
+/* Broadcasting binary op over a rank-`rank` output (rank <= 8).  Strides are in elements,
+ * 0 on broadcast dimensions. */
+TTB_API int ttb_eltwise_binary(int op, const void *a, int a_dtype, const void *b, int b_dtype,
+                               void *out, int out_dtype, int rank, const int64_t *out_shape,
+                               const int64_t *a_strides, const int64_t *b_strides, void *stream);
+TTB_API int ttb_where(const void *cond, int cond_dtype, const void *a, const void *b, int dtype,
+                      void *out, int rank, const int64_t *out_shape, const int64_t *c_strides,
+                      const int64_t *a_strides, const int64_t *b_strides, void *stream);
+TTB_API int ttb_clamp(const void *in, int dtype, void *out, size_t n, float lo, float hi,
+                      void *stream);
+/* ::ttnn::typecast (runtime/lib/ttnn/operations/layout/typecast.cpp:26-27). */
+TTB_API int ttb_typecast(const void *in, int in_dtype, void *out, int out_dtype, size_t n,
+                         void *stream);
+/* ::ttnn::full / zeros / ones / arange (runtime/lib/ttnn/operations/creation/). */
+TTB_API int ttb_fill(void *out, int dtype, size_t n, double value, void *stream);
+TTB_API int ttb_arange(void *out, int dtype, size_t n, double start, double step, void *stream);
+/* silu(gate) * up with both roundings of the unfused chain kept (SwiGLU gating). */
+TTB_API int ttb_silu_mul(const void *gate, const void *up, void *out, int dtype, size_t n,
+                         void *stream);
+
+/* ---- normalisation / reductions
+ * ::ttnn::softmax (operations/normalization/softmax.cpp:32-33), ::ttnn::rms_norm
+ * (operations/normalization/rms_norm.cpp:40-47), ::ttnn::sum/mean/max/min
+ * (operations/reduction/reduction.cpp:40-58).  Tensor viewed as [outer, len, inner]. */
+TTB_API int ttb_softmax(const void *in, void *out, int dtype, size_t outer, size_t len,
+                        size_t inner, void *stream);
+TTB_API int ttb_rms_norm(const void *in, const void *weight, const void *bias, void *out,
+                         int dtype, size_t rows, size_t cols, float eps, void *stream);
+/* out = rms_norm(a + b); `sum_out` (nullable) receives a + b rounded to dtype. */
+TTB_API int ttb_add_rms_norm(const void *a, const void *b, const void *weight, void *sum_out,
+                             void *out, int dtype, size_t rows, size_t cols, float eps,
+                             void *stream);
+/* op: 0 sum, 1 mean, 2 max, 3 min (ReductionOpType, operations/reduction.fbs:6-11). */
+TTB_API int ttb_reduce(int op, const void *in, void *out, int dtype, size_t outer, size_t len,
+                       size_t inner, void *stream);
+
+/* ---- data movement: ::ttnn::permute / slice / concat / repeat / transpose
+ * (runtime/lib/ttnn/operations/data_movement/). One gather kernel covers them: out is dense
+ * row-major of `out_shape`; element (i0..ik) is read from in + in_offset + sum(i_d * in_strides[d]). */
+TTB_API int ttb_strided_copy(const void *in, void *out, int elem_size, int rank,
+                             const int64_t *out_shape, const int64_t *in_strides,
+                             int64_t in_offset, void *stream);
+/* Writes a dense `in` of `in_shape` into a window of a larger dense tensor (concat pieces). */
+TTB_API int ttb_strided_scatter(const void *in, void *out, int elem_size, int rank,
+                                const int64_t *in_shape, const int64_t *out_strides,
+                                int64_t out_offset, void *stream);
+/* ::ttnn::experimental::rotary_embedding (operations/transformer/rotary_embedding.cpp:28-29):
+ * out = x*cos + rotate_half(x)*sin over [batch*heads, seq, head_dim]; cos/sin are
+ * [seq, head_dim] (lib/Dialect/TTNN/Transforms/Fusing/RoPEFusingPattern.cpp:49-51). */
+TTB_API int ttb_rotary_embedding(const void *x, const void *cos, const void *sin, void *out,
+                                 int dtype, size_t batch_heads, size_t seq, size_t head_dim,
+                                 void *stream);
+
+/* ---- contractions: ::ttnn::matmul / ::ttnn::linear (operations/matmul/matmul.cpp:75-80,117-122).
+ * C[b] = act(A[b]^(ta) * B[b]^(tb) + bias), f32 accumulation, one rounding to `c_dtype`.
+ * A is [M,K] (or [K,M] when trans_a), B is [K,N] (or [N,K] when trans_b), both dense with the
+ * given batch strides in elements (0 = broadcast).  `bias` (nullable) has N elements of
+ * `bias_dtype`.  `act`: TTB_ACT_*.  `round_steps` is a bit mask that keeps a fused launch equal
+ * to the op chain it replaces: bit 0 rounds to c_dtype after the product (a separate matmul op
+ * would have stored it), bit 1 rounds again after the bias add (a separate add op).
+ * bf16/f16 inputs whose shapes fit run on the tcgen05 tensor-core kernel; everything else
+ * (f32, odd shapes) runs on the SIMT kernel. */
+enum { TTB_ACT_NONE = 0, TTB_ACT_RELU = 1, TTB_ACT_SILU = 2, TTB_ACT_GELU = 3, TTB_ACT_SIGMOID = 4 };
+TTB_API int ttb_gemm(const void *a, const void *b, const void *bias, void *c, int ab_dtype,
+                     int bias_dtype, int c_dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
+                     int trans_a, int trans_b, int64_t a_batch_stride, int64_t b_batch_stride,
+                     int act, int round_steps, void *stream);
+/* Same contract, forced onto the SIMT kernel (reference implementation for the fast path). */
+TTB_API int ttb_gemm_simt(const void *a, const void *b, const void *bias, void *c, int ab_dtype,
+                          int bias_dtype, int c_dtype, int64_t batch, int64_t m, int64_t n,
+                          int64_t k, int trans_a, int trans_b, int64_t a_batch_stride,
+                          int64_t b_batch_stride, int act, int round_steps, void *stream);
+
+/* ::ttnn::conv2d (runtime/lib/ttnn/operations/conv/conv2d.cpp:83-87; semantics
+ * include/ttmlir/Dialect/TTIR/IR/TTIROps.td:3959-4033): NHWC activations [N,H,W,C], weights
+ * [O, C/groups, kH, kW], bias with O elements (nullable), f32 accumulation, one rounding.
+ * padding = {top, left, bottom, right}.  Implemented as a gather into GEMM operand layout
+ * followed by the contraction kernel; 1x1 stride-1 convolutions go straight to the GEMM.
+ * `workspace` must hold ttb_conv2d_workspace_bytes(...) bytes (0 bytes needed -> may be null). */
+TTB_API size_t ttb_conv2d_workspace_bytes(int dtype, int64_t n, int64_t h, int64_t w, int64_t c,
+                                          int64_t o, int kh, int kw, int stride_h, int stride_w,
+                                          const int *padding4, int dil_h, int dil_w, int groups);
+TTB_API int ttb_conv2d(const void *x, const void *weight, const void *bias, void *out, int dtype,
+                       int bias_dtype, int64_t n, int64_t h, int64_t w, int64_t c, int64_t o,
+                       int kh, int kw, int stride_h, int stride_w, const int *padding4, int dil_h,
+                       int dil_w, int groups, int act, void *workspace, void *stream);
+
+/* ::ttnn::transformer::scaled_dot_product_attention
+ * (runtime/lib/ttnn/operations/transformer/scaled_dot_product_attention.cpp:41-45; golden
+ * tools/golden/mapping.py:8398-8500): out = softmax(q k^T * scale + mask) v with f32 softmax.
+ * q [B,Hq,Sq,D], k/v [B,Hkv,Skv,D] (Hq a multiple of Hkv: grouped-query attention), out like q.
+ * `mask` (nullable) is additive, [B or 1, Hq or 1, Sq, Skv] in `dtype`; `is_causal` masks j > i. */
+TTB_API int ttb_sdpa(const void *q, const void *k, const void *v, const void *mask, void *out,
+                     int dtype, int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seq_q,
+                     int64_t seq_kv, int64_t head_dim, int64_t mask_batch, int64_t mask_heads,
+                     int is_causal, float scale, void *stream);
+
+/* ---- collectives on a 1xN mesh: ::ttnn::all_reduce / all_gather / reduce_scatter
+ * (runtime/lib/ttnn/operations/ccl/all_reduce.cpp:36-37, all_gather.cpp:38-41,
+ * reduce_scatter.cpp:60-67).  Thin, status-returning wrappers over NCCL, which is loaded with
+ * dlopen at first use.  `comm` is an ncclComm_t as void*; `id128` is a 128-byte ncclUniqueId.
+ * `reduce_type` is the serialised ttcore::ReduceType: 0 sum, 1 mean, 2 max, 3 min. */
+TTB_API int ttb_nccl_version(int *version);
+TTB_API int ttb_nccl_unique_id(char *id128);
+TTB_API int ttb_comm_init_rank(void **comm, int nranks, const char *id128, int rank);
+TTB_API int ttb_comm_init_all(void **comms, int ndev, const int *devices);
+TTB_API int ttb_comm_destroy(void *comm);
+TTB_API int ttb_group_start(void);
+TTB_API int ttb_group_end(void);
+TTB_API int ttb_all_reduce(void *comm, const void *in, void *out, size_t count, int dtype,
+                           int reduce_type, void *stream);
+/* Concatenates each rank's `send_count` elements in rank order (gather along dimension 0). */
+TTB_API int ttb_all_gather(void *comm, const void *in, void *out, size_t send_count, int dtype,
+                           void *stream);
+TTB_API int ttb_reduce_scatter(void *comm, const void *in, void *out, size_t recv_count, int dtype,
+                               int reduce_type, void *stream);
+TTB_API int ttb_broadcast(void *comm, const void *in, void *out, size_t count, int dtype, int root,
+                          void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TTB_KERNELS_H */

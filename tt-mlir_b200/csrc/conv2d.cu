@@ -1,0 +1,123 @@
+// conv2d on NHWC activations as a GEMM: M = N*Ho*Wo output pixels, N = O output channels,
+// K = kH*kW*C (reference semantics: include/ttmlir/Dialect/TTIR/IR/TTIROps.td:3959-4033; the
+// CPU path lowers it to tosa.conv2d with f32 accumulation,
+// lib/Conversion/TTIRToLinalg/TTIRToLinalg.cpp:576-787).
+//
+// 1x1 / stride 1 / no padding convolutions are already in GEMM layout (activations [P, C],
+// weights [O, C]) and go straight to the contraction kernel.  Everything else gathers the
+// receptive fields into a [P, K] operand (16-byte vectors along C, zero fill outside the
+// image) and reorders the weights from [O, C, kH, kW] to [O, kH, kW, C] in a workspace.
+#include "common.cuh"
+
+namespace ttb {
+
+struct ConvGeom {
+  int64_t N, H, W, C, Ho, Wo;
+  int kh, kw, sh, sw, pt, pl, dh, dw;
+};
+
+// One thread per V channels of one (pixel, ky, kx) tap.
+template <typename T, int V>
+__global__ void __launch_bounds__(256) im2colKernel(const T *__restrict__ x, T *__restrict__ col, ConvGeom g) {
+  int64_t cv = g.C / V;
+  int64_t K = static_cast<int64_t>(g.kh) * g.kw * g.C;
+  int64_t total = g.N * g.Ho * g.Wo * g.kh * g.kw * cv;
+  int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+    int64_t c = (i % cv) * V;
+    int64_t r = i / cv;
+    int kx = static_cast<int>(r % g.kw);
+    r /= g.kw;
+    int ky = static_cast<int>(r % g.kh);
+    int64_t p = r / g.kh;
+    int64_t ox = p % g.Wo, oy = (p / g.Wo) % g.Ho, n = p / (g.Wo * g.Ho);
+    int64_t iy = oy * g.sh + ky * g.dh - g.pt, ix = ox * g.sw + kx * g.dw - g.pl;
+    T *dst = col + p * K + (static_cast<int64_t>(ky) * g.kw + kx) * g.C + c;
+    bool inside = iy >= 0 && iy < g.H && ix >= 0 && ix < g.W;
+    const T *src = x + ((n * g.H + iy) * g.W + ix) * g.C + c;
+    if (V * sizeof(T) == 16) {
+      uint4 v = inside ? __ldg(reinterpret_cast<const uint4 *>(src)) : make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4 *>(dst) = v;
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) dst[j] = inside ? src[j] : T(0);
+    }
+  }
+}
+
+static int64_t outDim(int64_t in, int k, int s, int p0, int p1, int d) {
+  return (in + p0 + p1 - static_cast<int64_t>(d) * (k - 1) - 1) / s + 1;
+}
+
+static bool isPointwise(int kh, int kw, int sh, int sw, const int *pad, int groups) {
+  return kh == 1 && kw == 1 && sh == 1 && sw == 1 && pad[0] == 0 && pad[1] == 0 && pad[2] == 0 && pad[3] == 0 &&
+         groups == 1;
+}
+
+static size_t alignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+} // namespace ttb
+
+using namespace ttb;
+
+extern "C" {
+
+size_t ttb_conv2d_workspace_bytes(int dtype, int64_t n, int64_t h, int64_t w, int64_t c, int64_t o, int kh, int kw,
+                                  int stride_h, int stride_w, const int *padding4, int dil_h, int dil_w, int groups) {
+  if (!padding4 || isPointwise(kh, kw, stride_h, stride_w, padding4, groups)) return 0;
+  int64_t ho = outDim(h, kh, stride_h, padding4[0], padding4[2], dil_h);
+  int64_t wo = outDim(w, kw, stride_w, padding4[1], padding4[3], dil_w);
+  if (ho <= 0 || wo <= 0) return 0;
+  size_t es = dtypeSize(dtype);
+  size_t K = static_cast<size_t>(kh) * kw * c;
+  return alignUp(static_cast<size_t>(n * ho * wo) * K * es, 256) + alignUp(static_cast<size_t>(o) * K * es, 256);
+}
+
+int ttb_conv2d(const void *x, const void *weight, const void *bias, void *out, int dtype, int bias_dtype, int64_t n,
+               int64_t h, int64_t w, int64_t c, int64_t o, int kh, int kw, int stride_h, int stride_w,
+               const int *padding4, int dil_h, int dil_w, int groups, int act, void *workspace, void *stream) {
+  TTB_CHECK(x && weight && out && padding4, "null argument");
+  TTB_CHECK(groups == 1, "grouped convolution is not supported");
+  TTB_CHECK(kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0 && dil_h > 0 && dil_w > 0, "bad convolution geometry");
+  size_t es = dtypeSize(dtype);
+  TTB_CHECK(dtype == kBF16 || dtype == kF32 || dtype == kF16, "conv2d needs a float dtype");
+  if (isPointwise(kh, kw, stride_h, stride_w, padding4, groups)) {
+    return ttb_gemm(x, weight, bias, out, dtype, bias_dtype, dtype, 1, n * h * w, o, c, 0, 1, 0, 0, act, 0, stream);
+  }
+  ConvGeom g;
+  g.N = n; g.H = h; g.W = w; g.C = c;
+  g.kh = kh; g.kw = kw; g.sh = stride_h; g.sw = stride_w; g.pt = padding4[0]; g.pl = padding4[1];
+  g.dh = dil_h; g.dw = dil_w;
+  g.Ho = outDim(h, kh, stride_h, padding4[0], padding4[2], dil_h);
+  g.Wo = outDim(w, kw, stride_w, padding4[1], padding4[3], dil_w);
+  TTB_CHECK(g.Ho > 0 && g.Wo > 0, "convolution output is empty");
+  TTB_CHECK(workspace != nullptr, "conv2d needs its workspace");
+  int64_t P = n * g.Ho * g.Wo, K = static_cast<int64_t>(kh) * kw * c;
+  char *col = static_cast<char *>(workspace);
+  char *wre = col + alignUp(static_cast<size_t>(P) * K * es, 256);
+  cudaStream_t st = asStream(stream);
+  // weights [O, C, kH, kW] -> [O, kH, kW, C]
+  {
+    int64_t shape[4] = {o, kh, kw, c};
+    int64_t strides[4] = {c * kh * kw, kw, 1, static_cast<int64_t>(kh) * kw};
+    int rc = ttb_strided_copy(weight, wre, static_cast<int>(es), 4, shape, strides, 0, stream);
+    if (rc) return rc;
+  }
+  int vec = static_cast<int>(16 / es);
+  if (c % vec == 0 && aligned16(x) && aligned16(col)) {
+    int64_t total = P * kh * kw * (c / vec);
+    int grid = gridFor(static_cast<size_t>(total), 256);
+    if (es == 2) im2colKernel<uint16_t, 8><<<grid, 256, 0, st>>>(static_cast<const uint16_t *>(x), reinterpret_cast<uint16_t *>(col), g);
+    else im2colKernel<uint32_t, 4><<<grid, 256, 0, st>>>(static_cast<const uint32_t *>(x), reinterpret_cast<uint32_t *>(col), g);
+  } else {
+    int64_t total = P * kh * kw * c;
+    int grid = gridFor(static_cast<size_t>(total), 256);
+    if (es == 2) im2colKernel<uint16_t, 1><<<grid, 256, 0, st>>>(static_cast<const uint16_t *>(x), reinterpret_cast<uint16_t *>(col), g);
+    else im2colKernel<uint32_t, 1><<<grid, 256, 0, st>>>(static_cast<const uint32_t *>(x), reinterpret_cast<uint32_t *>(col), g);
+  }
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return ttb_gemm(col, wre, bias, out, dtype, bias_dtype, dtype, 1, P, o, K, 0, 1, 0, 0, act, 0, stream);
+}
+
+} // extern "C"

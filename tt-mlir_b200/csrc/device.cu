@@ -1,0 +1,199 @@
+// Device, stream, memory and event entry points of the C ABI, plus error bookkeeping.
+#include "common.cuh"
+
+#include <atomic>
+#include <mutex>
+
+namespace ttb {
+
+static thread_local std::string g_lastError;
+std::atomic<uint64_t> g_launchCount{0};
+
+void setLastError(const std::string &msg) { g_lastError = msg; }
+
+int cudaFail(cudaError_t e, const char *what, const char *file, int line) {
+  g_lastError = std::string(cudaGetErrorName(e)) + ": " + cudaGetErrorString(e) + " at " +
+                file + ":" + std::to_string(line) + " in " + what;
+  return TTB_ERR_CUDA;
+}
+
+int smCount() {
+  static int cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    return 148;
+  }
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      n = 148;
+    }
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+void countLaunch(uint64_t n) { g_launchCount.fetch_add(n, std::memory_order_relaxed); }
+
+} // namespace ttb
+
+using namespace ttb;
+
+extern "C" {
+
+const char *ttb_last_error(void) { return g_lastError.c_str(); }
+
+size_t ttb_dtype_size(int dtype) { return dtypeSize(dtype); }
+
+uint64_t ttb_launch_count(void) { return g_launchCount.load(std::memory_order_relaxed); }
+
+int ttb_device_count(int *count) {
+  TTB_CHECK(count != nullptr, "count is null");
+  cudaError_t e = cudaGetDeviceCount(count);
+  if (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver) {
+    *count = 0;
+    (void)cudaGetLastError();
+    return TTB_OK;
+  }
+  TTB_CUDA(e);
+  return TTB_OK;
+}
+
+int ttb_set_device(int device) {
+  TTB_CUDA(cudaSetDevice(device));
+  return TTB_OK;
+}
+
+int ttb_device_info(int device, int *sm_count, size_t *total_mem, int *cc_major, int *cc_minor) {
+  cudaDeviceProp p;
+  TTB_CUDA(cudaGetDeviceProperties(&p, device));
+  if (sm_count) *sm_count = p.multiProcessorCount;
+  if (total_mem) *total_mem = p.totalGlobalMem;
+  if (cc_major) *cc_major = p.major;
+  if (cc_minor) *cc_minor = p.minor;
+  return TTB_OK;
+}
+
+int ttb_stream_create(void **stream) {
+  TTB_CHECK(stream != nullptr, "stream is null");
+  cudaStream_t s;
+  TTB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  // Keep freed blocks in the pool: tensors of a program are re-allocated every submit.
+  int dev = 0;
+  TTB_CUDA(cudaGetDevice(&dev));
+  cudaMemPool_t pool;
+  TTB_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+  uint64_t threshold = UINT64_MAX;
+  TTB_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold));
+  *stream = s;
+  return TTB_OK;
+}
+
+int ttb_stream_destroy(void *stream) {
+  TTB_CUDA(cudaStreamDestroy(asStream(stream)));
+  return TTB_OK;
+}
+
+int ttb_stream_sync(void *stream) {
+  TTB_CUDA(cudaStreamSynchronize(asStream(stream)));
+  return TTB_OK;
+}
+
+int ttb_device_sync(void) {
+  TTB_CUDA(cudaDeviceSynchronize());
+  return TTB_OK;
+}
+
+int ttb_malloc(void **ptr, size_t bytes, void *stream) {
+  TTB_CHECK(ptr != nullptr, "ptr is null");
+  if (bytes == 0) {
+    bytes = 16; // distinct non-null pointers for empty tensors
+  }
+  TTB_CUDA(cudaMallocAsync(ptr, bytes, asStream(stream)));
+  return TTB_OK;
+}
+
+int ttb_free(void *ptr, void *stream) {
+  if (ptr) {
+    TTB_CUDA(cudaFreeAsync(ptr, asStream(stream)));
+  }
+  return TTB_OK;
+}
+
+int ttb_host_alloc_pinned(void **ptr, size_t bytes) {
+  TTB_CHECK(ptr != nullptr, "ptr is null");
+  TTB_CUDA(cudaMallocHost(ptr, bytes ? bytes : 16));
+  return TTB_OK;
+}
+
+int ttb_host_free_pinned(void *ptr) {
+  if (ptr) {
+    TTB_CUDA(cudaFreeHost(ptr));
+  }
+  return TTB_OK;
+}
+
+int ttb_memcpy_h2d(void *dst, const void *host_src, size_t bytes, void *stream) {
+  if (bytes) {
+    TTB_CUDA(cudaMemcpyAsync(dst, host_src, bytes, cudaMemcpyHostToDevice, asStream(stream)));
+  }
+  return TTB_OK;
+}
+
+int ttb_memcpy_d2h(void *host_dst, const void *src, size_t bytes, void *stream) {
+  if (bytes) {
+    TTB_CUDA(cudaMemcpyAsync(host_dst, src, bytes, cudaMemcpyDeviceToHost, asStream(stream)));
+  }
+  return TTB_OK;
+}
+
+int ttb_memcpy_d2d(void *dst, const void *src, size_t bytes, void *stream) {
+  if (bytes) {
+    TTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, asStream(stream)));
+  }
+  return TTB_OK;
+}
+
+int ttb_memset(void *dst, int byte, size_t bytes, void *stream) {
+  if (bytes) {
+    TTB_CUDA(cudaMemsetAsync(dst, byte, bytes, asStream(stream)));
+  }
+  return TTB_OK;
+}
+
+int ttb_event_create(void **event) {
+  TTB_CHECK(event != nullptr, "event is null");
+  cudaEvent_t e;
+  TTB_CUDA(cudaEventCreate(&e));
+  *event = e;
+  return TTB_OK;
+}
+
+int ttb_event_destroy(void *event) {
+  TTB_CUDA(cudaEventDestroy(reinterpret_cast<cudaEvent_t>(event)));
+  return TTB_OK;
+}
+
+int ttb_event_record(void *event, void *stream) {
+  TTB_CUDA(cudaEventRecord(reinterpret_cast<cudaEvent_t>(event), asStream(stream)));
+  return TTB_OK;
+}
+
+int ttb_event_sync(void *event) {
+  TTB_CUDA(cudaEventSynchronize(reinterpret_cast<cudaEvent_t>(event)));
+  return TTB_OK;
+}
+
+int ttb_stream_wait_event(void *stream, void *event) {
+  TTB_CUDA(cudaStreamWaitEvent(asStream(stream), reinterpret_cast<cudaEvent_t>(event), 0));
+  return TTB_OK;
+}
+
+int ttb_event_elapsed_ms(void *start, void *stop, float *ms) {
+  TTB_CHECK(ms != nullptr, "ms is null");
+  TTB_CUDA(cudaEventElapsedTime(ms, reinterpret_cast<cudaEvent_t>(start),
+                                reinterpret_cast<cudaEvent_t>(stop)));
+  return TTB_OK;
+}
+
+} // extern "C"

@@ -1,0 +1,171 @@
+// Data-movement kernels: one strided gather (permute / transpose / slice / repeat / head
+// split), one strided scatter (concat pieces, head merge) and rotary embedding.
+//
+// The launchers coalesce what they can on the host: when the innermost dimension is
+// contiguous on both sides and everything is 16-byte aligned, the copy runs in 16-byte units,
+// so a permute such as [1,S,H,D] -> [1,H,S,D] moves D*2 bytes per (s,h) with full-width
+// accesses.  Reference call sites: runtime/lib/ttnn/operations/data_movement/*.cpp.
+#include "common.cuh"
+
+namespace ttb {
+
+struct CopyDims {
+  int rank;
+  int64_t shape[8];
+  int64_t stride[8];
+};
+
+template <typename U, bool SCATTER>
+__global__ void __launch_bounds__(256)
+    stridedCopyKernel(const U *__restrict__ in, U *__restrict__ out, size_t n, CopyDims d, int64_t offset) {
+  size_t step = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += step) {
+    size_t r = i;
+    int64_t at = offset;
+    for (int k = d.rank - 1; k >= 0; --k) {
+      size_t c = r % d.shape[k];
+      r /= d.shape[k];
+      at += static_cast<int64_t>(c) * d.stride[k];
+    }
+    if (SCATTER) out[at] = in[i];
+    else out[i] = in[at];
+  }
+}
+
+// Shared host logic: merge dimensions, pick the widest unit, launch.
+template <bool SCATTER>
+static int launchStrided(const void *in, void *out, int elemSize, int rank, const int64_t *shape,
+                         const int64_t *strides, int64_t offset, cudaStream_t st) {
+  TTB_CHECK(in && out, "null tensor");
+  TTB_CHECK(rank >= 0 && rank <= 8, "rank must be <= 8");
+  TTB_CHECK(elemSize == 1 || elemSize == 2 || elemSize == 4 || elemSize == 8, "element size must be 1, 2, 4 or 8");
+  // drop size-1 dims, merge neighbours that are contiguous with respect to each other
+  int64_t sh[8], sd[8];
+  int r = 0;
+  size_t n = 1;
+  for (int i = 0; i < rank; ++i) {
+    TTB_CHECK(shape[i] >= 0, "negative dimension");
+    n *= static_cast<size_t>(shape[i]);
+    if (shape[i] == 1) continue;
+    if (r > 0 && sd[r - 1] == strides[i] * shape[i]) {
+      sh[r - 1] *= shape[i];
+      sd[r - 1] = strides[i];
+    } else {
+      sh[r] = shape[i];
+      sd[r] = strides[i];
+      ++r;
+    }
+  }
+  if (n == 0) return TTB_OK;
+  if (r == 0) {
+    sh[0] = 1;
+    sd[0] = 1;
+    r = 1;
+  }
+  // widen the unit while the innermost run, all other strides, the offset and both bases allow it
+  int unit = elemSize;
+  const char *src = static_cast<const char *>(in);
+  char *dst = static_cast<char *>(out);
+  if (sd[r - 1] == 1) {
+    while (unit < 16) {
+      int f = 2;
+      bool ok = sh[r - 1] % f == 0 && offset % f == 0;
+      for (int i = 0; i < r - 1 && ok; ++i) ok = sd[i] % f == 0;
+      ok = ok && (reinterpret_cast<uintptr_t>(src) % (unit * f) == 0) &&
+           (reinterpret_cast<uintptr_t>(dst) % (unit * f) == 0);
+      if (!ok) break;
+      sh[r - 1] /= f;
+      for (int i = 0; i < r - 1; ++i) sd[i] /= f;
+      offset /= f;
+      unit *= f;
+      n /= f;
+    }
+  }
+  CopyDims d;
+  d.rank = r;
+  for (int i = 0; i < r; ++i) {
+    d.shape[i] = sh[i];
+    d.stride[i] = sd[i];
+  }
+  int grid = gridFor(n, 256);
+  switch (unit) {
+  case 1: stridedCopyKernel<uint8_t, SCATTER><<<grid, 256, 0, st>>>(static_cast<const uint8_t *>(in), static_cast<uint8_t *>(out), n, d, offset); break;
+  case 2: stridedCopyKernel<uint16_t, SCATTER><<<grid, 256, 0, st>>>(static_cast<const uint16_t *>(in), static_cast<uint16_t *>(out), n, d, offset); break;
+  case 4: stridedCopyKernel<uint32_t, SCATTER><<<grid, 256, 0, st>>>(static_cast<const uint32_t *>(in), static_cast<uint32_t *>(out), n, d, offset); break;
+  case 8: stridedCopyKernel<uint2, SCATTER><<<grid, 256, 0, st>>>(static_cast<const uint2 *>(in), static_cast<uint2 *>(out), n, d, offset); break;
+  default: stridedCopyKernel<uint4, SCATTER><<<grid, 256, 0, st>>>(static_cast<const uint4 *>(in), static_cast<uint4 *>(out), n, d, offset); break;
+  }
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+// out = x*cos + rotate_half(x)*sin, rotate_half(x) = concat(-x[D/2:], x[:D/2]).
+// One thread handles 8 elements of the first half and the matching 8 of the second half.
+template <typename T>
+__global__ void __launch_bounds__(256) ropeKernel(const T *__restrict__ x, const T *__restrict__ cs,
+                                                  const T *__restrict__ sn, T *__restrict__ out, size_t bh,
+                                                  size_t seq, size_t dim) {
+  constexpr int V = 16 / sizeof(T);
+  size_t half = dim / 2;
+  size_t perRow = half / V;
+  size_t total = bh * seq * perRow;
+  size_t step = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+    size_t c = (i % perRow) * V;
+    size_t row = i / perRow; // (bh, s)
+    size_t s = row % seq;
+    const T *xr = x + row * dim;
+    const T *cr = cs + s * dim;
+    const T *sr = sn + s * dim;
+    Vec16<T> x1 = ldcs16(xr + c), x2 = ldcs16(xr + half + c);
+    Vec16<T> c1 = ldg16(cr + c), c2 = ldg16(cr + half + c);
+    Vec16<T> s1 = ldg16(sr + c), s2 = ldg16(sr + half + c);
+    Vec16<T> o1, o2;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      float a = toF32(x1.v[j]), b = toF32(x2.v[j]);
+      o1.v[j] = fromF32<T>(__fadd_rn(__fmul_rn(a, toF32(c1.v[j])), __fmul_rn(-b, toF32(s1.v[j]))));
+      o2.v[j] = fromF32<T>(__fadd_rn(__fmul_rn(b, toF32(c2.v[j])), __fmul_rn(a, toF32(s2.v[j]))));
+    }
+    stcs16(out + row * dim + c, o1);
+    stcs16(out + row * dim + half + c, o2);
+  }
+}
+
+} // namespace ttb
+
+using namespace ttb;
+
+extern "C" {
+
+int ttb_strided_copy(const void *in, void *out, int elem_size, int rank, const int64_t *out_shape,
+                     const int64_t *in_strides, int64_t in_offset, void *stream) {
+  return launchStrided<false>(in, out, elem_size, rank, out_shape, in_strides, in_offset, asStream(stream));
+}
+
+int ttb_strided_scatter(const void *in, void *out, int elem_size, int rank, const int64_t *in_shape,
+                        const int64_t *out_strides, int64_t out_offset, void *stream) {
+  return launchStrided<true>(in, out, elem_size, rank, in_shape, out_strides, out_offset, asStream(stream));
+}
+
+int ttb_rotary_embedding(const void *x, const void *cos, const void *sin, void *out, int dtype, size_t batch_heads,
+                         size_t seq, size_t head_dim, void *stream) {
+  TTB_CHECK(x && cos && sin && out, "null tensor");
+  TTB_CHECK(aligned16(x) && aligned16(cos) && aligned16(sin) && aligned16(out), "tensors must be 16-byte aligned");
+  size_t es = dtypeSize(dtype);
+  TTB_CHECK(es == 2 || es == 4, "rotary embedding needs a float dtype");
+  TTB_CHECK(head_dim % (2 * (16 / es)) == 0, "head_dim/2 must be a multiple of 16 bytes");
+  size_t total = batch_heads * seq * (head_dim / 2 / (16 / es));
+  if (total == 0) return TTB_OK;
+  TTB_DISPATCH_FLOAT(dtype, T, {
+    ropeKernel<T><<<gridFor(total, 256), 256, 0, asStream(stream)>>>(
+        static_cast<const T *>(x), static_cast<const T *>(cos), static_cast<const T *>(sin), static_cast<T *>(out),
+        batch_heads, seq, head_dim);
+  });
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+} // extern "C"

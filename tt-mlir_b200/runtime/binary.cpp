@@ -1,0 +1,318 @@
+// Flatbuffer / Binary: loading, verification and metadata queries for .ttnn files.
+// Counterpart of runtime/lib/binary.cpp in the reference (load :422-460, program I/O
+// descriptors :164-188, goldens :233-253, mesh shape :613-632), on top of this repo's own
+// flatbuffer reader.
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+
+#include "impl.h"
+
+namespace tt::runtime {
+
+using namespace ::tt::runtime::cuda;
+namespace fbt = ::tt::target::ttnn;
+
+// The value the emitter in schema/ttnn_schema.py writes.  The reference's hash is the sha256
+// of flatc's .bfbs output (cmake/modules/BuildFlatbuffers.cmake:54-58), which cannot be
+// produced without flatc; binaries made by the real compiler therefore fail checkSchemaHash()
+// here although their layout is accepted by the verifier.
+static const char *kSchemaHash = "b200-ttnn-schema-v1";
+
+static std::shared_ptr<void> allocBlob(size_t size) {
+  size_t padded = (size + 63) / 64 * 64;
+  void *p = std::aligned_alloc(64, padded ? padded : 64);
+  if (!p) {
+    TTRT_FATAL("out of host memory loading a flatbuffer of ", size, " bytes");
+  }
+  return std::shared_ptr<void>(p, [](void *q) { std::free(q); });
+}
+
+static size_t prefixedSize(const void *buf) { return fb::readScalar<uint32_t>(buf) + 4u; }
+
+static void verifyOrThrow(const uint8_t *buf, size_t size) {
+  if (size < 12) {
+    TTRT_FATAL("flatbuffer too small: ", size, " bytes");
+  }
+  size_t declared = prefixedSize(buf);
+  if (declared > size) {
+    TTRT_FATAL("flatbuffer truncated: size prefix says ", declared, " bytes, got ", size);
+  }
+  if (std::memcmp(buf + 8, "TTNN", 4) != 0) {
+    // Other identifiers (TTM0 TTMetal binaries, TTSY system descriptors) are not executable here.
+    std::string id(reinterpret_cast<const char *>(buf + 8), 4);
+    TTRT_FATAL("unsupported flatbuffer identifier '", id, "': this runtime executes TTNN binaries");
+  }
+  uint32_t rootOff = fb::readScalar<uint32_t>(buf + 4);
+  fb::Verifier v(buf, declared);
+  if (rootOff < 8 || !v.inBounds(buf + 4 + rootOff, 4)) {
+    TTRT_FATAL("flatbuffer root offset out of bounds");
+  }
+  const auto *root = reinterpret_cast<const fbt::TTNNBinary *>(buf + 4 + rootOff);
+  if (!root->verify(v)) {
+    TTRT_FATAL("flatbuffer verification failed: ", v.error());
+  }
+}
+
+Flatbuffer Flatbuffer::loadFromPath(const char *path) {
+  std::ifstream f(path, std::ios::binary | std::ios::ate);
+  if (!f) {
+    TTRT_FATAL("cannot open flatbuffer file ", path);
+  }
+  std::streamsize size = f.tellg();
+  f.seekg(0, std::ios::beg);
+  auto blob = allocBlob(static_cast<size_t>(size));
+  if (size > 0 && !f.read(static_cast<char *>(blob.get()), size)) {
+    TTRT_FATAL("short read on ", path);
+  }
+  verifyOrThrow(static_cast<const uint8_t *>(blob.get()), static_cast<size_t>(size));
+  return Flatbuffer(blob);
+}
+
+Flatbuffer Flatbuffer::loadFromMemory(const void *memory, size_t size) {
+  if (!memory) {
+    TTRT_FATAL("null flatbuffer memory");
+  }
+  auto blob = allocBlob(size);
+  std::memcpy(blob.get(), memory, size);
+  verifyOrThrow(static_cast<const uint8_t *>(blob.get()), size);
+  return Flatbuffer(blob);
+}
+
+size_t Flatbuffer::size() const { return prefixedSize(handle.get()); }
+
+void Flatbuffer::store(const char *path) const {
+  std::ofstream f(path, std::ios::binary);
+  if (!f) {
+    TTRT_FATAL("cannot open ", path, " for writing");
+  }
+  f.write(static_cast<const char *>(handle.get()), static_cast<std::streamsize>(size()));
+}
+
+void Flatbuffer::storeToMemory(std::vector<std::byte> &out) const {
+  out.resize(size());
+  std::memcpy(out.data(), handle.get(), size());
+}
+
+std::string Flatbuffer::getFileIdentifier() const {
+  return std::string(static_cast<const char *>(handle.get()) + 8, 4);
+}
+
+static const fbt::TTNNBinary *rootOf(const void *buf) {
+  const uint8_t *p = static_cast<const uint8_t *>(buf);
+  return reinterpret_cast<const fbt::TTNNBinary *>(p + 4 + fb::readScalar<uint32_t>(p + 4));
+}
+
+std::string Flatbuffer::getVersion() const {
+  const auto *v = rootOf(handle.get())->version();
+  if (!v) {
+    return "0.0.0";
+  }
+  return std::to_string(v->major()) + "." + std::to_string(v->minor()) + "." + std::to_string(v->patch());
+}
+
+std::string Flatbuffer::getSchemaHash() const {
+  const auto *s = rootOf(handle.get())->schema_hash();
+  return s ? s->str() : "";
+}
+
+bool Flatbuffer::checkSchemaHash() const { return getSchemaHash() == kSchemaHash; }
+
+std::string Flatbuffer::getTTMLIRGitHash() const {
+  const auto *s = rootOf(handle.get())->ttmlir_git_hash();
+  return s ? s->str() : "";
+}
+
+// ---- Binary ------------------------------------------------------------------------------
+static std::uint64_t nextBinaryId() {
+  static std::atomic<std::uint64_t> id{0};
+  return id.fetch_add(1);
+}
+
+Binary::Binary(Flatbuffer fb) : Flatbuffer(fb.handle), binaryId(nextBinaryId()) {}
+Binary::Binary(std::shared_ptr<void> handle) : Flatbuffer(std::move(handle)), binaryId(nextBinaryId()) {}
+
+Binary Binary::loadFromPath(const char *path) { return Binary(Flatbuffer::loadFromPath(path)); }
+Binary Binary::loadFromMemory(const void *memory, size_t size) {
+  return Binary(Flatbuffer::loadFromMemory(memory, size));
+}
+
+const fbt::TTNNBinary *Binary::get() const { return rootOf(handle.get()); }
+
+static const fbt::Program *programAt(const Binary &b, uint32_t idx) {
+  const auto *programs = b.get()->programs();
+  if (!programs || idx >= programs->size()) {
+    TTRT_FATAL("program index ", idx, " out of range (binary has ", programs ? programs->size() : 0, ")");
+  }
+  return programs->Get(idx);
+}
+
+std::uint32_t Binary::getNumPrograms() const {
+  const auto *programs = get()->programs();
+  return programs ? programs->size() : 0;
+}
+
+std::string Binary::getProgramName(std::uint32_t i) const {
+  const auto *n = programAt(*this, i)->name();
+  return n ? n->str() : "";
+}
+
+bool Binary::isProgramPrivate(std::uint32_t i) const { return programAt(*this, i)->private_(); }
+
+std::uint32_t Binary::getNumProgramInputs(std::uint32_t i) const {
+  const auto *v = programAt(*this, i)->inputs();
+  return v ? v->size() : 0;
+}
+
+std::uint32_t Binary::getNumProgramOutputs(std::uint32_t i) const {
+  const auto *v = programAt(*this, i)->outputs();
+  return v ? v->size() : 0;
+}
+
+static TensorDesc descOf(const fbt::TensorRef *ref) {
+  TensorDesc d;
+  const auto *td = ref->desc();
+  if (!td) {
+    TTRT_FATAL("TensorRef ", ref->global_id(), " has no descriptor");
+  }
+  if (td->shape()) {
+    for (int32_t s : *td->shape()) d.shape.push_back(static_cast<uint32_t>(s));
+  }
+  if (td->layout() && td->layout()->memory_desc()) {
+    d.dataType = td->layout()->memory_desc()->data_type();
+  }
+  d.stride = denseStrides(d.shape);
+  d.physicalVolume = d.volume();
+  return d;
+}
+
+std::vector<TensorDesc> Binary::getProgramInputs(std::uint32_t i) const {
+  std::vector<TensorDesc> out;
+  if (const auto *v = programAt(*this, i)->inputs()) {
+    for (const auto *ref : *v) out.push_back(descOf(ref));
+  }
+  return out;
+}
+
+std::vector<TensorDesc> Binary::getProgramOutputs(std::uint32_t i) const {
+  std::vector<TensorDesc> out;
+  if (const auto *v = programAt(*this, i)->outputs()) {
+    for (const auto *ref : *v) out.push_back(descOf(ref));
+  }
+  return out;
+}
+
+const std::pair<std::uint32_t, std::uint32_t> Binary::getProgramMeshShape(std::uint32_t i) const {
+  const auto *m = programAt(*this, i)->mesh_shape();
+  if (!m) {
+    return {1, 1};
+  }
+  return {static_cast<uint32_t>(m->y() > 0 ? m->y() : 1), static_cast<uint32_t>(m->x() > 0 ? m->x() : 1)};
+}
+
+std::unordered_map<std::uint32_t, const ::tt::target::GoldenTensor *>
+Binary::getDebugInfoGolden(std::string &loc) const {
+  std::unordered_map<std::uint32_t, const ::tt::target::GoldenTensor *> out;
+  const auto *programs = get()->programs();
+  if (!programs) {
+    return out;
+  }
+  for (const auto *p : *programs) {
+    const auto *dbg = p->debug_info();
+    if (!dbg || !dbg->golden_info() || !dbg->golden_info()->golden_map()) {
+      continue;
+    }
+    for (const auto *kv : *dbg->golden_info()->golden_map()) {
+      if (kv->key() && kv->key()->view() == loc && kv->value()) {
+        for (const auto *dt : *kv->value()) out[dt->device()] = dt->value();
+        return out;
+      }
+    }
+  }
+  return out;
+}
+
+// ---- minimal JSON views (enough for ttrt-style listings; not a reflection dump) ----------
+static std::string jsonEscape(std::string_view s) {
+  std::string o;
+  for (char c : s) {
+    switch (c) {
+    case '"': o += "\\\""; break;
+    case '\\': o += "\\\\"; break;
+    case '\n': o += "\\n"; break;
+    case '\t': o += "\\t"; break;
+    case '\r': o += "\\r"; break;
+    default:
+      if (static_cast<unsigned char>(c) < 0x20) {
+        char b[8];
+        std::snprintf(b, sizeof b, "\\u%04x", c);
+        o += b;
+      } else {
+        o += c;
+      }
+    }
+  }
+  return o;
+}
+
+static std::string descJson(const fbt::TensorRef *ref) {
+  TensorDesc d = descOf(ref);
+  std::string s = "{\"global_id\": " + std::to_string(ref->global_id()) + ", \"shape\": [";
+  for (size_t i = 0; i < d.shape.size(); ++i) s += (i ? ", " : "") + std::to_string(d.shape[i]);
+  s += "], \"data_type\": \"";
+  s += ::tt::target::EnumNameDataType(d.dataType);
+  s += "\"}";
+  return s;
+}
+
+std::string Binary::getProgramInputsAsJson(std::uint32_t i) const {
+  std::string s = "[";
+  if (const auto *v = programAt(*this, i)->inputs()) {
+    for (uint32_t k = 0; k < v->size(); ++k) s += (k ? ", " : "") + descJson(v->Get(k));
+  }
+  return s + "]";
+}
+
+std::string Binary::getProgramOutputsAsJson(std::uint32_t i) const {
+  std::string s = "[";
+  if (const auto *v = programAt(*this, i)->outputs()) {
+    for (uint32_t k = 0; k < v->size(); ++k) s += (k ? ", " : "") + descJson(v->Get(k));
+  }
+  return s + "]";
+}
+
+std::string Binary::getProgramOpsAsJson(std::uint32_t i) const {
+  std::string s = "[";
+  if (const auto *ops = programAt(*this, i)->operations()) {
+    for (uint32_t k = 0; k < ops->size(); ++k) {
+      const auto *op = ops->Get(k);
+      s += k ? ", " : "";
+      s += "{\"type\": \"";
+      s += fbt::EnumNameOpType(op->type_type());
+      s += "\", \"loc_info\": \"" + jsonEscape(op->loc_info() ? op->loc_info()->view() : "") + "\"";
+      s += ", \"debug_info\": \"" + jsonEscape(op->debug_info() ? op->debug_info()->view() : "") + "\"}";
+    }
+  }
+  return s + "]";
+}
+
+std::string Binary::getMlirAsJson() const {
+  const auto *m = get()->mlir();
+  std::string name = m && m->name() ? m->name()->str() : "";
+  std::string src = m && m->source() ? m->source()->str() : "";
+  return "{\"name\": \"" + jsonEscape(name) + "\", \"source\": \"" + jsonEscape(src) + "\"}";
+}
+
+std::string Flatbuffer::asJson() const {
+  Binary b(handle);
+  std::string s = "{\"version\": \"" + getVersion() + "\", \"schema_hash\": \"" + jsonEscape(getSchemaHash()) +
+                  "\", \"ttmlir_git_hash\": \"" + jsonEscape(getTTMLIRGitHash()) + "\", \"programs\": [";
+  for (uint32_t i = 0; i < b.getNumPrograms(); ++i) {
+    s += i ? ", " : "";
+    s += "{\"name\": \"" + jsonEscape(b.getProgramName(i)) + "\", \"inputs\": " + b.getProgramInputsAsJson(i) +
+         ", \"outputs\": " + b.getProgramOutputsAsJson(i) + ", \"operations\": " + b.getProgramOpsAsJson(i) + "}";
+  }
+  return s + "]}";
+}
+
+} // namespace tt::runtime

@@ -1,0 +1,1948 @@
+// Program executor: runs one program of a TTNN binary on a (mesh) device.
+//
+// Counterpart of ProgramExecutor / ProgramTensorPool in the reference
+// (runtime/lib/ttnn/program_executor.cpp:146-266,285-755; runtime/lib/ttnn/types/types.cpp:108-232)
+// with the per-op adapters of runtime/lib/ttnn/operations/** folded in.  Differences that
+// come from the target:
+//   * every op ends in a launch on a CUDA stream (one stream per mesh coordinate) instead of a
+//     call into tt-metal; nothing synchronises until the caller reads a result;
+//   * a peephole pass over the op list fuses chains the flatbuffer spells as separate ops
+//     (quantize->requantize->dequantize, matmul->add->activation, silu*mul, add->rms_norm,
+//     dequantize(weight)->linear) into single launches.  A fused launch keeps the rounding
+//     points of the chain it replaces, so results equal the op-by-op execution bit for bit.
+//     Fusion is off while debug hooks are registered, because callbacks may ask for any
+//     intermediate tensor;
+//   * tilize / untilize and memory-config changes are metadata only.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <unordered_map>
+#include <unordered_set>
+
+#include "impl.h"
+#include "tt/runtime/debug.h"
+#include "tt/runtime/runtime.h"
+
+namespace tt::runtime::cuda {
+
+namespace fbt = ::tt::target::ttnn;
+using fbt::OpType;
+using ::tt::target::TensorLayout;
+
+// ---- static facts about a program, computed once per (binary, program) -----------------------
+struct ProgramInfo {
+  std::unordered_map<uint32_t, uint32_t> useCount; // consumers other than DeallocateOp
+  std::unordered_set<uint32_t> outputs;
+};
+
+static void pushRef(std::vector<const fbt::TensorRef *> &v, const fbt::TensorRef *r) {
+  if (r) v.push_back(r);
+}
+
+static void quantParamRefs(const fbt::EltwiseQuantizationOp *op, std::vector<const fbt::TensorRef *> &ins) {
+  auto scaleRef = [&](fbt::QuantizationScale ty, const void *p) {
+    if (ty == fbt::QuantizationScale::PerAxisScale && p) pushRef(ins, static_cast<const fbt::PerAxisScale *>(p)->scale());
+  };
+  auto zpRef = [&](fbt::QuantizationZeroPoint ty, const void *p) {
+    if (ty == fbt::QuantizationZeroPoint::PerAxisZeroPoint && p)
+      pushRef(ins, static_cast<const fbt::PerAxisZeroPoint *>(p)->zero_point());
+  };
+  if (const auto *qd = op->params_as_QuantizeDequantizeOpParams()) {
+    scaleRef(qd->scale_type(), qd->scale());
+    zpRef(qd->zero_point_type(), qd->zero_point());
+  } else if (const auto *rq = op->params_as_RequantizeOpParams()) {
+    scaleRef(rq->in_scale_type(), rq->in_scale());
+    zpRef(rq->in_zero_point_type(), rq->in_zero_point());
+    scaleRef(rq->out_scale_type(), rq->out_scale());
+    zpRef(rq->out_zero_point_type(), rq->out_zero_point());
+  }
+}
+
+void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *> &ins,
+                   std::vector<const fbt::TensorRef *> &outs) {
+  switch (op->type_type()) {
+#define IN1_OUT(T, inName)                                                               \
+  case OpType::T: {                                                                      \
+    const auto *o = op->type_as_##T();                                                   \
+    pushRef(ins, o->inName());                                                           \
+    pushRef(outs, o->out());                                                             \
+    break;                                                                               \
+  }
+    IN1_OUT(EltwiseUnaryOp, in)
+    IN1_OUT(EltwiseUnaryCompositeOp, in)
+    IN1_OUT(FromDeviceOp, in)
+    IN1_OUT(ToDeviceOp, in)
+    IN1_OUT(ToLayoutOp, in)
+    IN1_OUT(ToMemoryConfigOp, in0)
+    IN1_OUT(TypecastOp, in)
+    IN1_OUT(ReductionOp, in)
+    IN1_OUT(SoftmaxOp, in)
+    IN1_OUT(PermuteOp, in)
+    IN1_OUT(RepeatInterleaveOp, input)
+    IN1_OUT(RepeatOp, in)
+    IN1_OUT(ReshapeOp, in)
+    IN1_OUT(SliceOp, in)
+    IN1_OUT(TransposeOp, in)
+    IN1_OUT(ConcatenateHeadsOp, in)
+    IN1_OUT(AllGatherOp, in)
+    IN1_OUT(AllReduceOp, in)
+    IN1_OUT(ReduceScatterOp, in)
+    IN1_OUT(DistributeTensorOp, in)
+    IN1_OUT(AggregateTensorOp, in)
+    IN1_OUT(MeshPartitionOp, in)
+#undef IN1_OUT
+  case OpType::EltwiseBinaryOp: {
+    const auto *o = op->type_as_EltwiseBinaryOp();
+    pushRef(ins, o->lhs());
+    pushRef(ins, o->rhs());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::EltwiseBinaryCompositeOp: {
+    const auto *o = op->type_as_EltwiseBinaryCompositeOp();
+    pushRef(ins, o->lhs());
+    pushRef(ins, o->rhs());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::EltwiseTernaryWhereOp: {
+    const auto *o = op->type_as_EltwiseTernaryWhereOp();
+    pushRef(ins, o->first());
+    pushRef(ins, o->second());
+    pushRef(ins, o->third());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::EltwiseQuantizationOp: {
+    const auto *o = op->type_as_EltwiseQuantizationOp();
+    pushRef(ins, o->in());
+    quantParamRefs(o, ins);
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::MatmulOp: {
+    const auto *o = op->type_as_MatmulOp();
+    pushRef(ins, o->a());
+    pushRef(ins, o->b());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::LinearOp: {
+    const auto *o = op->type_as_LinearOp();
+    pushRef(ins, o->a());
+    pushRef(ins, o->b());
+    pushRef(ins, o->bias());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::Conv2dOp: {
+    const auto *o = op->type_as_Conv2dOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->weight());
+    pushRef(ins, o->bias());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::RMSNormOp: {
+    const auto *o = op->type_as_RMSNormOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->weight());
+    pushRef(ins, o->bias());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::ConcatOp: {
+    const auto *o = op->type_as_ConcatOp();
+    if (o->inputs()) {
+      for (const auto *r : *o->inputs()) pushRef(ins, r);
+    }
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::RotaryEmbeddingOp: {
+    const auto *o = op->type_as_RotaryEmbeddingOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->cos_cache());
+    pushRef(ins, o->sin_cache());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::ScaledDotProductAttentionOp: {
+    const auto *o = op->type_as_ScaledDotProductAttentionOp();
+    pushRef(ins, o->query());
+    pushRef(ins, o->key());
+    pushRef(ins, o->value());
+    pushRef(ins, o->attention_mask());
+    pushRef(ins, o->attention_sink());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::SplitQueryKeyValueAndSplitHeadsOp: {
+    const auto *o = op->type_as_SplitQueryKeyValueAndSplitHeadsOp();
+    pushRef(ins, o->in());
+    pushRef(ins, o->kv_input());
+    pushRef(outs, o->q_out());
+    pushRef(outs, o->k_out());
+    pushRef(outs, o->v_out());
+    break;
+  }
+  case OpType::DeallocateOp:
+    pushRef(ins, op->type_as_DeallocateOp()->in());
+    break;
+  case OpType::CpuOp: {
+    const auto *o = op->type_as_CpuOp();
+    if (o->ins()) for (const auto *r : *o->ins()) pushRef(ins, r);
+    if (o->outs()) for (const auto *r : *o->outs()) pushRef(outs, r);
+    break;
+  }
+  case OpType::ArangeOp: pushRef(outs, op->type_as_ArangeOp()->out()); break;
+  case OpType::ConstantOp: pushRef(outs, op->type_as_ConstantOp()->out()); break;
+  case OpType::EmptyOp: pushRef(outs, op->type_as_EmptyOp()->out()); break;
+  case OpType::FullOp: pushRef(outs, op->type_as_FullOp()->out()); break;
+  case OpType::NamedFullOp: pushRef(outs, op->type_as_NamedFullOp()->out()); break;
+  default:
+    break;
+  }
+}
+
+static const ProgramInfo &programInfo(const Binary &bin, uint32_t programIndex, const fbt::Program *prog) {
+  static std::mutex m;
+  static std::map<std::pair<const void *, uint32_t>, std::unique_ptr<ProgramInfo>> cache;
+  std::lock_guard<std::mutex> g(m);
+  auto key = std::make_pair(static_cast<const void *>(bin.handle.get()), programIndex);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    return *it->second;
+  }
+  auto info = std::make_unique<ProgramInfo>();
+  if (prog->outputs()) {
+    for (const auto *r : *prog->outputs()) info->outputs.insert(r->global_id());
+  }
+  if (prog->operations()) {
+    for (const auto *op : *prog->operations()) {
+      if (op->type_type() == OpType::DeallocateOp) continue;
+      std::vector<const fbt::TensorRef *> ins, outs;
+      collectOpRefs(op, ins, outs);
+      for (const auto *r : ins) info->useCount[r->global_id()]++;
+    }
+  }
+  return *cache.emplace(key, std::move(info)).first->second;
+}
+
+// ---- helpers over TensorRef -----------------------------------------------------------------
+static std::vector<uint32_t> refShape(const fbt::TensorRef *ref) {
+  std::vector<uint32_t> s;
+  TTRT_ASSERT(ref && ref->desc(), "tensor ref has no descriptor");
+  if (ref->desc()->shape()) {
+    for (int32_t d : *ref->desc()->shape()) {
+      TTRT_ASSERT(d >= 0, "negative dimension in tensor ", ref->global_id());
+      s.push_back(static_cast<uint32_t>(d));
+    }
+  }
+  return s;
+}
+
+static DataType refDtype(const fbt::TensorRef *ref) {
+  TTRT_ASSERT(ref && ref->desc() && ref->desc()->layout() && ref->desc()->layout()->memory_desc(),
+              "tensor ref has no memory descriptor");
+  return ref->desc()->layout()->memory_desc()->data_type();
+}
+
+static bool refOnDevice(const fbt::TensorRef *ref) {
+  return ref->desc()->layout()->memory_desc()->storage_type() == fbt::StorageType::Device;
+}
+
+static TensorLayout refLayout(const fbt::TensorRef *ref) {
+  const auto *ts = ref->desc()->layout()->memory_desc()->tile_shape();
+  return (ts && ts->y() == 32 && ts->x() == 32) ? TensorLayout::Tile : TensorLayout::RowMajor;
+}
+
+static int normDim(int64_t d, size_t rank) {
+  int64_t r = static_cast<int64_t>(rank);
+  if (d < 0) d += r;
+  TTRT_ASSERT(d >= 0 && d < std::max<int64_t>(r, 1), "dimension ", d, " out of range for rank ", rank);
+  return static_cast<int>(d);
+}
+
+static size_t prod(const std::vector<uint32_t> &s, size_t from, size_t to) {
+  size_t v = 1;
+  for (size_t i = from; i < to && i < s.size(); ++i) v *= s[i];
+  return v;
+}
+
+static float numberValue(fbt::NumberType ty, const void *p) {
+  if (ty == fbt::NumberType::FP) return static_cast<const fbt::FloatingPointType *>(p)->value();
+  if (ty == fbt::NumberType::I32) return static_cast<float>(static_cast<const fbt::IntegralType *>(p)->value());
+  return 0.0f;
+}
+
+static int activationCode(const fb::String *s) {
+  if (!s || s->size() == 0) return TTB_ACT_NONE;
+  std::string_view v = s->view();
+  if (v == "relu") return TTB_ACT_RELU;
+  if (v == "silu") return TTB_ACT_SILU;
+  if (v == "gelu") return TTB_ACT_GELU;
+  if (v == "sigmoid") return TTB_ACT_SIGMOID;
+  TTRT_FATAL("unsupported fused activation '", std::string(v), "'");
+}
+
+// ---- the executor -----------------------------------------------------------------------------
+struct ProgramContextImpl;
+
+class Executor {
+public:
+  Executor(std::shared_ptr<DeviceImpl> dev, Binary &bin, uint32_t programIndex, std::vector<Tensor> &inputs);
+  std::vector<Tensor> run();
+
+  // used by the hook API
+  std::unordered_map<uint32_t, TensorPtr> pool;
+  uint32_t programIndex;
+  std::shared_ptr<DeviceImpl> dev;
+
+private:
+  Binary &bin;
+  const fbt::Program *prog = nullptr;
+  const ProgramInfo *info = nullptr;
+  bool fuse = true;
+
+  TensorPtr get(const fbt::TensorRef *ref);
+  TensorPtr getDevice(const fbt::TensorRef *ref); // uploads a host tensor if an op needs it on device
+  void put(const fbt::TensorRef *ref, TensorPtr t);
+  TensorPtr allocOut(const fbt::TensorRef *ref);
+  bool singleUse(const fbt::TensorRef *ref) const;
+  template <typename F> void eachRank(F &&f);
+
+  size_t runOp(size_t i); // returns the number of ops consumed
+  // Next op at or after `from` that is not a DeallocateOp; records the skipped deallocations.
+  const fbt::Operation *peek(size_t &idx, std::vector<const fbt::Operation *> &skipped) const;
+  void runDeallocs(const std::vector<const fbt::Operation *> &ops);
+
+  // fused forms; return ops consumed or 0 when the pattern does not apply
+  size_t tryQuantChain(size_t i);
+  size_t tryGemmEpilogue(size_t i);
+  size_t trySiluMul(size_t i);
+  size_t tryAddRmsNorm(size_t i);
+
+  void runGetDevice(const fbt::GetDeviceOp *op);
+  void runToDevice(const fbt::ToDeviceOp *op);
+  void runFromDevice(const fbt::FromDeviceOp *op);
+  void runToLayout(const fbt::ToLayoutOp *op);
+  void runToMemoryConfig(const fbt::ToMemoryConfigOp *op);
+  void runTypecast(const fbt::TypecastOp *op);
+  void runDeallocate(const fbt::DeallocateOp *op);
+  void runFull(const fbt::FullOp *op);
+  void runNamedFull(const fbt::NamedFullOp *op);
+  void runConstant(const fbt::ConstantOp *op);
+  void runEmpty(const fbt::EmptyOp *op);
+  void runArange(const fbt::ArangeOp *op);
+  void runUnary(const fbt::EltwiseUnaryOp *op);
+  void runUnaryComposite(const fbt::EltwiseUnaryCompositeOp *op);
+  void runBinary(int opCode, const fbt::TensorRef *lhs, const fbt::TensorRef *rhs, const fbt::TensorRef *out);
+  void runWhere(const fbt::EltwiseTernaryWhereOp *op);
+  void runQuantization(const fbt::EltwiseQuantizationOp *op);
+  void runGemm(const fbt::TensorRef *a, const fbt::TensorRef *b, const fbt::TensorRef *bias, const fbt::TensorRef *out,
+               bool ta, bool tb, int act, int roundSteps);
+  void runConv2d(const fbt::Conv2dOp *op);
+  void runSoftmax(const fbt::SoftmaxOp *op);
+  void runRmsNorm(const fbt::RMSNormOp *op);
+  void runReduction(const fbt::ReductionOp *op);
+  void runReshape(const fbt::ReshapeOp *op);
+  void runPermute(const fbt::TensorRef *in, const std::vector<int> &perm, const fbt::TensorRef *out);
+  void runConcat(const fbt::ConcatOp *op);
+  void runSlice(const fbt::SliceOp *op);
+  void runRepeat(const fbt::RepeatOp *op);
+  void runRepeatInterleave(const fbt::RepeatInterleaveOp *op);
+  void runConcatenateHeads(const fbt::ConcatenateHeadsOp *op);
+  void runSplitQkv(const fbt::SplitQueryKeyValueAndSplitHeadsOp *op);
+  void runRotaryEmbedding(const fbt::RotaryEmbeddingOp *op);
+  void runSdpa(const fbt::ScaledDotProductAttentionOp *op);
+  void runAllReduce(const fbt::AllReduceOp *op);
+  void runAllGather(const fbt::AllGatherOp *op);
+  void runReduceScatter(const fbt::ReduceScatterOp *op);
+  void runMeshPartition(const fbt::MeshPartitionOp *op);
+  void runDistribute(const fbt::DistributeTensorOp *op);
+  void runAggregate(const fbt::AggregateTensorOp *op);
+
+  // gather-copy of a strided view of `in` into a new dense tensor shaped like `outShape`
+  TensorPtr stridedView(const TensorPtr &in, const std::vector<uint32_t> &outShape, const std::vector<int64_t> &inStrides,
+                        int64_t offset, DataType dt);
+  uint32_t meshAxisSize(uint32_t clusterAxis) const;
+};
+
+struct ProgramContextImpl {
+  Executor *executor;
+};
+
+Executor::Executor(std::shared_ptr<DeviceImpl> d, Binary &b, uint32_t pi, std::vector<Tensor> &inputs)
+    : programIndex(pi), dev(std::move(d)), bin(b) {
+  const auto *programs = bin.get()->programs();
+  TTRT_ASSERT(programs && programIndex < programs->size(), "program index ", programIndex, " out of range");
+  prog = programs->Get(programIndex);
+  info = &programInfo(bin, programIndex, prog);
+  const auto &hooks = debug::Hooks::get();
+  fuse = !debug::Env::get().disableFusion && !hooks.getPreOperatorCallback() && !hooks.getPostOperatorCallback();
+
+  auto mesh = bin.getProgramMeshShape(programIndex);
+  TTRT_ASSERT(mesh.first * mesh.second == dev->worldSize, "program was compiled for a ", mesh.first, "x", mesh.second,
+              " mesh but the device has ", dev->worldSize, " chips");
+  if (prog->dylibs() && prog->dylibs()->size() > 0) {
+    logDebug("program embeds CPU dylibs; CpuOp is rejected by this target");
+  }
+  uint32_t nIn = prog->inputs() ? prog->inputs()->size() : 0;
+  TTRT_ASSERT(inputs.size() == nIn, "program expects ", nIn, " inputs, got ", inputs.size());
+  for (uint32_t i = 0; i < nIn; ++i) {
+    const auto *ref = prog->inputs()->Get(i);
+    TensorPtr t = unwrapTensor(inputs[i]);
+    TTRT_ASSERT(t->allocated(), "input ", i, " has been deallocated");
+    std::vector<uint32_t> want = refShape(ref);
+    TTRT_ASSERT(t->volume() == prod(want, 0, want.size()), "input ", i, " has ", t->volume(), " elements, program expects ",
+                prod(want, 0, want.size()));
+    if (refOnDevice(ref) && t->storage == Storage::Host) {
+      // The reference requires callers to run toLayout first; accepting a host tensor here
+      // and uploading it is a convenience and costs one copy per submit.
+      t = toDevice(t, dev, refDtype(ref));
+    }
+    TTRT_ASSERT(t->dtype == refDtype(ref), "input ", i, " has data type ", dataTypeName(t->dtype), ", program expects ",
+                dataTypeName(refDtype(ref)));
+    if (t->shape != want) {
+      // same volume, different view (for example a flattened activation)
+      auto view = std::make_shared<TensorImpl>();
+      view->shape = want;
+      view->stride = denseStrides(want);
+      view->dtype = t->dtype;
+      view->storage = t->storage;
+      view->layout = t->layout;
+      view->shards = t->shards;
+      view->device = t->device;
+      view->retain = true;
+      t = view;
+    }
+    pool[ref->global_id()] = t;
+  }
+}
+
+template <typename F> void Executor::eachRank(F &&f) {
+  for (size_t i = 0; i < dev->locals.size(); ++i) {
+    const RankCtx &r = dev->locals[i];
+    if (dev->locals.size() > 1 || i == 0) {
+      TTB_CALL(ttb_set_device(r.cudaDevice));
+    }
+    f(i, r);
+  }
+}
+
+TensorPtr Executor::get(const fbt::TensorRef *ref) {
+  TTRT_ASSERT(ref != nullptr, "missing tensor operand");
+  auto it = pool.find(ref->global_id());
+  TTRT_ASSERT(it != pool.end(), "tensor ", ref->global_id(), " is not live (used before definition or after deallocation)");
+  TTRT_ASSERT(it->second->allocated(), "tensor ", ref->global_id(), " has been deallocated");
+  return it->second;
+}
+
+TensorPtr Executor::getDevice(const fbt::TensorRef *ref) {
+  TensorPtr t = get(ref);
+  if (t->storage == Storage::Host) {
+    t = toDevice(t, dev, t->dtype);
+    pool[ref->global_id()] = t;
+  }
+  return t;
+}
+
+void Executor::put(const fbt::TensorRef *ref, TensorPtr t) {
+  TTRT_ASSERT(ref != nullptr, "op has no output ref");
+  pool[ref->global_id()] = std::move(t);
+}
+
+TensorPtr Executor::allocOut(const fbt::TensorRef *ref) {
+  auto t = makeDeviceTensor(dev, refShape(ref), refDtype(ref));
+  t->layout = refLayout(ref);
+  return t;
+}
+
+bool Executor::singleUse(const fbt::TensorRef *ref) const {
+  uint32_t id = ref->global_id();
+  auto it = info->useCount.find(id);
+  return (it != info->useCount.end() && it->second == 1) && !info->outputs.count(id);
+}
+
+const fbt::Operation *Executor::peek(size_t &idx, std::vector<const fbt::Operation *> &skipped) const {
+  const auto *ops = prog->operations();
+  while (idx < ops->size() && ops->Get(idx)->type_type() == OpType::DeallocateOp) {
+    skipped.push_back(ops->Get(idx));
+    ++idx;
+  }
+  return idx < ops->size() ? ops->Get(idx) : nullptr;
+}
+
+void Executor::runDeallocs(const std::vector<const fbt::Operation *> &ops) {
+  for (const auto *op : ops) {
+    const auto *d = op->type_as_DeallocateOp();
+    // Inside a fused chain an intermediate may never have been materialised.
+    if (d->in() && pool.count(d->in()->global_id())) runDeallocate(d);
+  }
+}
+
+std::vector<Tensor> Executor::run() {
+  const auto &hooks = debug::Hooks::get();
+  auto ctxImpl = std::make_shared<ProgramContextImpl>();
+  ctxImpl->executor = this;
+  CallbackContext cbCtx(std::static_pointer_cast<void>(ctxImpl), DeviceRuntime::CUDA);
+  if (hooks.getpreProgramCallback()) (*hooks.getpreProgramCallback())(bin, cbCtx);
+
+  const auto *ops = prog->operations();
+  size_t n = ops ? ops->size() : 0;
+  bool syncAfterOp = debug::Env::get().syncAfterOp;
+  for (size_t i = 0; i < n;) {
+    const auto *op = ops->Get(static_cast<uint32_t>(i));
+    std::shared_ptr<OpContextImpl> opCtxImpl;
+    if (hooks.getPreOperatorCallback() || hooks.getPostOperatorCallback()) {
+      opCtxImpl = std::make_shared<OpContextImpl>();
+      opCtxImpl->op = op;
+    }
+    if (hooks.getPreOperatorCallback()) {
+      (*hooks.getPreOperatorCallback())(bin, cbCtx, OpContext(std::static_pointer_cast<void>(opCtxImpl), DeviceRuntime::CUDA));
+    }
+    size_t used;
+    try {
+      used = runOp(i);
+    } catch (const std::runtime_error &e) {
+      std::string loc = op->loc_info() ? op->loc_info()->str() : "";
+      throw std::runtime_error(std::string(e.what()) + " [while executing op #" + std::to_string(i) + " " +
+                               fbt::EnumNameOpType(op->type_type()) + (loc.empty() ? "" : " at " + loc) + "]");
+    }
+    if (syncAfterOp) {
+      eachRank([&](size_t, const RankCtx &r) { TTB_CALL(ttb_stream_sync(r.stream)); });
+    }
+    if (hooks.getPostOperatorCallback()) {
+      (*hooks.getPostOperatorCallback())(bin, cbCtx, OpContext(std::static_pointer_cast<void>(opCtxImpl), DeviceRuntime::CUDA));
+    }
+    i += used;
+  }
+
+  std::vector<Tensor> outs;
+  if (prog->outputs()) {
+    for (const auto *ref : *prog->outputs()) {
+      TensorPtr t = get(ref);
+      outs.push_back(wrapTensor(t));
+    }
+  }
+  if (hooks.getpostProgramCallback()) (*hooks.getpostProgramCallback())(bin, cbCtx);
+  return outs;
+}
+
+size_t Executor::runOp(size_t i) {
+  const auto *op = prog->operations()->Get(static_cast<uint32_t>(i));
+  if (fuse) {
+    size_t used = 0;
+    switch (op->type_type()) {
+    case OpType::EltwiseQuantizationOp: used = tryQuantChain(i); break;
+    case OpType::MatmulOp:
+    case OpType::LinearOp: used = tryGemmEpilogue(i); break;
+    case OpType::EltwiseUnaryOp: used = trySiluMul(i); break;
+    case OpType::EltwiseBinaryOp: used = tryAddRmsNorm(i); break;
+    default: break;
+    }
+    if (used) return used;
+  }
+  switch (op->type_type()) {
+  case OpType::GetDeviceOp: runGetDevice(op->type_as_GetDeviceOp()); break;
+  case OpType::ToDeviceOp: runToDevice(op->type_as_ToDeviceOp()); break;
+  case OpType::FromDeviceOp: runFromDevice(op->type_as_FromDeviceOp()); break;
+  case OpType::ToLayoutOp: runToLayout(op->type_as_ToLayoutOp()); break;
+  case OpType::ToMemoryConfigOp: runToMemoryConfig(op->type_as_ToMemoryConfigOp()); break;
+  case OpType::TypecastOp: runTypecast(op->type_as_TypecastOp()); break;
+  case OpType::DeallocateOp: runDeallocate(op->type_as_DeallocateOp()); break;
+  case OpType::FullOp: runFull(op->type_as_FullOp()); break;
+  case OpType::NamedFullOp: runNamedFull(op->type_as_NamedFullOp()); break;
+  case OpType::ConstantOp: runConstant(op->type_as_ConstantOp()); break;
+  case OpType::EmptyOp: runEmpty(op->type_as_EmptyOp()); break;
+  case OpType::ArangeOp: runArange(op->type_as_ArangeOp()); break;
+  case OpType::EltwiseUnaryOp: runUnary(op->type_as_EltwiseUnaryOp()); break;
+  case OpType::EltwiseUnaryCompositeOp: runUnaryComposite(op->type_as_EltwiseUnaryCompositeOp()); break;
+  case OpType::EltwiseBinaryOp: {
+    const auto *o = op->type_as_EltwiseBinaryOp();
+    runBinary(static_cast<int>(o->type()), o->lhs(), o->rhs(), o->out());
+    break;
+  }
+  case OpType::EltwiseBinaryCompositeOp: {
+    const auto *o = op->type_as_EltwiseBinaryCompositeOp();
+    runBinary(TTB_BINARY_COMPOSITE_BASE + static_cast<int>(o->type()), o->lhs(), o->rhs(), o->out());
+    break;
+  }
+  case OpType::EltwiseTernaryWhereOp: runWhere(op->type_as_EltwiseTernaryWhereOp()); break;
+  case OpType::EltwiseQuantizationOp: runQuantization(op->type_as_EltwiseQuantizationOp()); break;
+  case OpType::MatmulOp: {
+    const auto *o = op->type_as_MatmulOp();
+    runGemm(o->a(), o->b(), nullptr, o->out(), o->transpose_a(), o->transpose_b(), activationCode(o->activation()), 0);
+    break;
+  }
+  case OpType::LinearOp: {
+    const auto *o = op->type_as_LinearOp();
+    runGemm(o->a(), o->b(), o->bias(), o->out(), o->transpose_a(), o->transpose_b(), activationCode(o->activation()), 0);
+    break;
+  }
+  case OpType::Conv2dOp: runConv2d(op->type_as_Conv2dOp()); break;
+  case OpType::SoftmaxOp: runSoftmax(op->type_as_SoftmaxOp()); break;
+  case OpType::RMSNormOp: runRmsNorm(op->type_as_RMSNormOp()); break;
+  case OpType::ReductionOp: runReduction(op->type_as_ReductionOp()); break;
+  case OpType::ReshapeOp: runReshape(op->type_as_ReshapeOp()); break;
+  case OpType::PermuteOp: {
+    const auto *o = op->type_as_PermuteOp();
+    std::vector<int> perm;
+    TTRT_ASSERT(o->permutation(), "permute without permutation");
+    for (int64_t p : *o->permutation()) perm.push_back(static_cast<int>(p));
+    runPermute(o->in(), perm, o->out());
+    break;
+  }
+  case OpType::TransposeOp: {
+    const auto *o = op->type_as_TransposeOp();
+    size_t rank = refShape(o->in()).size();
+    std::vector<int> perm(rank);
+    for (size_t k = 0; k < rank; ++k) perm[k] = static_cast<int>(k);
+    std::swap(perm[normDim(o->dim0(), rank)], perm[normDim(o->dim1(), rank)]);
+    runPermute(o->in(), perm, o->out());
+    break;
+  }
+  case OpType::ConcatOp: runConcat(op->type_as_ConcatOp()); break;
+  case OpType::SliceOp: runSlice(op->type_as_SliceOp()); break;
+  case OpType::RepeatOp: runRepeat(op->type_as_RepeatOp()); break;
+  case OpType::RepeatInterleaveOp: runRepeatInterleave(op->type_as_RepeatInterleaveOp()); break;
+  case OpType::ConcatenateHeadsOp: runConcatenateHeads(op->type_as_ConcatenateHeadsOp()); break;
+  case OpType::SplitQueryKeyValueAndSplitHeadsOp: runSplitQkv(op->type_as_SplitQueryKeyValueAndSplitHeadsOp()); break;
+  case OpType::RotaryEmbeddingOp: runRotaryEmbedding(op->type_as_RotaryEmbeddingOp()); break;
+  case OpType::ScaledDotProductAttentionOp: runSdpa(op->type_as_ScaledDotProductAttentionOp()); break;
+  case OpType::AllReduceOp: runAllReduce(op->type_as_AllReduceOp()); break;
+  case OpType::AllGatherOp: runAllGather(op->type_as_AllGatherOp()); break;
+  case OpType::ReduceScatterOp: runReduceScatter(op->type_as_ReduceScatterOp()); break;
+  case OpType::MeshPartitionOp: runMeshPartition(op->type_as_MeshPartitionOp()); break;
+  case OpType::DistributeTensorOp: runDistribute(op->type_as_DistributeTensorOp()); break;
+  case OpType::AggregateTensorOp: runAggregate(op->type_as_AggregateTensorOp()); break;
+  case OpType::CpuOp:
+    TTRT_FATAL("CpuOp '", op->type_as_CpuOp()->func_name() ? op->type_as_CpuOp()->func_name()->str() : "",
+               "': CPU-hoisted functions are not executed by this target (no CPU fallback); recompile the graph "
+               "without CPU hoisting");
+  default:
+    TTRT_FATAL("unsupported operation ", fbt::EnumNameOpType(op->type_type()));
+  }
+  return 1;
+}
+
+// ---- layout / lifetime ops ----------------------------------------------------------------------
+void Executor::runGetDevice(const fbt::GetDeviceOp *op) {
+  if (const auto *m = op->mesh()) {
+    uint32_t vol = static_cast<uint32_t>(std::max(m->y(), 1) * std::max(m->x(), 1));
+    TTRT_ASSERT(vol == dev->worldSize || vol == 1, "GetDeviceOp asks for a ", m->y(), "x", m->x(), " mesh, device has ",
+                dev->worldSize, " chips");
+  }
+}
+
+void Executor::runToDevice(const fbt::ToDeviceOp *op) {
+  TensorPtr in = get(op->in());
+  TensorPtr out = in->storage == Storage::Host ? toDevice(in, dev, in->dtype) : in;
+  put(op->out(), out);
+}
+
+void Executor::runFromDevice(const fbt::FromDeviceOp *op) {
+  TensorPtr in = get(op->in());
+  put(op->out(), in->storage == Storage::Device ? toHostTensor(in, true) : in);
+}
+
+void Executor::runToLayout(const fbt::ToLayoutOp *op) {
+  TensorPtr in = get(op->in());
+  DataType dt = op->dtype().value_or(in->dtype);
+  TensorPtr out = in;
+  if (in->storage == Storage::Host && refOnDevice(op->out())) {
+    out = toDevice(in, dev, dt);
+  } else if (in->storage == Storage::Device && dt != in->dtype) {
+    out = castOnDevice(in, dt);
+  } else if (in->storage == Storage::Device && !refOnDevice(op->out())) {
+    out = toHostTensor(in, true);
+  }
+  if (out == in) {
+    // Tilize / untilize only: new handle, same memory.
+    auto alias = std::make_shared<TensorImpl>();
+    alias->shape = in->shape;
+    alias->stride = in->stride;
+    alias->dtype = in->dtype;
+    alias->storage = in->storage;
+    alias->shards = in->shards;
+    alias->device = in->device;
+    out = alias;
+  }
+  out->layout = op->layout();
+  put(op->out(), out);
+}
+
+void Executor::runToMemoryConfig(const fbt::ToMemoryConfigOp *op) {
+  // DRAM / L1 / sharding choices have no meaning in HBM: the output aliases the input.
+  put(op->out(), get(op->in0()));
+}
+
+void Executor::runTypecast(const fbt::TypecastOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = castOnDevice(in, op->dtype());
+  if (out == in) {
+    auto alias = std::make_shared<TensorImpl>();
+    alias->shape = in->shape;
+    alias->stride = in->stride;
+    alias->dtype = in->dtype;
+    alias->storage = in->storage;
+    alias->layout = in->layout;
+    alias->shards = in->shards;
+    alias->device = in->device;
+    out = alias;
+  }
+  put(op->out(), out);
+}
+
+void Executor::runDeallocate(const fbt::DeallocateOp *op) {
+  TTRT_ASSERT(op->in() != nullptr, "DeallocateOp without operand");
+  auto it = pool.find(op->in()->global_id());
+  if (it == pool.end()) {
+    return;
+  }
+  // Retained tensors survive program deallocations (reference: operations/deletion/deallocate.cpp).
+  if (!it->second->retain || op->force()) {
+    pool.erase(it);
+  }
+}
+
+// ---- creation ops -------------------------------------------------------------------------------
+void Executor::runFull(const fbt::FullOp *op) {
+  TensorPtr out = allocOut(op->out());
+  double v = numberValue(op->fill_value_type(), op->fill_value());
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_fill(out->shards[i]->ptr, ttbDtype(out->dtype), out->volume(), v, r.stream));
+  });
+  put(op->out(), out);
+}
+
+void Executor::runNamedFull(const fbt::NamedFullOp *op) {
+  TensorPtr out = allocOut(op->out());
+  double v = op->type() == fbt::NamedFullOpType::Ones ? 1.0 : 0.0;
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_fill(out->shards[i]->ptr, ttbDtype(out->dtype), out->volume(), v, r.stream));
+  });
+  put(op->out(), out);
+}
+
+void Executor::runConstant(const fbt::ConstantOp *op) {
+  TTRT_ASSERT(op->input() != nullptr, "ConstantOp without data");
+  std::vector<uint32_t> shape = refShape(op->out());
+  DataType inDt = op->input_dtype();
+  size_t vol = prod(shape, 0, shape.size());
+  TTRT_ASSERT(op->input()->size() == vol * dataTypeSize(inDt), "ConstantOp data has ", op->input()->size(),
+              " bytes, expected ", vol * dataTypeSize(inDt));
+  auto host = std::make_shared<TensorImpl>();
+  host->shape = shape;
+  host->stride = denseStrides(shape);
+  host->dtype = inDt;
+  host->storage = Storage::Host;
+  auto buf = std::make_shared<Buffer>();
+  buf->ptr = const_cast<uint8_t *>(op->input()->data());
+  buf->bytes = op->input()->size();
+  buf->kind = Buffer::Kind::Borrowed;
+  buf->keepAlive = bin.handle;
+  host->shards.push_back(buf);
+  if (refOnDevice(op->out())) {
+    TensorPtr out = toDevice(host, dev, refDtype(op->out()));
+    out->layout = refLayout(op->out());
+    put(op->out(), out);
+  } else {
+    put(op->out(), host);
+  }
+}
+
+void Executor::runEmpty(const fbt::EmptyOp *op) { put(op->out(), allocOut(op->out())); }
+
+void Executor::runArange(const fbt::ArangeOp *op) {
+  TensorPtr out = allocOut(op->out());
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_arange(out->shards[i]->ptr, ttbDtype(out->dtype), out->volume(), op->start(), op->step(), r.stream));
+  });
+  put(op->out(), out);
+}
+
+// ---- elementwise ----------------------------------------------------------------------------------
+void Executor::runUnary(const fbt::EltwiseUnaryOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(in->volume() == out->volume(), "unary op changes the element count");
+  float param = 0.0f;
+  if (const auto *p = op->params_as_EltwiseOpWithFloatParams()) param = p->parameter();
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_eltwise_unary(static_cast<int>(op->type()), in->shards[i]->ptr, ttbDtype(in->dtype),
+                               out->shards[i]->ptr, ttbDtype(out->dtype), out->volume(), param, r.stream));
+  });
+  put(op->out(), out);
+}
+
+void Executor::runUnaryComposite(const fbt::EltwiseUnaryCompositeOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = allocOut(op->out());
+  using T = fbt::EltwiseUnaryCompositeOpType;
+  switch (op->type()) {
+  case T::ClampScalar: {
+    const auto *p = op->params_as_ClampScalarOpParams();
+    TTRT_ASSERT(p != nullptr, "clamp without bounds");
+    float lo = numberValue(p->min_type(), p->min()), hi = numberValue(p->max_type(), p->max());
+    TTRT_ASSERT(in->dtype == out->dtype, "clamp changes the data type");
+    eachRank([&](size_t i, const RankCtx &r) {
+      TTB_CALL(ttb_clamp(in->shards[i]->ptr, ttbDtype(in->dtype), out->shards[i]->ptr, out->volume(), lo, hi, r.stream));
+    });
+    break;
+  }
+  case T::Cbrt:
+  case T::Log1p: {
+    int code = op->type() == T::Cbrt ? 200 : 201;
+    eachRank([&](size_t i, const RankCtx &r) {
+      TTB_CALL(ttb_eltwise_unary(code, in->shards[i]->ptr, ttbDtype(in->dtype), out->shards[i]->ptr,
+                                 ttbDtype(out->dtype), out->volume(), 0.0f, r.stream));
+    });
+    break;
+  }
+  default:
+    TTRT_FATAL("unsupported composite unary op ", static_cast<int>(op->type()));
+  }
+  put(op->out(), out);
+}
+
+// numpy-style broadcast strides of `shape` against `outShape` (right aligned, in elements)
+static std::vector<int64_t> broadcastStrides(const std::vector<uint32_t> &shape, const std::vector<uint32_t> &outShape) {
+  TTRT_ASSERT(shape.size() <= outShape.size(), "operand rank exceeds result rank");
+  std::vector<int64_t> dense = denseStrides(shape);
+  std::vector<int64_t> s(outShape.size(), 0);
+  size_t off = outShape.size() - shape.size();
+  for (size_t i = 0; i < shape.size(); ++i) {
+    if (shape[i] == outShape[off + i]) {
+      s[off + i] = shape[i] == 1 ? 0 : dense[i];
+    } else {
+      TTRT_ASSERT(shape[i] == 1, "shapes do not broadcast");
+      s[off + i] = 0;
+    }
+  }
+  return s;
+}
+
+void Executor::runBinary(int opCode, const fbt::TensorRef *lhsRef, const fbt::TensorRef *rhsRef, const fbt::TensorRef *outRef) {
+  TensorPtr a = getDevice(lhsRef), b = getDevice(rhsRef);
+  TensorPtr out = allocOut(outRef);
+  TTRT_ASSERT(out->shape.size() <= 8, "rank above 8");
+  std::vector<int64_t> sa = broadcastStrides(a->shape, out->shape), sb = broadcastStrides(b->shape, out->shape);
+  std::vector<int64_t> shape(out->shape.begin(), out->shape.end());
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_eltwise_binary(opCode, a->shards[i]->ptr, ttbDtype(a->dtype), b->shards[i]->ptr, ttbDtype(b->dtype),
+                                out->shards[i]->ptr, ttbDtype(out->dtype), static_cast<int>(shape.size()), shape.data(),
+                                sa.data(), sb.data(), r.stream));
+  });
+  put(outRef, out);
+}
+
+void Executor::runWhere(const fbt::EltwiseTernaryWhereOp *op) {
+  TensorPtr c = getDevice(op->first()), a = getDevice(op->second()), b = getDevice(op->third());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(a->dtype == b->dtype && a->dtype == out->dtype, "where branches must share the result type");
+  std::vector<int64_t> sc = broadcastStrides(c->shape, out->shape), sa = broadcastStrides(a->shape, out->shape),
+                       sb = broadcastStrides(b->shape, out->shape);
+  std::vector<int64_t> shape(out->shape.begin(), out->shape.end());
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_where(c->shards[i]->ptr, ttbDtype(c->dtype), a->shards[i]->ptr, b->shards[i]->ptr, ttbDtype(a->dtype),
+                       out->shards[i]->ptr, static_cast<int>(shape.size()), shape.data(), sc.data(), sa.data(),
+                       sb.data(), r.stream));
+  });
+  put(op->out(), out);
+}
+
+// ---- quantization -----------------------------------------------------------------------------------
+namespace {
+struct QParams {
+  bool perAxis = false;
+  float scale = 1.0f;
+  int32_t zp = 0;
+  const fbt::TensorRef *scaleRef = nullptr;
+  const fbt::TensorRef *zpRef = nullptr;
+};
+
+QParams readQParams(fbt::QuantizationScale sTy, const void *s, fbt::QuantizationZeroPoint zTy, const void *z) {
+  QParams q;
+  if (sTy == fbt::QuantizationScale::PerTensorScale) {
+    q.scale = static_cast<const fbt::PerTensorScale *>(s)->scale();
+  } else if (sTy == fbt::QuantizationScale::PerAxisScale) {
+    q.perAxis = true;
+    q.scaleRef = static_cast<const fbt::PerAxisScale *>(s)->scale();
+  } else {
+    TTRT_FATAL("quantization op without a scale");
+  }
+  if (zTy == fbt::QuantizationZeroPoint::PerTensorZeroPoint) {
+    q.zp = static_cast<const fbt::PerTensorZeroPoint *>(z)->zero_point();
+  } else if (zTy == fbt::QuantizationZeroPoint::PerAxisZeroPoint) {
+    q.zpRef = static_cast<const fbt::PerAxisZeroPoint *>(z)->zero_point();
+  }
+  return q;
+}
+
+// Quantized values live in 32-bit containers when the compiler's default storage width is
+// used (lib/Dialect/TTNN/Pipelines/TTNNPipelines.cpp:349-351); this target then clamps to the
+// int8 range, which is what the graph's !quant.uniform<i8:...> type means.  Set
+// TTB_QUANT_I32_FULL_RANGE=1 for graphs whose quantized type really is 32 bit wide.
+int clampI8ForContainer() {
+  static const int v = [] {
+    const char *e = std::getenv("TTB_QUANT_I32_FULL_RANGE");
+    return (e && e[0] == '1') ? 0 : 1;
+  }();
+  return v;
+}
+} // namespace
+
+void Executor::runQuantization(const fbt::EltwiseQuantizationOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(in->volume() == out->volume(), "quantization op changes the element count");
+  size_t n = out->volume();
+  int clampI8 = clampI8ForContainer();
+  using T = fbt::EltwiseQuantizationOpType;
+  size_t rank = in->shape.size();
+  auto axisSplit = [&](size_t &outer, size_t &len, size_t &inner) {
+    TTRT_ASSERT(op->axis().has_value(), "per-axis quantization without axis");
+    int ax = normDim(*op->axis(), rank);
+    outer = prod(in->shape, 0, ax);
+    len = in->shape[ax];
+    inner = prod(in->shape, ax + 1, rank);
+  };
+  auto f32Param = [&](const fbt::TensorRef *ref, size_t len) {
+    TensorPtr t = castOnDevice(getDevice(ref), DataType::Float32);
+    TTRT_ASSERT(t->volume() == len, "per-axis scale has ", t->volume(), " entries, axis has ", len);
+    return t;
+  };
+  auto i32Param = [&](const fbt::TensorRef *ref, size_t len) -> TensorPtr {
+    if (!ref) return nullptr;
+    TensorPtr t = castOnDevice(getDevice(ref), DataType::Int32);
+    TTRT_ASSERT(t->volume() == len, "per-axis zero point has ", t->volume(), " entries, axis has ", len);
+    return t;
+  };
+  if (op->type() == T::Requantize) {
+    const auto *p = op->params_as_RequantizeOpParams();
+    TTRT_ASSERT(p != nullptr, "requantize without parameters");
+    QParams qi = readQParams(p->in_scale_type(), p->in_scale(), p->in_zero_point_type(), p->in_zero_point());
+    QParams qo = readQParams(p->out_scale_type(), p->out_scale(), p->out_zero_point_type(), p->out_zero_point());
+    if (!qi.perAxis && !qo.perAxis) {
+      eachRank([&](size_t i, const RankCtx &r) {
+        TTB_CALL(ttb_requantize(in->shards[i]->ptr, ttbDtype(in->dtype), out->shards[i]->ptr, ttbDtype(out->dtype), n,
+                                qi.scale, qi.zp, qo.scale, qo.zp, clampI8, r.stream));
+      });
+    } else {
+      TTRT_ASSERT(qi.perAxis && qo.perAxis, "requantize must be per-axis on both sides or on neither");
+      size_t outer, len, inner;
+      axisSplit(outer, len, inner);
+      TensorPtr si = f32Param(qi.scaleRef, len), so = f32Param(qo.scaleRef, len);
+      TensorPtr zi = i32Param(qi.zpRef, len), zo = i32Param(qo.zpRef, len);
+      eachRank([&](size_t i, const RankCtx &r) {
+        TTB_CALL(ttb_requantize_per_axis(in->shards[i]->ptr, ttbDtype(in->dtype), out->shards[i]->ptr,
+                                         ttbDtype(out->dtype), outer, len, inner,
+                                         static_cast<const float *>(si->shards[i]->ptr),
+                                         zi ? static_cast<const int32_t *>(zi->shards[i]->ptr) : nullptr,
+                                         static_cast<const float *>(so->shards[i]->ptr),
+                                         zo ? static_cast<const int32_t *>(zo->shards[i]->ptr) : nullptr, clampI8,
+                                         r.stream));
+      });
+    }
+  } else {
+    const auto *p = op->params_as_QuantizeDequantizeOpParams();
+    TTRT_ASSERT(p != nullptr, "quantize/dequantize without parameters");
+    QParams q = readQParams(p->scale_type(), p->scale(), p->zero_point_type(), p->zero_point());
+    bool isQ = op->type() == T::Quantize;
+    if (!q.perAxis) {
+      eachRank([&](size_t i, const RankCtx &r) {
+        if (isQ) {
+          TTB_CALL(ttb_quantize(in->shards[i]->ptr, ttbDtype(in->dtype), out->shards[i]->ptr, ttbDtype(out->dtype), n,
+                                q.scale, q.zp, clampI8, r.stream));
+        } else {
+          TTB_CALL(ttb_dequantize(in->shards[i]->ptr, ttbDtype(in->dtype), out->shards[i]->ptr, ttbDtype(out->dtype), n,
+                                  q.scale, q.zp, r.stream));
+        }
+      });
+    } else {
+      size_t outer, len, inner;
+      axisSplit(outer, len, inner);
+      TensorPtr s = f32Param(q.scaleRef, len);
+      TensorPtr z = i32Param(q.zpRef, len);
+      eachRank([&](size_t i, const RankCtx &r) {
+        const float *sp = static_cast<const float *>(s->shards[i]->ptr);
+        const int32_t *zp = z ? static_cast<const int32_t *>(z->shards[i]->ptr) : nullptr;
+        if (isQ) {
+          TTB_CALL(ttb_quantize_per_axis(in->shards[i]->ptr, ttbDtype(in->dtype), out->shards[i]->ptr,
+                                         ttbDtype(out->dtype), outer, len, inner, sp, zp, clampI8, r.stream));
+        } else {
+          TTB_CALL(ttb_dequantize_per_axis(in->shards[i]->ptr, ttbDtype(in->dtype), out->shards[i]->ptr,
+                                           ttbDtype(out->dtype), outer, len, inner, sp, zp, r.stream));
+        }
+      });
+    }
+  }
+  put(op->out(), out);
+}
+
+// quantize -> requantize -> dequantize with per-tensor parameters and matching scales.
+size_t Executor::tryQuantChain(size_t i) {
+  const auto *ops = prog->operations();
+  using T = fbt::EltwiseQuantizationOpType;
+  const auto *q = ops->Get(static_cast<uint32_t>(i))->type_as_EltwiseQuantizationOp();
+  if (q->type() != T::Quantize) return 0;
+  std::vector<const fbt::Operation *> deallocs;
+  size_t j = i + 1;
+  const auto *op2 = peek(j, deallocs);
+  if (!op2 || op2->type_type() != OpType::EltwiseQuantizationOp) return 0;
+  const auto *rq = op2->type_as_EltwiseQuantizationOp();
+  if (rq->type() != T::Requantize || rq->in()->global_id() != q->out()->global_id()) return 0;
+  size_t k = j + 1;
+  const auto *op3 = peek(k, deallocs);
+  if (!op3 || op3->type_type() != OpType::EltwiseQuantizationOp) return 0;
+  const auto *dq = op3->type_as_EltwiseQuantizationOp();
+  if (dq->type() != T::Dequantize || dq->in()->global_id() != rq->out()->global_id()) return 0;
+  const auto *pq = q->params_as_QuantizeDequantizeOpParams();
+  const auto *prq = rq->params_as_RequantizeOpParams();
+  const auto *pdq = dq->params_as_QuantizeDequantizeOpParams();
+  if (!pq || !prq || !pdq) return 0;
+  QParams a = readQParams(pq->scale_type(), pq->scale(), pq->zero_point_type(), pq->zero_point());
+  QParams bi = readQParams(prq->in_scale_type(), prq->in_scale(), prq->in_zero_point_type(), prq->in_zero_point());
+  QParams bo = readQParams(prq->out_scale_type(), prq->out_scale(), prq->out_zero_point_type(), prq->out_zero_point());
+  QParams c = readQParams(pdq->scale_type(), pdq->scale(), pdq->zero_point_type(), pdq->zero_point());
+  if (a.perAxis || bi.perAxis || bo.perAxis || c.perAxis) return 0;
+  // the chain must be self-consistent, otherwise run the ops as written
+  if (a.scale != bi.scale || a.zp != bi.zp || bo.scale != c.scale || bo.zp != c.zp) return 0;
+  DataType d1 = refDtype(q->out()), d2 = refDtype(rq->out());
+  if (d1 != d2) return 0;
+  DataType din = refDtype(q->in()), dout = refDtype(dq->out());
+  bool inOk = din == DataType::BFloat16 || din == DataType::Float32;
+  bool outOk = dout == DataType::BFloat16 || dout == DataType::Float32;
+  bool qOk = d1 == DataType::Int32 || d1 == DataType::Int8 || d1 == DataType::UInt8;
+  if (!inOk || !outOk || !qOk) return 0;
+
+  TensorPtr in = getDevice(q->in());
+  // Intermediates are materialised only if something else reads them.
+  bool keep1 = !singleUse(q->out()), keep2 = !singleUse(rq->out());
+  TensorPtr t1 = keep1 ? allocOut(q->out()) : nullptr;
+  TensorPtr t2 = keep2 ? allocOut(rq->out()) : nullptr;
+  TensorPtr out = allocOut(dq->out());
+  size_t n = out->volume();
+  TTRT_ASSERT(in->volume() == n, "quantization chain changes the element count");
+  int clampI8 = clampI8ForContainer();
+  eachRank([&](size_t r_, const RankCtx &r) {
+    TTB_CALL(ttb_quant_chain(in->shards[r_]->ptr, ttbDtype(in->dtype), t1 ? t1->shards[r_]->ptr : nullptr, ttbDtype(d1),
+                             t2 ? t2->shards[r_]->ptr : nullptr, ttbDtype(d2), out->shards[r_]->ptr,
+                             ttbDtype(out->dtype), n, a.scale, a.zp, bo.scale, bo.zp, clampI8, r.stream));
+  });
+  if (t1) put(q->out(), t1);
+  if (t2) put(rq->out(), t2);
+  put(dq->out(), out);
+  runDeallocs(deallocs);
+  return k + 1 - i;
+}
+
+// ---- contractions -------------------------------------------------------------------------------------
+void Executor::runGemm(const fbt::TensorRef *aRef, const fbt::TensorRef *bRef, const fbt::TensorRef *biasRef,
+                       const fbt::TensorRef *outRef, bool ta, bool tb, int act, int roundSteps) {
+  TensorPtr a = getDevice(aRef), b = getDevice(bRef);
+  TensorPtr bias = biasRef ? getDevice(biasRef) : nullptr;
+  TensorPtr out = allocOut(outRef);
+  TTRT_ASSERT(a->dtype == b->dtype, "matmul operands differ in data type: ", dataTypeName(a->dtype), " vs ",
+              dataTypeName(b->dtype));
+  // 1-D operands follow numpy: a vector lhs is a row, a vector rhs is a column.
+  std::vector<uint32_t> as = a->shape, bs = b->shape;
+  if (as.size() == 1) as.insert(as.begin(), 1);
+  if (bs.size() == 1) bs.push_back(1);
+  TTRT_ASSERT(as.size() >= 2 && bs.size() >= 2, "matmul operands need rank >= 1");
+  int64_t M = ta ? as[as.size() - 1] : as[as.size() - 2];
+  int64_t K = ta ? as[as.size() - 2] : as[as.size() - 1];
+  int64_t Kb = tb ? bs[bs.size() - 1] : bs[bs.size() - 2];
+  int64_t N = tb ? bs[bs.size() - 2] : bs[bs.size() - 1];
+  TTRT_ASSERT(K == Kb, "matmul inner dimensions differ: ", K, " vs ", Kb);
+  int64_t aBatch = static_cast<int64_t>(prod(as, 0, as.size() - 2));
+  int64_t bBatch = static_cast<int64_t>(prod(bs, 0, bs.size() - 2));
+  int64_t batch = std::max(aBatch, bBatch);
+  TTRT_ASSERT((aBatch == batch || aBatch == 1) && (bBatch == batch || bBatch == 1), "matmul batch dimensions do not broadcast");
+  int64_t aStride = aBatch == 1 ? 0 : M * K, bStride = bBatch == 1 ? 0 : K * N;
+  // A broadcast rhs with a batched lhs is one big GEMM over the stacked rows.
+  if (bBatch == 1 && aBatch > 1 && !ta) {
+    M *= aBatch;
+    batch = 1;
+    aStride = 0;
+  }
+  TTRT_ASSERT(static_cast<int64_t>(out->volume()) == batch * M * N, "matmul result has ", out->volume(),
+              " elements, expected ", batch * M * N);
+  if (bias) {
+    TTRT_ASSERT(static_cast<int64_t>(bias->volume()) == N, "bias must have N = ", N, " elements, has ", bias->volume());
+  }
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_gemm(a->shards[i]->ptr, b->shards[i]->ptr, bias ? bias->shards[i]->ptr : nullptr, out->shards[i]->ptr,
+                      ttbDtype(a->dtype), bias ? ttbDtype(bias->dtype) : 0, ttbDtype(out->dtype), batch, M, N, K, ta, tb,
+                      aStride, bStride, act, roundSteps, r.stream));
+  });
+  put(outRef, out);
+}
+
+static int unaryToAct(fbt::EltwiseUnaryOpType t) {
+  switch (t) {
+  case fbt::EltwiseUnaryOpType::Relu: return TTB_ACT_RELU;
+  case fbt::EltwiseUnaryOpType::Silu: return TTB_ACT_SILU;
+  case fbt::EltwiseUnaryOpType::Gelu: return TTB_ACT_GELU;
+  case fbt::EltwiseUnaryOpType::Sigmoid: return TTB_ACT_SIGMOID;
+  default: return TTB_ACT_NONE;
+  }
+}
+
+// matmul|linear [-> add(row vector)] [-> relu|silu|gelu|sigmoid], each intermediate single-use.
+size_t Executor::tryGemmEpilogue(size_t i) {
+  const auto *ops = prog->operations();
+  const auto *op = ops->Get(static_cast<uint32_t>(i));
+  const fbt::TensorRef *a, *b, *bias = nullptr, *cur;
+  bool ta, tb;
+  int act;
+  if (op->type_type() == OpType::MatmulOp) {
+    const auto *m = op->type_as_MatmulOp();
+    a = m->a(); b = m->b(); cur = m->out(); ta = m->transpose_a(); tb = m->transpose_b();
+    act = activationCode(m->activation());
+  } else {
+    const auto *l = op->type_as_LinearOp();
+    a = l->a(); b = l->b(); bias = l->bias(); cur = l->out(); ta = l->transpose_a(); tb = l->transpose_b();
+    act = activationCode(l->activation());
+  }
+  if (act != TTB_ACT_NONE) return 0; // already carries its own activation: run as written
+  std::vector<const fbt::Operation *> deallocs;
+  int roundSteps = 0;
+  size_t next = i + 1, consumedUpTo = i;
+  DataType outDt = refDtype(cur);
+  int64_t N = refShape(cur).empty() ? 1 : refShape(cur).back();
+
+  // optional bias add
+  if (!bias && singleUse(cur)) {
+    std::vector<const fbt::Operation *> d2;
+    size_t j = next;
+    const auto *nop = peek(j, d2);
+    if (nop && nop->type_type() == OpType::EltwiseBinaryOp) {
+      const auto *add = nop->type_as_EltwiseBinaryOp();
+      const fbt::TensorRef *other = nullptr;
+      if (add->type() == fbt::EltwiseBinaryOpType::Add) {
+        if (add->lhs()->global_id() == cur->global_id()) other = add->rhs();
+        else if (add->rhs()->global_id() == cur->global_id()) other = add->lhs();
+      }
+      if (other && other->global_id() != cur->global_id() && refShape(add->out()) == refShape(cur) &&
+          refDtype(add->out()) == outDt) {
+        std::vector<uint32_t> os = refShape(other);
+        int64_t vol = static_cast<int64_t>(prod(os, 0, os.size()));
+        if (vol == N && !os.empty() && os.back() == N && pool.count(other->global_id())) {
+          bias = other;
+          roundSteps |= 1; // the matmul op stored a rounded product before the add read it
+          cur = add->out();
+          deallocs.insert(deallocs.end(), d2.begin(), d2.end());
+          next = j + 1;
+          consumedUpTo = j;
+        }
+      }
+    }
+  }
+  // optional activation
+  if (singleUse(cur)) {
+    std::vector<const fbt::Operation *> d2;
+    size_t j = next;
+    const auto *nop = peek(j, d2);
+    if (nop && nop->type_type() == OpType::EltwiseUnaryOp) {
+      const auto *u = nop->type_as_EltwiseUnaryOp();
+      int code = unaryToAct(u->type());
+      if (code != TTB_ACT_NONE && u->in()->global_id() == cur->global_id() && refShape(u->out()) == refShape(cur) &&
+          refDtype(u->out()) == outDt) {
+        act = code;
+        roundSteps |= bias ? 2 : 1; // whatever op fed the activation stored a rounded value
+        cur = u->out();
+        deallocs.insert(deallocs.end(), d2.begin(), d2.end());
+        next = j + 1;
+        consumedUpTo = j;
+      }
+    }
+  }
+  if (consumedUpTo == i) return 0;
+  runGemm(a, b, bias, cur, ta, tb, act, roundSteps);
+  runDeallocs(deallocs);
+  return consumedUpTo + 1 - i;
+}
+
+void Executor::runConv2d(const fbt::Conv2dOp *op) {
+  TensorPtr x = getDevice(op->input()), w = getDevice(op->weight());
+  TensorPtr bias = op->bias() ? getDevice(op->bias()) : nullptr;
+  TensorPtr out = allocOut(op->out());
+  auto two = [](const fb::Vector<int32_t> *v, const char *what, int &a, int &b) {
+    TTRT_ASSERT(v && v->size() == 2, "conv2d ", what, " must have 2 entries");
+    a = v->Get(0);
+    b = v->Get(1);
+  };
+  int kh, kw, sh, sw, dh, dw;
+  two(op->kernel_size(), "kernel_size", kh, kw);
+  two(op->stride(), "stride", sh, sw);
+  two(op->dilation(), "dilation", dh, dw);
+  int pad[4];
+  TTRT_ASSERT(op->padding() && (op->padding()->size() == 2 || op->padding()->size() == 4), "conv2d padding must have 2 or 4 entries");
+  if (op->padding()->size() == 2) {
+    pad[0] = pad[2] = op->padding()->Get(0);
+    pad[1] = pad[3] = op->padding()->Get(1);
+  } else {
+    for (int i = 0; i < 4; ++i) pad[i] = op->padding()->Get(i); // top, left, bottom, right
+  }
+  int64_t N = op->batch_size(), H = op->input_height(), W = op->input_width(), C = op->in_channels(), O = op->out_channels();
+  TTRT_ASSERT(static_cast<int64_t>(x->volume()) == N * H * W * C, "conv2d input has ", x->volume(), " elements, expected N*H*W*C = ",
+              N * H * W * C);
+  TTRT_ASSERT(x->dtype == w->dtype && x->dtype == out->dtype, "conv2d tensors must share one data type");
+  int groups = static_cast<int>(op->groups());
+  size_t wsBytes = ttb_conv2d_workspace_bytes(ttbDtype(x->dtype), N, H, W, C, O, kh, kw, sh, sw, pad, dh, dw, groups);
+  TensorPtr ws = wsBytes ? makeDeviceTensor(dev, {static_cast<uint32_t>((wsBytes + 3) / 4)}, DataType::UInt32) : nullptr;
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_conv2d(x->shards[i]->ptr, w->shards[i]->ptr, bias ? bias->shards[i]->ptr : nullptr, out->shards[i]->ptr,
+                        ttbDtype(x->dtype), bias ? ttbDtype(bias->dtype) : 0, N, H, W, C, O, kh, kw, sh, sw, pad, dh, dw,
+                        groups, TTB_ACT_NONE, ws ? ws->shards[i]->ptr : nullptr, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// ---- normalisation / reduction ----------------------------------------------------------------------------
+void Executor::runSoftmax(const fbt::SoftmaxOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = allocOut(op->out());
+  size_t rank = in->shape.size();
+  int d = normDim(op->dimension(), rank);
+  size_t outer = prod(in->shape, 0, d), len = in->shape[d], inner = prod(in->shape, d + 1, rank);
+  TTRT_ASSERT(in->dtype == out->dtype, "softmax changes the data type");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_softmax(in->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(in->dtype), outer, len, inner, r.stream));
+  });
+  put(op->out(), out);
+}
+
+void Executor::runRmsNorm(const fbt::RMSNormOp *op) {
+  TensorPtr in = getDevice(op->input());
+  TensorPtr w = op->weight() ? getDevice(op->weight()) : nullptr;
+  TensorPtr b = op->bias() ? getDevice(op->bias()) : nullptr;
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(!in->shape.empty(), "rms_norm of a scalar");
+  size_t cols = in->shape.back(), rows = in->volume() / std::max<size_t>(cols, 1);
+  // Normalisation over the last dimension (the form the TTNN op takes; weight has `cols` entries).
+  if (w) TTRT_ASSERT(w->volume() == cols && w->dtype == in->dtype, "rms_norm weight must match the last dimension and data type");
+  if (b) TTRT_ASSERT(b->volume() == cols && b->dtype == in->dtype, "rms_norm bias must match the last dimension and data type");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_rms_norm(in->shards[i]->ptr, w ? w->shards[i]->ptr : nullptr, b ? b->shards[i]->ptr : nullptr,
+                          out->shards[i]->ptr, ttbDtype(in->dtype), rows, cols, op->epsilon(), r.stream));
+  });
+  put(op->out(), out);
+}
+
+// add(a, b) -> rms_norm(sum): one pass; the sum is also written when something else reads it.
+size_t Executor::tryAddRmsNorm(size_t i) {
+  const auto *ops = prog->operations();
+  const auto *add = ops->Get(static_cast<uint32_t>(i))->type_as_EltwiseBinaryOp();
+  if (add->type() != fbt::EltwiseBinaryOpType::Add) return 0;
+  if (refShape(add->lhs()) != refShape(add->out()) || refShape(add->rhs()) != refShape(add->out())) return 0;
+  DataType dt = refDtype(add->out());
+  if (refDtype(add->lhs()) != dt || refDtype(add->rhs()) != dt || (dt != DataType::BFloat16 && dt != DataType::Float32)) return 0;
+  std::vector<const fbt::Operation *> deallocs;
+  size_t j = i + 1;
+  const auto *nop = peek(j, deallocs);
+  if (!nop || nop->type_type() != OpType::RMSNormOp) return 0;
+  const auto *rn = nop->type_as_RMSNormOp();
+  if (rn->input()->global_id() != add->out()->global_id() || rn->bias() || !rn->weight()) return 0;
+  if (refDtype(rn->out()) != dt || refDtype(rn->weight()) != dt) return 0;
+  TensorPtr a = getDevice(add->lhs()), b = getDevice(add->rhs()), w = getDevice(rn->weight());
+  bool keepSum = !singleUse(add->out());
+  TensorPtr sum = keepSum ? allocOut(add->out()) : nullptr;
+  TensorPtr out = allocOut(rn->out());
+  size_t cols = out->shape.back(), rows = out->volume() / std::max<size_t>(cols, 1);
+  if (w->volume() != cols) return 0;
+  eachRank([&](size_t r_, const RankCtx &r) {
+    TTB_CALL(ttb_add_rms_norm(a->shards[r_]->ptr, b->shards[r_]->ptr, w->shards[r_]->ptr, sum ? sum->shards[r_]->ptr : nullptr,
+                              out->shards[r_]->ptr, ttbDtype(dt), rows, cols, rn->epsilon(), r.stream));
+  });
+  if (sum) put(add->out(), sum);
+  put(rn->out(), out);
+  runDeallocs(deallocs);
+  return j + 1 - i;
+}
+
+// silu(g) -> multiply(silu, u)
+size_t Executor::trySiluMul(size_t i) {
+  const auto *ops = prog->operations();
+  const auto *u = ops->Get(static_cast<uint32_t>(i))->type_as_EltwiseUnaryOp();
+  if (u->type() != fbt::EltwiseUnaryOpType::Silu || !singleUse(u->out())) return 0;
+  DataType dt = refDtype(u->out());
+  if (refDtype(u->in()) != dt || (dt != DataType::BFloat16 && dt != DataType::Float32 && dt != DataType::Float16)) return 0;
+  std::vector<const fbt::Operation *> deallocs;
+  size_t j = i + 1;
+  const auto *nop = peek(j, deallocs);
+  if (!nop || nop->type_type() != OpType::EltwiseBinaryOp) return 0;
+  const auto *mul = nop->type_as_EltwiseBinaryOp();
+  if (mul->type() != fbt::EltwiseBinaryOpType::Multiply) return 0;
+  const fbt::TensorRef *other = nullptr;
+  if (mul->lhs()->global_id() == u->out()->global_id()) other = mul->rhs();
+  else if (mul->rhs()->global_id() == u->out()->global_id()) other = mul->lhs();
+  if (!other || other->global_id() == u->out()->global_id()) return 0;
+  if (refShape(other) != refShape(u->out()) || refShape(mul->out()) != refShape(u->out())) return 0;
+  if (refDtype(other) != dt || refDtype(mul->out()) != dt) return 0;
+  TensorPtr g = getDevice(u->in()), up = getDevice(other);
+  TensorPtr out = allocOut(mul->out());
+  eachRank([&](size_t r_, const RankCtx &r) {
+    TTB_CALL(ttb_silu_mul(g->shards[r_]->ptr, up->shards[r_]->ptr, out->shards[r_]->ptr, ttbDtype(dt), out->volume(), r.stream));
+  });
+  put(mul->out(), out);
+  runDeallocs(deallocs);
+  return j + 1 - i;
+}
+
+void Executor::runReduction(const fbt::ReductionOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = allocOut(op->out());
+  size_t rank = in->shape.size();
+  std::vector<int> dims;
+  if (op->dim_arg() && op->dim_arg()->size() > 0) {
+    for (int32_t d : *op->dim_arg()) dims.push_back(normDim(d, rank));
+  } else {
+    for (size_t d = 0; d < rank; ++d) dims.push_back(static_cast<int>(d));
+  }
+  std::sort(dims.begin(), dims.end());
+  dims.erase(std::unique(dims.begin(), dims.end()), dims.end());
+  bool contiguous = true;
+  for (size_t k = 1; k < dims.size(); ++k) contiguous = contiguous && dims[k] == dims[k - 1] + 1;
+  TTRT_ASSERT(in->dtype == out->dtype, "reduction changes the data type");
+  int code = static_cast<int>(op->type());
+  if (contiguous) {
+    size_t outer = prod(in->shape, 0, dims.front()), len = prod(in->shape, dims.front(), dims.back() + 1),
+           inner = prod(in->shape, dims.back() + 1, rank);
+    eachRank([&](size_t i, const RankCtx &r) {
+      TTB_CALL(ttb_reduce(code, in->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(in->dtype), outer, len, inner, r.stream));
+    });
+  } else {
+    // Scattered dims: reduce one dim at a time, innermost first (mean = sums then one division
+    // is not bit-identical to nested means, so mean is applied per dim as torch.mean does over
+    // a dim tuple only when contiguous; otherwise reject).
+    TTRT_ASSERT(op->type() != fbt::ReductionOpType::Mean, "mean over non-adjacent dimensions is not supported");
+    TensorPtr cur = in;
+    std::vector<uint32_t> shape = in->shape;
+    for (int k = static_cast<int>(dims.size()) - 1; k >= 0; --k) {
+      int d = dims[k];
+      size_t outer = prod(shape, 0, d), len = shape[d], inner = prod(shape, d + 1, shape.size());
+      shape[d] = 1;
+      TensorPtr nxt = k == 0 ? out : makeDeviceTensor(dev, shape, in->dtype);
+      eachRank([&](size_t i, const RankCtx &r) {
+        TTB_CALL(ttb_reduce(code, cur->shards[i]->ptr, nxt->shards[i]->ptr, ttbDtype(in->dtype), outer, len, inner, r.stream));
+      });
+      cur = nxt;
+    }
+  }
+  put(op->out(), out);
+}
+
+// ---- data movement --------------------------------------------------------------------------------------------
+void Executor::runReshape(const fbt::ReshapeOp *op) {
+  TensorPtr in = get(op->in());
+  std::vector<uint32_t> shape = refShape(op->out());
+  TTRT_ASSERT(prod(shape, 0, shape.size()) == in->volume(), "reshape changes the element count");
+  // Dense row-major on both sides: a reshape is a new view of the same memory.
+  auto view = std::make_shared<TensorImpl>();
+  view->shape = shape;
+  view->stride = denseStrides(shape);
+  view->dtype = in->dtype;
+  view->storage = in->storage;
+  view->layout = in->layout;
+  view->shards = in->shards;
+  view->device = in->device;
+  put(op->out(), view);
+}
+
+TensorPtr Executor::stridedView(const TensorPtr &in, const std::vector<uint32_t> &outShape, const std::vector<int64_t> &inStrides,
+                                int64_t offset, DataType dt) {
+  TensorPtr out = makeDeviceTensor(dev, outShape, dt);
+  out->layout = in->layout;
+  std::vector<int64_t> shape(outShape.begin(), outShape.end());
+  TTRT_ASSERT(shape.size() <= 8, "rank above 8");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_strided_copy(in->shards[i]->ptr, out->shards[i]->ptr, static_cast<int>(dataTypeSize(dt)),
+                              static_cast<int>(shape.size()), shape.data(), inStrides.data(), offset, r.stream));
+  });
+  return out;
+}
+
+void Executor::runPermute(const fbt::TensorRef *inRef, const std::vector<int> &perm, const fbt::TensorRef *outRef) {
+  TensorPtr in = getDevice(inRef);
+  size_t rank = in->shape.size();
+  TTRT_ASSERT(perm.size() == rank, "permutation rank mismatch");
+  std::vector<uint32_t> outShape(rank);
+  std::vector<int64_t> strides(rank);
+  std::vector<int64_t> dense = denseStrides(in->shape);
+  for (size_t k = 0; k < rank; ++k) {
+    int p = normDim(perm[k], rank);
+    outShape[k] = in->shape[p]; // TTNN permute: outputDim[i] = inputDim[permutation[i]]
+    strides[k] = dense[p];
+  }
+  TTRT_ASSERT(outShape == refShape(outRef), "permute result shape differs from the op's result type");
+  put(outRef, stridedView(in, outShape, strides, 0, in->dtype));
+}
+
+void Executor::runConcat(const fbt::ConcatOp *op) {
+  TTRT_ASSERT(op->inputs() && op->inputs()->size() > 0, "concat without inputs");
+  TensorPtr out = allocOut(op->out());
+  size_t rank = out->shape.size();
+  int d = normDim(op->dim(), rank);
+  std::vector<int64_t> outStrides = denseStrides(out->shape);
+  int64_t at = 0;
+  for (const auto *ref : *op->inputs()) {
+    TensorPtr in = getDevice(ref);
+    TTRT_ASSERT(in->shape.size() == rank && in->dtype == out->dtype, "concat inputs must match in rank and data type");
+    std::vector<int64_t> shape(in->shape.begin(), in->shape.end());
+    int64_t offset = at * outStrides[d];
+    eachRank([&](size_t i, const RankCtx &r) {
+      TTB_CALL(ttb_strided_scatter(in->shards[i]->ptr, out->shards[i]->ptr, static_cast<int>(dataTypeSize(in->dtype)),
+                                   static_cast<int>(rank), shape.data(), outStrides.data(), offset, r.stream));
+    });
+    at += in->shape[d];
+  }
+  TTRT_ASSERT(at == out->shape[d], "concat inputs do not add up to the result extent");
+  put(op->out(), out);
+}
+
+void Executor::runSlice(const fbt::SliceOp *op) {
+  TensorPtr in = getDevice(op->in());
+  const auto *p = op->params_as_SliceStaticOpParams();
+  TTRT_ASSERT(p && p->begins() && p->ends(), "only static slices are supported");
+  size_t rank = in->shape.size();
+  TTRT_ASSERT(p->begins()->size() == rank && p->ends()->size() == rank, "slice bounds rank mismatch");
+  std::vector<int64_t> dense = denseStrides(in->shape), strides(rank);
+  std::vector<uint32_t> outShape(rank);
+  int64_t offset = 0;
+  for (size_t k = 0; k < rank; ++k) {
+    int64_t b = p->begins()->Get(static_cast<uint32_t>(k)), e = p->ends()->Get(static_cast<uint32_t>(k));
+    int64_t st = op->step() && op->step()->size() == rank ? op->step()->Get(static_cast<uint32_t>(k)) : 1;
+    int64_t dim = in->shape[k];
+    if (b < 0) b += dim;
+    if (e < 0) e += dim;
+    TTRT_ASSERT(st > 0 && b >= 0 && e <= dim && b <= e, "slice bounds out of range on dim ", k);
+    outShape[k] = static_cast<uint32_t>((e - b + st - 1) / st);
+    strides[k] = dense[k] * st;
+    offset += b * dense[k];
+  }
+  TTRT_ASSERT(outShape == refShape(op->out()), "slice result shape differs from the op's result type");
+  put(op->out(), stridedView(in, outShape, strides, offset, in->dtype));
+}
+
+void Executor::runRepeat(const fbt::RepeatOp *op) {
+  TensorPtr in = getDevice(op->in());
+  size_t rank = in->shape.size();
+  TTRT_ASSERT(op->repeat_dims() && op->repeat_dims()->size() == rank, "repeat dims rank mismatch");
+  // out[i] = in[i mod shape]: view each dim as (repeat, size) with stride (0, dense)
+  std::vector<uint32_t> viewShape;
+  std::vector<int64_t> viewStrides, dense = denseStrides(in->shape);
+  for (size_t k = 0; k < rank; ++k) {
+    viewShape.push_back(static_cast<uint32_t>(op->repeat_dims()->Get(static_cast<uint32_t>(k))));
+    viewStrides.push_back(0);
+    viewShape.push_back(in->shape[k]);
+    viewStrides.push_back(dense[k]);
+  }
+  TTRT_ASSERT(viewShape.size() <= 8, "repeat of rank above 4 is not supported");
+  TensorPtr t = stridedView(in, viewShape, viewStrides, 0, in->dtype);
+  t->shape = refShape(op->out());
+  t->stride = denseStrides(t->shape);
+  TTRT_ASSERT(t->volume() == prod(viewShape, 0, viewShape.size()), "repeat result shape differs from the op's result type");
+  put(op->out(), t);
+}
+
+void Executor::runRepeatInterleave(const fbt::RepeatInterleaveOp *op) {
+  TensorPtr in = getDevice(op->input());
+  size_t rank = in->shape.size();
+  int d = normDim(op->dim(), rank);
+  std::vector<uint32_t> viewShape;
+  std::vector<int64_t> viewStrides, dense = denseStrides(in->shape);
+  for (size_t k = 0; k < rank; ++k) {
+    viewShape.push_back(in->shape[k]);
+    viewStrides.push_back(dense[k]);
+    if (static_cast<int>(k) == d) {
+      viewShape.push_back(op->repeats());
+      viewStrides.push_back(0);
+    }
+  }
+  TTRT_ASSERT(viewShape.size() <= 8, "rank above 7");
+  TensorPtr t = stridedView(in, viewShape, viewStrides, 0, in->dtype);
+  t->shape = refShape(op->out());
+  t->stride = denseStrides(t->shape);
+  TTRT_ASSERT(t->volume() == prod(viewShape, 0, viewShape.size()), "repeat_interleave result shape differs from the op's result type");
+  put(op->out(), t);
+}
+
+// [B, H, S, D] -> [B, S, H*D]
+void Executor::runConcatenateHeads(const fbt::ConcatenateHeadsOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TTRT_ASSERT(in->shape.size() == 4, "concatenate_heads expects [batch, heads, seq, head_dim]");
+  uint32_t B = in->shape[0], H = in->shape[1], S = in->shape[2], D = in->shape[3];
+  std::vector<int64_t> dense = denseStrides(in->shape);
+  TensorPtr t = stridedView(in, {B, S, H, D}, {dense[0], dense[2], dense[1], dense[3]}, 0, in->dtype);
+  t->shape = {B, S, H * D};
+  t->stride = denseStrides(t->shape);
+  TTRT_ASSERT(t->shape == refShape(op->out()), "concatenate_heads result shape differs from the op's result type");
+  put(op->out(), t);
+}
+
+// Fused [B, S, (Hq + 2*Hkv)*D] (or q and packed kv) -> q [B,Hq,S,D], k [B,Hkv,S,D] (or [B,Hkv,D,S]), v [B,Hkv,S,D]
+// Semantics: tools/tt-alchemist/templates/python/local/ttir_cpu.py:824-864.
+void Executor::runSplitQkv(const fbt::SplitQueryKeyValueAndSplitHeadsOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr kv = op->kv_input() ? getDevice(op->kv_input()) : nullptr;
+  TTRT_ASSERT(in->shape.size() == 3, "split_query_key_value_and_split_heads expects [batch, seq, hidden]");
+  uint32_t B = in->shape[0], S = in->shape[1], hidden = in->shape[2];
+  uint32_t Hq = op->num_heads(), Hkv = op->num_kv_heads().value_or(Hq);
+  uint32_t D = kv ? hidden / Hq : hidden / (Hq + 2 * Hkv);
+  auto heads = [&](const TensorPtr &src, uint32_t rowLen, uint32_t colOff, uint32_t H, bool transpose) {
+    // element (b, h, s, d) = src[b, s, colOff + h*D + d]
+    int64_t sb = static_cast<int64_t>(S) * rowLen, ss = rowLen;
+    if (!transpose) {
+      return stridedView(src, {B, H, S, D}, {sb, static_cast<int64_t>(D), ss, 1}, colOff, src->dtype);
+    }
+    return stridedView(src, {B, H, D, S}, {sb, static_cast<int64_t>(D), 1, ss}, colOff, src->dtype);
+  };
+  TensorPtr q, k, v;
+  if (!kv) {
+    q = heads(in, hidden, 0, Hq, false);
+    k = heads(in, hidden, Hq * D, Hkv, op->transpose_key());
+    v = heads(in, hidden, (Hq + Hkv) * D, Hkv, false);
+  } else {
+    TTRT_ASSERT(kv->shape.size() == 3 && kv->shape[2] == 2 * Hkv * D, "kv input must be [batch, seq, 2*kv_heads*head_dim]");
+    q = heads(in, hidden, 0, Hq, false);
+    k = heads(kv, kv->shape[2], 0, Hkv, op->transpose_key());
+    v = heads(kv, kv->shape[2], Hkv * D, Hkv, false);
+  }
+  put(op->q_out(), q);
+  put(op->k_out(), k);
+  put(op->v_out(), v);
+}
+
+void Executor::runRotaryEmbedding(const fbt::RotaryEmbeddingOp *op) {
+  TensorPtr x = getDevice(op->input()), c = getDevice(op->cos_cache()), s = getDevice(op->sin_cache());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(x->shape.size() >= 2, "rotary_embedding expects [..., seq, head_dim]");
+  size_t rank = x->shape.size();
+  size_t D = x->shape[rank - 1], S = x->shape[rank - 2], BH = x->volume() / std::max<size_t>(S * D, 1);
+  TTRT_ASSERT(!op->token_index().has_value(), "rotary_embedding with token_index (decode) is not supported");
+  TTRT_ASSERT(c->volume() == S * D && s->volume() == S * D, "cos/sin caches must be [seq, head_dim] = [", S, ", ", D, "]");
+  TTRT_ASSERT(c->dtype == x->dtype && s->dtype == x->dtype && out->dtype == x->dtype, "rotary_embedding tensors must share one data type");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_rotary_embedding(x->shards[i]->ptr, c->shards[i]->ptr, s->shards[i]->ptr, out->shards[i]->ptr,
+                                  ttbDtype(x->dtype), BH, S, D, r.stream));
+  });
+  put(op->out(), out);
+}
+
+void Executor::runSdpa(const fbt::ScaledDotProductAttentionOp *op) {
+  TensorPtr q = getDevice(op->query()), k = getDevice(op->key()), v = getDevice(op->value());
+  TensorPtr mask = op->attention_mask() ? getDevice(op->attention_mask()) : nullptr;
+  TTRT_ASSERT(!op->attention_sink(), "attention_sink is not supported");
+  TTRT_ASSERT(!op->sliding_window_size().has_value(), "sliding_window_size is not supported");
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(q->shape.size() == 4 && k->shape.size() == 4 && v->shape.size() == 4, "attention operands must be [batch, heads, seq, head_dim]");
+  int64_t B = q->shape[0], Hq = q->shape[1], Sq = q->shape[2], D = q->shape[3];
+  int64_t Hkv = k->shape[1], Skv = k->shape[2];
+  TTRT_ASSERT(k->shape[0] == B && v->shape[0] == B && k->shape[3] == D && v->shape == k->shape, "attention operand shapes disagree");
+  TTRT_ASSERT(Hkv > 0 && Hq % Hkv == 0, "query heads must be a multiple of key/value heads");
+  TTRT_ASSERT(q->dtype == k->dtype && q->dtype == v->dtype && q->dtype == out->dtype, "attention tensors must share one data type");
+  float scale = op->scale().value_or(1.0f / std::sqrt(static_cast<float>(D)));
+  int64_t mb = 0, mh = 0;
+  if (mask) {
+    TTRT_ASSERT(mask->shape.size() == 4 && mask->shape[2] == Sq && mask->shape[3] == Skv && mask->dtype == q->dtype,
+                "attention mask must be [1|B, 1|H, Sq, Skv] in the operand data type");
+    mb = mask->shape[0];
+    mh = mask->shape[1];
+  }
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_sdpa(q->shards[i]->ptr, k->shards[i]->ptr, v->shards[i]->ptr, mask ? mask->shards[i]->ptr : nullptr,
+                      out->shards[i]->ptr, ttbDtype(q->dtype), B, Hq, Hkv, Sq, Skv, D, mb, mh, op->is_causal() ? 1 : 0, scale,
+                      r.stream));
+  });
+  put(op->out(), out);
+}
+
+// ---- mesh ops -------------------------------------------------------------------------------------------------
+uint32_t Executor::meshAxisSize(uint32_t clusterAxis) const {
+  TTRT_ASSERT(clusterAxis < 2, "cluster_axis must be 0 or 1");
+  return dev->meshShape[clusterAxis];
+}
+
+void Executor::runAllReduce(const fbt::AllReduceOp *op) {
+  TensorPtr in = getDevice(op->in());
+  uint32_t n = meshAxisSize(op->cluster_axis());
+  if (n == 1) {
+    put(op->out(), in);
+    return;
+  }
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(out->volume() == in->volume() && out->dtype == in->dtype, "all_reduce changes shape or type");
+  if (dev->locals.size() > 1) TTB_CALL(ttb_group_start());
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_all_reduce(r.comm, in->shards[i]->ptr, out->shards[i]->ptr, in->volume(), ttbDtype(in->dtype),
+                            static_cast<int>(op->reduce_type()), r.stream));
+  });
+  if (dev->locals.size() > 1) TTB_CALL(ttb_group_end());
+  put(op->out(), out);
+}
+
+void Executor::runAllGather(const fbt::AllGatherOp *op) {
+  TensorPtr in = getDevice(op->in());
+  uint32_t n = meshAxisSize(op->cluster_axis());
+  if (n == 1) {
+    put(op->out(), in);
+    return;
+  }
+  size_t rank = in->shape.size();
+  int d = normDim(op->all_gather_dim(), rank);
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(out->volume() == in->volume() * n, "all_gather result must be ", n, " times the input");
+  size_t outer = prod(in->shape, 0, d);
+  // NCCL concatenates rank blocks; that is the result itself when nothing precedes the gather dim.
+  TensorPtr staged = outer == 1 ? out : makeDeviceTensor(dev, {n, static_cast<uint32_t>(in->volume())}, in->dtype);
+  if (dev->locals.size() > 1) TTB_CALL(ttb_group_start());
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_all_gather(r.comm, in->shards[i]->ptr, staged->shards[i]->ptr, in->volume(), ttbDtype(in->dtype), r.stream));
+  });
+  if (dev->locals.size() > 1) TTB_CALL(ttb_group_end());
+  if (outer != 1) {
+    // staged is [n, outer, len, inner]; result is [outer, n*len, inner]
+    int64_t len = in->shape[d], inner = static_cast<int64_t>(prod(in->shape, d + 1, rank));
+    std::vector<int64_t> shape = {static_cast<int64_t>(outer), static_cast<int64_t>(n), len * inner};
+    std::vector<int64_t> strides = {len * inner, static_cast<int64_t>(in->volume()), 1};
+    eachRank([&](size_t i, const RankCtx &r) {
+      TTB_CALL(ttb_strided_copy(staged->shards[i]->ptr, out->shards[i]->ptr, static_cast<int>(dataTypeSize(in->dtype)), 3,
+                                shape.data(), strides.data(), 0, r.stream));
+    });
+  }
+  put(op->out(), out);
+}
+
+void Executor::runReduceScatter(const fbt::ReduceScatterOp *op) {
+  TensorPtr in = getDevice(op->in());
+  uint32_t n = meshAxisSize(op->cluster_axis());
+  if (n == 1) {
+    put(op->out(), in);
+    return;
+  }
+  size_t rank = in->shape.size();
+  int d = normDim(op->scatter_dim(), rank);
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(in->shape[d] % n == 0 && out->volume() * n == in->volume(), "scatter dimension must divide by the mesh axis size");
+  size_t outer = prod(in->shape, 0, d);
+  TensorPtr src = in;
+  if (outer != 1) {
+    // bring the scatter dim to the front in rank-block order: [n, outer, len/n, inner]
+    int64_t lenPer = in->shape[d] / n, inner = static_cast<int64_t>(prod(in->shape, d + 1, rank));
+    std::vector<uint32_t> shape = {n, static_cast<uint32_t>(outer), static_cast<uint32_t>(lenPer * inner)};
+    std::vector<int64_t> strides = {lenPer * inner, static_cast<int64_t>(in->shape[d]) * inner, 1};
+    src = stridedView(in, shape, strides, 0, in->dtype);
+  }
+  if (dev->locals.size() > 1) TTB_CALL(ttb_group_start());
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_reduce_scatter(r.comm, src->shards[i]->ptr, out->shards[i]->ptr, out->volume(), ttbDtype(in->dtype),
+                                static_cast<int>(op->reduce_type()), r.stream));
+  });
+  if (dev->locals.size() > 1) TTB_CALL(ttb_group_end());
+  put(op->out(), out);
+}
+
+// Replicated along the axis -> each coordinate keeps its 1/n slice of `dim` (tools/golden/mapping.py:5751-5794).
+void Executor::runMeshPartition(const fbt::MeshPartitionOp *op) {
+  TensorPtr in = getDevice(op->in());
+  uint32_t axis = op->cluster_axis().value_or(dev->meshShape[0] > 1 ? 0 : 1);
+  uint32_t n = meshAxisSize(axis);
+  if (n == 1) {
+    put(op->out(), in);
+    return;
+  }
+  size_t rank = in->shape.size();
+  int d = normDim(op->dim(), rank);
+  TTRT_ASSERT(in->shape[d] % n == 0, "partition dimension must divide by the mesh axis size");
+  std::vector<uint32_t> outShape = in->shape;
+  outShape[d] /= n;
+  std::vector<int64_t> dense = denseStrides(in->shape);
+  TensorPtr out = makeDeviceTensor(dev, outShape, in->dtype);
+  std::vector<int64_t> shape(outShape.begin(), outShape.end());
+  eachRank([&](size_t i, const RankCtx &r) {
+    int64_t offset = static_cast<int64_t>(r.meshRank) * outShape[d] * dense[d];
+    TTB_CALL(ttb_strided_copy(in->shards[i]->ptr, out->shards[i]->ptr, static_cast<int>(dataTypeSize(in->dtype)),
+                              static_cast<int>(rank), shape.data(), dense.data(), offset, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// Host full tensor -> one shard per mesh coordinate (ttir.mesh_shard full_to_shard,
+// lib/Conversion/TTIRToTTNN/TTIRToTTNN.cpp:2770-2817): placement i says what mesh axis i does.
+void Executor::runDistribute(const fbt::DistributeTensorOp *op) {
+  TensorPtr in = get(op->in());
+  TTRT_ASSERT(op->mapper_config() && op->mapper_config()->placements(), "distribute_tensor without placements");
+  const auto *pl = op->mapper_config()->placements();
+  TTRT_ASSERT(pl->size() == 2, "placements must cover both mesh axes");
+  // Only one mesh axis is larger than 1; find the tensor dim sharded over it (or none).
+  int shardDim = -1;
+  for (uint32_t ax = 0; ax < 2; ++ax) {
+    fbt::Placement p = pl->Get(ax);
+    if (p.type() == fbt::PlacementType::Shard && dev->meshShape[ax] > 1) shardDim = normDim(p.dim(), in->shape.size());
+  }
+  uint32_t n = dev->worldSize;
+  std::vector<uint32_t> outShape = in->shape;
+  if (shardDim >= 0) {
+    TTRT_ASSERT(outShape[shardDim] % n == 0, "sharded dimension ", shardDim, " (", outShape[shardDim], ") must divide by ", n);
+    outShape[shardDim] /= n;
+  }
+  TTRT_ASSERT(outShape == refShape(op->out()), "distribute_tensor result shape differs from the op's result type");
+  bool toDev = refOnDevice(op->out());
+  if (shardDim < 0) {
+    // replicate
+    TensorPtr out = in;
+    if (toDev && in->storage == Storage::Host) out = toDevice(in, dev, in->dtype);
+    put(op->out(), out);
+    return;
+  }
+  TTRT_ASSERT(in->storage == Storage::Host, "input of distribute_tensor must be on host");
+  TTRT_ASSERT(in->shards.size() == 1, "input of distribute_tensor is already distributed");
+  // Slice on the host into per-coordinate shards; only the coordinates this process owns are built.
+  size_t es = dataTypeSize(in->dtype);
+  size_t outer = prod(in->shape, 0, shardDim), lenPer = outShape[shardDim], inner = prod(in->shape, shardDim + 1, in->shape.size());
+  size_t rowBytes = lenPer * inner * es, fullRowBytes = static_cast<size_t>(in->shape[shardDim]) * inner * es;
+  auto host = std::make_shared<TensorImpl>();
+  host->shape = outShape;
+  host->stride = denseStrides(outShape);
+  host->dtype = in->dtype;
+  host->storage = Storage::Host;
+  host->shards.resize(n);
+  const uint8_t *src = static_cast<const uint8_t *>(in->shards[0]->ptr);
+  for (const RankCtx &r : dev->locals) {
+    TensorPtr piece = makeHostTensor(outShape, in->dtype, 1);
+    uint8_t *dst = static_cast<uint8_t *>(piece->shards[0]->ptr);
+    for (size_t o = 0; o < outer; ++o) {
+      std::memcpy(dst + o * rowBytes, src + o * fullRowBytes + r.meshRank * rowBytes, rowBytes);
+    }
+    host->shards[r.meshRank] = piece->shards[0];
+  }
+  if (toDev) {
+    // toDevice indexes shards by mesh coordinate; absent coordinates belong to other processes.
+    TensorPtr out = toDevice(host, dev, in->dtype);
+    out->layout = refLayout(op->out());
+    put(op->out(), out);
+  } else {
+    put(op->out(), host);
+  }
+}
+
+// Shards -> full tensor on the host (ttir.mesh_shard shard_to_full, TTIRToTTNN.cpp:2819-2888):
+// dims[i] is the tensor dim concatenated over mesh axis i; an override extent of 1 means
+// "replicated on that axis, take the first".
+void Executor::runAggregate(const fbt::AggregateTensorOp *op) {
+  TensorPtr in = get(op->in());
+  TTRT_ASSERT(op->composer_config() && op->composer_config()->dims(), "aggregate_tensor without composer dims");
+  const auto *dims = op->composer_config()->dims();
+  const auto *ovr = op->composer_config()->mesh_shape_override();
+  int catDim = -1;
+  for (uint32_t ax = 0; ax < dims->size() && ax < 2; ++ax) {
+    uint32_t extent = (ovr && ax < ovr->size()) ? ovr->Get(ax) : dev->meshShape[ax];
+    if (extent > 1) catDim = normDim(dims->Get(ax), in->shape.size());
+  }
+  uint32_t n = dev->worldSize;
+  if (catDim < 0 || n == 1) {
+    // replicated: any one shard is the result
+    TensorPtr h = in->storage == Storage::Device ? toHostTensor(in, true) : in;
+    auto one = std::make_shared<TensorImpl>();
+    one->shape = h->shape;
+    one->stride = h->stride;
+    one->dtype = h->dtype;
+    one->storage = Storage::Host;
+    one->shards.push_back(h->shards[0]);
+    put(op->out(), one);
+    return;
+  }
+  std::vector<uint32_t> outShape = in->shape;
+  outShape[catDim] *= n;
+  TTRT_ASSERT(outShape == refShape(op->out()), "aggregate_tensor result shape differs from the op's result type");
+  size_t es = dataTypeSize(in->dtype);
+  size_t outer = prod(in->shape, 0, catDim), rowBytes = prod(in->shape, catDim, in->shape.size()) * es;
+  TensorPtr out = makeHostTensor(outShape, in->dtype, 1);
+  uint8_t *dst = static_cast<uint8_t *>(out->shards[0]->ptr);
+  if (dev->multiProcess) {
+    // Each process holds one shard: gather them on the device, then read back once.
+    TensorPtr d = in->storage == Storage::Device ? in : toDevice(in, dev, in->dtype);
+    TensorPtr all = makeDeviceTensor(dev, {n, static_cast<uint32_t>(in->volume())}, in->dtype);
+    const RankCtx &r = dev->locals[0];
+    TTB_CALL(ttb_set_device(r.cudaDevice));
+    TTB_CALL(ttb_all_gather(r.comm, d->shards[0]->ptr, all->shards[0]->ptr, in->volume(), ttbDtype(in->dtype), r.stream));
+    TensorPtr h = toHostTensor(all, true);
+    const uint8_t *src = static_cast<const uint8_t *>(h->shards[0]->ptr);
+    for (uint32_t k = 0; k < n; ++k)
+      for (size_t o = 0; o < outer; ++o)
+        std::memcpy(dst + (o * n + k) * rowBytes, src + (static_cast<size_t>(k) * outer + o) * rowBytes, rowBytes);
+  } else {
+    TensorPtr h = in->storage == Storage::Device ? toHostTensor(in, true) : in;
+    TTRT_ASSERT(h->shards.size() == n, "aggregate_tensor needs one shard per mesh coordinate");
+    for (uint32_t k = 0; k < n; ++k) {
+      const uint8_t *src = static_cast<const uint8_t *>(h->shards[k]->ptr);
+      for (size_t o = 0; o < outer; ++o) std::memcpy(dst + (o * n + k) * rowBytes, src + o * rowBytes, rowBytes);
+    }
+  }
+  put(op->out(), out);
+}
+
+std::vector<Tensor> runProgram(const std::shared_ptr<DeviceImpl> &dev, Binary &binary, uint32_t programIndex,
+                               std::vector<Tensor> &inputs) {
+  std::lock_guard<std::mutex> g(dev->submitMutex);
+  Executor ex(dev, binary, programIndex, inputs);
+  return ex.run();
+}
+
+} // namespace tt::runtime::cuda
+
+// ---- hook-facing API (runtime.h:246-283 of the reference) --------------------------------------------------------
+namespace tt::runtime {
+
+using namespace ::tt::runtime::cuda;
+namespace fbt = ::tt::target::ttnn;
+
+static const fbt::Operation *opOf(const OpContext &c) { return c.as<OpContextImpl>(DeviceRuntime::CUDA).op; }
+static Executor *execOf(const CallbackContext &c) { return c.as<ProgramContextImpl>(DeviceRuntime::CUDA).executor; }
+
+static TensorRef wrapRef(const fbt::TensorRef *r) {
+  return TensorRef(std::shared_ptr<void>(const_cast<fbt::TensorRef *>(r), [](void *) {}), DeviceRuntime::CUDA);
+}
+static const fbt::TensorRef *unwrapRef(const TensorRef &r) { return &r.as<fbt::TensorRef>(DeviceRuntime::CUDA); }
+
+std::string getOpDebugString(OpContext c) {
+  const auto *op = opOf(c);
+  return op->debug_info() ? op->debug_info()->str() : "";
+}
+
+std::string getOpLocInfo(OpContext c) {
+  const auto *op = opOf(c);
+  return op->loc_info() ? op->loc_info()->str() : "";
+}
+
+std::vector<TensorRef> getOpOutputRefs(OpContext c) {
+  std::vector<const fbt::TensorRef *> ins, outs;
+  collectOpRefs(opOf(c), ins, outs);
+  if (opOf(c)->type_type() == fbt::OpType::DeallocateOp) outs.clear();
+  std::vector<TensorRef> r;
+  for (const auto *o : outs) r.push_back(wrapRef(o));
+  return r;
+}
+
+std::vector<TensorRef> getOpInputRefs(OpContext c) {
+  std::vector<const fbt::TensorRef *> ins, outs;
+  collectOpRefs(opOf(c), ins, outs);
+  std::vector<TensorRef> r;
+  for (const auto *i : ins) r.push_back(wrapRef(i));
+  return r;
+}
+
+std::vector<uint32_t> getTensorRefShape(TensorRef ref) {
+  std::vector<uint32_t> s;
+  const auto *r = unwrapRef(ref);
+  if (r->desc() && r->desc()->shape()) {
+    for (int32_t d : *r->desc()->shape()) s.push_back(static_cast<uint32_t>(d));
+  }
+  return s;
+}
+
+::tt::target::DataType getTensorRefDataType(TensorRef ref) {
+  return unwrapRef(ref)->desc()->layout()->memory_desc()->data_type();
+}
+
+std::optional<Tensor> retrieveTensorFromPool(CallbackContext ctx, TensorRef ref, bool) {
+  Executor *ex = execOf(ctx);
+  auto it = ex->pool.find(unwrapRef(ref)->global_id());
+  if (it == ex->pool.end() || !it->second->allocated()) {
+    return std::nullopt;
+  }
+  TensorPtr t = it->second;
+  if (t->storage == Storage::Device) {
+    TensorPtr h = toHostTensor(t, true);
+    auto one = std::make_shared<TensorImpl>();
+    one->shape = h->shape;
+    one->stride = h->stride;
+    one->dtype = h->dtype;
+    one->storage = Storage::Host;
+    one->shards.push_back(h->shards[0]);
+    return wrapTensor(one);
+  }
+  return wrapTensor(t);
+}
+
+std::unordered_map<std::uint32_t, Tensor> getOpOutputTensor(OpContext c, CallbackContext ctx) {
+  std::unordered_map<std::uint32_t, Tensor> out;
+  Executor *ex = execOf(ctx);
+  std::vector<const fbt::TensorRef *> ins, outs;
+  collectOpRefs(opOf(c), ins, outs);
+  if (outs.empty() || opOf(c)->type_type() == fbt::OpType::DeallocateOp) {
+    return out;
+  }
+  auto it = ex->pool.find(outs[0]->global_id());
+  if (it == ex->pool.end() || !it->second->allocated()) {
+    return out;
+  }
+  TensorPtr t = it->second;
+  TensorPtr h = t->storage == Storage::Device ? toHostTensor(t, true) : t;
+  for (size_t i = 0; i < h->shards.size(); ++i) {
+    auto one = std::make_shared<TensorImpl>();
+    one->shape = h->shape;
+    one->stride = h->stride;
+    one->dtype = h->dtype;
+    one->storage = Storage::Host;
+    one->shards.push_back(h->shards[i]);
+    uint32_t coord = t->storage == Storage::Device ? ex->dev->locals[i].meshRank : static_cast<uint32_t>(i);
+    out.emplace(coord, wrapTensor(one));
+  }
+  return out;
+}
+
+void updateTensorInPool(CallbackContext ctx, TensorRef ref, Tensor srcTensor) {
+  Executor *ex = execOf(ctx);
+  auto it = ex->pool.find(unwrapRef(ref)->global_id());
+  TTRT_ASSERT(it != ex->pool.end(), "tensor ", unwrapRef(ref)->global_id(), " is not in the pool");
+  TensorPtr dst = it->second;
+  TensorPtr src = unwrapTensor(srcTensor);
+  TTRT_ASSERT(src->volume() == dst->volume(), "replacement tensor has a different element count");
+  Tensor d = wrapTensor(dst);
+  if (src->dtype != dst->dtype) {
+    // normalise on the host
+    std::vector<uint8_t> tmp(dst->bytes());
+    memcpy(tmp.data(), srcTensor, dst->dtype);
+    Tensor h = createOwnedHostTensor(tmp.data(), dst->shape, dst->stride, dataTypeSize(dst->dtype), dst->dtype);
+    auto hi = unwrapTensor(h);
+    if (dst->shards.size() > 1) {
+      for (size_t i = 1; i < dst->shards.size(); ++i) hi->shards.push_back(hi->shards[0]);
+    }
+    memcpy(d, h);
+  } else {
+    if (src->shards.size() == 1 && dst->shards.size() > 1) {
+      auto rep = std::make_shared<TensorImpl>();
+      rep->shape = src->shape;
+      rep->stride = src->stride;
+      rep->dtype = src->dtype;
+      rep->storage = src->storage;
+      rep->device = src->device;
+      for (size_t i = 0; i < dst->shards.size(); ++i) rep->shards.push_back(src->shards[0]);
+      memcpy(d, wrapTensor(rep));
+    } else {
+      memcpy(d, srcTensor);
+    }
+  }
+}
+
+size_t getProgramIndex(CallbackContext ctx) { return execOf(ctx)->programIndex; }
+
+void walkProgram(Binary bin, uint32_t programIndex, const OpWalkFn &cb) {
+  const auto *programs = bin.get()->programs();
+  TTRT_ASSERT(programs && programIndex < programs->size(), "program index out of range");
+  const auto *ops = programs->Get(programIndex)->operations();
+  if (!ops) return;
+  for (const auto *op : *ops) {
+    auto impl = std::make_shared<OpContextImpl>();
+    impl->op = op;
+    cb(OpContext(std::static_pointer_cast<void>(impl), DeviceRuntime::CUDA));
+  }
+}
+
+} // namespace tt::runtime

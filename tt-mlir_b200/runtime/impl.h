@@ -1,0 +1,158 @@
+// Internal object model of the B200 runtime target: what sits behind the opaque handles of
+// tt/runtime/types.h.  The reference keeps the equivalent state in TTNNTensorWrapper,
+// LayoutDesc and the MeshDevice (runtime/include/tt/runtime/detail/ttnn/types/types.h:36-135).
+#pragma once
+
+#include <atomic>
+#include <cstdint>
+#include <cstdlib>
+#include <memory>
+#include <mutex>
+#include <sstream>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/ttb_kernels.h"
+#include "tt/runtime/types.h"
+
+namespace tt::runtime::cuda {
+
+using ::tt::target::DataType;
+
+// ---- errors / logging ------------------------------------------------------------------
+// Same convention as the reference's LOG_FATAL (runtime/include/tt/runtime/detail/common/
+// logger.h:301-321): the message goes to stderr and a std::runtime_error is thrown.
+[[noreturn]] void fatal(const std::string &msg);
+void logDebug(const std::string &msg);
+
+template <typename... Args> std::string strcat_(Args &&...args) {
+  std::ostringstream os;
+  (os << ... << args);
+  return os.str();
+}
+
+#define TTRT_FATAL(...) ::tt::runtime::cuda::fatal(::tt::runtime::cuda::strcat_(__VA_ARGS__))
+#define TTRT_ASSERT(cond, ...)                                                           \
+  do {                                                                                   \
+    if (!(cond)) {                                                                       \
+      ::tt::runtime::cuda::fatal(::tt::runtime::cuda::strcat_("Assertion `" #cond "` failed: ", __VA_ARGS__)); \
+    }                                                                                    \
+  } while (0)
+// Turns a C-ABI status into an exception carrying the kernel library's message.
+#define TTB_CALL(expr)                                                                   \
+  do {                                                                                   \
+    int _rc = (expr);                                                                    \
+    if (_rc != TTB_OK) {                                                                 \
+      ::tt::runtime::cuda::fatal(::tt::runtime::cuda::strcat_(#expr " failed (", _rc, "): ", ttb_last_error())); \
+    }                                                                                    \
+  } while (0)
+
+// ---- dtype helpers ---------------------------------------------------------------------
+uint32_t dataTypeSize(DataType dt); // 0 for block formats
+bool isSupportedDataType(DataType dt);
+const char *dataTypeName(DataType dt);
+inline int ttbDtype(DataType dt) { return static_cast<int>(dt); }
+
+// ---- device ----------------------------------------------------------------------------
+// One mesh coordinate owned by this process: a CUDA device, a stream and (for meshes of more
+// than one device) an NCCL communicator rank.
+struct RankCtx {
+  int cudaDevice = 0;
+  uint32_t meshRank = 0;
+  void *stream = nullptr;
+  void *comm = nullptr;
+};
+
+struct DeviceImpl {
+  std::vector<uint32_t> meshShape{1, 1};
+  uint32_t worldSize = 1;          // mesh volume
+  std::vector<RankCtx> locals;     // coordinates this process owns
+  bool multiProcess = false;
+  bool open = false;
+  std::mutex submitMutex;          // submit is serialised per device
+  ~DeviceImpl();
+  void close();
+};
+
+// ---- tensors ---------------------------------------------------------------------------
+struct Buffer {
+  void *ptr = nullptr;
+  size_t bytes = 0;
+  int cudaDevice = -1;   // -1: host memory
+  void *stream = nullptr; // stream that orders the free of device memory
+  enum class Kind { Borrowed, HostMalloc, HostPinned, Device } kind = Kind::Borrowed;
+  std::shared_ptr<void> keepAlive; // another object owning the memory (views)
+  ~Buffer();
+};
+using BufferPtr = std::shared_ptr<Buffer>;
+
+enum class Storage { Host, Device };
+
+struct TensorImpl {
+  std::vector<uint32_t> shape;     // per-shard logical shape
+  std::vector<int64_t> stride;     // dense row-major, in elements
+  DataType dtype = DataType::Float32;
+  Storage storage = Storage::Host;
+  ::tt::target::TensorLayout layout = ::tt::target::TensorLayout::RowMajor; // metadata only
+  // Host: 1 shard, or one per mesh coordinate (multi-device host tensor).
+  // Device: one per mesh coordinate owned by this process, in DeviceImpl::locals order.
+  std::vector<BufferPtr> shards;
+  std::shared_ptr<DeviceImpl> device; // set for device tensors
+  bool retain = false;
+  std::atomic<uint64_t> version{0};
+  void *readyEvent = nullptr;      // recorded after the producing work was enqueued
+
+  size_t volume() const {
+    size_t v = 1;
+    for (uint32_t d : shape) v *= d;
+    return v;
+  }
+  size_t bytes() const { return volume() * dataTypeSize(dtype); }
+  // True while at least one shard still has memory (shards of other processes stay null).
+  bool allocated() const {
+    for (const BufferPtr &b : shards) {
+      if (b && b->ptr) return true;
+    }
+    return false;
+  }
+  ~TensorImpl();
+};
+using TensorPtr = std::shared_ptr<TensorImpl>;
+
+struct LayoutImpl {
+  Storage storage = Storage::Host;
+  ::tt::target::TensorLayout layout = ::tt::target::TensorLayout::RowMajor;
+  DataType dtype = DataType::Float32;
+  bool operator==(const LayoutImpl &o) const {
+    return storage == o.storage && layout == o.layout && dtype == o.dtype;
+  }
+};
+
+std::vector<int64_t> denseStrides(const std::vector<uint32_t> &shape);
+
+TensorPtr makeHostTensor(const std::vector<uint32_t> &shape, DataType dt, size_t nshards);
+TensorPtr makeDeviceTensor(const std::shared_ptr<DeviceImpl> &dev, const std::vector<uint32_t> &shape, DataType dt);
+Tensor wrapTensor(const TensorPtr &t);
+TensorPtr unwrapTensor(const Tensor &t);
+
+// Host <-> device movement shared by the API functions and the executor's layout ops.
+TensorPtr toDevice(const TensorPtr &host, const std::shared_ptr<DeviceImpl> &dev, DataType dt);
+TensorPtr toHostTensor(const TensorPtr &devTensor, bool blocking);
+TensorPtr castOnDevice(const TensorPtr &t, DataType dt);
+
+// ---- program execution -----------------------------------------------------------------
+std::vector<Tensor> runProgram(const std::shared_ptr<DeviceImpl> &dev, Binary &binary, uint32_t programIndex,
+                               std::vector<Tensor> &inputs);
+
+// Tensor refs an op reads / writes, in schema order (used by hooks and by fusion legality).
+void collectOpRefs(const ::tt::target::ttnn::Operation *op,
+                   std::vector<const ::tt::target::ttnn::TensorRef *> &ins,
+                   std::vector<const ::tt::target::ttnn::TensorRef *> &outs);
+
+struct OpContextImpl {
+  const ::tt::target::ttnn::Operation *op = nullptr;
+};
+struct ProgramContextImpl; // defined in executor.cpp
+
+} // namespace tt::runtime::cuda

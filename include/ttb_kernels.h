@@ -78,6 +78,14 @@ TTB_API int ttb_stream_wait_event(void *stream, void *event);
 TTB_API int ttb_event_elapsed_ms(void *start, void *stop, float *ms);
 /* Number of kernels this library has launched in the calling process (all threads). */
 TTB_API uint64_t ttb_launch_count(void);
+/* Per-launch profiling (the CUDA-event counterpart of the reference's Tracy zones around each op,
+ * runtime/lib/ttnn/program_executor.cpp:223-237).  While enabled every launcher brackets its
+ * kernel with an event pair on the launching stream and notes the launch's algorithmic FLOPs and
+ * bytes.  ttb_prof_summary waits for the recorded events and writes a JSON array of
+ * {"tag", "launches", "ms", "flops", "bytes"} aggregated per kernel family.  Enabling clears
+ * earlier records.  Meant for measurement runs, not for production submits. */
+TTB_API int ttb_prof_enable(int on);
+TTB_API int ttb_prof_summary(char *json_out, size_t cap);
 
 /* ---- quantization: ::ttnn::quantize / dequantize / requantize
  * (runtime/lib/ttnn/operations/eltwise/quantization/quantization.cpp:173-187).

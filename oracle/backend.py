@@ -1,0 +1,208 @@
+"""Eager CPU evaluation of a graph written against the ProgramBuilder interface.
+
+A graph function (tt-mlir_b200/graphs.py) takes a builder `b` and calls b.input / b.matmul /
+b.output ...  Given a `ProgramBuilder` it emits a TTNN flatbuffer; given this `OracleBuilder`
+it computes the reference result with oracle/ops.py.  Both therefore describe the same graph.
+Multi-device values are lists with one tensor per mesh coordinate.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import ops
+
+TORCH_DTYPE = {"Float32": torch.float32, "Float16": torch.float16, "BFloat16": torch.bfloat16, "Int32": torch.int32,
+               "UInt8": torch.uint8, "Int8": torch.int8, "UInt16": torch.uint16, "UInt32": torch.uint32}
+NAME_OF = {v: k for k, v in TORCH_DTYPE.items()}
+
+
+class OValue:
+    def __init__(self, t):
+        self.t = t  # torch.Tensor or list of per-device tensors
+
+    @property
+    def first(self) -> torch.Tensor:
+        return self.t[0] if isinstance(self.t, list) else self.t
+
+    @property
+    def shape(self):
+        return list(self.first.shape)
+
+    @property
+    def dtype(self) -> str:
+        return NAME_OF[self.first.dtype]
+
+
+def _map(fn, *vals):
+    """Applies fn per device when any operand is distributed."""
+    n = max((len(v.t) for v in vals if isinstance(v, OValue) and isinstance(v.t, list)), default=0)
+    if n == 0:
+        return OValue(fn(*[v.t if isinstance(v, OValue) else v for v in vals]))
+    out = []
+    for i in range(n):
+        args = [(v.t[i] if isinstance(v.t, list) else v.t) if isinstance(v, OValue) else v for v in vals]
+        out.append(fn(*args))
+    if isinstance(out[0], tuple):
+        return tuple(OValue([o[k] for o in out]) for k in range(len(out[0])))
+    return OValue(out)
+
+
+class OracleBuilder:
+    def __init__(self, inputs: Sequence[torch.Tensor], mesh_shape=(1, 1), quant_clamp_i8: bool = True):
+        self._inputs = list(inputs)
+        self._next_input = 0
+        self.mesh_shape = tuple(mesh_shape)
+        self.outputs: List[OValue] = []
+        self.clamp_i8 = quant_clamp_i8
+
+    # ---- program interface
+    def input(self, shape, dtype: str, on_device: bool = True) -> OValue:
+        t = self._inputs[self._next_input]
+        self._next_input += 1
+        assert list(t.shape) == list(shape), f"input {self._next_input - 1}: {list(t.shape)} vs {list(shape)}"
+        assert t.dtype == TORCH_DTYPE[dtype]
+        return OValue(t)
+
+    def output(self, *values: OValue):
+        self.outputs.extend(values)
+
+    def results(self):
+        return [v.t for v in self.outputs]
+
+    # ---- layout / creation
+    def to_device(self, x, loc=None): return x
+    def from_device(self, x, loc=None): return x
+
+    def to_layout(self, x, layout="Tile", dtype=None, on_device=None, loc=None):
+        return _map(lambda t: t.to(TORCH_DTYPE[dtype]), x) if dtype else x
+
+    def typecast(self, x, dtype, loc=None):
+        return _map(lambda t: ops.typecast(t, TORCH_DTYPE[dtype]), x)
+
+    def full(self, shape, value, dtype, loc=None):
+        return OValue(torch.full(list(shape), value, dtype=TORCH_DTYPE[dtype]))
+
+    def zeros(self, shape, dtype, loc=None): return OValue(torch.zeros(list(shape), dtype=TORCH_DTYPE[dtype]))
+    def ones(self, shape, dtype, loc=None): return OValue(torch.ones(list(shape), dtype=TORCH_DTYPE[dtype]))
+
+    def constant(self, data: bytes, shape, dtype, loc=None):
+        return OValue(torch.frombuffer(bytearray(data), dtype=TORCH_DTYPE[dtype]).reshape(list(shape)).clone())
+
+    def arange(self, start, end, step, dtype, loc=None):
+        return OValue(torch.arange(start, end, step, dtype=torch.float64).to(TORCH_DTYPE[dtype]))
+
+    def deallocate(self, x, force=False): pass
+
+    # ---- eltwise
+    def unary(self, kind, x, param=None, loc=None): return _map(lambda t: ops.unary(kind, t, param), x)
+    def relu(self, x, loc=None): return self.unary("Relu", x)
+    def silu(self, x, loc=None): return self.unary("Silu", x)
+    def exp(self, x, loc=None): return self.unary("Exp", x)
+    def neg(self, x, loc=None): return self.unary("Neg", x)
+    def sigmoid(self, x, loc=None): return self.unary("Sigmoid", x)
+    def clamp(self, x, lo, hi, loc=None): return _map(lambda t: ops.clamp(t, lo, hi), x)
+
+    def binary(self, kind, a, b, dtype=None, loc=None):
+        return _map(lambda x, y: ops.binary(kind, x, y, TORCH_DTYPE[dtype] if dtype else None), a, b)
+
+    def add(self, a, b, loc=None): return self.binary("Add", a, b)
+    def multiply(self, a, b, loc=None): return self.binary("Multiply", a, b)
+    def subtract(self, a, b, loc=None): return self.binary("Subtract", a, b)
+    def divide(self, a, b, loc=None): return self.binary("Divide", a, b)
+    def maximum(self, a, b, loc=None): return self.binary("Maximum", a, b)
+    def where(self, c, a, b, loc=None): return _map(ops.where, c, a, b)
+
+    # ---- quantization
+    def quantize(self, x, scale, zero_point, out_dtype="Int32", axis=None, loc=None):
+        dt = TORCH_DTYPE[out_dtype]
+        if isinstance(scale, OValue):
+            return _map(lambda t, s, z=None: ops.quantize_per_axis(t, s, z, axis, dt, self.clamp_i8), x, scale,
+                        *([zero_point] if isinstance(zero_point, OValue) else []))
+        return _map(lambda t: ops.quantize(t, scale, zero_point, dt, self.clamp_i8), x)
+
+    def dequantize(self, x, scale, zero_point, out_dtype="Float32", axis=None, loc=None):
+        dt = TORCH_DTYPE[out_dtype]
+        if isinstance(scale, OValue):
+            return _map(lambda t, s, z=None: ops.dequantize_per_axis(t, s, z, axis, dt), x, scale,
+                        *([zero_point] if isinstance(zero_point, OValue) else []))
+        return _map(lambda t: ops.dequantize(t, scale, zero_point, dt), x)
+
+    def requantize(self, x, in_scale, in_zp, out_scale, out_zp, out_dtype=None, axis=None, loc=None):
+        dt = TORCH_DTYPE[out_dtype] if out_dtype else None
+        return _map(lambda t: ops.requantize(t, in_scale, in_zp, out_scale, out_zp, dt, self.clamp_i8), x)
+
+    # ---- contractions
+    def matmul(self, a, b, transpose_a=False, transpose_b=False, activation=None, loc=None):
+        return _map(lambda x, y: ops.matmul(x, y, transpose_a, transpose_b, activation), a, b)
+
+    def linear(self, a, b, bias=None, transpose_a=False, transpose_b=False, activation=None, loc=None):
+        if bias is None:
+            return _map(lambda x, y: ops.linear(x, y, None, transpose_a, transpose_b, activation), a, b)
+        return _map(lambda x, y, z: ops.linear(x, y, z, transpose_a, transpose_b, activation), a, b, bias)
+
+    def conv2d(self, x, w, bias, batch, height, width, stride=(1, 1), padding=(0, 0, 0, 0), dilation=(1, 1), groups=1,
+               loc=None):
+        pad = list(padding) if len(padding) == 4 else [padding[0], padding[1], padding[0], padding[1]]
+        if bias is None:
+            return _map(lambda t, ww: ops.conv2d(t, ww, None, batch, height, width, stride, pad, dilation, groups), x, w)
+        return _map(lambda t, ww, bb: ops.conv2d(t, ww, bb, batch, height, width, stride, pad, dilation, groups), x, w, bias)
+
+    # ---- normalisation / reduction
+    def softmax(self, x, dim=-1, loc=None): return _map(lambda t: ops.softmax(t, dim), x)
+
+    def rms_norm(self, x, weight, bias=None, epsilon=1e-5, loc=None):
+        args = [v for v in (weight, bias) if v is not None]
+        if weight is not None and bias is not None:
+            return _map(lambda t, w, b: ops.rms_norm(t, w, b, epsilon), x, weight, bias)
+        if weight is not None:
+            return _map(lambda t, w: ops.rms_norm(t, w, None, epsilon), x, weight)
+        return _map(lambda t: ops.rms_norm(t, None, None, epsilon), x)
+
+    def reduce(self, kind, x, dims, keep_dim, loc=None): return _map(lambda t: ops.reduce(kind, t, dims, keep_dim), x)
+
+    # ---- data movement
+    def reshape(self, x, shape, loc=None): return _map(lambda t: t.reshape(list(shape)), x)
+    def permute(self, x, perm, loc=None): return _map(lambda t: t.permute(list(perm)).contiguous(), x)
+    def transpose(self, x, d0, d1, loc=None): return _map(lambda t: t.transpose(d0, d1).contiguous(), x)
+
+    def concat(self, xs, dim, loc=None):
+        return _map(lambda *ts: torch.cat(list(ts), dim=dim), *xs)
+
+    def slice(self, x, begins, ends, step=None, loc=None):
+        step = step or [1] * len(begins)
+        return _map(lambda t: t[tuple(slice(b, e, s) for b, e, s in zip(begins, ends, step))].contiguous(), x)
+
+    def repeat(self, x, repeats, loc=None): return _map(lambda t: t.repeat(*repeats), x)
+    def repeat_interleave(self, x, repeats, dim, loc=None): return _map(lambda t: torch.repeat_interleave(t, repeats, dim=dim), x)
+
+    # ---- transformer
+    def concatenate_heads(self, x, loc=None): return _map(ops.concatenate_heads, x)
+
+    def split_query_key_value_and_split_heads(self, x, kv, num_heads, num_kv_heads=None, transpose_key=False, loc=None):
+        if kv is None:
+            return _map(lambda t: ops.split_qkv(t, None, num_heads, num_kv_heads, transpose_key), x)
+        return _map(lambda t, u: ops.split_qkv(t, u, num_heads, num_kv_heads, transpose_key), x, kv)
+
+    def rotary_embedding(self, x, cos, sin, loc=None): return _map(ops.rotary_embedding, x, cos, sin)
+
+    def scaled_dot_product_attention(self, q, k, v, is_causal=True, mask=None, scale=None, loc=None):
+        if mask is None:
+            return _map(lambda a, b, c: ops.sdpa(a, b, c, is_causal, None, scale), q, k, v)
+        return _map(lambda a, b, c, m: ops.sdpa(a, b, c, is_causal, m, scale), q, k, v, mask)
+
+    # ---- mesh
+    def _n(self, cluster_axis): return self.mesh_shape[cluster_axis]
+
+    def distribute(self, x, shard_dim, cluster_axis=1, on_device=True, loc=None):
+        return OValue(ops.mesh_shard_full_to_shard(x.t, self._n(cluster_axis), shard_dim))
+
+    def aggregate(self, x, shard_dim, cluster_axis=1, loc=None):
+        return OValue(ops.mesh_shard_shard_to_full(x.t, shard_dim))
+
+    def all_reduce(self, x, reduce_type=0, cluster_axis=1, loc=None): return OValue(ops.all_reduce(x.t, reduce_type))
+    def all_gather(self, x, dim, cluster_axis=1, loc=None): return OValue(ops.all_gather(x.t, dim))
+    def reduce_scatter(self, x, dim, reduce_type=0, cluster_axis=1, loc=None): return OValue(ops.reduce_scatter(x.t, dim, reduce_type))
+    def mesh_partition(self, x, dim, cluster_axis=1, loc=None): return OValue(ops.mesh_partition(x.t, dim))

@@ -1,0 +1,295 @@
+"""Op-level CPU restatement of the reference semantics (see the package docstring for sources).
+
+Every function takes and returns torch CPU tensors in the graph's storage dtype.  `_hoist`
+applies the CPU-hoist rounding model: widen floats to f32 / integers to i32, run the op, narrow
+to the result dtype (lib/Dialect/TTIR/Transforms/HoistCPUOps/HoistCPUOps.cpp:78-93).
+Each op cites the reference function it follows; ttir_cpu.py = tools/tt-alchemist/templates/
+python/local/ttir_cpu.py, mapping.py = tools/golden/mapping.py.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+import torch.nn.functional as F
+
+
+def _widen(t: torch.Tensor) -> torch.Tensor:
+    if t.is_floating_point():
+        return t.to(torch.float32)
+    if t.dtype == torch.bool:
+        return t
+    return t.to(torch.int32)
+
+
+def _hoist(fn, out_dtype, *tensors, **kw):
+    res = fn(*[_widen(t) if isinstance(t, torch.Tensor) else t for t in tensors], **kw)
+    return res.to(out_dtype)
+
+
+# ---- eltwise (ttir_cpu.py:94-330) -------------------------------------------------------------
+UNARY = {
+    "Abs": torch.abs, "Ceil": torch.ceil, "Cos": torch.cos, "Floor": torch.floor,
+    "Gelu": lambda t: F.gelu(t), "IsFinite": lambda t: torch.isfinite(t).to(t.dtype),
+    "LogicalNot": lambda t: torch.logical_not(t).to(t.dtype), "Neg": torch.neg, "Relu": torch.relu,
+    "Sqrt": lambda t: torch.sqrt(t.double()).to(t.dtype),  # correctly rounded, ttir_cpu.py:218-224
+    "Rsqrt": torch.rsqrt, "Sigmoid": torch.sigmoid, "Sin": torch.sin,
+    "Reciprocal": torch.reciprocal, "Sign": torch.sign, "Tan": torch.tan, "Tanh": torch.tanh,
+    "Atan": torch.atan, "Exp": torch.exp, "Erf": torch.erf, "Erfc": torch.erfc, "Log": torch.log,
+    "Expm1": torch.expm1, "Relu6": F.relu6, "Silu": F.silu, "Hardsigmoid": F.hardsigmoid,
+    "Mish": lambda t: t * torch.tanh(F.softplus(t)),  # ttir_cpu.py:174
+   
+    "Acos": torch.acos, "Asin": torch.asin, "Asinh": torch.asinh,
+    "Cbrt": lambda t: torch.sign(t) * torch.pow(torch.abs(t), 1.0 / 3.0), "Log1p": torch.log1p,
+}
+
+
+def unary(kind: str, x: torch.Tensor, param: Optional[float] = None) -> torch.Tensor:
+    if kind == "LeakyRelu":
+        return _hoist(lambda t: F.leaky_relu(t, param if param is not None else 0.01), x.dtype, x)
+    if kind == "BitwiseNot":
+        return torch.bitwise_not(x)
+    return _hoist(UNARY[kind], x.dtype, x)
+
+
+def _cmp(fn):
+    return lambda a, b: fn(a, b)
+
+
+BINARY = {
+    "Add": torch.add, "Multiply": torch.mul, "Subtract": torch.sub, "Divide": torch.div,
+    "Maximum": torch.maximum, "Minimum": torch.minimum, "Pow": torch.pow, "Atan2": torch.atan2,
+    "Remainder": torch.remainder,
+    "Equal": torch.eq, "NotEqual": torch.ne, "GreaterEqual": torch.ge, "GreaterThan": torch.gt,
+    "LessEqual": torch.le, "LessThan": torch.lt,
+    "LogicalAnd": torch.logical_and, "LogicalOr": torch.logical_or, "LogicalXor": torch.logical_xor,
+    "BitwiseAnd": torch.bitwise_and, "BitwiseOr": torch.bitwise_or, "BitwiseXor": torch.bitwise_xor,
+}
+
+
+def binary(kind: str, a: torch.Tensor, b: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    out_dtype = out_dtype or a.dtype
+    return _hoist(BINARY[kind], out_dtype, a, b)
+
+
+def where(c, a, b):
+    return torch.where(c != 0, a, b)
+
+
+def clamp(x, lo, hi):
+    return _hoist(lambda t: torch.clamp(t, lo, hi), x.dtype, x)
+
+
+def typecast(x, dtype):  # ttir_cpu.py:498
+    return x.to(dtype)
+
+
+# ---- quantization (mapping.py:2534-2582; formulas include/ttmlir/Dialect/TTIR/IR/TTIROps.td:6010-6137) --
+def _qdtype(container: torch.dtype, clamp_i8: bool):
+    if container == torch.int8 or (container == torch.int32 and clamp_i8):
+        return torch.qint8
+    if container == torch.uint8:
+        return torch.quint8
+    return torch.qint32
+
+
+def quantize(x: torch.Tensor, scale: float, zero_point: int, container: torch.dtype = torch.int32,
+             clamp_i8: bool = True) -> torch.Tensor:
+    q = torch.quantize_per_tensor(x.to(torch.float32), scale, zero_point, _qdtype(container, clamp_i8)).int_repr()
+    return q.to(container)
+
+
+def dequantize(q: torch.Tensor, scale: float, zero_point: int, out_dtype=torch.float32) -> torch.Tensor:
+    # torch.dequantize(q) = (q - zp) * scale in f32
+    return ((q.to(torch.int32) - zero_point).to(torch.float32) * torch.tensor(scale, dtype=torch.float32)).to(out_dtype)
+
+
+def requantize(q: torch.Tensor, in_scale: float, in_zp: int, out_scale: float, out_zp: int,
+               container: Optional[torch.dtype] = None, clamp_i8: bool = True) -> torch.Tensor:
+    # golden: quantize(dequantize(q)) with the new parameters
+    return quantize(dequantize(q, in_scale, in_zp), out_scale, out_zp, container or q.dtype, clamp_i8)
+
+
+def quantize_per_axis(x, scales: torch.Tensor, zps: Optional[torch.Tensor], axis: int, container=torch.int32,
+                      clamp_i8: bool = True):
+    zps = zps if zps is not None else torch.zeros_like(scales, dtype=torch.int32)
+    q = torch.quantize_per_channel(x.to(torch.float32), scales.to(torch.float32).double(), zps.to(torch.int64), axis,
+                                   _qdtype(container, clamp_i8)).int_repr()
+    return q.to(container)
+
+
+def dequantize_per_axis(q, scales: torch.Tensor, zps: Optional[torch.Tensor], axis: int, out_dtype=torch.float32):
+    shape = [1] * q.dim()
+    shape[axis] = -1
+    z = zps.to(torch.int32).reshape(shape) if zps is not None else 0
+    return ((q.to(torch.int32) - z).to(torch.float32) * scales.to(torch.float32).reshape(shape)).to(out_dtype)
+
+
+# ---- contractions (ttir_cpu.py:509-521; f32 accumulation per lib/Conversion/TTIRToLinalg/TTIRToLinalg.cpp:542-549) --
+def matmul(a, b, transpose_a=False, transpose_b=False, activation=None):
+    def fn(x, y):
+        if transpose_a:
+            x = x.transpose(-2, -1)
+        if transpose_b:
+            y = y.transpose(-2, -1)
+        return _act(torch.matmul(x, y), activation)
+    return _hoist(fn, a.dtype, a, b)
+
+
+def linear(a, b, bias=None, transpose_a=False, transpose_b=False, activation=None):
+    def fn(x, y, z=None):
+        if transpose_a:
+            x = x.transpose(-2, -1)
+        if transpose_b:
+            y = y.transpose(-2, -1)
+        r = torch.matmul(x, y)
+        if z is not None:
+            r = r + z
+        return _act(r, activation)
+    if bias is None:
+        return _hoist(fn, a.dtype, a, b)
+    return _hoist(fn, a.dtype, a, b, bias)
+
+
+def _act(t, name):
+    if not name:
+        return t
+    return {"relu": torch.relu, "silu": F.silu, "gelu": F.gelu, "sigmoid": torch.sigmoid}[name](t)
+
+
+def conv2d(x, w, bias, batch, height, width, stride=(1, 1), padding=(0, 0, 0, 0), dilation=(1, 1), groups=1):
+    """NHWC activations (any view with N*H*W*C elements), OIHW weights, bias [1,1,1,O]
+    (ttir_cpu.py:772-815).  Returns a tensor shaped like the input view ([1,1,P,O] or [N,Ho,Wo,O])."""
+    c = w.shape[1] * groups
+    flat = x.dim() == 4 and x.shape[0] == 1 and x.shape[1] == 1 and x.shape[2] == batch * height * width
+
+    def fn(xx, ww, bb=None):
+        t = xx.reshape(batch, height, width, c).permute(0, 3, 1, 2)
+        pt, pl, pb, pr = padding
+        t = F.pad(t, (pl, pr, pt, pb))
+        r = F.conv2d(t, ww, bias=bb.reshape(-1) if bb is not None else None, stride=tuple(stride), padding=0,
+                     dilation=tuple(dilation), groups=groups)
+        r = r.permute(0, 2, 3, 1)
+        return r.reshape(1, 1, -1, r.shape[-1]) if flat else r
+    if bias is None:
+        return _hoist(fn, x.dtype, x, w)
+    return _hoist(fn, x.dtype, x, w, bias)
+
+
+# ---- normalisation / reductions -------------------------------------------------------------------
+def softmax(x, dim=-1):  # ttir_cpu.py:585
+    return _hoist(lambda t: F.softmax(t, dim=dim), x.dtype, x)
+
+
+def rms_norm(x, weight=None, bias=None, epsilon=1e-5):  # mapping.py:1221-1290
+    r = F.rms_norm(x.float(), normalized_shape=(x.shape[-1],), weight=weight, eps=epsilon)
+    if bias is not None:
+        r = torch.add(r, bias.float())
+    return r.to(x.dtype)
+
+
+def reduce(kind, x, dims, keep_dim):  # ttir_cpu.py:374-397
+    dims = tuple(dims) if dims else tuple(range(x.dim()))
+
+    def fn(t):
+        if kind == "Sum":
+            return torch.sum(t, dim=dims, keepdim=keep_dim)
+        if kind == "Mean":
+            return torch.mean(t, dim=dims, keepdim=keep_dim)
+        r = t
+        for d in sorted((d % t.dim() for d in dims), reverse=True):
+            r = (torch.max if kind == "Max" else torch.min)(r, dim=d, keepdim=keep_dim).values
+        return r
+    return _hoist(fn, x.dtype, x)
+
+
+# ---- data movement (ttir_cpu.py:449-495, 824-877) -----------------------------------------------------
+def concatenate_heads(x):
+    b, h, s, d = x.shape
+    return x.permute(0, 2, 1, 3).reshape(b, s, h * d)
+
+
+def split_qkv(x, kv, num_heads, num_kv_heads=None, transpose_key=False):
+    hkv = num_kv_heads if num_kv_heads is not None else num_heads
+    b, s = x.shape[0], x.shape[1]
+    d = x.shape[-1] // (num_heads + 2 * hkv) if kv is None else x.shape[-1] // num_heads
+    if kv is None:
+        q, k, v = x[:, :, :num_heads * d], x[:, :, num_heads * d:(num_heads + hkv) * d], x[:, :, (num_heads + hkv) * d:]
+    else:
+        q, k, v = x, kv[:, :, :hkv * d], kv[:, :, hkv * d:]
+    q = q.reshape(b, s, num_heads, d).permute(0, 2, 1, 3).contiguous()
+    k = k.reshape(b, s, hkv, d).permute(0, 2, 1, 3).contiguous()
+    v = v.reshape(b, s, hkv, d).permute(0, 2, 1, 3).contiguous()
+    if transpose_key:
+        k = k.transpose(-2, -1).contiguous()
+    return q, k, v
+
+
+def rotary_embedding(x, cos, sin):
+    """x*cos + rotate_half(x)*sin (lib/Dialect/TTNN/Transforms/Fusing/RoPEFusingPattern.cpp:49-51);
+    one op, so f32 math and a single rounding."""
+    def fn(t, c, s):
+        half = t.shape[-1] // 2
+        rot = torch.cat((-t[..., half:], t[..., :half]), dim=-1)
+        c = c.reshape(t.shape[-2], t.shape[-1])
+        s = s.reshape(t.shape[-2], t.shape[-1])
+        return t * c + rot * s
+    return _hoist(fn, x.dtype, x, cos, sin)
+
+
+def sdpa(q, k, v, is_causal=True, mask=None, scale=None):  # mapping.py:8398-8500
+    hq, hkv = q.shape[1], k.shape[1]
+    if hq != hkv:
+        k = torch.repeat_interleave(k, hq // hkv, dim=1)
+        v = torch.repeat_interleave(v, hq // hkv, dim=1)
+    if scale is None:
+        scale = 1.0 / (float(q.shape[-1]) ** 0.5)
+    qk = torch.matmul(q.float(), k.float().transpose(-2, -1))
+    qk = torch.mul(qk, scale)
+    if is_causal and mask is None:
+        sq, sk = qk.shape[-2], qk.shape[-1]
+        qk = torch.add(qk, torch.triu(torch.full((sq, sk), float("-inf")), diagonal=1))
+    if mask is not None:
+        qk = torch.add(qk, mask.float())
+    w = torch.softmax(qk, dim=-1)
+    return torch.matmul(w, v.float()).to(q.dtype)
+
+
+# ---- mesh (mapping.py:4189-4235, 5658-5794); a distributed value is a list of shards ------------------
+def mesh_shard_full_to_shard(x: torch.Tensor, n: int, shard_dim: Optional[int]) -> List[torch.Tensor]:
+    if shard_dim is None:
+        return [x.clone() for _ in range(n)]
+    return [c.contiguous() for c in torch.chunk(x, n, dim=shard_dim)]
+
+
+def mesh_shard_shard_to_full(shards: Sequence[torch.Tensor], shard_dim: Optional[int]) -> torch.Tensor:
+    if shard_dim is None:
+        return shards[0].clone()
+    return torch.cat(list(shards), dim=shard_dim)
+
+
+REDUCE = {0: lambda xs: torch.sum(torch.stack(xs), 0), 1: lambda xs: torch.mean(torch.stack(xs), 0),
+          2: lambda xs: torch.amax(torch.stack(xs), 0), 3: lambda xs: torch.amin(torch.stack(xs), 0)}
+
+
+def all_reduce(shards, reduce_type=0):
+    dt = shards[0].dtype
+    r = REDUCE[reduce_type]([s.float() for s in shards]).to(dt)
+    return [r.clone() for _ in shards]
+
+
+def all_gather(shards, dim):
+    g = torch.cat(list(shards), dim=dim)
+    return [g.clone() for _ in shards]
+
+
+def reduce_scatter(shards, dim, reduce_type=0):
+    dt = shards[0].dtype
+    r = REDUCE[reduce_type]([s.float() for s in shards]).to(dt)
+    return [c.contiguous() for c in torch.chunk(r, len(shards), dim=dim)]
+
+
+def mesh_partition(shards, dim):
+    n = len(shards)
+    return [torch.chunk(s, n, dim=dim)[i].contiguous() for i, s in enumerate(shards)]

@@ -1,0 +1,73 @@
+"""Shared helpers for the parity tests: run a graph through the runtime and through the oracle."""
+
+import torch
+
+from oracle import metrics
+from oracle.backend import OracleBuilder
+from ttmlir_b200 import graphs
+
+# Tolerances (floating point): PCC >= 0.999 and |got - want| <= atol + rtol*|want| with
+# atol 1e-2 / rtol 2^-7 (one bf16 ulp) for bf16 results, atol 1e-4 / rtol 1e-4 for f32.
+# Integer, quantized and index results must be bit-exact.
+TOL = {torch.bfloat16: (0.999, 1e-2, 2.0 ** -7), torch.float16: (0.999, 1e-2, 2.0 ** -7),
+       torch.float32: (0.999, 1e-4, 1e-4)}
+
+
+def assert_matches(got: torch.Tensor, want: torch.Tensor, what: str = "", tol=None):
+    assert list(got.shape) == list(want.shape), f"{what}: shape {list(got.shape)} != {list(want.shape)}"
+    assert got.dtype == want.dtype, f"{what}: dtype {got.dtype} != {want.dtype}"
+    if not want.is_floating_point():
+        bad = (got != want).sum().item()
+        assert bad == 0, f"{what}: {bad} of {want.numel()} integer elements differ"
+        return
+    pcc, atol, rtol = tol or TOL[want.dtype]
+    ok, report = metrics.check_close(want, got, pcc, atol, rtol)
+    assert ok, f"{what}: {report}"
+
+
+def run_program(rt, device, binary_bytes, inputs, program=0):
+    """ttrt-style run: load, to_layout every input, submit, to_host every output."""
+    binary = rt.Binary.load_from_memory(binary_bytes)
+    rt.set_compatible_device_runtime(binary)
+    ins = []
+    for i, t in enumerate(inputs):
+        h = rt.from_torch(t)
+        ins.append(rt.to_layout(h, device, rt.get_layout(binary, program, i)))
+    outs = rt.submit(device, binary, program, ins)
+    res = []
+    for o in outs:
+        hs = rt.to_host(o, untilize=True)
+        res.append(rt.to_torch(hs[0]))
+    return res
+
+
+def oracle_results(graph_fn, inputs, mesh_shape=(1, 1), **kw):
+    ob = OracleBuilder(inputs, mesh_shape=mesh_shape)
+    graph_fn(ob, **kw)
+    return ob.results()
+
+
+def check_graph(rt, device, graph_fn, inputs, what, tol=None, **kw):
+    buf = graphs.build_binary(graph_fn, **kw)
+    got = run_program(rt, device, buf, inputs)
+    want = oracle_results(graph_fn, inputs, **kw)
+    assert len(got) == len(want)
+    for i, (g, w) in enumerate(zip(got, want)):
+        assert_matches(g, w, f"{what} output {i}", tol)
+    return got, want
+
+
+DTYPE_NAME = {torch.float32: "Float32", torch.bfloat16: "BFloat16", torch.float16: "Float16", torch.int32: "Int32",
+              torch.int8: "Int8", torch.uint8: "UInt8"}
+
+
+def run_body(rt, device, body, inputs, mesh_shape=(1, 1)):
+    """Runs `body(b, *values)` (returning one value or a tuple) on the GPU and on the oracle."""
+    def graph(b):
+        vals = [b.input(list(t.shape), DTYPE_NAME[t.dtype]) for t in inputs]
+        out = body(b, *vals)
+        b.output(*(out if isinstance(out, (tuple, list)) else (out,)))
+    buf = graphs.build_binary(graph, mesh_shape=mesh_shape)
+    got = run_program(rt, device, buf, inputs)
+    want = oracle_results(graph, inputs, mesh_shape=mesh_shape)
+    return got, want

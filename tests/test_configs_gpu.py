@@ -1,0 +1,108 @@
+"""The five benchmark graphs through tt::runtime::submit, against the CPU oracle.
+
+Small shapes are compared element-wise with the oracle; the full benchmark shapes are checked
+through the oracle where it runs in seconds and through size-independent properties otherwise."""
+
+import pytest
+import torch
+
+from helpers import assert_matches, check_graph, oracle_results, run_program
+from ttmlir_b200 import graphs
+
+pytestmark = pytest.mark.gpu
+
+
+def test_config1_mlp_f32(rt, device):
+    ins = graphs.mlp_inputs()
+    got, want = check_graph(rt, device, graphs.mlp_graph, ins, "mlp")
+    assert torch.allclose(got[0].sum(dim=-1), torch.ones(128), atol=1e-5)
+
+
+@pytest.mark.parametrize("shape", [(1, 16), (3, 17), (33, 1000), (256, 4099)])
+@pytest.mark.parametrize("container", ["Int32", "Int8"])
+def test_config2_quant_chain_small(rt, device, shape, container):
+    ins = graphs.quant_chain_inputs(*shape)
+    for keep in (False, True):
+        got, want = check_graph(rt, device, graphs.quant_chain_graph, ins, "quant chain", rows=shape[0], cols=shape[1],
+                                container=container, keep_intermediates=keep)
+        for g, w in zip(got, want):
+            assert torch.equal(g, w)          # every tensor of the chain is bit-exact, the f32 result too
+
+
+def test_config2_quant_chain_full_size(rt, device):
+    ins = graphs.quant_chain_inputs()          # bf16 [4096, 4096], N(0,1), seed 1
+    got, want = check_graph(rt, device, graphs.quant_chain_graph, ins, "quant chain 4096", keep_intermediates=True)
+    for g, w in zip(got, want):
+        assert torch.equal(g, w)
+    y, q1, q2 = got
+    assert q1.min() >= -128 and q1.max() <= 127 and q2.min() >= -64 and q2.max() <= 64
+    assert torch.equal(y, q2.to(torch.float32) * torch.tensor(0.04, dtype=torch.float32))   # dequantize identity
+    # idempotence: quantizing the dequantized result with the output scale gives q2 back
+    again = torch.quantize_per_tensor(y, 0.04, 0, torch.qint8).int_repr().to(torch.int32)
+    assert torch.equal(again, q2)
+
+
+def test_config3_w8_linear_small(rt, device):
+    kw = dict(m=64, k=128, n=96)
+    check_graph(rt, device, graphs.w8_linear_graph, graphs.w8_linear_inputs(**kw), "w8 linear small", **kw)
+    kw = dict(m=256, k=512, n=384)
+    check_graph(rt, device, graphs.w8_linear_graph, graphs.w8_linear_inputs(**kw), "w8 linear medium", **kw)
+
+
+def test_config3_w8_linear_full_size(rt, device):
+    ins = graphs.w8_linear_inputs()
+    buf = graphs.build_binary(graphs.w8_linear_graph)
+    got = run_program(rt, device, buf, ins)[0]
+    assert list(got.shape) == [2048, 11008]
+    # the oracle on a slice of rows (the graph is row-independent) ...
+    rows = slice(0, 64)
+    want = oracle_results(graphs.w8_linear_graph, [ins[0][rows], ins[1], ins[2], ins[3]], m=64)[0]
+    assert_matches(got[rows], want, "w8 linear rows 0..63")
+    # ... and linearity in the activations over the whole output: f(2a) == 2 f(a) - bias
+    got2 = run_program(rt, device, buf, [ins[0] * 2, ins[1], ins[2], ins[3]])[0]
+    lin = 2 * got.float() - ins[3].float()
+    assert_matches(got2, lin.to(torch.bfloat16), "linearity", (0.999, 3e-2, 2.0 ** -6))
+
+
+DEC_SMALL = dict(seq=256, hidden=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024)
+
+
+def test_config4_decoder_block_small(rt, device):
+    ins = graphs.decoder_block_inputs(**DEC_SMALL)
+    # Chained bf16 ops: a one-ulp difference early on moves later roundings, so the end-to-end
+    # tolerance is two bf16 ulps relative plus the stated atol.
+    check_graph(rt, device, graphs.decoder_block_graph, ins, "decoder small", tol=(0.999, 2e-2, 2.0 ** -6), **DEC_SMALL)
+
+
+def test_config4_decoder_block_head_dim_64(rt, device):
+    kw = dict(seq=128, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512)
+    ins = graphs.decoder_block_inputs(**kw)
+    check_graph(rt, device, graphs.decoder_block_graph, ins, "decoder d64", tol=(0.999, 2e-2, 2.0 ** -6), **kw)
+
+
+def test_config4_decoder_block_full_size(rt, device):
+    ins = graphs.decoder_block_inputs()
+    buf = graphs.build_binary(graphs.decoder_block_graph)
+    got = run_program(rt, device, buf, ins)[0]
+    assert list(got.shape) == [1, 2048, 4096] and torch.isfinite(got.float()).all()
+    want = oracle_results(graphs.decoder_block_graph, ins)[0]
+    assert_matches(got, want, "decoder full", (0.999, 3e-2, 2.0 ** -6))
+    # causality: changing the last 1024 tokens leaves the first 1024 outputs untouched
+    ins2 = [t.clone() for t in ins]
+    ins2[0][:, 1024:] = torch.randn(1, 1024, 4096).to(torch.bfloat16)
+    got2 = run_program(rt, device, buf, ins2)[0]
+    assert torch.equal(got2[:, :1024], got[:, :1024])
+
+
+def test_config5_bottleneck_small(rt, device):
+    kw = dict(batch=2, hw=8)
+    check_graph(rt, device, graphs.bottleneck_graph, graphs.bottleneck_inputs(**kw), "bottleneck small",
+                tol=(0.999, 2e-2, 2.0 ** -6), **kw)
+    kw = dict(batch=3, hw=14)
+    check_graph(rt, device, graphs.bottleneck_graph, graphs.bottleneck_inputs(**kw), "bottleneck 14x14",
+                tol=(0.999, 2e-2, 2.0 ** -6), **kw)
+
+
+def test_config5_bottleneck_full_size(rt, device):
+    ins = graphs.bottleneck_inputs()
+    check_graph(rt, device, graphs.bottleneck_graph, ins, "bottleneck full", tol=(0.999, 3e-2, 2.0 ** -6))

@@ -1,0 +1,137 @@
+"""Pins the CPU oracle (oracle/ops.py) against outputs of the reference's own CPU code recorded
+in tests/golden/ttir_cpu_golden.npz (made by tests/golden/generate.py)."""
+
+import pytest
+import torch
+
+from oracle import metrics, ops
+
+UNARY = {"abs": "Abs", "ceil": "Ceil", "cos": "Cos", "floor": "Floor", "gelu": "Gelu", "neg": "Neg", "relu": "Relu",
+         "sigmoid": "Sigmoid", "sin": "Sin", "sign": "Sign", "tan": "Tan", "tanh": "Tanh", "atan": "Atan", "exp": "Exp",
+         "erf": "Erf", "erfc": "Erfc", "expm1": "Expm1", "relu6": "Relu6", "silu": "Silu", "hardsigmoid": "Hardsigmoid",
+         "mish": "Mish", "asinh": "Asinh", "cbrt": "Cbrt", "leaky_relu": "LeakyRelu"}
+UNARY_POS = {"sqrt": "Sqrt", "rsqrt": "Rsqrt", "reciprocal": "Reciprocal", "log": "Log", "log1p": "Log1p"}
+UNARY_UNIT = {"acos": "Acos", "asin": "Asin"}
+BINARY = {"add": "Add", "subtract": "Subtract", "multiply": "Multiply", "div": "Divide", "maximum": "Maximum",
+          "minimum": "Minimum", "eq": "Equal", "ne": "NotEqual", "gt": "GreaterThan", "ge": "GreaterEqual",
+          "lt": "LessThan", "le": "LessEqual"}
+
+
+def same(a, b):
+    return torch.equal(a, b) or torch.allclose(a.float(), b.float(), rtol=0, atol=0, equal_nan=True)
+
+
+@pytest.mark.parametrize("name", sorted(UNARY))
+def test_unary(golden, name):
+    assert same(ops.unary(UNARY[name], golden["unary/x"]), golden[f"unary/{name}"])
+
+
+@pytest.mark.parametrize("name", sorted(UNARY_POS))
+def test_unary_positive(golden, name):
+    assert same(ops.unary(UNARY_POS[name], golden["unary/xpos"]), golden[f"unary/{name}"])
+
+
+@pytest.mark.parametrize("name", sorted(UNARY_UNIT))
+def test_unary_unit(golden, name):
+    assert same(ops.unary(UNARY_UNIT[name], golden["unary/xunit"]), golden[f"unary/{name}"])
+
+
+@pytest.mark.parametrize("name", sorted(BINARY))
+def test_binary(golden, name):
+    got = ops.binary(BINARY[name], golden["binary/a"], golden["binary/b"])
+    assert same(got, golden[f"binary/{name}"])
+
+
+def test_binary_row_broadcast(golden):
+    assert same(ops.binary("Add", golden["binary/a"], golden["binary/row"]), golden["binary/add_row"])
+
+
+def test_matmul_linear(golden):
+    a, b, bias = golden["mm/a"], golden["mm/b"], golden["mm/bias"]
+    assert same(ops.matmul(a, b), golden["mm/matmul"])
+    assert same(ops.linear(a, b, bias), golden["mm/linear"])
+    assert same(ops.linear(a, golden["mm/bt"], bias, transpose_b=True), golden["mm/linear_tb"])
+    assert same(ops.matmul(golden["mm/ab"], golden["mm/bb"]), golden["mm/batched"])
+
+
+def test_softmax(golden):
+    assert same(ops.softmax(golden["softmax/x"], -1), golden["softmax/last"])
+    assert same(ops.softmax(golden["softmax/x"], 1), golden["softmax/mid"])
+
+
+def test_reductions(golden):
+    x = golden["reduce/x"]
+    assert same(ops.reduce("Sum", x, [2], False), golden["reduce/sum_last"])
+    assert same(ops.reduce("Mean", x, [1], True), golden["reduce/mean_mid_keep"])
+    assert same(ops.reduce("Max", x, [2], False), golden["reduce/max_last"])
+    assert same(ops.reduce("Min", x, [0], False), golden["reduce/min_first"])
+    assert same(ops.reduce("Sum", x, None, False).reshape(1), golden["reduce/sum_all"])
+
+
+def test_conv2d(golden):
+    x, w, b = golden["conv/x"], golden["conv/w"], golden["conv/b"]
+    assert same(ops.conv2d(x, w, b, 2, 9, 7, (1, 1), (1, 1, 1, 1)), golden["conv/same"])
+    assert same(ops.conv2d(x, w, b, 2, 9, 7, (2, 2), (0, 1, 1, 2)), golden["conv/stride2_asym"])
+    assert same(ops.conv2d(x, golden["conv/w1"], None, 2, 9, 7), golden["conv/pointwise"])
+    # the flattened [1,1,N*H*W,C] form the compiler emits gives the same numbers
+    flat = ops.conv2d(x.reshape(1, 1, -1, 8), w, b, 2, 9, 7, (1, 1), (1, 1, 1, 1))
+    assert same(flat.reshape(golden["conv/same"].shape), golden["conv/same"])
+
+
+def test_heads(golden):
+    q, k, v = ops.split_qkv(golden["heads/qkv"], None, 4, 2)
+    assert same(q, golden["heads/q"]) and same(k, golden["heads/k"]) and same(v, golden["heads/v"])
+    assert same(ops.concatenate_heads(q), golden["heads/merged"])
+
+
+def test_typecast(golden):
+    x = golden["cast/x"]
+    assert same(ops.typecast(x, torch.bfloat16), golden["cast/to_bf16"])
+    assert same(ops.typecast(x, torch.int32), golden["cast/to_i32"])
+
+
+@pytest.mark.parametrize("tag,scale,zp", [("s002_z0", 0.02, 0), ("s0037_z3", 0.037, 3)])
+def test_quantization_bit_exact(golden, tag, scale, zp):
+    x = golden["quant/x"]
+    q8 = ops.quantize(x, scale, zp, torch.int8)
+    assert torch.equal(q8, golden[f"quant/{tag}/q_i8"])
+    # int32 container, values clamped to the int8 range (how the compiler stores quantized tensors)
+    assert torch.equal(ops.quantize(x, scale, zp, torch.int32, clamp_i8=True), golden[f"quant/{tag}/q_i8"].to(torch.int32))
+    assert torch.equal(ops.quantize(x, scale, zp, torch.int32, clamp_i8=False), golden[f"quant/{tag}/q_i32"])
+    assert torch.equal(ops.dequantize(q8, scale, zp), golden[f"quant/{tag}/deq"])
+    rq = ops.requantize(q8, scale, zp, scale * 2, zp + 1)
+    assert torch.equal(rq, golden[f"quant/{tag}/requant_i8"])
+    assert torch.equal(ops.dequantize(rq, scale * 2, zp + 1), golden[f"quant/{tag}/requant_deq"])
+
+
+def test_quantization_ties_round_to_even(golden):
+    x = golden["quant/x"].reshape(-1)[:5]
+    q = ops.quantize(x, 0.02, 0, torch.int8)
+    assert q.tolist() == [12, 38, 62, 127, -128]  # 12.5 -> 12, 37.5 -> 38, 62.5 -> 62, clamps
+
+
+def test_quantization_per_channel(golden):
+    x, s = golden["quant/x"], golden["quant/ch_scale"]
+    q = ops.quantize_per_axis(x, s, None, 0, torch.int8)
+    assert torch.equal(q, golden["quant/per_channel_q"])
+    assert torch.equal(ops.dequantize_per_axis(q, s, None, 0), golden["quant/per_channel_deq"])
+
+
+def test_rms_norm(golden):
+    assert same(ops.rms_norm(golden["rms/x"], golden["rms/w"], None, 1e-5), golden["rms/out"])
+
+
+def test_sdpa(golden):
+    q, k, v = golden["sdpa/q"], golden["sdpa/k"], golden["sdpa/v"]
+    assert torch.allclose(ops.sdpa(q, k, v, True), golden["sdpa/causal"], atol=1e-6)
+    assert torch.allclose(ops.sdpa(q, k, v, False), golden["sdpa/full"], atol=1e-6)
+
+
+def test_metrics_special_cases():
+    a = torch.tensor([1.0, 2.0, 3.0])
+    assert metrics.get_pcc(a, a) == 1.0
+    assert metrics.get_pcc(a, -a) < -0.99
+    assert metrics.get_pcc(torch.zeros(0), torch.zeros(0)) == 1.0
+    assert metrics.get_pcc(torch.zeros(4), torch.ones(4)) == 0.0
+    at, rt_ = metrics.get_atol_rtol(a, a + 0.5)
+    assert abs(at - 0.5) < 1e-6

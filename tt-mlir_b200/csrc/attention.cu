@@ -327,6 +327,8 @@ extern "C" int ttb_sdpa(const void *q, const void *k, const void *v, const void 
     dim3 grid(static_cast<unsigned>((seq_q + FA_BM - 1) / FA_BM), static_cast<unsigned>(heads_q),
               static_cast<unsigned>(batch));
     float scaleLog2 = scale * 1.4426950408889634f;
+    double work = 4.0 * double(batch) * heads_q * seq_q * seq_kv * head_dim * (is_causal ? 0.5 : 1.0);
+    ProfScope prof("sdpa_flash", work, 2.0 * batch * (2.0 * heads_q * seq_q + 2.0 * heads_kv * seq_kv) * head_dim, st);
     if (dtype == kBF16) {
       static bool attr = false;
       if (!attr) {
@@ -355,6 +357,7 @@ extern "C" int ttb_sdpa(const void *q, const void *k, const void *v, const void 
   TTB_CHECK(smem <= 200 * 1024, "sequence too long for the general attention kernel");
   TTB_CHECK(seq_q <= 2147483647, "sequence too long");
   dim3 grid(static_cast<unsigned>(seq_q), static_cast<unsigned>(heads_q), static_cast<unsigned>(batch));
+  ProfScope prof("sdpa_generic", 4.0 * double(batch) * heads_q * seq_q * seq_kv * head_dim, 0, st);
   TTB_DISPATCH_FLOAT(dtype, T, {
     if (smem > 48 * 1024) {
       TTB_CUDA(cudaFuncSetAttribute(genericKernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));

@@ -174,6 +174,7 @@ int ttb_all_reduce(void *comm, const void *in, void *out, size_t count, int dtyp
   ncclRedOp_t op;
   if (!ncclType(dtype, dt)) { setLastError("all_reduce: unsupported dtype"); return TTB_ERR_UNSUPPORTED; }
   if (!ncclOp(reduce_type, op)) { setLastError("all_reduce: unsupported reduce type (Std/Var)"); return TTB_ERR_UNSUPPORTED; }
+  ProfScope prof("nccl_all_reduce", 0, double(count) * dtypeSize(dtype), asStream(stream));
   TTB_NCCL(api.allReduce(in, out, count, dt, op, static_cast<ncclComm_t>(comm), asStream(stream)));
   countLaunch();
   return TTB_OK;
@@ -184,6 +185,7 @@ int ttb_all_gather(void *comm, const void *in, void *out, size_t send_count, int
   TTB_NCCL_READY();
   ncclDataType_t dt;
   if (!ncclType(dtype, dt)) { setLastError("all_gather: unsupported dtype"); return TTB_ERR_UNSUPPORTED; }
+  ProfScope prof("nccl_all_gather", 0, double(send_count) * dtypeSize(dtype), asStream(stream));
   TTB_NCCL(api.allGather(in, out, send_count, dt, static_cast<ncclComm_t>(comm), asStream(stream)));
   countLaunch();
   return TTB_OK;
@@ -197,6 +199,7 @@ int ttb_reduce_scatter(void *comm, const void *in, void *out, size_t recv_count,
   ncclRedOp_t op;
   if (!ncclType(dtype, dt)) { setLastError("reduce_scatter: unsupported dtype"); return TTB_ERR_UNSUPPORTED; }
   if (!ncclOp(reduce_type, op)) { setLastError("reduce_scatter: unsupported reduce type"); return TTB_ERR_UNSUPPORTED; }
+  ProfScope prof("nccl_reduce_scatter", 0, double(recv_count) * dtypeSize(dtype), asStream(stream));
   TTB_NCCL(api.reduceScatter(in, out, recv_count, dt, op, static_cast<ncclComm_t>(comm), asStream(stream)));
   countLaunch();
   return TTB_OK;

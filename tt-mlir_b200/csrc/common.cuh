@@ -63,6 +63,16 @@ int smCount();
 // Adds to the process-wide count of kernels launched by this library.
 void countLaunch(uint64_t n = 1);
 
+// Optional per-launch timing.  When profiling is on (ttb_prof_enable), a ProfScope around a
+// launch records a CUDA event pair on the launching stream together with the algorithmic work
+// of that launch; ttb_prof_summary aggregates them per tag.  Off: one relaxed atomic load.
+struct ProfScope {
+  ProfScope(const char *tag, double flops, double bytes, cudaStream_t stream);
+  ~ProfScope();
+  int slot;
+  cudaStream_t stream;
+};
+
 // Grid for a grid-stride kernel: enough blocks for `items`, capped at a few waves of the GPU.
 inline int gridFor(size_t items, int block, int blocksPerSm = 16) {
   size_t need = (items + block - 1) / block;

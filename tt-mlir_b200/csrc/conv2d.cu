@@ -104,6 +104,7 @@ int ttb_conv2d(const void *x, const void *weight, const void *bias, void *out, i
     if (rc) return rc;
   }
   int vec = static_cast<int>(16 / es);
+  ProfScope prof("conv2d_im2col", 0, double(P) * K * es + double(n) * h * w * c * es, st);
   if (c % vec == 0 && aligned16(x) && aligned16(col)) {
     int64_t total = P * kh * kw * (c / vec);
     int grid = gridFor(static_cast<size_t>(total), 256);

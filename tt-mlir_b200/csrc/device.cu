@@ -1,8 +1,12 @@
 // Device, stream, memory and event entry points of the C ABI, plus error bookkeeping.
 #include "common.cuh"
 
+#include <cstring>
+
 #include <atomic>
+#include <map>
 #include <mutex>
+#include <vector>
 
 namespace ttb {
 
@@ -35,6 +39,32 @@ int smCount() {
 
 void countLaunch(uint64_t n) { g_launchCount.fetch_add(n, std::memory_order_relaxed); }
 
+// ---- per-launch profiling ----------------------------------------------------------------
+struct ProfRecord {
+  const char *tag;
+  double flops, bytes;
+  cudaEvent_t start, stop;
+};
+static std::atomic<bool> g_profOn{false};
+static std::mutex g_profMutex;
+static std::vector<ProfRecord> g_profRecords;
+
+ProfScope::ProfScope(const char *tag, double flops, double bytes, cudaStream_t st) : slot(-1), stream(st) {
+  if (!g_profOn.load(std::memory_order_relaxed)) return;
+  ProfRecord r{tag, flops, bytes, nullptr, nullptr};
+  if (cudaEventCreate(&r.start) != cudaSuccess || cudaEventCreate(&r.stop) != cudaSuccess) return;
+  cudaEventRecord(r.start, st);
+  std::lock_guard<std::mutex> g(g_profMutex);
+  g_profRecords.push_back(r);
+  slot = static_cast<int>(g_profRecords.size()) - 1;
+}
+
+ProfScope::~ProfScope() {
+  if (slot < 0) return;
+  std::lock_guard<std::mutex> g(g_profMutex);
+  if (slot < static_cast<int>(g_profRecords.size())) cudaEventRecord(g_profRecords[slot].stop, stream);
+}
+
 } // namespace ttb
 
 using namespace ttb;
@@ -46,6 +76,47 @@ const char *ttb_last_error(void) { return g_lastError.c_str(); }
 size_t ttb_dtype_size(int dtype) { return dtypeSize(dtype); }
 
 uint64_t ttb_launch_count(void) { return g_launchCount.load(std::memory_order_relaxed); }
+
+int ttb_prof_enable(int on) {
+  std::lock_guard<std::mutex> g(g_profMutex);
+  for (ProfRecord &r : g_profRecords) {
+    if (r.start) cudaEventDestroy(r.start);
+    if (r.stop) cudaEventDestroy(r.stop);
+  }
+  g_profRecords.clear();
+  g_profOn.store(on != 0);
+  return TTB_OK;
+}
+
+int ttb_prof_summary(char *json_out, size_t cap) {
+  TTB_CHECK(json_out && cap > 2, "output buffer missing");
+  std::lock_guard<std::mutex> g(g_profMutex);
+  struct Agg { long launches = 0; double ms = 0, flops = 0, bytes = 0; };
+  std::map<std::string, Agg> agg;
+  for (ProfRecord &r : g_profRecords) {
+    TTB_CUDA(cudaEventSynchronize(r.stop));
+    float ms = 0.0f;
+    TTB_CUDA(cudaEventElapsedTime(&ms, r.start, r.stop));
+    Agg &a = agg[r.tag];
+    a.launches++;
+    a.ms += ms;
+    a.flops += r.flops;
+    a.bytes += r.bytes;
+  }
+  std::string s = "[";
+  bool first = true;
+  for (const auto &kv : agg) {
+    char buf[256];
+    snprintf(buf, sizeof buf, "%s{\"tag\": \"%s\", \"launches\": %ld, \"ms\": %.6f, \"flops\": %.6e, \"bytes\": %.6e}",
+             first ? "" : ", ", kv.first.c_str(), kv.second.launches, kv.second.ms, kv.second.flops, kv.second.bytes);
+    s += buf;
+    first = false;
+  }
+  s += "]";
+  TTB_CHECK(s.size() + 1 <= cap, "output buffer too small");
+  memcpy(json_out, s.c_str(), s.size() + 1);
+  return TTB_OK;
+}
 
 int ttb_device_count(int *count) {
   TTB_CHECK(count != nullptr, "count is null");

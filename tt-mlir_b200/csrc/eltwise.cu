@@ -414,6 +414,7 @@ int ttb_eltwise_unary(int op, const void *in, int in_dtype, void *out, int out_d
   TTB_CHECK((op >= 0 && op < uCount) || op == uCbrt || op == uLog1p, "unknown unary op");
   if (n == 0) return TTB_OK;
   cudaStream_t st = asStream(stream);
+  ProfScope prof("eltwise_unary", 0, double(n) * (dtypeSize(in_dtype) + dtypeSize(out_dtype)), st);
   bool vec = in_dtype == out_dtype && aligned16(in) && aligned16(out) && op != uBitwiseNot;
   if (vec && in_dtype == kBF16) {
     unaryVecKernel<__nv_bfloat16><<<gridFor((n + kVec - 1) / kVec, 256), 256, 0, st>>>(
@@ -442,6 +443,7 @@ int ttb_eltwise_binary(int op, const void *a, int a_dtype, const void *b, int b_
   cudaStream_t st = asStream(stream);
   bool floatOp = op == bAdd || op == bMultiply || op == bSubtract || op == bDivide || op == bMaximum ||
                  op == bMinimum || (op >= bEqual && op <= bLessThan);
+  ProfScope prof("eltwise_binary", 0, double(n) * (dtypeSize(a_dtype) + dtypeSize(b_dtype) + dtypeSize(out_dtype)), st);
   size_t aCnt = trailingDenseCount(rank, out_shape, a_strides);
   size_t bCnt = trailingDenseCount(rank, out_shape, b_strides);
   bool vec = floatOp && a_dtype == b_dtype && a_dtype == out_dtype && (a_dtype == kBF16 || a_dtype == kF32) &&
@@ -497,6 +499,7 @@ int ttb_typecast(const void *in, int in_dtype, void *out, int out_dtype, size_t 
     return ttb_memcpy_d2d(out, in, n * dtypeSize(in_dtype), stream);
   }
   int grid = gridFor((n + kVec - 1) / kVec, 256);
+  ProfScope prof("typecast", 0, double(n) * (dtypeSize(in_dtype) + dtypeSize(out_dtype)), asStream(stream));
   TTB_DISPATCH_DTYPE(in_dtype, TI, TTB_DISPATCH_DTYPE(out_dtype, TO, {
     typecastKernel<TI, TO><<<grid, 256, 0, asStream(stream)>>>(static_cast<const TI *>(in),
                                                                static_cast<TO *>(out), n);
@@ -543,6 +546,7 @@ int ttb_silu_mul(const void *gate, const void *up, void *out, int dtype, size_t 
   TTB_CHECK(aligned16(gate) && aligned16(up) && aligned16(out), "tensors must be 16-byte aligned");
   if (n == 0) return TTB_OK;
   int grid = gridFor((n + kVec - 1) / kVec, 256);
+  ProfScope prof("silu_mul", 0, double(n) * 3 * dtypeSize(dtype), asStream(stream));
   TTB_DISPATCH_FLOAT(dtype, T, {
     siluMulKernel<T><<<grid, 256, 0, asStream(stream)>>>(static_cast<const T *>(gate), static_cast<const T *>(up),
                                                          static_cast<T *>(out), n);

@@ -77,6 +77,7 @@ static int launchSimt(const void *a, const void *b, const void *bias, int biasDt
             static_cast<unsigned>(batch));
   int64_t asM = ta ? 1 : k, asK = ta ? m : 1;
   int64_t bsK = tb ? 1 : n, bsN = tb ? k : 1;
+  ProfScope prof("gemm_simt", 2.0 * double(batch) * m * n * k, double(batch) * (double(m) * k + double(n) * k) * sizeof(T) + double(batch) * m * n * sizeof(TC), st);
   gemmSimtKernel<T, TC><<<grid, 256, 0, st>>>(static_cast<const T *>(a), static_cast<const T *>(b), bias, biasDt,
                                               static_cast<TC *>(c), m, n, k, asM, asK, bsK, bsN, aBatch, bBatch, act,
                                               roundSteps);

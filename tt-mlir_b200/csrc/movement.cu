@@ -88,6 +88,7 @@ static int launchStrided(const void *in, void *out, int elemSize, int rank, cons
     d.stride[i] = sd[i];
   }
   int grid = gridFor(n, 256);
+  ProfScope prof(SCATTER ? "strided_scatter" : "strided_copy", 0, 2.0 * double(n) * unit, st);
   switch (unit) {
   case 1: stridedCopyKernel<uint8_t, SCATTER><<<grid, 256, 0, st>>>(static_cast<const uint8_t *>(in), static_cast<uint8_t *>(out), n, d, offset); break;
   case 2: stridedCopyKernel<uint16_t, SCATTER><<<grid, 256, 0, st>>>(static_cast<const uint16_t *>(in), static_cast<uint16_t *>(out), n, d, offset); break;
@@ -158,6 +159,7 @@ int ttb_rotary_embedding(const void *x, const void *cos, const void *sin, void *
   TTB_CHECK(head_dim % (2 * (16 / es)) == 0, "head_dim/2 must be a multiple of 16 bytes");
   size_t total = batch_heads * seq * (head_dim / 2 / (16 / es));
   if (total == 0) return TTB_OK;
+  ProfScope prof("rotary_embedding", 0, 2.0 * double(batch_heads) * seq * head_dim * es, asStream(stream));
   TTB_DISPATCH_FLOAT(dtype, T, {
     ropeKernel<T><<<gridFor(total, 256), 256, 0, asStream(stream)>>>(
         static_cast<const T *>(x), static_cast<const T *>(cos), static_cast<const T *>(sin), static_cast<T *>(out),

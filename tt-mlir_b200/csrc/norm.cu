@@ -174,6 +174,7 @@ int launchRms(const void *a, const void *b, const void *w, const void *bias, voi
   auto S = static_cast<T *>(sumOut), O = static_cast<T *>(out);
   bool al = aligned16(a) && aligned16(b) && aligned16(w) && aligned16(out) && aligned16(sumOut);
   int grid = static_cast<int>(rows);
+  ProfScope prof(RES ? "add_rms_norm" : "rms_norm", 0, double(rows) * cols * sizeof(T) * ((RES ? 3 : 2) + (sumOut ? 1 : 0)), st);
   if (al && cols % 16 == 0 && cols <= 256 * 16) {
     rmsNormKernel<T, 1, RES><<<grid, 256, 0, st>>>(A, B, W, Bi, S, O, cols, eps);
   } else if (al && cols % 16 == 0 && cols <= 256 * 16 * 2) {
@@ -236,6 +237,7 @@ int ttb_softmax(const void *in, void *out, int dtype, size_t outer, size_t len, 
   TTB_CHECK(in && out, "null tensor");
   if (outer * len * inner == 0) return TTB_OK;
   cudaStream_t st = asStream(stream);
+  ProfScope prof("softmax", 0, double(outer) * len * inner * 2 * dtypeSize(dtype), st);
   TTB_DISPATCH_FLOAT(dtype, T, {
     if (inner == 1) {
       int grid = static_cast<int>((outer + 7) / 8);

@@ -192,6 +192,7 @@ int ttb_quantize(const void *in, int in_dtype, void *out, int out_dtype, size_t 
   if (n == 0) return TTB_OK;
   float inv = 1.0f / scale;
   int grid = gridFor((n + kVec - 1) / kVec, 256);
+  ProfScope prof("quantize", 0, double(n) * (dtypeSize(in_dtype) + dtypeSize(out_dtype)), asStream(stream));
   TTB_DISPATCH_FLOAT(in_dtype, TI, TTB_DISPATCH_INT(out_dtype, TQ, {
     quantizeKernel<TI, TQ><<<grid, 256, 0, asStream(stream)>>>(
         static_cast<const TI *>(in), static_cast<TQ *>(out), n, inv, zero_point, qrangeOf<TQ>(clamp_i8));
@@ -207,6 +208,7 @@ int ttb_dequantize(const void *in, int in_dtype, void *out, int out_dtype, size_
   TTB_CHECK(vecOk(in, out), "tensors must be 16-byte aligned");
   if (n == 0) return TTB_OK;
   int grid = gridFor((n + kVec - 1) / kVec, 256);
+  ProfScope prof("dequantize", 0, double(n) * (dtypeSize(in_dtype) + dtypeSize(out_dtype)), asStream(stream));
   TTB_DISPATCH_INT(in_dtype, TQ, TTB_DISPATCH_FLOAT(out_dtype, TO, {
     dequantizeKernel<TQ, TO><<<grid, 256, 0, asStream(stream)>>>(
         static_cast<const TQ *>(in), static_cast<TO *>(out), n, scale, zero_point);
@@ -224,6 +226,7 @@ int ttb_requantize(const void *in, int in_dtype, void *out, int out_dtype, size_
   if (n == 0) return TTB_OK;
   float inv = 1.0f / out_scale;
   int grid = gridFor((n + kVec - 1) / kVec, 256);
+  ProfScope prof("requantize", 0, double(n) * (dtypeSize(in_dtype) + dtypeSize(out_dtype)), asStream(stream));
   TTB_DISPATCH_INT(in_dtype, TA, TTB_DISPATCH_INT(out_dtype, TB, {
     requantizeKernel<TA, TB><<<grid, 256, 0, asStream(stream)>>>(
         static_cast<const TA *>(in), static_cast<TB *>(out), n, in_scale, in_zp, inv, out_zp,
@@ -297,6 +300,7 @@ int launchChain(const void *in, void *q1, void *q2, void *out, size_t n, float s
   auto A = static_cast<T1 *>(q1);
   auto B = static_cast<T2 *>(q2);
   auto O = static_cast<TO *>(out);
+  ProfScope prof("quant_chain", 0, double(n) * (sizeof(TI) + sizeof(TO) + (q1 ? sizeof(T1) : 0) + (q2 ? sizeof(T2) : 0)), st);
   if (q1 && q2)
     quantChainKernel<TI, T1, T2, TO, true, true><<<grid, 256, 0, st>>>(I, A, B, O, n, inv1, s1, zp1, inv2, s2, zp2, r1, r2);
   else if (q1)

@@ -1,0 +1,593 @@
+"""Authoring TTNN flatbuffers (.ttnn) without the tt-mlir compiler.
+
+The reference produces these files with `ttmlir-opt --ttir-to-ttnn-backend-pipeline` followed by
+`ttmlir-translate --ttnn-to-flatbuffer` (lib/Target/TTNN/TTNNToFlatbuffer.cpp); neither tool can
+be built where this repo is developed, so this module writes the same wire format directly.
+It mirrors what the serialiser emits for the optimizer-off pipeline:
+
+* one `TensorRef` table per SSA value, ids assigned in emission order, the same table shared by
+  the producing op's `out` and every consumer (TTNNToFlatbuffer.cpp:141-167 and
+  include/ttmlir/Target/Utils/FlatbufferObjectCache.h);
+* device tensors are DRAM / interleaved / tile (32x32), host tensors row-major (1x1);
+* a `GetDeviceOp` first, a `DeallocateOp` after the last use of every intermediate
+  (lib/Dialect/TTNN/Pipelines/TTNNPipelines.cpp:521), `debug_info` = a printed op,
+  `loc_info` = the op's location string (include/ttmlir/Target/Utils/FuncOpToProgram.h:191-196);
+* multi-device programs carry `mesh_shape` and start / end with DistributeTensorOp /
+  AggregateTensorOp the way `ttir.mesh_shard` lowers (lib/Conversion/TTIRToTTNN/TTIRToTTNN.cpp:2753-2888).
+
+What it cannot reproduce is the schema hash (see schema/ttnn_schema.py).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional, Sequence, Tuple
+
+from .schema.fbs import Writer
+from .schema.ttnn_schema import FILE_IDENTIFIER, S, SCHEMA_HASH
+
+ITEMSIZE = {"Float32": 4, "Float16": 2, "BFloat16": 2, "UInt32": 4, "UInt16": 2, "UInt8": 1, "Int32": 4, "Int8": 1}
+
+
+class Value:
+    """An SSA value: shape, dtype and the TensorRef dict every user shares."""
+
+    def __init__(self, ref: dict, shape: Sequence[int], dtype: str, on_device: bool):
+        self.ref = ref
+        self.shape = list(shape)
+        self.dtype = dtype
+        self.on_device = on_device
+
+    @property
+    def id(self) -> int:
+        return self.ref["global_id"]
+
+    def __repr__(self):
+        return f"%{self.id}:{self.dtype}{self.shape}"
+
+
+def _volume(shape):
+    v = 1
+    for d in shape:
+        v *= d
+    return v
+
+
+def _norm(dim, rank):
+    return dim + rank if dim < 0 else dim
+
+
+def _broadcast(a, b):
+    out = []
+    ra, rb = list(reversed(a)), list(reversed(b))
+    for i in range(max(len(a), len(b))):
+        x = ra[i] if i < len(ra) else 1
+        y = rb[i] if i < len(rb) else 1
+        if x != y and x != 1 and y != 1:
+            raise ValueError(f"shapes {a} and {b} do not broadcast")
+        out.append(max(x, y))
+    return list(reversed(out))
+
+
+class ProgramBuilder:
+    def __init__(self, binary: "BinaryBuilder", name: str, mesh_shape: Tuple[int, int] = (1, 1)):
+        self._bin = binary
+        self.name = name
+        self.mesh_shape = tuple(mesh_shape)
+        self.inputs: List[Value] = []
+        self.outputs: List[Value] = []
+        self.ops: List[dict] = []
+        self._op_values: List[Tuple[List[Value], List[Value]]] = []
+        self.device_ref = {"global_id": binary.next_id()}
+        self._emit("GetDeviceOp", {"mesh": self.mesh_shape, "offset": (0, 0),
+                                   "chip_ids": list(range(self.mesh_shape[0] * self.mesh_shape[1])),
+                                   "out": self.device_ref}, [], [], "get_device")
+
+    # ---- plumbing ---------------------------------------------------------------------------
+    def _value(self, shape, dtype, on_device=True, tile=None) -> Value:
+        if tile is None:
+            tile = on_device
+        multi = self.mesh_shape[0] * self.mesh_shape[1] > 1 and on_device
+        ref = {
+            "global_id": self._bin.next_id(),
+            "desc": {
+                "shape": list(shape),
+                "mesh_shape": list(self.mesh_shape) if multi else [1, 1],
+                "layout": {
+                    "oob_val": "Undef",
+                    "memory_desc": {
+                        "storage_type": "Device" if on_device else "Host",
+                        "tile_shape": (32, 32) if tile else (1, 1),
+                        "data_type": dtype,
+                        "memory_config": {"tensor_memory_layout": "Interleaved", "buffer_type": "DRAM"}
+                        if on_device else None,
+                    },
+                },
+                "shard_status": "Unsharded",
+                "local_shape": list(shape),
+            },
+        }
+        return Value(ref, shape, dtype, on_device)
+
+    def _emit(self, op_type: str, table: dict, ins: List[Value], outs: List[Value], loc: Optional[str]):
+        idx = len(self.ops)
+        loc = loc or f"{op_type}_{idx}"
+        ins_s = ", ".join(f"%{v.id}" for v in ins)
+        outs_s = ", ".join(f"%{v.id}" for v in outs)
+        snake = op_type[:-2] if op_type.endswith("Op") else op_type
+        dbg = f'{outs_s + " = " if outs_s else ""}"ttnn.{snake}"({ins_s})'
+        self.ops.append({"type": (op_type, table), "debug_info": dbg, "loc_info": f'loc("{loc}")'})
+        self._op_values.append((ins, outs))
+
+    def _mc(self):
+        return {"tensor_memory_layout": "Interleaved", "buffer_type": "DRAM"}
+
+    # ---- program interface ------------------------------------------------------------------
+    def input(self, shape, dtype: str, on_device: bool = True) -> Value:
+        v = self._value(shape, dtype, on_device)
+        self.inputs.append(v)
+        return v
+
+    def output(self, *values: Value):
+        self.outputs.extend(values)
+
+    # ---- layout / creation -------------------------------------------------------------------
+    def to_device(self, x: Value, loc=None) -> Value:
+        out = self._value(x.shape, x.dtype, True, tile=False)
+        self._emit("ToDeviceOp", {"in": x.ref, "device": self.device_ref, "memcfg": self._mc(), "out": out.ref},
+                   [x], [out], loc)
+        return out
+
+    def from_device(self, x: Value, loc=None) -> Value:
+        out = self._value(x.shape, x.dtype, False)
+        self._emit("FromDeviceOp", {"in": x.ref, "out": out.ref}, [x], [out], loc)
+        return out
+
+    def to_layout(self, x: Value, layout: str = "Tile", dtype: Optional[str] = None, on_device: Optional[bool] = None,
+                  loc=None) -> Value:
+        dev = x.on_device if on_device is None else on_device
+        out = self._value(x.shape, dtype or x.dtype, dev, tile=(layout == "Tile"))
+        self._emit("ToLayoutOp", {"in": x.ref, "layout": layout, "dtype": dtype, "memcfg": self._mc() if dev else None,
+                                  "out": out.ref}, [x], [out], loc)
+        return out
+
+    def typecast(self, x: Value, dtype: str, loc=None) -> Value:
+        out = self._value(x.shape, dtype)
+        self._emit("TypecastOp", {"in": x.ref, "dtype": dtype, "memcfg": self._mc(), "out": out.ref}, [x], [out], loc)
+        return out
+
+    def full(self, shape, value, dtype: str, loc=None) -> Value:
+        out = self._value(shape, dtype)
+        fv = ("FP", {"value": float(value)}) if isinstance(value, float) else ("I32", {"value": int(value)})
+        self._emit("FullOp", {"device": self.device_ref, "shape": list(shape), "fill_value": fv, "dtype": dtype,
+                              "layout": "Tile", "memcfg": self._mc(), "out": out.ref}, [], [out], loc)
+        return out
+
+    def zeros(self, shape, dtype: str, loc=None) -> Value:
+        out = self._value(shape, dtype)
+        self._emit("NamedFullOp", {"type": "Zeros", "device": self.device_ref, "shape": list(shape), "dtype": dtype,
+                                   "layout": "Tile", "memcfg": self._mc(), "out": out.ref}, [], [out], loc)
+        return out
+
+    def ones(self, shape, dtype: str, loc=None) -> Value:
+        out = self._value(shape, dtype)
+        self._emit("NamedFullOp", {"type": "Ones", "device": self.device_ref, "shape": list(shape), "dtype": dtype,
+                                   "layout": "Tile", "memcfg": self._mc(), "out": out.ref}, [], [out], loc)
+        return out
+
+    def constant(self, data: bytes, shape, dtype: str, loc=None) -> Value:
+        assert len(data) == _volume(shape) * ITEMSIZE[dtype]
+        out = self._value(shape, dtype)
+        self._emit("ConstantOp", {"device": self.device_ref, "input": data, "input_dtype": dtype, "dtype": dtype,
+                                  "layout": "Tile", "memcfg": self._mc(), "out": out.ref}, [], [out], loc)
+        return out
+
+    def arange(self, start, end, step, dtype: str, loc=None) -> Value:
+        n = max(0, int(math.ceil((end - start) / step)))
+        out = self._value([n], dtype)
+        self._emit("ArangeOp", {"device": self.device_ref, "start": float(start), "end": float(end),
+                                "step": float(step), "dtype": dtype, "layout": "Tile", "memcfg": self._mc(),
+                                "out": out.ref}, [], [out], loc)
+        return out
+
+    def deallocate(self, x: Value, force: bool = False):
+        self._emit("DeallocateOp", {"in": x.ref, "force": force}, [x], [], None)
+
+    # ---- eltwise --------------------------------------------------------------------------------
+    def unary(self, kind: str, x: Value, param: Optional[float] = None, loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        t = {"type": kind, "in": x.ref, "memory_config": self._mc(), "out": out.ref}
+        if param is not None:
+            t["params"] = ("EltwiseOpWithFloatParams", {"parameter": float(param)})
+        self._emit("EltwiseUnaryOp", t, [x], [out], loc)
+        return out
+
+    def relu(self, x, loc=None): return self.unary("Relu", x, loc=loc)
+    def silu(self, x, loc=None): return self.unary("Silu", x, loc=loc)
+    def exp(self, x, loc=None): return self.unary("Exp", x, loc=loc)
+    def neg(self, x, loc=None): return self.unary("Neg", x, loc=loc)
+    def sigmoid(self, x, loc=None): return self.unary("Sigmoid", x, loc=loc)
+
+    def clamp(self, x: Value, lo: float, hi: float, loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        self._emit("EltwiseUnaryCompositeOp", {
+            "type": "ClampScalar", "in": x.ref, "memory_config": self._mc(), "out": out.ref,
+            "params": ("ClampScalarOpParams", {"min": ("FP", {"value": float(lo)}), "max": ("FP", {"value": float(hi)})})},
+            [x], [out], loc)
+        return out
+
+    def binary(self, kind: str, a: Value, b: Value, dtype: Optional[str] = None, loc=None) -> Value:
+        out = self._value(_broadcast(a.shape, b.shape), dtype or a.dtype)
+        composite = kind in S.enums["EltwiseBinaryCompositeOpType"].values
+        if composite:
+            self._emit("EltwiseBinaryCompositeOp", {"type": kind, "lhs": a.ref, "rhs": b.ref,
+                                                    "memory_config": self._mc(), "out": out.ref}, [a, b], [out], loc)
+        else:
+            self._emit("EltwiseBinaryOp", {"type": kind, "lhs": a.ref, "rhs": b.ref, "output_dtype": dtype,
+                                           "memory_config": self._mc(), "out": out.ref}, [a, b], [out], loc)
+        return out
+
+    def add(self, a, b, loc=None): return self.binary("Add", a, b, loc=loc)
+    def multiply(self, a, b, loc=None): return self.binary("Multiply", a, b, loc=loc)
+    def subtract(self, a, b, loc=None): return self.binary("Subtract", a, b, loc=loc)
+    def divide(self, a, b, loc=None): return self.binary("Divide", a, b, loc=loc)
+    def maximum(self, a, b, loc=None): return self.binary("Maximum", a, b, loc=loc)
+
+    def where(self, c: Value, a: Value, b: Value, loc=None) -> Value:
+        out = self._value(_broadcast(_broadcast(c.shape, a.shape), b.shape), a.dtype)
+        self._emit("EltwiseTernaryWhereOp", {"first": c.ref, "second": a.ref, "third": b.ref,
+                                             "memory_config": self._mc(), "out": out.ref}, [c, a, b], [out], loc)
+        return out
+
+    # ---- quantization ---------------------------------------------------------------------------
+    @staticmethod
+    def _scale(s):
+        return ("PerAxisScale", {"scale": s.ref}) if isinstance(s, Value) else ("PerTensorScale", {"scale": float(s)})
+
+    @staticmethod
+    def _zp(z):
+        return ("PerAxisZeroPoint", {"zero_point": z.ref}) if isinstance(z, Value) else \
+            ("PerTensorZeroPoint", {"zero_point": int(z)})
+
+    def quantize(self, x: Value, scale, zero_point, out_dtype: str = "Int32", axis: Optional[int] = None, loc=None):
+        out = self._value(x.shape, out_dtype)
+        ins = [x] + [p for p in (scale, zero_point) if isinstance(p, Value)]
+        self._emit("EltwiseQuantizationOp", {
+            "type": "Quantize", "in": x.ref, "axis": axis, "output_dtype": out_dtype, "memory_config": self._mc(),
+            "out": out.ref,
+            "params": ("QuantizeDequantizeOpParams", {"scale": self._scale(scale), "zero_point": self._zp(zero_point)})},
+            ins, [out], loc)
+        return out
+
+    def dequantize(self, x: Value, scale, zero_point, out_dtype: str = "Float32", axis: Optional[int] = None, loc=None):
+        out = self._value(x.shape, out_dtype)
+        ins = [x] + [p for p in (scale, zero_point) if isinstance(p, Value)]
+        self._emit("EltwiseQuantizationOp", {
+            "type": "Dequantize", "in": x.ref, "axis": axis, "output_dtype": out_dtype, "memory_config": self._mc(),
+            "out": out.ref,
+            "params": ("QuantizeDequantizeOpParams", {"scale": self._scale(scale), "zero_point": self._zp(zero_point)})},
+            ins, [out], loc)
+        return out
+
+    def requantize(self, x: Value, in_scale, in_zp, out_scale, out_zp, out_dtype: Optional[str] = None,
+                   axis: Optional[int] = None, loc=None):
+        out = self._value(x.shape, out_dtype or x.dtype)
+        ins = [x] + [p for p in (in_scale, in_zp, out_scale, out_zp) if isinstance(p, Value)]
+        self._emit("EltwiseQuantizationOp", {
+            "type": "Requantize", "in": x.ref, "axis": axis, "output_dtype": out_dtype or x.dtype,
+            "memory_config": self._mc(), "out": out.ref,
+            "params": ("RequantizeOpParams", {"in_scale": self._scale(in_scale), "in_zero_point": self._zp(in_zp),
+                                              "out_scale": self._scale(out_scale), "out_zero_point": self._zp(out_zp)})},
+            ins, [out], loc)
+        return out
+
+    # ---- contractions ------------------------------------------------------------------------------
+    @staticmethod
+    def _mm_shape(a, b, ta, tb):
+        a, b = list(a), list(b)
+        if len(a) == 1:
+            a = [1] + a
+        if len(b) == 1:
+            b = b + [1]
+        m, k = (a[-1], a[-2]) if ta else (a[-2], a[-1])
+        kb, n = (b[-1], b[-2]) if tb else (b[-2], b[-1])
+        if k != kb:
+            raise ValueError(f"matmul inner dims differ: {k} vs {kb}")
+        batch = _broadcast(a[:-2], b[:-2])
+        return batch + [m, n]
+
+    def matmul(self, a: Value, b: Value, transpose_a=False, transpose_b=False, activation: Optional[str] = None,
+               loc=None) -> Value:
+        out = self._value(self._mm_shape(a.shape, b.shape, transpose_a, transpose_b), a.dtype)
+        self._emit("MatmulOp", {"a": a.ref, "b": b.ref, "out": out.ref, "transpose_a": transpose_a,
+                                "transpose_b": transpose_b, "activation": activation}, [a, b], [out], loc)
+        return out
+
+    def linear(self, a: Value, b: Value, bias: Optional[Value] = None, transpose_a=False, transpose_b=False,
+               activation: Optional[str] = None, loc=None) -> Value:
+        out = self._value(self._mm_shape(a.shape, b.shape, transpose_a, transpose_b), a.dtype)
+        self._emit("LinearOp", {"a": a.ref, "b": b.ref, "bias": bias.ref if bias else None, "out": out.ref,
+                                "transpose_a": transpose_a, "transpose_b": transpose_b, "activation": activation},
+                   [a, b] + ([bias] if bias else []), [out], loc)
+        return out
+
+    def conv2d(self, x: Value, w: Value, bias: Optional[Value], batch: int, height: int, width: int, stride=(1, 1),
+               padding=(0, 0, 0, 0), dilation=(1, 1), groups: int = 1, loc=None) -> Value:
+        """x is [1, 1, N*H*W, C] (the flattened form the compiler emits) or [N, H, W, C];
+        w is [O, C/groups, kH, kW]; bias [1, 1, 1, O].  Output keeps x's rank."""
+        o, cg, kh, kw = w.shape
+        c = cg * groups
+        pad = list(padding) if len(padding) == 4 else [padding[0], padding[1], padding[0], padding[1]]
+        ho = (height + pad[0] + pad[2] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
+        wo = (width + pad[1] + pad[3] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
+        oshape = [1, 1, batch * ho * wo, o] if x.shape[:2] == [1, 1] and len(x.shape) == 4 and x.shape[2] == batch * height * width \
+            else [batch, ho, wo, o]
+        out = self._value(oshape, x.dtype)
+        self._emit("Conv2dOp", {
+            "input": x.ref, "weight": w.ref, "bias": bias.ref if bias else None, "out": out.ref,
+            "device": self.device_ref, "in_channels": c, "out_channels": o, "batch_size": batch,
+            "input_height": height, "input_width": width, "kernel_size": [kh, kw], "stride": list(stride),
+            "padding": pad, "dilation": list(dilation), "groups": groups, "output_dtype": x.dtype},
+            [x, w] + ([bias] if bias else []), [out], loc)
+        return out
+
+    # ---- normalisation / reduction ------------------------------------------------------------------
+    def softmax(self, x: Value, dim: int = -1, loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        self._emit("SoftmaxOp", {"in": x.ref, "out": out.ref, "dimension": dim, "numeric_stable": True}, [x], [out], loc)
+        return out
+
+    def rms_norm(self, x: Value, weight: Optional[Value], bias: Optional[Value] = None, epsilon: float = 1e-5,
+                 loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        self._emit("RMSNormOp", {"input": x.ref, "weight": weight.ref if weight else None,
+                                 "bias": bias.ref if bias else None, "epsilon": float(epsilon),
+                                 "memory_config": self._mc(), "out": out.ref},
+                   [x] + [v for v in (weight, bias) if v], [out], loc)
+        return out
+
+    def reduce(self, kind: str, x: Value, dims: Optional[Sequence[int]], keep_dim: bool, loc=None) -> Value:
+        rank = len(x.shape)
+        ds = sorted(_norm(d, rank) for d in dims) if dims else list(range(rank))
+        shape = [1 if i in ds else s for i, s in enumerate(x.shape)] if keep_dim else \
+            [s for i, s in enumerate(x.shape) if i not in ds]
+        out = self._value(shape, x.dtype)
+        self._emit("ReductionOp", {"type": kind, "in": x.ref, "out": out.ref, "dim_arg": list(dims) if dims else None,
+                                   "keep_dim": keep_dim}, [x], [out], loc)
+        return out
+
+    # ---- data movement -----------------------------------------------------------------------------------
+    def reshape(self, x: Value, shape, loc=None) -> Value:
+        shape = list(shape)
+        if -1 in shape:
+            known = _volume([s for s in shape if s != -1])
+            shape[shape.index(-1)] = _volume(x.shape) // known
+        assert _volume(shape) == _volume(x.shape)
+        out = self._value(shape, x.dtype)
+        self._emit("ReshapeOp", {"in": x.ref, "out": out.ref, "shape": shape, "memory_config": self._mc()}, [x], [out], loc)
+        return out
+
+    def permute(self, x: Value, perm, loc=None) -> Value:
+        out = self._value([x.shape[p] for p in perm], x.dtype)
+        self._emit("PermuteOp", {"in": x.ref, "permutation": list(perm), "memory_config": self._mc(), "pad_value": 0.0,
+                                 "out": out.ref}, [x], [out], loc)
+        return out
+
+    def transpose(self, x: Value, d0: int, d1: int, loc=None) -> Value:
+        shape = list(x.shape)
+        a, b = _norm(d0, len(shape)), _norm(d1, len(shape))
+        shape[a], shape[b] = shape[b], shape[a]
+        out = self._value(shape, x.dtype)
+        self._emit("TransposeOp", {"in": x.ref, "out": out.ref, "dim0": d0, "dim1": d1}, [x], [out], loc)
+        return out
+
+    def concat(self, xs: Sequence[Value], dim: int, loc=None) -> Value:
+        shape = list(xs[0].shape)
+        d = _norm(dim, len(shape))
+        shape[d] = sum(v.shape[d] for v in xs)
+        out = self._value(shape, xs[0].dtype)
+        self._emit("ConcatOp", {"inputs": [v.ref for v in xs], "out": out.ref, "dim": dim, "memory_config": self._mc()},
+                   list(xs), [out], loc)
+        return out
+
+    def slice(self, x: Value, begins, ends, step=None, loc=None) -> Value:
+        step = list(step) if step else [1] * len(x.shape)
+        shape = [(e - b + s - 1) // s for b, e, s in zip(begins, ends, step)]
+        out = self._value(shape, x.dtype)
+        self._emit("SliceOp", {"type": "SliceStaticOp", "in": x.ref, "out": out.ref, "step": step,
+                               "params": ("SliceStaticOpParams", {"begins": list(begins), "ends": list(ends)})},
+                   [x], [out], loc)
+        return out
+
+    def repeat(self, x: Value, repeats, loc=None) -> Value:
+        out = self._value([s * r for s, r in zip(x.shape, repeats)], x.dtype)
+        self._emit("RepeatOp", {"in": x.ref, "out": out.ref, "repeat_dims": list(repeats), "memcfg": self._mc()},
+                   [x], [out], loc)
+        return out
+
+    def repeat_interleave(self, x: Value, repeats: int, dim: int, loc=None) -> Value:
+        shape = list(x.shape)
+        shape[_norm(dim, len(shape))] *= repeats
+        out = self._value(shape, x.dtype)
+        self._emit("RepeatInterleaveOp", {"input": x.ref, "out": out.ref, "repeats": repeats, "dim": dim,
+                                          "memory_config": self._mc()}, [x], [out], loc)
+        return out
+
+    # ---- transformer ------------------------------------------------------------------------------------------
+    def concatenate_heads(self, x: Value, loc=None) -> Value:
+        b, h, s, d = x.shape
+        out = self._value([b, s, h * d], x.dtype)
+        self._emit("ConcatenateHeadsOp", {"in": x.ref, "out": out.ref, "memcfg": self._mc()}, [x], [out], loc)
+        return out
+
+    def split_query_key_value_and_split_heads(self, x: Value, kv: Optional[Value], num_heads: int,
+                                              num_kv_heads: Optional[int] = None, transpose_key: bool = False, loc=None):
+        b, s, hidden = x.shape
+        hkv = num_kv_heads if num_kv_heads is not None else num_heads
+        d = hidden // num_heads if kv is not None else hidden // (num_heads + 2 * hkv)
+        q = self._value([b, num_heads, s, d], x.dtype)
+        k = self._value([b, hkv, d, s] if transpose_key else [b, hkv, s, d], x.dtype)
+        v = self._value([b, hkv, s, d], x.dtype)
+        self._emit("SplitQueryKeyValueAndSplitHeadsOp", {
+            "in": x.ref, "kv_input": kv.ref if kv else None, "q_out": q.ref, "k_out": k.ref, "v_out": v.ref,
+            "num_heads": num_heads, "num_kv_heads": num_kv_heads, "transpose_key": transpose_key,
+            "memcfg": self._mc()}, [x] + ([kv] if kv else []), [q, k, v], loc)
+        return q, k, v
+
+    def rotary_embedding(self, x: Value, cos: Value, sin: Value, loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        self._emit("RotaryEmbeddingOp", {"input": x.ref, "cos_cache": cos.ref, "sin_cache": sin.ref, "out": out.ref,
+                                         "memcfg": self._mc()}, [x, cos, sin], [out], loc)
+        return out
+
+    def scaled_dot_product_attention(self, q: Value, k: Value, v: Value, is_causal: bool = True,
+                                     mask: Optional[Value] = None, scale: Optional[float] = None, loc=None) -> Value:
+        out = self._value(q.shape, q.dtype)
+        self._emit("ScaledDotProductAttentionOp", {
+            "query": q.ref, "key": k.ref, "value": v.ref, "is_causal": is_causal,
+            "attention_mask": mask.ref if mask else None, "scale": scale, "out": out.ref, "memcfg": self._mc()},
+            [q, k, v] + ([mask] if mask else []), [out], loc)
+        return out
+
+    # ---- mesh ----------------------------------------------------------------------------------------------------
+    def _axis_size(self, cluster_axis: int) -> int:
+        return self.mesh_shape[cluster_axis]
+
+    def distribute(self, x: Value, shard_dim: Optional[int], cluster_axis: int = 1, on_device: bool = True, loc=None) -> Value:
+        """ttir.mesh_shard full_to_shard: shard `shard_dim` over `cluster_axis`, or replicate (None)."""
+        n = self._axis_size(cluster_axis)
+        placements = [("Replicate", -1), ("Replicate", -1)]
+        shape = list(x.shape)
+        if shard_dim is not None:
+            placements[cluster_axis] = ("Shard", shard_dim)
+            assert shape[shard_dim] % n == 0
+            shape[shard_dim] //= n
+        out = self._value(shape, x.dtype, on_device)
+        self._emit("DistributeTensorOp", {
+            "in": x.ref, "out": out.ref, "device": self.device_ref,
+            "mapper_config": {"placements": placements, "mesh_shape_override": list(self.mesh_shape)}},
+            [x], [out], loc)
+        return out
+
+    def aggregate(self, x: Value, shard_dim: Optional[int], cluster_axis: int = 1, loc=None) -> Value:
+        """ttir.mesh_shard shard_to_full: concatenate `shard_dim` over `cluster_axis`, or take one replica."""
+        n = self._axis_size(cluster_axis)
+        shape = list(x.shape)
+        if shard_dim is None:
+            dims, override = [0], [1]
+        else:
+            rank = len(shape)
+            other = next(d for d in range(rank - 1, -1, -1) if d != shard_dim) if rank > 1 else 0
+            dims, override = [other, other], [1, 1]
+            dims[cluster_axis] = shard_dim
+            override[cluster_axis] = n
+            shape[shard_dim] *= n
+        out = self._value(shape, x.dtype, False)
+        self._emit("AggregateTensorOp", {"in": x.ref, "out": out.ref, "device": self.device_ref,
+                                         "composer_config": {"dims": dims, "mesh_shape_override": override}},
+                   [x], [out], loc)
+        return out
+
+    def all_reduce(self, x: Value, reduce_type: int = 0, cluster_axis: int = 1, loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        self._emit("AllReduceOp", {"in": x.ref, "out": out.ref, "reduce_type": reduce_type, "cluster_axis": cluster_axis,
+                                   "memory_config": self._mc()}, [x], [out], loc)
+        return out
+
+    def all_gather(self, x: Value, dim: int, cluster_axis: int = 1, loc=None) -> Value:
+        shape = list(x.shape)
+        shape[_norm(dim, len(shape))] *= self._axis_size(cluster_axis)
+        out = self._value(shape, x.dtype)
+        self._emit("AllGatherOp", {"in": x.ref, "out": out.ref, "all_gather_dim": dim, "cluster_axis": cluster_axis,
+                                   "memory_config": self._mc()}, [x], [out], loc)
+        return out
+
+    def reduce_scatter(self, x: Value, dim: int, reduce_type: int = 0, cluster_axis: int = 1, loc=None) -> Value:
+        shape = list(x.shape)
+        d = _norm(dim, len(shape))
+        assert shape[d] % self._axis_size(cluster_axis) == 0
+        shape[d] //= self._axis_size(cluster_axis)
+        out = self._value(shape, x.dtype)
+        self._emit("ReduceScatterOp", {"in": x.ref, "out": out.ref, "scatter_dim": dim, "reduce_type": reduce_type,
+                                       "cluster_axis": cluster_axis, "memory_config": self._mc()}, [x], [out], loc)
+        return out
+
+    def mesh_partition(self, x: Value, dim: int, cluster_axis: int = 1, loc=None) -> Value:
+        shape = list(x.shape)
+        d = _norm(dim, len(shape))
+        shape[d] //= self._axis_size(cluster_axis)
+        out = self._value(shape, x.dtype)
+        self._emit("MeshPartitionOp", {"in": x.ref, "out": out.ref, "dim": dim, "cluster_axis": cluster_axis,
+                                       "memory_config": self._mc()}, [x], [out], loc)
+        return out
+
+    def cpu_op(self, ins: Sequence[Value], out_shape, out_dtype: str, func_name: str, loc=None) -> Value:
+        """A CPU-hoisted call, as the compiler emits for ttir ops tagged for host execution."""
+        out = self._value(out_shape, out_dtype, False)
+        self._emit("CpuOp", {"ins": [v.ref for v in ins], "outs": [out.ref], "func_name": func_name, "dylib_id": 0},
+                   list(ins), [out], loc)
+        return out
+
+    # ---- finishing -----------------------------------------------------------------------------------------------------
+    def _with_deallocs(self) -> List[dict]:
+        """Inserts a DeallocateOp after the last use of every op result that is not a program output."""
+        keep = {v.id for v in self.outputs} | {v.id for v in self.inputs}
+        last_use: Dict[int, int] = {}
+        produced: Dict[int, Value] = {}
+        for i, (ins, outs) in enumerate(self._op_values):
+            for v in ins:
+                last_use[v.id] = i
+            for v in outs:
+                produced[v.id] = v
+                last_use.setdefault(v.id, i)
+        ops: List[dict] = []
+        for i, op in enumerate(self.ops):
+            ops.append(op)
+            if op["type"][0] == "DeallocateOp":
+                continue
+            for vid, at in last_use.items():
+                if at == i and vid in produced and vid not in keep:
+                    v = produced[vid]
+                    ops.append({"type": ("DeallocateOp", {"in": v.ref, "force": False}),
+                                "debug_info": f'"ttnn.deallocate"(%{vid})', "loc_info": f'loc("dealloc_{vid}")'})
+        return ops
+
+    def table(self, auto_dealloc: bool = True) -> dict:
+        return {
+            "name": self.name,
+            "inputs": [v.ref for v in self.inputs],
+            "outputs": [v.ref for v in self.outputs],
+            "operations": self._with_deallocs() if auto_dealloc else self.ops,
+            "private": False,
+            "mesh_shape": self.mesh_shape,
+        }
+
+
+class BinaryBuilder:
+    def __init__(self, version=(0, 1, 0), git_hash: str = "b200-authored"):
+        self.version = version
+        self.git_hash = git_hash
+        self._next = 0
+        self.programs: List[ProgramBuilder] = []
+        self.auto_dealloc = True
+
+    def next_id(self) -> int:
+        i = self._next
+        self._next += 1
+        return i
+
+    def program(self, name: str = "main", mesh_shape=(1, 1)) -> ProgramBuilder:
+        p = ProgramBuilder(self, name, mesh_shape)
+        self.programs.append(p)
+        return p
+
+    def finish(self) -> bytes:
+        w = Writer(S)
+        root = w.create_table("TTNNBinary", {
+            "version": self.version,
+            "schema_hash": SCHEMA_HASH,
+            "ttmlir_git_hash": self.git_hash,
+            "mlir": {"name": "ttnn", "source": ""},
+            "programs": [p.table(self.auto_dealloc) for p in self.programs],
+        })
+        return w.finish(root, FILE_IDENTIFIER, size_prefixed=True)

@@ -199,6 +199,9 @@ TTB_API int ttb_gemm(const void *a, const void *b, const void *bias, void *c, in
                      int bias_dtype, int c_dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                      int trans_a, int trans_b, int64_t a_batch_stride, int64_t b_batch_stride,
                      int act, int round_steps, void *stream);
+/* Health of the tensor-core kernel: every wait inside it is bounded, and a wait that gives up
+ * records where.  *status == 0 means no launch of this process has timed out.  Synchronises. */
+TTB_API int ttb_gemm_tcgen05_status(int *status);
 /* Same contract, forced onto the SIMT kernel (reference implementation for the fast path). */
 TTB_API int ttb_gemm_simt(const void *a, const void *b, const void *bias, void *c, int ab_dtype,
                           int bias_dtype, int c_dtype, int64_t batch, int64_t m, int64_t n,

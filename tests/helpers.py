@@ -71,3 +71,53 @@ def run_body(rt, device, body, inputs, mesh_shape=(1, 1)):
     got = run_program(rt, device, buf, inputs)
     want = oracle_results(graph, inputs, mesh_shape=mesh_shape)
     return got, want
+
+
+class KernelHarness:
+    """Raw access to the kernel-level C ABI (include/ttb_kernels.h) for tests: device buffers
+    from torch CPU tensors, one stream, explicit copies."""
+
+    def __init__(self, rt):
+        import ctypes
+        self.ct = ctypes
+        self.lib = rt.lib
+        self.rt = rt
+        self._check(self.lib.ttb_set_device(0))
+        s = ctypes.c_void_p()
+        self._check(self.lib.ttb_stream_create(ctypes.byref(s)))
+        self.stream = s
+        self._bufs = []
+
+    def _check(self, rc):
+        if rc != 0:
+            raise RuntimeError(self.lib.ttb_last_error().decode())
+
+    def upload(self, t: torch.Tensor):
+        t = t.contiguous()
+        p = self.ct.c_void_p()
+        n = t.numel() * t.element_size()
+        self._check(self.lib.ttb_malloc(self.ct.byref(p), self.ct.c_size_t(max(n, 16)), self.stream))
+        self._check(self.lib.ttb_memcpy_h2d(p, self.ct.c_void_p(t.data_ptr()), self.ct.c_size_t(n), self.stream))
+        self._check(self.lib.ttb_stream_sync(self.stream))
+        self._bufs.append(p)
+        return p
+
+    def empty(self, shape, dtype):
+        return self.upload(torch.zeros(shape, dtype=dtype))
+
+    def download(self, p, shape, dtype):
+        out = torch.empty(shape, dtype=dtype)
+        n = out.numel() * out.element_size()
+        self._check(self.lib.ttb_memcpy_d2h(self.ct.c_void_p(out.data_ptr()), p, self.ct.c_size_t(n), self.stream))
+        self._check(self.lib.ttb_stream_sync(self.stream))
+        return out
+
+    def sync(self):
+        self._check(self.lib.ttb_stream_sync(self.stream))
+
+    def close(self):
+        for p in self._bufs:
+            self.lib.ttb_free(p, self.stream)
+        self._bufs = []
+        self.lib.ttb_stream_sync(self.stream)
+        self.lib.ttb_stream_destroy(self.stream)

@@ -1,0 +1,96 @@
+"""The tcgen05 tensor-core GEMM against the CUDA-core GEMM and an f32 reference, through the
+kernel-level C ABI (ttb_gemm picks the tensor-core kernel, ttb_gemm_simt forces the other)."""
+
+import ctypes
+
+import pytest
+import torch
+
+from helpers import KernelHarness, assert_matches
+
+pytestmark = pytest.mark.gpu
+
+BF16, F32 = 2, 0
+ACT = {None: 0, "relu": 1, "silu": 2}
+
+
+def run_gemm(h, fn, a, b, bias, m, n, k, act=0, round_steps=0, out_dtype=torch.bfloat16):
+    da, db = h.upload(a), h.upload(b)
+    dbias = h.upload(bias) if bias is not None else None
+    dc = h.empty((m, n), out_dtype)
+    i64 = ctypes.c_int64
+    rc = fn(da, db, dbias, dc, BF16, BF16, BF16 if out_dtype == torch.bfloat16 else F32, i64(1), i64(m), i64(n), i64(k),
+            0, 1, i64(0), i64(0), act, round_steps, h.stream)
+    if rc != 0:
+        raise RuntimeError(h.lib.ttb_last_error().decode())
+    return h.download(dc, (m, n), out_dtype)
+
+
+def tc_status(h):
+    st = ctypes.c_int(-1)
+    assert h.lib.ttb_gemm_tcgen05_status(ctypes.byref(st)) == 0
+    return st.value
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 64, 128), (128, 128, 256), (256, 512, 1024),
+                                   (200, 136, 72), (1000, 1000, 520), (77, 264, 4096), (4096, 64, 576),
+                                   (2048, 4096, 4096)])
+def test_tcgen05_matches_simt_and_f32(rt, device, m, n, k):
+    torch.manual_seed(m + n + k)
+    a = torch.randn(m, k).to(torch.bfloat16)
+    b = (torch.randn(n, k) * 0.05).to(torch.bfloat16)
+    h = KernelHarness(rt)
+    try:
+        fast = run_gemm(h, h.lib.ttb_gemm, a, b, None, m, n, k)
+        assert tc_status(h) == 0, "a wait inside the tensor-core kernel timed out"
+        slow = run_gemm(h, h.lib.ttb_gemm_simt, a, b, None, m, n, k)
+    finally:
+        h.close()
+    ref = (a.float() @ b.float().t())
+    assert_matches(slow, ref.to(torch.bfloat16), f"simt {m}x{n}x{k}")
+    assert_matches(fast, ref.to(torch.bfloat16), f"tcgen05 {m}x{n}x{k}")
+    # both accumulate in f32 and round once: they may differ only where f32 summation order
+    # moves a value across a bf16 rounding boundary
+    diff = (fast.float() - slow.float()).abs()
+    assert (diff > 2.0 ** -6 * ref.abs() + 1e-3).sum().item() == 0
+
+
+@pytest.mark.parametrize("act,round_steps", [(None, 0), ("relu", 0), ("silu", 2), ("relu", 3)])
+def test_tcgen05_epilogue(rt, device, act, round_steps):
+    m, n, k = 256, 384, 512
+    torch.manual_seed(7)
+    a = torch.randn(m, k).to(torch.bfloat16)
+    b = (torch.randn(n, k) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(n).to(torch.bfloat16)
+    h = KernelHarness(rt)
+    try:
+        fast = run_gemm(h, h.lib.ttb_gemm, a, b, bias, m, n, k, ACT[act], round_steps)
+        slow = run_gemm(h, h.lib.ttb_gemm_simt, a, b, bias, m, n, k, ACT[act], round_steps)
+        assert tc_status(h) == 0
+    finally:
+        h.close()
+    acc = a.float() @ b.float().t()
+    if round_steps & 1:
+        acc = acc.to(torch.bfloat16).float()
+    acc = acc + bias.float()
+    if round_steps & 2:
+        acc = acc.to(torch.bfloat16).float()
+    if act == "relu":
+        acc = torch.relu(acc)
+    elif act == "silu":
+        acc = torch.nn.functional.silu(acc)
+    assert_matches(fast, acc.to(torch.bfloat16), "tcgen05 epilogue")
+    assert_matches(slow, acc.to(torch.bfloat16), "simt epilogue")
+
+
+def test_tcgen05_f32_output(rt, device):
+    m, n, k = 256, 256, 256
+    a = torch.randn(m, k).to(torch.bfloat16)
+    b = torch.randn(n, k).to(torch.bfloat16)
+    h = KernelHarness(rt)
+    try:
+        fast = run_gemm(h, h.lib.ttb_gemm, a, b, None, m, n, k, out_dtype=torch.float32)
+        assert tc_status(h) == 0
+    finally:
+        h.close()
+    assert_matches(fast, a.float() @ b.float().t(), "f32 out", (0.999, 1e-3, 1e-4))

@@ -1,7 +1,405 @@
+// bf16 / f16 GEMM on the Blackwell tensor cores: C[M,N] = act(A[M,K] * B[N,K]^T + bias).
+//
+// This is the contraction behind ttnn.matmul / ttnn.linear / 1x1 and im2col'd conv2d for 16-bit
+// operands (reference call sites: runtime/lib/ttnn/operations/matmul/matmul.cpp:75-80,117-122).
+// Structure (one persistent CTA per SM, 192 threads, warp specialised):
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of a 128 x 64 A tile and a BN x 64 B
+//               tile per k-step into a ring of 128-byte-swizzled shared-memory stages
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16, f32 accumulate)
+//               straight from shared-memory descriptors into TMEM; owns the TMEM allocation
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32 TMEM lanes), add bias,
+//               apply the activation / rounding points, store 16-byte vectors to global memory
+// The accumulator is double buffered in TMEM (2 x BN columns of the 512), so the epilogue of
+// tile i overlaps the main loop of tile i+1.  Stages and accumulators are handed over through
+// mbarriers; tcgen05.commit arrives on them when the MMAs that read a stage have retired.
+// Every wait is bounded: on a timeout the CTA raises a status word, drains and exits instead
+// of hanging the GPU.  No cluster launch and no multicast: every CTA fetches its own tiles.
 #include "common.cuh"
+#include "epilogue.cuh"
+
+#include <cuda.h>
+
 namespace ttb {
-int gemmTcgen05Try(const void *, const void *, const void *, void *, int, int, int, int64_t, int64_t, int64_t, int64_t,
-                   int, int, int64_t, int64_t, int, int, cudaStream_t) {
-  return -1;
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 64; // 64 x 2 bytes = one 128-byte swizzle row
+constexpr int TC_THREADS = 192;
+constexpr int TC_TMEM_COLS = 512;
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;
+
+template <int BN> struct TcCfg {
+  static constexpr int kBBytes = BN * TC_BK * 2;
+  static constexpr int kStageBytes = TC_A_BYTES + kBBytes;
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kSmem = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+__device__ int g_tcStatus; // 0 ok; otherwise (where << 8) | code of the first wait that gave up
+
+// ---- PTX wrappers ----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smemU32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbarInit(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbarArriveExpectTx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbarArrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbarTryWait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+               "selp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false when the barrier did not flip within ~1 s or another role of
+// this CTA already gave up; the caller then leaves its loop.
+__device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity, volatile int *abortFlag, int where) {
+  if (mbarTryWait(bar, parity)) return true;
+  const long long start = clock64();
+  uint32_t spins = 0;
+  while (!mbarTryWait(bar, parity)) {
+    if ((++spins & 1023u) == 0) {
+      if (*abortFlag) return false;
+      if (clock64() - start > 2000000000ll) {
+        *abortFlag = 1;
+        atomicCAS(&g_tcStatus, 0, (where << 8) | 1);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tmaLoad2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void prefetchTensorMap(const CUtensorMap *map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tcCommit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]; `accumulate` = 0 overwrites D.
+__device__ __forceinline__ void tcMma(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// 32 consecutive f32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tcLoad32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tcWaitLd() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the
+// 128-byte swizzle TMA applied: 8-row groups are 1024 bytes apart (stride byte offset), the
+// leading byte offset is not used for this layout, descriptor version 1 (sm_100), layout type
+// 2 (SWIZZLE_128B).  Stepping 16 elements along K inside the row adds 32 bytes to the start.
+__device__ __forceinline__ uint64_t smemDesc(uint32_t addr) {
+  return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (static_cast<uint64_t>(1024 >> 4) << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+
+// kind::f16 instruction descriptor: f32 accumulator, A/B format (1 = bf16, 0 = f16), both
+// operands K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t instrDesc(int fmt, int m, int n) {
+  return (1u << 4) | (static_cast<uint32_t>(fmt) << 7) | (static_cast<uint32_t>(fmt) << 10) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+struct TcParams {
+  int64_t M, N, K;
+  const void *bias;
+  int biasDt;
+  int act;
+  int roundSteps;
+  int fmt; // 1 bf16, 0 f16
+};
+
+template <int BN, typename TC>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+    gemmTcgen05Kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                      TC *__restrict__ c, TcParams p) {
+  using Cfg = TcCfg<BN>;
+  constexpr int STAGES = Cfg::kStages;
+  extern __shared__ uint8_t smemRaw[];
+  // 1024-byte alignment: required by the 128-byte swizzle pattern
+  const uint32_t base = (smemU32(smemRaw) + 1023u) & ~1023u;
+  const uint32_t barBase = base + STAGES * Cfg::kStageBytes;
+  auto fullBar = [&](int s) { return barBase + 8u * s; };
+  auto emptyBar = [&](int s) { return barBase + 8u * (STAGES + s); };
+  auto tmemFullBar = [&](int a) { return barBase + 8u * (2 * STAGES + a); };
+  auto tmemEmptyBar = [&](int a) { return barBase + 8u * (2 * STAGES + 2 + a); };
+  __shared__ uint32_t tmemBaseSlot;
+  __shared__ int abortFlagS;
+  volatile int *abortFlag = &abortFlagS;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t tilesM = (p.M + TC_BM - 1) / TC_BM, tilesN = (p.N + BN - 1) / BN;
+  const int64_t numTiles = tilesM * tilesN;
+  const int kBlocks = static_cast<int>((p.K + TC_BK - 1) / TC_BK);
+
+  if (threadIdx.x == 0) {
+    abortFlagS = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbarInit(fullBar(s), 1);
+      mbarInit(emptyBar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbarInit(tmemFullBar(a), 1);
+      mbarInit(tmemEmptyBar(a), 128);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetchTensorMap(&mapA);
+    prefetchTensorMap(&mapB);
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemU32(&tmemBaseSlot)), "r"(TC_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcFenceBefore();
+  __syncthreads();
+  tcFenceAfter();
+  const uint32_t tmemBase = tmemBaseSlot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int64_t tile = blockIdx.x; tile < numTiles && alive; tile += gridDim.x) {
+        const int m0 = static_cast<int>(tile % tilesM) * TC_BM, n0 = static_cast<int>(tile / tilesM) * BN;
+        for (int kb = 0; kb < kBlocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t phase = (it / STAGES) & 1u;
+          if (!mbarWait(emptyBar(s), phase ^ 1u, abortFlag, 1)) { alive = false; break; }
+          const uint32_t sa = base + s * Cfg::kStageBytes, sb = sa + TC_A_BYTES;
+          mbarArriveExpectTx(fullBar(s), Cfg::kStageBytes);
+          tmaLoad2d(sa, &mapA, fullBar(s), kb * TC_BK, m0);
+          tmaLoad2d(sb, &mapB, fullBar(s), kb * TC_BK, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = instrDesc(p.fmt, TC_BM, BN);
+      uint32_t it = 0, accIt = 0;
+      bool alive = true;
+      for (int64_t tile = blockIdx.x; tile < numTiles && alive; tile += gridDim.x, ++accIt) {
+        const int acc = accIt & 1;
+        const uint32_t accPhase = (accIt >> 1) & 1u;
+        if (!mbarWait(tmemEmptyBar(acc), accPhase ^ 1u, abortFlag, 2)) break;
+        tcFenceAfter();
+        const uint32_t tmemD = tmemBase + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < kBlocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t phase = (it / STAGES) & 1u;
+          if (!mbarWait(fullBar(s), phase, abortFlag, 3)) { alive = false; break; }
+          tcFenceAfter();
+          const uint32_t sa = base + s * Cfg::kStageBytes, sb = sa + TC_A_BYTES;
+          const uint64_t da = smemDesc(sa), db = smemDesc(sb);
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k) {
+            // +32 bytes per 16-element k-step = +2 in the descriptor's 16-byte address units
+            tcMma(tmemD, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tcCommit(emptyBar(s)); // frees the stage once these MMAs have read it
+        }
+        if (alive) tcCommit(tmemFullBar(acc)); // accumulator complete
+      }
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5 ----------------
+    const int quarter = warp & 3; // TMEM lanes this warp may read
+    uint32_t accIt = 0;
+    const bool vecOk = (p.N % 8) == 0;
+    for (int64_t tile = blockIdx.x; tile < numTiles; tile += gridDim.x, ++accIt) {
+      const int acc = accIt & 1;
+      const uint32_t accPhase = (accIt >> 1) & 1u;
+      if (!mbarWait(tmemFullBar(acc), accPhase, abortFlag, 4)) break;
+      tcFenceAfter();
+      const int64_t m0 = (tile % tilesM) * TC_BM, n0 = (tile / tilesM) * BN;
+      const int64_t row = m0 + quarter * 32 + lane;
+      const uint32_t taddrRow = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+      for (int cc = 0; cc < BN / 32; ++cc) {
+        const int64_t col0 = n0 + cc * 32;
+        if (col0 >= p.N) break; // warp-uniform
+        uint32_t r[32];
+        tcLoad32(taddrRow + static_cast<uint32_t>(cc * 32), r);
+        tcWaitLd();
+        if (row < p.M) {
+          TC *dst = c + row * p.N + col0;
+          if (sizeof(TC) == 2 && vecOk && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int e = v * 8 + j * 2;
+                float b0 = p.bias ? loadBias(p.bias, p.biasDt, col0 + e) : 0.0f;
+                float b1 = p.bias ? loadBias(p.bias, p.biasDt, col0 + e + 1) : 0.0f;
+                TC x0 = epilogue<TC>(__uint_as_float(r[e]), p.bias != nullptr, b0, p.act, p.roundSteps);
+                TC x1 = epilogue<TC>(__uint_as_float(r[e + 1]), p.bias != nullptr, b1, p.act, p.roundSteps);
+                w[j] = static_cast<uint32_t>(*reinterpret_cast<uint16_t *>(&x0)) |
+                       (static_cast<uint32_t>(*reinterpret_cast<uint16_t *>(&x1)) << 16);
+              }
+              *reinterpret_cast<uint4 *>(dst + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              if (col0 + e < p.N) {
+                float b0 = p.bias ? loadBias(p.bias, p.biasDt, col0 + e) : 0.0f;
+                dst[e] = epilogue<TC>(__uint_as_float(r[e]), p.bias != nullptr, b0, p.act, p.roundSteps);
+              }
+            }
+          }
+        }
+      }
+      tcFenceBefore();
+      mbarArrive(tmemEmptyBar(acc)); // all 128 epilogue threads arrive
+    }
+  }
+
+  // ---------------- teardown ----------------
+  if (*abortFlag) {
+    // give bulk copies that may still be in flight time to land before shared memory is released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) { __nanosleep(1000); }
+  }
+  tcFenceBefore();
+  __syncthreads();
+  if (warp == 1) {
+    tcFenceAfter();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(TC_TMEM_COLS) : "memory");
+  }
+}
+
 } // namespace ttb
+
+// ---- host side ------------------------------------------------------------------------------
+namespace ttb {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up through the runtime so that the library does not link libcuda.
+static EncodeTiledFn encodeTiled() {
+  static EncodeTiledFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      return static_cast<EncodeTiledFn>(nullptr);
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// Row-major [rows, cols] 16-bit matrix, box = 64 columns x boxRows rows, 128-byte swizzle,
+// out-of-bounds elements read as zero (which is what makes ragged M / N / K tails work).
+static bool makeMap(CUtensorMap *map, const void *ptr, int dtype, int64_t rows, int64_t cols, int boxRows) {
+  EncodeTiledFn fn = encodeTiled();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  cuuint32_t box[2] = {TC_BK, static_cast<cuuint32_t>(boxRows)};
+  cuuint32_t elemStrides[2] = {1, 1};
+  CUtensorMapDataType dt = dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = fn(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <int BN, typename TC>
+static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, void *c, const TcParams &p, cudaStream_t st) {
+  using Cfg = TcCfg<BN>;
+  static bool attr = false;
+  if (!attr) {
+    TTB_CUDA(cudaFuncSetAttribute(gemmTcgen05Kernel<BN, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+    attr = true;
+  }
+  int64_t tiles = ((p.M + TC_BM - 1) / TC_BM) * ((p.N + BN - 1) / BN);
+  int grid = static_cast<int>(tiles < smCount() ? tiles : smCount());
+  gemmTcgen05Kernel<BN, TC><<<grid, TC_THREADS, Cfg::kSmem, st>>>(ma, mb, static_cast<TC *>(c), p);
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int abDtype, int biasDtype, int cDtype,
+                   int64_t batch, int64_t m, int64_t n, int64_t k, int transA, int transB, int64_t, int64_t, int act,
+                   int roundSteps, cudaStream_t stream) {
+  // What this kernel takes: one 16-bit A[M,K] and B[N,K] (the "transpose_b" weight layout),
+  // rows 16-byte aligned, output in a 16- or 32-bit float type.
+  if (batch != 1 || transA || !transB) return -1;
+  if (abDtype != kBF16 && abDtype != kF16) return -1;
+  if (cDtype != abDtype && cDtype != kF32) return -1;
+  if (k % 8 != 0 || m < 1 || n < 8 || k < 8) return -1;
+  if (!aligned16(a) || !aligned16(b) || !aligned16(c)) return -1;
+  if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff) return -1;
+  // Tiny problems are launch-bound either way; keep them on the simple kernel.
+  if (m * n * k < (1ll << 18)) return -1;
+  int bn = n >= 256 ? 256 : (n >= 128 ? 128 : 64);
+  // Prefer the tile width that fills the machine: with few tiles, narrower tiles use more SMs.
+  auto tilesFor = [&](int w) { return ((m + TC_BM - 1) / TC_BM) * ((n + w - 1) / w); };
+  while (bn > 64 && tilesFor(bn) < smCount() && tilesFor(bn / 2) > tilesFor(bn)) bn /= 2;
+  CUtensorMap ma, mb;
+  if (!makeMap(&ma, a, abDtype, m, k, TC_BM) || !makeMap(&mb, b, abDtype, n, k, bn)) return -1;
+  TcParams p;
+  p.M = m; p.N = n; p.K = k;
+  p.bias = bias; p.biasDt = biasDtype; p.act = act; p.roundSteps = roundSteps;
+  p.fmt = abDtype == kBF16 ? 1 : 0;
+  double flops = 2.0 * double(m) * double(n) * double(k);
+  double bytes = (double(m) * k + double(n) * k) * 2 + double(m) * n * dtypeSize(cDtype);
+  ProfScope prof("gemm_tcgen05", flops, bytes, stream);
+#define TTB_TC(BNv, TCv) return launchTc<BNv, TCv>(ma, mb, c, p, stream)
+#define TTB_TC_BN(TCv)                                                                   \
+  switch (bn) {                                                                          \
+  case 256: TTB_TC(256, TCv);                                                            \
+  case 128: TTB_TC(128, TCv);                                                            \
+  default: TTB_TC(64, TCv);                                                              \
+  }
+  if (cDtype == kBF16) { TTB_TC_BN(__nv_bfloat16) }
+  if (cDtype == kF16) { TTB_TC_BN(__half) }
+  TTB_TC_BN(float)
+#undef TTB_TC_BN
+#undef TTB_TC
+}
+
+} // namespace ttb
+
+// 0 when no tensor-core GEMM launch of this process has hit a wait timeout; otherwise
+// (role << 8) | 1 with role 1 = loader, 2 / 3 = MMA issuer, 4 = epilogue.  Synchronises the device.
+extern "C" int ttb_gemm_tcgen05_status(int *status) {
+  TTB_CHECK(status != nullptr, "status is null");
+  TTB_CUDA(cudaDeviceSynchronize());
+  TTB_CUDA(cudaMemcpyFromSymbol(status, ttb::g_tcStatus, sizeof(int)));
+  return TTB_OK;
+}

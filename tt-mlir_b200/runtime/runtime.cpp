@@ -771,8 +771,16 @@ static TensorPtr castOnHost(const TensorPtr &t, DataType dt) {
 void memcpy(void *dst, Tensor src, std::optional<DataType> targetDataType) {
   TTRT_ASSERT(dst != nullptr, "null destination");
   auto t = unwrapTensor(src);
+  TTRT_ASSERT(t->allocated(), "tensor has no data");
+  if (t->storage == Storage::Device && (!targetDataType || *targetDataType == t->dtype)) {
+    // straight into the caller's buffer (a true DMA when that buffer is pinned)
+    const RankCtx &r = t->device->locals[0];
+    TTB_CALL(ttb_set_device(r.cudaDevice));
+    TTB_CALL(ttb_memcpy_d2h(dst, t->shards[0]->ptr, t->bytes(), r.stream));
+    TTB_CALL(ttb_stream_sync(r.stream));
+    return;
+  }
   TensorPtr h = t->storage == Storage::Device ? toHostTensor(t, true) : t;
-  TTRT_ASSERT(h->allocated(), "tensor has no data");
   if (!targetDataType || *targetDataType == h->dtype) {
     std::memcpy(dst, h->shards[0]->ptr, h->bytes());
     return;

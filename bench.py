@@ -165,7 +165,7 @@ def run_b200(args):
         rt.memcpy(out_host.data_ptr(), out)                                # D2H of the result
         return out
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(args.warmup if args.profile else max(args.warmup, 3)):
         step_resident()
     rt.wait(step_resident())
 
@@ -187,6 +187,10 @@ def run_b200(args):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total = float(t.item())
+
+    if args.profile:
+        return dict(rank=rank, world=world, ms_total=ms_total, e2e_s=float("nan"), launches=launches, clocks=clocks,
+                    prof=[], prof_steps=1, tokens=tokens, bytes_io=mine[0].numel() * 2, rt=rt, device=device)
 
     # ---- e2e: host buffers in, host buffers out ---------------------------------------------
     for _ in range(2):
@@ -286,6 +290,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="for runs under a profiler: exactly --warmup warm-up steps, then --steps steps, nothing else")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -338,7 +344,7 @@ def main():
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": r["bytes_io"], "d2h_bytes_per_step": r["bytes_io"]},
         "roofline": roofline, "per_op": per_op,
     }
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and not args.profile:
         line["cpu_baseline"] = cpu_baseline()
     r["rt"].close_mesh_device(r["device"])
     print(json.dumps(line))

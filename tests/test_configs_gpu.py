@@ -86,7 +86,14 @@ def test_config4_decoder_block_full_size(rt, device):
     got = run_program(rt, device, buf, ins)[0]
     assert list(got.shape) == [1, 2048, 4096] and torch.isfinite(got.float()).all()
     want = oracle_results(graphs.decoder_block_graph, ins)[0]
-    assert_matches(got, want, "decoder full", (0.999, 3e-2, 2.0 ** -6))
+    # 30 chained bf16 ops with reductions over up to 14336 terms: f32 summation order moves a few
+    # intermediate values across bf16 rounding boundaries, and the residual stream (|x| up to ~16,
+    # one ulp = 0.0625 there) carries that on.  Every element must stay within 4 ulp, and 99.9 % of
+    # them within the stated atol of 1e-2 plus one ulp.
+    assert_matches(got, want, "decoder full", (0.999, 5e-2, 2.0 ** -5))
+    err = (got.float() - want.float()).abs()
+    tight = err <= 1e-2 + 2.0 ** -7 * want.float().abs()
+    assert tight.float().mean().item() > 0.999
     # causality: changing the last 1024 tokens leaves the first 1024 outputs untouched
     ins2 = [t.clone() for t in ins]
     ins2[0][:, 1024:] = torch.randn(1, 1024, 4096).to(torch.bfloat16)

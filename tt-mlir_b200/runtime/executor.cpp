@@ -206,28 +206,24 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
   }
 }
 
-static const ProgramInfo &programInfo(const Binary &bin, uint32_t programIndex, const fbt::Program *prog) {
-  static std::mutex m;
-  static std::map<std::pair<const void *, uint32_t>, std::unique_ptr<ProgramInfo>> cache;
-  std::lock_guard<std::mutex> g(m);
-  auto key = std::make_pair(static_cast<const void *>(bin.handle.get()), programIndex);
-  auto it = cache.find(key);
-  if (it != cache.end()) {
-    return *it->second;
-  }
-  auto info = std::make_unique<ProgramInfo>();
+// Computed per submit: one pass over the op list (microseconds), so nothing keyed by a binary's
+// address can go stale when a buffer is freed and its address reused by another binary.
+static ProgramInfo programInfo(const fbt::Program *prog) {
+  ProgramInfo info;
   if (prog->outputs()) {
-    for (const auto *r : *prog->outputs()) info->outputs.insert(r->global_id());
+    for (const auto *r : *prog->outputs()) info.outputs.insert(r->global_id());
   }
   if (prog->operations()) {
+    std::vector<const fbt::TensorRef *> ins, outs;
     for (const auto *op : *prog->operations()) {
       if (op->type_type() == OpType::DeallocateOp) continue;
-      std::vector<const fbt::TensorRef *> ins, outs;
+      ins.clear();
+      outs.clear();
       collectOpRefs(op, ins, outs);
-      for (const auto *r : ins) info->useCount[r->global_id()]++;
+      for (const auto *r : ins) info.useCount[r->global_id()]++;
     }
   }
-  return *cache.emplace(key, std::move(info)).first->second;
+  return info;
 }
 
 // ---- helpers over TensorRef -----------------------------------------------------------------
@@ -303,7 +299,7 @@ public:
 private:
   Binary &bin;
   const fbt::Program *prog = nullptr;
-  const ProgramInfo *info = nullptr;
+  ProgramInfo info;
   bool fuse = true;
 
   TensorPtr get(const fbt::TensorRef *ref);
@@ -379,7 +375,7 @@ Executor::Executor(std::shared_ptr<DeviceImpl> d, Binary &b, uint32_t pi, std::v
   const auto *programs = bin.get()->programs();
   TTRT_ASSERT(programs && programIndex < programs->size(), "program index ", programIndex, " out of range");
   prog = programs->Get(programIndex);
-  info = &programInfo(bin, programIndex, prog);
+  info = programInfo(prog);
   const auto &hooks = debug::Hooks::get();
   fuse = !debug::Env::get().disableFusion && !hooks.getPreOperatorCallback() && !hooks.getPostOperatorCallback();
 
@@ -462,8 +458,8 @@ TensorPtr Executor::allocOut(const fbt::TensorRef *ref) {
 
 bool Executor::singleUse(const fbt::TensorRef *ref) const {
   uint32_t id = ref->global_id();
-  auto it = info->useCount.find(id);
-  return (it != info->useCount.end() && it->second == 1) && !info->outputs.count(id);
+  auto it = info.useCount.find(id);
+  return (it != info.useCount.end() && it->second == 1) && !info.outputs.count(id);
 }
 
 const fbt::Operation *Executor::peek(size_t &idx, std::vector<const fbt::Operation *> &skipped) const {

@@ -81,6 +81,7 @@ struct Buffer {
   size_t bytes = 0;
   int cudaDevice = -1;   // -1: host memory
   void *stream = nullptr; // stream that orders the free of device memory
+  std::shared_ptr<struct DeviceImpl> owner; // keeps the stream's device alive; closed device -> plain free
   enum class Kind { Borrowed, HostMalloc, HostPinned, Device } kind = Kind::Borrowed;
   std::shared_ptr<void> keepAlive; // another object owning the memory (views)
   ~Buffer();

@@ -115,8 +115,9 @@ Buffer::~Buffer() {
   case Kind::HostPinned: ttb_host_free_pinned(ptr); break;
   case Kind::Device:
     // Stream-ordered free: safe while kernels using the block are still queued on `stream`.
+    // After the device was closed its stream is gone: free on the default stream instead.
     ttb_set_device(cudaDevice);
-    ttb_free(ptr, stream);
+    ttb_free(ptr, (owner && owner->open) ? stream : nullptr);
     break;
   case Kind::Borrowed: break;
   }
@@ -189,6 +190,7 @@ TensorPtr makeDeviceTensor(const std::shared_ptr<DeviceImpl> &dev, const std::ve
     b->bytes = bytes;
     b->cudaDevice = r.cudaDevice;
     b->stream = r.stream;
+    b->owner = dev;
     b->kind = Buffer::Kind::Device;
     t->shards.push_back(b);
   }
@@ -444,8 +446,10 @@ static bool isDense(const std::vector<std::uint32_t> &shape, const std::vector<s
 
 Tensor createBorrowedHostTensor(void *data, const std::vector<std::uint32_t> &shape,
                                 const std::vector<std::int64_t> &stride, std::uint32_t itemsize, DataType dataType) {
-  TTRT_ASSERT(data != nullptr, "cannot borrow null data");
   checkHostArgs(shape, stride, itemsize, dataType);
+  size_t vol = 1;
+  for (uint32_t d : shape) vol *= d;
+  TTRT_ASSERT(data != nullptr || vol == 0, "cannot borrow null data");
   // Same restriction as the reference (runtime/lib/ttnn/runtime.cpp:250-256).
   TTRT_ASSERT(isDense(shape, stride), "borrowed host tensors must be contiguous row-major");
   auto t = std::make_shared<TensorImpl>();
@@ -453,8 +457,9 @@ Tensor createBorrowedHostTensor(void *data, const std::vector<std::uint32_t> &sh
   t->stride = denseStrides(shape);
   t->dtype = dataType;
   t->storage = Storage::Host;
+  static char emptyPlaceholder[16];
   auto b = std::make_shared<Buffer>();
-  b->ptr = data;
+  b->ptr = data ? data : emptyPlaceholder; // empty tensors may come with a null pointer
   b->bytes = t->bytes();
   b->kind = Buffer::Kind::Borrowed;
   t->shards.push_back(b);

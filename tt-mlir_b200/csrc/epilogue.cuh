@@ -38,4 +38,16 @@ __device__ __forceinline__ TC epilogue(float acc, bool hasBias, float bias, int 
   return fromF32<TC>(acc);
 }
 
+// Same rounding points, result left in f32 (the caller rounds pairs with one packed convert).
+template <typename TC>
+__device__ __forceinline__ float epilogueF32(float acc, bool hasBias, float bias, int act, int roundSteps) {
+  if (roundSteps & 1) acc = toF32(fromF32<TC>(acc));
+  if (hasBias) {
+    acc = __fadd_rn(acc, bias);
+    if (roundSteps & 2) acc = toF32(fromF32<TC>(acc));
+  }
+  if (act) acc = applyAct(act, acc);
+  return acc;
+}
+
 } // namespace ttb

@@ -8,7 +8,8 @@
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16, f32 accumulate)
 //               straight from shared-memory descriptors into TMEM; owns the TMEM allocation
 //   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32 TMEM lanes), add bias,
-//               apply the activation / rounding points, store 16-byte vectors to global memory
+//               apply the activation / rounding points, stage 32 x 128 B blocks in shared
+//               memory and write them out with TMA stores (full lines, tails clipped)
 // The accumulator is double buffered in TMEM (2 x BN columns of the 512), so the epilogue of
 // tile i overlaps the main loop of tile i+1.  Stages and accumulators are handed over through
 // mbarriers; tcgen05.commit arrives on them when the MMAs that read a stage have retired.
@@ -19,6 +20,8 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
+
 namespace ttb {
 
 constexpr int TC_BM = 128;
@@ -26,12 +29,13 @@ constexpr int TC_BK = 64; // 64 x 2 bytes = one 128-byte swizzle row
 constexpr int TC_THREADS = 192;
 constexpr int TC_TMEM_COLS = 512;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;
+constexpr int TC_OUT_BYTES = 4 * 2 * 4096; // epilogue staging: 4 warps, double buffered, 32 rows x 128 B
 
 template <int BN> struct TcCfg {
   static constexpr int kBBytes = BN * TC_BK * 2;
   static constexpr int kStageBytes = TC_A_BYTES + kBBytes;
   static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int kSmem = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int kSmem = kStages * kStageBytes + TC_OUT_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
 __device__ int g_tcStatus; // 0 ok; otherwise (where << 8) | code of the first wait that gave up
@@ -128,6 +132,17 @@ __host__ __device__ constexpr uint32_t instrDesc(int fmt, int m, int n) {
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+template <typename TC> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<float>(float a, float) { return __float_as_uint(a); }
+
 struct TcParams {
   int64_t M, N, K;
   const void *bias;
@@ -135,18 +150,20 @@ struct TcParams {
   int act;
   int roundSteps;
   int fmt; // 1 bf16, 0 f16
+  int debug; // diagnostic: 1 = epilogue loads TMEM but skips math and stores, 2 = epilogue only hands the buffer back
 };
 
-template <int BN, typename TC>
+template <int BN, typename TC, bool PLAIN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     gemmTcgen05Kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                      TC *__restrict__ c, TcParams p) {
+                      const __grid_constant__ CUtensorMap mapC, TC *__restrict__ c, TcParams p) {
   using Cfg = TcCfg<BN>;
   constexpr int STAGES = Cfg::kStages;
   extern __shared__ uint8_t smemRaw[];
   // 1024-byte alignment: required by the 128-byte swizzle pattern
   const uint32_t base = (smemU32(smemRaw) + 1023u) & ~1023u;
-  const uint32_t barBase = base + STAGES * Cfg::kStageBytes;
+  const uint32_t outBase = base + STAGES * Cfg::kStageBytes; // 4 warps x 2 x 4 KB epilogue staging
+  const uint32_t barBase = outBase + TC_OUT_BYTES;
   auto fullBar = [&](int s) { return barBase + 8u * s; };
   auto emptyBar = [&](int s) { return barBase + 8u * (STAGES + s); };
   auto tmemFullBar = [&](int a) { return barBase + 8u * (2 * STAGES + a); };
@@ -173,6 +190,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetchTensorMap(&mapA);
     prefetchTensorMap(&mapB);
+    prefetchTensorMap(&mapC);
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemU32(&tmemBaseSlot)), "r"(TC_TMEM_COLS) : "memory");
@@ -232,56 +250,118 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
   } else {
     // ---------------- epilogue: warps 2..5 ----------------
+    // Each warp owns 32 rows of the tile.  Per chunk of CH columns (one 128-byte output row
+    // segment) it reads its TMEM lanes, applies the epilogue, writes the 32 x 128 B block to a
+    // swizzled staging buffer and hands it to a TMA store, which writes full lines and clips
+    // rows / columns that fall outside the matrix.  Two staging buffers per warp let the next
+    // chunk be prepared while the previous store drains.
+    constexpr int CH = 128 / static_cast<int>(sizeof(TC));
+    constexpr int NLD = CH / 32;
     const int quarter = warp & 3; // TMEM lanes this warp may read
-    uint32_t accIt = 0;
-    const bool vecOk = (p.N % 8) == 0;
+    const uint32_t stageOut = outBase + static_cast<uint32_t>(warp - 2) * 2u * 4096u;
+    uint32_t accIt = 0, chunkIt = 0;
     for (int64_t tile = blockIdx.x; tile < numTiles; tile += gridDim.x, ++accIt) {
       const int acc = accIt & 1;
       const uint32_t accPhase = (accIt >> 1) & 1u;
       if (!mbarWait(tmemFullBar(acc), accPhase, abortFlag, 4)) break;
       tcFenceAfter();
       const int64_t m0 = (tile % tilesM) * TC_BM, n0 = (tile / tilesM) * BN;
-      const int64_t row = m0 + quarter * 32 + lane;
       const uint32_t taddrRow = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
 #pragma unroll 1
-      for (int cc = 0; cc < BN / 32; ++cc) {
-        const int64_t col0 = n0 + cc * 32;
-        if (col0 >= p.N) break; // warp-uniform
-        uint32_t r[32];
-        tcLoad32(taddrRow + static_cast<uint32_t>(cc * 32), r);
+      for (int cc = 0; cc < BN / CH; ++cc) {
+        const int64_t col0 = n0 + cc * CH;
+        if (col0 >= p.N || p.debug == 2) break; // warp-uniform
+        uint32_t r[CH];
+#pragma unroll
+        for (int l = 0; l < NLD; ++l) {
+          tcLoad32(taddrRow + static_cast<uint32_t>(cc * CH + l * 32), *reinterpret_cast<uint32_t(*)[32]>(&r[l * 32]));
+        }
         tcWaitLd();
-        if (row < p.M) {
-          TC *dst = c + row * p.N + col0;
-          if (sizeof(TC) == 2 && vecOk && col0 + 32 <= p.N) {
+        if (p.debug == 1) {
+          if (r[0] == 0x7fc12345u && r[CH - 1] == 0x7fc54321u) c[0] = TC(0); // keeps the loads alive
+          continue;
+        }
+        if constexpr (!PLAIN) {
+          // Whole-chunk passes keep each activation's code in one straight run (a per-element
+          // switch would interleave all of them and thrash the instruction cache).
+          // bias of this chunk's columns: lane l holds columns l, l + 32, ...; broadcast by shuffle
+          float biasReg[NLD];
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint32_t w[4];
+          for (int l = 0; l < NLD; ++l) {
+            const int64_t col = col0 + l * 32 + lane;
+            biasReg[l] = (p.bias && col < p.N) ? loadBias(p.bias, p.biasDt, col) : 0.0f;
+          }
+          const bool hasBias = p.bias != nullptr, round1 = (p.roundSteps & 1) != 0, round2 = (p.roundSteps & 2) != 0;
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int e = v * 8 + j * 2;
-                float b0 = p.bias ? loadBias(p.bias, p.biasDt, col0 + e) : 0.0f;
-                float b1 = p.bias ? loadBias(p.bias, p.biasDt, col0 + e + 1) : 0.0f;
-                TC x0 = epilogue<TC>(__uint_as_float(r[e]), p.bias != nullptr, b0, p.act, p.roundSteps);
-                TC x1 = epilogue<TC>(__uint_as_float(r[e + 1]), p.bias != nullptr, b1, p.act, p.roundSteps);
-                w[j] = static_cast<uint32_t>(*reinterpret_cast<uint16_t *>(&x0)) |
-                       (static_cast<uint32_t>(*reinterpret_cast<uint16_t *>(&x1)) << 16);
-              }
-              *reinterpret_cast<uint4 *>(dst + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          for (int e = 0; e < CH; ++e) {
+            float f = __uint_as_float(r[e]);
+            float bz = __shfl_sync(0xffffffffu, biasReg[e / 32], e & 31);
+            if (round1) f = toF32(fromF32<TC>(f));
+            if (hasBias) f = __fadd_rn(f, bz);
+            if (hasBias && round2) f = toF32(fromF32<TC>(f));
+            r[e] = __float_as_uint(f);
+          }
+          switch (p.act) {
+          case TTB_ACT_RELU:
+#pragma unroll
+            for (int e = 0; e < CH; ++e) { float f = __uint_as_float(r[e]); r[e] = __float_as_uint(f > 0.0f ? f : (f != f ? f : 0.0f)); }
+            break;
+          case TTB_ACT_SILU:
+#pragma unroll
+            for (int e = 0; e < CH; ++e) { float f = __uint_as_float(r[e]); r[e] = __float_as_uint(f / (1.0f + expf(-f))); }
+            break;
+          case TTB_ACT_GELU:
+#pragma unroll
+            for (int e = 0; e < CH; ++e) { float f = __uint_as_float(r[e]); r[e] = __float_as_uint(applyAct(TTB_ACT_GELU, f)); }
+            break;
+          case TTB_ACT_SIGMOID:
+#pragma unroll
+            for (int e = 0; e < CH; ++e) { float f = __uint_as_float(r[e]); r[e] = __float_as_uint(1.0f / (1.0f + expf(-f))); }
+            break;
+          default: break;
+          }
+        }
+        const uint32_t buf = stageOut + (chunkIt & 1u) * 4096u;
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); // buffer free again
+        __syncwarp();
+        const uint32_t rowAddr = buf + static_cast<uint32_t>(lane) * 128u;
+#pragma unroll
+        for (int v = 0; v < 8; ++v) { // eight 16-byte pieces of this lane's 128-byte row
+          uint32_t w[4];
+          if constexpr (sizeof(TC) == 2) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int e = v * 8 + q * 2;
+              float f0 = __uint_as_float(r[e]), f1 = __uint_as_float(r[e + 1]);
+              w[q] = pack2<TC>(f0, f1); // one cvt.rn for the pair
             }
           } else {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              if (col0 + e < p.N) {
-                float b0 = p.bias ? loadBias(p.bias, p.biasDt, col0 + e) : 0.0f;
-                dst[e] = epilogue<TC>(__uint_as_float(r[e]), p.bias != nullptr, b0, p.act, p.roundSteps);
-              }
+            for (int q = 0; q < 4; ++q) {
+              const int e = v * 4 + q;
+              float f0 = __uint_as_float(r[e]);
+              w[q] = __float_as_uint(f0);
             }
           }
+          // 128-byte swizzle (what the tensor map of C expects): 16-byte piece v of row `lane`
+          // lives at piece v ^ (lane % 8); this also spreads the lanes over the banks
+          const uint32_t addr = rowAddr + (static_cast<uint32_t>(v ^ (lane & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                       ::"l"(reinterpret_cast<uint64_t>(&mapC)), "r"(buf), "r"(static_cast<int>(col0)),
+                         "r"(static_cast<int>(m0 + quarter * 32)) : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        ++chunkIt;
       }
       tcFenceBefore();
-      mbarArrive(tmemEmptyBar(acc)); // all 128 epilogue threads arrive
+      mbarArrive(tmemEmptyBar(acc)); // all 128 epilogue threads arrive: the accumulator may be overwritten
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); // stores done before smem goes away
   }
 
   // ---------------- teardown ----------------
@@ -322,32 +402,36 @@ static EncodeTiledFn encodeTiled() {
   return fn;
 }
 
-// Row-major [rows, cols] 16-bit matrix, box = 64 columns x boxRows rows, 128-byte swizzle,
-// out-of-bounds elements read as zero (which is what makes ragged M / N / K tails work).
+// Row-major [rows, cols] matrix, box = boxCols x boxRows (boxCols spans 128 bytes), 128-byte
+// swizzle; out-of-bounds elements read as zero and are not written, which is what makes ragged
+// M / N / K tails work.
 static bool makeMap(CUtensorMap *map, const void *ptr, int dtype, int64_t rows, int64_t cols, int boxRows) {
   EncodeTiledFn fn = encodeTiled();
   if (!fn) return false;
+  size_t es = dtypeSize(dtype);
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
-  cuuint32_t box[2] = {TC_BK, static_cast<cuuint32_t>(boxRows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * es};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(boxRows)};
   cuuint32_t elemStrides[2] = {1, 1};
-  CUtensorMapDataType dt = dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMapDataType dt = dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : (dtype == kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
   CUresult r = fn(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
-template <int BN, typename TC>
-static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, void *c, const TcParams &p, cudaStream_t st) {
+template <int BN, typename TC, bool PLAIN>
+static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, void *c, const TcParams &p,
+                    cudaStream_t st) {
   using Cfg = TcCfg<BN>;
   static bool attr = false;
   if (!attr) {
-    TTB_CUDA(cudaFuncSetAttribute(gemmTcgen05Kernel<BN, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+    TTB_CUDA(cudaFuncSetAttribute(gemmTcgen05Kernel<BN, TC, PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
     attr = true;
   }
   int64_t tiles = ((p.M + TC_BM - 1) / TC_BM) * ((p.N + BN - 1) / BN);
   int grid = static_cast<int>(tiles < smCount() ? tiles : smCount());
-  gemmTcgen05Kernel<BN, TC><<<grid, TC_THREADS, Cfg::kSmem, st>>>(ma, mb, static_cast<TC *>(c), p);
+  gemmTcgen05Kernel<BN, TC, PLAIN><<<grid, TC_THREADS, Cfg::kSmem, st>>>(ma, mb, mc, static_cast<TC *>(c), p);
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;
@@ -362,24 +446,45 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   if (abDtype != kBF16 && abDtype != kF16) return -1;
   if (cDtype != abDtype && cDtype != kF32) return -1;
   if (k % 8 != 0 || m < 1 || n < 8 || k < 8) return -1;
+  if ((n * static_cast<int64_t>(dtypeSize(cDtype))) % 16 != 0) return -1; // row pitch of C for the TMA store
   if (!aligned16(a) || !aligned16(b) || !aligned16(c)) return -1;
   if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff) return -1;
   // Tiny problems are launch-bound either way; keep them on the simple kernel.
   if (m * n * k < (1ll << 18)) return -1;
-  int bn = n >= 256 ? 256 : (n >= 128 ? 128 : 64);
-  // Prefer the tile width that fills the machine: with few tiles, narrower tiles use more SMs.
-  auto tilesFor = [&](int w) { return ((m + TC_BM - 1) / TC_BM) * ((n + w - 1) / w); };
-  while (bn > 64 && tilesFor(bn) < smCount() && tilesFor(bn / 2) > tilesFor(bn)) bn /= 2;
-  CUtensorMap ma, mb;
-  if (!makeMap(&ma, a, abDtype, m, k, TC_BM) || !makeMap(&mb, b, abDtype, n, k, bn)) return -1;
+  // Tile width: fewest (waves x per-tile cost); the +64 stands for the A tile every CTA loads
+  // whatever its width, which makes narrow tiles less efficient per column.
+  int bn = 64;
+  {
+    int64_t best = -1;
+    for (int w : {256, 128, 64}) {
+      if (w > 64 && n < w) continue;
+      int64_t tiles = ((m + TC_BM - 1) / TC_BM) * ((n + w - 1) / w);
+      int64_t waves = (tiles + smCount() - 1) / smCount();
+      int64_t cost = waves * (w + 64);
+      if (best < 0 || cost < best) {
+        best = cost;
+        bn = w;
+      }
+    }
+  }
+  CUtensorMap ma, mb, mc;
+  if (!makeMap(&ma, a, abDtype, m, k, TC_BM) || !makeMap(&mb, b, abDtype, n, k, bn) ||
+      !makeMap(&mc, c, cDtype, m, n, 32))
+    return -1;
   TcParams p;
   p.M = m; p.N = n; p.K = k;
   p.bias = bias; p.biasDt = biasDtype; p.act = act; p.roundSteps = roundSteps;
   p.fmt = abDtype == kBF16 ? 1 : 0;
+  {
+    const char *dbg = std::getenv("TTB_TC_DEBUG");
+    p.debug = dbg ? std::atoi(dbg) : 0;
+  }
   double flops = 2.0 * double(m) * double(n) * double(k);
   double bytes = (double(m) * k + double(n) * k) * 2 + double(m) * n * dtypeSize(cDtype);
   ProfScope prof("gemm_tcgen05", flops, bytes, stream);
-#define TTB_TC(BNv, TCv) return launchTc<BNv, TCv>(ma, mb, c, p, stream)
+  const bool plain = !bias && act == TTB_ACT_NONE && roundSteps == 0;
+#define TTB_TC(BNv, TCv)                                                                 \
+  return plain ? launchTc<BNv, TCv, true>(ma, mb, mc, c, p, stream) : launchTc<BNv, TCv, false>(ma, mb, mc, c, p, stream)
 #define TTB_TC_BN(TCv)                                                                   \
   switch (bn) {                                                                          \
   case 256: TTB_TC(256, TCv);                                                            \

@@ -87,13 +87,17 @@ def test_config4_decoder_block_full_size(rt, device):
     assert list(got.shape) == [1, 2048, 4096] and torch.isfinite(got.float()).all()
     want = oracle_results(graphs.decoder_block_graph, ins)[0]
     # 30 chained bf16 ops with reductions over up to 14336 terms: f32 summation order moves a few
-    # intermediate values across bf16 rounding boundaries, and the residual stream (|x| up to ~16,
-    # one ulp = 0.0625 there) carries that on.  Every element must stay within 4 ulp, and 99.9 % of
-    # them within the stated atol of 1e-2 plus one ulp.
-    assert_matches(got, want, "decoder full", (0.999, 5e-2, 2.0 ** -5))
+    # intermediate values across bf16 rounding boundaries, and the residual adds (|x| up to ~16,
+    # one ulp = 0.0625 there) carry that into outputs of any magnitude, small ones included, so a
+    # per-element relative bound cannot hold.  Required instead: PCC >= 0.999, 99.9 % of the
+    # elements within the stated atol of 1e-2 plus one ulp of their own magnitude, and no element
+    # further off than one ulp of the largest magnitude in the tensor.
+    from oracle import metrics
+    assert metrics.get_pcc(want, got) >= 0.999
     err = (got.float() - want.float()).abs()
     tight = err <= 1e-2 + 2.0 ** -7 * want.float().abs()
-    assert tight.float().mean().item() > 0.999
+    assert tight.float().mean().item() > 0.999, f"only {tight.float().mean().item():.5f} of the elements are tight"
+    assert err.max().item() <= 2.0 ** -7 * want.float().abs().max().item(), f"max error {err.max().item()}"
     # causality: changing the last 1024 tokens leaves the first 1024 outputs untouched
     ins2 = [t.clone() for t in ins]
     ins2[0][:, 1024:] = torch.randn(1, 1024, 4096).to(torch.bfloat16)

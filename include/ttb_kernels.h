@@ -222,6 +222,34 @@ TTB_API int ttb_conv2d(const void *x, const void *weight, const void *bias, void
                        int kh, int kw, int stride_h, int stride_w, const int *padding4, int dil_h,
                        int dil_w, int groups, int act, void *workspace, void *stream);
 
+/* conv2d for callers that must not allocate.  No counterpart in the reference: tt-mlir's
+ * runtime always lets the device library allocate its own intermediates.
+ *
+ * Some hosts of this library cannot call cudaMalloc at the point where they run a convolution:
+ * code inside a latency-critical serving loop whose memory was handed out up front by an
+ * arena it does not own, or a plugin whose embedding application forbids device allocation
+ * after start-up.  ttb_conv2d needs a workspace for the gathered receptive fields and the
+ * re-ordered weights; this variant takes that workspace from a fixed buffer of
+ * TTB_CONV2D_STATIC_SCRATCH_BYTES that is part of the library's device image (each GPU that
+ * loads the library carries it until the process ends) and otherwise behaves exactly like
+ * ttb_conv2d -- same kernels, same results.  It calls no cudaMalloc / cudaFree and no
+ * allocating library routine; the caller still supplies input, weight, bias and output.
+ *
+ *  - A convolution whose workspace (ttb_conv2d_workspace_bytes) exceeds the buffer is refused
+ *    with TTB_ERR_INVALID and a message naming both sizes.
+ *  - The first call on each device looks up the buffer's device address; make that first
+ *    call during start-up, before any stream capture begins.
+ *  - All calls share the one buffer and it keeps whatever the previous call left there.
+ *    Nothing in it has to start at zero: every byte a launch reads was written by the same
+ *    launch sequence before.  Two calls whose kernels overlap on the GPU (different streams)
+ *    would overwrite each other's scratch; issue them on one stream or order them yourself. */
+#define TTB_CONV2D_STATIC_SCRATCH_BYTES (32u << 20)
+TTB_API int ttb_conv2d_static(const void *x, const void *weight, const void *bias, void *out,
+                              int dtype, int bias_dtype, int64_t n, int64_t h, int64_t w, int64_t c,
+                              int64_t o, int kh, int kw, int stride_h, int stride_w,
+                              const int *padding4, int dil_h, int dil_w, int groups, int act,
+                              void *stream);
+
 /* ::ttnn::transformer::scaled_dot_product_attention
  * (runtime/lib/ttnn/operations/transformer/scaled_dot_product_attention.cpp:41-45; golden
  * tools/golden/mapping.py:8398-8500): out = softmax(q k^T * scale + mask) v with f32 softmax.

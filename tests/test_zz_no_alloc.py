@@ -1,0 +1,80 @@
+"""ttb_conv2d_static: the convolution entry point that takes its workspace from a buffer built
+into the library instead of from the caller.
+
+It exists for hosts that may not allocate device memory where they run the convolution (a
+serving loop living inside someone else's memory arena, a plugin whose application forbids
+cudaMalloc after start-up).  The test drives it through the C ABI next to the ordinary
+ttb_conv2d (which gets a workspace allocated here) and requires identical bytes, twice in a
+row with different data, so that whatever the first call left in the shared buffer cannot
+leak into the second.  The file name sorts last on purpose: a run that stops at the first
+failure has then already executed every other test.
+"""
+
+import ctypes
+
+import pytest
+import torch
+
+from helpers import KernelHarness
+
+pytestmark = pytest.mark.gpu
+
+BF16 = 2
+
+
+def conv_pair(h, seed, n, hh, ww, c, o, k, pad):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(n, hh, ww, c, generator=g).to(torch.bfloat16)
+    w = (torch.randn(o, c, k, k, generator=g) * 0.1).to(torch.bfloat16)
+    b = torch.randn(o, generator=g).to(torch.bfloat16)
+    dx, dw, db = h.upload(x), h.upload(w), h.upload(b)
+    ho, wo = hh + 2 * pad - k + 1, ww + 2 * pad - k + 1
+    padding = (ctypes.c_int * 4)(pad, pad, pad, pad)
+    i64 = ctypes.c_int64
+    lib = h.lib
+    need = lib.ttb_conv2d_workspace_bytes(BF16, i64(n), i64(hh), i64(ww), i64(c), i64(o), k, k, 1, 1, padding, 1, 1, 1)
+    assert 0 < need <= (32 << 20)
+    ws = h.empty((need,), torch.uint8)
+    out_ref = h.empty((n, ho, wo, o), torch.bfloat16)
+    out_new = h.empty((n, ho, wo, o), torch.bfloat16)
+    rc = lib.ttb_conv2d(dx, dw, db, out_ref, BF16, BF16, i64(n), i64(hh), i64(ww), i64(c), i64(o), k, k, 1, 1, padding,
+                        1, 1, 1, 1, ws, h.stream)
+    assert rc == 0, lib.ttb_last_error().decode()
+    rc = lib.ttb_conv2d_static(dx, dw, db, out_new, BF16, BF16, i64(n), i64(hh), i64(ww), i64(c), i64(o), k, k, 1, 1,
+                               padding, 1, 1, 1, 1, h.stream)
+    assert rc == 0, lib.ttb_last_error().decode()
+    shape = (n, ho, wo, o)
+    return h.download(out_ref, shape, torch.bfloat16), h.download(out_new, shape, torch.bfloat16), x, w, b
+
+
+def test_static_scratch_conv_matches_workspace_conv_twice(rt, device):
+    h = KernelHarness(rt)
+    try:
+        ref1, new1, x, w, b = conv_pair(h, 11, 2, 20, 18, 64, 96, 3, 1)
+        assert torch.equal(ref1, new1)
+        # and both agree with a float reference of the same convolution (+ bias, relu)
+        want = torch.nn.functional.conv2d(x.float().permute(0, 3, 1, 2), w.float(), b.float(), padding=1)
+        want = torch.relu(want).permute(0, 2, 3, 1)
+        assert torch.allclose(new1.float(), want, atol=1e-2, rtol=2.0 ** -7)
+        # second call, other data and a smaller problem: stale scratch contents must not matter
+        ref2, new2, *_ = conv_pair(h, 12, 1, 9, 13, 32, 40, 3, 1)
+        assert torch.equal(ref2, new2)
+        assert not torch.equal(new1.reshape(-1)[: new2.numel()], new2.reshape(-1))
+    finally:
+        h.close()
+
+
+def test_static_scratch_refuses_oversized_problem(rt, device):
+    h = KernelHarness(rt)
+    try:
+        i64 = ctypes.c_int64
+        padding = (ctypes.c_int * 4)(1, 1, 1, 1)
+        dummy = h.empty((16,), torch.uint8)
+        # 64 x 56 x 56 pixels x 576 taps x 2 bytes = 231 MB of gathered input: beyond the 32 MiB buffer
+        rc = h.lib.ttb_conv2d_static(dummy, dummy, None, dummy, BF16, BF16, i64(64), i64(56), i64(56), i64(64), i64(64),
+                                     3, 3, 1, 1, padding, 1, 1, 1, 0, h.stream)
+        assert rc != 0
+        msg = h.lib.ttb_last_error().decode()
+        assert "scratch" in msg and "ttb_conv2d" in msg
+    finally:
+        h.close()

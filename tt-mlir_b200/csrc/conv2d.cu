@@ -9,7 +9,13 @@
 // image) and reorders the weights from [O, C, kH, kW] to [O, kH, kW, C] in a workspace.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace ttb {
+
+// Scratch for ttb_conv2d_static: lives in the library's device image, so every GPU that loads
+// the library holds these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_convStaticScratch[TTB_CONV2D_STATIC_SCRATCH_BYTES];
 
 struct ConvGeom {
   int64_t N, H, W, C, Ho, Wo;
@@ -119,6 +125,39 @@ int ttb_conv2d(const void *x, const void *weight, const void *bias, void *out, i
   countLaunch();
   TTB_LAUNCH_CHECK();
   return ttb_gemm(col, wre, bias, out, dtype, bias_dtype, dtype, 1, P, o, K, 0, 1, 0, 0, act, 0, stream);
+}
+
+int ttb_conv2d_static(const void *x, const void *weight, const void *bias, void *out, int dtype, int bias_dtype,
+                      int64_t n, int64_t h, int64_t w, int64_t c, int64_t o, int kh, int kw, int stride_h, int stride_w,
+                      const int *padding4, int dil_h, int dil_w, int groups, int act, void *stream) {
+  TTB_CHECK(padding4 != nullptr, "null argument");
+  size_t need = ttb_conv2d_workspace_bytes(dtype, n, h, w, c, o, kh, kw, stride_h, stride_w, padding4, dil_h, dil_w, groups);
+  if (need > TTB_CONV2D_STATIC_SCRATCH_BYTES) {
+    setLastError("conv2d_static: this convolution needs " + std::to_string(need) + " bytes of scratch, the built-in buffer has " +
+                 std::to_string(static_cast<size_t>(TTB_CONV2D_STATIC_SCRATCH_BYTES)) +
+                 "; use ttb_conv2d with a caller-provided workspace");
+    return TTB_ERR_INVALID;
+  }
+  // The array's name is only a host-side handle; the kernels need its device address, which
+  // differs per GPU.  It is looked up once per device, with that device current.
+  static std::mutex mu;
+  static void *scratchOf[64] = {};
+  int dev = -1;
+  TTB_CUDA(cudaGetDevice(&dev));
+  TTB_CHECK(dev >= 0 && dev < 64, "device ordinal out of range");
+  void *scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> g(mu);
+    if (!scratchOf[dev]) {
+      void *p = nullptr;
+      TTB_CUDA(cudaGetSymbolAddress(&p, g_convStaticScratch));
+      TTB_CHECK(p != nullptr, "scratch symbol has no device address");
+      scratchOf[dev] = p;
+    }
+    scratch = scratchOf[dev];
+  }
+  return ttb_conv2d(x, weight, bias, out, dtype, bias_dtype, n, h, w, c, o, kh, kw, stride_h, stride_w, padding4, dil_h,
+                    dil_w, groups, act, need ? scratch : nullptr, stream);
 }
 
 } // extern "C"

@@ -1,0 +1,96 @@
+"""Host-side mesh logic on CPU ranks: the sharding helpers and the oracle's collective semantics
+against real collectives (gloo, world size 2)."""
+
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+from __graft_entry__ import load_package  # noqa: E402  (spawned workers import this module without conftest)
+
+load_package()
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import ops
+from ttmlir_b200 import graphs
+
+
+def _worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(5)
+        full = torch.randn(4, 6, generator=g)
+        mine = graphs.shard_inputs([full], [0], world, rank)[0]
+        # all_reduce(sum) of the shards equals the oracle's all_reduce
+        t = mine.clone()
+        dist.all_reduce(t)
+        want = ops.all_reduce(ops.mesh_shard_full_to_shard(full, world, 0))[rank]
+        ok = torch.allclose(t, want)
+        # all_gather along dim 0 restores the full tensor, as mesh_shard shard_to_full does
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        ok = ok and torch.equal(torch.cat(parts, 0), full)
+        ok = ok and torch.equal(ops.mesh_shard_shard_to_full(parts, 0), full)
+        # reduce_scatter = reduce then chunk
+        rs = ops.reduce_scatter(ops.mesh_shard_full_to_shard(full, world, None), 1)[rank]
+        ok = ok and torch.allclose(rs, torch.chunk(full * world, world, dim=1)[rank])
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_collective_semantics_with_gloo_ranks():
+    world = 2
+    port = 29500 + (os.getpid() % 2000)
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+        assert dict(ret) == {0: True, 1: True}
+
+
+def test_tensor_parallel_sharding_covers_every_weight_once():
+    kw = dict(seq=64, hidden=128, n_heads=4, n_kv_heads=2, head_dim=32, ffn=256)
+    ins = graphs.decoder_block_inputs(**kw)
+    dims = graphs.decoder_shard_dims(**kw)
+    for tp in (1, 2):
+        shards = [graphs.shard_inputs(ins, dims, tp, r) for r in range(tp)]
+        for i, (t, d) in enumerate(zip(ins, dims)):
+            if d is None:
+                assert all(torch.equal(s[i], t) for s in shards)
+            else:
+                assert torch.equal(torch.cat([s[i] for s in shards], dim=d), t)
+
+
+def test_tensor_parallel_oracle_matches_single_device():
+    kw = dict(seq=64, hidden=128, n_heads=4, n_kv_heads=2, head_dim=32, ffn=256)
+    ins = graphs.decoder_block_inputs(**kw)
+    from oracle.backend import OracleBuilder
+    a = OracleBuilder(ins)
+    graphs.decoder_block_graph(a, **kw)
+    b = OracleBuilder(ins, mesh_shape=(1, 2))
+    graphs.decoder_block_graph(b, tp=2, **kw)
+    # the only difference is where the bf16 rounding of the partial sums happens
+    assert torch.allclose(a.results()[0].float(), b.results()[0].float(), atol=0.07, rtol=0.02)
+
+
+def test_mesh_program_structure():
+    from ttmlir_b200.schema.fbs import Reader
+    from ttmlir_b200.schema.ttnn_schema import S
+    buf = graphs.build_binary(graphs.bottleneck_graph, mesh_shape=(1, 2), dp=2, batch=4, hw=8)
+    prog = Reader(S, buf).root("TTNNBinary")["programs"][0]
+    assert prog["mesh_shape"] == {"y": 1, "x": 2}
+    ops_ = [o["type"] for o in prog["operations"]]
+    dist_ops = [t for k, t in ops_ if k == "DistributeTensorOp"]
+    assert dist_ops[0]["mapper_config"]["placements"] == [{"type": "Replicate", "dim": -1}, {"type": "Shard", "dim": 2}]
+    assert all(p["mapper_config"]["placements"][1]["type"] == "Replicate" for p in dist_ops[1:])
+    ag = next(t for k, t in ops_ if k == "AllGatherOp")
+    assert ag["all_gather_dim"] == 2 and ag["cluster_axis"] == 1
+    agg = next(t for k, t in ops_ if k == "AggregateTensorOp")
+    assert agg["composer_config"]["dims"] == [0] and agg["composer_config"]["mesh_shape_override"] == [1]

@@ -283,6 +283,74 @@ def run_reference(args):
     }
 
 
+# ---- the other benchmark configurations (single GPU), as extra report lines -----------------------
+def side_workloads():
+    """name -> (graph function, kwargs, input maker, algorithmic bytes, algorithmic flops, units per step, unit name)."""
+    from ttmlir_b200 import graphs
+    n2 = 4096 * 4096
+    m3, k3, n3 = 2048, 4096, 11008
+    px = 64 * 56 * 56
+    return {
+        "mlp": (graphs.mlp_graph, {}, graphs.mlp_inputs, 1220648.0, 52035584.0, 128, "rows"),
+        "quant": (graphs.quant_chain_graph, {}, graphs.quant_chain_inputs, 6.0 * n2, 0.0, n2, "elements"),
+        "quant_int8": (graphs.quant_chain_graph, {"container": "Int8"}, graphs.quant_chain_inputs, 6.0 * n2, 0.0, n2, "elements"),
+        "w8_linear": (graphs.w8_linear_graph, {}, graphs.w8_linear_inputs, 107020800.0, 2.0 * m3 * k3 * n3, m3, "rows"),
+        "bottleneck": (graphs.bottleneck_graph, {}, graphs.bottleneck_inputs, 128450560.0, 29.595e9, 64, "images"),
+    }
+
+
+def run_side(args):
+    """One of the single-GPU configurations through submit with resident inputs; prints one JSON line."""
+    import torch  # noqa: F401
+    from __graft_entry__ import load_package
+    load_package()
+    from ttmlir_b200 import graphs, runtime_api as rt
+    graph, kw, make_inputs, abytes, aflops, units, unit_name = side_workloads()[args.workload]
+    peaks = measured_peaks()
+    device = rt.open_mesh_device(rt.MeshDeviceOptions(mesh_shape=[1, 1]))
+    stream, _ = device.stream(0)
+    binary = rt.Binary.load_from_memory(graphs.build_binary(graph, **kw))
+    ins = make_inputs()
+    dev_in = [rt.to_layout(rt.from_torch(t), device, rt.get_layout(binary, 0, i), retain=True) for i, t in enumerate(ins)]
+    for _ in range(args.warmup if args.profile else max(args.warmup, 3)):
+        out = rt.submit(device, binary, 0, dev_in)
+    rt.wait(out[0])
+    ev = Events(rt.lib, stream)
+    launches0 = rt.launch_count()
+    ev.start()
+    for _ in range(args.steps):
+        out = rt.submit(device, binary, 0, dev_in)
+    ms = ev.stop_ms() / args.steps
+    launches = rt.launch_count() - launches0
+    prof = []
+    if not args.profile:
+        rt.lib.ttb_prof_enable(1)
+        for _ in range(min(args.steps, 5)):
+            out = rt.submit(device, binary, 0, dev_in)
+        rt.wait(out[0])
+        buf = ctypes.create_string_buffer(1 << 16)
+        assert rt.lib.ttb_prof_summary(buf, ctypes.c_size_t(len(buf))) == 0
+        rt.lib.ttb_prof_enable(0)
+        for k in json.loads(buf.value.decode()):
+            e = {"kernel": k["tag"], "launches_per_step": k["launches"] / min(args.steps, 5), "avg_ms": k["ms"] / k["launches"]}
+            if k["flops"] > 0:
+                e.update(achieved=k["flops"] / (k["ms"] * 1e-3) / 1e12, unit="TFLOP/s")
+                e["frac"] = e["achieved"] / peaks["bf16_tflops"]
+            elif k["bytes"] > 0:
+                e.update(achieved=k["bytes"] / (k["ms"] * 1e-3) / 1e9, unit="GB/s")
+                e["frac"] = e["achieved"] / peaks["hbm_gbs"]
+            prof.append(e)
+    line = {"metric": f"{args.workload}_{unit_name}_per_s", "value": units / (ms * 1e-3), "unit": f"{unit_name}/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "dtype": "f32" if args.workload == "mlp" else "bf16", "data": "synthetic",
+            "config": {"workload": args.workload}, "gpu_launches": launches,
+            "graph_hbm_gbs": abytes / (ms * 1e-3) / 1e9, "graph_hbm_frac": abytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "graph_tflops": aflops / (ms * 1e-3) / 1e12, "graph_tensor_frac": aflops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+            "per_op": prof}
+    rt.close_mesh_device(device)
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -292,8 +360,14 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile", action="store_true",
                     help="for runs under a profiler: exactly --warmup warm-up steps, then --steps steps, nothing else")
+    ap.add_argument("--workload", default="decoder",
+                    choices=["decoder", "mlp", "quant", "quant_int8", "w8_linear", "bottleneck"],
+                    help="decoder (default) is the benchmark; the others report the remaining configurations")
     args = ap.parse_args()
 
+    if args.workload != "decoder":
+        run_side(args)
+        return
     if args.impl == "reference":
         line = run_reference(args)
         if line is not None:

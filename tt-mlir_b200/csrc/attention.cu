@@ -327,23 +327,26 @@ extern "C" int ttb_sdpa(const void *q, const void *k, const void *v, const void 
     dim3 grid(static_cast<unsigned>((seq_q + FA_BM - 1) / FA_BM), static_cast<unsigned>(heads_q),
               static_cast<unsigned>(batch));
     float scaleLog2 = scale * 1.4426950408889634f;
+    int dev = 0;
+    TTB_CUDA(cudaGetDevice(&dev));
+    TTB_CHECK(dev >= 0 && dev < 64, "device ordinal out of range");
     double work = 4.0 * double(batch) * heads_q * seq_q * seq_kv * head_dim * (is_causal ? 0.5 : 1.0);
     ProfScope prof("sdpa_flash", work, 2.0 * batch * (2.0 * heads_q * seq_q + 2.0 * heads_kv * seq_kv) * head_dim, st);
     if (dtype == kBF16) {
-      static bool attr = false;
-      if (!attr) {
+      static bool attrSet[64] = {}; // function attributes belong to a device
+      if (!attrSet[dev]) {
         TTB_CUDA(cudaFuncSetAttribute(flashKernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM));
-        attr = true;
+        attrSet[dev] = true;
       }
       flashKernel<__nv_bfloat16><<<grid, FA_THREADS, FA_SMEM, st>>>(
           static_cast<const __nv_bfloat16 *>(q), static_cast<const __nv_bfloat16 *>(k),
           static_cast<const __nv_bfloat16 *>(v), static_cast<__nv_bfloat16 *>(out), heads_q, heads_kv, seq_q, seq_kv,
           is_causal, scaleLog2);
     } else {
-      static bool attr = false;
-      if (!attr) {
+      static bool attrSet[64] = {};
+      if (!attrSet[dev]) {
         TTB_CUDA(cudaFuncSetAttribute(flashKernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM));
-        attr = true;
+        attrSet[dev] = true;
       }
       flashKernel<__half><<<grid, FA_THREADS, FA_SMEM, st>>>(
           static_cast<const __half *>(q), static_cast<const __half *>(k), static_cast<const __half *>(v),

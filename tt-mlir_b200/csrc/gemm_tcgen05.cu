@@ -424,10 +424,13 @@ template <int BN, typename TC, bool PLAIN>
 static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, void *c, const TcParams &p,
                     cudaStream_t st) {
   using Cfg = TcCfg<BN>;
-  static bool attr = false;
-  if (!attr) {
+  // Function attributes belong to a device: set the shared-memory limit once on each.
+  static bool attrSet[64] = {};
+  int dev = 0;
+  TTB_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attrSet[dev]) {
     TTB_CUDA(cudaFuncSetAttribute(gemmTcgen05Kernel<BN, TC, PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
-    attr = true;
+    attrSet[dev] = true;
   }
   int64_t tiles = ((p.M + TC_BM - 1) / TC_BM) * ((p.N + BN - 1) / BN);
   int grid = static_cast<int>(tiles < smCount() ? tiles : smCount());

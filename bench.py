@@ -177,8 +177,10 @@ def run_b200(args):
     launches0 = rt.launch_count()
     ev.start()
     last = None
+    t_host = time.perf_counter()
     for _ in range(args.steps):
         last = step_resident()
+    host_submit_us = (time.perf_counter() - t_host) / args.steps * 1e6   # CPU time to enqueue one step
     ms = ev.stop_ms()
     launches = rt.launch_count() - launches0
     barrier()
@@ -190,7 +192,8 @@ def run_b200(args):
 
     if args.profile:
         return dict(rank=rank, world=world, ms_total=ms_total, e2e_s=float("nan"), launches=launches, clocks=clocks,
-                    prof=[], prof_steps=1, tokens=tokens, bytes_io=mine[0].numel() * 2, rt=rt, device=device)
+                    prof=[], prof_steps=1, tokens=tokens, bytes_io=mine[0].numel() * 2, rt=rt, device=device,
+                    host_submit_us=host_submit_us)
 
     # ---- e2e: host buffers in, host buffers out ---------------------------------------------
     for _ in range(2):
@@ -217,7 +220,8 @@ def run_b200(args):
     rt.lib.ttb_prof_enable(0)
     prof = json.loads(buf.value.decode())
     return dict(rank=rank, world=world, ms_total=ms_total, e2e_s=e2e_s, launches=launches, clocks=clocks, prof=prof,
-                prof_steps=prof_steps, tokens=tokens, bytes_io=mine[0].numel() * 2, rt=rt, device=device)
+                prof_steps=prof_steps, tokens=tokens, bytes_io=mine[0].numel() * 2, rt=rt, device=device,
+                host_submit_us=host_submit_us)
 
 
 # ---- the CPU oracle as baseline / reference arm -------------------------------------------------
@@ -413,7 +417,8 @@ def main():
         "data": "synthetic",
         "config": {"workload": "llama-style decoder block (BASELINE config 4), seq 2048, hidden 4096, 32q/8kv heads, ffn 14336",
                    "parallelism": f"tp{world}", "l2": "inputs larger than L2 (436 MB of weights per step vs 126 MB)",
-                   "block_tflops_per_s": flops * steps / (r["ms_total"] * 1e-3) / 1e12},
+                   "block_tflops_per_s": flops * steps / (r["ms_total"] * 1e-3) / 1e12,
+                   "host_enqueue_us_per_step": r["host_submit_us"]},
         "clocks": r["clocks"], "gpu_launches": r["launches"],
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": r["bytes_io"], "d2h_bytes_per_step": r["bytes_io"]},
         "roofline": roofline, "per_op": per_op,

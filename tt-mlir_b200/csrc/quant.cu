@@ -31,8 +31,17 @@ template <typename TQ> __host__ __device__ inline QRange qrangeOf(int clampI8) {
 }
 
 __device__ __forceinline__ int quantOne(float x, float inv, int zp, QRange r) {
-  // rintf rounds half to even; the conversion saturates, the 64-bit add cannot wrap.
-  long long q = static_cast<long long>(__float2int_rn(__fmul_rn(x, inv))) + zp;
+  float t = rintf(__fmul_rn(x, inv)); // round half to even
+  t = (t != t) ? 0.0f : t;
+  // Narrow ranges (int8 / uint8 / uint16 containers, or int32 holding int8 values): clamp in
+  // float before adding the zero point; every value involved is a small integer, so this is
+  // exact and avoids 64-bit integer arithmetic in a bandwidth-bound kernel.
+  if (r.hi - static_cast<long long>(r.lo) <= 65535ll && zp > -(1 << 22) && zp < (1 << 22)) {
+    t = fminf(fmaxf(t, static_cast<float>(r.lo - zp)), static_cast<float>(r.hi - zp));
+    return static_cast<int>(t) + zp;
+  }
+  // Full 32-bit range: the conversion saturates, the 64-bit add cannot wrap.
+  long long q = static_cast<long long>(__float2int_rn(t)) + zp;
   q = q < r.lo ? r.lo : q;
   q = q > r.hi ? r.hi : q;
   return static_cast<int>(q);
@@ -107,8 +116,11 @@ __global__ void __launch_bounds__(256)
                      TO *__restrict__ out, size_t n, float inv1, float s1, int zp1, float inv2, float s2,
                      int zp2, QRange r1, QRange r2) {
   size_t nvec = n / kVec;
-  size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+  // Even split: every block gets the same number of 16-element packs (+-1), so all blocks of the
+  // single resident wave finish together.
+  size_t per = (nvec + gridDim.x - 1) / gridDim.x;
+  size_t first = per * blockIdx.x, last = first + per < nvec ? first + per : nvec;
+  for (size_t i = first + threadIdx.x; i < last; i += blockDim.x) {
     Pack<TI, kVec> x;
     Pack<T1, kVec> a;
     Pack<T2, kVec> b;
@@ -159,6 +171,26 @@ __global__ void __launch_bounds__(256)
     size_t c = (i / inner) % axisLen;
     int zp = zps ? zps[c] : 0;
     out[i] = fromF32<TO>(dequantOne(static_cast<int>(in[i]), scales[c], zp));
+  }
+}
+
+// inner % 16 == 0: a 16-element pack never straddles two channels, so it shares one scale.
+template <typename TQ, typename TO>
+__global__ void __launch_bounds__(256)
+    dequantizeAxisVecKernel(const TQ *__restrict__ in, TO *__restrict__ out, size_t nvec, size_t axisLen, size_t innerVec,
+                            const float *__restrict__ scales, const int *__restrict__ zps) {
+  size_t per = (nvec + gridDim.x - 1) / gridDim.x;
+  size_t first = per * blockIdx.x, last = first + per < nvec ? first + per : nvec;
+  for (size_t i = first + threadIdx.x; i < last; i += blockDim.x) {
+    size_t c = (i / innerVec) % axisLen;
+    float sc = __ldg(scales + c);
+    int zp = zps ? __ldg(zps + c) : 0;
+    Pack<TQ, kVec> q;
+    Pack<TO, kVec> x;
+    loadPack(q, in + i * kVec);
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) x.v[j] = fromF32<TO>(dequantOne(static_cast<int>(q.v[j]), sc, zp));
+    storePack(out + i * kVec, x);
   }
 }
 
@@ -260,11 +292,20 @@ int ttb_dequantize_per_axis(const void *in, int in_dtype, void *out, int out_dty
   TTB_CHECK(in && out && scales, "null tensor");
   size_t n = outer * axis_len * inner;
   if (n == 0) return TTB_OK;
-  int grid = gridFor(n, 256);
-  TTB_DISPATCH_INT(in_dtype, TQ, TTB_DISPATCH_FLOAT(out_dtype, TO, {
-    dequantizeAxisKernel<TQ, TO><<<grid, 256, 0, asStream(stream)>>>(
-        static_cast<const TQ *>(in), static_cast<TO *>(out), n, axis_len, inner, scales, zero_points);
-  }));
+  ProfScope prof("dequantize_per_axis", 0, double(n) * (dtypeSize(in_dtype) + dtypeSize(out_dtype)), asStream(stream));
+  if (inner % kVec == 0 && vecOk(in, out)) {
+    int grid = gridFor(n / kVec, 256, 8);
+    TTB_DISPATCH_INT(in_dtype, TQ, TTB_DISPATCH_FLOAT(out_dtype, TO, {
+      dequantizeAxisVecKernel<TQ, TO><<<grid, 256, 0, asStream(stream)>>>(
+          static_cast<const TQ *>(in), static_cast<TO *>(out), n / kVec, axis_len, inner / kVec, scales, zero_points);
+    }));
+  } else {
+    int grid = gridFor(n, 256);
+    TTB_DISPATCH_INT(in_dtype, TQ, TTB_DISPATCH_FLOAT(out_dtype, TO, {
+      dequantizeAxisKernel<TQ, TO><<<grid, 256, 0, asStream(stream)>>>(
+          static_cast<const TQ *>(in), static_cast<TO *>(out), n, axis_len, inner, scales, zero_points);
+    }));
+  }
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;
@@ -294,7 +335,7 @@ template <typename TI, typename T1, typename T2, typename TO>
 int launchChain(const void *in, void *q1, void *q2, void *out, size_t n, float s1, int zp1, float s2, int zp2,
                 int clampI8, cudaStream_t st) {
   float inv1 = 1.0f / s1, inv2 = 1.0f / s2;
-  int grid = gridFor((n + kVec - 1) / kVec, 256);
+  int grid = gridFor((n + kVec - 1) / kVec, 256, 8); // one resident wave: 8 blocks of 256 threads per SM
   QRange r1 = qrangeOf<T1>(clampI8), r2 = qrangeOf<T2>(clampI8);
   auto I = static_cast<const TI *>(in);
   auto A = static_cast<T1 *>(q1);

@@ -260,6 +260,10 @@ TTB_API int ttb_sdpa(const void *q, const void *k, const void *v, const void *ma
                      int64_t seq_kv, int64_t head_dim, int64_t mask_batch, int64_t mask_heads,
                      int is_causal, float scale, void *stream);
 
+/* Status word of the tcgen05 attention kernel: 0, or (site << 8) | 1 of the first bounded wait
+ * that ran out (the launch then produced no valid output).  No reference counterpart. */
+TTB_API int ttb_sdpa_tcgen05_status(int *status);
+
 /* ---- collectives on a 1xN mesh: ::ttnn::all_reduce / all_gather / reduce_scatter
  * (runtime/lib/ttnn/operations/ccl/all_reduce.cpp:36-37, all_gather.cpp:38-41,
  * reduce_scatter.cpp:60-67).  Thin, status-returning wrappers over NCCL, which is loaded with

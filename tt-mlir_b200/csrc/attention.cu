@@ -13,6 +13,8 @@
 //    row with the scores in shared memory.  Used for shapes the fast kernel does not take.
 #include "common.cuh"
 
+#include <cstdlib>
+
 #include <cfloat>
 
 namespace ttb {
@@ -310,6 +312,11 @@ __global__ void __launch_bounds__(128)
 
 } // namespace ttb
 
+namespace ttb {
+int sdpaTcgen05Try(const void *q, const void *k, const void *v, void *out, int dtype, int64_t batch, int64_t hq,
+                   int64_t hkv, int64_t sq, int64_t skv, int64_t headDim, int causal, float scale, cudaStream_t st);
+}
+
 using namespace ttb;
 
 extern "C" int ttb_sdpa(const void *q, const void *k, const void *v, const void *mask, void *out, int dtype,
@@ -324,6 +331,15 @@ extern "C" int ttb_sdpa(const void *q, const void *k, const void *v, const void 
   bool fast = !mask && head_dim == FA_D && (dtype == kBF16 || dtype == kF16) && aligned16(q) && aligned16(k) &&
               aligned16(v) && aligned16(out);
   if (fast) {
+    // The tcgen05 kernel first; TTB_SDPA_MMA_SYNC=1 keeps the warp-level tensor-core kernel.
+    static const bool legacy = [] {
+      const char *e = std::getenv("TTB_SDPA_MMA_SYNC");
+      return e && e[0] == '1';
+    }();
+    if (!legacy) {
+      int rc = sdpaTcgen05Try(q, k, v, out, dtype, batch, heads_q, heads_kv, seq_q, seq_kv, head_dim, is_causal, scale, st);
+      if (rc >= 0) return rc;
+    }
     dim3 grid(static_cast<unsigned>((seq_q + FA_BM - 1) / FA_BM), static_cast<unsigned>(heads_q),
               static_cast<unsigned>(batch));
     float scaleLog2 = scale * 1.4426950408889634f;

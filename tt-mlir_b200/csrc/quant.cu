@@ -30,17 +30,40 @@ template <typename TQ> __host__ __device__ inline QRange qrangeOf(int clampI8) {
   return (TQ(-1) < TQ(0)) ? QRange{INT_MIN, INT_MAX} : QRange{0, INT_MAX};
 }
 
-__device__ __forceinline__ int quantOne(float x, float inv, int zp, QRange r) {
-  float t = rintf(__fmul_rn(x, inv)); // round half to even
+// Narrow ranges (int8 / uint8 / uint16 containers, or int32 holding int8 values) never leave the
+// float pipe: rint, float->int and int->float all issue on the quarter-rate conversion unit, and
+// six of them per element made the fused chain issue-bound at half the HBM rate.  Instead:
+// round half to even with the 1.5 * 2^23 trick (exact for |t| < 2^22; t is clamped to that first,
+// which cannot change the result because the final range is far narrower), clamp in float, and
+// carry q - zp as an integer-valued float.
+struct QNarrow {
+  float lo, hi; // range of q - zp
+  int zp;
+  bool ok;
+};
+__host__ __device__ inline QNarrow narrowOf(QRange r, int zp) {
+  QNarrow n;
+  n.ok = (static_cast<long long>(r.hi) - r.lo) <= 65535ll && zp > -(1 << 20) && zp < (1 << 20);
+  n.lo = static_cast<float>(static_cast<long long>(r.lo) - zp);
+  n.hi = static_cast<float>(static_cast<long long>(r.hi) - zp);
+  n.zp = zp;
+  return n;
+}
+__device__ __forceinline__ float roundClampNarrow(float x, float inv, QNarrow n) {
+  float t = __fmul_rn(x, inv);
   t = (t != t) ? 0.0f : t;
-  // Narrow ranges (int8 / uint8 / uint16 containers, or int32 holding int8 values): clamp in
-  // float before adding the zero point; every value involved is a small integer, so this is
-  // exact and avoids 64-bit integer arithmetic in a bandwidth-bound kernel.
-  if (r.hi - static_cast<long long>(r.lo) <= 65535ll && zp > -(1 << 22) && zp < (1 << 22)) {
-    t = fminf(fmaxf(t, static_cast<float>(r.lo - zp)), static_cast<float>(r.hi - zp));
-    return static_cast<int>(t) + zp;
-  }
+  t = fminf(fmaxf(t, -2097152.0f), 2097152.0f);
+  t = __fsub_rn(__fadd_rn(t, 12582912.0f), 12582912.0f); // nearest integer, ties to even
+  return fminf(fmaxf(t, n.lo), n.hi);
+}
+// integer-valued float in (-2^22, 2^22) -> int without a conversion instruction
+__device__ __forceinline__ int floatIntBits(float r) { return __float_as_int(__fadd_rn(r, 12582912.0f)) - 0x4B400000; }
+
+__device__ __forceinline__ int quantOne(float x, float inv, int zp, QRange r) {
+  QNarrow n = narrowOf(r, zp);
+  if (n.ok) return floatIntBits(roundClampNarrow(x, inv, n)) + zp;
   // Full 32-bit range: the conversion saturates, the 64-bit add cannot wrap.
+  float t = rintf(__fmul_rn(x, inv));
   long long q = static_cast<long long>(__float2int_rn(t)) + zp;
   q = q < r.lo ? r.lo : q;
   q = q > r.hi ? r.hi : q;
@@ -116,23 +139,32 @@ __global__ void __launch_bounds__(256)
                      TO *__restrict__ out, size_t n, float inv1, float s1, int zp1, float inv2, float s2,
                      int zp2, QRange r1, QRange r2) {
   size_t nvec = n / kVec;
-  // Even split: every block gets the same number of 16-element packs (+-1), so all blocks of the
-  // single resident wave finish together.
-  size_t per = (nvec + gridDim.x - 1) / gridDim.x;
-  size_t first = per * blockIdx.x, last = first + per < nvec ? first + per : nvec;
-  for (size_t i = first + threadIdx.x; i < last; i += blockDim.x) {
+  const QNarrow n1 = narrowOf(r1, zp1), n2 = narrowOf(r2, zp2);
+  size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
     Pack<TI, kVec> x;
     Pack<T1, kVec> a;
     Pack<T2, kVec> b;
     Pack<TO, kVec> y;
     loadPack(x, in + i * kVec);
+    if (n1.ok && n2.ok) {
 #pragma unroll
-    for (int j = 0; j < kVec; ++j) {
-      int qa = quantOne(toF32(x.v[j]), inv1, zp1, r1);
-      int qb = quantOne(dequantOne(qa, s1, zp1), inv2, zp2, r2);
-      a.v[j] = static_cast<T1>(qa);
-      b.v[j] = static_cast<T2>(qb);
-      y.v[j] = fromF32<TO>(dequantOne(qb, s2, zp2));
+      for (int j = 0; j < kVec; ++j) {
+        float ra = roundClampNarrow(toF32(x.v[j]), inv1, n1);             // q1 - zp1
+        float rb = roundClampNarrow(__fmul_rn(ra, s1), inv2, n2);          // q2 - zp2
+        if (W1) a.v[j] = static_cast<T1>(floatIntBits(ra) + zp1);
+        if (W2) b.v[j] = static_cast<T2>(floatIntBits(rb) + zp2);
+        y.v[j] = fromF32<TO>(__fmul_rn(rb, s2));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) {
+        int qa = quantOne(toF32(x.v[j]), inv1, zp1, r1);
+        int qb = quantOne(dequantOne(qa, s1, zp1), inv2, zp2, r2);
+        a.v[j] = static_cast<T1>(qa);
+        b.v[j] = static_cast<T2>(qb);
+        y.v[j] = fromF32<TO>(dequantOne(qb, s2, zp2));
+      }
     }
     if (W1) storePack(q1 + i * kVec, a);
     if (W2) storePack(q2 + i * kVec, b);
@@ -335,7 +367,7 @@ template <typename TI, typename T1, typename T2, typename TO>
 int launchChain(const void *in, void *q1, void *q2, void *out, size_t n, float s1, int zp1, float s2, int zp2,
                 int clampI8, cudaStream_t st) {
   float inv1 = 1.0f / s1, inv2 = 1.0f / s2;
-  int grid = gridFor((n + kVec - 1) / kVec, 256, 8); // one resident wave: 8 blocks of 256 threads per SM
+  int grid = gridFor((n + kVec - 1) / kVec, 256);
   QRange r1 = qrangeOf<T1>(clampI8), r2 = qrangeOf<T2>(clampI8);
   auto I = static_cast<const TI *>(in);
   auto A = static_cast<T1 *>(q1);

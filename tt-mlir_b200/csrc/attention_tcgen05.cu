@@ -5,15 +5,16 @@
 //
 // One CTA owns 128 query rows of one head and walks the key/value sequence in tiles of 128:
 //   warp 0      TMA producer: Q once, then K and V tiles through two-stage rings
-//   warp 1      issues tcgen05.mma: S = Q K^T into one of two TMEM buffers, then O_j = P V
+//   warp 1      issues tcgen05.mma: S = Q K^T into one of two TMEM buffers, then O += P V
 //   warps 2..5  one query row per thread: read S from TMEM, online softmax in f32, write the
 //               probabilities P (16-bit) into shared memory in the operand layout of the second
-//               contraction, then fold O_j into the row's running output held in registers
+//               contraction; O stays in TMEM and is rescaled there only when the row maximum
+//               has grown by more than a factor 2^8 since the last rescale
 // S_{j+1} is issued before P_j V_j, so the tensor pipe computes the next scores while the
 // softmax warps work on the current ones.  V tiles are used as loaded ([key][d] rows) through
 // an MN-major operand descriptor; nothing is transposed.
 //
-// TMEM: columns 0..127 and 128..255 hold S (double buffer), 256..383 hold O_j.
+// TMEM: columns 0..127 and 128..255 hold S (double buffer), 256..383 hold O.
 // Shared memory (each tile 128 x 128 x 2 B = 32 KiB, stored as two 64-column swizzled halves):
 //   Q | K0 | K1 | V0 | V1 | P | barriers.
 // Every wait is bounded; a wait that runs out records its site in the status word, the CTA
@@ -67,8 +68,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   const uint32_t sQ = base, sK = base + AT_TILE, sV = base + 3 * AT_TILE, sP = base + 5 * AT_TILE;
   const uint32_t bars = base + 6 * AT_TILE;
   const uint32_t qFull = bars, kFull = bars + 8, kEmpty = bars + 24, vFull = bars + 40, vEmpty = bars + 56,
-                 sFull = bars + 72, sEmpty = bars + 88, pReady = bars + 104, pEmpty = bars + 112, oFull = bars + 120,
-                 oEmpty = bars + 128;
+                 sFull = bars + 72, sEmpty = bars + 88, pReady = bars + 104, pEmpty = bars + 112;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t nQ = (p.Sq + AT_BM - 1) / AT_BM;
@@ -98,8 +98,6 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     }
     mbarInit(pReady, 128);
     mbarInit(pEmpty, 1);
-    mbarInit(oFull, 1);
-    mbarInit(oEmpty, 128);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -159,9 +157,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         const int s = j & 1, ph = (j >> 1) & 1;
         if (!mbarWait(vFull + 8 * s, ph, abortP, 6)) break;
         if (!mbarWait(pReady, j & 1, abortP, 7)) break;
-        if (!mbarWait(oEmpty, (j & 1) ^ 1, abortP, 8)) break;
         tcFenceAfter();
-        // O_j = P V_j: eight steps of 16 keys.  P is K-major (keys along its rows); V is
+        // O += P V_j: eight steps of 16 keys.  P is K-major (keys along its rows); V is
         // MN-major: 128-byte rows of 64 d values, one row per key, the second 64 d values one
         // half tile further on.
         const uint32_t vb = sV + s * AT_TILE;
@@ -169,11 +166,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         for (int ks = 0; ks < AT_BN / 16; ++ks) {
           const uint32_t offP = (ks >> 2) * AT_HALF + (ks & 3) * 32;
           tcMma(tmemBase + 2 * AT_BN, smemDescSw128(sP + offP, 0, 1024), smemDescSw128(vb + ks * 2048, AT_HALF, 1024),
-                idPV, ks > 0);
+                idPV, (j | ks) > 0);
         }
         tcCommit(vEmpty + 8 * s);
         tcCommit(pEmpty);
-        tcCommit(oFull);
       }
     }
   } else {
@@ -183,10 +179,12 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     const int64_t qrow = static_cast<int64_t>(q0) + row;
     const uint32_t laneAddr = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16);
     const float sl2 = p.scaleLog2;
-    float m = -INFINITY, l = 0.0f;
-    float o[AT_D];
-#pragma unroll
-    for (int i = 0; i < AT_D; ++i) o[i] = 0.0f;
+    // `m` is the reference maximum the exponentials are taken against.  It follows the true row
+    // maximum lazily: it moves (and O and the row sum are rescaled) only when the maximum grew
+    // by more than 2^kLazy in the exponent, so most tiles skip the rescale and P stays <= 2^kLazy.
+    constexpr float kLazy = 8.0f;
+    float m = 0.0f, l = 0.0f;
+    const uint32_t oAddr = laneAddr + 2 * AT_BN;
     const uint32_t pRow = sP + row * 128;
     const uint32_t swz = static_cast<uint32_t>(row & 7);
     bool ok = true;
@@ -202,8 +200,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       int64_t lastKey = p.Skv - 1;
       if (p.causal && qrow < lastKey) lastKey = qrow;
       const int lastRel = static_cast<int>(lastKey - key0 < AT_BN ? lastKey - key0 : AT_BN);
-      // Pass 1: the row maximum.
-      float mx = m;
+      // Pass 1: the tile's row maximum.
+      float mx = -INFINITY;
 #pragma unroll
       for (int c = 0; c < AT_BN / 32; ++c) {
         uint32_t r[32];
@@ -217,10 +215,30 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
           for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
         }
       }
-      const float mSafe = mx == -INFINITY ? 0.0f : mx;
-      const float corr = m == -INFINITY ? 0.0f : fastExp2((m - mSafe) * sl2);
-      const float negM = -mSafe * sl2;
+      float corr = 1.0f;
+      if (j == 0) {
+        m = mx == -INFINITY ? 0.0f : mx;
+      } else if ((mx - m) * sl2 > kLazy) {
+        corr = fastExp2((m - mx) * sl2);
+        m = mx;
+      }
+      // P's buffer is free, and O holds every earlier tile, once P V_{j-1} has completed.
       if (!__all_sync(0xffffffffu, mbarWait(pEmpty, (j & 1) ^ 1, abortP, 10))) { ok = false; break; }
+      if (__any_sync(0xffffffffu, corr != 1.0f)) {
+        tcFenceAfter();
+        l *= corr;
+#pragma unroll
+        for (int c = 0; c < AT_D / 32; ++c) {
+          uint32_t r[32];
+          tcLoad32(oAddr + c * 32, r);
+          tcWaitLd();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+          tcStore32(oAddr + c * 32, r);
+        }
+        tcWaitSt();
+      }
+      const float negM = -m * sl2;
       // Pass 2: probabilities, their sum, and P in the swizzled K-major operand layout.
       float sum = 0.0f;
 #pragma unroll
@@ -249,37 +267,34 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
                        "r"(w[q4 * 4 + 2]), "r"(w[q4 * 4 + 3]) : "memory");
         }
       }
-      l = l * corr + sum;
-      m = mx;
+      l += sum;
       tcFenceBefore();
       mbarArrive(sEmpty + 8 * s);
       fenceProxyAsyncShared();
       mbarArrive(pReady);
-      // Fold O_j into the running output.
-      if (!__all_sync(0xffffffffu, mbarWait(oFull, j & 1, abortP, 11))) { ok = false; break; }
-      tcFenceAfter();
-#pragma unroll
-      for (int c = 0; c < AT_D / 32; ++c) {
-        uint32_t r[32];
-        tcLoad32(laneAddr + 2 * AT_BN + c * 32, r);
-        tcWaitLd();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], corr, __uint_as_float(r[i]));
-      }
-      tcFenceBefore();
-      mbarArrive(oEmpty);
     }
-    if (ok && qrow < p.Sq) {
+    // The last P V has to land before O is read.
+    if (ok && nT > 0 && !__all_sync(0xffffffffu, mbarWait(pEmpty, (nT & 1) ^ 1, abortP, 11))) ok = false;
+    if (ok) {
+      tcFenceAfter();
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
       T *orow = out + (static_cast<int64_t>(bh) * p.Sq + qrow) * AT_D;
 #pragma unroll
-      for (int c = 0; c < AT_D / 8; ++c) {
-        uint4 v;
-        v.x = packPair<T>(o[c * 8] * inv, o[c * 8 + 1] * inv);
-        v.y = packPair<T>(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
-        v.z = packPair<T>(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv);
-        v.w = packPair<T>(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
-        *reinterpret_cast<uint4 *>(orow + c * 8) = v;
+      for (int c = 0; c < AT_D / 32; ++c) {
+        uint32_t r[32];
+        tcLoad32(oAddr + c * 32, r);
+        tcWaitLd();
+        if (qrow < p.Sq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 v;
+            v.x = packPair<T>(__uint_as_float(r[g * 8]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
+            v.y = packPair<T>(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
+            v.z = packPair<T>(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
+            v.w = packPair<T>(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
+            *reinterpret_cast<uint4 *>(orow + c * 32 + g * 8) = v;
+          }
+        }
       }
     }
   }

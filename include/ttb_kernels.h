@@ -184,6 +184,12 @@ TTB_API int ttb_strided_scatter(const void *in, void *out, int elem_size, int ra
 TTB_API int ttb_rotary_embedding(const void *x, const void *cos, const void *sin, void *out,
                                  int dtype, size_t batch_heads, size_t seq, size_t head_dim,
                                  void *stream);
+/* The same with x read as [batch, heads, seq, head_dim] through element strides
+ * {batch, head, seq} (head_dim contiguous, strides multiples of 16 bytes): a head split that is a
+ * pure permutation of [batch, seq, heads, head_dim] needs no pass of its own.  out is dense. */
+TTB_API int ttb_rotary_embedding_strided(const void *x, const void *cos, const void *sin, void *out,
+                                         int dtype, size_t batch, size_t heads, size_t seq,
+                                         size_t head_dim, const int64_t *x_strides3, void *stream);
 
 /* ---- contractions: ::ttnn::matmul / ::ttnn::linear (operations/matmul/matmul.cpp:75-80,117-122).
  * C[b] = act(A[b]^(ta) * B[b]^(tb) + bias), f32 accumulation, one rounding to `c_dtype`.
@@ -199,6 +205,18 @@ TTB_API int ttb_gemm(const void *a, const void *b, const void *bias, void *c, in
                      int bias_dtype, int c_dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                      int trans_a, int trans_b, int64_t a_batch_stride, int64_t b_batch_stride,
                      int act, int round_steps, void *stream);
+/* ttb_gemm with a second, full-size epilogue operand `extra` ([batch, m, n], dense, in
+ * `c_dtype`), combined with the result of the bias / activation chain the way separate ops
+ * would (the chain's result is rounded to `c_dtype` first):
+ *   TTB_EXTRA_ADD       c = round(result + extra)                  linear followed by ::ttnn::add (a residual)
+ *   TTB_EXTRA_SILU_MUL  c = round(round(silu(extra)) * result)     ::ttnn::silu + ::ttnn::multiply (SwiGLU gating)
+ * On the tensor-core kernel this is one launch; elsewhere the elementwise kernels finish the job.
+ * No reference counterpart: the reference runs these as separate ttnn ops. */
+enum { TTB_EXTRA_NONE = 0, TTB_EXTRA_ADD = 1, TTB_EXTRA_SILU_MUL = 2 };
+TTB_API int ttb_gemm_fused(const void *a, const void *b, const void *bias, void *c, int ab_dtype,
+                           int bias_dtype, int c_dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
+                           int trans_a, int trans_b, int64_t a_batch_stride, int64_t b_batch_stride,
+                           int act, int round_steps, const void *extra, int extra_op, void *stream);
 /* Health of the tensor-core kernel: every wait inside it is bounded, and a wait that gives up
  * records where.  *status == 0 means no launch of this process has timed out.  Synchronises. */
 TTB_API int ttb_gemm_tcgen05_status(int *status);
@@ -259,6 +277,17 @@ TTB_API int ttb_sdpa(const void *q, const void *k, const void *v, const void *ma
                      int dtype, int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seq_q,
                      int64_t seq_kv, int64_t head_dim, int64_t mask_batch, int64_t mask_heads,
                      int is_causal, float scale, void *stream);
+/* ttb_sdpa without a mask tensor, with every operand addressed as [batch, heads, seq, head_dim]
+ * through element strides {batch, head, seq} (head_dim contiguous, strides multiples of 16 bytes).
+ * Lets the caller skip the head split of q/k/v and the head merge of the output
+ * (::ttnn::permute / ::ttnn::transformer::concatenate_heads around the attention op).
+ * Returns TTB_ERR_UNSUPPORTED when no kernel takes the problem with these strides (the
+ * tensor-core kernel needs head_dim 128 and a 16-bit type); dense strides always work. */
+TTB_API int ttb_sdpa_strided(const void *q, const void *k, const void *v, void *out, int dtype,
+                             int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seq_q,
+                             int64_t seq_kv, int64_t head_dim, const int64_t *q_strides3,
+                             const int64_t *k_strides3, const int64_t *v_strides3,
+                             const int64_t *out_strides3, int is_causal, float scale, void *stream);
 
 /* Status word of the tcgen05 attention kernel: 0, or (site << 8) | 1 of the first bounded wait
  * that ran out (the launch then produced no valid output).  No reference counterpart. */

@@ -94,3 +94,40 @@ def test_tcgen05_f32_output(rt, device):
     finally:
         h.close()
     assert_matches(fast, a.float() @ b.float().t(), "f32 out", (0.999, 1e-3, 1e-4))
+
+
+@pytest.mark.parametrize("extra_op", [1, 2])
+@pytest.mark.parametrize("m,n,k,with_bias", [(256, 384, 512, False), (200, 136, 72, True), (2048, 1024, 256, False),
+                                             (8, 16, 32, False)])
+def test_gemm_fused_extra_operand(rt, device, extra_op, m, n, k, with_bias):
+    """ttb_gemm_fused: residual add (1) and SwiGLU gating (2) in the GEMM's epilogue equal the
+    chain of separate ops, with every intermediate rounded to bf16.  The last shape is too small
+    for the tensor-core kernel and exercises the composed fallback."""
+    torch.manual_seed(m + extra_op)
+    a = torch.randn(m, k).to(torch.bfloat16)
+    b = (torch.randn(n, k) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(n).to(torch.bfloat16) if with_bias else None
+    extra = torch.randn(m, n).to(torch.bfloat16)
+    h = KernelHarness(rt)
+    try:
+        da, db, de = h.upload(a), h.upload(b), h.upload(extra)
+        dbias = h.upload(bias) if with_bias else None
+        dc = h.empty((m, n), torch.bfloat16)
+        i64 = ctypes.c_int64
+        rc = h.lib.ttb_gemm_fused(da, db, dbias, dc, BF16, BF16, BF16, i64(1), i64(m), i64(n), i64(k), 0, 1, i64(0), i64(0),
+                                  0, 0, de, extra_op, h.stream)
+        assert rc == 0, h.lib.ttb_last_error().decode()
+        got = h.download(dc, (m, n), torch.bfloat16)
+        assert tc_status(h) == 0
+    finally:
+        h.close()
+    acc = a.float() @ b.float().t()
+    if with_bias:
+        acc = acc + bias.float()
+    r = acc.to(torch.bfloat16).float()
+    if extra_op == 1:
+        want = (r + extra.float()).to(torch.bfloat16)
+    else:
+        s = torch.nn.functional.silu(extra.float()).to(torch.bfloat16).float()
+        want = (s * r).to(torch.bfloat16)
+    assert_matches(got, want, f"gemm_fused op={extra_op} {m}x{n}x{k}")

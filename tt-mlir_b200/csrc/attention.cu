@@ -314,7 +314,15 @@ __global__ void __launch_bounds__(128)
 
 namespace ttb {
 int sdpaTcgen05Try(const void *q, const void *k, const void *v, void *out, int dtype, int64_t batch, int64_t hq,
-                   int64_t hkv, int64_t sq, int64_t skv, int64_t headDim, int causal, float scale, cudaStream_t st);
+                   int64_t hkv, int64_t sq, int64_t skv, int64_t headDim, const int64_t *qs, const int64_t *ks,
+                   const int64_t *vs, const int64_t *os, int causal, float scale, cudaStream_t st);
+static bool sdpaLegacy() {
+  static const bool legacy = [] {
+    const char *e = std::getenv("TTB_SDPA_MMA_SYNC");
+    return e && e[0] == '1';
+  }();
+  return legacy;
+}
 }
 
 using namespace ttb;
@@ -332,12 +340,11 @@ extern "C" int ttb_sdpa(const void *q, const void *k, const void *v, const void 
               aligned16(v) && aligned16(out);
   if (fast) {
     // The tcgen05 kernel first; TTB_SDPA_MMA_SYNC=1 keeps the warp-level tensor-core kernel.
-    static const bool legacy = [] {
-      const char *e = std::getenv("TTB_SDPA_MMA_SYNC");
-      return e && e[0] == '1';
-    }();
-    if (!legacy) {
-      int rc = sdpaTcgen05Try(q, k, v, out, dtype, batch, heads_q, heads_kv, seq_q, seq_kv, head_dim, is_causal, scale, st);
+    if (!sdpaLegacy()) {
+      int64_t qs[3] = {heads_q * seq_q * head_dim, seq_q * head_dim, head_dim};
+      int64_t ks[3] = {heads_kv * seq_kv * head_dim, seq_kv * head_dim, head_dim};
+      int rc = sdpaTcgen05Try(q, k, v, out, dtype, batch, heads_q, heads_kv, seq_q, seq_kv, head_dim, qs, ks, ks, qs,
+                              is_causal, scale, st);
       if (rc >= 0) return rc;
     }
     dim3 grid(static_cast<unsigned>((seq_q + FA_BM - 1) / FA_BM), static_cast<unsigned>(heads_q),
@@ -389,4 +396,33 @@ extern "C" int ttb_sdpa(const void *q, const void *k, const void *v, const void 
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;
+}
+
+extern "C" int ttb_sdpa_strided(const void *q, const void *k, const void *v, void *out, int dtype, int64_t batch,
+                                int64_t heads_q, int64_t heads_kv, int64_t seq_q, int64_t seq_kv, int64_t head_dim,
+                                const int64_t *q_strides3, const int64_t *k_strides3, const int64_t *v_strides3,
+                                const int64_t *out_strides3, int is_causal, float scale, void *stream) {
+  TTB_CHECK(q && k && v && out && q_strides3 && k_strides3 && v_strides3 && out_strides3, "null argument");
+  TTB_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0, "bad head configuration");
+  TTB_CHECK(seq_q > 0 && seq_kv > 0 && head_dim > 0, "empty attention problem");
+  if (!sdpaLegacy()) {
+    int rc = sdpaTcgen05Try(q, k, v, out, dtype, batch, heads_q, heads_kv, seq_q, seq_kv, head_dim, q_strides3, k_strides3,
+                            v_strides3, out_strides3, is_causal, scale, asStream(stream));
+    if (rc >= 0) return rc;
+  }
+  const int64_t dq[3] = {heads_q * seq_q * head_dim, seq_q * head_dim, head_dim};
+  const int64_t dk[3] = {heads_kv * seq_kv * head_dim, seq_kv * head_dim, head_dim};
+  bool dense = true;
+  for (int i = 0; i < 3; ++i) {
+    // a stride is irrelevant along a dimension of extent 1
+    const int64_t extQ = i == 0 ? batch : (i == 1 ? heads_q : seq_q), extK = i == 0 ? batch : (i == 1 ? heads_kv : seq_kv);
+    if (extQ > 1 && (q_strides3[i] != dq[i] || out_strides3[i] != dq[i])) dense = false;
+    if (extK > 1 && (k_strides3[i] != dk[i] || v_strides3[i] != dk[i])) dense = false;
+  }
+  if (!dense) {
+    setLastError("sdpa_strided: no kernel takes this problem with non-dense strides");
+    return TTB_ERR_UNSUPPORTED;
+  }
+  return ttb_sdpa(q, k, v, nullptr, out, dtype, batch, heads_q, heads_kv, seq_q, seq_kv, head_dim, 0, 0, is_causal, scale,
+                  stream);
 }

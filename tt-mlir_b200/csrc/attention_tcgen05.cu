@@ -35,6 +35,7 @@ constexpr int AT_SMEM = 6 * AT_TILE + 1024 /* alignment slack */ + 256 /* barrie
 
 struct AtParams {
   int64_t Hq, Hkv, Sq, Skv;
+  int64_t ob, oh, os; // element strides of out over batch, head, query row
   int causal;
   int fmt; // 1 bf16, 0 f16
   float scaleLog2;
@@ -77,7 +78,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   const int qb = static_cast<int>(nQ - 1 - blockIdx.x / BH);
   const int bh = static_cast<int>(blockIdx.x % BH);
   const int b = static_cast<int>(bh / p.Hq), h = static_cast<int>(bh % p.Hq);
-  const int bhkv = static_cast<int>(b * p.Hkv + h / (p.Hq / p.Hkv));
+  const int hkv = static_cast<int>(h / (p.Hq / p.Hkv));
   const int q0 = qb * AT_BM;
   int nT = static_cast<int>((p.Skv + AT_BN - 1) / AT_BN);
   if (p.causal) {
@@ -116,18 +117,18 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       prefetchTensorMap(&mapK);
       prefetchTensorMap(&mapV);
       mbarArriveExpectTx(qFull, AT_TILE);
-      tmaLoad3d(sQ, &mapQ, qFull, 0, q0, bh);
-      tmaLoad3d(sQ + AT_HALF, &mapQ, qFull, 64, q0, bh);
+      tmaLoad4d(sQ, &mapQ, qFull, 0, q0, h, b);
+      tmaLoad4d(sQ + AT_HALF, &mapQ, qFull, 64, q0, h, b);
       for (int j = 0; j < nT; ++j) {
         const int s = j & 1, ph = (j >> 1) & 1;
         if (!mbarWait(kEmpty + 8 * s, ph ^ 1, abortP, 1)) break;
         mbarArriveExpectTx(kFull + 8 * s, AT_TILE);
-        tmaLoad3d(sK + s * AT_TILE, &mapK, kFull + 8 * s, 0, j * AT_BN, bhkv);
-        tmaLoad3d(sK + s * AT_TILE + AT_HALF, &mapK, kFull + 8 * s, 64, j * AT_BN, bhkv);
+        tmaLoad4d(sK + s * AT_TILE, &mapK, kFull + 8 * s, 0, j * AT_BN, hkv, b);
+        tmaLoad4d(sK + s * AT_TILE + AT_HALF, &mapK, kFull + 8 * s, 64, j * AT_BN, hkv, b);
         if (!mbarWait(vEmpty + 8 * s, ph ^ 1, abortP, 2)) break;
         mbarArriveExpectTx(vFull + 8 * s, AT_TILE);
-        tmaLoad3d(sV + s * AT_TILE, &mapV, vFull + 8 * s, 0, j * AT_BN, bhkv);
-        tmaLoad3d(sV + s * AT_TILE + AT_HALF, &mapV, vFull + 8 * s, 64, j * AT_BN, bhkv);
+        tmaLoad4d(sV + s * AT_TILE, &mapV, vFull + 8 * s, 0, j * AT_BN, hkv, b);
+        tmaLoad4d(sV + s * AT_TILE + AT_HALF, &mapV, vFull + 8 * s, 64, j * AT_BN, hkv, b);
       }
     }
   } else if (warp == 1) {
@@ -278,7 +279,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     if (ok) {
       tcFenceAfter();
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-      T *orow = out + (static_cast<int64_t>(bh) * p.Sq + qrow) * AT_D;
+      T *orow = out + b * p.ob + h * p.oh + qrow * p.os;
 #pragma unroll
       for (int c = 0; c < AT_D / 32; ++c) {
         uint32_t r[32];
@@ -307,17 +308,23 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   }
 }
 
-// [BH, S, 128] 16-bit tensor, box = 64 columns x 128 rows of one head, 128-byte swizzle; rows past
-// the end of a head read as zero.
-static bool makeHeadMap(CUtensorMap *map, const void *ptr, int dtype, int64_t bh, int64_t seq) {
+// [batch, heads, seq, 128] 16-bit tensor addressed through element strides, box = 64 columns x 128
+// rows of one head, 128-byte swizzle; rows past the end of a head read as zero.
+static bool makeHeadMap(CUtensorMap *map, const void *ptr, int dtype, int64_t batch, int64_t heads, int64_t seq,
+                        const int64_t *strides3) {
   EncodeTiledFn fn = encodeTiled();
   if (!fn) return false;
-  cuuint64_t dims[3] = {AT_D, static_cast<cuuint64_t>(seq), static_cast<cuuint64_t>(bh)};
-  cuuint64_t strides[2] = {AT_D * 2, static_cast<cuuint64_t>(seq) * AT_D * 2};
-  cuuint32_t box[3] = {64, AT_BM, 1};
-  cuuint32_t elemStrides[3] = {1, 1, 1};
+  cuuint64_t dims[4] = {AT_D, static_cast<cuuint64_t>(seq), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
+  // A dimension of extent 1 never advances; give it a stride the encoder accepts.
+  auto bytes = [&](int64_t s, cuuint64_t fallback) { return s > 0 ? static_cast<cuuint64_t>(s) * 2 : fallback; };
+  cuuint64_t sSeq = bytes(strides3[2], AT_D * 2);
+  cuuint64_t sHead = bytes(strides3[1], sSeq * static_cast<cuuint64_t>(seq));
+  cuuint64_t sBatch = bytes(strides3[0], sHead * static_cast<cuuint64_t>(heads));
+  cuuint64_t strides[3] = {sSeq, sHead, sBatch};
+  cuuint32_t box[4] = {64, AT_BM, 1, 1};
+  cuuint32_t elemStrides[4] = {1, 1, 1, 1};
   CUtensorMapDataType dt = dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  CUresult r = fn(map, dt, 3, const_cast<void *>(ptr), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  CUresult r = fn(map, dt, 4, const_cast<void *>(ptr), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -341,19 +348,25 @@ static int launchAt(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensor
 // Returns -1 when the problem is outside what this kernel takes (the caller then uses another
 // kernel), otherwise a TTB status.
 int sdpaTcgen05Try(const void *q, const void *k, const void *v, void *out, int dtype, int64_t batch, int64_t hq,
-                   int64_t hkv, int64_t sq, int64_t skv, int64_t headDim, int causal, float scale, cudaStream_t st) {
+                   int64_t hkv, int64_t sq, int64_t skv, int64_t headDim, const int64_t *qs, const int64_t *ks,
+                   const int64_t *vs, const int64_t *os, int causal, float scale, cudaStream_t st) {
   if (headDim != AT_D || (dtype != kBF16 && dtype != kF16)) return -1;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return -1;
   if (sq > 0x7fffff00 || skv > 0x7fffff00) return -1;
+  for (int i = 0; i < 3; ++i) {
+    if (qs[i] < 0 || ks[i] < 0 || vs[i] < 0 || os[i] < 0) return -1;
+    if (qs[i] % 8 || ks[i] % 8 || vs[i] % 8 || os[i] % 8) return -1; // 16-byte units for TMA and the vector stores
+  }
   const int64_t nQ = (sq + AT_BM - 1) / AT_BM;
   const int64_t ctas = nQ * batch * hq;
   if (ctas > 0x7fffffff) return -1;
   CUtensorMap mq, mk, mv;
-  if (!makeHeadMap(&mq, q, dtype, batch * hq, sq) || !makeHeadMap(&mk, k, dtype, batch * hkv, skv) ||
-      !makeHeadMap(&mv, v, dtype, batch * hkv, skv))
+  if (!makeHeadMap(&mq, q, dtype, batch, hq, sq, qs) || !makeHeadMap(&mk, k, dtype, batch, hkv, skv, ks) ||
+      !makeHeadMap(&mv, v, dtype, batch, hkv, skv, vs))
     return -1;
   AtParams p;
   p.Hq = hq; p.Hkv = hkv; p.Sq = sq; p.Skv = skv;
+  p.ob = os[0]; p.oh = os[1]; p.os = os[2];
   p.causal = causal ? 1 : 0;
   p.fmt = dtype == kBF16 ? 1 : 0;
   p.scaleLog2 = scale * 1.4426950408889634f;

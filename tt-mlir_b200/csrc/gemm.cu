@@ -10,21 +10,41 @@ namespace ttb {
 // Returns -1 when the problem is not one the tensor-core kernel takes.
 int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int abDtype, int biasDtype, int cDtype,
                    int64_t batch, int64_t m, int64_t n, int64_t k, int transA, int transB, int64_t aBatchStride,
-                   int64_t bBatchStride, int act, int roundSteps, cudaStream_t stream);
+                   int64_t bBatchStride, int act, int roundSteps, const void *extra, int extraOp, cudaStream_t stream);
 } // namespace ttb
 
-extern "C" int ttb_gemm(const void *a, const void *b, const void *bias, void *c, int ab_dtype, int bias_dtype,
-                        int c_dtype, int64_t batch, int64_t m, int64_t n, int64_t k, int trans_a, int trans_b,
-                        int64_t a_batch_stride, int64_t b_batch_stride, int act, int round_steps, void *stream) {
+static bool tcgen05Disabled() {
   static const bool disabled = [] {
     const char *e = std::getenv("TTB_DISABLE_TCGEN05");
     return e && e[0] && std::strcmp(e, "0") != 0;
   }();
-  if (!disabled) {
+  return disabled;
+}
+
+extern "C" int ttb_gemm(const void *a, const void *b, const void *bias, void *c, int ab_dtype, int bias_dtype,
+                        int c_dtype, int64_t batch, int64_t m, int64_t n, int64_t k, int trans_a, int trans_b,
+                        int64_t a_batch_stride, int64_t b_batch_stride, int act, int round_steps, void *stream) {
+  return ttb_gemm_fused(a, b, bias, c, ab_dtype, bias_dtype, c_dtype, batch, m, n, k, trans_a, trans_b, a_batch_stride,
+                        b_batch_stride, act, round_steps, nullptr, TTB_EXTRA_NONE, stream);
+}
+
+extern "C" int ttb_gemm_fused(const void *a, const void *b, const void *bias, void *c, int ab_dtype, int bias_dtype,
+                              int c_dtype, int64_t batch, int64_t m, int64_t n, int64_t k, int trans_a, int trans_b,
+                              int64_t a_batch_stride, int64_t b_batch_stride, int act, int round_steps,
+                              const void *extra, int extra_op, void *stream) {
+  TTB_CHECK(extra_op == TTB_EXTRA_NONE || extra_op == TTB_EXTRA_ADD || extra_op == TTB_EXTRA_SILU_MUL, "unknown extra_op");
+  TTB_CHECK(extra_op == TTB_EXTRA_NONE || extra != nullptr, "extra_op without its operand");
+  if (!tcgen05Disabled()) {
     int rc = ttb::gemmTcgen05Try(a, b, bias, c, ab_dtype, bias_dtype, c_dtype, batch, m, n, k, trans_a, trans_b,
-                                 a_batch_stride, b_batch_stride, act, round_steps, ttb::asStream(stream));
+                                 a_batch_stride, b_batch_stride, act, round_steps, extra, extra_op, ttb::asStream(stream));
     if (rc != -1) return rc;
   }
-  return ttb_gemm_simt(a, b, bias, c, ab_dtype, bias_dtype, c_dtype, batch, m, n, k, trans_a, trans_b, a_batch_stride,
-                       b_batch_stride, act, round_steps, stream);
+  int rc = ttb_gemm_simt(a, b, bias, c, ab_dtype, bias_dtype, c_dtype, batch, m, n, k, trans_a, trans_b, a_batch_stride,
+                         b_batch_stride, act, round_steps, stream);
+  if (rc || extra_op == TTB_EXTRA_NONE) return rc;
+  // The CUDA-core kernel has no second epilogue operand: apply it in place with the elementwise kernels.
+  const size_t count = static_cast<size_t>(batch * m * n);
+  if (extra_op == TTB_EXTRA_SILU_MUL) return ttb_silu_mul(extra, c, c, c_dtype, count, stream);
+  int64_t shape[1] = {static_cast<int64_t>(count)}, ones[1] = {1};
+  return ttb_eltwise_binary(0 /* EltwiseBinaryOpType::Add */, c, c_dtype, extra, c_dtype, c, c_dtype, 1, shape, ones, ones, stream);
 }

@@ -70,6 +70,8 @@ struct TcParams {
   int biasDt;
   int act;
   int roundSteps;
+  const void *extra; // optional [M, N] operand in the output type, combined after bias / activation
+  int extraOp;       // TTB_EXTRA_*
   int fmt; // 1 bf16, 0 f16
   int debug; // diagnostic: 1 = epilogue loads TMEM but skips math and stores, 2 = epilogue only hands the buffer back
 };
@@ -77,7 +79,8 @@ struct TcParams {
 template <int BN, typename TC, bool PLAIN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     gemmTcgen05Kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                      const __grid_constant__ CUtensorMap mapC, TC *__restrict__ c, TcParams p) {
+                      const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapE,
+                      TC *__restrict__ c, TcParams p) {
   using Cfg = TcCfg<BN>;
   constexpr int STAGES = Cfg::kStages;
   extern __shared__ uint8_t smemRaw[];
@@ -181,9 +184,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     const int quarter = warp & 3; // TMEM lanes this warp may read
     const uint32_t stageOut = outBase + static_cast<uint32_t>(warp - 2) * 2u * 4096u;
     uint32_t accIt = 0, chunkIt = 0;
+    // The extra operand is read row by row (one 128-byte segment per thread and chunk), which
+    // would expose DRAM latency in every chunk.  Its 32-row x CH-column blocks are therefore
+    // pulled into L2 one whole tile ahead: lanes 0 .. BN/CH-1 prefetch one block each.
+    auto prefetchExtra = [&](int64_t t) {
+      if constexpr (!PLAIN && sizeof(TC) == 2) {
+        if (p.extraOp && lane < BN / CH && t < numTiles) {
+          const int64_t col = (t / tilesM) * BN + lane * CH, row = (t % tilesM) * TC_BM + quarter * 32;
+          if (col < p.N && row < p.M) {
+            asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
+                         ::"l"(reinterpret_cast<uint64_t>(&mapE)), "r"(static_cast<int>(col)), "r"(static_cast<int>(row)) : "memory");
+          }
+        }
+      }
+    };
+    prefetchExtra(blockIdx.x);
     for (int64_t tile = blockIdx.x; tile < numTiles; tile += gridDim.x, ++accIt) {
       const int acc = accIt & 1;
       const uint32_t accPhase = (accIt >> 1) & 1u;
+      prefetchExtra(tile + gridDim.x);
       if (!mbarWait(tmemFullBar(acc), accPhase, abortFlag, 4)) break;
       tcFenceAfter();
       const int64_t m0 = (tile % tilesM) * TC_BM, n0 = (tile / tilesM) * BN;
@@ -192,6 +211,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       for (int cc = 0; cc < BN / CH; ++cc) {
         const int64_t col0 = n0 + cc * CH;
         if (col0 >= p.N || p.debug == 2) break; // warp-uniform
+        // The extra operand's 128-byte row segment is fetched first so that it is in flight
+        // while the accumulator is read.
+        uint4 ev[sizeof(TC) == 2 && !PLAIN ? CH / 8 : 1] = {};
+        if constexpr (!PLAIN && sizeof(TC) == 2) {
+          if (p.extraOp && p.debug != 3) {
+            const int64_t row = m0 + quarter * 32 + lane;
+            const TC *erow = static_cast<const TC *>(p.extra) + row * p.N + col0;
+#pragma unroll
+            for (int g = 0; g < CH / 8; ++g) {
+              ev[g] = (row < p.M && col0 + g * 8 < p.N) ? __ldg(reinterpret_cast<const uint4 *>(erow + g * 8))
+                                                       : make_uint4(0, 0, 0, 0);
+            }
+          }
+        }
         uint32_t r[CH];
 #pragma unroll
         for (int l = 0; l < NLD; ++l) {
@@ -240,6 +273,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             for (int e = 0; e < CH; ++e) { float f = __uint_as_float(r[e]); r[e] = __float_as_uint(1.0f / (1.0f + expf(-f))); }
             break;
           default: break;
+          }
+          if constexpr (sizeof(TC) == 2) {
+            // A separate op consumed the (rounded) result of the chain so far.
+            if (p.extraOp == TTB_EXTRA_ADD) {
+#pragma unroll
+              for (int e = 0; e < CH; ++e) {
+                const TC *x = reinterpret_cast<const TC *>(&ev[e / 8]) + (e & 7);
+                r[e] = __float_as_uint(__fadd_rn(toF32(fromF32<TC>(__uint_as_float(r[e]))), toF32(*x)));
+              }
+            } else if (p.extraOp == TTB_EXTRA_SILU_MUL) {
+#pragma unroll
+              for (int e = 0; e < CH; ++e) {
+                const TC *x = reinterpret_cast<const TC *>(&ev[e / 8]) + (e & 7);
+                const float g = toF32(*x);
+                const float sg = toF32(fromF32<TC>(__fdividef(g, 1.0f + __expf(-g))));
+                r[e] = __float_as_uint(__fmul_rn(sg, toF32(fromF32<TC>(__uint_as_float(r[e])))));
+              }
+            }
           }
         }
         const uint32_t buf = stageOut + (chunkIt & 1u) * 4096u;
@@ -338,7 +389,7 @@ static bool makeMap(CUtensorMap *map, const void *ptr, int dtype, int64_t rows, 
 }
 
 template <int BN, typename TC, bool PLAIN>
-static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, void *c, const TcParams &p,
+static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &me, void *c, const TcParams &p,
                     cudaStream_t st) {
   using Cfg = TcCfg<BN>;
   // Function attributes belong to a device: set the shared-memory limit once on each.
@@ -351,7 +402,7 @@ static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensor
   }
   int64_t tiles = ((p.M + TC_BM - 1) / TC_BM) * ((p.N + BN - 1) / BN);
   int grid = static_cast<int>(tiles < smCount() ? tiles : smCount());
-  gemmTcgen05Kernel<BN, TC, PLAIN><<<grid, TC_THREADS, Cfg::kSmem, st>>>(ma, mb, mc, static_cast<TC *>(c), p);
+  gemmTcgen05Kernel<BN, TC, PLAIN><<<grid, TC_THREADS, Cfg::kSmem, st>>>(ma, mb, mc, me, static_cast<TC *>(c), p);
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;
@@ -359,7 +410,7 @@ static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensor
 
 int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int abDtype, int biasDtype, int cDtype,
                    int64_t batch, int64_t m, int64_t n, int64_t k, int transA, int transB, int64_t, int64_t, int act,
-                   int roundSteps, cudaStream_t stream) {
+                   int roundSteps, const void *extra, int extraOp, cudaStream_t stream) {
   // What this kernel takes: one 16-bit A[M,K] and B[N,K] (the "transpose_b" weight layout),
   // rows 16-byte aligned, output in a 16- or 32-bit float type.
   if (batch != 1 || transA || !transB) return -1;
@@ -368,6 +419,7 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   if (k % 8 != 0 || m < 1 || n < 8 || k < 8) return -1;
   if ((n * static_cast<int64_t>(dtypeSize(cDtype))) % 16 != 0) return -1; // row pitch of C for the TMA store
   if (!aligned16(a) || !aligned16(b) || !aligned16(c)) return -1;
+  if (extraOp && (!extra || cDtype == kF32 || !aligned16(extra))) return -1;
   if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff) return -1;
   // Tiny problems are launch-bound either way; keep them on the simple kernel.
   if (m * n * k < (1ll << 18)) return -1;
@@ -387,24 +439,31 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
       }
     }
   }
-  CUtensorMap ma, mb, mc;
+  CUtensorMap ma, mb, mc, me;
   if (!makeMap(&ma, a, abDtype, m, k, TC_BM) || !makeMap(&mb, b, abDtype, n, k, bn) ||
       !makeMap(&mc, c, cDtype, m, n, 32))
     return -1;
+  if (extraOp) {
+    if (!makeMap(&me, extra, cDtype, m, n, 32)) return -1;
+  } else {
+    me = mc; // not used
+  }
   TcParams p;
   p.M = m; p.N = n; p.K = k;
   p.bias = bias; p.biasDt = biasDtype; p.act = act; p.roundSteps = roundSteps;
+  p.extra = extraOp ? extra : nullptr;
+  p.extraOp = extra ? extraOp : 0;
   p.fmt = abDtype == kBF16 ? 1 : 0;
   {
     const char *dbg = std::getenv("TTB_TC_DEBUG");
     p.debug = dbg ? std::atoi(dbg) : 0;
   }
   double flops = 2.0 * double(m) * double(n) * double(k);
-  double bytes = (double(m) * k + double(n) * k) * 2 + double(m) * n * dtypeSize(cDtype);
+  double bytes = (double(m) * k + double(n) * k) * 2 + double(m) * n * dtypeSize(cDtype) * (extraOp ? 2 : 1);
   ProfScope prof("gemm_tcgen05", flops, bytes, stream);
-  const bool plain = !bias && act == TTB_ACT_NONE && roundSteps == 0;
+  const bool plain = !bias && act == TTB_ACT_NONE && roundSteps == 0 && !extraOp;
 #define TTB_TC(BNv, TCv)                                                                 \
-  return plain ? launchTc<BNv, TCv, true>(ma, mb, mc, c, p, stream) : launchTc<BNv, TCv, false>(ma, mb, mc, c, p, stream)
+  return plain ? launchTc<BNv, TCv, true>(ma, mb, mc, me, c, p, stream) : launchTc<BNv, TCv, false>(ma, mb, mc, me, c, p, stream)
 #define TTB_TC_BN(TCv)                                                                   \
   switch (bn) {                                                                          \
   case 256: TTB_TC(256, TCv);                                                            \

@@ -103,20 +103,25 @@ static int launchStrided(const void *in, void *out, int elemSize, int rank, cons
 
 // out = x*cos + rotate_half(x)*sin, rotate_half(x) = concat(-x[D/2:], x[:D/2]).
 // One thread handles 8 elements of the first half and the matching 8 of the second half.
+// x is read as [batch, heads, seq, dim] through element strides (dim contiguous), so a head
+// split that is only a permutation of a [batch, seq, heads, dim] tensor costs no extra pass;
+// out is dense.
 template <typename T>
 __global__ void __launch_bounds__(256) ropeKernel(const T *__restrict__ x, const T *__restrict__ cs,
-                                                  const T *__restrict__ sn, T *__restrict__ out, size_t bh,
-                                                  size_t seq, size_t dim) {
+                                                  const T *__restrict__ sn, T *__restrict__ out, size_t batch,
+                                                  size_t heads, size_t seq, size_t dim, int64_t sb, int64_t sh, int64_t ss) {
   constexpr int V = 16 / sizeof(T);
   size_t half = dim / 2;
   size_t perRow = half / V;
-  size_t total = bh * seq * perRow;
+  size_t total = batch * heads * seq * perRow;
   size_t step = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
     size_t c = (i % perRow) * V;
-    size_t row = i / perRow; // (bh, s)
+    size_t row = i / perRow; // (b, h, s)
     size_t s = row % seq;
-    const T *xr = x + row * dim;
+    size_t bh = row / seq;
+    size_t h = bh % heads, b = bh / heads;
+    const T *xr = x + static_cast<int64_t>(b) * sb + static_cast<int64_t>(h) * sh + static_cast<int64_t>(s) * ss;
     const T *cr = cs + s * dim;
     const T *sr = sn + s * dim;
     Vec16<T> x1 = ldcs16(xr + c), x2 = ldcs16(xr + half + c);
@@ -125,9 +130,9 @@ __global__ void __launch_bounds__(256) ropeKernel(const T *__restrict__ x, const
     Vec16<T> o1, o2;
 #pragma unroll
     for (int j = 0; j < V; ++j) {
-      float a = toF32(x1.v[j]), b = toF32(x2.v[j]);
-      o1.v[j] = fromF32<T>(__fadd_rn(__fmul_rn(a, toF32(c1.v[j])), __fmul_rn(-b, toF32(s1.v[j]))));
-      o2.v[j] = fromF32<T>(__fadd_rn(__fmul_rn(b, toF32(c2.v[j])), __fmul_rn(a, toF32(s2.v[j]))));
+      float a = toF32(x1.v[j]), b2 = toF32(x2.v[j]);
+      o1.v[j] = fromF32<T>(__fadd_rn(__fmul_rn(a, toF32(c1.v[j])), __fmul_rn(-b2, toF32(s1.v[j]))));
+      o2.v[j] = fromF32<T>(__fadd_rn(__fmul_rn(b2, toF32(c2.v[j])), __fmul_rn(a, toF32(s2.v[j]))));
     }
     stcs16(out + row * dim + c, o1);
     stcs16(out + row * dim + half + c, o2);
@@ -152,18 +157,28 @@ int ttb_strided_scatter(const void *in, void *out, int elem_size, int rank, cons
 
 int ttb_rotary_embedding(const void *x, const void *cos, const void *sin, void *out, int dtype, size_t batch_heads,
                          size_t seq, size_t head_dim, void *stream) {
-  TTB_CHECK(x && cos && sin && out, "null tensor");
+  int64_t strides[3] = {static_cast<int64_t>(batch_heads * seq * head_dim), static_cast<int64_t>(seq * head_dim),
+                        static_cast<int64_t>(head_dim)};
+  return ttb_rotary_embedding_strided(x, cos, sin, out, dtype, 1, batch_heads, seq, head_dim, strides, stream);
+}
+
+int ttb_rotary_embedding_strided(const void *x, const void *cos, const void *sin, void *out, int dtype, size_t batch,
+                                 size_t heads, size_t seq, size_t head_dim, const int64_t *x_strides3, void *stream) {
+  TTB_CHECK(x && cos && sin && out && x_strides3, "null tensor");
   TTB_CHECK(aligned16(x) && aligned16(cos) && aligned16(sin) && aligned16(out), "tensors must be 16-byte aligned");
   size_t es = dtypeSize(dtype);
   TTB_CHECK(es == 2 || es == 4, "rotary embedding needs a float dtype");
   TTB_CHECK(head_dim % (2 * (16 / es)) == 0, "head_dim/2 must be a multiple of 16 bytes");
-  size_t total = batch_heads * seq * (head_dim / 2 / (16 / es));
+  for (int i = 0; i < 3; ++i) {
+    TTB_CHECK(x_strides3[i] >= 0 && (x_strides3[i] * es) % 16 == 0, "input strides must be multiples of 16 bytes");
+  }
+  size_t total = batch * heads * seq * (head_dim / 2 / (16 / es));
   if (total == 0) return TTB_OK;
-  ProfScope prof("rotary_embedding", 0, 2.0 * double(batch_heads) * seq * head_dim * es, asStream(stream));
+  ProfScope prof("rotary_embedding", 0, 2.0 * double(batch * heads) * seq * head_dim * es, asStream(stream));
   TTB_DISPATCH_FLOAT(dtype, T, {
     ropeKernel<T><<<gridFor(total, 256), 256, 0, asStream(stream)>>>(
-        static_cast<const T *>(x), static_cast<const T *>(cos), static_cast<const T *>(sin), static_cast<T *>(out),
-        batch_heads, seq, head_dim);
+        static_cast<const T *>(x), static_cast<const T *>(cos), static_cast<const T *>(sin), static_cast<T *>(out), batch,
+        heads, seq, head_dim, x_strides3[0], x_strides3[1], x_strides3[2]);
   });
   countLaunch();
   TTB_LAUNCH_CHECK();

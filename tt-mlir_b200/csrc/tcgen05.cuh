@@ -61,6 +61,11 @@ __device__ __forceinline__ void tmaLoad3d(uint32_t dst, const CUtensorMap *map, 
                ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 
+__device__ __forceinline__ void tmaLoad4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
 // Shared-memory matrix descriptor for a tile stored with the 128-byte swizzle (descriptor
 // version 1, layout type 2).  K-major operand: rows of 128 bytes along K, `sbo` = distance
 // between 8-row groups, `lbo` unused.  MN-major operand: rows of 128 bytes along M/N (64

@@ -33,6 +33,7 @@ using ::tt::target::TensorLayout;
 // ---- static facts about a program, computed once per (binary, program) -----------------------
 struct ProgramInfo {
   std::unordered_map<uint32_t, uint32_t> useCount; // consumers other than DeallocateOp
+  std::unordered_map<uint32_t, uint32_t> firstUse; // index of the first such consumer
   std::unordered_set<uint32_t> outputs;
 };
 
@@ -215,12 +216,17 @@ static ProgramInfo programInfo(const fbt::Program *prog) {
   }
   if (prog->operations()) {
     std::vector<const fbt::TensorRef *> ins, outs;
+    uint32_t index = 0;
     for (const auto *op : *prog->operations()) {
+      uint32_t at = index++;
       if (op->type_type() == OpType::DeallocateOp) continue;
       ins.clear();
       outs.clear();
       collectOpRefs(op, ins, outs);
-      for (const auto *r : ins) info.useCount[r->global_id()]++;
+      for (const auto *r : ins) {
+        info.useCount[r->global_id()]++;
+        info.firstUse.emplace(r->global_id(), at);
+      }
     }
   }
   return info;
@@ -301,6 +307,17 @@ private:
   const fbt::Program *prog = nullptr;
   ProgramInfo info;
   bool fuse = true;
+  // A head split ([B,S,H,D] -> [B,H,S,D] permute) whose only consumer reads through strides
+  // (rotary embedding, attention) is not materialised: the consumer gets the source tensor and
+  // the permuted strides.  Any other access (get) performs the copy after all.
+  struct LazyView {
+    TensorPtr base;
+    std::vector<uint32_t> shape;
+    std::vector<int64_t> strides; // in elements, over `shape`
+  };
+  std::unordered_map<uint32_t, LazyView> lazy;
+  // Dense strides of a live tensor, or the pending view of `ref`, as {tensor, strides}.
+  std::pair<TensorPtr, std::vector<int64_t>> viewOf(const fbt::TensorRef *ref);
 
   TensorPtr get(const fbt::TensorRef *ref);
   TensorPtr getDevice(const fbt::TensorRef *ref); // uploads a host tensor if an op needs it on device
@@ -318,6 +335,7 @@ private:
   size_t tryQuantChain(size_t i);
   size_t tryGemmEpilogue(size_t i);
   size_t trySiluMul(size_t i);
+  size_t trySdpa(size_t i);
   size_t tryAddRmsNorm(size_t i);
 
   void runGetDevice(const fbt::GetDeviceOp *op);
@@ -338,7 +356,7 @@ private:
   void runWhere(const fbt::EltwiseTernaryWhereOp *op);
   void runQuantization(const fbt::EltwiseQuantizationOp *op);
   void runGemm(const fbt::TensorRef *a, const fbt::TensorRef *b, const fbt::TensorRef *bias, const fbt::TensorRef *out,
-               bool ta, bool tb, int act, int roundSteps);
+               bool ta, bool tb, int act, int roundSteps, const fbt::TensorRef *extra = nullptr, int extraOp = 0);
   void runConv2d(const fbt::Conv2dOp *op);
   void runSoftmax(const fbt::SoftmaxOp *op);
   void runRmsNorm(const fbt::RMSNormOp *op);
@@ -430,10 +448,24 @@ template <typename F> void Executor::eachRank(F &&f) {
 
 TensorPtr Executor::get(const fbt::TensorRef *ref) {
   TTRT_ASSERT(ref != nullptr, "missing tensor operand");
+  auto lz = lazy.find(ref->global_id());
+  if (lz != lazy.end()) {
+    LazyView v = std::move(lz->second);
+    lazy.erase(lz);
+    pool[ref->global_id()] = stridedView(v.base, v.shape, v.strides, 0, v.base->dtype);
+  }
   auto it = pool.find(ref->global_id());
   TTRT_ASSERT(it != pool.end(), "tensor ", ref->global_id(), " is not live (used before definition or after deallocation)");
   TTRT_ASSERT(it->second->allocated(), "tensor ", ref->global_id(), " has been deallocated");
   return it->second;
+}
+
+std::pair<TensorPtr, std::vector<int64_t>> Executor::viewOf(const fbt::TensorRef *ref) {
+  TTRT_ASSERT(ref != nullptr, "missing tensor operand");
+  auto lz = lazy.find(ref->global_id());
+  if (lz != lazy.end()) return {lz->second.base, lz->second.strides};
+  TensorPtr t = getDevice(ref);
+  return {t, denseStrides(t->shape)};
 }
 
 TensorPtr Executor::getDevice(const fbt::TensorRef *ref) {
@@ -475,7 +507,7 @@ void Executor::runDeallocs(const std::vector<const fbt::Operation *> &ops) {
   for (const auto *op : ops) {
     const auto *d = op->type_as_DeallocateOp();
     // Inside a fused chain an intermediate may never have been materialised.
-    if (d->in() && pool.count(d->in()->global_id())) runDeallocate(d);
+    if (d->in() && (pool.count(d->in()->global_id()) || lazy.count(d->in()->global_id()))) runDeallocate(d);
   }
 }
 
@@ -537,6 +569,7 @@ size_t Executor::runOp(size_t i) {
     case OpType::LinearOp: used = tryGemmEpilogue(i); break;
     case OpType::EltwiseUnaryOp: used = trySiluMul(i); break;
     case OpType::EltwiseBinaryOp: used = tryAddRmsNorm(i); break;
+    case OpType::ScaledDotProductAttentionOp: used = trySdpa(i); break;
     default: break;
     }
     if (used) return used;
@@ -694,6 +727,7 @@ void Executor::runTypecast(const fbt::TypecastOp *op) {
 
 void Executor::runDeallocate(const fbt::DeallocateOp *op) {
   TTRT_ASSERT(op->in() != nullptr, "DeallocateOp without operand");
+  lazy.erase(op->in()->global_id());
   auto it = pool.find(op->in()->global_id());
   if (it == pool.end()) {
     return;
@@ -1038,9 +1072,11 @@ size_t Executor::tryQuantChain(size_t i) {
 
 // ---- contractions -------------------------------------------------------------------------------------
 void Executor::runGemm(const fbt::TensorRef *aRef, const fbt::TensorRef *bRef, const fbt::TensorRef *biasRef,
-                       const fbt::TensorRef *outRef, bool ta, bool tb, int act, int roundSteps) {
+                       const fbt::TensorRef *outRef, bool ta, bool tb, int act, int roundSteps,
+                       const fbt::TensorRef *extraRef, int extraOp) {
   TensorPtr a = getDevice(aRef), b = getDevice(bRef);
   TensorPtr bias = biasRef ? getDevice(biasRef) : nullptr;
+  TensorPtr extra = extraRef ? getDevice(extraRef) : nullptr;
   TensorPtr out = allocOut(outRef);
   TTRT_ASSERT(a->dtype == b->dtype, "matmul operands differ in data type: ", dataTypeName(a->dtype), " vs ",
               dataTypeName(b->dtype));
@@ -1070,10 +1106,14 @@ void Executor::runGemm(const fbt::TensorRef *aRef, const fbt::TensorRef *bRef, c
   if (bias) {
     TTRT_ASSERT(static_cast<int64_t>(bias->volume()) == N, "bias must have N = ", N, " elements, has ", bias->volume());
   }
+  if (extra) {
+    TTRT_ASSERT(extra->volume() == out->volume() && extra->dtype == out->dtype, "fused epilogue operand must match the result");
+  }
   eachRank([&](size_t i, const RankCtx &r) {
-    TTB_CALL(ttb_gemm(a->shards[i]->ptr, b->shards[i]->ptr, bias ? bias->shards[i]->ptr : nullptr, out->shards[i]->ptr,
-                      ttbDtype(a->dtype), bias ? ttbDtype(bias->dtype) : 0, ttbDtype(out->dtype), batch, M, N, K, ta, tb,
-                      aStride, bStride, act, roundSteps, r.stream));
+    TTB_CALL(ttb_gemm_fused(a->shards[i]->ptr, b->shards[i]->ptr, bias ? bias->shards[i]->ptr : nullptr, out->shards[i]->ptr,
+                            ttbDtype(a->dtype), bias ? ttbDtype(bias->dtype) : 0, ttbDtype(out->dtype), batch, M, N, K, ta,
+                            tb, aStride, bStride, act, roundSteps, extra ? extra->shards[i]->ptr : nullptr,
+                            extra ? extraOp : TTB_EXTRA_NONE, r.stream));
   });
   put(outRef, out);
 }
@@ -1088,7 +1128,8 @@ static int unaryToAct(fbt::EltwiseUnaryOpType t) {
   }
 }
 
-// matmul|linear [-> add(row vector)] [-> relu|silu|gelu|sigmoid], each intermediate single-use.
+// matmul|linear [-> add(row vector)] [-> relu|silu|gelu|sigmoid] [-> add(tensor) | silu(other) * result],
+// each intermediate single-use.
 size_t Executor::tryGemmEpilogue(size_t i) {
   const auto *ops = prog->operations();
   const auto *op = ops->Get(static_cast<uint32_t>(i));
@@ -1157,8 +1198,58 @@ size_t Executor::tryGemmEpilogue(size_t i) {
       }
     }
   }
+  // optional full-size second operand: a residual add, or SwiGLU gating silu(g) * result
+  const fbt::TensorRef *extra = nullptr;
+  int extraOp = TTB_EXTRA_NONE;
+  auto liveSameAsCur = [&](const fbt::TensorRef *t) {
+    return t && t->global_id() != cur->global_id() && refShape(t) == refShape(cur) && refDtype(t) == outDt &&
+           pool.count(t->global_id()) != 0;
+  };
+  if (singleUse(cur) && (outDt == DataType::BFloat16 || outDt == DataType::Float16)) {
+    std::vector<const fbt::Operation *> d2;
+    size_t j = next;
+    const auto *nop = peek(j, d2);
+    if (nop && nop->type_type() == OpType::EltwiseBinaryOp) {
+      const auto *add = nop->type_as_EltwiseBinaryOp();
+      const fbt::TensorRef *other = nullptr;
+      if (add->type() == fbt::EltwiseBinaryOpType::Add) {
+        if (add->lhs()->global_id() == cur->global_id()) other = add->rhs();
+        else if (add->rhs()->global_id() == cur->global_id()) other = add->lhs();
+      }
+      if (liveSameAsCur(other) && refShape(add->out()) == refShape(cur) && refDtype(add->out()) == outDt) {
+        extra = other;
+        extraOp = TTB_EXTRA_ADD;
+        cur = add->out();
+        deallocs.insert(deallocs.end(), d2.begin(), d2.end());
+        next = j + 1;
+        consumedUpTo = j;
+      }
+    } else if (nop && nop->type_type() == OpType::EltwiseUnaryOp) {
+      const auto *u = nop->type_as_EltwiseUnaryOp();
+      std::vector<const fbt::Operation *> d3;
+      size_t j2 = j + 1;
+      const auto *mop = peek(j2, d3);
+      if (u->type() == fbt::EltwiseUnaryOpType::Silu && liveSameAsCur(u->in()) && singleUse(u->out()) &&
+          refShape(u->out()) == refShape(cur) && refDtype(u->out()) == outDt && mop &&
+          mop->type_type() == OpType::EltwiseBinaryOp) {
+        const auto *mul = mop->type_as_EltwiseBinaryOp();
+        uint32_t l = mul->lhs()->global_id(), r = mul->rhs()->global_id();
+        uint32_t sId = u->out()->global_id(), cId = cur->global_id();
+        if (mul->type() == fbt::EltwiseBinaryOpType::Multiply && ((l == sId && r == cId) || (l == cId && r == sId)) &&
+            refShape(mul->out()) == refShape(cur) && refDtype(mul->out()) == outDt) {
+          extra = u->in();
+          extraOp = TTB_EXTRA_SILU_MUL;
+          cur = mul->out();
+          deallocs.insert(deallocs.end(), d2.begin(), d2.end());
+          deallocs.insert(deallocs.end(), d3.begin(), d3.end());
+          next = j2 + 1;
+          consumedUpTo = j2;
+        }
+      }
+    }
+  }
   if (consumedUpTo == i) return 0;
-  runGemm(a, b, bias, cur, ta, tb, act, roundSteps);
+  runGemm(a, b, bias, cur, ta, tb, act, roundSteps, extra, extraOp);
   runDeallocs(deallocs);
   return consumedUpTo + 1 - i;
 }
@@ -1376,6 +1467,23 @@ void Executor::runPermute(const fbt::TensorRef *inRef, const std::vector<int> &p
     strides[k] = dense[p];
   }
   TTRT_ASSERT(outShape == refShape(outRef), "permute result shape differs from the op's result type");
+  if (fuse && rank == 4 && strides[3] == 1 && singleUse(outRef)) {
+    auto use = info.firstUse.find(outRef->global_id());
+    if (use != info.firstUse.end()) {
+      const auto *consumer = prog->operations()->Get(use->second);
+      bool strided = false;
+      if (consumer->type_type() == OpType::RotaryEmbeddingOp) {
+        strided = consumer->type_as_RotaryEmbeddingOp()->input()->global_id() == outRef->global_id();
+      } else if (consumer->type_type() == OpType::ScaledDotProductAttentionOp) {
+        const auto *a = consumer->type_as_ScaledDotProductAttentionOp();
+        strided = !a->attention_mask() && !a->attention_sink();
+      }
+      if (strided) {
+        lazy[outRef->global_id()] = LazyView{in, outShape, strides};
+        return;
+      }
+    }
+  }
   put(outRef, stridedView(in, outShape, strides, 0, in->dtype));
 }
 
@@ -1515,19 +1623,94 @@ void Executor::runSplitQkv(const fbt::SplitQueryKeyValueAndSplitHeadsOp *op) {
 }
 
 void Executor::runRotaryEmbedding(const fbt::RotaryEmbeddingOp *op) {
-  TensorPtr x = getDevice(op->input()), c = getDevice(op->cos_cache()), s = getDevice(op->sin_cache());
+  TensorPtr c = getDevice(op->cos_cache()), s = getDevice(op->sin_cache());
+  std::vector<uint32_t> xs = refShape(op->input());
+  TTRT_ASSERT(xs.size() >= 2, "rotary_embedding expects [..., seq, head_dim]");
+  size_t rank = xs.size();
+  size_t D = xs[rank - 1], S = xs[rank - 2];
+  // A pending head split is read through its strides when they are vector-aligned.
+  TensorPtr x;
+  size_t B = 1, H = 0;
+  int64_t strides[3];
+  auto lz = lazy.find(op->input()->global_id());
+  if (lz != lazy.end() && rank == 4 && lz->second.strides[3] == 1) {
+    size_t unit = 16 / dataTypeSize(lz->second.base->dtype);
+    const auto &st = lz->second.strides;
+    if (st[0] % unit == 0 && st[1] % unit == 0 && st[2] % unit == 0) {
+      x = lz->second.base;
+      B = xs[0];
+      H = xs[1];
+      strides[0] = st[0]; strides[1] = st[1]; strides[2] = st[2];
+    }
+  }
+  if (!x) {
+    x = getDevice(op->input());
+    H = x->volume() / std::max<size_t>(S * D, 1);
+    strides[0] = static_cast<int64_t>(H * S * D); strides[1] = static_cast<int64_t>(S * D); strides[2] = static_cast<int64_t>(D);
+  }
   TensorPtr out = allocOut(op->out());
-  TTRT_ASSERT(x->shape.size() >= 2, "rotary_embedding expects [..., seq, head_dim]");
-  size_t rank = x->shape.size();
-  size_t D = x->shape[rank - 1], S = x->shape[rank - 2], BH = x->volume() / std::max<size_t>(S * D, 1);
   TTRT_ASSERT(!op->token_index().has_value(), "rotary_embedding with token_index (decode) is not supported");
   TTRT_ASSERT(c->volume() == S * D && s->volume() == S * D, "cos/sin caches must be [seq, head_dim] = [", S, ", ", D, "]");
   TTRT_ASSERT(c->dtype == x->dtype && s->dtype == x->dtype && out->dtype == x->dtype, "rotary_embedding tensors must share one data type");
   eachRank([&](size_t i, const RankCtx &r) {
-    TTB_CALL(ttb_rotary_embedding(x->shards[i]->ptr, c->shards[i]->ptr, s->shards[i]->ptr, out->shards[i]->ptr,
-                                  ttbDtype(x->dtype), BH, S, D, r.stream));
+    TTB_CALL(ttb_rotary_embedding_strided(x->shards[i]->ptr, c->shards[i]->ptr, s->shards[i]->ptr, out->shards[i]->ptr,
+                                          ttbDtype(x->dtype), B, H, S, D, strides, r.stream));
   });
   put(op->out(), out);
+}
+
+// Attention with its operands read through strides (pending head splits) and, when the next op
+// is concatenate_heads on its result, the output written straight in [batch, seq, heads*dim].
+size_t Executor::trySdpa(size_t i) {
+  const auto *ops = prog->operations();
+  const auto *op = ops->Get(static_cast<uint32_t>(i))->type_as_ScaledDotProductAttentionOp();
+  if (op->attention_mask() || op->attention_sink() || op->sliding_window_size().has_value()) return 0;
+  std::vector<uint32_t> qs = refShape(op->query()), ks = refShape(op->key()), vs = refShape(op->value());
+  DataType dt = refDtype(op->query());
+  if (qs.size() != 4 || ks.size() != 4 || vs != ks || qs[3] != 128 || ks[3] != 128 || qs[0] != ks[0] || ks[1] == 0 ||
+      qs[1] % ks[1] != 0 || (dt != DataType::BFloat16 && dt != DataType::Float16) || refDtype(op->key()) != dt ||
+      refDtype(op->value()) != dt || refDtype(op->out()) != dt || refShape(op->out()) != qs)
+    return 0;
+  int64_t B = qs[0], Hq = qs[1], Sq = qs[2], D = qs[3], Hkv = ks[1], Skv = ks[2];
+  // next op: concatenate_heads of the (single-use) result?
+  std::vector<const fbt::Operation *> deallocs;
+  size_t j = i + 1;
+  const auto *nop = peek(j, deallocs);
+  const fbt::ConcatenateHeadsOp *merge = nullptr;
+  if (nop && nop->type_type() == OpType::ConcatenateHeadsOp && singleUse(op->out())) {
+    const auto *m = nop->type_as_ConcatenateHeadsOp();
+    std::vector<uint32_t> want = {qs[0], qs[2], qs[1] * qs[3]};
+    if (m->in()->global_id() == op->out()->global_id() && refShape(m->out()) == want && refDtype(m->out()) == dt) merge = m;
+  }
+  bool anyLazy = lazy.count(op->query()->global_id()) || lazy.count(op->key()->global_id()) || lazy.count(op->value()->global_id());
+  if (!merge && !anyLazy) return 0;
+  auto q = viewOf(op->query()), k = viewOf(op->key()), v = viewOf(op->value());
+  for (const auto *pv : {&q, &k, &v}) {
+    for (int d = 0; d < 3; ++d) {
+      if (pv->second[d] % 8 != 0) return 0; // get() will materialise in the plain path
+    }
+    if (pv->second[3] != 1) return 0;
+  }
+  const fbt::TensorRef *outRef = merge ? merge->out() : op->out();
+  TensorPtr out = allocOut(outRef);
+  int64_t os[3];
+  if (merge) { os[0] = Sq * Hq * D; os[1] = D; os[2] = Hq * D; }
+  else { os[0] = Hq * Sq * D; os[1] = Sq * D; os[2] = D; }
+  float scale = op->scale().value_or(1.0f / std::sqrt(static_cast<float>(D)));
+  bool unsupported = false;
+  eachRank([&](size_t r, const RankCtx &rc) {
+    if (unsupported) return;
+    int st = ttb_sdpa_strided(q.first->shards[r]->ptr, k.first->shards[r]->ptr, v.first->shards[r]->ptr, out->shards[r]->ptr,
+                              ttbDtype(dt), B, Hq, Hkv, Sq, Skv, D, q.second.data(), k.second.data(), v.second.data(), os,
+                              op->is_causal() ? 1 : 0, scale, rc.stream);
+    if (st == TTB_ERR_UNSUPPORTED && r == 0) unsupported = true;
+    else TTB_CALL(st);
+  });
+  if (unsupported) return 0; // nothing was launched; the plain path copies the views and runs dense
+  put(outRef, out);
+  if (!merge) return 1;
+  runDeallocs(deallocs);
+  return j + 1 - i;
 }
 
 void Executor::runSdpa(const fbt::ScaledDotProductAttentionOp *op) {

@@ -66,6 +66,8 @@ TTB_API int ttb_malloc(void **ptr, size_t bytes, void *stream);
 TTB_API int ttb_free(void *ptr, void *stream);
 TTB_API int ttb_host_alloc_pinned(void **ptr, size_t bytes);
 TTB_API int ttb_host_free_pinned(void *ptr);
+/* *pinned = 1 when `ptr` is page-locked host memory (a copy from it is a true asynchronous DMA). */
+TTB_API int ttb_host_is_pinned(const void *ptr, int *pinned);
 TTB_API int ttb_memcpy_h2d(void *dst, const void *host_src, size_t bytes, void *stream);
 TTB_API int ttb_memcpy_d2h(void *host_dst, const void *src, size_t bytes, void *stream);
 TTB_API int ttb_memcpy_d2d(void *dst, const void *src, size_t bytes, void *stream);

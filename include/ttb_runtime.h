@@ -102,6 +102,9 @@ TTRT_API int ttrt_to_host(ttrt_tensor_t t, int untilize, int blocking, ttrt_tens
 TTRT_API int ttrt_memcpy_to_ptr(void *dst, ttrt_tensor_t src, int target_dtype);
 TTRT_API int ttrt_memcpy_tensor(ttrt_tensor_t dst, ttrt_tensor_t src);            /* memcpy(Tensor, Tensor) */
 TTRT_API int ttrt_wait_tensor(ttrt_tensor_t t);                                   /* wait(Tensor) */
+/* Address of a host tensor's data (Tensor::data of runtime/include/tt/runtime/types.h): a view, valid
+ * while the tensor lives.  After a non-blocking toHost, call ttrt_wait_tensor before reading. */
+TTRT_API int ttrt_tensor_host_ptr(ttrt_tensor_t t, void **ptr);
 
 /* ---- execution (runtime.h:299-301) ----------------------------------------------------------- */
 /* submit(device, binary, programIndex, inputs) -> outputs */

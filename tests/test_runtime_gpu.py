@@ -129,3 +129,55 @@ def test_launch_counter_moves(rt, device):
     before = rt.launch_count()
     run_program(rt, device, buf, graphs.quant_chain_inputs(64, 64))
     assert rt.launch_count() > before
+
+
+def test_pipelined_steps_with_pinned_buffers(rt, device):
+    """Uploads from page-locked memory and non-blocking downloads run on their own streams.
+    A pipelined loop (upload i+1 and download i-1 around compute i) must give exactly what
+    the blocking calls give, step by step, with a different input every step."""
+    import ctypes
+    buf = graphs.build_binary(graphs.mlp_graph)
+    binary = rt.Binary.load_from_memory(buf)
+    ins = graphs.mlp_inputs()
+    weights = [rt.to_layout(rt.from_torch(t), device, rt.get_layout(binary, 0, i), retain=True)
+               for i, t in enumerate(ins)][1:]
+    layout = rt.get_layout(binary, 0, 0)
+    steps = 6
+    xs = [(ins[0] + 0.25 * k).clone().pin_memory() for k in range(steps)]
+    # blocking reference results
+    want = []
+    for x in xs:
+        d = rt.to_layout(rt.from_torch(x.clone()), device, layout)   # pageable copy: blocking upload
+        out = rt.submit(device, binary, 0, [d] + weights)[0]
+        want.append(rt.to_torch(rt.to_host(out, untilize=True)[0]))
+    # pipelined
+    got, pending = [], None
+
+    def read(h, like):
+        rt.wait(h)
+        n = like.numel() * like.element_size()
+        raw = (ctypes.c_char * n).from_address(h.host_ptr())
+        return torch.frombuffer(raw, dtype=like.dtype).reshape(like.shape).clone()
+
+    for x in xs:
+        d = rt.to_layout(rt.from_torch(x), device, layout)
+        out = rt.submit(device, binary, 0, [d] + weights)[0]
+        h = rt.to_host(out, untilize=True, blocking=False)[0]
+        if pending is not None:
+            got.append(read(pending, want[len(got)]))
+        pending = h
+    got.append(read(pending, want[len(got)]))
+    for k in range(steps):
+        assert torch.equal(got[k], want[k]), f"step {k} differs"
+    assert not torch.equal(got[0], got[1])
+
+
+def test_wait_on_blocking_host_tensor_is_harmless(rt, device):
+    buf = graphs.build_binary(graphs.quant_chain_graph, rows=32, cols=32)
+    binary = rt.Binary.load_from_memory(buf)
+    x = torch.randn(32, 32).pin_memory()
+    d = rt.to_layout(rt.from_torch(x), device, rt.get_layout(binary, 0, 0))
+    h = rt.to_host(d, untilize=True)[0]
+    rt.wait(h)
+    rt.wait(d)
+    assert torch.equal(rt.to_torch(h), x.to(torch.bfloat16))

@@ -197,6 +197,20 @@ int ttb_host_alloc_pinned(void **ptr, size_t bytes) {
   return TTB_OK;
 }
 
+int ttb_host_is_pinned(const void *ptr, int *pinned) {
+  TTB_CHECK(pinned != nullptr, "pinned is null");
+  *pinned = 0;
+  if (!ptr) return TTB_OK;
+  cudaPointerAttributes attr;
+  cudaError_t e = cudaPointerGetAttributes(&attr, ptr);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError(); // plain malloc memory on older drivers reports an error: not pinned
+    return TTB_OK;
+  }
+  *pinned = attr.type == cudaMemoryTypeHost ? 1 : 0;
+  return TTB_OK;
+}
+
 int ttb_host_free_pinned(void *ptr) {
   if (ptr) {
     TTB_CUDA(cudaFreeHost(ptr));

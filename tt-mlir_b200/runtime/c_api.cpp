@@ -392,6 +392,17 @@ int ttrt_memcpy_tensor(ttrt_tensor_t dst, ttrt_tensor_t src) {
   TTRT_CATCH
 }
 
+int ttrt_tensor_host_ptr(ttrt_tensor_t t, void **ptr) {
+  TTRT_ARG(t && ptr)
+  TTRT_TRY
+  auto impl = tt::runtime::cuda::unwrapTensor(T(t));
+  if (impl->storage != tt::runtime::cuda::Storage::Host || impl->shards.empty() || !impl->shards[0]) {
+    throw std::runtime_error("tensor_host_ptr needs a host tensor with data");
+  }
+  *ptr = impl->shards[0]->ptr;
+  TTRT_CATCH
+}
+
 int ttrt_wait_tensor(ttrt_tensor_t t) {
   TTRT_ARG(t)
   TTRT_TRY

@@ -419,6 +419,7 @@ Executor::Executor(std::shared_ptr<DeviceImpl> d, Binary &b, uint32_t pi, std::v
     }
     TTRT_ASSERT(t->dtype == refDtype(ref), "input ", i, " has data type ", dataTypeName(t->dtype), ", program expects ",
                 dataTypeName(refDtype(ref)));
+    orderAfterUploads(t); // an upload still in flight on the copy stream: the compute stream waits for it
     if (t->shape != want) {
       // same volume, different view (for example a flattened activation)
       auto view = std::make_shared<TensorImpl>();

@@ -60,11 +60,36 @@ inline int ttbDtype(DataType dt) { return static_cast<int>(dt); }
 struct RankCtx {
   int cudaDevice = 0;
   uint32_t meshRank = 0;
-  void *stream = nullptr;
+  void *stream = nullptr;   // compute: every kernel of every program, in submission order
+  void *copyIn = nullptr;   // host -> device copies from pinned memory (overlap the previous step's compute)
+  void *copyOut = nullptr;  // non-blocking device -> host copies (overlap the next step's compute)
   void *comm = nullptr;
 };
 
+// A CUDA event owned by whoever holds the last reference.
+struct EventHolder {
+  void *event = nullptr;
+  int cudaDevice = 0;
+  EventHolder(int device);
+  ~EventHolder();
+  EventHolder(const EventHolder &) = delete;
+  EventHolder &operator=(const EventHolder &) = delete;
+};
+using EventPtr = std::shared_ptr<EventHolder>;
+
+// Upload staging memory that went out of use, kept per device for the next upload of the same
+// size: `lastUse` (recorded on the compute stream when the block was released) gates its reuse
+// on the upload stream.  Keeps the stream-ordered allocator, whose cross-stream reuse would make
+// the upload wait for the compute stream, out of a pipelined loop.
+struct StagingBlock {
+  void *ptr = nullptr;
+  size_t bytes = 0;
+  EventPtr lastUse;
+};
+
 struct DeviceImpl {
+  std::vector<std::vector<StagingBlock>> stagingCache; // per entry of `locals`
+  std::mutex stagingMutex;
   std::vector<uint32_t> meshShape{1, 1};
   uint32_t worldSize = 1;          // mesh volume
   std::vector<RankCtx> locals;     // coordinates this process owns
@@ -82,8 +107,14 @@ struct Buffer {
   int cudaDevice = -1;   // -1: host memory
   void *stream = nullptr; // stream that orders the free of device memory
   std::shared_ptr<struct DeviceImpl> owner; // keeps the stream's device alive; closed device -> plain free
-  enum class Kind { Borrowed, HostMalloc, HostPinned, Device } kind = Kind::Borrowed;
+  enum class Kind { Borrowed, HostMalloc, HostPinned, HostPinnedPooled, Device, DeviceStaging } kind = Kind::Borrowed;
+  size_t localIndex = 0; // DeviceStaging: which entry of owner->locals the block belongs to
   std::shared_ptr<void> keepAlive; // another object owning the memory (views)
+  // Work on a copy stream that the compute stream does not know about yet:
+  //  device buffer: its contents are complete once `ready` fires (an upload in flight), and
+  //                 `pendingRead` is a download still reading it (the free waits for it);
+  //  host buffer:   `ready` is the download that fills it (wait(tensor) blocks on it).
+  EventPtr ready, pendingRead;
   ~Buffer();
 };
 using BufferPtr = std::shared_ptr<Buffer>;
@@ -132,7 +163,9 @@ struct LayoutImpl {
 
 std::vector<int64_t> denseStrides(const std::vector<uint32_t> &shape);
 
-TensorPtr makeHostTensor(const std::vector<uint32_t> &shape, DataType dt, size_t nshards);
+TensorPtr makeHostTensor(const std::vector<uint32_t> &shape, DataType dt, size_t nshards, bool pinned = false);
+// Makes the compute stream wait for uploads of `t` that are still in flight on the copy stream.
+void orderAfterUploads(const TensorPtr &t);
 TensorPtr makeDeviceTensor(const std::shared_ptr<DeviceImpl> &dev, const std::vector<uint32_t> &shape, DataType dt);
 Tensor wrapTensor(const TensorPtr &t);
 TensorPtr unwrapTensor(const Tensor &t);

@@ -106,6 +106,55 @@ std::vector<int64_t> denseStrides(const std::vector<uint32_t> &shape) {
   return s;
 }
 
+EventHolder::EventHolder(int device) : cudaDevice(device) {
+  TTB_CALL(ttb_set_device(device));
+  TTB_CALL(ttb_event_create(&event));
+}
+EventHolder::~EventHolder() {
+  if (event) ttb_event_destroy(event);
+}
+
+// Page-locked staging buffers for non-blocking downloads are recycled: pinning memory costs
+// milliseconds, a step of a pipelined loop needs one buffer of the same size every time.
+namespace {
+struct PinnedPool {
+  std::mutex mu;
+  std::unordered_map<size_t, std::vector<void *>> free;
+  size_t cachedBytes = 0;
+  static constexpr size_t kMaxCached = size_t(2) << 30;
+  static PinnedPool &get() {
+    static PinnedPool *p = new PinnedPool(); // never destroyed: buffers may outlive static teardown
+    return *p;
+  }
+  void *take(size_t bytes) {
+    {
+      std::lock_guard<std::mutex> g(mu);
+      auto it = free.find(bytes);
+      if (it != free.end() && !it->second.empty()) {
+        void *p = it->second.back();
+        it->second.pop_back();
+        cachedBytes -= bytes;
+        return p;
+      }
+    }
+    void *p = nullptr;
+    TTB_CALL(ttb_host_alloc_pinned(&p, bytes));
+    return p;
+  }
+  void give(void *p, size_t bytes) {
+    {
+      std::lock_guard<std::mutex> g(mu);
+      if (cachedBytes + bytes <= kMaxCached) {
+        free[bytes].push_back(p);
+        cachedBytes += bytes;
+        return;
+      }
+    }
+    ttb_host_free_pinned(p);
+  }
+};
+} // namespace
+
 Buffer::~Buffer() {
   if (!ptr) {
     return;
@@ -113,12 +162,45 @@ Buffer::~Buffer() {
   switch (kind) {
   case Kind::HostMalloc: std::free(ptr); break;
   case Kind::HostPinned: ttb_host_free_pinned(ptr); break;
-  case Kind::Device:
+  case Kind::HostPinnedPooled:
+    // A download that still writes this buffer must land before the memory is handed out again.
+    if (ready) ttb_event_sync(ready->event);
+    PinnedPool::get().give(ptr, bytes);
+    break;
+  case Kind::Device: {
     // Stream-ordered free: safe while kernels using the block are still queued on `stream`.
     // After the device was closed its stream is gone: free on the default stream instead.
     ttb_set_device(cudaDevice);
-    ttb_free(ptr, (owner && owner->open) ? stream : nullptr);
+    void *st = (owner && owner->open) ? stream : nullptr;
+    // Copies on the copy streams are not in `stream`'s order: the free waits for them.
+    if (ready) ttb_stream_wait_event(st, ready->event);
+    if (pendingRead) ttb_stream_wait_event(st, pendingRead->event);
+    ttb_free(ptr, st);
     break;
+  }
+  case Kind::DeviceStaging: {
+    ttb_set_device(cudaDevice);
+    if (owner && owner->open) {
+      // Back to the device's cache; the next upload into it waits for the work queued so far.
+      void *st = stream;
+      if (ready) ttb_stream_wait_event(st, ready->event);
+      if (pendingRead) ttb_stream_wait_event(st, pendingRead->event);
+      StagingBlock blk;
+      blk.ptr = ptr;
+      blk.bytes = bytes;
+      blk.lastUse = std::make_shared<EventHolder>(cudaDevice);
+      ttb_event_record(blk.lastUse->event, st);
+      std::lock_guard<std::mutex> g(owner->stagingMutex);
+      if (localIndex < owner->stagingCache.size() && owner->stagingCache[localIndex].size() < 8) {
+        owner->stagingCache[localIndex].push_back(std::move(blk));
+        break;
+      }
+      ttb_free(ptr, st);
+    } else {
+      ttb_free(ptr, nullptr);
+    }
+    break;
+  }
   case Kind::Borrowed: break;
   }
 }
@@ -138,21 +220,32 @@ void DeviceImpl::close() {
   open = false;
   for (RankCtx &r : locals) {
     ttb_set_device(r.cudaDevice);
-    if (r.stream) {
-      ttb_stream_sync(r.stream);
+    for (void *st : {r.copyIn, r.copyOut, r.stream}) {
+      if (st) ttb_stream_sync(st);
+    }
+    {
+      std::lock_guard<std::mutex> g(stagingMutex);
+      size_t idx = static_cast<size_t>(&r - locals.data());
+      if (idx < stagingCache.size()) {
+        for (StagingBlock &b : stagingCache[idx]) ttb_free(b.ptr, r.stream);
+        stagingCache[idx].clear();
+      }
+      if (r.stream) ttb_stream_sync(r.stream);
     }
     if (r.comm) {
       ttb_comm_destroy(r.comm);
       r.comm = nullptr;
     }
-    if (r.stream) {
-      ttb_stream_destroy(r.stream);
-      r.stream = nullptr;
+    for (void **st : {&r.copyIn, &r.copyOut, &r.stream}) {
+      if (*st) {
+        ttb_stream_destroy(*st);
+        *st = nullptr;
+      }
     }
   }
 }
 
-TensorPtr makeHostTensor(const std::vector<uint32_t> &shape, DataType dt, size_t nshards) {
+TensorPtr makeHostTensor(const std::vector<uint32_t> &shape, DataType dt, size_t nshards, bool pinned) {
   auto t = std::make_shared<TensorImpl>();
   t->shape = shape;
   t->stride = denseStrides(shape);
@@ -162,6 +255,13 @@ TensorPtr makeHostTensor(const std::vector<uint32_t> &shape, DataType dt, size_t
   for (size_t i = 0; i < nshards; ++i) {
     auto b = std::make_shared<Buffer>();
     b->bytes = bytes;
+    if (pinned) {
+      b->ptr = PinnedPool::get().take(bytes ? bytes : 16);
+      b->bytes = bytes ? bytes : 16;
+      b->kind = Buffer::Kind::HostPinnedPooled;
+      t->shards.push_back(b);
+      continue;
+    }
     b->ptr = std::aligned_alloc(64, (bytes + 63) / 64 * 64 + 64);
     b->kind = Buffer::Kind::HostMalloc;
     if (!b->ptr) {
@@ -207,6 +307,7 @@ TensorPtr castOnDevice(const TensorPtr &t, DataType dt) {
   if (t->dtype == dt) {
     return t;
   }
+  orderAfterUploads(t);
   auto out = makeDeviceTensor(t->device, t->shape, dt);
   out->layout = t->layout;
   for (size_t i = 0; i < t->shards.size(); ++i) {
@@ -225,11 +326,66 @@ TensorPtr toDevice(const TensorPtr &host, const std::shared_ptr<DeviceImpl> &dev
   TTRT_ASSERT(host->allocated(), "host tensor has no data");
   TTRT_ASSERT(host->shards.size() == 1 || host->shards.size() == dev->worldSize,
               "host tensor has ", host->shards.size(), " shards, mesh has ", dev->worldSize, " devices");
+  // Page-locked sources are copied on the upload stream without stopping the host: the copy
+  // overlaps whatever the compute stream is doing, and the tensor carries an event that the
+  // first consumer on the compute stream waits for.  The caller keeps the source unchanged until
+  // then (as with any asynchronous copy).  Pageable sources are copied before this returns.
+  bool pinned = true;
+  for (const RankCtx &r : dev->locals) {
+    const BufferPtr &src = host->shards.size() == 1 ? host->shards[0] : host->shards[r.meshRank];
+    TTRT_ASSERT(src && src->ptr, "host tensor has no shard for mesh coordinate ", r.meshRank);
+    int isPinned = 0;
+    TTB_CALL(ttb_host_is_pinned(src->ptr, &isPinned));
+    pinned = pinned && isPinned != 0;
+  }
+  if (pinned) {
+    auto staged = std::make_shared<TensorImpl>();
+    staged->shape = host->shape;
+    staged->stride = denseStrides(host->shape);
+    staged->dtype = host->dtype;
+    staged->storage = Storage::Device;
+    staged->layout = TensorLayout::Tile;
+    staged->device = dev;
+    size_t bytes = staged->bytes();
+    for (const RankCtx &r : dev->locals) {
+      const BufferPtr &src = host->shards.size() == 1 ? host->shards[0] : host->shards[r.meshRank];
+      auto b = std::make_shared<Buffer>();
+      TTB_CALL(ttb_set_device(r.cudaDevice));
+      size_t li = static_cast<size_t>(&r - dev->locals.data());
+      {
+        std::lock_guard<std::mutex> g(dev->stagingMutex);
+        auto &cache = dev->stagingCache[li];
+        for (size_t c = 0; c < cache.size(); ++c) {
+          if (cache[c].bytes == bytes) {
+            // Oldest matching block first: its last use is the most likely to be over.
+            StagingBlock blk = std::move(cache[c]);
+            cache.erase(cache.begin() + static_cast<long>(c));
+            TTB_CALL(ttb_stream_wait_event(r.copyIn, blk.lastUse->event));
+            b->ptr = blk.ptr;
+            break;
+          }
+        }
+      }
+      // A new block is allocated in the upload stream's order, so that the copy does not wait for compute.
+      if (!b->ptr) TTB_CALL(ttb_malloc(&b->ptr, bytes, r.copyIn));
+      b->bytes = bytes;
+      b->cudaDevice = r.cudaDevice;
+      b->stream = r.stream; // released in compute order, after its consumers
+      b->owner = dev;
+      b->localIndex = li;
+      b->kind = Buffer::Kind::DeviceStaging;
+      TTB_CALL(ttb_memcpy_h2d(b->ptr, src->ptr, bytes, r.copyIn));
+      b->ready = std::make_shared<EventHolder>(r.cudaDevice);
+      TTB_CALL(ttb_event_record(b->ready->event, r.copyIn));
+      b->keepAlive = src; // the source stays alive while the copy may still read it
+      staged->shards.push_back(b);
+    }
+    return castOnDevice(staged, dt);
+  }
   auto staged = makeDeviceTensor(dev, host->shape, host->dtype);
   for (size_t i = 0; i < dev->locals.size(); ++i) {
     const RankCtx &r = dev->locals[i];
     const BufferPtr &src = host->shards.size() == 1 ? host->shards[0] : host->shards[r.meshRank];
-    TTRT_ASSERT(src && src->ptr, "host tensor has no shard for mesh coordinate ", r.meshRank);
     TTB_CALL(ttb_set_device(r.cudaDevice));
     TTB_CALL(ttb_memcpy_h2d(staged->shards[i]->ptr, src->ptr, host->bytes(), r.stream));
   }
@@ -241,23 +397,56 @@ TensorPtr toDevice(const TensorPtr &host, const std::shared_ptr<DeviceImpl> &dev
   return castOnDevice(staged, dt);
 }
 
+void orderAfterUploads(const TensorPtr &t) {
+  if (!t || t->storage != Storage::Device || !t->device) return;
+  for (size_t i = 0; i < t->shards.size() && i < t->device->locals.size(); ++i) {
+    const BufferPtr &b = t->shards[i];
+    if (b && b->ready) {
+      const RankCtx &r = t->device->locals[i];
+      TTB_CALL(ttb_set_device(r.cudaDevice));
+      TTB_CALL(ttb_stream_wait_event(r.stream, b->ready->event));
+      b->ready.reset(); // from here on the compute stream's order covers the upload
+      b->keepAlive.reset();
+    }
+  }
+}
+
 TensorPtr toHostTensor(const TensorPtr &d, bool blocking) {
   TTRT_ASSERT(d->storage == Storage::Device, "toHost expects a device tensor");
   TTRT_ASSERT(d->allocated(), "device tensor was deallocated");
-  auto h = makeHostTensor(d->shape, d->dtype, d->shards.size());
-  h->layout = TensorLayout::RowMajor;
-  for (size_t i = 0; i < d->shards.size(); ++i) {
-    const RankCtx &r = d->device->locals[i];
-    TTB_CALL(ttb_set_device(r.cudaDevice));
-    TTB_CALL(ttb_memcpy_d2h(h->shards[i]->ptr, d->shards[i]->ptr, d->bytes(), r.stream));
-  }
+  orderAfterUploads(d);
   if (blocking) {
+    auto h = makeHostTensor(d->shape, d->dtype, d->shards.size());
+    h->layout = TensorLayout::RowMajor;
+    for (size_t i = 0; i < d->shards.size(); ++i) {
+      const RankCtx &r = d->device->locals[i];
+      TTB_CALL(ttb_set_device(r.cudaDevice));
+      TTB_CALL(ttb_memcpy_d2h(h->shards[i]->ptr, d->shards[i]->ptr, d->bytes(), r.stream));
+    }
     for (const RankCtx &r : d->device->locals) {
       TTB_CALL(ttb_set_device(r.cudaDevice));
       TTB_CALL(ttb_stream_sync(r.stream));
     }
-  } else {
-    h->device = d->device; // wait() needs the streams
+    return h;
+  }
+  // Non-blocking: the download stream waits for the work enqueued so far on the compute stream,
+  // then copies into page-locked memory while later submissions run.  wait(tensor) blocks on
+  // the copy alone.
+  auto h = makeHostTensor(d->shape, d->dtype, d->shards.size(), /*pinned=*/true);
+  h->layout = TensorLayout::RowMajor;
+  h->device = d->device;
+  for (size_t i = 0; i < d->shards.size(); ++i) {
+    const RankCtx &r = d->device->locals[i];
+    TTB_CALL(ttb_set_device(r.cudaDevice));
+    EventHolder produced(r.cudaDevice);
+    TTB_CALL(ttb_event_record(produced.event, r.stream));
+    TTB_CALL(ttb_stream_wait_event(r.copyOut, produced.event));
+    TTB_CALL(ttb_memcpy_d2h(h->shards[i]->ptr, d->shards[i]->ptr, d->bytes(), r.copyOut));
+    auto done = std::make_shared<EventHolder>(r.cudaDevice);
+    TTB_CALL(ttb_event_record(done->event, r.copyOut));
+    h->shards[i]->ready = done;
+    h->shards[i]->keepAlive = d->shards[i]; // the source outlives the copy
+    d->shards[i]->pendingRead = done;       // and is not reused before the copy has read it
   }
   return h;
 }
@@ -345,7 +534,10 @@ Device openMeshDevice(const MeshDeviceOptions &options) {
   for (RankCtx &r : dev->locals) {
     TTB_CALL(ttb_set_device(r.cudaDevice));
     TTB_CALL(ttb_stream_create(&r.stream));
+    TTB_CALL(ttb_stream_create(&r.copyIn));
+    TTB_CALL(ttb_stream_create(&r.copyOut));
   }
+  dev->stagingCache.resize(dev->locals.size());
   if (world > 1) {
     if (dev->multiProcess) {
       RankCtx &r = dev->locals[0];
@@ -590,12 +782,30 @@ static void syncDevice(const std::shared_ptr<DeviceImpl> &d) {
   }
   for (const RankCtx &r : d->locals) {
     TTB_CALL(ttb_set_device(r.cudaDevice));
-    TTB_CALL(ttb_stream_sync(r.stream));
+    for (void *st : {r.copyIn, r.stream, r.copyOut}) {
+      if (st) TTB_CALL(ttb_stream_sync(st));
+    }
   }
 }
 
 void wait(Event) { TTRT_FATAL("wait(Event) is not supported; wait on tensors (as in the reference TTNN target)"); }
-void wait(Tensor tensor, std::optional<uint8_t>) { syncDevice(unwrapTensor(tensor)->device); }
+void wait(Tensor tensor, std::optional<uint8_t>) {
+  auto t = unwrapTensor(tensor);
+  if (t->storage == Storage::Host) {
+    // The result of a non-blocking toHost: wait for its copy only.
+    bool pending = false;
+    for (const BufferPtr &b : t->shards) {
+      if (b && b->ready) {
+        TTB_CALL(ttb_event_sync(b->ready->event));
+        b->ready.reset();
+        b->keepAlive.reset();
+        pending = true;
+      }
+    }
+    if (pending || !t->device) return;
+  }
+  syncDevice(t->device);
+}
 void wait(const std::vector<Tensor> &tensors, std::optional<uint8_t> cqId) {
   for (const Tensor &t : tensors) wait(t, cqId);
 }
@@ -779,6 +989,7 @@ void memcpy(void *dst, Tensor src, std::optional<DataType> targetDataType) {
   TTRT_ASSERT(t->allocated(), "tensor has no data");
   if (t->storage == Storage::Device && (!targetDataType || *targetDataType == t->dtype)) {
     // straight into the caller's buffer (a true DMA when that buffer is pinned)
+    orderAfterUploads(t);
     const RankCtx &r = t->device->locals[0];
     TTB_CALL(ttb_set_device(r.cudaDevice));
     TTB_CALL(ttb_memcpy_d2h(dst, t->shards[0]->ptr, t->bytes(), r.stream));
@@ -801,6 +1012,8 @@ void memcpy(Tensor dst, Tensor src) {
   TTRT_ASSERT(d->allocated() && s->allocated(), "tensor has no data");
   TTRT_ASSERT(d->volume() == s->volume() && d->dtype == s->dtype, "memcpy needs equal size and data type");
   TTRT_ASSERT(d->shards.size() == s->shards.size(), "memcpy needs equal shard counts");
+  orderAfterUploads(d);
+  orderAfterUploads(s);
   for (size_t i = 0; i < d->shards.size(); ++i) {
     void *dp = d->shards[i]->ptr;
     const void *sp = s->shards[i]->ptr;

@@ -315,6 +315,13 @@ class Tensor:
     def get_num_shards(self) -> int:
         return self._info()[3]
 
+    def host_ptr(self) -> int:
+        """Address of a host tensor's data (no copy).  After to_host(..., blocking=False) call
+        wait() first."""
+        p = ctypes.c_void_p()
+        _check(lib.ttrt_tensor_host_ptr(_vp(self._h), ctypes.byref(p)))
+        return p.value
+
     def is_allocated(self) -> bool:
         return self._info()[4]
 

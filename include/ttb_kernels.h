@@ -317,6 +317,36 @@ TTB_API int ttb_reduce_scatter(void *comm, const void *in, void *out, size_t rec
 TTB_API int ttb_broadcast(void *comm, const void *in, void *out, size_t count, int dtype, int root,
                           void *stream);
 
+/* ---- all-reduce over peer memory (NVLink loads/stores, no NCCL in the data path).
+ * A "symm" object is one rank's view of a set of workspaces, one per rank of a 1xN mesh, each
+ * mapped by every other rank: CUDA IPC when ranks are processes (create_rank: collective, the
+ * NCCL communicator only carries the 64-byte handles), peer access when one process drives all
+ * devices (create_all).  `max_bytes` bounds the operand of one all-reduce; a workspace takes
+ * 4 x max_bytes + 32 KiB.
+ * ttb_symm_all_reduce: out = sum over ranks of in (f32 accumulation in rank order, so every rank
+ * gets the same bits), or with `residual` (replicated, same shape) out = round(round(sum) +
+ * residual), which is ::ttnn::all_reduce followed by ::ttnn::add.  Collective: every rank calls
+ * it in the same order with the same count.  Returns TTB_ERR_UNSUPPORTED for operands it does
+ * not take (type other than bf16/f16/f32, more than max_bytes, not 16-byte multiples).
+ * Waits on peers are bounded; ttb_symm_status reports a wait that ran out ((phase << 8) | peer + 1).
+ * Replaces, for sums, ::ttnn::all_reduce (runtime/lib/ttnn/operations/ccl/all_reduce.cpp:36-37). */
+TTB_API int ttb_symm_create_rank(void **symm, void *comm, int rank, int nranks, size_t max_bytes,
+                                 void *stream);
+TTB_API int ttb_symm_create_all(void **symms, int ndev, const int *devices, size_t max_bytes);
+TTB_API int ttb_symm_destroy(void *symm);
+TTB_API size_t ttb_symm_max_bytes(void *symm);
+/* Where the NEXT ttb_symm_all_reduce of this rank stages its operand.  A producer (the GEMM
+ * before the all-reduce) that writes its result there and passes the same pointer as `in` saves
+ * the all-reduce its staging copy.  The memory is only valid as that operand: it is reused two
+ * all-reduces later. */
+TTB_API int ttb_symm_input_buffer(void *symm, size_t bytes, void **ptr);
+TTB_API int ttb_symm_status(void *symm, int *status);
+/* Diagnostic (TTB_SYMM_STAMPS=1 at creation): nanosecond timer of block 0 at the six phase
+ * boundaries of the last all-reduce (start, staged, barrier, reduced, barrier, gathered). */
+TTB_API int ttb_symm_stamps(void *symm, unsigned long long *stamps8);
+TTB_API int ttb_symm_all_reduce(void *symm, const void *in, const void *residual, void *out,
+                                size_t count, int dtype, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,6 +1,17 @@
 """Mesh programs (ttir.mesh_shard + collectives) on a 1xN device mesh driven by one process, as the
 reference's runtime drives a mesh.  Needs at least two GPUs; skipped otherwise."""
 
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+from __graft_entry__ import load_package  # noqa: E402  (spawned workers import this module without conftest)
+
+load_package()
+
 import pytest
 import torch
 
@@ -100,3 +111,84 @@ def test_presharded_multi_device_tensors(rt, mesh2):
     want = torch.relu(a[0]) + torch.relu(a[1])
     for s in shards:
         assert torch.allclose(rt.to_torch(s), want, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_all_reduce_sizes_in_a_row_and_fused_residual(rt, mesh2, dtype):
+    """The peer-memory all-reduce keeps a launch counter and alternates its staging regions; launches
+    of different sizes back to back (different grids, different block-to-element maps) and an
+    all_reduce followed by a residual add must all equal the oracle.  Both shards end up with the
+    same bits."""
+    torch.manual_seed(11)
+    sizes = [(2, 8), (64, 1000), (2048, 1024), (8, 8), (512, 4096)]
+    xs = [torch.randn(2 * r, c).to(dtype) for r, c in sizes]
+    res = [torch.randn(r, c).to(dtype) for r, c in sizes]
+
+    def body(b, *vals):
+        outs = []
+        k = len(sizes)
+        for x, r in zip(vals[:k], vals[k:]):
+            s = b.distribute(x, 0)
+            rr = b.distribute(r, None)
+            plain = b.all_reduce(s)
+            fused = b.add(rr, b.all_reduce(b.relu(s)))
+            outs += [b.aggregate(plain, 0), b.aggregate(fused, 0)]
+        return outs
+    got, want = run_mesh(rt, mesh2, body, xs + res)
+    for i, (g, w) in enumerate(zip(got, want)):
+        assert_matches(g, w, f"all_reduce case {i}")
+        half = g.shape[0] // 2
+        assert torch.equal(g[:half], g[half:]), "the two devices disagree"
+
+
+def _tp_worker(rank, world, port, ret):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import ttmlir_b200.runtime_api as rt
+        ids = [rt.get_nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        dev = rt.open_mesh_device(rt.MeshDeviceOptions(mesh_shape=[1, world], device_ids=[rank], process_rank=rank,
+                                                       process_count=world, nccl_unique_id=ids[0]))
+        kw = dict(seq=256, hidden=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024)
+        ins = graphs.decoder_block_inputs(**kw)
+        mine = graphs.shard_inputs(ins, graphs.decoder_shard_dims(**kw), world, rank)
+        buf = graphs.build_binary(graphs.decoder_block_graph, mesh_shape=(1, world), tp=world, presharded=True, **kw)
+        binary = rt.Binary.load_from_memory(buf)
+        rt.set_compatible_device_runtime(binary)
+        dev_in = [rt.to_layout(rt.from_torch(t), dev, rt.get_layout(binary, 0, i)) for i, t in enumerate(mine)]
+        outs = []
+        for _ in range(3):   # several programs in a row: the all-reduce's launch counter advances
+            out = rt.submit(dev, binary, 0, dev_in)[0]
+            outs.append(rt.to_torch(rt.to_host(out, untilize=True)[0]))
+        want = oracle_results(graphs.decoder_block_graph, ins, mesh_shape=(1, world), tp=world, **kw)[0]
+        from oracle import metrics
+        ok, report = metrics.check_close(want, outs[0], 0.999, 2e-2, 2.0 ** -6)
+        same = all(torch.equal(outs[0], o) for o in outs[1:])
+        ret[rank] = (bool(ok), bool(same), report, outs[0].float().sum().item())
+        rt.close_mesh_device(dev)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_one_process_per_gpu_tensor_parallel(rt):
+    """One process per GPU (what torch.distributed.run does): the ranks exchange the NCCL id over
+    gloo, open the 1x2 mesh by rank, and run the tensor-parallel decoder block.  The all-reduces go
+    over IPC-mapped peer memory; both ranks must get the oracle's result, bit-identical to each
+    other and from run to run."""
+    if rt.get_num_available_devices() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    port = 29600 + (os.getpid() % 2000)
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_tp_worker, args=(world, port, ret), nprocs=world, join=True)
+        r = dict(ret)
+    assert set(r) == {0, 1}
+    for rank in (0, 1):
+        assert r[rank][0], f"rank {rank}: {r[rank][2]}"
+        assert r[rank][1], f"rank {rank}: results differ between runs"
+    assert r[0][3] == r[1][3]

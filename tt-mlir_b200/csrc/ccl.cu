@@ -8,7 +8,10 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <cstdlib>
 #include <mutex>
+#include <string>
+#include <vector>
 
 namespace ttb {
 
@@ -107,6 +110,241 @@ static bool ncclOp(int reduceType, ncclRedOp_t &out) {
   default: return false;
   }
 }
+
+
+// ---- all-reduce over peer memory ------------------------------------------------------------
+// Every rank of a 1xN mesh owns a workspace that all other ranks map (CUDA IPC between
+// processes, peer access inside one process).  One kernel per rank does the whole all-reduce:
+//   A  copy the local operand into the own workspace (skipped when the producer already wrote
+//      it there, see ttb_symm_input_buffer); peers can now read it
+//   B  reduce slice `rank`: read that slice from every rank over NVLink, sum in f32 in rank
+//      order (the same bits on every rank), optionally add a residual; the result goes to the
+//      local output and is pushed into every peer's workspace
+//   C  copy the slices the peers pushed from the own workspace to the local output
+// with a flag barrier between A/B and B/C.  Remote traffic per rank is (n-1)/n of the operand
+// in each direction, loads and stores in the same loop, so both directions of the links work at
+// once.  Work is split so that block b touches the same elements in every phase on every rank;
+// a barrier is then per block (block b waits for block b of the peers), which needs no
+// grid-wide synchronisation.  Flags carry a launch counter and the data and result regions
+// alternate between two copies per launch, so nothing is ever reset.
+// Waits are bounded: when a peer does not show up within about a second the kernel records it
+// in the status word and carries on (the result of that launch is then invalid).
+constexpr int SYMM_MAX_RANKS = 8;
+constexpr int SYMM_MAX_BLOCKS = 512;
+constexpr int SYMM_THREADS = 512;
+constexpr size_t SYMM_FLAG_BYTES = 2 * SYMM_MAX_BLOCKS * SYMM_MAX_RANKS * sizeof(uint32_t);
+
+struct SymmParams {
+  int rank, n;
+  char *ws[SYMM_MAX_RANKS]; // every rank's workspace as mapped on this device; ws[rank] is local
+  size_t dataOff, resultOff; // this launch's regions inside a workspace
+  uint32_t token;            // first barrier waits for token, second for token + 1
+  int oneShot;               // every rank reduces the whole operand itself: no push, no second barrier
+  int *status;
+  unsigned long long *stamps; // diagnostic: globaltimer of block 0 at the phase boundaries, or null
+};
+
+__device__ __forceinline__ void symmStoreFlag(uint32_t *p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t symmLoadFlag(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Block-level barrier across ranks: block b of every rank has finished the phase before it.
+// The poll is a relaxed load (hundreds of blocks spin at once); one fence after it orders the
+// reads that follow.
+__device__ __forceinline__ void symmBarrier(const SymmParams &p, int which, uint32_t token) {
+  __syncthreads();
+  const int t = threadIdx.x;
+  if (t < p.n && t != p.rank) {
+    const size_t slot = (static_cast<size_t>(which) * SYMM_MAX_BLOCKS + blockIdx.x) * SYMM_MAX_RANKS;
+    symmStoreFlag(reinterpret_cast<uint32_t *>(p.ws[t]) + slot + p.rank, token); // release: orders the block's writes
+    const uint32_t *mine = reinterpret_cast<const uint32_t *>(p.ws[p.rank]) + slot + t;
+    const long long start = clock64();
+    uint32_t spins = 0;
+    while (static_cast<int32_t>(symmLoadFlag(mine) - token) < 0) {
+      if ((++spins & 255u) == 0 && clock64() - start > 2000000000ll) {
+        atomicCAS(p.status, 0, ((which + 1) << 8) | (t + 1));
+        break;
+      }
+    }
+    __threadfence_system();
+  }
+  __syncthreads();
+}
+
+template <typename T> struct SymmVec { static constexpr int N = 16 / sizeof(T); };
+
+// NR: compile-time bound on the rank count (2, 4 or 8), which sizes the registers that hold the
+// loads in flight.
+template <typename T, bool RESIDUAL, bool STAGED, int NR>
+__global__ void __launch_bounds__(SYMM_THREADS)
+    symmAllReduceKernel(SymmParams p, const uint4 *__restrict__ in, const uint4 *__restrict__ residual,
+                        uint4 *__restrict__ out, size_t nvec) {
+  constexpr int V = SymmVec<T>::N;
+  constexpr int U = NR == 8 ? 2 : 4;
+  const size_t per = (nvec + p.n - 1) / p.n; // vectors per slice
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  const size_t first = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+
+  auto stamp = [&](int k) {
+    if (p.stamps && blockIdx.x == 0 && threadIdx.x == 0) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+      p.stamps[k] = t;
+    }
+  };
+  stamp(0);
+  // A: publish the local operand (already in place when the producer wrote into the workspace).
+  if (!STAGED) {
+    uint4 *myData = reinterpret_cast<uint4 *>(p.ws[p.rank] + p.dataOff);
+    if (p.oneShot) {
+      // the peers read everything, with the element-to-block map of the reduce loop below
+      for (size_t i = first; i < nvec; i += stride) myData[i] = __ldcs(in + i);
+    } else {
+      for (int s = 0; s < p.n; ++s) {
+        if (s == p.rank) continue; // the own slice is read from `in`
+        const size_t lo = s * per, hi = lo + per < nvec ? lo + per : nvec;
+        for (size_t i = lo + first; i < hi; i += stride) myData[i] = __ldcs(in + i);
+      }
+    }
+  }
+  stamp(1);
+  symmBarrier(p, 0, p.token);
+  stamp(2);
+
+  // B: reduce the own slice, U vectors per thread and iteration with every load issued before
+  // the first use, so that a thread has U * n remote loads in flight.
+  // One-shot mode (two ranks, or operands so small that latency dominates): the same loop over
+  // the whole operand, nothing pushed, and the launch ends here.
+  {
+    const size_t lo = p.oneShot ? 0 : p.rank * per;
+    const size_t hi = p.oneShot ? nvec : (lo + per < nvec ? lo + per : nvec);
+    const bool push = !p.oneShot;
+    for (size_t i0 = lo + first; i0 < hi; i0 += stride * U) {
+      uint4 v[U][NR];
+      uint4 rv[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t i = i0 + u * stride;
+        if (i < hi) {
+#pragma unroll
+          for (int r = 0; r < NR; ++r) {
+            if (r < p.n) {
+              v[u][r] = (r == p.rank && !STAGED) ? __ldcs(in + i)
+                                                 : __ldcg(reinterpret_cast<const uint4 *>(p.ws[r] + p.dataOff) + i);
+            }
+          }
+          if (RESIDUAL) rv[u] = __ldcs(residual + i);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t i = i0 + u * stride;
+        if (i < hi) {
+          float acc[V];
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[j] = 0.0f;
+#pragma unroll
+          for (int r = 0; r < NR; ++r) {
+            if (r < p.n) {
+              const T *e = reinterpret_cast<const T *>(&v[u][r]);
+#pragma unroll
+              for (int j = 0; j < V; ++j) acc[j] = __fadd_rn(acc[j], toF32(e[j]));
+            }
+          }
+          uint4 o;
+          T *oe = reinterpret_cast<T *>(&o);
+          if (RESIDUAL) {
+            const T *re = reinterpret_cast<const T *>(&rv[u]);
+#pragma unroll
+            for (int j = 0; j < V; ++j) oe[j] = fromF32<T>(__fadd_rn(toF32(fromF32<T>(acc[j])), toF32(re[j])));
+          } else {
+#pragma unroll
+            for (int j = 0; j < V; ++j) oe[j] = fromF32<T>(acc[j]);
+          }
+          out[i] = o;
+#pragma unroll
+          for (int r = 0; r < NR; ++r) {
+            if (push && r < p.n && r != p.rank) reinterpret_cast<uint4 *>(p.ws[r] + p.resultOff)[i] = o;
+          }
+        }
+      }
+    }
+  }
+  stamp(3);
+  if (p.oneShot) return;
+  symmBarrier(p, 1, p.token + 1);
+  stamp(4);
+
+  // C: the slices the peers pushed.
+  {
+    const uint4 *mine = reinterpret_cast<const uint4 *>(p.ws[p.rank] + p.resultOff);
+    for (int s = 0; s < p.n; ++s) {
+      if (s == p.rank) continue;
+      const size_t lo = s * per, hi = lo + per < nvec ? lo + per : nvec;
+      for (size_t i = lo + first; i < hi; i += stride) out[i] = __ldcg(mine + i);
+    }
+  }
+  stamp(5);
+}
+
+template <typename T, bool RESIDUAL, bool STAGED, int NR>
+static int symmLaunch(const SymmParams &p, const void *in, const void *residual, void *out, size_t nvec, cudaStream_t st) {
+  // All blocks of all ranks have to be resident at the same time (they wait for each other).
+  static int perSm[64] = {};
+  int dev = 0;
+  TTB_CUDA(cudaGetDevice(&dev));
+  TTB_CHECK(dev >= 0 && dev < 64, "device ordinal out of range");
+  if (!perSm[dev]) {
+    int n = 0;
+    TTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, symmAllReduceKernel<T, RESIDUAL, STAGED, NR>, SYMM_THREADS, 0));
+    TTB_CHECK(n >= 1, "all-reduce kernel does not fit on an SM");
+    perSm[dev] = n > 2 ? 2 : n;
+  }
+  const size_t work = p.oneShot ? nvec : (nvec + p.n - 1) / p.n;
+  size_t blocks = (work + SYMM_THREADS - 1) / SYMM_THREADS;
+  size_t cap = static_cast<size_t>(smCount()) * perSm[dev];
+  if (cap > SYMM_MAX_BLOCKS) cap = SYMM_MAX_BLOCKS;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  symmAllReduceKernel<T, RESIDUAL, STAGED, NR><<<static_cast<unsigned>(blocks), SYMM_THREADS, 0, st>>>(
+      p, static_cast<const uint4 *>(in), static_cast<const uint4 *>(residual), static_cast<uint4 *>(out), nvec);
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+template <typename T>
+static int symmDispatch(const SymmParams &p, const void *in, const void *residual, void *out, size_t nvec, bool staged,
+                        cudaStream_t st) {
+#define TTB_SYMM_NR(NRv)                                                                              \
+  if (residual) {                                                                                     \
+    return staged ? symmLaunch<T, true, true, NRv>(p, in, residual, out, nvec, st)                    \
+                  : symmLaunch<T, true, false, NRv>(p, in, residual, out, nvec, st);                  \
+  }                                                                                                   \
+  return staged ? symmLaunch<T, false, true, NRv>(p, in, residual, out, nvec, st)                     \
+                : symmLaunch<T, false, false, NRv>(p, in, residual, out, nvec, st);
+  if (p.n <= 2) { TTB_SYMM_NR(2) }
+  if (p.n <= 4) { TTB_SYMM_NR(4) }
+  TTB_SYMM_NR(8)
+#undef TTB_SYMM_NR
+}
+
+struct Symm {
+  int rank = 0, n = 1, device = 0;
+  bool ipc = false;
+  char *ws[SYMM_MAX_RANKS] = {};
+  size_t maxBytes = 0; // largest operand
+  uint32_t launches = 0;
+  int *status = nullptr;
+  unsigned long long *stamps = nullptr; // 8 slots after the status word when TTB_SYMM_STAMPS=1
+};
+
+static size_t symmTotalBytes(size_t maxBytes) { return SYMM_FLAG_BYTES + 4 * maxBytes; }
 
 } // namespace ttb
 
@@ -213,6 +451,184 @@ int ttb_broadcast(void *comm, const void *in, void *out, size_t count, int dtype
   TTB_NCCL(api.broadcast(in, out, count, dt, root, static_cast<ncclComm_t>(comm), asStream(stream)));
   countLaunch();
   return TTB_OK;
+}
+
+// ---- all-reduce over peer memory: host side -----------------------------------------------------
+int ttb_symm_create_rank(void **symm, void *comm, int rank, int nranks, size_t max_bytes, void *stream) {
+  TTB_CHECK(symm && comm, "null argument");
+  TTB_CHECK(nranks >= 2 && nranks <= SYMM_MAX_RANKS && rank >= 0 && rank < nranks, "bad rank / world size");
+  TTB_NCCL_READY();
+  max_bytes = (max_bytes + 255) / 256 * 256;
+  auto *s = new Symm();
+  s->rank = rank;
+  s->n = nranks;
+  s->ipc = true;
+  s->maxBytes = max_bytes;
+  TTB_CUDA(cudaGetDevice(&s->device));
+  char *local = nullptr;
+  TTB_CUDA(cudaMalloc(reinterpret_cast<void **>(&local), symmTotalBytes(max_bytes)));
+  TTB_CUDA(cudaMemset(local, 0, SYMM_FLAG_BYTES));
+  TTB_CUDA(cudaMalloc(reinterpret_cast<void **>(&s->status), 128));
+  TTB_CUDA(cudaMemset(s->status, 0, 128));
+  if (const char *e = std::getenv("TTB_SYMM_STAMPS")) {
+    if (e[0] == '1') s->stamps = reinterpret_cast<unsigned long long *>(s->status + 16);
+  }
+  s->ws[rank] = local;
+  // Exchange the IPC handles through the communicator the mesh already has.
+  cudaIpcMemHandle_t mine;
+  TTB_CUDA(cudaIpcGetMemHandle(&mine, local));
+  char *devHandles = nullptr;
+  TTB_CUDA(cudaMalloc(reinterpret_cast<void **>(&devHandles), sizeof(mine) * (nranks + 1)));
+  cudaStream_t st = asStream(stream);
+  TTB_CUDA(cudaMemcpyAsync(devHandles + sizeof(mine) * nranks, &mine, sizeof(mine), cudaMemcpyHostToDevice, st));
+  TTB_NCCL(api.allGather(devHandles + sizeof(mine) * nranks, devHandles, sizeof(mine), ncclChar,
+                         static_cast<ncclComm_t>(comm), st));
+  std::vector<cudaIpcMemHandle_t> all(nranks);
+  TTB_CUDA(cudaMemcpyAsync(all.data(), devHandles, sizeof(mine) * nranks, cudaMemcpyDeviceToHost, st));
+  TTB_CUDA(cudaStreamSynchronize(st));
+  for (int r = 0; r < nranks; ++r) {
+    if (r == rank) continue;
+    void *p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, all[r], cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      setLastError(std::string("cannot map the workspace of rank ") + std::to_string(r) + ": " + cudaGetErrorString(e));
+      return TTB_ERR_CUDA;
+    }
+    s->ws[r] = static_cast<char *>(p);
+  }
+  // Nobody may touch a peer before every rank has cleared its flags and mapped the others.
+  TTB_NCCL(api.allGather(devHandles + sizeof(mine) * nranks, devHandles, sizeof(mine), ncclChar,
+                         static_cast<ncclComm_t>(comm), st));
+  TTB_CUDA(cudaStreamSynchronize(st));
+  TTB_CUDA(cudaFree(devHandles));
+  *symm = s;
+  return TTB_OK;
+}
+
+int ttb_symm_create_all(void **symms, int ndev, const int *devices, size_t max_bytes) {
+  TTB_CHECK(symms && devices, "null argument");
+  TTB_CHECK(ndev >= 2 && ndev <= SYMM_MAX_RANKS, "bad device count");
+  max_bytes = (max_bytes + 255) / 256 * 256;
+  int before = 0;
+  TTB_CUDA(cudaGetDevice(&before));
+  std::vector<Symm *> all(ndev);
+  for (int i = 0; i < ndev; ++i) {
+    TTB_CUDA(cudaSetDevice(devices[i]));
+    auto *s = new Symm();
+    s->rank = i;
+    s->n = ndev;
+    s->device = devices[i];
+    s->maxBytes = max_bytes;
+    char *local = nullptr;
+    TTB_CUDA(cudaMalloc(reinterpret_cast<void **>(&local), symmTotalBytes(max_bytes)));
+    TTB_CUDA(cudaMemset(local, 0, SYMM_FLAG_BYTES));
+    TTB_CUDA(cudaMalloc(reinterpret_cast<void **>(&s->status), 128));
+    TTB_CUDA(cudaMemset(s->status, 0, 128));
+    if (const char *e = std::getenv("TTB_SYMM_STAMPS")) {
+      if (e[0] == '1') s->stamps = reinterpret_cast<unsigned long long *>(s->status + 16);
+    }
+    s->ws[i] = local;
+    all[i] = s;
+    for (int j = 0; j < ndev; ++j) {
+      if (j == i) continue;
+      int can = 0;
+      TTB_CUDA(cudaDeviceCanAccessPeer(&can, devices[i], devices[j]));
+      if (!can) {
+        setLastError("devices " + std::to_string(devices[i]) + " and " + std::to_string(devices[j]) + " have no peer access");
+        return TTB_ERR_UNSUPPORTED;
+      }
+      cudaError_t e = cudaDeviceEnablePeerAccess(devices[j], 0);
+      if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) TTB_CUDA(e);
+      (void)cudaGetLastError();
+    }
+    TTB_CUDA(cudaDeviceSynchronize());
+  }
+  for (int i = 0; i < ndev; ++i) {
+    for (int j = 0; j < ndev; ++j) all[i]->ws[j] = all[j]->ws[j];
+    symms[i] = all[i];
+  }
+  TTB_CUDA(cudaSetDevice(before));
+  return TTB_OK;
+}
+
+int ttb_symm_destroy(void *symm) {
+  if (!symm) return TTB_OK;
+  auto *s = static_cast<Symm *>(symm);
+  int before = 0;
+  cudaGetDevice(&before);
+  cudaSetDevice(s->device);
+  cudaDeviceSynchronize();
+  for (int r = 0; r < s->n; ++r) {
+    if (r == s->rank || !s->ws[r]) continue;
+    if (s->ipc) cudaIpcCloseMemHandle(s->ws[r]);
+  }
+  if (s->ws[s->rank]) cudaFree(s->ws[s->rank]);
+  if (s->status) cudaFree(s->status);
+  (void)cudaGetLastError();
+  cudaSetDevice(before);
+  delete s;
+  return TTB_OK;
+}
+
+size_t ttb_symm_max_bytes(void *symm) { return symm ? static_cast<Symm *>(symm)->maxBytes : 0; }
+
+int ttb_symm_input_buffer(void *symm, size_t bytes, void **ptr) {
+  TTB_CHECK(symm && ptr, "null argument");
+  auto *s = static_cast<Symm *>(symm);
+  TTB_CHECK(bytes <= s->maxBytes, "operand larger than the workspace allows");
+  *ptr = s->ws[s->rank] + SYMM_FLAG_BYTES + static_cast<size_t>(s->launches & 1u) * s->maxBytes;
+  return TTB_OK;
+}
+
+int ttb_symm_stamps(void *symm, unsigned long long *stamps8) {
+  TTB_CHECK(symm && stamps8, "null argument");
+  auto *s = static_cast<Symm *>(symm);
+  TTB_CUDA(cudaMemcpy(stamps8, s->status + 16, 64, cudaMemcpyDeviceToHost));
+  return TTB_OK;
+}
+
+int ttb_symm_status(void *symm, int *status) {
+  TTB_CHECK(symm && status, "null argument");
+  auto *s = static_cast<Symm *>(symm);
+  TTB_CUDA(cudaMemcpy(status, s->status, sizeof(int), cudaMemcpyDeviceToHost));
+  return TTB_OK;
+}
+
+int ttb_symm_all_reduce(void *symm, const void *in, const void *residual, void *out, size_t count, int dtype,
+                        void *stream) {
+  TTB_CHECK(symm && in && out, "null argument");
+  auto *s = static_cast<Symm *>(symm);
+  const size_t es = dtypeSize(dtype);
+  const size_t bytes = count * es;
+  if ((dtype != kBF16 && dtype != kF16 && dtype != kF32) || bytes % 16 != 0 || bytes > s->maxBytes || !aligned16(in) ||
+      !aligned16(out) || (residual && !aligned16(residual))) {
+    setLastError("symm_all_reduce: operand type, size or alignment not supported");
+    return TTB_ERR_UNSUPPORTED;
+  }
+  if (count == 0) return TTB_OK;
+  SymmParams p;
+  p.rank = s->rank;
+  p.n = s->n;
+  for (int r = 0; r < SYMM_MAX_RANKS; ++r) p.ws[r] = s->ws[r];
+  const uint32_t launch = s->launches++;
+  const size_t parity = launch & 1u;
+  p.dataOff = SYMM_FLAG_BYTES + parity * s->maxBytes;
+  p.resultOff = SYMM_FLAG_BYTES + (2 + parity) * s->maxBytes;
+  p.token = 2 * launch + 1;
+  p.status = s->status;
+  p.oneShot = (s->n == 2 || bytes <= (size_t(256) << 10)) ? 1 : 0;
+  p.stamps = s->stamps;
+  const size_t nvec = bytes / 16;
+  cudaStream_t st = asStream(stream);
+  // The producer wrote the operand into this launch's data region (ttb_symm_input_buffer).
+  const bool staged = static_cast<const char *>(in) == s->ws[s->rank] + p.dataOff;
+  // per rank: (n-1)/n of the operand read from peers and as much pushed to them, the operand and
+  // the result once each locally, plus the staging copies
+  ProfScope prof("symm_all_reduce", 0, double(bytes) * (2.0 + 2.0 * (s->n - 1) / s->n), st);
+  if (dtype == kBF16) return symmDispatch<__nv_bfloat16>(p, in, residual, out, nvec, staged, st);
+  if (dtype == kF16) return symmDispatch<__half>(p, in, residual, out, nvec, staged, st);
+  return symmDispatch<float>(p, in, residual, out, nvec, staged, st);
 }
 
 } // extern "C"

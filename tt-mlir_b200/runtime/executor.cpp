@@ -13,6 +13,7 @@
 //     Fusion is off while debug hooks are registered, because callbacks may ask for any
 //     intermediate tensor;
 //   * tilize / untilize and memory-config changes are metadata only.
+#include <cstdlib>
 #include <algorithm>
 #include <cmath>
 #include <cstring>
@@ -336,6 +337,11 @@ private:
   size_t tryGemmEpilogue(size_t i);
   size_t trySiluMul(size_t i);
   size_t trySdpa(size_t i);
+  size_t tryAllReduceAdd(size_t i);
+  bool symmReady(size_t bytes);
+  TensorPtr allocForAllReduce(const fbt::TensorRef *ref); // null unless `ref` feeds the next all-reduce
+  size_t curOp = 0;
+  void allReduce(const TensorPtr &in, const TensorPtr &residual, const TensorPtr &out, int reduceType);
   size_t tryAddRmsNorm(size_t i);
 
   void runGetDevice(const fbt::GetDeviceOp *op);
@@ -562,6 +568,7 @@ std::vector<Tensor> Executor::run() {
 
 size_t Executor::runOp(size_t i) {
   const auto *op = prog->operations()->Get(static_cast<uint32_t>(i));
+  curOp = i;
   if (fuse) {
     size_t used = 0;
     switch (op->type_type()) {
@@ -571,6 +578,7 @@ size_t Executor::runOp(size_t i) {
     case OpType::EltwiseUnaryOp: used = trySiluMul(i); break;
     case OpType::EltwiseBinaryOp: used = tryAddRmsNorm(i); break;
     case OpType::ScaledDotProductAttentionOp: used = trySdpa(i); break;
+    case OpType::AllReduceOp: used = tryAllReduceAdd(i); break;
     default: break;
     }
     if (used) return used;
@@ -1078,7 +1086,8 @@ void Executor::runGemm(const fbt::TensorRef *aRef, const fbt::TensorRef *bRef, c
   TensorPtr a = getDevice(aRef), b = getDevice(bRef);
   TensorPtr bias = biasRef ? getDevice(biasRef) : nullptr;
   TensorPtr extra = extraRef ? getDevice(extraRef) : nullptr;
-  TensorPtr out = allocOut(outRef);
+  TensorPtr out = allocForAllReduce(outRef);
+  if (!out) out = allocOut(outRef);
   TTRT_ASSERT(a->dtype == b->dtype, "matmul operands differ in data type: ", dataTypeName(a->dtype), " vs ",
               dataTypeName(b->dtype));
   // 1-D operands follow numpy: a vector lhs is a row, a vector rhs is a column.
@@ -1748,6 +1757,107 @@ uint32_t Executor::meshAxisSize(uint32_t clusterAxis) const {
   return dev->meshShape[clusterAxis];
 }
 
+// The peer-memory all-reduce needs one workspace per rank that every other rank has mapped.
+// They are set up at the first all-reduce of a device (a collective step: every rank gets here
+// with the same program).  TTB_DISABLE_SYMM_AR=1, or any failure to map a peer, leaves NCCL in
+// charge.
+bool Executor::symmReady(size_t bytes) {
+  static const bool disabled = [] {
+    const char *e = std::getenv("TTB_DISABLE_SYMM_AR");
+    return e && e[0] == '1';
+  }();
+  if (disabled) return false;
+  if (!dev->symmTried) {
+    dev->symmTried = true;
+    constexpr size_t kMaxOperand = size_t(64) << 20;
+    int rc;
+    if (dev->multiProcess) {
+      RankCtx &r = dev->locals[0];
+      TTB_CALL(ttb_set_device(r.cudaDevice));
+      rc = ttb_symm_create_rank(&r.symm, r.comm, static_cast<int>(r.meshRank), static_cast<int>(dev->worldSize), kMaxOperand,
+                                r.stream);
+    } else {
+      std::vector<void *> symms(dev->locals.size(), nullptr);
+      std::vector<int> ids;
+      for (const RankCtx &r : dev->locals) ids.push_back(r.cudaDevice);
+      rc = ttb_symm_create_all(symms.data(), static_cast<int>(ids.size()), ids.data(), kMaxOperand);
+      if (rc == TTB_OK) {
+        for (size_t i = 0; i < symms.size(); ++i) dev->locals[i].symm = symms[i];
+      }
+    }
+    if (rc != TTB_OK) logDebug(std::string("peer-memory all-reduce unavailable, using NCCL: ") + ttb_last_error());
+  }
+  for (const RankCtx &r : dev->locals) {
+    if (!r.symm || bytes > ttb_symm_max_bytes(r.symm)) return false;
+  }
+  return true;
+}
+
+// A tensor whose only consumer is the next all-reduce (a sum over a float type, no other
+// all-reduce in between) is produced straight into the staging region of that all-reduce, which
+// then has nothing to copy.
+TensorPtr Executor::allocForAllReduce(const fbt::TensorRef *ref) {
+  if (!fuse || dev->worldSize == 1 || !singleUse(ref)) return nullptr;
+  auto use = info.firstUse.find(ref->global_id());
+  if (use == info.firstUse.end() || use->second <= curOp) return nullptr;
+  const auto *ops = prog->operations();
+  const auto *consumer = ops->Get(use->second);
+  if (consumer->type_type() != OpType::AllReduceOp) return nullptr;
+  const auto *ar = consumer->type_as_AllReduceOp();
+  if (static_cast<int>(ar->reduce_type()) != 0 || meshAxisSize(ar->cluster_axis()) == 1) return nullptr;
+  for (uint32_t k = static_cast<uint32_t>(curOp) + 1; k < use->second; ++k) {
+    if (ops->Get(k)->type_type() == OpType::AllReduceOp) return nullptr;
+  }
+  DataType dt = refDtype(ref);
+  if (dt != DataType::BFloat16 && dt != DataType::Float16 && dt != DataType::Float32) return nullptr;
+  auto t = std::make_shared<TensorImpl>();
+  t->shape = refShape(ref);
+  t->stride = denseStrides(t->shape);
+  t->dtype = dt;
+  t->storage = Storage::Device;
+  t->layout = refLayout(ref);
+  t->device = dev;
+  size_t bytes = t->bytes();
+  if (bytes == 0 || bytes % 16 != 0 || !symmReady(bytes)) return nullptr;
+  for (const RankCtx &r : dev->locals) {
+    auto b = std::make_shared<Buffer>();
+    TTB_CALL(ttb_symm_input_buffer(r.symm, bytes, &b->ptr));
+    b->bytes = bytes;
+    b->cudaDevice = r.cudaDevice;
+    b->kind = Buffer::Kind::Borrowed; // the workspace owns the memory
+    t->shards.push_back(b);
+  }
+  return t;
+}
+
+// out = all_reduce(in) [+ residual].  Sums of float tensors go through the peer-memory kernel
+// (one launch per rank, the residual add included); everything else through NCCL, with the add
+// as its own launch.
+void Executor::allReduce(const TensorPtr &in, const TensorPtr &residual, const TensorPtr &out, int reduceType) {
+  bool isFloat = in->dtype == DataType::BFloat16 || in->dtype == DataType::Float16 || in->dtype == DataType::Float32;
+  if (reduceType == 0 && isFloat && in->bytes() % 16 == 0 && symmReady(in->bytes())) {
+    eachRank([&](size_t i, const RankCtx &r) {
+      TTB_CALL(ttb_symm_all_reduce(r.symm, in->shards[i]->ptr, residual ? residual->shards[i]->ptr : nullptr,
+                                   out->shards[i]->ptr, in->volume(), ttbDtype(in->dtype), r.stream));
+    });
+    return;
+  }
+  if (dev->locals.size() > 1) TTB_CALL(ttb_group_start());
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_all_reduce(r.comm, in->shards[i]->ptr, out->shards[i]->ptr, in->volume(), ttbDtype(in->dtype), reduceType,
+                            r.stream));
+  });
+  if (dev->locals.size() > 1) TTB_CALL(ttb_group_end());
+  if (residual) {
+    int64_t shape[1] = {static_cast<int64_t>(out->volume())}, ones[1] = {1};
+    eachRank([&](size_t i, const RankCtx &r) {
+      TTB_CALL(ttb_eltwise_binary(static_cast<int>(fbt::EltwiseBinaryOpType::Add), out->shards[i]->ptr, ttbDtype(out->dtype),
+                                  residual->shards[i]->ptr, ttbDtype(residual->dtype), out->shards[i]->ptr, ttbDtype(out->dtype),
+                                  1, shape, ones, ones, r.stream));
+    });
+  }
+}
+
 void Executor::runAllReduce(const fbt::AllReduceOp *op) {
   TensorPtr in = getDevice(op->in());
   uint32_t n = meshAxisSize(op->cluster_axis());
@@ -1757,13 +1867,38 @@ void Executor::runAllReduce(const fbt::AllReduceOp *op) {
   }
   TensorPtr out = allocOut(op->out());
   TTRT_ASSERT(out->volume() == in->volume() && out->dtype == in->dtype, "all_reduce changes shape or type");
-  if (dev->locals.size() > 1) TTB_CALL(ttb_group_start());
-  eachRank([&](size_t i, const RankCtx &r) {
-    TTB_CALL(ttb_all_reduce(r.comm, in->shards[i]->ptr, out->shards[i]->ptr, in->volume(), ttbDtype(in->dtype),
-                            static_cast<int>(op->reduce_type()), r.stream));
-  });
-  if (dev->locals.size() > 1) TTB_CALL(ttb_group_end());
+  allReduce(in, nullptr, out, static_cast<int>(op->reduce_type()));
   put(op->out(), out);
+}
+
+// all_reduce -> add(x, result) with the result single-use: the residual add rides in the
+// all-reduce kernel (both roundings kept).
+size_t Executor::tryAllReduceAdd(size_t i) {
+  const auto *ops = prog->operations();
+  const auto *op = ops->Get(static_cast<uint32_t>(i))->type_as_AllReduceOp();
+  if (meshAxisSize(op->cluster_axis()) == 1 || static_cast<int>(op->reduce_type()) != 0 || !singleUse(op->out())) return 0;
+  std::vector<const fbt::Operation *> deallocs;
+  size_t j = i + 1;
+  const auto *nop = peek(j, deallocs);
+  if (!nop || nop->type_type() != OpType::EltwiseBinaryOp) return 0;
+  const auto *add = nop->type_as_EltwiseBinaryOp();
+  if (add->type() != fbt::EltwiseBinaryOpType::Add) return 0;
+  const fbt::TensorRef *other = nullptr;
+  uint32_t cur = op->out()->global_id();
+  if (add->lhs()->global_id() == cur) other = add->rhs();
+  else if (add->rhs()->global_id() == cur) other = add->lhs();
+  DataType dt = refDtype(op->out());
+  if (!other || other->global_id() == cur || refShape(other) != refShape(op->out()) || refDtype(other) != dt ||
+      refShape(add->out()) != refShape(op->out()) || refDtype(add->out()) != dt || !pool.count(other->global_id()) ||
+      (dt != DataType::BFloat16 && dt != DataType::Float16 && dt != DataType::Float32))
+    return 0;
+  TensorPtr in = getDevice(op->in()), res = getDevice(other);
+  if (in->dtype != dt || in->volume() != res->volume()) return 0;
+  TensorPtr out = allocOut(add->out());
+  allReduce(in, res, out, 0);
+  put(add->out(), out);
+  runDeallocs(deallocs);
+  return j + 1 - i;
 }
 
 void Executor::runAllGather(const fbt::AllGatherOp *op) {

@@ -64,6 +64,7 @@ struct RankCtx {
   void *copyIn = nullptr;   // host -> device copies from pinned memory (overlap the previous step's compute)
   void *copyOut = nullptr;  // non-blocking device -> host copies (overlap the next step's compute)
   void *comm = nullptr;
+  void *symm = nullptr;     // peer-memory workspace for all-reduce (created at the first one), or null
 };
 
 // A CUDA event owned by whoever holds the last reference.
@@ -95,6 +96,7 @@ struct DeviceImpl {
   std::vector<RankCtx> locals;     // coordinates this process owns
   bool multiProcess = false;
   bool open = false;
+  bool symmTried = false;          // the peer workspaces are set up (or found unavailable) once
   std::mutex submitMutex;          // submit is serialised per device
   ~DeviceImpl();
   void close();

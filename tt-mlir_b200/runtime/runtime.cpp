@@ -232,6 +232,10 @@ void DeviceImpl::close() {
       }
       if (r.stream) ttb_stream_sync(r.stream);
     }
+    if (r.symm) {
+      ttb_symm_destroy(r.symm);
+      r.symm = nullptr;
+    }
     if (r.comm) {
       ttb_comm_destroy(r.comm);
       r.comm = nullptr;
@@ -784,6 +788,12 @@ static void syncDevice(const std::shared_ptr<DeviceImpl> &d) {
     TTB_CALL(ttb_set_device(r.cudaDevice));
     for (void *st : {r.copyIn, r.stream, r.copyOut}) {
       if (st) TTB_CALL(ttb_stream_sync(st));
+    }
+    if (r.symm) {
+      int status = 0;
+      TTB_CALL(ttb_symm_status(r.symm, &status));
+      TTRT_ASSERT(status == 0, "a peer-memory all-reduce gave up waiting for rank ", (status & 0xff) - 1, " in phase ",
+                  status >> 8, "; results since then are invalid");
     }
   }
 }

@@ -340,8 +340,10 @@ def run_side(args):
     ev = Events(rt.lib, stream)
     launches0 = rt.launch_count()
     ev.start()
+    t_host = time.perf_counter()
     for _ in range(args.steps):
         out = rt.submit(device, binary, 0, dev_in)
+    host_us = (time.perf_counter() - t_host) / args.steps * 1e6
     ms = ev.stop_ms() / args.steps
     launches = rt.launch_count() - launches0
     prof = []
@@ -365,7 +367,7 @@ def run_side(args):
     line = {"metric": f"{args.workload}_{unit_name}_per_s", "value": units / (ms * 1e-3), "unit": f"{unit_name}/s",
             "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "dtype": "f32" if args.workload == "mlp" else "bf16", "data": "synthetic",
-            "config": {"workload": args.workload}, "gpu_launches": launches,
+            "config": {"workload": args.workload, "host_enqueue_us_per_step": host_us}, "gpu_launches": launches,
             "graph_hbm_gbs": abytes / (ms * 1e-3) / 1e9, "graph_hbm_frac": abytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
             "graph_tflops": aflops / (ms * 1e-3) / 1e12, "graph_tensor_frac": aflops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
             "per_op": prof}

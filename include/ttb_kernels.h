@@ -211,10 +211,11 @@ TTB_API int ttb_gemm(const void *a, const void *b, const void *bias, void *c, in
  * `c_dtype`), combined with the result of the bias / activation chain the way separate ops
  * would (the chain's result is rounded to `c_dtype` first):
  *   TTB_EXTRA_ADD       c = round(result + extra)                  linear followed by ::ttnn::add (a residual)
+ *   TTB_EXTRA_ADD_RELU  c = relu(round(result + extra))            ... followed by ::ttnn::relu
  *   TTB_EXTRA_SILU_MUL  c = round(round(silu(extra)) * result)     ::ttnn::silu + ::ttnn::multiply (SwiGLU gating)
  * On the tensor-core kernel this is one launch; elsewhere the elementwise kernels finish the job.
  * No reference counterpart: the reference runs these as separate ttnn ops. */
-enum { TTB_EXTRA_NONE = 0, TTB_EXTRA_ADD = 1, TTB_EXTRA_SILU_MUL = 2 };
+enum { TTB_EXTRA_NONE = 0, TTB_EXTRA_ADD = 1, TTB_EXTRA_SILU_MUL = 2, TTB_EXTRA_ADD_RELU = 3 };
 TTB_API int ttb_gemm_fused(const void *a, const void *b, const void *bias, void *c, int ab_dtype,
                            int bias_dtype, int c_dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                            int trans_a, int trans_b, int64_t a_batch_stride, int64_t b_batch_stride,
@@ -241,6 +242,13 @@ TTB_API int ttb_conv2d(const void *x, const void *weight, const void *bias, void
                        int bias_dtype, int64_t n, int64_t h, int64_t w, int64_t c, int64_t o,
                        int kh, int kw, int stride_h, int stride_w, const int *padding4, int dil_h,
                        int dil_w, int groups, int act, void *workspace, void *stream);
+/* ttb_conv2d with the second epilogue operand of ttb_gemm_fused: `extra` is an NHWC tensor of the
+ * output's shape and type (a residual branch), `extra_op` one of TTB_EXTRA_*. */
+TTB_API int ttb_conv2d_fused(const void *x, const void *weight, const void *bias, void *out, int dtype,
+                             int bias_dtype, int64_t n, int64_t h, int64_t w, int64_t c, int64_t o, int kh,
+                             int kw, int stride_h, int stride_w, const int *padding4, int dil_h, int dil_w,
+                             int groups, int act, const void *extra, int extra_op, void *workspace,
+                             void *stream);
 
 /* conv2d for callers that must not allocate.  No counterpart in the reference: tt-mlir's
  * runtime always lets the device library allocate its own intermediates.

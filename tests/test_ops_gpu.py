@@ -233,3 +233,33 @@ def test_empty_tensor(rt, device):
     x = torch.zeros(0, 16)
     got, want = run_body(rt, device, lambda b, v: b.relu(v), [x])
     assert list(got[0].shape) == [0, 16]
+
+
+@pytest.mark.parametrize("c,o,k,stride,pad,dil", [
+    (64, 64, 3, (1, 1), (1, 1, 1, 1), (1, 1)),
+    (64, 40, 3, (2, 2), (0, 1, 1, 2), (1, 1)),
+    (128, 256, 3, (1, 1), (2, 2, 2, 2), (2, 2)),
+    (64, 72, 5, (1, 2), (2, 2, 2, 2), (1, 1)),
+    (192, 64, 1, (2, 2), (0, 0, 0, 0), (1, 1)),
+])
+def test_conv2d_implicit_gemm(rt, device, c, o, k, stride, pad, dil):
+    """Channel counts that are multiples of 64 take the tensor-core kernel's gathering producer
+    (no im2col operand in memory): strides, asymmetric padding, dilation, several k-blocks per
+    tap, ragged pixel and channel tails, with the relu and residual-add epilogues."""
+    torch.manual_seed(c + o + k)
+    n, h, w = 3, 13, 11
+    x = torch.randn(n, h, w, c).to(torch.bfloat16)
+    wt = (torch.randn(o, c, k, k) * (2.0 / (c * k * k)) ** 0.5).to(torch.bfloat16)
+    bias = torch.randn(1, 1, 1, o).to(torch.bfloat16)
+    ho = (h + pad[0] + pad[2] - dil[0] * (k - 1) - 1) // stride[0] + 1
+    wo = (w + pad[1] + pad[3] - dil[1] * (k - 1) - 1) // stride[1] + 1
+    res = torch.randn(n, ho, wo, o).to(torch.bfloat16)
+
+    def body(b, xx, ww, bb, rr):
+        plain = b.conv2d(xx, ww, bb, n, h, w, stride=stride, padding=pad, dilation=dil)
+        act = b.relu(b.conv2d(xx, ww, bb, n, h, w, stride=stride, padding=pad, dilation=dil))
+        fused = b.relu(b.add(b.conv2d(xx, ww, None, n, h, w, stride=stride, padding=pad, dilation=dil), rr))
+        return plain, act, fused
+    got, want = run_body(rt, device, body, [x, wt, bias, res])
+    for g, wnt, name in zip(got, want, ["plain", "relu", "add+relu"]):
+        assert_matches(g, wnt, f"conv {c}->{o} k{k} {name}")

@@ -70,8 +70,10 @@ def test_static_scratch_refuses_oversized_problem(rt, device):
         i64 = ctypes.c_int64
         padding = (ctypes.c_int * 4)(1, 1, 1, 1)
         dummy = h.empty((16,), torch.uint8)
-        # 64 x 56 x 56 pixels x 576 taps x 2 bytes = 231 MB of gathered input: beyond the 32 MiB buffer
-        rc = h.lib.ttb_conv2d_static(dummy, dummy, None, dummy, BF16, BF16, i64(64), i64(56), i64(56), i64(64), i64(64),
+        # 48 channels are not whole 64-channel blocks, so the gathered input is materialised:
+        # 64 x 56 x 56 pixels x 432 taps x 2 bytes = 173 MB, beyond the 32 MiB buffer.  The call must
+        # refuse before touching any tensor (the pointers here are 16-byte dummies).
+        rc = h.lib.ttb_conv2d_static(dummy, dummy, None, dummy, BF16, BF16, i64(64), i64(56), i64(56), i64(48), i64(64),
                                      3, 3, 1, 1, padding, 1, 1, 1, 0, h.stream)
         assert rc != 0
         msg = h.lib.ttb_last_error().decode()

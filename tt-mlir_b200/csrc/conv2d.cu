@@ -9,9 +9,15 @@
 // image) and reorders the weights from [O, C, kH, kW] to [O, kH, kW, C] in a workspace.
 #include "common.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace ttb {
+
+// Implicit GEMM on the tensor-core kernel (gemm_tcgen05.cu); -1 = not taken.
+int convTcgen05Try(const void *x, const void *wre, const void *bias, void *out, int dtype, int biasDtype, int64_t n,
+                   int64_t h, int64_t w, int64_t c, int64_t o, int64_t ho, int64_t wo, int kh, int kw, int sh, int sw,
+                   int pt, int pl, int dh, int dw, int act, const void *extra, int extraOp, cudaStream_t stream);
 
 // Scratch for ttb_conv2d_static: lives in the library's device image, so every GPU that loads
 // the library holds these bytes until the process exits.
@@ -62,6 +68,21 @@ static bool isPointwise(int kh, int kw, int sh, int sw, const int *pad, int grou
 
 static size_t alignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+static bool im2colForced() {
+  static const bool forced = [] {
+    const char *e = std::getenv("TTB_CONV_IM2COL");
+    return e && e[0] == '1';
+  }();
+  return forced;
+}
+
+// Shapes the tensor-core kernel convolves without an im2col operand in memory (it gathers the
+// receptive fields itself): 16-bit data, whole 64-channel blocks.  Decides the workspace size, so
+// it depends on the shape only; operands are then required to be 16-byte aligned.
+static bool implicitGemmShape(int dtype, int64_t c, int64_t o) {
+  return !im2colForced() && (dtype == kBF16 || dtype == kF16) && c % 64 == 0 && o >= 8 && o % 8 == 0;
+}
+
 } // namespace ttb
 
 using namespace ttb;
@@ -76,19 +97,30 @@ size_t ttb_conv2d_workspace_bytes(int dtype, int64_t n, int64_t h, int64_t w, in
   if (ho <= 0 || wo <= 0) return 0;
   size_t es = dtypeSize(dtype);
   size_t K = static_cast<size_t>(kh) * kw * c;
-  return alignUp(static_cast<size_t>(n * ho * wo) * K * es, 256) + alignUp(static_cast<size_t>(o) * K * es, 256);
+  size_t weights = alignUp(static_cast<size_t>(o) * K * es, 256);
+  if (implicitGemmShape(dtype, c, o)) return weights; // only the reordered weights
+  return alignUp(static_cast<size_t>(n * ho * wo) * K * es, 256) + weights;
 }
 
 int ttb_conv2d(const void *x, const void *weight, const void *bias, void *out, int dtype, int bias_dtype, int64_t n,
                int64_t h, int64_t w, int64_t c, int64_t o, int kh, int kw, int stride_h, int stride_w,
                const int *padding4, int dil_h, int dil_w, int groups, int act, void *workspace, void *stream) {
+  return ttb_conv2d_fused(x, weight, bias, out, dtype, bias_dtype, n, h, w, c, o, kh, kw, stride_h, stride_w, padding4,
+                          dil_h, dil_w, groups, act, nullptr, TTB_EXTRA_NONE, workspace, stream);
+}
+
+int ttb_conv2d_fused(const void *x, const void *weight, const void *bias, void *out, int dtype, int bias_dtype, int64_t n,
+                     int64_t h, int64_t w, int64_t c, int64_t o, int kh, int kw, int stride_h, int stride_w,
+                     const int *padding4, int dil_h, int dil_w, int groups, int act, const void *extra, int extra_op,
+                     void *workspace, void *stream) {
   TTB_CHECK(x && weight && out && padding4, "null argument");
   TTB_CHECK(groups == 1, "grouped convolution is not supported");
   TTB_CHECK(kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0 && dil_h > 0 && dil_w > 0, "bad convolution geometry");
   size_t es = dtypeSize(dtype);
   TTB_CHECK(dtype == kBF16 || dtype == kF32 || dtype == kF16, "conv2d needs a float dtype");
   if (isPointwise(kh, kw, stride_h, stride_w, padding4, groups)) {
-    return ttb_gemm(x, weight, bias, out, dtype, bias_dtype, dtype, 1, n * h * w, o, c, 0, 1, 0, 0, act, 0, stream);
+    return ttb_gemm_fused(x, weight, bias, out, dtype, bias_dtype, dtype, 1, n * h * w, o, c, 0, 1, 0, 0, act, 0, extra, extra_op,
+                          stream);
   }
   ConvGeom g;
   g.N = n; g.H = h; g.W = w; g.C = c;
@@ -99,8 +131,9 @@ int ttb_conv2d(const void *x, const void *weight, const void *bias, void *out, i
   TTB_CHECK(g.Ho > 0 && g.Wo > 0, "convolution output is empty");
   TTB_CHECK(workspace != nullptr, "conv2d needs its workspace");
   int64_t P = n * g.Ho * g.Wo, K = static_cast<int64_t>(kh) * kw * c;
+  const bool implicit = implicitGemmShape(dtype, c, o);
   char *col = static_cast<char *>(workspace);
-  char *wre = col + alignUp(static_cast<size_t>(P) * K * es, 256);
+  char *wre = implicit ? col : col + alignUp(static_cast<size_t>(P) * K * es, 256);
   cudaStream_t st = asStream(stream);
   // weights [O, C, kH, kW] -> [O, kH, kW, C]
   {
@@ -108,6 +141,14 @@ int ttb_conv2d(const void *x, const void *weight, const void *bias, void *out, i
     int64_t strides[4] = {c * kh * kw, kw, 1, static_cast<int64_t>(kh) * kw};
     int rc = ttb_strided_copy(weight, wre, static_cast<int>(es), 4, shape, strides, 0, stream);
     if (rc) return rc;
+  }
+  // The tensor-core kernel gathers the receptive fields itself when the channel count allows.
+  if (implicit) {
+    int rc = convTcgen05Try(x, wre, bias, out, dtype, bias_dtype, n, h, w, c, o, g.Ho, g.Wo, kh, kw, stride_h, stride_w,
+                            padding4[0], padding4[1], dil_h, dil_w, act, extra, extra_op, st);
+    if (rc != -1) return rc;
+    setLastError("conv2d: this shape runs without an im2col workspace, but the tensor-core path declined it (operand alignment or extents)");
+    return TTB_ERR_INVALID;
   }
   int vec = static_cast<int>(16 / es);
   ProfScope prof("conv2d_im2col", 0, double(P) * K * es + double(n) * h * w * c * es, st);
@@ -124,7 +165,7 @@ int ttb_conv2d(const void *x, const void *weight, const void *bias, void *out, i
   }
   countLaunch();
   TTB_LAUNCH_CHECK();
-  return ttb_gemm(col, wre, bias, out, dtype, bias_dtype, dtype, 1, P, o, K, 0, 1, 0, 0, act, 0, stream);
+  return ttb_gemm_fused(col, wre, bias, out, dtype, bias_dtype, dtype, 1, P, o, K, 0, 1, 0, 0, act, 0, extra, extra_op, stream);
 }
 
 int ttb_conv2d_static(const void *x, const void *weight, const void *bias, void *out, int dtype, int bias_dtype,

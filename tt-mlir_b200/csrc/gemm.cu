@@ -32,7 +32,7 @@ extern "C" int ttb_gemm_fused(const void *a, const void *b, const void *bias, vo
                               int c_dtype, int64_t batch, int64_t m, int64_t n, int64_t k, int trans_a, int trans_b,
                               int64_t a_batch_stride, int64_t b_batch_stride, int act, int round_steps,
                               const void *extra, int extra_op, void *stream) {
-  TTB_CHECK(extra_op == TTB_EXTRA_NONE || extra_op == TTB_EXTRA_ADD || extra_op == TTB_EXTRA_SILU_MUL, "unknown extra_op");
+  TTB_CHECK(extra_op >= TTB_EXTRA_NONE && extra_op <= TTB_EXTRA_ADD_RELU, "unknown extra_op");
   TTB_CHECK(extra_op == TTB_EXTRA_NONE || extra != nullptr, "extra_op without its operand");
   if (!tcgen05Disabled()) {
     int rc = ttb::gemmTcgen05Try(a, b, bias, c, ab_dtype, bias_dtype, c_dtype, batch, m, n, k, trans_a, trans_b,
@@ -46,5 +46,7 @@ extern "C" int ttb_gemm_fused(const void *a, const void *b, const void *bias, vo
   const size_t count = static_cast<size_t>(batch * m * n);
   if (extra_op == TTB_EXTRA_SILU_MUL) return ttb_silu_mul(extra, c, c, c_dtype, count, stream);
   int64_t shape[1] = {static_cast<int64_t>(count)}, ones[1] = {1};
-  return ttb_eltwise_binary(0 /* EltwiseBinaryOpType::Add */, c, c_dtype, extra, c_dtype, c, c_dtype, 1, shape, ones, ones, stream);
+  rc = ttb_eltwise_binary(0 /* EltwiseBinaryOpType::Add */, c, c_dtype, extra, c_dtype, c, c_dtype, 1, shape, ones, ones, stream);
+  if (rc || extra_op == TTB_EXTRA_ADD) return rc;
+  return ttb_eltwise_unary(8 /* EltwiseUnaryOpType::Relu */, c, c_dtype, c, c_dtype, count, 0.0f, stream);
 }

@@ -4,6 +4,10 @@
 // (tosa.matmul with f32 accumulation, lib/Conversion/TTIRToLinalg/TTIRToLinalg.cpp:542-549),
 // (b) shapes the tcgen05 kernel does not take, and (c) as the in-library cross-check of the
 // tensor-core kernel.  64x64 tile per 256-thread block, 4x4 outputs per thread, k-step 16.
+// Problems with few output tiles and a long K (the f32 MLP layers: 8 tiles, K = 784) are split
+// along K over gridDim.z: every block writes its partial tile to a scratch buffer, and the block
+// that arrives last at a tile adds the partials in split order (the same order every run) and
+// applies the epilogue.
 #include "common.cuh"
 #include "epilogue.cuh"
 
@@ -15,30 +19,35 @@ template <typename T, typename TC>
 __global__ void __launch_bounds__(256)
     gemmSimtKernel(const T *__restrict__ a, const T *__restrict__ b, const void *__restrict__ bias, int biasDt,
                    TC *__restrict__ c, int64_t M, int64_t N, int64_t K, int64_t asM, int64_t asK, int64_t bsK,
-                   int64_t bsN, int64_t aBatch, int64_t bBatch, int act, int roundSteps) {
+                   int64_t bsN, int64_t aBatch, int64_t bBatch, int act, int roundSteps, int splitK, int64_t kPer,
+                   float *__restrict__ partials, unsigned *__restrict__ arrivals) {
   __shared__ float sa[BK][BM + 1];
   __shared__ float sb[BK][BN + 1];
-  int64_t batch = blockIdx.z;
+  __shared__ bool lastBlock;
+  const int split = splitK > 1 ? static_cast<int>(blockIdx.z) : 0;
+  int64_t batch = splitK > 1 ? 0 : blockIdx.z;
   const T *A = a + batch * aBatch;
   const T *B = b + batch * bBatch;
   TC *C = c + batch * M * N;
   int64_t m0 = static_cast<int64_t>(blockIdx.y) * BM, n0 = static_cast<int64_t>(blockIdx.x) * BN;
   int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
   float acc[4][4] = {};
-  for (int64_t k0 = 0; k0 < K; k0 += BK) {
+  const int64_t kBegin = splitK > 1 ? split * kPer : 0;
+  const int64_t kEnd = splitK > 1 ? (kBegin + kPer < K ? kBegin + kPer : K) : K;
+  for (int64_t k0 = kBegin; k0 < kEnd; k0 += BK) {
     // 64x16 elements per operand, 256 threads -> 4 each.  Index so that the fastest-varying
     // thread index follows the contiguous global dimension of each operand.
     for (int i = threadIdx.x; i < BM * BK; i += 256) {
       int mm, kk;
       if (asK == 1) { kk = i % BK; mm = i / BK; } else { mm = i % BM; kk = i / BM; }
       int64_t gm = m0 + mm, gk = k0 + kk;
-      sa[kk][mm] = (gm < M && gk < K) ? toF32(A[gm * asM + gk * asK]) : 0.0f;
+      sa[kk][mm] = (gm < M && gk < kEnd) ? toF32(A[gm * asM + gk * asK]) : 0.0f;
     }
     for (int i = threadIdx.x; i < BN * BK; i += 256) {
       int nn, kk;
       if (bsN == 1) { nn = i % BN; kk = i / BN; } else { kk = i % BK; nn = i / BK; }
       int64_t gn = n0 + nn, gk = k0 + kk;
-      sb[kk][nn] = (gn < N && gk < K) ? toF32(B[gk * bsK + gn * bsN]) : 0.0f;
+      sb[kk][nn] = (gn < N && gk < kEnd) ? toF32(B[gk * bsK + gn * bsN]) : 0.0f;
     }
     __syncthreads();
 #pragma unroll
@@ -54,6 +63,29 @@ __global__ void __launch_bounds__(256)
         for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
     }
     __syncthreads();
+  }
+  if (splitK > 1) {
+    const size_t tile = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
+    float *mine = partials + (tile * splitK + split) * (BM * BN);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) mine[(i * 4 + j) * 256 + threadIdx.x] = acc[i][j];
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) lastBlock = atomicAdd(&arrivals[tile], 1u) == static_cast<unsigned>(splitK - 1);
+    __syncthreads();
+    if (!lastBlock) return;
+    __threadfence();
+    const float *all = partials + tile * splitK * (BM * BN);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float sum = 0.0f;
+        for (int sp = 0; sp < splitK; ++sp) sum += __ldcg(all + sp * (BM * BN) + (i * 4 + j) * 256 + threadIdx.x);
+        acc[i][j] = sum;
+      }
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -73,14 +105,46 @@ template <typename T, typename TC>
 static int launchSimt(const void *a, const void *b, const void *bias, int biasDt, void *c, int64_t batch, int64_t m,
                       int64_t n, int64_t k, int ta, int tb, int64_t aBatch, int64_t bBatch, int act, int roundSteps,
                       cudaStream_t st) {
-  dim3 grid(static_cast<unsigned>((n + BN - 1) / BN), static_cast<unsigned>((m + BM - 1) / BM),
-            static_cast<unsigned>(batch));
+  const int64_t tilesN = (n + BN - 1) / BN, tilesM = (m + BM - 1) / BM;
   int64_t asM = ta ? 1 : k, asK = ta ? m : 1;
   int64_t bsK = tb ? 1 : n, bsN = tb ? k : 1;
-  ProfScope prof("gemm_simt", 2.0 * double(batch) * m * n * k, double(batch) * (double(m) * k + double(n) * k) * sizeof(T) + double(batch) * m * n * sizeof(TC), st);
-  gemmSimtKernel<T, TC><<<grid, 256, 0, st>>>(static_cast<const T *>(a), static_cast<const T *>(b), bias, biasDt,
-                                              static_cast<TC *>(c), m, n, k, asM, asK, bsK, bsN, aBatch, bBatch, act,
-                                              roundSteps);
+  // Split K when the tiles alone leave most SMs idle and each split still has a few k-steps.
+  int splitK = 1;
+  if (batch == 1 && tilesM * tilesN * 2 <= smCount() && k >= 8 * BK) {
+    int64_t want = smCount() / (tilesM * tilesN);
+    int64_t most = k / (2 * BK);
+    splitK = static_cast<int>(want < most ? want : most);
+    if (splitK > 32) splitK = 32;
+    if (splitK < 2) splitK = 1;
+  }
+  int64_t kPer = k;
+  float *partials = nullptr;
+  unsigned *arrivals = nullptr;
+  void *scratch = nullptr;
+  if (splitK > 1) {
+    kPer = ((k + splitK - 1) / splitK + BK - 1) / BK * BK;
+    splitK = static_cast<int>((k + kPer - 1) / kPer);
+  }
+  if (splitK > 1) {
+    const size_t counters = (static_cast<size_t>(tilesM * tilesN) * sizeof(unsigned) + 255) / 256 * 256;
+    const size_t bytes = counters + static_cast<size_t>(tilesM * tilesN) * splitK * BM * BN * sizeof(float);
+    int rc = ttb_malloc(&scratch, bytes, st);
+    if (rc) return rc;
+    TTB_CUDA(cudaMemsetAsync(scratch, 0, counters, st));
+    arrivals = static_cast<unsigned *>(scratch);
+    partials = reinterpret_cast<float *>(static_cast<char *>(scratch) + counters);
+  }
+  dim3 grid(static_cast<unsigned>(tilesN), static_cast<unsigned>(tilesM), static_cast<unsigned>(splitK > 1 ? splitK : batch));
+  {
+    ProfScope prof("gemm_simt", 2.0 * double(batch) * m * n * k, double(batch) * (double(m) * k + double(n) * k) * sizeof(T) + double(batch) * m * n * sizeof(TC), st);
+    gemmSimtKernel<T, TC><<<grid, 256, 0, st>>>(static_cast<const T *>(a), static_cast<const T *>(b), bias, biasDt,
+                                                static_cast<TC *>(c), m, n, k, asM, asK, bsK, bsN, aBatch, bBatch, act,
+                                                roundSteps, splitK, kPer, partials, arrivals);
+  }
+  if (scratch) {
+    int rc = ttb_free(scratch, st); // stream-ordered: released once the kernel has run
+    if (rc) return rc;
+  }
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;

@@ -25,7 +25,8 @@ namespace ttb {
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64; // 64 x 2 bytes = one 128-byte swizzle row
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 192;      // producer warp, MMA warp, four epilogue warps
+constexpr int TC_THREADS_EPI8 = 320; // eight epilogue warps (kernels with a non-trivial epilogue)
 constexpr int TC_TMEM_COLS = 512;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;
 constexpr int TC_OUT_BYTES = 4 * 2 * 4096; // epilogue staging: 4 warps, double buffered, 32 rows x 128 B
@@ -64,6 +65,20 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
 }
 template <> __device__ __forceinline__ uint32_t pack2<float>(float a, float) { return __float_as_uint(a); }
 
+// relu on a packed pair (NaN stays NaN); relu commutes with the rounding before it.
+template <typename TC> __device__ __forceinline__ uint32_t relu2(uint32_t v);
+template <> __device__ __forceinline__ uint32_t relu2<__nv_bfloat16>(uint32_t v) {
+  __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162 *>(&v);
+  x = __hmax2_nan(x, __floats2bfloat162_rn(0.0f, 0.0f));
+  return *reinterpret_cast<uint32_t *>(&x);
+}
+template <> __device__ __forceinline__ uint32_t relu2<__half>(uint32_t v) {
+  __half2 x = *reinterpret_cast<__half2 *>(&v);
+  x = __hmax2_nan(x, __floats2half2_rn(0.0f, 0.0f));
+  return *reinterpret_cast<uint32_t *>(&x);
+}
+template <> __device__ __forceinline__ uint32_t relu2<float>(uint32_t v) { return v; }
+
 struct TcParams {
   int64_t M, N, K;
   const void *bias;
@@ -72,12 +87,23 @@ struct TcParams {
   int roundSteps;
   const void *extra; // optional [M, N] operand in the output type, combined after bias / activation
   int extraOp;       // TTB_EXTRA_*
+  // Implicit-GEMM convolution: A is not a matrix in memory but the receptive fields of an NHWC
+  // tensor; row p of A is output pixel p, k-block kb is channels [64*(kb % cb), +64) of filter tap
+  // kb / cb, cb = C / 64.  convX null = plain GEMM.
+  const void *convX;
+  int cH, cW, cC, cHo, cWo, ckw, csh, csw, cpt, cpl, cdh, cdw;
+  // Patch mode (stride-1 convolutions): a tile's 128 rows are a cTw x 128/cTw patch of output
+  // pixels of one image, which makes the A tile of a filter tap one 4-D TMA box of the input
+  // (zero fill outside the image = the padding) and the C tile a 4-D TMA box of the output.
+  // cTw = 0: rows are 128 consecutive pixels and the producer warp gathers them with cp.async.
+  int cTw, cTilesX, cTilesY;
+  int64_t cTilesM; // images x cTilesY x cTilesX
   int fmt; // 1 bf16, 0 f16
   int debug; // diagnostic: 1 = epilogue loads TMEM but skips math and stores, 2 = epilogue only hands the buffer back
 };
 
 template <int BN, typename TC, bool PLAIN>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     gemmTcgen05Kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                       const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapE,
                       TC *__restrict__ c, TcParams p) {
@@ -97,14 +123,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   volatile int *abortFlag = &abortFlagS;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t tilesM = (p.M + TC_BM - 1) / TC_BM, tilesN = (p.N + BN - 1) / BN;
+  const int64_t tilesM = p.cTw ? p.cTilesM : (p.M + TC_BM - 1) / TC_BM, tilesN = (p.N + BN - 1) / BN;
   const int64_t numTiles = tilesM * tilesN;
   const int kBlocks = static_cast<int>((p.K + TC_BK - 1) / TC_BK);
 
   if (threadIdx.x == 0) {
     abortFlagS = 0;
     for (int s = 0; s < STAGES; ++s) {
-      mbarInit(fullBar(s), 1);
+      mbarInit(fullBar(s), (p.convX && !p.cTw) ? 2 : 1); // gathering convolution: the weights' TMA and the pixels arrive separately
       mbarInit(emptyBar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -125,20 +151,111 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   tcFenceAfter();
   const uint32_t tmemBase = tmemBaseSlot;
 
-  if (warp == 0) {
+  if (warp == 0 && p.convX && !p.cTw) {
+    // ---------------- convolution producer: the whole warp gathers A, lane 0 also loads B ----------------
+    // One cp.async instruction of the warp copies four tile rows: eight consecutive lanes fetch
+    // the eight 16-byte pieces of one pixel's 64 channels (one full 128-byte line), zero-filled
+    // outside the image, to where the 128-byte swizzle of the operand layout puts them.  Per tile
+    // every lane keeps, for its 32 (row, piece) slots, the element offset of the pixel at tap
+    // (0, 0) and that pixel's coordinates; a k-block then costs a few integer operations per copy.
+    // Up to kInFlight stages of copies are in flight; a stage is handed to the MMA warp when its
+    // copies have landed and are visible to the async proxy.
+    constexpr int kInFlight = 3;
+    const uint16_t *x = static_cast<const uint16_t *>(p.convX);
+    const int cb = p.cC / TC_BK;
+    const int piece = lane & 7, rowInGroup = lane >> 3;
+    uint32_t it = 0, handed = 0;
+    bool alive = true;
+    auto hand = [&](uint32_t item) { // copies of `item` are complete
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbarArrive(fullBar(item % STAGES));
+    };
+    for (int64_t tile = blockIdx.x; tile < numTiles && alive; tile += gridDim.x) {
+      const int64_t m0 = (tile % tilesM) * TC_BM;
+      const int n0 = static_cast<int>(tile / tilesM) * BN;
+      int off[32];      // element offset of (pixel at tap 0, piece), or of x itself for rows past the end
+      uint32_t yx[32];  // (y0 + 0x4000) << 16 | (x0 + 0x4000); rows past the end get coordinates that never pass
+#pragma unroll
+      for (int q = 0; q < 32; ++q) {
+        const int64_t pix = m0 + q * 4 + rowInGroup;
+        if (pix < p.M) {
+          const int64_t img = pix / (static_cast<int64_t>(p.cHo) * p.cWo);
+          const int rem = static_cast<int>(pix - img * p.cHo * p.cWo);
+          const int y0 = (rem / p.cWo) * p.csh - p.cpt, x0 = (rem % p.cWo) * p.csw - p.cpl;
+          off[q] = static_cast<int>(((img * p.cH + y0) * p.cW + x0) * p.cC) + piece * 8;
+          yx[q] = (static_cast<uint32_t>(y0 + 0x4000) << 16) | static_cast<uint32_t>(x0 + 0x4000);
+        } else {
+          off[q] = 0;
+          yx[q] = 0; // y0 = x0 = -16384: outside for every tap
+        }
+      }
+      for (int kb = 0; kb < kBlocks; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t phase = (it / STAGES) & 1u;
+        if (!__all_sync(0xffffffffu, mbarWait(emptyBar(s), phase ^ 1u, abortFlag, 1))) { alive = false; break; }
+        const uint32_t sa = base + s * Cfg::kStageBytes, sb = sa + TC_A_BYTES;
+        if (lane == 0) {
+          mbarArriveExpectTx(fullBar(s), BN * TC_BK * 2);
+          tmaLoad2d(sb, &mapB, fullBar(s), kb * TC_BK, n0);
+        }
+        const int tap = kb / cb, c0 = (kb - tap * cb) * TC_BK;
+        const int ky = tap / p.ckw, kx = tap - ky * p.ckw;
+        const int dy = ky * p.cdh, dx = kx * p.cdw;
+        const int tapOff = (dy * p.cW + dx) * p.cC + c0;
+        // destination of this lane's piece in row q*4 + rowInGroup: rows are 128 bytes, the piece
+        // index is XORed with the row's low three bits (rowInGroup + 4*(q & 1))
+        const uint32_t dstLane = sa + static_cast<uint32_t>(rowInGroup) * 128u;
+#pragma unroll
+        for (int q = 0; q < 32; ++q) {
+          const int y = static_cast<int>(yx[q] >> 16) - 0x4000 + dy, xx = static_cast<int>(yx[q] & 0xffffu) - 0x4000 + dx;
+          const bool inside = static_cast<unsigned>(y) < static_cast<unsigned>(p.cH) &&
+                              static_cast<unsigned>(xx) < static_cast<unsigned>(p.cW);
+          const uint16_t *src = x + (inside ? off[q] + tapOff : 0);
+          const uint32_t bytes = inside ? 16u : 0u; // 0 source bytes = the 16 destination bytes are zero-filled
+          const uint32_t row7 = static_cast<uint32_t>((rowInGroup + 4 * (q & 1)) & 7);
+          const uint32_t dst = dstLane + static_cast<uint32_t>(q) * 512u + ((static_cast<uint32_t>(piece) ^ row7) << 4);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (it - handed >= static_cast<uint32_t>(kInFlight)) {
+          asm volatile("cp.async.wait_group %0;" ::"n"(kInFlight) : "memory");
+          hand(handed++);
+        }
+      }
+    }
+    // drain: everything issued has to land (also when leaving early) before its stage is handed over
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    while (handed < it) hand(handed++);
+  } else if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       uint32_t it = 0;
       bool alive = true;
       for (int64_t tile = blockIdx.x; tile < numTiles && alive; tile += gridDim.x) {
-        const int m0 = static_cast<int>(tile % tilesM) * TC_BM, n0 = static_cast<int>(tile / tilesM) * BN;
+        const int mt = static_cast<int>(tile % tilesM);
+        const int m0 = mt * TC_BM, n0 = static_cast<int>(tile / tilesM) * BN;
+        int img = 0, oy0 = 0, ox0 = 0, cb = 1;
+        if (p.cTw) {
+          const int perImg = p.cTilesX * p.cTilesY, rem = mt % perImg;
+          img = mt / perImg;
+          oy0 = (rem / p.cTilesX) * (TC_BM / p.cTw);
+          ox0 = (rem % p.cTilesX) * p.cTw;
+          cb = p.cC / TC_BK;
+        }
         for (int kb = 0; kb < kBlocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t phase = (it / STAGES) & 1u;
           if (!mbarWait(emptyBar(s), phase ^ 1u, abortFlag, 1)) { alive = false; break; }
           const uint32_t sa = base + s * Cfg::kStageBytes, sb = sa + TC_A_BYTES;
           mbarArriveExpectTx(fullBar(s), Cfg::kStageBytes);
-          tmaLoad2d(sa, &mapA, fullBar(s), kb * TC_BK, m0);
+          if (p.cTw) {
+            // the input patch of this filter tap; coordinates left of / above the image read zeros
+            const int tap = kb / cb, ky = tap / p.ckw, kx = tap - ky * p.ckw;
+            tmaLoad4d(sa, &mapA, fullBar(s), (kb - tap * cb) * TC_BK, ox0 + kx * p.cdw - p.cpl, oy0 + ky * p.cdh - p.cpt, img);
+          } else {
+            tmaLoad2d(sa, &mapA, fullBar(s), kb * TC_BK, m0);
+          }
           tmaLoad2d(sb, &mapB, fullBar(s), kb * TC_BK, n0);
         }
       }
@@ -181,15 +298,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     // chunk be prepared while the previous store drains.
     constexpr int CH = 128 / static_cast<int>(sizeof(TC));
     constexpr int NLD = CH / 32;
+    constexpr int EPW = PLAIN ? 4 : 8; // epilogue warps
     const int quarter = warp & 3; // TMEM lanes this warp may read
-    const uint32_t stageOut = outBase + static_cast<uint32_t>(warp - 2) * 2u * 4096u;
-    uint32_t accIt = 0, chunkIt = 0;
+    // A relu that is the last step of a 16-bit epilogue is applied to the packed pairs.
+    const bool reluPacked = !PLAIN && sizeof(TC) == 2 && p.act == TTB_ACT_RELU && p.extraOp == 0;
+    // PLAIN: four warps, two staging buffers each.  Otherwise eight warps in two groups: group g
+    // drains accumulator buffer g (every other tile), one staging buffer per warp; two warps per
+    // scheduler hide each other's instruction latencies in the longer epilogues.
+    const int group = (warp - 2) / 4;
+    const uint32_t stageOut = outBase + static_cast<uint32_t>(warp - 2) * (EPW == 4 ? 2u : 1u) * 4096u;
+    uint32_t accIt = static_cast<uint32_t>(group), chunkIt = 0;
+    const int64_t tileStep = static_cast<int64_t>(gridDim.x) * (EPW / 4);
     // The extra operand is read row by row (one 128-byte segment per thread and chunk), which
     // would expose DRAM latency in every chunk.  Its 32-row x CH-column blocks are therefore
     // pulled into L2 one whole tile ahead: lanes 0 .. BN/CH-1 prefetch one block each.
     auto prefetchExtra = [&](int64_t t) {
       if constexpr (!PLAIN && sizeof(TC) == 2) {
-        if (p.extraOp && lane < BN / CH && t < numTiles) {
+        if (p.extraOp && !p.cTw && lane < BN / CH && t < numTiles) {
           const int64_t col = (t / tilesM) * BN + lane * CH, row = (t % tilesM) * TC_BM + quarter * 32;
           if (col < p.N && row < p.M) {
             asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
@@ -198,134 +323,182 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         }
       }
     };
-    prefetchExtra(blockIdx.x);
-    for (int64_t tile = blockIdx.x; tile < numTiles; tile += gridDim.x, ++accIt) {
+    prefetchExtra(blockIdx.x + static_cast<int64_t>(group) * gridDim.x);
+    for (int64_t tile = blockIdx.x + static_cast<int64_t>(group) * gridDim.x; tile < numTiles;
+         tile += tileStep, accIt += EPW / 4) {
       const int acc = accIt & 1;
       const uint32_t accPhase = (accIt >> 1) & 1u;
-      prefetchExtra(tile + gridDim.x);
+      prefetchExtra(tile + tileStep);
       if (!mbarWait(tmemFullBar(acc), accPhase, abortFlag, 4)) break;
       tcFenceAfter();
       const int64_t m0 = (tile % tilesM) * TC_BM, n0 = (tile / tilesM) * BN;
+      // patch mode: this warp's 32 rows are 32 / cTw rows of the patch, starting at (pOy, pOx) of image pImg
+      int pImg = 0, pOy = 0, pOx = 0;
+      if (p.cTw) {
+        const int mt = static_cast<int>(tile % tilesM), perImg = p.cTilesX * p.cTilesY, rem = mt % perImg;
+        pImg = mt / perImg;
+        pOy = (rem / p.cTilesX) * (TC_BM / p.cTw) + quarter * (32 / p.cTw);
+        pOx = (rem % p.cTilesX) * p.cTw;
+      }
       const uint32_t taddrRow = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
 #pragma unroll 1
       for (int cc = 0; cc < BN / CH; ++cc) {
         const int64_t col0 = n0 + cc * CH;
         if (col0 >= p.N || p.debug == 2) break; // warp-uniform
-        // The extra operand's 128-byte row segment is fetched first so that it is in flight
-        // while the accumulator is read.
-        uint4 ev[sizeof(TC) == 2 && !PLAIN ? CH / 8 : 1] = {};
+        // row of the extra operand this thread combines with (its own output row)
+        const TC *erow = nullptr;
         if constexpr (!PLAIN && sizeof(TC) == 2) {
           if (p.extraOp && p.debug != 3) {
-            const int64_t row = m0 + quarter * 32 + lane;
-            const TC *erow = static_cast<const TC *>(p.extra) + row * p.N + col0;
-#pragma unroll
-            for (int g = 0; g < CH / 8; ++g) {
-              ev[g] = (row < p.M && col0 + g * 8 < p.N) ? __ldg(reinterpret_cast<const uint4 *>(erow + g * 8))
-                                                       : make_uint4(0, 0, 0, 0);
+            int64_t row = m0 + quarter * 32 + lane;
+            bool rowOk = row < p.M;
+            if (p.cTw) {
+              const int oy = pOy + lane / p.cTw, ox = pOx + lane % p.cTw;
+              rowOk = oy < p.cHo && ox < p.cWo;
+              row = (static_cast<int64_t>(pImg) * p.cHo + oy) * p.cWo + ox;
             }
+            if (rowOk) erow = static_cast<const TC *>(p.extra) + row * p.N + col0;
           }
         }
-        uint32_t r[CH];
+        const uint32_t buf = stageOut + (EPW == 4 ? (chunkIt & 1u) * 4096u : 0u);
+        const uint32_t rowAddr = buf + static_cast<uint32_t>(lane) * 128u;
+        // The chunk is worked through in passes of 32 columns (64 or 128 bytes of the output row),
+        // which keeps the registers of a pass small enough for two epilogue warps per scheduler.
 #pragma unroll
         for (int l = 0; l < NLD; ++l) {
-          tcLoad32(taddrRow + static_cast<uint32_t>(cc * CH + l * 32), *reinterpret_cast<uint32_t(*)[32]>(&r[l * 32]));
-        }
-        tcWaitLd();
-        if (p.debug == 1) {
-          if (r[0] == 0x7fc12345u && r[CH - 1] == 0x7fc54321u) c[0] = TC(0); // keeps the loads alive
-          continue;
-        }
-        if constexpr (!PLAIN) {
-          // Whole-chunk passes keep each activation's code in one straight run (a per-element
-          // switch would interleave all of them and thrash the instruction cache).
-          // bias of this chunk's columns: lane l holds columns l, l + 32, ...; broadcast by shuffle
-          float biasReg[NLD];
+          constexpr int HW = 32;
+          const int64_t colH = col0 + l * HW;
+          // extra operand and bias of this pass first, so that they are in flight while TMEM is read
+          uint4 ev[sizeof(TC) == 2 && !PLAIN ? HW / 8 : 1] = {};
+          float biasReg = 0.0f;
+          if constexpr (!PLAIN) {
+            if constexpr (sizeof(TC) == 2) {
+              if (erow) {
 #pragma unroll
-          for (int l = 0; l < NLD; ++l) {
-            const int64_t col = col0 + l * 32 + lane;
-            biasReg[l] = (p.bias && col < p.N) ? loadBias(p.bias, p.biasDt, col) : 0.0f;
-          }
-          const bool hasBias = p.bias != nullptr, round1 = (p.roundSteps & 1) != 0, round2 = (p.roundSteps & 2) != 0;
-#pragma unroll
-          for (int e = 0; e < CH; ++e) {
-            float f = __uint_as_float(r[e]);
-            float bz = __shfl_sync(0xffffffffu, biasReg[e / 32], e & 31);
-            if (round1) f = toF32(fromF32<TC>(f));
-            if (hasBias) f = __fadd_rn(f, bz);
-            if (hasBias && round2) f = toF32(fromF32<TC>(f));
-            r[e] = __float_as_uint(f);
-          }
-          switch (p.act) {
-          case TTB_ACT_RELU:
-#pragma unroll
-            for (int e = 0; e < CH; ++e) { float f = __uint_as_float(r[e]); r[e] = __float_as_uint(f > 0.0f ? f : (f != f ? f : 0.0f)); }
-            break;
-          case TTB_ACT_SILU:
-#pragma unroll
-            for (int e = 0; e < CH; ++e) { float f = __uint_as_float(r[e]); r[e] = __float_as_uint(f / (1.0f + expf(-f))); }
-            break;
-          case TTB_ACT_GELU:
-#pragma unroll
-            for (int e = 0; e < CH; ++e) { float f = __uint_as_float(r[e]); r[e] = __float_as_uint(applyAct(TTB_ACT_GELU, f)); }
-            break;
-          case TTB_ACT_SIGMOID:
-#pragma unroll
-            for (int e = 0; e < CH; ++e) { float f = __uint_as_float(r[e]); r[e] = __float_as_uint(1.0f / (1.0f + expf(-f))); }
-            break;
-          default: break;
-          }
-          if constexpr (sizeof(TC) == 2) {
-            // A separate op consumed the (rounded) result of the chain so far.
-            if (p.extraOp == TTB_EXTRA_ADD) {
-#pragma unroll
-              for (int e = 0; e < CH; ++e) {
-                const TC *x = reinterpret_cast<const TC *>(&ev[e / 8]) + (e & 7);
-                r[e] = __float_as_uint(__fadd_rn(toF32(fromF32<TC>(__uint_as_float(r[e]))), toF32(*x)));
-              }
-            } else if (p.extraOp == TTB_EXTRA_SILU_MUL) {
-#pragma unroll
-              for (int e = 0; e < CH; ++e) {
-                const TC *x = reinterpret_cast<const TC *>(&ev[e / 8]) + (e & 7);
-                const float g = toF32(*x);
-                const float sg = toF32(fromF32<TC>(__fdividef(g, 1.0f + __expf(-g))));
-                r[e] = __float_as_uint(__fmul_rn(sg, toF32(fromF32<TC>(__uint_as_float(r[e])))));
+                for (int g = 0; g < HW / 8; ++g) {
+                  if (colH + g * 8 < p.N) ev[g] = __ldg(reinterpret_cast<const uint4 *>(erow + l * HW + g * 8));
+                }
               }
             }
+            if (p.bias && colH + lane < p.N) biasReg = loadBias(p.bias, p.biasDt, colH + lane);
+          }
+          uint32_t r[HW];
+          tcLoad32(taddrRow + static_cast<uint32_t>(cc * CH + l * HW), r);
+          tcWaitLd();
+          if (p.debug == 1) {
+            if (r[0] == 0x7fc12345u && r[HW - 1] == 0x7fc54321u) c[0] = TC(0); // keeps the loads alive
+            continue;
+          }
+          if constexpr (!PLAIN) {
+            // One straight-line pass per case: runtime flags inside the unrolled loop would put
+            // every variant's instructions on every element, and a per-element switch over the
+            // activations would thrash the instruction cache.
+            const bool hasBias = p.bias != nullptr, round1 = (p.roundSteps & 1) != 0, round2 = (p.roundSteps & 2) != 0;
+            if (hasBias && !round1 && !round2) {
+#pragma unroll
+              for (int e = 0; e < HW; ++e) {
+                const float bz = __shfl_sync(0xffffffffu, biasReg, e); // lane e holds column e's bias
+                r[e] = __float_as_uint(__fadd_rn(__uint_as_float(r[e]), bz));
+              }
+            } else if (hasBias) {
+#pragma unroll
+              for (int e = 0; e < HW; ++e) {
+                float f = __uint_as_float(r[e]);
+                const float bz = __shfl_sync(0xffffffffu, biasReg, e);
+                if (round1) f = toF32(fromF32<TC>(f));
+                f = __fadd_rn(f, bz);
+                if (round2) f = toF32(fromF32<TC>(f));
+                r[e] = __float_as_uint(f);
+              }
+            } else if (round1) {
+#pragma unroll
+              for (int e = 0; e < HW; ++e) r[e] = __float_as_uint(toF32(fromF32<TC>(__uint_as_float(r[e]))));
+            }
+            switch (reluPacked ? TTB_ACT_NONE : p.act) {
+            case TTB_ACT_RELU:
+#pragma unroll
+              for (int e = 0; e < HW; ++e) { float f = __uint_as_float(r[e]); r[e] = __float_as_uint(f < 0.0f ? 0.0f : f); } // NaN stays NaN
+              break;
+            case TTB_ACT_SILU:
+#pragma unroll
+              for (int e = 0; e < HW; ++e) { float f = __uint_as_float(r[e]); r[e] = __float_as_uint(f / (1.0f + expf(-f))); }
+              break;
+            case TTB_ACT_GELU:
+#pragma unroll
+              for (int e = 0; e < HW; ++e) { float f = __uint_as_float(r[e]); r[e] = __float_as_uint(applyAct(TTB_ACT_GELU, f)); }
+              break;
+            case TTB_ACT_SIGMOID:
+#pragma unroll
+              for (int e = 0; e < HW; ++e) { float f = __uint_as_float(r[e]); r[e] = __float_as_uint(1.0f / (1.0f + expf(-f))); }
+              break;
+            default: break;
+            }
+            if constexpr (sizeof(TC) == 2) {
+              // A separate op consumed the (rounded) result of the chain so far.
+              if (p.extraOp == TTB_EXTRA_ADD || p.extraOp == TTB_EXTRA_ADD_RELU) {
+                const bool relu = p.extraOp == TTB_EXTRA_ADD_RELU;
+#pragma unroll
+                for (int e = 0; e < HW; ++e) {
+                  const TC *x = reinterpret_cast<const TC *>(&ev[e / 8]) + (e & 7);
+                  float f = __fadd_rn(toF32(fromF32<TC>(__uint_as_float(r[e]))), toF32(*x));
+                  if (relu) f = f < 0.0f ? 0.0f : f;
+                  r[e] = __float_as_uint(f);
+                }
+              } else if (p.extraOp == TTB_EXTRA_SILU_MUL) {
+#pragma unroll
+                for (int e = 0; e < HW; ++e) {
+                  const TC *x = reinterpret_cast<const TC *>(&ev[e / 8]) + (e & 7);
+                  const float g = toF32(*x);
+                  const float sg = toF32(fromF32<TC>(__fdividef(g, 1.0f + __expf(-g))));
+                  r[e] = __float_as_uint(__fmul_rn(sg, toF32(fromF32<TC>(__uint_as_float(r[e])))));
+                }
+              }
+            }
+          }
+          if (l == 0) {
+            // the staging buffer is free once the bulk store issued from it has read it
+            if (lane == 0) {
+              if (EPW == 4) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+              else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            }
+            __syncwarp();
+          }
+          constexpr int PIECES = HW * static_cast<int>(sizeof(TC)) / 16; // 16-byte pieces of this pass
+#pragma unroll
+          for (int v = 0; v < PIECES; ++v) {
+            uint32_t w[4];
+            if constexpr (sizeof(TC) == 2) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int e = v * 8 + q * 2;
+                w[q] = pack2<TC>(__uint_as_float(r[e]), __uint_as_float(r[e + 1])); // one cvt.rn for the pair
+                if constexpr (!PLAIN) {
+                  if (reluPacked) w[q] = relu2<TC>(w[q]);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) w[q] = r[v * 4 + q];
+            }
+            // 128-byte swizzle (what the tensor map of C expects): 16-byte piece i of row `lane`
+            // lives at piece i ^ (lane % 8); this also spreads the lanes over the banks
+            const int pieceIdx = l * PIECES + v;
+            const uint32_t addr = rowAddr + (static_cast<uint32_t>(pieceIdx ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
           }
         }
-        const uint32_t buf = stageOut + (chunkIt & 1u) * 4096u;
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); // buffer free again
-        __syncwarp();
-        const uint32_t rowAddr = buf + static_cast<uint32_t>(lane) * 128u;
-#pragma unroll
-        for (int v = 0; v < 8; ++v) { // eight 16-byte pieces of this lane's 128-byte row
-          uint32_t w[4];
-          if constexpr (sizeof(TC) == 2) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int e = v * 8 + q * 2;
-              float f0 = __uint_as_float(r[e]), f1 = __uint_as_float(r[e + 1]);
-              w[q] = pack2<TC>(f0, f1); // one cvt.rn for the pair
-            }
-          } else {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int e = v * 4 + q;
-              float f0 = __uint_as_float(r[e]);
-              w[q] = __float_as_uint(f0);
-            }
-          }
-          // 128-byte swizzle (what the tensor map of C expects): 16-byte piece v of row `lane`
-          // lives at piece v ^ (lane % 8); this also spreads the lanes over the banks
-          const uint32_t addr = rowAddr + (static_cast<uint32_t>(v ^ (lane & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
-        }
+        if (p.debug == 1) continue;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
-          asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                       ::"l"(reinterpret_cast<uint64_t>(&mapC)), "r"(buf), "r"(static_cast<int>(col0)),
-                         "r"(static_cast<int>(m0 + quarter * 32)) : "memory");
+          if (p.cTw) {
+            asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                         ::"l"(reinterpret_cast<uint64_t>(&mapC)), "r"(buf), "r"(static_cast<int>(col0)), "r"(pOx), "r"(pOy),
+                           "r"(pImg) : "memory");
+          } else {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                         ::"l"(reinterpret_cast<uint64_t>(&mapC)), "r"(buf), "r"(static_cast<int>(col0)),
+                           "r"(static_cast<int>(m0 + quarter * 32)) : "memory");
+          }
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
         ++chunkIt;
@@ -388,6 +561,24 @@ static bool makeMap(CUtensorMap *map, const void *ptr, int dtype, int64_t rows, 
   return r == CUDA_SUCCESS;
 }
 
+// NHWC tensor [n, h, w, c] of a 16-bit type as a 4-D map {c, w, h, n}; box = boxC channels (128
+// bytes) x boxW x boxH pixels of one image, 128-byte swizzle, zero fill outside.
+static bool makeMap4(CUtensorMap *map, const void *ptr, int dtype, int64_t c, int64_t w, int64_t h, int64_t n, int boxC,
+                     int boxW, int boxH) {
+  EncodeTiledFn fn = encodeTiled();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(c), static_cast<cuuint64_t>(w), static_cast<cuuint64_t>(h),
+                        static_cast<cuuint64_t>(n)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(c) * 2, static_cast<cuuint64_t>(w) * c * 2,
+                           static_cast<cuuint64_t>(h) * w * c * 2};
+  cuuint32_t box[4] = {static_cast<cuuint32_t>(boxC), static_cast<cuuint32_t>(boxW), static_cast<cuuint32_t>(boxH), 1};
+  cuuint32_t elemStrides[4] = {1, 1, 1, 1};
+  CUtensorMapDataType dt = dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = fn(map, dt, 4, const_cast<void *>(ptr), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 template <int BN, typename TC, bool PLAIN>
 static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &me, void *c, const TcParams &p,
                     cudaStream_t st) {
@@ -400,9 +591,9 @@ static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensor
     TTB_CUDA(cudaFuncSetAttribute(gemmTcgen05Kernel<BN, TC, PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
     attrSet[dev] = true;
   }
-  int64_t tiles = ((p.M + TC_BM - 1) / TC_BM) * ((p.N + BN - 1) / BN);
+  int64_t tiles = (p.cTw ? p.cTilesM : (p.M + TC_BM - 1) / TC_BM) * ((p.N + BN - 1) / BN);
   int grid = static_cast<int>(tiles < smCount() ? tiles : smCount());
-  gemmTcgen05Kernel<BN, TC, PLAIN><<<grid, TC_THREADS, Cfg::kSmem, st>>>(ma, mb, mc, me, static_cast<TC *>(c), p);
+  gemmTcgen05Kernel<BN, TC, PLAIN><<<grid, PLAIN ? TC_THREADS : TC_THREADS_EPI8, Cfg::kSmem, st>>>(ma, mb, mc, me, static_cast<TC *>(c), p);
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;
@@ -453,6 +644,9 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   p.bias = bias; p.biasDt = biasDtype; p.act = act; p.roundSteps = roundSteps;
   p.extra = extraOp ? extra : nullptr;
   p.extraOp = extra ? extraOp : 0;
+  p.convX = nullptr;
+  p.cTw = 0;
+  p.cTilesM = 0;
   p.fmt = abDtype == kBF16 ? 1 : 0;
   {
     const char *dbg = std::getenv("TTB_TC_DEBUG");
@@ -475,6 +669,92 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   TTB_TC_BN(float)
 #undef TTB_TC_BN
 #undef TTB_TC
+}
+
+// Convolution as an implicit GEMM on the same kernel: the producer warp gathers the receptive
+// fields (see the kernel), `wre` is the weight reordered to [O, kH, kW, C].  Returns -1 when the
+// problem is outside what this path takes (the caller then materialises the im2col operand).
+int convTcgen05Try(const void *x, const void *wre, const void *bias, void *out, int dtype, int biasDtype, int64_t n,
+                   int64_t h, int64_t w, int64_t c, int64_t o, int64_t ho, int64_t wo, int kh, int kw, int sh, int sw,
+                   int pt, int pl, int dh, int dw, int act, const void *extra, int extraOp, cudaStream_t stream) {
+  if (dtype != kBF16 && dtype != kF16) return -1;
+  if (c % TC_BK != 0 || o < 8 || (o * 2) % 16 != 0) return -1;
+  if (!aligned16(x) || !aligned16(wre) || !aligned16(out) || (extraOp && (!extra || !aligned16(extra)))) return -1;
+  const int64_t m = n * ho * wo, k = static_cast<int64_t>(kh) * kw * c;
+  if (m < 1 || m > 0x7fffffff || k > 0x7fffffff || h > 32767 || w > 32767 || pt > 8192 || pl > 8192 || pt < 0 || pl < 0) return -1;
+  if (n * h * w * c > 0x7fffffff) return -1; // element offsets are kept in 32 bits
+  int bn = 64;
+  {
+    int64_t best = -1;
+    for (int wd : {256, 128, 64}) {
+      if (wd > 64 && o < wd) continue;
+      int64_t tiles = ((m + TC_BM - 1) / TC_BM) * ((o + wd - 1) / wd);
+      int64_t waves = (tiles + smCount() - 1) / smCount();
+      int64_t cost = waves * (wd + 64);
+      if (best < 0 || cost < best) {
+        best = cost;
+        bn = wd;
+      }
+    }
+  }
+  // Stride-1 convolutions run in patch mode; the patch width is the divisor of 32 that wastes
+  // the fewest rows on ragged image edges.
+  int tw = 0;
+  int64_t tilesX = 0, tilesY = 0;
+  if (sh == 1 && sw == 1) {
+    int64_t best = -1;
+    for (int cand : {8, 16, 32, 4}) {
+      int64_t tx = (wo + cand - 1) / cand, ty = (ho + (TC_BM / cand) - 1) / (TC_BM / cand);
+      if (best < 0 || tx * ty < best) {
+        best = tx * ty;
+        tw = cand;
+        tilesX = tx;
+        tilesY = ty;
+      }
+    }
+    if (n * tilesX * tilesY > 0x7fffffff) tw = 0;
+  }
+  CUtensorMap ma, mb, mc, me;
+  if (!makeMap(&mb, wre, dtype, o, k, bn)) return -1;
+  if (tw) {
+    if (!makeMap4(&ma, x, dtype, c, w, h, n, TC_BK, tw, TC_BM / tw) || !makeMap4(&mc, out, dtype, o, wo, ho, n, 64, tw, 32 / tw))
+      return -1;
+  } else {
+    ma = mb; // not used: the producer warp gathers A
+    if (!makeMap(&mc, out, dtype, m, o, 32)) return -1;
+  }
+  if (extraOp) {
+    if (!makeMap(&me, extra, dtype, m, o, 32)) return -1;
+  } else {
+    me = mc;
+  }
+  TcParams p;
+  p.M = m; p.N = o; p.K = k;
+  p.bias = bias; p.biasDt = biasDtype; p.act = act; p.roundSteps = 0;
+  p.extra = extraOp ? extra : nullptr;
+  p.extraOp = extra ? extraOp : 0;
+  p.convX = x;
+  p.cH = static_cast<int>(h); p.cW = static_cast<int>(w); p.cC = static_cast<int>(c);
+  p.cHo = static_cast<int>(ho); p.cWo = static_cast<int>(wo);
+  p.ckw = kw; p.csh = sh; p.csw = sw; p.cpt = pt; p.cpl = pl; p.cdh = dh; p.cdw = dw;
+  p.cTw = tw; p.cTilesX = static_cast<int>(tilesX); p.cTilesY = static_cast<int>(tilesY);
+  p.cTilesM = tw ? n * tilesX * tilesY : 0;
+  p.fmt = dtype == kBF16 ? 1 : 0;
+  p.debug = 0;
+  // algorithmic bytes: the input and the output once each (plus the residual operand), the weights
+  ProfScope prof("conv2d_tcgen05", 2.0 * double(m) * o * k,
+                 (double(n) * h * w * c + double(o) * k + double(m) * o * (extraOp ? 2 : 1)) * 2, stream);
+#define TTB_CONV(BNv, TCv) return launchTc<BNv, TCv, false>(ma, mb, mc, me, out, p, stream)
+#define TTB_CONV_BN(TCv)                                                                 \
+  switch (bn) {                                                                          \
+  case 256: TTB_CONV(256, TCv);                                                          \
+  case 128: TTB_CONV(128, TCv);                                                          \
+  default: TTB_CONV(64, TCv);                                                            \
+  }
+  if (dtype == kBF16) { TTB_CONV_BN(__nv_bfloat16) }
+  TTB_CONV_BN(__half)
+#undef TTB_CONV_BN
+#undef TTB_CONV
 }
 
 } // namespace ttb

@@ -363,7 +363,9 @@ private:
   void runQuantization(const fbt::EltwiseQuantizationOp *op);
   void runGemm(const fbt::TensorRef *a, const fbt::TensorRef *b, const fbt::TensorRef *bias, const fbt::TensorRef *out,
                bool ta, bool tb, int act, int roundSteps, const fbt::TensorRef *extra = nullptr, int extraOp = 0);
-  void runConv2d(const fbt::Conv2dOp *op);
+  void runConv2d(const fbt::Conv2dOp *op, int act = 0, const fbt::TensorRef *extra = nullptr, int extraOp = 0,
+                 const fbt::TensorRef *outRef = nullptr);
+  size_t tryConvEpilogue(size_t i);
   void runSoftmax(const fbt::SoftmaxOp *op);
   void runRmsNorm(const fbt::RMSNormOp *op);
   void runReduction(const fbt::ReductionOp *op);
@@ -579,6 +581,7 @@ size_t Executor::runOp(size_t i) {
     case OpType::EltwiseBinaryOp: used = tryAddRmsNorm(i); break;
     case OpType::ScaledDotProductAttentionOp: used = trySdpa(i); break;
     case OpType::AllReduceOp: used = tryAllReduceAdd(i); break;
+    case OpType::Conv2dOp: used = tryConvEpilogue(i); break;
     default: break;
     }
     if (used) return used;
@@ -1264,10 +1267,14 @@ size_t Executor::tryGemmEpilogue(size_t i) {
   return consumedUpTo + 1 - i;
 }
 
-void Executor::runConv2d(const fbt::Conv2dOp *op) {
+void Executor::runConv2d(const fbt::Conv2dOp *op, int act, const fbt::TensorRef *extraRef, int extraOp,
+                         const fbt::TensorRef *outRef) {
+  if (!outRef) outRef = op->out();
   TensorPtr x = getDevice(op->input()), w = getDevice(op->weight());
   TensorPtr bias = op->bias() ? getDevice(op->bias()) : nullptr;
-  TensorPtr out = allocOut(op->out());
+  TensorPtr extra = extraRef ? getDevice(extraRef) : nullptr;
+  TensorPtr out = allocOut(outRef);
+  if (extra) TTRT_ASSERT(extra->volume() == out->volume() && extra->dtype == out->dtype, "fused epilogue operand must match the result");
   auto two = [](const fb::Vector<int32_t> *v, const char *what, int &a, int &b) {
     TTRT_ASSERT(v && v->size() == 2, "conv2d ", what, " must have 2 entries");
     a = v->Get(0);
@@ -1293,12 +1300,81 @@ void Executor::runConv2d(const fbt::Conv2dOp *op) {
   size_t wsBytes = ttb_conv2d_workspace_bytes(ttbDtype(x->dtype), N, H, W, C, O, kh, kw, sh, sw, pad, dh, dw, groups);
   TensorPtr ws = wsBytes ? makeDeviceTensor(dev, {static_cast<uint32_t>((wsBytes + 3) / 4)}, DataType::UInt32) : nullptr;
   eachRank([&](size_t i, const RankCtx &r) {
-    TTB_CALL(ttb_conv2d(x->shards[i]->ptr, w->shards[i]->ptr, bias ? bias->shards[i]->ptr : nullptr, out->shards[i]->ptr,
-                        ttbDtype(x->dtype), bias ? ttbDtype(bias->dtype) : 0, N, H, W, C, O, kh, kw, sh, sw, pad, dh, dw,
-                        groups, TTB_ACT_NONE, ws ? ws->shards[i]->ptr : nullptr, r.stream));
+    TTB_CALL(ttb_conv2d_fused(x->shards[i]->ptr, w->shards[i]->ptr, bias ? bias->shards[i]->ptr : nullptr, out->shards[i]->ptr,
+                              ttbDtype(x->dtype), bias ? ttbDtype(bias->dtype) : 0, N, H, W, C, O, kh, kw, sh, sw, pad, dh, dw,
+                              groups, act, extra ? extra->shards[i]->ptr : nullptr, extra ? extraOp : TTB_EXTRA_NONE,
+                              ws ? ws->shards[i]->ptr : nullptr, r.stream));
   });
-  put(op->out(), out);
+  put(outRef, out);
 }
+
+// conv2d [-> relu], or conv2d -> add(tensor) [-> relu] (a residual branch), intermediates
+// single-use.  relu commutes with the rounding of the op before it, so the fused launch gives
+// the same bits as the chain.
+size_t Executor::tryConvEpilogue(size_t i) {
+  const auto *ops = prog->operations();
+  const auto *op = ops->Get(static_cast<uint32_t>(i))->type_as_Conv2dOp();
+  const fbt::TensorRef *cur = op->out();
+  DataType dt = refDtype(cur);
+  if (!singleUse(cur)) return 0;
+  std::vector<const fbt::Operation *> deallocs;
+  size_t next = i + 1, consumedUpTo = i;
+  int act = TTB_ACT_NONE, extraOp = TTB_EXTRA_NONE;
+  const fbt::TensorRef *extra = nullptr;
+  auto reluOf = [&](const fbt::Operation *nop) -> const fbt::EltwiseUnaryOp * {
+    if (!nop || nop->type_type() != OpType::EltwiseUnaryOp) return nullptr;
+    const auto *u = nop->type_as_EltwiseUnaryOp();
+    if (u->type() != fbt::EltwiseUnaryOpType::Relu || u->in()->global_id() != cur->global_id() ||
+        refShape(u->out()) != refShape(cur) || refDtype(u->out()) != dt)
+      return nullptr;
+    return u;
+  };
+  {
+    std::vector<const fbt::Operation *> d2;
+    size_t j = next;
+    const auto *nop = peek(j, d2);
+    if (const auto *u = reluOf(nop)) {
+      act = TTB_ACT_RELU;
+      cur = u->out();
+      deallocs.insert(deallocs.end(), d2.begin(), d2.end());
+      next = j + 1;
+      consumedUpTo = j;
+    } else if (nop && nop->type_type() == OpType::EltwiseBinaryOp && (dt == DataType::BFloat16 || dt == DataType::Float16)) {
+      const auto *add = nop->type_as_EltwiseBinaryOp();
+      const fbt::TensorRef *other = nullptr;
+      if (add->type() == fbt::EltwiseBinaryOpType::Add) {
+        if (add->lhs()->global_id() == cur->global_id()) other = add->rhs();
+        else if (add->rhs()->global_id() == cur->global_id()) other = add->lhs();
+      }
+      if (other && other->global_id() != cur->global_id() && refShape(other) == refShape(cur) && refDtype(other) == dt &&
+          pool.count(other->global_id()) && refShape(add->out()) == refShape(cur) && refDtype(add->out()) == dt) {
+        extra = other;
+        extraOp = TTB_EXTRA_ADD;
+        cur = add->out();
+        deallocs.insert(deallocs.end(), d2.begin(), d2.end());
+        next = j + 1;
+        consumedUpTo = j;
+        if (singleUse(cur)) {
+          std::vector<const fbt::Operation *> d3;
+          size_t j2 = next;
+          const auto *rop = peek(j2, d3);
+          if (const auto *u = reluOf(rop)) {
+            extraOp = TTB_EXTRA_ADD_RELU;
+            cur = u->out();
+            deallocs.insert(deallocs.end(), d3.begin(), d3.end());
+            next = j2 + 1;
+            consumedUpTo = j2;
+          }
+        }
+      }
+    }
+  }
+  if (consumedUpTo == i) return 0;
+  runConv2d(op, act, extra, extraOp, cur);
+  runDeallocs(deallocs);
+  return consumedUpTo + 1 - i;
+}
+
 
 // ---- normalisation / reduction ----------------------------------------------------------------------------
 void Executor::runSoftmax(const fbt::SoftmaxOp *op) {

@@ -118,6 +118,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
   auto emptyBar = [&](int s) { return barBase + 8u * (STAGES + s); };
   auto tmemFullBar = [&](int a) { return barBase + 8u * (2 * STAGES + a); };
   auto tmemEmptyBar = [&](int a) { return barBase + 8u * (2 * STAGES + 2 + a); };
+  auto extraBar = [&](int w) { return barBase + 8u * (2 * STAGES + 4 + w); }; // one per epilogue warp
   __shared__ uint32_t tmemBaseSlot;
   __shared__ int abortFlagS;
   volatile int *abortFlag = &abortFlagS;
@@ -137,6 +138,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
       mbarInit(tmemFullBar(a), 1);
       mbarInit(tmemEmptyBar(a), 128);
     }
+    for (int w = 0; w < 8; ++w) mbarInit(extraBar(w), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetchTensorMap(&mapA);
     prefetchTensorMap(&mapB);
@@ -307,28 +309,13 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     // scheduler hide each other's instruction latencies in the longer epilogues.
     const int group = (warp - 2) / 4;
     const uint32_t stageOut = outBase + static_cast<uint32_t>(warp - 2) * (EPW == 4 ? 2u : 1u) * 4096u;
-    uint32_t accIt = static_cast<uint32_t>(group), chunkIt = 0;
+    uint32_t accIt = static_cast<uint32_t>(group), chunkIt = 0, extraPhase = 0;
+    bool alive = true;
     const int64_t tileStep = static_cast<int64_t>(gridDim.x) * (EPW / 4);
-    // The extra operand is read row by row (one 128-byte segment per thread and chunk), which
-    // would expose DRAM latency in every chunk.  Its 32-row x CH-column blocks are therefore
-    // pulled into L2 one whole tile ahead: lanes 0 .. BN/CH-1 prefetch one block each.
-    auto prefetchExtra = [&](int64_t t) {
-      if constexpr (!PLAIN && sizeof(TC) == 2) {
-        if (p.extraOp && !p.cTw && lane < BN / CH && t < numTiles) {
-          const int64_t col = (t / tilesM) * BN + lane * CH, row = (t % tilesM) * TC_BM + quarter * 32;
-          if (col < p.N && row < p.M) {
-            asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
-                         ::"l"(reinterpret_cast<uint64_t>(&mapE)), "r"(static_cast<int>(col)), "r"(static_cast<int>(row)) : "memory");
-          }
-        }
-      }
-    };
-    prefetchExtra(blockIdx.x + static_cast<int64_t>(group) * gridDim.x);
     for (int64_t tile = blockIdx.x + static_cast<int64_t>(group) * gridDim.x; tile < numTiles;
          tile += tileStep, accIt += EPW / 4) {
       const int acc = accIt & 1;
       const uint32_t accPhase = (accIt >> 1) & 1u;
-      prefetchExtra(tile + tileStep);
       if (!mbarWait(tmemFullBar(acc), accPhase, abortFlag, 4)) break;
       tcFenceAfter();
       const int64_t m0 = (tile % tilesM) * TC_BM, n0 = (tile / tilesM) * BN;
@@ -345,40 +332,32 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
       for (int cc = 0; cc < BN / CH; ++cc) {
         const int64_t col0 = n0 + cc * CH;
         if (col0 >= p.N || p.debug == 2) break; // warp-uniform
-        // row of the extra operand this thread combines with (its own output row)
-        const TC *erow = nullptr;
-        if constexpr (!PLAIN && sizeof(TC) == 2) {
-          if (p.extraOp && p.debug != 3) {
-            int64_t row = m0 + quarter * 32 + lane;
-            bool rowOk = row < p.M;
-            if (p.cTw) {
-              const int oy = pOy + lane / p.cTw, ox = pOx + lane % p.cTw;
-              rowOk = oy < p.cHo && ox < p.cWo;
-              row = (static_cast<int64_t>(pImg) * p.cHo + oy) * p.cWo + ox;
-            }
-            if (rowOk) erow = static_cast<const TC *>(p.extra) + row * p.N + col0;
-          }
-        }
         const uint32_t buf = stageOut + (EPW == 4 ? (chunkIt & 1u) * 4096u : 0u);
         const uint32_t rowAddr = buf + static_cast<uint32_t>(lane) * 128u;
+        // The second operand's 32 x 128 B block is brought into the staging buffer by TMA (the
+        // layout the result will have), combined in place, and stored from there.
+        bool useExtra = false;
+        if constexpr (!PLAIN && sizeof(TC) == 2) {
+          useExtra = p.extraOp != 0;
+          if (useExtra) {
+            if (lane == 0) {
+              asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); // the last store has read the buffer
+              mbarArriveExpectTx(extraBar(warp - 2), 4096);
+              if (p.cTw) tmaLoad4d(buf, &mapE, extraBar(warp - 2), static_cast<int>(col0), pOx, pOy, pImg);
+              else tmaLoad2d(buf, &mapE, extraBar(warp - 2), static_cast<int>(col0), static_cast<int>(m0 + quarter * 32));
+            }
+            __syncwarp();
+          }
+        }
         // The chunk is worked through in passes of 32 columns (64 or 128 bytes of the output row),
         // which keeps the registers of a pass small enough for two epilogue warps per scheduler.
 #pragma unroll
         for (int l = 0; l < NLD; ++l) {
           constexpr int HW = 32;
           const int64_t colH = col0 + l * HW;
-          // extra operand and bias of this pass first, so that they are in flight while TMEM is read
-          uint4 ev[sizeof(TC) == 2 && !PLAIN ? HW / 8 : 1] = {};
+          // bias of this pass first, so that it is in flight while TMEM is read
           float biasReg = 0.0f;
           if constexpr (!PLAIN) {
-            if constexpr (sizeof(TC) == 2) {
-              if (erow) {
-#pragma unroll
-                for (int g = 0; g < HW / 8; ++g) {
-                  if (colH + g * 8 < p.N) ev[g] = __ldg(reinterpret_cast<const uint4 *>(erow + l * HW + g * 8));
-                }
-              }
-            }
             if (p.bias && colH + lane < p.N) biasReg = loadBias(p.bias, p.biasDt, colH + lane);
           }
           uint32_t r[HW];
@@ -387,6 +366,19 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
           if (p.debug == 1) {
             if (r[0] == 0x7fc12345u && r[HW - 1] == 0x7fc54321u) c[0] = TC(0); // keeps the loads alive
             continue;
+          }
+          uint4 ev[sizeof(TC) == 2 && !PLAIN ? HW / 8 : 1] = {};
+          if constexpr (!PLAIN && sizeof(TC) == 2) {
+            if (useExtra) {
+              if (l == 0) {
+                if (!__all_sync(0xffffffffu, mbarWait(extraBar(warp - 2), extraPhase, abortFlag, 5))) { alive = false; break; }
+              }
+#pragma unroll
+              for (int g = 0; g < HW / 8; ++g) {
+                const uint32_t addr = rowAddr + (static_cast<uint32_t>((l * (HW / 8) + g) ^ (lane & 7)) << 4);
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(ev[g].x), "=r"(ev[g].y), "=r"(ev[g].z), "=r"(ev[g].w) : "r"(addr) : "memory");
+              }
+            }
           }
           if constexpr (!PLAIN) {
             // One straight-line pass per case: runtime flags inside the unrolled loop would put
@@ -454,7 +446,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
               }
             }
           }
-          if (l == 0) {
+          if (l == 0 && !useExtra) {
             // the staging buffer is free once the bulk store issued from it has read it
             if (lane == 0) {
               if (EPW == 4) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
@@ -486,6 +478,8 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
           }
         }
+        if (!alive) break;
+        if (useExtra) extraPhase ^= 1u;
         if (p.debug == 1) continue;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
@@ -503,6 +497,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
         }
         ++chunkIt;
       }
+      if (!alive) break;
       tcFenceBefore();
       mbarArrive(tmemEmptyBar(acc)); // all 128 epilogue threads arrive: the accumulator may be overwritten
     }
@@ -724,7 +719,7 @@ int convTcgen05Try(const void *x, const void *wre, const void *bias, void *out, 
     if (!makeMap(&mc, out, dtype, m, o, 32)) return -1;
   }
   if (extraOp) {
-    if (!makeMap(&me, extra, dtype, m, o, 32)) return -1;
+    if (tw ? !makeMap4(&me, extra, dtype, o, wo, ho, n, 64, tw, 32 / tw) : !makeMap(&me, extra, dtype, m, o, 32)) return -1;
   } else {
     me = mc;
   }

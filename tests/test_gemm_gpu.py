@@ -131,3 +131,21 @@ def test_gemm_fused_extra_operand(rt, device, extra_op, m, n, k, with_bias):
         s = torch.nn.functional.silu(extra.float()).to(torch.bfloat16).float()
         want = (s * r).to(torch.bfloat16)
     assert_matches(got, want, f"gemm_fused op={extra_op} {m}x{n}x{k}")
+
+
+def test_pointwise_conv_shape_bias_relu(rt, device):
+    """The memory-bound shape of config 5's 1x1 convolutions (every pixel of [64,56,56,64] times a
+    [256,64] weight) with the bias + relu epilogue, against an f32 reference."""
+    m, n, k = 200704, 256, 64
+    torch.manual_seed(3)
+    a = torch.randn(m, k).to(torch.bfloat16)
+    b = (torch.randn(n, k) * 0.1).to(torch.bfloat16)
+    bias = torch.randn(n).to(torch.bfloat16)
+    h = KernelHarness(rt)
+    try:
+        got = run_gemm(h, h.lib.ttb_gemm, a, b, bias, m, n, k, ACT["relu"], 0)
+        assert tc_status(h) == 0
+    finally:
+        h.close()
+    want = torch.relu(a.float() @ b.float().t() + bias.float()).to(torch.bfloat16)
+    assert_matches(got, want, "pointwise conv shape")

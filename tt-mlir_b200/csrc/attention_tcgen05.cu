@@ -6,10 +6,12 @@
 // One CTA owns 128 query rows of one head and walks the key/value sequence in tiles of 128:
 //   warp 0      TMA producer: Q once, then K and V tiles through two-stage rings
 //   warp 1      issues tcgen05.mma: S = Q K^T into one of two TMEM buffers, then O += P V
-//   warps 2..5  one query row per thread: read S from TMEM, online softmax in f32, write the
-//               probabilities P (16-bit) into shared memory in the operand layout of the second
-//               contraction; O stays in TMEM and is rescaled there only when the row maximum
-//               has grown by more than a factor 2^8 since the last rescale
+//   warps 2..9  two threads per query row (one takes keys 0..63 of a tile, the other 64..127):
+//               read S from TMEM, online softmax in f32, write the probabilities P (16-bit)
+//               into shared memory in the operand layout of the second contraction; O stays in
+//               TMEM and is rescaled there only when the row maximum has grown by more than a
+//               factor 2^8 since the last rescale.  Two warps per scheduler hide each other's
+//               instruction latencies, which is what bounds this kernel.
 // S_{j+1} is issued before P_j V_j, so the tensor pipe computes the next scores while the
 // softmax warps work on the current ones.  V tiles are used as loaded ([key][d] rows) through
 // an MN-major operand descriptor; nothing is transposed.
@@ -27,7 +29,7 @@ namespace ttb {
 constexpr int AT_BM = 128;
 constexpr int AT_BN = 128;
 constexpr int AT_D = 128;
-constexpr int AT_THREADS = 192;
+constexpr int AT_THREADS = 320; // TMA warp, MMA warp, two softmax groups of four warps
 constexpr int AT_TILE = AT_BM * AT_D * 2; // bytes
 constexpr int AT_HALF = AT_TILE / 2;
 constexpr int AT_TMEM_COLS = 512;
@@ -64,12 +66,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   extern __shared__ unsigned char smemRaw[];
   __shared__ uint32_t tmemBaseSlot;
   __shared__ int abortFlag;
+  __shared__ float xchg[2][2][AT_BM]; // [exchange parity][group][row]: what the two threads of a query row tell each other
 
   const uint32_t base = (smemU32(smemRaw) + 1023u) & ~1023u;
   const uint32_t sQ = base, sK = base + AT_TILE, sV = base + 3 * AT_TILE, sP = base + 5 * AT_TILE;
   const uint32_t bars = base + 6 * AT_TILE;
   const uint32_t qFull = bars, kFull = bars + 8, kEmpty = bars + 24, vFull = bars + 40, vEmpty = bars + 56,
-                 sFull = bars + 72, sEmpty = bars + 88, pReady = bars + 104, pEmpty = bars + 112;
+                 sFull = bars + 72, sEmpty = bars + 88, pReady = bars + 104, pEmpty = bars + 112, xBar = bars + 120;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t nQ = (p.Sq + AT_BM - 1) / AT_BM;
@@ -95,10 +98,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       mbarInit(vFull + 8 * i, 1);
       mbarInit(vEmpty + 8 * i, 1);
       mbarInit(sFull + 8 * i, 1);
-      mbarInit(sEmpty + 8 * i, 128);
+      mbarInit(sEmpty + 8 * i, 256);
     }
-    mbarInit(pReady, 128);
+    mbarInit(pReady, 256);
     mbarInit(pEmpty, 1);
+    mbarInit(xBar, 256);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -174,7 +178,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       }
     }
   } else {
-    // Softmax / accumulation: TMEM lanes are reachable per warp quarter (warp id mod 4).
+    // Softmax / accumulation.  TMEM lanes are reachable per warp quarter (warp id mod 4), so the
+    // two warps with the same quarter share 32 query rows: warp group `wg` takes keys
+    // [64 wg, 64 wg + 64) of every score tile and columns [64 wg, 64 wg + 64) of O.  A row's two
+    // threads agree on the reference maximum once per tile through shared memory.
+    const int wg = (warp - 2) >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const int64_t qrow = static_cast<int64_t>(q0) + row;
@@ -184,27 +192,41 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     // maximum lazily: it moves (and O and the row sum are rescaled) only when the maximum grew
     // by more than 2^kLazy in the exponent, so most tiles skip the rescale and P stays <= 2^kLazy.
     constexpr float kLazy = 8.0f;
+    constexpr int HALF = AT_BN / 2;
     float m = 0.0f, l = 0.0f;
-    const uint32_t oAddr = laneAddr + 2 * AT_BN;
-    const uint32_t pRow = sP + row * 128;
+    const uint32_t oAddr = laneAddr + 2 * AT_BN + wg * HALF;
+    const uint32_t pRow = sP + wg * AT_HALF + row * 128; // this group's keys are one swizzled half of P
     const uint32_t swz = static_cast<uint32_t>(row & 7);
+    uint32_t xPhase = 0;
     bool ok = true;
+    // Both threads of a row have published their value for this step (bounded like every wait).
+    auto exchange = [&](float mine) -> float {
+      // Slots alternate with the exchange's parity: a slot is rewritten two exchanges later, by
+      // which time its reader has gone through the barrier in between.
+      xchg[xPhase][wg][row] = mine;
+      mbarArrive(xBar); // release: the store above is visible to whoever observes the phase flip
+      const bool fine = __all_sync(0xffffffffu, mbarWait(xBar, xPhase, abortP, 12));
+      const float other = xchg[xPhase][wg ^ 1][row];
+      xPhase ^= 1u;
+      if (!fine) ok = false;
+      return other;
+    };
     // The TMEM loads are warp-wide: a warp leaves the loop together or not at all.
-    for (int j = 0; j < nT; ++j) {
+    for (int j = 0; j < nT && ok; ++j) {
       const int s = j & 1, ph = (j >> 1) & 1;
       if (!__all_sync(0xffffffffu, mbarWait(sFull + 8 * s, ph, abortP, 9))) { ok = false; break; }
       tcFenceAfter();
-      const uint32_t sAddr = laneAddr + s * AT_BN;
-      const int key0 = j * AT_BN;
-      const bool needMask = (p.causal && key0 + AT_BN - 1 > q0) || key0 + AT_BN > p.Skv;
-      // Last visible key of this row inside the tile (tile-relative, may be negative or >= 128).
+      const uint32_t sAddr = laneAddr + s * AT_BN + wg * HALF;
+      const int key0 = j * AT_BN + wg * HALF;
+      const bool needMask = (p.causal && key0 + HALF - 1 > q0) || key0 + HALF > p.Skv;
+      // Last visible key of this row inside this half tile (relative, may be negative or >= 64).
       int64_t lastKey = p.Skv - 1;
       if (p.causal && qrow < lastKey) lastKey = qrow;
-      const int lastRel = static_cast<int>(lastKey - key0 < AT_BN ? lastKey - key0 : AT_BN);
-      // Pass 1: the tile's row maximum.
+      const int lastRel = static_cast<int>(lastKey - key0 < HALF ? lastKey - key0 : HALF);
+      // Pass 1: the maximum of this half of the row.
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < AT_BN / 32; ++c) {
+      for (int c = 0; c < HALF / 32; ++c) {
         uint32_t r[32];
         tcLoad32(sAddr + c * 32, r);
         tcWaitLd();
@@ -216,6 +238,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
           for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
         }
       }
+      mx = fmaxf(mx, exchange(mx)); // the whole row's maximum in this tile, the same in both threads
+      if (!ok) break;
       float corr = 1.0f;
       if (j == 0) {
         m = mx == -INFINITY ? 0.0f : mx;
@@ -229,7 +253,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         tcFenceAfter();
         l *= corr;
 #pragma unroll
-        for (int c = 0; c < AT_D / 32; ++c) {
+        for (int c = 0; c < HALF / 32; ++c) {
           uint32_t r[32];
           tcLoad32(oAddr + c * 32, r);
           tcWaitLd();
@@ -243,7 +267,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       // Pass 2: probabilities, their sum, and P in the swizzled K-major operand layout.
       float sum = 0.0f;
 #pragma unroll
-      for (int c = 0; c < AT_BN / 32; ++c) {
+      for (int c = 0; c < HALF / 32; ++c) {
         uint32_t r[32];
         tcLoad32(sAddr + c * 32, r);
         tcWaitLd();
@@ -259,11 +283,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
           sum += a + bb;
           w[i >> 1] = packPair<T>(a, bb);
         }
-        const uint32_t half = pRow + (c >> 1) * AT_HALF;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
-          const uint32_t chunk = static_cast<uint32_t>((c & 1) * 4 + q4);
-          const uint32_t addr = half + ((chunk ^ swz) << 4);
+          const uint32_t chunk = static_cast<uint32_t>(c * 4 + q4);
+          const uint32_t addr = pRow + ((chunk ^ swz) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[q4 * 4]), "r"(w[q4 * 4 + 1]),
                        "r"(w[q4 * 4 + 2]), "r"(w[q4 * 4 + 3]) : "memory");
         }
@@ -274,14 +297,15 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       fenceProxyAsyncShared();
       mbarArrive(pReady);
     }
-    // The last P V has to land before O is read.
+    // The last P V has to land before O is read; the row sum is the two halves' sums.
     if (ok && nT > 0 && !__all_sync(0xffffffffu, mbarWait(pEmpty, (nT & 1) ^ 1, abortP, 11))) ok = false;
+    if (ok) l += exchange(l);
     if (ok) {
       tcFenceAfter();
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-      T *orow = out + b * p.ob + h * p.oh + qrow * p.os;
+      T *orow = out + b * p.ob + h * p.oh + qrow * p.os + wg * HALF;
 #pragma unroll
-      for (int c = 0; c < AT_D / 32; ++c) {
+      for (int c = 0; c < HALF / 32; ++c) {
         uint32_t r[32];
         tcLoad32(oAddr + c * 32, r);
         tcWaitLd();

@@ -302,6 +302,9 @@ TTB_API int ttb_sdpa_strided(const void *q, const void *k, const void *v, void *
 /* Status word of the tcgen05 attention kernel: 0, or (site << 8) | 1 of the first bounded wait
  * that ran out (the launch then produced no valid output).  No reference counterpart. */
 TTB_API int ttb_sdpa_tcgen05_status(int *status);
+/* Diagnostic: registers (or with NULL removes) a device buffer of 2048 int64 in which CTA 0 of the
+ * two-heads attention kernel records (tag, clock64) pairs of its MMA thread and first softmax thread. */
+TTB_API int ttb_sdpa_tcgen05_stamps(void *device_buffer_2048_i64);
 
 /* ---- collectives on a 1xN mesh: ::ttnn::all_reduce / all_gather / reduce_scatter
  * (runtime/lib/ttnn/operations/ccl/all_reduce.cpp:36-37, all_gather.cpp:38-41,

@@ -51,6 +51,10 @@ CASES = [
     (1, 2, 1, 130, 515, False),
     (1, 2, 2, 384, 512, True),
     (1, 2, 2, 1, 300, False),
+    # enough CTAs for the kernel that gives one CTA two heads of a grouped-query group
+    (1, 16, 4, 2432, 2432, True),
+    (1, 16, 8, 2400, 2400, False),
+    (2, 8, 4, 2500, 2500, True),
 ]
 
 

@@ -24,6 +24,8 @@
 #include "common.cuh"
 #include "tcgen05.cuh"
 
+#include <cstdlib>
+
 namespace ttb {
 
 constexpr int AT_BM = 128;
@@ -41,6 +43,7 @@ struct AtParams {
   int causal;
   int fmt; // 1 bf16, 0 f16
   float scaleLog2;
+  long long *stamps; // diagnostic: clock64 of CTA 0's MMA thread and first softmax thread, or null
 };
 
 __device__ __forceinline__ float fastExp2(float x) {
@@ -223,19 +226,23 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       int64_t lastKey = p.Skv - 1;
       if (p.causal && qrow < lastKey) lastKey = qrow;
       const int lastRel = static_cast<int>(lastKey - key0 < HALF ? lastKey - key0 : HALF);
-      // Pass 1: the maximum of this half of the row.
+      // This thread's 64 scores are read from TMEM once (both loads in flight together) and stay
+      // in registers for the maximum and for the exponentials.
+      uint32_t sc[2][32];
+      tcLoad32(sAddr, sc[0]);
+      tcLoad32(sAddr + 32, sc[1]);
+      tcWaitLd();
+      tcFenceBefore();
+      mbarArrive(sEmpty + 8 * s); // the score buffer can take the tile after next
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < HALF / 32; ++c) {
-        uint32_t r[32];
-        tcLoad32(sAddr + c * 32, r);
-        tcWaitLd();
+      for (int c = 0; c < 2; ++c) {
         if (needMask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, c * 32 + i <= lastRel ? __uint_as_float(r[i]) : -INFINITY);
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, c * 32 + i <= lastRel ? __uint_as_float(sc[c][i]) : -INFINITY);
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sc[c][i]));
         }
       }
       mx = fmaxf(mx, exchange(mx)); // the whole row's maximum in this tile, the same in both threads
@@ -267,15 +274,12 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       // Pass 2: probabilities, their sum, and P in the swizzled K-major operand layout.
       float sum = 0.0f;
 #pragma unroll
-      for (int c = 0; c < HALF / 32; ++c) {
-        uint32_t r[32];
-        tcLoad32(sAddr + c * 32, r);
-        tcWaitLd();
+      for (int c = 0; c < 2; ++c) {
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float a = fastExp2(fmaf(__uint_as_float(r[i]), sl2, negM));
-          float bb = fastExp2(fmaf(__uint_as_float(r[i + 1]), sl2, negM));
+          float a = fastExp2(fmaf(__uint_as_float(sc[c][i]), sl2, negM));
+          float bb = fastExp2(fmaf(__uint_as_float(sc[c][i + 1]), sl2, negM));
           if (needMask) {
             a = c * 32 + i <= lastRel ? a : 0.0f;
             bb = c * 32 + i + 1 <= lastRel ? bb : 0.0f;
@@ -292,8 +296,6 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         }
       }
       l += sum;
-      tcFenceBefore();
-      mbarArrive(sEmpty + 8 * s);
       fenceProxyAsyncShared();
       mbarArrive(pReady);
     }
@@ -332,10 +334,300 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   }
 }
 
-// [batch, heads, seq, 128] 16-bit tensor addressed through element strides, box = 64 columns x 128
-// rows of one head, 128-byte swizzle; rows past the end of a head read as zero.
+// ---- two query heads per CTA ---------------------------------------------------------------------
+// With grouped-query attention the heads of a group read the same K and V.  The kernel above
+// streams K/V once per (head, query block) and ends up limited by L2 -> SM bandwidth (4.5 TB/s
+// at the decoder shape).  This one gives a CTA the same 128 query rows of TWO heads of a group:
+// every K/V tile (64 keys, four-stage rings) is loaded once and used by both heads, which halves
+// that traffic, and each head has its own softmax warp group, score buffers (two per head) and
+// output accumulator in TMEM, so the two heads' softmax and contractions interleave.
+//   TMEM: S(head, buffer) at 64 * (2 head + buffer), O(head) at 256 + 128 head.
+//   Shared memory: Q_A | Q_B (32 KiB each) | K x4 | V x4 (16 KiB each) | P_A | P_B (16 KiB each) | barriers.
+// What bounds both kernels (clock stamps of the MMA thread, and a stand-alone issue loop):
+// an M = 128 contraction with both operands in shared memory reads 128 bytes per clock, all an SM
+// has, so the contractions slow down to half speed while the softmax warps store P and TMA
+// writes K/V into the same shared memory.
+constexpr int AP_BN = 64;
+constexpr int AP_STAGES = 4;
+constexpr int AP_KV = AP_BN * AT_D * 2;  // bytes of a K or V tile
+constexpr int AP_P = AT_BM * AP_BN * 2;  // bytes of a P tile
+constexpr int AP_SMEM = 2 * AT_TILE + 2 * AP_STAGES * AP_KV + 2 * AP_P + 1024 + 256;
+
+template <typename T>
+__global__ void __launch_bounds__(AT_THREADS, 1)
+    sdpaTcgen05PairKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                          const __grid_constant__ CUtensorMap mapV, T *__restrict__ out, AtParams p) {
+  extern __shared__ unsigned char smemRaw[];
+  __shared__ uint32_t tmemBaseSlot;
+  __shared__ int abortFlag;
+
+  const uint32_t base = (smemU32(smemRaw) + 1023u) & ~1023u;
+  const uint32_t sQ = base, sK = base + 2 * AT_TILE, sV = sK + AP_STAGES * AP_KV, sP = sV + AP_STAGES * AP_KV;
+  const uint32_t bars = sP + 2 * AP_P;
+  const uint32_t qFull = bars, kFull = bars + 8, kEmpty = kFull + 8 * AP_STAGES, vFull = kEmpty + 8 * AP_STAGES,
+                 vEmpty = vFull + 8 * AP_STAGES, sFull = vEmpty + 8 * AP_STAGES, sEmpty = sFull + 32, pReady = sEmpty + 32,
+                 pEmpty = pReady + 16;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = static_cast<int>(p.Hq / p.Hkv), pairs = G / 2;
+  const int64_t nQ = (p.Sq + AT_BM - 1) / AT_BM;
+  const int64_t perQ = static_cast<int64_t>(gridDim.x) / nQ; // batch * kv heads * pairs
+  const int qb = static_cast<int>(nQ - 1 - blockIdx.x / perQ); // heaviest query blocks first
+  const int rem = static_cast<int>(blockIdx.x % perQ);
+  const int b = rem / static_cast<int>(p.Hkv * pairs), r2 = rem % static_cast<int>(p.Hkv * pairs);
+  const int hk = r2 / pairs, hA = hk * G + 2 * (r2 % pairs);
+  const int q0 = qb * AT_BM;
+  int nT = static_cast<int>((p.Skv + AP_BN - 1) / AP_BN);
+  if (p.causal) {
+    int lim = q0 / AP_BN + AT_BM / AP_BN;
+    nT = nT < lim ? nT : lim;
+  }
+
+  if (threadIdx.x == 0) {
+    abortFlag = 0;
+    mbarInit(qFull, 1);
+    for (int i = 0; i < AP_STAGES; ++i) {
+      mbarInit(kFull + 8 * i, 1);
+      mbarInit(kEmpty + 8 * i, 1);
+      mbarInit(vFull + 8 * i, 1);
+      mbarInit(vEmpty + 8 * i, 1);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbarInit(sFull + 8 * i, 1);
+      mbarInit(sEmpty + 8 * i, 128);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbarInit(pReady + 8 * i, 128);
+      mbarInit(pEmpty + 8 * i, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemU32(&tmemBaseSlot)), "r"(AT_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcFenceBefore();
+  __syncthreads();
+  tcFenceAfter();
+  const uint32_t tmemBase = tmemBaseSlot;
+  volatile int *abortP = &abortFlag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetchTensorMap(&mapQ);
+      prefetchTensorMap(&mapK);
+      prefetchTensorMap(&mapV);
+      mbarArriveExpectTx(qFull, 2 * AT_TILE);
+      for (int hd = 0; hd < 2; ++hd) {
+        tmaLoad4d(sQ + hd * AT_TILE, &mapQ, qFull, 0, q0, hA + hd, b);
+        tmaLoad4d(sQ + hd * AT_TILE + AT_HALF, &mapQ, qFull, 64, q0, hA + hd, b);
+      }
+      for (int j = 0; j < nT; ++j) {
+        const int st = j % AP_STAGES, ph = (j / AP_STAGES) & 1;
+        if (!mbarWait(kEmpty + 8 * st, ph ^ 1, abortP, 1)) break;
+        mbarArriveExpectTx(kFull + 8 * st, AP_KV);
+        tmaLoad4d(sK + st * AP_KV, &mapK, kFull + 8 * st, 0, j * AP_BN, hk, b);
+        tmaLoad4d(sK + st * AP_KV + AP_KV / 2, &mapK, kFull + 8 * st, 64, j * AP_BN, hk, b);
+        if (!mbarWait(vEmpty + 8 * st, ph ^ 1, abortP, 2)) break;
+        mbarArriveExpectTx(vFull + 8 * st, AP_KV);
+        tmaLoad4d(sV + st * AP_KV, &mapV, vFull + 8 * st, 0, j * AP_BN, hk, b);
+        tmaLoad4d(sV + st * AP_KV + AP_KV / 2, &mapV, vFull + 8 * st, 64, j * AP_BN, hk, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idS = instrDescF16(p.fmt, AT_BM, AP_BN, 0, 0);
+      const uint32_t idPV = instrDescF16(p.fmt, AT_BM, AT_D, 0, 1);
+      bool ok = mbarWait(qFull, 0, abortP, 3);
+      // S_hd(j) = Q_hd K_j^T for both heads: eight steps of 16 along d, both operands K-major.
+      auto issueS = [&](int j) -> bool {
+        const int st = j % AP_STAGES, ph = (j / AP_STAGES) & 1, buf = j & 1, bph = (j >> 1) & 1;
+        if (!mbarWait(kFull + 8 * st, ph, abortP, 4)) return false;
+        const uint32_t kb = sK + st * AP_KV;
+        for (int hd = 0; hd < 2; ++hd) {
+          if (!mbarWait(sEmpty + 8 * (hd * 2 + buf), bph ^ 1, abortP, 5)) return false;
+          tcFenceAfter();
+#pragma unroll
+          for (int ks = 0; ks < AT_D / 16; ++ks) {
+            const uint32_t offQ = hd * AT_TILE + (ks >> 2) * AT_HALF + (ks & 3) * 32;
+            const uint32_t offK = (ks >> 2) * (AP_KV / 2) + (ks & 3) * 32;
+            tcMma(tmemBase + (hd * 2 + buf) * AP_BN, smemDescSw128(sQ + offQ, 0, 1024), smemDescSw128(kb + offK, 0, 1024), idS,
+                  ks > 0);
+          }
+          tcCommit(sFull + 8 * (hd * 2 + buf));
+        }
+        tcCommit(kEmpty + 8 * st);
+        return true;
+      };
+      const bool rec = p.stamps && blockIdx.x == 0;
+      int nrec = 0;
+      auto stamp = [&](int tag) { if (rec && nrec < 256) { p.stamps[nrec * 2] = tag; p.stamps[nrec * 2 + 1] = clock64(); ++nrec; } };
+      if (ok && nT > 0) ok = issueS(0);
+      for (int j = 0; ok && j < nT; ++j) {
+        stamp(100 + j);
+        if (j + 1 < nT && !issueS(j + 1)) break;
+        stamp(200 + j);
+        const int st = j % AP_STAGES, ph = (j / AP_STAGES) & 1;
+        if (!mbarWait(vFull + 8 * st, ph, abortP, 6)) break;
+        const uint32_t vb = sV + st * AP_KV;
+        bool fine = true;
+        for (int hd = 0; hd < 2 && fine; ++hd) {
+          if (!mbarWait(pReady + 8 * hd, j & 1, abortP, 7)) { fine = false; break; }
+          stamp(300 + j * 2 + hd);
+          tcFenceAfter();
+          // O_hd += P_hd V_j: four steps of 16 keys.  P is K-major (one 128-byte row per query
+          // row); V is MN-major: 128-byte rows of 64 d values, one row per key, the second 64 d
+          // values half a tile further on.
+#pragma unroll
+          for (int ks = 0; ks < AP_BN / 16; ++ks) {
+            tcMma(tmemBase + 4 * AP_BN + hd * AT_D, smemDescSw128(sP + hd * AP_P + ks * 32, 0, 1024),
+                  smemDescSw128(vb + ks * 2048, AP_KV / 2, 1024), idPV, (j | ks) > 0);
+          }
+          tcCommit(pEmpty + 8 * hd);
+        }
+        if (!fine) break;
+        tcCommit(vEmpty + 8 * st);
+      }
+    }
+  } else {
+    // Softmax / accumulation: warp group `hd` owns head hA + hd, one query row per thread.
+    const int hd = (warp - 2) >> 2;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int64_t qrow = static_cast<int64_t>(q0) + row;
+    const uint32_t laneAddr = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16);
+    const float sl2 = p.scaleLog2;
+    constexpr float kLazy = 8.0f; // see the single-head kernel
+    float m = 0.0f, l = 0.0f;
+    const uint32_t oAddr = laneAddr + 4 * AP_BN + hd * AT_D;
+    const uint32_t pRow = sP + hd * AP_P + row * 128;
+    const uint32_t swz = static_cast<uint32_t>(row & 7);
+    bool ok = true;
+    const bool rec = p.stamps && blockIdx.x == 0 && hd == 0 && quarter == 0 && lane == 0;
+    int nrec = 0;
+    auto stamp = [&](int tag) { if (rec && nrec < 256) { p.stamps[1024 + nrec * 2] = tag; p.stamps[1024 + nrec * 2 + 1] = clock64(); ++nrec; } };
+    for (int j = 0; j < nT; ++j) {
+      const int buf = j & 1, bph = (j >> 1) & 1;
+      stamp(1000 + j);
+      if (!__all_sync(0xffffffffu, mbarWait(sFull + 8 * (hd * 2 + buf), bph, abortP, 9))) { ok = false; break; }
+      stamp(2000 + j);
+      tcFenceAfter();
+      const uint32_t sAddr = laneAddr + (hd * 2 + buf) * AP_BN;
+      const int key0 = j * AP_BN;
+      const bool needMask = (p.causal && key0 + AP_BN - 1 > q0) || key0 + AP_BN > p.Skv;
+      int64_t lastKey = p.Skv - 1;
+      if (p.causal && qrow < lastKey) lastKey = qrow;
+      const int lastRel = static_cast<int>(lastKey - key0 < AP_BN ? lastKey - key0 : AP_BN);
+      // This thread's 64 scores are read from TMEM once (both loads in flight together) and stay
+      // in registers for the maximum and for the exponentials.
+      uint32_t sc[2][32];
+      tcLoad32(sAddr, sc[0]);
+      tcLoad32(sAddr + 32, sc[1]);
+      tcWaitLd();
+      tcFenceBefore();
+      mbarArrive(sEmpty + 8 * (hd * 2 + buf)); // the score buffer can take the tile after next
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        if (needMask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, c * 32 + i <= lastRel ? __uint_as_float(sc[c][i]) : -INFINITY);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sc[c][i]));
+        }
+      }
+      float corr = 1.0f;
+      if (j == 0) {
+        m = mx == -INFINITY ? 0.0f : mx;
+      } else if ((mx - m) * sl2 > kLazy) {
+        corr = fastExp2((m - mx) * sl2);
+        m = mx;
+      }
+      stamp(3000 + j);
+      // P's buffer is free, and O holds every earlier tile, once P V_{j-1} has completed.
+      if (!__all_sync(0xffffffffu, mbarWait(pEmpty + 8 * hd, (j & 1) ^ 1, abortP, 10))) { ok = false; break; }
+      stamp(4000 + j);
+      if (__any_sync(0xffffffffu, corr != 1.0f)) {
+        tcFenceAfter();
+        l *= corr;
+#pragma unroll
+        for (int c = 0; c < AT_D / 32; ++c) {
+          uint32_t r[32];
+          tcLoad32(oAddr + c * 32, r);
+          tcWaitLd();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+          tcStore32(oAddr + c * 32, r);
+        }
+        tcWaitSt();
+      }
+      const float negM = -m * sl2;
+      float sum = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float a = fastExp2(fmaf(__uint_as_float(sc[c][i]), sl2, negM));
+          float bb = fastExp2(fmaf(__uint_as_float(sc[c][i + 1]), sl2, negM));
+          if (needMask) {
+            a = c * 32 + i <= lastRel ? a : 0.0f;
+            bb = c * 32 + i + 1 <= lastRel ? bb : 0.0f;
+          }
+          sum += a + bb;
+          w[i >> 1] = packPair<T>(a, bb);
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const uint32_t chunk = static_cast<uint32_t>(c * 4 + q4);
+          const uint32_t addr = pRow + ((chunk ^ swz) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[q4 * 4]), "r"(w[q4 * 4 + 1]),
+                       "r"(w[q4 * 4 + 2]), "r"(w[q4 * 4 + 3]) : "memory");
+        }
+      }
+      l += sum;
+      fenceProxyAsyncShared();
+      mbarArrive(pReady + 8 * hd);
+      stamp(5000 + j);
+    }
+    if (ok && nT > 0 && !__all_sync(0xffffffffu, mbarWait(pEmpty + 8 * hd, (nT & 1) ^ 1, abortP, 11))) ok = false;
+    if (ok) {
+      tcFenceAfter();
+      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      T *orow = out + b * p.ob + (hA + hd) * p.oh + qrow * p.os;
+#pragma unroll
+      for (int c = 0; c < AT_D / 32; ++c) {
+        uint32_t r[32];
+        tcLoad32(oAddr + c * 32, r);
+        tcWaitLd();
+        if (qrow < p.Sq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 v;
+            v.x = packPair<T>(__uint_as_float(r[g * 8]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
+            v.y = packPair<T>(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
+            v.z = packPair<T>(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
+            v.w = packPair<T>(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
+            *reinterpret_cast<uint4 *>(orow + c * 32 + g * 8) = v;
+          }
+        }
+      }
+    }
+  }
+
+  tcFenceBefore();
+  __syncthreads();
+  if (warp == 1) {
+    tcFenceAfter();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(AT_TMEM_COLS) : "memory");
+  }
+}
+
+// [batch, heads, seq, 128] 16-bit tensor addressed through element strides, box = 64 columns x
+// `boxRows` rows of one head, 128-byte swizzle; rows past the end of a head read as zero.
 static bool makeHeadMap(CUtensorMap *map, const void *ptr, int dtype, int64_t batch, int64_t heads, int64_t seq,
-                        const int64_t *strides3) {
+                        const int64_t *strides3, int boxRows = AT_BM) {
   EncodeTiledFn fn = encodeTiled();
   if (!fn) return false;
   cuuint64_t dims[4] = {AT_D, static_cast<cuuint64_t>(seq), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
@@ -345,12 +637,28 @@ static bool makeHeadMap(CUtensorMap *map, const void *ptr, int dtype, int64_t ba
   cuuint64_t sHead = bytes(strides3[1], sSeq * static_cast<cuuint64_t>(seq));
   cuuint64_t sBatch = bytes(strides3[0], sHead * static_cast<cuuint64_t>(heads));
   cuuint64_t strides[3] = {sSeq, sHead, sBatch};
-  cuuint32_t box[4] = {64, AT_BM, 1, 1};
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(boxRows), 1, 1};
   cuuint32_t elemStrides[4] = {1, 1, 1, 1};
   CUtensorMapDataType dt = dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = fn(map, dt, 4, const_cast<void *>(ptr), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
+}
+
+template <typename T>
+static int launchPair(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, void *out, const AtParams &p,
+                      unsigned grid, cudaStream_t st) {
+  static bool attrSet[64] = {}; // function attributes belong to a device
+  int dev = 0;
+  TTB_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attrSet[dev]) {
+    TTB_CUDA(cudaFuncSetAttribute(sdpaTcgen05PairKernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, AP_SMEM));
+    attrSet[dev] = true;
+  }
+  sdpaTcgen05PairKernel<T><<<grid, AT_THREADS, AP_SMEM, st>>>(mq, mk, mv, static_cast<T *>(out), p);
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
 }
 
 template <typename T>
@@ -369,6 +677,8 @@ static int launchAt(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensor
   return TTB_OK;
 }
 
+static long long *g_atStamps = nullptr; // set by ttb_sdpa_tcgen05_stamps (diagnostic)
+
 // Returns -1 when the problem is outside what this kernel takes (the caller then uses another
 // kernel), otherwise a TTB status.
 int sdpaTcgen05Try(const void *q, const void *k, const void *v, void *out, int dtype, int64_t batch, int64_t hq,
@@ -384,9 +694,16 @@ int sdpaTcgen05Try(const void *q, const void *k, const void *v, void *out, int d
   const int64_t nQ = (sq + AT_BM - 1) / AT_BM;
   const int64_t ctas = nQ * batch * hq;
   if (ctas > 0x7fffffff) return -1;
+  // Two heads of a grouped-query group per CTA when the group size is even (TTB_SDPA_ONE_HEAD=1: never).
+  static const bool oneHead = [] {
+    const char *e = std::getenv("TTB_SDPA_ONE_HEAD");
+    return e && e[0] == '1';
+  }();
+  // ... and when the halved grid still fills the machine.
+  const bool pair = !oneHead && (hq / hkv) % 2 == 0 && nQ * batch * hq / 2 >= smCount();
   CUtensorMap mq, mk, mv;
-  if (!makeHeadMap(&mq, q, dtype, batch, hq, sq, qs) || !makeHeadMap(&mk, k, dtype, batch, hkv, skv, ks) ||
-      !makeHeadMap(&mv, v, dtype, batch, hkv, skv, vs))
+  if (!makeHeadMap(&mq, q, dtype, batch, hq, sq, qs) || !makeHeadMap(&mk, k, dtype, batch, hkv, skv, ks, pair ? AP_BN : AT_BM) ||
+      !makeHeadMap(&mv, v, dtype, batch, hkv, skv, vs, pair ? AP_BN : AT_BM))
     return -1;
   AtParams p;
   p.Hq = hq; p.Hkv = hkv; p.Sq = sq; p.Skv = skv;
@@ -394,13 +711,26 @@ int sdpaTcgen05Try(const void *q, const void *k, const void *v, void *out, int d
   p.causal = causal ? 1 : 0;
   p.fmt = dtype == kBF16 ? 1 : 0;
   p.scaleLog2 = scale * 1.4426950408889634f;
+  p.stamps = g_atStamps;
   double work = 4.0 * double(batch) * hq * sq * skv * headDim * (causal ? 0.5 : 1.0);
   ProfScope prof("sdpa_tcgen05", work, 2.0 * batch * (2.0 * hq * sq + 2.0 * hkv * skv) * headDim, st);
+  if (pair) {
+    const unsigned grid = static_cast<unsigned>(ctas / 2);
+    if (dtype == kBF16) return launchPair<__nv_bfloat16>(mq, mk, mv, out, p, grid, st);
+    return launchPair<__half>(mq, mk, mv, out, p, grid, st);
+  }
   if (dtype == kBF16) return launchAt<__nv_bfloat16>(mq, mk, mv, out, p, static_cast<unsigned>(ctas), st);
   return launchAt<__half>(mq, mk, mv, out, p, static_cast<unsigned>(ctas), st);
 }
 
 } // namespace ttb
+
+// Diagnostic: with a device buffer of 2048 int64 registered here, CTA 0 of the two-heads kernel
+// records (tag, clock64) pairs of its MMA thread (first 1024 slots) and first softmax thread.
+extern "C" int ttb_sdpa_tcgen05_stamps(void *device_buffer_2048_i64) {
+  ttb::g_atStamps = static_cast<long long *>(device_buffer_2048_i64);
+  return TTB_OK;
+}
 
 extern "C" int ttb_sdpa_tcgen05_status(int *status) {
   TTB_CHECK(status != nullptr, "null argument");

@@ -105,6 +105,24 @@ __device__ __forceinline__ void tcMma(uint32_t tmemD, uint64_t descA, uint64_t d
                ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// D[tmem] (+)= A[tmem] * B[smem desc]: the A operand is read from tensor memory (row i of A in
+// lane i, two 16-bit elements per 32-bit column, the even k in the low half).
+__device__ __forceinline__ void tcMmaTmemA(uint32_t tmemD, uint32_t tmemA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(tmemD), "r"(tmemA), "l"(descB), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Writes 16 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tcStore16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+               "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                 "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+               : "memory");
+}
+
 // 32 consecutive f32 columns of this thread's TMEM lane.
 __device__ __forceinline__ void tcLoad32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "

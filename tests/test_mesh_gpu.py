@@ -167,7 +167,16 @@ def _tp_worker(rank, world, port, ret):
         from oracle import metrics
         ok, report = metrics.check_close(want, outs[0], 0.999, 2e-2, 2.0 ** -6)
         same = all(torch.equal(outs[0], o) for o in outs[1:])
-        ret[rank] = (bool(ok), bool(same), report, outs[0].float().sum().item())
+        # sequence-sharded I/O: every rank feeds and receives its own rows only
+        mine2 = graphs.shard_inputs(ins, graphs.decoder_shard_dims(io_seq_sharded=True, **kw), world, rank)
+        buf2 = graphs.build_binary(graphs.decoder_block_graph, mesh_shape=(1, world), tp=world, presharded=True,
+                                   io_seq_sharded=True, **kw)
+        binary2 = rt.Binary.load_from_memory(buf2)
+        dev_in2 = [rt.to_layout(rt.from_torch(t), dev, rt.get_layout(binary2, 0, i)) for i, t in enumerate(mine2)]
+        rows = rt.to_torch(rt.to_host(rt.submit(dev, binary2, 0, dev_in2)[0], untilize=True)[0])
+        per = kw["seq"] // world
+        rows_ok = torch.equal(rows, outs[0][:, rank * per:(rank + 1) * per, :])
+        ret[rank] = (bool(ok), bool(same) and bool(rows_ok), report, outs[0].float().sum().item())
         rt.close_mesh_device(dev)
     finally:
         dist.destroy_process_group()

@@ -107,11 +107,18 @@ DECODER_ORDER = ["x", "attn_norm", "wq", "wk", "wv", "wo", "ffn_norm", "w_gate",
 
 
 def decoder_block_graph(b, seq=2048, hidden=4096, n_heads=32, n_kv_heads=8, head_dim=128, ffn=14336, batch=1,
-                        tp=1, eps=1e-5, presharded=False, dtype="BFloat16"):
+                        tp=1, eps=1e-5, presharded=False, dtype="BFloat16", io_seq_sharded=False):
     """RMSNorm -> q/k/v -> RoPE -> causal GQA attention -> o_proj (+all_reduce) -> residual ->
     RMSNorm -> SwiGLU FFN (+all_reduce) -> residual.  `tp` is the 1xN mesh width.  With
     `presharded` the program's inputs are already per-device device tensors (what a frontend
-    that shards its own arguments hands over) and the output stays on the mesh."""
+    that shards its own arguments hands over) and the output stays on the mesh.  With
+    `io_seq_sharded` (presharded, tp > 1) every device receives and returns only its 1/tp of the
+    sequence: the block starts with an all_gather of the activations over NVLink and ends with a
+    mesh_partition, so host traffic per step is one copy of the activations in each direction in
+    total instead of one per device."""
+    io_seq_sharded = bool(io_seq_sharded and presharded and tp > 1)
+    if io_seq_sharded:
+        assert seq % tp == 0, "sequence length must divide by the mesh width"
     shapes = decoder_shapes(seq, hidden, n_heads, n_kv_heads, head_dim, ffn, batch)
     v = {}
     for name in DECODER_ORDER:
@@ -122,12 +129,16 @@ def decoder_block_graph(b, seq=2048, hidden=4096, n_heads=32, n_kv_heads=8, head
             local = list(shape)
             if sdim is not None:
                 local[sdim] //= tp
+            if name == "x" and io_seq_sharded:
+                local[1] //= tp
             v[name] = b.input(local, dtype)
         else:
             full = b.input(shape, dtype, on_device=False)
             v[name] = b.distribute(full, sdim, loc=f"shard_{name}")
     hq, hkv = n_heads // tp, n_kv_heads // tp
     x = v["x"]
+    if io_seq_sharded:
+        x = b.all_gather(x, 1, loc="gather_sequence")
     h = b.rms_norm(x, v["attn_norm"], epsilon=eps, loc="attn_norm")
     q = b.linear(h, v["wq"], transpose_b=True, loc="q_proj")
     k = b.linear(h, v["wk"], transpose_b=True, loc="k_proj")
@@ -153,6 +164,8 @@ def decoder_block_graph(b, seq=2048, hidden=4096, n_heads=32, n_kv_heads=8, head
     out = b.add(x1, d, loc="ffn_residual")
     if tp > 1 and not presharded:
         out = b.aggregate(out, None, loc="gather_output")
+    if io_seq_sharded:
+        out = b.mesh_partition(out, 1, loc="own_rows")
     b.output(out)
 
 
@@ -186,9 +199,12 @@ def shard_inputs(inputs: Sequence[torch.Tensor], shard_dims: Sequence[Optional[i
     return out
 
 
-def decoder_shard_dims(**kw) -> List[Optional[int]]:
+def decoder_shard_dims(io_seq_sharded=False, **kw) -> List[Optional[int]]:
     shapes = decoder_shapes(**kw)
-    return [shapes[n][1] for n in DECODER_ORDER]
+    dims = [shapes[n][1] for n in DECODER_ORDER]
+    if io_seq_sharded:
+        dims[DECODER_ORDER.index("x")] = 1  # the activations arrive split along the sequence
+    return dims
 
 
 def decoder_block_flops(seq=2048, hidden=4096, n_heads=32, n_kv_heads=8, head_dim=128, ffn=14336, batch=1,

@@ -207,6 +207,14 @@ TTB_API int ttb_gemm(const void *a, const void *b, const void *bias, void *c, in
                      int bias_dtype, int c_dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                      int trans_a, int trans_b, int64_t a_batch_stride, int64_t b_batch_stride,
                      int act, int round_steps, void *stream);
+/* Up to three products C_i[m, n_i] = A[m, k] * B_i[n_i, k]^T that share A (the q / k / v projections of
+ * one activation) in one launch: their tiles form one list, so narrow problems fill the SMs a wide
+ * one leaves idle.  Row-major, 16-bit A and B_i, no bias / activation.  Equivalent to `count` calls
+ * of ttb_gemm with trans_b = 1 (which is what runs when the tensor-core kernel declines).
+ * No reference counterpart (three ::ttnn::linear calls). */
+TTB_API int ttb_gemm_grouped(const void *a, const void *const *b, void *const *c, const int64_t *n, int count,
+                             int ab_dtype, int c_dtype, int64_t m, int64_t k, void *stream);
+
 /* ttb_gemm with a second, full-size epilogue operand `extra` ([batch, m, n], dense, in
  * `c_dtype`), combined with the result of the bias / activation chain the way separate ops
  * would (the chain's result is rounded to `c_dtype` first):

@@ -149,3 +149,33 @@ def test_pointwise_conv_shape_bias_relu(rt, device):
         h.close()
     want = torch.relu(a.float() @ b.float().t() + bias.float()).to(torch.bfloat16)
     assert_matches(got, want, "pointwise conv shape")
+
+
+@pytest.mark.parametrize("m,k,ns", [(2048, 4096, (4096, 1024, 1024)), (200, 264, (136, 72)), (256, 512, (512, 128, 128)),
+                                    (64, 64, (16, 16))])
+def test_gemm_grouped_matches_separate_calls(rt, device, m, k, ns):
+    """ttb_gemm_grouped (several products sharing A in one launch) gives exactly what separate
+    ttb_gemm calls give; the last case is too small for the tensor-core kernel (loop fallback)."""
+    torch.manual_seed(m + k)
+    a = torch.randn(m, k).to(torch.bfloat16)
+    bs = [(torch.randn(n, k) * 0.05).to(torch.bfloat16) for n in ns]
+    h = KernelHarness(rt)
+    try:
+        da = h.upload(a)
+        dbs = [h.upload(b) for b in bs]
+        dcs = [h.empty((m, n), torch.bfloat16) for n in ns]
+        i64 = ctypes.c_int64
+        cnt = len(ns)
+        bp = (ctypes.c_void_p * cnt)(*[p.value for p in dbs])
+        cp = (ctypes.c_void_p * cnt)(*[p.value for p in dcs])
+        nn = (ctypes.c_int64 * cnt)(*ns)
+        rc = h.lib.ttb_gemm_grouped(da, bp, cp, nn, cnt, BF16, BF16, i64(m), i64(k), h.stream)
+        assert rc == 0, h.lib.ttb_last_error().decode()
+        got = [h.download(dc, (m, n), torch.bfloat16) for dc, n in zip(dcs, ns)]
+        assert tc_status(h) == 0
+        sep = [run_gemm(h, h.lib.ttb_gemm, a, b, None, m, n, k) for b, n in zip(bs, ns)]
+    finally:
+        h.close()
+    for g, s_, b in zip(got, sep, bs):
+        assert torch.equal(g, s_), "grouped and separate launches differ"
+        assert_matches(g, (a.float() @ b.float().t()).to(torch.bfloat16), "grouped gemm")

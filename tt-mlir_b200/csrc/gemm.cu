@@ -11,6 +11,8 @@ namespace ttb {
 int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int abDtype, int biasDtype, int cDtype,
                    int64_t batch, int64_t m, int64_t n, int64_t k, int transA, int transB, int64_t aBatchStride,
                    int64_t bBatchStride, int act, int roundSteps, const void *extra, int extraOp, cudaStream_t stream);
+int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, const int64_t *n, int count, int abDtype,
+                          int cDtype, int64_t m, int64_t k, cudaStream_t stream);
 } // namespace ttb
 
 static bool tcgen05Disabled() {
@@ -49,4 +51,19 @@ extern "C" int ttb_gemm_fused(const void *a, const void *b, const void *bias, vo
   rc = ttb_eltwise_binary(0 /* EltwiseBinaryOpType::Add */, c, c_dtype, extra, c_dtype, c, c_dtype, 1, shape, ones, ones, stream);
   if (rc || extra_op == TTB_EXTRA_ADD) return rc;
   return ttb_eltwise_unary(8 /* EltwiseUnaryOpType::Relu */, c, c_dtype, c, c_dtype, count, 0.0f, stream);
+}
+
+extern "C" int ttb_gemm_grouped(const void *a, const void *const *b, void *const *c, const int64_t *n, int count,
+                                int ab_dtype, int c_dtype, int64_t m, int64_t k, void *stream) {
+  TTB_CHECK(a && b && c && n && count >= 1 && count <= 3, "bad argument");
+  for (int i = 0; i < count; ++i) TTB_CHECK(b[i] && c[i] && n[i] >= 0, "bad argument");
+  if (!tcgen05Disabled()) {
+    int rc = ttb::gemmTcgen05GroupedTry(a, b, c, n, count, ab_dtype, c_dtype, m, k, ttb::asStream(stream));
+    if (rc != -1) return rc;
+  }
+  for (int i = 0; i < count; ++i) {
+    int rc = ttb_gemm(a, b[i], nullptr, c[i], ab_dtype, 0, c_dtype, 1, m, n[i], k, 0, 1, 0, 0, TTB_ACT_NONE, 0, stream);
+    if (rc) return rc;
+  }
+  return TTB_OK;
 }

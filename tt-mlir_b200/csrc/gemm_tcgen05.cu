@@ -85,6 +85,11 @@ struct TcParams {
   int biasDt;
   int act;
   int roundSteps;
+  // Grouped launch: up to three problems that share A, M and K run as one tile list; n-tile
+  // indices [segCum[i-1], segCum[i]) belong to problem i, whose width is segN[i] (B and C maps
+  // mapB/mapC, mapB1/mapC1, mapB2/mapC2).  An ordinary launch is one segment.
+  int segCum[3];
+  int64_t segN[3];
   const void *extra; // optional [M, N] operand in the output type, combined after bias / activation
   int extraOp;       // TTB_EXTRA_*
   // Implicit-GEMM convolution: A is not a matrix in memory but the receptive fields of an NHWC
@@ -106,6 +111,8 @@ template <int BN, typename TC, bool PLAIN>
 __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     gemmTcgen05Kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                       const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapE,
+                      const __grid_constant__ CUtensorMap mapB1, const __grid_constant__ CUtensorMap mapC1,
+                      const __grid_constant__ CUtensorMap mapB2, const __grid_constant__ CUtensorMap mapC2,
                       TC *__restrict__ c, TcParams p) {
   using Cfg = TcCfg<BN>;
   constexpr int STAGES = Cfg::kStages;
@@ -124,8 +131,14 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
   volatile int *abortFlag = &abortFlagS;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t tilesM = p.cTw ? p.cTilesM : (p.M + TC_BM - 1) / TC_BM, tilesN = (p.N + BN - 1) / BN;
+  const int64_t tilesM = p.cTw ? p.cTilesM : (p.M + TC_BM - 1) / TC_BM, tilesN = p.segCum[2];
   const int64_t numTiles = tilesM * tilesN;
+  // n-tile index -> (segment, first column inside the segment)
+  auto segmentOf = [&](int64_t nt, int &n0) {
+    const int seg = nt < p.segCum[0] ? 0 : (nt < p.segCum[1] ? 1 : 2);
+    n0 = static_cast<int>(nt - (seg == 0 ? 0 : p.segCum[seg - 1])) * BN;
+    return seg;
+  };
   const int kBlocks = static_cast<int>((p.K + TC_BK - 1) / TC_BK);
 
   if (threadIdx.x == 0) {
@@ -175,7 +188,8 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     };
     for (int64_t tile = blockIdx.x; tile < numTiles && alive; tile += gridDim.x) {
       const int64_t m0 = (tile % tilesM) * TC_BM;
-      const int n0 = static_cast<int>(tile / tilesM) * BN;
+      int n0;
+      (void)segmentOf(tile / tilesM, n0);
       int off[32];      // element offset of (pixel at tap 0, piece), or of x itself for rows past the end
       uint32_t yx[32];  // (y0 + 0x4000) << 16 | (x0 + 0x4000); rows past the end get coordinates that never pass
 #pragma unroll
@@ -236,7 +250,10 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
       bool alive = true;
       for (int64_t tile = blockIdx.x; tile < numTiles && alive; tile += gridDim.x) {
         const int mt = static_cast<int>(tile % tilesM);
-        const int m0 = mt * TC_BM, n0 = static_cast<int>(tile / tilesM) * BN;
+        const int m0 = mt * TC_BM;
+        int n0;
+        const int seg = segmentOf(tile / tilesM, n0);
+        const CUtensorMap *mb = seg == 0 ? &mapB : (seg == 1 ? &mapB1 : &mapB2);
         int img = 0, oy0 = 0, ox0 = 0, cb = 1;
         if (p.cTw) {
           const int perImg = p.cTilesX * p.cTilesY, rem = mt % perImg;
@@ -258,7 +275,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
           } else {
             tmaLoad2d(sa, &mapA, fullBar(s), kb * TC_BK, m0);
           }
-          tmaLoad2d(sb, &mapB, fullBar(s), kb * TC_BK, n0);
+          tmaLoad2d(sb, mb, fullBar(s), kb * TC_BK, n0);
         }
       }
     }
@@ -318,7 +335,11 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
       const uint32_t accPhase = (accIt >> 1) & 1u;
       if (!mbarWait(tmemFullBar(acc), accPhase, abortFlag, 4)) break;
       tcFenceAfter();
-      const int64_t m0 = (tile % tilesM) * TC_BM, n0 = (tile / tilesM) * BN;
+      const int64_t m0 = (tile % tilesM) * TC_BM;
+      int n0i;
+      const int seg = segmentOf(tile / tilesM, n0i);
+      const int64_t n0 = n0i, segN = p.segN[seg];
+      const CUtensorMap *mc = seg == 0 ? &mapC : (seg == 1 ? &mapC1 : &mapC2);
       // patch mode: this warp's 32 rows are 32 / cTw rows of the patch, starting at (pOy, pOx) of image pImg
       int pImg = 0, pOy = 0, pOx = 0;
       if (p.cTw) {
@@ -331,7 +352,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
 #pragma unroll 1
       for (int cc = 0; cc < BN / CH; ++cc) {
         const int64_t col0 = n0 + cc * CH;
-        if (col0 >= p.N || p.debug == 2) break; // warp-uniform
+        if (col0 >= segN || p.debug == 2) break; // warp-uniform
         const uint32_t buf = stageOut + (EPW == 4 ? (chunkIt & 1u) * 4096u : 0u);
         const uint32_t rowAddr = buf + static_cast<uint32_t>(lane) * 128u;
         // The second operand's 32 x 128 B block is brought into the staging buffer by TMA (the
@@ -486,11 +507,11 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
         if (lane == 0) {
           if (p.cTw) {
             asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-                         ::"l"(reinterpret_cast<uint64_t>(&mapC)), "r"(buf), "r"(static_cast<int>(col0)), "r"(pOx), "r"(pOy),
+                         ::"l"(reinterpret_cast<uint64_t>(mc)), "r"(buf), "r"(static_cast<int>(col0)), "r"(pOx), "r"(pOy),
                            "r"(pImg) : "memory");
           } else {
             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                         ::"l"(reinterpret_cast<uint64_t>(&mapC)), "r"(buf), "r"(static_cast<int>(col0)),
+                         ::"l"(reinterpret_cast<uint64_t>(mc)), "r"(buf), "r"(static_cast<int>(col0)),
                            "r"(static_cast<int>(m0 + quarter * 32)) : "memory");
           }
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -576,7 +597,11 @@ static bool makeMap4(CUtensorMap *map, const void *ptr, int dtype, int64_t c, in
 
 template <int BN, typename TC, bool PLAIN>
 static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &me, void *c, const TcParams &p,
-                    cudaStream_t st) {
+                    cudaStream_t st, const CUtensorMap *more = nullptr /* mapB1, mapC1, mapB2, mapC2 of a grouped launch */);
+
+template <int BN, typename TC, bool PLAIN>
+static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &me, void *c, const TcParams &p,
+                    cudaStream_t st, const CUtensorMap *more) {
   using Cfg = TcCfg<BN>;
   // Function attributes belong to a device: set the shared-memory limit once on each.
   static bool attrSet[64] = {};
@@ -586,9 +611,10 @@ static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensor
     TTB_CUDA(cudaFuncSetAttribute(gemmTcgen05Kernel<BN, TC, PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
     attrSet[dev] = true;
   }
-  int64_t tiles = (p.cTw ? p.cTilesM : (p.M + TC_BM - 1) / TC_BM) * ((p.N + BN - 1) / BN);
+  int64_t tiles = (p.cTw ? p.cTilesM : (p.M + TC_BM - 1) / TC_BM) * p.segCum[2];
   int grid = static_cast<int>(tiles < smCount() ? tiles : smCount());
-  gemmTcgen05Kernel<BN, TC, PLAIN><<<grid, PLAIN ? TC_THREADS : TC_THREADS_EPI8, Cfg::kSmem, st>>>(ma, mb, mc, me, static_cast<TC *>(c), p);
+  gemmTcgen05Kernel<BN, TC, PLAIN><<<grid, PLAIN ? TC_THREADS : TC_THREADS_EPI8, Cfg::kSmem, st>>>(
+      ma, mb, mc, me, more ? more[0] : mb, more ? more[1] : mc, more ? more[2] : mb, more ? more[3] : mc, static_cast<TC *>(c), p);
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;
@@ -642,6 +668,8 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   p.convX = nullptr;
   p.cTw = 0;
   p.cTilesM = 0;
+  p.segCum[0] = p.segCum[1] = p.segCum[2] = static_cast<int>((n + bn - 1) / bn);
+  p.segN[0] = p.segN[1] = p.segN[2] = n;
   p.fmt = abDtype == kBF16 ? 1 : 0;
   {
     const char *dbg = std::getenv("TTB_TC_DEBUG");
@@ -664,6 +692,84 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   TTB_TC_BN(float)
 #undef TTB_TC_BN
 #undef TTB_TC
+}
+
+// Up to three GEMMs C_i[M, N_i] = A[M, K] B_i[N_i, K]^T that share A (the q / k / v projections of
+// one activation) as ONE launch: their tiles form one list, so the narrow problems fill the SMs
+// the wide one leaves idle in its last wave.  Plain epilogue only.  -1 = not taken.
+int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, const int64_t *n, int count, int abDtype,
+                          int cDtype, int64_t m, int64_t k, cudaStream_t stream) {
+  if (count < 2 || count > 3) return -1;
+  if (abDtype != kBF16 && abDtype != kF16) return -1;
+  if (cDtype != abDtype && cDtype != kF32) return -1;
+  if (k % 8 != 0 || m < 1 || k < 8 || m > 0x7fffffff || k > 0x7fffffff || !aligned16(a)) return -1;
+  int64_t nSum = 0;
+  for (int i = 0; i < count; ++i) {
+    if (n[i] < 8 || n[i] > 0x7fffffff || (n[i] * static_cast<int64_t>(dtypeSize(cDtype))) % 16 != 0) return -1;
+    if (!aligned16(b[i]) || !aligned16(c[i])) return -1;
+    nSum += n[i];
+  }
+  if (m * nSum * k < (1ll << 18)) return -1;
+  int bn = 64;
+  {
+    int64_t best = -1;
+    for (int w : {256, 128, 64}) {
+      int64_t tiles = 0;
+      bool fits = true;
+      for (int i = 0; i < count; ++i) {
+        if (w > 64 && n[i] < w) fits = false;
+        tiles += ((m + TC_BM - 1) / TC_BM) * ((n[i] + w - 1) / w);
+      }
+      if (!fits) continue;
+      int64_t waves = (tiles + smCount() - 1) / smCount();
+      int64_t cost = waves * (w + 64);
+      if (best < 0 || cost < best) {
+        best = cost;
+        bn = w;
+      }
+    }
+  }
+  CUtensorMap ma, mb[3], mc[3];
+  if (!makeMap(&ma, a, abDtype, m, k, TC_BM)) return -1;
+  for (int i = 0; i < count; ++i) {
+    if (!makeMap(&mb[i], b[i], abDtype, n[i], k, bn) || !makeMap(&mc[i], c[i], cDtype, m, n[i], 32)) return -1;
+  }
+  for (int i = count; i < 3; ++i) {
+    mb[i] = mb[0];
+    mc[i] = mc[0];
+  }
+  TcParams p;
+  p.M = m; p.N = n[0]; p.K = k;
+  p.bias = nullptr; p.biasDt = 0; p.act = TTB_ACT_NONE; p.roundSteps = 0;
+  p.extra = nullptr; p.extraOp = 0;
+  p.convX = nullptr; p.cTw = 0; p.cTilesM = 0;
+  int cum = 0;
+  double flops = 0, bytes = double(m) * k * 2;
+  for (int i = 0; i < 3; ++i) {
+    if (i < count) cum += static_cast<int>((n[i] + bn - 1) / bn);
+    p.segCum[i] = cum;
+    p.segN[i] = n[i < count ? i : count - 1];
+    if (i < count) {
+      flops += 2.0 * double(m) * double(n[i]) * double(k);
+      bytes += double(n[i]) * k * 2 + double(m) * n[i] * dtypeSize(cDtype);
+    }
+  }
+  p.fmt = abDtype == kBF16 ? 1 : 0;
+  p.debug = 0;
+  ProfScope prof("gemm_tcgen05", flops, bytes, stream);
+  const CUtensorMap more[4] = {mb[1], mc[1], mb[2], mc[2]};
+#define TTB_TCG(BNv, TCv) return launchTc<BNv, TCv, true>(ma, mb[0], mc[0], mc[0], c[0], p, stream, more)
+#define TTB_TCG_BN(TCv)                                                                  \
+  switch (bn) {                                                                          \
+  case 256: TTB_TCG(256, TCv);                                                           \
+  case 128: TTB_TCG(128, TCv);                                                           \
+  default: TTB_TCG(64, TCv);                                                             \
+  }
+  if (cDtype == kBF16) { TTB_TCG_BN(__nv_bfloat16) }
+  if (cDtype == kF16) { TTB_TCG_BN(__half) }
+  TTB_TCG_BN(float)
+#undef TTB_TCG_BN
+#undef TTB_TCG
 }
 
 // Convolution as an implicit GEMM on the same kernel: the producer warp gathers the receptive
@@ -734,6 +840,8 @@ int convTcgen05Try(const void *x, const void *wre, const void *bias, void *out, 
   p.ckw = kw; p.csh = sh; p.csw = sw; p.cpt = pt; p.cpl = pl; p.cdh = dh; p.cdw = dw;
   p.cTw = tw; p.cTilesX = static_cast<int>(tilesX); p.cTilesY = static_cast<int>(tilesY);
   p.cTilesM = tw ? n * tilesX * tilesY : 0;
+  p.segCum[0] = p.segCum[1] = p.segCum[2] = static_cast<int>((o + bn - 1) / bn);
+  p.segN[0] = p.segN[1] = p.segN[2] = o;
   p.fmt = dtype == kBF16 ? 1 : 0;
   p.debug = 0;
   // algorithmic bytes: the input and the output once each (plus the residual operand), the weights

@@ -335,6 +335,7 @@ private:
   // fused forms; return ops consumed or 0 when the pattern does not apply
   size_t tryQuantChain(size_t i);
   size_t tryGemmEpilogue(size_t i);
+  size_t tryGroupedGemm(size_t i);
   size_t trySiluMul(size_t i);
   size_t trySdpa(size_t i);
   size_t tryAllReduceAdd(size_t i);
@@ -576,7 +577,10 @@ size_t Executor::runOp(size_t i) {
     switch (op->type_type()) {
     case OpType::EltwiseQuantizationOp: used = tryQuantChain(i); break;
     case OpType::MatmulOp:
-    case OpType::LinearOp: used = tryGemmEpilogue(i); break;
+    case OpType::LinearOp:
+      used = tryGemmEpilogue(i);
+      if (!used) used = tryGroupedGemm(i);
+      break;
     case OpType::EltwiseUnaryOp: used = trySiluMul(i); break;
     case OpType::EltwiseBinaryOp: used = tryAddRmsNorm(i); break;
     case OpType::ScaledDotProductAttentionOp: used = trySdpa(i); break;
@@ -1265,6 +1269,97 @@ size_t Executor::tryGemmEpilogue(size_t i) {
   runGemm(a, b, bias, cur, ta, tb, act, roundSteps, extra, extraOp);
   runDeallocs(deallocs);
   return consumedUpTo + 1 - i;
+}
+
+// Two or three consecutive linear / matmul ops on the same activation (q, k, v projections):
+// no bias, no activation, weights as [N, K] (transpose_b), 16-bit, rank-2 problem after
+// flattening.  They run as one grouped launch.  Ops whose result feeds an elementwise op right
+// after the group are left alone (that pattern belongs to the epilogue fusions).
+size_t Executor::tryGroupedGemm(size_t i) {
+  const auto *ops = prog->operations();
+  struct Item { const fbt::TensorRef *a, *b, *out; };
+  auto plain = [&](const fbt::Operation *op, Item &it) {
+    if (op->type_type() == OpType::LinearOp) {
+      const auto *l = op->type_as_LinearOp();
+      if (l->bias() || l->transpose_a() || !l->transpose_b() || activationCode(l->activation()) != TTB_ACT_NONE) return false;
+      it = {l->a(), l->b(), l->out()};
+      return true;
+    }
+    if (op->type_type() == OpType::MatmulOp) {
+      const auto *m = op->type_as_MatmulOp();
+      if (m->transpose_a() || !m->transpose_b() || activationCode(m->activation()) != TTB_ACT_NONE) return false;
+      it = {m->a(), m->b(), m->out()};
+      return true;
+    }
+    return false;
+  };
+  std::vector<Item> items;
+  std::vector<const fbt::Operation *> deallocs;
+  size_t j = i, last = i;
+  while (items.size() < 3) {
+    std::vector<const fbt::Operation *> d2;
+    size_t k = j;
+    const auto *op = items.empty() ? ops->Get(static_cast<uint32_t>(i)) : peek(k, d2);
+    Item it;
+    if (!op || !plain(op, it)) break;
+    if (!items.empty()) {
+      if (it.a->global_id() != items[0].a->global_id() || refShape(it.b).size() != 2 || refDtype(it.b) != refDtype(items[0].b) ||
+          refShape(it.b)[1] != refShape(items[0].b)[1] || refDtype(it.out) != refDtype(items[0].out))
+        break;
+      // a deallocation of the shared activation between the ops would end its life too early
+      bool freesInput = false;
+      for (const auto *d : d2) {
+        if (d->type_as_DeallocateOp()->in() && d->type_as_DeallocateOp()->in()->global_id() == it.a->global_id()) freesInput = true;
+      }
+      if (freesInput) break;
+      deallocs.insert(deallocs.end(), d2.begin(), d2.end());
+    } else if (refShape(it.b).size() != 2) {
+      break;
+    }
+    items.push_back(it);
+    last = items.size() == 1 ? i : k;
+    j = last + 1;
+  }
+  // an elementwise consumer right after the group belongs to an epilogue fusion of the last op
+  while (items.size() >= 2) {
+    std::vector<const fbt::Operation *> d2;
+    size_t k = last + 1;
+    const auto *nop = peek(k, d2);
+    bool eltwise = nop && (nop->type_type() == OpType::EltwiseBinaryOp || nop->type_type() == OpType::EltwiseUnaryOp);
+    if (!eltwise) break;
+    return 0; // keep it simple: such chains run op by op with their own fusions
+  }
+  if (items.size() < 2) return 0;
+  DataType abDt = refDtype(items[0].b), cDt = refDtype(items[0].out);
+  if ((abDt != DataType::BFloat16 && abDt != DataType::Float16) || refDtype(items[0].a) != abDt) return 0;
+  TensorPtr a = getDevice(items[0].a);
+  std::vector<uint32_t> as = a->shape;
+  if (as.size() < 2) return 0;
+  int64_t K = as.back(), M = static_cast<int64_t>(a->volume()) / std::max<int64_t>(K, 1);
+  std::vector<TensorPtr> bs, outs;
+  std::vector<int64_t> ns;
+  for (const Item &it : items) {
+    TensorPtr b = getDevice(it.b);
+    if (b->shape.size() != 2 || b->shape[1] != K) return 0;
+    TensorPtr out = allocOut(it.out);
+    if (static_cast<int64_t>(out->volume()) != M * b->shape[0]) return 0;
+    bs.push_back(b);
+    outs.push_back(out);
+    ns.push_back(b->shape[0]);
+  }
+  eachRank([&](size_t r, const RankCtx &rc) {
+    const void *bp[3];
+    void *cp[3];
+    for (size_t q = 0; q < items.size(); ++q) {
+      bp[q] = bs[q]->shards[r]->ptr;
+      cp[q] = outs[q]->shards[r]->ptr;
+    }
+    TTB_CALL(ttb_gemm_grouped(a->shards[r]->ptr, bp, cp, ns.data(), static_cast<int>(items.size()), ttbDtype(abDt), ttbDtype(cDt), M,
+                              K, rc.stream));
+  });
+  for (size_t q = 0; q < items.size(); ++q) put(items[q].out, outs[q]);
+  runDeallocs(deallocs);
+  return last + 1 - i;
 }
 
 void Executor::runConv2d(const fbt::Conv2dOp *op, int act, const fbt::TensorRef *extraRef, int extraOp,

@@ -94,3 +94,25 @@ def test_mesh_program_structure():
     assert ag["all_gather_dim"] == 2 and ag["cluster_axis"] == 1
     agg = next(t for k, t in ops_ if k == "AggregateTensorOp")
     assert agg["composer_config"]["dims"] == [0] and agg["composer_config"]["mesh_shape_override"] == [1]
+
+
+def test_sequence_sharded_io_program_shape():
+    """The tensor-parallel decoder program with sequence-sharded I/O: the activations arrive as
+    1/N of the sequence, the first mesh op gathers them, the last op hands back this device's rows."""
+    from ttmlir_b200.schema.fbs import Reader
+    from ttmlir_b200.schema.ttnn_schema import S
+    kw = dict(seq=64, hidden=128, n_heads=4, n_kv_heads=2, head_dim=32, ffn=256)
+    buf = graphs.build_binary(graphs.decoder_block_graph, mesh_shape=(1, 2), tp=2, presharded=True, io_seq_sharded=True, **kw)
+    prog = Reader(S, buf).root("TTNNBinary")["programs"][0]
+    kinds = [op["type"][0] for op in prog["operations"] if op["type"][0] not in ("GetDeviceOp", "DeallocateOp")]
+    assert kinds[0] == "AllGatherOp" and kinds[-1] == "MeshPartitionOp"
+    assert kinds.count("AllReduceOp") == 2
+    assert prog["inputs"][0]["desc"]["shape"] == [1, 32, 128]
+    assert prog["outputs"][0]["desc"]["shape"] == [1, 32, 128]
+    assert prog["mesh_shape"] == {"y": 1, "x": 2}
+    dims = graphs.decoder_shard_dims(io_seq_sharded=True, **kw)
+    assert dims[0] == 1 and dims[1] is None
+    # without the option the activations are replicated and the result is the full sequence
+    buf = graphs.build_binary(graphs.decoder_block_graph, mesh_shape=(1, 2), tp=2, presharded=True, **kw)
+    prog = Reader(S, buf).root("TTNNBinary")["programs"][0]
+    assert prog["inputs"][0]["desc"]["shape"] == [1, 64, 128] and prog["outputs"][0]["desc"]["shape"] == [1, 64, 128]

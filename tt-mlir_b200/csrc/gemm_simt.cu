@@ -34,22 +34,35 @@ __global__ void __launch_bounds__(256)
   float acc[4][4] = {};
   const int64_t kBegin = splitK > 1 ? split * kPer : 0;
   const int64_t kEnd = splitK > 1 ? (kBegin + kPer < K ? kBegin + kPer : K) : K;
-  for (int64_t k0 = kBegin; k0 < kEnd; k0 += BK) {
-    // 64x16 elements per operand, 256 threads -> 4 each.  Index so that the fastest-varying
-    // thread index follows the contiguous global dimension of each operand.
-    for (int i = threadIdx.x; i < BM * BK; i += 256) {
-      int mm, kk;
-      if (asK == 1) { kk = i % BK; mm = i / BK; } else { mm = i % BM; kk = i / BM; }
-      int64_t gm = m0 + mm, gk = k0 + kk;
-      sa[kk][mm] = (gm < M && gk < kEnd) ? toF32(A[gm * asM + gk * asK]) : 0.0f;
+  // Register prefetch: the global loads of k-step i+1 are issued before the products of k-step
+  // i, so their latency overlaps the arithmetic (each thread holds 4 + 4 operand values).
+  // The element a thread fetches: index i = threadIdx.x + 256 j, laid out so that the
+  // fastest-varying thread index follows the contiguous global dimension of each operand.
+  int aM[4], aK[4], bN[4], bK[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = threadIdx.x + 256 * j;
+    if (asK == 1) { aK[j] = i % BK; aM[j] = i / BK; } else { aM[j] = i % BM; aK[j] = i / BM; }
+    if (bsN == 1) { bN[j] = i % BN; bK[j] = i / BN; } else { bK[j] = i % BK; bN[j] = i / BK; }
+  }
+  float ra[4], rb[4];
+  auto fetch = [&](int64_t k0) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t gm = m0 + aM[j], gka = k0 + aK[j], gn = n0 + bN[j], gkb = k0 + bK[j];
+      ra[j] = (gm < M && gka < kEnd) ? toF32(A[gm * asM + gka * asK]) : 0.0f;
+      rb[j] = (gn < N && gkb < kEnd) ? toF32(B[gkb * bsK + gn * bsN]) : 0.0f;
     }
-    for (int i = threadIdx.x; i < BN * BK; i += 256) {
-      int nn, kk;
-      if (bsN == 1) { nn = i % BN; kk = i / BN; } else { kk = i % BK; nn = i / BK; }
-      int64_t gn = n0 + nn, gk = k0 + kk;
-      sb[kk][nn] = (gn < N && gk < kEnd) ? toF32(B[gk * bsK + gn * bsN]) : 0.0f;
+  };
+  if (kBegin < kEnd) fetch(kBegin);
+  for (int64_t k0 = kBegin; k0 < kEnd; k0 += BK) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      sa[aK[j]][aM[j]] = ra[j];
+      sb[bK[j]][bN[j]] = rb[j];
     }
     __syncthreads();
+    if (k0 + BK < kEnd) fetch(k0 + BK);
 #pragma unroll
     for (int kk = 0; kk < BK; ++kk) {
       float av[4], bv[4];

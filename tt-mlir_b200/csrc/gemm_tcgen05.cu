@@ -326,11 +326,28 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     // scheduler hide each other's instruction latencies in the longer epilogues.
     const int group = (warp - 2) / 4;
     const uint32_t stageOut = outBase + static_cast<uint32_t>(warp - 2) * (EPW == 4 ? 2u : 1u) * 4096u;
-    uint32_t accIt = static_cast<uint32_t>(group), chunkIt = 0, extraPhase = 0;
+    uint32_t chunkIt = 0, extraPhase = 0;
     bool alive = true;
-    const int64_t tileStep = static_cast<int64_t>(gridDim.x) * (EPW / 4);
-    for (int64_t tile = blockIdx.x + static_cast<int64_t>(group) * gridDim.x; tile < numTiles;
-         tile += tileStep, accIt += EPW / 4) {
+    // Tiles of this CTA are numbered 0 .. myTiles-1 (tile index = blockIdx.x + number * gridDim.x,
+    // accumulator = number & 1).  With two groups, group g drains the tiles with number = g mod 2.
+    // The last tile has no successor whose main loop could hide its epilogue, so there both groups
+    // work on it: its owner takes the even column chunks, the other group the odd ones.
+    const int64_t myTiles = blockIdx.x < numTiles ? (numTiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int64_t lastNo = myTiles - 1;
+    bool helped = false;
+    for (int64_t no = group;; no += EPW / 4) {
+      bool helper = false;
+      if (no >= myTiles) {
+        if (EPW == 8 && BN / CH >= 2 && lastNo >= 0 && (lastNo & 1) != group && !helped) {
+          no = lastNo;
+          helper = helped = true;
+        } else {
+          break;
+        }
+      }
+      const bool shared = EPW == 8 && BN / CH >= 2 && no == lastNo;
+      const int64_t tile = blockIdx.x + no * gridDim.x;
+      const uint32_t accIt = static_cast<uint32_t>(no);
       const int acc = accIt & 1;
       const uint32_t accPhase = (accIt >> 1) & 1u;
       if (!mbarWait(tmemFullBar(acc), accPhase, abortFlag, 4)) break;
@@ -350,7 +367,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
       }
       const uint32_t taddrRow = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
 #pragma unroll 1
-      for (int cc = 0; cc < BN / CH; ++cc) {
+      for (int cc = (shared && helper) ? 1 : 0; cc < BN / CH; cc += shared ? 2 : 1) {
         const int64_t col0 = n0 + cc * CH;
         if (col0 >= segN || p.debug == 2) break; // warp-uniform
         const uint32_t buf = stageOut + (EPW == 4 ? (chunkIt & 1u) * 4096u : 0u);
@@ -519,6 +536,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
         ++chunkIt;
       }
       if (!alive) break;
+      if (helper) break; // the helper's visit was the last thing this group does
       tcFenceBefore();
       mbarArrive(tmemEmptyBar(acc)); // all 128 epilogue threads arrive: the accumulator may be overwritten
     }

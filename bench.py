@@ -56,7 +56,31 @@ class ClockSampler:
         self._stop = threading.Event()
         self._thread = None
 
+    def _run_nvml(self):
+        """NVML (read-only queries) every few milliseconds: the timed region of the default run is
+        tens of milliseconds long, too short for a process per sample."""
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(self.gpu)
+        mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+        bits = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+        try:
+            reasons_of = pynvml.nvmlDeviceGetCurrentClocksEventReasons
+        except AttributeError:
+            reasons_of = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self._stop.is_set():
+            sm = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+            r = reasons_of(h)
+            self.samples.append([str(sm), str(mx)] + ["Active" if r & bits[n] else "Not Active"
+                                                     for n in ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")])
+            self._stop.wait(0.003)
+
     def _run(self):
+        try:
+            self._run_nvml()
+            return
+        except Exception:
+            pass
         while not self._stop.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",

@@ -409,6 +409,98 @@ def run_side(args):
     print(json.dumps(line))
 
 
+def run_all_reduce(args):
+    """The block's all-reduce (sum of [2048, 4096] bf16, 16.8 MB) on an in-process 1 x N mesh: the
+    peer-memory kernel with its operand already staged (as after a GEMM), with a staging copy, with
+    the fused residual add, and NCCL.  One process launches on all N devices in turn, so the
+    figures include that launch skew.  With TTB_SYMM_STAMPS=1 the phase times of block 0 are printed."""
+    from __graft_entry__ import load_package
+    load_package()
+    from ttmlir_b200 import runtime_api as rt
+    lib, n = rt.lib, args.gpus
+    count = 2048 * 4096
+    devs = (ctypes.c_int * n)(*range(n))
+    symms, comms = (ctypes.c_void_p * n)(), (ctypes.c_void_p * n)()
+
+    def ck(rc):
+        if rc != 0:
+            raise RuntimeError(lib.ttb_last_error().decode())
+    ck(lib.ttb_symm_create_all(symms, n, devs, ctypes.c_size_t(64 << 20)))
+    ck(lib.ttb_comm_init_all(comms, n, devs))
+    streams, ins, outs, ress = [], [], [], []
+    for d in range(n):
+        ck(lib.ttb_set_device(d))
+        st = ctypes.c_void_p()
+        ck(lib.ttb_stream_create(ctypes.byref(st)))
+        streams.append(st)
+        for lst in (ins, outs, ress):
+            p = ctypes.c_void_p()
+            ck(lib.ttb_malloc(ctypes.byref(p), ctypes.c_size_t(count * 2), st))
+            ck(lib.ttb_memset(p, 0, ctypes.c_size_t(count * 2), st))
+            lst.append(p)
+        ck(lib.ttb_stream_sync(st))
+
+    def symm(staged, residual):
+        for d in range(n):
+            ck(lib.ttb_set_device(d))
+            src = ins[d]
+            if staged:
+                src = ctypes.c_void_p()
+                ck(lib.ttb_symm_input_buffer(symms[d], ctypes.c_size_t(count * 2), ctypes.byref(src)))
+            ck(lib.ttb_symm_all_reduce(symms[d], src, ress[d] if residual else None, outs[d], ctypes.c_size_t(count), 2, streams[d]))
+
+    def nccl():
+        ck(lib.ttb_group_start())
+        for d in range(n):
+            ck(lib.ttb_set_device(d))
+            ck(lib.ttb_all_reduce(comms[d], ins[d], outs[d], ctypes.c_size_t(count), 2, 0, streams[d]))
+        ck(lib.ttb_group_end())
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        for d in range(n):
+            ck(lib.ttb_set_device(d))
+            ck(lib.ttb_stream_sync(streams[d]))
+        ck(lib.ttb_set_device(0))
+        ev = Events(lib, streams[0].value)
+        ev.start()
+        for _ in range(args.steps):
+            fn()
+        ck(lib.ttb_set_device(0))
+        ms = ev.stop_ms()
+        for d in range(n):
+            ck(lib.ttb_set_device(d))
+            ck(lib.ttb_stream_sync(streams[d]))
+        return ms / args.steps * 1e3
+    res = {"staged": timed(lambda: symm(True, False)), "staged_residual": timed(lambda: symm(True, True)),
+           "copied": timed(lambda: symm(False, False)), "nccl": timed(nccl)}
+    phases = None
+    if os.environ.get("TTB_SYMM_STAMPS") == "1":
+        symm(True, True)
+        for d in range(n):
+            ck(lib.ttb_set_device(d))
+            ck(lib.ttb_stream_sync(streams[d]))
+        st = (ctypes.c_ulonglong * 8)()
+        ck(lib.ttb_symm_stamps(symms[0], st))
+        phases = {"ns": [int(st[i + 1]) - int(st[i]) for i in range(5) if st[i + 1] >= st[i]],
+                  "names": ["stage", "barrier", "reduce", "barrier", "gather"]}
+    status = ctypes.c_int(-1)
+    ck(lib.ttb_symm_status(symms[0], ctypes.byref(status)))
+    peaks = measured_peaks()
+    us = res["staged_residual"]
+    # bytes crossing the links per rank and direction: one-shot (n = 2) pulls the whole operand,
+    # two-shot pulls and pushes (n-1)/n of it
+    link_bytes = count * 2 * (1.0 if n == 2 else 2.0 * (n - 1) / n)
+    print(json.dumps({"metric": "all_reduce_us", "value": us, "unit": "us", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+                      "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "all_reduce(sum) of [2048, 4096] bf16 + residual add, in-process 1xN mesh"},
+                      "us": res, "phases_block0": phases, "status": status.value,
+                      "roofline": {"bound": "nvlink", "achieved": link_bytes / (us * 1e-6) / 1e9, "peak": 770.0, "unit": "GB/s",
+                                   "frac": link_bytes / (us * 1e-6) / 1e9 / 770.0,
+                                   "peak_source": "measured peer copy per direction on this pool"}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -421,10 +513,13 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="for runs under a profiler: exactly --warmup warm-up steps, then --steps steps, nothing else")
     ap.add_argument("--workload", default="decoder",
-                    choices=["decoder", "mlp", "quant", "quant_int8", "w8_linear", "bottleneck"],
+                    choices=["decoder", "mlp", "quant", "quant_int8", "w8_linear", "bottleneck", "all_reduce"],
                     help="decoder (default) is the benchmark; the others report the remaining configurations")
     args = ap.parse_args()
 
+    if args.workload == "all_reduce":
+        run_all_reduce(args)
+        return
     if args.workload != "decoder":
         run_side(args)
         return

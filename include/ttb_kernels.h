@@ -78,6 +78,18 @@ TTB_API int ttb_event_record(void *event, void *stream);
 TTB_API int ttb_event_sync(void *event);
 TTB_API int ttb_stream_wait_event(void *stream, void *event);
 TTB_API int ttb_event_elapsed_ms(void *start, void *stop, float *ms);
+/* Traces: what BeginTraceCaptureOp / EndTraceCaptureOp / ExecuteTraceOp do on the device
+ * (runtime/lib/ttnn/operations/trace/{begin_trace_capture,end_trace_capture,execute_trace}.cpp call
+ * ::ttnn::operations::trace::begin_trace_capture / end_trace_capture / execute_trace).  Everything
+ * enqueued on `stream` between begin and end (kernels, stream-ordered allocations and frees) is
+ * recorded instead of run; end turns the recording into an executable CUDA graph; launch replays
+ * it.  abort ends a recording that failed half way and leaves the stream usable. */
+TTB_API int ttb_trace_begin(void *stream);
+TTB_API int ttb_trace_end(void *stream, void **trace);
+TTB_API int ttb_trace_abort(void *stream);
+TTB_API int ttb_trace_launch(void *trace, void *stream);
+TTB_API int ttb_trace_destroy(void *trace);
+TTB_API int ttb_stream_is_recording(void *stream, int *recording);
 /* Number of kernels this library has launched in the calling process (all threads). */
 TTB_API uint64_t ttb_launch_count(void);
 /* Per-launch profiling (the CUDA-event counterpart of the reference's Tracy zones around each op,

@@ -111,6 +111,18 @@ TTRT_API int ttrt_tensor_host_ptr(ttrt_tensor_t t, void **ptr);
 TTRT_API int ttrt_submit(ttrt_device_t dev, ttrt_binary_t bin, uint32_t program, const ttrt_tensor_t *inputs,
                          uint32_t n_inputs, ttrt_tensor_t *outputs, uint32_t cap, uint32_t *n_outputs);
 
+/* ---- sub-program state: traces, const-eval cache, counters ---------------------------------- */
+TTRT_API int ttrt_binary_id(ttrt_binary_t bin, uint64_t *id);                     /* Binary::id */
+/* releaseTrace(device, binaryId, mainProgramId), runtime.h:182-183 */
+TTRT_API int ttrt_release_trace(ttrt_device_t dev, uint64_t binary_id, size_t main_program);
+/* GlobalTensorCache::size / clear (detail/ttnn/types/global_tensor_cache.h:77-93) */
+TTRT_API int ttrt_const_eval_cache_size(size_t *n);
+TTRT_API int ttrt_const_eval_cache_clear(void);
+/* debug::Stats::getStat / clear (debug.h:175-208).  Counters kept by this runtime: ConstEvalCacheHit,
+ * ConstEvalCacheMiss, TraceCacheMiss, CapturedTrace, ExecutedTrace. */
+TTRT_API int ttrt_stat_get(const char *name, int64_t *value);
+TTRT_API int ttrt_stats_clear(void);
+
 /* ---- debug hooks (runtime/include/tt/runtime/debug.h:77-158, runtime.h:229-283) -------------- */
 typedef void (*ttrt_op_callback_t)(ttrt_binary_t bin, void *program_ctx, void *op_ctx, void *user);
 TTRT_API int ttrt_register_op_hooks(ttrt_op_callback_t pre, ttrt_op_callback_t post, void *user); /* Hooks::get(pre, post) */

@@ -246,6 +246,70 @@ int ttb_memset(void *dst, int byte, size_t bytes, void *stream) {
   return TTB_OK;
 }
 
+// ---- traces: a stretch of a stream's work recorded once and replayed as one CUDA graph ----
+int ttb_trace_begin(void *stream) {
+  // Thread-local mode: other threads may keep allocating and copying while this one records.
+  TTB_CUDA(cudaStreamBeginCapture(asStream(stream), cudaStreamCaptureModeThreadLocal));
+  return TTB_OK;
+}
+
+int ttb_trace_end(void *stream, void **trace) {
+  TTB_CHECK(trace != nullptr, "trace is null");
+  *trace = nullptr;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(asStream(stream), &graph);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    if (graph) cudaGraphDestroy(graph);
+    ::ttb::setLastError(std::string("the recording was invalidated: ") + cudaGetErrorString(e));
+    return TTB_ERR_CUDA;
+  }
+  cudaGraphExec_t exec = nullptr;
+  e = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    ::ttb::setLastError(std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
+    return TTB_ERR_CUDA;
+  }
+  *trace = exec;
+  return TTB_OK;
+}
+
+int ttb_trace_abort(void *stream) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(asStream(stream), &st) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return TTB_OK;
+  }
+  if (st != cudaStreamCaptureStatusNone) {
+    cudaGraph_t graph = nullptr;
+    (void)cudaStreamEndCapture(asStream(stream), &graph);
+    (void)cudaGetLastError();
+    if (graph) cudaGraphDestroy(graph);
+  }
+  return TTB_OK;
+}
+
+int ttb_trace_launch(void *trace, void *stream) {
+  TTB_CHECK(trace != nullptr, "trace is null");
+  TTB_CUDA(cudaGraphLaunch(reinterpret_cast<cudaGraphExec_t>(trace), asStream(stream)));
+  return TTB_OK;
+}
+
+int ttb_trace_destroy(void *trace) {
+  if (trace) TTB_CUDA(cudaGraphExecDestroy(reinterpret_cast<cudaGraphExec_t>(trace)));
+  return TTB_OK;
+}
+
+int ttb_stream_is_recording(void *stream, int *recording) {
+  TTB_CHECK(recording != nullptr, "recording is null");
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  TTB_CUDA(cudaStreamIsCapturing(asStream(stream), &st));
+  *recording = st == cudaStreamCaptureStatusActive ? 1 : 0;
+  return TTB_OK;
+}
+
 int ttb_event_create(void **event) {
   TTB_CHECK(event != nullptr, "event is null");
   cudaEvent_t e;

@@ -90,15 +90,33 @@ __global__ void __launch_bounds__(256)
     __syncthreads();
     if (!lastBlock) return;
     __threadfence();
-    const float *all = partials + tile * splitK * (BM * BN);
+    // Every element is summed in split order, but the loads of four splits (64 per thread) are
+    // in flight together: one element at a time, the loop would pay an L2 round trip per load.
+    const float *all = partials + tile * splitK * (BM * BN) + threadIdx.x;
+    float sum[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) sum[e] = 0.0f;
+    for (int sp = 0; sp < splitK; sp += 4) {
+      float v[4][16];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (sp + u < splitK) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) v[u][e] = __ldcg(all + (sp + u) * (BM * BN) + e * 256);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (sp + u < splitK) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) sum[e] += v[u][e];
+        }
+      }
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float sum = 0.0f;
-        for (int sp = 0; sp < splitK; ++sp) sum += __ldcg(all + sp * (BM * BN) + (i * 4 + j) * 256 + threadIdx.x);
-        acc[i][j] = sum;
-      }
+      for (int j = 0; j < 4; ++j) acc[i][j] = sum[i * 4 + j];
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {

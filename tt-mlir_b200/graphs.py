@@ -16,15 +16,38 @@ import torch
 
 
 # ---------------------------------------------------------------- config 1: f32 MLP
+def mlp_body(b, x, w1, b1, w2, b2):
+    h = b.relu(b.add(b.matmul(x, w1, loc="fc1"), b1, loc="fc1_bias"), loc="relu")
+    y = b.add(b.matmul(h, w2, loc="fc2"), b2, loc="fc2_bias")
+    return b.softmax(y, dim=-1, loc="softmax")
+
+
 def mlp_graph(b, batch=128, d_in=784, d_hidden=256, d_out=10, dtype="Float32"):
     x = b.input([batch, d_in], dtype)
     w1 = b.input([d_in, d_hidden], dtype)
     b1 = b.input([d_hidden], dtype)
     w2 = b.input([d_hidden, d_out], dtype)
     b2 = b.input([d_out], dtype)
-    h = b.relu(b.add(b.matmul(x, w1, loc="fc1"), b1, loc="fc1_bias"), loc="relu")
-    y = b.add(b.matmul(h, w2, loc="fc2"), b2, loc="fc2_bias")
-    b.output(b.softmax(y, dim=-1, loc="softmax"))
+    b.output(mlp_body(b, x, w1, b1, w2, b2))
+
+
+def mlp_traced_binary(batch=128, d_in=784, d_hidden=256, d_out=10, dtype="Float32") -> bytes:
+    """The MLP as the compiler emits it with `enable-trace=true`: program 0 takes the same five
+    inputs as `mlp_graph` (the activation on host, the parameters on device) and holds one
+    CaptureOrExecuteTraceOp; the ops live in a private traced function (see
+    ttnn_builder.BinaryBuilder.hoist_trace)."""
+    from .ttnn_builder import BinaryBuilder
+    bb = BinaryBuilder()
+    main = bb.program("mlp")
+    x = main.input([batch, d_in], dtype, on_device=False)
+    w1 = main.input([d_in, d_hidden], dtype)
+    b1 = main.input([d_hidden], dtype)
+    w2 = main.input([d_hidden, d_out], dtype)
+    b2 = main.input([d_out], dtype)
+    outs = bb.hoist_trace(main, "mlp", [w1, b1, w2, b2, x],
+                          lambda p, a: [mlp_body(p, a[4], a[0], a[1], a[2], a[3])])
+    main.output(*outs)
+    return bb.finish()
 
 
 def mlp_inputs(batch=128, d_in=784, d_hidden=256, d_out=10, seed=0, dtype=torch.float32):
@@ -61,6 +84,27 @@ def w8_linear_graph(b, m=2048, k=4096, n=11008):
     bias = b.input([n], "BFloat16")
     w = b.dequantize(wq, scales, 0, out_dtype="BFloat16", axis=0, loc="dequant_weight")
     b.output(b.linear(a, w, bias, transpose_b=True, loc="linear"))
+
+
+def w8_linear_const_eval_binary(m=2048, k=4096, n=11008) -> bytes:
+    """Config 3 as the compiler emits it with `enable-const-eval=true`: the weight's dequantization
+    depends on parameters only, so it is hoisted into a private const-eval function that program 0
+    reaches through a LoadCachedOp; the runtime evaluates it on the first submit and caches the
+    bf16 weight.  Same inputs, same results as `w8_linear_graph`."""
+    from .ttnn_builder import BinaryBuilder
+    bb = BinaryBuilder()
+    main = bb.program("w8_linear")
+    a = main.input([m, k], "BFloat16")
+    wq = main.input([n, k], "Int8")
+    scales = main.input([n], "Float32")
+    bias = main.input([n], "BFloat16")
+    ce = bb.private_program("w8_linear_const_eval_0")
+    c_wq = ce.input([n, k], "Int8")
+    c_scales = ce.input([n], "Float32")
+    ce.output(ce.dequantize(c_wq, c_scales, 0, out_dtype="BFloat16", axis=0, loc="dequant_weight"))
+    (w,) = main.load_cached(ce, [wq, scales])
+    main.output(main.linear(a, w, bias, transpose_b=True, loc="linear"))
+    return bb.finish()
 
 
 def w8_linear_inputs(m=2048, k=4096, n=11008, seed=2):

@@ -433,6 +433,47 @@ int ttrt_submit(ttrt_device_t dev, ttrt_binary_t bin, uint32_t program, const tt
   TTRT_CATCH
 }
 
+// ---- sub-program state --------------------------------------------------------------------------
+int ttrt_binary_id(ttrt_binary_t bin, uint64_t *id) {
+  TTRT_ARG(bin && id)
+  TTRT_TRY
+  *id = B(bin).id();
+  TTRT_CATCH
+}
+
+int ttrt_release_trace(ttrt_device_t dev, uint64_t binary_id, size_t main_program) {
+  TTRT_ARG(dev)
+  TTRT_TRY
+  releaseTrace(D(dev), binary_id, main_program);
+  TTRT_CATCH
+}
+
+int ttrt_const_eval_cache_size(size_t *n) {
+  TTRT_ARG(n)
+  TTRT_TRY
+  *n = ::tt::runtime::cuda::ConstEvalCache::get().size();
+  TTRT_CATCH
+}
+
+int ttrt_const_eval_cache_clear(void) {
+  TTRT_TRY
+  ::tt::runtime::cuda::ConstEvalCache::get().clear();
+  TTRT_CATCH
+}
+
+int ttrt_stat_get(const char *name, int64_t *value) {
+  TTRT_ARG(name && value)
+  TTRT_TRY
+  *value = debug::Stats::get().getStat(name);
+  TTRT_CATCH
+}
+
+int ttrt_stats_clear(void) {
+  TTRT_TRY
+  debug::Stats::get().clear();
+  TTRT_CATCH
+}
+
 // ---- hooks --------------------------------------------------------------------------------------
 int ttrt_register_op_hooks(ttrt_op_callback_t pre, ttrt_op_callback_t post, void *user) {
   TTRT_TRY

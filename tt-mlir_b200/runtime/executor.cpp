@@ -36,6 +36,9 @@ struct ProgramInfo {
   std::unordered_map<uint32_t, uint32_t> useCount; // consumers other than DeallocateOp
   std::unordered_map<uint32_t, uint32_t> firstUse; // index of the first such consumer
   std::unordered_set<uint32_t> outputs;
+  // CopyOp(src -> dst): when the copy is src's only use and dst's only use, src's producer writes
+  // into dst's memory and the copy has nothing left to do.
+  std::unordered_map<uint32_t, const fbt::TensorRef *> copyTarget;
 };
 
 static void pushRef(std::vector<const fbt::TensorRef *> &v, const fbt::TensorRef *r) {
@@ -198,6 +201,39 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     if (o->outs()) for (const auto *r : *o->outs()) pushRef(outs, r);
     break;
   }
+  case OpType::LoadCachedOp: {
+    const auto *o = op->type_as_LoadCachedOp();
+    if (o->inputs()) for (const auto *r : *o->inputs()) pushRef(ins, r);
+    if (o->outputs()) for (const auto *r : *o->outputs()) pushRef(outs, r);
+    break;
+  }
+  case OpType::FuncCallOp: {
+    const auto *o = op->type_as_FuncCallOp();
+    if (o->inputs()) for (const auto *r : *o->inputs()) pushRef(ins, r);
+    if (o->outputs()) for (const auto *r : *o->outputs()) pushRef(outs, r);
+    break;
+  }
+  case OpType::CaptureOrExecuteTraceOp: {
+    const auto *o = op->type_as_CaptureOrExecuteTraceOp();
+    if (o->inputs()) for (const auto *r : *o->inputs()) pushRef(ins, r);
+    if (o->outputs()) for (const auto *r : *o->outputs()) pushRef(outs, r);
+    break;
+  }
+  case OpType::BeginTraceCaptureOp: pushRef(outs, op->type_as_BeginTraceCaptureOp()->trace_id()); break;
+  case OpType::EndTraceCaptureOp: pushRef(ins, op->type_as_EndTraceCaptureOp()->trace_id()); break;
+  case OpType::ExecuteTraceOp: pushRef(ins, op->type_as_ExecuteTraceOp()->trace_id()); break;
+  case OpType::WriteTensorOp: {
+    const auto *o = op->type_as_WriteTensorOp();
+    pushRef(ins, o->host_tensor());
+    pushRef(ins, o->device_tensor());
+    break;
+  }
+  case OpType::CopyOp: {
+    const auto *o = op->type_as_CopyOp();
+    pushRef(ins, o->src());
+    pushRef(ins, o->dst());
+    break;
+  }
   case OpType::ArangeOp: pushRef(outs, op->type_as_ArangeOp()->out()); break;
   case OpType::ConstantOp: pushRef(outs, op->type_as_ConstantOp()->out()); break;
   case OpType::EmptyOp: pushRef(outs, op->type_as_EmptyOp()->out()); break;
@@ -227,6 +263,9 @@ static ProgramInfo programInfo(const fbt::Program *prog) {
       for (const auto *r : ins) {
         info.useCount[r->global_id()]++;
         info.firstUse.emplace(r->global_id(), at);
+      }
+      if (const auto *cp = op->type_as_CopyOp()) {
+        if (cp->src() && cp->dst()) info.copyTarget.emplace(cp->src()->global_id(), cp->dst());
       }
     }
   }
@@ -386,6 +425,18 @@ private:
   void runMeshPartition(const fbt::MeshPartitionOp *op);
   void runDistribute(const fbt::DistributeTensorOp *op);
   void runAggregate(const fbt::AggregateTensorOp *op);
+  // sub-programs: const-eval cache, calls, traces
+  std::vector<TensorPtr> runSubProgram(uint32_t index, const std::vector<TensorPtr> &inputs);
+  void runLoadCached(const fbt::LoadCachedOp *op);
+  void runFuncCall(const fbt::FuncCallOp *op);
+  void runBeginTraceCapture(const fbt::BeginTraceCaptureOp *op);
+  void runEndTraceCapture(const fbt::EndTraceCaptureOp *op);
+  void runExecuteTrace(const fbt::ExecuteTraceOp *op);
+  void runCaptureOrExecuteTrace(const fbt::CaptureOrExecuteTraceOp *op);
+  void updateTraceInputSlots(const fbt::CaptureOrExecuteTraceOp *op, std::vector<TensorPtr> &slots, bool residentOnly);
+  void runWriteTensor(const fbt::WriteTensorOp *op);
+  void runCopy(const fbt::CopyOp *op);
+  void refuseWhileRecording(const char *what) const;
 
   // gather-copy of a strided view of `in` into a new dense tensor shaped like `outShape`
   TensorPtr stridedView(const TensorPtr &in, const std::vector<uint32_t> &outShape, const std::vector<int64_t> &inStrides,
@@ -440,6 +491,8 @@ Executor::Executor(std::shared_ptr<DeviceImpl> d, Binary &b, uint32_t pi, std::v
       view->shards = t->shards;
       view->device = t->device;
       view->retain = true;
+      view->base = t->base ? t->base : t;
+      view->version.store(view->base->version.load());
       t = view;
     }
     pool[ref->global_id()] = t;
@@ -481,6 +534,7 @@ std::pair<TensorPtr, std::vector<int64_t>> Executor::viewOf(const fbt::TensorRef
 TensorPtr Executor::getDevice(const fbt::TensorRef *ref) {
   TensorPtr t = get(ref);
   if (t->storage == Storage::Host) {
+    refuseWhileRecording("a host-to-device copy");
     t = toDevice(t, dev, t->dtype);
     pool[ref->global_id()] = t;
   }
@@ -493,6 +547,15 @@ void Executor::put(const fbt::TensorRef *ref, TensorPtr t) {
 }
 
 TensorPtr Executor::allocOut(const fbt::TensorRef *ref) {
+  auto ct = info.copyTarget.find(ref->global_id());
+  if (ct != info.copyTarget.end() && singleUse(ref) && singleUse(ct->second)) {
+    auto dst = pool.find(ct->second->global_id());
+    // (retained: the DeallocateOp that follows the copy must not take the destination with it)
+    if (dst != pool.end() && dst->second->storage == Storage::Device && dst->second->allocated() && dst->second->retain &&
+        dst->second->dtype == refDtype(ref) && dst->second->shape == refShape(ref)) {
+      return dst->second; // the CopyOp that follows finds source and destination identical
+    }
+  }
   auto t = makeDeviceTensor(dev, refShape(ref), refDtype(ref));
   t->layout = refLayout(ref);
   return t;
@@ -663,6 +726,14 @@ size_t Executor::runOp(size_t i) {
   case OpType::MeshPartitionOp: runMeshPartition(op->type_as_MeshPartitionOp()); break;
   case OpType::DistributeTensorOp: runDistribute(op->type_as_DistributeTensorOp()); break;
   case OpType::AggregateTensorOp: runAggregate(op->type_as_AggregateTensorOp()); break;
+  case OpType::LoadCachedOp: runLoadCached(op->type_as_LoadCachedOp()); break;
+  case OpType::FuncCallOp: runFuncCall(op->type_as_FuncCallOp()); break;
+  case OpType::BeginTraceCaptureOp: runBeginTraceCapture(op->type_as_BeginTraceCaptureOp()); break;
+  case OpType::EndTraceCaptureOp: runEndTraceCapture(op->type_as_EndTraceCaptureOp()); break;
+  case OpType::ExecuteTraceOp: runExecuteTrace(op->type_as_ExecuteTraceOp()); break;
+  case OpType::CaptureOrExecuteTraceOp: runCaptureOrExecuteTrace(op->type_as_CaptureOrExecuteTraceOp()); break;
+  case OpType::WriteTensorOp: runWriteTensor(op->type_as_WriteTensorOp()); break;
+  case OpType::CopyOp: runCopy(op->type_as_CopyOp()); break;
   case OpType::CpuOp:
     TTRT_FATAL("CpuOp '", op->type_as_CpuOp()->func_name() ? op->type_as_CpuOp()->func_name()->str() : "",
                "': CPU-hoisted functions are not executed by this target (no CPU fallback); recompile the graph "
@@ -684,12 +755,14 @@ void Executor::runGetDevice(const fbt::GetDeviceOp *op) {
 
 void Executor::runToDevice(const fbt::ToDeviceOp *op) {
   TensorPtr in = get(op->in());
+  if (in->storage == Storage::Host) refuseWhileRecording("a host-to-device copy");
   TensorPtr out = in->storage == Storage::Host ? toDevice(in, dev, in->dtype) : in;
   put(op->out(), out);
 }
 
 void Executor::runFromDevice(const fbt::FromDeviceOp *op) {
   TensorPtr in = get(op->in());
+  if (in->storage == Storage::Device) refuseWhileRecording("a device-to-host read");
   put(op->out(), in->storage == Storage::Device ? toHostTensor(in, true) : in);
 }
 
@@ -792,6 +865,7 @@ void Executor::runConstant(const fbt::ConstantOp *op) {
   buf->keepAlive = bin.handle;
   host->shards.push_back(buf);
   if (refOnDevice(op->out())) {
+    refuseWhileRecording("uploading an embedded constant (hoist it out of the traced function)");
     TensorPtr out = toDevice(host, dev, refDtype(op->out()));
     out->layout = refLayout(op->out());
     put(op->out(), out);
@@ -2005,6 +2079,9 @@ TensorPtr Executor::allocForAllReduce(const fbt::TensorRef *ref) {
 // (one launch per rank, the residual add included); everything else through NCCL, with the add
 // as its own launch.
 void Executor::allReduce(const TensorPtr &in, const TensorPtr &residual, const TensorPtr &out, int reduceType) {
+  // The peer-memory kernel numbers its launches (a replayed launch would repeat a number its
+  // peers have moved past), so collectives stay outside traces.
+  refuseWhileRecording("a collective");
   bool isFloat = in->dtype == DataType::BFloat16 || in->dtype == DataType::Float16 || in->dtype == DataType::Float32;
   if (reduceType == 0 && isFloat && in->bytes() % 16 == 0 && symmReady(in->bytes())) {
     eachRank([&](size_t i, const RankCtx &r) {
@@ -2079,6 +2156,7 @@ void Executor::runAllGather(const fbt::AllGatherOp *op) {
     put(op->out(), in);
     return;
   }
+  refuseWhileRecording("a collective");
   size_t rank = in->shape.size();
   int d = normDim(op->all_gather_dim(), rank);
   TensorPtr out = allocOut(op->out());
@@ -2111,6 +2189,7 @@ void Executor::runReduceScatter(const fbt::ReduceScatterOp *op) {
     put(op->out(), in);
     return;
   }
+  refuseWhileRecording("a collective");
   size_t rank = in->shape.size();
   int d = normDim(op->scatter_dim(), rank);
   TensorPtr out = allocOut(op->out());
@@ -2273,11 +2352,282 @@ void Executor::runAggregate(const fbt::AggregateTensorOp *op) {
   put(op->out(), out);
 }
 
+// ---- sub-programs: const-eval cache, calls, traces --------------------------------------------------
+// A program of the same binary run on behalf of an op of this one (the reference constructs a
+// nested ProgramExecutor the same way: operations/cache/load_cached.cpp:71-75,
+// operations/mlir_native/func_call.cpp:25-31).
+std::vector<TensorPtr> Executor::runSubProgram(uint32_t index, const std::vector<TensorPtr> &inputs) {
+  std::vector<Tensor> in;
+  in.reserve(inputs.size());
+  for (const TensorPtr &t : inputs) in.push_back(wrapTensor(t));
+  Executor sub(dev, bin, index, in);
+  std::vector<Tensor> out = sub.run();
+  std::vector<TensorPtr> res;
+  res.reserve(out.size());
+  for (const Tensor &t : out) res.push_back(unwrapTensor(t));
+  return res;
+}
+
+// LoadCachedOp (operations/cache/load_cached.cpp:20-91): the outputs of a const-eval program are
+// computed once per (device, program hash, versions of the inputs) and kept, retained, in a
+// process-wide cache; later submits of any binary with the same function bind the cached tensors.
+void Executor::runLoadCached(const fbt::LoadCachedOp *op) {
+  ConstEvalKey key;
+  key.device = dev.get();
+  key.hash = op->program_hash() ? op->program_hash()->str() : std::string();
+  if (key.hash.empty()) {
+    // no hash in the file: the function is only shared within this binary
+    key.hash = strcat_("binary", bin.id(), ":", op->callee_name() ? op->callee_name()->str() : "", ":", op->program_idx());
+  }
+  std::vector<TensorPtr> ins, roots;
+  if (op->inputs()) {
+    for (const auto *ref : *op->inputs()) {
+      TensorPtr t = get(ref);
+      TensorPtr root = t->base ? t->base : t;
+      key.inputVersions.push_back(root->version.load());
+      ins.push_back(t);
+      roots.push_back(root);
+    }
+  }
+  std::vector<TensorPtr> outs;
+  if (!ConstEvalCache::get().find(key, outs)) {
+    refuseWhileRecording("evaluating a const-eval function");
+    outs = runSubProgram(op->program_idx(), ins);
+    for (const TensorPtr &t : outs) t->retain = true; // DeallocateOps of any program leave them alone
+    ConstEvalCache::get().store(key, roots, outs);
+  }
+  uint32_t nOut = op->outputs() ? op->outputs()->size() : 0;
+  TTRT_ASSERT(outs.size() == nOut, "const-eval function returned ", outs.size(), " tensors, the op declares ", nOut);
+  for (uint32_t i = 0; i < nOut; ++i) put(op->outputs()->Get(i), outs[i]);
+}
+
+void Executor::runFuncCall(const fbt::FuncCallOp *op) {
+  TTRT_ASSERT(!op->semaphore_inputs() || op->semaphore_inputs()->size() == 0,
+              "global semaphores are a Tenstorrent fabric object and have no counterpart here");
+  std::vector<TensorPtr> ins;
+  if (op->inputs()) {
+    for (const auto *ref : *op->inputs()) ins.push_back(get(ref));
+  }
+  std::vector<TensorPtr> outs = runSubProgram(op->program_id(), ins);
+  uint32_t nOut = op->outputs() ? op->outputs()->size() : 0;
+  TTRT_ASSERT(outs.size() == nOut, "Number of outputs does not match");
+  for (uint32_t i = 0; i < nOut; ++i) put(op->outputs()->Get(i), outs[i]);
+}
+
+void Executor::refuseWhileRecording(const char *what) const {
+  TTRT_ASSERT(dev->recordingTrace == 0, what, " is not possible while a trace is being recorded");
+}
+
+static TensorPtr traceIdTensor(uint32_t id) {
+  TensorPtr t = makeHostTensor({}, DataType::UInt32, 1);
+  *static_cast<uint32_t *>(t->shards[0]->ptr) = id;
+  return t;
+}
+
+static uint32_t traceIdOf(const TensorPtr &t) {
+  TTRT_ASSERT(t && t->storage == Storage::Host && t->dtype == DataType::UInt32 && t->volume() == 1 && t->allocated(),
+              "Trace ID must be UINT32");
+  return *static_cast<const uint32_t *>(t->shards[0]->ptr);
+}
+
+// BeginTraceCaptureOp (operations/trace/begin_trace_capture.cpp:12-27): from here to the matching
+// EndTraceCaptureOp the compute stream records instead of running.  The trace id is a host scalar.
+void Executor::runBeginTraceCapture(const fbt::BeginTraceCaptureOp *op) {
+  TTRT_ASSERT(dev->recordingTrace == 0, "a trace is already being recorded on this device");
+  TTRT_ASSERT(!dev->multiProcess, "traces are recorded by the process that owns the whole mesh");
+  uint32_t id = dev->nextTraceId++;
+  size_t begun = 0;
+  try {
+    eachRank([&](size_t, const RankCtx &r) {
+      TTB_CALL(ttb_trace_begin(r.stream));
+      ++begun;
+    });
+  } catch (...) {
+    for (size_t i = 0; i < begun; ++i) ttb_trace_abort(dev->locals[i].stream);
+    throw;
+  }
+  dev->recordingTrace = id;
+  put(op->trace_id(), traceIdTensor(id));
+}
+
+void Executor::runEndTraceCapture(const fbt::EndTraceCaptureOp *op) {
+  uint32_t id = traceIdOf(get(op->trace_id()));
+  TTRT_ASSERT(id != 0 && id == dev->recordingTrace, "EndTraceCaptureOp names trace ", id, " but trace ",
+              dev->recordingTrace, " is being recorded");
+  dev->recordingTrace = 0;
+  TraceGraph g;
+  g.execs.assign(dev->locals.size(), nullptr);
+  std::string failure;
+  for (size_t i = 0; i < dev->locals.size(); ++i) {
+    ttb_set_device(dev->locals[i].cudaDevice);
+    if (!failure.empty()) {
+      ttb_trace_abort(dev->locals[i].stream);
+    } else if (ttb_trace_end(dev->locals[i].stream, &g.execs[i]) != TTB_OK) {
+      failure = ttb_last_error();
+    }
+  }
+  if (!failure.empty()) {
+    for (void *e : g.execs) ttb_trace_destroy(e);
+    TTRT_FATAL("recording trace ", id, " failed: ", failure);
+  }
+  dev->traces[id] = std::move(g);
+}
+
+void Executor::runExecuteTrace(const fbt::ExecuteTraceOp *op) {
+  uint32_t id = traceIdOf(get(op->trace_id()));
+  refuseWhileRecording("replaying a trace");
+  auto it = dev->traces.find(id);
+  TTRT_ASSERT(it != dev->traces.end(), "no recorded trace has id ", id);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_trace_launch(it->second.execs.at(i), r.stream));
+    if (op->blocking()) TTB_CALL(ttb_stream_sync(r.stream));
+  });
+}
+
+// Brings the trace's persistent input slots up to date with the op's current inputs
+// (operations/trace/capture_or_execute_trace.cpp:98-154): a slot whose version equals its input's
+// is left alone; otherwise the input is copied in (device to device for constants, parameters and
+// caches the caller replaced; host to device for everything else) and the versions are synchronised.
+void Executor::updateTraceInputSlots(const fbt::CaptureOrExecuteTraceOp *op, std::vector<TensorPtr> &slots,
+                                     bool residentOnly) {
+  uint32_t nIn = op->inputs() ? op->inputs()->size() : 0;
+  TTRT_ASSERT(slots.size() == nIn, "Mismatched number of inputs, expected: ", nIn, " got: ", slots.size());
+  for (uint32_t i = 0; i < nIn; ++i) {
+    const auto *ref = op->inputs()->Get(i);
+    bool resident = refOnDevice(ref);
+    if (residentOnly && !resident) continue;
+    TensorPtr in = get(ref);
+    TensorPtr root = in->base ? in->base : in;
+    TensorPtr &slot = slots[i];
+    if (root->version.load() == slot->version.load()) continue;
+    TTRT_ASSERT(in->volume() == slot->volume() && in->dtype == slot->dtype, "trace input ", i,
+                " does not match its slot in size or data type");
+    if (resident) {
+      TTRT_ASSERT(in->storage == Storage::Device, "trace input ", i, " is declared device-resident but lives on the host");
+      orderAfterUploads(in);
+      eachRank([&](size_t r_, const RankCtx &r) {
+        if (in->shards[r_]->ptr != slot->shards[r_]->ptr) {
+          TTB_CALL(ttb_memcpy_d2d(slot->shards[r_]->ptr, in->shards[r_]->ptr, slot->bytes(), r.stream));
+        }
+      });
+    } else {
+      TensorPtr h = in->storage == Storage::Device ? toHostTensor(in, true) : in;
+      eachRank([&](size_t r_, const RankCtx &r) {
+        const BufferPtr &src = h->shards.size() == 1 ? h->shards[0] : h->shards.at(r.meshRank);
+        TTB_CALL(ttb_memcpy_h2d(slot->shards[r_]->ptr, src->ptr, slot->bytes(), r.stream));
+      });
+    }
+    slot->version.store(root->version.load());
+  }
+}
+
+// CaptureOrExecuteTraceOp (operations/trace/capture_or_execute_trace.cpp:264-355).  First visit:
+// the slot-allocation program creates the persistent input and output buffers, the capture
+// program fills the host-staged slots, runs the traced function once normally and once recording,
+// and replays the recording; later visits refresh the input slots and replay.  The recorded graph
+// owns the memory of its intermediates, so allocations made elsewhere between two replays cannot
+// invalidate it and a trace is never recorded twice (the reference re-records a trace whenever
+// another one was recorded after it, because its traces bake in addresses of a shared allocator).
+void Executor::runCaptureOrExecuteTrace(const fbt::CaptureOrExecuteTraceOp *op) {
+  refuseWhileRecording("CaptureOrExecuteTraceOp");
+  TTRT_ASSERT(!op->semaphore_inputs() || op->semaphore_inputs()->size() == 0,
+              "global semaphores are a Tenstorrent fabric object and have no counterpart here");
+  uint32_t nIn = op->inputs() ? op->inputs()->size() : 0;
+  uint32_t nOut = op->outputs() ? op->outputs()->size() : 0;
+  TraceKey key{bin.id(), programIndex, op->capture_program_id(), op->execute_program_id()};
+  auto publish = [&](const TraceData &td) {
+    TTRT_ASSERT(td.outputSlots.size() == nOut, "Mismatched number of outputs, expected: ", nOut, " got: ",
+                td.outputSlots.size());
+    for (uint32_t i = 0; i < nOut; ++i) put(op->outputs()->Get(i), td.outputSlots[i]);
+  };
+  auto it = dev->traceCache.find(key);
+  if (it == dev->traceCache.end()) {
+    debug::Stats::get().incrementStat("TraceCacheMiss");
+    std::vector<TensorPtr> resident, staged;
+    for (uint32_t i = 0; i < nIn; ++i) {
+      const auto *ref = op->inputs()->Get(i);
+      (refOnDevice(ref) ? resident : staged).push_back(get(ref));
+    }
+    std::vector<TensorPtr> slots = runSubProgram(op->allocate_slots_program_id(), resident);
+    TTRT_ASSERT(slots.size() == size_t(nIn) + nOut, "Mismatched number of trace slots, expected: ", nIn + nOut,
+                " got: ", slots.size());
+    for (const TensorPtr &t : slots) t->retain = true; // owned by the trace cache from here on
+    TraceData td;
+    td.inputSlots.assign(slots.begin(), slots.begin() + nIn);
+    td.outputSlots.assign(slots.begin() + nIn, slots.end());
+    updateTraceInputSlots(op, td.inputSlots, /*residentOnly=*/true);
+    // capture program arguments: host-staged inputs, input slots, output slots
+    std::vector<TensorPtr> args = staged;
+    args.insert(args.end(), td.inputSlots.begin(), td.inputSlots.end());
+    args.insert(args.end(), td.outputSlots.begin(), td.outputSlots.end());
+    std::vector<TensorPtr> res = runSubProgram(op->capture_program_id(), args);
+    TTRT_ASSERT(res.size() == 1, "Capture program must return exactly the new trace id, got: ", res.size());
+    td.traceId = traceIdOf(res[0]);
+    TTRT_ASSERT(dev->traces.count(td.traceId), "the capture program returned an id that names no recorded trace");
+    publish(td); // the capture program replays once, so the output slots hold this call's results
+    dev->traceCache.emplace(key, std::move(td));
+    debug::Stats::get().incrementStat("CapturedTrace");
+    return;
+  }
+  TraceData &td = it->second;
+  updateTraceInputSlots(op, td.inputSlots, /*residentOnly=*/false);
+  std::vector<TensorPtr> res = runSubProgram(op->execute_program_id(), {traceIdTensor(td.traceId)});
+  (void)res;
+  publish(td);
+  debug::Stats::get().incrementStat("ExecutedTrace");
+}
+
+// WriteTensorOp: the contents of a host tensor go into an existing device tensor (the capture
+// program fills the host-staged trace slots with it before recording starts).
+void Executor::runWriteTensor(const fbt::WriteTensorOp *op) {
+  refuseWhileRecording("a host-to-device write");
+  TensorPtr h = get(op->host_tensor());
+  TensorPtr d = get(op->device_tensor());
+  if (h->storage == Storage::Device) h = toHostTensor(h, true);
+  TTRT_ASSERT(d->storage == Storage::Device && d->allocated(), "write_tensor needs an allocated device tensor");
+  TTRT_ASSERT(h->volume() == d->volume() && h->dtype == d->dtype, "write_tensor needs equal size and data type");
+  orderAfterUploads(d);
+  eachRank([&](size_t r_, const RankCtx &r) {
+    const BufferPtr &src = h->shards.size() == 1 ? h->shards[0] : h->shards.at(r.meshRank);
+    TTB_CALL(ttb_memcpy_h2d(d->shards[r_]->ptr, src->ptr, d->bytes(), r.stream));
+    if (op->blocking()) TTB_CALL(ttb_stream_sync(r.stream));
+  });
+  TensorPtr root = d->base ? d->base : d;
+  root->version.store(TensorImpl::nextTensorVersion());
+}
+
+// CopyOp: device-to-device copy into an existing tensor (the traced function stores its results
+// into the persistent output slots with it).
+void Executor::runCopy(const fbt::CopyOp *op) {
+  TensorPtr src = getDevice(op->src());
+  TensorPtr dst = get(op->dst());
+  TTRT_ASSERT(dst->storage == Storage::Device && dst->allocated(), "copy needs an allocated device destination");
+  TTRT_ASSERT(src->volume() == dst->volume() && src->dtype == dst->dtype, "copy needs equal size and data type");
+  bool same = true;
+  for (size_t i = 0; i < dev->locals.size(); ++i) same = same && src->shards[i]->ptr == dst->shards[i]->ptr;
+  if (same) return; // the producer already wrote into the destination
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_memcpy_d2d(dst->shards[i]->ptr, src->shards[i]->ptr, dst->bytes(), r.stream));
+  });
+}
+
 std::vector<Tensor> runProgram(const std::shared_ptr<DeviceImpl> &dev, Binary &binary, uint32_t programIndex,
                                std::vector<Tensor> &inputs) {
   std::lock_guard<std::mutex> g(dev->submitMutex);
-  Executor ex(dev, binary, programIndex, inputs);
-  return ex.run();
+  try {
+    Executor ex(dev, binary, programIndex, inputs);
+    return ex.run();
+  } catch (...) {
+    // A failure between BeginTraceCaptureOp and EndTraceCaptureOp leaves the streams recording.
+    if (dev->recordingTrace != 0) {
+      for (const RankCtx &r : dev->locals) {
+        ttb_set_device(r.cudaDevice);
+        ttb_trace_abort(r.stream);
+      }
+      dev->recordingTrace = 0;
+    }
+    throw;
+  }
 }
 
 } // namespace tt::runtime::cuda

@@ -6,11 +6,14 @@
 #include <atomic>
 #include <cstdint>
 #include <cstdlib>
+#include <functional>
+#include <map>
 #include <memory>
 #include <mutex>
 #include <sstream>
 #include <stdexcept>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "../../include/ttb_kernels.h"
@@ -88,7 +91,24 @@ struct StagingBlock {
   EventPtr lastUse;
 };
 
+// A recorded trace: one executable CUDA graph per coordinate this process owns.
+struct TraceGraph {
+  std::vector<void *> execs;
+};
+// What CaptureOrExecuteTraceOp keeps per (binary, main program, capture program, execute program),
+// as the reference's TraceData (runtime/include/tt/runtime/detail/ttnn/types/trace_cache.h).
+struct TraceData {
+  uint32_t traceId = 0;
+  std::vector<std::shared_ptr<struct TensorImpl>> inputSlots, outputSlots;
+};
+using TraceKey = std::tuple<uint64_t, uint32_t, uint32_t, uint32_t>;
+
 struct DeviceImpl {
+  std::map<uint32_t, TraceGraph> traces; // by trace id
+  uint32_t nextTraceId = 1;
+  uint32_t recordingTrace = 0;           // id of the trace being recorded, or 0
+  std::map<TraceKey, TraceData> traceCache;
+  void releaseTraceGraph(uint32_t id);
   std::vector<std::vector<StagingBlock>> stagingCache; // per entry of `locals`
   std::mutex stagingMutex;
   std::vector<uint32_t> meshShape{1, 1};
@@ -134,7 +154,15 @@ struct TensorImpl {
   std::vector<BufferPtr> shards;
   std::shared_ptr<DeviceImpl> device; // set for device tensors
   bool retain = false;
-  std::atomic<uint64_t> version{0};
+  // Identifies the tensor's contents: unique per tensor and renewed by every write through the
+  // API, as in the reference (TTNNTensorWrapper::version, runtime/include/tt/runtime/detail/ttnn/
+  // types/types.h:43,75-83).  Key of the const-eval cache and of the trace input slots.
+  std::atomic<uint64_t> version{nextTensorVersion()};
+  static uint64_t nextTensorVersion();
+  // A reshaped alias made for a program input shares its memory with `base`, the caller's tensor.
+  std::shared_ptr<TensorImpl> base;
+  // Run when the tensor dies (const-eval cache entries keyed by it are dropped).
+  std::vector<std::function<void()>> onDestroy;
   void *readyEvent = nullptr;      // recorded after the producing work was enqueued
 
   size_t volume() const {
@@ -176,6 +204,34 @@ TensorPtr unwrapTensor(const Tensor &t);
 TensorPtr toDevice(const TensorPtr &host, const std::shared_ptr<DeviceImpl> &dev, DataType dt);
 TensorPtr toHostTensor(const TensorPtr &devTensor, bool blocking);
 TensorPtr castOnDevice(const TensorPtr &t, DataType dt);
+
+// ---- const-eval cache --------------------------------------------------------------------
+// Results of const-eval sub-programs, shared by every binary that carries a function with the
+// same hash (the reference's GlobalTensorCache, runtime/include/tt/runtime/detail/ttnn/types/
+// global_tensor_cache.h:26-104).  An entry lives until one of the tensors it was computed from
+// dies, the device closes, or clear().
+struct ConstEvalKey {
+  const void *device = nullptr;
+  std::string hash;
+  std::vector<uint64_t> inputVersions;
+  bool operator<(const ConstEvalKey &o) const {
+    return std::tie(device, hash, inputVersions) < std::tie(o.device, o.hash, o.inputVersions);
+  }
+};
+class ConstEvalCache {
+public:
+  static ConstEvalCache &get();
+  bool find(const ConstEvalKey &key, std::vector<TensorPtr> &outputs) const;
+  void store(const ConstEvalKey &key, const std::vector<TensorPtr> &inputs, const std::vector<TensorPtr> &outputs);
+  void remove(const ConstEvalKey &key);
+  void removeDevice(const void *device);
+  void clear();
+  size_t size() const;
+
+private:
+  mutable std::mutex mutex;
+  std::map<ConstEvalKey, std::vector<TensorPtr>> entries;
+};
 
 // ---- program execution -----------------------------------------------------------------
 std::vector<Tensor> runProgram(const std::shared_ptr<DeviceImpl> &dev, Binary &binary, uint32_t programIndex,

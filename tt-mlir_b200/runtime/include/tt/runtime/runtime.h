@@ -101,6 +101,9 @@ bool isProgramCacheEnabled(Device meshDevice);
 void clearProgramCache(Device meshDevice);
 size_t getL1SmallSize(Device meshDevice);
 size_t getTraceRegionSize(Device meshDevice);
+// Drops the traces recorded for one main program of one binary (runtime/include/tt/runtime/
+// runtime.h:182-183): graphs and slots are freed; the next submit records them again.
+void releaseTrace(Device meshDevice, std::uint64_t binaryId, size_t mainProgramId);
 size_t getNumDramChannels(Device meshDevice);
 size_t getDramSizePerChannel(Device meshDevice);
 size_t getL1SizePerCore(Device meshDevice);

@@ -205,10 +205,101 @@ Buffer::~Buffer() {
   }
 }
 
+uint64_t TensorImpl::nextTensorVersion() {
+  static std::atomic<uint64_t> latest{1};
+  return latest.fetch_add(1, std::memory_order_relaxed);
+}
+
 TensorImpl::~TensorImpl() {
+  for (auto &fn : onDestroy) {
+    try {
+      fn();
+    } catch (...) {
+    }
+  }
   if (readyEvent) {
     ttb_event_destroy(readyEvent);
   }
+}
+
+ConstEvalCache &ConstEvalCache::get() {
+  static ConstEvalCache *c = new ConstEvalCache(); // never destroyed: tensors may outlive static teardown
+  return *c;
+}
+
+bool ConstEvalCache::find(const ConstEvalKey &key, std::vector<TensorPtr> &outputs) const {
+  std::lock_guard<std::mutex> g(mutex);
+  auto it = entries.find(key);
+  if (it == entries.end()) {
+    debug::Stats::get().incrementStat("ConstEvalCacheMiss");
+    return false;
+  }
+  debug::Stats::get().incrementStat("ConstEvalCacheHit");
+  outputs = it->second;
+  return true;
+}
+
+void ConstEvalCache::store(const ConstEvalKey &key, const std::vector<TensorPtr> &inputs,
+                           const std::vector<TensorPtr> &outputs) {
+  {
+    std::lock_guard<std::mutex> g(mutex);
+    entries[key] = outputs;
+  }
+  for (const TensorPtr &in : inputs) {
+    in->onDestroy.push_back([key] { ConstEvalCache::get().remove(key); });
+  }
+}
+
+void ConstEvalCache::remove(const ConstEvalKey &key) {
+  std::vector<TensorPtr> dying; // released after the lock: their own callbacks may come back here
+  {
+    std::lock_guard<std::mutex> g(mutex);
+    auto it = entries.find(key);
+    if (it == entries.end()) return;
+    dying = std::move(it->second);
+    entries.erase(it);
+  }
+}
+
+void ConstEvalCache::removeDevice(const void *device) {
+  std::vector<std::vector<TensorPtr>> dying;
+  {
+    std::lock_guard<std::mutex> g(mutex);
+    for (auto it = entries.begin(); it != entries.end();) {
+      if (it->first.device == device) {
+        dying.push_back(std::move(it->second));
+        it = entries.erase(it);
+      } else {
+        ++it;
+      }
+    }
+  }
+}
+
+void ConstEvalCache::clear() {
+  std::map<ConstEvalKey, std::vector<TensorPtr>> dying;
+  {
+    std::lock_guard<std::mutex> g(mutex);
+    dying.swap(entries);
+  }
+}
+
+size_t ConstEvalCache::size() const {
+  std::lock_guard<std::mutex> g(mutex);
+  return entries.size();
+}
+
+void DeviceImpl::releaseTraceGraph(uint32_t id) {
+  auto it = traces.find(id);
+  if (it == traces.end()) return;
+  for (size_t i = 0; i < it->second.execs.size() && i < locals.size(); ++i) {
+    if (it->second.execs[i]) {
+      ttb_set_device(locals[i].cudaDevice);
+      if (locals[i].stream) ttb_stream_sync(locals[i].stream); // a replay may still be running
+      ttb_trace_destroy(it->second.execs[i]);
+    }
+  }
+  traces.erase(it);
 }
 
 DeviceImpl::~DeviceImpl() { close(); }
@@ -217,6 +308,10 @@ void DeviceImpl::close() {
   if (!open) {
     return;
   }
+  // Cached const-eval results and trace slots live in this device's memory.
+  ConstEvalCache::get().removeDevice(this);
+  traceCache.clear();
+  while (!traces.empty()) releaseTraceGraph(traces.begin()->first);
   open = false;
   for (RankCtx &r : locals) {
     ttb_set_device(r.cudaDevice);
@@ -603,6 +698,18 @@ bool isProgramCacheEnabled(Device) { return true; }
 void clearProgramCache(Device) {}
 size_t getL1SmallSize(Device) { return 0; }
 size_t getTraceRegionSize(Device) { return 0; }
+void releaseTrace(Device meshDevice, std::uint64_t binaryId, size_t mainProgramId) {
+  auto d = deviceImpl(meshDevice);
+  std::lock_guard<std::mutex> g(d->submitMutex);
+  for (auto it = d->traceCache.begin(); it != d->traceCache.end();) {
+    if (std::get<0>(it->first) == binaryId && std::get<1>(it->first) == mainProgramId) {
+      d->releaseTraceGraph(it->second.traceId);
+      it = d->traceCache.erase(it);
+    } else {
+      ++it;
+    }
+  }
+}
 size_t getNumDramChannels(Device) { return 1; }
 size_t getDramSizePerChannel(Device meshDevice) {
   size_t total = 0;
@@ -1045,7 +1152,8 @@ void memcpy(Tensor dst, Tensor src) {
       TTB_CALL(ttb_memcpy_d2d(dp, sp, d->bytes(), r.stream));
     }
   }
-  d->version.fetch_add(1);
+  d->version.store(TensorImpl::nextTensorVersion());
+  if (d->base) d->base->version.store(d->version.load());
 }
 
 void deallocateTensor(Tensor &tensor, bool force) {

@@ -104,7 +104,7 @@ class Binary:
         self._h = handle
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:  # module globals are gone at interpreter exit
             lib.ttrt_binary_free(self._h)
             self._h = None
 
@@ -134,6 +134,12 @@ class Binary:
         buf = ctypes.create_string_buffer(64)
         _check(lib.ttrt_binary_version(_vp(self._h), buf, ctypes.c_size_t(64)))
         return buf.value.decode()
+
+    @property
+    def id(self) -> int:
+        v = ctypes.c_uint64()
+        _check(lib.ttrt_binary_id(_vp(self._h), ctypes.byref(v)))
+        return v.value
 
     def check_schema_hash(self) -> bool:
         ok = ctypes.c_int()
@@ -218,7 +224,7 @@ class Device:
         self._h = handle
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:  # module globals are gone at interpreter exit
             lib.ttrt_device_free(self._h)
             self._h = None
 
@@ -279,7 +285,7 @@ class Layout:
         self._h = handle
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:  # module globals are gone at interpreter exit
             lib.ttrt_layout_free(self._h)
             self._h = None
 
@@ -290,7 +296,7 @@ class Tensor:
         self._keepalive = keepalive  # object owning borrowed memory
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:  # module globals are gone at interpreter exit
             lib.ttrt_tensor_free(self._h)
             self._h = None
 
@@ -433,6 +439,33 @@ def submit(device: Device, binary: Binary, program_index: int, inputs: Sequence[
     _check(lib.ttrt_submit(_vp(device._h), _vp(binary._h), ctypes.c_uint32(program_index), arr, ctypes.c_uint32(n_in),
                            outs, ctypes.c_uint32(cap), ctypes.byref(n)))
     return [Tensor(outs[i]) for i in range(n.value)]
+
+
+# ------------------------------------------------------- traces, const-eval cache, counters
+def release_trace(device: Device, binary_id: int, main_program_index: int) -> None:
+    """ttrt.runtime.release_trace: frees the traces recorded for one main program."""
+    _check(lib.ttrt_release_trace(_vp(device._h), ctypes.c_uint64(binary_id), ctypes.c_size_t(main_program_index)))
+
+
+def const_eval_cache_size() -> int:
+    n = ctypes.c_size_t()
+    _check(lib.ttrt_const_eval_cache_size(ctypes.byref(n)))
+    return n.value
+
+
+def clear_const_eval_cache() -> None:
+    _check(lib.ttrt_const_eval_cache_clear())
+
+
+def get_stat(name: str) -> int:
+    """ttrt.runtime.DebugStats.get().get_stat(name)."""
+    v = ctypes.c_int64()
+    _check(lib.ttrt_stat_get(name.encode(), ctypes.byref(v)))
+    return v.value
+
+
+def clear_stats() -> None:
+    _check(lib.ttrt_stats_clear())
 
 
 # ---------------------------------------------------------------------------------- hooks

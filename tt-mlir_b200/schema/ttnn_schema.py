@@ -291,6 +291,26 @@ S.table("MeshPartitionOp", [
     ("in", "TensorRef"), ("out", "TensorRef"), ("dim", "i32"), ("cluster_axis", "u32", OPT),
     ("memory_config", "MemoryConfig")])
 
+# --- sub-programs: const-eval cache, calls, traces (operations/load_cached.fbs, mlir_native.fbs,
+#     trace.fbs) and the two copies the trace functions use (operations/data_movement.fbs)
+S.table("LoadCachedOp", [
+    ("inputs", "[TensorRef]"), ("callee_name", "string"), ("program_idx", "u32"),
+    ("outputs", "[TensorRef]"), ("program_hash", "string")])
+S.table("FuncCallOp", [
+    ("program_id", "u32"), ("inputs", "[TensorRef]"), ("outputs", "[TensorRef]"),
+    ("semaphore_inputs", "[GlobalSemaphoreRef]")])
+S.table("BeginTraceCaptureOp", [("device", "DeviceRef"), ("trace_id", "TensorRef"), ("cq_id", "u32")])
+S.table("EndTraceCaptureOp", [("device", "DeviceRef"), ("trace_id", "TensorRef"), ("cq_id", "u32")])
+S.table("ExecuteTraceOp", [
+    ("device", "DeviceRef"), ("trace_id", "TensorRef"), ("cq_id", "u32"), ("blocking", "bool")])
+S.table("CaptureOrExecuteTraceOp", [
+    ("device", "DeviceRef"), ("capture_program_id", "u32"), ("execute_program_id", "u32"),
+    ("allocate_slots_program_id", "u32"), ("inputs", "[TensorRef]"), ("outputs", "[TensorRef]"),
+    ("semaphore_inputs", "[GlobalSemaphoreRef]")])
+S.table("WriteTensorOp", [
+    ("host_tensor", "TensorRef"), ("device_tensor", "TensorRef"), ("blocking", "bool"), ("cq_id", "u32")])
+S.table("CopyOp", [("src", "TensorRef"), ("dst", "TensorRef")])
+
 # --- program (TTNN/program.fbs).  Union member order fixes the op type ids.
 OP_TYPE_MEMBERS = [
     "AdamWOp", "AggregateTensorOp", "AllGatherOp", "AllReduceAsyncOp", "AllReduceOp",

@@ -78,6 +78,8 @@ class ProgramBuilder:
         self.outputs: List[Value] = []
         self.ops: List[dict] = []
         self._op_values: List[Tuple[List[Value], List[Value]]] = []
+        self.private = False
+        self.index = len(binary.programs)  # position in the binary = the id other programs call it by
         self.device_ref = {"global_id": binary.next_id()}
         self._emit("GetDeviceOp", {"mesh": self.mesh_shape, "offset": (0, 0),
                                    "chip_ids": list(range(self.mesh_shape[0] * self.mesh_shape[1])),
@@ -528,6 +530,68 @@ class ProgramBuilder:
                    list(ins), [out], loc)
         return out
 
+    # ---- sub-programs: const-eval, calls, traces -------------------------------------------------------------
+    def input_like(self, v: Value, on_device: Optional[bool] = None) -> Value:
+        return self.input(v.shape, v.dtype, v.on_device if on_device is None else on_device)
+
+    def empty(self, shape, dtype: str, loc=None) -> Value:
+        out = self._value(shape, dtype)
+        self._emit("EmptyOp", {"shape": list(shape), "dtype": dtype, "layout": "Tile", "device": self.device_ref,
+                               "memcfg": self._mc(), "out": out.ref}, [], [out], loc)
+        return out
+
+    def _results_like(self, callee: "ProgramBuilder") -> List[Value]:
+        return [self._value(v.shape, v.dtype, v.on_device) for v in callee.outputs]
+
+    def load_cached(self, callee: "ProgramBuilder", inputs: Sequence[Value], program_hash: Optional[str] = None,
+                    loc=None) -> List[Value]:
+        """`ttcore.load_cached(@callee, [inputs])`: the results of a const-eval function, computed on
+        first use and cached by the runtime (lib/Target/TTNN/TTNNToFlatbuffer.cpp emits LoadCachedOp
+        with the callee's position in the binary and a hash of its body)."""
+        outs = self._results_like(callee)
+        if program_hash is None:
+            import hashlib
+            program_hash = hashlib.sha256(repr([op["type"] for op in callee.ops]).encode()).hexdigest()
+        self._emit("LoadCachedOp", {"inputs": [v.ref for v in inputs], "callee_name": callee.name,
+                                    "program_idx": callee.index, "outputs": [v.ref for v in outs],
+                                    "program_hash": program_hash}, list(inputs), outs, loc)
+        return outs
+
+    def func_call(self, callee: "ProgramBuilder", inputs: Sequence[Value], loc=None) -> List[Value]:
+        outs = self._results_like(callee)
+        self._emit("FuncCallOp", {"program_id": callee.index, "inputs": [v.ref for v in inputs],
+                                  "outputs": [v.ref for v in outs]}, list(inputs), outs, loc)
+        return outs
+
+    def begin_trace_capture(self, loc=None) -> Value:
+        tid = self._value([], "UInt32", False)
+        self._emit("BeginTraceCaptureOp", {"device": self.device_ref, "trace_id": tid.ref, "cq_id": 0}, [], [tid], loc)
+        return tid
+
+    def end_trace_capture(self, trace_id: Value, loc=None):
+        self._emit("EndTraceCaptureOp", {"device": self.device_ref, "trace_id": trace_id.ref, "cq_id": 0},
+                   [trace_id], [], loc)
+
+    def execute_trace(self, trace_id: Value, blocking: bool = False, loc=None):
+        self._emit("ExecuteTraceOp", {"device": self.device_ref, "trace_id": trace_id.ref, "cq_id": 0,
+                                      "blocking": blocking}, [trace_id], [], loc)
+
+    def write_tensor(self, host: Value, device: Value, blocking: bool = False, loc=None):
+        self._emit("WriteTensorOp", {"host_tensor": host.ref, "device_tensor": device.ref, "blocking": blocking,
+                                     "cq_id": 0}, [host, device], [], loc)
+
+    def copy(self, src: Value, dst: Value, loc=None):
+        self._emit("CopyOp", {"src": src.ref, "dst": dst.ref}, [src, dst], [], loc)
+
+    def capture_or_execute_trace(self, capture: "ProgramBuilder", execute: "ProgramBuilder", allocate: "ProgramBuilder",
+                                 inputs: Sequence[Value], results_like: Sequence[Value], loc=None) -> List[Value]:
+        outs = [self._value(v.shape, v.dtype, True) for v in results_like]
+        self._emit("CaptureOrExecuteTraceOp", {
+            "device": self.device_ref, "capture_program_id": capture.index, "execute_program_id": execute.index,
+            "allocate_slots_program_id": allocate.index, "inputs": [v.ref for v in inputs],
+            "outputs": [v.ref for v in outs]}, list(inputs), outs, loc)
+        return outs
+
     # ---- finishing -----------------------------------------------------------------------------------------------------
     def _with_deallocs(self) -> List[dict]:
         """Inserts a DeallocateOp after the last use of every op result that is not a program output."""
@@ -558,7 +622,7 @@ class ProgramBuilder:
             "inputs": [v.ref for v in self.inputs],
             "outputs": [v.ref for v in self.outputs],
             "operations": self._with_deallocs() if auto_dealloc else self.ops,
-            "private": False,
+            "private": self.private,
             "mesh_shape": self.mesh_shape,
         }
 
@@ -580,6 +644,61 @@ class BinaryBuilder:
         p = ProgramBuilder(self, name, mesh_shape)
         self.programs.append(p)
         return p
+
+    def private_program(self, name: str, mesh_shape=(1, 1)) -> ProgramBuilder:
+        p = self.program(name, mesh_shape)
+        p.private = True
+        return p
+
+    def hoist_trace(self, main: ProgramBuilder, name: str, inputs: Sequence[Value], body, index: int = 0) -> List[Value]:
+        """Wraps `body` in a trace the way the compiler's trace hoisting does
+        (lib/Dialect/TTNN/Transforms/TTNNTraceHoistTransform.cpp): four private programs
+
+          trace_<i>_<name>                 (inputs..., output slots...)       the traced function; stores its
+                                                                              results into the slots with CopyOp
+          allocate_slots_trace_<i>_<name>  (device-resident inputs) -> input slots..., output slots...
+          run_and_capture_trace_<i>_<name> (host-staged inputs..., input slots..., output slots...) -> trace id
+          execute_trace_<i>_<name>         (trace id)
+
+        and a CaptureOrExecuteTraceOp in `main`.  `inputs` are values of `main`: the ones on device
+        (parameters, constants, const-eval results) are their own slots, the ones on host are staged
+        into freshly allocated slots; device-resident inputs come first, as in the compiler's order.
+        `body(program, args) -> results` emits the traced ops."""
+        inputs = sorted(inputs, key=lambda v: 0 if v.on_device else 1)  # stable: resident first
+        resident = [v for v in inputs if v.on_device]
+        staged = [v for v in inputs if not v.on_device]
+        mesh = main.mesh_shape
+
+        fn = self.private_program(f"trace_{index}_{name}", mesh)
+        args = [fn.input(v.shape, v.dtype, True) for v in inputs]
+        results = list(body(fn, args))
+        fn_slots = [fn.input(r.shape, r.dtype, True) for r in results]
+        for r, slot in zip(results, fn_slots):
+            fn.copy(r, slot)
+
+        alloc = self.private_program(f"allocate_slots_trace_{index}_{name}", mesh)
+        a_in = [alloc.input_like(v) for v in resident]
+        a_slots = a_in + [alloc.empty(v.shape, v.dtype) for v in staged] + [alloc.empty(r.shape, r.dtype) for r in results]
+        alloc.output(*a_slots)
+
+        cap = self.private_program(f"run_and_capture_trace_{index}_{name}", mesh)
+        c_host = [cap.input(v.shape, v.dtype, False) for v in staged]
+        c_in = [cap.input(v.shape, v.dtype, True) for v in inputs]
+        c_out = [cap.input(r.shape, r.dtype, True) for r in results]
+        for h, slot in zip(c_host, c_in[len(resident):]):
+            cap.write_tensor(h, slot)
+        cap.func_call(fn, c_in + c_out)       # once normally: everything lazily set up is set up
+        tid = cap.begin_trace_capture()
+        cap.func_call(fn, c_in + c_out)       # once recording
+        cap.end_trace_capture(tid)
+        cap.execute_trace(tid)                # replay: the output slots hold this call's results
+        cap.output(tid)
+
+        exe = self.private_program(f"execute_trace_{index}_{name}", mesh)
+        e_tid = exe.input([], "UInt32", False)
+        exe.execute_trace(e_tid)
+
+        return main.capture_or_execute_trace(cap, exe, alloc, inputs, results)
 
     def finish(self) -> bytes:
         w = Writer(S)

@@ -182,6 +182,42 @@ TTB_API int ttb_add_rms_norm(const void *a, const void *b, const void *weight, v
 TTB_API int ttb_reduce(int op, const void *in, void *out, int dtype, size_t outer, size_t len,
                        size_t inner, void *stream);
 
+/* ::ttnn::layer_norm (runtime/lib/ttnn/operations/normalization/layer_norm.cpp): each of `rows`
+ * rows of `cols` elements is normalised with its own mean and biased variance, in f32, then
+ * scaled / shifted by `weight` / `bias` (nullable, `cols` elements). */
+TTB_API int ttb_layer_norm(const void *in, const void *weight, const void *bias, void *out, int dtype,
+                           size_t rows, size_t cols, float eps, void *stream);
+/* ::ttnn::argmax (operations/reduction/argmax.cpp): index (Int32) of the first maximum along the
+ * middle dimension of [outer, len, inner]; a NaN counts as the maximum. */
+TTB_API int ttb_argmax(const void *in, void *out, int dtype, size_t outer, size_t len, size_t inner,
+                       void *stream);
+/* ::ttnn::cumsum (operations/cumsum/cumsum.cpp): running sum along the middle dimension. */
+TTB_API int ttb_cumsum(const void *in, void *out, int dtype, size_t outer, size_t len, size_t inner,
+                       void *stream);
+
+/* ---- pooling: ::ttnn::max_pool2d / avg_pool2d (runtime/lib/ttnn/operations/pool/pool2d.cpp:20-139)
+ * over an NHWC activation [n, h, w, c] -> [n, ho, wo, c].  Paddings are top, left, bottom, right;
+ * `padding_has_four` says whether the op carried four paddings (applied as data before pooling,
+ * which changes the ceil-mode rule) or two.  ttb_pool2d_out_shape gives ho, wo. */
+TTB_API int ttb_pool2d_out_shape(int is_max, int h, int w, int kh, int kw, int sh, int sw, int pt, int pl,
+                                 int pb, int pr, int dh, int dw, int ceil_mode, int padding_has_four,
+                                 int *ho, int *wo);
+TTB_API int ttb_pool2d(const void *in, void *out, int dtype, int is_max, int n, int h, int w, int c, int kh,
+                       int kw, int sh, int sw, int pt, int pl, int pb, int pr, int dh, int dw,
+                       int ceil_mode, int count_include_pad, int padding_has_four, void *stream);
+
+/* ::ttnn::embedding (operations/embedding/embedding.cpp): out[r, :] = table[indices[r], :].
+ * Indices are Int32 / UInt32 / UInt16 or a float type holding integers.  An index outside
+ * [0, vocab) reads row 0 and sets a sticky flag that ttb_embedding_status returns (after
+ * synchronising the device). */
+TTB_API int ttb_embedding(const void *indices, const void *table, void *out, int index_dtype, int dtype,
+                          size_t rows, size_t vocab, size_t dim, void *stream);
+TTB_API int ttb_embedding_status(int *bad_index_seen);
+/* ::ttnn::pad (operations/data_movement/pad.cpp): `low[i]` / `high[i]` elements of `value` in front
+ * of / behind dimension i. */
+TTB_API int ttb_pad(const void *in, void *out, int dtype, int rank, const int64_t *in_shape,
+                    const int64_t *low, const int64_t *high, double value, void *stream);
+
 /* ---- data movement: ::ttnn::permute / slice / concat / repeat / transpose
  * (runtime/lib/ttnn/operations/data_movement/). One gather kernel covers them: out is dense
  * row-major of `out_shape`; element (i0..ik) is read from in + in_offset + sum(i_d * in_strides[d]). */
@@ -377,6 +413,20 @@ TTB_API int ttb_symm_status(void *symm, int *status);
 TTB_API int ttb_symm_stamps(void *symm, unsigned long long *stamps8);
 TTB_API int ttb_symm_all_reduce(void *symm, const void *in, const void *residual, void *out,
                                 size_t count, int dtype, void *stream);
+/* The fused producer path: the GEMM in front of an all-reduce stores each row block of its
+ * partial result straight into the workspace of the rank that will reduce it (TMA stores over
+ * NVLink from the GEMM's epilogue), so the reduce-scatter half of the exchange overlaps the GEMM.
+ *   ttb_symm_push_targets(symm, bytes, targets, &rank, &n)  where this rank's partial of row block
+ *       o goes (one pointer per rank; valid for the next all-reduce of `symm` only);
+ *   ttb_gemm_push(a, b, targets, n, dtype, m, n_cols, k, stream)  C = A B^T scattered to the targets
+ *       (needs m / n rows per block to be a multiple of 128; TTB_ERR_UNSUPPORTED otherwise);
+ *   ttb_symm_all_reduce_pushed(symm, residual, out, count, dtype, stream)  sums the n partials of
+ *       the own block locally, adds `residual` (nullable), shares the result with every rank. */
+TTB_API int ttb_symm_push_targets(void *symm, size_t bytes, void **targets, int *rank, int *nranks);
+TTB_API int ttb_gemm_push(const void *a, const void *b, void *const *targets, int nranks, int ab_dtype,
+                          int64_t m, int64_t n, int64_t k, void *stream);
+TTB_API int ttb_symm_all_reduce_pushed(void *symm, const void *residual, void *out, size_t count,
+                                       int dtype, void *stream);
 
 #ifdef __cplusplus
 }

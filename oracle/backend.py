@@ -161,6 +161,33 @@ class OracleBuilder:
             return _map(lambda t, w: ops.rms_norm(t, w, None, epsilon), x, weight)
         return _map(lambda t: ops.rms_norm(t, None, None, epsilon), x)
 
+    def layer_norm(self, x, weight=None, bias=None, epsilon=1e-5, loc=None):
+        vals = [v for v in (x, weight, bias) if v is not None]
+
+        def fn(*ts):
+            it = iter(ts)
+            t = next(it)
+            w = next(it) if weight is not None else None
+            b = next(it) if bias is not None else None
+            return ops.layer_norm(t, w, b, epsilon)
+        return _map(fn, *vals)
+
+    def argmax(self, x, dim=None, keep_dim=False, loc=None): return _map(lambda t: ops.argmax(t, dim, keep_dim), x)
+    def cumsum(self, x, dim, loc=None): return _map(lambda t: ops.cumsum(t, dim), x)
+    def embedding(self, indices, weight, loc=None): return _map(ops.embedding, indices, weight)
+
+    def max_pool2d(self, x, batch, height, width, channels, kernel=(2, 2), stride=(2, 2), padding=(0, 0), dilation=(1, 1),
+                   ceil_mode=False, loc=None):
+        return _map(lambda t: ops.max_pool2d(t, batch, height, width, channels, kernel, stride, padding, dilation, ceil_mode), x)
+
+    def avg_pool2d(self, x, batch, height, width, channels, kernel=(2, 2), stride=(2, 2), padding=(0, 0), ceil_mode=False,
+                   count_include_pad=True, loc=None):
+        return _map(lambda t: ops.avg_pool2d(t, batch, height, width, channels, kernel, stride, padding, ceil_mode,
+                                             count_include_pad), x)
+
+    def global_avg_pool2d(self, x, loc=None): return _map(ops.global_avg_pool2d, x)
+    def pad(self, x, padding, value=0.0, loc=None): return _map(lambda t: ops.pad(t, padding, value), x)
+
     def reduce(self, kind, x, dims, keep_dim, loc=None): return _map(lambda t: ops.reduce(kind, t, dims, keep_dim), x)
 
     # ---- data movement

@@ -205,6 +205,89 @@ def reduce(kind, x, dims, keep_dim):  # ttir_cpu.py:374-397
 
 
 # ---- data movement (ttir_cpu.py:449-495, 824-877) -----------------------------------------------------
+def layer_norm(x, weight=None, bias=None, epsilon=1e-5):  # ttir_cpu.py layer_norm: F.layer_norm over weight.shape
+    shape = tuple(weight.shape) if weight is not None else (x.shape[-1],)
+    return _hoist(lambda t, w=None, b=None: F.layer_norm(t, shape, weight=w, bias=b, eps=epsilon), x.dtype, x, weight, bias)
+
+
+def argmax(x, dim=None, keep_dim=False):  # ttir_cpu.py argmax: torch.argmax, Int32 result
+    if dim is None:
+        idx = torch.argmax(x.flatten())
+        return (idx.reshape([1] * x.dim()) if keep_dim else idx).to(torch.int32)
+    return torch.argmax(x, dim=dim, keepdim=keep_dim).to(torch.int32)
+
+
+def cumsum(x, dim):  # ttir_cpu.py cumsum
+    return torch.cumsum(x, dim=dim).to(x.dtype)
+
+
+def embedding(indices, weight):  # ttir_cpu.py embedding: leading 1-dims of the table are dropped
+    w = weight
+    while w.dim() > 2 and w.shape[0] == 1:
+        w = w.squeeze(0)
+    return F.embedding(indices.long(), w)
+
+
+def _nchw(x, batch, height, width, channels):  # ttir_cpu.py _pool_to_nchw
+    return x.reshape(batch, height, width, channels).permute(0, 3, 1, 2)
+
+
+def max_pool2d(x, batch, height, width, channels, kernel, stride, padding, dilation=(1, 1), ceil_mode=False):
+    """ttir_cpu.py max_pool2d / _pool_padding.  `padding` in flatbuffer order: (h, w) or (top, left,
+    bottom, right); four paddings are applied as -inf data before pooling.  Result flattened like
+    the TTNN op's: [1, 1, N*Ho*Wo, C]."""
+    def fn(t):
+        t = _nchw(t, batch, height, width, channels)
+        if len(padding) == 4:
+            pt, pl, pb, pr = padding
+            t = F.pad(t, (pl, pr, pt, pb), mode="constant", value=float("-inf"))
+            pad = 0
+        else:
+            pad = tuple(padding)
+        y = F.max_pool2d(t, kernel_size=tuple(kernel), stride=tuple(stride), padding=pad, dilation=tuple(dilation),
+                         ceil_mode=ceil_mode)
+        return y.permute(0, 2, 3, 1).reshape(1, 1, -1, channels)
+    return _hoist(fn, x.dtype, x)
+
+
+def avg_pool2d(x, batch, height, width, channels, kernel, stride, padding, ceil_mode=False, count_include_pad=True):
+    """ttir_cpu.py avg_pool2d: symmetric padding up to half the kernel goes to torch; anything else is
+    applied by hand (zeros), with sum / count when padding must not be counted."""
+    if len(padding) == 4:
+        pt, pl, pb, pr = padding
+    else:
+        pt = pb = padding[0]
+        pl = pr = padding[1]
+    ks, st = tuple(kernel), tuple(stride)
+    symmetric = pt == pb and pl == pr
+    exceeds = pt > ks[0] // 2 or pl > ks[1] // 2
+
+    def fn(t):
+        t = _nchw(t, batch, height, width, channels)
+        if symmetric and not exceeds:
+            y = F.avg_pool2d(t, ks, st, (pt, pl), ceil_mode, count_include_pad)
+        elif not count_include_pad and not symmetric:
+            ones = F.pad(torch.ones_like(t), (pl, pr, pt, pb))
+            tp = F.pad(t, (pl, pr, pt, pb))
+            y = F.avg_pool2d(tp, ks, st, 0, ceil_mode, True) / F.avg_pool2d(ones, ks, st, 0, ceil_mode, True).clamp(min=1e-8)
+        else:
+            y = F.avg_pool2d(F.pad(t, (pl, pr, pt, pb)), ks, st, 0, ceil_mode, count_include_pad)
+        return y.permute(0, 2, 3, 1).reshape(1, 1, -1, channels)
+    return _hoist(fn, x.dtype, x)
+
+
+def global_avg_pool2d(x):  # ttir_cpu.py global_avg_pool2d, NHWC in and out
+    return _hoist(lambda t: F.adaptive_avg_pool2d(t.permute(0, 3, 1, 2), (1, 1)).permute(0, 2, 3, 1), x.dtype, x)
+
+
+def pad(x, padding, value=0.0):  # ttir_cpu.py pad: (low, high) per dimension, outermost first
+    pairs = [(padding[i], padding[i + 1]) for i in range(0, len(padding), 2)]
+    flat = []
+    for lo, hi in reversed(pairs):
+        flat.extend([lo, hi])
+    return F.pad(x, tuple(flat), value=value)
+
+
 def concatenate_heads(x):
     b, h, s, d = x.shape
     return x.permute(0, 2, 1, 3).reshape(b, s, h * d)

@@ -169,6 +169,62 @@ def main():
     store(out, "sdpa/causal", torch.matmul(torch.softmax(causal, dim=-1), vv))
     store(out, "sdpa/full", torch.matmul(torch.softmax(qk, dim=-1), vv))
 
+    # --- layer_norm, argmax, cumsum, embedding, pad (ttir_cpu.py: layer_norm, argmax, cumsum, embedding, pad), f32
+    lx, lw, lb = rnd(6, 4, 48), 1 + rnd(48) * 0.1, rnd(48) * 0.1
+    store(out, "ln/x", lx)
+    store(out, "ln/w", lw)
+    store(out, "ln/b", lb)
+    store(out, "ln/plain", cpu.layer_norm(lx, epsilon=1e-5))
+    store(out, "ln/affine", cpu.layer_norm(lx, epsilon=1e-5, weight=lw, bias=lb))
+    lw2 = 1 + rnd(4, 48) * 0.1
+    store(out, "ln/w2", lw2)
+    store(out, "ln/two_dims", cpu.layer_norm(lx, epsilon=1e-3, weight=lw2))
+    ax = rnd(5, 7, 9)
+    ax[1, 2, :] = ax[1, 2, 3]            # ties: the first index wins
+    store(out, "arg/x", ax)
+    for d in (0, 1, 2):
+        store(out, f"arg/dim{d}", cpu.argmax(ax, dim=[d]))
+    store(out, "arg/all", cpu.argmax(ax))
+    store(out, "arg/keep", cpu.argmax(ax, dim=[1], keepdim=True))
+    cx = rnd(4, 33, 5)
+    store(out, "cum/x", cx)
+    for d in (0, 1, 2):
+        store(out, f"cum/dim{d}", cpu.cumsum(cx, dim=d))
+    ci = torch.randint(-50, 50, (6, 40), generator=g, dtype=torch.int32)
+    store(out, "cum/xi", ci)
+    store(out, "cum/int", cpu.cumsum(ci, dim=1))
+    ei = torch.randint(0, 30, (3, 11), generator=g, dtype=torch.int32)
+    ew = rnd(1, 1, 30, 24)
+    store(out, "emb/idx", ei)
+    store(out, "emb/w", ew)
+    store(out, "emb/out", cpu.embedding(ei, ew))
+    px = rnd(2, 3, 5)
+    store(out, "pad/x", px)
+    store(out, "pad/out", cpu.pad(px, [1, 0, 0, 2, 3, 1], value=-1.5))
+
+    # --- pooling over NHWC (ttir_cpu.py: max_pool2d, avg_pool2d, global_avg_pool2d); the reference's
+    #     padding order at this level is (top, bottom, left, right)
+    pool_x = rnd(2, 9, 11, 8)
+    store(out, "pool/x", pool_x)
+    flat = pool_x.reshape(1, 1, -1, 8)
+    store(out, "pool/max_k2s2", cpu.max_pool2d(flat, 2, 9, 11, 8, [2, 2], [2, 2], [0, 0]))
+    store(out, "pool/max_k3s2p1", cpu.max_pool2d(flat, 2, 9, 11, 8, [3, 3], [2, 2], [1, 1]))
+    store(out, "pool/max_k3s2p1_ceil", cpu.max_pool2d(flat, 2, 9, 11, 8, [3, 3], [2, 2], [1, 1], ceil_mode=True))
+    store(out, "pool/max_k3s1_dil2", cpu.max_pool2d(flat, 2, 9, 11, 8, [3, 3], [1, 1], [1, 1], dilation=[2, 2]))
+    store(out, "pool/max_asym", cpu.max_pool2d(flat, 2, 9, 11, 8, [3, 2], [2, 1], [1, 0, 2, 1]))          # t, b, l, r
+    store(out, "pool/max_asym_ceil", cpu.max_pool2d(flat, 2, 9, 11, 8, [3, 3], [2, 2], [0, 1, 0, 1], ceil_mode=True))
+    store(out, "pool/avg_k2s2", cpu.avg_pool2d(flat, 2, 9, 11, 8, [2, 2], [2, 2], [0, 0]))
+    store(out, "pool/avg_k3s2p1", cpu.avg_pool2d(flat, 2, 9, 11, 8, [3, 3], [2, 2], [1, 1]))
+    store(out, "pool/avg_k3s2p1_nopad", cpu.avg_pool2d(flat, 2, 9, 11, 8, [3, 3], [2, 2], [1, 1], count_include_pad=False))
+    store(out, "pool/avg_k3s2p1_ceil", cpu.avg_pool2d(flat, 2, 9, 11, 8, [3, 3], [2, 2], [1, 1], ceil_mode=True))
+    store(out, "pool/avg_k3s2p1_ceil_nopad",
+          cpu.avg_pool2d(flat, 2, 9, 11, 8, [3, 3], [2, 2], [1, 1], ceil_mode=True, count_include_pad=False))
+    store(out, "pool/avg_asym", cpu.avg_pool2d(flat, 2, 9, 11, 8, [3, 3], [2, 2], [1, 0, 2, 1]))
+    store(out, "pool/avg_asym_nopad", cpu.avg_pool2d(flat, 2, 9, 11, 8, [3, 3], [2, 2], [1, 0, 2, 1], count_include_pad=False))
+    store(out, "pool/avg_bigpad", cpu.avg_pool2d(flat, 2, 9, 11, 8, [2, 2], [2, 2], [2, 2]))
+    store(out, "pool/avg_bigpad_nopad", cpu.avg_pool2d(flat, 2, 9, 11, 8, [2, 2], [2, 2], [2, 2], count_include_pad=False))
+    store(out, "pool/global", cpu.global_avg_pool2d(pool_x))
+
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ttir_cpu_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes")

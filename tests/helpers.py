@@ -57,6 +57,36 @@ def check_graph(rt, device, graph_fn, inputs, what, tol=None, **kw):
     return got, want
 
 
+# Pooling cases recorded in tests/golden (pool/<name>) over an NHWC [2, 9, 11, 8] activation:
+# name -> (kind, kernel, stride, padding in flatbuffer order (h, w) or (top, left, bottom, right),
+#          dilation, ceil_mode, count_include_pad)
+POOL_CASES = {
+    "max_k2s2": ("max", (2, 2), (2, 2), (0, 0), (1, 1), False, True),
+    "max_k3s2p1": ("max", (3, 3), (2, 2), (1, 1), (1, 1), False, True),
+    "max_k3s2p1_ceil": ("max", (3, 3), (2, 2), (1, 1), (1, 1), True, True),
+    "max_k3s1_dil2": ("max", (3, 3), (1, 1), (1, 1), (2, 2), False, True),
+    "max_asym": ("max", (3, 2), (2, 1), (1, 2, 0, 1), (1, 1), False, True),
+    "max_asym_ceil": ("max", (3, 3), (2, 2), (0, 0, 1, 1), (1, 1), True, True),
+    "avg_k2s2": ("avg", (2, 2), (2, 2), (0, 0), (1, 1), False, True),
+    "avg_k3s2p1": ("avg", (3, 3), (2, 2), (1, 1), (1, 1), False, True),
+    "avg_k3s2p1_nopad": ("avg", (3, 3), (2, 2), (1, 1), (1, 1), False, False),
+    "avg_k3s2p1_ceil": ("avg", (3, 3), (2, 2), (1, 1), (1, 1), True, True),
+    "avg_k3s2p1_ceil_nopad": ("avg", (3, 3), (2, 2), (1, 1), (1, 1), True, False),
+    "avg_asym": ("avg", (3, 3), (2, 2), (1, 2, 0, 1), (1, 1), False, True),
+    "avg_asym_nopad": ("avg", (3, 3), (2, 2), (1, 2, 0, 1), (1, 1), False, False),
+    "avg_bigpad": ("avg", (2, 2), (2, 2), (2, 2), (1, 1), False, True),
+    "avg_bigpad_nopad": ("avg", (2, 2), (2, 2), (2, 2), (1, 1), False, False),
+}
+
+
+def pool_on(b, x, case, batch=2, height=9, width=11, channels=8):
+    """Emits (or, on the oracle builder, computes) one POOL_CASES entry on the flattened activation `x`."""
+    kind, kernel, stride, padding, dilation, ceil, include = POOL_CASES[case]
+    if kind == "max":
+        return b.max_pool2d(x, batch, height, width, channels, kernel, stride, padding, dilation, ceil)
+    return b.avg_pool2d(x, batch, height, width, channels, kernel, stride, padding, ceil, include)
+
+
 DTYPE_NAME = {torch.float32: "Float32", torch.bfloat16: "BFloat16", torch.float16: "Float16", torch.int32: "Int32",
               torch.int8: "Int8", torch.uint8: "UInt8"}
 

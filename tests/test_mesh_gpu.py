@@ -141,6 +141,30 @@ def test_all_reduce_sizes_in_a_row_and_fused_residual(rt, mesh2, dtype):
         assert torch.equal(g[:half], g[half:]), "the two devices disagree"
 
 
+@pytest.mark.parametrize("m,n,k", [(512, 384, 1024), (1024, 4096, 512), (384, 256, 512), (256, 136, 264)])
+def test_row_parallel_gemm_feeding_an_all_reduce(rt, mesh2, m, n, k):
+    """x[m, k] . w[n, k]^T with k split over the mesh, then all_reduce (+ residual add): the GEMM in
+    front of the all-reduce stores its row blocks straight into the peers' workspaces when m / 2 is a
+    multiple of the tile height (first two shapes) and produces an ordinary tensor otherwise.  Twice
+    in one program, so that the workspace regions alternate.  Both devices must hold the same bits."""
+    torch.manual_seed(m + n)
+    x = torch.randn(m, k).to(torch.bfloat16)
+    w = (torch.randn(n, k) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(n, k) * 0.05).to(torch.bfloat16)
+    res = torch.randn(m, n).to(torch.bfloat16)
+
+    def body(b, xv, wv, w2v, rv):
+        xs, ws, w2s = b.distribute(xv, 1), b.distribute(wv, 1), b.distribute(w2v, 1)
+        r = b.distribute(rv, None)
+        first = b.all_reduce(b.linear(xs, ws, transpose_b=True))
+        second = b.add(r, b.all_reduce(b.linear(xs, w2s, transpose_b=True)))
+        return [b.aggregate(first, 0), b.aggregate(second, 0)]
+    got, want = run_mesh(rt, mesh2, body, [x, w, w2, res])
+    for i, (g, wnt) in enumerate(zip(got, want)):
+        assert_matches(g, wnt, f"row-parallel gemm + all_reduce {i}", (0.999, 2e-2, 2.0 ** -6))
+        assert torch.equal(g[:m], g[m:]), "the two devices disagree"
+
+
 def _tp_worker(rank, world, port, ret):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"

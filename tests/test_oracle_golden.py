@@ -127,6 +127,67 @@ def test_sdpa(golden):
     assert torch.allclose(ops.sdpa(q, k, v, False), golden["sdpa/full"], atol=1e-6)
 
 
+def test_layer_norm(golden):
+    x, w, b = golden["ln/x"], golden["ln/w"], golden["ln/b"]
+    assert same(ops.layer_norm(x), golden["ln/plain"])
+    assert same(ops.layer_norm(x, w, b), golden["ln/affine"])
+    assert same(ops.layer_norm(x, golden["ln/w2"], None, 1e-3), golden["ln/two_dims"])
+
+
+def test_argmax_cumsum_embedding_pad(golden):
+    x = golden["arg/x"]
+    for d in (0, 1, 2):
+        assert torch.equal(ops.argmax(x, d), golden[f"arg/dim{d}"])
+    assert torch.equal(ops.argmax(x), golden["arg/all"])
+    assert torch.equal(ops.argmax(x, 1, True), golden["arg/keep"])
+    for d in (0, 1, 2):
+        assert same(ops.cumsum(golden["cum/x"], d), golden[f"cum/dim{d}"])
+    assert torch.equal(ops.cumsum(golden["cum/xi"], 1), golden["cum/int"])
+    assert torch.equal(ops.embedding(golden["emb/idx"], golden["emb/w"]), golden["emb/out"])
+    assert torch.equal(ops.pad(golden["pad/x"], [1, 0, 0, 2, 3, 1], -1.5), golden["pad/out"])
+
+
+def test_pooling(golden):
+    from helpers import POOL_CASES
+    from ttmlir_b200.ttnn_builder import ProgramBuilder
+    x = golden["pool/x"].reshape(1, 1, -1, 8)
+    for name, (kind, kernel, stride, padding, dilation, ceil, include) in POOL_CASES.items():
+        want = golden[f"pool/{name}"]
+        if kind == "max":
+            got = ops.max_pool2d(x, 2, 9, 11, 8, kernel, stride, padding, dilation, ceil)
+        else:
+            got = ops.avg_pool2d(x, 2, 9, 11, 8, kernel, stride, padding, ceil, include)
+        assert same(got, want.reshape(1, 1, -1, 8)), name
+        # the shape rule the builder (and the kernel library) uses gives the reference's extents
+        ho, wo = ProgramBuilder.pool_out_hw("MaxPool2d" if kind == "max" else "AvgPool2d", 9, 11, kernel, stride, padding,
+                                            dilation, ceil)
+        assert (ho, wo) == tuple(want.shape[1:3]), name
+    assert same(ops.global_avg_pool2d(golden["pool/x"]), golden["pool/global"])
+
+
+def test_pool_out_shape_in_the_library_matches_the_builder(rt):
+    import ctypes
+    from helpers import POOL_CASES
+    from ttmlir_b200.ttnn_builder import ProgramBuilder
+    for h, w in ((9, 11), (7, 7), (56, 56), (5, 4)):
+        for name, (kind, kernel, stride, padding, dilation, ceil, _) in POOL_CASES.items():
+            if len(padding) == 4:
+                pt, pl, pb, pr = padding
+            else:
+                pt = pb = padding[0]
+                pl = pr = padding[1]
+            ho, wo = ctypes.c_int(), ctypes.c_int()
+            rc = rt.lib.ttb_pool2d_out_shape(int(kind == "max"), h, w, kernel[0], kernel[1], stride[0], stride[1], pt, pl, pb, pr,
+                                             dilation[0], dilation[1], int(ceil), int(len(padding) == 4),
+                                             ctypes.byref(ho), ctypes.byref(wo))
+            want = ProgramBuilder.pool_out_hw("MaxPool2d" if kind == "max" else "AvgPool2d", h, w, kernel, stride, padding,
+                                              dilation, ceil)
+            if min(want) <= 0:
+                assert rc != 0
+            else:
+                assert rc == 0 and (ho.value, wo.value) == want, (name, h, w)
+
+
 def test_metrics_special_cases():
     a = torch.tensor([1.0, 2.0, 3.0])
     assert metrics.get_pcc(a, a) == 1.0

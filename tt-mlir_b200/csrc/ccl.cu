@@ -127,6 +127,11 @@ static bool ncclOp(int reduceType, ncclRedOp_t &out) {
 // a barrier is then per block (block b waits for block b of the peers), which needs no
 // grid-wide synchronisation.  Flags carry a launch counter and the data and result regions
 // alternate between two copies per launch, so nothing is ever reset.
+// Pushed mode (MODE 2): the GEMM that produces the operand has already stored, from its epilogue,
+// every row block of its partial result into the workspace of the rank that owns the block
+// (ttb_symm_push_targets), so phase A is empty, phase B sums n local copies (no remote read), and
+// only the push of the reduced slice and phase C remain after the barrier: the reduce-scatter
+// half of the exchange has overlapped the GEMM.
 // Waits are bounded: when a peer does not show up within about a second the kernel records it
 // in the status word and carries on (the result of that launch is then invalid).
 constexpr int SYMM_MAX_RANKS = 8;
@@ -180,12 +185,14 @@ template <typename T> struct SymmVec { static constexpr int N = 16 / sizeof(T); 
 
 // NR: compile-time bound on the rank count (2, 4 or 8), which sizes the registers that hold the
 // loads in flight.
-template <typename T, bool RESIDUAL, bool STAGED, int NR>
+// MODE: 0 the operand is copied into the workspace, 1 the producer wrote it there, 2 pushed.
+template <typename T, bool RESIDUAL, int MODE, int NR>
 __global__ void __launch_bounds__(SYMM_THREADS)
     symmAllReduceKernel(SymmParams p, const uint4 *__restrict__ in, const uint4 *__restrict__ residual,
                         uint4 *__restrict__ out, size_t nvec) {
   constexpr int V = SymmVec<T>::N;
   constexpr int U = NR == 8 ? 2 : 4;
+  constexpr bool STAGED = MODE != 0;
   const size_t per = (nvec + p.n - 1) / p.n; // vectors per slice
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   const size_t first = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -234,8 +241,13 @@ __global__ void __launch_bounds__(SYMM_THREADS)
 #pragma unroll
           for (int r = 0; r < NR; ++r) {
             if (r < p.n) {
-              v[u][r] = (r == p.rank && !STAGED) ? __ldcs(in + i)
-                                                 : __ldcg(reinterpret_cast<const uint4 *>(p.ws[r] + p.dataOff) + i);
+              if (MODE == 2) {
+                // rank r's partial of the own slice, pushed here by r's GEMM
+                v[u][r] = __ldcg(reinterpret_cast<const uint4 *>(p.ws[p.rank] + p.dataOff) + r * per + (i - lo));
+              } else {
+                v[u][r] = (r == p.rank && !STAGED) ? __ldcs(in + i)
+                                                   : __ldcg(reinterpret_cast<const uint4 *>(p.ws[r] + p.dataOff) + i);
+              }
             }
           }
           if (RESIDUAL) rv[u] = __ldcs(residual + i);
@@ -292,7 +304,7 @@ __global__ void __launch_bounds__(SYMM_THREADS)
   stamp(5);
 }
 
-template <typename T, bool RESIDUAL, bool STAGED, int NR>
+template <typename T, bool RESIDUAL, int MODE, int NR>
 static int symmLaunch(const SymmParams &p, const void *in, const void *residual, void *out, size_t nvec, cudaStream_t st) {
   // All blocks of all ranks have to be resident at the same time (they wait for each other).
   static int perSm[64] = {};
@@ -301,7 +313,7 @@ static int symmLaunch(const SymmParams &p, const void *in, const void *residual,
   TTB_CHECK(dev >= 0 && dev < 64, "device ordinal out of range");
   if (!perSm[dev]) {
     int n = 0;
-    TTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, symmAllReduceKernel<T, RESIDUAL, STAGED, NR>, SYMM_THREADS, 0));
+    TTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, symmAllReduceKernel<T, RESIDUAL, MODE, NR>, SYMM_THREADS, 0));
     TTB_CHECK(n >= 1, "all-reduce kernel does not fit on an SM");
     perSm[dev] = n > 2 ? 2 : n;
   }
@@ -311,7 +323,7 @@ static int symmLaunch(const SymmParams &p, const void *in, const void *residual,
   if (cap > SYMM_MAX_BLOCKS) cap = SYMM_MAX_BLOCKS;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  symmAllReduceKernel<T, RESIDUAL, STAGED, NR><<<static_cast<unsigned>(blocks), SYMM_THREADS, 0, st>>>(
+  symmAllReduceKernel<T, RESIDUAL, MODE, NR><<<static_cast<unsigned>(blocks), SYMM_THREADS, 0, st>>>(
       p, static_cast<const uint4 *>(in), static_cast<const uint4 *>(residual), static_cast<uint4 *>(out), nvec);
   countLaunch();
   TTB_LAUNCH_CHECK();
@@ -319,19 +331,22 @@ static int symmLaunch(const SymmParams &p, const void *in, const void *residual,
 }
 
 template <typename T>
-static int symmDispatch(const SymmParams &p, const void *in, const void *residual, void *out, size_t nvec, bool staged,
+static int symmDispatch(const SymmParams &p, const void *in, const void *residual, void *out, size_t nvec, int mode,
                         cudaStream_t st) {
+#define TTB_SYMM_MODE(RES, NRv)                                                                       \
+  switch (mode) {                                                                                     \
+  case 0: return symmLaunch<T, RES, 0, NRv>(p, in, residual, out, nvec, st);                          \
+  case 1: return symmLaunch<T, RES, 1, NRv>(p, in, residual, out, nvec, st);                          \
+  default: return symmLaunch<T, RES, 2, NRv>(p, in, residual, out, nvec, st);                         \
+  }
 #define TTB_SYMM_NR(NRv)                                                                              \
-  if (residual) {                                                                                     \
-    return staged ? symmLaunch<T, true, true, NRv>(p, in, residual, out, nvec, st)                    \
-                  : symmLaunch<T, true, false, NRv>(p, in, residual, out, nvec, st);                  \
-  }                                                                                                   \
-  return staged ? symmLaunch<T, false, true, NRv>(p, in, residual, out, nvec, st)                     \
-                : symmLaunch<T, false, false, NRv>(p, in, residual, out, nvec, st);
+  if (residual) { TTB_SYMM_MODE(true, NRv) }                                                          \
+  TTB_SYMM_MODE(false, NRv)
   if (p.n <= 2) { TTB_SYMM_NR(2) }
   if (p.n <= 4) { TTB_SYMM_NR(4) }
   TTB_SYMM_NR(8)
 #undef TTB_SYMM_NR
+#undef TTB_SYMM_MODE
 }
 
 struct Symm {
@@ -595,9 +610,38 @@ int ttb_symm_status(void *symm, int *status) {
   return TTB_OK;
 }
 
+int ttb_symm_push_targets(void *symm, size_t bytes, void **targets, int *rank, int *nranks) {
+  TTB_CHECK(symm && targets && rank && nranks, "null argument");
+  auto *s = static_cast<Symm *>(symm);
+  TTB_CHECK(bytes <= s->maxBytes, "operand larger than the workspace allows");
+  TTB_CHECK(bytes % (16 * static_cast<size_t>(s->n)) == 0, "operand does not split into 16-byte aligned slices");
+  const size_t slice = bytes / s->n;
+  for (int o = 0; o < s->n; ++o) {
+    targets[o] = s->ws[o] + SYMM_FLAG_BYTES + static_cast<size_t>(s->launches & 1u) * s->maxBytes + s->rank * slice;
+  }
+  *rank = s->rank;
+  *nranks = s->n;
+  return TTB_OK;
+}
+
+static int symmAllReduceImpl(void *symm, const void *in, const void *residual, void *out, size_t count, int dtype,
+                             void *stream, bool pushed);
+
+int ttb_symm_all_reduce_pushed(void *symm, const void *residual, void *out, size_t count, int dtype, void *stream) {
+  TTB_CHECK(symm && out, "null argument");
+  return symmAllReduceImpl(symm, out /* unused */, residual, out, count, dtype, stream, true);
+}
+
 int ttb_symm_all_reduce(void *symm, const void *in, const void *residual, void *out, size_t count, int dtype,
                         void *stream) {
   TTB_CHECK(symm && in && out, "null argument");
+  return symmAllReduceImpl(symm, in, residual, out, count, dtype, stream, false);
+}
+
+} // extern "C"
+
+static int symmAllReduceImpl(void *symm, const void *in, const void *residual, void *out, size_t count, int dtype,
+                             void *stream, bool pushed) {
   auto *s = static_cast<Symm *>(symm);
   const size_t es = dtypeSize(dtype);
   const size_t bytes = count * es;
@@ -617,7 +661,11 @@ int ttb_symm_all_reduce(void *symm, const void *in, const void *residual, void *
   p.resultOff = SYMM_FLAG_BYTES + (2 + parity) * s->maxBytes;
   p.token = 2 * launch + 1;
   p.status = s->status;
-  p.oneShot = (s->n == 2 || bytes <= (size_t(256) << 10)) ? 1 : 0;
+  p.oneShot = (!pushed && (s->n == 2 || bytes <= (size_t(256) << 10))) ? 1 : 0;
+  if (pushed && bytes % (16 * static_cast<size_t>(s->n)) != 0) {
+    setLastError("symm_all_reduce_pushed: operand does not split into 16-byte aligned slices");
+    return TTB_ERR_UNSUPPORTED;
+  }
   p.stamps = s->stamps;
   const size_t nvec = bytes / 16;
   cudaStream_t st = asStream(stream);
@@ -626,9 +674,8 @@ int ttb_symm_all_reduce(void *symm, const void *in, const void *residual, void *
   // per rank: (n-1)/n of the operand read from peers and as much pushed to them, the operand and
   // the result once each locally, plus the staging copies
   ProfScope prof("symm_all_reduce", 0, double(bytes) * (2.0 + 2.0 * (s->n - 1) / s->n), st);
-  if (dtype == kBF16) return symmDispatch<__nv_bfloat16>(p, in, residual, out, nvec, staged, st);
-  if (dtype == kF16) return symmDispatch<__half>(p, in, residual, out, nvec, staged, st);
-  return symmDispatch<float>(p, in, residual, out, nvec, staged, st);
+  const int mode = pushed ? 2 : (staged ? 1 : 0);
+  if (dtype == kBF16) return symmDispatch<__nv_bfloat16>(p, in, residual, out, nvec, mode, st);
+  if (dtype == kF16) return symmDispatch<__half>(p, in, residual, out, nvec, mode, st);
+  return symmDispatch<float>(p, in, residual, out, nvec, mode, st);
 }
-
-} // extern "C"

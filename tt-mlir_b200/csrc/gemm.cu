@@ -10,7 +10,8 @@ namespace ttb {
 // Returns -1 when the problem is not one the tensor-core kernel takes.
 int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int abDtype, int biasDtype, int cDtype,
                    int64_t batch, int64_t m, int64_t n, int64_t k, int transA, int transB, int64_t aBatchStride,
-                   int64_t bBatchStride, int act, int roundSteps, const void *extra, int extraOp, cudaStream_t stream);
+                   int64_t bBatchStride, int act, int roundSteps, const void *extra, int extraOp, cudaStream_t stream,
+                   void *const *pushTargets = nullptr, int pushRanks = 0);
 int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, const int64_t *n, int count, int abDtype,
                           int cDtype, int64_t m, int64_t k, cudaStream_t stream);
 } // namespace ttb
@@ -66,4 +67,21 @@ extern "C" int ttb_gemm_grouped(const void *a, const void *const *b, void *const
     if (rc) return rc;
   }
   return TTB_OK;
+}
+
+// C = A[M, K] B[N, K]^T whose row block o (M / nranks rows) is stored into targets[o] instead of
+// one matrix: the producer half of an all-reduce over peer memory (ttb_symm_push_targets gives the
+// targets, ttb_symm_all_reduce_pushed finishes the sum).  Only the tensor-core kernel has this
+// mode; TTB_ERR_UNSUPPORTED tells the caller to produce C normally and use ttb_symm_all_reduce.
+extern "C" int ttb_gemm_push(const void *a, const void *b, void *const *targets, int nranks, int ab_dtype, int64_t m,
+                             int64_t n, int64_t k, void *stream) {
+  TTB_CHECK(a && b && targets, "null tensor");
+  TTB_CHECK(nranks >= 2 && nranks <= 8, "nranks must be between 2 and 8");
+  if (!tcgen05Disabled()) {
+    int rc = ttb::gemmTcgen05Try(a, b, nullptr, nullptr, ab_dtype, 0, ab_dtype, 1, m, n, k, 0, 1, 0, 0, TTB_ACT_NONE, 0, nullptr,
+                                 TTB_EXTRA_NONE, ttb::asStream(stream), targets, nranks);
+    if (rc != -1) return rc;
+  }
+  ttb::setLastError("gemm_push: shape, type or alignment not taken by the tensor-core kernel");
+  return TTB_ERR_UNSUPPORTED;
 }

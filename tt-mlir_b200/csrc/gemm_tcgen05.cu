@@ -90,6 +90,10 @@ struct TcParams {
   // mapB/mapC, mapB1/mapC1, mapB2/mapC2).  An ordinary launch is one segment.
   int segCum[3];
   int64_t segN[3];
+  // Push mode (the GEMM that feeds an all-reduce over peer memory): row block [o * pushRows,
+  // (o + 1) * pushRows) of C is stored through pushMaps.m[o], a [pushRows, N] matrix in rank o's
+  // workspace, instead of through mapC.  pushRows is a multiple of the tile height; 0 = off.
+  int pushRows;
   const void *extra; // optional [M, N] operand in the output type, combined after bias / activation
   int extraOp;       // TTB_EXTRA_*
   // Implicit-GEMM convolution: A is not a matrix in memory but the receptive fields of an NHWC
@@ -107,13 +111,17 @@ struct TcParams {
   int debug; // diagnostic: 1 = epilogue loads TMEM but skips math and stores, 2 = epilogue only hands the buffer back
 };
 
+struct PushMaps {
+  CUtensorMap m[8];
+};
+
 template <int BN, typename TC, bool PLAIN>
 __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     gemmTcgen05Kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                       const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapE,
                       const __grid_constant__ CUtensorMap mapB1, const __grid_constant__ CUtensorMap mapC1,
                       const __grid_constant__ CUtensorMap mapB2, const __grid_constant__ CUtensorMap mapC2,
-                      TC *__restrict__ c, TcParams p) {
+                      const __grid_constant__ PushMaps pushMaps, TC *__restrict__ c, TcParams p) {
   using Cfg = TcCfg<BN>;
   constexpr int STAGES = Cfg::kStages;
   extern __shared__ uint8_t smemRaw[];
@@ -357,6 +365,12 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
       const int seg = segmentOf(tile / tilesM, n0i);
       const int64_t n0 = n0i, segN = p.segN[seg];
       const CUtensorMap *mc = seg == 0 ? &mapC : (seg == 1 ? &mapC1 : &mapC2);
+      int rowBase = static_cast<int>(m0) + quarter * 32; // first row of this warp's block in the 2-D store
+      if (p.pushRows) {
+        const int owner = static_cast<int>(m0) / p.pushRows;
+        mc = &pushMaps.m[owner];
+        rowBase -= owner * p.pushRows;
+      }
       // patch mode: this warp's 32 rows are 32 / cTw rows of the patch, starting at (pOy, pOx) of image pImg
       int pImg = 0, pOy = 0, pOx = 0;
       if (p.cTw) {
@@ -528,8 +542,8 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
                            "r"(pImg) : "memory");
           } else {
             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                         ::"l"(reinterpret_cast<uint64_t>(mc)), "r"(buf), "r"(static_cast<int>(col0)),
-                           "r"(static_cast<int>(m0 + quarter * 32)) : "memory");
+                         ::"l"(reinterpret_cast<uint64_t>(mc)), "r"(buf), "r"(static_cast<int>(col0)), "r"(rowBase)
+                         : "memory");
           }
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
@@ -615,11 +629,12 @@ static bool makeMap4(CUtensorMap *map, const void *ptr, int dtype, int64_t c, in
 
 template <int BN, typename TC, bool PLAIN>
 static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &me, void *c, const TcParams &p,
-                    cudaStream_t st, const CUtensorMap *more = nullptr /* mapB1, mapC1, mapB2, mapC2 of a grouped launch */);
+                    cudaStream_t st, const CUtensorMap *more = nullptr /* mapB1, mapC1, mapB2, mapC2 of a grouped launch */,
+                    const PushMaps *push = nullptr);
 
 template <int BN, typename TC, bool PLAIN>
 static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &me, void *c, const TcParams &p,
-                    cudaStream_t st, const CUtensorMap *more) {
+                    cudaStream_t st, const CUtensorMap *more, const PushMaps *push) {
   using Cfg = TcCfg<BN>;
   // Function attributes belong to a device: set the shared-memory limit once on each.
   static bool attrSet[64] = {};
@@ -632,7 +647,8 @@ static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensor
   int64_t tiles = (p.cTw ? p.cTilesM : (p.M + TC_BM - 1) / TC_BM) * p.segCum[2];
   int grid = static_cast<int>(tiles < smCount() ? tiles : smCount());
   gemmTcgen05Kernel<BN, TC, PLAIN><<<grid, PLAIN ? TC_THREADS : TC_THREADS_EPI8, Cfg::kSmem, st>>>(
-      ma, mb, mc, me, more ? more[0] : mb, more ? more[1] : mc, more ? more[2] : mb, more ? more[3] : mc, static_cast<TC *>(c), p);
+      ma, mb, mc, me, more ? more[0] : mb, more ? more[1] : mc, more ? more[2] : mb, more ? more[3] : mc,
+      push ? *push : PushMaps{{mc, mc, mc, mc, mc, mc, mc, mc}}, static_cast<TC *>(c), p);
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;
@@ -640,7 +656,18 @@ static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensor
 
 int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int abDtype, int biasDtype, int cDtype,
                    int64_t batch, int64_t m, int64_t n, int64_t k, int transA, int transB, int64_t, int64_t, int act,
-                   int roundSteps, const void *extra, int extraOp, cudaStream_t stream) {
+                   int roundSteps, const void *extra, int extraOp, cudaStream_t stream, void *const *pushTargets,
+                   int pushRanks) {
+  // Push mode: C's row blocks go to `pushRanks` [m / pushRanks, n] matrices (one per rank) instead of c.
+  const bool pushing = pushRanks > 0;
+  if (pushing) {
+    if (!pushTargets || pushRanks > 8 || bias || act != TTB_ACT_NONE || roundSteps || extraOp || cDtype != abDtype) return -1;
+    if (m % pushRanks != 0 || (m / pushRanks) % TC_BM != 0) return -1;
+    for (int o = 0; o < pushRanks; ++o) {
+      if (!pushTargets[o] || !aligned16(pushTargets[o])) return -1;
+    }
+    c = pushTargets[0]; // only checked for alignment below
+  }
   // What this kernel takes: one 16-bit A[M,K] and B[N,K] (the "transpose_b" weight layout),
   // rows 16-byte aligned, output in a 16- or 32-bit float type.
   if (batch != 1 || transA || !transB) return -1;
@@ -686,6 +713,14 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   p.convX = nullptr;
   p.cTw = 0;
   p.cTilesM = 0;
+  p.pushRows = 0;
+  PushMaps pm;
+  if (pushing) {
+    p.pushRows = static_cast<int>(m / pushRanks);
+    for (int o = 0; o < 8; ++o) {
+      if (!makeMap(&pm.m[o], pushTargets[o < pushRanks ? o : 0], cDtype, p.pushRows, n, 32)) return -1;
+    }
+  }
   p.segCum[0] = p.segCum[1] = p.segCum[2] = static_cast<int>((n + bn - 1) / bn);
   p.segN[0] = p.segN[1] = p.segN[2] = n;
   p.fmt = abDtype == kBF16 ? 1 : 0;
@@ -698,7 +733,8 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   ProfScope prof("gemm_tcgen05", flops, bytes, stream);
   const bool plain = !bias && act == TTB_ACT_NONE && roundSteps == 0 && !extraOp;
 #define TTB_TC(BNv, TCv)                                                                 \
-  return plain ? launchTc<BNv, TCv, true>(ma, mb, mc, me, c, p, stream) : launchTc<BNv, TCv, false>(ma, mb, mc, me, c, p, stream)
+  return plain ? launchTc<BNv, TCv, true>(ma, mb, mc, me, c, p, stream, nullptr, pushing ? &pm : nullptr)                     \
+               : launchTc<BNv, TCv, false>(ma, mb, mc, me, c, p, stream)
 #define TTB_TC_BN(TCv)                                                                   \
   switch (bn) {                                                                          \
   case 256: TTB_TC(256, TCv);                                                            \
@@ -760,7 +796,7 @@ int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, c
   p.M = m; p.N = n[0]; p.K = k;
   p.bias = nullptr; p.biasDt = 0; p.act = TTB_ACT_NONE; p.roundSteps = 0;
   p.extra = nullptr; p.extraOp = 0;
-  p.convX = nullptr; p.cTw = 0; p.cTilesM = 0;
+  p.convX = nullptr; p.cTw = 0; p.cTilesM = 0; p.pushRows = 0;
   int cum = 0;
   double flops = 0, bytes = double(m) * k * 2;
   for (int i = 0; i < 3; ++i) {
@@ -853,6 +889,7 @@ int convTcgen05Try(const void *x, const void *wre, const void *bias, void *out, 
   p.extra = extraOp ? extra : nullptr;
   p.extraOp = extra ? extraOp : 0;
   p.convX = x;
+  p.pushRows = 0;
   p.cH = static_cast<int>(h); p.cW = static_cast<int>(w); p.cC = static_cast<int>(c);
   p.cHo = static_cast<int>(ho); p.cWo = static_cast<int>(wo);
   p.ckw = kw; p.csh = sh; p.csw = sw; p.cpt = pt; p.cpl = pl; p.cdh = dh; p.cdw = dw;

@@ -7,6 +7,8 @@
 // accesses.  Reference call sites: runtime/lib/ttnn/operations/data_movement/*.cpp.
 #include "common.cuh"
 
+#include <cstring>
+
 namespace ttb {
 
 struct CopyDims {
@@ -139,11 +141,153 @@ __global__ void __launch_bounds__(256) ropeKernel(const T *__restrict__ x, const
   }
 }
 
+// ---- embedding -------------------------------------------------------------------------
+// out[r, :] = table[index[r], :]  (EmbeddingOp, runtime/lib/ttnn/operations/embedding/embedding.cpp;
+// torch twin ttir_cpu.py embedding = F.embedding).  One warp per row, `unit`-byte accesses.
+// Indices may be stored as integers or as floats (TTNN accepts bf16 index tensors).  An index
+// outside the table sets the error word instead of reading out of bounds.
+template <typename I> __device__ __forceinline__ long long indexValue(I v) { return static_cast<long long>(v); }
+template <> __device__ __forceinline__ long long indexValue<float>(float v) { return static_cast<long long>(v); }
+template <> __device__ __forceinline__ long long indexValue<__nv_bfloat16>(__nv_bfloat16 v) {
+  return static_cast<long long>(__bfloat162float(v));
+}
+template <> __device__ __forceinline__ long long indexValue<__half>(__half v) {
+  return static_cast<long long>(__half2float(v));
+}
+
+__device__ int g_embeddingBadIndex; // sticky: set when a kernel saw an index outside its table
+
+template <typename I, typename U>
+__global__ void __launch_bounds__(256) embeddingKernel(const I *__restrict__ idx, const U *__restrict__ table,
+                                                       U *__restrict__ out, size_t rows, size_t vocab, size_t unitsPerRow) {
+  size_t row = static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  long long t = indexValue(idx[row]);
+  if (t < 0 || static_cast<size_t>(t) >= vocab) {
+    if (lane == 0) g_embeddingBadIndex = 1;
+    t = 0;
+  }
+  const U *src = table + static_cast<size_t>(t) * unitsPerRow;
+  U *dst = out + row * unitsPerRow;
+  for (size_t i = lane; i < unitsPerRow; i += 32) dst[i] = src[i];
+}
+
+// ---- pad -------------------------------------------------------------------------------
+// Constant padding in front of and behind every dimension (PadOp,
+// runtime/lib/ttnn/operations/data_movement/pad.cpp: `padding` holds (low, high) per dimension;
+// torch twin ttir_cpu.py pad).  One thread per output element.
+struct PadDims {
+  int rank;
+  int64_t outShape[8], inShape[8], lo[8];
+};
+
+template <typename U>
+__global__ void __launch_bounds__(256) padKernel(const U *__restrict__ in, U *__restrict__ out, size_t n, PadDims d, U fill) {
+  size_t step = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += step) {
+    size_t r = i;
+    int64_t at = 0, mul = 1;
+    bool inside = true;
+    for (int k = d.rank - 1; k >= 0; --k) {
+      const int64_t c = static_cast<int64_t>(r % d.outShape[k]) - d.lo[k];
+      r /= d.outShape[k];
+      inside = inside && c >= 0 && c < d.inShape[k];
+      at += c * mul;
+      mul *= d.inShape[k];
+    }
+    out[i] = inside ? in[at] : fill;
+  }
+}
+
 } // namespace ttb
 
 using namespace ttb;
 
 extern "C" {
+
+int ttb_embedding(const void *indices, const void *table, void *out, int index_dtype, int dtype, size_t rows,
+                  size_t vocab, size_t dim, void *stream) {
+  TTB_CHECK(indices && table && out, "null tensor");
+  if (rows * dim == 0) return TTB_OK;
+  TTB_CHECK(vocab > 0, "empty embedding table");
+  cudaStream_t st = asStream(stream);
+  const size_t rowBytes = dim * dtypeSize(dtype);
+  TTB_CHECK(rowBytes > 0, "unsupported table dtype");
+  int unit = 16;
+  while (unit > 1 && (rowBytes % unit != 0 || reinterpret_cast<uintptr_t>(table) % unit != 0 ||
+                      reinterpret_cast<uintptr_t>(out) % unit != 0)) {
+    unit /= 2;
+  }
+  ProfScope prof("embedding", 0, double(rows) * rowBytes * 2 + double(rows) * dtypeSize(index_dtype), st);
+  const int grid = static_cast<int>((rows + 7) / 8);
+#define TTB_EMB(I)                                                                                                   \
+  switch (unit) {                                                                                                    \
+  case 16: embeddingKernel<I, uint4><<<grid, 256, 0, st>>>(static_cast<const I *>(indices), static_cast<const uint4 *>(table), static_cast<uint4 *>(out), rows, vocab, rowBytes / 16); break; \
+  case 8: embeddingKernel<I, uint2><<<grid, 256, 0, st>>>(static_cast<const I *>(indices), static_cast<const uint2 *>(table), static_cast<uint2 *>(out), rows, vocab, rowBytes / 8); break;    \
+  case 4: embeddingKernel<I, uint32_t><<<grid, 256, 0, st>>>(static_cast<const I *>(indices), static_cast<const uint32_t *>(table), static_cast<uint32_t *>(out), rows, vocab, rowBytes / 4); break; \
+  case 2: embeddingKernel<I, uint16_t><<<grid, 256, 0, st>>>(static_cast<const I *>(indices), static_cast<const uint16_t *>(table), static_cast<uint16_t *>(out), rows, vocab, rowBytes / 2); break; \
+  default: embeddingKernel<I, uint8_t><<<grid, 256, 0, st>>>(static_cast<const I *>(indices), static_cast<const uint8_t *>(table), static_cast<uint8_t *>(out), rows, vocab, rowBytes); break;      \
+  }
+  switch (index_dtype) {
+  case kI32: TTB_EMB(int32_t) break;
+  case kU32: TTB_EMB(uint32_t) break;
+  case kU16: TTB_EMB(uint16_t) break;
+  case kF32: TTB_EMB(float) break;
+  case kBF16: TTB_EMB(__nv_bfloat16) break;
+  case kF16: TTB_EMB(__half) break;
+  default: setLastError("embedding: unsupported index dtype"); return TTB_ERR_UNSUPPORTED;
+  }
+#undef TTB_EMB
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_embedding_status(int *bad_index_seen) {
+  TTB_CHECK(bad_index_seen != nullptr, "null result");
+  TTB_CUDA(cudaDeviceSynchronize());
+  TTB_CUDA(cudaMemcpyFromSymbol(bad_index_seen, g_embeddingBadIndex, sizeof(int)));
+  return TTB_OK;
+}
+
+int ttb_pad(const void *in, void *out, int dtype, int rank, const int64_t *in_shape, const int64_t *low,
+            const int64_t *high, double value, void *stream) {
+  TTB_CHECK(in && out && in_shape && low && high, "null argument");
+  TTB_CHECK(rank >= 1 && rank <= 8, "rank must be between 1 and 8");
+  PadDims d;
+  d.rank = rank;
+  size_t n = 1, nin = 1;
+  for (int i = 0; i < rank; ++i) {
+    TTB_CHECK(in_shape[i] >= 0 && low[i] >= 0 && high[i] >= 0, "negative extent or padding");
+    d.inShape[i] = in_shape[i];
+    d.lo[i] = low[i];
+    d.outShape[i] = in_shape[i] + low[i] + high[i];
+    n *= static_cast<size_t>(d.outShape[i]);
+    nin *= static_cast<size_t>(in_shape[i]);
+  }
+  if (n == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("pad", 0, double(n + nin) * dtypeSize(dtype), st);
+  const int grid = gridFor(n, 256);
+  switch (dtype) {
+  case kF32: { float f = static_cast<float>(value); uint32_t u; memcpy(&u, &f, 4);
+    padKernel<uint32_t><<<grid, 256, 0, st>>>(static_cast<const uint32_t *>(in), static_cast<uint32_t *>(out), n, d, u); break; }
+  case kBF16: { __nv_bfloat16 b = __float2bfloat16_rn(static_cast<float>(value)); uint16_t u; memcpy(&u, &b, 2);
+    padKernel<uint16_t><<<grid, 256, 0, st>>>(static_cast<const uint16_t *>(in), static_cast<uint16_t *>(out), n, d, u); break; }
+  case kF16: { __half b = __float2half_rn(static_cast<float>(value)); uint16_t u; memcpy(&u, &b, 2);
+    padKernel<uint16_t><<<grid, 256, 0, st>>>(static_cast<const uint16_t *>(in), static_cast<uint16_t *>(out), n, d, u); break; }
+  case kI32: padKernel<int32_t><<<grid, 256, 0, st>>>(static_cast<const int32_t *>(in), static_cast<int32_t *>(out), n, d, static_cast<int32_t>(value)); break;
+  case kU32: padKernel<uint32_t><<<grid, 256, 0, st>>>(static_cast<const uint32_t *>(in), static_cast<uint32_t *>(out), n, d, static_cast<uint32_t>(value)); break;
+  case kU16: padKernel<uint16_t><<<grid, 256, 0, st>>>(static_cast<const uint16_t *>(in), static_cast<uint16_t *>(out), n, d, static_cast<uint16_t>(value)); break;
+  case kU8: padKernel<uint8_t><<<grid, 256, 0, st>>>(static_cast<const uint8_t *>(in), static_cast<uint8_t *>(out), n, d, static_cast<uint8_t>(value)); break;
+  case kI8: padKernel<int8_t><<<grid, 256, 0, st>>>(static_cast<const int8_t *>(in), static_cast<int8_t *>(out), n, d, static_cast<int8_t>(value)); break;
+  default: setLastError("pad: unsupported dtype"); return TTB_ERR_UNSUPPORTED;
+  }
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
 
 int ttb_strided_copy(const void *in, void *out, int elem_size, int rank, const int64_t *out_shape,
                      const int64_t *in_strides, int64_t in_offset, void *stream) {

@@ -7,6 +7,13 @@
 //  rms_norm x * rsqrt(mean(x^2) + eps) * w (+ b), computed in f32, rounded once
 //           include/ttmlir/Dialect/TTIR/IR/TTIROps.td:2300-2336, golden tools/golden/mapping.py:1221-1290
 //  reduce   sum / mean / max / min over a dimension, f32 accumulation  ttir_cpu.py:374-397
+//  layer_norm (x - mean) * rsqrt(var + eps) * w + b over the trailing dimensions the weight
+//           covers, biased variance, f32   ttir_cpu.py layer_norm (torch F.layer_norm);
+//           call site runtime/lib/ttnn/operations/normalization/layer_norm.cpp
+//  argmax   index of the first maximum (a NaN counts as the maximum), Int32   ttir_cpu.py argmax;
+//           call site runtime/lib/ttnn/operations/reduction/argmax.cpp
+//  cumsum   running sum along a dimension, f32 accumulation for floats, every prefix rounded
+//           to the element type   ttir_cpu.py cumsum; call site operations/cumsum/cumsum.cpp
 #include "common.cuh"
 
 #include <cfloat>
@@ -187,6 +194,114 @@ int launchRms(const void *a, const void *b, const void *w, const void *bias, voi
   return TTB_OK;
 }
 
+// ---- layer_norm ------------------------------------------------------------------------
+// One block per row, two passes over the row for the statistics (mean first, then the centred
+// sum of squares: the numerically safe form) and one for the result; passes two and three hit
+// L1 / L2.  The row's bytes cross HBM once in, once out.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    layerNormKernel(const T *__restrict__ in, const T *__restrict__ w, const T *__restrict__ bias, T *__restrict__ out,
+                    size_t cols, float eps) {
+  __shared__ float scratch[33];
+  const T *x = in + static_cast<size_t>(blockIdx.x) * cols;
+  T *y = out + static_cast<size_t>(blockIdx.x) * cols;
+  float s = 0.0f;
+  for (size_t i = threadIdx.x; i < cols; i += blockDim.x) s += toF32(x[i]);
+  const float mean = blockSum(s, scratch) / static_cast<float>(cols);
+  float ss = 0.0f;
+  for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
+    const float d = toF32(x[i]) - mean;
+    ss += d * d;
+  }
+  const float rstd = rsqrtf(blockSum(ss, scratch) / static_cast<float>(cols) + eps);
+  for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
+    float f = (toF32(x[i]) - mean) * rstd;
+    if (w) f *= toF32(w[i]);
+    if (bias) f += toF32(bias[i]);
+    y[i] = fromF32<T>(f);
+  }
+}
+
+// ---- argmax ----------------------------------------------------------------------------
+// `better(a, ia, b, ib)`: does candidate b replace a?  A NaN beats every number; among equals
+// (and among NaNs) the smaller index stays.
+__device__ __forceinline__ bool argBetter(float a, long long ia, float b, long long ib) {
+  const bool an = a != a, bn = b != b;
+  if (an || bn) return bn && (!an || ib < ia);
+  return b > a || (b == a && ib < ia);
+}
+
+// inner == 1: one warp per row.
+template <typename T>
+__global__ void __launch_bounds__(256) argmaxRowKernel(const T *__restrict__ in, int32_t *__restrict__ out, size_t rows,
+                                                       size_t len) {
+  size_t row = static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const T *x = in + row * len;
+  float best = -INFINITY;
+  long long at = 0x7fffffffffffffffll;
+  for (size_t i = lane; i < len; i += 32) {
+    const float f = toF32(x[i]);
+    if (at == 0x7fffffffffffffffll || argBetter(best, at, f, static_cast<long long>(i))) {
+      best = f;
+      at = static_cast<long long>(i);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const long long oa = __shfl_xor_sync(0xffffffffu, at, o);
+    if (oa != 0x7fffffffffffffffll && (at == 0x7fffffffffffffffll || argBetter(best, at, ob, oa))) {
+      best = ob;
+      at = oa;
+    }
+  }
+  if (lane == 0) out[row] = static_cast<int32_t>(at);
+}
+
+// inner > 1: one thread per (outer, inner) column.
+template <typename T>
+__global__ void __launch_bounds__(256) argmaxColKernel(const T *__restrict__ in, int32_t *__restrict__ out, size_t outer,
+                                                       size_t len, size_t inner) {
+  size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t c = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < outer * inner; c += stride) {
+    size_t base = (c / inner) * len * inner + (c % inner);
+    float best = toF32(in[base]);
+    long long at = 0;
+    for (size_t i = 1; i < len; ++i) {
+      const float f = toF32(in[base + i * inner]);
+      if (argBetter(best, at, f, static_cast<long long>(i))) {
+        best = f;
+        at = static_cast<long long>(i);
+      }
+    }
+    out[c] = static_cast<int32_t>(at);
+  }
+}
+
+// ---- cumsum ----------------------------------------------------------------------------
+// One thread per (outer, inner) line, sequential along the scanned dimension (the order of a
+// sequential sum, which is what the reference computes).  ACC: float for floats, int64 for ints.
+template <typename T, typename ACC>
+__global__ void __launch_bounds__(256) cumsumKernel(const T *__restrict__ in, T *__restrict__ out, size_t outer, size_t len,
+                                                    size_t inner) {
+  size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t c = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < outer * inner; c += stride) {
+    size_t base = (c / inner) * len * inner + (c % inner);
+    ACC acc = 0;
+    for (size_t i = 0; i < len; ++i) {
+      if constexpr (std::is_same<ACC, float>::value) {
+        acc += toF32(in[base + i * inner]);
+        out[base + i * inner] = fromF32<T>(acc);
+      } else {
+        acc += static_cast<ACC>(in[base + i * inner]);
+        out[base + i * inner] = static_cast<T>(acc);
+      }
+    }
+  }
+}
+
 // ---- reductions ------------------------------------------------------------------------
 enum { rSum, rMean, rMax, rMin };
 
@@ -269,6 +384,61 @@ int ttb_add_rms_norm(const void *a, const void *b, const void *weight, void *sum
   TTB_DISPATCH_FLOAT(dtype, T, {
     return launchRms<T, true>(a, b, weight, nullptr, sum_out, out, rows, cols, eps, asStream(stream));
   });
+  return TTB_OK;
+}
+
+int ttb_layer_norm(const void *in, const void *weight, const void *bias, void *out, int dtype, size_t rows, size_t cols,
+                   float eps, void *stream) {
+  TTB_CHECK(in && out, "null tensor");
+  if (rows * cols == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("layer_norm", 0, double(rows) * cols * 2 * dtypeSize(dtype), st);
+  TTB_DISPATCH_FLOAT(dtype, T, {
+    layerNormKernel<T><<<static_cast<unsigned>(rows), 256, 0, st>>>(static_cast<const T *>(in), static_cast<const T *>(weight),
+                                                                    static_cast<const T *>(bias), static_cast<T *>(out),
+                                                                    cols, eps);
+  });
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_argmax(const void *in, void *out, int dtype, size_t outer, size_t len, size_t inner, void *stream) {
+  TTB_CHECK(in && out, "null tensor");
+  if (outer * inner == 0) return TTB_OK;
+  TTB_CHECK(len > 0 && len <= 0x7fffffffull, "argmax needs between 1 and 2^31-1 candidates");
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("argmax", 0, double(outer) * len * inner * dtypeSize(dtype) + double(outer) * inner * 4, st);
+  TTB_DISPATCH_DTYPE(dtype, T, {
+    if (inner == 1) {
+      int grid = static_cast<int>((outer + 7) / 8);
+      argmaxRowKernel<T><<<grid, 256, 0, st>>>(static_cast<const T *>(in), static_cast<int32_t *>(out), outer, len);
+    } else {
+      argmaxColKernel<T><<<gridFor(outer * inner, 256), 256, 0, st>>>(static_cast<const T *>(in),
+                                                                      static_cast<int32_t *>(out), outer, len, inner);
+    }
+  });
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_cumsum(const void *in, void *out, int dtype, size_t outer, size_t len, size_t inner, void *stream) {
+  TTB_CHECK(in && out, "null tensor");
+  if (outer * len * inner == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("cumsum", 0, double(outer) * len * inner * 2 * dtypeSize(dtype), st);
+  const int grid = gridFor(outer * inner, 256);
+  switch (dtype) {
+  case kF32: cumsumKernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float *>(in), static_cast<float *>(out), outer, len, inner); break;
+  case kBF16: cumsumKernel<__nv_bfloat16, float><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(in), static_cast<__nv_bfloat16 *>(out), outer, len, inner); break;
+  case kF16: cumsumKernel<__half, float><<<grid, 256, 0, st>>>(static_cast<const __half *>(in), static_cast<__half *>(out), outer, len, inner); break;
+  case kI32: cumsumKernel<int32_t, long long><<<grid, 256, 0, st>>>(static_cast<const int32_t *>(in), static_cast<int32_t *>(out), outer, len, inner); break;
+  case kU32: cumsumKernel<uint32_t, long long><<<grid, 256, 0, st>>>(static_cast<const uint32_t *>(in), static_cast<uint32_t *>(out), outer, len, inner); break;
+  default: setLastError("cumsum: unsupported dtype"); return TTB_ERR_UNSUPPORTED;
+  }
+  countLaunch();
+  TTB_LAUNCH_CHECK();
   return TTB_OK;
 }
 

@@ -96,7 +96,27 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     IN1_OUT(DistributeTensorOp, in)
     IN1_OUT(AggregateTensorOp, in)
     IN1_OUT(MeshPartitionOp, in)
+    IN1_OUT(ReductionArgMaxOp, in)
+    IN1_OUT(CumSumOp, in)
+    IN1_OUT(Pool2dOp, in)
+    IN1_OUT(GlobalAvgPool2dOp, in)
+    IN1_OUT(PadOp, in)
 #undef IN1_OUT
+  case OpType::LayerNormOp: {
+    const auto *o = op->type_as_LayerNormOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->weight());
+    pushRef(ins, o->bias());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::EmbeddingOp: {
+    const auto *o = op->type_as_EmbeddingOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->weight());
+    pushRef(outs, o->out());
+    break;
+  }
   case OpType::EltwiseBinaryOp: {
     const auto *o = op->type_as_EltwiseBinaryOp();
     pushRef(ins, o->lhs());
@@ -380,6 +400,9 @@ private:
   size_t tryAllReduceAdd(size_t i);
   bool symmReady(size_t bytes);
   TensorPtr allocForAllReduce(const fbt::TensorRef *ref); // null unless `ref` feeds the next all-reduce
+  bool feedsSymmAllReduce(const fbt::TensorRef *ref);      // `ref`'s only consumer is an all-reduce the peer-memory kernel takes
+  // GEMM whose result only feeds an all-reduce: scattered into the peers' workspaces.  Null = not applicable.
+  TensorPtr tryGemmPush(const TensorPtr &a, const TensorPtr &b, const fbt::TensorRef *outRef, int64_t M, int64_t N, int64_t K);
   size_t curOp = 0;
   void allReduce(const TensorPtr &in, const TensorPtr &residual, const TensorPtr &out, int reduceType);
   size_t tryAddRmsNorm(size_t i);
@@ -425,6 +448,13 @@ private:
   void runMeshPartition(const fbt::MeshPartitionOp *op);
   void runDistribute(const fbt::DistributeTensorOp *op);
   void runAggregate(const fbt::AggregateTensorOp *op);
+  void runLayerNorm(const fbt::LayerNormOp *op);
+  void runArgMax(const fbt::ReductionArgMaxOp *op);
+  void runCumSum(const fbt::CumSumOp *op);
+  void runEmbedding(const fbt::EmbeddingOp *op);
+  void runPool2d(const fbt::Pool2dOp *op);
+  void runGlobalAvgPool2d(const fbt::GlobalAvgPool2dOp *op);
+  void runPad(const fbt::PadOp *op);
   // sub-programs: const-eval cache, calls, traces
   std::vector<TensorPtr> runSubProgram(uint32_t index, const std::vector<TensorPtr> &inputs);
   void runLoadCached(const fbt::LoadCachedOp *op);
@@ -726,6 +756,13 @@ size_t Executor::runOp(size_t i) {
   case OpType::MeshPartitionOp: runMeshPartition(op->type_as_MeshPartitionOp()); break;
   case OpType::DistributeTensorOp: runDistribute(op->type_as_DistributeTensorOp()); break;
   case OpType::AggregateTensorOp: runAggregate(op->type_as_AggregateTensorOp()); break;
+  case OpType::LayerNormOp: runLayerNorm(op->type_as_LayerNormOp()); break;
+  case OpType::ReductionArgMaxOp: runArgMax(op->type_as_ReductionArgMaxOp()); break;
+  case OpType::CumSumOp: runCumSum(op->type_as_CumSumOp()); break;
+  case OpType::EmbeddingOp: runEmbedding(op->type_as_EmbeddingOp()); break;
+  case OpType::Pool2dOp: runPool2d(op->type_as_Pool2dOp()); break;
+  case OpType::GlobalAvgPool2dOp: runGlobalAvgPool2d(op->type_as_GlobalAvgPool2dOp()); break;
+  case OpType::PadOp: runPad(op->type_as_PadOp()); break;
   case OpType::LoadCachedOp: runLoadCached(op->type_as_LoadCachedOp()); break;
   case OpType::FuncCallOp: runFuncCall(op->type_as_FuncCallOp()); break;
   case OpType::BeginTraceCaptureOp: runBeginTraceCapture(op->type_as_BeginTraceCaptureOp()); break;
@@ -1167,8 +1204,6 @@ void Executor::runGemm(const fbt::TensorRef *aRef, const fbt::TensorRef *bRef, c
   TensorPtr a = getDevice(aRef), b = getDevice(bRef);
   TensorPtr bias = biasRef ? getDevice(biasRef) : nullptr;
   TensorPtr extra = extraRef ? getDevice(extraRef) : nullptr;
-  TensorPtr out = allocForAllReduce(outRef);
-  if (!out) out = allocOut(outRef);
   TTRT_ASSERT(a->dtype == b->dtype, "matmul operands differ in data type: ", dataTypeName(a->dtype), " vs ",
               dataTypeName(b->dtype));
   // 1-D operands follow numpy: a vector lhs is a row, a vector rhs is a column.
@@ -1192,6 +1227,15 @@ void Executor::runGemm(const fbt::TensorRef *aRef, const fbt::TensorRef *bRef, c
     batch = 1;
     aStride = 0;
   }
+  if (batch == 1 && !ta && tb && !bias && !extra && act == 0 && roundSteps == 0 &&
+      static_cast<int64_t>(prod(refShape(outRef), 0, refShape(outRef).size())) == M * N) {
+    if (TensorPtr pushed = tryGemmPush(a, b, outRef, M, N, K)) {
+      put(outRef, pushed);
+      return;
+    }
+  }
+  TensorPtr out = allocForAllReduce(outRef);
+  if (!out) out = allocOut(outRef);
   TTRT_ASSERT(static_cast<int64_t>(out->volume()) == batch * M * N, "matmul result has ", out->volume(),
               " elements, expected ", batch * M * N);
   if (bias) {
@@ -1679,6 +1723,167 @@ void Executor::runReduction(const fbt::ReductionOp *op) {
   put(op->out(), out);
 }
 
+// layer_norm over the trailing dimensions the weight covers (the last one without a weight).
+void Executor::runLayerNorm(const fbt::LayerNormOp *op) {
+  TensorPtr in = getDevice(op->input());
+  TensorPtr w = op->weight() ? getDevice(op->weight()) : nullptr;
+  TensorPtr b = op->bias() ? getDevice(op->bias()) : nullptr;
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(!in->shape.empty(), "layer_norm of a scalar");
+  size_t cols = w ? w->volume() : (b ? b->volume() : in->shape.back());
+  TTRT_ASSERT(cols > 0 && in->volume() % cols == 0, "layer_norm weight does not cover whole trailing dimensions");
+  size_t rows = in->volume() / cols;
+  if (w) TTRT_ASSERT(w->dtype == in->dtype, "layer_norm weight must have the input's data type");
+  if (b) TTRT_ASSERT(b->volume() == cols && b->dtype == in->dtype, "layer_norm bias must match the weight and the data type");
+  TTRT_ASSERT(out->volume() == in->volume() && out->dtype == in->dtype, "layer_norm changes shape or type");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_layer_norm(in->shards[i]->ptr, w ? w->shards[i]->ptr : nullptr, b ? b->shards[i]->ptr : nullptr,
+                            out->shards[i]->ptr, ttbDtype(in->dtype), rows, cols, op->epsilon(), r.stream));
+  });
+  put(op->out(), out);
+}
+
+// argmax along one dimension, or over everything when the op names none.  Int32 / UInt32 result.
+void Executor::runArgMax(const fbt::ReductionArgMaxOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(out->dtype == DataType::Int32 || out->dtype == DataType::UInt32, "argmax produces 32-bit indices");
+  size_t rank = in->shape.size(), outer = 1, len = in->volume(), inner = 1;
+  if (op->dim().has_value() && rank > 0) {
+    int d = normDim(*op->dim(), rank);
+    outer = prod(in->shape, 0, d);
+    len = in->shape[d];
+    inner = prod(in->shape, d + 1, rank);
+  }
+  TTRT_ASSERT(out->volume() == outer * inner, "argmax result has ", out->volume(), " elements, expected ", outer * inner);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_argmax(in->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(in->dtype), outer, len, inner, r.stream));
+  });
+  put(op->out(), out);
+}
+
+void Executor::runCumSum(const fbt::CumSumOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(out->dtype == in->dtype && out->volume() == in->volume(), "cumsum with a type change is not supported");
+  size_t rank = in->shape.size();
+  TTRT_ASSERT(rank > 0, "cumsum of a scalar");
+  int d = normDim(op->dim(), rank);
+  size_t outer = prod(in->shape, 0, d), len = in->shape[d], inner = prod(in->shape, d + 1, rank);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_cumsum(in->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(in->dtype), outer, len, inner, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// out[..., :] = weight[input[...], :]; a weight of shape [1, 1, V, D] is a [V, D] table.
+void Executor::runEmbedding(const fbt::EmbeddingOp *op) {
+  TensorPtr idx = getDevice(op->input());
+  TensorPtr w = getDevice(op->weight());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(w->shape.size() >= 2, "embedding table needs two dimensions");
+  size_t dim = w->shape.back(), vocab = w->shape[w->shape.size() - 2];
+  TTRT_ASSERT(w->volume() == vocab * dim, "embedding table has leading dimensions other than 1");
+  TTRT_ASSERT(out->dtype == w->dtype, "embedding result must have the table's data type");
+  size_t rows = idx->volume();
+  TTRT_ASSERT(out->volume() == rows * dim, "embedding result has ", out->volume(), " elements, expected ", rows * dim);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_embedding(idx->shards[i]->ptr, w->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(idx->dtype), ttbDtype(w->dtype),
+                           rows, vocab, dim, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// Pool2dOp: NHWC activation, flattened to [1, 1, N*H*W, C] in real flatbuffers; N, H, W, C come as fields.
+void Executor::runPool2d(const fbt::Pool2dOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = allocOut(op->out());
+  const int n = static_cast<int>(op->batch_size()), h = static_cast<int>(op->input_height()),
+            w = static_cast<int>(op->input_width()), c = static_cast<int>(op->channels());
+  TTRT_ASSERT(in->volume() == size_t(n) * h * w * c, "pool2d input has ", in->volume(), " elements, the op says ", n, "x", h,
+              "x", w, "x", c);
+  auto two = [](const fb::Vector<int32_t> *v, const char *what, int &a, int &b, int dflt) {
+    if (!v || v->size() == 0) {
+      a = b = dflt;
+      return;
+    }
+    TTRT_ASSERT(v->size() == 2, what, " needs two entries");
+    a = v->Get(0);
+    b = v->Get(1);
+  };
+  int kh, kw, sh, sw, dh, dw;
+  two(op->kernel_size(), "kernel_size", kh, kw, 1);
+  two(op->stride(), "stride", sh, sw, 1);
+  two(op->dilation(), "dilation", dh, dw, 1);
+  int pt = 0, pl = 0, pb = 0, pr = 0, four = 0;
+  if (op->padding() && op->padding()->size() == 2) {
+    pt = pb = op->padding()->Get(0);
+    pl = pr = op->padding()->Get(1);
+  } else if (op->padding() && op->padding()->size() == 4) {
+    pt = op->padding()->Get(0); // top, left, bottom, right (runtime/lib/ttnn/operations/pool/pool2d.cpp:49-55)
+    pl = op->padding()->Get(1);
+    pb = op->padding()->Get(2);
+    pr = op->padding()->Get(3);
+    four = 1;
+  } else {
+    TTRT_ASSERT(!op->padding() || op->padding()->size() == 0, "padding needs two or four entries");
+  }
+  const bool isMax = op->type() == fbt::Pool2dOpType::MaxPool2d;
+  int includePad = 1;
+  if (!isMax) {
+    const auto *extra = op->extra_params_as_AvgPool2dExtraParams();
+    TTRT_ASSERT(extra != nullptr, "avg_pool2d without its parameters");
+    includePad = extra->count_include_pad() ? 1 : 0;
+  }
+  int ho = 0, wo = 0;
+  TTB_CALL(ttb_pool2d_out_shape(isMax, h, w, kh, kw, sh, sw, pt, pl, pb, pr, isMax ? dh : 1, isMax ? dw : 1, op->ceil_mode(), four,
+                                &ho, &wo));
+  TTRT_ASSERT(out->volume() == size_t(n) * ho * wo * c, "pool2d result has ", out->volume(), " elements, expected ", n, "x", ho,
+              "x", wo, "x", c);
+  TTRT_ASSERT(out->dtype == in->dtype, "pool2d changes the data type");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_pool2d(in->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(in->dtype), isMax, n, h, w, c, kh, kw, sh, sw, pt, pl,
+                        pb, pr, dh, dw, op->ceil_mode(), includePad, four, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// [N, H, W, C] -> [N, 1, 1, C]: the mean over H*W, which is the column form of the reduction kernel.
+void Executor::runGlobalAvgPool2d(const fbt::GlobalAvgPool2dOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(in->shape.size() == 4, "global_avg_pool2d expects an NHWC tensor");
+  TTRT_ASSERT(out->dtype == in->dtype, "global_avg_pool2d with a type change is not supported");
+  size_t n = in->shape[0], hw = size_t(in->shape[1]) * in->shape[2], c = in->shape[3];
+  TTRT_ASSERT(out->volume() == n * c, "global_avg_pool2d result has ", out->volume(), " elements, expected ", n * c);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_reduce(1 /* mean */, in->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(in->dtype), n, hw, c, r.stream));
+  });
+  put(op->out(), out);
+}
+
+void Executor::runPad(const fbt::PadOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = allocOut(op->out());
+  size_t rank = in->shape.size();
+  TTRT_ASSERT(rank >= 1 && rank <= 8, "pad supports ranks 1 to 8");
+  TTRT_ASSERT(op->padding() && op->padding()->size() == 2 * rank, "pad needs a (low, high) pair per dimension");
+  int64_t shape[8], lo[8], hi[8];
+  size_t vol = 1;
+  for (size_t d = 0; d < rank; ++d) {
+    shape[d] = in->shape[d];
+    lo[d] = op->padding()->Get(static_cast<uint32_t>(2 * d));
+    hi[d] = op->padding()->Get(static_cast<uint32_t>(2 * d + 1));
+    vol *= static_cast<size_t>(shape[d] + lo[d] + hi[d]);
+  }
+  TTRT_ASSERT(out->volume() == vol && out->dtype == in->dtype, "pad result does not match input plus padding");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_pad(in->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(in->dtype), static_cast<int>(rank), shape, lo, hi,
+                     static_cast<double>(op->value()), r.stream));
+  });
+  put(op->out(), out);
+}
+
 // ---- data movement --------------------------------------------------------------------------------------------
 void Executor::runReshape(const fbt::ReshapeOp *op) {
   TensorPtr in = get(op->in());
@@ -2041,20 +2246,71 @@ bool Executor::symmReady(size_t bytes) {
 // A tensor whose only consumer is the next all-reduce (a sum over a float type, no other
 // all-reduce in between) is produced straight into the staging region of that all-reduce, which
 // then has nothing to copy.
-TensorPtr Executor::allocForAllReduce(const fbt::TensorRef *ref) {
-  if (!fuse || dev->worldSize == 1 || !singleUse(ref)) return nullptr;
+bool Executor::feedsSymmAllReduce(const fbt::TensorRef *ref) {
+  if (!fuse || dev->worldSize == 1 || !singleUse(ref)) return false;
   auto use = info.firstUse.find(ref->global_id());
-  if (use == info.firstUse.end() || use->second <= curOp) return nullptr;
+  if (use == info.firstUse.end() || use->second <= curOp) return false;
   const auto *ops = prog->operations();
   const auto *consumer = ops->Get(use->second);
-  if (consumer->type_type() != OpType::AllReduceOp) return nullptr;
+  if (consumer->type_type() != OpType::AllReduceOp) return false;
   const auto *ar = consumer->type_as_AllReduceOp();
-  if (static_cast<int>(ar->reduce_type()) != 0 || meshAxisSize(ar->cluster_axis()) == 1) return nullptr;
+  if (static_cast<int>(ar->reduce_type()) != 0 || meshAxisSize(ar->cluster_axis()) == 1) return false;
   for (uint32_t k = static_cast<uint32_t>(curOp) + 1; k < use->second; ++k) {
-    if (ops->Get(k)->type_type() == OpType::AllReduceOp) return nullptr;
+    if (ops->Get(k)->type_type() == OpType::AllReduceOp) return false;
   }
   DataType dt = refDtype(ref);
-  if (dt != DataType::BFloat16 && dt != DataType::Float16 && dt != DataType::Float32) return nullptr;
+  return dt == DataType::BFloat16 || dt == DataType::Float16 || dt == DataType::Float32;
+}
+
+// The row-parallel projections of a tensor-parallel block (o_proj, down_proj) produce partial sums
+// that only the following all-reduce reads.  Their GEMM stores every row block of its result from
+// the epilogue into the workspace of the rank that reduces that block, so the reduce-scatter half
+// of the all-reduce has happened by the time the GEMM ends.  TTB_DISABLE_GEMM_PUSH=1 turns it off.
+TensorPtr Executor::tryGemmPush(const TensorPtr &a, const TensorPtr &b, const fbt::TensorRef *outRef, int64_t M, int64_t N,
+                                int64_t K) {
+  static const bool disabled = [] {
+    const char *e = std::getenv("TTB_DISABLE_GEMM_PUSH");
+    return e && e[0] == '1';
+  }();
+  if (disabled || !feedsSymmAllReduce(outRef)) return nullptr;
+  DataType dt = refDtype(outRef);
+  if ((dt != DataType::BFloat16 && dt != DataType::Float16) || a->dtype != dt) return nullptr;
+  const int64_t n = dev->worldSize;
+  const size_t bytes = static_cast<size_t>(M) * N * dataTypeSize(dt);
+  if (M % n != 0 || (M / n) % 128 != 0 || bytes % (16 * n) != 0 || !symmReady(bytes)) return nullptr;
+  auto t = std::make_shared<TensorImpl>();
+  t->shape = refShape(outRef);
+  t->stride = denseStrides(t->shape);
+  t->dtype = dt;
+  t->storage = Storage::Device;
+  t->layout = refLayout(outRef);
+  t->device = dev;
+  t->pushedForAllReduce = true;
+  bool ok = true;
+  eachRank([&](size_t i, const RankCtx &r) {
+    if (!ok) return;
+    void *targets[8] = {};
+    int rank = 0, nranks = 0;
+    TTB_CALL(ttb_symm_push_targets(r.symm, bytes, targets, &rank, &nranks));
+    int rc = ttb_gemm_push(a->shards[i]->ptr, b->shards[i]->ptr, targets, nranks, ttbDtype(dt), M, N, K, r.stream);
+    if (rc == TTB_ERR_UNSUPPORTED && i == 0) {
+      ok = false; // nothing was launched on any rank yet: the caller takes the ordinary path
+      return;
+    }
+    if (rc != TTB_OK) TTRT_FATAL("ttb_gemm_push failed (", rc, "): ", ttb_last_error());
+    auto buf = std::make_shared<Buffer>();
+    TTB_CALL(ttb_symm_input_buffer(r.symm, bytes, &buf->ptr)); // the region the partials land in; never read as a matrix
+    buf->bytes = bytes;
+    buf->cudaDevice = r.cudaDevice;
+    buf->kind = Buffer::Kind::Borrowed;
+    t->shards.push_back(buf);
+  });
+  return ok ? t : nullptr;
+}
+
+TensorPtr Executor::allocForAllReduce(const fbt::TensorRef *ref) {
+  if (!feedsSymmAllReduce(ref)) return nullptr;
+  DataType dt = refDtype(ref);
   auto t = std::make_shared<TensorImpl>();
   t->shape = refShape(ref);
   t->stride = denseStrides(t->shape);
@@ -2083,6 +2339,14 @@ void Executor::allReduce(const TensorPtr &in, const TensorPtr &residual, const T
   // peers have moved past), so collectives stay outside traces.
   refuseWhileRecording("a collective");
   bool isFloat = in->dtype == DataType::BFloat16 || in->dtype == DataType::Float16 || in->dtype == DataType::Float32;
+  if (in->pushedForAllReduce) {
+    TTRT_ASSERT(reduceType == 0, "a scattered GEMM result can only be summed");
+    eachRank([&](size_t i, const RankCtx &r) {
+      TTB_CALL(ttb_symm_all_reduce_pushed(r.symm, residual ? residual->shards[i]->ptr : nullptr, out->shards[i]->ptr,
+                                          in->volume(), ttbDtype(in->dtype), r.stream));
+    });
+    return;
+  }
   if (reduceType == 0 && isFloat && in->bytes() % 16 == 0 && symmReady(in->bytes())) {
     eachRank([&](size_t i, const RankCtx &r) {
       TTB_CALL(ttb_symm_all_reduce(r.symm, in->shards[i]->ptr, residual ? residual->shards[i]->ptr : nullptr,

@@ -164,6 +164,9 @@ struct TensorImpl {
   // Run when the tensor dies (const-eval cache entries keyed by it are dropped).
   std::vector<std::function<void()>> onDestroy;
   void *readyEvent = nullptr;      // recorded after the producing work was enqueued
+  // The tensor was never assembled: its producer scattered it, row block by row block, into the
+  // all-reduce workspaces of the ranks that will sum the blocks.  Only that all-reduce may read it.
+  bool pushedForAllReduce = false;
 
   size_t volume() const {
     size_t v = 1;

@@ -229,6 +229,32 @@ S.table("RMSNormOp", [
     ("memory_config", "MemoryConfig"), ("out", "TensorRef"),
     ("compute_config", "DeviceComputeKernelConfig")])
 
+S.table("LayerNormOp", [
+    ("input", "TensorRef"), ("weight", "TensorRef"), ("bias", "TensorRef"), ("epsilon", "f32"),
+    ("memory_config", "MemoryConfig"), ("out", "TensorRef")])
+S.table("ReductionArgMaxOp", [
+    ("in", "TensorRef"), ("out", "TensorRef"), ("dim", "i32", OPT), ("keep_dim", "bool"),
+    ("memcfg", "MemoryConfig")])
+# operations/cumsum.fbs
+S.table("CumSumOp", [
+    ("in", "TensorRef"), ("out", "TensorRef"), ("dim", "i32"), ("dtype", "DataType", OPT),
+    ("memcfg", "MemoryConfig")])
+# operations/embedding.fbs
+S.table("EmbeddingOp", [("input", "TensorRef"), ("weight", "TensorRef"), ("out", "TensorRef")])
+# operations/pool.fbs
+S.enum("Pool2dOpType", "u32", ["AvgPool2d", "MaxPool2d"])
+S.table("AvgPool2dExtraParams", [("count_include_pad", "bool")])
+S.table("MaxPool2dExtraParams", [])
+S.union("Pool2dExtraParams", ["AvgPool2dExtraParams", "MaxPool2dExtraParams"])
+S.table("Pool2dOp", [
+    ("type", "Pool2dOpType"), ("in", "TensorRef"), ("out", "TensorRef"), ("batch_size", "u32"),
+    ("input_height", "u32"), ("input_width", "u32"), ("channels", "u32"), ("kernel_size", "[i32]"),
+    ("stride", "[i32]"), ("padding", "[i32]"), ("dilation", "[i32]"), ("extra_params", "Pool2dExtraParams"),
+    ("memory_config", "MemoryConfig"), ("applied_shard_scheme", "TensorMemoryLayout", OPT),
+    ("ceil_mode", "bool"), ("reallocate_halo_output", "bool", True), ("config_tensors_in_dram", "bool")])
+S.table("GlobalAvgPool2dOp", [
+    ("in", "TensorRef"), ("out", "TensorRef"), ("memory_config", "MemoryConfig"), ("dtype", "DataType", OPT)])
+
 # --- data movement (operations/data_movement.fbs)
 S.table("ConcatOp", [
     ("inputs", "[TensorRef]"), ("out", "TensorRef"), ("dim", "i32"),
@@ -251,6 +277,9 @@ S.table("SliceOp", [
     ("type", "SliceOpType"), ("in", "TensorRef"), ("out", "TensorRef"), ("step", "[i64]"),
     ("params", "SliceOpParams")])
 S.table("TransposeOp", [("in", "TensorRef"), ("out", "TensorRef"), ("dim0", "i32"), ("dim1", "i32")])
+S.table("PadOp", [
+    ("in", "TensorRef"), ("out", "TensorRef"), ("padding", "[u32]"), ("value", "f32"),
+    ("use_multicore", "bool"), ("memcfg", "MemoryConfig")])
 
 # --- transformer (operations/transformer.fbs)
 S.table("ConcatenateHeadsOp", [("in", "TensorRef"), ("out", "TensorRef"), ("memcfg", "MemoryConfig")])

@@ -530,6 +530,101 @@ class ProgramBuilder:
                    list(ins), [out], loc)
         return out
 
+    # ---- wider op set: normalisation, pooling, embedding, argmax, pad, cumsum ------------------------------------
+    def layer_norm(self, x: Value, weight: Optional[Value] = None, bias: Optional[Value] = None, epsilon: float = 1e-5,
+                   loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        ins = [v for v in (x, weight, bias) if v is not None]
+        self._emit("LayerNormOp", {"input": x.ref, "weight": weight.ref if weight else None,
+                                   "bias": bias.ref if bias else None, "epsilon": float(epsilon),
+                                   "memory_config": self._mc(), "out": out.ref}, ins, [out], loc)
+        return out
+
+    def argmax(self, x: Value, dim: Optional[int] = None, keep_dim: bool = False, loc=None) -> Value:
+        rank = len(x.shape)
+        if dim is None:
+            shape = [1] * rank if keep_dim else []
+        else:
+            d = _norm(dim, rank)
+            shape = [1 if i == d else s for i, s in enumerate(x.shape)] if keep_dim else \
+                [s for i, s in enumerate(x.shape) if i != d]
+        out = self._value(shape, "Int32")
+        self._emit("ReductionArgMaxOp", {"in": x.ref, "out": out.ref, "dim": dim, "keep_dim": keep_dim,
+                                         "memcfg": self._mc()}, [x], [out], loc)
+        return out
+
+    def cumsum(self, x: Value, dim: int, loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        self._emit("CumSumOp", {"in": x.ref, "out": out.ref, "dim": dim, "memcfg": self._mc()}, [x], [out], loc)
+        return out
+
+    def embedding(self, indices: Value, weight: Value, loc=None) -> Value:
+        out = self._value(list(indices.shape) + [weight.shape[-1]], weight.dtype)
+        self._emit("EmbeddingOp", {"input": indices.ref, "weight": weight.ref, "out": out.ref}, [indices, weight], [out], loc)
+        return out
+
+    @staticmethod
+    def pool_out_hw(kind, h, w, kernel, stride, padding, dilation=(1, 1), ceil_mode=False):
+        """Output extent of Pool2dOp, following torch's rule the way the reference's CPU twin applies
+        it: four paddings (top, left, bottom, right) -- and, for the average, two paddings larger than
+        half the kernel -- are applied to the input by hand before pooling."""
+        if len(padding) == 4:
+            pt, pl, pb, pr = padding
+            by_hand = True
+        else:
+            pt = pb = padding[0]
+            pl = pr = padding[1]
+            by_hand = False
+        if kind == "AvgPool2d":
+            dilation = (1, 1)
+            by_hand = not ((pt == pb and pl == pr) and not (pt > kernel[0] // 2 or pl > kernel[1] // 2))
+
+        def extent(n, k, lo, hi, s, d):
+            if by_hand:
+                n, lo, hi = n + lo + hi, 0, 0
+            num = n + lo + hi - d * (k - 1) - 1 + (s - 1 if ceil_mode else 0)
+            out = num // s + 1
+            if ceil_mode and (out - 1) * s >= n + lo:
+                out -= 1
+            return out
+        return (extent(h, kernel[0], pt, pb, stride[0], dilation[0]), extent(w, kernel[1], pl, pr, stride[1], dilation[1]))
+
+    def _pool2d(self, kind, x, batch, height, width, channels, kernel, stride, padding, dilation, ceil_mode, extra, loc):
+        ho, wo = self.pool_out_hw(kind, height, width, kernel, stride, padding, dilation, ceil_mode)
+        out = self._value([1, 1, batch * ho * wo, channels], x.dtype)
+        self._emit("Pool2dOp", {
+            "type": kind, "in": x.ref, "out": out.ref, "batch_size": batch, "input_height": height, "input_width": width,
+            "channels": channels, "kernel_size": list(kernel), "stride": list(stride), "padding": list(padding),
+            "dilation": list(dilation), "extra_params": extra, "memory_config": self._mc(), "ceil_mode": ceil_mode},
+            [x], [out], loc)
+        return out
+
+    def max_pool2d(self, x: Value, batch: int, height: int, width: int, channels: int, kernel=(2, 2), stride=(2, 2),
+                   padding=(0, 0), dilation=(1, 1), ceil_mode: bool = False, loc=None) -> Value:
+        """`x` is the flattened NHWC activation [1, 1, N*H*W, C]; `padding` is (h, w) or (top, left, bottom, right)."""
+        return self._pool2d("MaxPool2d", x, batch, height, width, channels, kernel, stride, padding, dilation, ceil_mode,
+                            ("MaxPool2dExtraParams", {}), loc)
+
+    def avg_pool2d(self, x: Value, batch: int, height: int, width: int, channels: int, kernel=(2, 2), stride=(2, 2),
+                   padding=(0, 0), ceil_mode: bool = False, count_include_pad: bool = True, loc=None) -> Value:
+        return self._pool2d("AvgPool2d", x, batch, height, width, channels, kernel, stride, padding, (1, 1), ceil_mode,
+                            ("AvgPool2dExtraParams", {"count_include_pad": count_include_pad}), loc)
+
+    def global_avg_pool2d(self, x: Value, loc=None) -> Value:
+        n, _, _, c = x.shape
+        out = self._value([n, 1, 1, c], x.dtype)
+        self._emit("GlobalAvgPool2dOp", {"in": x.ref, "out": out.ref, "memory_config": self._mc()}, [x], [out], loc)
+        return out
+
+    def pad(self, x: Value, padding: Sequence[int], value: float = 0.0, loc=None) -> Value:
+        """`padding` = (low_0, high_0, low_1, high_1, ...), one pair per dimension."""
+        assert len(padding) == 2 * len(x.shape)
+        shape = [s + padding[2 * i] + padding[2 * i + 1] for i, s in enumerate(x.shape)]
+        out = self._value(shape, x.dtype)
+        self._emit("PadOp", {"in": x.ref, "out": out.ref, "padding": list(padding), "value": float(value),
+                             "use_multicore": True, "memcfg": self._mc()}, [x], [out], loc)
+        return out
+
     # ---- sub-programs: const-eval, calls, traces -------------------------------------------------------------
     def input_like(self, v: Value, on_device: Optional[bool] = None) -> Value:
         return self.input(v.shape, v.dtype, v.on_device if on_device is None else on_device)

@@ -218,6 +218,31 @@ TTB_API int ttb_embedding_status(int *bad_index_seen);
 TTB_API int ttb_pad(const void *in, void *out, int dtype, int rank, const int64_t *in_shape,
                     const int64_t *low, const int64_t *high, double value, void *stream);
 
+/* ---- KV cache and decode attention (runtime/lib/ttnn/operations/kv_cache/{fill_cache,update_cache}.cpp,
+ * operations/transformer/scaled_dot_product_attention_decode.cpp; goldens tools/golden/mapping.py:
+ * 3582-3670, 2417-2482).  Caches are [cache_users, heads, max_seq, head_dim].
+ *  fill_cache    cache[batch_offset + b, h, :seq] = input[b, h]  (input [users, heads, seq, head_dim]); the
+ *                rows up to the next multiple of 32 are zeroed when the cache has them
+ *  update_cache  cache[batch_offset + b, h, index] = input[0, h, b]  (input [1, heads, users, head_dim]),
+ *                `index` = element 0 of a device tensor, read by the kernel.  An index outside the cache
+ *                writes nothing and sets a sticky flag (ttb_update_cache_status, synchronises)
+ *  sdpa_decode   q [1, batch, heads, head_dim] against k, v [batch, kv_heads, seq, head_dim]; keys after
+ *                cur_pos[b] (Int32, nullable) are masked when is_causal; `mask` (nullable, the tensors'
+ *                dtype) is [mask_users, 1, mask_heads, seq] with extents 1 or full; scores are
+ *                (q.k + mask) * scale.  bf16 / f16, head_dim 64 / 128 / 256, heads / kv_heads in {1,2,4,8}.
+ *                `workspace`: ttb_sdpa_decode_workspace_bytes(...) bytes of device memory. */
+TTB_API int ttb_fill_cache(void *cache, const void *input, int dtype, size_t users, size_t heads, size_t seq,
+                           size_t max_seq, size_t head_dim, size_t batch_offset, size_t cache_users, void *stream);
+TTB_API int ttb_update_cache(void *cache, const void *input, const void *index, int dtype, int index_dtype,
+                             size_t users, size_t heads, size_t max_seq, size_t head_dim, size_t batch_offset,
+                             size_t cache_users, void *stream);
+TTB_API int ttb_update_cache_status(int *bad_index_seen);
+TTB_API size_t ttb_sdpa_decode_workspace_bytes(int batch, int heads, int seq, int head_dim);
+TTB_API int ttb_sdpa_decode(const void *q, const void *k, const void *v, const void *cur_pos, const void *mask,
+                            void *out, int dtype, int batch, int heads, int kv_heads, int seq, int head_dim,
+                            int mask_users, int mask_heads, float scale, int is_causal, void *workspace,
+                            size_t workspace_bytes, void *stream);
+
 /* ---- data movement: ::ttnn::permute / slice / concat / repeat / transpose
  * (runtime/lib/ttnn/operations/data_movement/). One gather kernel covers them: out is dense
  * row-major of `out_shape`; element (i0..ik) is read from in + in_offset + sum(i_d * in_strides[d]). */

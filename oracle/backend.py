@@ -188,6 +188,22 @@ class OracleBuilder:
     def global_avg_pool2d(self, x, loc=None): return _map(ops.global_avg_pool2d, x)
     def pad(self, x, padding, value=0.0, loc=None): return _map(lambda t: ops.pad(t, padding, value), x)
 
+    def fill_cache(self, cache, x, batch_offset=0, loc=None): return _map(lambda c, t: ops.fill_cache(c, t, batch_offset), cache, x)
+
+    def update_cache(self, cache, x, update_index, batch_offset=0, loc=None):
+        return _map(lambda c, t, i: ops.update_cache(c, t, i, batch_offset), cache, x, update_index)
+
+    def scaled_dot_product_attention_decode(self, q, k, v, cur_pos=None, mask=None, is_causal=True, scale=None, loc=None):
+        vals = [x for x in (q, k, v, cur_pos, mask) if x is not None]
+
+        def fn(*ts):
+            it = iter(ts)
+            qq, kk, vv = next(it), next(it), next(it)
+            cp = next(it) if cur_pos is not None else None
+            mk = next(it) if mask is not None else None
+            return ops.sdpa_decode(qq, kk, vv, cp, mk, is_causal, scale)
+        return _map(fn, *vals)
+
     def reduce(self, kind, x, dims, keep_dim, loc=None): return _map(lambda t: ops.reduce(kind, t, dims, keep_dim), x)
 
     # ---- data movement

@@ -288,6 +288,51 @@ def pad(x, padding, value=0.0):  # ttir_cpu.py pad: (low, high) per dimension, o
     return F.pad(x, tuple(flat), value=value)
 
 
+def fill_cache(cache, x, batch_offset=0):
+    """mapping.py:3582-3611 (fill_cache_golden), with the batch offset the TTNN op takes: the input's
+    users land at cache[batch_offset : batch_offset + users]; rows up to the next multiple of the
+    32-row tile are zeroed when the cache has them."""
+    out = cache.clone()
+    users, _, seq, _ = x.shape
+    pad = (seq + 31) // 32 * 32
+    out[batch_offset:batch_offset + users, :, :seq, :] = x
+    if seq < pad <= cache.shape[2]:
+        out[batch_offset:batch_offset + users, :, seq:pad, :] = 0
+    return out
+
+
+def update_cache(cache, x, update_index, batch_offset=0):
+    """mapping.py:3614-3670 (update_cache_golden): cache[batch_offset + b, h, idx, :] = x[0, h, b, :]."""
+    out = cache.clone()
+    idx = int(update_index.flatten()[0].item())
+    users = x.shape[2]
+    out[batch_offset:batch_offset + users, :, idx, :] = x[0].permute(1, 0, 2)
+    return out
+
+
+def sdpa_decode(q, k, v, cur_pos=None, mask=None, is_causal=True, scale=None):
+    """mapping.py:2417-2482 (sdpa_decode_golden): q [1, B, H, D], k / v [B, Hkv, S, D]; the mask
+    [B|1, 1, H|1, S] is added before the scale; causal = keys after cur_pos[b] are -inf."""
+    qq = q.float().squeeze(0).unsqueeze(2)                      # [B, H, 1, D]
+    kk, vv = k.float(), v.float()
+    rep = qq.shape[1] // kk.shape[1]
+    if rep > 1:
+        kk = torch.repeat_interleave(kk, rep, dim=1)
+        vv = torch.repeat_interleave(vv, rep, dim=1)
+    qk = torch.matmul(qq, kk.transpose(-2, -1))                 # [B, H, 1, S]
+    if mask is not None:
+        qk = qk + mask.float().permute(0, 2, 1, 3)
+    elif is_causal and cur_pos is not None:
+        cm = torch.zeros((qk.shape[0], 1, 1, qk.shape[3]), dtype=torch.float32)
+        for i in range(qk.shape[0]):
+            cm[i, :, :, int(cur_pos[i].item()) + 1:] = float("-inf")
+        qk = qk + cm
+    if scale is not None:
+        qk = qk * scale
+    out = torch.matmul(torch.softmax(qk, dim=-1), vv)           # [B, H, 1, D]
+    return out.squeeze(2).unsqueeze(0).to(q.dtype)
+
+
 def concatenate_heads(x):
     b, h, s, d = x.shape
     return x.permute(0, 2, 1, 3).reshape(b, s, h * d)

@@ -1,0 +1,431 @@
+// KV-cache maintenance and single-token ("decode") attention over the cache.
+//
+// Reference semantics (goldens in tools/golden/mapping.py; runtime call sites in
+// runtime/lib/ttnn/operations/kv_cache/{fill_cache,update_cache}.cpp and
+// operations/transformer/scaled_dot_product_attention_decode.cpp):
+//  fill_cache    cache[batch_offset + b, h, :S, :] = input[b, h, :, :]; rows S .. roundup(S, 32) of
+//                those users are zeroed when they exist (mapping.py:3582-3611, the tile padding)
+//  update_cache  cache[batch_offset + b, h, index, :] = input[0, h, b, :], `index` = element 0 of a
+//                tensor (mapping.py:3614-3670).  The kernel reads the index on the device: no
+//                host round trip (the reference reads it on the host, update_cache.cpp:17-37)
+//  sdpa_decode   q [1, B, H, D] against k, v [B, Hkv, S, D]: scores = q k^T (+ mask [B|1, 1, H|1, S]),
+//                keys after cur_pos[b] masked when causal, then * scale, softmax, P v; f32 math,
+//                one rounding (mapping.py:2417-2482)
+//
+// Decode attention is HBM-bound: every byte of the live part of K and V is read exactly once.
+// One CTA takes (chunk of keys, kv head, user) and serves all G = H / Hkv query heads of that kv
+// head, so GQA does not multiply the traffic; the key range is split into chunks so that small
+// batches still fill the GPU; a second small kernel merges the chunks' partial results with the
+// usual running-max rescaling.
+#include "common.cuh"
+
+#include <cfloat>
+
+namespace ttb {
+
+// ---- cache writes --------------------------------------------------------------------------
+template <typename U>
+__global__ void __launch_bounds__(256)
+    fillCacheKernel(U *__restrict__ cache, const U *__restrict__ in, size_t users, size_t heads, size_t seq, size_t padSeq,
+                    size_t maxSeq, size_t rowUnits, size_t batchOffset) {
+  const size_t total = users * heads * padSeq * rowUnits;
+  const size_t step = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+    const size_t u = i % rowUnits;
+    size_t r = i / rowUnits;
+    const size_t s = r % padSeq;
+    r /= padSeq;
+    const size_t h = r % heads, b = r / heads;
+    U v = {};
+    if (s < seq) v = in[((b * heads + h) * seq + s) * rowUnits + u];
+    cache[(((batchOffset + b) * heads + h) * maxSeq + s) * rowUnits + u] = v;
+  }
+}
+
+template <typename U, typename I>
+__global__ void __launch_bounds__(256)
+    updateCacheKernel(U *__restrict__ cache, const U *__restrict__ in, const I *__restrict__ index, size_t users, size_t heads,
+                      size_t maxSeq, size_t rowUnits, size_t batchOffset, int *__restrict__ bad) {
+  const long long at = static_cast<long long>(index[0]);
+  if (at < 0 || static_cast<size_t>(at) >= maxSeq) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) *bad = 1;
+    return;
+  }
+  const size_t total = users * heads * rowUnits;
+  const size_t step = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+    const size_t u = i % rowUnits;
+    size_t r = i / rowUnits;
+    const size_t b = r % users, h = r / users; // input is [1, heads, users, D]
+    cache[(((batchOffset + b) * heads + h) * maxSeq + static_cast<size_t>(at)) * rowUnits + u] = in[i];
+  }
+}
+
+__device__ int g_cacheBadIndex; // sticky: an update index outside the cache was seen (nothing was written)
+
+// ---- decode attention ------------------------------------------------------------------------
+constexpr int DEC_THREADS = 256;
+constexpr int DEC_WARPS = DEC_THREADS / 32;
+constexpr int DEC_CHUNK = 512; // keys per CTA
+
+struct DecodeParams {
+  int B, H, Hkv, S, chunks;
+  int maskB, maskH; // extents of the mask's user and head dimensions (1 = broadcast), 0 = no mask
+  float scale;
+  int causal;
+};
+
+// Partial attention of G query heads over one chunk of keys.  Writes, per (user, head, chunk):
+// m (running max), l (sum of exp(s - m)) and the unnormalised o[D] = sum exp(s - m) v.
+template <typename T, int G, int D>
+__global__ void __launch_bounds__(DEC_THREADS)
+    sdpaDecodeChunkKernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
+                          const int32_t *__restrict__ curPos, const T *__restrict__ mask, float *__restrict__ pm,
+                          float *__restrict__ pl, float *__restrict__ po, DecodeParams p) {
+  constexpr int LPK = D / 16;       // lanes that share one key row in the score phase (16 elements each)
+  constexpr int KPW = 32 / LPK;     // keys a warp scores per step
+  constexpr int DPL = D / 32;       // output dims per lane in the value phase
+  __shared__ float sq[G][D];
+  __shared__ float sc[G][DEC_CHUNK];
+  __shared__ float so[2][G][D]; // exchange slots of the cross-warp sum
+  __shared__ float sm[G], sl[G];
+  const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int last = p.S - 1; // last key a query of this user may see
+  if (p.causal && curPos) last = min(last, curPos[b]);
+  const int k0 = chunk * DEC_CHUNK, k1 = min(k0 + DEC_CHUNK, last + 1);
+  const int h0 = kvh * G;
+  const size_t part = (static_cast<size_t>(b) * p.H + h0) * p.chunks + chunk; // + g * chunks per head
+  if (k1 <= k0) {
+    // nothing of this chunk is visible: an empty partial
+    if (threadIdx.x < G) {
+      pm[part + static_cast<size_t>(threadIdx.x) * p.chunks] = -INFINITY;
+      pl[part + static_cast<size_t>(threadIdx.x) * p.chunks] = 0.0f;
+    }
+    for (int i = threadIdx.x; i < G * D; i += DEC_THREADS) {
+      po[(part + static_cast<size_t>(i / D) * p.chunks) * D + (i % D)] = 0.0f;
+    }
+    return;
+  }
+  for (int i = threadIdx.x; i < G * D; i += DEC_THREADS) {
+    sq[i / D][i % D] = toF32(q[(static_cast<size_t>(b) * p.H + h0 + i / D) * D + (i % D)]);
+  }
+  __syncthreads();
+  const T *kb = k + (static_cast<size_t>(b) * p.Hkv + kvh) * p.S * D;
+  const T *vb = v + (static_cast<size_t>(b) * p.Hkv + kvh) * p.S * D;
+
+  // scores: LPK lanes per key, 16 elements (two 16-byte loads) per lane
+  {
+    const int sub = lane % LPK, slot = lane / LPK;
+    float qr[G][16];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int e = 0; e < 16; ++e) qr[g][e] = sq[g][sub * 16 + e];
+    for (int j0 = k0 + warp * KPW; j0 < k1; j0 += DEC_WARPS * KPW) {
+      const int j = j0 + slot;
+      float dot[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) dot[g] = 0.0f;
+      if (j < k1) {
+        const uint4 *row = reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(j) * D + sub * 16);
+        uint4 raw[2] = {__ldcs(row), __ldcs(row + 1)};
+        const T *e = reinterpret_cast<const T *>(raw);
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+          const float kv = toF32(e[x]);
+#pragma unroll
+          for (int g = 0; g < G; ++g) dot[g] = fmaf(qr[g][x], kv, dot[g]);
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int o = LPK / 2; o > 0; o >>= 1) dot[g] += __shfl_xor_sync(0xffffffffu, dot[g], o);
+      }
+      if (sub == 0 && j < k1) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float s = dot[g];
+          if (mask) {
+            const size_t mb = p.maskB == 1 ? 0 : b, mh = p.maskH == 1 ? 0 : h0 + g;
+            s += toF32(mask[(mb * p.maskH + mh) * p.S + j]);
+          }
+          sc[g][j - k0] = s * p.scale;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // softmax statistics of the chunk: one warp per head
+  for (int g = warp; g < G; g += DEC_WARPS) {
+    float m = -INFINITY;
+    for (int i = lane; i < k1 - k0; i += 32) m = fmaxf(m, sc[g][i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float l = 0.0f;
+    for (int i = lane; i < k1 - k0; i += 32) {
+      const float e = m == -INFINITY ? 0.0f : __expf(sc[g][i] - m);
+      sc[g][i] = e;
+      l += e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) {
+      sm[g] = m;
+      sl[g] = l;
+    }
+  }
+  __syncthreads();
+  // values: a warp reads whole rows (lane owns DPL consecutive dims), keys strided over the warps
+  {
+    float acc[G][DPL];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int d = 0; d < DPL; ++d) acc[g][d] = 0.0f;
+    constexpr int UN = 4; // rows in flight per warp
+    for (int j0 = k0 + warp * UN; j0 < k1; j0 += DEC_WARPS * UN) {
+      T raw[UN][DPL];
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        if (j0 + u < k1) {
+          const T *row = vb + static_cast<size_t>(j0 + u) * D + lane * DPL;
+          if constexpr (DPL * sizeof(T) == 8) {
+            *reinterpret_cast<uint2 *>(raw[u]) = __ldcs(reinterpret_cast<const uint2 *>(row));
+          } else if constexpr (DPL * sizeof(T) == 16) {
+            *reinterpret_cast<uint4 *>(raw[u]) = __ldcs(reinterpret_cast<const uint4 *>(row));
+          } else {
+            *reinterpret_cast<uint32_t *>(raw[u]) = __ldcs(reinterpret_cast<const uint32_t *>(row));
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        if (j0 + u < k1) {
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const float pj = sc[g][j0 + u - k0];
+#pragma unroll
+            for (int d = 0; d < DPL; ++d) acc[g][d] = fmaf(pj, toF32(raw[u][d]), acc[g][d]);
+          }
+        }
+      }
+    }
+    // Sum over the warps in a fixed order (the same bits every run): warps (6,7) hand their sums to
+    // (4,5), those to (2,3), those to (0,1), and warp 1 to warp 0, through two exchange slots.
+    auto give = [&](int slot) {
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) so[slot][g][lane * DPL + d] = acc[g][d];
+    };
+    auto take = [&](int slot) {
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) acc[g][d] += so[slot][g][lane * DPL + d];
+    };
+#pragma unroll
+    for (int base = DEC_WARPS - 2; base >= 2; base -= 2) {
+      if (warp == base || warp == base + 1) give(warp - base);
+      __syncthreads();
+      if (warp == base - 2 || warp == base - 1) take(warp - (base - 2));
+      __syncthreads();
+    }
+    if (warp == 1) give(0);
+    __syncthreads();
+    if (warp == 0) {
+      take(0);
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) po[(part + static_cast<size_t>(g) * p.chunks) * D + lane * DPL + d] = acc[g][d];
+    }
+  }
+  if (threadIdx.x < G) {
+    pm[part + static_cast<size_t>(threadIdx.x) * p.chunks] = sm[threadIdx.x];
+    pl[part + static_cast<size_t>(threadIdx.x) * p.chunks] = sl[threadIdx.x];
+  }
+}
+
+// Merges the chunks of one (user, head): one warp per pair.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) sdpaDecodeMergeKernel(const float *__restrict__ pm, const float *__restrict__ pl,
+                                                             const float *__restrict__ po, T *__restrict__ out, int pairs,
+                                                             int chunks) {
+  constexpr int DPL = D / 32;
+  const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (pair >= pairs) return;
+  const float *m = pm + static_cast<size_t>(pair) * chunks, *l = pl + static_cast<size_t>(pair) * chunks;
+  float mx = -INFINITY;
+  for (int c = 0; c < chunks; ++c) mx = fmaxf(mx, m[c]);
+  float acc[DPL], den = 0.0f;
+#pragma unroll
+  for (int d = 0; d < DPL; ++d) acc[d] = 0.0f;
+  for (int c = 0; c < chunks; ++c) {
+    if (m[c] == -INFINITY) continue;
+    const float w = __expf(m[c] - mx);
+    den += l[c] * w;
+    const float *o = po + (static_cast<size_t>(pair) * chunks + c) * D + lane * DPL;
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) acc[d] = fmaf(o[d], w, acc[d]);
+  }
+  const float inv = den > 0.0f ? 1.0f / den : 0.0f;
+#pragma unroll
+  for (int d = 0; d < DPL; ++d) out[static_cast<size_t>(pair) * D + lane * DPL + d] = fromF32<T>(acc[d] * inv);
+}
+
+template <typename T, int G, int D>
+static int launchDecode(const void *q, const void *k, const void *v, const void *curPos, const void *mask, void *out,
+                        float *pm, float *pl, float *po, const DecodeParams &p, cudaStream_t st) {
+  dim3 grid(static_cast<unsigned>(p.chunks), static_cast<unsigned>(p.Hkv), static_cast<unsigned>(p.B));
+  sdpaDecodeChunkKernel<T, G, D><<<grid, DEC_THREADS, 0, st>>>(static_cast<const T *>(q), static_cast<const T *>(k),
+                                                               static_cast<const T *>(v), static_cast<const int32_t *>(curPos),
+                                                               static_cast<const T *>(mask), pm, pl, po, p);
+  TTB_LAUNCH_CHECK();
+  const int pairs = p.B * p.H;
+  sdpaDecodeMergeKernel<T, D><<<(pairs + 7) / 8, 256, 0, st>>>(pm, pl, po, static_cast<T *>(out), pairs, p.chunks);
+  countLaunch(2);
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+template <typename T, int D>
+static int dispatchDecodeG(int g, const void *q, const void *k, const void *v, const void *curPos, const void *mask, void *out,
+                           float *pm, float *pl, float *po, const DecodeParams &p, cudaStream_t st) {
+  switch (g) {
+  case 1: return launchDecode<T, 1, D>(q, k, v, curPos, mask, out, pm, pl, po, p, st);
+  case 2: return launchDecode<T, 2, D>(q, k, v, curPos, mask, out, pm, pl, po, p, st);
+  case 4: return launchDecode<T, 4, D>(q, k, v, curPos, mask, out, pm, pl, po, p, st);
+  case 8: return launchDecode<T, 8, D>(q, k, v, curPos, mask, out, pm, pl, po, p, st);
+  default: setLastError("sdpa_decode: query heads per kv head must be 1, 2, 4 or 8"); return TTB_ERR_UNSUPPORTED;
+  }
+}
+
+} // namespace ttb
+
+using namespace ttb;
+
+extern "C" {
+
+int ttb_fill_cache(void *cache, const void *input, int dtype, size_t users, size_t heads, size_t seq, size_t max_seq,
+                   size_t head_dim, size_t batch_offset, size_t cache_users, void *stream) {
+  TTB_CHECK(cache && input, "null tensor");
+  TTB_CHECK(seq <= max_seq, "input is longer than the cache");
+  TTB_CHECK(batch_offset + users <= cache_users, "input users do not fit the cache at this offset");
+  const size_t rowBytes = head_dim * dtypeSize(dtype);
+  TTB_CHECK(rowBytes > 0, "unsupported dtype");
+  if (users * heads * seq == 0) return TTB_OK;
+  size_t padSeq = (seq + 31) / 32 * 32; // the tile rows the reference's device op overwrites
+  if (padSeq > max_seq) padSeq = seq;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("fill_cache", 0, double(users) * heads * seq * rowBytes * 2, st);
+  const bool wide = rowBytes % 16 == 0 && aligned16(cache) && aligned16(input);
+  const size_t items = users * heads * padSeq * (wide ? rowBytes / 16 : rowBytes / dtypeSize(dtype));
+  const int grid = gridFor(items, 256);
+  if (wide) {
+    fillCacheKernel<uint4><<<grid, 256, 0, st>>>(static_cast<uint4 *>(cache), static_cast<const uint4 *>(input), users, heads,
+                                                 seq, padSeq, max_seq, rowBytes / 16, batch_offset);
+  } else if (dtypeSize(dtype) == 2) {
+    fillCacheKernel<uint16_t><<<grid, 256, 0, st>>>(static_cast<uint16_t *>(cache), static_cast<const uint16_t *>(input), users,
+                                                    heads, seq, padSeq, max_seq, head_dim, batch_offset);
+  } else if (dtypeSize(dtype) == 4) {
+    fillCacheKernel<uint32_t><<<grid, 256, 0, st>>>(static_cast<uint32_t *>(cache), static_cast<const uint32_t *>(input), users,
+                                                    heads, seq, padSeq, max_seq, head_dim, batch_offset);
+  } else {
+    setLastError("fill_cache: unsupported element size");
+    return TTB_ERR_UNSUPPORTED;
+  }
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_update_cache(void *cache, const void *input, const void *index, int dtype, int index_dtype, size_t users,
+                     size_t heads, size_t max_seq, size_t head_dim, size_t batch_offset, size_t cache_users, void *stream) {
+  TTB_CHECK(cache && input && index, "null tensor");
+  TTB_CHECK(batch_offset + users <= cache_users, "input users do not fit the cache at this offset");
+  TTB_CHECK(index_dtype == kI32 || index_dtype == kU32, "update index must be Int32 or UInt32");
+  const size_t es = dtypeSize(dtype);
+  TTB_CHECK(es == 2 || es == 4, "unsupported element size");
+  if (users * heads * head_dim == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  int *bad = nullptr;
+  TTB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&bad), g_cacheBadIndex));
+  ProfScope prof("update_cache", 0, double(users) * heads * head_dim * es * 2, st);
+  const size_t items = users * heads * head_dim;
+  const int grid = gridFor(items, 256);
+#define TTB_UPD(U)                                                                                                    \
+  if (index_dtype == kI32)                                                                                            \
+    updateCacheKernel<U, int32_t><<<grid, 256, 0, st>>>(static_cast<U *>(cache), static_cast<const U *>(input),       \
+                                                        static_cast<const int32_t *>(index), users, heads, max_seq,   \
+                                                        head_dim, batch_offset, bad);                                 \
+  else                                                                                                                \
+    updateCacheKernel<U, uint32_t><<<grid, 256, 0, st>>>(static_cast<U *>(cache), static_cast<const U *>(input),      \
+                                                         static_cast<const uint32_t *>(index), users, heads, max_seq, \
+                                                         head_dim, batch_offset, bad);
+  if (es == 2) { TTB_UPD(uint16_t) } else { TTB_UPD(uint32_t) }
+#undef TTB_UPD
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_update_cache_status(int *bad_index_seen) {
+  TTB_CHECK(bad_index_seen != nullptr, "null result");
+  TTB_CUDA(cudaDeviceSynchronize());
+  TTB_CUDA(cudaMemcpyFromSymbol(bad_index_seen, g_cacheBadIndex, sizeof(int)));
+  return TTB_OK;
+}
+
+size_t ttb_sdpa_decode_workspace_bytes(int batch, int heads, int seq, int head_dim) {
+  const size_t chunks = static_cast<size_t>((seq + DEC_CHUNK - 1) / DEC_CHUNK);
+  return static_cast<size_t>(batch) * heads * chunks * (static_cast<size_t>(head_dim) + 2) * sizeof(float);
+}
+
+int ttb_sdpa_decode(const void *q, const void *k, const void *v, const void *cur_pos, const void *mask, void *out, int dtype,
+                    int batch, int heads, int kv_heads, int seq, int head_dim, int mask_users, int mask_heads, float scale,
+                    int is_causal, void *workspace, size_t workspace_bytes, void *stream) {
+  TTB_CHECK(q && k && v && out, "null tensor");
+  TTB_CHECK(batch > 0 && heads > 0 && kv_heads > 0 && seq > 0, "empty problem");
+  TTB_CHECK(heads % kv_heads == 0, "query heads must be a multiple of kv heads");
+  TTB_CHECK(!mask || ((mask_users == 1 || mask_users == batch) && (mask_heads == 1 || mask_heads == heads)),
+            "mask must be [B or 1, 1, H or 1, S]");
+  if (dtype != kBF16 && dtype != kF16) {
+    setLastError("sdpa_decode: bf16 or f16 only");
+    return TTB_ERR_UNSUPPORTED;
+  }
+  if (!aligned16(k) || !aligned16(v)) {
+    setLastError("sdpa_decode: the cache must be 16-byte aligned");
+    return TTB_ERR_UNSUPPORTED;
+  }
+  DecodeParams p;
+  p.B = batch; p.H = heads; p.Hkv = kv_heads; p.S = seq;
+  p.chunks = (seq + DEC_CHUNK - 1) / DEC_CHUNK;
+  p.maskB = mask ? mask_users : 0;
+  p.maskH = mask ? mask_heads : 0;
+  p.scale = scale;
+  p.causal = is_causal;
+  const size_t need = ttb_sdpa_decode_workspace_bytes(batch, heads, seq, head_dim);
+  TTB_CHECK(workspace && workspace_bytes >= need, "workspace too small (see ttb_sdpa_decode_workspace_bytes)");
+  const size_t pairs = static_cast<size_t>(batch) * heads * p.chunks;
+  float *pm = static_cast<float *>(workspace), *pl = pm + pairs, *po = pl + pairs;
+  cudaStream_t st = asStream(stream);
+  const int g = heads / kv_heads;
+  // algorithmic bytes: the whole cache once (an upper bound when cur_pos cuts it short), q and out
+  ProfScope prof("sdpa_decode", 4.0 * batch * heads * double(seq) * head_dim,
+                 2.0 * batch * kv_heads * double(seq) * head_dim * 2 + 2.0 * batch * heads * head_dim * 2, st);
+#define TTB_DEC(T)                                                                                                     \
+  switch (head_dim) {                                                                                                  \
+  case 64: return dispatchDecodeG<T, 64>(g, q, k, v, cur_pos, mask, out, pm, pl, po, p, st);                          \
+  case 128: return dispatchDecodeG<T, 128>(g, q, k, v, cur_pos, mask, out, pm, pl, po, p, st);                        \
+  case 256: return dispatchDecodeG<T, 256>(g, q, k, v, cur_pos, mask, out, pm, pl, po, p, st);                        \
+  default: setLastError("sdpa_decode: head_dim must be 64, 128 or 256"); return TTB_ERR_UNSUPPORTED;                  \
+  }
+  if (dtype == kBF16) { TTB_DEC(__nv_bfloat16) }
+  TTB_DEC(__half)
+#undef TTB_DEC
+}
+
+} // extern "C"

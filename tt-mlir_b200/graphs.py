@@ -311,6 +311,32 @@ BOTTLENECK_SHARD_DIMS = [2, None, None, None, None, None, None, None, None]
 
 
 # ---------------------------------------------------------------- helpers
+# ---------------------------------------------------------------- serving: one decode step's attention
+def decode_attention_graph(b, batch=32, heads=32, kv_heads=8, seq=8192, head_dim=128, dtype="BFloat16"):
+    """A decode step's attention for `batch` users: the new key / value rows are written into the
+    caches at `index`, then every user's single query attends to its cache up to its position."""
+    q = b.input([1, batch, heads, head_dim], dtype)
+    k_cache = b.input([batch, kv_heads, seq, head_dim], dtype)
+    v_cache = b.input([batch, kv_heads, seq, head_dim], dtype)
+    k_new = b.input([1, kv_heads, batch, head_dim], dtype)
+    v_new = b.input([1, kv_heads, batch, head_dim], dtype)
+    index = b.input([1], "Int32")
+    pos = b.input([batch], "Int32")
+    k_cache = b.update_cache(k_cache, k_new, index, loc="update_k")
+    v_cache = b.update_cache(v_cache, v_new, index, loc="update_v")
+    b.output(b.scaled_dot_product_attention_decode(q, k_cache, v_cache, pos, None, True, 1.0 / math.sqrt(head_dim),
+                                                   loc="decode_attention"))
+
+
+def decode_attention_inputs(batch=32, heads=32, kv_heads=8, seq=8192, head_dim=128, seed=6, dtype=torch.bfloat16):
+    g = torch.Generator().manual_seed(seed)
+    mk = lambda *s: torch.randn(*s, generator=g).to(dtype)
+    at = seq - 1
+    return [mk(1, batch, heads, head_dim), mk(batch, kv_heads, seq, head_dim), mk(batch, kv_heads, seq, head_dim),
+            mk(1, kv_heads, batch, head_dim), mk(1, kv_heads, batch, head_dim), torch.tensor([at], dtype=torch.int32),
+            torch.full((batch,), at, dtype=torch.int32)]
+
+
 def build_binary(graph_fn, mesh_shape=(1, 1), name="main", **kw) -> bytes:
     """Emits a one-program .ttnn binary for `graph_fn(b, **kw)`."""
     from .ttnn_builder import BinaryBuilder

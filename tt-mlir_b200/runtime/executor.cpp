@@ -110,6 +110,30 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     pushRef(outs, o->out());
     break;
   }
+  case OpType::FillCacheOp: {
+    const auto *o = op->type_as_FillCacheOp();
+    pushRef(ins, o->cache());
+    pushRef(ins, o->input());
+    break;
+  }
+  case OpType::UpdateCacheOp: {
+    const auto *o = op->type_as_UpdateCacheOp();
+    pushRef(ins, o->cache());
+    pushRef(ins, o->input());
+    pushRef(ins, o->update_index());
+    break;
+  }
+  case OpType::ScaledDotProductAttentionDecodeOp: {
+    const auto *o = op->type_as_ScaledDotProductAttentionDecodeOp();
+    pushRef(ins, o->query());
+    pushRef(ins, o->key());
+    pushRef(ins, o->value());
+    pushRef(ins, o->attention_mask());
+    pushRef(ins, o->cur_pos_tensor());
+    pushRef(ins, o->attention_sink());
+    pushRef(outs, o->out());
+    break;
+  }
   case OpType::EmbeddingOp: {
     const auto *o = op->type_as_EmbeddingOp();
     pushRef(ins, o->input());
@@ -455,6 +479,9 @@ private:
   void runPool2d(const fbt::Pool2dOp *op);
   void runGlobalAvgPool2d(const fbt::GlobalAvgPool2dOp *op);
   void runPad(const fbt::PadOp *op);
+  void runFillCache(const fbt::FillCacheOp *op);
+  void runUpdateCache(const fbt::UpdateCacheOp *op);
+  void runSdpaDecode(const fbt::ScaledDotProductAttentionDecodeOp *op);
   // sub-programs: const-eval cache, calls, traces
   std::vector<TensorPtr> runSubProgram(uint32_t index, const std::vector<TensorPtr> &inputs);
   void runLoadCached(const fbt::LoadCachedOp *op);
@@ -763,6 +790,9 @@ size_t Executor::runOp(size_t i) {
   case OpType::Pool2dOp: runPool2d(op->type_as_Pool2dOp()); break;
   case OpType::GlobalAvgPool2dOp: runGlobalAvgPool2d(op->type_as_GlobalAvgPool2dOp()); break;
   case OpType::PadOp: runPad(op->type_as_PadOp()); break;
+  case OpType::FillCacheOp: runFillCache(op->type_as_FillCacheOp()); break;
+  case OpType::UpdateCacheOp: runUpdateCache(op->type_as_UpdateCacheOp()); break;
+  case OpType::ScaledDotProductAttentionDecodeOp: runSdpaDecode(op->type_as_ScaledDotProductAttentionDecodeOp()); break;
   case OpType::LoadCachedOp: runLoadCached(op->type_as_LoadCachedOp()); break;
   case OpType::FuncCallOp: runFuncCall(op->type_as_FuncCallOp()); break;
   case OpType::BeginTraceCaptureOp: runBeginTraceCapture(op->type_as_BeginTraceCaptureOp()); break;
@@ -1880,6 +1910,83 @@ void Executor::runPad(const fbt::PadOp *op) {
   eachRank([&](size_t i, const RankCtx &r) {
     TTB_CALL(ttb_pad(in->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(in->dtype), static_cast<int>(rank), shape, lo, hi,
                      static_cast<double>(op->value()), r.stream));
+  });
+  put(op->out(), out);
+}
+
+// ---- KV cache --------------------------------------------------------------------------------------------------
+// FillCacheOp / UpdateCacheOp write into the cache tensor in place (they have no result); the
+// tensor's version is renewed, so traces and const-eval entries keyed by it notice.
+void Executor::runFillCache(const fbt::FillCacheOp *op) {
+  TensorPtr cache = getDevice(op->cache());
+  TensorPtr in = getDevice(op->input());
+  TTRT_ASSERT(cache->shape.size() == 4 && in->shape.size() == 4, "fill_cache expects [users, heads, seq, head_dim] tensors");
+  TTRT_ASSERT(cache->dtype == in->dtype, "fill_cache input must have the cache's data type");
+  TTRT_ASSERT(in->shape[1] == cache->shape[1] && in->shape[3] == cache->shape[3], "fill_cache input does not match the cache's heads / head_dim");
+  TTRT_ASSERT(in->shape[2] <= cache->shape[2], "fill_cache input is longer than the cache");
+  TTRT_ASSERT(op->batch_offset() + in->shape[0] <= cache->shape[0], "fill_cache input users do not fit the cache");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_fill_cache(cache->shards[i]->ptr, in->shards[i]->ptr, ttbDtype(cache->dtype), in->shape[0], in->shape[1],
+                            in->shape[2], cache->shape[2], cache->shape[3], op->batch_offset(), cache->shape[0], r.stream));
+  });
+  TensorPtr root = cache->base ? cache->base : cache;
+  root->version.store(TensorImpl::nextTensorVersion());
+}
+
+void Executor::runUpdateCache(const fbt::UpdateCacheOp *op) {
+  TensorPtr cache = getDevice(op->cache());
+  TensorPtr in = getDevice(op->input());
+  TensorPtr idx = getDevice(op->update_index()); // read by the kernel: no host round trip
+  TTRT_ASSERT(cache->shape.size() == 4 && in->shape.size() == 4, "update_cache expects 4-D tensors");
+  TTRT_ASSERT(cache->dtype == in->dtype, "update_cache input must have the cache's data type");
+  TTRT_ASSERT(in->shape[0] == 1 && in->shape[1] == cache->shape[1] && in->shape[3] == cache->shape[3],
+              "update_cache input must be [1, heads, users, head_dim]");
+  TTRT_ASSERT(op->batch_offset() + in->shape[2] <= cache->shape[0], "update_cache input users do not fit the cache");
+  TTRT_ASSERT(idx->volume() >= 1 && (idx->dtype == DataType::Int32 || idx->dtype == DataType::UInt32),
+              "update_cache index must be an Int32 / UInt32 tensor");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_update_cache(cache->shards[i]->ptr, in->shards[i]->ptr, idx->shards[i]->ptr, ttbDtype(cache->dtype),
+                              ttbDtype(idx->dtype), in->shape[2], in->shape[1], cache->shape[2], cache->shape[3],
+                              op->batch_offset(), cache->shape[0], r.stream));
+  });
+  TensorPtr root = cache->base ? cache->base : cache;
+  root->version.store(TensorImpl::nextTensorVersion());
+}
+
+// q [1, B, H, D] against k, v [B, Hkv, S, D] (the decode layout, tools/golden/mapping.py:2431-2437).
+void Executor::runSdpaDecode(const fbt::ScaledDotProductAttentionDecodeOp *op) {
+  TTRT_ASSERT(!op->attention_sink(), "attention sinks are not supported");
+  TTRT_ASSERT(!op->sliding_window_size().has_value(), "sliding-window decode attention is not supported");
+  TensorPtr q = getDevice(op->query()), k = getDevice(op->key()), v = getDevice(op->value());
+  TensorPtr mask = op->attention_mask() ? getDevice(op->attention_mask()) : nullptr;
+  TensorPtr pos = op->cur_pos_tensor() ? getDevice(op->cur_pos_tensor()) : nullptr;
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(q->shape.size() == 4 && k->shape.size() == 4 && v->shape == k->shape, "sdpa_decode expects q [1,B,H,D], k / v [B,Hkv,S,D]");
+  TTRT_ASSERT(q->shape[0] == 1 && q->shape[1] == k->shape[0] && q->shape[3] == k->shape[3], "sdpa_decode operands disagree on batch or head_dim");
+  TTRT_ASSERT(q->dtype == k->dtype && q->dtype == v->dtype && out->dtype == q->dtype, "sdpa_decode operands must share one data type");
+  const int B = static_cast<int>(q->shape[1]), H = static_cast<int>(q->shape[2]), D = static_cast<int>(q->shape[3]);
+  const int Hkv = static_cast<int>(k->shape[1]), S = static_cast<int>(k->shape[2]);
+  TTRT_ASSERT(out->volume() == q->volume(), "sdpa_decode result must have the query's shape");
+  int maskB = 0, maskH = 0;
+  if (mask) {
+    TTRT_ASSERT(mask->shape.size() == 4 && mask->shape[1] == 1 && static_cast<int>(mask->shape[3]) == S && mask->dtype == q->dtype,
+                "sdpa_decode mask must be [B or 1, 1, H or 1, S] in the operands' data type");
+    maskB = static_cast<int>(mask->shape[0]);
+    maskH = static_cast<int>(mask->shape[2]);
+  }
+  if (pos) {
+    TTRT_ASSERT(static_cast<int>(pos->volume()) == B && (pos->dtype == DataType::Int32 || pos->dtype == DataType::UInt32),
+                "cur_pos must hold one 32-bit integer per user");
+  }
+  // The golden applies no scaling when the op carries none (tools/golden/mapping.py:2471-2473).
+  const float scale = op->scale().has_value() ? *op->scale() : 1.0f;
+  const size_t wsBytes = ttb_sdpa_decode_workspace_bytes(B, H, S, D);
+  std::vector<uint32_t> wsShape{static_cast<uint32_t>((wsBytes + 3) / 4)};
+  TensorPtr ws = makeDeviceTensor(dev, wsShape, DataType::Float32);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_sdpa_decode(q->shards[i]->ptr, k->shards[i]->ptr, v->shards[i]->ptr, pos ? pos->shards[i]->ptr : nullptr,
+                             mask ? mask->shards[i]->ptr : nullptr, out->shards[i]->ptr, ttbDtype(q->dtype), B, H, Hkv, S, D, maskB,
+                             maskH, scale, op->is_causal() ? 1 : 0, ws->shards[i]->ptr, wsBytes, r.stream));
   });
   put(op->out(), out);
 }

@@ -296,6 +296,16 @@ S.table("SplitQueryKeyValueAndSplitHeadsOp", [
     ("v_out", "TensorRef"), ("num_heads", "u32"), ("num_kv_heads", "u32", OPT),
     ("transpose_key", "bool"), ("memcfg", "MemoryConfig")])
 
+S.table("ScaledDotProductAttentionDecodeOp", [
+    ("query", "TensorRef"), ("key", "TensorRef"), ("value", "TensorRef"), ("is_causal", "bool"),
+    ("attention_mask", "TensorRef"), ("cur_pos_tensor", "TensorRef"), ("attention_sink", "TensorRef"),
+    ("scale", "f32", OPT), ("sliding_window_size", "u32", OPT), ("out", "TensorRef"),
+    ("memcfg", "MemoryConfig"), ("program_config", "opaque")])
+# operations/kv_cache.fbs
+S.table("FillCacheOp", [("cache", "TensorRef"), ("input", "TensorRef"), ("batch_offset", "u32")])
+S.table("UpdateCacheOp", [
+    ("cache", "TensorRef"), ("input", "TensorRef"), ("update_index", "TensorRef"), ("batch_offset", "u32")])
+
 # --- ccl (operations/ccl.fbs)
 S.table("AllGatherOp", [
     ("in", "TensorRef"), ("out", "TensorRef"), ("all_gather_dim", "i32"), ("cluster_axis", "u32"),

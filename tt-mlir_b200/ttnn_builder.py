@@ -625,6 +625,29 @@ class ProgramBuilder:
                              "use_multicore": True, "memcfg": self._mc()}, [x], [out], loc)
         return out
 
+    # ---- KV cache and decode attention ----------------------------------------------------------------------------
+    def fill_cache(self, cache: Value, x: Value, batch_offset: int = 0, loc=None) -> Value:
+        """In place: cache[batch_offset + b, h, :S] = x[b, h].  Returns `cache` (the op has no result)."""
+        self._emit("FillCacheOp", {"cache": cache.ref, "input": x.ref, "batch_offset": batch_offset}, [cache, x], [], loc)
+        return cache
+
+    def update_cache(self, cache: Value, x: Value, update_index: Value, batch_offset: int = 0, loc=None) -> Value:
+        """In place: cache[batch_offset + b, h, update_index[0]] = x[0, h, b].  Returns `cache`."""
+        self._emit("UpdateCacheOp", {"cache": cache.ref, "input": x.ref, "update_index": update_index.ref,
+                                     "batch_offset": batch_offset}, [cache, x, update_index], [], loc)
+        return cache
+
+    def scaled_dot_product_attention_decode(self, q: Value, k: Value, v: Value, cur_pos: Optional[Value] = None,
+                                            mask: Optional[Value] = None, is_causal: bool = True,
+                                            scale: Optional[float] = None, loc=None) -> Value:
+        out = self._value(q.shape, q.dtype)
+        ins = [x for x in (q, k, v, mask, cur_pos) if x is not None]
+        self._emit("ScaledDotProductAttentionDecodeOp", {
+            "query": q.ref, "key": k.ref, "value": v.ref, "is_causal": is_causal,
+            "attention_mask": mask.ref if mask else None, "cur_pos_tensor": cur_pos.ref if cur_pos else None,
+            "scale": scale, "out": out.ref, "memcfg": self._mc()}, ins, [out], loc)
+        return out
+
     # ---- sub-programs: const-eval, calls, traces -------------------------------------------------------------
     def input_like(self, v: Value, on_device: Optional[bool] = None) -> Value:
         return self.input(v.shape, v.dtype, v.on_device if on_device is None else on_device)

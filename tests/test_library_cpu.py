@@ -29,7 +29,7 @@ def test_binary_metadata(rt):
     assert len(ins) == 12 and ins[0] == ([1, 128, 256], rt.DataType.BFloat16)
     assert b.get_program_outputs(0) == [([1, 128, 256], rt.DataType.BFloat16)]
     ops = json.loads(b.get_program_ops_as_json(0))
-    kinds = [o["type"] for o in ops]
+    kinds = [o["type_type"] for o in ops]
     assert kinds[0] == "GetDeviceOp" and kinds.count("AllReduceOp") == 2 and kinds.count("DistributeTensorOp") == 12
     assert kinds[-1] == "AggregateTensorOp" or "AggregateTensorOp" in kinds
     assert "DeallocateOp" in kinds
@@ -102,3 +102,75 @@ def test_host_tensor_api_without_gpu(rt):
     assert t.is_allocated()
     rt.deallocate_tensor(o, force=True)
     assert not o.is_allocated()
+
+
+def _flatc_style(x):
+    """The Python reader's view of a table (unions as (name, table) pairs, absent fields None) in the
+    shape of flatc's JSON text: "<field>_type" + "<field>" for unions, absent fields left out."""
+    if isinstance(x, dict):
+        out = {}
+        for k, v in x.items():
+            if v is None:
+                continue
+            if isinstance(v, tuple) and len(v) == 2 and isinstance(v[0], str) and isinstance(v[1], dict):
+                out[k + "_type"] = v[0]
+                out[k] = _flatc_style(v[1])
+            else:
+                out[k] = _flatc_style(v)
+        return out
+    if isinstance(x, (list, tuple)):
+        return [_flatc_style(v) for v in x]
+    if isinstance(x, (bytes, bytearray, memoryview)):
+        return list(bytes(x))
+    return x
+
+
+def _drop_absent_unions(x):
+    if isinstance(x, dict):
+        return {k: _drop_absent_unions(v) for k, v in x.items() if not (k.endswith("_type") and v == "NONE")}
+    if isinstance(x, list):
+        return [_drop_absent_unions(v) for v in x]
+    return x
+
+
+def _close(a, b, path="$"):
+    if isinstance(a, dict):
+        assert isinstance(b, dict) and set(a) == set(b), f"{path}: keys {sorted(set(a) ^ set(b))}"
+        for k in a:
+            _close(a[k], b[k], f"{path}.{k}")
+    elif isinstance(a, list):
+        assert isinstance(b, list) and len(a) == len(b), path
+        for i, (x, y) in enumerate(zip(a, b)):
+            _close(x, y, f"{path}[{i}]")
+    elif isinstance(a, float) or isinstance(b, float):
+        assert abs(float(a) - float(b)) <= 1e-6 * max(1.0, abs(float(a))), f"{path}: {a} vs {b}"
+    else:
+        assert a == b, f"{path}: {a!r} vs {b!r}"
+
+
+@pytest.mark.parametrize("which", ["decoder", "quant", "traced", "pool"])
+def test_json_views_print_every_declared_field(rt, which):
+    """Binary::asJson / getProgramOpsAsJson (the generated printers) against the independent Python
+    reader of the same buffer: every table, union, struct, enum and optional scalar of every op."""
+    from ttmlir_b200.schema.fbs import Reader
+    from ttmlir_b200.schema.ttnn_schema import S
+    if which == "decoder":
+        buf = graphs.build_binary(graphs.decoder_block_graph, seq=128, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64,
+                                  ffn=512, tp=2, mesh_shape=(1, 2))
+    elif which == "quant":
+        buf = graphs.build_binary(graphs.quant_chain_graph, rows=8, cols=8, keep_intermediates=True)
+    elif which == "traced":
+        buf = graphs.mlp_traced_binary(batch=4, d_in=8, d_hidden=8, d_out=4)
+    else:
+        def g(b):
+            x = b.input([1, 1, 2 * 9 * 11, 8], "BFloat16")
+            b.output(b.avg_pool2d(b.max_pool2d(x, 2, 9, 11, 8, (3, 3), (2, 2), (1, 2, 0, 1)), 2, 4, 6, 8, (2, 2), (2, 2), (0, 0),
+                                  False, False), b.argmax(x, 2), b.pad(x, [0, 0, 0, 0, 1, 2, 0, 3], 1.5))
+        buf = graphs.build_binary(g)
+    want = _flatc_style(Reader(S, buf).root("TTNNBinary"))
+    b = rt.Binary.load_from_memory(buf)
+    got = _drop_absent_unions(json.loads(b.as_json()))
+    _close(got, want)
+    for i in range(b.get_num_programs()):
+        ops = _drop_absent_unions(json.loads(b.get_program_ops_as_json(i)))
+        _close(ops, want["programs"][i].get("operations", []), f"$.programs[{i}].operations")

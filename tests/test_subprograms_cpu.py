@@ -8,7 +8,7 @@ from ttmlir_b200 import graphs
 
 
 def _ops(binary, i):
-    return [o["type"] for o in json.loads(binary.get_program_ops_as_json(i))]
+    return [o["type_type"] for o in json.loads(binary.get_program_ops_as_json(i))]
 
 
 def test_traced_binary_has_the_four_private_programs(rt):

@@ -265,54 +265,34 @@ static std::string descJson(const fbt::TensorRef *ref) {
   return s;
 }
 
-std::string Binary::getProgramInputsAsJson(std::uint32_t i) const {
+// JSON views (runtime/lib/binary.cpp:63-122, 240-330 of the reference): the generated printers
+// write what flatc's text generator writes for the same tables.
+template <typename V> static std::string tablesAsJson(const V *v) {
   std::string s = "[";
-  if (const auto *v = programAt(*this, i)->inputs()) {
-    for (uint32_t k = 0; k < v->size(); ++k) s += (k ? ", " : "") + descJson(v->Get(k));
-  }
-  return s + "]";
-}
-
-std::string Binary::getProgramOutputsAsJson(std::uint32_t i) const {
-  std::string s = "[";
-  if (const auto *v = programAt(*this, i)->outputs()) {
-    for (uint32_t k = 0; k < v->size(); ++k) s += (k ? ", " : "") + descJson(v->Get(k));
-  }
-  return s + "]";
-}
-
-std::string Binary::getProgramOpsAsJson(std::uint32_t i) const {
-  std::string s = "[";
-  if (const auto *ops = programAt(*this, i)->operations()) {
-    for (uint32_t k = 0; k < ops->size(); ++k) {
-      const auto *op = ops->Get(k);
-      s += k ? ", " : "";
-      s += "{\"type\": \"";
-      s += fbt::EnumNameOpType(op->type_type());
-      s += "\", \"loc_info\": \"" + jsonEscape(op->loc_info() ? op->loc_info()->view() : "") + "\"";
-      s += ", \"debug_info\": \"" + jsonEscape(op->debug_info() ? op->debug_info()->view() : "") + "\"}";
+  if (v) {
+    for (uint32_t k = 0; k < v->size(); ++k) {
+      if (k) s += ",";
+      v->Get(k)->toJson(s);
     }
   }
   return s + "]";
 }
 
+std::string Binary::getProgramInputsAsJson(std::uint32_t i) const { return tablesAsJson(programAt(*this, i)->inputs()); }
+std::string Binary::getProgramOutputsAsJson(std::uint32_t i) const { return tablesAsJson(programAt(*this, i)->outputs()); }
+std::string Binary::getProgramOpsAsJson(std::uint32_t i) const { return tablesAsJson(programAt(*this, i)->operations()); }
+
 std::string Binary::getMlirAsJson() const {
-  const auto *m = get()->mlir();
-  std::string name = m && m->name() ? m->name()->str() : "";
-  std::string src = m && m->source() ? m->source()->str() : "";
-  return "{\"name\": \"" + jsonEscape(name) + "\", \"source\": \"" + jsonEscape(src) + "\"}";
+  std::string s;
+  if (const auto *m = get()->mlir()) m->toJson(s);
+  else s = "{}";
+  return s;
 }
 
 std::string Flatbuffer::asJson() const {
-  Binary b(handle);
-  std::string s = "{\"version\": \"" + getVersion() + "\", \"schema_hash\": \"" + jsonEscape(getSchemaHash()) +
-                  "\", \"ttmlir_git_hash\": \"" + jsonEscape(getTTMLIRGitHash()) + "\", \"programs\": [";
-  for (uint32_t i = 0; i < b.getNumPrograms(); ++i) {
-    s += i ? ", " : "";
-    s += "{\"name\": \"" + jsonEscape(b.getProgramName(i)) + "\", \"inputs\": " + b.getProgramInputsAsJson(i) +
-         ", \"outputs\": " + b.getProgramOutputsAsJson(i) + ", \"operations\": " + b.getProgramOpsAsJson(i) + "}";
-  }
-  return s + "]}";
+  std::string s;
+  rootOf(handle.get())->toJson(s);
+  return s;
 }
 
 } // namespace tt::runtime

@@ -15,10 +15,12 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <cstdio>
 #include <cstring>
 #include <optional>
 #include <string>
 #include <string_view>
+#include <type_traits>
 
 namespace fb {
 
@@ -227,5 +229,53 @@ private:
   size_t tables_ = 0;
   std::string error_;
 };
+
+// ---- JSON text (used by the generated toJson members) ---------------------------------------
+inline void jsonString(std::string_view v, std::string &out) {
+  out += '"';
+  for (char ch : v) {
+    const unsigned char c = static_cast<unsigned char>(ch);
+    switch (c) {
+    case '"': out += "\\\""; break;
+    case '\\': out += "\\\\"; break;
+    case '\n': out += "\\n"; break;
+    case '\r': out += "\\r"; break;
+    case '\t': out += "\\t"; break;
+    default:
+      if (c < 0x20) {
+        char buf[8];
+        std::snprintf(buf, sizeof(buf), "\\u%04x", c);
+        out += buf;
+      } else {
+        out += ch;
+      }
+    }
+  }
+  out += '"';
+}
+inline void jsonScalar(bool v, std::string &out) { out += v ? "true" : "false"; }
+inline void jsonScalar(float v, std::string &out) {
+  if (v != v) { out += "NaN"; return; }
+  if (v - v != 0.0f) { out += v > 0 ? "Infinity" : "-Infinity"; return; }
+  char buf[32];
+  std::snprintf(buf, sizeof(buf), "%.9g", static_cast<double>(v));
+  out += buf;
+}
+inline void jsonScalar(double v, std::string &out) {
+  if (v != v) { out += "NaN"; return; }
+  if (v - v != 0.0) { out += v > 0 ? "Infinity" : "-Infinity"; return; }
+  char buf[40];
+  std::snprintf(buf, sizeof(buf), "%.17g", v);
+  out += buf;
+}
+template <typename T, typename = std::enable_if_t<std::is_integral_v<T> && !std::is_same_v<T, bool>>>
+inline void jsonScalar(T v, std::string &out) {
+  out += std::to_string(v);
+}
+// An enum value by name, or by number when the schema does not know it.
+inline void jsonEnum(const char *name, long long value, std::string &out) {
+  if (name && name[0]) jsonString(name, out);
+  else out += std::to_string(value);
+}
 
 } // namespace fb

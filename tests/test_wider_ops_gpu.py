@@ -89,7 +89,10 @@ def test_pooling_matches_the_reference_outputs(rt, device, golden, case):
     # bf16 activations, channel count that is not a multiple of the 16-byte vector
     xb = golden["pool/x"][..., :7].contiguous().to(torch.bfloat16).reshape(1, 1, -1, 7)
     got, want = run_body(rt, device, lambda b, v: pool_on(b, v, case, channels=7), [xb])
-    assert_matches(got[0], want[0], f"{case} bf16 c=7")
+    if case.startswith("max"):
+        assert torch.equal(got[0], want[0])        # a maximum is exact; windows that lie in the padding give -inf
+    else:
+        assert_matches(got[0], want[0], f"{case} bf16 c=7")
 
 
 def test_resnet_stem_pool_and_head(rt, device):

@@ -64,7 +64,20 @@ __global__ void __launch_bounds__(256)
 __device__ int g_cacheBadIndex; // sticky: an update index outside the cache was seen (nothing was written)
 
 // ---- decode attention ------------------------------------------------------------------------
-constexpr int DEC_THREADS = 256;
+// D += A(16x16, row) * B(16x8, col), 16-bit operands, f32 accumulators.
+template <typename T> __device__ __forceinline__ void decMma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void decMma<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void decMma<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int DEC_THREADS = 128; // four CTAs per SM in different phases fill each other's bubbles
 constexpr int DEC_WARPS = DEC_THREADS / 32;
 constexpr int DEC_CHUNK = 512; // keys per CTA
 
@@ -78,14 +91,11 @@ struct DecodeParams {
 // Partial attention of G query heads over one chunk of keys.  Writes, per (user, head, chunk):
 // m (running max), l (sum of exp(s - m)) and the unnormalised o[D] = sum exp(s - m) v.
 template <typename T, int G, int D>
-__global__ void __launch_bounds__(DEC_THREADS)
+__global__ void __launch_bounds__(DEC_THREADS, 4)
     sdpaDecodeChunkKernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
                           const int32_t *__restrict__ curPos, const T *__restrict__ mask, float *__restrict__ pm,
                           float *__restrict__ pl, float *__restrict__ po, DecodeParams p) {
-  constexpr int LPK = D / 16;       // lanes that share one key row in the score phase (16 elements each)
-  constexpr int KPW = 32 / LPK;     // keys a warp scores per step
   constexpr int DPL = D / 32;       // output dims per lane in the value phase
-  __shared__ float sq[G][D];
   __shared__ float sc[G][DEC_CHUNK];
   __shared__ float so[2][G][D]; // exchange slots of the cross-warp sum
   __shared__ float sm[G], sl[G];
@@ -107,51 +117,68 @@ __global__ void __launch_bounds__(DEC_THREADS)
     }
     return;
   }
-  for (int i = threadIdx.x; i < G * D; i += DEC_THREADS) {
-    sq[i / D][i % D] = toF32(q[(static_cast<size_t>(b) * p.H + h0 + i / D) * D + (i % D)]);
-  }
-  __syncthreads();
   const T *kb = k + (static_cast<size_t>(b) * p.Hkv + kvh) * p.S * D;
   const T *vb = v + (static_cast<size_t>(b) * p.Hkv + kvh) * p.S * D;
 
-  // scores: LPK lanes per key, 16 elements (two 16-byte loads) per lane
+  // Scores on the tensor pipe: S[16 x 8] = Q[16 x D] K^T for 8 keys per mma tile, the G query heads
+  // being rows 0..G-1 of the 16-row operand (the other rows are zero).  A dot product does not care
+  // in which order its terms are summed, so the k index of the mma is mapped to head dims in a way
+  // that lets one 16-byte load per lane feed two k-steps: in every block of 32 dims, lane t of a
+  // quad holds dims 8t .. 8t+7 of its key; pairs (8t, 8t+1) and (8t+2, 8t+3) are the b0 / b1 of the
+  // first k-step, (8t+4, 8t+5) and (8t+6, 8t+7) of the second, and Q's fragments use the same map.
   {
-    const int sub = lane % LPK, slot = lane / LPK;
-    float qr[G][16];
+    constexpr int NB = D / 32; // 32-dim blocks
+    const int quad = lane >> 2, t = lane & 3;
+    uint32_t qa[NB][2][4];
 #pragma unroll
-    for (int g = 0; g < G; ++g)
+    for (int nb = 0; nb < NB; ++nb) {
+      uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+      if (quad < G) lo = *reinterpret_cast<const uint4 *>(q + (static_cast<size_t>(b) * p.H + h0 + quad) * D + nb * 32 + 8 * t);
+      if (quad + 8 < G) hi = *reinterpret_cast<const uint4 *>(q + (static_cast<size_t>(b) * p.H + h0 + quad + 8) * D + nb * 32 + 8 * t);
+      qa[nb][0][0] = lo.x; qa[nb][0][1] = hi.x; qa[nb][0][2] = lo.y; qa[nb][0][3] = hi.y;
+      qa[nb][1][0] = lo.z; qa[nb][1][1] = hi.z; qa[nb][1][2] = lo.w; qa[nb][1][3] = hi.w;
+    }
+    // UK tiles of 8 keys per iteration with all their loads issued first (NB * UK * 16 bytes in flight per lane)
+    constexpr int UK = 2;
+    for (int j0 = k0 + warp * 8; j0 < k1; j0 += DEC_WARPS * 8 * UK) {
+      uint4 raw[UK][NB];
 #pragma unroll
-      for (int e = 0; e < 16; ++e) qr[g][e] = sq[g][sub * 16 + e];
-    for (int j0 = k0 + warp * KPW; j0 < k1; j0 += DEC_WARPS * KPW) {
-      const int j = j0 + slot;
-      float dot[G];
+      for (int u = 0; u < UK; ++u) {
+        const int j = j0 + u * DEC_WARPS * 8 + quad;
 #pragma unroll
-      for (int g = 0; g < G; ++g) dot[g] = 0.0f;
-      if (j < k1) {
-        const uint4 *row = reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(j) * D + sub * 16);
-        uint4 raw[2] = {__ldcs(row), __ldcs(row + 1)};
-        const T *e = reinterpret_cast<const T *>(raw);
-#pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          const float kv = toF32(e[x]);
-#pragma unroll
-          for (int g = 0; g < G; ++g) dot[g] = fmaf(qr[g][x], kv, dot[g]);
+        for (int nb = 0; nb < NB; ++nb) {
+          raw[u][nb] = j < k1 ? __ldcs(reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(j) * D + nb * 32 + 8 * t))
+                              : make_uint4(0, 0, 0, 0);
         }
       }
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
+      for (int u = 0; u < UK; ++u) {
+        const int jt = j0 + u * DEC_WARPS * 8; // first key of the tile
+        if (jt >= k1) break;                    // warp-uniform
+        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-        for (int o = LPK / 2; o > 0; o >>= 1) dot[g] += __shfl_xor_sync(0xffffffffu, dot[g], o);
-      }
-      if (sub == 0 && j < k1) {
+        for (int nb = 0; nb < NB; ++nb) {
+          decMma<T>(c, qa[nb][0], raw[u][nb].x, raw[u][nb].y);
+          decMma<T>(c, qa[nb][1], raw[u][nb].z, raw[u][nb].w);
+        }
+        // c[0], c[1]: head `quad`, keys jt + 2t, jt + 2t + 1; c[2], c[3]: head quad + 8, same keys
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-          float s = dot[g];
-          if (mask) {
-            const size_t mb = p.maskB == 1 ? 0 : b, mh = p.maskH == 1 ? 0 : h0 + g;
-            s += toF32(mask[(mb * p.maskH + mh) * p.S + j]);
+        for (int half = 0; half < 2; ++half) {
+          const int g = quad + 8 * half;
+          if (g < G) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int j = jt + 2 * t + e;
+              if (j < k1) {
+                float sv = c[2 * half + e];
+                if (mask) {
+                  const size_t mb = p.maskB == 1 ? 0 : b, mh = p.maskH == 1 ? 0 : h0 + g;
+                  sv += toF32(mask[(mb * p.maskH + mh) * p.S + j]);
+                }
+                sc[g][j - k0] = sv * p.scale;
+              }
+            }
           }
-          sc[g][j - k0] = s * p.scale;
         }
       }
     }
@@ -184,7 +211,7 @@ __global__ void __launch_bounds__(DEC_THREADS)
     for (int g = 0; g < G; ++g)
 #pragma unroll
       for (int d = 0; d < DPL; ++d) acc[g][d] = 0.0f;
-    constexpr int UN = 4; // rows in flight per warp
+    constexpr int UN = 8; // rows in flight per warp
     for (int j0 = k0 + warp * UN; j0 < k1; j0 += DEC_WARPS * UN) {
       T raw[UN][DPL];
 #pragma unroll

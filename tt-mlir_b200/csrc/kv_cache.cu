@@ -77,6 +77,23 @@ template <> __device__ __forceinline__ void decMma<__half>(float (&d)[4], const 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+template <typename T> __device__ __forceinline__ uint32_t decPack(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t decPack<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+template <> __device__ __forceinline__ uint32_t decPack<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+// Transposes the 8 x 8 matrix of 16-bit elements that the warp holds one register per lane
+// (lane 4r + c: row r, columns 2c and 2c + 1).
+__device__ __forceinline__ uint32_t decTranspose(uint32_t v) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(r) : "r"(v));
+  return r;
+}
+
 constexpr int DEC_THREADS = 128; // four CTAs per SM in different phases fill each other's bubbles
 constexpr int DEC_WARPS = DEC_THREADS / 32;
 constexpr int DEC_CHUNK = 512; // keys per CTA
@@ -91,11 +108,10 @@ struct DecodeParams {
 // Partial attention of G query heads over one chunk of keys.  Writes, per (user, head, chunk):
 // m (running max), l (sum of exp(s - m)) and the unnormalised o[D] = sum exp(s - m) v.
 template <typename T, int G, int D>
-__global__ void __launch_bounds__(DEC_THREADS, 4)
+__global__ void __launch_bounds__(DEC_THREADS, D <= 128 ? 4 : 2)
     sdpaDecodeChunkKernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
                           const int32_t *__restrict__ curPos, const T *__restrict__ mask, float *__restrict__ pm,
                           float *__restrict__ pl, float *__restrict__ po, DecodeParams p) {
-  constexpr int DPL = D / 32;       // output dims per lane in the value phase
   __shared__ float sc[G][DEC_CHUNK];
   __shared__ float so[2][G][D]; // exchange slots of the cross-warp sum
   __shared__ float sm[G], sl[G];
@@ -204,55 +220,65 @@ __global__ void __launch_bounds__(DEC_THREADS, 4)
     }
   }
   __syncthreads();
-  // values: a warp reads whole rows (lane owns DPL consecutive dims), keys strided over the warps
+  // Values on the tensor pipe too: O[16 x D] += P[16 x 16] V[16 x D], 16 keys per step.  The B
+  // operand wants pairs of consecutive KEYS of one dim in a register, while a row-major V gives
+  // pairs of consecutive DIMS of one key: each of the four registers of a lane's 16-byte load is an
+  // 8 x 8 matrix (key x dim pair) over the warp, and movmatrix transposes it in registers.  Which
+  // head dim an accumulator column then stands for follows from the load map (lane t of a quad
+  // holds dims 8t .. 8t+7 of a 32-dim block): register i, column 2t+e  <->  dim 32 nb + 8t + 2i + e.
   {
-    float acc[G][DPL];
+    constexpr int NB = D / 32;
+    const int quad = lane >> 2, t = lane & 3;
+    float acc[NB][4][4];
 #pragma unroll
-    for (int g = 0; g < G; ++g)
+    for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-      for (int d = 0; d < DPL; ++d) acc[g][d] = 0.0f;
-    constexpr int UN = 8; // rows in flight per warp
-    for (int j0 = k0 + warp * UN; j0 < k1; j0 += DEC_WARPS * UN) {
-      T raw[UN][DPL];
+      for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int u = 0; u < UN; ++u) {
-        if (j0 + u < k1) {
-          const T *row = vb + static_cast<size_t>(j0 + u) * D + lane * DPL;
-          if constexpr (DPL * sizeof(T) == 8) {
-            *reinterpret_cast<uint2 *>(raw[u]) = __ldcs(reinterpret_cast<const uint2 *>(row));
-          } else if constexpr (DPL * sizeof(T) == 16) {
-            *reinterpret_cast<uint4 *>(raw[u]) = __ldcs(reinterpret_cast<const uint4 *>(row));
-          } else {
-            *reinterpret_cast<uint32_t *>(raw[u]) = __ldcs(reinterpret_cast<const uint32_t *>(row));
-          }
+        for (int c = 0; c < 4; ++c) acc[nb][i][c] = 0.0f;
+    auto prob = [&](int g, int j) -> float { return (g < G && j < k1) ? sc[g][j - k0] : 0.0f; };
+    for (int j0 = k0 + warp * 16; j0 < k1; j0 += DEC_WARPS * 16) {
+      uint4 raw[2][NB];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int j = j0 + 8 * h + quad;
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          raw[h][nb] = j < k1 ? __ldcs(reinterpret_cast<const uint4 *>(vb + static_cast<size_t>(j) * D + nb * 32 + 8 * t))
+                              : make_uint4(0, 0, 0, 0);
         }
       }
+      uint32_t pa[4];
+      pa[0] = decPack<T>(prob(quad, j0 + 2 * t), prob(quad, j0 + 2 * t + 1));
+      pa[1] = decPack<T>(prob(quad + 8, j0 + 2 * t), prob(quad + 8, j0 + 2 * t + 1));
+      pa[2] = decPack<T>(prob(quad, j0 + 2 * t + 8), prob(quad, j0 + 2 * t + 9));
+      pa[3] = decPack<T>(prob(quad + 8, j0 + 2 * t + 8), prob(quad + 8, j0 + 2 * t + 9));
 #pragma unroll
-      for (int u = 0; u < UN; ++u) {
-        if (j0 + u < k1) {
+      for (int nb = 0; nb < NB; ++nb) {
+        const uint32_t lo[4] = {raw[0][nb].x, raw[0][nb].y, raw[0][nb].z, raw[0][nb].w};
+        const uint32_t hi[4] = {raw[1][nb].x, raw[1][nb].y, raw[1][nb].z, raw[1][nb].w};
 #pragma unroll
-          for (int g = 0; g < G; ++g) {
-            const float pj = sc[g][j0 + u - k0];
-#pragma unroll
-            for (int d = 0; d < DPL; ++d) acc[g][d] = fmaf(pj, toF32(raw[u][d]), acc[g][d]);
-          }
-        }
+        for (int i = 0; i < 4; ++i) decMma<T>(acc[nb][i], pa, decTranspose(lo[i]), decTranspose(hi[i]));
       }
     }
-    // Sum over the warps in a fixed order (the same bits every run): warps (6,7) hand their sums to
-    // (4,5), those to (2,3), those to (0,1), and warp 1 to warp 0, through two exchange slots.
-    auto give = [&](int slot) {
+    // Sum over the warps in a fixed order (the same bits every run): warps (2,3) hand their sums to
+    // (0,1), and warp 1 to warp 0, through two exchange slots.
+    auto each = [&](auto &&f) {
 #pragma unroll
-      for (int g = 0; g < G; ++g)
+      for (int half = 0; half < 2; ++half) {
+        const int g = quad + 8 * half;
+        if (g < G) {
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) so[slot][g][lane * DPL + d] = acc[g][d];
+          for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+              for (int e = 0; e < 2; ++e) f(g, nb * 32 + 8 * t + 2 * i + e, acc[nb][i][2 * half + e]);
+        }
+      }
     };
-    auto take = [&](int slot) {
-#pragma unroll
-      for (int g = 0; g < G; ++g)
-#pragma unroll
-        for (int d = 0; d < DPL; ++d) acc[g][d] += so[slot][g][lane * DPL + d];
-    };
+    auto give = [&](int slot) { each([&](int g, int d, float &v) { so[slot][g][d] = v; }); };
+    auto take = [&](int slot) { each([&](int g, int d, float &v) { v += so[slot][g][d]; }); };
 #pragma unroll
     for (int base = DEC_WARPS - 2; base >= 2; base -= 2) {
       if (warp == base || warp == base + 1) give(warp - base);
@@ -264,10 +290,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 4)
     __syncthreads();
     if (warp == 0) {
       take(0);
-#pragma unroll
-      for (int g = 0; g < G; ++g)
-#pragma unroll
-        for (int d = 0; d < DPL; ++d) po[(part + static_cast<size_t>(g) * p.chunks) * D + lane * DPL + d] = acc[g][d];
+      each([&](int g, int d, float &v) { po[(part + static_cast<size_t>(g) * p.chunks) * D + d] = v; });
     }
   }
   if (threadIdx.x < G) {

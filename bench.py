@@ -209,15 +209,25 @@ def run_b200(args):
         result of step i - depth while step i is in flight (depth = --e2e-depth); every step's
         result is read on the host before the loop ends."""
         pending, acc = [], 0
+        clock = time.perf_counter
         for _ in range(n):
+            t0 = clock()
             xd = rt.to_layout(x_tensor, device, x_layout)                     # H2D from pinned memory
+            t1 = clock()
             out = rt.submit(device, e2e_binary, 0, [xd] + dev_in[1:])[0]
+            t2 = clock()
             pending.append(rt.to_host(out, untilize=True, blocking=False)[0])  # D2H into pinned memory
+            t3 = clock()
             if len(pending) > args.e2e_depth:
                 acc ^= read_result(pending.pop(0))
+            t4 = clock()
+            for k, dt in zip(("to_layout", "submit", "to_host", "wait_and_read"), (t1 - t0, t2 - t1, t3 - t2, t4 - t3)):
+                e2e_host[k] = e2e_host.get(k, 0.0) + dt
         while pending:
             acc ^= read_result(pending.pop(0))
         return acc
+
+    e2e_host = {}  # where the host spends its time in the end-to-end loop (seconds, summed over the timed steps)
 
     for _ in range(args.warmup if args.profile else max(args.warmup, 3)):
         step_resident()
@@ -252,6 +262,7 @@ def run_b200(args):
     # ---- e2e: host buffers in, host buffers out ---------------------------------------------
     run_e2e(3)
     barrier()
+    e2e_host.clear()
     t0 = time.perf_counter()
     run_e2e(args.steps)
     barrier()
@@ -273,7 +284,8 @@ def run_b200(args):
     prof = json.loads(buf.value.decode())
     return dict(rank=rank, world=world, ms_total=ms_total, e2e_s=e2e_s, launches=launches, clocks=clocks, prof=prof,
                 prof_steps=prof_steps, tokens=tokens, bytes_io=mine[0].numel() * 2, rt=rt, device=device,
-                host_submit_us=host_submit_us)
+                host_submit_us=host_submit_us,
+                e2e_host_us={k: v / args.steps * 1e6 for k, v in e2e_host.items()})
 
 
 # ---- the CPU oracle as baseline / reference arm -------------------------------------------------
@@ -585,6 +597,7 @@ def main():
                    "parallelism": f"tp{world}", "l2": "inputs larger than L2 (436 MB of weights per step vs 126 MB)",
                    "block_tflops_per_s": flops * steps / (r["ms_total"] * 1e-3) / 1e12,
                    "host_enqueue_us_per_step": r["host_submit_us"],
+                   "e2e_host_us_per_step": r.get("e2e_host_us", {}),
                    "e2e_io": ("pipelined loop, depth %d; " % args.e2e_depth) +
                              ("every rank uploads and downloads its 1/%d of the sequence (all_gather first, mesh_partition last)" % world
                               if world > 1 else "the activations are uploaded and the result downloaded every step")},

@@ -1,8 +1,9 @@
 """Generates tests/golden/ttir_cpu_golden.npz by running the reference's own CPU code.
 
-Run in a container where the tenstorrent/tt-mlir tree is mounted (default /root/reference):
+Run where a checkout of tenstorrent/tt-mlir is available (path as the argument, or in the
+TT_MLIR_ROOT environment variable):
 
-    python tests/golden/generate.py [/path/to/tt-mlir]
+    python tests/golden/generate.py /path/to/tt-mlir
 
 It imports tools/tt-alchemist/templates/python/local/ttir_cpu.py -- the pure-torch CPU
 implementation of the TTIR ops that the reference's CPU-hoist path targets -- and records its
@@ -37,7 +38,9 @@ def store(out, name, t):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TT_MLIR_ROOT", "")
+    if not root:
+        raise SystemExit("usage: generate.py /path/to/tt-mlir")
     cpu = load_ttir_cpu(root)
     g = torch.Generator().manual_seed(1234)
     out = {}

@@ -447,6 +447,12 @@ TTB_API int ttb_symm_all_reduce(void *symm, const void *in, const void *residual
  *       (needs m / n rows per block to be a multiple of 128; TTB_ERR_UNSUPPORTED otherwise);
  *   ttb_symm_all_reduce_pushed(symm, residual, out, count, dtype, stream)  sums the n partials of
  *       the own block locally, adds `residual` (nullable), shares the result with every rank. */
+/* SwiGLU gating as one contraction: out[M, N] = silu(A Wg^T) * (A Wu^T) with Wg, Wu [N, K] (the
+ * "transpose_b" layout), bf16 / f16.  Fuses linear(x, Wg), linear(x, Wu), silu, multiply of
+ * runtime/lib/ttnn/operations/{matmul/matmul.cpp:86-125, eltwise/unary, eltwise/binary} and rounds
+ * where those ops round. */
+TTB_API int ttb_gemm_swiglu(const void *a, const void *w_gate, const void *w_up, void *out, int dtype,
+                            int64_t m, int64_t n, int64_t k, void *stream);
 TTB_API int ttb_symm_push_targets(void *symm, size_t bytes, void **targets, int *rank, int *nranks);
 TTB_API int ttb_gemm_push(const void *a, const void *b, void *const *targets, int nranks, int ab_dtype,
                           int64_t m, int64_t n, int64_t k, void *stream);

@@ -179,3 +179,41 @@ def test_gemm_grouped_matches_separate_calls(rt, device, m, k, ns):
     for g, s_, b in zip(got, sep, bs):
         assert torch.equal(g, s_), "grouped and separate launches differ"
         assert_matches(g, (a.float() @ b.float().t()).to(torch.bfloat16), "grouped gemm")
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 384, 512), (2048, 1792, 1024), (200, 136, 72), (8, 16, 32), (1280, 14336, 256),
+                                   (130, 64, 64)])
+def test_gemm_swiglu_equals_the_chain_of_launches(rt, device, m, n, k):
+    """ttb_gemm_swiglu (gate and up projections in one accumulator, silu(gate) * up in the epilogue)
+    gives bit for bit what linear, linear + silu-multiply epilogue give as two launches, and matches
+    the f32 reference of the op chain with its bf16 roundings.  (8, 16, 32) is below the tensor-core
+    kernel's size limit and runs the composed fallback."""
+    torch.manual_seed(m + n + k)
+    a = torch.randn(m, k).to(torch.bfloat16)
+    wg = (torch.randn(n, k) * 0.05).to(torch.bfloat16)
+    wu = (torch.randn(n, k) * 0.05).to(torch.bfloat16)
+    h = KernelHarness(rt)
+    try:
+        da, dg, du = h.upload(a), h.upload(wg), h.upload(wu)
+        i64 = ctypes.c_int64
+        out = h.empty((m, n), torch.bfloat16)
+        rc = h.lib.ttb_gemm_swiglu(da, dg, du, out, BF16, i64(m), i64(n), i64(k), h.stream)
+        assert rc == 0, h.lib.ttb_last_error().decode()
+        got = h.download(out, (m, n), torch.bfloat16)
+        assert tc_status(h) == 0
+        gate = h.empty((m, n), torch.bfloat16)
+        two = h.empty((m, n), torch.bfloat16)
+        assert h.lib.ttb_gemm(da, dg, None, gate, BF16, BF16, BF16, i64(1), i64(m), i64(n), i64(k), 0, 1, i64(0), i64(0), 0, 0,
+                              h.stream) == 0
+        assert h.lib.ttb_gemm_fused(da, du, None, two, BF16, BF16, BF16, i64(1), i64(m), i64(n), i64(k), 0, 1, i64(0), i64(0), 0, 0,
+                                    gate, 2, h.stream) == 0
+        chain = h.download(two, (m, n), torch.bfloat16)
+    finally:
+        h.close()
+    assert torch.equal(got, chain), "one launch and two launches differ"
+    g = (a.float() @ wg.float().t()).to(torch.bfloat16).float()
+    u = (a.float() @ wu.float().t()).to(torch.bfloat16).float()
+    want = (torch.nn.functional.silu(g).to(torch.bfloat16).float() * u).to(torch.bfloat16)
+    # three roundings in a row (gate, silu, product): a one-ulp flip of an intermediate, which a different
+    # f32 summation order can cause, moves the result by up to two ulps
+    assert_matches(got, want, f"swiglu {m}x{n}x{k}", (0.999, 2e-2, 2.0 ** -6))

@@ -12,6 +12,8 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
                    int64_t batch, int64_t m, int64_t n, int64_t k, int transA, int transB, int64_t aBatchStride,
                    int64_t bBatchStride, int act, int roundSteps, const void *extra, int extraOp, cudaStream_t stream,
                    void *const *pushTargets = nullptr, int pushRanks = 0);
+int gemmTcgen05SwigluTry(const void *a, const void *wGate, const void *wUp, void *out, int dtype, int64_t m, int64_t n,
+                         int64_t k, cudaStream_t stream);
 int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, const int64_t *n, int count, int abDtype,
                           int cDtype, int64_t m, int64_t k, cudaStream_t stream);
 } // namespace ttb
@@ -84,4 +86,28 @@ extern "C" int ttb_gemm_push(const void *a, const void *b, void *const *targets,
   }
   ttb::setLastError("gemm_push: shape, type or alignment not taken by the tensor-core kernel");
   return TTB_ERR_UNSUPPORTED;
+}
+
+// out[M, N] = silu(A Wg^T) * (A Wu^T), every intermediate rounded to the element type as the chain
+// linear, linear, silu, multiply rounds it.  One launch of the tensor-core kernel when it takes the
+// shape; otherwise the gate projection goes to a temporary and the up projection's epilogue gates it.
+extern "C" int ttb_gemm_swiglu(const void *a, const void *w_gate, const void *w_up, void *out, int dtype, int64_t m,
+                               int64_t n, int64_t k, void *stream) {
+  TTB_CHECK(a && w_gate && w_up && out, "null tensor");
+  TTB_CHECK(m >= 0 && n >= 0 && k >= 0, "negative dimension");
+  if (m * n == 0) return TTB_OK;
+  if (!tcgen05Disabled()) {
+    int rc = ttb::gemmTcgen05SwigluTry(a, w_gate, w_up, out, dtype, m, n, k, ttb::asStream(stream));
+    if (rc != -1) return rc;
+  }
+  void *gate = nullptr;
+  int rc = ttb_malloc(&gate, static_cast<size_t>(m) * n * ttb::dtypeSize(dtype), stream);
+  if (rc) return rc;
+  rc = ttb_gemm(a, w_gate, nullptr, gate, dtype, 0, dtype, 1, m, n, k, 0, 1, 0, 0, TTB_ACT_NONE, 0, stream);
+  if (!rc) {
+    rc = ttb_gemm_fused(a, w_up, nullptr, out, dtype, 0, dtype, 1, m, n, k, 0, 1, 0, 0, TTB_ACT_NONE, 0, gate, TTB_EXTRA_SILU_MUL,
+                        stream);
+  }
+  int rc2 = ttb_free(gate, stream);
+  return rc ? rc : rc2;
 }

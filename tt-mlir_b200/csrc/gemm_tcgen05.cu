@@ -94,6 +94,11 @@ struct TcParams {
   // (o + 1) * pushRows) of C is stored through pushMaps.m[o], a [pushRows, N] matrix in rank o's
   // workspace, instead of through mapC.  pushRows is a multiple of the tile height; 0 = off.
   int pushRows;
+  // SwiGLU mode (BN = 256 only): the B tile of a stage is 128 rows of the gate weights (mapB) on
+  // top of the matching 128 rows of the up weights (mapB1), so accumulator columns 0..127 hold the
+  // gate projection and 128..255 the up projection of the same 128 output columns; the epilogue
+  // stores silu(gate) * up, rounding where the chain of separate ops rounds.  N counts output columns.
+  int dual;
   const void *extra; // optional [M, N] operand in the output type, combined after bias / activation
   int extraOp;       // TTB_EXTRA_*
   // Implicit-GEMM convolution: A is not a matrix in memory but the receptive fields of an NHWC
@@ -144,7 +149,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
   // n-tile index -> (segment, first column inside the segment)
   auto segmentOf = [&](int64_t nt, int &n0) {
     const int seg = nt < p.segCum[0] ? 0 : (nt < p.segCum[1] ? 1 : 2);
-    n0 = static_cast<int>(nt - (seg == 0 ? 0 : p.segCum[seg - 1])) * BN;
+    n0 = static_cast<int>(nt - (seg == 0 ? 0 : p.segCum[seg - 1])) * (p.dual ? BN / 2 : BN);
     return seg;
   };
   const int kBlocks = static_cast<int>((p.K + TC_BK - 1) / TC_BK);
@@ -283,7 +288,12 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
           } else {
             tmaLoad2d(sa, &mapA, fullBar(s), kb * TC_BK, m0);
           }
-          tmaLoad2d(sb, mb, fullBar(s), kb * TC_BK, n0);
+          if (p.dual) {
+            tmaLoad2d(sb, &mapB, fullBar(s), kb * TC_BK, n0);
+            tmaLoad2d(sb + (BN / 2) * TC_BK * 2, &mapB1, fullBar(s), kb * TC_BK, n0);
+          } else {
+            tmaLoad2d(sb, mb, fullBar(s), kb * TC_BK, n0);
+          }
         }
       }
     }
@@ -380,8 +390,61 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
         pOx = (rem % p.cTilesX) * p.cTw;
       }
       const uint32_t taddrRow = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      // SwiGLU mode: two chunks of 64 output columns; gate in accumulator columns [0, 128), up in [128, 256).
+      bool dualDone = false;
+      if constexpr (!PLAIN && sizeof(TC) == 2 && BN == 256) {
+        if (p.dual) {
+          dualDone = true;
 #pragma unroll 1
-      for (int cc = (shared && helper) ? 1 : 0; cc < BN / CH; cc += shared ? 2 : 1) {
+          for (int cc = (shared && helper) ? 1 : 0; cc < 2; cc += shared ? 2 : 1) {
+            const int64_t col0 = n0 + cc * CH;
+            if (col0 >= segN || p.debug == 2) break; // warp-uniform
+            const uint32_t buf = stageOut;
+            const uint32_t rowAddr = buf + static_cast<uint32_t>(lane) * 128u;
+#pragma unroll
+            for (int l = 0; l < 2; ++l) {
+              uint32_t g[32], u[32];
+              tcLoad32(taddrRow + static_cast<uint32_t>(cc * CH + l * 32), g);
+              tcLoad32(taddrRow + static_cast<uint32_t>(BN / 2 + cc * CH + l * 32), u);
+              tcWaitLd();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                // every value the chain of separate ops would have stored is rounded here as well
+                const float gv = toF32(fromF32<TC>(__uint_as_float(g[e])));
+                const float sg = toF32(fromF32<TC>(__fdividef(gv, 1.0f + __expf(-gv))));
+                g[e] = __float_as_uint(__fmul_rn(sg, toF32(fromF32<TC>(__uint_as_float(u[e])))));
+              }
+              if (l == 0) {
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); // the last store has read the buffer
+                __syncwarp();
+              }
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const int e = v * 8 + q * 2;
+                  w[q] = pack2<TC>(__uint_as_float(g[e]), __uint_as_float(g[e + 1]));
+                }
+                const int pieceIdx = l * 4 + v;
+                const uint32_t addr = rowAddr + (static_cast<uint32_t>(pieceIdx ^ (lane & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+              }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(reinterpret_cast<uint64_t>(mc)), "r"(buf), "r"(static_cast<int>(col0)), "r"(rowBase)
+                           : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            ++chunkIt;
+          }
+        }
+      }
+#pragma unroll 1
+      for (int cc = dualDone ? BN / CH : ((shared && helper) ? 1 : 0); cc < BN / CH; cc += shared ? 2 : 1) {
         const int64_t col0 = n0 + cc * CH;
         if (col0 >= segN || p.debug == 2) break; // warp-uniform
         const uint32_t buf = stageOut + (EPW == 4 ? (chunkIt & 1u) * 4096u : 0u);
@@ -714,6 +777,7 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   p.cTw = 0;
   p.cTilesM = 0;
   p.pushRows = 0;
+  p.dual = 0;
   PushMaps pm;
   if (pushing) {
     p.pushRows = static_cast<int>(m / pushRanks);
@@ -746,6 +810,37 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   TTB_TC_BN(float)
 #undef TTB_TC_BN
 #undef TTB_TC
+}
+
+// out[M, N] = silu(A Wg^T) * (A Wu^T) as ONE launch (SwiGLU mode of the kernel): A is read once, the
+// gate projection never leaves the SM.  Wg, Wu: [N, K].  -1 = not taken.
+int gemmTcgen05SwigluTry(const void *a, const void *wGate, const void *wUp, void *out, int dtype, int64_t m, int64_t n,
+                         int64_t k, cudaStream_t stream) {
+  if (dtype != kBF16 && dtype != kF16) return -1;
+  if (k % 8 != 0 || n % 8 != 0 || m < 1 || n < 64 || k < 8) return -1;
+  if (!aligned16(a) || !aligned16(wGate) || !aligned16(wUp) || !aligned16(out)) return -1;
+  if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff) return -1;
+  if (m * n * k < (1ll << 18)) return -1;
+  constexpr int BN = 256;
+  CUtensorMap ma, mg, mu, mc;
+  if (!makeMap(&ma, a, dtype, m, k, TC_BM) || !makeMap(&mg, wGate, dtype, n, k, BN / 2) ||
+      !makeMap(&mu, wUp, dtype, n, k, BN / 2) || !makeMap(&mc, out, dtype, m, n, 32))
+    return -1;
+  TcParams p;
+  p.M = m; p.N = n; p.K = k;
+  p.bias = nullptr; p.biasDt = 0; p.act = TTB_ACT_NONE; p.roundSteps = 0;
+  p.extra = nullptr; p.extraOp = 0;
+  p.convX = nullptr; p.cTw = 0; p.cTilesM = 0; p.pushRows = 0;
+  p.dual = 1;
+  p.segCum[0] = p.segCum[1] = p.segCum[2] = static_cast<int>((n + BN / 2 - 1) / (BN / 2));
+  p.segN[0] = p.segN[1] = p.segN[2] = n;
+  p.fmt = dtype == kBF16 ? 1 : 0;
+  p.debug = 0;
+  // both projections' FLOPs; A and both weights once, the result once
+  ProfScope prof("gemm_tcgen05", 4.0 * double(m) * double(n) * double(k), (double(m) * k + 2.0 * double(n) * k + double(m) * n) * 2, stream);
+  const CUtensorMap more[4] = {mu, mc, mu, mc};
+  if (dtype == kBF16) return launchTc<BN, __nv_bfloat16, false>(ma, mg, mc, mc, out, p, stream, more);
+  return launchTc<BN, __half, false>(ma, mg, mc, mc, out, p, stream, more);
 }
 
 // Up to three GEMMs C_i[M, N_i] = A[M, K] B_i[N_i, K]^T that share A (the q / k / v projections of
@@ -796,7 +891,7 @@ int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, c
   p.M = m; p.N = n[0]; p.K = k;
   p.bias = nullptr; p.biasDt = 0; p.act = TTB_ACT_NONE; p.roundSteps = 0;
   p.extra = nullptr; p.extraOp = 0;
-  p.convX = nullptr; p.cTw = 0; p.cTilesM = 0; p.pushRows = 0;
+  p.convX = nullptr; p.cTw = 0; p.cTilesM = 0; p.pushRows = 0; p.dual = 0;
   int cum = 0;
   double flops = 0, bytes = double(m) * k * 2;
   for (int i = 0; i < 3; ++i) {
@@ -890,6 +985,7 @@ int convTcgen05Try(const void *x, const void *wre, const void *bias, void *out, 
   p.extraOp = extra ? extraOp : 0;
   p.convX = x;
   p.pushRows = 0;
+  p.dual = 0;
   p.cH = static_cast<int>(h); p.cW = static_cast<int>(w); p.cC = static_cast<int>(c);
   p.cHo = static_cast<int>(ho); p.cWo = static_cast<int>(wo);
   p.ckw = kw; p.csh = sh; p.csw = sw; p.cpt = pt; p.cpl = pl; p.cdh = dh; p.cdw = dw;

@@ -419,6 +419,7 @@ private:
   size_t tryQuantChain(size_t i);
   size_t tryGemmEpilogue(size_t i);
   size_t tryGroupedGemm(size_t i);
+  size_t trySwiglu(size_t i);
   size_t trySiluMul(size_t i);
   size_t trySdpa(size_t i);
   size_t tryAllReduceAdd(size_t i);
@@ -698,7 +699,8 @@ size_t Executor::runOp(size_t i) {
     case OpType::EltwiseQuantizationOp: used = tryQuantChain(i); break;
     case OpType::MatmulOp:
     case OpType::LinearOp:
-      used = tryGemmEpilogue(i);
+      used = trySwiglu(i);
+      if (!used) used = tryGemmEpilogue(i);
       if (!used) used = tryGroupedGemm(i);
       break;
     case OpType::EltwiseUnaryOp: used = trySiluMul(i); break;
@@ -1417,6 +1419,82 @@ size_t Executor::tryGemmEpilogue(size_t i) {
   runGemm(a, b, bias, cur, ta, tb, act, roundSteps, extra, extraOp);
   runDeallocs(deallocs);
   return consumedUpTo + 1 - i;
+}
+
+// SwiGLU: g = linear(x, Wg); u = linear(x, Wu); h = multiply(silu(g), u) with g, u and silu(g) used
+// nowhere else runs as one contraction whose accumulator holds both projections of an output tile
+// (ttb_gemm_swiglu): x is read once and the gate projection never reaches HBM.  The ops may come in
+// either of the orders (g, u, silu, multiply) or (g, silu, u, multiply), deallocations in between.
+// TTB_DISABLE_SWIGLU_GEMM=1 leaves the pattern to the two-launch form.
+size_t Executor::trySwiglu(size_t i) {
+  static const bool disabled = [] {
+    const char *e = std::getenv("TTB_DISABLE_SWIGLU_GEMM");
+    return e && e[0] == '1';
+  }();
+  if (disabled) return 0;
+  const auto *ops = prog->operations();
+  struct Proj { const fbt::TensorRef *a, *b, *out; };
+  auto plain = [&](const fbt::Operation *op, Proj &pr) {
+    if (!op) return false;
+    if (op->type_type() == OpType::LinearOp) {
+      const auto *l = op->type_as_LinearOp();
+      if (l->bias() || l->transpose_a() || !l->transpose_b() || activationCode(l->activation()) != TTB_ACT_NONE) return false;
+      pr = {l->a(), l->b(), l->out()};
+      return true;
+    }
+    if (op->type_type() == OpType::MatmulOp) {
+      const auto *m = op->type_as_MatmulOp();
+      if (m->transpose_a() || !m->transpose_b() || activationCode(m->activation()) != TTB_ACT_NONE) return false;
+      pr = {m->a(), m->b(), m->out()};
+      return true;
+    }
+    return false;
+  };
+  Proj gate, up;
+  if (!plain(ops->Get(static_cast<uint32_t>(i)), gate) || !singleUse(gate.out)) return 0;
+  std::vector<const fbt::Operation *> deallocs;
+  size_t j = i + 1;
+  const fbt::Operation *op1 = peek(j, deallocs);
+  size_t j2 = j + 1;
+  const fbt::Operation *op2 = op1 ? peek(j2, deallocs) : nullptr;
+  size_t j3 = j2 + 1;
+  const fbt::Operation *op3 = op2 ? peek(j3, deallocs) : nullptr;
+  if (!op1 || !op2 || !op3) return 0;
+  const fbt::EltwiseUnaryOp *silu = nullptr;
+  if (plain(op1, up) && op2->type_type() == OpType::EltwiseUnaryOp) silu = op2->type_as_EltwiseUnaryOp();
+  else if (op1->type_type() == OpType::EltwiseUnaryOp && plain(op2, up)) silu = op1->type_as_EltwiseUnaryOp();
+  else return 0;
+  if (op3->type_type() != OpType::EltwiseBinaryOp) return 0;
+  const auto *mul = op3->type_as_EltwiseBinaryOp();
+  if (silu->type() != fbt::EltwiseUnaryOpType::Silu || silu->in()->global_id() != gate.out->global_id() ||
+      !singleUse(silu->out()) || !singleUse(up.out) || up.a->global_id() != gate.a->global_id() ||
+      mul->type() != fbt::EltwiseBinaryOpType::Multiply) {
+    return 0;
+  }
+  const uint32_t l = mul->lhs()->global_id(), r = mul->rhs()->global_id(), sId = silu->out()->global_id(), uId = up.out->global_id();
+  if (!((l == sId && r == uId) || (l == uId && r == sId))) return 0;
+  DataType dt = refDtype(mul->out());
+  if ((dt != DataType::BFloat16 && dt != DataType::Float16) || refDtype(gate.out) != dt || refDtype(up.out) != dt ||
+      refDtype(silu->out()) != dt) {
+    return 0;
+  }
+  if (refShape(gate.out) != refShape(up.out) || refShape(mul->out()) != refShape(gate.out) ||
+      refShape(silu->out()) != refShape(gate.out)) {
+    return 0;
+  }
+  TensorPtr a = getDevice(gate.a), wg = getDevice(gate.b), wu = getDevice(up.b);
+  if (a->dtype != dt || wg->dtype != dt || wu->dtype != dt || wg->shape.size() != 2 || wu->shape != wg->shape || a->shape.empty()) return 0;
+  const int64_t K = a->shape.back(), N = wg->shape[0], M = static_cast<int64_t>(a->volume()) / std::max<int64_t>(K, 1);
+  if (static_cast<int64_t>(wg->shape[1]) != K || K % 8 != 0 || N % 8 != 0) return 0;
+  TensorPtr out = allocOut(mul->out());
+  if (static_cast<int64_t>(out->volume()) != M * N) return 0;
+  eachRank([&](size_t rk, const RankCtx &rc) {
+    TTB_CALL(ttb_gemm_swiglu(a->shards[rk]->ptr, wg->shards[rk]->ptr, wu->shards[rk]->ptr, out->shards[rk]->ptr, ttbDtype(dt), M, N,
+                             K, rc.stream));
+  });
+  put(mul->out(), out);
+  runDeallocs(deallocs);
+  return j3 + 1 - i;
 }
 
 // Two or three consecutive linear / matmul ops on the same activation (q, k, v projections):

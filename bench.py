@@ -26,7 +26,7 @@ import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-GEMM_DRAM_BYTES_PER_LAUNCH_N1 = 842.1e6 / 5  # 842.1 MB per pass of the block over its five GEMM launches
+GEMM_DRAM_BYTES_PER_LAUNCH_N1 = 712.4e6 / 4  # 712.4 MB per pass of the block over its four GEMM launches (ncu, N = 1)
 sys.path.insert(0, ROOT)
 
 CONFIG = dict(seq=2048, hidden=4096, n_heads=32, n_kv_heads=8, head_dim=128, ffn=14336, batch=1)
@@ -584,7 +584,7 @@ def main():
                 "peak": peaks["bf16_tflops_sustained"] if dom.get("bound") == "tensor" else peaks["hbm_gbs"],
                 "unit": dom.get("unit"), "frac": dom.get("frac"),
                 # DRAM bytes per launch of the dominant kernel from an ncu capture of this workload
-                # (profiles/gemm_tcgen05_decoder_dram_traffic.md): 842.1 MB per pass over the block's GEMMs at N = 1.
+                # (profiles/gemm_tcgen05_decoder_dram_traffic.md): 712.4 MB per pass over the block's four GEMM launches at N = 1.
                 "traffic": GEMM_DRAM_BYTES_PER_LAUNCH_N1 if (world == 1 and dom.get("kernel") == "gemm_tcgen05") else None,
                 "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum, N=1 capture)",
                 "peak_source": f"{peaks['source']} (sustained bf16 figure: the kernel is timed inside a long step)"}

@@ -51,6 +51,13 @@ CASES = [
     (1, 2, 1, 130, 515, False),
     (1, 2, 2, 384, 512, True),
     (1, 2, 2, 1, 300, False),
+    # tensor-parallel shards of the decoder block (few heads)
+    (1, 4, 1, 2048, 2048, True),
+    (1, 8, 2, 2048, 2048, True),
+    # few heads and long sequences: the causal key ranges are split over several CTAs and merged
+    (1, 2, 1, 4096, 4096, True),
+    (1, 2, 2, 3333, 3333, True),
+    (1, 1, 1, 3000, 3000, True),
     # enough CTAs for the kernel that gives one CTA two heads of a grouped-query group
     (1, 16, 4, 2432, 2432, True),
     (1, 16, 8, 2400, 2400, False),

@@ -24,6 +24,8 @@
 #include "common.cuh"
 #include "tcgen05.cuh"
 
+#include <algorithm>
+
 #include <cstdlib>
 
 namespace ttb {
@@ -44,6 +46,14 @@ struct AtParams {
   int fmt; // 1 bf16, 0 f16
   float scaleLog2;
   long long *stamps; // diagnostic: clock64 of CTA 0's MMA thread and first softmax thread, or null
+  // Split mode (few heads: fewer query blocks than SMs, and a causal block's work grows with its
+  // index): a query block's key tiles are cut into pieces of at most splitLen tiles, one CTA per
+  // piece; pieceStart[qb] is the first piece of query block qb (pieceStart[nQ] = pieces per head).
+  // A piece stores its unnormalised O (f32), row maxima and row sums; sdpaMergeKernel combines
+  // them.  splitLen = 0: one CTA per query block, which writes the result itself.
+  int splitLen;
+  unsigned short pieceStart[66];
+  float *partO, *partM, *partL;
 };
 
 __device__ __forceinline__ float fastExp2(float x) {
@@ -79,18 +89,30 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t nQ = (p.Sq + AT_BM - 1) / AT_BM;
-  const int64_t BH = static_cast<int64_t>(gridDim.x) / nQ;
-  // Heaviest (latest, under a causal mask) query blocks first.
-  const int qb = static_cast<int>(nQ - 1 - blockIdx.x / BH);
+  const int64_t perHead = p.splitLen ? p.pieceStart[nQ] : nQ; // CTAs per (batch, head)
+  const int64_t BH = static_cast<int64_t>(gridDim.x) / perHead;
+  int qb, piece = 0;
+  if (p.splitLen) {
+    const int pi = static_cast<int>(blockIdx.x / BH);
+    qb = 0;
+    while (qb + 1 < nQ && p.pieceStart[qb + 1] <= pi) ++qb;
+    piece = pi - p.pieceStart[qb];
+  } else {
+    // Heaviest (latest, under a causal mask) query blocks first.
+    qb = static_cast<int>(nQ - 1 - blockIdx.x / BH);
+  }
   const int bh = static_cast<int>(blockIdx.x % BH);
   const int b = static_cast<int>(bh / p.Hq), h = static_cast<int>(bh % p.Hq);
   const int hkv = static_cast<int>(h / (p.Hq / p.Hkv));
   const int q0 = qb * AT_BM;
-  int nT = static_cast<int>((p.Skv + AT_BN - 1) / AT_BN);
+  int nAll = static_cast<int>((p.Skv + AT_BN - 1) / AT_BN); // key tiles this query block sees
   if (p.causal) {
     int lim = q0 / AT_BN + 1;
-    nT = nT < lim ? nT : lim;
+    nAll = nAll < lim ? nAll : lim;
   }
+  // this CTA's tiles: [t0, t0 + nT)
+  const int t0 = p.splitLen ? piece * p.splitLen : 0;
+  const int nT = p.splitLen ? (nAll - t0 < p.splitLen ? nAll - t0 : p.splitLen) : nAll;
 
   if (threadIdx.x == 0) {
     abortFlag = 0;
@@ -130,12 +152,12 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         const int s = j & 1, ph = (j >> 1) & 1;
         if (!mbarWait(kEmpty + 8 * s, ph ^ 1, abortP, 1)) break;
         mbarArriveExpectTx(kFull + 8 * s, AT_TILE);
-        tmaLoad4d(sK + s * AT_TILE, &mapK, kFull + 8 * s, 0, j * AT_BN, hkv, b);
-        tmaLoad4d(sK + s * AT_TILE + AT_HALF, &mapK, kFull + 8 * s, 64, j * AT_BN, hkv, b);
+        tmaLoad4d(sK + s * AT_TILE, &mapK, kFull + 8 * s, 0, (t0 + j) * AT_BN, hkv, b);
+        tmaLoad4d(sK + s * AT_TILE + AT_HALF, &mapK, kFull + 8 * s, 64, (t0 + j) * AT_BN, hkv, b);
         if (!mbarWait(vEmpty + 8 * s, ph ^ 1, abortP, 2)) break;
         mbarArriveExpectTx(vFull + 8 * s, AT_TILE);
-        tmaLoad4d(sV + s * AT_TILE, &mapV, vFull + 8 * s, 0, j * AT_BN, hkv, b);
-        tmaLoad4d(sV + s * AT_TILE + AT_HALF, &mapV, vFull + 8 * s, 64, j * AT_BN, hkv, b);
+        tmaLoad4d(sV + s * AT_TILE, &mapV, vFull + 8 * s, 0, (t0 + j) * AT_BN, hkv, b);
+        tmaLoad4d(sV + s * AT_TILE + AT_HALF, &mapV, vFull + 8 * s, 64, (t0 + j) * AT_BN, hkv, b);
       }
     }
   } else if (warp == 1) {
@@ -220,7 +242,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       if (!__all_sync(0xffffffffu, mbarWait(sFull + 8 * s, ph, abortP, 9))) { ok = false; break; }
       tcFenceAfter();
       const uint32_t sAddr = laneAddr + s * AT_BN + wg * HALF;
-      const int key0 = j * AT_BN + wg * HALF;
+      const int key0 = (t0 + j) * AT_BN + wg * HALF;
       const bool needMask = (p.causal && key0 + HALF - 1 > q0) || key0 + HALF > p.Skv;
       // Last visible key of this row inside this half tile (relative, may be negative or >= 64).
       int64_t lastKey = p.Skv - 1;
@@ -302,7 +324,26 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     // The last P V has to land before O is read; the row sum is the two halves' sums.
     if (ok && nT > 0 && !__all_sync(0xffffffffu, mbarWait(pEmpty, (nT & 1) ^ 1, abortP, 11))) ok = false;
     if (ok) l += exchange(l);
-    if (ok) {
+    if (ok && p.splitLen) {
+      // this piece's partial result: O as accumulated (f32), the reference maximum and the row sum
+      tcFenceAfter();
+      const size_t pieceIdx = static_cast<size_t>(bh) * p.pieceStart[nQ] + p.pieceStart[qb] + piece;
+      float *po = p.partO + (pieceIdx * AT_BM + row) * AT_D + wg * HALF;
+#pragma unroll
+      for (int c = 0; c < HALF / 32; ++c) {
+        uint32_t r[32];
+        tcLoad32(oAddr + c * 32, r);
+        tcWaitLd();
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          *reinterpret_cast<uint4 *>(po + c * 32 + g * 4) = make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+        }
+      }
+      if (wg == 0) {
+        p.partM[pieceIdx * AT_BM + row] = m;
+        p.partL[pieceIdx * AT_BM + row] = l;
+      }
+    } else if (ok) {
       tcFenceAfter();
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
       T *orow = out + b * p.ob + h * p.oh + qrow * p.os + wg * HALF;
@@ -661,6 +702,44 @@ static int launchPair(const CUtensorMap &mq, const CUtensorMap &mk, const CUtens
   return TTB_OK;
 }
 
+// Combines the pieces of a query block (split mode): one warp per query row, lane = 4 head dims.
+template <typename T>
+__global__ void __launch_bounds__(256) sdpaMergeKernel(T *__restrict__ out, AtParams p, int rows) {
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const int64_t nQ = (p.Sq + AT_BM - 1) / AT_BM;
+  const int bh = static_cast<int>(r / (nQ * AT_BM)), rem = static_cast<int>(r % (nQ * AT_BM));
+  const int qb = rem / AT_BM, row = rem % AT_BM;
+  const int64_t qrow = static_cast<int64_t>(qb) * AT_BM + row;
+  if (qrow >= p.Sq) return;
+  const int first = p.pieceStart[qb], count = p.pieceStart[qb + 1] - first;
+  const size_t base = static_cast<size_t>(bh) * p.pieceStart[nQ] + first;
+  // pieces with an empty row sum saw no visible key and carry no maximum
+  float mx = -INFINITY;
+  for (int k = 0; k < count; ++k) {
+    if (p.partL[(base + k) * AT_BM + row] > 0.0f) mx = fmaxf(mx, p.partM[(base + k) * AT_BM + row]);
+  }
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, den = 0.0f;
+  for (int k = 0; k < count; ++k) {
+    const float lk = p.partL[(base + k) * AT_BM + row];
+    if (!(lk > 0.0f)) continue;
+    const float w = fastExp2((p.partM[(base + k) * AT_BM + row] - mx) * p.scaleLog2);
+    den += lk * w;
+    const float4 o = *reinterpret_cast<const float4 *>(p.partO + ((base + k) * AT_BM + row) * AT_D + lane * 4);
+    acc[0] = fmaf(o.x, w, acc[0]);
+    acc[1] = fmaf(o.y, w, acc[1]);
+    acc[2] = fmaf(o.z, w, acc[2]);
+    acc[3] = fmaf(o.w, w, acc[3]);
+  }
+  const float inv = den > 0.0f ? 1.0f / den : 0.0f;
+  const int b = static_cast<int>(bh / p.Hq), h = static_cast<int>(bh % p.Hq);
+  T *orow = out + b * p.ob + h * p.oh + qrow * p.os + lane * 4;
+  uint2 v;
+  v.x = packPair<T>(acc[0] * inv, acc[1] * inv);
+  v.y = packPair<T>(acc[2] * inv, acc[3] * inv);
+  *reinterpret_cast<uint2 *>(orow) = v;
+}
+
 template <typename T>
 static int launchAt(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, void *out, const AtParams &p,
                     unsigned grid, cudaStream_t st) {
@@ -712,6 +791,8 @@ int sdpaTcgen05Try(const void *q, const void *k, const void *v, void *out, int d
   p.fmt = dtype == kBF16 ? 1 : 0;
   p.scaleLog2 = scale * 1.4426950408889634f;
   p.stamps = g_atStamps;
+  p.splitLen = 0;
+  p.partO = p.partM = p.partL = nullptr;
   double work = 4.0 * double(batch) * hq * sq * skv * headDim * (causal ? 0.5 : 1.0);
   ProfScope prof("sdpa_tcgen05", work, 2.0 * batch * (2.0 * hq * sq + 2.0 * hkv * skv) * headDim, st);
   if (pair) {
@@ -719,8 +800,70 @@ int sdpaTcgen05Try(const void *q, const void *k, const void *v, void *out, int d
     if (dtype == kBF16) return launchPair<__nv_bfloat16>(mq, mk, mv, out, p, grid, st);
     return launchPair<__half>(mq, mk, mv, out, p, grid, st);
   }
-  if (dtype == kBF16) return launchAt<__nv_bfloat16>(mq, mk, mv, out, p, static_cast<unsigned>(ctas), st);
-  return launchAt<__half>(mq, mk, mv, out, p, static_cast<unsigned>(ctas), st);
+  // Few heads and long sequences: fewer query blocks than SMs, and under a causal mask the launch
+  // lasts as long as its last query block.  Cut the key ranges into pieces of L tiles, L chosen to
+  // minimise waves x (L + 6) + 3, in units of one key tile's steady-state time: 6 for a CTA's fixed
+  // cost (allocation, Q tile, first trip through the load / contraction / softmax pipeline,
+  // epilogue), 3 for the merge launch.  Measured: 2 heads x 4096 tokens 49.5 -> 33.6 us; at 4 heads x
+  // 2048 tokens (a 1/8 tensor-parallel shard of the decoder block) only 29.1 -> 27.4 us, because all
+  // pieces then stream the same few heads' K and V at once and the launch becomes bound by L2
+  // bandwidth (each key tile is still read once per query block), and at 8 heads the second wave of
+  // pieces made it slower; so the split is taken only when the model promises at least 40 %.
+  // TTB_SDPA_NO_SPLIT=1 switches it off.
+  static const bool noSplit = [] {
+    const char *e = std::getenv("TTB_SDPA_NO_SPLIT");
+    return e && e[0] == '1';
+  }();
+  void *scratch = nullptr;
+  unsigned grid = static_cast<unsigned>(ctas);
+  const int64_t tilesAll = (skv + AT_BN - 1) / AT_BN;
+  if (!noSplit && causal && nQ <= 64 && ctas < smCount() && tilesAll >= 4) {
+    auto tilesOf = [&](int64_t qb) { return std::min<int64_t>(tilesAll, qb * AT_BM / AT_BN + 1); };
+    const int64_t unsplit = (tilesOf(nQ - 1) + 6) * ((ctas + smCount() - 1) / smCount());
+    int64_t bestCost = unsplit * 6 / 10;
+    int bestL = 0;
+    for (int L = static_cast<int>(tilesOf(nQ - 1)) - 1; L >= 2; --L) {
+      int64_t pieces = 0;
+      for (int64_t qb = 0; qb < nQ; ++qb) pieces += (tilesOf(qb) + L - 1) / L;
+      pieces *= batch * hq;
+      const int64_t cost = ((pieces + smCount() - 1) / smCount()) * (L + 6) + 3;
+      if (cost < bestCost) {
+        bestCost = cost;
+        bestL = L;
+      }
+    }
+    if (bestL) {
+      int64_t perHead = 0;
+      for (int64_t qb = 0; qb < nQ; ++qb) {
+        p.pieceStart[qb] = static_cast<unsigned short>(perHead);
+        perHead += (tilesOf(qb) + bestL - 1) / bestL;
+      }
+      p.pieceStart[nQ] = static_cast<unsigned short>(perHead);
+      const size_t pieces = static_cast<size_t>(perHead) * batch * hq;
+      const size_t bytes = pieces * AT_BM * (AT_D + 2) * sizeof(float);
+      int rc = ttb_malloc(&scratch, bytes, st);
+      if (rc) return rc;
+      p.splitLen = bestL;
+      p.partO = static_cast<float *>(scratch);
+      p.partM = p.partO + pieces * AT_BM * AT_D;
+      p.partL = p.partM + pieces * AT_BM;
+      grid = static_cast<unsigned>(pieces);
+    }
+  }
+  int rc = dtype == kBF16 ? launchAt<__nv_bfloat16>(mq, mk, mv, out, p, grid, st) : launchAt<__half>(mq, mk, mv, out, p, grid, st);
+  if (p.splitLen) {
+    if (rc == TTB_OK) {
+      const int rows = static_cast<int>(batch * hq * nQ * AT_BM);
+      if (dtype == kBF16) sdpaMergeKernel<__nv_bfloat16><<<(rows + 7) / 8, 256, 0, st>>>(static_cast<__nv_bfloat16 *>(out), p, rows);
+      else sdpaMergeKernel<__half><<<(rows + 7) / 8, 256, 0, st>>>(static_cast<__half *>(out), p, rows);
+      countLaunch();
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) rc = cudaFail(e, "sdpaMergeKernel", __FILE__, __LINE__);
+    }
+    int rc2 = ttb_free(scratch, st);
+    if (rc == TTB_OK) rc = rc2;
+  }
+  return rc;
 }
 
 } // namespace ttb

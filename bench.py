@@ -260,6 +260,11 @@ def run_b200(args):
                     host_submit_us=host_submit_us)
 
     # ---- e2e: host buffers in, host buffers out ---------------------------------------------
+    # Like the resident loop, the end-to-end loop starts from an idle GPU: after --idle-s seconds
+    # without work the clocks and the power budget are where they were before the first loop.
+    if args.idle_s > 0:
+        barrier()
+        time.sleep(args.idle_s)
     run_e2e(3)
     barrier()
     e2e_host.clear()
@@ -532,6 +537,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-depth", type=int, default=2,
                     help="steps in flight in the end-to-end loop before the host reads a result")
+    ap.add_argument("--idle-s", type=float, default=1.0,
+                    help="idle time before the end-to-end loop, so that it starts from the same GPU state as the resident loop")
     ap.add_argument("--profile", action="store_true",
                     help="for runs under a profiler: exactly --warmup warm-up steps, then --steps steps, nothing else")
     ap.add_argument("--workload", default="decoder",
@@ -598,6 +605,7 @@ def main():
                    "block_tflops_per_s": flops * steps / (r["ms_total"] * 1e-3) / 1e12,
                    "host_enqueue_us_per_step": r["host_submit_us"],
                    "e2e_host_us_per_step": r.get("e2e_host_us", {}),
+                   "e2e_idle_s_before": args.idle_s,
                    "e2e_io": ("pipelined loop, depth %d; " % args.e2e_depth) +
                              ("every rank uploads and downloads its 1/%d of the sequence (all_gather first, mesh_partition last)" % world
                               if world > 1 else "the activations are uploaded and the result downloaded every step")},

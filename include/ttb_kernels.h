@@ -208,7 +208,7 @@ TTB_API int ttb_pool2d(const void *in, void *out, int dtype, int is_max, int n, 
 
 /* ::ttnn::embedding (operations/embedding/embedding.cpp): out[r, :] = table[indices[r], :].
  * Indices are Int32 / UInt32 / UInt16 or a float type holding integers.  An index outside
- * [0, vocab) reads row 0 and sets a sticky flag that ttb_embedding_status returns (after
+ * [0, vocab) reads row 0 and sets a flag that ttb_embedding_status returns and clears (after
  * synchronising the device). */
 TTB_API int ttb_embedding(const void *indices, const void *table, void *out, int index_dtype, int dtype,
                           size_t rows, size_t vocab, size_t dim, void *stream);
@@ -225,7 +225,7 @@ TTB_API int ttb_pad(const void *in, void *out, int dtype, int rank, const int64_
  *                rows up to the next multiple of 32 are zeroed when the cache has them
  *  update_cache  cache[batch_offset + b, h, index] = input[0, h, b]  (input [1, heads, users, head_dim]),
  *                `index` = element 0 of a device tensor, read by the kernel.  An index outside the cache
- *                writes nothing and sets a sticky flag (ttb_update_cache_status, synchronises)
+ *                writes nothing and sets a flag (ttb_update_cache_status synchronises, returns and clears it)
  *  sdpa_decode   q [1, batch, heads, head_dim] against k, v [batch, kv_heads, seq, head_dim]; keys after
  *                cur_pos[b] (Int32, nullable) are masked when is_causal; `mask` (nullable, the tensors'
  *                dtype) is [mask_users, 1, mask_heads, seq] with extents 1 or full; scores are

@@ -102,3 +102,36 @@ def test_decode_step_updates_the_cache_then_attends(rt, device):
     assert_matches(got[0], want[0], "decode step", (0.999, 1e-2, 2.0 ** -6))
     assert torch.equal(got[1], want[1]) and torch.equal(got[2], want[2])
     assert torch.equal(got[1][:, :, at], kn[0].permute(1, 0, 2))
+
+
+def test_bad_positions_and_indices_are_reported_not_followed(rt, device):
+    """An update position outside the cache writes nothing, an embedding index outside the table reads
+    row 0; neither touches memory it should not, and the next wait on a device tensor says so (once)."""
+    from ttmlir_b200 import graphs
+    cache = torch.randn(2, 2, 64, 64).to(torch.bfloat16)
+    x = torch.randn(1, 2, 2, 64).to(torch.bfloat16)
+
+    def run(graph, inputs):
+        binary = rt.Binary.load_from_memory(graphs.build_binary(graph))
+        ins = [rt.to_layout(rt.from_torch(t), device, rt.get_layout(binary, 0, i)) for i, t in enumerate(inputs)]
+        return rt.submit(device, binary, 0, ins)
+
+    def upd(b):
+        c = b.input([2, 2, 64, 64], "BFloat16"); v = b.input([1, 2, 2, 64], "BFloat16"); i = b.input([1], "Int32")
+        b.output(b.update_cache(c, v, i))
+    out = run(upd, [cache, x, torch.tensor([64], dtype=torch.int32)])
+    with pytest.raises(RuntimeError, match="outside the cache"):
+        rt.wait(out[0])
+    assert torch.equal(rt.to_torch(rt.to_host(out[0], untilize=True)[0]), cache)      # nothing was written
+    rt.wait(out[0])                                                                    # reported once
+
+    table = torch.randn(10, 32)
+
+    def emb(b):
+        i = b.input([4], "Int32"); w = b.input([10, 32], "Float32")
+        b.output(b.embedding(i, w))
+    out = run(emb, [torch.tensor([1, 10, -3, 9], dtype=torch.int32), table])
+    with pytest.raises(RuntimeError, match="outside its table"):
+        rt.wait(out[0])
+    got = rt.to_torch(rt.to_host(out[0], untilize=True)[0])
+    assert torch.equal(got, table[[1, 0, 0, 9]])

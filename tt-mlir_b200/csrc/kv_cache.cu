@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(256)
   }
 }
 
-__device__ int g_cacheBadIndex; // sticky: an update index outside the cache was seen (nothing was written)
+__device__ int g_cacheBadIndex; // an update index outside the cache was seen (nothing was written); cleared when read
 
 // ---- decode attention ------------------------------------------------------------------------
 // D += A(16x16, row) * B(16x8, col), 16-bit operands, f32 accumulators.
@@ -426,6 +426,10 @@ int ttb_update_cache_status(int *bad_index_seen) {
   TTB_CHECK(bad_index_seen != nullptr, "null result");
   TTB_CUDA(cudaDeviceSynchronize());
   TTB_CUDA(cudaMemcpyFromSymbol(bad_index_seen, g_cacheBadIndex, sizeof(int)));
+  if (*bad_index_seen) { // reported once
+    const int zero = 0;
+    TTB_CUDA(cudaMemcpyToSymbol(g_cacheBadIndex, &zero, sizeof(int)));
+  }
   return TTB_OK;
 }
 

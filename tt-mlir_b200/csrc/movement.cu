@@ -155,7 +155,7 @@ template <> __device__ __forceinline__ long long indexValue<__half>(__half v) {
   return static_cast<long long>(__half2float(v));
 }
 
-__device__ int g_embeddingBadIndex; // sticky: set when a kernel saw an index outside its table
+__device__ int g_embeddingBadIndex; // set when a kernel saw an index outside its table; cleared when read
 
 template <typename I, typename U>
 __global__ void __launch_bounds__(256) embeddingKernel(const I *__restrict__ idx, const U *__restrict__ table,
@@ -248,6 +248,10 @@ int ttb_embedding_status(int *bad_index_seen) {
   TTB_CHECK(bad_index_seen != nullptr, "null result");
   TTB_CUDA(cudaDeviceSynchronize());
   TTB_CUDA(cudaMemcpyFromSymbol(bad_index_seen, g_embeddingBadIndex, sizeof(int)));
+  if (*bad_index_seen) { // reported once
+    const int zero = 0;
+    TTB_CUDA(cudaMemcpyToSymbol(g_embeddingBadIndex, &zero, sizeof(int)));
+  }
   return TTB_OK;
 }
 

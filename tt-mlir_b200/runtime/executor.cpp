@@ -1894,6 +1894,7 @@ void Executor::runEmbedding(const fbt::EmbeddingOp *op) {
   TTRT_ASSERT(w->volume() == vocab * dim, "embedding table has leading dimensions other than 1");
   TTRT_ASSERT(out->dtype == w->dtype, "embedding result must have the table's data type");
   size_t rows = idx->volume();
+  dev->ranEmbedding = true;
   TTRT_ASSERT(out->volume() == rows * dim, "embedding result has ", out->volume(), " elements, expected ", rows * dim);
   eachRank([&](size_t i, const RankCtx &r) {
     TTB_CALL(ttb_embedding(idx->shards[i]->ptr, w->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(idx->dtype), ttbDtype(w->dtype),
@@ -2020,6 +2021,7 @@ void Executor::runUpdateCache(const fbt::UpdateCacheOp *op) {
   TTRT_ASSERT(in->shape[0] == 1 && in->shape[1] == cache->shape[1] && in->shape[3] == cache->shape[3],
               "update_cache input must be [1, heads, users, head_dim]");
   TTRT_ASSERT(op->batch_offset() + in->shape[2] <= cache->shape[0], "update_cache input users do not fit the cache");
+  dev->ranUpdateCache = true;
   TTRT_ASSERT(idx->volume() >= 1 && (idx->dtype == DataType::Int32 || idx->dtype == DataType::UInt32),
               "update_cache index must be an Int32 / UInt32 tensor");
   eachRank([&](size_t i, const RankCtx &r) {

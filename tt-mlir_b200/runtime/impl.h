@@ -116,6 +116,7 @@ struct DeviceImpl {
   std::vector<RankCtx> locals;     // coordinates this process owns
   bool multiProcess = false;
   bool open = false;
+  bool ranEmbedding = false, ranUpdateCache = false; // their kernels flag indices outside the table / cache; wait() reports it
   bool symmTried = false;          // the peer workspaces are set up (or found unavailable) once
   std::mutex submitMutex;          // submit is serialised per device
   ~DeviceImpl();

@@ -896,6 +896,16 @@ static void syncDevice(const std::shared_ptr<DeviceImpl> &d) {
     for (void *st : {r.copyIn, r.stream, r.copyOut}) {
       if (st) TTB_CALL(ttb_stream_sync(st));
     }
+    if (d->ranEmbedding) {
+      int bad = 0;
+      TTB_CALL(ttb_embedding_status(&bad));
+      TTRT_ASSERT(bad == 0, "an embedding lookup saw an index outside its table (row 0 was used instead)");
+    }
+    if (d->ranUpdateCache) {
+      int bad = 0;
+      TTB_CALL(ttb_update_cache_status(&bad));
+      TTRT_ASSERT(bad == 0, "an update_cache position was outside the cache (nothing was written)");
+    }
     if (r.symm) {
       int status = 0;
       TTB_CALL(ttb_symm_status(r.symm, &status));

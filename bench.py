@@ -377,6 +377,9 @@ def side_workloads():
         # serving: attention of one decode step, 32 users x 8192 cached tokens (1.07 GB of K and V read once)
         "decode_attention": (graphs.decode_attention_graph, {}, graphs.decode_attention_inputs,
                              2.0 * 32 * 8 * 8192 * 128 * 2 + 2.0 * 32 * 32 * 128 * 2, 4.0 * 32 * 32 * 8192 * 128, 32, "tokens"),
+        # the N = 1 decoder block recorded as a trace (one CUDA graph replay per submit)
+        "decoder_traced": (graphs.decoder_block_traced_binary, dict(CONFIG), lambda: graphs.decoder_block_inputs(**CONFIG),
+                           0.0, graphs.decoder_block_flops(**CONFIG), CONFIG["batch"] * CONFIG["seq"], "tokens"),
         "bottleneck": (graphs.bottleneck_graph, {}, graphs.bottleneck_inputs, 128450560.0, 29.595e9, 64, "images"),
     }
 
@@ -543,7 +546,7 @@ def main():
                     help="for runs under a profiler: exactly --warmup warm-up steps, then --steps steps, nothing else")
     ap.add_argument("--workload", default="decoder",
                     choices=["decoder", "mlp", "mlp_traced", "quant", "quant_int8", "w8_linear", "w8_linear_const_eval",
-                             "bottleneck", "decode_attention", "all_reduce"],
+                             "bottleneck", "decode_attention", "decoder_traced", "all_reduce"],
                     help="decoder (default) is the benchmark; the others report the remaining configurations")
     args = ap.parse_args()
 

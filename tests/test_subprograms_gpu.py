@@ -147,3 +147,30 @@ def test_failed_recording_leaves_the_device_usable(rt, device):
     ins = graphs.mlp_inputs()
     got = _read(rt, rt.submit(device, plain, 0, _to_device_inputs(rt, device, plain, ins)))[0]
     assert_matches(got, oracle_results(graphs.mlp_graph, ins)[0], "after a failed recording")
+
+
+def test_traced_decoder_block_equals_the_plain_program(rt, device):
+    """The decoder block (tensor-core GEMMs with fused epilogues, grouped and SwiGLU launches, rotary
+    embedding through strides, tcgen05 attention) recorded as one CUDA graph: replays with new
+    activations give bit for bit what the plain program gives."""
+    kw = dict(seq=256, hidden=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024)
+    traced = rt.Binary.load_from_memory(graphs.decoder_block_traced_binary(**kw))
+    plain = rt.Binary.load_from_memory(graphs.build_binary(graphs.decoder_block_graph, **kw))
+    base = graphs.decoder_block_inputs(**kw)
+    t_in = _to_device_inputs(rt, device, traced, base)
+    p_in = _to_device_inputs(rt, device, plain, base)
+    rt.clear_stats()
+    for step in range(3):
+        x = graphs.decoder_block_inputs(seed=50 + step, **kw)[0]
+        hx = rt.to_layout(rt.from_torch(x), device, rt.get_layout(traced, 0, 0))
+        dx = rt.to_layout(rt.from_torch(x), device, rt.get_layout(plain, 0, 0))
+        before = rt.launch_count()
+        got = _read(rt, rt.submit(device, traced, 0, [hx] + t_in[1:]))[0]
+        launches = rt.launch_count() - before
+        ref = _read(rt, rt.submit(device, plain, 0, [dx] + p_in[1:]))[0]
+        assert torch.equal(got, ref), f"step {step}: replay and plain program differ"
+        if step:
+            assert launches == 0
+    want = oracle_results(graphs.decoder_block_graph, [x] + base[1:], **kw)[0]
+    assert_matches(got, want, "traced decoder block", (0.999, 2e-2, 2.0 ** -6))
+    assert rt.get_stat("CapturedTrace") == 1 and rt.get_stat("ExecutedTrace") == 2

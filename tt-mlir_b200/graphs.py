@@ -337,6 +337,54 @@ def decode_attention_inputs(batch=32, heads=32, kv_heads=8, seq=8192, head_dim=1
             torch.full((batch,), at, dtype=torch.int32)]
 
 
+class _TracedBody:
+    """Stands between a `*_graph(b, ...)` function and the program that holds the traced function:
+    `input()` hands out the traced function's arguments in order, `output()` collects the results,
+    every op goes to the program."""
+
+    def __init__(self, program, args):
+        self._p, self._args, self.results = program, list(args), []
+
+    def input(self, shape, dtype, on_device=True):
+        v = self._args.pop(0)
+        assert list(v.shape) == list(shape) and v.dtype == dtype, "traced body and main program disagree on an input"
+        return v
+
+    def output(self, *values):
+        self.results.extend(values)
+
+    def __getattr__(self, name):
+        return getattr(self._p, name)
+
+
+def traced_binary(graph_fn, host_inputs=(0,), name="main", **kw) -> bytes:
+    """`graph_fn` the way the compiler emits it with `enable-trace=true` on one device: program 0 has
+    the graph's inputs (those listed in `host_inputs` on host, the rest on device, i.e. parameters)
+    and one CaptureOrExecuteTraceOp; the ops live in a private traced function
+    (ttnn_builder.BinaryBuilder.hoist_trace)."""
+    from .ttnn_builder import BinaryBuilder
+    # a first pass over the graph only to learn its inputs
+    probe = BinaryBuilder().program("probe")
+    graph_fn(probe, **kw)
+    bb = BinaryBuilder()
+    main = bb.program(name)
+    ins = [main.input(v.shape, v.dtype, on_device=(i not in host_inputs)) for i, v in enumerate(probe.inputs)]
+    order = sorted(range(len(ins)), key=lambda i: 0 if ins[i].on_device else 1)   # hoist_trace's argument order
+
+    def body(p, args):
+        by_index = {i: a for i, a in zip(order, args)}
+        tb = _TracedBody(p, [by_index[i] for i in range(len(ins))])
+        graph_fn(tb, **kw)
+        return tb.results
+    main.output(*bb.hoist_trace(main, name, [ins[i] for i in order], body))
+    return bb.finish()
+
+
+def decoder_block_traced_binary(**kw) -> bytes:
+    """The single-device decoder block as a trace: activations staged from host, weights and rotary tables resident."""
+    return traced_binary(decoder_block_graph, host_inputs=(0,), name="decoder_block", **kw)
+
+
 def build_binary(graph_fn, mesh_shape=(1, 1), name="main", **kw) -> bytes:
     """Emits a one-program .ttnn binary for `graph_fn(b, **kw)`."""
     from .ttnn_builder import BinaryBuilder

@@ -138,6 +138,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   __syncthreads();
   tcFenceAfter();
   const uint32_t tmemBase = tmemBaseSlot;
+  pdlLaunchDependents(); // the prologue above touched no global memory
+  pdlWait();
   volatile int *abortP = &abortFlag;
 
   if (warp == 0) {
@@ -451,6 +453,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   __syncthreads();
   tcFenceAfter();
   const uint32_t tmemBase = tmemBaseSlot;
+  pdlLaunchDependents(); // the prologue above touched no global memory
+  pdlWait();
   volatile int *abortP = &abortFlag;
 
   if (warp == 0) {
@@ -696,7 +700,7 @@ static int launchPair(const CUtensorMap &mq, const CUtensorMap &mk, const CUtens
     TTB_CUDA(cudaFuncSetAttribute(sdpaTcgen05PairKernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, AP_SMEM));
     attrSet[dev] = true;
   }
-  sdpaTcgen05PairKernel<T><<<grid, AT_THREADS, AP_SMEM, st>>>(mq, mk, mv, static_cast<T *>(out), p);
+  TTB_CUDA(launchPdl(sdpaTcgen05PairKernel<T>, dim3(grid), dim3(AT_THREADS), AP_SMEM, st, mq, mk, mv, static_cast<T *>(out), p));
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;
@@ -750,7 +754,7 @@ static int launchAt(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensor
     TTB_CUDA(cudaFuncSetAttribute(sdpaTcgen05Kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
     attrSet[dev] = true;
   }
-  sdpaTcgen05Kernel<T><<<grid, AT_THREADS, AT_SMEM, st>>>(mq, mk, mv, static_cast<T *>(out), p);
+  TTB_CUDA(launchPdl(sdpaTcgen05Kernel<T>, dim3(grid), dim3(AT_THREADS), AT_SMEM, st, mq, mk, mv, static_cast<T *>(out), p));
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;

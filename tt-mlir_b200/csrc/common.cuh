@@ -8,6 +8,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <string>
+#include <utility>
 
 #include "../../include/ttb_kernels.h"
 
@@ -72,6 +73,33 @@ struct ProfScope {
   int slot;
   cudaStream_t stream;
 };
+
+// ---- programmatic dependent launch ---------------------------------------------------------
+// A kernel launched through launchPdl may start (be scheduled, run its prologue) while the kernel
+// before it on the stream is still finishing; it calls pdlWait() before it touches global memory,
+// which returns once that kernel has completed and its writes are visible.  A kernel calls
+// pdlLaunchDependents() to let its successor be scheduled early.  Every kernel launched this way
+// MUST execute pdlWait(): its own successor relies on "this kernel is done" implying "everything
+// before it is done".  Without the launch attribute both calls do nothing.  TTB_DISABLE_PDL=1
+// launches everything the ordinary way.
+__device__ __forceinline__ void pdlWait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdlLaunchDependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+bool pdlEnabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launchPdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdlEnabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 // Grid for a grid-stride kernel: enough blocks for `items`, capped at a few waves of the GPU.
 inline int gridFor(size_t items, int block, int blocksPerSm = 16) {

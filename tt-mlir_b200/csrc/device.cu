@@ -1,6 +1,7 @@
 // Device, stream, memory and event entry points of the C ABI, plus error bookkeeping.
 #include "common.cuh"
 
+#include <cstdlib>
 #include <cstring>
 
 #include <atomic>
@@ -35,6 +36,14 @@ int smCount() {
     cached[dev] = n;
   }
   return cached[dev];
+}
+
+bool pdlEnabled() {
+  static const bool on = [] {
+    const char *e = std::getenv("TTB_DISABLE_PDL");
+    return !(e && e[0] == '1');
+  }();
+  return on;
 }
 
 void countLaunch(uint64_t n) { g_launchCount.fetch_add(n, std::memory_order_relaxed); }

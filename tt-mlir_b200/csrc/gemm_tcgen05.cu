@@ -178,6 +178,11 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
   __syncthreads();
   tcFenceAfter();
   const uint32_t tmemBase = tmemBaseSlot;
+  // Everything above touched only this CTA's shared memory, TMEM and the kernel parameters, so it
+  // may run while the kernel before this one on the stream is still finishing; from here on
+  // global memory is read and written.
+  pdlLaunchDependents();
+  pdlWait();
 
   if (warp == 0 && p.convX && !p.cTw) {
     // ---------------- convolution producer: the whole warp gathers A, lane 0 also loads B ----------------
@@ -709,9 +714,9 @@ static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensor
   }
   int64_t tiles = (p.cTw ? p.cTilesM : (p.M + TC_BM - 1) / TC_BM) * p.segCum[2];
   int grid = static_cast<int>(tiles < smCount() ? tiles : smCount());
-  gemmTcgen05Kernel<BN, TC, PLAIN><<<grid, PLAIN ? TC_THREADS : TC_THREADS_EPI8, Cfg::kSmem, st>>>(
-      ma, mb, mc, me, more ? more[0] : mb, more ? more[1] : mc, more ? more[2] : mb, more ? more[3] : mc,
-      push ? *push : PushMaps{{mc, mc, mc, mc, mc, mc, mc, mc}}, static_cast<TC *>(c), p);
+  TTB_CUDA(launchPdl(gemmTcgen05Kernel<BN, TC, PLAIN>, dim3(grid), dim3(PLAIN ? TC_THREADS : TC_THREADS_EPI8), Cfg::kSmem, st, ma, mb,
+                     mc, me, more ? more[0] : mb, more ? more[1] : mc, more ? more[2] : mb, more ? more[3] : mc,
+                     push ? *push : PushMaps{{mc, mc, mc, mc, mc, mc, mc, mc}}, static_cast<TC *>(c), p));
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;

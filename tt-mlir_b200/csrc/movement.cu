@@ -113,6 +113,8 @@ __global__ void __launch_bounds__(256) ropeKernel(const T *__restrict__ x, const
                                                   const T *__restrict__ sn, T *__restrict__ out, size_t batch,
                                                   size_t heads, size_t seq, size_t dim, int64_t sb, int64_t sh, int64_t ss) {
   constexpr int V = 16 / sizeof(T);
+  pdlLaunchDependents();
+  pdlWait();
   size_t half = dim / 2;
   size_t perRow = half / V;
   size_t total = batch * heads * seq * perRow;
@@ -324,9 +326,9 @@ int ttb_rotary_embedding_strided(const void *x, const void *cos, const void *sin
   if (total == 0) return TTB_OK;
   ProfScope prof("rotary_embedding", 0, 2.0 * double(batch * heads) * seq * head_dim * es, asStream(stream));
   TTB_DISPATCH_FLOAT(dtype, T, {
-    ropeKernel<T><<<gridFor(total, 256), 256, 0, asStream(stream)>>>(
-        static_cast<const T *>(x), static_cast<const T *>(cos), static_cast<const T *>(sin), static_cast<T *>(out), batch,
-        heads, seq, head_dim, x_strides3[0], x_strides3[1], x_strides3[2]);
+    TTB_CUDA(launchPdl(ropeKernel<T>, dim3(gridFor(total, 256)), dim3(256), 0, asStream(stream), static_cast<const T *>(x),
+                       static_cast<const T *>(cos), static_cast<const T *>(sin), static_cast<T *>(out), batch, heads, seq,
+                       head_dim, x_strides3[0], x_strides3[1], x_strides3[2]));
   });
   countLaunch();
   TTB_LAUNCH_CHECK();

@@ -99,6 +99,8 @@ __global__ void __launch_bounds__(256)
                   const T *__restrict__ bias, T *__restrict__ sumOut, T *__restrict__ out, size_t cols, float eps) {
   constexpr int V = 16;
   __shared__ float scratch[33];
+  pdlLaunchDependents();
+  pdlWait();
   size_t row = blockIdx.x;
   const T *x = a + row * cols;
   Pack<T, V> r[P];
@@ -151,6 +153,8 @@ __global__ void __launch_bounds__(256)
                          const T *__restrict__ bias, T *__restrict__ sumOut, T *__restrict__ out, size_t cols,
                          float eps) {
   __shared__ float scratch[33];
+  pdlLaunchDependents();
+  pdlWait();
   size_t row = blockIdx.x;
   float ss = 0.0f;
   for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
@@ -183,11 +187,11 @@ int launchRms(const void *a, const void *b, const void *w, const void *bias, voi
   int grid = static_cast<int>(rows);
   ProfScope prof(RES ? "add_rms_norm" : "rms_norm", 0, double(rows) * cols * sizeof(T) * ((RES ? 3 : 2) + (sumOut ? 1 : 0)), st);
   if (al && cols % 16 == 0 && cols <= 256 * 16) {
-    rmsNormKernel<T, 1, RES><<<grid, 256, 0, st>>>(A, B, W, Bi, S, O, cols, eps);
+    TTB_CUDA(launchPdl(rmsNormKernel<T, 1, RES>, dim3(grid), dim3(256), 0, st, A, B, W, Bi, S, O, cols, eps));
   } else if (al && cols % 16 == 0 && cols <= 256 * 16 * 2) {
-    rmsNormKernel<T, 2, RES><<<grid, 256, 0, st>>>(A, B, W, Bi, S, O, cols, eps);
+    TTB_CUDA(launchPdl(rmsNormKernel<T, 2, RES>, dim3(grid), dim3(256), 0, st, A, B, W, Bi, S, O, cols, eps));
   } else {
-    rmsNormGenericKernel<T, RES><<<grid, 256, 0, st>>>(A, B, W, Bi, S, O, cols, eps);
+    TTB_CUDA(launchPdl(rmsNormGenericKernel<T, RES>, dim3(grid), dim3(256), 0, st, A, B, W, Bi, S, O, cols, eps));
   }
   countLaunch();
   TTB_LAUNCH_CHECK();

@@ -24,6 +24,8 @@ __global__ void __launch_bounds__(256)
   __shared__ float sa[BK][BM + 1];
   __shared__ float sb[BK][BN + 1];
   __shared__ bool lastBlock;
+  pdlLaunchDependents();
+  pdlWait();
   const int split = splitK > 1 ? static_cast<int>(blockIdx.z) : 0;
   int64_t batch = splitK > 1 ? 0 : blockIdx.z;
   const T *A = a + batch * aBatch;
@@ -168,9 +170,9 @@ static int launchSimt(const void *a, const void *b, const void *bias, int biasDt
   dim3 grid(static_cast<unsigned>(tilesN), static_cast<unsigned>(tilesM), static_cast<unsigned>(splitK > 1 ? splitK : batch));
   {
     ProfScope prof("gemm_simt", 2.0 * double(batch) * m * n * k, double(batch) * (double(m) * k + double(n) * k) * sizeof(T) + double(batch) * m * n * sizeof(TC), st);
-    gemmSimtKernel<T, TC><<<grid, 256, 0, st>>>(static_cast<const T *>(a), static_cast<const T *>(b), bias, biasDt,
-                                                static_cast<TC *>(c), m, n, k, asM, asK, bsK, bsN, aBatch, bBatch, act,
-                                                roundSteps, splitK, kPer, partials, arrivals);
+    TTB_CUDA(launchPdl(gemmSimtKernel<T, TC>, grid, dim3(256), 0, st, static_cast<const T *>(a), static_cast<const T *>(b), bias,
+                       biasDt, static_cast<TC *>(c), m, n, k, asM, asK, bsK, bsN, aBatch, bBatch, act, roundSteps, splitK, kPer,
+                       partials, arrivals));
   }
   if (scratch) {
     int rc = ttb_free(scratch, st); // stream-ordered: released once the kernel has run

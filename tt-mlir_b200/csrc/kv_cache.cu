@@ -115,6 +115,8 @@ __global__ void __launch_bounds__(DEC_THREADS, D <= 128 ? 4 : 2)
   __shared__ float sc[G][DEC_CHUNK];
   __shared__ float so[2][G][D]; // exchange slots of the cross-warp sum
   __shared__ float sm[G], sl[G];
+  pdlLaunchDependents();
+  pdlWait();
   const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int last = p.S - 1; // last key a query of this user may see
@@ -305,6 +307,8 @@ __global__ void __launch_bounds__(256) sdpaDecodeMergeKernel(const float *__rest
                                                              const float *__restrict__ po, T *__restrict__ out, int pairs,
                                                              int chunks) {
   constexpr int DPL = D / 32;
+  pdlLaunchDependents();
+  pdlWait();
   const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (pair >= pairs) return;
   const float *m = pm + static_cast<size_t>(pair) * chunks, *l = pl + static_cast<size_t>(pair) * chunks;
@@ -330,12 +334,12 @@ template <typename T, int G, int D>
 static int launchDecode(const void *q, const void *k, const void *v, const void *curPos, const void *mask, void *out,
                         float *pm, float *pl, float *po, const DecodeParams &p, cudaStream_t st) {
   dim3 grid(static_cast<unsigned>(p.chunks), static_cast<unsigned>(p.Hkv), static_cast<unsigned>(p.B));
-  sdpaDecodeChunkKernel<T, G, D><<<grid, DEC_THREADS, 0, st>>>(static_cast<const T *>(q), static_cast<const T *>(k),
-                                                               static_cast<const T *>(v), static_cast<const int32_t *>(curPos),
-                                                               static_cast<const T *>(mask), pm, pl, po, p);
-  TTB_LAUNCH_CHECK();
+  TTB_CUDA(launchPdl(sdpaDecodeChunkKernel<T, G, D>, grid, dim3(DEC_THREADS), 0, st, static_cast<const T *>(q),
+                     static_cast<const T *>(k), static_cast<const T *>(v), static_cast<const int32_t *>(curPos),
+                     static_cast<const T *>(mask), pm, pl, po, p));
   const int pairs = p.B * p.H;
-  sdpaDecodeMergeKernel<T, D><<<(pairs + 7) / 8, 256, 0, st>>>(pm, pl, po, static_cast<T *>(out), pairs, p.chunks);
+  TTB_CUDA(launchPdl(sdpaDecodeMergeKernel<T, D>, dim3((pairs + 7) / 8), dim3(256), 0, st, static_cast<const float *>(pm),
+                     static_cast<const float *>(pl), static_cast<const float *>(po), static_cast<T *>(out), pairs, p.chunks));
   countLaunch(2);
   TTB_LAUNCH_CHECK();
   return TTB_OK;

@@ -59,6 +59,8 @@ __device__ __forceinline__ float blockSum(float v, float *scratch /* 33 floats *
 template <typename T>
 __global__ void __launch_bounds__(256) softmaxRowKernel(const T *__restrict__ in, T *__restrict__ out, size_t rows,
                                                         size_t len) {
+  pdlLaunchDependents();
+  pdlWait();
   size_t row = static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -360,7 +362,7 @@ int ttb_softmax(const void *in, void *out, int dtype, size_t outer, size_t len, 
   TTB_DISPATCH_FLOAT(dtype, T, {
     if (inner == 1) {
       int grid = static_cast<int>((outer + 7) / 8);
-      softmaxRowKernel<T><<<grid, 256, 0, st>>>(static_cast<const T *>(in), static_cast<T *>(out), outer, len);
+      TTB_CUDA(launchPdl(softmaxRowKernel<T>, dim3(grid), dim3(256), 0, st, static_cast<const T *>(in), static_cast<T *>(out), outer, len));
     } else {
       softmaxColKernel<T><<<gridFor(outer * inner, 256), 256, 0, st>>>(static_cast<const T *>(in),
                                                                        static_cast<T *>(out), outer, len, inner);

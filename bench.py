@@ -410,6 +410,23 @@ def run_side(args):
     host_us = (time.perf_counter() - t_host) / args.steps * 1e6
     ms = ev.stop_ms() / args.steps
     launches = rt.launch_count() - launches0
+    # The same pass with cold caches: several of these workloads are smaller than the 126 MB L2, so the
+    # loop above re-reads inputs the previous pass left there.  Here a 256 MB buffer is overwritten
+    # before every pass (outside the timed region) and every pass is timed on its own.
+    flushed_ms = None
+    if not args.profile:
+        scratch = ctypes.c_void_p()
+        flush_bytes = 256 << 20
+        assert rt.lib.ttb_malloc(ctypes.byref(scratch), ctypes.c_size_t(flush_bytes), ctypes.c_void_p(stream)) == 0
+        total = 0.0
+        reps = min(args.steps, 30)
+        for _ in range(reps):
+            assert rt.lib.ttb_memset(scratch, 0, ctypes.c_size_t(flush_bytes), ctypes.c_void_p(stream)) == 0
+            ev.start()
+            out = rt.submit(device, binary, 0, dev_in)
+            total += ev.stop_ms()
+        flushed_ms = total / reps
+        assert rt.lib.ttb_free(scratch, ctypes.c_void_p(stream)) == 0
     prof = []
     if not args.profile:
         rt.lib.ttb_prof_enable(1)
@@ -432,6 +449,7 @@ def run_side(args):
             "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "dtype": "f32" if args.workload.startswith("mlp") else "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "host_enqueue_us_per_step": host_us}, "gpu_launches": launches,
+            "ms_per_step_l2_flushed": flushed_ms,
             "graph_hbm_gbs": abytes / (ms * 1e-3) / 1e9, "graph_hbm_frac": abytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
             "graph_tflops": aflops / (ms * 1e-3) / 1e12, "graph_tensor_frac": aflops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
             "per_op": prof}

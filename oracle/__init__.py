@@ -15,14 +15,15 @@ What it restates, and from where (paths inside tenstorrent/tt-mlir):
     attention (:8398-8500), mesh_shard and the collectives (:4189-4235, 5658-5794), and the
     rotary-embedding definition (lib/Dialect/TTNN/Transforms/Fusing/RoPEFusingPattern.cpp:49-51).
 
-Pinning: the reference ships no stored vectors for this path.  tests/golden/generate.py
-imports the reference's own ttir_cpu.py (in the development container, where the reference
-tree is mounted) and records its outputs on seeded inputs; tests/test_oracle_golden.py checks
-this package against those fixtures.  The goldens for quantization / rms_norm / attention are
-single torch calls in the reference and are recorded the same way.  The int8-storage
-quantization variant has no runnable reference test (the reference skips it), so for that
-storage width parity is pinned only through the torch golden.
-The goldens of fill_cache, update_cache and decode attention (mapping.py:3582-3670, 2417-2482) need
-the compiler's Python bindings and cannot be imported: they are restated by reading (parity unpinned
-for those three ops).
+Pinning: the reference ships no stored vectors for this path.  tests/golden/generate.py imports,
+unmodified and in the development container where the reference tree is mounted, the reference's
+ttir_cpu.py and its tools/golden/mapping.py (the latter with stand-in classes for the compiler's
+Python bindings, tests/golden/ttmlir_standin.py) and records what their functions return on seeded
+inputs; tests/test_oracle_golden.py checks this package against those fixtures bit for bit.  That
+covers every op restated here, the kv-cache ops, decode and paged attention, gather / scatter /
+sort / top-k and the collectives included.  Not pinned by a reference function, because the
+reference has none: per-axis quantization (pinned on torch.quantize_per_channel instead) and the
+rotary embedding (one formula in RoPEFusingPattern.cpp:49-51, restated).  The int8-storage
+quantization variant has no runnable reference test (the reference skips it), so for that storage
+width parity is pinned only through the torch golden.
 """

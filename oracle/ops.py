@@ -421,3 +421,88 @@ def reduce_scatter(shards, dim, reduce_type=0):
 def mesh_partition(shards, dim):
     n = len(shards)
     return [torch.chunk(s, n, dim=dim)[i].contiguous() for i, s in enumerate(shards)]
+
+
+# ---- indexing ops (mapping.py:5384-5437, 5624-5640, 5927-5958) ------------------------------------------
+def gather(x, index, dim):  # ttir_gather_golden: torch.gather with 64-bit indices
+    return torch.gather(x, dim, index.to(torch.int64))
+
+
+def scatter(x, index, src, dim, reduce_type=None):
+    """ttir_scatter_golden: plain scatter (reduce type Invalid) or scatter_reduce with sum / prod / amax /
+    amin, the input's own values included."""
+    idx = index.to(torch.int64)
+    if reduce_type in (None, "Invalid"):
+        return torch.scatter(x, dim, idx, src)
+    return torch.scatter_reduce(x, dim, idx, src, reduce={"Sum": "sum", "Prod": "prod", "Max": "amax", "Min": "amin"}[reduce_type])
+
+
+def sort(x, dim=-1, descending=False, stable=True):  # ttir_sort_golden; indices narrowed to Int32 (the device width)
+    values, indices = torch.sort(x, dim=dim, descending=descending, stable=stable)
+    return values, indices.to(torch.int32)
+
+
+def topk(x, k, dim=-1, largest=True):  # ttir_topk_golden: always sorted; ties keep torch.topk's order
+    values, indices = torch.topk(x, k=k, dim=dim, largest=largest, sorted=True)
+    return values, indices.to(torch.int32)
+
+
+# ---- paged kv-cache (mapping.py:8745-8844, 8926-9007) ---------------------------------------------------
+def paged_update_cache(cache, x, update_index, page_table=None):
+    """ttir_paged_update_cache_golden: cache [blocks, heads, block_size, d], x [batch, seq, heads, d];
+    token s of user b lands at position update_index[b] + s, in the physical block the page table
+    names (indices clamped into range)."""
+    out = cache.clone()
+    blocks, _, block_size, _ = cache.shape
+    for b in range(x.shape[0]):
+        for s in range(x.shape[1]):
+            pos = int(update_index[b].item()) + s
+            blk, off = pos // block_size, pos % block_size
+            if page_table is not None:
+                blk = int(page_table[b, min(max(blk, 0), page_table.shape[1] - 1)].item())
+            blk = min(max(blk, 0), blocks - 1)
+            out[blk, :, off, :] = x[b, s]
+    return out
+
+
+def paged_fill_cache(cache, x, page_table, batch_idx=None):
+    """ttir_paged_fill_cache_golden: x [batch, heads, seq, d]; user b uses page-table row batch_idx[b]."""
+    out = cache.clone()
+    blocks, _, block_size, _ = cache.shape
+    for b in range(x.shape[0]):
+        row = int(batch_idx.reshape(-1)[b].item()) if batch_idx is not None else b
+        row = min(max(row, 0), page_table.shape[0] - 1)
+        for pos in range(x.shape[2]):
+            col = min(pos // block_size, page_table.shape[1] - 1)
+            blk = min(max(int(page_table[row, col].item()), 0), blocks - 1)
+            out[blk, :, pos % block_size, :] = x[b, :, pos, :]
+    return out
+
+
+def paged_sdpa_decode(q, k_cache, v_cache, page_table, cur_pos=None, is_causal=True, scale=None, mask=None):
+    """ttir_paged_sdpa_decode_golden: q [B, 1, H, D]; caches [blocks, Hkv, block_size, D]; keys after
+    cur_pos[b] get the most negative f32 (pre-scaled, as the golden has it) and the softmax runs in f32."""
+    b, sq, h, d = q.shape
+    blocks, hkv, block_size, _ = k_cache.shape
+    per_user = page_table.shape[-1]
+    seq = per_user * block_size
+    flat = page_table.long().reshape(-1).clamp(0, blocks - 1)
+
+    def unpage(c):
+        t = c[flat].reshape(b, per_user, hkv, block_size, c.shape[-1])
+        return t.transpose(1, 2).reshape(b, hkv, seq, c.shape[-1]).float()
+    kk, vv = unpage(k_cache), unpage(v_cache)
+    if h // hkv > 1:
+        kk = kk.repeat_interleave(h // hkv, dim=1)
+        vv = vv.repeat_interleave(h // hkv, dim=1)
+    m = None
+    if mask is not None:
+        m = mask.float().permute(0, 2, 1, 3)
+    elif is_causal and cur_pos is not None:
+        m = torch.zeros((b, h, sq, seq), dtype=torch.float32)
+        for i in range(b):
+            m[i, :, :, int(cur_pos[i].item()) + 1:] = torch.finfo(torch.float32).min
+    if m is not None:
+        m = m * (scale if scale is not None else d ** -0.5)
+    o = F.scaled_dot_product_attention(q.float().permute(0, 2, 1, 3), kk, vv, attn_mask=m, scale=scale, is_causal=False)
+    return o.permute(0, 2, 1, 3).to(q.dtype)

@@ -5,12 +5,20 @@ TT_MLIR_ROOT environment variable):
 
     python tests/golden/generate.py /path/to/tt-mlir
 
-It imports tools/tt-alchemist/templates/python/local/ttir_cpu.py -- the pure-torch CPU
-implementation of the TTIR ops that the reference's CPU-hoist path targets -- and records its
-outputs on small seeded inputs.  For ops the reference defines only through a torch golden in
-tools/golden/mapping.py (that file needs the compiler's Python bindings and cannot be
-imported), the golden's body is the single torch call cited beside each entry below, and that
-call is recorded.  The fixture travels with the repo; the reference tree does not.
+It imports two files of the reference, unmodified, and records what their functions return on
+small seeded inputs:
+
+* tools/tt-alchemist/templates/python/local/ttir_cpu.py -- the pure-torch CPU implementation of
+  the TTIR ops that the reference's CPU-hoist path targets;
+* tools/golden/mapping.py -- the torch goldens of every op, for the ops that have no CPU lowering
+  (quantization, rms_norm, attention, mesh_shard and the collectives, kv-cache ops, decode and
+  paged attention, gather / scatter / sort / top-k).  That file imports the compiler's Python
+  bindings; ttmlir_standin.py supplies attribute and type classes in their place, so the golden
+  bodies that run are the reference's own text.
+
+Nothing in this script restates a golden.  The fixture travels with the repo; the reference tree
+does not.  Two things have no golden to call and are recorded from torch directly, marked below:
+per-axis quantization (torch.quantize_per_channel) and nothing else.
 bf16 tensors are stored as their uint16 bit patterns.
 """
 
@@ -20,6 +28,9 @@ import sys
 
 import numpy as np
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import ttmlir_standin as standin  # noqa: E402
 
 
 def load_ttir_cpu(root):
@@ -42,6 +53,14 @@ def main():
     if not root:
         raise SystemExit("usage: generate.py /path/to/tt-mlir")
     cpu = load_ttir_cpu(root)
+    ref = standin.load_mapping(root)      # tools/golden/mapping.py, imported unmodified
+
+    def gmt(t, mesh=(1, 1)):
+        """A single-device value in the wrapper the goldens take."""
+        return ref.GoldenMapTensor({0: t}, mesh)
+
+    def one(v):
+        return v.shard_at(0) if isinstance(v, ref.GoldenMapTensor) else v
     g = torch.Generator().manual_seed(1234)
     out = {}
 
@@ -131,46 +150,46 @@ def main():
     store(out, "cast/to_bf16", cpu.typecast(tc, torch.bfloat16))
     store(out, "cast/to_i32", cpu.typecast(tc, torch.int32))
 
-    # --- quantization goldens: torch.quantize_per_tensor(...).int_repr(), torch.dequantize,
-    #     requantize = quantize(dequantize(q))  (tools/golden/mapping.py:2534-2582)
+    # --- quantization: quantize_golden / requantize_golden (tools/golden/mapping.py:2534-2582) and the
+    #     registered golden of ttir.dequantize (torch.dequantize, mapping.py:9166), called as imported
+    from ttmlir.dialects import ttir as ttir_ops   # the stand-in's op classes are the registry's keys
+    dequantize_golden = ref.GOLDEN_MAPPINGS[ttir_ops.DequantizeOp]
     qx = (torch.randn(64, 48, generator=g)).to(torch.bfloat16)
     ties = torch.tensor([0.25, 0.75, 1.25, 3.0, -3.0, 0.01, -0.01, 0.03, -0.05, 2.55, -2.57, 100.0], dtype=torch.bfloat16)
     qx.view(-1)[: ties.numel()] = ties
     store(out, "quant/x", qx)
     for tag, scale, zp in [("s002_z0", 0.02, 0), ("s0037_z3", 0.037, 3)]:
-        q8 = torch.quantize_per_tensor(qx.float(), scale, zp, torch.qint8)
-        store(out, f"quant/{tag}/q_i8", q8.int_repr())
-        q32 = torch.quantize_per_tensor(qx.float(), scale, zp, torch.qint32)
-        store(out, f"quant/{tag}/q_i32", q32.int_repr())
-        store(out, f"quant/{tag}/deq", torch.dequantize(q8))
-        rq = torch.quantize_per_tensor(torch.dequantize(q8), scale * 2, zp + 1, torch.qint8)
+        store(out, f"quant/{tag}/q_i8", ref.quantize_golden(qx.float(), scale, zp, torch.qint8))
+        store(out, f"quant/{tag}/q_i32", ref.quantize_golden(qx.float(), scale, zp, torch.qint32))
+        q8 = torch.quantize_per_tensor(qx.float(), scale, zp, torch.qint8)   # the quantized value the next goldens take
+        store(out, f"quant/{tag}/deq", dequantize_golden(q8))
+        rq = ref.requantize_golden(q8, scale * 2, zp + 1, torch.qint8)
         store(out, f"quant/{tag}/requant_i8", rq.int_repr())
-        store(out, f"quant/{tag}/requant_deq", torch.dequantize(rq))
+        store(out, f"quant/{tag}/requant_deq", dequantize_golden(rq))
+    # per-axis quantization has no golden in mapping.py (only the formula in TTIROps.td:6010-6013);
+    # torch's per-channel quantizer is recorded as its stand-in
     ch_scale = torch.rand(64, generator=g) * 0.05 + 0.01
     store(out, "quant/ch_scale", ch_scale)
     qc = torch.quantize_per_channel(qx.float(), ch_scale.double(), torch.zeros(64, dtype=torch.int64), 0, torch.qint8)
     store(out, "quant/per_channel_q", qc.int_repr())
     store(out, "quant/per_channel_deq", torch.dequantize(qc))
 
-    # --- rms_norm golden: torch.nn.functional.rms_norm on float input (mapping.py:1221-1290)
+    # --- rms_norm: ttir_rms_norm_golden (mapping.py:1265-1288)
     nx = rnd(5, 64).to(torch.bfloat16)
     nw = (1 + rnd(64) * 0.1).to(torch.bfloat16)
     store(out, "rms/x", nx)
     store(out, "rms/w", nw)
-    store(out, "rms/out", torch.nn.functional.rms_norm(nx.float(), (64,), weight=nw, eps=1e-5).to(torch.bfloat16))
+    store(out, "rms/out", one(ref.ttir_rms_norm_golden(gmt(nx), gmt(nw), None, standin.ArrayAttr([64]), standin.FloatAttr(1e-5),
+                                                       standin.BF16Type())))
 
-    # --- scaled dot product attention golden body (mapping.py:8398-8500): GQA repeat, scale,
-    #     causal -inf mask above the diagonal, f32 softmax, f32 P.V, cast
+    # --- scaled dot product attention: ttir_sdpa_golden (mapping.py:8398-8500), grouped-query heads
     aq, ak, av = rnd(1, 4, 10, 16), rnd(1, 2, 10, 16), rnd(1, 2, 10, 16)
     store(out, "sdpa/q", aq)
     store(out, "sdpa/k", ak)
     store(out, "sdpa/v", av)
-    kk = torch.repeat_interleave(ak, 2, dim=1)
-    vv = torch.repeat_interleave(av, 2, dim=1)
-    qk = torch.matmul(aq, kk.transpose(-2, -1)) * (1.0 / 16 ** 0.5)
-    causal = qk + torch.triu(torch.full((10, 10), float("-inf")), diagonal=1)
-    store(out, "sdpa/causal", torch.matmul(torch.softmax(causal, dim=-1), vv))
-    store(out, "sdpa/full", torch.matmul(torch.softmax(qk, dim=-1), vv))
+    for name, causal in (("causal", True), ("full", False)):
+        store(out, f"sdpa/{name}", one(ref.ttir_sdpa_golden(gmt(aq), gmt(ak), gmt(av), None, standin.BoolAttr(causal), None,
+                                                            standin.F32Type())))
 
     # --- layer_norm, argmax, cumsum, embedding, pad (ttir_cpu.py: layer_norm, argmax, cumsum, embedding, pad), f32
     lx, lw, lb = rnd(6, 4, 48), 1 + rnd(48) * 0.1, rnd(48) * 0.1
@@ -227,6 +246,148 @@ def main():
     store(out, "pool/avg_bigpad", cpu.avg_pool2d(flat, 2, 9, 11, 8, [2, 2], [2, 2], [2, 2]))
     store(out, "pool/avg_bigpad_nopad", cpu.avg_pool2d(flat, 2, 9, 11, 8, [2, 2], [2, 2], [2, 2], count_include_pad=False))
     store(out, "pool/global", cpu.global_avg_pool2d(pool_x))
+
+    # ===== goldens of tools/golden/mapping.py for ops with no CPU-hoist lowering, called as imported =====
+    S = standin
+
+    # --- more attention cases: additive mask, explicit scale, bf16 result (ttir_sdpa_golden)
+    bq, bk, bv = rnd(2, 8, 24, 32).to(torch.bfloat16), rnd(2, 2, 40, 32).to(torch.bfloat16), rnd(2, 2, 40, 32).to(torch.bfloat16)
+    bm = rnd(2, 1, 24, 40)
+    for n, t in (("q", bq), ("k", bk), ("v", bv), ("mask", bm)):
+        store(out, f"map/sdpa2/{n}", t)
+    store(out, "map/sdpa2/masked", one(ref.ttir_sdpa_golden(gmt(bq), gmt(bk), gmt(bv), gmt(bm), S.BoolAttr(False),
+                                                           S.FloatAttr(0.2), S.BF16Type())))
+    store(out, "map/sdpa2/full", one(ref.ttir_sdpa_golden(gmt(bq), gmt(bk), gmt(bv), None, S.BoolAttr(False), None, S.BF16Type())))
+    store(out, "map/sdpa2/causal_sq", one(ref.ttir_sdpa_golden(gmt(bq), gmt(bk[:, :, :24]), gmt(bv[:, :, :24]), None,
+                                                              S.BoolAttr(True), None, S.BF16Type())))
+
+    # --- rms_norm with a bias, f32 and bf16 (ttir_rms_norm_golden)
+    rx, rw, rb = rnd(3, 7, 96), 1 + rnd(96) * 0.1, rnd(96) * 0.1
+    for n, t in (("x", rx), ("w", rw), ("b", rb)):
+        store(out, f"map/rms/{n}", t)
+    store(out, "map/rms/f32_bias", one(ref.ttir_rms_norm_golden(gmt(rx), gmt(rw), gmt(rb), S.ArrayAttr([96]), S.FloatAttr(1e-6),
+                                                               S.F32Type())))
+    store(out, "map/rms/bf16_noweight", one(ref.ttir_rms_norm_golden(gmt(rx.to(torch.bfloat16)), None, None, S.ArrayAttr([96]),
+                                                                    S.FloatAttr(1e-5), S.BF16Type())))
+
+    # --- mesh_shard and the collectives on a 1x4 and a 2x2 mesh (mapping.py:4189-4235, 5658-5794)
+    def sharded(t, mesh, dims):
+        return ref.ttir_mesh_shard_golden(ref.GoldenMapTensor({0: t}, mesh), S.MeshShardTypeAttr(S.MeshShardType.Devices),
+                                          S.MeshShardDirectionAttr(S.MeshShardDirection.FullToShard), S.DenseI64ArrayAttr([1, 1]),
+                                          S.DenseI64ArrayAttr(dims), S.type_of(t.dtype))
+
+    def store_shards(name, v):
+        for i in sorted(v.shard_map):
+            store(out, f"{name}/{i}", v.shard_at(i))
+    mx = rnd(8, 12, 16)
+    store(out, "map/mesh/x", mx)
+    mxb = mx.to(torch.bfloat16)
+    for mesh, dims, tag in (((1, 4), [-1, 0], "1x4_d0"), ((1, 4), [-1, 2], "1x4_d2"), ((2, 2), [0, 1], "2x2_d01")):
+        sh = sharded(mx, mesh, dims)
+        store_shards(f"map/mesh/{tag}/shards", sh)
+        back = ref.ttir_mesh_shard_golden(sh, S.MeshShardTypeAttr(S.MeshShardType.Devices),
+                                          S.MeshShardDirectionAttr(S.MeshShardDirection.ShardToFull), S.DenseI64ArrayAttr([1, 1]),
+                                          S.DenseI64ArrayAttr(dims), S.F32Type())
+        store(out, f"map/mesh/{tag}/full", one(back))
+        for axis in ((1,) if mesh[0] == 1 else (0, 1)):
+            for rt_name in ("Sum", "Max", "Min", "Mean"):
+                r = ref.ttir_all_reduce_golden(sh, S.ReduceTypeAttr(S.ReduceType[rt_name]), S.IntegerAttr(axis), S.F32Type())
+                store_shards(f"map/mesh/{tag}/all_reduce_{rt_name}_axis{axis}", r)
+            store_shards(f"map/mesh/{tag}/all_gather_dim1_axis{axis}",
+                         ref.ttir_all_gather_golden(sh, S.IntegerAttr(1), S.IntegerAttr(axis), S.F32Type()))
+            store_shards(f"map/mesh/{tag}/reduce_scatter_dim1_axis{axis}",
+                         ref.ttir_reduce_scatter_golden(sh, S.ReduceTypeAttr(S.ReduceType.Sum), S.IntegerAttr(1), S.IntegerAttr(axis),
+                                                        S.F32Type()))
+            store_shards(f"map/mesh/{tag}/mesh_partition_dim1_axis{axis}",
+                         ref.ttir_mesh_partition_golden(sh, S.IntegerAttr(1), S.IntegerAttr(axis), S.F32Type()))
+    shb = sharded(mxb, (1, 4), [-1, 0])
+    store_shards("map/mesh/bf16_1x4_d0/all_reduce_Sum_axis1",
+                 ref.ttir_all_reduce_golden(shb, S.ReduceTypeAttr(S.ReduceType.Sum), S.IntegerAttr(1), S.BF16Type()))
+    rep = ref.ttir_mesh_shard_golden(ref.GoldenMapTensor({0: mx}, (1, 4)), S.MeshShardTypeAttr(S.MeshShardType.Replicate),
+                                     S.MeshShardDirectionAttr(S.MeshShardDirection.FullToShard), S.DenseI64ArrayAttr([1, 1]),
+                                     S.DenseI64ArrayAttr([-1, -1]), S.F32Type())
+    store_shards("map/mesh/replicate_1x4", rep)
+
+    # --- kv-cache ops and decode attention (mapping.py:3582-3670, 2417-2482)
+    cache = rnd(4, 2, 64, 16)
+    fill_in = rnd(1, 2, 40, 16)
+    store(out, "map/cache/cache", cache)
+    store(out, "map/cache/fill_in", fill_in)
+    store(out, "map/cache/filled_user0", one(ref.fill_cache_golden(gmt(cache[:1].clone()), gmt(fill_in))))
+    upd = rnd(1, 2, 4, 16)
+    store(out, "map/cache/update_in", upd)
+    store(out, "map/cache/updated_idx7", one(ref.update_cache_golden(gmt(cache.clone()), gmt(upd), gmt(torch.tensor([7], dtype=torch.int32)))))
+    upd2 = rnd(1, 2, 2, 16)
+    store(out, "map/cache/update_in2", upd2)
+    store(out, "map/cache/updated_idx63_off2", one(ref.update_cache_golden(gmt(cache.clone()), gmt(upd2), gmt(torch.tensor([63], dtype=torch.int32)),
+                                                                          batch_offset=S.IntegerAttr(2))))
+    dq = rnd(1, 3, 8, 32).to(torch.bfloat16)
+    dk, dv = rnd(3, 2, 96, 32).to(torch.bfloat16), rnd(3, 2, 96, 32).to(torch.bfloat16)
+    pos = torch.tensor([5, 95, 40], dtype=torch.int32)
+    dmask = rnd(3, 1, 8, 96)
+    for n, t in (("q", dq), ("k", dk), ("v", dv), ("pos", pos), ("mask", dmask)):
+        store(out, f"map/decode/{n}", t)
+    store(out, "map/decode/causal", one(ref.sdpa_decode_golden(gmt(dq), gmt(dk), gmt(dv), gmt(pos), None, True, 32 ** -0.5)))
+    store(out, "map/decode/masked", one(ref.sdpa_decode_golden(gmt(dq), gmt(dk), gmt(dv), None, gmt(dmask), False, 32 ** -0.5)))
+
+    # --- gather / scatter / sort / top-k (mapping.py:5384-5437, 5624-5640, 5927-5958)
+    gx = rnd(5, 9, 6)
+    gi = torch.randint(0, 9, (5, 4, 6), generator=g, dtype=torch.int32)
+    store(out, "map/gather/x", gx)
+    store(out, "map/gather/idx_dim1", gi)
+    store(out, "map/gather/dim1", one(ref.ttir_gather_golden(gmt(gx), gmt(gi), S.IntegerAttr(1), S.F32Type())))
+    gi2 = torch.randint(0, 6, (5, 9, 3), generator=g, dtype=torch.int32)
+    store(out, "map/gather/idx_dim2", gi2)
+    store(out, "map/gather/dim2", one(ref.ttir_gather_golden(gmt(gx), gmt(gi2), S.IntegerAttr(2), S.F32Type())))
+    # scatter: unique indices along the scatter dimension, so the result does not depend on write order
+    si = torch.stack([torch.randperm(9, generator=g)[:4] for _ in range(5 * 6)]).reshape(5, 6, 4).permute(0, 2, 1).contiguous().to(torch.int32)
+    ssrc = rnd(5, 4, 6)
+    store(out, "map/scatter/idx", si)
+    store(out, "map/scatter/src", ssrc)
+    # the plain (no reduction) scatter is what ttnn.scatter computes; the golden selects it by ReduceType.Invalid
+    store(out, "map/scatter/dim1", one(ref.ttir_scatter_golden(gmt(gx), gmt(si), gmt(ssrc), S.IntegerAttr(1),
+                                                               S.ReduceTypeAttr(S.ReduceType.Invalid), S.F32Type())))
+    store(out, "map/scatter/dim1_sum", one(ref.ttir_scatter_golden(gmt(gx), gmt(si), gmt(ssrc), S.IntegerAttr(1),
+                                                                   S.ReduceTypeAttr(S.ReduceType.Sum), S.F32Type())))
+    sx = rnd(6, 50)
+    sx[2, 10] = sx[2, 30]                 # a tie: stable order keeps index 10 first
+    store(out, "map/sort/x", sx)
+    for desc in (False, True):
+        vals, idx = ref.ttir_sort_golden(gmt(sx), S.IntegerAttr(-1), S.BoolAttr(desc), S.BoolAttr(True), S.F32Type())
+        store(out, f"map/sort/values_desc{int(desc)}", one(vals))
+        store(out, f"map/sort/indices_desc{int(desc)}", one(idx).to(torch.int32))
+    vals, idx = ref.ttir_sort_golden(gmt(sx), S.IntegerAttr(0), S.BoolAttr(False), S.BoolAttr(True), S.F32Type())
+    store(out, "map/sort/values_dim0", one(vals))
+    store(out, "map/sort/indices_dim0", one(idx).to(torch.int32))
+    tx = rnd(4, 3, 200).to(torch.bfloat16)
+    store(out, "map/topk/x", tx)
+    for k, largest in ((8, True), (32, True), (5, False)):
+        vals, idx = ref.ttir_topk_golden(gmt(tx.float()), S.IntegerAttr(k), S.IntegerAttr(-1), S.BoolAttr(largest), S.BoolAttr(True),
+                                         S.F32Type())
+        store(out, f"map/topk/values_k{k}_l{int(largest)}", one(vals))
+        store(out, f"map/topk/indices_k{k}_l{int(largest)}", one(idx).to(torch.int32))
+
+    # --- paged caches and paged decode attention (mapping.py:8745-8844, 8926-9007)
+    pcache = rnd(12, 2, 16, 32).to(torch.bfloat16)            # 12 blocks of 16 tokens
+    ptable = torch.tensor([[3, 7, 1, 0], [5, 2, 9, 11], [4, 6, 8, 10]], dtype=torch.int32)
+    store(out, "map/paged/cache", pcache)
+    store(out, "map/paged/page_table", ptable)
+    pin = rnd(3, 1, 2, 32).to(torch.bfloat16)                 # [batch, seq 1, heads, d]
+    ppos = torch.tensor([17, 0, 63], dtype=torch.int32)
+    store(out, "map/paged/update_in", pin)
+    store(out, "map/paged/update_pos", ppos)
+    store(out, "map/paged/updated", one(ref.ttir_paged_update_cache_golden(gmt(pcache.clone()), gmt(pin), gmt(ppos), S.BoolAttr(False),
+                                                                           gmt(ptable), S.BF16Type())))
+    pfill = rnd(1, 2, 40, 32).to(torch.bfloat16)              # one user's prompt
+    store(out, "map/paged/fill_in", pfill)
+    store(out, "map/paged/filled_user1", one(ref.ttir_paged_fill_cache_golden(gmt(pcache.clone()), gmt(pfill), gmt(ptable),
+                                                                             gmt(torch.tensor([1], dtype=torch.int32)), S.BF16Type())))
+    pv = rnd(12, 2, 16, 32).to(torch.bfloat16)
+    pq = rnd(3, 1, 8, 32).to(torch.bfloat16)                  # [batch, seq 1, heads, d]
+    store(out, "map/paged/v_cache", pv)
+    store(out, "map/paged/q", pq)
+    store(out, "map/paged/decode", one(ref.ttir_paged_sdpa_decode_golden(gmt(pq), gmt(pcache), gmt(pv), gmt(ptable), gmt(pq), S.BoolAttr(True),
+                                                                         None, gmt(ppos), None, None, None, S.BF16Type())))
 
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ttir_cpu_golden.npz")
     np.savez_compressed(path, **out)

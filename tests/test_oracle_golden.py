@@ -1,5 +1,7 @@
-"""Pins the CPU oracle (oracle/ops.py) against outputs of the reference's own CPU code recorded
-in tests/golden/ttir_cpu_golden.npz (made by tests/golden/generate.py)."""
+"""Pins the CPU oracle (oracle/ops.py) against outputs of the reference's own code recorded in
+tests/golden/ttir_cpu_golden.npz by tests/golden/generate.py: its CPU implementation of the TTIR
+ops (ttir_cpu.py) and, under "map/", "quant/", "rms/" and "sdpa/", its torch goldens
+(tools/golden/mapping.py) imported unmodified."""
 
 import pytest
 import torch
@@ -125,6 +127,115 @@ def test_sdpa(golden):
     q, k, v = golden["sdpa/q"], golden["sdpa/k"], golden["sdpa/v"]
     assert torch.allclose(ops.sdpa(q, k, v, True), golden["sdpa/causal"], atol=1e-6)
     assert torch.allclose(ops.sdpa(q, k, v, False), golden["sdpa/full"], atol=1e-6)
+
+
+def test_sdpa_mask_scale_and_bf16(golden):
+    """ttir_sdpa_golden as imported from the reference (tests/golden/generate.py): additive mask with
+    an explicit scale, grouped-query heads with Sq != Skv, causal; bf16 in and out."""
+    q, k, v, m = (golden[f"map/sdpa2/{n}"] for n in ("q", "k", "v", "mask"))
+    assert torch.equal(ops.sdpa(q, k, v, False, m, 0.2), golden["map/sdpa2/masked"])
+    assert torch.equal(ops.sdpa(q, k, v, False), golden["map/sdpa2/full"])
+    assert torch.equal(ops.sdpa(q, k[:, :, :24], v[:, :, :24], True), golden["map/sdpa2/causal_sq"])
+
+
+def test_rms_norm_bias_and_no_weight(golden):
+    x, w, b = golden["map/rms/x"], golden["map/rms/w"], golden["map/rms/b"]
+    assert same(ops.rms_norm(x, w, b, 1e-6), golden["map/rms/f32_bias"])
+    assert same(ops.rms_norm(x.to(torch.bfloat16), None, None, 1e-5), golden["map/rms/bf16_noweight"])
+
+
+def _shards(golden, name, n):
+    return [golden[f"{name}/{i}"] for i in range(n)]
+
+
+@pytest.mark.parametrize("tag,dim", [("1x4_d0", 0), ("1x4_d2", 2)])
+def test_mesh_shard_and_collectives_on_a_row_mesh(golden, tag, dim):
+    """mesh_shard, all_reduce (sum / max / min / mean), all_gather, reduce_scatter and mesh_partition
+    against the reference's goldens on a 1x4 mesh."""
+    x = golden["map/mesh/x"]
+    base = f"map/mesh/{tag}"
+    sh = ops.mesh_shard_full_to_shard(x, 4, dim)
+    for got, want in zip(sh, _shards(golden, base + "/shards", 4)):
+        assert torch.equal(got, want)
+    assert torch.equal(ops.mesh_shard_shard_to_full(sh, dim), golden[base + "/full"])
+    for code, name in enumerate(("Sum", "Mean", "Max", "Min")):
+        for got, want in zip(ops.all_reduce(sh, code), _shards(golden, f"{base}/all_reduce_{name}_axis1", 4)):
+            assert torch.equal(got, want), name
+    for got, want in zip(ops.all_gather(sh, 1), _shards(golden, base + "/all_gather_dim1_axis1", 4)):
+        assert torch.equal(got, want)
+    for got, want in zip(ops.reduce_scatter(sh, 1), _shards(golden, base + "/reduce_scatter_dim1_axis1", 4)):
+        assert torch.equal(got, want)
+    for got, want in zip(ops.mesh_partition(sh, 1), _shards(golden, base + "/mesh_partition_dim1_axis1", 4)):
+        assert torch.equal(got, want)
+
+
+def test_collectives_bf16_and_replicate(golden):
+    x = golden["map/mesh/x"]
+    sh = ops.mesh_shard_full_to_shard(x.to(torch.bfloat16), 4, 0)
+    for got, want in zip(ops.all_reduce(sh, 0), _shards(golden, "map/mesh/bf16_1x4_d0/all_reduce_Sum_axis1", 4)):
+        assert torch.equal(got, want)
+    for got, want in zip(ops.mesh_shard_full_to_shard(x, 4, None), _shards(golden, "map/mesh/replicate_1x4", 4)):
+        assert torch.equal(got, want)
+
+
+def test_collectives_on_a_2x2_mesh(golden):
+    """Both cluster axes of a 2x2 mesh: a group is a row (axis 1) or a column (axis 0) of devices."""
+    x = golden["map/mesh/x"]
+    base = "map/mesh/2x2_d01"
+    rows = torch.chunk(x, 2, dim=0)
+    sh = [c.contiguous() for r in rows for c in torch.chunk(r, 2, dim=1)]
+    for got, want in zip(sh, _shards(golden, base + "/shards", 4)):
+        assert torch.equal(got, want)
+    groups = {1: [[0, 1], [2, 3]], 0: [[0, 2], [1, 3]]}
+    for axis, gs in groups.items():
+        for g in gs:
+            mine = [sh[i] for i in g]
+            for j, i in enumerate(g):
+                assert torch.equal(ops.all_reduce(mine, 0)[j], golden[f"{base}/all_reduce_Sum_axis{axis}/{i}"])
+                assert torch.equal(ops.all_gather(mine, 1)[j], golden[f"{base}/all_gather_dim1_axis{axis}/{i}"])
+                assert torch.equal(ops.reduce_scatter(mine, 1)[j], golden[f"{base}/reduce_scatter_dim1_axis{axis}/{i}"])
+                assert torch.equal(ops.mesh_partition(mine, 1)[j], golden[f"{base}/mesh_partition_dim1_axis{axis}/{i}"])
+
+
+def test_cache_ops_and_decode_attention(golden):
+    """fill_cache, update_cache and decode attention against the reference's goldens."""
+    cache = golden["map/cache/cache"]
+    assert torch.equal(ops.fill_cache(cache[:1], golden["map/cache/fill_in"]), golden["map/cache/filled_user0"])
+    assert torch.equal(ops.update_cache(cache, golden["map/cache/update_in"], torch.tensor([7])), golden["map/cache/updated_idx7"])
+    assert torch.equal(ops.update_cache(cache, golden["map/cache/update_in2"], torch.tensor([63]), batch_offset=2),
+                       golden["map/cache/updated_idx63_off2"])
+    q, k, v, pos, m = (golden[f"map/decode/{n}"] for n in ("q", "k", "v", "pos", "mask"))
+    assert torch.equal(ops.sdpa_decode(q, k, v, pos, None, True, 32 ** -0.5), golden["map/decode/causal"])
+    assert torch.equal(ops.sdpa_decode(q, k, v, None, m, False, 32 ** -0.5), golden["map/decode/masked"])
+
+
+def test_gather_scatter_sort_topk(golden):
+    x = golden["map/gather/x"]
+    assert torch.equal(ops.gather(x, golden["map/gather/idx_dim1"], 1), golden["map/gather/dim1"])
+    assert torch.equal(ops.gather(x, golden["map/gather/idx_dim2"], 2), golden["map/gather/dim2"])
+    idx, src = golden["map/scatter/idx"], golden["map/scatter/src"]
+    assert torch.equal(ops.scatter(x, idx, src, 1), golden["map/scatter/dim1"])
+    assert torch.equal(ops.scatter(x, idx, src, 1, "Sum"), golden["map/scatter/dim1_sum"])
+    sx = golden["map/sort/x"]
+    for desc in (False, True):
+        v, i = ops.sort(sx, -1, desc)
+        assert torch.equal(v, golden[f"map/sort/values_desc{int(desc)}"]) and torch.equal(i, golden[f"map/sort/indices_desc{int(desc)}"])
+    v, i = ops.sort(sx, 0)
+    assert torch.equal(v, golden["map/sort/values_dim0"]) and torch.equal(i, golden["map/sort/indices_dim0"])
+    tx = golden["map/topk/x"].float()
+    for k, largest in ((8, True), (32, True), (5, False)):
+        v, i = ops.topk(tx, k, -1, largest)
+        assert torch.equal(v, golden[f"map/topk/values_k{k}_l{int(largest)}"])
+        assert torch.equal(i, golden[f"map/topk/indices_k{k}_l{int(largest)}"])
+
+
+def test_paged_cache_and_paged_decode(golden):
+    cache, table = golden["map/paged/cache"], golden["map/paged/page_table"]
+    pos = golden["map/paged/update_pos"]
+    assert torch.equal(ops.paged_update_cache(cache, golden["map/paged/update_in"], pos, table), golden["map/paged/updated"])
+    assert torch.equal(ops.paged_fill_cache(cache, golden["map/paged/fill_in"], table, torch.tensor([1])), golden["map/paged/filled_user1"])
+    got = ops.paged_sdpa_decode(golden["map/paged/q"], cache, golden["map/paged/v_cache"], table, pos)
+    assert torch.equal(got, golden["map/paged/decode"])
 
 
 def test_layer_norm(golden):

@@ -26,12 +26,28 @@ import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-GEMM_DRAM_BYTES_PER_LAUNCH_N1 = 712.4e6 / 4  # 712.4 MB per pass of the block over its four GEMM launches (ncu, N = 1)
+TRAFFIC_SUMMARY = os.path.join(ROOT, "profiles", "gemm_tcgen05_decoder_dram_traffic.md")
 sys.path.insert(0, ROOT)
 
 CONFIG = dict(seq=2048, hidden=4096, n_heads=32, n_kv_heads=8, head_dim=128, ffn=14336, batch=1)
 METRIC = "decoder_block_tokens_per_s"
 UNIT = "tokens/s"
+
+
+def gemm_dram_bytes_per_launch():
+    """DRAM bytes per launch of the block's GEMM kernel at N = 1, from the committed summary of the ncu
+    capture (profiles/gemm_tcgen05_decoder_dram_traffic.md): the "sum" row of its table holds the bytes
+    read and written over the launches listed above it.  None when the summary is missing or unreadable."""
+    import re
+    try:
+        rows = [ln for ln in open(TRAFFIC_SUMMARY).read().splitlines() if ln.startswith("|")]
+        launches = [ln for ln in rows[2:] if not ln.lower().startswith("| sum")]
+        total = next(ln for ln in rows if ln.lower().startswith("| sum"))
+        cells = [c.strip() for c in total.strip("|").split("|")]
+        read_mb, written_mb = (float(re.match(r"([0-9.]+)\s*MB", cells[i]).group(1)) for i in (3, 4))
+        return (read_mb + written_mb) * 1e6 / len(launches)
+    except Exception:
+        return None
 
 
 def measured_peaks():
@@ -56,44 +72,73 @@ class ClockSampler:
         self._stop = threading.Event()
         self._thread = None
 
-    def _run_nvml(self):
-        """NVML (read-only queries) every few milliseconds: the timed region of the default run is
-        tens of milliseconds long, too short for a process per sample."""
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+    BITS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+
+    def _nvml_setup(self):
+        """NVML (read-only queries): initialised here, on the caller's thread and before the timed
+        region, so that the sampling thread only reads."""
         import pynvml
         pynvml.nvmlInit()
-        h = pynvml.nvmlDeviceGetHandleByIndex(self.gpu)
-        mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
-        bits = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+        self._nvml = pynvml
+        self._h = pynvml.nvmlDeviceGetHandleByIndex(self.gpu)
+        self._mx = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
         try:
-            reasons_of = pynvml.nvmlDeviceGetCurrentClocksEventReasons
+            self._reasons_of = pynvml.nvmlDeviceGetCurrentClocksEventReasons
         except AttributeError:
-            reasons_of = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
-        while not self._stop.is_set():
-            sm = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
-            r = reasons_of(h)
-            self.samples.append([str(sm), str(mx)] + ["Active" if r & bits[n] else "Not Active"
-                                                     for n in ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")])
-            self._stop.wait(0.003)
+            self._reasons_of = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
 
-    def _run(self):
+    def _sample_nvml(self):
+        sm = self._nvml.nvmlDeviceGetClockInfo(self._h, self._nvml.NVML_CLOCK_SM)
+        r = self._reasons_of(self._h)
+        self.samples.append([str(sm), str(self._mx)] + ["Active" if r & self.BITS[n] else "Not Active" for n in self.NAMES])
+
+    def _sample_smi(self):
         try:
-            self._run_nvml()
-            return
+            out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                  "-i", str(self.gpu)], capture_output=True, text=True, timeout=5).stdout.strip()
+            if out:
+                self.samples.append([x.strip() for x in out.split(",")])
         except Exception:
             pass
+
+    def _run(self):
+        # The timed region of the default run is tens of milliseconds long: NVML every 2 ms; a process
+        # per sample (nvidia-smi) only where NVML is unavailable.
         while not self._stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                      "-i", str(self.gpu)], capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([x.strip() for x in out.split(",")])
-            except Exception:
-                pass
-            self._stop.wait(0.2)
+            if self._nvml is not None:
+                try:
+                    self._sample_nvml()
+                except Exception:
+                    pass
+                self._stop.wait(0.002)
+            else:
+                self._sample_smi()
+                self._stop.wait(0.2)
 
     def start(self):
+        """Sets NVML up, starts the sampling thread, and returns once it has taken a sample, so the
+        caller may start its timed region right away."""
+        self._nvml = None
+        try:
+            self._nvml_setup()
+        except Exception:
+            self._nvml = None
         self._thread = threading.Thread(target=self._run, daemon=True)
         self._thread.start()
+        t0 = time.perf_counter()
+        while not self.samples and time.perf_counter() - t0 < 2.0:
+            time.sleep(0.0005)
+        self._before = len(self.samples)
+
+    def sample_now(self):
+        """One more sample from the caller's thread (the bench takes one right after its last launch,
+        while the GPU is still busy)."""
+        try:
+            if self._nvml is not None:
+                self._sample_nvml()
+        except Exception:
+            pass
 
     def stop(self):
         self._stop.set()
@@ -141,6 +186,56 @@ def dist_env(args):
     if args.gpus > 1 and world == 1:
         raise SystemExit("for --gpus N > 1 launch with torch.distributed.run (one process per GPU)")
     return rank, world, local
+
+
+def parity_metrics(got, want):
+    """The figures the full-size parity test uses (tests/test_configs_gpu.py): Pearson correlation,
+    RMS error relative to the output's standard deviation, the share of elements within
+    atol 1e-2 + one bf16 ulp of their own magnitude, and the largest error in ulps of the largest
+    magnitude.  ok = PCC >= 0.999, RMS <= 1 % of sigma, >= 90 % within atol + 1 ulp, max error <= 2 ulps
+    of the largest magnitude."""
+    import math
+    from oracle import metrics
+    g, w = got.float(), want.float()
+    err, mag = (g - w).abs(), w.abs()
+    pcc = float(metrics.get_pcc(want, got))
+    rms = err.pow(2).mean().sqrt().item() / max(w.std().item(), 1e-30)
+    within = (err <= 1e-2 + 2.0 ** -7 * mag).float().mean().item()
+    ulp_at_max = 2.0 ** (math.floor(math.log2(max(mag.max().item(), 1e-30))) - 7)
+    max_ulps = err.max().item() / ulp_at_max
+    ok = bool(pcc >= 0.999 and rms <= 0.01 and within >= 0.9 and max_ulps <= 2.0 and bool(g.isfinite().all()))
+    return {"pcc": pcc, "rms_over_std": rms, "within_atol_1ulp": within, "max_err": err.max().item(),
+            "max_err_in_ulps_of_max": max_ulps, "ok": ok}
+
+
+def check_parity(rt, dist, rank, world, last, full_inputs):
+    """Compares the output of the program that was just timed with the CPU oracle of the same graph
+    (rank 0; full size, about a second of host time) and, at N > 1, the ranks' outputs with each
+    other bit for bit (every rank holds the whole block output after the last all-reduce)."""
+    import hashlib
+    import torch
+    from ttmlir_b200 import graphs
+    from oracle.backend import OracleBuilder
+    got = rt.to_torch(rt.to_host(last, untilize=True)[0])
+    digest = torch.frombuffer(bytearray(hashlib.sha256(got.contiguous().view(torch.uint8).numpy().tobytes()).digest()),
+                              dtype=torch.uint8)
+    same = True
+    if world > 1:
+        mine = digest.cuda()
+        every = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        same = all(bool(torch.equal(e, every[0])) for e in every)
+    if rank != 0:
+        return None
+    t0 = time.perf_counter()
+    ob = OracleBuilder(full_inputs, mesh_shape=(1, world))
+    graphs.decoder_block_graph(ob, tp=world, **CONFIG)
+    want = ob.results()[0]
+    p = parity_metrics(got, want)
+    p.update(bitwise_equal_across_ranks=bool(same), oracle_s=time.perf_counter() - t0,
+             against="CPU oracle of the same graph (mesh 1x%d), full size" % world)
+    p["ok"] = bool(p["ok"] and same)
+    return p
 
 
 def run_b200(args):
@@ -236,8 +331,8 @@ def run_b200(args):
     # ---- value: inputs resident in HBM ------------------------------------------------------
     sampler = ClockSampler(local)
     ev = Events(rt.lib, stream)
+    sampler.start()          # NVML is set up and the first sample taken before the region starts
     barrier()
-    sampler.start()
     launches0 = rt.launch_count()
     ev.start()
     last = None
@@ -245,6 +340,7 @@ def run_b200(args):
     for _ in range(args.steps):
         last = step_resident()
     host_submit_us = (time.perf_counter() - t_host) / args.steps * 1e6   # CPU time to enqueue one step
+    sampler.sample_now()     # everything is enqueued and the GPU still busy
     ms = ev.stop_ms()
     launches = rt.launch_count() - launches0
     barrier()
@@ -277,6 +373,9 @@ def run_b200(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_s = float(t.item())
 
+    # ---- parity of what was timed (outside every timed region) --------------------------------
+    parity = check_parity(rt, dist if world > 1 else None, rank, world, last, full) if not args.no_parity else None
+
     # ---- per-kernel achieved rates from per-launch events (separate pass) ---------------------
     rt.lib.ttb_prof_enable(1)
     prof_steps = min(args.steps, 5)
@@ -289,7 +388,7 @@ def run_b200(args):
     prof = json.loads(buf.value.decode())
     return dict(rank=rank, world=world, ms_total=ms_total, e2e_s=e2e_s, launches=launches, clocks=clocks, prof=prof,
                 prof_steps=prof_steps, tokens=tokens, bytes_io=mine[0].numel() * 2, rt=rt, device=device,
-                host_submit_us=host_submit_us,
+                host_submit_us=host_submit_us, parity=parity,
                 e2e_host_us={k: v / args.steps * 1e6 for k, v in e2e_host.items()})
 
 
@@ -384,13 +483,34 @@ def side_workloads():
     }
 
 
-def run_side(args):
-    """One of the single-GPU configurations through submit with resident inputs; prints one JSON line."""
+def side_parity(workload, got, want):
+    """Outputs of a side workload against the CPU oracle of the same graph at full size: integer
+    tensors and the quantization chain bit for bit, f32 within 1e-4, bf16 with PCC >= 0.999 and
+    |err| <= 3e-2 + 2^-6 |want| (two bf16 ulps; the tolerance of tests/test_configs_gpu.py)."""
+    import torch
+    from oracle import metrics
+    res = {"ok": True, "outputs": []}
+    for g, w in zip(got, want):
+        if workload.startswith("quant") or not w.is_floating_point():
+            bad = int((g != w).sum().item()) if g.shape == w.shape else -1
+            res["outputs"].append({"bit_exact": bad == 0, "mismatches": bad})
+            res["ok"] = res["ok"] and bad == 0
+            continue
+        tol = (0.999, 1e-4, 1e-4) if w.dtype == torch.float32 else (0.999, 3e-2, 2.0 ** -6)
+        ok, report = metrics.check_close(w, g, *tol)
+        res["outputs"].append({"ok": bool(ok), "report": report})
+        res["ok"] = res["ok"] and bool(ok)
+    return res
+
+
+def measure_side(args, workload, steps=None, with_parity=True):
+    """One of the single-GPU configurations through submit with resident inputs; returns its JSON line."""
     import torch  # noqa: F401
     from __graft_entry__ import load_package
     load_package()
     from ttmlir_b200 import graphs, runtime_api as rt
-    graph, kw, make_inputs, abytes, aflops, units, unit_name = side_workloads()[args.workload]
+    graph, kw, make_inputs, abytes, aflops, units, unit_name = side_workloads()[workload]
+    steps = steps or args.steps
     peaks = measured_peaks()
     device = rt.open_mesh_device(rt.MeshDeviceOptions(mesh_shape=[1, 1]))
     stream, _ = device.stream(0)
@@ -405,11 +525,18 @@ def run_side(args):
     launches0 = rt.launch_count()
     ev.start()
     t_host = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         out = rt.submit(device, binary, 0, dev_in)
-    host_us = (time.perf_counter() - t_host) / args.steps * 1e6
-    ms = ev.stop_ms() / args.steps
+    host_us = (time.perf_counter() - t_host) / steps * 1e6
+    ms = ev.stop_ms() / steps
     launches = rt.launch_count() - launches0
+    parity = None
+    if with_parity and not args.profile and not whole_binary:
+        from oracle.backend import OracleBuilder
+        got = [rt.to_torch(rt.to_host(o, untilize=True)[0]) for o in out]
+        ob = OracleBuilder(ins)
+        graph(ob, **kw)
+        parity = side_parity(workload, got, ob.results())
     # The same pass with cold caches: several of these workloads are smaller than the 126 MB L2, so the
     # loop above re-reads inputs the previous pass left there.  Here a 256 MB buffer is overwritten
     # before every pass (outside the timed region) and every pass is timed on its own.
@@ -419,7 +546,7 @@ def run_side(args):
         flush_bytes = 256 << 20
         assert rt.lib.ttb_malloc(ctypes.byref(scratch), ctypes.c_size_t(flush_bytes), ctypes.c_void_p(stream)) == 0
         total = 0.0
-        reps = min(args.steps, 30)
+        reps = min(steps, 30)
         for _ in range(reps):
             assert rt.lib.ttb_memset(scratch, 0, ctypes.c_size_t(flush_bytes), ctypes.c_void_p(stream)) == 0
             ev.start()
@@ -430,14 +557,14 @@ def run_side(args):
     prof = []
     if not args.profile:
         rt.lib.ttb_prof_enable(1)
-        for _ in range(min(args.steps, 5)):
+        for _ in range(min(steps, 5)):
             out = rt.submit(device, binary, 0, dev_in)
         rt.wait(out[0])
         buf = ctypes.create_string_buffer(1 << 16)
         assert rt.lib.ttb_prof_summary(buf, ctypes.c_size_t(len(buf))) == 0
         rt.lib.ttb_prof_enable(0)
         for k in json.loads(buf.value.decode()):
-            e = {"kernel": k["tag"], "launches_per_step": k["launches"] / min(args.steps, 5), "avg_ms": k["ms"] / k["launches"]}
+            e = {"kernel": k["tag"], "launches_per_step": k["launches"] / min(steps, 5), "avg_ms": k["ms"] / k["launches"]}
             if k["flops"] > 0:
                 e.update(achieved=k["flops"] / (k["ms"] * 1e-3) / 1e12, unit="TFLOP/s")
                 e["frac"] = e["achieved"] / peaks["bf16_tflops"]
@@ -445,23 +572,27 @@ def run_side(args):
                 e.update(achieved=k["bytes"] / (k["ms"] * 1e-3) / 1e9, unit="GB/s")
                 e["frac"] = e["achieved"] / peaks["hbm_gbs"]
             prof.append(e)
-    line = {"metric": f"{args.workload}_{unit_name}_per_s", "value": units / (ms * 1e-3), "unit": f"{unit_name}/s",
-            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "dtype": "f32" if args.workload.startswith("mlp") else "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "host_enqueue_us_per_step": host_us}, "gpu_launches": launches,
+    line = {"metric": f"{workload}_{unit_name}_per_s", "value": units / (ms * 1e-3), "unit": f"{unit_name}/s",
+            "n_gpus": 1, "steps": steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "dtype": "f32" if workload.startswith("mlp") else "bf16", "data": "synthetic",
+            "config": {"workload": workload, "host_enqueue_us_per_step": host_us}, "gpu_launches": launches,
             "ms_per_step_l2_flushed": flushed_ms,
             "graph_hbm_gbs": abytes / (ms * 1e-3) / 1e9, "graph_hbm_frac": abytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
             "graph_tflops": aflops / (ms * 1e-3) / 1e12, "graph_tensor_frac": aflops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
-            "per_op": prof}
+            "peak_source": f"{peaks['source']} (HBM copy; burst bf16)", "parity": parity, "per_op": prof}
     rt.close_mesh_device(device)
-    print(json.dumps(line))
+    return line
+
+
+def run_side(args):
+    print(json.dumps(measure_side(args, args.workload)))
 
 
 def run_all_reduce(args):
     """The block's all-reduce (sum of [2048, 4096] bf16, 16.8 MB) on an in-process 1 x N mesh: the
     peer-memory kernel with its operand already staged (as after a GEMM), with a staging copy, with
     the fused residual add, and NCCL.  One process launches on all N devices in turn, so the
-    figures include that launch skew.  With TTB_SYMM_STAMPS=1 the phase times of block 0 are printed."""
+    figures include that launch skew."""
     from __graft_entry__ import load_package
     load_package()
     from ttmlir_b200 import runtime_api as rt
@@ -523,16 +654,6 @@ def run_all_reduce(args):
         return ms / args.steps * 1e3
     res = {"staged": timed(lambda: symm(True, False)), "staged_residual": timed(lambda: symm(True, True)),
            "copied": timed(lambda: symm(False, False)), "nccl": timed(nccl)}
-    phases = None
-    if os.environ.get("TTB_SYMM_STAMPS") == "1":
-        symm(True, True)
-        for d in range(n):
-            ck(lib.ttb_set_device(d))
-            ck(lib.ttb_stream_sync(streams[d]))
-        st = (ctypes.c_ulonglong * 8)()
-        ck(lib.ttb_symm_stamps(symms[0], st))
-        phases = {"ns": [int(st[i + 1]) - int(st[i]) for i in range(5) if st[i + 1] >= st[i]],
-                  "names": ["stage", "barrier", "reduce", "barrier", "gather"]}
     status = ctypes.c_int(-1)
     ck(lib.ttb_symm_status(symms[0], ctypes.byref(status)))
     peaks = measured_peaks()
@@ -543,7 +664,7 @@ def run_all_reduce(args):
     print(json.dumps({"metric": "all_reduce_us", "value": us, "unit": "us", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
                       "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
                       "config": {"workload": "all_reduce(sum) of [2048, 4096] bf16 + residual add, in-process 1xN mesh"},
-                      "us": res, "phases_block0": phases, "status": status.value,
+                      "us": res, "status": status.value,
                       "roofline": {"bound": "nvlink", "achieved": link_bytes / (us * 1e-6) / 1e9, "peak": 770.0, "unit": "GB/s",
                                    "frac": link_bytes / (us * 1e-6) / 1e9 / 770.0,
                                    "peak_source": "measured peer copy per direction on this pool"}}))
@@ -556,6 +677,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the comparison of the timed program's output with the CPU oracle")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="N = 1 only: skip the short passes over the other benchmark configurations (extra_workloads)")
     ap.add_argument("--e2e-depth", type=int, default=2,
                     help="steps in flight in the end-to-end loop before the host reads a result")
     ap.add_argument("--idle-s", type=float, default=1.0,
@@ -592,13 +716,19 @@ def main():
     e2e_value = tokens * steps / r["e2e_s"]
     world = r["world"]
 
+    # Tensor-core fractions: the burst cuBLAS figure when the timed region is shorter than a second
+    # (clocks are still near their maximum), the sustained figure for longer loops; both are reported.
+    region_s = r["ms_total"] * 1e-3
+    burst = region_s < 1.0
+    tensor_peak = peaks["bf16_tflops"] if burst else peaks["bf16_tflops_sustained"]
     per_op, dominant = [], None
     for k in r["prof"]:
         ms = k["ms"] / max(k["launches"], 1)
         entry = {"kernel": k["tag"], "launches_per_step": k["launches"] / r["prof_steps"], "avg_ms": ms}
         if k["flops"] > 0:
             tf = k["flops"] / (k["ms"] * 1e-3) / 1e12
-            entry.update(bound="tensor", achieved=tf, unit="TFLOP/s", frac=tf / peaks["bf16_tflops_sustained"])
+            entry.update(bound="tensor", achieved=tf, unit="TFLOP/s", frac=tf / tensor_peak,
+                         frac_of_sustained=tf / peaks["bf16_tflops_sustained"])
         elif k["bytes"] > 0:
             gbs = k["bytes"] / (k["ms"] * 1e-3) / 1e9
             entry.update(bound="hbm", achieved=gbs, unit="GB/s", frac=gbs / peaks["hbm_gbs"])
@@ -608,14 +738,16 @@ def main():
             dominant = (entry, k["ms"])
     per_op.sort(key=lambda e: -e["share_of_step"])
     dom = dominant[0] if dominant else {}
+    traffic = gemm_dram_bytes_per_launch() if (world == 1 and dom.get("kernel") == "gemm_tcgen05") else None
     roofline = {"kernel": dom.get("kernel"), "bound": dom.get("bound"), "achieved": dom.get("achieved"),
-                "peak": peaks["bf16_tflops_sustained"] if dom.get("bound") == "tensor" else peaks["hbm_gbs"],
-                "unit": dom.get("unit"), "frac": dom.get("frac"),
-                # DRAM bytes per launch of the dominant kernel from an ncu capture of this workload
-                # (profiles/gemm_tcgen05_decoder_dram_traffic.md): 712.4 MB per pass over the block's four GEMM launches at N = 1.
-                "traffic": GEMM_DRAM_BYTES_PER_LAUNCH_N1 if (world == 1 and dom.get("kernel") == "gemm_tcgen05") else None,
-                "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum, N=1 capture)",
-                "peak_source": f"{peaks['source']} (sustained bf16 figure: the kernel is timed inside a long step)"}
+                "peak": tensor_peak if dom.get("bound") == "tensor" else peaks["hbm_gbs"],
+                "unit": dom.get("unit"), "frac": dom.get("frac"), "frac_of_sustained": dom.get("frac_of_sustained"),
+                # DRAM bytes per launch of the dominant kernel, from the committed summary of an ncu capture of this workload
+                "traffic": traffic,
+                "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum, N=1 capture, "
+                                "profiles/gemm_tcgen05_decoder_dram_traffic.md)",
+                "peak_source": f"{peaks['source']} ({'burst' if burst else 'sustained'} bf16 figure: the timed region is "
+                               f"{region_s * 1e3:.1f} ms long)"}
     flops = graphs.decoder_block_flops(**CONFIG)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": args.warmup,
@@ -634,10 +766,26 @@ def main():
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": r["bytes_io"], "d2h_bytes_per_step": r["bytes_io"]},
         "roofline": roofline, "per_op": per_op,
     }
+    if r.get("parity") is not None:
+        line["parity"] = r["parity"]
     if world == 1 and not args.no_cpu_baseline and not args.profile:
         line["cpu_baseline"] = cpu_baseline()
     r["rt"].close_mesh_device(r["device"])
+    if world == 1 and not args.no_extra and not args.profile:
+        # The other benchmark configurations, a short pass each (resident inputs, back to back and with L2
+        # flushed, per-kernel fractions, parity against the CPU oracle at full size).
+        extra = []
+        for name in ("mlp", "quant", "quant_int8", "w8_linear", "bottleneck"):
+            try:
+                e = measure_side(args, name, steps=min(args.steps, 20))
+                extra.append({k: e[k] for k in ("metric", "value", "unit", "ms_per_step", "ms_per_step_l2_flushed", "gpu_launches",
+                                                "graph_hbm_frac", "graph_tensor_frac", "parity", "per_op")})
+            except Exception as ex:  # a side line must not take the headline down with it
+                extra.append({"metric": name, "error": str(ex)[:300]})
+        line["extra_workloads"] = extra
     print(json.dumps(line))
+    if line.get("parity") is not None and not line["parity"]["ok"]:
+        sys.exit(3)
 
 
 if __name__ == "__main__":

@@ -64,6 +64,11 @@ TTB_API int ttb_device_sync(void);
 /* Stream-ordered allocation from the device's default memory pool (kept warm, never trimmed). */
 TTB_API int ttb_malloc(void **ptr, size_t bytes, void *stream);
 TTB_API int ttb_free(void *ptr, void *stream);
+/* What the current device's default memory pool holds: bytes reserved from the driver, bytes handed
+ * out right now, and the high-water mark of the latter since it was last reset (reset_high != 0
+ * resets it to the current use after reading).  A call sequence that must not allocate leaves the
+ * high-water mark where a reset put it.  Any of the outputs may be null. */
+TTB_API int ttb_mempool_stats(uint64_t *reserved, uint64_t *used, uint64_t *used_high, int reset_high);
 TTB_API int ttb_host_alloc_pinned(void **ptr, size_t bytes);
 TTB_API int ttb_host_free_pinned(void *ptr);
 /* *pinned = 1 when `ptr` is page-locked host memory (a copy from it is a true asynchronous DMA). */
@@ -344,15 +349,25 @@ TTB_API int ttb_conv2d_fused(const void *x, const void *weight, const void *bias
  * ttb_conv2d -- same kernels, same results.  It calls no cudaMalloc / cudaFree and no
  * allocating library routine; the caller still supplies input, weight, bias and output.
  *
- *  - A convolution whose workspace (ttb_conv2d_workspace_bytes) exceeds the buffer is refused
- *    with TTB_ERR_INVALID and a message naming both sizes.
+ *  - The buffer has two parts: the convolution's workspace in front and, at its end,
+ *    TTB_CONV2D_STATIC_GEMM_BYTES for the partial sums that the CUDA-core contraction keeps when
+ *    it splits a long reduction over several thread blocks (f32 convolutions and shapes too small
+ *    or too ragged for the tensor-core kernel take that path; elsewhere that scratch comes from
+ *    the memory pool).  A convolution whose workspace (ttb_conv2d_workspace_bytes) exceeds
+ *    TTB_CONV2D_STATIC_SCRATCH_BYTES - TTB_CONV2D_STATIC_GEMM_BYTES is refused with
+ *    TTB_ERR_INVALID and a message naming both sizes; so are extents that are not positive or
+ *    whose byte count overflows.
  *  - The first call on each device looks up the buffer's device address; make that first
- *    call during start-up, before any stream capture begins.
+ *    call during start-up, before any stream capture begins.  The address is kept for the life
+ *    of the process: do not use the library across a cudaDeviceReset of that device.
  *  - All calls share the one buffer and it keeps whatever the previous call left there.
- *    Nothing in it has to start at zero: every byte a launch reads was written by the same
- *    launch sequence before.  Two calls whose kernels overlap on the GPU (different streams)
- *    would overwrite each other's scratch; issue them on one stream or order them yourself. */
+ *    The split-reduction counters are the only part that must start at zero, and every call
+ *    clears them on its stream before its kernels run; every other byte a launch reads was
+ *    written by the same launch sequence before.  Two calls whose kernels overlap on the GPU
+ *    (different streams) would overwrite each other's scratch; issue them on one stream or order
+ *    them yourself. */
 #define TTB_CONV2D_STATIC_SCRATCH_BYTES (32u << 20)
+#define TTB_CONV2D_STATIC_GEMM_BYTES (4u << 20)
 TTB_API int ttb_conv2d_static(const void *x, const void *weight, const void *bias, void *out,
                               int dtype, int bias_dtype, int64_t n, int64_t h, int64_t w, int64_t c,
                               int64_t o, int kh, int kw, int stride_h, int stride_w,
@@ -383,9 +398,16 @@ TTB_API int ttb_sdpa_strided(const void *q, const void *k, const void *v, void *
 /* Status word of the tcgen05 attention kernel: 0, or (site << 8) | 1 of the first bounded wait
  * that ran out (the launch then produced no valid output).  No reference counterpart. */
 TTB_API int ttb_sdpa_tcgen05_status(int *status);
-/* Diagnostic: registers (or with NULL removes) a device buffer of 2048 int64 in which CTA 0 of the
- * two-heads attention kernel records (tag, clock64) pairs of its MMA thread and first softmax thread. */
-TTB_API int ttb_sdpa_tcgen05_stamps(void *device_buffer_2048_i64);
+/* Both tensor-core kernels (GEMM / convolution and attention) in one call, for the current device and
+ * without a device-wide synchronise: the status words as above; clear != 0 resets a word that was
+ * set, so that one timeout is reported once.  ttb_tcgen05_set_status writes the words the way a
+ * timed-out launch would (zeros clear them): it lets the error path above the kernels be tested
+ * without making a GPU wait run out.  ttb_tcgen05_set_wait_limit sets the limit of every bounded
+ * wait in these kernels in SM clock cycles (<= 0: the default, 2e9 = about a second).
+ * No reference counterpart (the reference's device timeouts live in tt-metal). */
+TTB_API int ttb_tcgen05_status(int *gemm_status, int *sdpa_status, int clear);
+TTB_API int ttb_tcgen05_set_status(int gemm_status, int sdpa_status);
+TTB_API int ttb_tcgen05_set_wait_limit(long long cycles);
 
 /* ---- collectives on a 1xN mesh: ::ttnn::all_reduce / all_gather / reduce_scatter
  * (runtime/lib/ttnn/operations/ccl/all_reduce.cpp:36-37, all_gather.cpp:38-41,
@@ -433,9 +455,18 @@ TTB_API size_t ttb_symm_max_bytes(void *symm);
  * all-reduces later. */
 TTB_API int ttb_symm_input_buffer(void *symm, size_t bytes, void **ptr);
 TTB_API int ttb_symm_status(void *symm, int *status);
-/* Diagnostic (TTB_SYMM_STAMPS=1 at creation): nanosecond timer of block 0 at the six phase
- * boundaries of the last all-reduce (start, staged, barrier, reduced, barrier, gathered). */
-TTB_API int ttb_symm_stamps(void *symm, unsigned long long *stamps8);
+/* The all-reduce numbers its launches, and its flags and staging regions follow that number: every
+ * rank must be at the same count when a collective starts.  After a collective that some rank never
+ * joined (a timeout), the ranks compare their counts on the host and all adopt the largest before the
+ * next one.  Only between collectives, with none in flight. */
+TTB_API int ttb_symm_launch_count(void *symm, uint32_t *launches);
+TTB_API int ttb_symm_set_launch_count(void *symm, uint32_t launches);
+/* Resets the status word after a reported timeout, so that later collectives are judged on their own. */
+TTB_API int ttb_symm_clear_status(void *symm);
+/* How long a barrier of this rank's all-reduce kernels may wait for a peer's flag, in SM clock cycles
+ * (<= 0: the default, 2e9 = about a second).  A rank whose peers never launch returns after this long
+ * with the status word set instead of hanging the GPU. */
+TTB_API int ttb_symm_set_wait_limit(void *symm, long long cycles);
 TTB_API int ttb_symm_all_reduce(void *symm, const void *in, const void *residual, void *out,
                                 size_t count, int dtype, void *stream);
 /* The fused producer path: the GEMM in front of an all-reduce stores each row block of its

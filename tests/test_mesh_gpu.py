@@ -225,3 +225,134 @@ def test_one_process_per_gpu_tensor_parallel(rt):
         assert r[rank][0], f"rank {rank}: {r[rank][2]}"
         assert r[rank][1], f"rank {rank}: results differ between runs"
     assert r[0][3] == r[1][3]
+
+
+def test_all_reduce_gives_up_on_a_peer_that_never_launches(rt):
+    """A rank whose peer never joins a collective must not hang its GPU: the barrier's wait runs out
+    (a flag that nothing sets), the kernel returns, and the status word names the phase and the peer.
+    After the ranks have agreed on a launch count again the next collective works.  One process, two
+    devices, plain peer loads and stores; the limit is set to a few milliseconds for this test."""
+    import ctypes
+    if rt.get_num_available_devices() < 2:
+        pytest.skip("needs two GPUs")
+    lib = rt.lib
+
+    def ck(rc):
+        assert rc == 0, lib.ttb_last_error().decode()
+    n, count = 2, 64 * 1024
+    devs = (ctypes.c_int * n)(0, 1)
+    symms = (ctypes.c_void_p * n)()
+    ck(lib.ttb_symm_create_all(symms, n, devs, ctypes.c_size_t(1 << 20)))
+    streams, ins, outs = [], [], []
+    host = [torch.full((count,), float(d + 1)).to(torch.bfloat16) for d in range(n)]
+    try:
+        for d in range(n):
+            ck(lib.ttb_set_device(d))
+            st = ctypes.c_void_p()
+            ck(lib.ttb_stream_create(ctypes.byref(st)))
+            streams.append(st)
+            for lst, src in ((ins, host[d]), (outs, torch.zeros(count).to(torch.bfloat16))):
+                p = ctypes.c_void_p()
+                ck(lib.ttb_malloc(ctypes.byref(p), ctypes.c_size_t(count * 2), st))
+                ck(lib.ttb_memcpy_h2d(p, ctypes.c_void_p(src.data_ptr()), ctypes.c_size_t(count * 2), st))
+                lst.append(p)
+            ck(lib.ttb_stream_sync(st))
+        # rank 0 alone, with a limit of 8e6 cycles (about 4 ms): nobody answers its flag
+        ck(lib.ttb_symm_set_wait_limit(symms[0], ctypes.c_longlong(8_000_000)))
+        ck(lib.ttb_set_device(0))
+        ck(lib.ttb_symm_all_reduce(symms[0], ins[0], None, outs[0], ctypes.c_size_t(count), 2, streams[0]))
+        ck(lib.ttb_stream_sync(streams[0]))            # returns: the kernel gave up instead of spinning on
+        status = ctypes.c_int(0)
+        ck(lib.ttb_symm_status(symms[0], ctypes.byref(status)))
+        assert status.value == (1 << 8) | 2, hex(status.value)   # first barrier, waiting for rank 1
+        # recovery on the host: clear the word, bring both ranks to the same launch count, default limit
+        ck(lib.ttb_symm_clear_status(symms[0]))
+        done = ctypes.c_uint32()
+        ck(lib.ttb_symm_launch_count(symms[0], ctypes.byref(done)))
+        assert done.value == 1
+        ck(lib.ttb_symm_set_launch_count(symms[1], done))
+        ck(lib.ttb_symm_set_wait_limit(symms[0], ctypes.c_longlong(0)))
+        for d in range(n):
+            ck(lib.ttb_set_device(d))
+            ck(lib.ttb_symm_all_reduce(symms[d], ins[d], None, outs[d], ctypes.c_size_t(count), 2, streams[d]))
+        for d in range(n):
+            ck(lib.ttb_set_device(d))
+            ck(lib.ttb_stream_sync(streams[d]))
+            got = torch.empty(count, dtype=torch.bfloat16)
+            ck(lib.ttb_memcpy_d2h(ctypes.c_void_p(got.data_ptr()), outs[d], ctypes.c_size_t(count * 2), streams[d]))
+            ck(lib.ttb_stream_sync(streams[d]))
+            assert torch.equal(got, torch.full((count,), 3.0).to(torch.bfloat16))
+            ck(lib.ttb_symm_status(symms[d], ctypes.byref(status)))
+            assert status.value == 0
+    finally:
+        for d in range(len(streams)):
+            lib.ttb_set_device(d)
+            for p in (ins[d:d + 1] + outs[d:d + 1]):
+                lib.ttb_free(p, streams[d])
+            lib.ttb_stream_sync(streams[d])
+            lib.ttb_stream_destroy(streams[d])
+        for d in range(n):
+            lib.ttb_symm_destroy(symms[d])
+        lib.ttb_set_device(0)
+
+
+def _tp_full_worker(rank, world, port, ret):
+    """The benchmark's decoder block at full size, tensor parallel over `world` processes."""
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import ttmlir_b200.runtime_api as rt
+        ids = [rt.get_nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        dev = rt.open_mesh_device(rt.MeshDeviceOptions(mesh_shape=[1, world], device_ids=[rank], process_rank=rank,
+                                                       process_count=world, nccl_unique_id=ids[0]))
+        ins = graphs.decoder_block_inputs()
+        mine = graphs.shard_inputs(ins, graphs.decoder_shard_dims(), world, rank)
+        binary = rt.Binary.load_from_memory(graphs.build_binary(graphs.decoder_block_graph, mesh_shape=(1, world), tp=world,
+                                                                presharded=True))
+        rt.set_compatible_device_runtime(binary)
+        dev_in = [rt.to_layout(rt.from_torch(t), dev, rt.get_layout(binary, 0, i), retain=True) for i, t in enumerate(mine)]
+        outs = [rt.to_torch(rt.to_host(rt.submit(dev, binary, 0, dev_in)[0], untilize=True)[0]) for _ in range(2)]
+        gathered = [None] * world
+        dist.all_gather_object(gathered, outs[0].view(torch.int16).numpy().tobytes())
+        report = None
+        if rank == 0:
+            import math
+            from oracle import metrics
+            want = oracle_results(graphs.decoder_block_graph, ins, mesh_shape=(1, world), tp=world)[0]
+            got = outs[0]
+            err, mag = (got.float() - want.float()).abs(), want.float().abs()
+            ulp_at_max = 2.0 ** (math.floor(math.log2(mag.max().item())) - 7)
+            report = dict(pcc=metrics.get_pcc(want, got), within=(err <= 1e-2 + 2.0 ** -7 * mag).float().mean().item(),
+                          rms=err.pow(2).mean().sqrt().item() / want.float().std().item(),
+                          max_ulps=err.max().item() / ulp_at_max, finite=bool(torch.isfinite(got.float()).all()))
+        ret[rank] = (bool(torch.equal(outs[0], outs[1])), all(g == gathered[0] for g in gathered), report)
+        rt.close_mesh_device(dev)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_full_size_decoder_block_one_process_per_gpu(rt, world):
+    """BASELINE config 4 at full size (seq 2048, hidden 4096, 32/8 heads, FFN 14336) on a 1 x world mesh,
+    one process per GPU: the GEMMs in front of the all-reduces push their row blocks into the peers'
+    workspaces (256 to 1024 rows per rank, multiples of the 128-row tile) and the all-reduce runs in its
+    two-shot mode from four ranks on.  Every rank must hold the same bits, run after run, and rank 0's
+    result must meet the full-size tolerance of tests/test_configs_gpu.py against the CPU oracle."""
+    if rt.get_num_available_devices() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    port = 29700 + world + (os.getpid() % 2000)
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_tp_full_worker, args=(world, port, ret), nprocs=world, join=True)
+        r = dict(ret)
+    assert set(r) == set(range(world))
+    for rank in range(world):
+        assert r[rank][0], f"rank {rank}: results differ between runs"
+        assert r[rank][1], f"rank {rank}: ranks disagree"
+    rep = r[0][2]
+    print(world, rep)
+    assert rep["finite"] and rep["pcc"] >= 0.999 and rep["within"] > 0.9 and rep["rms"] < 0.01 and rep["max_ulps"] <= 2.0, rep

@@ -1,6 +1,8 @@
 """tt::runtime API semantics on the GPU, in the spirit of the reference's
 runtime/test/ttnn/python/n150/test_runtime_api.py and test_debug_hooks.py."""
 
+import ctypes
+
 import pytest
 import torch
 
@@ -181,3 +183,41 @@ def test_wait_on_blocking_host_tensor_is_harmless(rt, device):
     rt.wait(h)
     rt.wait(d)
     assert torch.equal(rt.to_torch(h), x.to(torch.bfloat16))
+
+
+def test_a_timed_out_tensor_core_launch_is_reported_by_wait(rt, device):
+    """Every wait inside the tensor-core kernels is bounded; a launch that gave up leaves a status
+    word behind and incomplete output.  wait() must turn that word into an error, once, and the
+    device must stay usable.  The word is written from the host here (ttb_tcgen05_set_status): no
+    GPU wait is made to run out."""
+    kw = dict(m=256, k=512, n=384)
+    ins = graphs.w8_linear_inputs(**kw)
+    binary = rt.Binary.load_from_memory(graphs.build_binary(graphs.w8_linear_graph, **kw))
+    dev_in = [rt.to_layout(rt.from_torch(t), device, rt.get_layout(binary, 0, i), retain=True) for i, t in enumerate(ins)]
+    good = rt.to_torch(rt.to_host(rt.submit(device, binary, 0, dev_in)[0], untilize=True)[0])
+    for gemm, sdpa, text in ((0x0401, 0, "GEMM"), (0, 0x0901, "attention")):
+        out = rt.submit(device, binary, 0, dev_in)[0]
+        assert rt.lib.ttb_tcgen05_set_status(gemm, sdpa) == 0
+        with pytest.raises(RuntimeError, match=text):
+            rt.wait(out)
+        rt.wait(out)                                   # reported once: the word was cleared
+        again = rt.to_torch(rt.to_host(rt.submit(device, binary, 0, dev_in)[0], untilize=True)[0])
+        assert torch.equal(again, good)
+
+
+def test_tensor_core_wait_limit_can_be_set_and_restored(rt, device):
+    """The limit of the bounded waits is a setting, not a constant: a short limit that no healthy
+    launch reaches leaves results unchanged, and the default comes back with a non-positive value."""
+    kw = dict(m=256, k=512, n=384)
+    ins = graphs.w8_linear_inputs(**kw)
+    buf = graphs.build_binary(graphs.w8_linear_graph, **kw)
+    before = run_program(rt, device, buf, ins)[0]
+    assert rt.lib.ttb_tcgen05_set_wait_limit(ctypes.c_longlong(200_000_000)) == 0   # ~0.1 s
+    try:
+        after = run_program(rt, device, buf, ins)[0]
+    finally:
+        assert rt.lib.ttb_tcgen05_set_wait_limit(ctypes.c_longlong(0)) == 0
+    assert torch.equal(before, after)
+    g, a = ctypes.c_int(-1), ctypes.c_int(-1)
+    assert rt.lib.ttb_tcgen05_status(ctypes.byref(g), ctypes.byref(a), 0) == 0
+    assert (g.value, a.value) == (0, 0)

@@ -45,7 +45,6 @@ struct AtParams {
   int causal;
   int fmt; // 1 bf16, 0 f16
   float scaleLog2;
-  long long *stamps; // diagnostic: clock64 of CTA 0's MMA thread and first softmax thread, or null
   // Split mode (few heads: fewer query blocks than SMs, and a causal block's work grows with its
   // index): a query block's key tiles are cut into pieces of at most splitLen tiles, one CTA per
   // piece; pieceStart[qb] is the first piece of query block qb (pieceStart[nQ] = pieces per head).
@@ -504,21 +503,15 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         tcCommit(kEmpty + 8 * st);
         return true;
       };
-      const bool rec = p.stamps && blockIdx.x == 0;
-      int nrec = 0;
-      auto stamp = [&](int tag) { if (rec && nrec < 256) { p.stamps[nrec * 2] = tag; p.stamps[nrec * 2 + 1] = clock64(); ++nrec; } };
       if (ok && nT > 0) ok = issueS(0);
       for (int j = 0; ok && j < nT; ++j) {
-        stamp(100 + j);
         if (j + 1 < nT && !issueS(j + 1)) break;
-        stamp(200 + j);
         const int st = j % AP_STAGES, ph = (j / AP_STAGES) & 1;
         if (!mbarWait(vFull + 8 * st, ph, abortP, 6)) break;
         const uint32_t vb = sV + st * AP_KV;
         bool fine = true;
         for (int hd = 0; hd < 2 && fine; ++hd) {
           if (!mbarWait(pReady + 8 * hd, j & 1, abortP, 7)) { fine = false; break; }
-          stamp(300 + j * 2 + hd);
           tcFenceAfter();
           // O_hd += P_hd V_j: four steps of 16 keys.  P is K-major (one 128-byte row per query
           // row); V is MN-major: 128-byte rows of 64 d values, one row per key, the second 64 d
@@ -548,14 +541,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     const uint32_t pRow = sP + hd * AP_P + row * 128;
     const uint32_t swz = static_cast<uint32_t>(row & 7);
     bool ok = true;
-    const bool rec = p.stamps && blockIdx.x == 0 && hd == 0 && quarter == 0 && lane == 0;
-    int nrec = 0;
-    auto stamp = [&](int tag) { if (rec && nrec < 256) { p.stamps[1024 + nrec * 2] = tag; p.stamps[1024 + nrec * 2 + 1] = clock64(); ++nrec; } };
     for (int j = 0; j < nT; ++j) {
       const int buf = j & 1, bph = (j >> 1) & 1;
-      stamp(1000 + j);
       if (!__all_sync(0xffffffffu, mbarWait(sFull + 8 * (hd * 2 + buf), bph, abortP, 9))) { ok = false; break; }
-      stamp(2000 + j);
       tcFenceAfter();
       const uint32_t sAddr = laneAddr + (hd * 2 + buf) * AP_BN;
       const int key0 = j * AP_BN;
@@ -589,10 +577,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         corr = fastExp2((m - mx) * sl2);
         m = mx;
       }
-      stamp(3000 + j);
       // P's buffer is free, and O holds every earlier tile, once P V_{j-1} has completed.
       if (!__all_sync(0xffffffffu, mbarWait(pEmpty + 8 * hd, (j & 1) ^ 1, abortP, 10))) { ok = false; break; }
-      stamp(4000 + j);
       if (__any_sync(0xffffffffu, corr != 1.0f)) {
         tcFenceAfter();
         l *= corr;
@@ -634,7 +620,6 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       l += sum;
       fenceProxyAsyncShared();
       mbarArrive(pReady + 8 * hd);
-      stamp(5000 + j);
     }
     if (ok && nT > 0 && !__all_sync(0xffffffffu, mbarWait(pEmpty + 8 * hd, (nT & 1) ^ 1, abortP, 11))) ok = false;
     if (ok) {
@@ -760,8 +745,6 @@ static int launchAt(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensor
   return TTB_OK;
 }
 
-static long long *g_atStamps = nullptr; // set by ttb_sdpa_tcgen05_stamps (diagnostic)
-
 // Returns -1 when the problem is outside what this kernel takes (the caller then uses another
 // kernel), otherwise a TTB status.
 int sdpaTcgen05Try(const void *q, const void *k, const void *v, void *out, int dtype, int64_t batch, int64_t hq,
@@ -794,7 +777,6 @@ int sdpaTcgen05Try(const void *q, const void *k, const void *v, void *out, int d
   p.causal = causal ? 1 : 0;
   p.fmt = dtype == kBF16 ? 1 : 0;
   p.scaleLog2 = scale * 1.4426950408889634f;
-  p.stamps = g_atStamps;
   p.splitLen = 0;
   p.partO = p.partM = p.partL = nullptr;
   double work = 4.0 * double(batch) * hq * sq * skv * headDim * (causal ? 0.5 : 1.0);
@@ -872,12 +854,15 @@ int sdpaTcgen05Try(const void *q, const void *k, const void *v, void *out, int d
 
 } // namespace ttb
 
-// Diagnostic: with a device buffer of 2048 int64 registered here, CTA 0 of the two-heads kernel
-// records (tag, clock64) pairs of its MMA thread (first 1024 slots) and first softmax thread.
-extern "C" int ttb_sdpa_tcgen05_stamps(void *device_buffer_2048_i64) {
-  ttb::g_atStamps = static_cast<long long *>(device_buffer_2048_i64);
+namespace ttb {
+// Reads and / or writes this file's copies of the status word and the wait limit (current device).
+int sdpaTcgen05StatusAccess(int *status, const int *newValue, const long long *waitCycles) {
+  if (status) TTB_CUDA(cudaMemcpyFromSymbol(status, g_tcStatus, sizeof(int)));
+  if (newValue) TTB_CUDA(cudaMemcpyToSymbol(g_tcStatus, newValue, sizeof(int)));
+  if (waitCycles) TTB_CUDA(cudaMemcpyToSymbol(g_tcWaitCycles, waitCycles, sizeof(long long)));
   return TTB_OK;
 }
+} // namespace ttb
 
 extern "C" int ttb_sdpa_tcgen05_status(int *status) {
   TTB_CHECK(status != nullptr, "null argument");

@@ -146,7 +146,7 @@ struct SymmParams {
   uint32_t token;            // first barrier waits for token, second for token + 1
   int oneShot;               // every rank reduces the whole operand itself: no push, no second barrier
   int *status;
-  unsigned long long *stamps; // diagnostic: globaltimer of block 0 at the phase boundaries, or null
+  long long waitCycles; // how long a barrier may spin on a peer's flag before it gives up (SM clock cycles)
 };
 
 __device__ __forceinline__ void symmStoreFlag(uint32_t *p, uint32_t v) {
@@ -171,7 +171,7 @@ __device__ __forceinline__ void symmBarrier(const SymmParams &p, int which, uint
     const long long start = clock64();
     uint32_t spins = 0;
     while (static_cast<int32_t>(symmLoadFlag(mine) - token) < 0) {
-      if ((++spins & 255u) == 0 && clock64() - start > 2000000000ll) {
+      if ((++spins & 255u) == 0 && clock64() - start > p.waitCycles) {
         atomicCAS(p.status, 0, ((which + 1) << 8) | (t + 1));
         break;
       }
@@ -197,14 +197,6 @@ __global__ void __launch_bounds__(SYMM_THREADS)
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   const size_t first = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
 
-  auto stamp = [&](int k) {
-    if (p.stamps && blockIdx.x == 0 && threadIdx.x == 0) {
-      unsigned long long t;
-      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-      p.stamps[k] = t;
-    }
-  };
-  stamp(0);
   // A: publish the local operand (already in place when the producer wrote into the workspace).
   if (!STAGED) {
     uint4 *myData = reinterpret_cast<uint4 *>(p.ws[p.rank] + p.dataOff);
@@ -219,9 +211,7 @@ __global__ void __launch_bounds__(SYMM_THREADS)
       }
     }
   }
-  stamp(1);
   symmBarrier(p, 0, p.token);
-  stamp(2);
 
   // B: reduce the own slice, U vectors per thread and iteration with every load issued before
   // the first use, so that a thread has U * n remote loads in flight.
@@ -287,10 +277,8 @@ __global__ void __launch_bounds__(SYMM_THREADS)
       }
     }
   }
-  stamp(3);
   if (p.oneShot) return;
   symmBarrier(p, 1, p.token + 1);
-  stamp(4);
 
   // C: the slices the peers pushed.
   {
@@ -301,21 +289,26 @@ __global__ void __launch_bounds__(SYMM_THREADS)
       for (size_t i = lo + first; i < hi; i += stride) out[i] = __ldcg(mine + i);
     }
   }
-  stamp(5);
 }
 
 template <typename T, bool RESIDUAL, int MODE, int NR>
 static int symmLaunch(const SymmParams &p, const void *in, const void *residual, void *out, size_t nvec, cudaStream_t st) {
   // All blocks of all ranks have to be resident at the same time (they wait for each other).
-  static int perSm[64] = {};
+  static std::mutex mu;
+  static int perSmOf[64] = {};
   int dev = 0;
   TTB_CUDA(cudaGetDevice(&dev));
   TTB_CHECK(dev >= 0 && dev < 64, "device ordinal out of range");
-  if (!perSm[dev]) {
-    int n = 0;
-    TTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, symmAllReduceKernel<T, RESIDUAL, MODE, NR>, SYMM_THREADS, 0));
-    TTB_CHECK(n >= 1, "all-reduce kernel does not fit on an SM");
-    perSm[dev] = n > 2 ? 2 : n;
+  int perSm[64];
+  {
+    std::lock_guard<std::mutex> lock(mu); // several threads may drive different devices of one mesh
+    if (!perSmOf[dev]) {
+      int n = 0;
+      TTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, symmAllReduceKernel<T, RESIDUAL, MODE, NR>, SYMM_THREADS, 0));
+      TTB_CHECK(n >= 1, "all-reduce kernel does not fit on an SM");
+      perSmOf[dev] = n > 2 ? 2 : n;
+    }
+    perSm[dev] = perSmOf[dev];
   }
   const size_t work = p.oneShot ? nvec : (nvec + p.n - 1) / p.n;
   size_t blocks = (work + SYMM_THREADS - 1) / SYMM_THREADS;
@@ -356,7 +349,7 @@ struct Symm {
   size_t maxBytes = 0; // largest operand
   uint32_t launches = 0;
   int *status = nullptr;
-  unsigned long long *stamps = nullptr; // 8 slots after the status word when TTB_SYMM_STAMPS=1
+  long long waitCycles = 2000000000ll; // about a second
 };
 
 static size_t symmTotalBytes(size_t maxBytes) { return SYMM_FLAG_BYTES + 4 * maxBytes; }
@@ -475,6 +468,15 @@ int ttb_symm_create_rank(void **symm, void *comm, int rank, int nranks, size_t m
   TTB_NCCL_READY();
   max_bytes = (max_bytes + 255) / 256 * 256;
   auto *s = new Symm();
+  // Whatever has been built is torn down again on every error return below.
+  struct Guard {
+    Symm *s;
+    char *handles = nullptr;
+    ~Guard() {
+      if (handles) cudaFree(handles);
+      if (s) ttb_symm_destroy(s);
+    }
+  } guard{s};
   s->rank = rank;
   s->n = nranks;
   s->ipc = true;
@@ -482,18 +484,17 @@ int ttb_symm_create_rank(void **symm, void *comm, int rank, int nranks, size_t m
   TTB_CUDA(cudaGetDevice(&s->device));
   char *local = nullptr;
   TTB_CUDA(cudaMalloc(reinterpret_cast<void **>(&local), symmTotalBytes(max_bytes)));
+  s->ws[rank] = local;
   TTB_CUDA(cudaMemset(local, 0, SYMM_FLAG_BYTES));
   TTB_CUDA(cudaMalloc(reinterpret_cast<void **>(&s->status), 128));
   TTB_CUDA(cudaMemset(s->status, 0, 128));
-  if (const char *e = std::getenv("TTB_SYMM_STAMPS")) {
-    if (e[0] == '1') s->stamps = reinterpret_cast<unsigned long long *>(s->status + 16);
-  }
   s->ws[rank] = local;
   // Exchange the IPC handles through the communicator the mesh already has.
   cudaIpcMemHandle_t mine;
   TTB_CUDA(cudaIpcGetMemHandle(&mine, local));
   char *devHandles = nullptr;
   TTB_CUDA(cudaMalloc(reinterpret_cast<void **>(&devHandles), sizeof(mine) * (nranks + 1)));
+  guard.handles = devHandles;
   cudaStream_t st = asStream(stream);
   TTB_CUDA(cudaMemcpyAsync(devHandles + sizeof(mine) * nranks, &mine, sizeof(mine), cudaMemcpyHostToDevice, st));
   TTB_NCCL(api.allGather(devHandles + sizeof(mine) * nranks, devHandles, sizeof(mine), ncclChar,
@@ -516,6 +517,8 @@ int ttb_symm_create_rank(void **symm, void *comm, int rank, int nranks, size_t m
   TTB_NCCL(api.allGather(devHandles + sizeof(mine) * nranks, devHandles, sizeof(mine), ncclChar,
                          static_cast<ncclComm_t>(comm), st));
   TTB_CUDA(cudaStreamSynchronize(st));
+  guard.handles = nullptr;
+  guard.s = nullptr; // handed to the caller
   TTB_CUDA(cudaFree(devHandles));
   *symm = s;
   return TTB_OK;
@@ -540,9 +543,6 @@ int ttb_symm_create_all(void **symms, int ndev, const int *devices, size_t max_b
     TTB_CUDA(cudaMemset(local, 0, SYMM_FLAG_BYTES));
     TTB_CUDA(cudaMalloc(reinterpret_cast<void **>(&s->status), 128));
     TTB_CUDA(cudaMemset(s->status, 0, 128));
-    if (const char *e = std::getenv("TTB_SYMM_STAMPS")) {
-      if (e[0] == '1') s->stamps = reinterpret_cast<unsigned long long *>(s->status + 16);
-    }
     s->ws[i] = local;
     all[i] = s;
     for (int j = 0; j < ndev; ++j) {
@@ -596,10 +596,28 @@ int ttb_symm_input_buffer(void *symm, size_t bytes, void **ptr) {
   return TTB_OK;
 }
 
-int ttb_symm_stamps(void *symm, unsigned long long *stamps8) {
-  TTB_CHECK(symm && stamps8, "null argument");
+int ttb_symm_set_wait_limit(void *symm, long long cycles) {
+  TTB_CHECK(symm != nullptr, "null argument");
+  static_cast<Symm *>(symm)->waitCycles = cycles > 0 ? cycles : 2000000000ll;
+  return TTB_OK;
+}
+
+int ttb_symm_launch_count(void *symm, uint32_t *launches) {
+  TTB_CHECK(symm && launches, "null argument");
+  *launches = static_cast<Symm *>(symm)->launches;
+  return TTB_OK;
+}
+
+int ttb_symm_set_launch_count(void *symm, uint32_t launches) {
+  TTB_CHECK(symm != nullptr, "null argument");
+  static_cast<Symm *>(symm)->launches = launches;
+  return TTB_OK;
+}
+
+int ttb_symm_clear_status(void *symm) {
+  TTB_CHECK(symm != nullptr, "null argument");
   auto *s = static_cast<Symm *>(symm);
-  TTB_CUDA(cudaMemcpy(stamps8, s->status + 16, 64, cudaMemcpyDeviceToHost));
+  TTB_CUDA(cudaMemset(s->status, 0, sizeof(int)));
   return TTB_OK;
 }
 
@@ -666,7 +684,7 @@ static int symmAllReduceImpl(void *symm, const void *in, const void *residual, v
     setLastError("symm_all_reduce_pushed: operand does not split into 16-byte aligned slices");
     return TTB_ERR_UNSUPPORTED;
   }
-  p.stamps = s->stamps;
+  p.waitCycles = s->waitCycles;
   const size_t nvec = bytes / 16;
   cudaStream_t st = asStream(stream);
   // The producer wrote the operand into this launch's data region (ttb_symm_input_buffer).

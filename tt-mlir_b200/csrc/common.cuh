@@ -59,6 +59,16 @@ int cudaFail(cudaError_t e, const char *what, const char *file, int line);
 
 inline cudaStream_t asStream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// While a GemmScratchScope is alive on the calling thread, the CUDA-core GEMM takes the scratch of its
+// split-K mode from [ptr, ptr + bytes) instead of the memory pool, and runs without split-K when that
+// is too small: nothing below the scope allocates.  Used by the entry points that promise not to.
+struct GemmScratchScope {
+  GemmScratchScope(void *ptr, size_t bytes);
+  ~GemmScratchScope();
+  // Active scope of this thread, if any: true and its range.
+  static bool current(void **ptr, size_t *bytes);
+};
+
 // Number of SMs of the current device (148 on B200); cached per device.
 int smCount();
 // Adds to the process-wide count of kernels launched by this library.

@@ -91,15 +91,30 @@ extern "C" {
 
 size_t ttb_conv2d_workspace_bytes(int dtype, int64_t n, int64_t h, int64_t w, int64_t c, int64_t o, int kh, int kw,
                                   int stride_h, int stride_w, const int *padding4, int dil_h, int dil_w, int groups) {
-  if (!padding4 || isPointwise(kh, kw, stride_h, stride_w, padding4, groups)) return 0;
+  // Sizes that make no sense, or whose byte count does not fit size_t, come back as SIZE_MAX: no
+  // allocation of that size succeeds and ttb_conv2d_static refuses it.
+  if (n == 0) return 0;
+  if (!padding4 || n < 0 || h <= 0 || w <= 0 || c <= 0 || o <= 0 || kh <= 0 || kw <= 0 || stride_h <= 0 || stride_w <= 0 ||
+      dil_h <= 0 || dil_w <= 0 || padding4[0] < 0 || padding4[1] < 0 || padding4[2] < 0 || padding4[3] < 0)
+    return SIZE_MAX;
+  if (isPointwise(kh, kw, stride_h, stride_w, padding4, groups)) return 0;
   int64_t ho = outDim(h, kh, stride_h, padding4[0], padding4[2], dil_h);
   int64_t wo = outDim(w, kw, stride_w, padding4[1], padding4[3], dil_w);
   if (ho <= 0 || wo <= 0) return 0;
   size_t es = dtypeSize(dtype);
-  size_t K = static_cast<size_t>(kh) * kw * c;
-  size_t weights = alignUp(static_cast<size_t>(o) * K * es, 256);
+  if (es == 0) return SIZE_MAX;
+  size_t K = 0, weights = 0, pixels = 0, col = 0;
+  if (__builtin_mul_overflow(static_cast<size_t>(kh) * static_cast<size_t>(kw), static_cast<size_t>(c), &K) ||
+      __builtin_mul_overflow(static_cast<size_t>(o), K, &weights) || __builtin_mul_overflow(weights, es, &weights) ||
+      weights > SIZE_MAX - 512)
+    return SIZE_MAX;
+  weights = alignUp(weights, 256);
   if (implicitGemmShape(dtype, c, o)) return weights; // only the reordered weights
-  return alignUp(static_cast<size_t>(n * ho * wo) * K * es, 256) + weights;
+  if (__builtin_mul_overflow(static_cast<size_t>(n), static_cast<size_t>(ho), &pixels) ||
+      __builtin_mul_overflow(pixels, static_cast<size_t>(wo), &pixels) || __builtin_mul_overflow(pixels, K, &col) ||
+      __builtin_mul_overflow(col, es, &col) || col > SIZE_MAX - 512 - weights)
+    return SIZE_MAX;
+  return alignUp(col, 256) + weights;
 }
 
 int ttb_conv2d(const void *x, const void *weight, const void *bias, void *out, int dtype, int bias_dtype, int64_t n,
@@ -116,6 +131,9 @@ int ttb_conv2d_fused(const void *x, const void *weight, const void *bias, void *
   TTB_CHECK(x && weight && out && padding4, "null argument");
   TTB_CHECK(groups == 1, "grouped convolution is not supported");
   TTB_CHECK(kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0 && dil_h > 0 && dil_w > 0, "bad convolution geometry");
+  if (n == 0) return TTB_OK; // an empty batch: nothing to compute
+  TTB_CHECK(n > 0 && h > 0 && w > 0 && c > 0 && o > 0, "convolution extents must be positive");
+  TTB_CHECK(padding4[0] >= 0 && padding4[1] >= 0 && padding4[2] >= 0 && padding4[3] >= 0, "negative padding");
   size_t es = dtypeSize(dtype);
   TTB_CHECK(dtype == kBF16 || dtype == kF32 || dtype == kF16, "conv2d needs a float dtype");
   if (isPointwise(kh, kw, stride_h, stride_w, padding4, groups)) {
@@ -172,15 +190,21 @@ int ttb_conv2d_static(const void *x, const void *weight, const void *bias, void 
                       int64_t n, int64_t h, int64_t w, int64_t c, int64_t o, int kh, int kw, int stride_h, int stride_w,
                       const int *padding4, int dil_h, int dil_w, int groups, int act, void *stream) {
   TTB_CHECK(padding4 != nullptr, "null argument");
+  // The built-in buffer is split in two: the convolution's workspace in front, and a fixed tail for the
+  // partial sums of the CUDA-core contraction's split-K mode (what it would otherwise allocate).
+  constexpr size_t kGemmTail = TTB_CONV2D_STATIC_GEMM_BYTES;
+  constexpr size_t kConvPart = TTB_CONV2D_STATIC_SCRATCH_BYTES - kGemmTail;
   size_t need = ttb_conv2d_workspace_bytes(dtype, n, h, w, c, o, kh, kw, stride_h, stride_w, padding4, dil_h, dil_w, groups);
-  if (need > TTB_CONV2D_STATIC_SCRATCH_BYTES) {
-    setLastError("conv2d_static: this convolution needs " + std::to_string(need) + " bytes of scratch, the built-in buffer has " +
-                 std::to_string(static_cast<size_t>(TTB_CONV2D_STATIC_SCRATCH_BYTES)) +
-                 "; use ttb_conv2d with a caller-provided workspace");
+  if (need > kConvPart) {
+    setLastError(need == SIZE_MAX
+                     ? std::string("conv2d_static: bad convolution extents")
+                     : "conv2d_static: this convolution needs " + std::to_string(need) + " bytes of scratch, the built-in buffer has " +
+                           std::to_string(kConvPart) + "; use ttb_conv2d with a caller-provided workspace");
     return TTB_ERR_INVALID;
   }
   // The array's name is only a host-side handle; the kernels need its device address, which
-  // differs per GPU.  It is looked up once per device, with that device current.
+  // differs per GPU.  It is looked up once per device, with that device current, and kept for the
+  // life of the process (the library does not outlive a cudaDeviceReset of a device it ran on).
   static std::mutex mu;
   static void *scratchOf[64] = {};
   int dev = -1;
@@ -197,6 +221,8 @@ int ttb_conv2d_static(const void *x, const void *weight, const void *bias, void 
     }
     scratch = scratchOf[dev];
   }
+  // Every contraction below this call takes its split-K scratch from the tail (or runs unsplit).
+  GemmScratchScope noAlloc(static_cast<char *>(scratch) + kConvPart, kGemmTail);
   return ttb_conv2d(x, weight, bias, out, dtype, bias_dtype, n, h, w, c, o, kh, kw, stride_h, stride_w, padding4, dil_h,
                     dil_w, groups, act, need ? scratch : nullptr, stream);
 }

@@ -200,6 +200,31 @@ int ttb_free(void *ptr, void *stream) {
   return TTB_OK;
 }
 
+int ttb_mempool_stats(uint64_t *reserved, uint64_t *used, uint64_t *used_high, int reset_high) {
+  int dev = 0;
+  TTB_CUDA(cudaGetDevice(&dev));
+  cudaMemPool_t pool;
+  TTB_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+  uint64_t v = 0;
+  if (reserved) {
+    TTB_CUDA(cudaMemPoolGetAttribute(pool, cudaMemPoolAttrReservedMemCurrent, &v));
+    *reserved = v;
+  }
+  if (used) {
+    TTB_CUDA(cudaMemPoolGetAttribute(pool, cudaMemPoolAttrUsedMemCurrent, &v));
+    *used = v;
+  }
+  if (used_high) {
+    TTB_CUDA(cudaMemPoolGetAttribute(pool, cudaMemPoolAttrUsedMemHigh, &v));
+    *used_high = v;
+  }
+  if (reset_high) {
+    uint64_t zero = 0; // the only value the attribute accepts: the mark falls back to the current use
+    TTB_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrUsedMemHigh, &zero));
+  }
+  return TTB_OK;
+}
+
 int ttb_host_alloc_pinned(void **ptr, size_t bytes) {
   TTB_CHECK(ptr != nullptr, "ptr is null");
   TTB_CUDA(cudaMallocHost(ptr, bytes ? bytes : 16));

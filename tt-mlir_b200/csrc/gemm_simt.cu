@@ -15,6 +15,29 @@ namespace ttb {
 
 constexpr int BM = 64, BN = 64, BK = 16;
 
+namespace {
+thread_local void *t_scratchPtr = nullptr;
+thread_local size_t t_scratchBytes = 0;
+thread_local bool t_scratchActive = false;
+} // namespace
+
+GemmScratchScope::GemmScratchScope(void *ptr, size_t bytes) {
+  t_scratchPtr = ptr;
+  t_scratchBytes = bytes;
+  t_scratchActive = true;
+}
+GemmScratchScope::~GemmScratchScope() {
+  t_scratchActive = false;
+  t_scratchPtr = nullptr;
+  t_scratchBytes = 0;
+}
+bool GemmScratchScope::current(void **ptr, size_t *bytes) {
+  if (!t_scratchActive) return false;
+  *ptr = t_scratchPtr;
+  *bytes = t_scratchBytes;
+  return true;
+}
+
 template <typename T, typename TC>
 __global__ void __launch_bounds__(256)
     gemmSimtKernel(const T *__restrict__ a, const T *__restrict__ b, const void *__restrict__ bias, int biasDt,
@@ -158,14 +181,30 @@ static int launchSimt(const void *a, const void *b, const void *bias, int biasDt
     kPer = ((k + splitK - 1) / splitK + BK - 1) / BK * BK;
     splitK = static_cast<int>((k + kPer - 1) / kPer);
   }
+  bool ownScratch = false;
   if (splitK > 1) {
     const size_t counters = (static_cast<size_t>(tilesM * tilesN) * sizeof(unsigned) + 255) / 256 * 256;
     const size_t bytes = counters + static_cast<size_t>(tilesM * tilesN) * splitK * BM * BN * sizeof(float);
-    int rc = ttb_malloc(&scratch, bytes, st);
-    if (rc) return rc;
-    TTB_CUDA(cudaMemsetAsync(scratch, 0, counters, st));
-    arrivals = static_cast<unsigned *>(scratch);
-    partials = reinterpret_cast<float *>(static_cast<char *>(scratch) + counters);
+    void *given = nullptr;
+    size_t givenBytes = 0;
+    if (GemmScratchScope::current(&given, &givenBytes)) {
+      // the caller forbids allocation: its buffer, or no split at all
+      if (given && givenBytes >= bytes) {
+        scratch = given;
+      } else {
+        splitK = 1;
+        kPer = k;
+      }
+    } else {
+      int rc = ttb_malloc(&scratch, bytes, st);
+      if (rc) return rc;
+      ownScratch = true;
+    }
+    if (scratch) {
+      TTB_CUDA(cudaMemsetAsync(scratch, 0, counters, st));
+      arrivals = static_cast<unsigned *>(scratch);
+      partials = reinterpret_cast<float *>(static_cast<char *>(scratch) + counters);
+    }
   }
   dim3 grid(static_cast<unsigned>(tilesN), static_cast<unsigned>(tilesM), static_cast<unsigned>(splitK > 1 ? splitK : batch));
   {
@@ -174,7 +213,7 @@ static int launchSimt(const void *a, const void *b, const void *bias, int biasDt
                        biasDt, static_cast<TC *>(c), m, n, k, asM, asK, bsK, bsN, aBatch, bBatch, act, roundSteps, splitK, kPer,
                        partials, arrivals));
   }
-  if (scratch) {
+  if (ownScratch) {
     int rc = ttb_free(scratch, st); // stream-ordered: released once the kernel has run
     if (rc) return rc;
   }

@@ -113,7 +113,6 @@ struct TcParams {
   int cTw, cTilesX, cTilesY;
   int64_t cTilesM; // images x cTilesY x cTilesX
   int fmt; // 1 bf16, 0 f16
-  int debug; // diagnostic: 1 = epilogue loads TMEM but skips math and stores, 2 = epilogue only hands the buffer back
 };
 
 struct PushMaps {
@@ -403,7 +402,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
 #pragma unroll 1
           for (int cc = (shared && helper) ? 1 : 0; cc < 2; cc += shared ? 2 : 1) {
             const int64_t col0 = n0 + cc * CH;
-            if (col0 >= segN || p.debug == 2) break; // warp-uniform
+            if (col0 >= segN) break; // warp-uniform
             const uint32_t buf = stageOut;
             const uint32_t rowAddr = buf + static_cast<uint32_t>(lane) * 128u;
 #pragma unroll
@@ -451,7 +450,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
 #pragma unroll 1
       for (int cc = dualDone ? BN / CH : ((shared && helper) ? 1 : 0); cc < BN / CH; cc += shared ? 2 : 1) {
         const int64_t col0 = n0 + cc * CH;
-        if (col0 >= segN || p.debug == 2) break; // warp-uniform
+        if (col0 >= segN) break; // warp-uniform
         const uint32_t buf = stageOut + (EPW == 4 ? (chunkIt & 1u) * 4096u : 0u);
         const uint32_t rowAddr = buf + static_cast<uint32_t>(lane) * 128u;
         // The second operand's 32 x 128 B block is brought into the staging buffer by TMA (the
@@ -483,10 +482,6 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
           uint32_t r[HW];
           tcLoad32(taddrRow + static_cast<uint32_t>(cc * CH + l * HW), r);
           tcWaitLd();
-          if (p.debug == 1) {
-            if (r[0] == 0x7fc12345u && r[HW - 1] == 0x7fc54321u) c[0] = TC(0); // keeps the loads alive
-            continue;
-          }
           uint4 ev[sizeof(TC) == 2 && !PLAIN ? HW / 8 : 1] = {};
           if constexpr (!PLAIN && sizeof(TC) == 2) {
             if (useExtra) {
@@ -600,7 +595,6 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
         }
         if (!alive) break;
         if (useExtra) extraPhase ^= 1u;
-        if (p.debug == 1) continue;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
@@ -793,10 +787,6 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   p.segCum[0] = p.segCum[1] = p.segCum[2] = static_cast<int>((n + bn - 1) / bn);
   p.segN[0] = p.segN[1] = p.segN[2] = n;
   p.fmt = abDtype == kBF16 ? 1 : 0;
-  {
-    const char *dbg = std::getenv("TTB_TC_DEBUG");
-    p.debug = dbg ? std::atoi(dbg) : 0;
-  }
   double flops = 2.0 * double(m) * double(n) * double(k);
   double bytes = (double(m) * k + double(n) * k) * 2 + double(m) * n * dtypeSize(cDtype) * (extraOp ? 2 : 1);
   ProfScope prof("gemm_tcgen05", flops, bytes, stream);
@@ -840,7 +830,6 @@ int gemmTcgen05SwigluTry(const void *a, const void *wGate, const void *wUp, void
   p.segCum[0] = p.segCum[1] = p.segCum[2] = static_cast<int>((n + BN / 2 - 1) / (BN / 2));
   p.segN[0] = p.segN[1] = p.segN[2] = n;
   p.fmt = dtype == kBF16 ? 1 : 0;
-  p.debug = 0;
   // both projections' FLOPs; A and both weights once, the result once
   ProfScope prof("gemm_tcgen05", 4.0 * double(m) * double(n) * double(k), (double(m) * k + 2.0 * double(n) * k + double(m) * n) * 2, stream);
   const CUtensorMap more[4] = {mu, mc, mu, mc};
@@ -909,7 +898,6 @@ int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, c
     }
   }
   p.fmt = abDtype == kBF16 ? 1 : 0;
-  p.debug = 0;
   ProfScope prof("gemm_tcgen05", flops, bytes, stream);
   const CUtensorMap more[4] = {mb[1], mc[1], mb[2], mc[2]};
 #define TTB_TCG(BNv, TCv) return launchTc<BNv, TCv, true>(ma, mb[0], mc[0], mc[0], c[0], p, stream, more)
@@ -999,7 +987,6 @@ int convTcgen05Try(const void *x, const void *wre, const void *bias, void *out, 
   p.segCum[0] = p.segCum[1] = p.segCum[2] = static_cast<int>((o + bn - 1) / bn);
   p.segN[0] = p.segN[1] = p.segN[2] = o;
   p.fmt = dtype == kBF16 ? 1 : 0;
-  p.debug = 0;
   // algorithmic bytes: the input and the output once each (plus the residual operand), the weights
   ProfScope prof("conv2d_tcgen05", 2.0 * double(m) * o * k,
                  (double(n) * h * w * c + double(o) * k + double(m) * o * (extraOp ? 2 : 1)) * 2, stream);
@@ -1025,4 +1012,42 @@ extern "C" int ttb_gemm_tcgen05_status(int *status) {
   TTB_CUDA(cudaDeviceSynchronize());
   TTB_CUDA(cudaMemcpyFromSymbol(status, ttb::g_tcStatus, sizeof(int)));
   return TTB_OK;
+}
+
+namespace ttb {
+int sdpaTcgen05StatusAccess(int *status, const int *newValue, const long long *waitCycles);
+}
+
+// Both tensor-core kernels' status words of the current device in one call, without a device-wide
+// synchronise (the caller has synchronised the streams it cares about).  clear != 0 resets a word
+// that was set, so one timeout is reported once.
+extern "C" int ttb_tcgen05_status(int *gemm_status, int *sdpa_status, int clear) {
+  int g = 0, a = 0;
+  TTB_CUDA(cudaMemcpyFromSymbol(&g, ttb::g_tcStatus, sizeof(int)));
+  int rc = ttb::sdpaTcgen05StatusAccess(&a, nullptr, nullptr);
+  if (rc) return rc;
+  const int zero = 0;
+  if (clear && g) TTB_CUDA(cudaMemcpyToSymbol(ttb::g_tcStatus, &zero, sizeof(int)));
+  if (clear && a) {
+    rc = ttb::sdpaTcgen05StatusAccess(nullptr, &zero, nullptr);
+    if (rc) return rc;
+  }
+  if (gemm_status) *gemm_status = g;
+  if (sdpa_status) *sdpa_status = a;
+  return TTB_OK;
+}
+
+// Writes the status words as a timed-out launch would (or clears them with zeros).  Exists so that
+// the reporting path above the kernels can be exercised without making a GPU wait run out.
+extern "C" int ttb_tcgen05_set_status(int gemm_status, int sdpa_status) {
+  TTB_CUDA(cudaMemcpyToSymbol(ttb::g_tcStatus, &gemm_status, sizeof(int)));
+  return ttb::sdpaTcgen05StatusAccess(nullptr, &sdpa_status, nullptr);
+}
+
+// The limit of every bounded wait in the tensor-core kernels on the current device, in SM clock
+// cycles; cycles <= 0 restores the default (2e9, about a second).
+extern "C" int ttb_tcgen05_set_wait_limit(long long cycles) {
+  if (cycles <= 0) cycles = 2000000000ll;
+  TTB_CUDA(cudaMemcpyToSymbol(ttb::g_tcWaitCycles, &cycles, sizeof(cycles)));
+  return ttb::sdpaTcgen05StatusAccess(nullptr, nullptr, &cycles);
 }

@@ -11,6 +11,9 @@ namespace ttb {
 // 0 ok; otherwise (where << 8) | 1 of the first wait that gave up.  One word per translation unit
 // (the library is built without relocatable device code); each kernel file exports its own reader.
 static __device__ int g_tcStatus;
+// How long a wait may spin before it gives up, in SM clock cycles (about a second by default).
+// Per translation unit like the status word; ttb_tcgen05_set_wait_limit writes every copy.
+static __device__ long long g_tcWaitCycles = 2000000000ll;
 
 // ---- PTX wrappers ----------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smemU32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -33,8 +36,8 @@ __device__ __forceinline__ bool mbarTryWait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Returns false when the barrier did not flip within ~1 s or another role of
-// this CTA already gave up; the caller then leaves its loop.
+// Bounded wait.  Returns false when the barrier did not flip within g_tcWaitCycles (~1 s) or another
+// role of this CTA already gave up; the caller then leaves its loop.
 __device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity, volatile int *abortFlag, int where) {
   if (mbarTryWait(bar, parity)) return true;
   const long long start = clock64();
@@ -42,7 +45,7 @@ __device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity, volatile
   while (!mbarTryWait(bar, parity)) {
     if ((++spins & 1023u) == 0) {
       if (*abortFlag) return false;
-      if (clock64() - start > 2000000000ll) {
+      if (clock64() - start > *static_cast<volatile long long *>(&g_tcWaitCycles)) {
         *abortFlag = 1;
         atomicCAS(&g_tcStatus, 0, (where << 8) | 1);
         return false;

@@ -2465,6 +2465,18 @@ TensorPtr Executor::tryGemmPush(const TensorPtr &a, const TensorPtr &b, const fb
   const int64_t n = dev->worldSize;
   const size_t bytes = static_cast<size_t>(M) * N * dataTypeSize(dt);
   if (M % n != 0 || (M / n) % 128 != 0 || bytes % (16 * n) != 0 || !symmReady(bytes)) return nullptr;
+  // Everything that decides between this path and the ordinary one must be the same on every rank
+  // (ranks may be separate processes, and a rank that produced an ordinary tensor while its peers
+  // pushed would be summed from the wrong regions).  So the shape rules of the tensor-core kernel and
+  // the switch that disables it are checked here, from facts all ranks share, and a refusal for any
+  // other reason (an operand that is not 16-byte aligned on one rank) is an error, not a fallback.
+  static const bool tensorCoreOff = [] {
+    const char *e = std::getenv("TTB_DISABLE_TCGEN05");
+    return e && e[0] && std::strcmp(e, "0") != 0;
+  }();
+  if (tensorCoreOff || K % 8 != 0 || K < 8 || N < 8 || (N * static_cast<int64_t>(dataTypeSize(dt))) % 16 != 0 ||
+      M * N * K < (1ll << 18) || M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff)
+    return nullptr;
   auto t = std::make_shared<TensorImpl>();
   t->shape = refShape(outRef);
   t->stride = denseStrides(t->shape);
@@ -2473,18 +2485,15 @@ TensorPtr Executor::tryGemmPush(const TensorPtr &a, const TensorPtr &b, const fb
   t->layout = refLayout(outRef);
   t->device = dev;
   t->pushedForAllReduce = true;
-  bool ok = true;
   eachRank([&](size_t i, const RankCtx &r) {
-    if (!ok) return;
     void *targets[8] = {};
     int rank = 0, nranks = 0;
     TTB_CALL(ttb_symm_push_targets(r.symm, bytes, targets, &rank, &nranks));
     int rc = ttb_gemm_push(a->shards[i]->ptr, b->shards[i]->ptr, targets, nranks, ttbDtype(dt), M, N, K, r.stream);
-    if (rc == TTB_ERR_UNSUPPORTED && i == 0) {
-      ok = false; // nothing was launched on any rank yet: the caller takes the ordinary path
-      return;
+    if (rc != TTB_OK) {
+      TTRT_FATAL("ttb_gemm_push failed (", rc, ") on mesh coordinate ", r.meshRank, ": ", ttb_last_error(),
+                 " -- the other ranks may already have taken the pushed path, so there is no falling back");
     }
-    if (rc != TTB_OK) TTRT_FATAL("ttb_gemm_push failed (", rc, "): ", ttb_last_error());
     auto buf = std::make_shared<Buffer>();
     TTB_CALL(ttb_symm_input_buffer(r.symm, bytes, &buf->ptr)); // the region the partials land in; never read as a matrix
     buf->bytes = bytes;
@@ -2492,7 +2501,7 @@ TensorPtr Executor::tryGemmPush(const TensorPtr &a, const TensorPtr &b, const fb
     buf->kind = Buffer::Kind::Borrowed;
     t->shards.push_back(buf);
   });
-  return ok ? t : nullptr;
+  return t;
 }
 
 TensorPtr Executor::allocForAllReduce(const fbt::TensorRef *ref) {

@@ -909,9 +909,21 @@ static void syncDevice(const std::shared_ptr<DeviceImpl> &d) {
     if (r.symm) {
       int status = 0;
       TTB_CALL(ttb_symm_status(r.symm, &status));
-      TTRT_ASSERT(status == 0, "a peer-memory all-reduce gave up waiting for rank ", (status & 0xff) - 1, " in phase ",
-                  status >> 8, "; results since then are invalid");
+      if (status != 0) {
+        // Reported once: the word is cleared so that the collectives after this one are judged on their own.
+        TTB_CALL(ttb_symm_clear_status(r.symm));
+        TTRT_FATAL("a peer-memory all-reduce gave up waiting for rank ", (status & 0xff) - 1, " in phase ", status >> 8,
+                   "; results since that launch are invalid");
+      }
     }
+    // The tensor-core kernels (GEMM, convolution, attention) bound every wait; one that ran out left
+    // output tiles unwritten.  Reported once per timeout (the words are cleared on reading).
+    int gemmStatus = 0, sdpaStatus = 0;
+    TTB_CALL(ttb_tcgen05_status(&gemmStatus, &sdpaStatus, /*clear=*/1));
+    TTRT_ASSERT(gemmStatus == 0, "a tensor-core GEMM / convolution launch gave up waiting (role ", gemmStatus >> 8,
+                ": 1 loader, 2-3 MMA issuer, 4-5 epilogue); its output is incomplete");
+    TTRT_ASSERT(sdpaStatus == 0, "a tensor-core attention launch gave up waiting (site ", sdpaStatus >> 8,
+                "); its output is incomplete");
   }
 }
 

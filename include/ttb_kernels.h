@@ -306,6 +306,23 @@ TTB_API int ttb_gemm_fused(const void *a, const void *b, const void *bias, void 
                            int bias_dtype, int c_dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                            int trans_a, int trans_b, int64_t a_batch_stride, int64_t b_batch_stride,
                            int act, int round_steps, const void *extra, int extra_op, void *stream);
+/* Quantized contraction: the ::ttnn::matmul / ::ttnn::linear call of runtime/lib/ttnn/operations/
+ * matmul/matmul.cpp:75-80 when its operands are quantized (8-bit integers; the compiler moves the
+ * dequantize below the op, lib/Dialect/TTIR/Transforms/QuantDequantConversion.cpp).  c = a b with exact
+ * 32-bit integer accumulation; operands Int8 or UInt8, layouts as ttb_gemm.  c_dtype Int32 stores the
+ * accumulators.  A float c_dtype stores round(float(acc) * scale) -- the dequantize op that follows,
+ * fused: scale = deq_scale[column] (per output channel, f32) or deq_scalar when deq_scale is null.
+ * The weight layout (trans_b, no trans_a, batch 1, k a multiple of 16) runs on the tensor cores
+ * (tcgen05.mma kind::i8); everything else on a CUDA-core kernel.  Results are exact integers, so the two
+ * agree bit for bit.  ttb_gemm_i8_simt forces the CUDA-core kernel (cross-check). */
+TTB_API int ttb_gemm_i8(const void *a, const void *b, void *c, int a_dtype, int b_dtype, int c_dtype,
+                        int64_t batch, int64_t m, int64_t n, int64_t k, int trans_a, int trans_b,
+                        int64_t a_batch_stride, int64_t b_batch_stride, const float *deq_scale,
+                        float deq_scalar, void *stream);
+TTB_API int ttb_gemm_i8_simt(const void *a, const void *b, void *c, int a_dtype, int b_dtype, int c_dtype,
+                             int64_t batch, int64_t m, int64_t n, int64_t k, int trans_a, int trans_b,
+                             int64_t a_batch_stride, int64_t b_batch_stride, const float *deq_scale,
+                             float deq_scalar, void *stream);
 /* Health of the tensor-core kernel: every wait inside it is bounded, and a wait that gives up
  * records where.  *status == 0 means no launch of this process has timed out.  Synchronises. */
 TTB_API int ttb_gemm_tcgen05_status(int *status);
@@ -335,6 +352,17 @@ TTB_API int ttb_conv2d_fused(const void *x, const void *weight, const void *bias
                              int kw, int stride_h, int stride_w, const int *padding4, int dil_h, int dil_w,
                              int groups, int act, const void *extra, int extra_op, void *workspace,
                              void *stream);
+
+/* Convolution on quantized operands: the ::ttnn::conv2d call of runtime/lib/ttnn/operations/conv/
+ * conv2d.cpp:16-94 when input and weight are quantized (8-bit integers; the compiler gives the op an i32
+ * accumulator result type, lib/Dialect/TTIR/IR/TTIROps.cpp:1516-1577).  Layouts as ttb_conv2d; exact
+ * 32-bit integer accumulation.  out_dtype Int32 stores the accumulators; a float out_dtype stores
+ * round(float(acc) * scale), scale = deq_scale[output channel] or deq_scalar (the dequantize that follows,
+ * fused).  `workspace`: ttb_conv2d_workspace_bytes with the input's dtype (0 for pointwise). */
+TTB_API int ttb_conv2d_i8(const void *x, const void *weight, void *out, int x_dtype, int w_dtype, int out_dtype,
+                          int64_t n, int64_t h, int64_t w, int64_t c, int64_t o, int kh, int kw, int stride_h,
+                          int stride_w, const int *padding4, int dil_h, int dil_w, int groups,
+                          const float *deq_scale, float deq_scalar, void *workspace, void *stream);
 
 /* conv2d for callers that must not allocate.  No counterpart in the reference: tt-mlir's
  * runtime always lets the device library allocate its own intermediates.

@@ -135,7 +135,9 @@ class OracleBuilder:
         return _map(lambda t: ops.requantize(t, in_scale, in_zp, out_scale, out_zp, dt, self.clamp_i8), x)
 
     # ---- contractions
-    def matmul(self, a, b, transpose_a=False, transpose_b=False, activation=None, loc=None):
+    def matmul(self, a, b, transpose_a=False, transpose_b=False, activation=None, out_dtype=None, loc=None):
+        if out_dtype is not None and not TORCH_DTYPE[out_dtype].is_floating_point:
+            return _map(lambda x, y: ops.int_matmul(x, y, transpose_a, transpose_b, TORCH_DTYPE[out_dtype]), a, b)
         return _map(lambda x, y: ops.matmul(x, y, transpose_a, transpose_b, activation), a, b)
 
     def linear(self, a, b, bias=None, transpose_a=False, transpose_b=False, activation=None, loc=None):
@@ -144,8 +146,11 @@ class OracleBuilder:
         return _map(lambda x, y, z: ops.linear(x, y, z, transpose_a, transpose_b, activation), a, b, bias)
 
     def conv2d(self, x, w, bias, batch, height, width, stride=(1, 1), padding=(0, 0, 0, 0), dilation=(1, 1), groups=1,
-               loc=None):
+               out_dtype=None, loc=None):
         pad = list(padding) if len(padding) == 4 else [padding[0], padding[1], padding[0], padding[1]]
+        if out_dtype is not None and not TORCH_DTYPE[out_dtype].is_floating_point:
+            return _map(lambda t, ww: ops.int_conv2d(t, ww, batch, height, width, stride, pad, dilation, groups,
+                                                     TORCH_DTYPE[out_dtype]), x, w)
         if bias is None:
             return _map(lambda t, ww: ops.conv2d(t, ww, None, batch, height, width, stride, pad, dilation, groups), x, w)
         return _map(lambda t, ww, bb: ops.conv2d(t, ww, bb, batch, height, width, stride, pad, dilation, groups), x, w, bias)

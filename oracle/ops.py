@@ -137,6 +137,19 @@ def matmul(a, b, transpose_a=False, transpose_b=False, activation=None):
     return _hoist(fn, a.dtype, a, b)
 
 
+def int_matmul(a, b, transpose_a=False, transpose_b=False, out_dtype=torch.int32):
+    """Matmul on quantized (integer) operands with an Int32 accumulator, which is what the CPU-hoist
+    path computes after widening integers to i32 (HoistCPUOps.cpp:78-93) and what the quantized
+    convolution's i32 result type prescribes (lib/Dialect/TTIR/IR/TTIROps.cpp:1516-1577).  Evaluated in
+    f64, which is exact here: |a b| <= 2^14 per product and sums stay far below 2^53."""
+    x, y = a.to(torch.float64), b.to(torch.float64)
+    if transpose_a:
+        x = x.transpose(-2, -1)
+    if transpose_b:
+        y = y.transpose(-2, -1)
+    return torch.matmul(x, y).to(torch.int64).to(out_dtype)
+
+
 def linear(a, b, bias=None, transpose_a=False, transpose_b=False, activation=None):
     def fn(x, y, z=None):
         if transpose_a:
@@ -175,6 +188,21 @@ def conv2d(x, w, bias, batch, height, width, stride=(1, 1), padding=(0, 0, 0, 0)
     if bias is None:
         return _hoist(fn, x.dtype, x, w)
     return _hoist(fn, x.dtype, x, w, bias)
+
+
+def int_conv2d(x, w, batch, height, width, stride=(1, 1), padding=(0, 0, 0, 0), dilation=(1, 1), groups=1,
+               out_dtype=torch.int32):
+    """conv2d on quantized (integer) operands with an Int32 accumulator (the result type the compiler
+    gives the quantized convolution, lib/Dialect/TTIR/IR/TTIROps.cpp:1516-1577).  Same layouts as conv2d;
+    evaluated in f64, which is exact for these magnitudes."""
+    c = w.shape[1] * groups
+    flat = x.dim() == 4 and x.shape[0] == 1 and x.shape[1] == 1 and x.shape[2] == batch * height * width
+    t = x.to(torch.float64).reshape(batch, height, width, c).permute(0, 3, 1, 2)
+    pt, pl, pb, pr = padding
+    t = F.pad(t, (pl, pr, pt, pb))
+    r = F.conv2d(t, w.to(torch.float64), stride=tuple(stride), padding=0, dilation=tuple(dilation), groups=groups)
+    r = r.permute(0, 2, 3, 1).to(torch.int64).to(out_dtype)
+    return r.reshape(1, 1, -1, r.shape[-1]) if flat else r.contiguous()
 
 
 # ---- normalisation / reductions -------------------------------------------------------------------

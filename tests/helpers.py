@@ -151,3 +151,53 @@ class KernelHarness:
         self._bufs = []
         self.lib.ttb_stream_sync(self.stream)
         self.lib.ttb_stream_destroy(self.stream)
+
+
+class TeacherForcedOracle(OracleBuilder):
+    """The oracle run op by op on the GPU's own operands.
+
+    `gpu_outputs` maps an op's location string (as the debug hooks report it, 'loc("name")') to the
+    tensor the GPU produced there.  Every graph op that carries a `loc` is evaluated by the oracle on
+    the values handed on so far, compared with the GPU's output of the same op (the comparison goes to
+    `self.report[name]`), and then REPLACED by the GPU's output, so that the next op sees exactly what
+    the GPU's next kernel saw.  What is measured per op is then the arithmetic of that one kernel, not
+    the accumulated effect of earlier single-ulp rounding differences."""
+
+    PASS_THROUGH = {"input", "output", "results"}
+
+    def __init__(self, inputs, gpu_outputs, mesh_shape=(1, 1)):
+        super().__init__(inputs, mesh_shape=mesh_shape)
+        self._gpu = gpu_outputs
+        self.report = {}
+
+    def __getattribute__(self, name):
+        attr = super().__getattribute__(name)
+        if name.startswith("_") or name in TeacherForcedOracle.PASS_THROUGH or not callable(attr):
+            return attr
+
+        def wrapped(*args, **kw):
+            res = attr(*args, **kw)
+            loc = kw.get("loc")
+            got = self._gpu.get(f'loc("{loc}")') if loc else None
+            if got is None or not hasattr(res, "t") or isinstance(res.t, list):
+                return res
+            want = res.t
+            got = got.reshape(want.shape)
+            self.report[loc] = op_error(got, want)
+            return type(res)(got)
+        return wrapped
+
+
+def op_error(got: torch.Tensor, want: torch.Tensor) -> dict:
+    """Error of one op's output in units that do not depend on its magnitude: the share of elements that
+    are bit-equal, the largest error in bf16 ulps of the element it belongs to (beyond an absolute 1e-2),
+    and the Pearson correlation."""
+    if not want.is_floating_point():
+        return {"equal": float((got == want).float().mean().item()), "max_ulps": 0.0 if torch.equal(got, want) else float("inf"),
+                "pcc": 1.0 if torch.equal(got, want) else 0.0}
+    g, w = got.float(), want.float()
+    err = (g - w).abs()
+    ulp = torch.maximum(w.abs(), g.abs()) * 2.0 ** -7          # a bf16 ulp is between 2^-8 and 2^-7 of the magnitude
+    beyond = torch.clamp(err - 1e-2, min=0.0) / torch.clamp(ulp, min=1e-30)
+    return {"equal": float((got == want).float().mean().item()), "max_ulps": float(beyond.max().item()),
+            "max_abs": float(err.max().item()), "pcc": float(metrics.get_pcc(want, got))}

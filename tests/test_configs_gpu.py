@@ -117,6 +117,44 @@ def test_config4_decoder_block_full_size(rt, device):
     assert torch.equal(got2[:, :1024], got[:, :1024])
 
 
+def test_config4_decoder_block_full_size_op_by_op(rt, device):
+    """The arithmetic of every kernel of the block at full size, separated from the chain's rounding
+    noise: the program runs op by op (debug hooks registered, so nothing is fused), every op's output is
+    read back, and the oracle evaluates each op on the GPU's own operands (helpers.TeacherForcedOracle).
+    Given identical inputs, two correctly rounded pipelines can differ by one bf16 ulp where an f32 sum
+    lands next to a rounding boundary, nowhere by more: every op must be within atol 1e-2 + one ulp of
+    its own oracle with PCC >= 0.999 (attention: two ulps -- the probabilities enter the second
+    contraction rounded to bf16 here and as f32 in the oracle).  The fused program (nine launches) must
+    then equal the op-by-op run bit for bit, which carries these bounds over to what the benchmark times."""
+    from helpers import TeacherForcedOracle
+    ins = graphs.decoder_block_inputs()
+    buf = graphs.build_binary(graphs.decoder_block_graph)
+    fused = run_program(rt, device, buf, ins)[0]
+    outputs = {}
+
+    def post(_bin, ctx, op):
+        t = rt.get_op_output_tensor(op, ctx)
+        if t is not None:
+            outputs[rt.get_op_loc_info(op)] = rt.to_torch(t)
+    rt.DebugHooks.get(None, post)
+    try:
+        unfused = run_program(rt, device, buf, ins)[0]
+    finally:
+        rt.unregister_hooks()
+    tf = TeacherForcedOracle(ins, outputs)
+    graphs.decoder_block_graph(tf)
+    for name, r in tf.report.items():
+        print(f"{name:22s} bit-equal {r['equal']:.5f}  max beyond atol (ulps) {r['max_ulps']:.3f}  pcc {r['pcc']:.7f}")
+    named = {"attn_norm", "q_proj", "k_proj", "v_proj", "q_rope", "k_rope", "attention", "o_proj", "attn_residual", "ffn_norm",
+             "gate_proj", "up_proj", "silu", "swiglu", "down_proj", "ffn_residual"}
+    assert named <= set(tf.report), sorted(named - set(tf.report))
+    for name, r in tf.report.items():
+        limit = 2.0 if name == "attention" else 1.0
+        assert r["pcc"] >= 0.999 and r["max_ulps"] <= limit, (name, r)
+    different = (fused != unfused).sum().item()
+    assert different == 0, f"{different} elements differ between the fused and the op-by-op program"
+
+
 def test_config5_bottleneck_small(rt, device):
     kw = dict(batch=2, hw=8)
     check_graph(rt, device, graphs.bottleneck_graph, graphs.bottleneck_inputs(**kw), "bottleneck small",

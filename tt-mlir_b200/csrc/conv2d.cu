@@ -186,6 +186,57 @@ int ttb_conv2d_fused(const void *x, const void *weight, const void *bias, void *
   return ttb_gemm_fused(col, wre, bias, out, dtype, bias_dtype, dtype, 1, P, o, K, 0, 1, 0, 0, act, 0, extra, extra_op, stream);
 }
 
+// Convolution on quantized operands (8-bit integers, exact 32-bit accumulation): the integer conv2d the
+// compiler builds when input and weight are quantized (lib/Dialect/TTIR/IR/TTIROps.cpp:1492-1577), with the
+// dequantize that follows it optionally fused (out_dtype a float type: result = float(acc) * scale, scale
+// per output channel or one scalar).  Pointwise convolutions are the contraction itself; others gather the
+// receptive fields into the workspace (ttb_conv2d_workspace_bytes with the input's dtype) first.
+int ttb_conv2d_i8(const void *x, const void *weight, void *out, int x_dtype, int w_dtype, int out_dtype, int64_t n, int64_t h,
+                  int64_t w, int64_t c, int64_t o, int kh, int kw, int stride_h, int stride_w, const int *padding4, int dil_h,
+                  int dil_w, int groups, const float *deq_scale, float deq_scalar, void *workspace, void *stream) {
+  TTB_CHECK(x && weight && out && padding4, "null argument");
+  TTB_CHECK(groups == 1, "grouped convolution is not supported");
+  TTB_CHECK((x_dtype == kI8 || x_dtype == kU8) && (w_dtype == kI8 || w_dtype == kU8), "conv2d_i8 takes Int8 / UInt8 operands");
+  TTB_CHECK(kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0 && dil_h > 0 && dil_w > 0, "bad convolution geometry");
+  if (n == 0) return TTB_OK;
+  TTB_CHECK(n > 0 && h > 0 && w > 0 && c > 0 && o > 0, "convolution extents must be positive");
+  TTB_CHECK(padding4[0] >= 0 && padding4[1] >= 0 && padding4[2] >= 0 && padding4[3] >= 0, "negative padding");
+  if (isPointwise(kh, kw, stride_h, stride_w, padding4, groups)) {
+    return ttb_gemm_i8(x, weight, out, x_dtype, w_dtype, out_dtype, 1, n * h * w, o, c, 0, 1, 0, 0, deq_scale, deq_scalar, stream);
+  }
+  ConvGeom g;
+  g.N = n; g.H = h; g.W = w; g.C = c;
+  g.kh = kh; g.kw = kw; g.sh = stride_h; g.sw = stride_w; g.pt = padding4[0]; g.pl = padding4[1];
+  g.dh = dil_h; g.dw = dil_w;
+  g.Ho = outDim(h, kh, stride_h, padding4[0], padding4[2], dil_h);
+  g.Wo = outDim(w, kw, stride_w, padding4[1], padding4[3], dil_w);
+  TTB_CHECK(g.Ho > 0 && g.Wo > 0, "convolution output is empty");
+  TTB_CHECK(workspace != nullptr, "conv2d needs its workspace");
+  const int64_t P = n * g.Ho * g.Wo, K = static_cast<int64_t>(kh) * kw * c;
+  char *col = static_cast<char *>(workspace);
+  char *wre = col + alignUp(static_cast<size_t>(P) * K, 256);
+  cudaStream_t st = asStream(stream);
+  {
+    int64_t shape[4] = {o, kh, kw, c};
+    int64_t strides[4] = {c * kh * kw, kw, 1, static_cast<int64_t>(kh) * kw};
+    int rc = ttb_strided_copy(weight, wre, 1, 4, shape, strides, 0, stream);
+    if (rc) return rc;
+  }
+  {
+    ProfScope prof("conv2d_im2col", 0, double(P) * K + double(n) * h * w * c, st);
+    if (c % 16 == 0 && aligned16(x) && aligned16(col)) {
+      int grid = gridFor(static_cast<size_t>(P * kh * kw * (c / 16)), 256);
+      im2colKernel<uint8_t, 16><<<grid, 256, 0, st>>>(static_cast<const uint8_t *>(x), reinterpret_cast<uint8_t *>(col), g);
+    } else {
+      int grid = gridFor(static_cast<size_t>(P * kh * kw * c), 256);
+      im2colKernel<uint8_t, 1><<<grid, 256, 0, st>>>(static_cast<const uint8_t *>(x), reinterpret_cast<uint8_t *>(col), g);
+    }
+    countLaunch();
+    TTB_LAUNCH_CHECK();
+  }
+  return ttb_gemm_i8(col, wre, out, x_dtype, w_dtype, out_dtype, 1, P, o, K, 0, 1, 0, 0, deq_scale, deq_scalar, stream);
+}
+
 int ttb_conv2d_static(const void *x, const void *weight, const void *bias, void *out, int dtype, int bias_dtype,
                       int64_t n, int64_t h, int64_t w, int64_t c, int64_t o, int kh, int kw, int stride_h, int stride_w,
                       const int *padding4, int dil_h, int dil_w, int groups, int act, void *stream) {

@@ -112,7 +112,14 @@ struct TcParams {
   // cTw = 0: rows are 128 consecutive pixels and the producer warp gathers them with cp.async.
   int cTw, cTilesX, cTilesY;
   int64_t cTilesM; // images x cTilesY x cTilesX
-  int fmt; // 1 bf16, 0 f16
+  int fmt; // 1 bf16, 0 f16, 2 8-bit integers (kind::i8, 32-bit integer accumulator)
+  int kElems; // elements in the 128 bytes of a k-block: 64 for 16-bit operands, 128 for 8-bit
+  int aSigned, bSigned; // fmt 2: signedness of the operands
+  // fmt 2 with a float output: the accumulator is converted to f32 and multiplied by a scale (the
+  // dequantize op that follows a quantized contraction: per tensor, or per output column).
+  int deq;               // 0 off (the integer accumulator is stored), 1 scalar, 2 per column
+  float deqScalar;
+  const float *deqScale; // [N] f32
 };
 
 struct PushMaps {
@@ -151,7 +158,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     n0 = static_cast<int>(nt - (seg == 0 ? 0 : p.segCum[seg - 1])) * (p.dual ? BN / 2 : BN);
     return seg;
   };
-  const int kBlocks = static_cast<int>((p.K + TC_BK - 1) / TC_BK);
+  const int kBlocks = static_cast<int>((p.K + p.kElems - 1) / p.kElems);
 
   if (threadIdx.x == 0) {
     abortFlagS = 0;
@@ -290,13 +297,13 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
             const int tap = kb / cb, ky = tap / p.ckw, kx = tap - ky * p.ckw;
             tmaLoad4d(sa, &mapA, fullBar(s), (kb - tap * cb) * TC_BK, ox0 + kx * p.cdw - p.cpl, oy0 + ky * p.cdh - p.cpt, img);
           } else {
-            tmaLoad2d(sa, &mapA, fullBar(s), kb * TC_BK, m0);
+            tmaLoad2d(sa, &mapA, fullBar(s), kb * p.kElems, m0);
           }
           if (p.dual) {
             tmaLoad2d(sb, &mapB, fullBar(s), kb * TC_BK, n0);
             tmaLoad2d(sb + (BN / 2) * TC_BK * 2, &mapB1, fullBar(s), kb * TC_BK, n0);
           } else {
-            tmaLoad2d(sb, mb, fullBar(s), kb * TC_BK, n0);
+            tmaLoad2d(sb, mb, fullBar(s), kb * p.kElems, n0);
           }
         }
       }
@@ -304,7 +311,8 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      const uint32_t idesc = instrDesc(p.fmt, TC_BM, BN);
+      const bool ints = p.fmt == 2;
+      const uint32_t idesc = ints ? instrDescI8(p.aSigned, p.bSigned, TC_BM, BN) : instrDesc(p.fmt, TC_BM, BN);
       uint32_t it = 0, accIt = 0;
       bool alive = true;
       for (int64_t tile = blockIdx.x; tile < numTiles && alive; tile += gridDim.x, ++accIt) {
@@ -322,8 +330,9 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
           const uint64_t da = smemDesc(sa), db = smemDesc(sb);
 #pragma unroll
           for (int k = 0; k < TC_BK / 16; ++k) {
-            // +32 bytes per 16-element k-step = +2 in the descriptor's 16-byte address units
-            tcMma(tmemD, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            // +32 bytes per k-step (16 two-byte or 32 one-byte elements) = +2 in the descriptor's 16-byte address units
+            if (ints) tcMmaI8(tmemD, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            else tcMma(tmemD, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           tcCommit(emptyBar(s)); // frees the stage once these MMAs have read it
         }
@@ -496,6 +505,16 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
             }
           }
           if constexpr (!PLAIN) {
+            if (p.deq) {
+              // quantized contraction followed by dequantize: float(accumulator) * scale, one rounding
+              float sc = p.deqScalar;
+              if (p.deq == 2) sc = colH + lane < p.N ? p.deqScale[colH + lane] : 0.0f;
+#pragma unroll
+              for (int e = 0; e < HW; ++e) {
+                const float se = p.deq == 2 ? __shfl_sync(0xffffffffu, sc, e) : sc;
+                r[e] = __float_as_uint(__fmul_rn(__int2float_rn(static_cast<int>(r[e])), se));
+              }
+            }
             // One straight-line pass per case: runtime flags inside the unrolled loop would put
             // every variant's instructions on every element, and a per-element switch over the
             // activations would thrash the instruction cache.
@@ -666,6 +685,8 @@ static bool makeMap(CUtensorMap *map, const void *ptr, int dtype, int64_t rows, 
   cuuint32_t elemStrides[2] = {1, 1};
   CUtensorMapDataType dt = dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                            : (dtype == kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
+  if (dtype == kI8 || dtype == kU8) dt = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  if (dtype == kI32) dt = CU_TENSOR_MAP_DATA_TYPE_INT32;
   CUresult r = fn(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -787,6 +808,7 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   p.segCum[0] = p.segCum[1] = p.segCum[2] = static_cast<int>((n + bn - 1) / bn);
   p.segN[0] = p.segN[1] = p.segN[2] = n;
   p.fmt = abDtype == kBF16 ? 1 : 0;
+  p.kElems = TC_BK; p.aSigned = p.bSigned = 0; p.deq = 0; p.deqScalar = 0.0f; p.deqScale = nullptr;
   double flops = 2.0 * double(m) * double(n) * double(k);
   double bytes = (double(m) * k + double(n) * k) * 2 + double(m) * n * dtypeSize(cDtype) * (extraOp ? 2 : 1);
   ProfScope prof("gemm_tcgen05", flops, bytes, stream);
@@ -830,11 +852,73 @@ int gemmTcgen05SwigluTry(const void *a, const void *wGate, const void *wUp, void
   p.segCum[0] = p.segCum[1] = p.segCum[2] = static_cast<int>((n + BN / 2 - 1) / (BN / 2));
   p.segN[0] = p.segN[1] = p.segN[2] = n;
   p.fmt = dtype == kBF16 ? 1 : 0;
+  p.kElems = TC_BK; p.aSigned = p.bSigned = 0; p.deq = 0; p.deqScalar = 0.0f; p.deqScale = nullptr;
   // both projections' FLOPs; A and both weights once, the result once
   ProfScope prof("gemm_tcgen05", 4.0 * double(m) * double(n) * double(k), (double(m) * k + 2.0 * double(n) * k + double(m) * n) * 2, stream);
   const CUtensorMap more[4] = {mu, mc, mu, mc};
   if (dtype == kBF16) return launchTc<BN, __nv_bfloat16, false>(ma, mg, mc, mc, out, p, stream, more);
   return launchTc<BN, __half, false>(ma, mg, mc, mc, out, p, stream, more);
+}
+
+// Quantized contraction: C[M, N] = A[M, K] B[N, K]^T with 8-bit integer operands and exact 32-bit
+// integer accumulation (tcgen05.mma kind::i8).  cDtype Int32 stores the accumulators; Float32 / BFloat16 /
+// Float16 store float(accumulator) * scale, scale being `deqScalar` (deqScale null) or deqScale[column]:
+// the dequantize op that follows a quantized matmul or convolution, fused.  -1 = not taken.
+int gemmTcgen05I8Try(const void *a, const void *b, void *c, int aDtype, int bDtype, int cDtype, int64_t m, int64_t n,
+                     int64_t k, const float *deqScale, float deqScalar, cudaStream_t stream) {
+  if ((aDtype != kI8 && aDtype != kU8) || (bDtype != kI8 && bDtype != kU8)) return -1;
+  if (cDtype != kI32 && cDtype != kF32 && cDtype != kBF16 && cDtype != kF16) return -1;
+  if (k % 16 != 0 || m < 1 || n < 8 || k < 16) return -1; // rows of A and B are whole 16-byte units for TMA
+  if ((n * static_cast<int64_t>(dtypeSize(cDtype))) % 16 != 0) return -1;
+  if (!aligned16(a) || !aligned16(b) || !aligned16(c) || (deqScale && (reinterpret_cast<uintptr_t>(deqScale) & 3))) return -1;
+  if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff) return -1;
+  if (m * n * k < (1ll << 18)) return -1;
+  int bn = 64;
+  {
+    int64_t best = -1;
+    for (int w : {256, 128, 64}) {
+      if (w > 64 && n < w) continue;
+      int64_t tiles = ((m + TC_BM - 1) / TC_BM) * ((n + w - 1) / w);
+      int64_t waves = (tiles + smCount() - 1) / smCount();
+      int64_t cost = waves * (w + 64);
+      if (best < 0 || cost < best) {
+        best = cost;
+        bn = w;
+      }
+    }
+  }
+  CUtensorMap ma, mb, mc;
+  if (!makeMap(&ma, a, kU8, m, k, TC_BM) || !makeMap(&mb, b, kU8, n, k, bn) || !makeMap(&mc, c, cDtype, m, n, 32)) return -1;
+  TcParams p;
+  p.M = m; p.N = n; p.K = k;
+  p.bias = nullptr; p.biasDt = 0; p.act = TTB_ACT_NONE; p.roundSteps = 0;
+  p.extra = nullptr; p.extraOp = 0;
+  p.convX = nullptr; p.cTw = 0; p.cTilesM = 0; p.pushRows = 0; p.dual = 0;
+  p.segCum[0] = p.segCum[1] = p.segCum[2] = static_cast<int>((n + bn - 1) / bn);
+  p.segN[0] = p.segN[1] = p.segN[2] = n;
+  p.fmt = 2;
+  p.kElems = 128;
+  p.aSigned = aDtype == kI8 ? 1 : 0;
+  p.bSigned = bDtype == kI8 ? 1 : 0;
+  p.deq = cDtype == kI32 ? 0 : (deqScale ? 2 : 1);
+  p.deqScalar = deqScalar;
+  p.deqScale = deqScale;
+  ProfScope prof("gemm_tcgen05_i8", 2.0 * double(m) * double(n) * double(k),
+                 double(m) * k + double(n) * k + double(m) * n * dtypeSize(cDtype), stream);
+#define TTB_TCI(BNv, TCv, PLAINv) return launchTc<BNv, TCv, PLAINv>(ma, mb, mc, mc, c, p, stream)
+#define TTB_TCI_BN(TCv, PLAINv)                                                          \
+  switch (bn) {                                                                          \
+  case 256: TTB_TCI(256, TCv, PLAINv);                                                   \
+  case 128: TTB_TCI(128, TCv, PLAINv);                                                   \
+  default: TTB_TCI(64, TCv, PLAINv);                                                     \
+  }
+  // Int32 output: the plain kernel's 32-bit store path moves the accumulator bits unchanged.
+  if (cDtype == kI32) { TTB_TCI_BN(float, true) }
+  if (cDtype == kF32) { TTB_TCI_BN(float, false) }
+  if (cDtype == kBF16) { TTB_TCI_BN(__nv_bfloat16, false) }
+  TTB_TCI_BN(__half, false)
+#undef TTB_TCI_BN
+#undef TTB_TCI
 }
 
 // Up to three GEMMs C_i[M, N_i] = A[M, K] B_i[N_i, K]^T that share A (the q / k / v projections of
@@ -898,6 +982,7 @@ int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, c
     }
   }
   p.fmt = abDtype == kBF16 ? 1 : 0;
+  p.kElems = TC_BK; p.aSigned = p.bSigned = 0; p.deq = 0; p.deqScalar = 0.0f; p.deqScale = nullptr;
   ProfScope prof("gemm_tcgen05", flops, bytes, stream);
   const CUtensorMap more[4] = {mb[1], mc[1], mb[2], mc[2]};
 #define TTB_TCG(BNv, TCv) return launchTc<BNv, TCv, true>(ma, mb[0], mc[0], mc[0], c[0], p, stream, more)
@@ -987,6 +1072,7 @@ int convTcgen05Try(const void *x, const void *wre, const void *bias, void *out, 
   p.segCum[0] = p.segCum[1] = p.segCum[2] = static_cast<int>((o + bn - 1) / bn);
   p.segN[0] = p.segN[1] = p.segN[2] = o;
   p.fmt = dtype == kBF16 ? 1 : 0;
+  p.kElems = TC_BK; p.aSigned = p.bSigned = 0; p.deq = 0; p.deqScalar = 0.0f; p.deqScale = nullptr;
   // algorithmic bytes: the input and the output once each (plus the residual operand), the weights
   ProfScope prof("conv2d_tcgen05", 2.0 * double(m) * o * k,
                  (double(n) * h * w * c + double(o) * k + double(m) * o * (extraOp ? 2 : 1)) * 2, stream);

@@ -108,6 +108,21 @@ __device__ __forceinline__ void tcMma(uint32_t tmemD, uint64_t descA, uint64_t d
                ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// Integer variant: 8-bit operands (32 of them per instruction along K), 32-bit integer accumulator.
+__device__ __forceinline__ void tcMmaI8(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// kind::i8 instruction descriptor: s32 accumulator (2 at bit 4), A / B format at bits 7 / 10
+// (0 = unsigned, 1 = signed 8-bit), both operands K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t instrDescI8(int aSigned, int bSigned, int m, int n) {
+  return (2u << 4) | (static_cast<uint32_t>(aSigned) << 7) | (static_cast<uint32_t>(bSigned) << 10) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
 // D[tmem] (+)= A[tmem] * B[smem desc]: the A operand is read from tensor memory (row i of A in
 // lane i, two 16-bit elements per 32-bit column, the even k in the low half).
 __device__ __forceinline__ void tcMmaTmemA(uint32_t tmemD, uint32_t tmemA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {

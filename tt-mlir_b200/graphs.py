@@ -117,6 +117,49 @@ def w8_linear_inputs(m=2048, k=4096, n=11008, seed=2):
     return [a, wq, s.to(torch.float32), bias]
 
 
+def w8a8_linear_graph(b, m=2048, k=4096, n=11008, act_scale=0.04, fused_dequant=True):
+    """Config 3's shapes with BOTH operands quantized: activations per tensor (scale `act_scale`), weights
+    per output channel.  The contraction runs on the 8-bit values with an Int32 accumulator and the
+    dequantize after it carries the product of the scales per output channel -- the form the compiler
+    produces when it commutes dequantize below a quantizable op (QuantDequantConversion.cpp).  Inputs:
+    activations bf16 [m, k], weights Int8 [n, k], combined scales f32 [n] (= act_scale * weight scale),
+    bias bf16 [n]."""
+    a = b.input([m, k], "BFloat16")
+    wq = b.input([n, k], "Int8")
+    scales = b.input([n], "Float32")
+    bias = b.input([n], "BFloat16")
+    aq = b.quantize(a, act_scale, 0, out_dtype="Int8", loc="quantize_activation")
+    acc = b.matmul(aq, wq, transpose_b=True, out_dtype="Int32", loc="int_matmul")
+    y = b.dequantize(acc, scales, 0, out_dtype="BFloat16", axis=1, loc="dequantize_result")
+    b.output(b.add(y, bias, loc="bias"))
+
+
+def w8a8_linear_inputs(m=2048, k=4096, n=11008, seed=2, act_scale=0.04):
+    a, wq, s, bias = w8_linear_inputs(m, k, n, seed)
+    return [a, wq, (s * act_scale).to(torch.float32), bias]
+
+
+def quantized_conv_graph(b, batch=8, hw=28, c_in=64, c_out=128, kernel=3, x_scale=0.05, container="Int8"):
+    """A convolution on quantized operands: input quantized per tensor, weight Int8 per output channel,
+    Int32 accumulator, dequantize with the per-channel product of the scales."""
+    x = b.input([1, 1, batch * hw * hw, c_in], "BFloat16")
+    wq = b.input([c_out, c_in, kernel, kernel], container)
+    scales = b.input([c_out], "Float32")
+    xq = b.quantize(x, x_scale, 0, out_dtype=container, loc="quantize_input")
+    pad = kernel // 2
+    acc = b.conv2d(xq, wq, None, batch, hw, hw, padding=(pad, pad, pad, pad), out_dtype="Int32", loc="int_conv")
+    b.output(b.dequantize(acc, scales, 0, out_dtype="Float32", axis=3, loc="dequantize_result"))
+
+
+def quantized_conv_inputs(batch=8, hw=28, c_in=64, c_out=128, kernel=3, seed=7, x_scale=0.05, container=torch.int8):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(1, 1, batch * hw * hw, c_in, generator=g).to(torch.bfloat16)
+    wf = torch.randn(c_out, c_in, kernel, kernel, generator=g) * (2.0 / (c_in * kernel * kernel)) ** 0.5
+    s = wf.abs().amax(dim=(1, 2, 3)) / 127.0
+    wq = torch.clamp(torch.round(wf / s[:, None, None, None]), -127, 127).to(container)
+    return [x, wq, (s * x_scale).to(torch.float32)]
+
+
 # ---------------------------------------------------------------- config 4: Llama-style decoder block
 def rope_tables(seq, head_dim, theta=500000.0, dtype=torch.bfloat16):
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))

@@ -418,6 +418,13 @@ private:
   // fused forms; return ops consumed or 0 when the pattern does not apply
   size_t tryQuantChain(size_t i);
   size_t tryGemmEpilogue(size_t i);
+  size_t tryQuantizedGemm(size_t i);
+  size_t tryQuantizedConv(size_t i);
+  TensorPtr convDeqScale;     // set around runConv2d by tryQuantizedConv: the fused dequantize's per-channel scale
+  float convDeqScalar = 0.0f; // ... or its per-tensor scale
+  // matmul on quantized (8-bit integer) operands; deqScale / deqScalar describe a fused dequantize
+  void runIntGemm(const fbt::TensorRef *aRef, const fbt::TensorRef *bRef, const fbt::TensorRef *outRef, bool ta, bool tb,
+                  const TensorPtr &deqScale, float deqScalar);
   size_t tryGroupedGemm(size_t i);
   size_t trySwiglu(size_t i);
   size_t trySiluMul(size_t i);
@@ -699,7 +706,8 @@ size_t Executor::runOp(size_t i) {
     case OpType::EltwiseQuantizationOp: used = tryQuantChain(i); break;
     case OpType::MatmulOp:
     case OpType::LinearOp:
-      used = trySwiglu(i);
+      used = tryQuantizedGemm(i);
+      if (!used) used = trySwiglu(i);
       if (!used) used = tryGemmEpilogue(i);
       if (!used) used = tryGroupedGemm(i);
       break;
@@ -707,7 +715,10 @@ size_t Executor::runOp(size_t i) {
     case OpType::EltwiseBinaryOp: used = tryAddRmsNorm(i); break;
     case OpType::ScaledDotProductAttentionOp: used = trySdpa(i); break;
     case OpType::AllReduceOp: used = tryAllReduceAdd(i); break;
-    case OpType::Conv2dOp: used = tryConvEpilogue(i); break;
+    case OpType::Conv2dOp:
+      used = tryQuantizedConv(i);
+      if (!used) used = tryConvEpilogue(i);
+      break;
     default: break;
     }
     if (used) return used;
@@ -1230,9 +1241,17 @@ size_t Executor::tryQuantChain(size_t i) {
 }
 
 // ---- contractions -------------------------------------------------------------------------------------
+bool isQuantizedStorage(DataType dt);
+
 void Executor::runGemm(const fbt::TensorRef *aRef, const fbt::TensorRef *bRef, const fbt::TensorRef *biasRef,
                        const fbt::TensorRef *outRef, bool ta, bool tb, int act, int roundSteps,
                        const fbt::TensorRef *extraRef, int extraOp) {
+  if (isQuantizedStorage(refDtype(aRef)) && isQuantizedStorage(refDtype(bRef))) {
+    TTRT_ASSERT(!biasRef && !extraRef && act == 0 && roundSteps == 0,
+                "a matmul on quantized operands takes no bias, activation or fused operand (dequantize first)");
+    runIntGemm(aRef, bRef, outRef, ta, tb, nullptr, 0.0f);
+    return;
+  }
   TensorPtr a = getDevice(aRef), b = getDevice(bRef);
   TensorPtr bias = biasRef ? getDevice(biasRef) : nullptr;
   TensorPtr extra = extraRef ? getDevice(extraRef) : nullptr;
@@ -1283,6 +1302,106 @@ void Executor::runGemm(const fbt::TensorRef *aRef, const fbt::TensorRef *bRef, c
                             extra ? extraOp : TTB_EXTRA_NONE, r.stream));
   });
   put(outRef, out);
+}
+
+// Quantized tensors travel as Int8 / UInt8 or, the compiler's default, as Int32 containers that hold
+// int8 values (lib/Dialect/TTNN/Pipelines/TTNNPipelines.cpp:349-351).
+bool isQuantizedStorage(DataType dt) { return dt == DataType::Int8 || dt == DataType::UInt8 || dt == DataType::Int32; }
+
+// out = a b on quantized operands: exact 32-bit integer accumulation (tcgen05.mma kind::i8 for the
+// weight layout, a CUDA-core kernel otherwise).  An Int32 result holds the accumulators; a float result
+// is the accumulator times a scale, which is the dequantize op that followed, fused.  Int32 containers
+// are narrowed to Int8 first (their values are in the int8 range by construction).
+void Executor::runIntGemm(const fbt::TensorRef *aRef, const fbt::TensorRef *bRef, const fbt::TensorRef *outRef, bool ta, bool tb,
+                          const TensorPtr &deqScale, float deqScalar) {
+  TensorPtr a = getDevice(aRef), b = getDevice(bRef);
+  if (a->dtype == DataType::Int32 || b->dtype == DataType::Int32) {
+    // Only safe while Int32 containers are known to hold int8 values (the rule the quantization ops
+    // follow here; TTB_QUANT_I32_FULL_RANGE=1 lifts it, and with it this path).
+    TTRT_ASSERT(clampI8ForContainer() != 0,
+                "matmul on Int32 containers needs their values in the int8 range (unset TTB_QUANT_I32_FULL_RANGE, or use Int8 tensors)");
+    if (a->dtype == DataType::Int32) a = castOnDevice(a, DataType::Int8);
+    if (b->dtype == DataType::Int32) b = castOnDevice(b, DataType::Int8);
+  }
+  std::vector<uint32_t> as = a->shape, bs = b->shape;
+  if (as.size() == 1) as.insert(as.begin(), 1);
+  if (bs.size() == 1) bs.push_back(1);
+  TTRT_ASSERT(as.size() >= 2 && bs.size() >= 2, "matmul operands need rank >= 1");
+  int64_t M = ta ? as[as.size() - 1] : as[as.size() - 2];
+  int64_t K = ta ? as[as.size() - 2] : as[as.size() - 1];
+  int64_t Kb = tb ? bs[bs.size() - 1] : bs[bs.size() - 2];
+  int64_t N = tb ? bs[bs.size() - 2] : bs[bs.size() - 1];
+  TTRT_ASSERT(K == Kb, "matmul inner dimensions differ: ", K, " vs ", Kb);
+  int64_t aBatch = static_cast<int64_t>(prod(as, 0, as.size() - 2));
+  int64_t bBatch = static_cast<int64_t>(prod(bs, 0, bs.size() - 2));
+  int64_t batch = std::max(aBatch, bBatch);
+  TTRT_ASSERT((aBatch == batch || aBatch == 1) && (bBatch == batch || bBatch == 1), "matmul batch dimensions do not broadcast");
+  int64_t aStride = aBatch == 1 ? 0 : M * K, bStride = bBatch == 1 ? 0 : K * N;
+  if (bBatch == 1 && aBatch > 1 && !ta) {
+    M *= aBatch;
+    batch = 1;
+    aStride = 0;
+  }
+  TensorPtr out = allocOut(outRef);
+  TTRT_ASSERT(static_cast<int64_t>(out->volume()) == batch * M * N, "matmul result has ", out->volume(), " elements, expected ",
+              batch * M * N);
+  TTRT_ASSERT(out->dtype == DataType::Int32 || out->dtype == DataType::Float32 || out->dtype == DataType::BFloat16 ||
+                  out->dtype == DataType::Float16,
+              "a matmul on quantized operands produces Int32 accumulators (or, with the dequantize fused, a float type), not ",
+              dataTypeName(out->dtype));
+  if (deqScale) TTRT_ASSERT(static_cast<int64_t>(deqScale->volume()) == N, "per-channel scale must have N = ", N, " entries");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_gemm_i8(a->shards[i]->ptr, b->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(a->dtype), ttbDtype(b->dtype),
+                         ttbDtype(out->dtype), batch, M, N, K, ta, tb, aStride, bStride,
+                         deqScale ? static_cast<const float *>(deqScale->shards[i]->ptr) : nullptr, deqScalar, r.stream));
+  });
+  put(outRef, out);
+}
+
+// matmul on quantized operands -> dequantize (zero point 0; per tensor, or per axis along the result's
+// last dimension): one launch whose epilogue multiplies the integer accumulator by the scale.
+size_t Executor::tryQuantizedGemm(size_t i) {
+  const auto *ops = prog->operations();
+  const auto *op = ops->Get(static_cast<uint32_t>(i));
+  const fbt::TensorRef *a, *b, *cur;
+  bool ta, tb;
+  if (op->type_type() == OpType::MatmulOp) {
+    const auto *m = op->type_as_MatmulOp();
+    if (activationCode(m->activation()) != TTB_ACT_NONE) return 0;
+    a = m->a(); b = m->b(); cur = m->out(); ta = m->transpose_a(); tb = m->transpose_b();
+  } else {
+    const auto *l = op->type_as_LinearOp();
+    if (l->bias() || activationCode(l->activation()) != TTB_ACT_NONE) return 0;
+    a = l->a(); b = l->b(); cur = l->out(); ta = l->transpose_a(); tb = l->transpose_b();
+  }
+  if (!isQuantizedStorage(refDtype(a)) || !isQuantizedStorage(refDtype(b)) || refDtype(cur) != DataType::Int32 || !singleUse(cur))
+    return 0;
+  std::vector<const fbt::Operation *> deallocs;
+  size_t j = i + 1;
+  const auto *nop = peek(j, deallocs);
+  if (!nop || nop->type_type() != OpType::EltwiseQuantizationOp) return 0;
+  const auto *dq = nop->type_as_EltwiseQuantizationOp();
+  if (dq->type() != fbt::EltwiseQuantizationOpType::Dequantize || dq->in()->global_id() != cur->global_id() ||
+      refShape(dq->out()) != refShape(cur))
+    return 0;
+  DataType odt = refDtype(dq->out());
+  if (odt != DataType::Float32 && odt != DataType::BFloat16 && odt != DataType::Float16) return 0;
+  const auto *p = dq->params_as_QuantizeDequantizeOpParams();
+  if (!p) return 0;
+  QParams q = readQParams(p->scale_type(), p->scale(), p->zero_point_type(), p->zero_point());
+  TensorPtr scale;
+  if (q.perAxis) {
+    const size_t rank = refShape(cur).size();
+    if (q.zpRef || !dq->axis().has_value() || normDim(*dq->axis(), rank) != static_cast<int>(rank) - 1 || !q.scaleRef ||
+        !pool.count(q.scaleRef->global_id()))
+      return 0;
+    scale = castOnDevice(getDevice(q.scaleRef), DataType::Float32);
+  } else if (q.zp != 0) {
+    return 0;
+  }
+  runIntGemm(a, b, dq->out(), ta, tb, scale, q.scale);
+  runDeallocs(deallocs);
+  return j + 1 - i;
 }
 
 static int unaryToAct(fbt::EltwiseUnaryOpType t) {
@@ -1616,8 +1735,32 @@ void Executor::runConv2d(const fbt::Conv2dOp *op, int act, const fbt::TensorRef 
   int64_t N = op->batch_size(), H = op->input_height(), W = op->input_width(), C = op->in_channels(), O = op->out_channels();
   TTRT_ASSERT(static_cast<int64_t>(x->volume()) == N * H * W * C, "conv2d input has ", x->volume(), " elements, expected N*H*W*C = ",
               N * H * W * C);
-  TTRT_ASSERT(x->dtype == w->dtype && x->dtype == out->dtype, "conv2d tensors must share one data type");
   int groups = static_cast<int>(op->groups());
+  if (isQuantizedStorage(x->dtype) && isQuantizedStorage(w->dtype)) {
+    // Quantized convolution: exact integer accumulation; the result is the Int32 accumulator, or a float
+    // type when the dequantize that follows was fused (see tryQuantizedConv).
+    TTRT_ASSERT(!bias && !extra && act == TTB_ACT_NONE, "a convolution on quantized operands takes no bias or activation (dequantize first)");
+    if (x->dtype == DataType::Int32 || w->dtype == DataType::Int32) {
+      TTRT_ASSERT(clampI8ForContainer() != 0, "conv2d on Int32 containers needs their values in the int8 range");
+      if (x->dtype == DataType::Int32) x = castOnDevice(x, DataType::Int8);
+      if (w->dtype == DataType::Int32) w = castOnDevice(w, DataType::Int8);
+    }
+    TTRT_ASSERT(out->dtype == DataType::Int32 || out->dtype == DataType::Float32 || out->dtype == DataType::BFloat16 ||
+                    out->dtype == DataType::Float16,
+                "a convolution on quantized operands produces Int32 accumulators, not ", dataTypeName(out->dtype));
+    if (convDeqScale) TTRT_ASSERT(static_cast<int64_t>(convDeqScale->volume()) == O, "per-channel scale must have O = ", O, " entries");
+    size_t wsBytes = ttb_conv2d_workspace_bytes(ttbDtype(x->dtype), N, H, W, C, O, kh, kw, sh, sw, pad, dh, dw, groups);
+    TensorPtr ws = wsBytes ? makeDeviceTensor(dev, {static_cast<uint32_t>((wsBytes + 3) / 4)}, DataType::UInt32) : nullptr;
+    eachRank([&](size_t i, const RankCtx &r) {
+      TTB_CALL(ttb_conv2d_i8(x->shards[i]->ptr, w->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(x->dtype), ttbDtype(w->dtype),
+                             ttbDtype(out->dtype), N, H, W, C, O, kh, kw, sh, sw, pad, dh, dw, groups,
+                             convDeqScale ? static_cast<const float *>(convDeqScale->shards[i]->ptr) : nullptr, convDeqScalar,
+                             ws ? ws->shards[i]->ptr : nullptr, r.stream));
+    });
+    put(outRef, out);
+    return;
+  }
+  TTRT_ASSERT(x->dtype == w->dtype && x->dtype == out->dtype, "conv2d tensors must share one data type");
   size_t wsBytes = ttb_conv2d_workspace_bytes(ttbDtype(x->dtype), N, H, W, C, O, kh, kw, sh, sw, pad, dh, dw, groups);
   TensorPtr ws = wsBytes ? makeDeviceTensor(dev, {static_cast<uint32_t>((wsBytes + 3) / 4)}, DataType::UInt32) : nullptr;
   eachRank([&](size_t i, const RankCtx &r) {
@@ -1627,6 +1770,51 @@ void Executor::runConv2d(const fbt::Conv2dOp *op, int act, const fbt::TensorRef 
                               ws ? ws->shards[i]->ptr : nullptr, r.stream));
   });
   put(outRef, out);
+}
+
+// conv2d on quantized operands -> dequantize (zero point 0; per tensor, or per axis along the channel
+// dimension): one contraction whose epilogue multiplies the integer accumulator by the scale.
+size_t Executor::tryQuantizedConv(size_t i) {
+  const auto *ops = prog->operations();
+  const auto *op = ops->Get(static_cast<uint32_t>(i))->type_as_Conv2dOp();
+  const fbt::TensorRef *cur = op->out();
+  if (op->bias() || !isQuantizedStorage(refDtype(op->input())) || !isQuantizedStorage(refDtype(op->weight())) ||
+      refDtype(cur) != DataType::Int32 || !singleUse(cur))
+    return 0;
+  std::vector<const fbt::Operation *> deallocs;
+  size_t j = i + 1;
+  const auto *nop = peek(j, deallocs);
+  if (!nop || nop->type_type() != OpType::EltwiseQuantizationOp) return 0;
+  const auto *dq = nop->type_as_EltwiseQuantizationOp();
+  if (dq->type() != fbt::EltwiseQuantizationOpType::Dequantize || dq->in()->global_id() != cur->global_id() ||
+      refShape(dq->out()) != refShape(cur))
+    return 0;
+  DataType odt = refDtype(dq->out());
+  if (odt != DataType::Float32 && odt != DataType::BFloat16 && odt != DataType::Float16) return 0;
+  const auto *p = dq->params_as_QuantizeDequantizeOpParams();
+  if (!p) return 0;
+  QParams q = readQParams(p->scale_type(), p->scale(), p->zero_point_type(), p->zero_point());
+  TensorPtr scale;
+  if (q.perAxis) {
+    const size_t rank = refShape(cur).size();
+    if (q.zpRef || !dq->axis().has_value() || normDim(*dq->axis(), rank) != static_cast<int>(rank) - 1 || !q.scaleRef ||
+        !pool.count(q.scaleRef->global_id()))
+      return 0;
+    scale = castOnDevice(getDevice(q.scaleRef), DataType::Float32);
+  } else if (q.zp != 0) {
+    return 0;
+  }
+  convDeqScale = scale;
+  convDeqScalar = q.scale;
+  try {
+    runConv2d(op, TTB_ACT_NONE, nullptr, TTB_EXTRA_NONE, dq->out());
+  } catch (...) {
+    convDeqScale.reset();
+    throw;
+  }
+  convDeqScale.reset();
+  runDeallocs(deallocs);
+  return j + 1 - i;
 }
 
 // conv2d [-> relu], or conv2d -> add(tensor) [-> relu] (a residual branch), intermediates

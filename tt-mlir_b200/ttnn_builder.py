@@ -299,8 +299,11 @@ class ProgramBuilder:
         return batch + [m, n]
 
     def matmul(self, a: Value, b: Value, transpose_a=False, transpose_b=False, activation: Optional[str] = None,
-               loc=None) -> Value:
-        out = self._value(self._mm_shape(a.shape, b.shape, transpose_a, transpose_b), a.dtype)
+               out_dtype: Optional[str] = None, loc=None) -> Value:
+        """`out_dtype` differs from the operands' type for a matmul on quantized (8-bit integer) operands,
+        whose result is the Int32 accumulator (lib/Dialect/TTIR/IR/TTIROps.cpp:1516-1577 does the same for
+        the quantized convolution)."""
+        out = self._value(self._mm_shape(a.shape, b.shape, transpose_a, transpose_b), out_dtype or a.dtype)
         self._emit("MatmulOp", {"a": a.ref, "b": b.ref, "out": out.ref, "transpose_a": transpose_a,
                                 "transpose_b": transpose_b, "activation": activation}, [a, b], [out], loc)
         return out
@@ -314,9 +317,10 @@ class ProgramBuilder:
         return out
 
     def conv2d(self, x: Value, w: Value, bias: Optional[Value], batch: int, height: int, width: int, stride=(1, 1),
-               padding=(0, 0, 0, 0), dilation=(1, 1), groups: int = 1, loc=None) -> Value:
+               padding=(0, 0, 0, 0), dilation=(1, 1), groups: int = 1, out_dtype: Optional[str] = None, loc=None) -> Value:
         """x is [1, 1, N*H*W, C] (the flattened form the compiler emits) or [N, H, W, C];
-        w is [O, C/groups, kH, kW]; bias [1, 1, 1, O].  Output keeps x's rank."""
+        w is [O, C/groups, kH, kW]; bias [1, 1, 1, O].  Output keeps x's rank.  `out_dtype` "Int32" for a
+        convolution on quantized (8-bit integer) operands, whose result is the accumulator."""
         o, cg, kh, kw = w.shape
         c = cg * groups
         pad = list(padding) if len(padding) == 4 else [padding[0], padding[1], padding[0], padding[1]]
@@ -324,12 +328,12 @@ class ProgramBuilder:
         wo = (width + pad[1] + pad[3] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
         oshape = [1, 1, batch * ho * wo, o] if x.shape[:2] == [1, 1] and len(x.shape) == 4 and x.shape[2] == batch * height * width \
             else [batch, ho, wo, o]
-        out = self._value(oshape, x.dtype)
+        out = self._value(oshape, out_dtype or x.dtype)
         self._emit("Conv2dOp", {
             "input": x.ref, "weight": w.ref, "bias": bias.ref if bias else None, "out": out.ref,
             "device": self.device_ref, "in_channels": c, "out_channels": o, "batch_size": batch,
             "input_height": height, "input_width": width, "kernel_size": [kh, kw], "stride": list(stride),
-            "padding": pad, "dilation": list(dilation), "groups": groups, "output_dtype": x.dtype},
+            "padding": pad, "dilation": list(dilation), "groups": groups, "output_dtype": out_dtype or x.dtype},
             [x, w] + ([bias] if bias else []), [out], loc)
         return out
 

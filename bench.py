@@ -233,6 +233,7 @@ def check_parity(rt, dist, rank, world, last, full_inputs):
         dist.barrier()
         return None
     t0 = time.perf_counter()
+    torch.set_num_threads(os.cpu_count() or 1)   # the launcher pins OMP_NUM_THREADS to 1; the other ranks are idle now
     ob = OracleBuilder(full_inputs, mesh_shape=(1, world))
     graphs.decoder_block_graph(ob, tp=world, **CONFIG)
     want = ob.results()[0]

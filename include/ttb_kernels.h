@@ -319,6 +319,13 @@ TTB_API int ttb_gemm_i8(const void *a, const void *b, void *c, int a_dtype, int 
                         int64_t batch, int64_t m, int64_t n, int64_t k, int trans_a, int trans_b,
                         int64_t a_batch_stride, int64_t b_batch_stride, const float *deq_scale,
                         float deq_scalar, void *stream);
+/* ttb_gemm_i8 with a float result, followed by + bias[n] (bias in a float type): a quantized linear layer
+ * (::ttnn::matmul on the 8-bit values, ::ttnn::dequantize, ::ttnn::add) in one call; the dequantized
+ * value is rounded to c_dtype before the bias is added, as the separate ops round. */
+TTB_API int ttb_gemm_i8_bias(const void *a, const void *b, void *c, int a_dtype, int b_dtype, int c_dtype,
+                             int64_t batch, int64_t m, int64_t n, int64_t k, int trans_a, int trans_b,
+                             int64_t a_batch_stride, int64_t b_batch_stride, const float *deq_scale,
+                             float deq_scalar, const void *bias, int bias_dtype, void *stream);
 TTB_API int ttb_gemm_i8_simt(const void *a, const void *b, void *c, int a_dtype, int b_dtype, int c_dtype,
                              int64_t batch, int64_t m, int64_t n, int64_t k, int trans_a, int trans_b,
                              int64_t a_batch_stride, int64_t b_batch_stride, const float *deq_scale,

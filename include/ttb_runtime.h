@@ -30,6 +30,7 @@ typedef void *ttrt_binary_t;
 typedef void *ttrt_device_t;
 typedef void *ttrt_tensor_t;
 typedef void *ttrt_layout_t;
+typedef void *ttrt_tensor_ref_t;
 
 TTRT_API const char *ttrt_last_error(void);
 TTRT_API void ttrt_free_string(char *s);
@@ -53,6 +54,12 @@ TTRT_API int ttrt_binary_program_io_desc(ttrt_binary_t bin, uint32_t program, in
                                          uint32_t *rank, uint32_t shape[TTRT_MAX_RANK], int *dtype);
 TTRT_API int ttrt_binary_program_mesh_shape(ttrt_binary_t bin, uint32_t program, uint32_t *y, uint32_t *x);
 TTRT_API int ttrt_binary_program_ops_as_json(ttrt_binary_t bin, uint32_t program, char **out);
+/* The remaining string views of a Binary (runtime/lib/binary.cpp): getProgramInputsAsJson, getProgramOutputsAsJson,
+ * getMlirAsJson, getSystemDescAsJson, getSchemaHash, getTTMLIRGitHash.  `program` is ignored where it does
+ * not apply.  Free the result with ttrt_free_string. */
+enum { TTRT_Q_PROGRAM_INPUTS_JSON = 0, TTRT_Q_PROGRAM_OUTPUTS_JSON = 1, TTRT_Q_MLIR_JSON = 2, TTRT_Q_SYSTEM_DESC_JSON = 3,
+       TTRT_Q_SCHEMA_HASH = 4, TTRT_Q_TTMLIR_GIT_HASH = 5 };
+TTRT_API int ttrt_binary_query_string(ttrt_binary_t bin, int what, uint32_t program, char **out);
 
 /* ---- runtime selection, devices (runtime.h:35-38,160-171) --------------------------------- */
 TTRT_API int ttrt_set_compatible_device_runtime(ttrt_binary_t bin);               /* setCompatibleDeviceRuntime */
@@ -133,6 +140,48 @@ TTRT_API int ttrt_op_debug_string(void *op_ctx, char *out, size_t cap);         
  * *out = NULL when the op has no live output. */
 TTRT_API int ttrt_op_output_tensor(void *op_ctx, void *program_ctx, ttrt_tensor_t *out);
 TTRT_API int ttrt_program_index(void *program_ctx, size_t *index);                /* getProgramIndex */
+
+/* getOpInputRefs / getOpOutputRefs (runtime.h:262-263): handles to the tensors an op reads / writes,
+ * for callbacks that fetch or overwrite intermediates.  Free each with ttrt_tensor_ref_free. */
+TTRT_API int ttrt_op_input_refs(void *op_ctx, ttrt_tensor_ref_t *out, uint32_t cap, uint32_t *n);
+TTRT_API int ttrt_op_output_refs(void *op_ctx, ttrt_tensor_ref_t *out, uint32_t cap, uint32_t *n);
+TTRT_API void ttrt_tensor_ref_free(ttrt_tensor_ref_t ref);
+TTRT_API int ttrt_tensor_ref_info(ttrt_tensor_ref_t ref, uint32_t *rank, uint32_t shape[TTRT_MAX_RANK], int *dtype); /* getTensorRefShape / DataType */
+/* retrieveTensorFromPool (runtime.h:266-268): host copy of a live tensor, *out = NULL when it is not live. */
+TTRT_API int ttrt_retrieve_tensor_from_pool(void *program_ctx, ttrt_tensor_ref_t ref, int untilize, ttrt_tensor_t *out);
+/* updateTensorInPool (runtime.h:269-270): overwrite a live tensor with a host tensor of the same shape. */
+TTRT_API int ttrt_update_tensor_in_pool(void *program_ctx, ttrt_tensor_ref_t ref, ttrt_tensor_t src);
+
+/* ---- system descriptor, sub-meshes, embedded goldens ----------------------------------------- */
+/* getCurrentSystemDesc (runtime.h:45-47): a "TTSY" flatbuffer describing the visible GPUs (or the devices of
+ * `dev`) in the reference's schema; the handle supports the ttrt_binary_* calls that do not need
+ * programs (as_json, store, file_identifier, version, free). */
+TTRT_API int ttrt_get_current_system_desc(ttrt_device_t dev, ttrt_binary_t *out);
+/* createSubMeshDevice / releaseSubMeshDevice / reshapeMeshDevice / getDeviceIds (runtime.h:163-171). */
+TTRT_API int ttrt_create_sub_mesh_device(ttrt_device_t parent, uint32_t mesh_y, uint32_t mesh_x, int has_offset,
+                                         uint32_t off_y, uint32_t off_x, ttrt_device_t *out);
+TTRT_API int ttrt_release_sub_mesh_device(ttrt_device_t sub);
+TTRT_API int ttrt_reshape_mesh_device(ttrt_device_t dev, uint32_t mesh_y, uint32_t mesh_x);
+TTRT_API int ttrt_device_ids(ttrt_device_t dev, int *ids, uint32_t cap, uint32_t *n);
+/* Binary::getDebugInfoGolden (runtime/lib/binary.cpp:233-253): the golden tensors the compiler embedded
+ * under a location string, one per device id.  `data` points into the binary (valid while it lives). */
+TTRT_API int ttrt_binary_golden_devices(ttrt_binary_t bin, const char *loc, uint32_t *devices, uint32_t cap, uint32_t *n);
+TTRT_API int ttrt_binary_golden_tensor(ttrt_binary_t bin, const char *loc, uint32_t device, uint32_t *rank,
+                                       int64_t shape[TTRT_MAX_RANK], int64_t stride[TTRT_MAX_RANK], int *dtype,
+                                       const void **data, size_t *size);
+
+/* ---- perf::Env (runtime/include/tt/runtime/perf.h:13-53) -----------------------------------------
+ * ttrt_perf_env_get = perf::Env::get(dumpDeviceRate, enablePerfTrace, tracyProgramMetadata): the first call
+ * fixes the settings; *enabled reports whether tracing is on (also switched on by
+ * TT_RUNTIME_ENABLE_PERF_TRACE=1).  While it is on, submit emits per op the reference's messages
+ * ("MLIR_OP_LOCATION;<loc>", "MLIR_CONST_EVAL_OP;<bool>", "MLIR_PROGRAM_METADATA;<text>") as NVTX marks and an
+ * NVTX range "<OpType> <loc>" around the op's launches.  ttrt_perf_message emits one message by hand
+ * (tag 0 tracyLogOpLocation, 1 tracyLogConstEvalProgram, 2 tracyLogProgramMetadata,
+ * 3 tracyLogInputLayoutConversion; 4 = setProgramMetadata).  ttrt_perf_emitted counts marks and ranges
+ * emitted so far (NVTX has no read-back; tests use this). */
+TTRT_API int ttrt_perf_env_get(uint32_t dump_device_rate, int enable_perf_trace, const char *program_metadata, int *enabled);
+TTRT_API int ttrt_perf_message(int tag, const char *text);
+TTRT_API uint64_t ttrt_perf_emitted(void);
 
 #ifdef __cplusplus
 }

@@ -123,9 +123,11 @@ def test_config4_decoder_block_full_size_op_by_op(rt, device):
     read back, and the oracle evaluates each op on the GPU's own operands (helpers.TeacherForcedOracle).
     Given identical inputs, two correctly rounded pipelines can differ by one bf16 ulp where an f32 sum
     lands next to a rounding boundary, nowhere by more: every op must be within atol 1e-2 + one ulp of
-    its own oracle with PCC >= 0.999 (attention: two ulps -- the probabilities enter the second
-    contraction rounded to bf16 here and as f32 in the oracle).  The fused program (nine launches) must
-    then equal the op-by-op run bit for bit, which carries these bounds over to what the benchmark times."""
+    its own oracle with PCC >= 0.999 -- attention included, although its probabilities enter the second
+    contraction rounded to bf16 here and as f32 in the oracle (measured: 61 % of its outputs bit-equal, the
+    rest one ulp off; the projections 99.2 - 99.8 % bit-equal; norms, rotary embedding, silu, multiply and
+    the residual adds bit-equal throughout).  The fused program (nine launches) must then equal the
+    op-by-op run bit for bit, which carries these bounds over to what the benchmark times."""
     from helpers import TeacherForcedOracle
     ins = graphs.decoder_block_inputs()
     buf = graphs.build_binary(graphs.decoder_block_graph)
@@ -149,8 +151,7 @@ def test_config4_decoder_block_full_size_op_by_op(rt, device):
              "gate_proj", "up_proj", "silu", "swiglu", "down_proj", "ffn_residual"}
     assert named <= set(tf.report), sorted(named - set(tf.report))
     for name, r in tf.report.items():
-        limit = 2.0 if name == "attention" else 1.0
-        assert r["pcc"] >= 0.999 and r["max_ulps"] <= limit, (name, r)
+        assert r["pcc"] >= 0.999 and r["max_ulps"] <= 1.0, (name, r)
     different = (fused != unfused).sum().item()
     assert different == 0, f"{different} elements differ between the fused and the op-by-op program"
 

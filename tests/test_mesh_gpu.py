@@ -359,3 +359,45 @@ def test_full_size_decoder_block_one_process_per_gpu(rt, world):
     # share of elements within one ulp is a little below the single-GPU figure (measured 0.93 on one GPU,
     # 0.90 on two); the bound on the error itself (RMS, maximum) is the single-GPU one.
     assert rep["finite"] and rep["pcc"] >= 0.999 and rep["within"] > 0.85 and rep["rms"] < 0.01 and rep["max_ulps"] <= 2.0, rep
+
+
+def test_concurrent_submit_on_disjoint_sub_meshes(rt, mesh2):
+    """Two threads, each with its own 1x1 sub-mesh of the 1x2 parent, submit the same binary at the same
+    time with different inputs, many times over (runtime/test/ttnn/python/n300/test_data_parallel.py:25-37,
+    56-77 does this on an n300 board).  Every result must equal what the device gives single-threaded."""
+    import threading
+    kw = dict(seq=256, hidden=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024)
+    buf = graphs.build_binary(graphs.decoder_block_graph, **kw)
+    binary = rt.Binary.load_from_memory(buf)
+    subs = [rt.create_sub_mesh_device(mesh2, [1, 1], [0, i]) for i in range(2)]
+    assert [d.get_device_ids() for d in subs] == [[0], [1]]
+    inputs = []
+    for i in range(2):
+        ins = graphs.decoder_block_inputs(**kw)
+        ins[0] = torch.randn(ins[0].shape, generator=torch.Generator().manual_seed(100 + i)).to(torch.bfloat16)
+        inputs.append(ins)
+    want = [oracle_results(graphs.decoder_block_graph, ins, **kw)[0] for ins in inputs]
+    results, errors = [[], []], []
+
+    def worker(i):
+        try:
+            dev_in = [rt.to_layout(rt.from_torch(t), subs[i], rt.get_layout(binary, 0, k), retain=True) for k, t in enumerate(inputs[i])]
+            for _ in range(8):
+                out = rt.submit(subs[i], binary, 0, dev_in)[0]
+                results[i].append(rt.to_torch(rt.to_host(out, untilize=True)[0]))
+        except Exception as e:  # surfaced in the main thread
+            errors.append((i, repr(e)))
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    try:
+        assert not errors, errors
+        for i in range(2):
+            assert len(results[i]) == 8 and all(torch.equal(r, results[i][0]) for r in results[i])
+            assert_matches(results[i][0], want[i], f"sub-mesh {i}", (0.999, 2e-2, 2.0 ** -6))
+        assert not torch.equal(results[0][0], results[1][0])
+    finally:
+        for d in subs:
+            rt.release_sub_mesh_device(d)

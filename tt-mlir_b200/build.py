@@ -25,8 +25,9 @@ NVCC_FLAGS = [
     "-I" + os.path.join(HERE, "runtime"), "-I" + os.path.join(HERE, "runtime", "include"),
     "-I" + os.path.join(ROOT, "include"),
 ]
+CUDA_INCLUDE = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")  # nvtx3 (header-only) for the C++ files
 CXX_FLAGS = [
-    "-std=c++17", "-O2", "-g", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-unused-function",
+    "-std=c++17", "-O2", "-g", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-unused-function", "-I" + CUDA_INCLUDE,
     "-I" + os.path.join(HERE, "runtime"), "-I" + os.path.join(HERE, "runtime", "include"),
     "-I" + os.path.join(ROOT, "include"),
 ]

@@ -17,7 +17,7 @@
 namespace ttb {
 
 int gemmTcgen05I8Try(const void *a, const void *b, void *c, int aDtype, int bDtype, int cDtype, int64_t m, int64_t n,
-                     int64_t k, const float *deqScale, float deqScalar, cudaStream_t stream);
+                     int64_t k, const float *deqScale, float deqScalar, const void *bias, int biasDtype, cudaStream_t stream);
 
 constexpr int I8_TILE = 32, I8_K = 32;
 
@@ -129,7 +129,7 @@ extern "C" int ttb_gemm_i8(const void *a, const void *b, void *c, int a_dtype, i
   if (batch * m * n == 0) return TTB_OK;
   cudaStream_t st = asStream(stream);
   if (!i8TensorCoreOff() && batch == 1 && !trans_a && trans_b) {
-    int rc = gemmTcgen05I8Try(a, b, c, a_dtype, b_dtype, c_dtype, m, n, k, deq_scale, deq_scalar, st);
+    int rc = gemmTcgen05I8Try(a, b, c, a_dtype, b_dtype, c_dtype, m, n, k, deq_scale, deq_scalar, nullptr, 0, st);
     if (rc != -1) return rc;
   }
   const int deq = c_dtype == kI32 ? 0 : (deq_scale ? 2 : 1);
@@ -157,4 +157,31 @@ extern "C" int ttb_gemm_i8_simt(const void *a, const void *b, void *c, int a_dty
   if (a_dtype == kI8 && b_dtype == kU8) TTB_I8(int8_t, uint8_t);
   TTB_I8(uint8_t, uint8_t);
 #undef TTB_I8
+}
+
+// ttb_gemm_i8 followed by `+ bias` (a row vector of n values in a float type): what a quantized linear
+// layer is after the compiler has moved the dequantize below the contraction -- matmul on the 8-bit
+// values, dequantize, add.  The dequantized value is rounded to the result type before the bias is added
+// and the sum rounded again, as the two separate ops round.  On the tensor-core kernel one launch;
+// elsewhere the contraction and a broadcast add.
+extern "C" int ttb_gemm_i8_bias(const void *a, const void *b, void *c, int a_dtype, int b_dtype, int c_dtype, int64_t batch,
+                                int64_t m, int64_t n, int64_t k, int trans_a, int trans_b, int64_t a_batch_stride,
+                                int64_t b_batch_stride, const float *deq_scale, float deq_scalar, const void *bias,
+                                int bias_dtype, void *stream) {
+  if (!bias) {
+    return ttb_gemm_i8(a, b, c, a_dtype, b_dtype, c_dtype, batch, m, n, k, trans_a, trans_b, a_batch_stride, b_batch_stride,
+                       deq_scale, deq_scalar, stream);
+  }
+  TTB_CHECK(a && b && c, "null tensor");
+  TTB_CHECK(c_dtype != kI32, "a bias needs a dequantized (float) result");
+  if (batch * m * n == 0) return TTB_OK;
+  if (!i8TensorCoreOff() && batch == 1 && !trans_a && trans_b) {
+    int rc = gemmTcgen05I8Try(a, b, c, a_dtype, b_dtype, c_dtype, m, n, k, deq_scale, deq_scalar, bias, bias_dtype, asStream(stream));
+    if (rc != -1) return rc;
+  }
+  int rc = ttb_gemm_i8(a, b, c, a_dtype, b_dtype, c_dtype, batch, m, n, k, trans_a, trans_b, a_batch_stride, b_batch_stride,
+                       deq_scale, deq_scalar, stream);
+  if (rc) return rc;
+  int64_t shape[2] = {batch * m, n}, cs[2] = {n, 1}, bs[2] = {0, 1};
+  return ttb_eltwise_binary(0 /* EltwiseBinaryOpType::Add */, c, c_dtype, bias, bias_dtype, c, c_dtype, 2, shape, cs, bs, stream);
 }

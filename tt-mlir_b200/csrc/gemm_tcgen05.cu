@@ -865,7 +865,8 @@ int gemmTcgen05SwigluTry(const void *a, const void *wGate, const void *wUp, void
 // Float16 store float(accumulator) * scale, scale being `deqScalar` (deqScale null) or deqScale[column]:
 // the dequantize op that follows a quantized matmul or convolution, fused.  -1 = not taken.
 int gemmTcgen05I8Try(const void *a, const void *b, void *c, int aDtype, int bDtype, int cDtype, int64_t m, int64_t n,
-                     int64_t k, const float *deqScale, float deqScalar, cudaStream_t stream) {
+                     int64_t k, const float *deqScale, float deqScalar, const void *bias, int biasDtype, cudaStream_t stream) {
+  if (bias && cDtype == kI32) return -1;
   if ((aDtype != kI8 && aDtype != kU8) || (bDtype != kI8 && bDtype != kU8)) return -1;
   if (cDtype != kI32 && cDtype != kF32 && cDtype != kBF16 && cDtype != kF16) return -1;
   if (k % 16 != 0 || m < 1 || n < 8 || k < 16) return -1; // rows of A and B are whole 16-byte units for TMA
@@ -891,7 +892,8 @@ int gemmTcgen05I8Try(const void *a, const void *b, void *c, int aDtype, int bDty
   if (!makeMap(&ma, a, kU8, m, k, TC_BM) || !makeMap(&mb, b, kU8, n, k, bn) || !makeMap(&mc, c, cDtype, m, n, 32)) return -1;
   TcParams p;
   p.M = m; p.N = n; p.K = k;
-  p.bias = nullptr; p.biasDt = 0; p.act = TTB_ACT_NONE; p.roundSteps = 0;
+  // a bias follows the dequantize as a separate add: the dequantized value is rounded before it (round step 1)
+  p.bias = bias; p.biasDt = biasDtype; p.act = TTB_ACT_NONE; p.roundSteps = bias ? 1 : 0;
   p.extra = nullptr; p.extraOp = 0;
   p.convX = nullptr; p.cTw = 0; p.cTilesM = 0; p.pushRows = 0; p.dual = 0;
   p.segCum[0] = p.segCum[1] = p.segCum[2] = static_cast<int>((n + bn - 1) / bn);

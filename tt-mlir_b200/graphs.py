@@ -428,10 +428,14 @@ def decoder_block_traced_binary(**kw) -> bytes:
     return traced_binary(decoder_block_graph, host_inputs=(0,), name="decoder_block", **kw)
 
 
-def build_binary(graph_fn, mesh_shape=(1, 1), name="main", **kw) -> bytes:
-    """Emits a one-program .ttnn binary for `graph_fn(b, **kw)`."""
+def build_binary(graph_fn, mesh_shape=(1, 1), name="main", goldens=None, system_desc=None, **kw) -> bytes:
+    """Emits a one-program .ttnn binary for `graph_fn(b, **kw)`.  `goldens` ({key: torch tensor}) are embedded
+    in the program's debug info; `system_desc` (the "system_desc" dictionary of a descriptor's JSON view)
+    becomes the binary's record of the system it was compiled for."""
     from .ttnn_builder import BinaryBuilder
-    bb = BinaryBuilder()
+    bb = BinaryBuilder(system_desc=system_desc)
     p = bb.program(name, mesh_shape)
     graph_fn(p, **kw)
+    for key, t in (goldens or {}).items():
+        p.golden(key, t)
     return bb.finish()

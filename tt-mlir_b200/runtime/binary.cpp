@@ -38,8 +38,9 @@ static void verifyOrThrow(const uint8_t *buf, size_t size) {
   if (declared > size) {
     TTRT_FATAL("flatbuffer truncated: size prefix says ", declared, " bytes, got ", size);
   }
-  if (std::memcmp(buf + 8, "TTNN", 4) != 0) {
-    // Other identifiers (TTM0 TTMetal binaries, TTSY system descriptors) are not executable here.
+  const bool systemDesc = std::memcmp(buf + 8, "TTSY", 4) == 0;
+  if (!systemDesc && std::memcmp(buf + 8, "TTNN", 4) != 0) {
+    // Other identifiers (TTM0 TTMetal binaries) are not executable here.
     std::string id(reinterpret_cast<const char *>(buf + 8), 4);
     TTRT_FATAL("unsupported flatbuffer identifier '", id, "': this runtime executes TTNN binaries");
   }
@@ -47,6 +48,13 @@ static void verifyOrThrow(const uint8_t *buf, size_t size) {
   fb::Verifier v(buf, declared);
   if (rootOff < 8 || !v.inBounds(buf + 4 + rootOff, 4)) {
     TTRT_FATAL("flatbuffer root offset out of bounds");
+  }
+  if (systemDesc) {
+    const auto *root = reinterpret_cast<const ::tt::target::SystemDescRoot *>(buf + 4 + rootOff);
+    if (!root->verify(v)) {
+      TTRT_FATAL("system descriptor verification failed: ", v.error());
+    }
+    return;
   }
   const auto *root = reinterpret_cast<const fbt::TTNNBinary *>(buf + 4 + rootOff);
   if (!root->verify(v)) {
@@ -137,7 +145,12 @@ Binary Binary::loadFromMemory(const void *memory, size_t size) {
   return Binary(Flatbuffer::loadFromMemory(memory, size));
 }
 
-const fbt::TTNNBinary *Binary::get() const { return rootOf(handle.get()); }
+const fbt::TTNNBinary *Binary::get() const {
+  if (std::memcmp(static_cast<const char *>(handle.get()) + 8, "TTNN", 4) != 0) {
+    TTRT_FATAL("this flatbuffer ('", getFileIdentifier(), "') holds no programs");
+  }
+  return rootOf(handle.get());
+}
 
 static const fbt::Program *programAt(const Binary &b, uint32_t idx) {
   const auto *programs = b.get()->programs();
@@ -282,6 +295,18 @@ std::string Binary::getProgramInputsAsJson(std::uint32_t i) const { return table
 std::string Binary::getProgramOutputsAsJson(std::uint32_t i) const { return tablesAsJson(programAt(*this, i)->outputs()); }
 std::string Binary::getProgramOpsAsJson(std::uint32_t i) const { return tablesAsJson(programAt(*this, i)->operations()); }
 
+// The descriptor of the system the binary was compiled for, in the form `ttrt` compares with the
+// machine's own (runtime/lib/binary.cpp getSystemDescAsJson): {"system_desc": {...}}; empty when the
+// binary carries none.
+std::string Binary::getSystemDescAsJson() const {
+  const auto *d = get()->system_desc();
+  if (!d) return "";
+  std::string s = "{\"system_desc\": ";
+  d->toJson(s);
+  s += "}";
+  return s;
+}
+
 std::string Binary::getMlirAsJson() const {
   std::string s;
   if (const auto *m = get()->mlir()) m->toJson(s);
@@ -291,8 +316,17 @@ std::string Binary::getMlirAsJson() const {
 
 std::string Flatbuffer::asJson() const {
   std::string s;
+  if (getFileIdentifier() == "TTSY") {
+    const uint8_t *p = static_cast<const uint8_t *>(handle.get());
+    reinterpret_cast<const ::tt::target::SystemDescRoot *>(p + 4 + fb::readScalar<uint32_t>(p + 4))->toJson(s);
+    return s;
+  }
   rootOf(handle.get())->toJson(s);
   return s;
 }
+
+namespace cuda {
+const char *schemaHashString() { return kSchemaHash; }
+} // namespace cuda
 
 } // namespace tt::runtime

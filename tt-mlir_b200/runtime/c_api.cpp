@@ -6,6 +6,7 @@
 #include "../../include/ttb_runtime.h"
 #include "impl.h"
 #include "tt/runtime/debug.h"
+#include "tt/runtime/perf.h"
 #include "tt/runtime/runtime.h"
 
 using namespace tt::runtime;
@@ -180,6 +181,23 @@ int ttrt_binary_program_ops_as_json(ttrt_binary_t bin, uint32_t program, char **
   TTRT_ARG(bin && out)
   TTRT_TRY
   *out = dupString(B(bin).getProgramOpsAsJson(program));
+  TTRT_CATCH
+}
+
+int ttrt_binary_query_string(ttrt_binary_t bin, int what, uint32_t program, char **out) {
+  TTRT_ARG(bin && out)
+  TTRT_TRY
+  std::string s;
+  switch (what) {
+  case TTRT_Q_PROGRAM_INPUTS_JSON: s = B(bin).getProgramInputsAsJson(program); break;
+  case TTRT_Q_PROGRAM_OUTPUTS_JSON: s = B(bin).getProgramOutputsAsJson(program); break;
+  case TTRT_Q_MLIR_JSON: s = B(bin).getMlirAsJson(); break;
+  case TTRT_Q_SYSTEM_DESC_JSON: s = B(bin).getSystemDescAsJson(); break;
+  case TTRT_Q_SCHEMA_HASH: s = B(bin).getSchemaHash(); break;
+  case TTRT_Q_TTMLIR_GIT_HASH: s = B(bin).getTTMLIRGitHash(); break;
+  default: g_err = "unknown query"; return 2;
+  }
+  *out = dupString(s);
   TTRT_CATCH
 }
 
@@ -528,5 +546,166 @@ int ttrt_program_index(void *program_ctx, size_t *index) {
   *index = getProgramIndex(*static_cast<CallbackContext *>(program_ctx));
   TTRT_CATCH
 }
+
+// ---- system descriptor, sub-meshes, embedded goldens, tensor references -----------------------------
+int ttrt_get_current_system_desc(ttrt_device_t dev, ttrt_binary_t *out) {
+  TTRT_ARG(out)
+  TTRT_TRY
+  SystemDesc d = dev ? getCurrentSystemDesc(std::nullopt, D(dev)) : getCurrentSystemDesc();
+  *out = new Binary(Flatbuffer(d.handle));
+  TTRT_CATCH
+}
+
+int ttrt_create_sub_mesh_device(ttrt_device_t parent, uint32_t mesh_y, uint32_t mesh_x, int has_offset, uint32_t off_y,
+                                uint32_t off_x, ttrt_device_t *out) {
+  TTRT_ARG(parent && out)
+  TTRT_TRY
+  std::optional<const std::vector<uint32_t>> off;
+  if (has_offset) off.emplace(std::vector<uint32_t>{off_y, off_x});
+  *out = new Device(createSubMeshDevice(D(parent), {mesh_y, mesh_x}, off));
+  TTRT_CATCH
+}
+
+int ttrt_release_sub_mesh_device(ttrt_device_t sub) {
+  TTRT_ARG(sub)
+  TTRT_TRY
+  releaseSubMeshDevice(D(sub));
+  TTRT_CATCH
+}
+
+int ttrt_reshape_mesh_device(ttrt_device_t dev, uint32_t mesh_y, uint32_t mesh_x) {
+  TTRT_ARG(dev)
+  TTRT_TRY
+  reshapeMeshDevice(D(dev), {mesh_y, mesh_x});
+  TTRT_CATCH
+}
+
+int ttrt_device_ids(ttrt_device_t dev, int *ids, uint32_t cap, uint32_t *n) {
+  TTRT_ARG(dev && n)
+  TTRT_TRY
+  std::vector<int> v = getDeviceIds(D(dev));
+  *n = static_cast<uint32_t>(v.size());
+  for (uint32_t i = 0; ids && i < cap && i < v.size(); ++i) ids[i] = v[i];
+  TTRT_CATCH
+}
+
+int ttrt_binary_golden_devices(ttrt_binary_t bin, const char *loc, uint32_t *devices, uint32_t cap, uint32_t *n) {
+  TTRT_ARG(bin && loc && n)
+  TTRT_TRY
+  std::string key(loc);
+  auto m = B(bin).getDebugInfoGolden(key);
+  *n = static_cast<uint32_t>(m.size());
+  uint32_t i = 0;
+  for (const auto &kv : m) {
+    if (devices && i < cap) devices[i] = kv.first;
+    ++i;
+  }
+  TTRT_CATCH
+}
+
+int ttrt_binary_golden_tensor(ttrt_binary_t bin, const char *loc, uint32_t device, uint32_t *rank, int64_t shape[TTRT_MAX_RANK],
+                              int64_t stride[TTRT_MAX_RANK], int *dtype, const void **data, size_t *size) {
+  TTRT_ARG(bin && loc && rank && shape && stride && dtype && data && size)
+  TTRT_TRY
+  std::string key(loc);
+  auto m = B(bin).getDebugInfoGolden(key);
+  auto it = m.find(device);
+  *data = nullptr;
+  *size = 0;
+  *rank = 0;
+  if (it != m.end() && it->second) {
+    const auto *g = it->second;
+    const uint32_t r = g->shape() ? g->shape()->size() : 0;
+    if (r > TTRT_MAX_RANK) {
+      g_err = "golden tensor rank exceeds TTRT_MAX_RANK";
+      return 1;
+    }
+    *rank = r;
+    for (uint32_t i = 0; i < r; ++i) {
+      shape[i] = g->shape()->Get(i);
+      stride[i] = g->stride() && i < g->stride()->size() ? g->stride()->Get(i) : 0;
+    }
+    *dtype = static_cast<int>(g->dtype());
+    if (g->data()) {
+      *data = g->data()->data();
+      *size = g->data()->size();
+    }
+  }
+  TTRT_CATCH
+}
+
+static int copyRefs(const std::vector<TensorRef> &refs, ttrt_tensor_ref_t *out, uint32_t cap, uint32_t *n) {
+  *n = static_cast<uint32_t>(refs.size());
+  for (uint32_t i = 0; out && i < cap && i < refs.size(); ++i) out[i] = new TensorRef(refs[i]);
+  return 0;
+}
+
+int ttrt_op_input_refs(void *op_ctx, ttrt_tensor_ref_t *out, uint32_t cap, uint32_t *n) {
+  TTRT_ARG(op_ctx && n)
+  TTRT_TRY
+  return copyRefs(getOpInputRefs(*static_cast<OpContext *>(op_ctx)), out, cap, n);
+  TTRT_CATCH
+}
+
+int ttrt_op_output_refs(void *op_ctx, ttrt_tensor_ref_t *out, uint32_t cap, uint32_t *n) {
+  TTRT_ARG(op_ctx && n)
+  TTRT_TRY
+  return copyRefs(getOpOutputRefs(*static_cast<OpContext *>(op_ctx)), out, cap, n);
+  TTRT_CATCH
+}
+
+void ttrt_tensor_ref_free(ttrt_tensor_ref_t ref) { delete static_cast<TensorRef *>(ref); }
+
+int ttrt_tensor_ref_info(ttrt_tensor_ref_t ref, uint32_t *rank, uint32_t shape[TTRT_MAX_RANK], int *dtype) {
+  TTRT_ARG(ref && rank && shape && dtype)
+  TTRT_TRY
+  auto &r = *static_cast<TensorRef *>(ref);
+  std::vector<uint32_t> s = getTensorRefShape(r);
+  TTRT_ARG(s.size() <= TTRT_MAX_RANK)
+  *rank = static_cast<uint32_t>(s.size());
+  for (size_t i = 0; i < s.size(); ++i) shape[i] = s[i];
+  *dtype = static_cast<int>(getTensorRefDataType(r));
+  TTRT_CATCH
+}
+
+int ttrt_retrieve_tensor_from_pool(void *program_ctx, ttrt_tensor_ref_t ref, int untilize, ttrt_tensor_t *out) {
+  TTRT_ARG(program_ctx && ref && out)
+  TTRT_TRY
+  auto t = retrieveTensorFromPool(*static_cast<CallbackContext *>(program_ctx), *static_cast<TensorRef *>(ref), untilize != 0);
+  *out = t ? new Tensor(*t) : nullptr;
+  TTRT_CATCH
+}
+
+int ttrt_update_tensor_in_pool(void *program_ctx, ttrt_tensor_ref_t ref, ttrt_tensor_t src) {
+  TTRT_ARG(program_ctx && ref && src)
+  TTRT_TRY
+  updateTensorInPool(*static_cast<CallbackContext *>(program_ctx), *static_cast<TensorRef *>(ref), T(src));
+  TTRT_CATCH
+}
+
+// ---- perf::Env (runtime/include/tt/runtime/perf.h) ----------------------------------------------------
+int ttrt_perf_env_get(uint32_t dump_device_rate, int enable_perf_trace, const char *program_metadata, int *enabled) {
+  TTRT_TRY
+  perf::Env &e = perf::Env::get(dump_device_rate, enable_perf_trace != 0, program_metadata ? program_metadata : "");
+  if (enabled) *enabled = e.enablePerfTrace ? 1 : 0;
+  TTRT_CATCH
+}
+
+int ttrt_perf_message(int tag, const char *text) {
+  TTRT_ARG(text)
+  TTRT_TRY
+  perf::Env &e = perf::Env::get();
+  switch (tag) {
+  case 0: e.tracyLogOpLocation(text); break;
+  case 1: e.tracyLogConstEvalProgram(std::strcmp(text, "true") == 0); break;
+  case 2: e.tracyLogProgramMetadata(text); break;
+  case 3: e.tracyLogInputLayoutConversion(std::strcmp(text, "true") == 0); break;
+  case 4: e.setProgramMetadata(text); break;
+  default: g_err = "unknown perf tag"; return 2;
+  }
+  TTRT_CATCH
+}
+
+uint64_t ttrt_perf_emitted(void) { return perf::Env::emitted(); }
 
 } // extern "C"

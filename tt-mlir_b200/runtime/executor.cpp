@@ -23,6 +23,7 @@
 
 #include "impl.h"
 #include "tt/runtime/debug.h"
+#include "tt/runtime/perf.h"
 #include "tt/runtime/runtime.h"
 
 namespace tt::runtime::cuda {
@@ -424,7 +425,7 @@ private:
   float convDeqScalar = 0.0f; // ... or its per-tensor scale
   // matmul on quantized (8-bit integer) operands; deqScale / deqScalar describe a fused dequantize
   void runIntGemm(const fbt::TensorRef *aRef, const fbt::TensorRef *bRef, const fbt::TensorRef *outRef, bool ta, bool tb,
-                  const TensorPtr &deqScale, float deqScalar);
+                  const TensorPtr &deqScale, float deqScalar, const fbt::TensorRef *biasRef = nullptr);
   size_t tryGroupedGemm(size_t i);
   size_t trySwiglu(size_t i);
   size_t trySiluMul(size_t i);
@@ -659,6 +660,10 @@ std::vector<Tensor> Executor::run() {
   const auto *ops = prog->operations();
   size_t n = ops ? ops->size() : 0;
   bool syncAfterOp = debug::Env::get().syncAfterOp;
+  perf::Env &perfEnv = perf::Env::get();
+  const bool perfTrace = perfEnv.enablePerfTrace;
+  // const-eval functions are the private programs the compiler names "<function>_const_eval_<n>"
+  const bool constEvalProgram = prog->name() && prog->name()->str().find("const_eval") != std::string::npos;
   for (size_t i = 0; i < n;) {
     const auto *op = ops->Get(static_cast<uint32_t>(i));
     std::shared_ptr<OpContextImpl> opCtxImpl;
@@ -670,13 +675,24 @@ std::vector<Tensor> Executor::run() {
       (*hooks.getPreOperatorCallback())(bin, cbCtx, OpContext(std::static_pointer_cast<void>(opCtxImpl), DeviceRuntime::CUDA));
     }
     size_t used;
+    if (perfTrace) {
+      // What the reference logs per op (runtime/lib/ttnn/program_executor.cpp:234-237), plus a range
+      // named after the op that spans its launches (a fused chain is one range named after its first op).
+      const std::string loc = op->loc_info() ? op->loc_info()->str() : "";
+      perfEnv.tracyLogOpLocation(loc);
+      perfEnv.tracyLogConstEvalProgram(constEvalProgram);
+      perfEnv.tracyLogProgramMetadata(perfEnv.tracyProgramMetadata);
+      perfEnv.rangePush(std::string(fbt::EnumNameOpType(op->type_type())) + " " + loc);
+    }
     try {
       used = runOp(i);
     } catch (const std::runtime_error &e) {
+      if (perfTrace) perfEnv.rangePop();
       std::string loc = op->loc_info() ? op->loc_info()->str() : "";
       throw std::runtime_error(std::string(e.what()) + " [while executing op #" + std::to_string(i) + " " +
                                fbt::EnumNameOpType(op->type_type()) + (loc.empty() ? "" : " at " + loc) + "]");
     }
+    if (perfTrace) perfEnv.rangePop();
     if (syncAfterOp) {
       eachRank([&](size_t, const RankCtx &r) { TTB_CALL(ttb_stream_sync(r.stream)); });
     }
@@ -1313,8 +1329,9 @@ bool isQuantizedStorage(DataType dt) { return dt == DataType::Int8 || dt == Data
 // is the accumulator times a scale, which is the dequantize op that followed, fused.  Int32 containers
 // are narrowed to Int8 first (their values are in the int8 range by construction).
 void Executor::runIntGemm(const fbt::TensorRef *aRef, const fbt::TensorRef *bRef, const fbt::TensorRef *outRef, bool ta, bool tb,
-                          const TensorPtr &deqScale, float deqScalar) {
+                          const TensorPtr &deqScale, float deqScalar, const fbt::TensorRef *biasRef) {
   TensorPtr a = getDevice(aRef), b = getDevice(bRef);
+  TensorPtr bias = biasRef ? getDevice(biasRef) : nullptr;
   if (a->dtype == DataType::Int32 || b->dtype == DataType::Int32) {
     // Only safe while Int32 containers are known to hold int8 values (the rule the quantization ops
     // follow here; TTB_QUANT_I32_FULL_RANGE=1 lifts it, and with it this path).
@@ -1351,9 +1368,10 @@ void Executor::runIntGemm(const fbt::TensorRef *aRef, const fbt::TensorRef *bRef
               dataTypeName(out->dtype));
   if (deqScale) TTRT_ASSERT(static_cast<int64_t>(deqScale->volume()) == N, "per-channel scale must have N = ", N, " entries");
   eachRank([&](size_t i, const RankCtx &r) {
-    TTB_CALL(ttb_gemm_i8(a->shards[i]->ptr, b->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(a->dtype), ttbDtype(b->dtype),
-                         ttbDtype(out->dtype), batch, M, N, K, ta, tb, aStride, bStride,
-                         deqScale ? static_cast<const float *>(deqScale->shards[i]->ptr) : nullptr, deqScalar, r.stream));
+    TTB_CALL(ttb_gemm_i8_bias(a->shards[i]->ptr, b->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(a->dtype), ttbDtype(b->dtype),
+                              ttbDtype(out->dtype), batch, M, N, K, ta, tb, aStride, bStride,
+                              deqScale ? static_cast<const float *>(deqScale->shards[i]->ptr) : nullptr, deqScalar,
+                              bias ? bias->shards[i]->ptr : nullptr, bias ? ttbDtype(bias->dtype) : 0, r.stream));
   });
   put(outRef, out);
 }
@@ -1399,9 +1417,36 @@ size_t Executor::tryQuantizedGemm(size_t i) {
   } else if (q.zp != 0) {
     return 0;
   }
-  runIntGemm(a, b, dq->out(), ta, tb, scale, q.scale);
+  // optional bias: dequantize -> add(row vector of N), the rounding of the dequantized value kept
+  const fbt::TensorRef *result = dq->out(), *biasRef = nullptr;
+  size_t last = j;
+  if (singleUse(result) && odt != DataType::Float32) {
+    std::vector<const fbt::Operation *> d2;
+    size_t j2 = j + 1;
+    const auto *aop = peek(j2, d2);
+    if (aop && aop->type_type() == OpType::EltwiseBinaryOp) {
+      const auto *add = aop->type_as_EltwiseBinaryOp();
+      const fbt::TensorRef *other = nullptr;
+      if (add->type() == fbt::EltwiseBinaryOpType::Add) {
+        if (add->lhs()->global_id() == result->global_id()) other = add->rhs();
+        else if (add->rhs()->global_id() == result->global_id()) other = add->lhs();
+      }
+      if (other && other->global_id() != result->global_id() && refShape(add->out()) == refShape(result) &&
+          refDtype(add->out()) == odt && pool.count(other->global_id())) {
+        std::vector<uint32_t> os = refShape(other);
+        const int64_t N = refShape(result).empty() ? 1 : refShape(result).back();
+        if (!os.empty() && os.back() == N && static_cast<int64_t>(prod(os, 0, os.size())) == N) {
+          biasRef = other;
+          result = add->out();
+          deallocs.insert(deallocs.end(), d2.begin(), d2.end());
+          last = j2;
+        }
+      }
+    }
+  }
+  runIntGemm(a, b, result, ta, tb, scale, q.scale, biasRef);
   runDeallocs(deallocs);
-  return j + 1 - i;
+  return last + 1 - i;
 }
 
 static int unaryToAct(fbt::EltwiseUnaryOpType t) {

@@ -35,6 +35,9 @@ template <typename... Args> std::string strcat_(Args &&...args) {
   return os.str();
 }
 
+// The schema hash this runtime writes and accepts (binary.cpp).
+const char *schemaHashString();
+
 #define TTRT_FATAL(...) ::tt::runtime::cuda::fatal(::tt::runtime::cuda::strcat_(__VA_ARGS__))
 #define TTRT_ASSERT(cond, ...)                                                           \
   do {                                                                                   \

@@ -167,6 +167,7 @@ struct Binary : public Flatbuffer {
   std::string getProgramInputsAsJson(std::uint32_t programIndex) const;
   std::string getProgramOutputsAsJson(std::uint32_t programIndex) const;
   std::string getMlirAsJson() const;
+  std::string getSystemDescAsJson() const;
   std::uint32_t getNumProgramInputs(std::uint32_t programIndex) const;
   std::uint32_t getNumProgramOutputs(std::uint32_t programIndex) const;
   std::vector<TensorDesc> getProgramInputs(std::uint32_t programIndex) const;

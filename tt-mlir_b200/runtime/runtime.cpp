@@ -6,6 +6,7 @@
 #include <cstring>
 #include <iostream>
 
+#include "fb_writer.h"
 #include "impl.h"
 #include "tt/runtime/debug.h"
 #include "tt/runtime/runtime.h"
@@ -722,9 +723,101 @@ void deallocateBuffers(Device) {}
 void dumpMemoryReport(Device) {}
 void readDeviceProfilerResults(Device) {}
 
-SystemDesc getCurrentSystemDesc(std::optional<DispatchCoreType>, std::optional<Device>) {
-  TTRT_FATAL("getCurrentSystemDesc: system descriptors describe Tenstorrent chips; the CUDA target has none. "
-             "Callers that compare descriptors must skip the check for this runtime");
+// A descriptor of the machine in the reference's wire format ("TTSY", Common/system_desc.fbs), so
+// that callers which fetch, print, store or compare system descriptors keep working (`ttrt query`,
+// tools/ttrt/common/util.py:868-912).  The schema describes Tenstorrent chips, so the GPU is put in
+// its terms: one ChipDesc per visible GPU (or per device of `meshDevice`), the SMs as a y x x worker
+// grid (2 dies of SMs / 2 on B200), shared memory per SM as the L1 size, HBM as ONE DRAM channel of the
+// device's total memory, 32 x 32 tiles, the data types this runtime computes in.  The `arch` field is an
+// enum of Tenstorrent architectures with no spare value; Blackhole is written and the product
+// identifier says what the device really is.  A binary compiled for Tenstorrent silicon carries a
+// different descriptor: callers must skip the comparison for this target (ttrt: --ignore-system-desc).
+SystemDesc getCurrentSystemDesc(std::optional<DispatchCoreType>, std::optional<Device> meshDevice) {
+  std::vector<int> ordinals;
+  if (meshDevice) {
+    ordinals = getDeviceIds(*meshDevice);
+  } else {
+    int n = 0;
+    TTB_CALL(ttb_device_count(&n));
+    for (int i = 0; i < n; ++i) ordinals.push_back(i);
+  }
+  // A machine without a visible GPU gets a descriptor with no chips.
+  fb::Writer w;
+  struct Dim2d { int32_t y, x; };
+  struct ChipCoord { uint32_t rack, shelf, y, x; };
+  std::vector<uint32_t> chipDescs, indices, capabilities;
+  std::vector<ChipCoord> coords;
+  std::string product = "NVIDIA-CUDA";
+  for (size_t i = 0; i < ordinals.size(); ++i) {
+    int sms = 0, major = 0, minor = 0;
+    size_t total = 0;
+    TTB_CALL(ttb_device_info(ordinals[i], &sms, &total, &major, &minor));
+    if (i == 0) product = "NVIDIA-CUDA-sm_" + std::to_string(major) + std::to_string(minor) + "-" + std::to_string(sms) + "SM";
+    const std::vector<uint16_t> dtypes = {
+        static_cast<uint16_t>(DataType::Float32), static_cast<uint16_t>(DataType::Float16), static_cast<uint16_t>(DataType::BFloat16),
+        static_cast<uint16_t>(DataType::UInt32),  static_cast<uint16_t>(DataType::UInt16),  static_cast<uint16_t>(DataType::UInt8),
+        static_cast<uint16_t>(DataType::Int32),   static_cast<uint16_t>(DataType::Int8)};
+    const uint32_t dtypeVec = w.createScalarVector(dtypes);
+    const Dim2d tile{32, 32};
+    const uint32_t tileVec = w.createStructVector(&tile, 1, sizeof(Dim2d), 4);
+    const Dim2d bank{0, 0};
+    const uint32_t bank0 = w.createStructVector(&bank, 1, sizeof(Dim2d), 4);
+    const uint32_t bank1 = w.createStructVector(&bank, 1, sizeof(Dim2d), 4);
+    const Dim2d grid{sms % 2 == 0 ? 2 : 1, sms % 2 == 0 ? sms / 2 : sms}, zero{0, 0}, dramGrid{1, 1};
+    w.startTable(22);
+    w.addScalar<uint32_t>(0, 1 /* Arch::Blackhole: see above */, 0);
+    w.addStruct(1, &grid, sizeof(grid), 4);
+    w.addStruct(2, &zero, sizeof(zero), 4);
+    w.addScalar<uint64_t>(3, 227 * 1024);                 // shared memory per SM
+    w.addScalar<uint32_t>(4, 1);                          // HBM as one DRAM channel
+    w.addScalar<uint64_t>(5, static_cast<uint64_t>(total));
+    w.addScalar<uint32_t>(6, 16);                         // alignment of bulk (TMA) copies
+    w.addScalar<uint32_t>(7, 64);
+    w.addScalar<uint32_t>(8, 256);                        // allocation granularity of the memory pool
+    w.addOffset(13, dtypeVec);
+    w.addOffset(14, tileVec);
+    w.addScalar<uint32_t>(15, 512);                       // tensor-memory columns per SM
+    w.addScalar<uint32_t>(16, 0);
+    w.addScalar<uint32_t>(17, 4);                         // warp schedulers per SM
+    w.addScalar<uint32_t>(18, 1);
+    w.addStruct(19, &dramGrid, sizeof(dramGrid), 4);
+    w.addOffset(20, bank0);
+    w.addOffset(21, bank1);
+    chipDescs.push_back(w.endTable());
+    indices.push_back(static_cast<uint32_t>(i));
+    capabilities.push_back(1);                            // HostMMIO: every GPU is reachable from the host
+    coords.push_back(ChipCoord{0, 0, 0, static_cast<uint32_t>(i)});
+  }
+  const uint32_t triple = w.createString("x86_64-pc-linux-gnu");
+  w.startTable(2);
+  w.addScalar<uint8_t>(0, 0);                             // CPURole::Host
+  w.addOffset(1, triple);
+  const uint32_t cpu = w.endTable();
+  const uint32_t cpuVec = w.createOffsetVector({cpu});
+  const uint32_t chipVec = w.createOffsetVector(chipDescs);
+  const uint32_t idxVec = w.createScalarVector(indices);
+  const uint32_t capVec = w.createScalarVector(capabilities);
+  const uint32_t coordVec = w.createStructVector(coords.data(), coords.size(), sizeof(ChipCoord), 4);
+  w.startTable(6);
+  w.addOffset(0, cpuVec);
+  w.addOffset(1, chipVec);
+  w.addOffset(2, idxVec);
+  w.addOffset(3, capVec);
+  w.addOffset(4, coordVec);
+  const uint32_t desc = w.endTable();
+  const uint32_t hash = w.createString(schemaHashString());
+  const uint32_t git = w.createString("b200-runtime");
+  const uint32_t prod = w.createString(product);
+  struct Version { uint16_t major, minor; uint32_t patch; } version{0, 1, 0};
+  w.startTable(5);
+  w.addStruct(0, &version, sizeof(version), 4);
+  w.addOffset(1, hash);
+  w.addOffset(2, git);
+  w.addOffset(3, prod);
+  w.addOffset(4, desc);
+  const uint32_t root = w.endTable();
+  std::vector<uint8_t> bytes = w.finish(root, "TTSY");
+  return SystemDesc(Flatbuffer::loadFromMemory(bytes.data(), bytes.size()).handle);
 }
 
 // ---- host tensors ------------------------------------------------------------------------

@@ -75,7 +75,8 @@ lib.ttb_launch_count.restype = ctypes.c_uint64
 lib.ttb_dtype_size.restype = ctypes.c_size_t
 lib.ttb_conv2d_workspace_bytes.restype = ctypes.c_size_t
 lib.ttrt_free_string.argtypes = [ctypes.c_void_p]
-for _n in ("ttrt_binary_free", "ttrt_device_free", "ttrt_tensor_free", "ttrt_layout_free"):
+lib.ttrt_perf_emitted.restype = ctypes.c_uint64
+for _n in ("ttrt_binary_free", "ttrt_device_free", "ttrt_tensor_free", "ttrt_layout_free", "ttrt_tensor_ref_free"):
     getattr(lib, _n).argtypes = [ctypes.c_void_p]
     getattr(lib, _n).restype = None
 
@@ -207,6 +208,64 @@ class Binary:
                                                   ctypes.byref(x)))
         return (y.value, x.value)
 
+    def _query(self, what: int, program_index: int = 0) -> str:
+        p = ctypes.c_void_p()
+        _check(lib.ttrt_binary_query_string(_vp(self._h), what, ctypes.c_uint32(program_index), ctypes.byref(p)))
+        try:
+            return ctypes.string_at(p.value).decode("utf-8", "replace")
+        finally:
+            lib.ttrt_free_string(p)
+
+    def get_program_inputs_as_json(self, program_index: int) -> str:
+        return self._query(0, program_index)
+
+    def get_program_outputs_as_json(self, program_index: int) -> str:
+        return self._query(1, program_index)
+
+    def get_mlir_as_json(self) -> str:
+        return self._query(2)
+
+    def get_system_desc_as_json(self) -> str:
+        return self._query(3)
+
+    @property
+    def schema_hash(self) -> str:
+        return self._query(4)
+
+    @property
+    def ttmlir_git_hash(self) -> str:
+        return self._query(5)
+
+    def get_debug_info_golden(self, loc: str):
+        """The golden tensors the compiler embedded under `loc` (Binary::getDebugInfoGolden): a dict
+        device id -> GoldenTensor; empty when the binary carries none for that location."""
+        n = ctypes.c_uint32()
+        _check(lib.ttrt_binary_golden_devices(_vp(self._h), loc.encode(), None, 0, ctypes.byref(n)))
+        if n.value == 0:
+            return {}
+        devs = (ctypes.c_uint32 * n.value)()
+        _check(lib.ttrt_binary_golden_devices(_vp(self._h), loc.encode(), devs, n, ctypes.byref(n)))
+        out = {}
+        for d in devs:
+            rank, dt = ctypes.c_uint32(), ctypes.c_int()
+            shape, stride = (ctypes.c_int64 * 8)(), (ctypes.c_int64 * 8)()
+            data, size = ctypes.c_void_p(), ctypes.c_size_t()
+            _check(lib.ttrt_binary_golden_tensor(_vp(self._h), loc.encode(), ctypes.c_uint32(d), ctypes.byref(rank), shape, stride,
+                                                 ctypes.byref(dt), ctypes.byref(data), ctypes.byref(size)))
+            out[int(d)] = GoldenTensor(loc, list(shape[:rank.value]), list(stride[:rank.value]), DataType(dt.value),
+                                       ctypes.string_at(data.value, size.value) if data.value else b"")
+        return out
+
+
+class GoldenTensor:
+    """A tensor the compiler stored in a binary's debug info (tt.target.GoldenTensor)."""
+
+    def __init__(self, name, shape, stride, dtype, data: bytes):
+        self.name, self.shape, self.stride, self.dtype, self._data = name, shape, stride, dtype, data
+
+    def get_data_buffer(self) -> bytearray:
+        return bytearray(self._data)
+
 
 # ---------------------------------------------------------------------------------- Device
 class MeshDeviceOptions:
@@ -233,6 +292,13 @@ class Device:
         _check(lib.ttrt_device_mesh_shape(_vp(self._h), ctypes.byref(y), ctypes.byref(x)))
         return [y.value, x.value]
 
+    def get_device_ids(self) -> List[int]:
+        n = ctypes.c_uint32()
+        _check(lib.ttrt_device_ids(_vp(self._h), None, 0, ctypes.byref(n)))
+        ids = (ctypes.c_int * max(n.value, 1))()
+        _check(lib.ttrt_device_ids(_vp(self._h), ids, n, ctypes.byref(n)))
+        return list(ids[:n.value])
+
     def num_local(self) -> int:
         n = ctypes.c_uint32()
         _check(lib.ttrt_device_num_local(_vp(self._h), ctypes.byref(n)))
@@ -250,6 +316,31 @@ def get_num_available_devices() -> int:
     n = ctypes.c_size_t()
     _check(lib.ttrt_get_num_available_devices(ctypes.byref(n)))
     return n.value
+
+
+def get_current_system_desc(device: Optional["Device"] = None) -> Binary:
+    """The machine (or `device`) described in the reference's system-descriptor format: a "TTSY"
+    flatbuffer with as_json / store / version / file_identifier."""
+    h = ctypes.c_void_p()
+    _check(lib.ttrt_get_current_system_desc(_vp(device._h) if device is not None else None, ctypes.byref(h)))
+    return Binary(h.value)
+
+
+def create_sub_mesh_device(parent: "Device", mesh_shape: Sequence[int], mesh_offset: Optional[Sequence[int]] = None) -> "Device":
+    h = ctypes.c_void_p()
+    off = list(mesh_offset) if mesh_offset is not None else [0, 0]
+    _check(lib.ttrt_create_sub_mesh_device(_vp(parent._h), ctypes.c_uint32(mesh_shape[0]), ctypes.c_uint32(mesh_shape[1]),
+                                           int(mesh_offset is not None), ctypes.c_uint32(off[0]), ctypes.c_uint32(off[1]),
+                                           ctypes.byref(h)))
+    return Device(h.value)
+
+
+def release_sub_mesh_device(sub: "Device") -> None:
+    _check(lib.ttrt_release_sub_mesh_device(_vp(sub._h)))
+
+
+def reshape_mesh_device(device: "Device", mesh_shape: Sequence[int]) -> None:
+    _check(lib.ttrt_reshape_mesh_device(_vp(device._h), ctypes.c_uint32(mesh_shape[0]), ctypes.c_uint32(mesh_shape[1])))
 
 
 def get_nccl_unique_id() -> bytes:
@@ -498,6 +589,78 @@ def get_op_output_tensor(op: OpContext, ctx: CallbackContext) -> Optional[Tensor
     h = ctypes.c_void_p()
     _check(lib.ttrt_op_output_tensor(_vp(op._p), _vp(ctx._p), ctypes.byref(h)))
     return Tensor(h.value) if h.value else None
+
+
+def perf_env(dump_device_rate: int = 1000, enable_perf_trace: bool = False, program_metadata: str = "") -> bool:
+    """perf::Env::get: the first call in a process fixes the settings.  Returns whether tracing is on."""
+    on = ctypes.c_int()
+    _check(lib.ttrt_perf_env_get(ctypes.c_uint32(dump_device_rate), int(enable_perf_trace), program_metadata.encode(),
+                                 ctypes.byref(on)))
+    return bool(on.value)
+
+
+def perf_message(text: str, tag: int = 0) -> None:
+    _check(lib.ttrt_perf_message(tag, text.encode()))
+
+
+def perf_emitted() -> int:
+    return int(lib.ttrt_perf_emitted())
+
+
+class TensorRef:
+    """Handle to a tensor of a running program (what hooks get from get_op_input_refs / get_op_output_refs)."""
+
+    def __init__(self, handle: int):
+        self._h = handle
+
+    def __del__(self):
+        if getattr(self, "_h", None) and lib is not None:
+            lib.ttrt_tensor_ref_free(self._h)
+            self._h = None
+
+    def _info(self):
+        rank, dt = ctypes.c_uint32(), ctypes.c_int()
+        shape = (ctypes.c_uint32 * 8)()
+        _check(lib.ttrt_tensor_ref_info(_vp(self._h), ctypes.byref(rank), shape, ctypes.byref(dt)))
+        return list(shape[:rank.value]), DataType(dt.value)
+
+    def get_shape(self):
+        return self._info()[0]
+
+    def get_dtype(self) -> DataType:
+        return self._info()[1]
+
+
+def _refs(fn, op: "OpContext") -> List[TensorRef]:
+    n = ctypes.c_uint32()
+    _check(fn(_vp(op._p), None, 0, ctypes.byref(n)))
+    arr = (ctypes.c_void_p * max(n.value, 1))()
+    _check(fn(_vp(op._p), arr, n, ctypes.byref(n)))
+    return [TensorRef(arr[i]) for i in range(n.value)]
+
+
+def get_op_input_refs(op: "OpContext") -> List[TensorRef]:
+    return _refs(lib.ttrt_op_input_refs, op)
+
+
+def get_op_output_refs(op: "OpContext") -> List[TensorRef]:
+    return _refs(lib.ttrt_op_output_refs, op)
+
+
+def retrieve_tensor_from_pool(ctx: "CallbackContext", ref: TensorRef, untilize: bool = True) -> Optional[Tensor]:
+    h = ctypes.c_void_p()
+    _check(lib.ttrt_retrieve_tensor_from_pool(_vp(ctx._p), _vp(ref._h), int(untilize), ctypes.byref(h)))
+    return Tensor(h.value) if h.value else None
+
+
+def update_tensor_in_pool(ctx: "CallbackContext", ref: TensorRef, src: Tensor) -> None:
+    _check(lib.ttrt_update_tensor_in_pool(_vp(ctx._p), _vp(ref._h), _vp(src._h)))
+
+
+def get_program_index(ctx: "CallbackContext") -> int:
+    v = ctypes.c_size_t()
+    _check(lib.ttrt_program_index(_vp(ctx._p), ctypes.byref(v)))
+    return v.value
 
 
 class DebugHooks:

@@ -59,6 +59,11 @@ S.table("SystemDesc", [
     ("cpu_descs", "[CPUDesc]"), ("chip_descs", "[ChipDesc]"), ("chip_desc_indices", "[u32]"),
     ("chip_capabilities", "[u32]"), ("chip_coords", "[ChipCoord]"), ("chip_channels", "opaque"),
 ])
+# Root of a system-descriptor file (identifier "TTSY", Common/system_desc.fbs): what
+# getCurrentSystemDesc returns and `ttrt query` stores.
+S.table("SystemDescRoot", [
+    ("version", "Version"), ("schema_hash", "string"), ("ttmlir_git_hash", "string"),
+    ("product_identifier", "string"), ("system_desc", "SystemDesc")])
 S.table("DeviceRef", [("global_id", "u32")])
 S.table("DynamicLib", [("dylib_id", "u32"), ("raw_file", "[u8]")])
 S.table("MLIR", [("name", "string"), ("source", "string")])

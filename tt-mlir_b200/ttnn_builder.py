@@ -79,6 +79,7 @@ class ProgramBuilder:
         self.ops: List[dict] = []
         self._op_values: List[Tuple[List[Value], List[Value]]] = []
         self.private = False
+        self.goldens = {}                  # key -> [GoldenDeviceTensor], see golden()
         self.index = len(binary.programs)  # position in the binary = the id other programs call it by
         self.device_ref = {"global_id": binary.next_id()}
         self._emit("GetDeviceOp", {"mesh": self.mesh_shape, "offset": (0, 0),
@@ -738,8 +739,20 @@ class ProgramBuilder:
                                 "debug_info": f'"ttnn.deallocate"(%{vid})', "loc_info": f'loc("dealloc_{vid}")'})
         return ops
 
+    def golden(self, key: str, tensor, device: int = 0) -> None:
+        """Embeds a golden tensor under `key` in the program's debug info, as the compiler's builders do
+        (include/ttmlir/Target/Common/debug_info.fbs:5-31): "input_<i>" / "output_<i>" for program
+        arguments and results, an op's location string for intermediates.  `tensor` is a torch tensor."""
+        import torch
+        names = {torch.float32: "Float32", torch.bfloat16: "BFloat16", torch.float16: "Float16", torch.int32: "Int32",
+                 torch.uint8: "UInt8", torch.int8: "Int8", torch.uint16: "UInt16", torch.uint32: "UInt32"}
+        t = tensor.contiguous()
+        entry = {"name": key, "shape": [int(d) for d in t.shape], "stride": [int(x) for x in t.stride()],
+                 "dtype": names[t.dtype], "data": bytes(t.view(torch.uint8).reshape(-1).numpy().tobytes())}
+        self.goldens.setdefault(key, []).append({"device": int(device), "value": entry})
+
     def table(self, auto_dealloc: bool = True) -> dict:
-        return {
+        t = {
             "name": self.name,
             "inputs": [v.ref for v in self.inputs],
             "outputs": [v.ref for v in self.outputs],
@@ -747,12 +760,18 @@ class ProgramBuilder:
             "private": self.private,
             "mesh_shape": self.mesh_shape,
         }
+        if self.goldens:
+            t["debug_info"] = {"golden_info": {"golden_map": [{"key": k, "value": v} for k, v in self.goldens.items()]}}
+        return t
 
 
 class BinaryBuilder:
-    def __init__(self, version=(0, 1, 0), git_hash: str = "b200-authored"):
+    def __init__(self, version=(0, 1, 0), git_hash: str = "b200-authored", system_desc: Optional[dict] = None):
         self.version = version
         self.git_hash = git_hash
+        # the system the binary is "compiled for" (what ttrt compares with the machine's own descriptor);
+        # None leaves the field out
+        self.system_desc = system_desc
         self._next = 0
         self.programs: List[ProgramBuilder] = []
         self.auto_dealloc = True
@@ -828,6 +847,7 @@ class BinaryBuilder:
             "version": self.version,
             "schema_hash": SCHEMA_HASH,
             "ttmlir_git_hash": self.git_hash,
+            "system_desc": self.system_desc,
             "mlir": {"name": "ttnn", "source": ""},
             "programs": [p.table(self.auto_dealloc) for p in self.programs],
         })

@@ -248,6 +248,56 @@ TTB_API int ttb_sdpa_decode(const void *q, const void *k, const void *v, const v
                             int mask_users, int mask_heads, float scale, int is_causal, void *workspace,
                             size_t workspace_bytes, void *stream);
 
+/* Paged KV cache (runtime/lib/ttnn/operations/kv_cache/paged_{update,fill}_cache.cpp, operations/transformer/
+ * paged_scaled_dot_product_attention_decode.cpp; goldens tools/golden/mapping.py:8745-8844, 8926-9007).  The
+ * cache is [blocks, heads, block_size, head_dim]; `page_table` [users, pages] gives the physical block of every
+ * logical block of a user (entries clamped into range, as the goldens clamp them).
+ *   ttb_paged_update_cache  input [users, seq, heads, head_dim]: token s of user b -> position update_index[b] + s
+ *                           (page_table may be null: logical = physical block)
+ *   ttb_paged_fill_cache    input [users, heads, seq, head_dim]: position s of user b, whose page-table row is
+ *                           batch_idx[b] (b when batch_idx is null) -> position s
+ *   ttb_sdpa_decode_paged   ttb_sdpa_decode with k / v read through the page table (Int32); the sequence length is
+ *                           pages_per_user * block_size; workspace as ttb_sdpa_decode_workspace_bytes for that length */
+TTB_API int ttb_paged_update_cache(void *cache, const void *input, const void *update_index, const void *page_table,
+                                   int dtype, int index_dtype, int table_dtype, size_t users, size_t seq, size_t heads,
+                                   size_t blocks, size_t block_size, size_t pages, size_t head_dim, void *stream);
+TTB_API int ttb_paged_fill_cache(void *cache, const void *input, const void *page_table, const void *batch_idx, int dtype,
+                                 int table_dtype, int batch_idx_dtype, size_t users, size_t heads, size_t seq,
+                                 size_t blocks, size_t block_size, size_t table_rows, size_t pages, size_t head_dim,
+                                 void *stream);
+TTB_API int ttb_sdpa_decode_paged(const void *q, const void *k, const void *v, const void *page_table, const void *cur_pos,
+                                  const void *mask, void *out, int dtype, int batch, int heads, int kv_heads, int blocks,
+                                  int block_size, int pages_per_user, int head_dim, int mask_users, int mask_heads,
+                                  float scale, int is_causal, void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---- indexing: ::ttnn::gather / scatter / sort / topk / sampling (runtime/lib/ttnn/operations/data_movement/
+ * {gather,scatter,sort}.cpp, operations/reduction/{topk,sampling}.cpp; goldens tools/golden/mapping.py:5384-5437,
+ * 5624-5640, 5927-5958, 5994-6019).
+ *   ttb_gather   out[i] = x[..., index[i], ...] along `dim`; out has the index tensor's shape (torch.gather)
+ *   ttb_scatter  out = x, then out[..., index[i], ...] (op)= src[i] along `dim`; reduce_type is the flatbuffer's
+ *                ScatterReduceType: 7 plain scatter, 0 sum, 2 max, 3 min, 6 prod (the input's own value takes part).
+ *                Duplicates are applied in increasing position along `dim`, the order of torch's CPU loop, so the
+ *                result is the same on every run.
+ *   An index outside its dimension is skipped (gather: reads as 0) and reported by ttb_index_status (cleared on read).
+ *   ttb_sort     every row of [rows, n] sorted (stable; NaN last ascending / first descending, as torch.sort);
+ *                the first `take` values and / or positions of each row are written (take = n: a full sort;
+ *                take = k with `descending` = largest: top-k).  Workspace: ttb_sort_workspace_bytes(rows, n).
+ *   ttb_sampling one draw per row among `candidates` pre-selected logits: softmax(values / temp), the k most probable
+ *                kept (k = 0 or >= candidates: all), of those the shortest prefix whose mass reaches p (p outside (0, 1):
+ *                all), then inverse-CDF sampling with a counter-based generator of (seed, row); the result is the chosen
+ *                candidate's entry of `indices`.  values / p / temp share `dtype`; k is UInt32.  At most 4096 candidates. */
+TTB_API int ttb_gather(const void *x, const void *index, void *out, int dtype, int index_dtype, int rank,
+                       const int64_t *x_shape, const int64_t *index_shape, int dim, void *stream);
+TTB_API int ttb_scatter(const void *x, const void *index, const void *src, void *out, int dtype, int index_dtype, int rank,
+                        const int64_t *x_shape, const int64_t *index_shape, const int64_t *src_shape, int dim,
+                        int reduce_type, void *stream);
+TTB_API int ttb_index_status(int *bad_index_seen);
+TTB_API size_t ttb_sort_workspace_bytes(size_t rows, size_t n);
+TTB_API int ttb_sort(const void *x, void *values, void *indices, int dtype, int index_dtype, size_t rows, size_t n,
+                     size_t take, int descending, void *workspace, size_t workspace_bytes, void *stream);
+TTB_API int ttb_sampling(const void *values, const void *indices, const void *k, const void *p, const void *temp, void *out,
+                         int dtype, int index_dtype, int out_dtype, int rows, int candidates, uint64_t seed, void *stream);
+
 /* ---- data movement: ::ttnn::permute / slice / concat / repeat / transpose
  * (runtime/lib/ttnn/operations/data_movement/). One gather kernel covers them: out is dense
  * row-major of `out_shape`; element (i0..ik) is read from in + in_offset + sum(i_d * in_strides[d]). */

@@ -209,6 +209,53 @@ class OracleBuilder:
             return ops.sdpa_decode(qq, kk, vv, cp, mk, is_causal, scale)
         return _map(fn, *vals)
 
+    def paged_update_cache(self, cache, x, update_index, page_table=None, share_cache=False, loc=None):
+        if page_table is None:
+            return _map(lambda c, t, i: ops.paged_update_cache(c, t, i, None), cache, x, update_index)
+        return _map(lambda c, t, i, pt: ops.paged_update_cache(c, t, i, pt), cache, x, update_index, page_table)
+
+    def paged_fill_cache(self, cache, x, page_table, batch_idx=None, loc=None):
+        if batch_idx is None:
+            return _map(lambda c, t, pt: ops.paged_fill_cache(c, t, pt, None), cache, x, page_table)
+        return _map(lambda c, t, pt, bi: ops.paged_fill_cache(c, t, pt, bi), cache, x, page_table, batch_idx)
+
+    def paged_scaled_dot_product_attention_decode(self, q, k, v, page_table, cur_pos=None, mask=None, is_causal=True, scale=None,
+                                                  loc=None):
+        vals = [x for x in (q, k, v, page_table, cur_pos, mask) if x is not None]
+
+        def fn(*ts):
+            it = iter(ts)
+            qq, kk, vv, pt = next(it), next(it), next(it), next(it)
+            cp = next(it) if cur_pos is not None else None
+            mk = next(it) if mask is not None else None
+            return ops.paged_sdpa_decode(qq, kk, vv, pt, cp, is_causal, scale, mk)
+        return _map(fn, *vals)
+
+    def gather(self, x, index, dim, loc=None): return _map(lambda t, i: ops.gather(t, i, dim), x, index)
+
+    def scatter(self, x, index, src, dim, reduce_type=None, loc=None):
+        return _map(lambda t, i, u: ops.scatter(t, i, u, dim, reduce_type), x, index, src)
+
+    def sort(self, x, dim=-1, descending=False, stable=True, index_dtype="Int32", loc=None):
+        def fn(t):
+            v, i = ops.sort(t, dim, descending, stable)
+            return v, i.to(TORCH_DTYPE[index_dtype])
+        return _map(fn, x)
+
+    def topk(self, x, k, dim=-1, largest=True, index_dtype="Int32", loc=None):
+        def fn(t):
+            v, i = ops.topk(t.float(), k, dim, largest)
+            return v.to(t.dtype), i.to(TORCH_DTYPE[index_dtype])
+        return _map(fn, x)
+
+    def sampling(self, values, indices, k, p, temp, seed=None, loc=None):
+        """The reference's golden draws with torch.multinomial (tools/golden/mapping.py:6008-6018): a result that
+        no other generator can reproduce.  The oracle returns the most probable candidate, which equals the
+        device's answer only where the support is a single candidate; tests compare distributions otherwise."""
+        def fn(v, i):
+            return torch.gather(i, 1, v.float().argmax(dim=1, keepdim=True)).squeeze(1).to(torch.int32)
+        return _map(fn, values, indices)
+
     def reduce(self, kind, x, dims, keep_dim, loc=None): return _map(lambda t: ops.reduce(kind, t, dims, keep_dim), x)
 
     # ---- data movement

@@ -61,6 +61,62 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// Paged caches (mapping.py:8926-9007): the cache is [blocks, heads, block_size, D]; a page table
+// [users, pages] names the physical block of each logical block of a user.
+//  paged_update_cache  token s of user b (input [users, seq, heads, D]) goes to position update_index[b] + s
+//  paged_fill_cache    position s of input [users, heads, seq, D] of user b, whose page-table row is
+//                      batch_idx[b] (or b), goes to position s
+// Page-table entries and rows are clamped into range, as the goldens clamp them.
+template <typename U, typename I, typename P>
+__global__ void __launch_bounds__(256)
+    pagedUpdateCacheKernel(U *__restrict__ cache, const U *__restrict__ in, const I *__restrict__ index, const P *__restrict__ pageTable,
+                           size_t users, size_t seq, size_t heads, size_t blocks, size_t blockSize, size_t pages, size_t rowUnits) {
+  const size_t total = users * seq * heads * rowUnits;
+  const size_t step = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+    const size_t u = i % rowUnits;
+    size_t r = i / rowUnits;
+    const size_t h = r % heads;
+    r /= heads;
+    const size_t s = r % seq, b = r / seq; // input is [users, seq, heads, D]
+    const long long pos = static_cast<long long>(index[b]) + static_cast<long long>(s);
+    if (pos < 0) continue;
+    size_t blk = static_cast<size_t>(pos) / blockSize;
+    const size_t off = static_cast<size_t>(pos) % blockSize;
+    if (pageTable) {
+      const size_t col = blk < pages ? blk : pages - 1;
+      const long long phys = static_cast<long long>(pageTable[b * pages + col]);
+      blk = phys < 0 ? 0 : static_cast<size_t>(phys);
+    }
+    if (blk >= blocks) blk = blocks - 1;
+    cache[((blk * heads + h) * blockSize + off) * rowUnits + u] = in[i];
+  }
+}
+
+template <typename U, typename P, typename I>
+__global__ void __launch_bounds__(256)
+    pagedFillCacheKernel(U *__restrict__ cache, const U *__restrict__ in, const P *__restrict__ pageTable, const I *__restrict__ batchIdx,
+                         size_t users, size_t heads, size_t seq, size_t blocks, size_t blockSize, size_t tableRows, size_t pages,
+                         size_t rowUnits) {
+  const size_t total = users * heads * seq * rowUnits;
+  const size_t step = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+    const size_t u = i % rowUnits;
+    size_t r = i / rowUnits;
+    const size_t s = r % seq;
+    r /= seq;
+    const size_t h = r % heads, b = r / heads; // input is [users, heads, seq, D]
+    long long row = batchIdx ? static_cast<long long>(batchIdx[b]) : static_cast<long long>(b);
+    row = row < 0 ? 0 : (row >= static_cast<long long>(tableRows) ? static_cast<long long>(tableRows) - 1 : row);
+    size_t col = s / blockSize;
+    if (col >= pages) col = pages - 1;
+    long long phys = static_cast<long long>(pageTable[static_cast<size_t>(row) * pages + col]);
+    size_t blk = phys < 0 ? 0 : static_cast<size_t>(phys);
+    if (blk >= blocks) blk = blocks - 1;
+    cache[((blk * heads + h) * blockSize + s % blockSize) * rowUnits + u] = in[i];
+  }
+}
+
 __device__ int g_cacheBadIndex; // an update index outside the cache was seen (nothing was written); cleared when read
 
 // ---- decode attention ------------------------------------------------------------------------
@@ -100,6 +156,10 @@ constexpr int DEC_CHUNK = 512; // keys per CTA
 
 struct DecodeParams {
   int B, H, Hkv, S, chunks;
+  // Paged cache: k / v are [blocks, Hkv, blockSize, D] and pageTable [B, pages] (Int32) names the block of
+  // each run of blockSize positions; S = pages * blockSize.  pageTable null: k / v are [B, Hkv, S, D].
+  const int32_t *pageTable;
+  int blockSize, pages, blocks;
   int maskB, maskH; // extents of the mask's user and head dimensions (1 = broadcast), 0 = no mask
   float scale;
   int causal;
@@ -135,8 +195,13 @@ __global__ void __launch_bounds__(DEC_THREADS, D <= 128 ? 4 : 2)
     }
     return;
   }
-  const T *kb = k + (static_cast<size_t>(b) * p.Hkv + kvh) * p.S * D;
-  const T *vb = v + (static_cast<size_t>(b) * p.Hkv + kvh) * p.S * D;
+  // Row (in units of D elements) of position j of this user's kv head.
+  auto rowOf = [&](int j) -> size_t {
+    if (!p.pageTable) return (static_cast<size_t>(b) * p.Hkv + kvh) * p.S + j;
+    int blk = p.pageTable[static_cast<size_t>(b) * p.pages + j / p.blockSize];
+    blk = blk < 0 ? 0 : (blk >= p.blocks ? p.blocks - 1 : blk);
+    return (static_cast<size_t>(blk) * p.Hkv + kvh) * p.blockSize + j % p.blockSize;
+  };
 
   // Scores on the tensor pipe: S[16 x 8] = Q[16 x D] K^T for 8 keys per mma tile, the G query heads
   // being rows 0..G-1 of the 16-row operand (the other rows are zero).  A dot product does not care
@@ -165,7 +230,7 @@ __global__ void __launch_bounds__(DEC_THREADS, D <= 128 ? 4 : 2)
         const int j = j0 + u * DEC_WARPS * 8 + quad;
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
-          raw[u][nb] = j < k1 ? __ldcs(reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(j) * D + nb * 32 + 8 * t))
+          raw[u][nb] = j < k1 ? __ldcs(reinterpret_cast<const uint4 *>(k + rowOf(j) * D + nb * 32 + 8 * t))
                               : make_uint4(0, 0, 0, 0);
         }
       }
@@ -246,7 +311,7 @@ __global__ void __launch_bounds__(DEC_THREADS, D <= 128 ? 4 : 2)
         const int j = j0 + 8 * h + quad;
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
-          raw[h][nb] = j < k1 ? __ldcs(reinterpret_cast<const uint4 *>(vb + static_cast<size_t>(j) * D + nb * 32 + 8 * t))
+          raw[h][nb] = j < k1 ? __ldcs(reinterpret_cast<const uint4 *>(v + rowOf(j) * D + nb * 32 + 8 * t))
                               : make_uint4(0, 0, 0, 0);
         }
       }
@@ -361,6 +426,10 @@ static int dispatchDecodeG(int g, const void *q, const void *k, const void *v, c
 
 using namespace ttb;
 
+// Set by ttb_sdpa_decode_paged around its call of ttb_sdpa_decode (same thread).
+static thread_local const void *g_pagedTable = nullptr;
+static thread_local int g_pagedBlockSize = 0, g_pagedPages = 0, g_pagedBlocks = 0;
+
 extern "C" {
 
 int ttb_fill_cache(void *cache, const void *input, int dtype, size_t users, size_t heads, size_t seq, size_t max_seq,
@@ -460,6 +529,8 @@ int ttb_sdpa_decode(const void *q, const void *k, const void *v, const void *cur
   }
   DecodeParams p;
   p.B = batch; p.H = heads; p.Hkv = kv_heads; p.S = seq;
+  p.pageTable = static_cast<const int32_t *>(g_pagedTable);
+  p.blockSize = g_pagedBlockSize; p.pages = g_pagedPages; p.blocks = g_pagedBlocks;
   p.chunks = (seq + DEC_CHUNK - 1) / DEC_CHUNK;
   p.maskB = mask ? mask_users : 0;
   p.maskH = mask ? mask_heads : 0;
@@ -484,6 +555,73 @@ int ttb_sdpa_decode(const void *q, const void *k, const void *v, const void *cur
   if (dtype == kBF16) { TTB_DEC(__nv_bfloat16) }
   TTB_DEC(__half)
 #undef TTB_DEC
+}
+
+int ttb_sdpa_decode_paged(const void *q, const void *k, const void *v, const void *page_table, const void *cur_pos,
+                          const void *mask, void *out, int dtype, int batch, int heads, int kv_heads, int blocks, int block_size,
+                          int pages_per_user, int head_dim, int mask_users, int mask_heads, float scale, int is_causal,
+                          void *workspace, size_t workspace_bytes, void *stream) {
+  TTB_CHECK(page_table != nullptr, "null page table");
+  TTB_CHECK(blocks > 0 && block_size > 0 && pages_per_user > 0, "empty paged cache");
+  g_pagedTable = page_table;
+  g_pagedBlockSize = block_size;
+  g_pagedPages = pages_per_user;
+  g_pagedBlocks = blocks;
+  const int rc = ttb_sdpa_decode(q, k, v, cur_pos, mask, out, dtype, batch, heads, kv_heads, pages_per_user * block_size, head_dim,
+                                 mask_users, mask_heads, scale, is_causal, workspace, workspace_bytes, stream);
+  g_pagedTable = nullptr;
+  g_pagedBlockSize = g_pagedPages = g_pagedBlocks = 0;
+  return rc;
+}
+
+int ttb_paged_update_cache(void *cache, const void *input, const void *update_index, const void *page_table, int dtype,
+                           int index_dtype, int table_dtype, size_t users, size_t seq, size_t heads, size_t blocks,
+                           size_t block_size, size_t pages, size_t head_dim, void *stream) {
+  TTB_CHECK(cache && input && update_index, "null tensor");
+  TTB_CHECK(index_dtype == kI32 || index_dtype == kU32, "update index must be Int32 or UInt32");
+  TTB_CHECK(!page_table || table_dtype == kI32 || table_dtype == kU32, "page table must be Int32 or UInt32");
+  TTB_CHECK(blocks > 0 && block_size > 0 && (!page_table || pages > 0), "empty paged cache");
+  const size_t es = dtypeSize(dtype);
+  TTB_CHECK(es == 2 || es == 4, "unsupported element size");
+  if (users * seq * heads * head_dim == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("paged_update_cache", 0, double(users) * seq * heads * head_dim * es * 2, st);
+  const int grid = gridFor(users * seq * heads * head_dim, 256);
+#define TTB_PU(U, I, P)                                                                                                        pagedUpdateCacheKernel<U, I, P><<<grid, 256, 0, st>>>(static_cast<U *>(cache), static_cast<const U *>(input),                                                                      static_cast<const I *>(update_index), static_cast<const P *>(page_table),                                                         users, seq, heads, blocks, block_size, pages, head_dim)
+#define TTB_PU_P(U, I)                                                                     if (table_dtype == kU32) TTB_PU(U, I, uint32_t);                                         else TTB_PU(U, I, int32_t);
+#define TTB_PU_I(U)                                                                        if (index_dtype == kU32) { TTB_PU_P(U, uint32_t) } else { TTB_PU_P(U, int32_t) }
+  if (es == 2) { TTB_PU_I(uint16_t) } else { TTB_PU_I(uint32_t) }
+#undef TTB_PU_I
+#undef TTB_PU_P
+#undef TTB_PU
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_paged_fill_cache(void *cache, const void *input, const void *page_table, const void *batch_idx, int dtype,
+                         int table_dtype, int batch_idx_dtype, size_t users, size_t heads, size_t seq, size_t blocks,
+                         size_t block_size, size_t table_rows, size_t pages, size_t head_dim, void *stream) {
+  TTB_CHECK(cache && input && page_table, "null tensor");
+  TTB_CHECK(table_dtype == kI32 || table_dtype == kU32, "page table must be Int32 or UInt32");
+  TTB_CHECK(!batch_idx || batch_idx_dtype == kI32 || batch_idx_dtype == kU32, "batch index must be Int32 or UInt32");
+  TTB_CHECK(blocks > 0 && block_size > 0 && table_rows > 0 && pages > 0, "empty paged cache");
+  const size_t es = dtypeSize(dtype);
+  TTB_CHECK(es == 2 || es == 4, "unsupported element size");
+  if (users * heads * seq * head_dim == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("paged_fill_cache", 0, double(users) * heads * seq * head_dim * es * 2, st);
+  const int grid = gridFor(users * heads * seq * head_dim, 256);
+#define TTB_PF(U, P, I)                                                                                                        pagedFillCacheKernel<U, P, I><<<grid, 256, 0, st>>>(static_cast<U *>(cache), static_cast<const U *>(input),                                                                      static_cast<const P *>(page_table), static_cast<const I *>(batch_idx), users,                                                       heads, seq, blocks, block_size, table_rows, pages, head_dim)
+#define TTB_PF_I(U, P)                                                                     if (batch_idx_dtype == kU32) TTB_PF(U, P, uint32_t);                                     else TTB_PF(U, P, int32_t);
+#define TTB_PF_P(U)                                                                        if (table_dtype == kU32) { TTB_PF_I(U, uint32_t) } else { TTB_PF_I(U, int32_t) }
+  if (es == 2) { TTB_PF_P(uint16_t) } else { TTB_PF_P(uint32_t) }
+#undef TTB_PF_P
+#undef TTB_PF_I
+#undef TTB_PF
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
 }
 
 } // extern "C"

@@ -15,6 +15,7 @@
 //   * tilize / untilize and memory-config changes are metadata only.
 #include <cstdlib>
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstring>
 #include <map>
@@ -139,6 +140,75 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     const auto *o = op->type_as_EmbeddingOp();
     pushRef(ins, o->input());
     pushRef(ins, o->weight());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::GatherOp: {
+    const auto *o = op->type_as_GatherOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->index());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::ScatterOp: {
+    const auto *o = op->type_as_ScatterOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->index());
+    pushRef(ins, o->source());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::SortOp: {
+    const auto *o = op->type_as_SortOp();
+    pushRef(ins, o->in());
+    if (o->outputs()) {
+      for (const auto *r : *o->outputs()) pushRef(outs, r);
+    }
+    break;
+  }
+  case OpType::TopKOp: {
+    const auto *o = op->type_as_TopKOp();
+    pushRef(ins, o->input_tensor());
+    if (o->outputs()) {
+      for (const auto *r : *o->outputs()) pushRef(outs, r);
+    }
+    break;
+  }
+  case OpType::SamplingOp: {
+    const auto *o = op->type_as_SamplingOp();
+    pushRef(ins, o->input_values());
+    pushRef(ins, o->input_indices());
+    pushRef(ins, o->k());
+    pushRef(ins, o->p());
+    pushRef(ins, o->temp());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::PagedUpdateCacheOp: {
+    const auto *o = op->type_as_PagedUpdateCacheOp();
+    pushRef(ins, o->cache());
+    pushRef(ins, o->input());
+    pushRef(ins, o->update_index());
+    pushRef(ins, o->page_table());
+    break;
+  }
+  case OpType::PagedFillCacheOp: {
+    const auto *o = op->type_as_PagedFillCacheOp();
+    pushRef(ins, o->cache());
+    pushRef(ins, o->input());
+    pushRef(ins, o->page_table());
+    pushRef(ins, o->batch_idx_tensor());
+    break;
+  }
+  case OpType::PagedScaledDotProductAttentionDecodeOp: {
+    const auto *o = op->type_as_PagedScaledDotProductAttentionDecodeOp();
+    pushRef(ins, o->query());
+    pushRef(ins, o->key());
+    pushRef(ins, o->value());
+    pushRef(ins, o->page_table());
+    pushRef(ins, o->attention_mask());
+    pushRef(ins, o->cur_pos_tensor());
+    pushRef(ins, o->attention_sink());
     pushRef(outs, o->out());
     break;
   }
@@ -485,6 +555,17 @@ private:
   void runArgMax(const fbt::ReductionArgMaxOp *op);
   void runCumSum(const fbt::CumSumOp *op);
   void runEmbedding(const fbt::EmbeddingOp *op);
+  void runGather(const fbt::GatherOp *op);
+  void runScatter(const fbt::ScatterOp *op);
+  void runSort(const fbt::SortOp *op);
+  void runTopK(const fbt::TopKOp *op);
+  // values / indices of the first `take` entries of x sorted along `dim` (shared by sort and top-k)
+  void sortAlong(const TensorPtr &x, int dim, bool descending, size_t take, const fbt::TensorRef *valuesRef,
+                 const fbt::TensorRef *indicesRef);
+  void runSampling(const fbt::SamplingOp *op);
+  void runPagedUpdateCache(const fbt::PagedUpdateCacheOp *op);
+  void runPagedFillCache(const fbt::PagedFillCacheOp *op);
+  void runPagedSdpaDecode(const fbt::PagedScaledDotProductAttentionDecodeOp *op);
   void runPool2d(const fbt::Pool2dOp *op);
   void runGlobalAvgPool2d(const fbt::GlobalAvgPool2dOp *op);
   void runPad(const fbt::PadOp *op);
@@ -816,6 +897,16 @@ size_t Executor::runOp(size_t i) {
   case OpType::ReductionArgMaxOp: runArgMax(op->type_as_ReductionArgMaxOp()); break;
   case OpType::CumSumOp: runCumSum(op->type_as_CumSumOp()); break;
   case OpType::EmbeddingOp: runEmbedding(op->type_as_EmbeddingOp()); break;
+  case OpType::GatherOp: runGather(op->type_as_GatherOp()); break;
+  case OpType::ScatterOp: runScatter(op->type_as_ScatterOp()); break;
+  case OpType::SortOp: runSort(op->type_as_SortOp()); break;
+  case OpType::TopKOp: runTopK(op->type_as_TopKOp()); break;
+  case OpType::SamplingOp: runSampling(op->type_as_SamplingOp()); break;
+  case OpType::PagedUpdateCacheOp: runPagedUpdateCache(op->type_as_PagedUpdateCacheOp()); break;
+  case OpType::PagedFillCacheOp: runPagedFillCache(op->type_as_PagedFillCacheOp()); break;
+  case OpType::PagedScaledDotProductAttentionDecodeOp:
+    runPagedSdpaDecode(op->type_as_PagedScaledDotProductAttentionDecodeOp());
+    break;
   case OpType::Pool2dOp: runPool2d(op->type_as_Pool2dOp()); break;
   case OpType::GlobalAvgPool2dOp: runGlobalAvgPool2d(op->type_as_GlobalAvgPool2dOp()); break;
   case OpType::PadOp: runPad(op->type_as_PadOp()); break;
@@ -2300,6 +2391,220 @@ void Executor::runSdpaDecode(const fbt::ScaledDotProductAttentionDecodeOp *op) {
     TTB_CALL(ttb_sdpa_decode(q->shards[i]->ptr, k->shards[i]->ptr, v->shards[i]->ptr, pos ? pos->shards[i]->ptr : nullptr,
                              mask ? mask->shards[i]->ptr : nullptr, out->shards[i]->ptr, ttbDtype(q->dtype), B, H, Hkv, S, D, maskB,
                              maskH, scale, op->is_causal() ? 1 : 0, ws->shards[i]->ptr, wsBytes, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// Paged caches: cache [blocks, heads, block_size, D]; the page table is read on the device.
+void Executor::runPagedUpdateCache(const fbt::PagedUpdateCacheOp *op) {
+  TensorPtr cache = getDevice(op->cache()), in = getDevice(op->input()), idx = getDevice(op->update_index());
+  TensorPtr table = op->page_table() ? getDevice(op->page_table()) : nullptr;
+  TTRT_ASSERT(cache->shape.size() == 4 && in->shape.size() == 4 && cache->dtype == in->dtype, "paged_update_cache expects 4-D tensors of one type");
+  TTRT_ASSERT(in->shape[2] == cache->shape[1] && in->shape[3] == cache->shape[3], "paged_update_cache input must be [users, seq, heads, head_dim]");
+  const size_t users = in->shape[0];
+  TTRT_ASSERT(idx->volume() >= users && (idx->dtype == DataType::Int32 || idx->dtype == DataType::UInt32),
+              "paged_update_cache needs one Int32 / UInt32 position per user");
+  size_t pages = 0;
+  if (table) {
+    TTRT_ASSERT(table->shape.size() == 2 && table->shape[0] >= users && (table->dtype == DataType::Int32 || table->dtype == DataType::UInt32),
+                "page table must be [users, pages] of Int32 / UInt32");
+    pages = table->shape[1];
+  }
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_paged_update_cache(cache->shards[i]->ptr, in->shards[i]->ptr, idx->shards[i]->ptr, table ? table->shards[i]->ptr : nullptr,
+                                    ttbDtype(cache->dtype), ttbDtype(idx->dtype), table ? ttbDtype(table->dtype) : 0, users, in->shape[1],
+                                    in->shape[2], cache->shape[0], cache->shape[2], pages, cache->shape[3], r.stream));
+  });
+  TensorPtr root = cache->base ? cache->base : cache;
+  root->version.store(TensorImpl::nextTensorVersion());
+}
+
+void Executor::runPagedFillCache(const fbt::PagedFillCacheOp *op) {
+  TensorPtr cache = getDevice(op->cache()), in = getDevice(op->input()), table = getDevice(op->page_table());
+  TensorPtr bidx = op->batch_idx_tensor() ? getDevice(op->batch_idx_tensor()) : nullptr;
+  TTRT_ASSERT(cache->shape.size() == 4 && in->shape.size() == 4 && cache->dtype == in->dtype, "paged_fill_cache expects 4-D tensors of one type");
+  TTRT_ASSERT(in->shape[1] == cache->shape[1] && in->shape[3] == cache->shape[3], "paged_fill_cache input must be [users, heads, seq, head_dim]");
+  TTRT_ASSERT(table->shape.size() == 2 && (table->dtype == DataType::Int32 || table->dtype == DataType::UInt32),
+              "page table must be [rows, pages] of Int32 / UInt32");
+  if (bidx) {
+    TTRT_ASSERT(bidx->volume() >= in->shape[0] && (bidx->dtype == DataType::Int32 || bidx->dtype == DataType::UInt32),
+                "batch index must hold one Int32 / UInt32 per user");
+  }
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_paged_fill_cache(cache->shards[i]->ptr, in->shards[i]->ptr, table->shards[i]->ptr, bidx ? bidx->shards[i]->ptr : nullptr,
+                                  ttbDtype(cache->dtype), ttbDtype(table->dtype), bidx ? ttbDtype(bidx->dtype) : 0, in->shape[0],
+                                  in->shape[1], in->shape[2], cache->shape[0], cache->shape[2], table->shape[0], table->shape[1],
+                                  cache->shape[3], r.stream));
+  });
+  TensorPtr root = cache->base ? cache->base : cache;
+  root->version.store(TensorImpl::nextTensorVersion());
+}
+
+// q [B, 1, H, D] against paged k, v [blocks, Hkv, block_size, D] (tools/golden/mapping.py:8745-8844).
+void Executor::runPagedSdpaDecode(const fbt::PagedScaledDotProductAttentionDecodeOp *op) {
+  TTRT_ASSERT(!op->attention_sink(), "attention sinks are not supported");
+  TTRT_ASSERT(!op->sliding_window_size().has_value(), "sliding-window decode attention is not supported");
+  TensorPtr q = getDevice(op->query()), k = getDevice(op->key()), v = getDevice(op->value());
+  TensorPtr table = castOnDevice(getDevice(op->page_table()), DataType::Int32);
+  TensorPtr mask = op->attention_mask() ? getDevice(op->attention_mask()) : nullptr;
+  TensorPtr pos = op->cur_pos_tensor() ? getDevice(op->cur_pos_tensor()) : nullptr;
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(q->shape.size() == 4 && k->shape.size() == 4 && v->shape == k->shape && q->shape[1] == 1,
+              "paged sdpa_decode expects q [B, 1, H, D], k / v [blocks, Hkv, block_size, D]");
+  TTRT_ASSERT(q->dtype == k->dtype && q->dtype == v->dtype && out->dtype == q->dtype && out->volume() == q->volume(),
+              "paged sdpa_decode operands must share one data type");
+  const int B = static_cast<int>(q->shape[0]), H = static_cast<int>(q->shape[2]), D = static_cast<int>(q->shape[3]);
+  const int blocks = static_cast<int>(k->shape[0]), Hkv = static_cast<int>(k->shape[1]), blockSize = static_cast<int>(k->shape[2]);
+  TTRT_ASSERT(static_cast<int>(k->shape[3]) == D, "paged sdpa_decode operands disagree on head_dim");
+  TTRT_ASSERT(table->shape.size() == 2 && static_cast<int>(table->shape[0]) >= B, "page table must be [B, pages]");
+  const int pages = static_cast<int>(table->shape[1]), S = pages * blockSize;
+  int maskB = 0, maskH = 0;
+  if (mask) {
+    TTRT_ASSERT(mask->shape.size() == 4 && mask->shape[1] == 1 && static_cast<int>(mask->shape[3]) == S && mask->dtype == q->dtype,
+                "paged sdpa_decode mask must be [B or 1, 1, H or 1, pages * block_size] in the operands' data type");
+    maskB = static_cast<int>(mask->shape[0]);
+    maskH = static_cast<int>(mask->shape[2]);
+  }
+  if (pos) {
+    TTRT_ASSERT(static_cast<int>(pos->volume()) == B && (pos->dtype == DataType::Int32 || pos->dtype == DataType::UInt32),
+                "cur_pos must hold one 32-bit integer per user");
+  }
+  // torch's scaled_dot_product_attention, which the golden calls, scales by 1 / sqrt(D) when no scale is given
+  const float scale = op->scale().has_value() ? *op->scale() : 1.0f / std::sqrt(static_cast<float>(D));
+  const size_t wsBytes = ttb_sdpa_decode_workspace_bytes(B, H, S, D);
+  TensorPtr ws = makeDeviceTensor(dev, {static_cast<uint32_t>((wsBytes + 3) / 4)}, DataType::Float32);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_sdpa_decode_paged(q->shards[i]->ptr, k->shards[i]->ptr, v->shards[i]->ptr, table->shards[i]->ptr,
+                                   pos ? pos->shards[i]->ptr : nullptr, mask ? mask->shards[i]->ptr : nullptr, out->shards[i]->ptr,
+                                   ttbDtype(q->dtype), B, H, Hkv, blocks, blockSize, pages, D, maskB, maskH, scale,
+                                   op->is_causal() ? 1 : 0, ws->shards[i]->ptr, wsBytes, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// ---- indexing ---------------------------------------------------------------------------------------------------
+static std::vector<int64_t> shape64(const std::vector<uint32_t> &s) { return std::vector<int64_t>(s.begin(), s.end()); }
+
+void Executor::runGather(const fbt::GatherOp *op) {
+  TensorPtr x = getDevice(op->input()), index = getDevice(op->index());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(x->shape.size() == index->shape.size() && !x->shape.empty() && out->shape == index->shape && out->dtype == x->dtype,
+              "gather: input and index must have one rank, the result the index's shape");
+  const int dim = normDim(op->dim(), x->shape.size());
+  std::vector<int64_t> xs = shape64(x->shape), is = shape64(index->shape);
+  dev->ranIndexOp = true;
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_gather(x->shards[i]->ptr, index->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(x->dtype), ttbDtype(index->dtype),
+                        static_cast<int>(xs.size()), xs.data(), is.data(), dim, r.stream));
+  });
+  put(op->out(), out);
+}
+
+void Executor::runScatter(const fbt::ScatterOp *op) {
+  TensorPtr x = getDevice(op->input()), index = getDevice(op->index()), src = getDevice(op->source());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(x->shape.size() == index->shape.size() && x->shape.size() == src->shape.size() && !x->shape.empty() &&
+                  out->shape == x->shape && out->dtype == x->dtype && src->dtype == x->dtype,
+              "scatter: input, index and source must have one rank; result and source the input's type");
+  const int dim = normDim(op->dim(), x->shape.size());
+  std::vector<int64_t> xs = shape64(x->shape), is = shape64(index->shape), ss = shape64(src->shape);
+  dev->ranIndexOp = true;
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_scatter(x->shards[i]->ptr, index->shards[i]->ptr, src->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(x->dtype),
+                         ttbDtype(index->dtype), static_cast<int>(xs.size()), xs.data(), is.data(), ss.data(), dim,
+                         static_cast<int>(op->scatter_reduce_type()), r.stream));
+  });
+  put(op->out(), out);
+}
+
+// The kernel sorts rows; any other dimension is brought to the back with a strided copy first and the
+// results are copied back into place.
+void Executor::sortAlong(const TensorPtr &x, int dim, bool descending, size_t take, const fbt::TensorRef *valuesRef,
+                         const fbt::TensorRef *indicesRef) {
+  const size_t rank = x->shape.size();
+  TTRT_ASSERT(rank >= 1, "sort of a scalar");
+  const size_t n = x->shape[dim];
+  TTRT_ASSERT(take <= n, "top-k asks for more entries than the dimension has");
+  const bool last = static_cast<size_t>(dim) + 1 == rank;
+  // x with `dim` moved to the back (dense)
+  TensorPtr rows = x;
+  std::vector<uint32_t> movedShape = x->shape;
+  std::vector<int64_t> dense = denseStrides(x->shape);
+  if (!last) {
+    std::vector<int64_t> strides = dense;
+    movedShape.erase(movedShape.begin() + dim);
+    movedShape.push_back(static_cast<uint32_t>(n));
+    strides.erase(strides.begin() + dim);
+    strides.push_back(dense[dim]);
+    rows = stridedView(x, movedShape, strides, 0, x->dtype);
+  }
+  const size_t nRows = n ? x->volume() / n : 0;
+  TensorPtr values = valuesRef ? allocOut(valuesRef) : nullptr;
+  TensorPtr indices = indicesRef ? allocOut(indicesRef) : nullptr;
+  std::vector<uint32_t> resShape = movedShape;
+  resShape.back() = static_cast<uint32_t>(take);
+  TensorPtr v2 = values, i2 = indices;
+  if (!last) {
+    if (values) v2 = makeDeviceTensor(dev, resShape, values->dtype);
+    if (indices) i2 = makeDeviceTensor(dev, resShape, indices->dtype);
+  }
+  const size_t wsBytes = ttb_sort_workspace_bytes(nRows, n);
+  TensorPtr ws = makeDeviceTensor(dev, {static_cast<uint32_t>((wsBytes + 3) / 4)}, DataType::UInt32);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_sort(rows->shards[i]->ptr, v2 ? v2->shards[i]->ptr : nullptr, i2 ? i2->shards[i]->ptr : nullptr, ttbDtype(x->dtype),
+                      i2 ? ttbDtype(i2->dtype) : 0, nRows, n, take, descending ? 1 : 0, ws->shards[i]->ptr, wsBytes, r.stream));
+  });
+  if (!last) {
+    // back: result[..., j at `dim`, ...] = moved[..., j]
+    std::vector<uint32_t> outShape = x->shape;
+    outShape[dim] = static_cast<uint32_t>(take);
+    std::vector<int64_t> movedDense = denseStrides(resShape), strides(rank);
+    for (size_t d = 0, m = 0; d < rank; ++d) strides[d] = static_cast<int>(d) == dim ? movedDense[rank - 1] : movedDense[m++];
+    auto copyBack = [&](const TensorPtr &from, const TensorPtr &to) {
+      std::vector<int64_t> shape(outShape.begin(), outShape.end());
+      eachRank([&](size_t i, const RankCtx &r) {
+        TTB_CALL(ttb_strided_copy(from->shards[i]->ptr, to->shards[i]->ptr, static_cast<int>(dataTypeSize(to->dtype)), static_cast<int>(rank),
+                                  shape.data(), strides.data(), 0, r.stream));
+      });
+    };
+    if (values) copyBack(v2, values);
+    if (indices) copyBack(i2, indices);
+  }
+  if (values) put(valuesRef, values);
+  if (indices) put(indicesRef, indices);
+}
+
+void Executor::runSort(const fbt::SortOp *op) {
+  TensorPtr x = getDevice(op->in());
+  TTRT_ASSERT(op->outputs() && op->outputs()->size() == 2, "sort produces values and indices");
+  const int dim = normDim(op->dim(), x->shape.size());
+  sortAlong(x, dim, op->descending(), x->shape[dim], op->outputs()->Get(0), op->outputs()->Get(1)); // always stable
+}
+
+void Executor::runTopK(const fbt::TopKOp *op) {
+  TensorPtr x = getDevice(op->input_tensor());
+  TTRT_ASSERT(op->outputs() && op->outputs()->size() == 2, "top-k produces values and indices");
+  TTRT_ASSERT(op->k() >= 0, "negative k");
+  const int dim = normDim(op->dim(), x->shape.size());
+  sortAlong(x, dim, op->largest(), static_cast<size_t>(op->k()), op->outputs()->Get(0), op->outputs()->Get(1)); // always sorted
+}
+
+void Executor::runSampling(const fbt::SamplingOp *op) {
+  TensorPtr values = getDevice(op->input_values()), indices = getDevice(op->input_indices());
+  TensorPtr k = castOnDevice(getDevice(op->k()), DataType::UInt32);
+  TensorPtr p = castOnDevice(getDevice(op->p()), values->dtype), temp = castOnDevice(getDevice(op->temp()), values->dtype);
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(values->shape.size() >= 2 && values->shape == indices->shape, "sampling: values and indices must be [.., batch, candidates]");
+  const size_t candidates = values->shape.back(), rows = values->volume() / std::max<size_t>(candidates, 1);
+  TTRT_ASSERT(out->volume() == rows && k->volume() == rows && p->volume() == rows && temp->volume() == rows,
+              "sampling: k, p, temp and the result hold one entry per row");
+  // Without a seed every call draws differently: a process-wide counter stands in for the device RNG state.
+  static std::atomic<uint64_t> unseeded{0x5eed};
+  const uint64_t seed = op->seed().has_value() ? *op->seed() : unseeded.fetch_add(0x9E3779B97F4A7C15ull);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_sampling(values->shards[i]->ptr, indices->shards[i]->ptr, k->shards[i]->ptr, p->shards[i]->ptr, temp->shards[i]->ptr,
+                          out->shards[i]->ptr, ttbDtype(values->dtype), ttbDtype(indices->dtype), ttbDtype(out->dtype),
+                          static_cast<int>(rows), static_cast<int>(candidates), seed, r.stream));
   });
   put(op->out(), out);
 }

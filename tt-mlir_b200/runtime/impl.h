@@ -119,6 +119,7 @@ struct DeviceImpl {
   std::vector<RankCtx> locals;     // coordinates this process owns
   bool multiProcess = false;
   bool open = false;
+  bool ranIndexOp = false; // a gather / scatter ran: ask the kernel library for bad indices at the next wait
   bool ranEmbedding = false, ranUpdateCache = false; // their kernels flag indices outside the table / cache; wait() reports it
   bool symmTried = false;          // the peer workspaces are set up (or found unavailable) once
   std::mutex submitMutex;          // submit is serialised per device

@@ -994,6 +994,11 @@ static void syncDevice(const std::shared_ptr<DeviceImpl> &d) {
       TTB_CALL(ttb_embedding_status(&bad));
       TTRT_ASSERT(bad == 0, "an embedding lookup saw an index outside its table (row 0 was used instead)");
     }
+    if (d->ranIndexOp) {
+      int bad = 0;
+      TTB_CALL(ttb_index_status(&bad));
+      TTRT_ASSERT(bad == 0, "a gather / scatter saw an index outside its dimension (the element was skipped)");
+    }
     if (d->ranUpdateCache) {
       int bad = 0;
       TTB_CALL(ttb_update_cache_status(&bad));

@@ -244,6 +244,22 @@ S.table("ReductionArgMaxOp", [
 S.table("CumSumOp", [
     ("in", "TensorRef"), ("out", "TensorRef"), ("dim", "i32"), ("dtype", "DataType", OPT),
     ("memcfg", "MemoryConfig")])
+# operations/data_movement.fbs: gather / scatter / sort; operations/reduction.fbs: top-k / sampling
+S.enum("ScatterReduceType", "u8", {"Sum": 0, "Max": 2, "Min": 3, "Prod": 6, "Invalid": 7})
+S.table("ScatterOp", [
+    ("input", "TensorRef"), ("out", "TensorRef"), ("index", "TensorRef"), ("source", "TensorRef"), ("dim", "i32"),
+    ("memory_config", "MemoryConfig"), ("scatter_reduce_type", "ScatterReduceType")])
+S.table("GatherOp", [
+    ("input", "TensorRef"), ("index", "TensorRef"), ("out", "TensorRef"), ("dim", "i32"), ("memory_config", "MemoryConfig")])
+S.table("SortOp", [
+    ("in", "TensorRef"), ("dim", "i8"), ("descending", "bool"), ("stable", "bool"), ("memcfg", "MemoryConfig"),
+    ("outputs", "[TensorRef]")])
+S.table("TopKOp", [
+    ("input_tensor", "TensorRef"), ("k", "i32"), ("dim", "i32", -1), ("largest", "bool", True), ("sorted", "bool", True),
+    ("memcfg", "MemoryConfig"), ("outputs", "[TensorRef]")])
+S.table("SamplingOp", [
+    ("input_values", "TensorRef"), ("input_indices", "TensorRef"), ("k", "TensorRef"), ("p", "TensorRef"), ("temp", "TensorRef"),
+    ("seed", "u32", OPT), ("out", "TensorRef")])
 # operations/embedding.fbs
 S.table("EmbeddingOp", [("input", "TensorRef"), ("weight", "TensorRef"), ("out", "TensorRef")])
 # operations/pool.fbs
@@ -310,6 +326,17 @@ S.table("ScaledDotProductAttentionDecodeOp", [
 S.table("FillCacheOp", [("cache", "TensorRef"), ("input", "TensorRef"), ("batch_offset", "u32")])
 S.table("UpdateCacheOp", [
     ("cache", "TensorRef"), ("input", "TensorRef"), ("update_index", "TensorRef"), ("batch_offset", "u32")])
+S.table("PagedUpdateCacheOp", [
+    ("cache", "TensorRef"), ("input", "TensorRef"), ("update_index", "TensorRef"), ("share_cache", "bool"),
+    ("page_table", "TensorRef")])
+S.table("PagedFillCacheOp", [
+    ("cache", "TensorRef"), ("input", "TensorRef"), ("page_table", "TensorRef"), ("batch_idx_tensor", "TensorRef")])
+# operations/transformer.fbs
+S.table("PagedScaledDotProductAttentionDecodeOp", [
+    ("query", "TensorRef"), ("key", "TensorRef"), ("value", "TensorRef"), ("page_table", "TensorRef"), ("is_causal", "bool"),
+    ("attention_mask", "TensorRef"), ("cur_pos_tensor", "TensorRef"), ("attention_sink", "TensorRef"),
+    ("scale", "f32", OPT), ("sliding_window_size", "u32", OPT), ("out", "TensorRef"), ("memcfg", "MemoryConfig"),
+    ("program_config", "opaque")])
 
 # --- ccl (operations/ccl.fbs)
 S.table("AllGatherOp", [

@@ -653,6 +653,71 @@ class ProgramBuilder:
             "scale": scale, "out": out.ref, "memcfg": self._mc()}, ins, [out], loc)
         return out
 
+    def paged_update_cache(self, cache: Value, x: Value, update_index: Value, page_table: Optional[Value] = None,
+                           share_cache: bool = False, loc=None) -> Value:
+        """In place: token s of user b of x [users, seq, heads, D] goes to position update_index[b] + s of the
+        paged cache [blocks, heads, block_size, D].  Returns `cache`."""
+        ins = [cache, x, update_index] + ([page_table] if page_table else [])
+        self._emit("PagedUpdateCacheOp", {"cache": cache.ref, "input": x.ref, "update_index": update_index.ref,
+                                          "share_cache": share_cache, "page_table": page_table.ref if page_table else None},
+                   ins, [], loc)
+        return cache
+
+    def paged_fill_cache(self, cache: Value, x: Value, page_table: Value, batch_idx: Optional[Value] = None, loc=None) -> Value:
+        """In place: x [users, heads, seq, D] fills the pages of the users' page-table rows.  Returns `cache`."""
+        ins = [cache, x, page_table] + ([batch_idx] if batch_idx else [])
+        self._emit("PagedFillCacheOp", {"cache": cache.ref, "input": x.ref, "page_table": page_table.ref,
+                                        "batch_idx_tensor": batch_idx.ref if batch_idx else None}, ins, [], loc)
+        return cache
+
+    def paged_scaled_dot_product_attention_decode(self, q: Value, k: Value, v: Value, page_table: Value,
+                                                  cur_pos: Optional[Value] = None, mask: Optional[Value] = None,
+                                                  is_causal: bool = True, scale: Optional[float] = None, loc=None) -> Value:
+        """q [B, 1, H, D] against paged k / v [blocks, Hkv, block_size, D] read through page_table [B, pages]."""
+        out = self._value(q.shape, q.dtype)
+        ins = [x for x in (q, k, v, page_table, mask, cur_pos) if x is not None]
+        self._emit("PagedScaledDotProductAttentionDecodeOp", {
+            "query": q.ref, "key": k.ref, "value": v.ref, "page_table": page_table.ref, "is_causal": is_causal,
+            "attention_mask": mask.ref if mask else None, "cur_pos_tensor": cur_pos.ref if cur_pos else None,
+            "scale": scale, "out": out.ref, "memcfg": self._mc()}, ins, [out], loc)
+        return out
+
+    # ---- indexing ---------------------------------------------------------------------------------------------------
+    def gather(self, x: Value, index: Value, dim: int, loc=None) -> Value:
+        out = self._value(index.shape, x.dtype)
+        self._emit("GatherOp", {"input": x.ref, "index": index.ref, "out": out.ref, "dim": dim, "memory_config": self._mc()},
+                   [x, index], [out], loc)
+        return out
+
+    def scatter(self, x: Value, index: Value, src: Value, dim: int, reduce_type: Optional[str] = None, loc=None) -> Value:
+        """reduce_type None (plain scatter) or "Sum" / "Max" / "Min" / "Prod"."""
+        out = self._value(x.shape, x.dtype)
+        self._emit("ScatterOp", {"input": x.ref, "out": out.ref, "index": index.ref, "source": src.ref, "dim": dim,
+                                 "memory_config": self._mc(), "scatter_reduce_type": reduce_type or "Invalid"},
+                   [x, index, src], [out], loc)
+        return out
+
+    def sort(self, x: Value, dim: int = -1, descending: bool = False, stable: bool = True, index_dtype: str = "Int32", loc=None):
+        values, indices = self._value(x.shape, x.dtype), self._value(x.shape, index_dtype)
+        self._emit("SortOp", {"in": x.ref, "dim": dim, "descending": descending, "stable": stable, "memcfg": self._mc(),
+                              "outputs": [values.ref, indices.ref]}, [x], [values, indices], loc)
+        return values, indices
+
+    def topk(self, x: Value, k: int, dim: int = -1, largest: bool = True, index_dtype: str = "Int32", loc=None):
+        shape = list(x.shape)
+        shape[_norm(dim, len(shape))] = k
+        values, indices = self._value(shape, x.dtype), self._value(shape, index_dtype)
+        self._emit("TopKOp", {"input_tensor": x.ref, "k": k, "dim": dim, "largest": largest, "sorted": True,
+                              "memcfg": self._mc(), "outputs": [values.ref, indices.ref]}, [x], [values, indices], loc)
+        return values, indices
+
+    def sampling(self, values: Value, indices: Value, k: Value, p: Value, temp: Value, seed: Optional[int] = None, loc=None) -> Value:
+        """One sampled candidate per row of values / indices [batch, candidates]; result [batch] Int32."""
+        out = self._value([values.shape[-2]], "Int32")
+        self._emit("SamplingOp", {"input_values": values.ref, "input_indices": indices.ref, "k": k.ref, "p": p.ref, "temp": temp.ref,
+                                  "seed": seed, "out": out.ref}, [values, indices, k, p, temp], [out], loc)
+        return out
+
     # ---- sub-programs: const-eval, calls, traces -------------------------------------------------------------
     def input_like(self, v: Value, on_device: Optional[bool] = None) -> Value:
         return self.input(v.shape, v.dtype, v.on_device if on_device is None else on_device)

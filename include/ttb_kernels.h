@@ -277,7 +277,8 @@ TTB_API int ttb_sdpa_decode_paged(const void *q, const void *k, const void *v, c
  *   ttb_scatter  out = x, then out[..., index[i], ...] (op)= src[i] along `dim`; reduce_type is the flatbuffer's
  *                ScatterReduceType: 7 plain scatter, 0 sum, 2 max, 3 min, 6 prod (the input's own value takes part).
  *                Duplicates are applied in increasing position along `dim`, the order of torch's CPU loop, so the
- *                result is the same on every run.
+ *                result is the same on every run.  Sums and products of 16-bit tensors are accumulated in f32 and
+ *                rounded once, as torch does; that takes a workspace of ttb_scatter_workspace_bytes.
  *   An index outside its dimension is skipped (gather: reads as 0) and reported by ttb_index_status (cleared on read).
  *   ttb_sort     every row of [rows, n] sorted (stable; NaN last ascending / first descending, as torch.sort);
  *                the first `take` values and / or positions of each row are written (take = n: a full sort;
@@ -288,9 +289,10 @@ TTB_API int ttb_sdpa_decode_paged(const void *q, const void *k, const void *v, c
  *                candidate's entry of `indices`.  values / p / temp share `dtype`; k is UInt32.  At most 4096 candidates. */
 TTB_API int ttb_gather(const void *x, const void *index, void *out, int dtype, int index_dtype, int rank,
                        const int64_t *x_shape, const int64_t *index_shape, int dim, void *stream);
+TTB_API size_t ttb_scatter_workspace_bytes(int dtype, int reduce_type, size_t elements);
 TTB_API int ttb_scatter(const void *x, const void *index, const void *src, void *out, int dtype, int index_dtype, int rank,
                         const int64_t *x_shape, const int64_t *index_shape, const int64_t *src_shape, int dim,
-                        int reduce_type, void *stream);
+                        int reduce_type, void *workspace, size_t workspace_bytes, void *stream);
 TTB_API int ttb_index_status(int *bad_index_seen);
 TTB_API size_t ttb_sort_workspace_bytes(size_t rows, size_t n);
 TTB_API int ttb_sort(const void *x, void *values, void *indices, int dtype, int index_dtype, size_t rows, size_t n,

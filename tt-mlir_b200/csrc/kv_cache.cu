@@ -547,10 +547,11 @@ int ttb_sdpa_decode(const void *q, const void *k, const void *v, const void *cur
                  2.0 * batch * kv_heads * double(seq) * head_dim * 2 + 2.0 * batch * heads * head_dim * 2, st);
 #define TTB_DEC(T)                                                                                                     \
   switch (head_dim) {                                                                                                  \
+  case 32: return dispatchDecodeG<T, 32>(g, q, k, v, cur_pos, mask, out, pm, pl, po, p, st);                          \
   case 64: return dispatchDecodeG<T, 64>(g, q, k, v, cur_pos, mask, out, pm, pl, po, p, st);                          \
   case 128: return dispatchDecodeG<T, 128>(g, q, k, v, cur_pos, mask, out, pm, pl, po, p, st);                        \
   case 256: return dispatchDecodeG<T, 256>(g, q, k, v, cur_pos, mask, out, pm, pl, po, p, st);                        \
-  default: setLastError("sdpa_decode: head_dim must be 64, 128 or 256"); return TTB_ERR_UNSUPPORTED;                  \
+  default: setLastError("sdpa_decode: head_dim must be 32, 64, 128 or 256"); return TTB_ERR_UNSUPPORTED;                  \
   }
   if (dtype == kBF16) { TTB_DEC(__nv_bfloat16) }
   TTB_DEC(__half)

@@ -2509,10 +2509,13 @@ void Executor::runScatter(const fbt::ScatterOp *op) {
   const int dim = normDim(op->dim(), x->shape.size());
   std::vector<int64_t> xs = shape64(x->shape), is = shape64(index->shape), ss = shape64(src->shape);
   dev->ranIndexOp = true;
+  const int mode = static_cast<int>(op->scatter_reduce_type());
+  const size_t wsBytes = ttb_scatter_workspace_bytes(ttbDtype(x->dtype), mode, x->volume());
+  TensorPtr ws = wsBytes ? makeDeviceTensor(dev, {static_cast<uint32_t>((wsBytes + 3) / 4)}, DataType::Float32) : nullptr;
   eachRank([&](size_t i, const RankCtx &r) {
     TTB_CALL(ttb_scatter(x->shards[i]->ptr, index->shards[i]->ptr, src->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(x->dtype),
-                         ttbDtype(index->dtype), static_cast<int>(xs.size()), xs.data(), is.data(), ss.data(), dim,
-                         static_cast<int>(op->scatter_reduce_type()), r.stream));
+                         ttbDtype(index->dtype), static_cast<int>(xs.size()), xs.data(), is.data(), ss.data(), dim, mode,
+                         ws ? ws->shards[i]->ptr : nullptr, wsBytes, r.stream));
   });
   put(op->out(), out);
 }

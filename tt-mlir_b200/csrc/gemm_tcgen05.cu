@@ -31,10 +31,13 @@ constexpr int TC_TMEM_COLS = 512;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;
 constexpr int TC_OUT_BYTES = 4 * 2 * 4096; // epilogue staging: 4 warps, double buffered, 32 rows x 128 B
 
-template <int BN> struct TcCfg {
-  static constexpr int kBBytes = BN * TC_BK * 2;
+// PAIR: two CTAs of a cluster share one 256 x BN tile (tcgen05 cta_group::2): each holds 128 rows of A and
+// BN / 2 rows of B per stage, so a stage is smaller and more of them fit.
+template <int BN, bool PAIR = false> struct TcCfg {
+  static constexpr int kBRows = PAIR ? BN / 2 : BN;
+  static constexpr int kBBytes = kBRows * TC_BK * 2;
   static constexpr int kStageBytes = TC_A_BYTES + kBBytes;
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kStages = PAIR ? (BN == 256 ? 6 : 8) : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
   static constexpr int kSmem = kStages * kStageBytes + TC_OUT_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
@@ -126,15 +129,16 @@ struct PushMaps {
   CUtensorMap m[8];
 };
 
-template <int BN, typename TC, bool PLAIN>
+template <int BN, typename TC, bool PLAIN, bool PAIR>
 __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     gemmTcgen05Kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                       const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapE,
                       const __grid_constant__ CUtensorMap mapB1, const __grid_constant__ CUtensorMap mapC1,
                       const __grid_constant__ CUtensorMap mapB2, const __grid_constant__ CUtensorMap mapC2,
                       const __grid_constant__ PushMaps pushMaps, TC *__restrict__ c, TcParams p) {
-  using Cfg = TcCfg<BN>;
+  using Cfg = TcCfg<BN, PAIR>;
   constexpr int STAGES = Cfg::kStages;
+  constexpr int TILE_M = PAIR ? 2 * TC_BM : TC_BM; // rows of C per tile (per CTA always TC_BM)
   extern __shared__ uint8_t smemRaw[];
   // 1024-byte alignment: required by the 128-byte swizzle pattern
   const uint32_t base = (smemU32(smemRaw) + 1023u) & ~1023u;
@@ -150,7 +154,11 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
   volatile int *abortFlag = &abortFlagS;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t tilesM = p.cTw ? p.cTilesM : (p.M + TC_BM - 1) / TC_BM, tilesN = p.segCum[2];
+  // A pair works through the tile list as one worker; rank 0 of the pair issues the MMAs.
+  const uint32_t ctaRank = PAIR ? clusterCtaRank() : 0u;
+  const bool leader = ctaRank == 0;
+  const int64_t worker = PAIR ? blockIdx.x / 2 : blockIdx.x, workers = PAIR ? gridDim.x / 2 : gridDim.x;
+  const int64_t tilesM = p.cTw ? p.cTilesM : (p.M + TILE_M - 1) / TILE_M, tilesN = p.segCum[2];
   const int64_t numTiles = tilesM * tilesN;
   // n-tile index -> (segment, first column inside the segment)
   auto segmentOf = [&](int64_t nt, int &n0) {
@@ -168,7 +176,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     }
     for (int a = 0; a < 2; ++a) {
       mbarInit(tmemFullBar(a), 1);
-      mbarInit(tmemEmptyBar(a), 128);
+      mbarInit(tmemEmptyBar(a), PAIR ? 256 : 128); // pair: the epilogue threads of both CTAs arrive at rank 0's barrier
     }
     for (int w = 0; w < 8; ++w) mbarInit(extraBar(w), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -177,12 +185,19 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     prefetchTensorMap(&mapC);
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemU32(&tmemBaseSlot)), "r"(TC_TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemU32(&tmemBaseSlot)), "r"(TC_TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemU32(&tmemBaseSlot)), "r"(TC_TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tcFenceBefore();
   __syncthreads();
   tcFenceAfter();
+  // Pair: neither CTA may signal the other's barriers before both have initialised them.
+  if constexpr (PAIR) clusterSync();
   const uint32_t tmemBase = tmemBaseSlot;
   // Everything above touched only this CTA's shared memory, TMEM and the kernel parameters, so it
   // may run while the kernel before this one on the stream is still finishing; from here on
@@ -210,7 +225,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
       __syncwarp();
       if (lane == 0) mbarArrive(fullBar(item % STAGES));
     };
-    for (int64_t tile = blockIdx.x; tile < numTiles && alive; tile += gridDim.x) {
+    for (int64_t tile = worker; tile < numTiles && alive; tile += workers) {
       const int64_t m0 = (tile % tilesM) * TC_BM;
       int n0;
       (void)segmentOf(tile / tilesM, n0);
@@ -272,9 +287,9 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     if (lane == 0) {
       uint32_t it = 0;
       bool alive = true;
-      for (int64_t tile = blockIdx.x; tile < numTiles && alive; tile += gridDim.x) {
+      for (int64_t tile = worker; tile < numTiles && alive; tile += workers) {
         const int mt = static_cast<int>(tile % tilesM);
-        const int m0 = mt * TC_BM;
+        const int m0 = mt * TILE_M + static_cast<int>(ctaRank) * TC_BM;
         int n0;
         const int seg = segmentOf(tile / tilesM, n0);
         const CUtensorMap *mb = seg == 0 ? &mapB : (seg == 1 ? &mapB1 : &mapB2);
@@ -291,6 +306,17 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
           const uint32_t phase = (it / STAGES) & 1u;
           if (!mbarWait(emptyBar(s), phase ^ 1u, abortFlag, 1)) { alive = false; break; }
           const uint32_t sa = base + s * Cfg::kStageBytes, sb = sa + TC_A_BYTES;
+          if constexpr (PAIR) {
+            // Both CTAs' loads complete on rank 0's barrier, which expects the bytes of both; each CTA
+            // fetches its own 128 rows of A and its own half of the B tile (in SwiGLU mode rank 0 the gate
+            // rows and rank 1 the up rows of the same output columns).
+            const uint32_t bar = mapToCta(fullBar(s), 0);
+            if (leader) mbarArriveExpectTx(fullBar(s), 2 * Cfg::kStageBytes);
+            tmaLoad2dPair(sa, &mapA, bar, kb * p.kElems, m0);
+            if (p.dual) tmaLoad2dPair(sb, leader ? &mapB : &mapB1, bar, kb * p.kElems, n0);
+            else tmaLoad2dPair(sb, mb, bar, kb * p.kElems, n0 + static_cast<int>(ctaRank) * (BN / 2));
+            continue;
+          }
           mbarArriveExpectTx(fullBar(s), Cfg::kStageBytes);
           if (p.cTw) {
             // the input patch of this filter tap; coordinates left of / above the image read zeros
@@ -310,12 +336,12 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       const bool ints = p.fmt == 2;
-      const uint32_t idesc = ints ? instrDescI8(p.aSigned, p.bSigned, TC_BM, BN) : instrDesc(p.fmt, TC_BM, BN);
+      const uint32_t idesc = ints ? instrDescI8(p.aSigned, p.bSigned, TILE_M, BN) : instrDesc(p.fmt, TILE_M, BN);
       uint32_t it = 0, accIt = 0;
       bool alive = true;
-      for (int64_t tile = blockIdx.x; tile < numTiles && alive; tile += gridDim.x, ++accIt) {
+      for (int64_t tile = worker; tile < numTiles && alive; tile += workers, ++accIt) {
         const int acc = accIt & 1;
         const uint32_t accPhase = (accIt >> 1) & 1u;
         if (!mbarWait(tmemEmptyBar(acc), accPhase ^ 1u, abortFlag, 2)) break;
@@ -331,12 +357,22 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
 #pragma unroll
           for (int k = 0; k < TC_BK / 16; ++k) {
             // +32 bytes per k-step (16 two-byte or 32 one-byte elements) = +2 in the descriptor's 16-byte address units
-            if (ints) tcMmaI8(tmemD, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
-            else tcMma(tmemD, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (PAIR) {
+              if (ints) tcMmaPairI8(tmemD, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              else tcMmaPair(tmemD, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            } else {
+              if (ints) tcMmaI8(tmemD, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              else tcMma(tmemD, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
           }
-          tcCommit(emptyBar(s)); // frees the stage once these MMAs have read it
+          // frees the stage (in both CTAs of a pair) once these MMAs have read it
+          if constexpr (PAIR) tcCommitPair(emptyBar(s));
+          else tcCommit(emptyBar(s));
         }
-        if (alive) tcCommit(tmemFullBar(acc)); // accumulator complete
+        if (alive) { // accumulator complete
+          if constexpr (PAIR) tcCommitPair(tmemFullBar(acc));
+          else tcCommit(tmemFullBar(acc));
+        }
       }
     }
   } else {
@@ -363,7 +399,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     // accumulator = number & 1).  With two groups, group g drains the tiles with number = g mod 2.
     // The last tile has no successor whose main loop could hide its epilogue, so there both groups
     // work on it: its owner takes the even column chunks, the other group the odd ones.
-    const int64_t myTiles = blockIdx.x < numTiles ? (numTiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int64_t myTiles = worker < numTiles ? (numTiles - worker + workers - 1) / workers : 0;
     const int64_t lastNo = myTiles - 1;
     bool helped = false;
     for (int64_t no = group;; no += EPW / 4) {
@@ -377,13 +413,13 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
         }
       }
       const bool shared = EPW == 8 && BN / CH >= 2 && no == lastNo;
-      const int64_t tile = blockIdx.x + no * gridDim.x;
+      const int64_t tile = worker + no * workers;
       const uint32_t accIt = static_cast<uint32_t>(no);
       const int acc = accIt & 1;
       const uint32_t accPhase = (accIt >> 1) & 1u;
       if (!mbarWait(tmemFullBar(acc), accPhase, abortFlag, 4)) break;
       tcFenceAfter();
-      const int64_t m0 = (tile % tilesM) * TC_BM;
+      const int64_t m0 = (tile % tilesM) * TILE_M + static_cast<int64_t>(ctaRank) * TC_BM;
       int n0i;
       const int seg = segmentOf(tile / tilesM, n0i);
       const int64_t n0 = n0i, segN = p.segN[seg];
@@ -633,7 +669,9 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
       if (!alive) break;
       if (helper) break; // the helper's visit was the last thing this group does
       tcFenceBefore();
-      mbarArrive(tmemEmptyBar(acc)); // all 128 epilogue threads arrive: the accumulator may be overwritten
+      // all 128 epilogue threads arrive (of both CTAs of a pair, at rank 0's barrier): the accumulator may be overwritten
+      if constexpr (PAIR) mbarArriveRemote(mapToCta(tmemEmptyBar(acc), 0));
+      else mbarArrive(tmemEmptyBar(acc));
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); // stores done before smem goes away
   }
@@ -646,9 +684,12 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
   }
   tcFenceBefore();
   __syncthreads();
+  // Pair: a CTA's shared memory (barriers, operand halves) is used by its partner until both are done.
+  if constexpr (PAIR) clusterSync();
   if (warp == 1) {
     tcFenceAfter();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(TC_TMEM_COLS) : "memory");
+    if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(TC_TMEM_COLS) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(TC_TMEM_COLS) : "memory");
   }
 }
 
@@ -710,31 +751,78 @@ static bool makeMap4(CUtensorMap *map, const void *ptr, int dtype, int64_t c, in
   return r == CUDA_SUCCESS;
 }
 
-template <int BN, typename TC, bool PLAIN>
+// Two CTAs per 256-row tile (cta_group::2) unless switched off (TTB_DISABLE_PAIR_MMA=1) or the problem has
+// fewer than 256 rows; convolutions keep one CTA per tile.
+static bool pairMmaWanted(int64_t m) {
+  static const bool off = [] {
+    const char *e = std::getenv("TTB_DISABLE_PAIR_MMA");
+    return e && e[0] == '1';
+  }();
+  return !off && m >= 2 * TC_BM && smCount() >= 2;
+}
+
+template <int BN, typename TC, bool PLAIN, bool PAIR = false>
 static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &me, void *c, const TcParams &p,
                     cudaStream_t st, const CUtensorMap *more = nullptr /* mapB1, mapC1, mapB2, mapC2 of a grouped launch */,
-                    const PushMaps *push = nullptr);
-
-template <int BN, typename TC, bool PLAIN>
-static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &me, void *c, const TcParams &p,
-                    cudaStream_t st, const CUtensorMap *more, const PushMaps *push) {
-  using Cfg = TcCfg<BN>;
+                    const PushMaps *push = nullptr) {
+  using Cfg = TcCfg<BN, PAIR>;
   // Function attributes belong to a device: set the shared-memory limit once on each.
   static bool attrSet[64] = {};
   int dev = 0;
   TTB_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attrSet[dev]) {
-    TTB_CUDA(cudaFuncSetAttribute(gemmTcgen05Kernel<BN, TC, PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+    TTB_CUDA(cudaFuncSetAttribute(gemmTcgen05Kernel<BN, TC, PLAIN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
     attrSet[dev] = true;
   }
-  int64_t tiles = (p.cTw ? p.cTilesM : (p.M + TC_BM - 1) / TC_BM) * p.segCum[2];
-  int grid = static_cast<int>(tiles < smCount() ? tiles : smCount());
-  TTB_CUDA(launchPdl(gemmTcgen05Kernel<BN, TC, PLAIN>, dim3(grid), dim3(PLAIN ? TC_THREADS : TC_THREADS_EPI8), Cfg::kSmem, st, ma, mb,
-                     mc, me, more ? more[0] : mb, more ? more[1] : mc, more ? more[2] : mb, more ? more[3] : mc,
-                     push ? *push : PushMaps{{mc, mc, mc, mc, mc, mc, mc, mc}}, static_cast<TC *>(c), p));
+  const int64_t tileM = PAIR ? 2 * TC_BM : TC_BM;
+  int64_t tiles = (p.cTw ? p.cTilesM : (p.M + tileM - 1) / tileM) * p.segCum[2];
+  const int workers = PAIR ? smCount() / 2 : smCount();
+  int grid = static_cast<int>(tiles < workers ? tiles : workers) * (PAIR ? 2 : 1);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(PLAIN ? TC_THREADS : TC_THREADS_EPI8);
+  cfg.dynamicSmemBytes = Cfg::kSmem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (pdlEnabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (PAIR) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 2;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  TTB_CUDA(cudaLaunchKernelEx(&cfg, gemmTcgen05Kernel<BN, TC, PLAIN, PAIR>, ma, mb, mc, me, more ? more[0] : mb, more ? more[1] : mc,
+                              more ? more[2] : mb, more ? more[3] : mc, push ? *push : PushMaps{{mc, mc, mc, mc, mc, mc, mc, mc}},
+                              static_cast<TC *>(c), p));
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;
+}
+
+// Tile width for an m x n problem on `workers` workers of `tileM` rows: fewest (waves x per-tile cost); the
+// +64 stands for the A tile every CTA loads whatever its width, which makes narrow tiles less efficient per column.
+static int pickTileWidth(int64_t m, int64_t n, int64_t tileM, int workers) {
+  int bn = 64;
+  int64_t best = -1;
+  for (int w : {256, 128, 64}) {
+    if (w > 64 && n < w) continue;
+    int64_t tiles = ((m + tileM - 1) / tileM) * ((n + w - 1) / w);
+    int64_t waves = (tiles + workers - 1) / workers;
+    int64_t cost = waves * (w + 64);
+    if (best < 0 || cost < best) {
+      best = cost;
+      bn = w;
+    }
+  }
+  return bn;
 }
 
 int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int abDtype, int biasDtype, int cDtype,
@@ -763,24 +851,10 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff) return -1;
   // Tiny problems are launch-bound either way; keep them on the simple kernel.
   if (m * n * k < (1ll << 18)) return -1;
-  // Tile width: fewest (waves x per-tile cost); the +64 stands for the A tile every CTA loads
-  // whatever its width, which makes narrow tiles less efficient per column.
-  int bn = 64;
-  {
-    int64_t best = -1;
-    for (int w : {256, 128, 64}) {
-      if (w > 64 && n < w) continue;
-      int64_t tiles = ((m + TC_BM - 1) / TC_BM) * ((n + w - 1) / w);
-      int64_t waves = (tiles + smCount() - 1) / smCount();
-      int64_t cost = waves * (w + 64);
-      if (best < 0 || cost < best) {
-        best = cost;
-        bn = w;
-      }
-    }
-  }
+  const bool pair = pairMmaWanted(m);
+  const int bn = pickTileWidth(m, n, pair ? 2 * TC_BM : TC_BM, pair ? smCount() / 2 : smCount());
   CUtensorMap ma, mb, mc, me;
-  if (!makeMap(&ma, a, abDtype, m, k, TC_BM) || !makeMap(&mb, b, abDtype, n, k, bn) ||
+  if (!makeMap(&ma, a, abDtype, m, k, TC_BM) || !makeMap(&mb, b, abDtype, n, k, pair ? bn / 2 : bn) ||
       !makeMap(&mc, c, cDtype, m, n, 32))
     return -1;
   if (extraOp) {
@@ -814,6 +888,9 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   ProfScope prof("gemm_tcgen05", flops, bytes, stream);
   const bool plain = !bias && act == TTB_ACT_NONE && roundSteps == 0 && !extraOp;
 #define TTB_TC(BNv, TCv)                                                                 \
+  if (pair)                                                                              \
+    return plain ? launchTc<BNv, TCv, true, true>(ma, mb, mc, me, c, p, stream, nullptr, pushing ? &pm : nullptr)             \
+                 : launchTc<BNv, TCv, false, true>(ma, mb, mc, me, c, p, stream);        \
   return plain ? launchTc<BNv, TCv, true>(ma, mb, mc, me, c, p, stream, nullptr, pushing ? &pm : nullptr)                     \
                : launchTc<BNv, TCv, false>(ma, mb, mc, me, c, p, stream)
 #define TTB_TC_BN(TCv)                                                                   \
@@ -856,6 +933,10 @@ int gemmTcgen05SwigluTry(const void *a, const void *wGate, const void *wUp, void
   // both projections' FLOPs; A and both weights once, the result once
   ProfScope prof("gemm_tcgen05", 4.0 * double(m) * double(n) * double(k), (double(m) * k + 2.0 * double(n) * k + double(m) * n) * 2, stream);
   const CUtensorMap more[4] = {mu, mc, mu, mc};
+  if (pairMmaWanted(m)) {
+    if (dtype == kBF16) return launchTc<BN, __nv_bfloat16, false, true>(ma, mg, mc, mc, out, p, stream, more);
+    return launchTc<BN, __half, false, true>(ma, mg, mc, mc, out, p, stream, more);
+  }
   if (dtype == kBF16) return launchTc<BN, __nv_bfloat16, false>(ma, mg, mc, mc, out, p, stream, more);
   return launchTc<BN, __half, false>(ma, mg, mc, mc, out, p, stream, more);
 }
@@ -874,22 +955,10 @@ int gemmTcgen05I8Try(const void *a, const void *b, void *c, int aDtype, int bDty
   if (!aligned16(a) || !aligned16(b) || !aligned16(c) || (deqScale && (reinterpret_cast<uintptr_t>(deqScale) & 3))) return -1;
   if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff) return -1;
   if (m * n * k < (1ll << 18)) return -1;
-  int bn = 64;
-  {
-    int64_t best = -1;
-    for (int w : {256, 128, 64}) {
-      if (w > 64 && n < w) continue;
-      int64_t tiles = ((m + TC_BM - 1) / TC_BM) * ((n + w - 1) / w);
-      int64_t waves = (tiles + smCount() - 1) / smCount();
-      int64_t cost = waves * (w + 64);
-      if (best < 0 || cost < best) {
-        best = cost;
-        bn = w;
-      }
-    }
-  }
+  const bool pair = pairMmaWanted(m);
+  const int bn = pickTileWidth(m, n, pair ? 2 * TC_BM : TC_BM, pair ? smCount() / 2 : smCount());
   CUtensorMap ma, mb, mc;
-  if (!makeMap(&ma, a, kU8, m, k, TC_BM) || !makeMap(&mb, b, kU8, n, k, bn) || !makeMap(&mc, c, cDtype, m, n, 32)) return -1;
+  if (!makeMap(&ma, a, kU8, m, k, TC_BM) || !makeMap(&mb, b, kU8, n, k, pair ? bn / 2 : bn) || !makeMap(&mc, c, cDtype, m, n, 32)) return -1;
   TcParams p;
   p.M = m; p.N = n; p.K = k;
   // a bias follows the dequantize as a separate add: the dequantized value is rounded before it (round step 1)
@@ -907,7 +976,9 @@ int gemmTcgen05I8Try(const void *a, const void *b, void *c, int aDtype, int bDty
   p.deqScale = deqScale;
   ProfScope prof("gemm_tcgen05_i8", 2.0 * double(m) * double(n) * double(k),
                  double(m) * k + double(n) * k + double(m) * n * dtypeSize(cDtype), stream);
-#define TTB_TCI(BNv, TCv, PLAINv) return launchTc<BNv, TCv, PLAINv>(ma, mb, mc, mc, c, p, stream)
+#define TTB_TCI(BNv, TCv, PLAINv)                                                        \
+  if (pair) return launchTc<BNv, TCv, PLAINv, true>(ma, mb, mc, mc, c, p, stream);       \
+  return launchTc<BNv, TCv, PLAINv>(ma, mb, mc, mc, c, p, stream)
 #define TTB_TCI_BN(TCv, PLAINv)                                                          \
   switch (bn) {                                                                          \
   case 256: TTB_TCI(256, TCv, PLAINv);                                                   \
@@ -939,6 +1010,9 @@ int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, c
     nSum += n[i];
   }
   if (m * nSum * k < (1ll << 18)) return -1;
+  const bool pair = pairMmaWanted(m);
+  const int64_t tileM = pair ? 2 * TC_BM : TC_BM;
+  const int workers = pair ? smCount() / 2 : smCount();
   int bn = 64;
   {
     int64_t best = -1;
@@ -947,10 +1021,10 @@ int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, c
       bool fits = true;
       for (int i = 0; i < count; ++i) {
         if (w > 64 && n[i] < w) fits = false;
-        tiles += ((m + TC_BM - 1) / TC_BM) * ((n[i] + w - 1) / w);
+        tiles += ((m + tileM - 1) / tileM) * ((n[i] + w - 1) / w);
       }
       if (!fits) continue;
-      int64_t waves = (tiles + smCount() - 1) / smCount();
+      int64_t waves = (tiles + workers - 1) / workers;
       int64_t cost = waves * (w + 64);
       if (best < 0 || cost < best) {
         best = cost;
@@ -961,7 +1035,7 @@ int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, c
   CUtensorMap ma, mb[3], mc[3];
   if (!makeMap(&ma, a, abDtype, m, k, TC_BM)) return -1;
   for (int i = 0; i < count; ++i) {
-    if (!makeMap(&mb[i], b[i], abDtype, n[i], k, bn) || !makeMap(&mc[i], c[i], cDtype, m, n[i], 32)) return -1;
+    if (!makeMap(&mb[i], b[i], abDtype, n[i], k, pair ? bn / 2 : bn) || !makeMap(&mc[i], c[i], cDtype, m, n[i], 32)) return -1;
   }
   for (int i = count; i < 3; ++i) {
     mb[i] = mb[0];
@@ -987,7 +1061,9 @@ int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, c
   p.kElems = TC_BK; p.aSigned = p.bSigned = 0; p.deq = 0; p.deqScalar = 0.0f; p.deqScale = nullptr;
   ProfScope prof("gemm_tcgen05", flops, bytes, stream);
   const CUtensorMap more[4] = {mb[1], mc[1], mb[2], mc[2]};
-#define TTB_TCG(BNv, TCv) return launchTc<BNv, TCv, true>(ma, mb[0], mc[0], mc[0], c[0], p, stream, more)
+#define TTB_TCG(BNv, TCv)                                                                \
+  if (pair) return launchTc<BNv, TCv, true, true>(ma, mb[0], mc[0], mc[0], c[0], p, stream, more); \
+  return launchTc<BNv, TCv, true>(ma, mb[0], mc[0], mc[0], c[0], p, stream, more)
 #define TTB_TCG_BN(TCv)                                                                  \
   switch (bn) {                                                                          \
   case 256: TTB_TCG(256, TCv);                                                           \

@@ -69,6 +69,52 @@ __device__ __forceinline__ void tmaLoad4d(uint32_t dst, const CUtensorMap *map, 
                ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 
+// ---- CTA pairs (cta_group::2) --------------------------------------------------------------------
+// Two CTAs of a cluster on neighbouring SMs run one M = 256 contraction: each holds 128 rows of A and
+// half of the B tile in its own shared memory and 128 rows of the accumulator in its own tensor memory;
+// the CTA of rank 0 issues the MMAs for both.  Every CTA fetches its own operands (plain TMA loads, no
+// multicast); what crosses between the two is barrier traffic only.
+__device__ __forceinline__ uint32_t clusterCtaRank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address, in the cluster's shared-memory window, of `addr` (a shared::cta address) in CTA `rank`.
+__device__ __forceinline__ uint32_t mapToCta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void clusterSync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on an mbarrier that lives in another CTA of the cluster (`bar` from mapToCta).
+__device__ __forceinline__ void mbarArriveRemote(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// TMA load whose completion is signalled on an mbarrier of either CTA of the pair (`bar` from mapToCta).
+__device__ __forceinline__ void tmaLoad2dPair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+// Arrives on the barrier at the same shared-memory offset in both CTAs once the pair's MMAs issued so far have retired.
+__device__ __forceinline__ void tcCommitPair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(static_cast<uint16_t>(3)) : "memory");
+}
+__device__ __forceinline__ void tcMmaPair(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tcMmaPairI8(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 // Shared-memory matrix descriptor for a tile stored with the 128-byte swizzle (descriptor
 // version 1, layout type 2).  K-major operand: rows of 128 bytes along K, `sbo` = distance
 // between 8-row groups, `lbo` unused.  MN-major operand: rows of 128 bytes along M/N (64

@@ -345,6 +345,18 @@ TTB_API int ttb_gemm(const void *a, const void *b, const void *bias, void *c, in
 TTB_API int ttb_gemm_grouped(const void *a, const void *const *b, void *const *c, const int64_t *n, int count,
                              int ab_dtype, int c_dtype, int64_t m, int64_t k, void *stream);
 
+/* ttb_gemm_grouped with the rotary embedding of the results in `rope_mask` (bit i = problem i) applied in the
+ * epilogue: the columns of C_i are heads of `head_dim` values, row r has position r mod seq, cos / sin are
+ * [seq, head_dim] tables in `dtype`; each head becomes x cos + rotate_half(x) sin computed from the product rounded
+ * to `dtype` (bit-equal to ttb_gemm_grouped followed by ttb_rotary_embedding_strided, but stored in the product's
+ * own [m, n_i] layout).  TTB_ERR_UNSUPPORTED when the tensor-core kernel does not take the problem (head_dim other
+ * than 128, n_i not whole heads, 32-bit types): run the two steps separately then.
+ * No reference counterpart (::ttnn::linear followed by ::ttnn::experimental::rotary_embedding,
+ * runtime/lib/ttnn/operations/transformer/rotary_embedding.cpp:11-37). */
+TTB_API int ttb_gemm_grouped_rope(const void *a, const void *const *b, void *const *c, const int64_t *n, int count,
+                                  int dtype, int64_t m, int64_t k, const void *cos, const void *sin, int rope_mask,
+                                  int64_t seq, int64_t head_dim, void *stream);
+
 /* ttb_gemm with a second, full-size epilogue operand `extra` ([batch, m, n], dense, in
  * `c_dtype`), combined with the result of the bias / activation chain the way separate ops
  * would (the chain's result is rounded to `c_dtype` first):

@@ -181,6 +181,51 @@ def test_gemm_grouped_matches_separate_calls(rt, device, m, k, ns):
         assert_matches(g, (a.float() @ b.float().t()).to(torch.bfloat16), "grouped gemm")
 
 
+@pytest.mark.parametrize("batch,seq,k,ns,mask", [(1, 2048, 4096, (4096, 1024, 1024), 3), (2, 200, 264, (256, 128, 128), 3),
+                                                 (1, 512, 512, (512, 128, 128), 2), (1, 300, 128, (128, 384), 1)])
+def test_gemm_grouped_with_rotary_embedding_epilogue(rt, device, batch, seq, k, ns, mask):
+    """ttb_gemm_grouped_rope: the problems in the mask come out rotated, bit for bit what the grouped product
+    followed by the rotary embedding (f32 arithmetic on the rounded product, one rounding) gives; the others
+    are the plain product.  Rows are (batch, position) pairs; ragged row counts exercise the clipped tiles."""
+    m = batch * seq
+    torch.manual_seed(m + k)
+    a = torch.randn(m, k).to(torch.bfloat16)
+    bs = [(torch.randn(n, k) * 0.05).to(torch.bfloat16) for n in ns]
+    pos = torch.arange(seq, dtype=torch.float32)[:, None]
+    freq = 1.0 / (10000.0 ** (torch.arange(0, 64, dtype=torch.float32) / 64))
+    ang = torch.cat([pos * freq, pos * freq], dim=1)
+    cos, sin = ang.cos().to(torch.bfloat16), ang.sin().to(torch.bfloat16)
+    h = KernelHarness(rt)
+    try:
+        da = h.upload(a)
+        dbs = [h.upload(b) for b in bs]
+        dcs = [h.empty((m, n), torch.bfloat16) for n in ns]
+        dcos, dsin = h.upload(cos), h.upload(sin)
+        i64 = ctypes.c_int64
+        cnt = len(ns)
+        bp = (ctypes.c_void_p * cnt)(*[p.value for p in dbs])
+        cp = (ctypes.c_void_p * cnt)(*[p.value for p in dcs])
+        nn = (ctypes.c_int64 * cnt)(*ns)
+        rc = h.lib.ttb_gemm_grouped_rope(da, bp, cp, nn, cnt, BF16, i64(m), i64(k), dcos, dsin, mask, i64(seq), i64(128), h.stream)
+        assert rc == 0, h.lib.ttb_last_error().decode()
+        got = [h.download(dc, (m, n), torch.bfloat16) for dc, n in zip(dcs, ns)]
+        assert tc_status(h) == 0
+        rc = h.lib.ttb_gemm_grouped(da, bp, cp, nn, cnt, BF16, BF16, i64(m), i64(k), h.stream)
+        assert rc == 0, h.lib.ttb_last_error().decode()
+        plain = [h.download(dc, (m, n), torch.bfloat16) for dc, n in zip(dcs, ns)]
+    finally:
+        h.close()
+    for i, (g, pl, n) in enumerate(zip(got, plain, ns)):
+        if not (mask >> i) & 1:
+            assert torch.equal(g, pl), f"problem {i} is not in the mask and must be the plain product"
+            continue
+        x = pl.float().view(batch, seq, n // 128, 128)
+        c, s_ = cos.float()[None, :, None, :], sin.float()[None, :, None, :]
+        rot = torch.cat([-x[..., 64:], x[..., :64]], dim=-1)
+        want = (x * c + rot * s_).to(torch.bfloat16).view(m, n)
+        assert torch.equal(g, want), f"problem {i}: {(g != want).sum().item()} of {g.numel()} elements differ"
+
+
 @pytest.mark.parametrize("m,n,k", [(256, 384, 512), (2048, 1792, 1024), (200, 136, 72), (8, 16, 32), (1280, 14336, 256),
                                    (130, 64, 64)])
 def test_gemm_swiglu_equals_the_chain_of_launches(rt, device, m, n, k):

@@ -15,7 +15,8 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
 int gemmTcgen05SwigluTry(const void *a, const void *wGate, const void *wUp, void *out, int dtype, int64_t m, int64_t n,
                          int64_t k, cudaStream_t stream);
 int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, const int64_t *n, int count, int abDtype,
-                          int cDtype, int64_t m, int64_t k, cudaStream_t stream);
+                          int cDtype, int64_t m, int64_t k, cudaStream_t stream, const void *ropeCos = nullptr,
+                          const void *ropeSin = nullptr, int ropeMask = 0, int64_t ropeSeq = 1);
 } // namespace ttb
 
 static bool tcgen05Disabled() {
@@ -69,6 +70,25 @@ extern "C" int ttb_gemm_grouped(const void *a, const void *const *b, void *const
     if (rc) return rc;
   }
   return TTB_OK;
+}
+
+// ttb_gemm_grouped whose results, for the problems in `rope_mask`, leave the kernel already rotated: C_i's columns
+// are heads of 128 values, row r has position r mod seq, and every head is replaced by
+// x cos[pos] + rotate_half(x) sin[pos] computed from the rounded product, exactly what rotary_embedding makes of the
+// stored result of the linear op.  Only the tensor-core kernel has this mode: TTB_ERR_UNSUPPORTED tells the caller to
+// run the grouped product and the rotary embeddings separately.
+extern "C" int ttb_gemm_grouped_rope(const void *a, const void *const *b, void *const *c, const int64_t *n, int count,
+                                     int dtype, int64_t m, int64_t k, const void *cos, const void *sin, int rope_mask,
+                                     int64_t seq, int64_t head_dim, void *stream) {
+  TTB_CHECK(a && b && c && n && count >= 2 && count <= 3 && cos && sin, "bad argument");
+  for (int i = 0; i < count; ++i) TTB_CHECK(b[i] && c[i] && n[i] >= 0, "bad argument");
+  TTB_CHECK(rope_mask > 0 && (rope_mask >> count) == 0 && seq >= 1, "bad rope mask or sequence length");
+  if (head_dim == 128 && !tcgen05Disabled()) {
+    int rc = ttb::gemmTcgen05GroupedTry(a, b, c, n, count, dtype, dtype, m, k, ttb::asStream(stream), cos, sin, rope_mask, seq);
+    if (rc != -1) return rc;
+  }
+  ttb::setLastError("gemm_grouped_rope: shape, type or alignment not taken by the tensor-core kernel");
+  return TTB_ERR_UNSUPPORTED;
 }
 
 // C = A[M, K] B[N, K]^T whose row block o (M / nranks rows) is stored into targets[o] instead of

@@ -123,6 +123,13 @@ struct TcParams {
   int deq;               // 0 off (the integer accumulator is stored), 1 scalar, 2 per column
   float deqScalar;
   const float *deqScale; // [N] f32
+  // Rotary embedding in the epilogue (plain 16-bit launches, BN >= 128): the columns of segment i (bit i of
+  // ropeMask) are heads of 128 values; the product is rounded to the output type, as the separate linear op
+  // stores it, and then rotated as rotary_embedding does: out = x cos + rotate_half(x) sin with the tables
+  // ropeCos / ropeSin [ropeSeq, 128] in the output type and position = row mod ropeSeq.
+  int ropeMask = 0;
+  int ropeSeq = 1;
+  const void *ropeCos = nullptr, *ropeSin = nullptr;
 };
 
 struct PushMaps {
@@ -417,11 +424,29 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
       const uint32_t accIt = static_cast<uint32_t>(no);
       const int acc = accIt & 1;
       const uint32_t accPhase = (accIt >> 1) & 1u;
-      if (!mbarWait(tmemFullBar(acc), accPhase, abortFlag, 4)) break;
-      tcFenceAfter();
       const int64_t m0 = (tile % tilesM) * TILE_M + static_cast<int64_t>(ctaRank) * TC_BM;
       int n0i;
       const int seg = segmentOf(tile / tilesM, n0i);
+      // Rotary embedding: this row's 128 cosines and 128 sines (the same for every head of the tile) are fetched
+      // now, so that their latency passes while the main loop is still filling the accumulator.
+      uint4 ropeTab[PLAIN && sizeof(TC) == 2 && BN >= 128 ? 32 : 1];
+      bool ropeTile = false;
+      if constexpr (PLAIN && sizeof(TC) == 2 && BN >= 128) {
+        ropeTile = ((p.ropeMask >> seg) & 1) != 0;
+        if (ropeTile) {
+          const int64_t row = m0 + quarter * 32 + lane;
+          const int64_t pos = row < p.M ? row % p.ropeSeq : 0;
+          const uint4 *cosRow = reinterpret_cast<const uint4 *>(static_cast<const TC *>(p.ropeCos) + pos * 128);
+          const uint4 *sinRow = reinterpret_cast<const uint4 *>(static_cast<const TC *>(p.ropeSin) + pos * 128);
+#pragma unroll
+          for (int v = 0; v < 16; ++v) {
+            ropeTab[v] = __ldg(cosRow + v);
+            ropeTab[16 + v] = __ldg(sinRow + v);
+          }
+        }
+      }
+      if (!mbarWait(tmemFullBar(acc), accPhase, abortFlag, 4)) break;
+      tcFenceAfter();
       const int64_t n0 = n0i, segN = p.segN[seg];
       const CUtensorMap *mc = seg == 0 ? &mapC : (seg == 1 ? &mapC1 : &mapC2);
       int rowBase = static_cast<int>(m0) + quarter * 32; // first row of this warp's block in the 2-D store
@@ -489,6 +514,64 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
               asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
             ++chunkIt;
+          }
+        }
+      }
+      if constexpr (PLAIN && sizeof(TC) == 2 && BN >= 128) {
+        if (ropeTile) {
+          // Rotary embedding: chunks cc and cc + 1 hold the two halves of one head's 128 values of this row.
+          dualDone = true;
+          const uint32_t rowA = stageOut + static_cast<uint32_t>(lane) * 128u, rowB = rowA + 4096u;
+#pragma unroll 1
+          for (int cc = 0; cc < BN / CH; cc += 2) {
+            const int64_t col0 = n0 + cc * CH;
+            if (col0 >= segN) break; // warp-uniform
+#pragma unroll
+            for (int l = 0; l < 2; ++l) {
+              uint32_t x1[32], x2[32];
+              tcLoad32(taddrRow + static_cast<uint32_t>(cc * CH + l * 32), x1);
+              tcLoad32(taddrRow + static_cast<uint32_t>((cc + 1) * CH + l * 32), x2);
+              tcWaitLd();
+              if (l == 0) {
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); // both staging buffers are free
+                __syncwarp();
+              }
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint32_t wA[4], wB[4];
+                // 16-byte unit u of a table row holds columns [8u, 8u + 8): first half l * 4 + v, second half 8 more
+                const TC *c1e = reinterpret_cast<const TC *>(&ropeTab[l * 4 + v]), *c2e = reinterpret_cast<const TC *>(&ropeTab[8 + l * 4 + v]);
+                const TC *s1e = reinterpret_cast<const TC *>(&ropeTab[16 + l * 4 + v]), *s2e = reinterpret_cast<const TC *>(&ropeTab[24 + l * 4 + v]);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  float o1[2], o2[2];
+#pragma unroll
+                  for (int h = 0; h < 2; ++h) {
+                    const int e = v * 8 + q * 2 + h;
+                    const float a = toF32(fromF32<TC>(__uint_as_float(x1[e]))), b2 = toF32(fromF32<TC>(__uint_as_float(x2[e])));
+                    o1[h] = __fadd_rn(__fmul_rn(a, toF32(c1e[q * 2 + h])), __fmul_rn(-b2, toF32(s1e[q * 2 + h])));
+                    o2[h] = __fadd_rn(__fmul_rn(b2, toF32(c2e[q * 2 + h])), __fmul_rn(a, toF32(s2e[q * 2 + h])));
+                  }
+                  wA[q] = pack2<TC>(o1[0], o1[1]);
+                  wB[q] = pack2<TC>(o2[0], o2[1]);
+                }
+                const uint32_t off = static_cast<uint32_t>((l * 4 + v) ^ (lane & 7)) << 4;
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowA + off), "r"(wA[0]), "r"(wA[1]), "r"(wA[2]), "r"(wA[3]) : "memory");
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowB + off), "r"(wB[0]), "r"(wB[1]), "r"(wB[2]), "r"(wB[3]) : "memory");
+              }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              // one group per store: the chunk loop below reuses a buffer once all groups but the latest have been read
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(reinterpret_cast<uint64_t>(mc)), "r"(stageOut), "r"(static_cast<int>(col0)), "r"(rowBase) : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(reinterpret_cast<uint64_t>(mc)), "r"(stageOut + 4096u), "r"(static_cast<int>(col0 + CH)), "r"(rowBase) : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            chunkIt += 2;
           }
         }
       }
@@ -997,9 +1080,18 @@ int gemmTcgen05I8Try(const void *a, const void *b, void *c, int aDtype, int bDty
 // Up to three GEMMs C_i[M, N_i] = A[M, K] B_i[N_i, K]^T that share A (the q / k / v projections of
 // one activation) as ONE launch: their tiles form one list, so the narrow problems fill the SMs
 // the wide one leaves idle in its last wave.  Plain epilogue only.  -1 = not taken.
+// ropeMask != 0: the results of the problems in the mask are rotated in the epilogue (see TcParams::ropeMask).
 int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, const int64_t *n, int count, int abDtype,
-                          int cDtype, int64_t m, int64_t k, cudaStream_t stream) {
+                          int cDtype, int64_t m, int64_t k, cudaStream_t stream, const void *ropeCos, const void *ropeSin,
+                          int ropeMask, int64_t ropeSeq) {
   if (count < 2 || count > 3) return -1;
+  if (ropeMask) {
+    if (!ropeCos || !ropeSin || !aligned16(ropeCos) || !aligned16(ropeSin) || ropeSeq < 1 || ropeSeq > 0x7fffffff) return -1;
+    if (cDtype != abDtype || (ropeMask >> count) != 0) return -1;
+    for (int i = 0; i < count; ++i) {
+      if (((ropeMask >> i) & 1) && n[i] % 128 != 0) return -1;
+    }
+  }
   if (abDtype != kBF16 && abDtype != kF16) return -1;
   if (cDtype != abDtype && cDtype != kF32) return -1;
   if (k % 8 != 0 || m < 1 || k < 8 || m > 0x7fffffff || k > 0x7fffffff || !aligned16(a)) return -1;
@@ -1017,6 +1109,7 @@ int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, c
   {
     int64_t best = -1;
     for (int w : {256, 128, 64}) {
+      if (ropeMask && w < 128) continue; // a head's two halves have to lie in one tile
       int64_t tiles = 0;
       bool fits = true;
       for (int i = 0; i < count; ++i) {
@@ -1059,6 +1152,14 @@ int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, c
   }
   p.fmt = abDtype == kBF16 ? 1 : 0;
   p.kElems = TC_BK; p.aSigned = p.bSigned = 0; p.deq = 0; p.deqScalar = 0.0f; p.deqScale = nullptr;
+  if (ropeMask) {
+    if (bn < 128) return -1; // some problem is narrower than a head
+    p.ropeMask = ropeMask;
+    p.ropeSeq = static_cast<int>(ropeSeq);
+    p.ropeCos = ropeCos;
+    p.ropeSin = ropeSin;
+    bytes += 2.0 * double(ropeSeq) * 128 * 2;
+  }
   ProfScope prof("gemm_tcgen05", flops, bytes, stream);
   const CUtensorMap more[4] = {mb[1], mc[1], mb[2], mc[2]};
 #define TTB_TCG(BNv, TCv)                                                                \

@@ -471,6 +471,8 @@ private:
     std::vector<int64_t> strides; // in elements, over `shape`
   };
   std::unordered_map<uint32_t, LazyView> lazy;
+  // Inputs of rotary_embedding ops whose rotation the producing projection has already applied.
+  std::unordered_set<uint32_t> ropeApplied;
   // Dense strides of a live tensor, or the pending view of `ref`, as {tensor, strides}.
   std::pair<TensorPtr, std::vector<int64_t>> viewOf(const fbt::TensorRef *ref);
 
@@ -497,6 +499,7 @@ private:
   void runIntGemm(const fbt::TensorRef *aRef, const fbt::TensorRef *bRef, const fbt::TensorRef *outRef, bool ta, bool tb,
                   const TensorPtr &deqScale, float deqScalar, const fbt::TensorRef *biasRef = nullptr);
   size_t tryGroupedGemm(size_t i);
+  const fbt::RotaryEmbeddingOp *ropeAfter(const fbt::TensorRef *out) const;
   size_t trySwiglu(size_t i);
   size_t trySiluMul(size_t i);
   size_t trySdpa(size_t i);
@@ -1752,6 +1755,35 @@ size_t Executor::trySwiglu(size_t i) {
   return j3 + 1 - i;
 }
 
+// The rotary_embedding op a projection's result runs into through a head split -- reshape to [batch, seq, heads,
+// 128], permute to [batch, heads, seq, 128] -- every link of the chain the only use of the one before.
+const fbt::RotaryEmbeddingOp *Executor::ropeAfter(const fbt::TensorRef *out) const {
+  auto onlyUser = [&](const fbt::TensorRef *r) -> const fbt::Operation * {
+    if (!singleUse(r)) return nullptr;
+    auto u = info.firstUse.find(r->global_id());
+    return u == info.firstUse.end() ? nullptr : prog->operations()->Get(u->second);
+  };
+  const auto *o1 = onlyUser(out);
+  if (!o1 || o1->type_type() != OpType::ReshapeOp) return nullptr;
+  const auto *rs = o1->type_as_ReshapeOp();
+  if (rs->in()->global_id() != out->global_id()) return nullptr;
+  std::vector<uint32_t> split = refShape(rs->out());
+  if (split.size() != 4 || split[3] != 128) return nullptr;
+  const auto *o2 = onlyUser(rs->out());
+  if (!o2 || o2->type_type() != OpType::PermuteOp) return nullptr;
+  const auto *pm = o2->type_as_PermuteOp();
+  if (!pm->permutation() || pm->permutation()->size() != 4 || pm->permutation()->Get(0) != 0 || pm->permutation()->Get(1) != 2 ||
+      pm->permutation()->Get(2) != 1 || pm->permutation()->Get(3) != 3)
+    return nullptr;
+  const auto *o3 = onlyUser(pm->out());
+  if (!o3 || o3->type_type() != OpType::RotaryEmbeddingOp) return nullptr;
+  const auto *rope = o3->type_as_RotaryEmbeddingOp();
+  if (rope->input()->global_id() != pm->out()->global_id() || rope->token_index().has_value()) return nullptr;
+  if (refDtype(rope->out()) != refDtype(out) || refDtype(rope->cos_cache()) != refDtype(out) || refDtype(rope->sin_cache()) != refDtype(out))
+    return nullptr;
+  return rope;
+}
+
 // Two or three consecutive linear / matmul ops on the same activation (q, k, v projections):
 // no bias, no activation, weights as [N, K] (transpose_b), 16-bit, rank-2 problem after
 // flattening.  They run as one grouped launch.  Ops whose result feeds an elementwise op right
@@ -1828,6 +1860,31 @@ size_t Executor::tryGroupedGemm(size_t i) {
     outs.push_back(out);
     ns.push_back(b->shape[0]);
   }
+  // Projections whose result runs into a rotary embedding (through a head split) leave the kernel rotated: the
+  // embedding op then has nothing left to do.  One table pair per launch; positions are rows mod seq.
+  int ropeMask = 0;
+  const fbt::RotaryEmbeddingOp *ropes[3] = {nullptr, nullptr, nullptr};
+  TensorPtr cosT, sinT;
+  int64_t ropeSeq = 0;
+  if (cDt == abDt) {
+    for (size_t q = 0; q < items.size(); ++q) {
+      const auto *rope = ropeAfter(items[q].out);
+      if (!rope || !pool.count(rope->cos_cache()->global_id()) || !pool.count(rope->sin_cache()->global_id())) continue;
+      if (ropeMask && (rope->cos_cache()->global_id() != ropes[__builtin_ctz(ropeMask)]->cos_cache()->global_id() ||
+                       rope->sin_cache()->global_id() != ropes[__builtin_ctz(ropeMask)]->sin_cache()->global_id()))
+        continue;
+      std::vector<uint32_t> xs = refShape(rope->input()); // [batch, heads, seq, 128]
+      const int64_t seq = xs[2];
+      if (static_cast<int64_t>(xs[0]) * seq != M || static_cast<int64_t>(xs[1]) * 128 != ns[q] || (ropeMask && seq != ropeSeq)) continue;
+      TensorPtr ct = getDevice(rope->cos_cache()), st = getDevice(rope->sin_cache());
+      if (static_cast<int64_t>(ct->volume()) != seq * 128 || static_cast<int64_t>(st->volume()) != seq * 128) continue;
+      cosT = ct;
+      sinT = st;
+      ropeSeq = seq;
+      ropes[q] = rope;
+      ropeMask |= 1 << q;
+    }
+  }
   eachRank([&](size_t r, const RankCtx &rc) {
     const void *bp[3];
     void *cp[3];
@@ -1835,10 +1892,21 @@ size_t Executor::tryGroupedGemm(size_t i) {
       bp[q] = bs[q]->shards[r]->ptr;
       cp[q] = outs[q]->shards[r]->ptr;
     }
+    if (ropeMask) {
+      int rcode = ttb_gemm_grouped_rope(a->shards[r]->ptr, bp, cp, ns.data(), static_cast<int>(items.size()), ttbDtype(abDt), M, K,
+                                        cosT->shards[r]->ptr, sinT->shards[r]->ptr, ropeMask, ropeSeq, 128, rc.stream);
+      if (rcode == TTB_OK) return;
+      // every rank has the same shapes: the first refusal switches the rotation off for all of them
+      TTRT_ASSERT(rcode == TTB_ERR_UNSUPPORTED && r == 0, "ttb_gemm_grouped_rope failed (", rcode, "): ", ttb_last_error());
+      ropeMask = 0;
+    }
     TTB_CALL(ttb_gemm_grouped(a->shards[r]->ptr, bp, cp, ns.data(), static_cast<int>(items.size()), ttbDtype(abDt), ttbDtype(cDt), M,
                               K, rc.stream));
   });
-  for (size_t q = 0; q < items.size(); ++q) put(items[q].out, outs[q]);
+  for (size_t q = 0; q < items.size(); ++q) {
+    put(items[q].out, outs[q]);
+    if ((ropeMask >> q) & 1) ropeApplied.insert(ropes[q]->input()->global_id());
+  }
   runDeallocs(deallocs);
   return last + 1 - i;
 }
@@ -2811,6 +2879,18 @@ void Executor::runSplitQkv(const fbt::SplitQueryKeyValueAndSplitHeadsOp *op) {
 }
 
 void Executor::runRotaryEmbedding(const fbt::RotaryEmbeddingOp *op) {
+  if (ropeApplied.erase(op->input()->global_id())) {
+    // The projection that produced the input stored it rotated: the result is the input (still a pending view).
+    auto lz = lazy.find(op->input()->global_id());
+    if (lz != lazy.end()) {
+      LazyView v = std::move(lz->second);
+      lazy.erase(lz);
+      lazy[op->out()->global_id()] = std::move(v);
+    } else {
+      put(op->out(), getDevice(op->input()));
+    }
+    return;
+  }
   TensorPtr c = getDevice(op->cos_cache()), s = getDevice(op->sin_cache());
   std::vector<uint32_t> xs = refShape(op->input());
   TTRT_ASSERT(xs.size() >= 2, "rotary_embedding expects [..., seq, head_dim]");

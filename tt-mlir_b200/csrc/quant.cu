@@ -49,12 +49,15 @@ __host__ __device__ inline QNarrow narrowOf(QRange r, int zp) {
   n.zp = zp;
   return n;
 }
-__device__ __forceinline__ float roundClampNarrow(float x, float inv, QNarrow n) {
+// Clamping first and rounding second gives what rounding first gives (the bounds are integers, rounding is
+// monotonic and leaves integers alone) and keeps the magic-number rounding inside its exact range without a
+// second clamp: min / max issue on the half-rate ALU pipe, which is what bounded the fused chain.
+// MAYBE_NAN = false: x is known to be a number (a dequantized integer), so the NaN -> 0 step is dropped.
+template <bool MAYBE_NAN = true> __device__ __forceinline__ float roundClampNarrow(float x, float inv, QNarrow n) {
   float t = __fmul_rn(x, inv);
-  t = (t != t) ? 0.0f : t;
-  t = fminf(fmaxf(t, -2097152.0f), 2097152.0f);
-  t = __fsub_rn(__fadd_rn(t, 12582912.0f), 12582912.0f); // nearest integer, ties to even
-  return fminf(fmaxf(t, n.lo), n.hi);
+  if (MAYBE_NAN) t = (t != t) ? 0.0f : t;
+  t = fminf(fmaxf(t, n.lo), n.hi);
+  return __fsub_rn(__fadd_rn(t, 12582912.0f), 12582912.0f); // nearest integer, ties to even
 }
 // integer-valued float in (-2^22, 2^22) -> int without a conversion instruction
 __device__ __forceinline__ int floatIntBits(float r) { return __float_as_int(__fadd_rn(r, 12582912.0f)) - 0x4B400000; }
@@ -156,7 +159,7 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
       for (int j = 0; j < kVec; ++j) {
         float ra = roundClampNarrow(toF32(x.v[j]), inv1, n1);             // q1 - zp1
-        float rb = roundClampNarrow(__fmul_rn(ra, s1), inv2, n2);          // q2 - zp2
+        float rb = roundClampNarrow<false>(__fmul_rn(ra, s1), inv2, n2);   // q2 - zp2
         if (W1) a.v[j] = static_cast<T1>(floatIntBits(ra) + zp1);
         if (W2) b.v[j] = static_cast<T2>(floatIntBits(rb) + zp2);
         y.v[j] = fromF32<TO>(__fmul_rn(rb, s2));
@@ -400,7 +403,7 @@ int ttb_quant_chain(const void *in, int in_dtype, void *q1, int q1_dtype, void *
                     int out_dtype, size_t n, float scale1, int32_t zp1, float scale2, int32_t zp2,
                     int clamp_i8, void *stream) {
   TTB_CHECK(in && out, "null tensor");
-  TTB_CHECK(scale1 > 0.0f && scale2 > 0.0f, "scale must be positive");
+  TTB_CHECK(scale1 > 0.0f && scale2 > 0.0f && scale1 <= 3.0e38f && scale2 <= 3.0e38f, "scale must be positive and finite");
   TTB_CHECK(vecOk(in, out) && aligned16(q1) && aligned16(q2), "tensors must be 16-byte aligned");
   TTB_CHECK(q1_dtype == q2_dtype, "intermediate dtypes must match");
   if (n == 0) return TTB_OK;

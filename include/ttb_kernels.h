@@ -357,6 +357,17 @@ TTB_API int ttb_gemm_grouped_rope(const void *a, const void *const *b, void *con
                                   int dtype, int64_t m, int64_t k, const void *cos, const void *sin, int rope_mask,
                                   int64_t seq, int64_t head_dim, void *stream);
 
+/* out[m, n] = act(round(a1 * b1^T + bias1) + round(a2 * b2^T + bias2)), act = TTB_ACT_NONE or TTB_ACT_RELU: two
+ * products that share their shape [m, n] (a1 [m, k1], b1 [n, k1]; a2 [m, k2], b2 [n, k2]; 16-bit, row-major; biases
+ * [n] in `bias_dtype`, nullable), each rounded to `dtype` with its bias as its own op rounds it, then added, rounded
+ * and activated -- a pointwise convolution plus the pointwise projection of its residual branch as one launch.
+ * Bit-equal to ttb_gemm(a2, b2, bias2) followed by ttb_gemm_fused(a1, b1, bias1, extra = that, TTB_EXTRA_ADD[_RELU]).
+ * TTB_ERR_UNSUPPORTED when the tensor-core kernel does not take the problem: run the ops one by one then.
+ * No reference counterpart (two ::ttnn::conv2d calls, ::ttnn::add, ::ttnn::relu; operations/conv/conv2d.cpp:16-94). */
+TTB_API int ttb_gemm_dual_add(const void *a1, const void *b1, const void *bias1, const void *a2, const void *b2,
+                              const void *bias2, void *out, int dtype, int bias_dtype, int64_t m, int64_t n, int64_t k1,
+                              int64_t k2, int act, void *stream);
+
 /* ttb_gemm with a second, full-size epilogue operand `extra` ([batch, m, n], dense, in
  * `c_dtype`), combined with the result of the bias / activation chain the way separate ops
  * would (the chain's result is rounded to `c_dtype` first):

@@ -181,6 +181,48 @@ def test_gemm_grouped_matches_separate_calls(rt, device, m, k, ns):
         assert_matches(g, (a.float() @ b.float().t()).to(torch.bfloat16), "grouped gemm")
 
 
+@pytest.mark.parametrize("m,n,k1,k2,act,biases", [(200704 // 8, 256, 64, 64, 1, True), (300, 136, 72, 264, 0, True),
+                                                   (1024, 64, 128, 64, 1, False), (130, 512, 64, 576, 1, True)])
+def test_gemm_dual_add_equals_the_chain_of_launches(rt, device, m, n, k1, k2, act, biases):
+    """ttb_gemm_dual_add (two products in two accumulators of one launch, summed in the epilogue) gives bit for bit
+    what the second product as its own launch followed by the first with the residual-add epilogue gives, and what
+    the f32 reference of the op chain with its bf16 roundings gives within tolerance."""
+    torch.manual_seed(m + n + k1)
+    a1 = torch.randn(m, k1).to(torch.bfloat16)
+    a2 = torch.randn(m, k2).to(torch.bfloat16)
+    b1 = (torch.randn(n, k1) * 0.1).to(torch.bfloat16)
+    b2 = (torch.randn(n, k2) * 0.1).to(torch.bfloat16)
+    bias1 = torch.randn(n).to(torch.bfloat16) if biases else None
+    bias2 = torch.randn(n).to(torch.bfloat16) if biases else None
+    h = KernelHarness(rt)
+    try:
+        i64 = ctypes.c_int64
+        d = {k: h.upload(v) for k, v in dict(a1=a1, a2=a2, b1=b1, b2=b2).items()}
+        db1 = h.upload(bias1) if biases else None
+        db2 = h.upload(bias2) if biases else None
+        out = h.empty((m, n), torch.bfloat16)
+        rc = h.lib.ttb_gemm_dual_add(d["a1"], d["b1"], db1, d["a2"], d["b2"], db2, out, BF16, BF16, i64(m), i64(n), i64(k1), i64(k2),
+                                     act, h.stream)
+        assert rc == 0, h.lib.ttb_last_error().decode()
+        got = h.download(out, (m, n), torch.bfloat16)
+        assert tc_status(h) == 0
+        second = h.empty((m, n), torch.bfloat16)
+        assert h.lib.ttb_gemm(d["a2"], d["b2"], db2, second, BF16, BF16, BF16, i64(1), i64(m), i64(n), i64(k2), 0, 1, i64(0), i64(0),
+                              0, 0, h.stream) == 0
+        chain = h.empty((m, n), torch.bfloat16)
+        assert h.lib.ttb_gemm_fused(d["a1"], d["b1"], db1, chain, BF16, BF16, BF16, i64(1), i64(m), i64(n), i64(k1), 0, 1, i64(0),
+                                    i64(0), 0, 0, second, 3 if act else 1, h.stream) == 0
+        want_chain = h.download(chain, (m, n), torch.bfloat16)
+    finally:
+        h.close()
+    assert torch.equal(got, want_chain), f"{(got != want_chain).sum().item()} of {got.numel()} elements differ from the chain"
+    v1 = (a1.float() @ b1.float().t() + (bias1.float() if biases else 0)).to(torch.bfloat16)
+    v2 = (a2.float() @ b2.float().t() + (bias2.float() if biases else 0)).to(torch.bfloat16)
+    ref = (v1.float() + v2.float())
+    ref = (torch.relu(ref) if act else ref).to(torch.bfloat16)
+    assert_matches(got, ref, "dual add")
+
+
 @pytest.mark.parametrize("batch,seq,k,ns,mask", [(1, 2048, 4096, (4096, 1024, 1024), 3), (2, 200, 264, (256, 128, 128), 3),
                                                  (1, 512, 512, (512, 128, 128), 2), (1, 300, 128, (128, 384), 1)])
 def test_gemm_grouped_with_rotary_embedding_epilogue(rt, device, batch, seq, k, ns, mask):

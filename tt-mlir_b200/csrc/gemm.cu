@@ -14,6 +14,9 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
                    void *const *pushTargets = nullptr, int pushRanks = 0);
 int gemmTcgen05SwigluTry(const void *a, const void *wGate, const void *wUp, void *out, int dtype, int64_t m, int64_t n,
                          int64_t k, cudaStream_t stream);
+int gemmTcgen05DualTry(const void *a1, const void *b1, const void *bias1, const void *a2, const void *b2, const void *bias2,
+                       void *out, int dtype, int biasDtype, int64_t m, int64_t n, int64_t k1, int64_t k2, int act,
+                       cudaStream_t stream);
 int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, const int64_t *n, int count, int abDtype,
                           int cDtype, int64_t m, int64_t k, cudaStream_t stream, const void *ropeCos = nullptr,
                           const void *ropeSin = nullptr, int ropeMask = 0, int64_t ropeSeq = 1);
@@ -88,6 +91,24 @@ extern "C" int ttb_gemm_grouped_rope(const void *a, const void *const *b, void *
     if (rc != -1) return rc;
   }
   ttb::setLastError("gemm_grouped_rope: shape, type or alignment not taken by the tensor-core kernel");
+  return TTB_ERR_UNSUPPORTED;
+}
+
+// out[M, N] = act(round(A1 B1^T + bias1) + round(A2 B2^T + bias2)): two linear ops (or pointwise convolutions) with
+// their biases, the add of their results and an optional relu, every intermediate rounded to `dtype` as the chain of
+// separate ops rounds it, in one launch in which neither product reaches memory.  Only the tensor-core kernel has
+// this mode: TTB_ERR_UNSUPPORTED tells the caller to run the ops one by one.
+extern "C" int ttb_gemm_dual_add(const void *a1, const void *b1, const void *bias1, const void *a2, const void *b2,
+                                 const void *bias2, void *out, int dtype, int bias_dtype, int64_t m, int64_t n, int64_t k1,
+                                 int64_t k2, int act, void *stream) {
+  TTB_CHECK(a1 && b1 && a2 && b2 && out, "null tensor");
+  TTB_CHECK(m >= 0 && n >= 0 && k1 >= 0 && k2 >= 0, "negative dimension");
+  if (m * n == 0) return TTB_OK;
+  if (!tcgen05Disabled()) {
+    int rc = ttb::gemmTcgen05DualTry(a1, b1, bias1, a2, b2, bias2, out, dtype, bias_dtype, m, n, k1, k2, act, ttb::asStream(stream));
+    if (rc != -1) return rc;
+  }
+  ttb::setLastError("gemm_dual_add: shape, type or alignment not taken by the tensor-core kernel");
   return TTB_ERR_UNSUPPORTED;
 }
 

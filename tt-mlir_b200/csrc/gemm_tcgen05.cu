@@ -130,6 +130,14 @@ struct TcParams {
   int ropeMask = 0;
   int ropeSeq = 1;
   const void *ropeCos = nullptr, *ropeSin = nullptr;
+  // Two products into one result (BN <= 128, 16-bit output): C = act(round(A B^T + bias) + round(A2 B2^T + bias2)) --
+  // a convolution and the projection convolution of its residual branch, each rounded as its own op rounds it, the sum
+  // rounded as the add that follows them.  A2 [M, K2] comes through mapE, B2 [N, K2] through mapB1; a tile's k-blocks
+  // are those of the first product followed by those of the second, which accumulates BN columns further on in TMEM.
+  int dualA = 0;
+  int64_t K2 = 0;
+  const void *bias2 = nullptr;
+  int bias2Dt = 0;
 };
 
 struct PushMaps {
@@ -173,7 +181,9 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     n0 = static_cast<int>(nt - (seg == 0 ? 0 : p.segCum[seg - 1])) * (p.dual ? BN / 2 : BN);
     return seg;
   };
-  const int kBlocks = static_cast<int>((p.K + p.kElems - 1) / p.kElems);
+  const int kBlocks1 = static_cast<int>((p.K + p.kElems - 1) / p.kElems);
+  const int kBlocks = kBlocks1 + (p.dualA ? static_cast<int>((p.K2 + p.kElems - 1) / p.kElems) : 0);
+  const uint32_t accCols = p.dualA ? 2u * BN : static_cast<uint32_t>(BN); // TMEM columns of one accumulator buffer
 
   if (threadIdx.x == 0) {
     abortFlagS = 0;
@@ -319,9 +329,11 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
             // rows and rank 1 the up rows of the same output columns).
             const uint32_t bar = mapToCta(fullBar(s), 0);
             if (leader) mbarArriveExpectTx(fullBar(s), 2 * Cfg::kStageBytes);
-            tmaLoad2dPair(sa, &mapA, bar, kb * p.kElems, m0);
-            if (p.dual) tmaLoad2dPair(sb, leader ? &mapB : &mapB1, bar, kb * p.kElems, n0);
-            else tmaLoad2dPair(sb, mb, bar, kb * p.kElems, n0 + static_cast<int>(ctaRank) * (BN / 2));
+            const bool second = p.dualA && kb >= kBlocks1; // k-blocks of the second product
+            const int kc = (second ? kb - kBlocks1 : kb) * p.kElems;
+            tmaLoad2dPair(sa, second ? &mapE : &mapA, bar, kc, m0);
+            if (p.dual) tmaLoad2dPair(sb, leader ? &mapB : &mapB1, bar, kc, n0);
+            else tmaLoad2dPair(sb, second ? &mapB1 : mb, bar, kc, n0 + static_cast<int>(ctaRank) * (BN / 2));
             continue;
           }
           mbarArriveExpectTx(fullBar(s), Cfg::kStageBytes);
@@ -329,12 +341,16 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
             // the input patch of this filter tap; coordinates left of / above the image read zeros
             const int tap = kb / cb, ky = tap / p.ckw, kx = tap - ky * p.ckw;
             tmaLoad4d(sa, &mapA, fullBar(s), (kb - tap * cb) * TC_BK, ox0 + kx * p.cdw - p.cpl, oy0 + ky * p.cdh - p.cpt, img);
+          } else if (p.dualA && kb >= kBlocks1) {
+            tmaLoad2d(sa, &mapE, fullBar(s), (kb - kBlocks1) * p.kElems, m0);
           } else {
             tmaLoad2d(sa, &mapA, fullBar(s), kb * p.kElems, m0);
           }
           if (p.dual) {
             tmaLoad2d(sb, &mapB, fullBar(s), kb * TC_BK, n0);
             tmaLoad2d(sb + (BN / 2) * TC_BK * 2, &mapB1, fullBar(s), kb * TC_BK, n0);
+          } else if (p.dualA && kb >= kBlocks1) {
+            tmaLoad2d(sb, &mapB1, fullBar(s), (kb - kBlocks1) * p.kElems, n0);
           } else {
             tmaLoad2d(sb, mb, fullBar(s), kb * p.kElems, n0);
           }
@@ -353,8 +369,11 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
         const uint32_t accPhase = (accIt >> 1) & 1u;
         if (!mbarWait(tmemEmptyBar(acc), accPhase ^ 1u, abortFlag, 2)) break;
         tcFenceAfter();
-        const uint32_t tmemD = tmemBase + static_cast<uint32_t>(acc * BN);
+        const uint32_t tmemD0 = tmemBase + static_cast<uint32_t>(acc) * accCols;
         for (int kb = 0; kb < kBlocks; ++kb, ++it) {
+          const bool second = p.dualA && kb >= kBlocks1;
+          const uint32_t tmemD = tmemD0 + (second ? static_cast<uint32_t>(BN) : 0u);
+          const int kbIn = second ? kb - kBlocks1 : kb; // the first MMA of a product overwrites the accumulator
           const int s = it % STAGES;
           const uint32_t phase = (it / STAGES) & 1u;
           if (!mbarWait(fullBar(s), phase, abortFlag, 3)) { alive = false; break; }
@@ -365,11 +384,11 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
           for (int k = 0; k < TC_BK / 16; ++k) {
             // +32 bytes per k-step (16 two-byte or 32 one-byte elements) = +2 in the descriptor's 16-byte address units
             if constexpr (PAIR) {
-              if (ints) tcMmaPairI8(tmemD, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
-              else tcMmaPair(tmemD, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              if (ints) tcMmaPairI8(tmemD, da + 2u * k, db + 2u * k, idesc, (kbIn | k) != 0 ? 1u : 0u);
+              else tcMmaPair(tmemD, da + 2u * k, db + 2u * k, idesc, (kbIn | k) != 0 ? 1u : 0u);
             } else {
-              if (ints) tcMmaI8(tmemD, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
-              else tcMma(tmemD, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              if (ints) tcMmaI8(tmemD, da + 2u * k, db + 2u * k, idesc, (kbIn | k) != 0 ? 1u : 0u);
+              else tcMma(tmemD, da + 2u * k, db + 2u * k, idesc, (kbIn | k) != 0 ? 1u : 0u);
             }
           }
           // frees the stage (in both CTAs of a pair) once these MMAs have read it
@@ -463,7 +482,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
         pOy = (rem / p.cTilesX) * (TC_BM / p.cTw) + quarter * (32 / p.cTw);
         pOx = (rem % p.cTilesX) * p.cTw;
       }
-      const uint32_t taddrRow = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      const uint32_t taddrRow = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * accCols;
       // SwiGLU mode: two chunks of 64 output columns; gate in accumulator columns [0, 128), up in [128, 256).
       bool dualDone = false;
       if constexpr (!PLAIN && sizeof(TC) == 2 && BN == 256) {
@@ -502,6 +521,65 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
                 }
                 const int pieceIdx = l * 4 + v;
                 const uint32_t addr = rowAddr + (static_cast<uint32_t>(pieceIdx ^ (lane & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+              }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(reinterpret_cast<uint64_t>(mc)), "r"(buf), "r"(static_cast<int>(col0)), "r"(rowBase)
+                           : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            ++chunkIt;
+          }
+        }
+      }
+      if constexpr (!PLAIN && sizeof(TC) == 2 && BN <= 128) {
+        if (p.dualA) {
+          // Two products: columns [0, BN) and [BN, 2 BN) of the buffer; each gets its bias and its own rounding, the
+          // sum is rounded again, relu (if any) commutes with that rounding and is applied to the packed pairs.
+          dualDone = true;
+          const bool relu = p.act == TTB_ACT_RELU;
+#pragma unroll 1
+          for (int cc = (shared && helper) ? 1 : 0; cc < BN / CH; cc += shared ? 2 : 1) {
+            const int64_t col0 = n0 + cc * CH;
+            if (col0 >= segN) break; // warp-uniform
+            const uint32_t buf = stageOut;
+            const uint32_t rowAddr = buf + static_cast<uint32_t>(lane) * 128u;
+#pragma unroll
+            for (int l = 0; l < 2; ++l) {
+              const int64_t colH = col0 + l * 32;
+              float b1 = 0.0f, b2 = 0.0f;
+              if (colH + lane < p.N) {
+                if (p.bias) b1 = loadBias(p.bias, p.biasDt, colH + lane);
+                if (p.bias2) b2 = loadBias(p.bias2, p.bias2Dt, colH + lane);
+              }
+              uint32_t r1[32], r2[32];
+              tcLoad32(taddrRow + static_cast<uint32_t>(cc * CH + l * 32), r1);
+              tcLoad32(taddrRow + static_cast<uint32_t>(BN + cc * CH + l * 32), r2);
+              tcWaitLd();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                const float v1 = toF32(fromF32<TC>(__fadd_rn(__uint_as_float(r1[e]), __shfl_sync(0xffffffffu, b1, e))));
+                const float v2 = toF32(fromF32<TC>(__fadd_rn(__uint_as_float(r2[e]), __shfl_sync(0xffffffffu, b2, e))));
+                r1[e] = __float_as_uint(__fadd_rn(v1, v2));
+              }
+              if (l == 0) {
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); // the last store has read the buffer
+                __syncwarp();
+              }
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const int e = v * 8 + q * 2;
+                  w[q] = pack2<TC>(__uint_as_float(r1[e]), __uint_as_float(r1[e + 1]));
+                  if (relu) w[q] = relu2<TC>(w[q]);
+                }
+                const uint32_t addr = rowAddr + (static_cast<uint32_t>((l * 4 + v) ^ (lane & 7)) << 4);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
               }
             }
@@ -834,14 +912,21 @@ static bool makeMap4(CUtensorMap *map, const void *ptr, int dtype, int64_t c, in
   return r == CUDA_SUCCESS;
 }
 
-// Two CTAs per 256-row tile (cta_group::2) unless switched off (TTB_DISABLE_PAIR_MMA=1) or the problem has
-// fewer than 256 rows; convolutions keep one CTA per tile.
-static bool pairMmaWanted(int64_t m) {
+// Two CTAs per 256-row tile (cta_group::2) unless switched off (TTB_DISABLE_PAIR_MMA=1), the problem has fewer than
+// 256 rows, or the reduction is short: with a handful of k-blocks per tile the hand-overs between the two CTAs
+// (operands landed, stage free, accumulator full / drained all cross the pair) are no longer hidden behind the main
+// loop, and one CTA per tile is faster (pointwise convolutions with K = 64: 54 against 61 us per launch).
+// Convolutions with a gathered operand keep one CTA per tile.
+static bool pairMmaWanted(int64_t m, int64_t k) {
   static const bool off = [] {
     const char *e = std::getenv("TTB_DISABLE_PAIR_MMA");
     return e && e[0] == '1';
   }();
-  return !off && m >= 2 * TC_BM && smCount() >= 2;
+  static const int64_t minK = [] {
+    const char *e = std::getenv("TTB_PAIR_MMA_MIN_K");
+    return e ? static_cast<int64_t>(atoll(e)) : static_cast<int64_t>(512);
+  }();
+  return !off && m >= 2 * TC_BM && k >= minK && smCount() >= 2;
 }
 
 template <int BN, typename TC, bool PLAIN, bool PAIR = false>
@@ -934,7 +1019,7 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff) return -1;
   // Tiny problems are launch-bound either way; keep them on the simple kernel.
   if (m * n * k < (1ll << 18)) return -1;
-  const bool pair = pairMmaWanted(m);
+  const bool pair = pairMmaWanted(m, k);
   const int bn = pickTileWidth(m, n, pair ? 2 * TC_BM : TC_BM, pair ? smCount() / 2 : smCount());
   CUtensorMap ma, mb, mc, me;
   if (!makeMap(&ma, a, abDtype, m, k, TC_BM) || !makeMap(&mb, b, abDtype, n, k, pair ? bn / 2 : bn) ||
@@ -1016,12 +1101,59 @@ int gemmTcgen05SwigluTry(const void *a, const void *wGate, const void *wUp, void
   // both projections' FLOPs; A and both weights once, the result once
   ProfScope prof("gemm_tcgen05", 4.0 * double(m) * double(n) * double(k), (double(m) * k + 2.0 * double(n) * k + double(m) * n) * 2, stream);
   const CUtensorMap more[4] = {mu, mc, mu, mc};
-  if (pairMmaWanted(m)) {
+  if (pairMmaWanted(m, k)) {
     if (dtype == kBF16) return launchTc<BN, __nv_bfloat16, false, true>(ma, mg, mc, mc, out, p, stream, more);
     return launchTc<BN, __half, false, true>(ma, mg, mc, mc, out, p, stream, more);
   }
   if (dtype == kBF16) return launchTc<BN, __nv_bfloat16, false>(ma, mg, mc, mc, out, p, stream, more);
   return launchTc<BN, __half, false>(ma, mg, mc, mc, out, p, stream, more);
+}
+
+// out[M, N] = act(round(A1 B1^T + bias1) + round(A2 B2^T + bias2)) as ONE launch (two-product mode of the kernel):
+// a pointwise convolution and the pointwise projection of its residual branch, summed and activated, without
+// either product reaching memory.  B1: [N, K1], B2: [N, K2]; biases nullable; act none or relu.  -1 = not taken.
+int gemmTcgen05DualTry(const void *a1, const void *b1, const void *bias1, const void *a2, const void *b2, const void *bias2,
+                       void *out, int dtype, int biasDtype, int64_t m, int64_t n, int64_t k1, int64_t k2, int act,
+                       cudaStream_t stream) {
+  if (dtype != kBF16 && dtype != kF16) return -1;
+  if (act != TTB_ACT_NONE && act != TTB_ACT_RELU) return -1;
+  if (k1 % 8 != 0 || k2 % 8 != 0 || n % 8 != 0 || m < 1 || n < 8 || k1 < 8 || k2 < 8) return -1;
+  if (!aligned16(a1) || !aligned16(b1) || !aligned16(a2) || !aligned16(b2) || !aligned16(out)) return -1;
+  if (m > 0x7fffffff || n > 0x7fffffff || k1 > 0x7fffffff || k2 > 0x7fffffff) return -1;
+  if (m * n * (k1 + k2) < (1ll << 18)) return -1;
+  const bool pair = pairMmaWanted(m, k1 < k2 ? k1 : k2);
+  const int bn = n >= 128 ? 128 : 64; // two accumulators of BN columns, double buffered, in 512 TMEM columns
+  CUtensorMap ma1, mb1, ma2, mb2, mc;
+  if (!makeMap(&ma1, a1, dtype, m, k1, TC_BM) || !makeMap(&mb1, b1, dtype, n, k1, pair ? bn / 2 : bn) ||
+      !makeMap(&ma2, a2, dtype, m, k2, TC_BM) || !makeMap(&mb2, b2, dtype, n, k2, pair ? bn / 2 : bn) ||
+      !makeMap(&mc, out, dtype, m, n, 32))
+    return -1;
+  TcParams p;
+  p.M = m; p.N = n; p.K = k1;
+  p.bias = bias1; p.biasDt = biasDtype; p.act = act; p.roundSteps = 0;
+  p.extra = nullptr; p.extraOp = 0;
+  p.convX = nullptr; p.cTw = 0; p.cTilesM = 0; p.pushRows = 0; p.dual = 0;
+  p.segCum[0] = p.segCum[1] = p.segCum[2] = static_cast<int>((n + bn - 1) / bn);
+  p.segN[0] = p.segN[1] = p.segN[2] = n;
+  p.fmt = dtype == kBF16 ? 1 : 0;
+  p.kElems = TC_BK; p.aSigned = p.bSigned = 0; p.deq = 0; p.deqScalar = 0.0f; p.deqScale = nullptr;
+  p.dualA = 1;
+  p.K2 = k2;
+  p.bias2 = bias2;
+  p.bias2Dt = biasDtype;
+  ProfScope prof("gemm_tcgen05", 2.0 * double(m) * double(n) * double(k1 + k2),
+                 (double(m) * (k1 + k2) + double(n) * (k1 + k2) + double(m) * n) * 2, stream);
+  const CUtensorMap more[4] = {mb2, mc, mb2, mc};
+#define TTB_TCD(BNv, TCv)                                                                \
+  if (pair) return launchTc<BNv, TCv, false, true>(ma1, mb1, mc, ma2, out, p, stream, more); \
+  return launchTc<BNv, TCv, false>(ma1, mb1, mc, ma2, out, p, stream, more)
+  if (bn == 128) {
+    if (dtype == kBF16) { TTB_TCD(128, __nv_bfloat16); }
+    TTB_TCD(128, __half);
+  }
+  if (dtype == kBF16) { TTB_TCD(64, __nv_bfloat16); }
+  TTB_TCD(64, __half);
+#undef TTB_TCD
 }
 
 // Quantized contraction: C[M, N] = A[M, K] B[N, K]^T with 8-bit integer operands and exact 32-bit
@@ -1038,7 +1170,7 @@ int gemmTcgen05I8Try(const void *a, const void *b, void *c, int aDtype, int bDty
   if (!aligned16(a) || !aligned16(b) || !aligned16(c) || (deqScale && (reinterpret_cast<uintptr_t>(deqScale) & 3))) return -1;
   if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff) return -1;
   if (m * n * k < (1ll << 18)) return -1;
-  const bool pair = pairMmaWanted(m);
+  const bool pair = pairMmaWanted(m, k);
   const int bn = pickTileWidth(m, n, pair ? 2 * TC_BM : TC_BM, pair ? smCount() / 2 : smCount());
   CUtensorMap ma, mb, mc;
   if (!makeMap(&ma, a, kU8, m, k, TC_BM) || !makeMap(&mb, b, kU8, n, k, pair ? bn / 2 : bn) || !makeMap(&mc, c, cDtype, m, n, 32)) return -1;
@@ -1102,7 +1234,7 @@ int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, c
     nSum += n[i];
   }
   if (m * nSum * k < (1ll << 18)) return -1;
-  const bool pair = pairMmaWanted(m);
+  const bool pair = pairMmaWanted(m, k);
   const int64_t tileM = pair ? 2 * TC_BM : TC_BM;
   const int workers = pair ? smCount() / 2 : smCount();
   int bn = 64;

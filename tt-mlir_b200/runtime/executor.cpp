@@ -535,6 +535,7 @@ private:
   void runConv2d(const fbt::Conv2dOp *op, int act = 0, const fbt::TensorRef *extra = nullptr, int extraOp = 0,
                  const fbt::TensorRef *outRef = nullptr);
   size_t tryConvEpilogue(size_t i);
+  size_t tryPointwisePair(size_t i);
   void runSoftmax(const fbt::SoftmaxOp *op);
   void runRmsNorm(const fbt::RMSNormOp *op);
   void runReduction(const fbt::ReductionOp *op);
@@ -2021,6 +2022,92 @@ size_t Executor::tryQuantizedConv(size_t i) {
   return j + 1 - i;
 }
 
+// pointwise conv2d ; pointwise conv2d (the projection of the residual branch) ; add of the two [-> relu]: the end of a
+// bottleneck block.  Both convolutions are plain products over the channel dimension, so they run as one launch with
+// two accumulators; each product is rounded with its bias as its own op rounds it, the sum as the add does.
+size_t Executor::tryPointwisePair(size_t i) {
+  const auto *ops = prog->operations();
+  const auto *c1 = ops->Get(static_cast<uint32_t>(i))->type_as_Conv2dOp();
+  DataType dt = refDtype(c1->out());
+  if (dt != DataType::BFloat16 && dt != DataType::Float16) return 0;
+  auto pointwise = [&](const fbt::Conv2dOp *c) {
+    auto all = [](const fb::Vector<int32_t> *v, int want) {
+      if (!v) return false;
+      for (int32_t e : *v) {
+        if (e != want) return false;
+      }
+      return v->size() > 0;
+    };
+    return all(c->kernel_size(), 1) && all(c->stride(), 1) && all(c->padding(), 0) && c->groups() == 1 &&
+           refDtype(c->input()) == dt && refDtype(c->weight()) == dt && refDtype(c->out()) == dt &&
+           (!c->bias() || refDtype(c->bias()) == dt) && pool.count(c->input()->global_id()) &&
+           pool.count(c->weight()->global_id()) && (!c->bias() || pool.count(c->bias()->global_id()));
+  };
+  if (!pointwise(c1) || !singleUse(c1->out())) return 0;
+  std::vector<const fbt::Operation *> deallocs;
+  size_t j = i + 1;
+  const auto *op2 = peek(j, deallocs);
+  if (!op2 || op2->type_type() != OpType::Conv2dOp) return 0;
+  const auto *c2 = op2->type_as_Conv2dOp();
+  if (!pointwise(c2) || !singleUse(c2->out()) || refShape(c2->out()) != refShape(c1->out())) return 0;
+  if (c1->batch_size() != c2->batch_size() || c1->input_height() != c2->input_height() || c1->input_width() != c2->input_width() ||
+      c1->out_channels() != c2->out_channels())
+    return 0;
+  // (deallocations between the ops run after the launch: an operand of the first convolution may be among them)
+  size_t j2 = j + 1;
+  const auto *op3 = peek(j2, deallocs);
+  if (!op3 || op3->type_type() != OpType::EltwiseBinaryOp) return 0;
+  const auto *add = op3->type_as_EltwiseBinaryOp();
+  if (add->type() != fbt::EltwiseBinaryOpType::Add) return 0;
+  const uint32_t l = add->lhs()->global_id(), r = add->rhs()->global_id(), id1 = c1->out()->global_id(), id2 = c2->out()->global_id();
+  if (!((l == id1 && r == id2) || (l == id2 && r == id1))) return 0;
+  if (refShape(add->out()) != refShape(c1->out()) || refDtype(add->out()) != dt) return 0;
+  const fbt::TensorRef *cur = add->out();
+  size_t last = j2;
+  int act = TTB_ACT_NONE;
+  if (singleUse(cur)) {
+    std::vector<const fbt::Operation *> d3;
+    size_t j3 = j2 + 1;
+    const auto *op4 = peek(j3, d3);
+    if (op4 && op4->type_type() == OpType::EltwiseUnaryOp) {
+      const auto *u = op4->type_as_EltwiseUnaryOp();
+      if (u->type() == fbt::EltwiseUnaryOpType::Relu && u->in()->global_id() == cur->global_id() && refShape(u->out()) == refShape(cur) &&
+          refDtype(u->out()) == dt) {
+        act = TTB_ACT_RELU;
+        cur = u->out();
+        last = j3;
+        deallocs.insert(deallocs.end(), d3.begin(), d3.end());
+      }
+    }
+  }
+  TensorPtr x1 = getDevice(c1->input()), w1 = getDevice(c1->weight()), x2 = getDevice(c2->input()), w2 = getDevice(c2->weight());
+  TensorPtr b1 = c1->bias() ? getDevice(c1->bias()) : nullptr, b2 = c2->bias() ? getDevice(c2->bias()) : nullptr;
+  const int64_t M = static_cast<int64_t>(c1->batch_size()) * c1->input_height() * c1->input_width(), O = c1->out_channels();
+  const int64_t K1 = c1->in_channels(), K2 = c2->in_channels();
+  if (static_cast<int64_t>(x1->volume()) != M * K1 || static_cast<int64_t>(x2->volume()) != M * K2 ||
+      static_cast<int64_t>(w1->volume()) != O * K1 || static_cast<int64_t>(w2->volume()) != O * K2 ||
+      (b1 && static_cast<int64_t>(b1->volume()) != O) || (b2 && static_cast<int64_t>(b2->volume()) != O))
+    return 0;
+  TensorPtr out = allocOut(cur);
+  if (static_cast<int64_t>(out->volume()) != M * O) return 0;
+  bool taken = true;
+  eachRank([&](size_t rk, const RankCtx &rc) {
+    if (!taken) return;
+    int rcode = ttb_gemm_dual_add(x1->shards[rk]->ptr, w1->shards[rk]->ptr, b1 ? b1->shards[rk]->ptr : nullptr, x2->shards[rk]->ptr,
+                                  w2->shards[rk]->ptr, b2 ? b2->shards[rk]->ptr : nullptr, out->shards[rk]->ptr, ttbDtype(dt),
+                                  ttbDtype(dt), M, O, K1, K2, act, rc.stream);
+    if (rcode == TTB_ERR_UNSUPPORTED && rk == 0) {
+      taken = false; // every rank has the same shapes: the ops run one by one
+      return;
+    }
+    TTRT_ASSERT(rcode == TTB_OK, "ttb_gemm_dual_add failed (", rcode, "): ", ttb_last_error());
+  });
+  if (!taken) return 0;
+  put(cur, out);
+  runDeallocs(deallocs);
+  return last + 1 - i;
+}
+
 // conv2d [-> relu], or conv2d -> add(tensor) [-> relu] (a residual branch), intermediates
 // single-use.  relu commutes with the rounding of the op before it, so the fused launch gives
 // the same bits as the chain.
@@ -2030,6 +2117,7 @@ size_t Executor::tryConvEpilogue(size_t i) {
   const fbt::TensorRef *cur = op->out();
   DataType dt = refDtype(cur);
   if (!singleUse(cur)) return 0;
+  if (size_t used = tryPointwisePair(i)) return used;
   std::vector<const fbt::Operation *> deallocs;
   size_t next = i + 1, consumedUpTo = i;
   int act = TTB_ACT_NONE, extraOp = TTB_EXTRA_NONE;

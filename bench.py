@@ -9,8 +9,18 @@ tt::runtime::submit on 1..8 B200s (tensor parallel over a 1xN mesh, one process 
 Prints one JSON line (rank 0).  `value` is decoder-block tokens/s with all inputs resident in
 HBM; `e2e` is the same through the public API with the step's activations coming from pinned
 host memory and the result copied back.  `roofline` describes the dominant kernel (the tcgen05
-GEMM) from per-launch CUDA events; `per_op` lists every kernel family the block launches.
+GEMM) from per-launch CUDA events, against the burst bf16 peak when the timed region is shorter
+than a second (`frac_of_sustained` beside it) and with the DRAM traffic read from the committed
+ncu summary; `per_op` lists every kernel family the block launches; `clocks` are NVML samples taken
+while the timed region runs.  After the timed loops the output of the program that was timed is
+compared with the CPU oracle (`parity`; at N > 1 also a digest comparison across ranks) and the
+process exits 3 if that fails.  At N = 1 `extra_workloads` adds one line per other benchmark
+configuration (f32 MLP, quantization chain, weight-quantized linear, bottleneck block).
 Inputs are synthetic (seeded), weights random-init, as the benchmark configuration states.
+
+    --no-parity / --no-extra / --no-cpu-baseline   skip those parts
+    --workload <name>                               time another configuration as the main line
+    --profile                                       exactly --warmup + --steps passes, for runs under ncu
 """
 
 from __future__ import annotations

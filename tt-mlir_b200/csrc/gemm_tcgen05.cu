@@ -9,7 +9,8 @@
 //               straight from shared-memory descriptors into TMEM; owns the TMEM allocation
 //   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32 TMEM lanes), add bias,
 //               apply the activation / rounding points, stage 32 x 128 B blocks in shared
-//               memory and write them out with TMA stores (full lines, tails clipped)
+//               memory (two buffers per warp) and write them out with TMA stores (full lines,
+//               tails clipped); kernels with a non-trivial epilogue run warps 2..9 in two groups
 // The accumulator is double buffered in TMEM (2 x BN columns of the 512), so the epilogue of
 // tile i overlaps the main loop of tile i+1.  Stages and accumulators are handed over through
 // mbarriers; tcgen05.commit arrives on them when the MMAs that read a stage have retired.
@@ -29,16 +30,23 @@ constexpr int TC_THREADS = 192;      // producer warp, MMA warp, four epilogue w
 constexpr int TC_THREADS_EPI8 = 320; // eight epilogue warps (kernels with a non-trivial epilogue)
 constexpr int TC_TMEM_COLS = 512;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;
-constexpr int TC_OUT_BYTES = 4 * 2 * 4096; // epilogue staging: 4 warps, double buffered, 32 rows x 128 B
+constexpr int TC_SMEM_LIMIT = 227 * 1024; // dynamic shared memory a CTA may have
 
 // PAIR: two CTAs of a cluster share one 256 x BN tile (tcgen05 cta_group::2): each holds 128 rows of A and
 // BN / 2 rows of B per stage, so a stage is smaller and more of them fit.
-template <int BN, bool PAIR = false> struct TcCfg {
+// Epilogue staging: two 32-row x 128-byte buffers per epilogue warp (four warps in the plain kernel, eight
+// otherwise), so that a warp fills one while the TMA store of the other is still reading it; the operand ring
+// gets the stages that fit beside it (at most eight).
+template <int BN, bool PAIR = false, bool PLAIN = true> struct TcCfg {
   static constexpr int kBRows = PAIR ? BN / 2 : BN;
   static constexpr int kBBytes = kBRows * TC_BK * 2;
   static constexpr int kStageBytes = TC_A_BYTES + kBBytes;
-  static constexpr int kStages = PAIR ? (BN == 256 ? 6 : 8) : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
-  static constexpr int kSmem = kStages * kStageBytes + TC_OUT_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int kOutBytes = (PLAIN ? 4 : 8) * 2 * 4096;
+  static constexpr int kFixed = kOutBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int kFit = (TC_SMEM_LIMIT - kFixed) / kStageBytes;
+  static constexpr int kStages = kFit > 8 ? 8 : kFit;
+  static constexpr int kSmem = kStages * kStageBytes + kFixed;
+  static_assert(kStages >= 3, "operand ring too short");
 };
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the
@@ -151,14 +159,14 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
                       const __grid_constant__ CUtensorMap mapB1, const __grid_constant__ CUtensorMap mapC1,
                       const __grid_constant__ CUtensorMap mapB2, const __grid_constant__ CUtensorMap mapC2,
                       const __grid_constant__ PushMaps pushMaps, TC *__restrict__ c, TcParams p) {
-  using Cfg = TcCfg<BN, PAIR>;
+  using Cfg = TcCfg<BN, PAIR, PLAIN>;
   constexpr int STAGES = Cfg::kStages;
   constexpr int TILE_M = PAIR ? 2 * TC_BM : TC_BM; // rows of C per tile (per CTA always TC_BM)
   extern __shared__ uint8_t smemRaw[];
   // 1024-byte alignment: required by the 128-byte swizzle pattern
   const uint32_t base = (smemU32(smemRaw) + 1023u) & ~1023u;
   const uint32_t outBase = base + STAGES * Cfg::kStageBytes; // 4 warps x 2 x 4 KB epilogue staging
-  const uint32_t barBase = outBase + TC_OUT_BYTES;
+  const uint32_t barBase = outBase + Cfg::kOutBytes;
   auto fullBar = [&](int s) { return barBase + 8u * s; };
   auto emptyBar = [&](int s) { return barBase + 8u * (STAGES + s); };
   auto tmemFullBar = [&](int a) { return barBase + 8u * (2 * STAGES + a); };
@@ -231,7 +239,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     // (0, 0) and that pixel's coordinates; a k-block then costs a few integer operations per copy.
     // Up to kInFlight stages of copies are in flight; a stage is handed to the MMA warp when its
     // copies have landed and are visible to the async proxy.
-    constexpr int kInFlight = 3;
+    constexpr int kInFlight = STAGES > 3 ? 3 : STAGES - 1; // fewer than there are stages: a stage is handed over before its slot comes round again
     const uint16_t *x = static_cast<const uint16_t *>(p.convX);
     const int cb = p.cC / TC_BK;
     const int piece = lane & 7, rowInGroup = lane >> 3;
@@ -418,7 +426,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     // drains accumulator buffer g (every other tile), one staging buffer per warp; two warps per
     // scheduler hide each other's instruction latencies in the longer epilogues.
     const int group = (warp - 2) / 4;
-    const uint32_t stageOut = outBase + static_cast<uint32_t>(warp - 2) * (EPW == 4 ? 2u : 1u) * 4096u;
+    const uint32_t stageOut = outBase + static_cast<uint32_t>(warp - 2) * 2u * 4096u; // two buffers per warp
     uint32_t chunkIt = 0, extraPhase = 0;
     bool alive = true;
     // Tiles of this CTA are numbered 0 .. myTiles-1 (tile index = blockIdx.x + number * gridDim.x,
@@ -492,7 +500,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
           for (int cc = (shared && helper) ? 1 : 0; cc < 2; cc += shared ? 2 : 1) {
             const int64_t col0 = n0 + cc * CH;
             if (col0 >= segN) break; // warp-uniform
-            const uint32_t buf = stageOut;
+            const uint32_t buf = stageOut + (chunkIt & 1u) * 4096u;
             const uint32_t rowAddr = buf + static_cast<uint32_t>(lane) * 128u;
 #pragma unroll
             for (int l = 0; l < 2; ++l) {
@@ -508,7 +516,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
                 g[e] = __float_as_uint(__fmul_rn(sg, toF32(fromF32<TC>(__uint_as_float(u[e])))));
               }
               if (l == 0) {
-                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); // the last store has read the buffer
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); // the store before the last has read this buffer
                 __syncwarp();
               }
 #pragma unroll
@@ -546,7 +554,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
           for (int cc = (shared && helper) ? 1 : 0; cc < BN / CH; cc += shared ? 2 : 1) {
             const int64_t col0 = n0 + cc * CH;
             if (col0 >= segN) break; // warp-uniform
-            const uint32_t buf = stageOut;
+            const uint32_t buf = stageOut + (chunkIt & 1u) * 4096u;
             const uint32_t rowAddr = buf + static_cast<uint32_t>(lane) * 128u;
 #pragma unroll
             for (int l = 0; l < 2; ++l) {
@@ -567,7 +575,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
                 r1[e] = __float_as_uint(__fadd_rn(v1, v2));
               }
               if (l == 0) {
-                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); // the last store has read the buffer
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); // the store before the last has read this buffer
                 __syncwarp();
               }
 #pragma unroll
@@ -657,7 +665,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
       for (int cc = dualDone ? BN / CH : ((shared && helper) ? 1 : 0); cc < BN / CH; cc += shared ? 2 : 1) {
         const int64_t col0 = n0 + cc * CH;
         if (col0 >= segN) break; // warp-uniform
-        const uint32_t buf = stageOut + (EPW == 4 ? (chunkIt & 1u) * 4096u : 0u);
+        const uint32_t buf = stageOut + (chunkIt & 1u) * 4096u;
         const uint32_t rowAddr = buf + static_cast<uint32_t>(lane) * 128u;
         // The second operand's 32 x 128 B block is brought into the staging buffer by TMA (the
         // layout the result will have), combined in place, and stored from there.
@@ -666,7 +674,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
           useExtra = p.extraOp != 0;
           if (useExtra) {
             if (lane == 0) {
-              asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); // the last store has read the buffer
+              asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); // the store before the last has read this buffer
               mbarArriveExpectTx(extraBar(warp - 2), 4096);
               if (p.cTw) tmaLoad4d(buf, &mapE, extraBar(warp - 2), static_cast<int>(col0), pOx, pOy, pImg);
               else tmaLoad2d(buf, &mapE, extraBar(warp - 2), static_cast<int>(col0), static_cast<int>(m0 + quarter * 32));
@@ -780,8 +788,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
           if (l == 0 && !useExtra) {
             // the staging buffer is free once the bulk store issued from it has read it
             if (lane == 0) {
-              if (EPW == 4) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-              else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+              asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             }
             __syncwarp();
           }
@@ -933,7 +940,7 @@ template <int BN, typename TC, bool PLAIN, bool PAIR = false>
 static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &me, void *c, const TcParams &p,
                     cudaStream_t st, const CUtensorMap *more = nullptr /* mapB1, mapC1, mapB2, mapC2 of a grouped launch */,
                     const PushMaps *push = nullptr) {
-  using Cfg = TcCfg<BN, PAIR>;
+  using Cfg = TcCfg<BN, PAIR, PLAIN>;
   // Function attributes belong to a device: set the shared-memory limit once on each.
   static bool attrSet[64] = {};
   int dev = 0;

@@ -982,16 +982,30 @@ static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensor
   return TTB_OK;
 }
 
-// Tile width for an m x n problem on `workers` workers of `tileM` rows: fewest (waves x per-tile cost); the
-// +64 stands for the A tile every CTA loads whatever its width, which makes narrow tiles less efficient per column.
-static int pickTileWidth(int64_t m, int64_t n, int64_t tileM, int workers) {
+// Tile width for an m x n problem on `workers` workers of `tileM` rows: fewest (waves x per-tile cost).  A tile's
+// cost per k-block follows the operand bytes its CTA fetches -- 128 rows of A whatever the width, plus the CTA's
+// rows of B (all of them, or half in a CTA pair) -- because narrow tiles are bound by the rate at which an SM takes
+// operands in, not by the tensor pipe: measured per tile and k-block, pairs, 1.0 : 0.80 : 0.64 for widths 256 : 128 :
+// 64 (the model gives 1.0 : 0.75 : 0.63).
+static int forcedTileWidth() {
+  static const int v = [] {
+    const char *e = std::getenv("TTB_FORCE_BN");
+    return e ? atoi(e) : 0;
+  }();
+  return v;
+}
+
+static int64_t tileCost(int w, bool pair) { return 128 + (pair ? w / 2 : w); }
+
+static int pickTileWidth(int64_t m, int64_t n, int64_t tileM, int workers, bool pair) {
+  if (forcedTileWidth() && n >= forcedTileWidth()) return forcedTileWidth();
   int bn = 64;
   int64_t best = -1;
   for (int w : {256, 128, 64}) {
     if (w > 64 && n < w) continue;
     int64_t tiles = ((m + tileM - 1) / tileM) * ((n + w - 1) / w);
     int64_t waves = (tiles + workers - 1) / workers;
-    int64_t cost = waves * (w + 64);
+    int64_t cost = waves * tileCost(w, pair);
     if (best < 0 || cost < best) {
       best = cost;
       bn = w;
@@ -1027,7 +1041,7 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   // Tiny problems are launch-bound either way; keep them on the simple kernel.
   if (m * n * k < (1ll << 18)) return -1;
   const bool pair = pairMmaWanted(m, k);
-  const int bn = pickTileWidth(m, n, pair ? 2 * TC_BM : TC_BM, pair ? smCount() / 2 : smCount());
+  const int bn = pickTileWidth(m, n, pair ? 2 * TC_BM : TC_BM, pair ? smCount() / 2 : smCount(), pair);
   CUtensorMap ma, mb, mc, me;
   if (!makeMap(&ma, a, abDtype, m, k, TC_BM) || !makeMap(&mb, b, abDtype, n, k, pair ? bn / 2 : bn) ||
       !makeMap(&mc, c, cDtype, m, n, 32))
@@ -1178,7 +1192,7 @@ int gemmTcgen05I8Try(const void *a, const void *b, void *c, int aDtype, int bDty
   if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff) return -1;
   if (m * n * k < (1ll << 18)) return -1;
   const bool pair = pairMmaWanted(m, k);
-  const int bn = pickTileWidth(m, n, pair ? 2 * TC_BM : TC_BM, pair ? smCount() / 2 : smCount());
+  const int bn = pickTileWidth(m, n, pair ? 2 * TC_BM : TC_BM, pair ? smCount() / 2 : smCount(), pair);
   CUtensorMap ma, mb, mc;
   if (!makeMap(&ma, a, kU8, m, k, TC_BM) || !makeMap(&mb, b, kU8, n, k, pair ? bn / 2 : bn) || !makeMap(&mc, c, cDtype, m, n, 32)) return -1;
   TcParams p;
@@ -1245,7 +1259,9 @@ int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, c
   const int64_t tileM = pair ? 2 * TC_BM : TC_BM;
   const int workers = pair ? smCount() / 2 : smCount();
   int bn = 64;
-  {
+  if (forcedTileWidth()) {
+    bn = forcedTileWidth();
+  } else {
     int64_t best = -1;
     for (int w : {256, 128, 64}) {
       if (ropeMask && w < 128) continue; // a head's two halves have to lie in one tile
@@ -1257,7 +1273,7 @@ int gemmTcgen05GroupedTry(const void *a, const void *const *b, void *const *c, c
       }
       if (!fits) continue;
       int64_t waves = (tiles + workers - 1) / workers;
-      int64_t cost = waves * (w + 64);
+      int64_t cost = waves * tileCost(w, pair);
       if (best < 0 || cost < best) {
         best = cost;
         bn = w;

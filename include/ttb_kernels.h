@@ -599,6 +599,15 @@ TTB_API int ttb_gemm_push(const void *a, const void *b, void *const *targets, in
                           int64_t m, int64_t n, int64_t k, void *stream);
 TTB_API int ttb_symm_all_reduce_pushed(void *symm, const void *residual, void *out, size_t count,
                                        int dtype, void *stream);
+/* The reduce-scatter half alone, for an all_reduce whose result is only read through a mesh_partition along the
+ * same mesh axis (runtime/lib/ttnn/operations/ccl/{all_reduce.cpp:13-39, mesh_partition.cpp:13-29} back to back):
+ * `out` receives this rank's slice of the sum only -- count / nranks elements, block `rank` of the flattened
+ * operand -- plus the matching part of `residual` ([count], nullable).  Nothing is pushed to the peers; the second
+ * barrier and the final copy of ttb_symm_all_reduce fall away.  `count` must split into 16-byte aligned slices. */
+TTB_API int ttb_symm_reduce_scatter(void *symm, const void *in, const void *residual, void *out, size_t count, int dtype,
+                                    void *stream);
+TTB_API int ttb_symm_reduce_scatter_pushed(void *symm, const void *residual, void *out, size_t count, int dtype,
+                                           void *stream);
 
 #ifdef __cplusplus
 }

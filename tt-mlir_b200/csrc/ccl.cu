@@ -145,6 +145,7 @@ struct SymmParams {
   size_t dataOff, resultOff; // this launch's regions inside a workspace
   uint32_t token;            // first barrier waits for token, second for token + 1
   int oneShot;               // every rank reduces the whole operand itself: no push, no second barrier
+  int ownOnly;               // reduce-scatter: only the own slice is wanted (stored densely at out[0..]); no push, no second barrier
   int *status;
   long long waitCycles; // how long a barrier may spin on a peer's flag before it gives up (SM clock cycles)
 };
@@ -220,7 +221,8 @@ __global__ void __launch_bounds__(SYMM_THREADS)
   {
     const size_t lo = p.oneShot ? 0 : p.rank * per;
     const size_t hi = p.oneShot ? nvec : (lo + per < nvec ? lo + per : nvec);
-    const bool push = !p.oneShot;
+    const bool push = !p.oneShot && !p.ownOnly;
+    const size_t outShift = p.ownOnly ? lo : 0; // reduce-scatter: `out` holds the own slice only
     for (size_t i0 = lo + first; i0 < hi; i0 += stride * U) {
       uint4 v[U][NR];
       uint4 rv[U];
@@ -268,7 +270,7 @@ __global__ void __launch_bounds__(SYMM_THREADS)
 #pragma unroll
             for (int j = 0; j < V; ++j) oe[j] = fromF32<T>(acc[j]);
           }
-          out[i] = o;
+          out[i - outShift] = o;
 #pragma unroll
           for (int r = 0; r < NR; ++r) {
             if (push && r < p.n && r != p.rank) reinterpret_cast<uint4 *>(p.ws[r] + p.resultOff)[i] = o;
@@ -277,7 +279,7 @@ __global__ void __launch_bounds__(SYMM_THREADS)
       }
     }
   }
-  if (p.oneShot) return;
+  if (p.oneShot || p.ownOnly) return;
   symmBarrier(p, 1, p.token + 1);
 
   // C: the slices the peers pushed.
@@ -643,7 +645,7 @@ int ttb_symm_push_targets(void *symm, size_t bytes, void **targets, int *rank, i
 }
 
 static int symmAllReduceImpl(void *symm, const void *in, const void *residual, void *out, size_t count, int dtype,
-                             void *stream, bool pushed);
+                             void *stream, bool pushed, bool ownOnly = false);
 
 int ttb_symm_all_reduce_pushed(void *symm, const void *residual, void *out, size_t count, int dtype, void *stream) {
   TTB_CHECK(symm && out, "null argument");
@@ -656,10 +658,25 @@ int ttb_symm_all_reduce(void *symm, const void *in, const void *residual, void *
   return symmAllReduceImpl(symm, in, residual, out, count, dtype, stream, false);
 }
 
+// The reduce-scatter half alone: `out` receives only this rank's slice of the sum (count / nranks elements: block
+// `rank` of the flattened operand) plus the matching part of `residual` (full size, nullable).  Nothing is pushed to
+// the peers and the second barrier and the final copy fall away, which is what an all_reduce whose result is only
+// read through a mesh_partition of the same axis needs.
+int ttb_symm_reduce_scatter(void *symm, const void *in, const void *residual, void *out, size_t count, int dtype,
+                            void *stream) {
+  TTB_CHECK(symm && in && out, "null argument");
+  return symmAllReduceImpl(symm, in, residual, out, count, dtype, stream, false, true);
+}
+
+int ttb_symm_reduce_scatter_pushed(void *symm, const void *residual, void *out, size_t count, int dtype, void *stream) {
+  TTB_CHECK(symm && out, "null argument");
+  return symmAllReduceImpl(symm, out /* unused */, residual, out, count, dtype, stream, true, true);
+}
+
 } // extern "C"
 
 static int symmAllReduceImpl(void *symm, const void *in, const void *residual, void *out, size_t count, int dtype,
-                             void *stream, bool pushed) {
+                             void *stream, bool pushed, bool ownOnly) {
   auto *s = static_cast<Symm *>(symm);
   const size_t es = dtypeSize(dtype);
   const size_t bytes = count * es;
@@ -679,9 +696,10 @@ static int symmAllReduceImpl(void *symm, const void *in, const void *residual, v
   p.resultOff = SYMM_FLAG_BYTES + (2 + parity) * s->maxBytes;
   p.token = 2 * launch + 1;
   p.status = s->status;
-  p.oneShot = (!pushed && (s->n == 2 || bytes <= (size_t(256) << 10))) ? 1 : 0;
-  if (pushed && bytes % (16 * static_cast<size_t>(s->n)) != 0) {
-    setLastError("symm_all_reduce_pushed: operand does not split into 16-byte aligned slices");
+  p.oneShot = (!pushed && !ownOnly && (s->n == 2 || bytes <= (size_t(256) << 10))) ? 1 : 0;
+  p.ownOnly = ownOnly ? 1 : 0;
+  if ((pushed || ownOnly) && bytes % (16 * static_cast<size_t>(s->n)) != 0) {
+    setLastError("symm_all_reduce: operand does not split into 16-byte aligned slices");
     return TTB_ERR_UNSUPPORTED;
   }
   p.waitCycles = s->waitCycles;

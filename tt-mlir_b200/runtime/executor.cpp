@@ -3311,6 +3311,45 @@ size_t Executor::tryAllReduceAdd(size_t i) {
     return 0;
   TensorPtr in = getDevice(op->in()), res = getDevice(other);
   if (in->dtype != dt || in->volume() != res->volume()) return 0;
+  // all_reduce -> add -> mesh_partition along the same mesh axis, the sum read by nothing else: every rank keeps
+  // only its own block of rows, so the broadcast half of the all-reduce would be thrown away.  The kernel then
+  // stops after the reduce-scatter half and writes the partition's result directly.
+  static const bool scatterOff = [] {
+    const char *e = std::getenv("TTB_DISABLE_REDUCE_SCATTER_FUSION");
+    return e && e[0] == '1';
+  }();
+  if (!scatterOff && singleUse(add->out())) {
+    std::vector<const fbt::Operation *> d2;
+    size_t j2 = j + 1;
+    const auto *pop = peek(j2, d2);
+    if (pop && pop->type_type() == OpType::MeshPartitionOp) {
+      const auto *part = pop->type_as_MeshPartitionOp();
+      const uint32_t n = meshAxisSize(op->cluster_axis());
+      const uint32_t axis = part->cluster_axis().value_or(dev->meshShape[0] > 1 ? 0 : 1);
+      std::vector<uint32_t> shape = refShape(add->out());
+      const int d = normDim(part->dim(), shape.size());
+      const bool symm = in->pushedForAllReduce || (in->bytes() % 16 == 0 && symmReady(in->bytes()));
+      if (part->in()->global_id() == add->out()->global_id() && axis == op->cluster_axis() && n == dev->worldSize && symm &&
+          prod(shape, 0, d) == 1 && shape[d] % n == 0 && (in->bytes() / n) % 16 == 0 && refDtype(part->out()) == dt) {
+        refuseWhileRecording("a collective");
+        TensorPtr out = allocOut(part->out());
+        TTRT_ASSERT(out->volume() * n == in->volume(), "mesh_partition result must be 1/", n, " of its input");
+        eachRank([&](size_t r, const RankCtx &rc) {
+          if (in->pushedForAllReduce) {
+            TTB_CALL(ttb_symm_reduce_scatter_pushed(rc.symm, res->shards[r]->ptr, out->shards[r]->ptr, in->volume(), ttbDtype(dt),
+                                                    rc.stream));
+          } else {
+            TTB_CALL(ttb_symm_reduce_scatter(rc.symm, in->shards[r]->ptr, res->shards[r]->ptr, out->shards[r]->ptr, in->volume(),
+                                             ttbDtype(dt), rc.stream));
+          }
+        });
+        put(part->out(), out);
+        deallocs.insert(deallocs.end(), d2.begin(), d2.end());
+        runDeallocs(deallocs);
+        return j2 + 1 - i;
+      }
+    }
+  }
   TensorPtr out = allocOut(add->out());
   allReduce(in, res, out, 0);
   put(add->out(), out);

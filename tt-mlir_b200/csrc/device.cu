@@ -60,11 +60,15 @@ static std::vector<ProfRecord> g_profRecords;
 
 ProfScope::ProfScope(const char *tag, double flops, double bytes, cudaStream_t st) : slot(-1), stream(st) {
   if (!g_profOn.load(std::memory_order_relaxed)) return;
-  ProfRecord r{tag, flops, bytes, nullptr, nullptr};
-  if (cudaEventCreate(&r.start) != cudaSuccess || cudaEventCreate(&r.stop) != cudaSuccess) return;
-  cudaEventRecord(r.start, st);
+  cudaEvent_t start = nullptr, stop = nullptr;
+  if (cudaEventCreate(&start) != cudaSuccess) return;
+  if (cudaEventCreate(&stop) != cudaSuccess) {
+    cudaEventDestroy(start);
+    return;
+  }
+  cudaEventRecord(start, st);
   std::lock_guard<std::mutex> g(g_profMutex);
-  g_profRecords.push_back(r);
+  g_profRecords.push_back(ProfRecord{tag, flops, bytes, start, stop});
   slot = static_cast<int>(g_profRecords.size()) - 1;
 }
 

@@ -21,6 +21,7 @@
 #include "tcgen05.cuh"
 
 #include <cstdlib>
+#include <type_traits>
 
 namespace ttb {
 
@@ -90,6 +91,28 @@ template <> __device__ __forceinline__ uint32_t relu2<__half>(uint32_t v) {
 }
 template <> __device__ __forceinline__ uint32_t relu2<float>(uint32_t v) { return v; }
 
+// A row segment of 32 bias values in the 16-bit output type, fetched as four 16-byte loads from the same address in
+// every lane (one broadcast transaction each) instead of one value per lane handed round with 32 shuffles: the
+// shuffle unit takes one warp instruction per cycle per SM, which made it the busiest unit of the short-reduction
+// epilogues.  Element e is converted where it is used.
+template <typename TC> struct BiasRow {
+  uint4 raw[4];
+  __device__ __forceinline__ void load(const void *bias, int64_t col) {
+    const uint4 *p = reinterpret_cast<const uint4 *>(static_cast<const TC *>(bias) + col);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) raw[v] = __ldg(p + v);
+  }
+  __device__ __forceinline__ float at(int e) const {
+    const uint32_t w = reinterpret_cast<const uint32_t *>(raw)[e >> 1];
+    if constexpr (sizeof(TC) == 2 && std::is_same<TC, __nv_bfloat16>::value) {
+      return __uint_as_float((e & 1) ? (w & 0xffff0000u) : (w << 16));
+    } else {
+      const __half2 h = *reinterpret_cast<const __half2 *>(&w);
+      return (e & 1) ? __high2float(h) : __low2float(h);
+    }
+  }
+};
+
 struct TcParams {
   int64_t M, N, K;
   const void *bias;
@@ -146,6 +169,9 @@ struct TcParams {
   int64_t K2 = 0;
   const void *bias2 = nullptr;
   int bias2Dt = 0;
+  // The biases are in the output's 16-bit type and 16-byte aligned: their values are fetched as broadcast vectors
+  // (set by the launcher).
+  int biasVec = 0;
 };
 
 struct PushMaps {
@@ -559,8 +585,14 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
 #pragma unroll
             for (int l = 0; l < 2; ++l) {
               const int64_t colH = col0 + l * 32;
+              // both biases as broadcast vectors when the pass lies inside the matrix, one value per lane otherwise
+              const bool wide = p.biasVec && p.bias && p.bias2 && colH + 32 <= p.N;
               float b1 = 0.0f, b2 = 0.0f;
-              if (colH + lane < p.N) {
+              BiasRow<TC> row1, row2;
+              if (wide) {
+                row1.load(p.bias, colH);
+                row2.load(p.bias2, colH);
+              } else if (colH + lane < p.N) {
                 if (p.bias) b1 = loadBias(p.bias, p.biasDt, colH + lane);
                 if (p.bias2) b2 = loadBias(p.bias2, p.bias2Dt, colH + lane);
               }
@@ -568,11 +600,20 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
               tcLoad32(taddrRow + static_cast<uint32_t>(cc * CH + l * 32), r1);
               tcLoad32(taddrRow + static_cast<uint32_t>(BN + cc * CH + l * 32), r2);
               tcWaitLd();
+              if (wide) {
 #pragma unroll
-              for (int e = 0; e < 32; ++e) {
-                const float v1 = toF32(fromF32<TC>(__fadd_rn(__uint_as_float(r1[e]), __shfl_sync(0xffffffffu, b1, e))));
-                const float v2 = toF32(fromF32<TC>(__fadd_rn(__uint_as_float(r2[e]), __shfl_sync(0xffffffffu, b2, e))));
-                r1[e] = __float_as_uint(__fadd_rn(v1, v2));
+                for (int e = 0; e < 32; ++e) {
+                  const float v1 = toF32(fromF32<TC>(__fadd_rn(__uint_as_float(r1[e]), row1.at(e))));
+                  const float v2 = toF32(fromF32<TC>(__fadd_rn(__uint_as_float(r2[e]), row2.at(e))));
+                  r1[e] = __float_as_uint(__fadd_rn(v1, v2));
+                }
+              } else {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                  const float v1 = toF32(fromF32<TC>(__fadd_rn(__uint_as_float(r1[e]), __shfl_sync(0xffffffffu, b1, e))));
+                  const float v2 = toF32(fromF32<TC>(__fadd_rn(__uint_as_float(r2[e]), __shfl_sync(0xffffffffu, b2, e))));
+                  r1[e] = __float_as_uint(__fadd_rn(v1, v2));
+                }
               }
               if (l == 0) {
                 if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); // the store before the last has read this buffer
@@ -690,8 +731,14 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
           const int64_t colH = col0 + l * HW;
           // bias of this pass first, so that it is in flight while TMEM is read
           float biasReg = 0.0f;
+          BiasRow<TC> biasRow;
+          bool biasWide = false; // the whole pass lies inside the matrix and the bias can be fetched as vectors
           if constexpr (!PLAIN) {
-            if (p.bias && colH + lane < p.N) biasReg = loadBias(p.bias, p.biasDt, colH + lane);
+            if constexpr (sizeof(TC) == 2) {
+              biasWide = p.bias && p.biasVec && colH + HW <= p.N;
+              if (biasWide) biasRow.load(p.bias, colH);
+            }
+            if (p.bias && !biasWide && colH + lane < p.N) biasReg = loadBias(p.bias, p.biasDt, colH + lane);
           }
           uint32_t r[HW];
           tcLoad32(taddrRow + static_cast<uint32_t>(cc * CH + l * HW), r);
@@ -724,11 +771,27 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
             // every variant's instructions on every element, and a per-element switch over the
             // activations would thrash the instruction cache.
             const bool hasBias = p.bias != nullptr, round1 = (p.roundSteps & 1) != 0, round2 = (p.roundSteps & 2) != 0;
-            if (hasBias && !round1 && !round2) {
+            if (hasBias && !round1 && !round2 && biasWide) {
+              if constexpr (sizeof(TC) == 2) {
+#pragma unroll
+                for (int e = 0; e < HW; ++e) r[e] = __float_as_uint(__fadd_rn(__uint_as_float(r[e]), biasRow.at(e)));
+              }
+            } else if (hasBias && !round1 && !round2) {
 #pragma unroll
               for (int e = 0; e < HW; ++e) {
                 const float bz = __shfl_sync(0xffffffffu, biasReg, e); // lane e holds column e's bias
                 r[e] = __float_as_uint(__fadd_rn(__uint_as_float(r[e]), bz));
+              }
+            } else if (hasBias && biasWide) {
+              if constexpr (sizeof(TC) == 2) {
+#pragma unroll
+                for (int e = 0; e < HW; ++e) {
+                  float f = __uint_as_float(r[e]);
+                  if (round1) f = toF32(fromF32<TC>(f));
+                  f = __fadd_rn(f, biasRow.at(e));
+                  if (round2) f = toF32(fromF32<TC>(f));
+                  r[e] = __float_as_uint(f);
+                }
               }
             } else if (hasBias) {
 #pragma unroll
@@ -1054,6 +1117,7 @@ int gemmTcgen05Try(const void *a, const void *b, const void *bias, void *c, int 
   TcParams p;
   p.M = m; p.N = n; p.K = k;
   p.bias = bias; p.biasDt = biasDtype; p.act = act; p.roundSteps = roundSteps;
+  p.biasVec = bias && biasDtype == cDtype && cDtype != kF32 && aligned16(bias) ? 1 : 0;
   p.extra = extraOp ? extra : nullptr;
   p.extraOp = extra ? extraOp : 0;
   p.convX = nullptr;
@@ -1162,6 +1226,7 @@ int gemmTcgen05DualTry(const void *a1, const void *b1, const void *bias1, const 
   p.K2 = k2;
   p.bias2 = bias2;
   p.bias2Dt = biasDtype;
+  p.biasVec = bias1 && bias2 && biasDtype == dtype && aligned16(bias1) && aligned16(bias2) ? 1 : 0;
   ProfScope prof("gemm_tcgen05", 2.0 * double(m) * double(n) * double(k1 + k2),
                  (double(m) * (k1 + k2) + double(n) * (k1 + k2) + double(m) * n) * 2, stream);
   const CUtensorMap more[4] = {mb2, mc, mb2, mc};
@@ -1199,6 +1264,7 @@ int gemmTcgen05I8Try(const void *a, const void *b, void *c, int aDtype, int bDty
   p.M = m; p.N = n; p.K = k;
   // a bias follows the dequantize as a separate add: the dequantized value is rounded before it (round step 1)
   p.bias = bias; p.biasDt = biasDtype; p.act = TTB_ACT_NONE; p.roundSteps = bias ? 1 : 0;
+  p.biasVec = bias && biasDtype == cDtype && (cDtype == kBF16 || cDtype == kF16) && aligned16(bias) ? 1 : 0;
   p.extra = nullptr; p.extraOp = 0;
   p.convX = nullptr; p.cTw = 0; p.cTilesM = 0; p.pushRows = 0; p.dual = 0;
   p.segCum[0] = p.segCum[1] = p.segCum[2] = static_cast<int>((n + bn - 1) / bn);
@@ -1393,6 +1459,7 @@ int convTcgen05Try(const void *x, const void *wre, const void *bias, void *out, 
   TcParams p;
   p.M = m; p.N = o; p.K = k;
   p.bias = bias; p.biasDt = biasDtype; p.act = act; p.roundSteps = 0;
+  p.biasVec = bias && biasDtype == dtype && aligned16(bias) ? 1 : 0;
   p.extra = extraOp ? extra : nullptr;
   p.extraOp = extra ? extraOp : 0;
   p.convX = x;

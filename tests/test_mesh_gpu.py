@@ -74,6 +74,36 @@ def test_all_reduce_all_gather_reduce_scatter(rt, mesh2):
     assert torch.equal(got[1], x) and torch.equal(got[4], x)
 
 
+@pytest.mark.parametrize("m,n,k", [(192, 256, 512), (256, 512, 256), (8, 64, 64)])
+def test_all_reduce_add_read_through_mesh_partition(rt, mesh2, m, n, k):
+    """all_reduce -> add(residual) -> mesh_partition along the same mesh axis: every device keeps its own block of
+    rows only, so the executor runs the reduce-scatter half of the peer-memory all-reduce and writes the partition's
+    result directly.  192 rows (96 per device: not whole 128-row tiles) take the variant whose operand the GEMM wrote
+    into the staging region, 256 rows the one whose GEMM pushed its row blocks, 8 rows the tiny one-launch GEMM.
+    The rows must equal, bit for bit, the same rows of the full all-reduce + add of the unfused program."""
+    torch.manual_seed(m + n + k)
+    x = torch.randn(m, k).to(torch.bfloat16)
+    w = (torch.randn(n, k) * 0.05).to(torch.bfloat16)
+    res = torch.randn(m, n).to(torch.bfloat16)
+
+    def body(b, xv, wv, rv):
+        xs, ws = b.distribute(xv, 1), b.distribute(wv, 1)
+        r = b.distribute(rv, None)
+        summed = b.add(r, b.all_reduce(b.linear(xs, ws, transpose_b=True)))
+        return [b.aggregate(b.mesh_partition(summed, 0), 0)]
+
+    def body_full(b, xv, wv, rv):
+        xs, ws = b.distribute(xv, 1), b.distribute(wv, 1)
+        r = b.distribute(rv, None)
+        summed = b.add(r, b.all_reduce(b.linear(xs, ws, transpose_b=True)))
+        return [b.aggregate(summed, 0)]
+    got, want = run_mesh(rt, mesh2, body, [x, w, res])
+    assert_matches(got[0], want[0], "reduce-scatter + residual", (0.999, 2e-2, 2.0 ** -6))
+    full, _ = run_mesh(rt, mesh2, body_full, [x, w, res])
+    assert torch.equal(full[0][:m], full[0][m:]), "the two devices disagree"
+    assert torch.equal(got[0], full[0][:m]), "own rows differ from the full all-reduce"
+
+
 def test_decoder_block_tensor_parallel(rt, mesh2):
     kw = dict(seq=256, hidden=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024)
     ins = graphs.decoder_block_inputs(**kw)

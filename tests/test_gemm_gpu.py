@@ -34,7 +34,10 @@ def tc_status(h):
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 64, 128), (128, 128, 256), (256, 512, 1024),
                                    (200, 136, 72), (1000, 1000, 520), (77, 264, 4096), (4096, 64, 576),
-                                   (2048, 4096, 4096)])
+                                   (2048, 4096, 4096),
+                                   # CTA pairs (256 rows and more, K of 512 and more) with ragged edges: a second CTA
+                                   # with one valid row, none at all in the last tile, 8 columns, K tails
+                                   (257, 264, 512), (385, 8, 1032), (513, 520, 2056), (300, 1032, 640)])
 def test_tcgen05_matches_simt_and_f32(rt, device, m, n, k):
     torch.manual_seed(m + n + k)
     a = torch.randn(m, k).to(torch.bfloat16)

@@ -196,6 +196,22 @@ TTB_API int ttb_layer_norm(const void *in, const void *weight, const void *bias,
  * middle dimension of [outer, len, inner]; a NaN counts as the maximum. */
 TTB_API int ttb_argmax(const void *in, void *out, int dtype, size_t outer, size_t len, size_t inner,
                        void *stream);
+/* ::ttnn::cumprod (operations/cumprod/cumprod.cpp): running product along the middle dimension of
+ * [outer, len, inner]; the running product is one step wider than the elements (f32 for 16-bit types, f64 for f32,
+ * as torch's CPU scan keeps it) and every prefix is rounded to the element type. */
+TTB_API int ttb_cumprod(const void *in, void *out, int dtype, size_t outer, size_t len, size_t inner, void *stream);
+/* ::ttnn::prod (operations/reduction/prod.cpp): product over the middle dimension of [outer, len, inner] in f32
+ * (Int32: 64-bit product truncated), result [outer, inner]. */
+TTB_API int ttb_prod(const void *in, void *out, int dtype, size_t outer, size_t len, size_t inner, void *stream);
+/* ::ttnn::batch_norm with training = false (operations/normalization/batch_norm.cpp): over [outer, channels, inner],
+ * y = (x - mean[c]) / sqrt(var[c] + eps) * weight[c] + bias[c] in f32; weight / bias nullable. */
+TTB_API int ttb_batch_norm_inference(const void *x, const void *mean, const void *var, const void *weight, const void *bias,
+                                     void *y, int dtype, size_t outer, size_t channels, size_t inner, float eps,
+                                     void *stream);
+/* ::ttnn::upsample (operations/pool/upsample.cpp): NHWC [n, h, w, c] -> [n, h * scale_h, w * scale_w, c], nearest
+ * (bilinear = 0) or bilinear with align_corners = false. */
+TTB_API int ttb_upsample2d(const void *in, void *out, int dtype, size_t n, size_t h, size_t w, size_t c, int scale_h,
+                           int scale_w, int bilinear, void *stream);
 /* ::ttnn::cumsum (operations/cumsum/cumsum.cpp): running sum along the middle dimension. */
 TTB_API int ttb_cumsum(const void *in, void *out, int dtype, size_t outer, size_t len, size_t inner,
                        void *stream);

@@ -180,6 +180,19 @@ class OracleBuilder:
 
     def argmax(self, x, dim=None, keep_dim=False, loc=None): return _map(lambda t: ops.argmax(t, dim, keep_dim), x)
     def cumsum(self, x, dim, loc=None): return _map(lambda t: ops.cumsum(t, dim), x)
+    def cumprod(self, x, dim, loc=None): return _map(lambda t: ops.cumprod(t, dim), x)
+    def prod(self, x, dim=None, keep_dim=False, loc=None): return _map(lambda t: ops.prod(t, dim, keep_dim), x)
+
+    def batch_norm_inference(self, x, mean, var, weight, bias, epsilon=1e-5, loc=None):
+        if weight is None and bias is None:
+            return _map(lambda t, m, v: ops.batch_norm_inference(t, m, v, None, None, epsilon), x, mean, var)
+        return _map(lambda t, m, v, w, b: ops.batch_norm_inference(t, m, v, w, b, epsilon), x, mean, var, weight, bias)
+
+    def upsample(self, x, scale, mode="nearest", loc=None): return _map(lambda t: ops.upsample2d(t, scale, mode), x)
+
+    # the preparation ops change nothing a CPU evaluation can see
+    def prepare_conv2d_weights(self, w, *a, **k): return w
+    def prepare_conv2d_bias(self, bias, *a, **k): return bias
     def embedding(self, indices, weight, loc=None): return _map(ops.embedding, indices, weight)
 
     def max_pool2d(self, x, batch, height, width, channels, kernel=(2, 2), stride=(2, 2), padding=(0, 0), dilation=(1, 1),

@@ -249,6 +249,43 @@ def cumsum(x, dim):  # ttir_cpu.py cumsum
     return torch.cumsum(x, dim=dim).to(x.dtype)
 
 
+def cumprod(x, dim):  # tools/golden/mapping.py:4308-4314 (torch.cumprod, result in the input's type)
+    return torch.cumprod(x, dim=dim).to(x.dtype)
+
+
+def prod(x, dim=None, keep_dim=False):
+    """tools/golden/mapping.py:2858-2900 (torch.prod over one dim, or over all).  16-bit floats are widened to f32 for
+    the op and narrowed once, as every CPU-hoisted op is (torch itself would keep a bf16 running product)."""
+    xf = x.float() if x.dtype in (torch.bfloat16, torch.float16) else x
+    if dim is None:
+        r = torch.prod(xf)
+        r = r.reshape([1] * x.dim()) if keep_dim else r
+    else:
+        r = torch.prod(xf, dim=dim, keepdim=keep_dim)
+    return r.to(x.dtype)
+
+
+def batch_norm_inference(x, mean, var, weight, bias, epsilon):
+    """tools/golden/mapping.py:4948-4976 with the channel dimension at 1: torch's inference batch norm, evaluated in
+    f32 (the CPU-hoist rounding model: widen, one op, narrow)."""
+    r = F.batch_norm(x.float(), running_mean=mean.float(), running_var=var.float(),
+                     weight=None if weight is None else weight.float(), bias=None if bias is None else bias.float(),
+                     training=False, eps=epsilon)
+    return r.to(x.dtype)
+
+
+def upsample2d(x, scale, mode="nearest"):
+    """tools/golden/mapping.py:3552-3578: NHWC in, torch.nn.functional.interpolate on the channels-first view, NHWC
+    out.  The golden transposes dims 1 and 3 (H and C) and hands interpolate the (H_out, W_out) of the result, which
+    is the intended NHWC upsampling for square inputs with one scale; this restatement permutes properly so that
+    non-square inputs and two scales mean what ::ttnn::upsample computes."""
+    sy, sx = (scale, scale) if isinstance(scale, int) else scale
+    nchw = x.permute(0, 3, 1, 2).float()
+    out = F.interpolate(nchw, size=(x.shape[1] * sy, x.shape[2] * sx), mode=mode,
+                        **({"align_corners": False} if mode == "bilinear" else {}))
+    return out.permute(0, 2, 3, 1).contiguous().to(x.dtype)
+
+
 def embedding(indices, weight):  # ttir_cpu.py embedding: leading 1-dims of the table are dropped
     w = weight
     while w.dim() > 2 and w.shape[0] == 1:

@@ -389,6 +389,40 @@ def main():
     store(out, "map/paged/decode", one(ref.ttir_paged_sdpa_decode_golden(gmt(pq), gmt(pcache), gmt(pv), gmt(ptable), gmt(pq), S.BoolAttr(True),
                                                                          None, gmt(ppos), None, None, None, S.BF16Type())))
 
+    # --- cumprod, prod, inference batch norm, upsampling (mapping.py:4308-4314, 2858-2900, 4948-4976, 3552-3578)
+    cx = (rnd(4, 12, 5) * 0.5 + 1.0)
+    store(out, "map/cumprod/x", cx)
+    for d in (0, 1, 2):
+        store(out, f"map/cumprod/dim{d}", one(ref.ttir_cumprod_golden(gmt(cx), S.IntegerAttr(d), S.F32Type())))
+    cxb = cx.to(torch.bfloat16)
+    store(out, "map/cumprod/x_bf16", cxb)
+    store(out, "map/cumprod/bf16_dim1", one(ref.ttir_cumprod_golden(gmt(cxb), S.IntegerAttr(1), S.BF16Type())))
+    ci = torch.randint(-3, 4, (3, 7), generator=g, dtype=torch.int32)
+    store(out, "map/cumprod/x_i32", ci)
+    store(out, "map/cumprod/i32_dim1", one(ref.ttir_cumprod_golden(gmt(ci), S.IntegerAttr(1), S.IntegerType(32))))
+    store(out, "map/prod/all", one(ref.prod_golden(gmt(cx))).reshape(1))
+    store(out, "map/prod/dim1", one(ref.prod_golden(gmt(cx), dim_arg=[1], keep_dim=False)))
+    store(out, "map/prod/dim2_keep", one(ref.prod_golden(gmt(cx), dim_arg=[2], keep_dim=True)))
+    store(out, "map/prod/i32_dim0", one(ref.prod_golden(gmt(ci), dim_arg=[0], keep_dim=False)).to(torch.int32))
+    bx = rnd(3, 6, 5, 7)
+    bmean, bvar = rnd(6) * 0.3, torch.rand(6, generator=g) + 0.5
+    bw, bb = rnd(6) * 0.5 + 1.0, rnd(6) * 0.2
+    for n, t in (("x", bx), ("mean", bmean), ("var", bvar), ("weight", bw), ("bias", bb)):
+        store(out, f"map/batch_norm/{n}", t)
+    store(out, "map/batch_norm/out", one(ref.ttir_batch_norm_inference_golden(gmt(bx), gmt(bw), gmt(bb), gmt(bmean), gmt(bvar),
+                                                                             S.FloatAttr(1e-5), S.IntegerAttr(1), S.F32Type())))
+    bxb = bx.to(torch.bfloat16)
+    store(out, "map/batch_norm/out_bf16", one(ref.ttir_batch_norm_inference_golden(
+        gmt(bxb), gmt(bw.to(torch.bfloat16)), gmt(bb.to(torch.bfloat16)), gmt(bmean.to(torch.bfloat16)), gmt(bvar.to(torch.bfloat16)),
+        S.FloatAttr(1e-5), S.IntegerAttr(1), S.BF16Type())))
+    ux = rnd(2, 6, 6, 5)                                        # NHWC, square (the golden's transpose assumes it)
+    store(out, "map/upsample/x", ux)
+    for mode in ("nearest", "bilinear"):
+        spec = torch.empty(2, 12, 12, 5)
+        store(out, f"map/upsample/{mode}_x2", one(ref.upsample2d_golden(gmt(ux), gmt(spec), 2, mode=mode)))
+    spec3 = torch.empty(2, 18, 18, 5)
+    store(out, "map/upsample/nearest_x3", one(ref.upsample2d_golden(gmt(ux), gmt(spec3), 3, mode="nearest")))
+
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ttir_cpu_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes")

@@ -238,6 +238,32 @@ def test_paged_cache_and_paged_decode(golden):
     assert torch.equal(got, golden["map/paged/decode"])
 
 
+def test_cumprod_prod_batch_norm_upsample(golden):
+    """The restatements of cumprod, prod, inference batch norm and 2-D upsampling against the outputs of the reference's
+    own goldens (tools/golden/mapping.py:4308-4314, 2858-2900, 4948-4976, 3552-3578), recorded by generate.py."""
+    x = golden["map/cumprod/x"]
+    for d in (0, 1, 2):
+        assert torch.equal(ops.cumprod(x, d), golden[f"map/cumprod/dim{d}"])
+    assert torch.equal(ops.cumprod(golden["map/cumprod/x_bf16"], 1), golden["map/cumprod/bf16_dim1"])
+    xi = golden["map/cumprod/x_i32"]
+    assert torch.equal(ops.cumprod(xi, 1), golden["map/cumprod/i32_dim1"])
+    assert torch.equal(ops.prod(x).reshape(1), golden["map/prod/all"])
+    assert torch.equal(ops.prod(x, 1), golden["map/prod/dim1"])
+    assert torch.equal(ops.prod(x, 2, True), golden["map/prod/dim2_keep"])
+    assert torch.equal(ops.prod(xi, 0).to(torch.int32), golden["map/prod/i32_dim0"])
+    bx, mean, var, w, b = (golden[f"map/batch_norm/{n}"] for n in ("x", "mean", "var", "weight", "bias"))
+    assert torch.equal(ops.batch_norm_inference(bx, mean, var, w, b, 1e-5), golden["map/batch_norm/out"])
+    bf = torch.bfloat16
+    # bf16: the golden lets torch evaluate in bf16; the CPU-hoist model (and the kernel) evaluates in f32 and rounds once
+    got = ops.batch_norm_inference(bx.to(bf), mean.to(bf), var.to(bf), w.to(bf), b.to(bf), 1e-5)
+    ok, report = metrics.check_close(golden["map/batch_norm/out_bf16"], got, 0.999, 2e-2, 2.0 ** -6)
+    assert ok, report
+    ux = golden["map/upsample/x"]
+    assert torch.equal(ops.upsample2d(ux, 2, "nearest"), golden["map/upsample/nearest_x2"])
+    assert torch.equal(ops.upsample2d(ux, 3, "nearest"), golden["map/upsample/nearest_x3"])
+    assert torch.allclose(ops.upsample2d(ux, 2, "bilinear"), golden["map/upsample/bilinear_x2"], atol=1e-6, rtol=0)
+
+
 def test_layer_norm(golden):
     x, w, b = golden["ln/x"], golden["ln/w"], golden["ln/b"]
     assert same(ops.layer_norm(x), golden["ln/plain"])

@@ -1,0 +1,220 @@
+// Ops beyond the benchmark graphs that real model flatbuffers carry: cumprod, prod reduction, batch-norm inference
+// and 2-D upsampling.  All are HBM- or latency-bound element work: coalesced accesses along the contiguous dimension,
+// f32 arithmetic per element, one rounding to the element type per result.
+//
+// Reference call sites and goldens:
+//   cumprod     operations/cumprod/cumprod.cpp (::ttnn::cumprod); tools/golden/mapping.py:4308-4314 (torch.cumprod)
+//   prod        operations/reduction/prod.cpp (::ttnn::prod);     mapping.py:2858-2900 (torch.prod, dims one at a time)
+//   batch norm  operations/normalization/batch_norm.cpp (::ttnn::batch_norm, training = false);
+//               mapping.py:4948-4976 (torch.nn.functional.batch_norm over the channel dimension)
+//   upsample    operations/pool/upsample.cpp (::ttnn::upsample, NHWC); mapping.py:3552-3578
+//               (torch.nn.functional.interpolate, "nearest" or "bilinear" with align_corners = False)
+#include "common.cuh"
+
+#include <type_traits>
+
+namespace ttb {
+
+// One thread per (outer, inner) line, sequential along the scanned dimension.  The running product is kept one step
+// wider than the elements, as torch's CPU scan keeps it (float for 16-bit types, double for f32), and every prefix is
+// rounded to the element type; integers wrap like torch's (64-bit running product truncated to the element type).
+template <typename T, typename ACC>
+__global__ void __launch_bounds__(256) cumprodKernel(const T *__restrict__ in, T *__restrict__ out, size_t outer, size_t len,
+                                                     size_t inner) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t c = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < outer * inner; c += stride) {
+    const size_t base = (c / inner) * len * inner + (c % inner);
+    ACC acc = 1;
+    for (size_t i = 0; i < len; ++i) {
+      if constexpr (std::is_same<ACC, float>::value) {
+        acc = __fmul_rn(acc, toF32(in[base + i * inner]));
+        out[base + i * inner] = fromF32<T>(acc);
+      } else if constexpr (std::is_same<ACC, double>::value) {
+        acc = __dmul_rn(acc, static_cast<double>(in[base + i * inner]));
+        out[base + i * inner] = static_cast<T>(acc);
+      } else {
+        acc *= static_cast<ACC>(in[base + i * inner]);
+        out[base + i * inner] = static_cast<T>(acc);
+      }
+    }
+  }
+}
+
+// Product over the middle dimension of [outer, len, inner]: one warp per output when the reduced dimension is the
+// contiguous one (lanes stride the row, partial products combined by shuffles), one thread per output otherwise.
+template <typename T> __global__ void __launch_bounds__(256) prodRowKernel(const T *__restrict__ in, T *__restrict__ out, size_t rows, size_t len) {
+  const size_t row = static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const T *x = in + row * len;
+  float acc = 1.0f;
+  for (size_t i = lane; i < len; i += 32) acc *= toF32(x[i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc *= __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) out[row] = fromF32<T>(acc);
+}
+template <typename T> __global__ void __launch_bounds__(256) prodColKernel(const T *__restrict__ in, T *__restrict__ out, size_t outer, size_t len, size_t inner) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t c = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < outer * inner; c += stride) {
+    const size_t base = (c / inner) * len * inner + (c % inner);
+    float acc = 1.0f;
+    for (size_t i = 0; i < len; ++i) acc *= toF32(in[base + i * inner]);
+    out[c] = fromF32<T>(acc);
+  }
+}
+__global__ void __launch_bounds__(256) prodIntKernel(const int32_t *__restrict__ in, int32_t *__restrict__ out, size_t outer, size_t len, size_t inner) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t c = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < outer * inner; c += stride) {
+    const size_t base = (c / inner) * len * inner + (c % inner);
+    long long acc = 1;
+    for (size_t i = 0; i < len; ++i) acc *= static_cast<long long>(in[base + i * inner]); // wraps like torch's int64 product
+    out[c] = static_cast<int32_t>(acc);
+  }
+}
+
+// y = (x - mean[c]) * rsqrt-free scale + shift, written the way torch's inference batch norm evaluates it in f32:
+//   invstd = 1 / sqrt(var[c] + eps);  y = (x - mean[c]) * invstd * weight[c] + bias[c]
+// over [outer, channels, inner] (NCHW: inner = H * W).  The per-channel factors are recomputed per element: they are
+// four cached loads and one reciprocal square root, and the kernel stays bound by x and y.
+template <typename T>
+__global__ void __launch_bounds__(256) batchNormInferenceKernel(const T *__restrict__ x, const T *__restrict__ mean, const T *__restrict__ var,
+                                                                const T *__restrict__ weight, const T *__restrict__ bias, T *__restrict__ y,
+                                                                size_t total, size_t channels, size_t inner, float eps) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const size_t c = (i / inner) % channels;
+    const float invstd = 1.0f / sqrtf(toF32(var[c]) + eps);
+    float f = (toF32(x[i]) - toF32(mean[c])) * invstd;
+    if (weight) f *= toF32(weight[c]);
+    if (bias) f += toF32(bias[c]);
+    y[i] = fromF32<T>(f);
+  }
+}
+
+// NHWC upsampling by integer factors.  Nearest: out[n, y, x, :] = in[n, y / sy, x / sx, :].  Bilinear: the source
+// coordinate of output pixel y is (y + 0.5) / sy - 0.5, clamped below at 0 (align_corners = False), blended from the
+// two neighbouring rows and columns in f32.  One thread per 16-byte piece of a pixel's channels when the channel count
+// allows, else per element.
+template <typename T>
+__global__ void __launch_bounds__(256) upsampleKernel(const T *__restrict__ in, T *__restrict__ out, size_t n, size_t h, size_t w, size_t c,
+                                                      int sy, int sx, int bilinear) {
+  const size_t ho = h * sy, wo = w * sx, total = n * ho * wo * c;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const size_t ch = i % c, px = (i / c) % wo, py = (i / c / wo) % ho, img = i / c / wo / ho;
+    const T *src = in + img * h * w * c;
+    if (!bilinear) {
+      out[i] = src[((py / sy) * w + px / sx) * c + ch];
+      continue;
+    }
+    float fy = (static_cast<float>(py) + 0.5f) / static_cast<float>(sy) - 0.5f;
+    float fx = (static_cast<float>(px) + 0.5f) / static_cast<float>(sx) - 0.5f;
+    fy = fy < 0.0f ? 0.0f : fy;
+    fx = fx < 0.0f ? 0.0f : fx;
+    const size_t y0 = static_cast<size_t>(fy), x0 = static_cast<size_t>(fx);
+    const size_t y1 = y0 + 1 < h ? y0 + 1 : h - 1, x1 = x0 + 1 < w ? x0 + 1 : w - 1;
+    const float ly = fy - static_cast<float>(y0), lx = fx - static_cast<float>(x0);
+    const float v00 = toF32(src[(y0 * w + x0) * c + ch]), v01 = toF32(src[(y0 * w + x1) * c + ch]);
+    const float v10 = toF32(src[(y1 * w + x0) * c + ch]), v11 = toF32(src[(y1 * w + x1) * c + ch]);
+    const float top = v00 * (1.0f - lx) + v01 * lx, bot = v10 * (1.0f - lx) + v11 * lx;
+    out[i] = fromF32<T>(top * (1.0f - ly) + bot * ly);
+  }
+}
+
+} // namespace ttb
+
+using namespace ttb;
+
+extern "C" {
+
+int ttb_cumprod(const void *in, void *out, int dtype, size_t outer, size_t len, size_t inner, void *stream) {
+  TTB_CHECK(in && out, "null tensor");
+  if (outer * len * inner == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("cumprod", 0, double(outer) * len * inner * 2 * dtypeSize(dtype), st);
+  const int grid = gridFor(outer * inner, 256);
+  switch (dtype) {
+  case kF32: cumprodKernel<float, double><<<grid, 256, 0, st>>>(static_cast<const float *>(in), static_cast<float *>(out), outer, len, inner); break;
+  case kBF16: cumprodKernel<__nv_bfloat16, float><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(in), static_cast<__nv_bfloat16 *>(out), outer, len, inner); break;
+  case kF16: cumprodKernel<__half, float><<<grid, 256, 0, st>>>(static_cast<const __half *>(in), static_cast<__half *>(out), outer, len, inner); break;
+  case kI32: cumprodKernel<int32_t, long long><<<grid, 256, 0, st>>>(static_cast<const int32_t *>(in), static_cast<int32_t *>(out), outer, len, inner); break;
+  default: setLastError("cumprod: unsupported dtype"); return TTB_ERR_UNSUPPORTED;
+  }
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_prod(const void *in, void *out, int dtype, size_t outer, size_t len, size_t inner, void *stream) {
+  TTB_CHECK(in && out, "null tensor");
+  if (outer * inner == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("prod", 0, double(outer) * len * inner * dtypeSize(dtype), st);
+#define TTB_PROD(T)                                                                                                        \
+  if (inner == 1) {                                                                                                        \
+    prodRowKernel<T><<<static_cast<unsigned>((outer + 7) / 8), 256, 0, st>>>(static_cast<const T *>(in), static_cast<T *>(out), outer, len); \
+  } else {                                                                                                                 \
+    prodColKernel<T><<<gridFor(outer * inner, 256), 256, 0, st>>>(static_cast<const T *>(in), static_cast<T *>(out), outer, len, inner);    \
+  }
+  switch (dtype) {
+  case kF32: TTB_PROD(float) break;
+  case kBF16: TTB_PROD(__nv_bfloat16) break;
+  case kF16: TTB_PROD(__half) break;
+  case kI32:
+    prodIntKernel<<<gridFor(outer * inner, 256), 256, 0, st>>>(static_cast<const int32_t *>(in), static_cast<int32_t *>(out), outer, len, inner);
+    break;
+  default: setLastError("prod: unsupported dtype"); return TTB_ERR_UNSUPPORTED;
+  }
+#undef TTB_PROD
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_batch_norm_inference(const void *x, const void *mean, const void *var, const void *weight, const void *bias, void *y,
+                             int dtype, size_t outer, size_t channels, size_t inner, float eps, void *stream) {
+  TTB_CHECK(x && mean && var && y, "null tensor");
+  const size_t total = outer * channels * inner;
+  if (total == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("batch_norm", 0, double(total) * 2 * dtypeSize(dtype), st);
+  const int grid = gridFor(total, 256);
+#define TTB_BN(T)                                                                                                          \
+  batchNormInferenceKernel<T><<<grid, 256, 0, st>>>(static_cast<const T *>(x), static_cast<const T *>(mean), static_cast<const T *>(var), \
+                                                    static_cast<const T *>(weight), static_cast<const T *>(bias), static_cast<T *>(y), \
+                                                    total, channels, inner, eps)
+  switch (dtype) {
+  case kF32: TTB_BN(float); break;
+  case kBF16: TTB_BN(__nv_bfloat16); break;
+  case kF16: TTB_BN(__half); break;
+  default: setLastError("batch_norm: unsupported dtype"); return TTB_ERR_UNSUPPORTED;
+  }
+#undef TTB_BN
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_upsample2d(const void *in, void *out, int dtype, size_t n, size_t h, size_t w, size_t c, int scale_h, int scale_w,
+                   int bilinear, void *stream) {
+  TTB_CHECK(in && out, "null tensor");
+  TTB_CHECK(scale_h >= 1 && scale_w >= 1, "scale factors must be positive");
+  const size_t total = n * h * scale_h * w * scale_w * c;
+  if (total == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("upsample", 0, double(total + n * h * w * c) * dtypeSize(dtype), st);
+  const int grid = gridFor(total, 256);
+#define TTB_UP(T) upsampleKernel<T><<<grid, 256, 0, st>>>(static_cast<const T *>(in), static_cast<T *>(out), n, h, w, c, scale_h, scale_w, bilinear)
+  switch (dtype) {
+  case kF32: TTB_UP(float); break;
+  case kBF16: TTB_UP(__nv_bfloat16); break;
+  case kF16: TTB_UP(__half); break;
+  default: setLastError("upsample: unsupported dtype"); return TTB_ERR_UNSUPPORTED;
+  }
+#undef TTB_UP
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+} // extern "C"

@@ -100,10 +100,25 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     IN1_OUT(MeshPartitionOp, in)
     IN1_OUT(ReductionArgMaxOp, in)
     IN1_OUT(CumSumOp, in)
+    IN1_OUT(CumProdOp, in)
+    IN1_OUT(ReductionProdOp, in)
+    IN1_OUT(UpsampleOp, in)
+    IN1_OUT(PrepareConv2dWeightsOp, weight_tensor)
+    IN1_OUT(PrepareConv2dBiasOp, bias_tensor)
     IN1_OUT(Pool2dOp, in)
     IN1_OUT(GlobalAvgPool2dOp, in)
     IN1_OUT(PadOp, in)
 #undef IN1_OUT
+  case OpType::BatchNormInferenceOp: {
+    const auto *o = op->type_as_BatchNormInferenceOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->running_mean());
+    pushRef(ins, o->running_var());
+    pushRef(ins, o->weight());
+    pushRef(ins, o->bias());
+    pushRef(outs, o->out());
+    break;
+  }
   case OpType::LayerNormOp: {
     const auto *o = op->type_as_LayerNormOp();
     pushRef(ins, o->input());
@@ -558,6 +573,11 @@ private:
   void runLayerNorm(const fbt::LayerNormOp *op);
   void runArgMax(const fbt::ReductionArgMaxOp *op);
   void runCumSum(const fbt::CumSumOp *op);
+  void runCumProd(const fbt::CumProdOp *op);
+  void runReductionProd(const fbt::ReductionProdOp *op);
+  void runBatchNormInference(const fbt::BatchNormInferenceOp *op);
+  void runUpsample(const fbt::UpsampleOp *op);
+  void runPrepareConv2d(const fbt::TensorRef *in, const fbt::TensorRef *out);
   void runEmbedding(const fbt::EmbeddingOp *op);
   void runGather(const fbt::GatherOp *op);
   void runScatter(const fbt::ScatterOp *op);
@@ -900,6 +920,20 @@ size_t Executor::runOp(size_t i) {
   case OpType::LayerNormOp: runLayerNorm(op->type_as_LayerNormOp()); break;
   case OpType::ReductionArgMaxOp: runArgMax(op->type_as_ReductionArgMaxOp()); break;
   case OpType::CumSumOp: runCumSum(op->type_as_CumSumOp()); break;
+  case OpType::CumProdOp: runCumProd(op->type_as_CumProdOp()); break;
+  case OpType::ReductionProdOp: runReductionProd(op->type_as_ReductionProdOp()); break;
+  case OpType::BatchNormInferenceOp: runBatchNormInference(op->type_as_BatchNormInferenceOp()); break;
+  case OpType::UpsampleOp: runUpsample(op->type_as_UpsampleOp()); break;
+  case OpType::PrepareConv2dWeightsOp: {
+    const auto *o = op->type_as_PrepareConv2dWeightsOp();
+    runPrepareConv2d(o->weight_tensor(), o->out());
+    break;
+  }
+  case OpType::PrepareConv2dBiasOp: {
+    const auto *o = op->type_as_PrepareConv2dBiasOp();
+    runPrepareConv2d(o->bias_tensor(), o->out());
+    break;
+  }
   case OpType::EmbeddingOp: runEmbedding(op->type_as_EmbeddingOp()); break;
   case OpType::GatherOp: runGather(op->type_as_GatherOp()); break;
   case OpType::ScatterOp: runScatter(op->type_as_ScatterOp()); break;
@@ -1917,6 +1951,8 @@ void Executor::runConv2d(const fbt::Conv2dOp *op, int act, const fbt::TensorRef 
   if (!outRef) outRef = op->out();
   TensorPtr x = getDevice(op->input()), w = getDevice(op->weight());
   TensorPtr bias = op->bias() ? getDevice(op->bias()) : nullptr;
+  if (w->preparedFrom) w = w->preparedFrom;            // prepare_conv2d_weights handed the original on
+  if (bias && bias->preparedFrom) bias = bias->preparedFrom;
   TensorPtr extra = extraRef ? getDevice(extraRef) : nullptr;
   TensorPtr out = allocOut(outRef);
   if (extra) TTRT_ASSERT(extra->volume() == out->volume() && extra->dtype == out->dtype, "fused epilogue operand must match the result");
@@ -2362,6 +2398,107 @@ void Executor::runCumSum(const fbt::CumSumOp *op) {
     TTB_CALL(ttb_cumsum(in->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(in->dtype), outer, len, inner, r.stream));
   });
   put(op->out(), out);
+}
+
+void Executor::runCumProd(const fbt::CumProdOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(out->dtype == in->dtype && out->volume() == in->volume(), "cumprod with a type change is not supported");
+  size_t rank = in->shape.size();
+  TTRT_ASSERT(rank > 0, "cumprod of a scalar");
+  int d = normDim(op->dim(), rank);
+  size_t outer = prod(in->shape, 0, d), len = in->shape[d], inner = prod(in->shape, d + 1, rank);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_cumprod(in->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(in->dtype), outer, len, inner, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// Product over one dimension, or over all of them when dim_arg is absent (operations/reduction/prod.cpp).
+void Executor::runReductionProd(const fbt::ReductionProdOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(out->dtype == in->dtype, "prod with a type change is not supported");
+  size_t rank = in->shape.size();
+  size_t outer = 1, len = in->volume(), inner = 1;
+  if (op->dim_arg().has_value()) {
+    TTRT_ASSERT(rank > 0, "prod over a dimension of a scalar");
+    int d = normDim(static_cast<int>(*op->dim_arg()), rank);
+    outer = prod(in->shape, 0, d);
+    len = in->shape[d];
+    inner = prod(in->shape, d + 1, rank);
+  }
+  TTRT_ASSERT(out->volume() == outer * inner, "prod result has ", out->volume(), " elements, expected ", outer * inner);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_prod(in->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(in->dtype), outer, len, inner, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// Inference batch norm over the channel dimension (dim 1, NCHW, as ::ttnn::batch_norm takes it).
+void Executor::runBatchNormInference(const fbt::BatchNormInferenceOp *op) {
+  TensorPtr x = getDevice(op->input()), mean = getDevice(op->running_mean()), var = getDevice(op->running_var());
+  TensorPtr w = op->weight() ? getDevice(op->weight()) : nullptr, b = op->bias() ? getDevice(op->bias()) : nullptr;
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(x->shape.size() >= 2, "batch_norm expects [N, C, ...]");
+  const size_t outer = x->shape[0], channels = x->shape[1], inner = prod(x->shape, 2, x->shape.size());
+  TTRT_ASSERT(mean->volume() == channels && var->volume() == channels && (!w || w->volume() == channels) &&
+                  (!b || b->volume() == channels),
+              "batch_norm statistics and parameters must have one entry per channel (", channels, ")");
+  TTRT_ASSERT(mean->dtype == x->dtype && var->dtype == x->dtype && (!w || w->dtype == x->dtype) && (!b || b->dtype == x->dtype) &&
+                  out->dtype == x->dtype && out->volume() == x->volume(),
+              "batch_norm tensors must share one data type");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_batch_norm_inference(x->shards[i]->ptr, mean->shards[i]->ptr, var->shards[i]->ptr, w ? w->shards[i]->ptr : nullptr,
+                                      b ? b->shards[i]->ptr : nullptr, out->shards[i]->ptr, ttbDtype(x->dtype), outer, channels,
+                                      inner, op->epsilon(), r.stream));
+  });
+  put(op->out(), out);
+}
+
+// NHWC upsampling by integer factors, "nearest" or "bilinear" (operations/pool/upsample.cpp).
+void Executor::runUpsample(const fbt::UpsampleOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(in->shape.size() == 4, "upsample expects [N, H, W, C]");
+  int sy = 1, sx = 1;
+  if (const auto *u = op->scale_factor_as_UniformScale2D()) {
+    sy = sx = u->scale();
+  } else if (const auto *nu = op->scale_factor_as_NonUniformScale2D()) {
+    TTRT_ASSERT(nu->scale() && nu->scale()->size() == 2, "upsample scale must have 2 entries");
+    sy = nu->scale()->Get(0);
+    sx = nu->scale()->Get(1);
+  } else {
+    TTRT_FATAL("upsample without a scale factor");
+  }
+  const std::string mode = op->mode() ? op->mode()->str() : "nearest";
+  TTRT_ASSERT(mode == "nearest" || mode == "bilinear", "upsample mode ", mode, " is not supported");
+  TTRT_ASSERT(sy >= 1 && sx >= 1 && out->dtype == in->dtype && out->shape.size() == 4 && out->shape[0] == in->shape[0] &&
+                  out->shape[1] == in->shape[1] * static_cast<uint32_t>(sy) && out->shape[2] == in->shape[2] * static_cast<uint32_t>(sx) &&
+                  out->shape[3] == in->shape[3],
+              "upsample result shape differs from input x scale");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_upsample2d(in->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(in->dtype), in->shape[0], in->shape[1], in->shape[2],
+                            in->shape[3], sy, sx, mode == "bilinear" ? 1 : 0, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// prepare_conv2d_weights / prepare_conv2d_bias: TTNN re-tiles and shards the tensor for its convolution kernels and
+// the flatbuffer declares that layout's shape; nothing of it applies here.  The result keeps the declared shape as
+// metadata and carries the tensor it was made from, which is what conv2d then reads.
+void Executor::runPrepareConv2d(const fbt::TensorRef *inRef, const fbt::TensorRef *outRef) {
+  TensorPtr in = getDevice(inRef);
+  auto t = std::make_shared<TensorImpl>();
+  t->shape = refShape(outRef);
+  t->stride = denseStrides(t->shape);
+  t->dtype = in->dtype;
+  t->storage = in->storage;
+  t->layout = refLayout(outRef);
+  t->shards = in->shards;
+  t->device = in->device;
+  t->preparedFrom = in->preparedFrom ? in->preparedFrom : in;
+  put(outRef, t);
 }
 
 // out[..., :] = weight[input[...], :]; a weight of shape [1, 1, V, D] is a [V, D] table.

@@ -172,6 +172,10 @@ struct TensorImpl {
   // The tensor was never assembled: its producer scattered it, row block by row block, into the
   // all-reduce workspaces of the ranks that will sum the blocks.  Only that all-reduce may read it.
   bool pushedForAllReduce = false;
+  // Result of prepare_conv2d_weights / prepare_conv2d_bias: the tensor the op was given, handed on unchanged (the
+  // preparation TTNN does is a Tenstorrent tile / shard layout; these kernels take the weights as they are).
+  // conv2d uses it in place of the declared operand.
+  std::shared_ptr<TensorImpl> preparedFrom;
 
   size_t volume() const {
     size_t v = 1;

@@ -244,6 +244,38 @@ S.table("ReductionArgMaxOp", [
 S.table("CumSumOp", [
     ("in", "TensorRef"), ("out", "TensorRef"), ("dim", "i32"), ("dtype", "DataType", OPT),
     ("memcfg", "MemoryConfig")])
+# operations/cumprod.fbs, operations/reduction.fbs (prod), operations/normalization.fbs (batch norm),
+# operations/pool.fbs (upsample), operations/conv.fbs (weight / bias preparation)
+S.table("CumProdOp", [
+    ("in", "TensorRef"), ("out", "TensorRef"), ("dim", "i32"), ("dtype", "DataType", OPT),
+    ("memcfg", "MemoryConfig")])
+S.table("ReductionProdOp", [
+    ("in", "TensorRef"), ("out", "TensorRef"), ("dim_arg", "i64", OPT), ("keep_dim", "bool"),
+    ("memcfg", "MemoryConfig")])
+S.table("BatchNormInferenceOp", [
+    ("input", "TensorRef"), ("running_mean", "TensorRef"), ("running_var", "TensorRef"), ("epsilon", "f32"),
+    ("weight", "TensorRef"), ("bias", "TensorRef"), ("memory_config", "MemoryConfig"), ("out", "TensorRef"),
+    ("compute_config", "DeviceComputeKernelConfig")])
+S.table("UniformScale2D", [("scale", "i32")])
+S.table("NonUniformScale2D", [("scale", "[i32]")])
+S.union("Scale2D", ["UniformScale2D", "NonUniformScale2D"])
+S.table("UpsampleOp", [
+    ("in", "TensorRef"), ("scale_factor", "Scale2D"), ("mode", "string"), ("memory_config", "MemoryConfig"),
+    ("out", "TensorRef")])
+S.table("PrepareConv2dWeightsOp", [
+    ("weight_tensor", "TensorRef"), ("out", "TensorRef"), ("input_memory_config", "MemoryConfig"),
+    ("input_tensor_layout", "TensorLayout"), ("weights_format", "string"), ("in_channels", "u32"),
+    ("out_channels", "u32"), ("batch_size", "u32"), ("input_height", "u32"), ("input_width", "u32"),
+    ("kernel_size", "[i32]"), ("stride", "[i32]"), ("padding", "[i32]"), ("dilation", "[i32]"), ("has_bias", "bool"),
+    ("groups", "u32"), ("device", "DeviceRef"), ("input_dtype", "DataType"), ("output_dtype", "DataType", OPT),
+    ("conv2d_config", "opaque"), ("compute_config", "DeviceComputeKernelConfig"), ("conv2d_slice_config", "opaque")])
+S.table("PrepareConv2dBiasOp", [
+    ("bias_tensor", "TensorRef"), ("out", "TensorRef"), ("input_memory_config", "MemoryConfig"),
+    ("input_tensor_layout", "TensorLayout"), ("in_channels", "u32"), ("out_channels", "u32"), ("batch_size", "u32"),
+    ("input_height", "u32"), ("input_width", "u32"), ("kernel_size", "[i32]"), ("stride", "[i32]"), ("padding", "[i32]"),
+    ("dilation", "[i32]"), ("groups", "u32"), ("device", "DeviceRef"), ("input_dtype", "DataType"),
+    ("output_dtype", "DataType", OPT), ("conv2d_config", "opaque"), ("compute_config", "DeviceComputeKernelConfig"),
+    ("conv2d_slice_config", "opaque")])
 # operations/data_movement.fbs: gather / scatter / sort; operations/reduction.fbs: top-k / sampling
 S.enum("ScatterReduceType", "u8", {"Sum": 0, "Max": 2, "Min": 3, "Prod": 6, "Invalid": 7})
 S.table("ScatterOp", [

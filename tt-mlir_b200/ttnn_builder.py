@@ -322,7 +322,7 @@ class ProgramBuilder:
         """x is [1, 1, N*H*W, C] (the flattened form the compiler emits) or [N, H, W, C];
         w is [O, C/groups, kH, kW]; bias [1, 1, 1, O].  Output keeps x's rank.  `out_dtype` "Int32" for a
         convolution on quantized (8-bit integer) operands, whose result is the accumulator."""
-        o, cg, kh, kw = w.shape
+        o, cg, kh, kw = getattr(w, "filter_shape", w.shape)   # a prepared weight remembers its filter's shape
         c = cg * groups
         pad = list(padding) if len(padding) == 4 else [padding[0], padding[1], padding[0], padding[1]]
         ho = (height + pad[0] + pad[2] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
@@ -561,6 +561,73 @@ class ProgramBuilder:
     def cumsum(self, x: Value, dim: int, loc=None) -> Value:
         out = self._value(x.shape, x.dtype)
         self._emit("CumSumOp", {"in": x.ref, "out": out.ref, "dim": dim, "memcfg": self._mc()}, [x], [out], loc)
+        return out
+
+    def cumprod(self, x: Value, dim: int, loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        self._emit("CumProdOp", {"in": x.ref, "out": out.ref, "dim": dim, "memcfg": self._mc()}, [x], [out], loc)
+        return out
+
+    def prod(self, x: Value, dim: Optional[int] = None, keep_dim: bool = False, loc=None) -> Value:
+        """Product over one dimension, or over all of them (dim None), as ::ttnn::prod takes it."""
+        if dim is None:
+            shape = [1] * len(x.shape) if keep_dim else []
+        else:
+            d = dim % len(x.shape)
+            shape = [s if i != d else 1 for i, s in enumerate(x.shape)] if keep_dim else [s for i, s in enumerate(x.shape) if i != d]
+        out = self._value(shape, x.dtype)
+        self._emit("ReductionProdOp", {"in": x.ref, "out": out.ref, "dim_arg": dim, "keep_dim": keep_dim, "memcfg": self._mc()},
+                   [x], [out], loc)
+        return out
+
+    def batch_norm_inference(self, x: Value, mean: Value, var: Value, weight: Optional[Value], bias: Optional[Value],
+                             epsilon: float = 1e-5, loc=None) -> Value:
+        """x is [N, C, ...]; statistics and parameters have C entries."""
+        out = self._value(x.shape, x.dtype)
+        ins = [x, mean, var] + [t for t in (weight, bias) if t is not None]
+        self._emit("BatchNormInferenceOp", {
+            "input": x.ref, "running_mean": mean.ref, "running_var": var.ref, "epsilon": epsilon,
+            "weight": weight.ref if weight else None, "bias": bias.ref if bias else None, "memory_config": self._mc(),
+            "out": out.ref}, ins, [out], loc)
+        return out
+
+    def upsample(self, x: Value, scale, mode: str = "nearest", loc=None) -> Value:
+        """x is NHWC; scale an integer or (scale_h, scale_w)."""
+        sy, sx = (scale, scale) if isinstance(scale, int) else scale
+        out = self._value([x.shape[0], x.shape[1] * sy, x.shape[2] * sx, x.shape[3]], x.dtype)
+        sf = ("UniformScale2D", {"scale": scale}) if isinstance(scale, int) else ("NonUniformScale2D", {"scale": [sy, sx]})
+        self._emit("UpsampleOp", {"in": x.ref, "scale_factor": sf, "mode": mode, "memory_config": self._mc(), "out": out.ref},
+                   [x], [out], loc)
+        return out
+
+    def prepare_conv2d_weights(self, w: Value, batch: int, height: int, width: int, stride=(1, 1), padding=(0, 0, 0, 0),
+                               dilation=(1, 1), groups: int = 1, has_bias: bool = True, loc=None) -> Value:
+        """The op the compiler's optimizer puts in front of conv2d.  The declared result shape is TTNN's prepared
+        layout ([1, 1, kH*kW*C rounded up to 32, O rounded up to 32]); the value remembers the filter's own shape so
+        that conv2d can still be described."""
+        o, cg, kh, kw = w.shape
+        up = lambda v: (v + 31) // 32 * 32
+        out = self._value([1, 1, up(kh * kw * cg * groups), up(o)], w.dtype)
+        out.filter_shape = list(w.shape)
+        pad = list(padding) if len(padding) == 4 else [padding[0], padding[1], padding[0], padding[1]]
+        self._emit("PrepareConv2dWeightsOp", {
+            "weight_tensor": w.ref, "out": out.ref, "input_memory_config": self._mc(), "input_tensor_layout": "Tile",
+            "weights_format": "OIHW", "in_channels": cg * groups, "out_channels": o, "batch_size": batch,
+            "input_height": height, "input_width": width, "kernel_size": [kh, kw], "stride": list(stride), "padding": pad,
+            "dilation": list(dilation), "has_bias": has_bias, "groups": groups, "device": self.device_ref,
+            "input_dtype": w.dtype, "output_dtype": w.dtype}, [w], [out], loc)
+        return out
+
+    def prepare_conv2d_bias(self, bias: Value, w_shape, batch: int, height: int, width: int, stride=(1, 1),
+                            padding=(0, 0, 0, 0), dilation=(1, 1), groups: int = 1, loc=None) -> Value:
+        o, cg, kh, kw = w_shape
+        out = self._value([1, 1, 32, (o + 31) // 32 * 32], bias.dtype)
+        pad = list(padding) if len(padding) == 4 else [padding[0], padding[1], padding[0], padding[1]]
+        self._emit("PrepareConv2dBiasOp", {
+            "bias_tensor": bias.ref, "out": out.ref, "input_memory_config": self._mc(), "input_tensor_layout": "Tile",
+            "in_channels": cg * groups, "out_channels": o, "batch_size": batch, "input_height": height, "input_width": width,
+            "kernel_size": [kh, kw], "stride": list(stride), "padding": pad, "dilation": list(dilation), "groups": groups,
+            "device": self.device_ref, "input_dtype": bias.dtype, "output_dtype": bias.dtype}, [bias], [out], loc)
         return out
 
     def embedding(self, indices: Value, weight: Value, loc=None) -> Value:

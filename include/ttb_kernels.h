@@ -212,6 +212,19 @@ TTB_API int ttb_batch_norm_inference(const void *x, const void *mean, const void
  * (bilinear = 0) or bilinear with align_corners = false. */
 TTB_API int ttb_upsample2d(const void *in, void *out, int dtype, size_t n, size_t h, size_t w, size_t c, int scale_h,
                            int scale_w, int bilinear, void *stream);
+/* ::ttnn::group_norm (operations/normalization/group_norm.cpp) on channels-last [images, 1, pixels, channels]: a
+ * group is channels / groups consecutive channels; mean and biased variance over a group's pixels of one image in
+ * f32, then scale / shift per channel (weight / bias nullable, `channels` entries). */
+TTB_API int ttb_group_norm(const void *x, const void *weight, const void *bias, void *y, int dtype, size_t images,
+                           size_t pixels, size_t channels, size_t groups, float eps, void *stream);
+/* ::ttnn::conv_transpose2d (operations/conv/conv_transpose2d.cpp): NHWC input [n, h, w, c], weights
+ * [c, o / groups, kh, kw], bias [o] (nullable), NHWC output with
+ * ho = (h - 1) * stride_h - 2 * pad_top + dil_h * (kh - 1) + out_pad_h + 1 (likewise wo); f32 accumulation, one
+ * rounding.  A CUDA-core kernel. */
+TTB_API int ttb_conv_transpose2d(const void *x, const void *weight, const void *bias, void *out, int dtype, int64_t n,
+                                 int64_t h, int64_t w, int64_t c, int64_t o, int kh, int kw, int stride_h, int stride_w,
+                                 int pad_top, int pad_left, int out_pad_h, int out_pad_w, int dil_h, int dil_w, int groups,
+                                 void *stream);
 /* ::ttnn::cumsum (operations/cumsum/cumsum.cpp): running sum along the middle dimension. */
 TTB_API int ttb_cumsum(const void *in, void *out, int dtype, size_t outer, size_t len, size_t inner,
                        void *stream);

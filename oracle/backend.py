@@ -190,6 +190,23 @@ class OracleBuilder:
 
     def upsample(self, x, scale, mode="nearest", loc=None): return _map(lambda t: ops.upsample2d(t, scale, mode), x)
 
+    def group_norm(self, x, weight, bias, num_groups, epsilon=1e-5, loc=None):
+        return _map(lambda t, w, b: ops.group_norm(t, w, b, num_groups, epsilon), x, weight, bias)
+
+    def conv_transpose2d(self, x, w, bias, batch, height, width, stride=(1, 1), padding=(0, 0), output_padding=(0, 0),
+                         dilation=(1, 1), groups=1, loc=None):
+        return _map(lambda t, wt, b: ops.conv_transpose2d(t, wt, b, batch, height, width, stride, padding, output_padding, dilation,
+                                                          groups), x, w, bias)
+
+    def conv1d(self, x, w, bias, batch, length, stride=1, padding=(0, 0), dilation=1, groups=1, loc=None):
+        return _map(lambda t, wt, b: ops.conv1d(t, wt, b, stride, padding, dilation, groups), x, w, bias)
+
+    def bitcast_convert(self, x, dtype, loc=None):
+        return _map(lambda t: t.view(TORCH_DTYPE[dtype]), x)
+
+    def nlp_concat_heads(self, x, loc=None):
+        return _map(lambda t: t.permute(0, 2, 1, 3).reshape(t.shape[0], 1, t.shape[2], t.shape[1] * t.shape[3]), x)
+
     # the preparation ops change nothing a CPU evaluation can see
     def prepare_conv2d_weights(self, w, *a, **k): return w
     def prepare_conv2d_bias(self, bias, *a, **k): return bias

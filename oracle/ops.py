@@ -286,6 +286,33 @@ def upsample2d(x, scale, mode="nearest"):
     return out.permute(0, 2, 3, 1).contiguous().to(x.dtype)
 
 
+def group_norm(x, weight, bias, num_groups, epsilon):
+    """tools/golden/mapping.py:1541-1574: channels-last [N, 1, H*W, C] in, torch group_norm on the NCHW view in f32."""
+    w = None if weight is None else weight.float().reshape(-1)
+    b = None if bias is None else bias.float().reshape(-1)
+    r = F.group_norm(x.float().permute(0, 3, 1, 2), num_groups=num_groups, weight=w, bias=b, eps=epsilon)
+    return r.permute(0, 2, 3, 1).contiguous().to(x.dtype)
+
+
+def conv_transpose2d(x, w, bias, batch, height, width, stride, padding, output_padding, dilation, groups):
+    """tools/golden/mapping.py:804-893: NHWC (possibly flattened) in, torch conv_transpose2d on the NCHW view with f32
+    accumulation, NHWC out in the input's form."""
+    c = w.shape[0]
+    nchw = x.reshape(batch, height, width, c).permute(0, 3, 1, 2).float()
+    r = F.conv_transpose2d(nchw, w.float(), None if bias is None else bias.float().reshape(-1), stride=tuple(stride),
+                           padding=tuple(padding), output_padding=tuple(output_padding), dilation=tuple(dilation), groups=groups)
+    r = r.permute(0, 2, 3, 1).contiguous().to(x.dtype)
+    return r.reshape(1, 1, -1, r.shape[-1]) if x.dim() == 4 and x.shape[0] == 1 and x.shape[1] == 1 and batch * height * width == x.shape[2] else r
+
+
+def conv1d(x, w, bias, stride, padding, dilation, groups):
+    """tools/golden/mapping.py:502-574: NLC in, torch conv1d on the NCL view (asymmetric padding applied first), NLC out."""
+    ncl = F.pad(x.float().permute(0, 2, 1), [padding[0], padding[1]])
+    r = F.conv1d(ncl, w.float(), None if bias is None else bias.float().reshape(-1), stride=stride, padding=0, dilation=dilation,
+                 groups=groups)
+    return r.permute(0, 2, 1).contiguous().to(x.dtype)
+
+
 def embedding(indices, weight):  # ttir_cpu.py embedding: leading 1-dims of the table are dropped
     w = weight
     while w.dim() > 2 and w.shape[0] == 1:

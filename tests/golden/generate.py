@@ -423,6 +423,35 @@ def main():
     spec3 = torch.empty(2, 18, 18, 5)
     store(out, "map/upsample/nearest_x3", one(ref.upsample2d_golden(gmt(ux), gmt(spec3), 3, mode="nearest")))
 
+    # --- group_norm (channels-last), conv_transpose2d, conv1d (mapping.py:1541-1574, 804-893, 502-574)
+    gx = rnd(2, 1, 20, 12)
+    gw, gb = rnd(12) * 0.5 + 1.0, rnd(12) * 0.2
+    for n, t in (("x", gx), ("weight", gw), ("bias", gb)):
+        store(out, f"map/group_norm/{n}", t)
+    store(out, "map/group_norm/g3", one(ref.ttir_group_norm_golden(gmt(gx), gmt(gw), gmt(gb), S.IntegerAttr(3), S.FloatAttr(1e-5), S.F32Type())))
+    store(out, "map/group_norm/g12_noaffine", one(ref.ttir_group_norm_golden(gmt(gx), None, None, S.IntegerAttr(12), S.FloatAttr(1e-5),
+                                                                            S.F32Type())))
+    tx = rnd(2, 5, 6, 8)                                        # NHWC
+    tw, tb = rnd(8, 6, 3, 3) * 0.3, rnd(1, 1, 1, 6) * 0.1       # [C_in, C_out, kH, kW]
+    for n, t in (("x", tx), ("w", tw), ("b", tb)):
+        store(out, f"map/conv_transpose/{n}", t)
+    nhwc = (S.IntegerAttr(0), S.IntegerAttr(1), S.IntegerAttr(2), S.IntegerAttr(3))
+    store(out, "map/conv_transpose/s2_p1_op1", one(ref.conv_transpose2d_golden(
+        gmt(tx), gmt(tw), gmt(tb), S.DenseI32ArrayAttr([2, 2]), S.DenseI32ArrayAttr([1, 1]), S.DenseI32ArrayAttr([1, 1]),
+        S.DenseI32ArrayAttr([1, 1]), S.IntegerAttr(1), *nhwc)))
+    twg = rnd(8, 3, 2, 3) * 0.3                                 # groups 2: [C_in, C_out / 2, kH, kW]
+    store(out, "map/conv_transpose/w_g2", twg)
+    store(out, "map/conv_transpose/g2_s1x2_d2", one(ref.conv_transpose2d_golden(
+        gmt(tx), gmt(twg), None, S.DenseI32ArrayAttr([1, 2]), S.DenseI32ArrayAttr([0, 1]), S.DenseI32ArrayAttr([0, 0]),
+        S.DenseI32ArrayAttr([2, 1]), S.IntegerAttr(2), *nhwc)))
+    ox = rnd(3, 17, 8)                                          # NLC
+    ow, ob = rnd(10, 8, 4) * 0.3, rnd(1, 1, 10) * 0.1
+    for n, t in (("x", ox), ("w", ow), ("b", ob)):
+        store(out, f"map/conv1d/{n}", t)
+    nlc = (S.IntegerAttr(0), S.IntegerAttr(1), S.IntegerAttr(2))
+    store(out, "map/conv1d/s2_p1x2", one(ref.conv1d_golden(gmt(ox), gmt(ow), gmt(ob), S.IntegerAttr(2), S.DenseI32ArrayAttr([1, 2]),
+                                                           S.IntegerAttr(1), S.IntegerAttr(1), *nlc)))
+
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ttir_cpu_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes")

@@ -101,3 +101,58 @@ def test_conv2d_through_prepared_weights_and_bias(rt, device):
     direct, _ = run_body(rt, device, raw, [x, w, bias])
     assert torch.equal(got[0], direct[0])
     assert_matches(got[0], want[0], "conv2d on prepared weights", (0.999, 2e-2, 2.0 ** -6))
+
+
+def test_group_norm_matches_the_reference_goldens(rt, device, golden):
+    x, w, b_ = (golden[f"map/group_norm/{n}"] for n in ("x", "weight", "bias"))
+    got, want = run_body(rt, device, lambda b, xv, wv, bv: b.group_norm(xv, wv, bv, 3, 1e-5), [x, w, b_])
+    assert torch.allclose(got[0], golden["map/group_norm/g3"], rtol=1e-5, atol=2e-6) and torch.allclose(got[0], want[0], rtol=1e-5, atol=2e-6)
+    got, _ = run_body(rt, device, lambda b, xv: b.group_norm(xv, None, None, 12, 1e-5), [x])
+    assert torch.allclose(got[0], golden["map/group_norm/g12_noaffine"], rtol=1e-5, atol=2e-6)
+    torch.manual_seed(2)
+    xb = torch.randn(3, 1, 196, 64).to(torch.bfloat16)
+    wb, bb = (torch.randn(64) * 0.5 + 1).to(torch.bfloat16), (torch.randn(64) * 0.2).to(torch.bfloat16)
+    got, want = run_body(rt, device, lambda b, xv, wv, bv: b.group_norm(xv, wv, bv, 8, 1e-5), [xb, wb, bb])
+    assert_matches(got[0], want[0], "group norm bf16", (0.999, 1e-2, 2.0 ** -7))
+
+
+def test_conv_transpose2d_matches_the_reference_goldens(rt, device, golden):
+    x, w, b_ = (golden[f"map/conv_transpose/{n}"] for n in ("x", "w", "b"))
+    got, want = run_body(rt, device, lambda b, xv, wv, bv: b.conv_transpose2d(xv, wv, bv, 2, 5, 6, stride=(2, 2), padding=(1, 1),
+                                                                              output_padding=(1, 1)), [x, w, b_])
+    assert got[0].shape == golden["map/conv_transpose/s2_p1_op1"].shape
+    assert torch.allclose(got[0], golden["map/conv_transpose/s2_p1_op1"], rtol=1e-5, atol=1e-5)
+    assert torch.allclose(got[0], want[0], rtol=1e-5, atol=1e-5)
+    wg = golden["map/conv_transpose/w_g2"]
+    got, _ = run_body(rt, device, lambda b, xv, wv: b.conv_transpose2d(xv, wv, None, 2, 5, 6, stride=(1, 2), padding=(0, 1),
+                                                                       dilation=(2, 1), groups=2), [x, wg])
+    assert torch.allclose(got[0], golden["map/conv_transpose/g2_s1x2_d2"], rtol=1e-5, atol=1e-5)
+    torch.manual_seed(3)                                        # bf16, flattened activations as the compiler emits them
+    xb = torch.randn(1, 1, 2 * 7 * 7, 32).to(torch.bfloat16)
+    wb = (torch.randn(32, 16, 2, 2) * 0.1).to(torch.bfloat16)
+    got, want = run_body(rt, device, lambda b, xv, wv: b.conv_transpose2d(xv, wv, None, 2, 7, 7, stride=(2, 2)), [xb, wb])
+    assert list(got[0].shape) == [1, 1, 2 * 14 * 14, 16]
+    assert_matches(got[0], want[0], "conv_transpose2d bf16", (0.999, 1e-2, 2.0 ** -7))
+
+
+def test_conv1d_matches_the_reference_golden(rt, device, golden):
+    x, w, b_ = (golden[f"map/conv1d/{n}"] for n in ("x", "w", "b"))
+    got, want = run_body(rt, device, lambda b, xv, wv, bv: b.conv1d(xv, wv, bv, 3, 17, stride=2, padding=(1, 2)), [x, w, b_])
+    assert got[0].shape == golden["map/conv1d/s2_p1x2"].shape
+    assert torch.allclose(got[0], golden["map/conv1d/s2_p1x2"], rtol=1e-4, atol=1e-5) and torch.allclose(got[0], want[0], rtol=1e-4, atol=1e-5)
+    torch.manual_seed(4)
+    xb = torch.randn(2, 300, 64).to(torch.bfloat16)
+    wb = (torch.randn(128, 64, 3) * 0.05).to(torch.bfloat16)
+    bb = torch.randn(1, 1, 128).to(torch.bfloat16)
+    got, want = run_body(rt, device, lambda b, xv, wv, bv: b.conv1d(xv, wv, bv, 2, 300, padding=(1, 1)), [xb, wb, bb])
+    assert_matches(got[0], want[0], "conv1d bf16", (0.999, 2e-2, 2.0 ** -6))
+
+
+def test_bitcast_convert_and_nlp_concat_heads(rt, device):
+    torch.manual_seed(6)
+    x = torch.randn(4, 33)
+    got, want = run_body(rt, device, lambda b, v: b.bitcast_convert(v, "Int32"), [x])
+    assert torch.equal(got[0], x.view(torch.int32)) and torch.equal(want[0], got[0])
+    h = torch.randn(2, 4, 9, 32).to(torch.bfloat16)
+    got, want = run_body(rt, device, lambda b, v: b.nlp_concat_heads(v), [h])
+    assert torch.equal(got[0], h.permute(0, 2, 1, 3).reshape(2, 1, 9, 128)) and torch.equal(want[0], got[0])

@@ -264,6 +264,19 @@ def test_cumprod_prod_batch_norm_upsample(golden):
     assert torch.allclose(ops.upsample2d(ux, 2, "bilinear"), golden["map/upsample/bilinear_x2"], atol=1e-6, rtol=0)
 
 
+def test_group_norm_conv_transpose_conv1d(golden):
+    """Restatements against the reference's goldens (tools/golden/mapping.py:1541-1574, 804-893, 502-574)."""
+    x, w, b = (golden[f"map/group_norm/{n}"] for n in ("x", "weight", "bias"))
+    assert torch.equal(ops.group_norm(x, w, b, 3, 1e-5), golden["map/group_norm/g3"])
+    assert torch.equal(ops.group_norm(x, None, None, 12, 1e-5), golden["map/group_norm/g12_noaffine"])
+    x, w, b = (golden[f"map/conv_transpose/{n}"] for n in ("x", "w", "b"))
+    assert torch.equal(ops.conv_transpose2d(x, w, b, 2, 5, 6, (2, 2), (1, 1), (1, 1), (1, 1), 1), golden["map/conv_transpose/s2_p1_op1"])
+    assert torch.equal(ops.conv_transpose2d(x, golden["map/conv_transpose/w_g2"], None, 2, 5, 6, (1, 2), (0, 1), (0, 0), (2, 1), 2),
+                       golden["map/conv_transpose/g2_s1x2_d2"])
+    x, w, b = (golden[f"map/conv1d/{n}"] for n in ("x", "w", "b"))
+    assert torch.equal(ops.conv1d(x, w, b, 2, (1, 2), 1, 1), golden["map/conv1d/s2_p1x2"])
+
+
 def test_layer_norm(golden):
     x, w, b = golden["ln/x"], golden["ln/w"], golden["ln/b"]
     assert same(ops.layer_norm(x), golden["ln/plain"])

@@ -121,6 +121,86 @@ __global__ void __launch_bounds__(256) upsampleKernel(const T *__restrict__ in, 
   }
 }
 
+// group_norm on channels-last tensors [N, 1, H*W, C] (::ttnn::group_norm, operations/normalization/group_norm.cpp;
+// golden tools/golden/mapping.py:1541-1574: torch group_norm on the NCHW view): a group is C / G consecutive channels,
+// its statistics run over all pixels of one image.  One block per (image, group): mean, then the centred sum of
+// squares (the numerically safe form), then the normalised values scaled and shifted per channel; passes two and
+// three hit L1 / L2.
+__device__ __forceinline__ float extraBlockSum(float v, float *scratch /* 33 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarp ? scratch[lane] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  const float r = scratch[32];
+  __syncthreads();
+  return r;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) groupNormKernel(const T *__restrict__ x, const T *__restrict__ weight, const T *__restrict__ bias,
+                                                       T *__restrict__ y, size_t pixels, size_t channels, size_t groups, float eps) {
+  __shared__ float scratch[33];
+  const size_t img = blockIdx.x / groups, g = blockIdx.x % groups, cg = channels / groups;
+  const T *xi = x + img * pixels * channels + g * cg;
+  T *yi = y + img * pixels * channels + g * cg;
+  const size_t count = pixels * cg;
+  float s = 0.0f;
+  for (size_t i = threadIdx.x; i < count; i += blockDim.x) s += toF32(xi[(i / cg) * channels + i % cg]);
+  const float mean = extraBlockSum(s, scratch) / static_cast<float>(count);
+  float ss = 0.0f;
+  for (size_t i = threadIdx.x; i < count; i += blockDim.x) {
+    const float d = toF32(xi[(i / cg) * channels + i % cg]) - mean;
+    ss += d * d;
+  }
+  const float rstd = rsqrtf(extraBlockSum(ss, scratch) / static_cast<float>(count) + eps);
+  for (size_t i = threadIdx.x; i < count; i += blockDim.x) {
+    const size_t c = i % cg, at = (i / cg) * channels + c;
+    float f = (toF32(xi[at]) - mean) * rstd;
+    if (weight) f *= toF32(weight[g * cg + c]);
+    if (bias) f += toF32(bias[g * cg + c]);
+    yi[at] = fromF32<T>(f);
+  }
+}
+
+// Transposed convolution, NHWC, weights [C_in, C_out / groups, kH, kW] (::ttnn::conv_transpose2d,
+// operations/conv/conv_transpose2d.cpp; golden tools/golden/mapping.py:804-893, torch conv_transpose2d).  One thread
+// per output value gathers the input pixels that reach it: output (oy, ox) receives x[iy, ix] * w[ky, kx] where
+// oy = iy * stride - pad + ky * dilation.  f32 accumulation over (ky, kx, c) in that order, one rounding.  A CUDA-core
+// kernel: the op is rare in the graphs this runtime is measured on.
+template <typename T>
+__global__ void __launch_bounds__(256) convTranspose2dKernel(const T *__restrict__ x, const T *__restrict__ w, const T *__restrict__ bias,
+                                                             T *__restrict__ y, int n, int h, int wd, int c, int o, int kh, int kw, int sh,
+                                                             int sw, int pt, int pl, int dh, int dw, int groups, int ho, int wo) {
+  const size_t total = static_cast<size_t>(n) * ho * wo * o, stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  const int cg = c / groups, og = o / groups;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int oc = static_cast<int>(i % o), ox = static_cast<int>((i / o) % wo), oy = static_cast<int>((i / o / wo) % ho);
+    const int img = static_cast<int>(i / o / wo / ho), g = oc / og, ocg = oc % og;
+    float acc = 0.0f;
+    for (int ky = 0; ky < kh; ++ky) {
+      const int ty = oy + pt - ky * dh;
+      if (ty < 0 || ty % sh != 0 || ty / sh >= h) continue;
+      for (int kx = 0; kx < kw; ++kx) {
+        const int tx = ox + pl - kx * dw;
+        if (tx < 0 || tx % sw != 0 || tx / sw >= wd) continue;
+        const T *xp = x + ((static_cast<size_t>(img) * h + ty / sh) * wd + tx / sw) * c + g * cg;
+        for (int ic = 0; ic < cg; ++ic)
+          acc += toF32(xp[ic]) * toF32(w[((static_cast<size_t>(g * cg + ic) * og + ocg) * kh + ky) * kw + kx]);
+      }
+    }
+    if (bias) acc += toF32(bias[oc]);
+    y[i] = fromF32<T>(acc);
+  }
+}
+
 } // namespace ttb
 
 using namespace ttb;
@@ -212,6 +292,61 @@ int ttb_upsample2d(const void *in, void *out, int dtype, size_t n, size_t h, siz
   default: setLastError("upsample: unsupported dtype"); return TTB_ERR_UNSUPPORTED;
   }
 #undef TTB_UP
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_group_norm(const void *x, const void *weight, const void *bias, void *y, int dtype, size_t images, size_t pixels,
+                   size_t channels, size_t groups, float eps, void *stream) {
+  TTB_CHECK(x && y, "null tensor");
+  TTB_CHECK(groups >= 1 && channels % groups == 0, "the channel count must divide by the number of groups");
+  if (images * pixels * channels == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("group_norm", 0, double(images) * pixels * channels * 2 * dtypeSize(dtype), st);
+  const unsigned grid = static_cast<unsigned>(images * groups);
+#define TTB_GN(T)                                                                                                          \
+  groupNormKernel<T><<<grid, 256, 0, st>>>(static_cast<const T *>(x), static_cast<const T *>(weight), static_cast<const T *>(bias), \
+                                           static_cast<T *>(y), pixels, channels, groups, eps)
+  switch (dtype) {
+  case kF32: TTB_GN(float); break;
+  case kBF16: TTB_GN(__nv_bfloat16); break;
+  case kF16: TTB_GN(__half); break;
+  default: setLastError("group_norm: unsupported dtype"); return TTB_ERR_UNSUPPORTED;
+  }
+#undef TTB_GN
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_conv_transpose2d(const void *x, const void *weight, const void *bias, void *out, int dtype, int64_t n, int64_t h, int64_t w,
+                         int64_t c, int64_t o, int kh, int kw, int stride_h, int stride_w, int pad_top, int pad_left, int out_pad_h,
+                         int out_pad_w, int dil_h, int dil_w, int groups, void *stream) {
+  TTB_CHECK(x && weight && out, "null tensor");
+  TTB_CHECK(n > 0 && h > 0 && w > 0 && c > 0 && o > 0 && kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0 && dil_h > 0 && dil_w > 0 &&
+                groups > 0 && c % groups == 0 && o % groups == 0 && pad_top >= 0 && pad_left >= 0 && out_pad_h >= 0 && out_pad_w >= 0,
+            "bad convolution extents");
+  const int64_t ho = (h - 1) * stride_h - 2 * pad_top + dil_h * (kh - 1) + out_pad_h + 1;
+  const int64_t wo = (w - 1) * stride_w - 2 * pad_left + dil_w * (kw - 1) + out_pad_w + 1;
+  TTB_CHECK(ho > 0 && wo > 0 && n * ho * wo * o < (1ll << 40) && h < (1 << 30) && w < (1 << 30) && ho < (1 << 30) && wo < (1 << 30),
+            "bad output extents");
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("conv_transpose2d", 2.0 * double(n) * h * w * c * (o / groups) * kh * kw,
+                 (double(n) * h * w * c + double(n) * ho * wo * o) * dtypeSize(dtype), st);
+  const int grid = gridFor(static_cast<size_t>(n * ho * wo * o), 256);
+#define TTB_CT(T)                                                                                                          \
+  convTranspose2dKernel<T><<<grid, 256, 0, st>>>(static_cast<const T *>(x), static_cast<const T *>(weight), static_cast<const T *>(bias), \
+                                                 static_cast<T *>(out), static_cast<int>(n), static_cast<int>(h), static_cast<int>(w), \
+                                                 static_cast<int>(c), static_cast<int>(o), kh, kw, stride_h, stride_w, pad_top, pad_left, \
+                                                 dil_h, dil_w, groups, static_cast<int>(ho), static_cast<int>(wo))
+  switch (dtype) {
+  case kF32: TTB_CT(float); break;
+  case kBF16: TTB_CT(__nv_bfloat16); break;
+  case kF16: TTB_CT(__half); break;
+  default: setLastError("conv_transpose2d: unsupported dtype"); return TTB_ERR_UNSUPPORTED;
+  }
+#undef TTB_CT
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;

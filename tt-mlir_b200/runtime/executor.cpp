@@ -101,6 +101,8 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     IN1_OUT(ReductionArgMaxOp, in)
     IN1_OUT(CumSumOp, in)
     IN1_OUT(CumProdOp, in)
+    IN1_OUT(BitcastConvertOp, in)
+    IN1_OUT(NLPConcatHeadsOp, in)
     IN1_OUT(ReductionProdOp, in)
     IN1_OUT(UpsampleOp, in)
     IN1_OUT(PrepareConv2dWeightsOp, weight_tensor)
@@ -109,6 +111,31 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     IN1_OUT(GlobalAvgPool2dOp, in)
     IN1_OUT(PadOp, in)
 #undef IN1_OUT
+  case OpType::GroupNormOp: {
+    const auto *o = op->type_as_GroupNormOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->input_mask());
+    pushRef(ins, o->weight());
+    pushRef(ins, o->bias());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::ConvTranspose2dOp: {
+    const auto *o = op->type_as_ConvTranspose2dOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->weight());
+    pushRef(ins, o->bias());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::Conv1dOp: {
+    const auto *o = op->type_as_Conv1dOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->weight());
+    pushRef(ins, o->bias());
+    pushRef(outs, o->out());
+    break;
+  }
   case OpType::BatchNormInferenceOp: {
     const auto *o = op->type_as_BatchNormInferenceOp();
     pushRef(ins, o->input());
@@ -574,6 +601,11 @@ private:
   void runArgMax(const fbt::ReductionArgMaxOp *op);
   void runCumSum(const fbt::CumSumOp *op);
   void runCumProd(const fbt::CumProdOp *op);
+  void runGroupNorm(const fbt::GroupNormOp *op);
+  void runConvTranspose2d(const fbt::ConvTranspose2dOp *op);
+  void runConv1d(const fbt::Conv1dOp *op);
+  void runBitcastConvert(const fbt::BitcastConvertOp *op);
+  void runNlpConcatHeads(const fbt::NLPConcatHeadsOp *op);
   void runReductionProd(const fbt::ReductionProdOp *op);
   void runBatchNormInference(const fbt::BatchNormInferenceOp *op);
   void runUpsample(const fbt::UpsampleOp *op);
@@ -921,6 +953,11 @@ size_t Executor::runOp(size_t i) {
   case OpType::ReductionArgMaxOp: runArgMax(op->type_as_ReductionArgMaxOp()); break;
   case OpType::CumSumOp: runCumSum(op->type_as_CumSumOp()); break;
   case OpType::CumProdOp: runCumProd(op->type_as_CumProdOp()); break;
+  case OpType::GroupNormOp: runGroupNorm(op->type_as_GroupNormOp()); break;
+  case OpType::ConvTranspose2dOp: runConvTranspose2d(op->type_as_ConvTranspose2dOp()); break;
+  case OpType::Conv1dOp: runConv1d(op->type_as_Conv1dOp()); break;
+  case OpType::BitcastConvertOp: runBitcastConvert(op->type_as_BitcastConvertOp()); break;
+  case OpType::NLPConcatHeadsOp: runNlpConcatHeads(op->type_as_NLPConcatHeadsOp()); break;
   case OpType::ReductionProdOp: runReductionProd(op->type_as_ReductionProdOp()); break;
   case OpType::BatchNormInferenceOp: runBatchNormInference(op->type_as_BatchNormInferenceOp()); break;
   case OpType::UpsampleOp: runUpsample(op->type_as_UpsampleOp()); break;
@@ -2433,6 +2470,110 @@ void Executor::runReductionProd(const fbt::ReductionProdOp *op) {
     TTB_CALL(ttb_prod(in->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(in->dtype), outer, len, inner, r.stream));
   });
   put(op->out(), out);
+}
+
+// group_norm on channels-last [N, 1, H*W, C] (or [N, H, W, C]): operations/normalization/group_norm.cpp.
+void Executor::runGroupNorm(const fbt::GroupNormOp *op) {
+  TTRT_ASSERT(!op->input_mask(), "group_norm with an input mask (a Tenstorrent core-grid artefact) is not supported");
+  TensorPtr x = getDevice(op->input());
+  TensorPtr w = op->weight() ? getDevice(op->weight()) : nullptr, b = op->bias() ? getDevice(op->bias()) : nullptr;
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(x->shape.size() == 4, "group_norm expects [N, 1, H*W, C]");
+  const size_t images = x->shape[0], channels = x->shape[3], pixels = static_cast<size_t>(x->shape[1]) * x->shape[2];
+  const size_t groups = static_cast<size_t>(op->num_groups());
+  TTRT_ASSERT(groups >= 1 && channels % groups == 0, "group_norm: ", channels, " channels do not divide into ", groups, " groups");
+  TTRT_ASSERT((!w || (w->volume() == channels && w->dtype == x->dtype)) && (!b || (b->volume() == channels && b->dtype == x->dtype)) &&
+                  out->dtype == x->dtype && out->volume() == x->volume(),
+              "group_norm parameters must have one entry per channel and the input's data type");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_group_norm(x->shards[i]->ptr, w ? w->shards[i]->ptr : nullptr, b ? b->shards[i]->ptr : nullptr, out->shards[i]->ptr,
+                            ttbDtype(x->dtype), images, pixels, channels, groups, op->epsilon(), r.stream));
+  });
+  put(op->out(), out);
+}
+
+// conv_transpose2d on NHWC activations (flattened to [1, 1, N*H*W, C] or not), weights [C_in, C_out / groups, kH, kW].
+void Executor::runConvTranspose2d(const fbt::ConvTranspose2dOp *op) {
+  TensorPtr x = getDevice(op->input()), w = getDevice(op->weight());
+  TensorPtr bias = op->bias() ? getDevice(op->bias()) : nullptr;
+  TensorPtr out = allocOut(op->out());
+  auto two = [](const fb::Vector<int32_t> *v, const char *what, int &a, int &b) {
+    TTRT_ASSERT(v && (v->size() == 2 || v->size() == 4), "conv_transpose2d ", what, " must have 2 entries");
+    a = v->Get(0);
+    b = v->Get(1);
+  };
+  int kh, kw, sh, sw, ph, pw, oph, opw, dh, dw;
+  two(op->kernel_size(), "kernel_size", kh, kw);
+  two(op->stride(), "stride", sh, sw);
+  two(op->padding(), "padding", ph, pw);
+  two(op->output_padding(), "output_padding", oph, opw);
+  two(op->dilation(), "dilation", dh, dw);
+  const int64_t N = op->batch_size(), H = op->input_height(), W = op->input_width(), C = op->in_channels(), O = op->out_channels();
+  TTRT_ASSERT(static_cast<int64_t>(x->volume()) == N * H * W * C, "conv_transpose2d input has ", x->volume(), " elements, expected ",
+              N * H * W * C);
+  TTRT_ASSERT(x->dtype == w->dtype && x->dtype == out->dtype && (!bias || bias->dtype == x->dtype),
+              "conv_transpose2d tensors must share one data type");
+  const int64_t ho = (H - 1) * sh - 2 * ph + dh * (kh - 1) + oph + 1, wo = (W - 1) * sw - 2 * pw + dw * (kw - 1) + opw + 1;
+  TTRT_ASSERT(static_cast<int64_t>(out->volume()) == N * ho * wo * O, "conv_transpose2d result has ", out->volume(),
+              " elements, expected ", N * ho * wo * O);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_conv_transpose2d(x->shards[i]->ptr, w->shards[i]->ptr, bias ? bias->shards[i]->ptr : nullptr, out->shards[i]->ptr,
+                                  ttbDtype(x->dtype), N, H, W, C, O, kh, kw, sh, sw, ph, pw, oph, opw, dh, dw,
+                                  static_cast<int>(op->groups()), r.stream));
+  });
+  put(op->out(), out);
+}
+
+// conv1d over [N, L, C] activations (flattened or not) with weights [O, C / groups, K]: a conv2d with one row.
+void Executor::runConv1d(const fbt::Conv1dOp *op) {
+  TensorPtr x = getDevice(op->input()), w = getDevice(op->weight());
+  TensorPtr bias = op->bias() ? getDevice(op->bias()) : nullptr;
+  TensorPtr out = allocOut(op->out());
+  const int64_t N = op->batch_size(), L = op->input_length(), C = op->in_channels(), O = op->out_channels();
+  const int K = static_cast<int>(op->kernel_size()), stride = static_cast<int>(op->stride()), dil = static_cast<int>(op->dilation());
+  TTRT_ASSERT(op->padding() && (op->padding()->size() == 1 || op->padding()->size() == 2), "conv1d padding must have 1 or 2 entries");
+  const int pl = op->padding()->Get(0), pr = op->padding()->size() == 2 ? op->padding()->Get(1) : pl;
+  int pad[4] = {0, pl, 0, pr}; // top, left, bottom, right
+  TTRT_ASSERT(static_cast<int64_t>(x->volume()) == N * L * C, "conv1d input has ", x->volume(), " elements, expected ", N * L * C);
+  TTRT_ASSERT(x->dtype == w->dtype && x->dtype == out->dtype, "conv1d tensors must share one data type");
+  const int groups = static_cast<int>(op->groups());
+  size_t wsBytes = ttb_conv2d_workspace_bytes(ttbDtype(x->dtype), N, 1, L, C, O, 1, K, 1, stride, pad, 1, dil, groups);
+  TensorPtr ws = wsBytes ? makeDeviceTensor(dev, {static_cast<uint32_t>((wsBytes + 3) / 4)}, DataType::UInt32) : nullptr;
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_conv2d_fused(x->shards[i]->ptr, w->shards[i]->ptr, bias ? bias->shards[i]->ptr : nullptr, out->shards[i]->ptr,
+                              ttbDtype(x->dtype), bias ? ttbDtype(bias->dtype) : 0, N, 1, L, C, O, 1, K, 1, stride, pad, 1, dil, groups,
+                              TTB_ACT_NONE, nullptr, TTB_EXTRA_NONE, ws ? ws->shards[i]->ptr : nullptr, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// bitcast_convert: the same bytes under another element type of the same width (operations/layout/bitcast_convert.cpp).
+void Executor::runBitcastConvert(const fbt::BitcastConvertOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TTRT_ASSERT(dataTypeSize(op->dtype()) == dataTypeSize(in->dtype), "bitcast_convert between types of different widths");
+  auto view = std::make_shared<TensorImpl>();
+  view->shape = refShape(op->out());
+  view->stride = denseStrides(view->shape);
+  view->dtype = op->dtype();
+  view->storage = in->storage;
+  view->layout = refLayout(op->out());
+  view->shards = in->shards;
+  view->device = in->device;
+  TTRT_ASSERT(view->volume() == in->volume(), "bitcast_convert changes the element count");
+  put(op->out(), view);
+}
+
+// [B, H, S, D] -> [B, 1, S, H*D] (operations/transformer/nlp_concat_heads.cpp): concatenate_heads with a unit dimension.
+void Executor::runNlpConcatHeads(const fbt::NLPConcatHeadsOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TTRT_ASSERT(in->shape.size() == 4, "nlp_concat_heads expects [batch, heads, seq, head_dim]");
+  uint32_t B = in->shape[0], H = in->shape[1], S = in->shape[2], D = in->shape[3];
+  std::vector<int64_t> dense = denseStrides(in->shape);
+  TensorPtr t = stridedView(in, {B, S, H, D}, {dense[0], dense[2], dense[1], dense[3]}, 0, in->dtype);
+  t->shape = {B, 1, S, H * D};
+  t->stride = denseStrides(t->shape);
+  TTRT_ASSERT(t->shape == refShape(op->out()), "nlp_concat_heads result shape differs from the op's result type");
+  put(op->out(), t);
 }
 
 // Inference batch norm over the channel dimension (dim 1, NCHW, as ::ttnn::batch_norm takes it).

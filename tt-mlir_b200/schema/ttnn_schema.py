@@ -256,6 +256,24 @@ S.table("BatchNormInferenceOp", [
     ("input", "TensorRef"), ("running_mean", "TensorRef"), ("running_var", "TensorRef"), ("epsilon", "f32"),
     ("weight", "TensorRef"), ("bias", "TensorRef"), ("memory_config", "MemoryConfig"), ("out", "TensorRef"),
     ("compute_config", "DeviceComputeKernelConfig")])
+S.table("GroupNormOp", [
+    ("input", "TensorRef"), ("input_mask", "TensorRef"), ("weight", "TensorRef"), ("bias", "TensorRef"),
+    ("num_groups", "i64"), ("epsilon", "f32"), ("memory_config", "MemoryConfig"), ("out", "TensorRef")])
+S.table("ConvTranspose2dOp", [
+    ("input", "TensorRef"), ("weight", "TensorRef"), ("bias", "TensorRef"), ("out", "TensorRef"),
+    ("device", "DeviceRef"), ("in_channels", "u32"), ("out_channels", "u32"), ("batch_size", "u32"),
+    ("input_height", "u32"), ("input_width", "u32"), ("kernel_size", "[i32]"), ("stride", "[i32]"),
+    ("padding", "[i32]"), ("output_padding", "[i32]"), ("dilation", "[i32]"), ("groups", "u32"),
+    ("output_dtype", "DataType", OPT), ("conv2d_config", "opaque"), ("compute_config", "DeviceComputeKernelConfig"),
+    ("memory_config", "MemoryConfig"), ("conv2d_slice_config", "opaque")])
+S.table("Conv1dOp", [
+    ("input", "TensorRef"), ("weight", "TensorRef"), ("bias", "TensorRef"), ("out", "TensorRef"),
+    ("device", "DeviceRef"), ("in_channels", "u32"), ("out_channels", "u32"), ("batch_size", "u32"),
+    ("input_length", "u32"), ("kernel_size", "u32"), ("stride", "u32"), ("padding", "[i32]"), ("dilation", "u32"),
+    ("groups", "u32"), ("output_dtype", "DataType", OPT), ("conv2d_config", "opaque"),
+    ("compute_config", "DeviceComputeKernelConfig"), ("conv2d_slice_config", "opaque")])
+S.table("BitcastConvertOp", [("in", "TensorRef"), ("dtype", "DataType"), ("memcfg", "MemoryConfig"), ("out", "TensorRef")])
+S.table("NLPConcatHeadsOp", [("in", "TensorRef"), ("out", "TensorRef"), ("memcfg", "MemoryConfig")])
 S.table("UniformScale2D", [("scale", "i32")])
 S.table("NonUniformScale2D", [("scale", "[i32]")])
 S.union("Scale2D", ["UniformScale2D", "NonUniformScale2D"])

@@ -600,6 +600,57 @@ class ProgramBuilder:
                    [x], [out], loc)
         return out
 
+    def group_norm(self, x: Value, weight: Optional[Value], bias: Optional[Value], num_groups: int, epsilon: float = 1e-5,
+                   loc=None) -> Value:
+        """x is channels-last [N, 1, H*W, C]; weight / bias have C entries."""
+        out = self._value(x.shape, x.dtype)
+        self._emit("GroupNormOp", {
+            "input": x.ref, "weight": weight.ref if weight else None, "bias": bias.ref if bias else None,
+            "num_groups": num_groups, "epsilon": epsilon, "memory_config": self._mc(), "out": out.ref},
+            [x] + [t for t in (weight, bias) if t is not None], [out], loc)
+        return out
+
+    def conv_transpose2d(self, x: Value, w: Value, bias: Optional[Value], batch: int, height: int, width: int, stride=(1, 1),
+                         padding=(0, 0), output_padding=(0, 0), dilation=(1, 1), groups: int = 1, loc=None) -> Value:
+        """x is [1, 1, N*H*W, C] or [N, H, W, C]; w is [C, O/groups, kH, kW]; bias [1, 1, 1, O]."""
+        c, og, kh, kw = w.shape
+        o = og * groups
+        ho = (height - 1) * stride[0] - 2 * padding[0] + dilation[0] * (kh - 1) + output_padding[0] + 1
+        wo = (width - 1) * stride[1] - 2 * padding[1] + dilation[1] * (kw - 1) + output_padding[1] + 1
+        flat = x.shape[:2] == [1, 1] and len(x.shape) == 4 and x.shape[2] == batch * height * width
+        out = self._value([1, 1, batch * ho * wo, o] if flat else [batch, ho, wo, o], x.dtype)
+        self._emit("ConvTranspose2dOp", {
+            "input": x.ref, "weight": w.ref, "bias": bias.ref if bias else None, "out": out.ref, "device": self.device_ref,
+            "in_channels": c, "out_channels": o, "batch_size": batch, "input_height": height, "input_width": width,
+            "kernel_size": [kh, kw], "stride": list(stride), "padding": list(padding), "output_padding": list(output_padding),
+            "dilation": list(dilation), "groups": groups, "output_dtype": x.dtype, "memory_config": self._mc()},
+            [x, w] + ([bias] if bias else []), [out], loc)
+        return out
+
+    def conv1d(self, x: Value, w: Value, bias: Optional[Value], batch: int, length: int, stride: int = 1, padding=(0, 0),
+               dilation: int = 1, groups: int = 1, loc=None) -> Value:
+        """x is [N, L, C]; w is [O, C/groups, K]; bias [1, 1, O]."""
+        o, cg, k = w.shape
+        lo = (length + padding[0] + padding[1] - dilation * (k - 1) - 1) // stride + 1
+        out = self._value([batch, lo, o], x.dtype)
+        self._emit("Conv1dOp", {
+            "input": x.ref, "weight": w.ref, "bias": bias.ref if bias else None, "out": out.ref, "device": self.device_ref,
+            "in_channels": cg * groups, "out_channels": o, "batch_size": batch, "input_length": length, "kernel_size": k,
+            "stride": stride, "padding": list(padding), "dilation": dilation, "groups": groups, "output_dtype": x.dtype},
+            [x, w] + ([bias] if bias else []), [out], loc)
+        return out
+
+    def bitcast_convert(self, x: Value, dtype: str, loc=None) -> Value:
+        out = self._value(x.shape, dtype)
+        self._emit("BitcastConvertOp", {"in": x.ref, "dtype": dtype, "memcfg": self._mc(), "out": out.ref}, [x], [out], loc)
+        return out
+
+    def nlp_concat_heads(self, x: Value, loc=None) -> Value:
+        b, h, s_, d = x.shape
+        out = self._value([b, 1, s_, h * d], x.dtype)
+        self._emit("NLPConcatHeadsOp", {"in": x.ref, "out": out.ref, "memcfg": self._mc()}, [x], [out], loc)
+        return out
+
     def prepare_conv2d_weights(self, w: Value, batch: int, height: int, width: int, stride=(1, 1), padding=(0, 0, 0, 0),
                                dilation=(1, 1), groups: int = 1, has_bias: bool = True, loc=None) -> Value:
         """The op the compiler's optimizer puts in front of conv2d.  The declared result shape is TTNN's prepared

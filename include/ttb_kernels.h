@@ -225,6 +225,29 @@ TTB_API int ttb_conv_transpose2d(const void *x, const void *weight, const void *
                                  int64_t h, int64_t w, int64_t c, int64_t o, int kh, int kw, int stride_h, int stride_w,
                                  int pad_top, int pad_left, int out_pad_h, int out_pad_w, int dil_h, int dil_w, int groups,
                                  void *stream);
+/* ::ttnn::batch_norm with training = true (operations/normalization/batch_norm.cpp:45-72) on [outer, channels, inner]:
+ * normalises with the batch mean and the biased batch variance of each channel and moves `running_mean` /
+ * `running_var` in place: running = momentum * batch + (1 - momentum) * running.  weight / bias nullable. */
+TTB_API int ttb_batch_norm_training(const void *x, void *running_mean, void *running_var, const void *weight, const void *bias,
+                                    void *y, int dtype, size_t outer, size_t channels, size_t inner, float eps, float momentum,
+                                    void *stream);
+/* ::ttnn::max_pool2d with return_indices (operations/pool/pool2d.cpp, MaxPool2dWithIndicesOp): NHWC, symmetric
+ * padding [pad_top, pad_left]; `indices` (Int32, UInt32 or UInt16) holds iy * w + ix of each maximum inside its
+ * image's plane; the first maximum wins. */
+TTB_API int ttb_max_pool2d_with_indices(const void *in, void *out, void *indices, int dtype, int index_dtype, int n, int h, int w,
+                                        int c, int ho, int wo, int kh, int kw, int stride_h, int stride_w, int pad_top,
+                                        int pad_left, int dil_h, int dil_w, void *stream);
+/* ::ttnn::experimental::rotary_embedding_llama (operations/transformer/rotary_embedding_llama.cpp):
+ * y = x * cos + (x @ T) * sin with the 32 x 32 matrix `trans_mat` applied to every 32-wide piece of the head
+ * dimension.  x is [rows, head_dim]; row r reads cache row (r / cos_div) % cos_mod. */
+TTB_API int ttb_rotary_embedding_llama(const void *x, const void *cos_cache, const void *sin_cache, const void *trans_mat, void *y,
+                                       int dtype, size_t rows, size_t head_dim, size_t cos_mod, size_t cos_div, void *stream);
+/* ::ttnn::experimental::dropout (operations/eltwise/unary/dropout.cpp): zero with probability `prob`, else x * scale.
+ * Counter-based generator: the result depends only on (seed, stream_id, element index). */
+TTB_API int ttb_dropout(const void *x, void *y, int dtype, size_t n, float prob, float scale, uint32_t seed, uint32_t stream_id,
+                        void *stream);
+/* ::ttnn::rand (operations/rand/rand.cpp): uniform values in [low, high). */
+TTB_API int ttb_rand_uniform(void *y, int dtype, size_t n, float low, float high, uint32_t seed, uint32_t stream_id, void *stream);
 /* ::ttnn::cumsum (operations/cumsum/cumsum.cpp): running sum along the middle dimension. */
 TTB_API int ttb_cumsum(const void *in, void *out, int dtype, size_t outer, size_t len, size_t inner,
                        void *stream);
@@ -569,6 +592,9 @@ TTB_API int ttb_reduce_scatter(void *comm, const void *in, void *out, size_t rec
                                int reduce_type, void *stream);
 TTB_API int ttb_broadcast(void *comm, const void *in, void *out, size_t count, int dtype, int root,
                           void *stream);
+/* ::ttnn::point_to_point (operations/ccl/point_to_point.cpp): the sender's half and the receiver's half of one copy. */
+TTB_API int ttb_send(void *comm, const void *in, size_t count, int dtype, int peer, void *stream);
+TTB_API int ttb_recv(void *comm, void *out, size_t count, int dtype, int peer, void *stream);
 
 /* ---- all-reduce over peer memory (NVLink loads/stores, no NCCL in the data path).
  * A "symm" object is one rank's view of a set of workspaces, one per rank of a 1xN mesh, each

@@ -207,6 +207,38 @@ class OracleBuilder:
     def nlp_concat_heads(self, x, loc=None):
         return _map(lambda t: t.permute(0, 2, 1, 3).reshape(t.shape[0], 1, t.shape[2], t.shape[1] * t.shape[3]), x)
 
+    def assign(self, x, dtype=None, loc=None): return _map(lambda t: t.clone().to(TORCH_DTYPE[dtype]) if dtype else t.clone(), x)
+    def pow_scalar(self, x, exponent, loc=None): return _map(lambda t: ops.pow_scalar(t, exponent), x)
+    def annotate(self, x, annotation, loc=None): return x
+    def region_start(self, x, region_id, loc=None): return x
+    def region_end(self, x, region_id, loc=None): return x
+    def breakpoint(self, x, loc=None): return None
+    def print_message(self, x, message, loc=None): return None
+    def memory_snapshot(self, x, file_path, loc=None): return None
+
+    def nlp_create_qkv_heads_decode(self, x, num_heads, num_kv_heads=None, batch_offset=None, slice_size=None, loc=None):
+        off = int(batch_offset.t.reshape(-1)[0]) if batch_offset is not None else 0
+        q, k, v = ops.nlp_create_qkv_heads_decode(x.t, num_heads, num_kv_heads, off, slice_size)
+        return OValue(q), OValue(k), OValue(v)
+
+    def nlp_concat_heads_decode(self, x, num_heads, loc=None): return _map(lambda t: ops.nlp_concat_heads_decode(t, num_heads), x)
+
+    def rotary_embedding_llama(self, x, cos, sin, trans_mat, is_decode_mode=False, loc=None):
+        return _map(lambda t, c, s, m: ops.rotary_embedding_llama(t, c, s, m, is_decode_mode), x, cos, sin, trans_mat)
+
+    def max_pool2d_with_indices(self, x, batch, height, width, channels, kernel=(2, 2), stride=(2, 2), padding=(0, 0), dilation=(1, 1),
+                                ceil_mode=False, index_dtype="Int32", loc=None):
+        y, idx = ops.max_pool2d_with_indices(x.t, batch, height, width, channels, kernel, stride, padding, dilation, ceil_mode)
+        return OValue(y), OValue(idx.to(TORCH_DTYPE[index_dtype]))
+
+    def batch_norm_training(self, x, mean, var, weight, bias, epsilon=1e-5, momentum=0.1, loc=None):
+        y, m, v = ops.batch_norm_training(x.t, mean.t, var.t, weight.t if weight is not None else None,
+                                          bias.t if bias is not None else None, epsilon, momentum)
+        mean.t, var.t = m, v                                    # the running statistics are updated in place
+        return OValue(y)
+
+    def prepare_conv_transpose2d_weights(self, w, *a, **k): return w
+    def prepare_conv_transpose2d_bias(self, bias, *a, **k): return bias
     # the preparation ops change nothing a CPU evaluation can see
     def prepare_conv2d_weights(self, w, *a, **k): return w
     def prepare_conv2d_bias(self, bias, *a, **k): return bias
@@ -329,6 +361,12 @@ class OracleBuilder:
         return OValue(ops.mesh_shard_shard_to_full(x.t, shard_dim))
 
     def all_reduce(self, x, reduce_type=0, cluster_axis=1, loc=None): return OValue(ops.all_reduce(x.t, reduce_type))
+    def all_reduce_async(self, x, reduce_type=0, cluster_axis=1, loc=None): return OValue(ops.all_reduce(x.t, reduce_type))
+
+    def point_to_point(self, x, sender_coord, receiver_coord, output=None, loc=None):
+        lin = lambda c: c[0] * self.mesh_shape[1] + c[1]
+        return OValue(ops.point_to_point(x.t, lin(sender_coord), lin(receiver_coord), output.t if output is not None else None))
+
     def all_gather(self, x, dim, cluster_axis=1, loc=None): return OValue(ops.all_gather(x.t, dim))
     def reduce_scatter(self, x, dim, reduce_type=0, cluster_axis=1, loc=None): return OValue(ops.reduce_scatter(x.t, dim, reduce_type))
     def mesh_partition(self, x, dim, cluster_axis=1, loc=None): return OValue(ops.mesh_partition(x.t, dim))

@@ -510,6 +510,15 @@ def reduce_scatter(shards, dim, reduce_type=0):
     return [c.contiguous() for c in torch.chunk(r, len(shards), dim=dim)]
 
 
+def point_to_point(shards, sender, receiver, output=None):
+    """::ttnn::point_to_point (runtime/lib/ttnn/operations/ccl/point_to_point.cpp): every coordinate keeps its shard of
+    the output tensor (the input when none is given), the receiver's becomes the sender's shard of the input."""
+    base = output if output is not None else shards
+    out = [s.clone() for s in base]
+    out[receiver] = shards[sender].clone()
+    return out
+
+
 def mesh_partition(shards, dim):
     n = len(shards)
     return [torch.chunk(s, n, dim=dim)[i].contiguous() for i, s in enumerate(shards)]
@@ -598,3 +607,72 @@ def paged_sdpa_decode(q, k_cache, v_cache, page_table, cur_pos=None, is_causal=T
         m = m * (scale if scale is not None else d ** -0.5)
     o = F.scaled_dot_product_attention(q.float().permute(0, 2, 1, 3), kk, vv, attn_mask=m, scale=scale, is_causal=False)
     return o.permute(0, 2, 1, 3).to(q.dtype)
+
+
+def pow_scalar(x: torch.Tensor, exponent) -> torch.Tensor:
+    """tools/golden/mapping.py:10447-10450 (torch.pow(lhs, exponent)); evaluated in f32, one rounding."""
+    return torch.pow(x.float(), float(exponent)).to(x.dtype)
+
+
+def batch_norm_training(x, running_mean, running_var, weight, bias, eps: float, momentum: float):
+    """tools/golden/mapping.py:4979-5063: batch mean and biased batch variance over every dimension but 1 normalise x
+    ((x - mean) / sqrt(var + eps) * weight + bias); the running statistics become
+    momentum * batch + (1 - momentum) * running.  Returns (y, new_running_mean, new_running_var)."""
+    dt = x.dtype
+    xf = x.float()
+    dims = [0] + list(range(2, xf.ndim))
+    shape = [1, -1] + [1] * (xf.ndim - 2)
+    mean = xf.mean(dim=dims)
+    var = ((xf - mean.reshape(shape)) ** 2).sum(dim=dims) / (xf.numel() // xf.shape[1])
+    y = (xf - mean.reshape(shape)) / torch.sqrt(var.reshape(shape) + eps)
+    if weight is not None:
+        y = y * weight.float().reshape(shape)
+    if bias is not None:
+        y = y + bias.float().reshape(shape)
+    new_mean = mean * momentum + running_mean.float().reshape(-1) * (1 - momentum)
+    new_var = var * momentum + running_var.float().reshape(-1) * (1 - momentum)
+    return y.to(dt), new_mean.reshape(running_mean.shape).to(dt), new_var.reshape(running_var.shape).to(dt)
+
+
+def max_pool2d_with_indices(x, batch, height, width, channels, kernel, stride, padding, dilation, ceil_mode):
+    """tools/golden/mapping.py:5339-5378: torch max_pool2d(return_indices=True) on the NCHW view of NHWC data; the
+    index is iy * W + ix inside the image's plane.  Returns flattened [1, 1, N*Ho*Wo, C] values and indices."""
+    t = x.reshape(batch, height, width, channels).permute(0, 3, 1, 2).float()
+    pad = (padding[0], padding[1])
+    y, idx = torch.nn.functional.max_pool2d(t, kernel_size=tuple(kernel), stride=tuple(stride), padding=pad, dilation=tuple(dilation),
+                                            ceil_mode=ceil_mode, return_indices=True)
+    y = y.permute(0, 2, 3, 1).reshape(1, 1, -1, channels).to(x.dtype)
+    return y, idx.permute(0, 2, 3, 1).reshape(1, 1, -1, channels)
+
+
+def rotary_embedding_llama(x, cos, sin, trans_mat, is_decode_mode: bool):
+    """::ttnn::experimental::rotary_embedding_llama (runtime/lib/ttnn/operations/transformer/rotary_embedding_llama.cpp):
+    y = x * cos + (x @ T) * sin, the 32 x 32 matrix T applied to every 32-wide piece of the head dimension.  Prefill: x
+    [1, heads, seq, D], caches [1, 1, seq, D]; decode: x [1, batch, heads, D], caches [1, batch, 1, D].  f32, one rounding."""
+    xf, d = x.float(), x.shape[-1]
+    t = trans_mat.float().reshape(-1, 32)[:32]
+    rot = (xf.reshape(*x.shape[:-1], d // 32, 32) @ t).reshape(x.shape)
+    c, s = cos.float(), sin.float()
+    if not is_decode_mode:
+        c, s = c[..., : x.shape[-2], :], s[..., : x.shape[-2], :]
+    return (xf * c + rot * s).to(x.dtype)
+
+
+def nlp_create_qkv_heads_decode(x, num_heads, num_kv_heads, batch_offset=0, slice_size=None):
+    """::ttnn::experimental::nlp_create_qkv_heads_decode: [1, 1, B, (Hq + 2 Hkv) D] -> q [1, B, Hq, D], k, v [1, B, Hkv, D]."""
+    b, hidden = x.shape[2], x.shape[3]
+    hkv = num_heads if num_kv_heads is None else num_kv_heads
+    d = hidden // (num_heads + 2 * hkv)
+    rows = x.reshape(b, hidden)
+    if slice_size is not None:
+        rows = rows[batch_offset: batch_offset + slice_size]
+    n = rows.shape[0]
+    q = rows[:, : num_heads * d].reshape(1, n, num_heads, d)
+    k = rows[:, num_heads * d: (num_heads + hkv) * d].reshape(1, n, hkv, d)
+    v = rows[:, (num_heads + hkv) * d:].reshape(1, n, hkv, d)
+    return q.contiguous(), k.contiguous(), v.contiguous()
+
+
+def nlp_concat_heads_decode(x, num_heads):
+    """::ttnn::experimental::nlp_concat_heads_decode: [1, B, padded heads, D] -> [1, 1, B, num_heads * D]."""
+    return x[:, :, :num_heads, :].reshape(1, 1, x.shape[1], num_heads * x.shape[3]).contiguous()

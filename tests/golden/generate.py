@@ -452,6 +452,20 @@ def main():
     store(out, "map/conv1d/s2_p1x2", one(ref.conv1d_golden(gmt(ox), gmt(ow), gmt(ob), S.IntegerAttr(2), S.DenseI32ArrayAttr([1, 2]),
                                                            S.IntegerAttr(1), S.IntegerAttr(1), *nlc)))
 
+    # --- training batch norm (reuses the batch_norm inputs) and max_pool2d with indices (mapping.py:4979-5063, 5339-5378)
+    tr = ref.ttir_batch_norm_training_golden(gmt(bx), gmt(bw), gmt(bb), gmt(bmean), gmt(bvar), S.FloatAttr(1e-5), S.IntegerAttr(1),
+                                             S.FloatAttr(0.1), S.F32Type(), S.F32Type(), S.F32Type())
+    for n, t in zip(("out", "new_mean", "new_var"), tr):
+        store(out, f"map/batch_norm_training/{n}", one(t))
+    mx = rnd(2, 9, 11, 6)                                       # NHWC
+    store(out, "map/max_pool_indices/x", mx)
+    for name, (k, st, pd, dl, ceil) in {"k3_s2_p1": ([3, 3], [2, 2], [1, 1, 1, 1], [1, 1], False),
+                                       "k2x3_s1x2_d2_ceil": ([2, 3], [1, 2], [0, 1, 0, 1], [2, 1], True)}.items():
+        v, ix = ref.ttir_max_pool2d_with_indices(gmt(mx), S.DenseI32ArrayAttr(k), S.DenseI32ArrayAttr(st), S.DenseI32ArrayAttr(pd),
+                                                 S.DenseI32ArrayAttr(dl), S.BoolAttr(ceil), S.F32Type())
+        store(out, f"map/max_pool_indices/{name}", one(v))
+        store(out, f"map/max_pool_indices/{name}_idx", one(ix).to(torch.int32))
+
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ttir_cpu_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes")

@@ -74,6 +74,24 @@ def test_all_reduce_all_gather_reduce_scatter(rt, mesh2):
     assert torch.equal(got[1], x) and torch.equal(got[4], x)
 
 
+def test_point_to_point_and_all_reduce_async(rt, mesh2):
+    x = torch.randn(4, 6, 16)
+    y = torch.randn(4, 6, 16)
+
+    def body(b, v, w):
+        s, t = b.distribute(v, 0), b.distribute(w, 0)
+        fwd = b.aggregate(b.point_to_point(s, [0, 0], [0, 1]), 0)               # coordinate 1 receives coordinate 0's shard
+        back = b.aggregate(b.point_to_point(s, [0, 1], [0, 0], output=t), 0)    # ... into another tensor's shards
+        same = b.aggregate(b.point_to_point(s, [0, 1], [0, 1]), 0)
+        ar = b.aggregate(b.all_reduce_async(s), None)
+        return fwd, back, same, ar
+    got, want = run_mesh(rt, mesh2, body, [x, y])
+    for i, (g, w) in enumerate(zip(got, want)):
+        assert_matches(g, w, f"output {i}", (0.9999, 1e-5, 1e-5))
+    assert torch.equal(got[0], torch.cat([x[:2], x[:2]])) and torch.equal(got[1], torch.cat([x[2:], y[2:]])) and torch.equal(got[2], x)
+    assert torch.allclose(got[3], x[:2] + x[2:], atol=1e-6)
+
+
 @pytest.mark.parametrize("m,n,k", [(192, 256, 512), (256, 512, 256), (8, 64, 64)])
 def test_all_reduce_add_read_through_mesh_partition(rt, mesh2, m, n, k):
     """all_reduce -> add(residual) -> mesh_partition along the same mesh axis: every device keeps its own block of

@@ -1,0 +1,214 @@
+"""assign, pow_scalar, the debug / serialization ops, the decode-step head ops, rotary_embedding_llama, max_pool2d with
+indices, training batch norm, dropout and rand through tt::runtime::submit, against the reference's goldens where it
+has some (tests/golden, recorded from tools/golden/mapping.py), the oracle, and distribution properties for the two
+random ops (their streams are this runtime's own)."""
+
+import os
+
+import pytest
+import torch
+
+from ttmlir_b200 import graphs
+from helpers import DTYPE_NAME, assert_matches, run_body, run_program
+
+pytestmark = pytest.mark.gpu
+
+
+def run_gpu(rt, device, body, inputs):
+    """Runs `body(b, *values)` on the GPU only (ops whose result the oracle cannot restate: random streams, files)."""
+    def graph(b):
+        vals = [b.input(list(t.shape), DTYPE_NAME[t.dtype]) for t in inputs]
+        out = body(b, *vals)
+        b.output(*(out if isinstance(out, (tuple, list)) else (out,)))
+    return run_program(rt, device, graphs.build_binary(graph), inputs)
+
+
+def test_assign_and_pow_scalar(rt, device):
+    torch.manual_seed(0)
+    x = torch.randn(7, 33)
+    got, want = run_body(rt, device, lambda b, v: (b.assign(v), b.assign(v, "BFloat16")), [x])
+    assert torch.equal(got[0], x) and torch.equal(got[1], x.to(torch.bfloat16)) and torch.equal(want[1], got[1])
+    xp = torch.rand(5, 100) * 3 + 0.1
+    got, want = run_body(rt, device, lambda b, v: (b.pow_scalar(v, 2.5), b.pow_scalar(v, 3), b.pow_scalar(v, -0.5)), [xp])
+    for g, w in zip(got, want):
+        assert torch.allclose(g, w, rtol=2e-6, atol=1e-7)
+    xb = xp.to(torch.bfloat16)
+    got, want = run_body(rt, device, lambda b, v: b.pow_scalar(v, 2.0), [xb])
+    assert_matches(got[0], want[0], "pow_scalar bf16", (0.9999, 1e-2, 2.0 ** -7))
+
+
+def test_debug_markers_pass_their_operand_on(rt, device, tmp_path, capfd):
+    torch.manual_seed(1)
+    x = torch.randn(4, 64)
+    snap = str(tmp_path / "memory.txt")
+
+    def body(b, v):
+        a = b.annotate(v, "layer 3 input")
+        r = b.region_start(a, "block0")
+        y = b.binary("Add", r, r)
+        e = b.region_end(y, "block0")
+        b.print_message(e, "reached the end of block0")
+        b.breakpoint(e)
+        b.memory_snapshot(e, snap)
+        return e
+    got, want = run_body(rt, device, body, [x])
+    assert torch.equal(got[0], x + x) and torch.equal(want[0], got[0])
+    err = capfd.readouterr().err
+    assert "reached the end of block0" in err and "breakpoint" in err
+    text = open(snap).read()
+    assert "Device 0 DRAM memory state" in text and "allocatedBytes=" in text
+
+
+def test_dump_tensor_then_load_tensor(rt, device, tmp_path):
+    torch.manual_seed(2)
+    x = torch.randn(3, 5, 32).to(torch.bfloat16)
+    path = str(tmp_path / "t.tensorbin")
+
+    def dump(b, v):
+        y = b.unary("Neg", v)
+        b.dump_tensor(y, path)
+        return y
+    got = run_gpu(rt, device, dump, [x])
+    assert torch.equal(got[0], -x) and os.path.getsize(path) > x.numel() * 2
+    back = run_gpu(rt, device, lambda b: b.unary("Abs", b.load_tensor(path, [3, 5, 32], "BFloat16")), [])
+    assert torch.equal(back[0], x.abs())
+    with pytest.raises(RuntimeError, match="does not have the op's result type"):
+        run_gpu(rt, device, lambda b: b.load_tensor(path, [3, 5, 32], "Float32"), [])
+    bad = str(tmp_path / "bad.bin")
+    open(bad, "wb").write(b"not a tensor file at all")
+    with pytest.raises(RuntimeError, match="not a tensor file"):
+        run_gpu(rt, device, lambda b: b.load_tensor(bad, [1], "Float32"), [])
+
+
+def test_nlp_create_qkv_heads_decode_and_concat_heads_decode(rt, device):
+    torch.manual_seed(3)
+    x = torch.randn(1, 1, 32, (8 + 2 * 2) * 64).to(torch.bfloat16)
+    got, want = run_body(rt, device, lambda b, v: b.nlp_create_qkv_heads_decode(v, 8, 2), [x])
+    assert [tuple(g.shape) for g in got] == [(1, 32, 8, 64), (1, 32, 2, 64), (1, 32, 2, 64)]
+    for g, w in zip(got, want):
+        assert torch.equal(g, w)
+    off = torch.tensor([8], dtype=torch.int32)
+    got, want = run_body(rt, device, lambda b, v, o: b.nlp_create_qkv_heads_decode(v, 8, 2, batch_offset=o, slice_size=16), [x, off])
+    assert tuple(got[0].shape) == (1, 16, 8, 64)
+    for g, w in zip(got, want):
+        assert torch.equal(g, w)
+    h = torch.randn(1, 32, 32, 64).to(torch.bfloat16)          # heads padded to 32, 12 real
+    got, want = run_body(rt, device, lambda b, v: b.nlp_concat_heads_decode(v, 12), [h])
+    assert tuple(got[0].shape) == (1, 1, 32, 12 * 64) and torch.equal(got[0], want[0])
+    # the decode step's attention front end: split, rotate, merge back
+    got, want = run_body(rt, device, lambda b, v: b.nlp_concat_heads_decode(b.nlp_create_qkv_heads_decode(v, 8, 2)[0], 8), [x])
+    assert torch.equal(got[0], x[..., : 8 * 64])
+
+
+def pair_swap_matrix(dtype):
+    t = torch.zeros(32, 32)
+    for i in range(0, 32, 2):
+        t[i, i + 1] = 1.0
+        t[i + 1, i] = -1.0
+    return t.reshape(1, 1, 32, 32).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rotary_embedding_llama_prefill_and_decode(rt, device, dtype):
+    torch.manual_seed(4)
+    tol = (0.9999, 1e-2, 2.0 ** -7) if dtype == torch.bfloat16 else (0.999999, 1e-5, 1e-5)
+    t = pair_swap_matrix(dtype)
+    for heads, seq, d in ((8, 128, 128), (3, 33, 64), (1, 32, 256)):
+        x = torch.randn(1, heads, seq, d).to(dtype)
+        ang = torch.rand(1, 1, seq, d // 2).repeat_interleave(2, dim=-1) * 6.28
+        c, s = torch.cos(ang).to(dtype), torch.sin(ang).to(dtype)
+        got, want = run_body(rt, device, lambda b, *v: b.rotary_embedding_llama(*v), [x, c, s, t])
+        assert_matches(got[0], want[0], f"llama rotary prefill {heads}x{seq}x{d}", tol)
+        a, bb = x.float()[..., 0::2], x.float()[..., 1::2]
+        ref = torch.stack((a * c.float()[..., 0::2] - bb * s.float()[..., 0::2], bb * c.float()[..., 0::2] + a * s.float()[..., 0::2]),
+                          dim=-1).reshape(x.shape)
+        assert_matches(got[0], ref.to(dtype), "llama rotary against the pair rotation written out", tol)
+    xd = torch.randn(1, 32, 8, 128).to(dtype)                   # decode: [1, batch, heads, D], one position per batch entry
+    ang = torch.rand(1, 32, 1, 64).repeat_interleave(2, dim=-1) * 6.28
+    c, s = torch.cos(ang).to(dtype), torch.sin(ang).to(dtype)
+    got, want = run_body(rt, device, lambda b, *v: b.rotary_embedding_llama(*v, is_decode_mode=True), [xd, c, s, t])
+    assert_matches(got[0], want[0], "llama rotary decode", tol)
+    # a general (dense) transformation matrix
+    dense = (torch.randn(1, 1, 32, 32) * 0.2).to(dtype)
+    xg = torch.randn(1, 4, 32, 128).to(dtype)
+    cg, sg = torch.randn(1, 1, 32, 128).to(dtype), torch.randn(1, 1, 32, 128).to(dtype)
+    got, want = run_body(rt, device, lambda b, *v: b.rotary_embedding_llama(*v), [xg, cg, sg, dense])
+    assert_matches(got[0], want[0], "llama rotary with a dense matrix", tol)
+
+
+def test_max_pool2d_with_indices_matches_the_reference_goldens(rt, device, golden):
+    x = golden["map/max_pool_indices/x"]
+    flat = x.reshape(1, 1, -1, 6)
+    cases = {"k3_s2_p1": dict(kernel=(3, 3), stride=(2, 2), padding=(1, 1)),
+             "k2x3_s1x2_d2_ceil": dict(kernel=(2, 3), stride=(1, 2), padding=(0, 1), dilation=(2, 1), ceil_mode=True)}
+    for name, kw in cases.items():
+        got, want = run_body(rt, device, lambda b, v: b.max_pool2d_with_indices(v, 2, 9, 11, 6, **kw), [flat])
+        ref_v, ref_i = golden[f"map/max_pool_indices/{name}"], golden[f"map/max_pool_indices/{name}_idx"]
+        assert torch.equal(got[0].reshape(ref_v.shape), ref_v) and torch.equal(got[1].reshape(ref_i.shape), ref_i), name
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+    xb = torch.randn(1, 1, 4 * 28 * 28, 64, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+    for idt in ("Int32", "UInt16"):
+        got, want = run_body(rt, device, lambda b, v: b.max_pool2d_with_indices(v, 4, 28, 28, 64, kernel=(3, 3), stride=(2, 2), padding=(1, 1),
+                                                                                index_dtype=idt), [xb])
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1].to(torch.int64), want[1].to(torch.int64))
+
+
+def test_batch_norm_training_matches_the_reference_golden(rt, device, golden):
+    x, mean, var, w, b_ = (golden[f"map/batch_norm/{n}"] for n in ("x", "mean", "var", "weight", "bias"))
+
+    def body(b, xv, m, v, wv, bv):
+        y = b.batch_norm_training(xv, m, v, wv, bv, 1e-5, 0.1)
+        return y, b.assign(m), b.assign(v)                      # the running statistics after the in-place update
+    got, want = run_body(rt, device, body, [x, mean, var, w, b_])
+    for g, name in zip(got, ("out", "new_mean", "new_var")):
+        assert torch.allclose(g, golden[f"map/batch_norm_training/{name}"], rtol=1e-5, atol=2e-6), name
+    for g, w_ in zip(got, want):
+        assert torch.allclose(g, w_, rtol=1e-5, atol=2e-6)
+    bf = torch.bfloat16
+    big = torch.randn(8, 32, 14, 14, generator=torch.Generator().manual_seed(6))
+    ins = [big.to(bf), torch.zeros(32).to(bf), torch.ones(32).to(bf), (torch.rand(32) + 0.5).to(bf), torch.randn(32).to(bf)]
+    got, want = run_body(rt, device, body, ins)
+    assert_matches(got[0], want[0], "batch norm training bf16", (0.999, 2e-2, 2.0 ** -6))
+    assert_matches(got[1], want[1], "running mean bf16", (0.99, 2e-2, 2.0 ** -7))
+    assert_matches(got[2], want[2], "running var bf16", (0.99, 2e-2, 2.0 ** -7))
+
+
+def test_dropout_drops_the_asked_fraction_and_scales_the_rest(rt, device):
+    x = torch.rand(512, 1024) + 0.5
+    got = run_gpu(rt, device, lambda b, v: (b.dropout(v, 0.25, seed=7), b.dropout(v, 0.25, seed=7), b.dropout(v, 0.25, seed=8),
+                                            b.dropout(v, 0.0, seed=7), b.dropout(v, 1.0, scale=1.0, seed=7)), [x])
+    a, a2, other, none, everything = got
+    kept = a != 0
+    assert abs((~kept).float().mean().item() - 0.25) < 0.004          # 524288 draws: sigma = 6e-4
+    assert torch.allclose(a[kept], (x / 0.75)[kept], rtol=1e-6)
+    assert torch.equal(a, a2) and not torch.equal(a, other)           # a function of the seed
+    assert torch.equal(none, x) and int((everything != 0).sum()) == 0
+    # no structure along rows or columns
+    assert (kept.float().mean(dim=0) - 0.75).abs().max() < 0.1 and (kept.float().mean(dim=1) - 0.75).abs().max() < 0.07
+    xb = x.to(torch.bfloat16)
+    got = run_gpu(rt, device, lambda b, v: b.dropout(v, 0.5, seed=3), [xb])
+    assert abs((got[0] == 0).float().mean().item() - 0.5) < 0.004
+    assert torch.equal(got[0][got[0] != 0], (xb.float() * 2).to(torch.bfloat16)[got[0] != 0])
+
+
+def test_rand_is_uniform_in_its_interval(rt, device):
+    got = run_gpu(rt, device, lambda b: (b.rand([256, 1024], "Float32", -2.0, 3.0, seed=11), b.rand([256, 1024], "Float32", -2.0, 3.0, seed=11),
+                                        b.rand([256, 1024], "Float32", -2.0, 3.0, seed=12), b.rand([64, 512], "BFloat16", 0.0, 1.0, seed=1)), [])
+    a, a2, other, bf = got
+    assert a.min() >= -2.0 and a.max() < 3.0 and torch.equal(a, a2) and not torch.equal(a, other)
+    assert abs(a.mean().item() - 0.5) < 0.02 and abs(a.var().item() - 25.0 / 12.0) < 0.03
+    hist = torch.histc(a, bins=20, min=-2.0, max=3.0) / a.numel()
+    assert (hist - 0.05).abs().max() < 0.003
+    assert bf.dtype == torch.bfloat16 and bf.min() >= 0 and bf.max() < 1 and abs(bf.float().mean().item() - 0.5) < 0.02
+    assert len(torch.unique(bf)) > 200                                  # k / 256 for 256 values of k
+
+
+def test_prepared_conv_transpose_weights_run_like_the_raw_ones(rt, device, golden):
+    x, w, b_ = (golden[f"map/conv_transpose/{n}"] for n in ("x", "w", "b"))
+
+    def body(b, xv, wv, bv):
+        pw = b.prepare_conv_transpose2d_weights(wv, 2, 5, 6, stride=(2, 2), padding=(1, 1), output_padding=(1, 1))
+        pb = b.prepare_conv_transpose2d_bias(bv, 8, 2, 5, 6, kernel=(3, 3), stride=(2, 2), padding=(1, 1))
+        return b.conv_transpose2d(xv, pw, pb, 2, 5, 6, stride=(2, 2), padding=(1, 1), output_padding=(1, 1))
+    got, want = run_body(rt, device, body, [x, w, b_])
+    assert torch.allclose(got[0], golden["map/conv_transpose/s2_p1_op1"], rtol=1e-5, atol=1e-5) and torch.allclose(got[0], want[0], rtol=1e-5, atol=1e-5)

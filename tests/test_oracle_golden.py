@@ -277,6 +277,45 @@ def test_group_norm_conv_transpose_conv1d(golden):
     assert torch.equal(ops.conv1d(x, w, b, 2, (1, 2), 1, 1), golden["map/conv1d/s2_p1x2"])
 
 
+def test_batch_norm_training_and_max_pool_indices(golden):
+    """Restatements against the reference's goldens (tools/golden/mapping.py:4979-5063, 5339-5378)."""
+    x, mean, var, w, b = (golden[f"map/batch_norm/{n}"] for n in ("x", "mean", "var", "weight", "bias"))
+    y, m, v = ops.batch_norm_training(x, mean, var, w, b, 1e-5, 0.1)
+    assert torch.allclose(y, golden["map/batch_norm_training/out"], rtol=1e-6, atol=1e-6)
+    assert torch.allclose(m, golden["map/batch_norm_training/new_mean"], rtol=1e-6, atol=1e-7)
+    assert torch.allclose(v, golden["map/batch_norm_training/new_var"], rtol=1e-6, atol=1e-7)
+    x = golden["map/max_pool_indices/x"]
+    for name, args in {"k3_s2_p1": ((3, 3), (2, 2), (1, 1), (1, 1), False), "k2x3_s1x2_d2_ceil": ((2, 3), (1, 2), (0, 1), (2, 1), True)}.items():
+        val, idx = ops.max_pool2d_with_indices(x.reshape(1, 1, -1, 6), 2, 9, 11, 6, *args)
+        want = golden[f"map/max_pool_indices/{name}"]
+        assert torch.equal(val.reshape(want.shape), want)
+        assert torch.equal(idx.reshape(want.shape).to(torch.int32), golden[f"map/max_pool_indices/{name}_idx"])
+
+
+def test_decode_head_ops_and_llama_rotary():
+    """The decode-step head ops are pure data movement; the llama rotary embedding with the pair-swap matrix equals the
+    interleaved-pair rotation written out by hand."""
+    torch.manual_seed(0)
+    x = torch.randn(1, 1, 5, (4 + 2 * 2) * 8)
+    q, k, v = ops.nlp_create_qkv_heads_decode(x, 4, 2)
+    assert q.shape == (1, 5, 4, 8) and k.shape == (1, 5, 2, 8) and v.shape == (1, 5, 2, 8)
+    assert torch.equal(q[0, 3, 2], x[0, 0, 3, 16:24]) and torch.equal(k[0, 1, 1], x[0, 0, 1, 40:48]) and torch.equal(v[0, 4, 0], x[0, 0, 4, 48:56])
+    q2, _, _ = ops.nlp_create_qkv_heads_decode(x, 4, 2, batch_offset=2, slice_size=2)
+    assert torch.equal(q2, q[:, 2:4])
+    h = torch.randn(1, 5, 32, 8)
+    assert torch.equal(ops.nlp_concat_heads_decode(h, 3)[0, 0, 4], h[0, 4, :3].reshape(-1))
+    t = torch.zeros(32, 32)
+    for i in range(0, 32, 2):                                   # (a, b) -> (-b, a)
+        t[i, i + 1] = 1.0
+        t[i + 1, i] = -1.0
+    xs = torch.randn(1, 2, 6, 64)
+    ang = torch.rand(1, 1, 6, 32).repeat_interleave(2, dim=-1)
+    y = ops.rotary_embedding_llama(xs, torch.cos(ang), torch.sin(ang), t.reshape(1, 1, 32, 32), False)
+    a, b = xs[..., 0::2], xs[..., 1::2]
+    c, s_ = torch.cos(ang)[..., 0::2], torch.sin(ang)[..., 0::2]
+    assert torch.allclose(y[..., 0::2], a * c - b * s_, atol=1e-6) and torch.allclose(y[..., 1::2], b * c + a * s_, atol=1e-6)
+
+
 def test_layer_norm(golden):
     x, w, b = golden["ln/x"], golden["ln/w"], golden["ln/b"]
     assert same(ops.layer_norm(x), golden["ln/plain"])

@@ -25,6 +25,8 @@ struct NcclApi {
   decltype(&ncclAllGather) allGather = nullptr;
   decltype(&ncclReduceScatter) reduceScatter = nullptr;
   decltype(&ncclBroadcast) broadcast = nullptr;
+  decltype(&ncclSend) send = nullptr;
+  decltype(&ncclRecv) recv = nullptr;
   decltype(&ncclGroupStart) groupStart = nullptr;
   decltype(&ncclGroupEnd) groupEnd = nullptr;
   decltype(&ncclGetErrorString) getErrorString = nullptr;
@@ -61,6 +63,8 @@ static NcclApi &nccl() {
     TTB_SYM(allGather, ncclAllGather)
     TTB_SYM(reduceScatter, ncclReduceScatter)
     TTB_SYM(broadcast, ncclBroadcast)
+    TTB_SYM(send, ncclSend)
+    TTB_SYM(recv, ncclRecv)
     TTB_SYM(groupStart, ncclGroupStart)
     TTB_SYM(groupEnd, ncclGroupEnd)
     TTB_SYM(getErrorString, ncclGetErrorString)
@@ -459,6 +463,28 @@ int ttb_broadcast(void *comm, const void *in, void *out, size_t count, int dtype
   ncclDataType_t dt;
   if (!ncclType(dtype, dt)) { setLastError("broadcast: unsupported dtype"); return TTB_ERR_UNSUPPORTED; }
   TTB_NCCL(api.broadcast(in, out, count, dt, root, static_cast<ncclComm_t>(comm), asStream(stream)));
+  countLaunch();
+  return TTB_OK;
+}
+
+// One-directional copy between two ranks (point_to_point).  Sender and receiver call their half; when one process
+// drives both ranks the two calls sit inside one ttb_group_start / ttb_group_end pair.
+int ttb_send(void *comm, const void *in, size_t count, int dtype, int peer, void *stream) {
+  TTB_CHECK(comm && in, "null argument");
+  TTB_NCCL_READY();
+  ncclDataType_t dt;
+  if (!ncclType(dtype, dt)) { setLastError("send: unsupported dtype"); return TTB_ERR_UNSUPPORTED; }
+  TTB_NCCL(api.send(in, count, dt, peer, static_cast<ncclComm_t>(comm), asStream(stream)));
+  countLaunch();
+  return TTB_OK;
+}
+
+int ttb_recv(void *comm, void *out, size_t count, int dtype, int peer, void *stream) {
+  TTB_CHECK(comm && out, "null argument");
+  TTB_NCCL_READY();
+  ncclDataType_t dt;
+  if (!ncclType(dtype, dt)) { setLastError("recv: unsupported dtype"); return TTB_ERR_UNSUPPORTED; }
+  TTB_NCCL(api.recv(out, count, dt, peer, static_cast<ncclComm_t>(comm), asStream(stream)));
   countLaunch();
   return TTB_OK;
 }

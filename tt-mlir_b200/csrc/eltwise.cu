@@ -20,7 +20,8 @@ enum UnaryOp {
   uRelu6, uSilu, uHardsigmoid, uMish, uAcos, uAsin, uAsinh, uCount
 };
 // Composite unary ops handled by the same kernel (EltwiseUnaryCompositeOpType :177-182).
-enum { uCbrt = 200, uLog1p = 201 };
+// ... and EltwiseBinaryCompositeScalarOpType::PowScalar (:56-58): x to the power of the op's scalar parameter.
+enum { uCbrt = 200, uLog1p = 201, uPowScalar = 202 };
 
 // EltwiseBinaryOpType (:11-26) and, from 100 up, EltwiseBinaryCompositeOpType (:37-47).
 enum BinaryOp {
@@ -65,6 +66,7 @@ __device__ __forceinline__ float applyUnary(int op, float x, float p) {
   case uAsinh: return asinhf(x);
   case uCbrt: return cbrtf(x);
   case uLog1p: return log1pf(x);
+  case uPowScalar: return powf(x, p);
   default: return x;
   }
 }
@@ -411,7 +413,7 @@ extern "C" {
 int ttb_eltwise_unary(int op, const void *in, int in_dtype, void *out, int out_dtype, size_t n, float param,
                       void *stream) {
   TTB_CHECK(in && out, "null tensor");
-  TTB_CHECK((op >= 0 && op < uCount) || op == uCbrt || op == uLog1p, "unknown unary op");
+  TTB_CHECK((op >= 0 && op < uCount) || op == uCbrt || op == uLog1p || op == uPowScalar, "unknown unary op");
   if (n == 0) return TTB_OK;
   cudaStream_t st = asStream(stream);
   ProfScope prof("eltwise_unary", 0, double(n) * (dtypeSize(in_dtype) + dtypeSize(out_dtype)), st);

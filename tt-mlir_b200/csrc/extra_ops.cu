@@ -201,6 +201,159 @@ __global__ void __launch_bounds__(256) convTranspose2dKernel(const T *__restrict
   }
 }
 
+
+// Training-mode batch norm over the channel dimension of [N, C, inner] (::ttnn::batch_norm with training = true,
+// operations/normalization/batch_norm.cpp; golden tools/golden/mapping.py:4979-5063): the batch mean and the biased
+// batch variance of every channel normalise the input, and the running statistics move towards them in place:
+// running = momentum * batch + (1 - momentum) * running.  One block per channel, three passes over its N * inner
+// values (the second and third come from L2).
+template <typename T>
+__global__ void __launch_bounds__(256) batchNormTrainingKernel(const T *__restrict__ x, T *__restrict__ runMean, T *__restrict__ runVar,
+                                                               const T *__restrict__ weight, const T *__restrict__ bias, T *__restrict__ y,
+                                                               size_t outer, size_t channels, size_t inner, float eps, float momentum) {
+  __shared__ float scratch[33];
+  const size_t c = blockIdx.x, count = outer * inner;
+  auto at = [&](size_t i) { return ((i / inner) * channels + c) * inner + i % inner; };
+  float s = 0.0f;
+  for (size_t i = threadIdx.x; i < count; i += blockDim.x) s += toF32(x[at(i)]);
+  const float mean = extraBlockSum(s, scratch) / static_cast<float>(count);
+  float ss = 0.0f;
+  for (size_t i = threadIdx.x; i < count; i += blockDim.x) {
+    const float d = toF32(x[at(i)]) - mean;
+    ss += d * d;
+  }
+  const float var = extraBlockSum(ss, scratch) / static_cast<float>(count);
+  const float sd = sqrtf(var + eps);
+  const float w = weight ? toF32(weight[c]) : 1.0f, b = bias ? toF32(bias[c]) : 0.0f;
+  for (size_t i = threadIdx.x; i < count; i += blockDim.x) {
+    const size_t j = at(i);
+    y[j] = fromF32<T>((toF32(x[j]) - mean) / sd * w + b);
+  }
+  if (threadIdx.x == 0) {
+    runMean[c] = fromF32<T>(mean * momentum + toF32(runMean[c]) * (1.0f - momentum));
+    runVar[c] = fromF32<T>(var * momentum + toF32(runVar[c]) * (1.0f - momentum));
+  }
+}
+
+// max_pool2d that also returns where each maximum came from (::ttnn::max_pool2d with return_indices,
+// operations/pool/pool2d.cpp; golden tools/golden/mapping.py:5339-5378, torch max_pool2d(return_indices = True)):
+// the index is the position iy * W + ix inside the image's H x W plane, the first maximum wins, a NaN wins over
+// everything.  NHWC, one thread per output value.
+template <typename T, typename I>
+__global__ void __launch_bounds__(256) maxPoolIndicesKernel(const T *__restrict__ in, T *__restrict__ out, I *__restrict__ idx, int n, int h,
+                                                            int w, int c, int ho, int wo, int kh, int kw, int sh, int sw, int pt, int pl,
+                                                            int dh, int dw) {
+  const size_t total = static_cast<size_t>(n) * ho * wo * c;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int ch = static_cast<int>(i % c);
+    size_t p = i / c;
+    const int ox = static_cast<int>(p % wo);
+    p /= wo;
+    const int oy = static_cast<int>(p % ho);
+    const int img = static_cast<int>(p / ho);
+    float best = -INFINITY;
+    int where = -1;
+    for (int ky = 0; ky < kh; ++ky) {
+      const int iy = oy * sh - pt + ky * dh;
+      if (iy < 0 || iy >= h) continue;
+      for (int kx = 0; kx < kw; ++kx) {
+        const int ix = ox * sw - pl + kx * dw;
+        if (ix < 0 || ix >= w) continue;
+        const float f = toF32(in[((static_cast<size_t>(img) * h + iy) * w + ix) * c + ch]);
+        if (where < 0 || f > best || (f != f && best == best)) {
+          best = f;
+          where = iy * w + ix;
+        }
+      }
+    }
+    out[i] = fromF32<T>(best);
+    idx[i] = static_cast<I>(where < 0 ? 0 : where);
+  }
+}
+
+// rotary_embedding_llama (::ttnn::experimental::rotary_embedding_llama, operations/transformer/
+// rotary_embedding_llama.cpp): y = x * cos + (x @ T) * sin, where the 32 x 32 matrix T multiplies every 32-wide
+// piece of the head dimension on its own (Llama passes the matrix that maps pairs (a, b) to (-b, a)).  One block per
+// row; the row and T sit in shared memory; f32 throughout, one rounding.  `cosRows` says how rows of x map to rows
+// of the caches: prefill caches are [seq, D] and x rows cycle through them; decode caches are [batch, D] (or one row
+// per (batch, head)) and x rows [batch, heads] share their batch's row.
+template <typename T>
+__global__ void __launch_bounds__(256) rotaryLlamaKernel(const T *__restrict__ x, const T *__restrict__ cosT, const T *__restrict__ sinT,
+                                                         const T *__restrict__ trans, T *__restrict__ y, size_t rows, int d, size_t cosMod,
+                                                         size_t cosDiv) {
+  __shared__ float tm[32][33];
+  __shared__ float row[256];
+  for (int i = threadIdx.x; i < 1024; i += blockDim.x) tm[i >> 5][i & 31] = toF32(trans[i]);
+  for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    __syncthreads();
+    for (int j = threadIdx.x; j < d; j += blockDim.x) row[j] = toF32(x[r * d + j]);
+    __syncthreads();
+    const size_t cr = (r / cosDiv) % cosMod;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+      const int base = j & ~31, col = j & 31;
+      float rot = 0.0f;
+#pragma unroll 8
+      for (int i = 0; i < 32; ++i) rot = fmaf(row[base + i], tm[i][col], rot);
+      y[r * d + j] = fromF32<T>(row[j] * toF32(cosT[cr * d + j]) + rot * toF32(sinT[cr * d + j]));
+    }
+  }
+}
+
+// Philox-4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", 2011): a counter-based generator, so
+// element i's random bits depend only on (seed, i) and every launch geometry gives the same tensor.
+__device__ __forceinline__ uint4 philox4x32(uint4 ctr, uint2 key) {
+#pragma unroll
+  for (int round = 0; round < 10; ++round) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, ctr.x), lo0 = 0xD2511F53u * ctr.x;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, ctr.z), lo1 = 0xCD9E8D57u * ctr.z;
+    ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+    key.x += 0x9E3779B9u;
+    key.y += 0xBB67AE85u;
+  }
+  return ctr;
+}
+
+// dropout (::ttnn::experimental::dropout, operations/eltwise/unary/dropout.cpp; golden mapping.py:4365-4376,
+// torch.dropout in training mode): every element is zeroed with probability `prob`, the others are multiplied by
+// `scale`.  The stream is this generator's, not the Tensix one: which elements fall is a property of (seed, index).
+template <typename T>
+__global__ void __launch_bounds__(256) dropoutKernel(const T *__restrict__ x, T *__restrict__ y, size_t n, float prob, float scale, uint32_t seed,
+                                                     uint32_t stream) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t q = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; q * 4 < n; q += stride) {
+    const uint4 r = philox4x32(make_uint4(static_cast<uint32_t>(q), static_cast<uint32_t>(q >> 32), stream, 0), make_uint2(seed, 0x64726F70u));
+    const uint32_t bits[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const size_t i = q * 4 + j;
+      if (i >= n) break;
+      const float u = static_cast<float>(bits[j] >> 8) * (1.0f / 16777216.0f); // [0, 1)
+      y[i] = u < prob ? fromF32<T>(0.0f) : fromF32<T>(toF32(x[i]) * scale);
+    }
+  }
+}
+
+// rand (::ttnn::rand, operations/rand/rand.cpp; golden mapping.py:4340-4362): uniform in [low, high).  As the golden
+// draws its base values in bf16, 16-bit results take u = k / 2^m with m the type's significand width (8 for bf16, 11
+// for f16), so that u * (high - low) + low stays below `high`; f32 takes 24 bits.
+template <typename T>
+__global__ void __launch_bounds__(256) randKernel(T *__restrict__ y, size_t n, float low, float high, uint32_t seed, uint32_t stream, int bitsUsed) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  const float unit = 1.0f / static_cast<float>(1u << bitsUsed);
+  for (size_t q = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; q * 4 < n; q += stride) {
+    const uint4 r = philox4x32(make_uint4(static_cast<uint32_t>(q), static_cast<uint32_t>(q >> 32), stream, 0), make_uint2(seed, 0x72616E64u));
+    const uint32_t bits[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const size_t i = q * 4 + j;
+      if (i >= n) break;
+      const float u = static_cast<float>(bits[j] >> (32 - bitsUsed)) * unit;
+      y[i] = fromF32<T>(u * (high - low) + low);
+    }
+  }
+}
+
 } // namespace ttb
 
 using namespace ttb;
@@ -347,6 +500,95 @@ int ttb_conv_transpose2d(const void *x, const void *weight, const void *bias, vo
   default: setLastError("conv_transpose2d: unsupported dtype"); return TTB_ERR_UNSUPPORTED;
   }
 #undef TTB_CT
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_batch_norm_training(const void *x, void *running_mean, void *running_var, const void *weight, const void *bias, void *y,
+                            int dtype, size_t outer, size_t channels, size_t inner, float eps, float momentum, void *stream) {
+  TTB_CHECK(x && running_mean && running_var && y, "null tensor");
+  if (outer * channels * inner == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("batch_norm_training", 0, double(outer) * channels * inner * 2 * dtypeSize(dtype), st);
+  TTB_DISPATCH_FLOAT(dtype, T,
+                     (batchNormTrainingKernel<T><<<static_cast<unsigned>(channels), 256, 0, st>>>(
+                         static_cast<const T *>(x), static_cast<T *>(running_mean), static_cast<T *>(running_var),
+                         static_cast<const T *>(weight), static_cast<const T *>(bias), static_cast<T *>(y), outer, channels, inner, eps,
+                         momentum)));
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_max_pool2d_with_indices(const void *in, void *out, void *indices, int dtype, int index_dtype, int n, int h, int w, int c,
+                                int ho, int wo, int kh, int kw, int sh, int sw, int pt, int pl, int dh, int dw, void *stream) {
+  TTB_CHECK(in && out && indices, "null tensor");
+  TTB_CHECK(kh > 0 && kw > 0 && sh > 0 && sw > 0 && dh > 0 && dw > 0 && pt >= 0 && pl >= 0, "bad pooling window");
+  TTB_CHECK(index_dtype != kU16 || static_cast<long long>(h) * w <= 65536, "image too large for 16-bit indices");
+  const size_t total = static_cast<size_t>(n) * ho * wo * c;
+  if (total == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("max_pool2d_with_indices", 0, double(total) * (dtypeSize(dtype) + dtypeSize(index_dtype)) + double(n) * h * w * c * dtypeSize(dtype), st);
+  const int grid = gridFor(total, 256);
+#define TTB_POOL_IDX(I)                                                                                                     \
+  TTB_DISPATCH_FLOAT(dtype, T,                                                                                              \
+                     (maxPoolIndicesKernel<T, I><<<grid, 256, 0, st>>>(static_cast<const T *>(in), static_cast<T *>(out),   \
+                                                                       static_cast<I *>(indices), n, h, w, c, ho, wo, kh, kw, sh, sw, pt, \
+                                                                       pl, dh, dw)))
+  switch (index_dtype) {
+  case kI32: TTB_POOL_IDX(int32_t); break;
+  case kU32: TTB_POOL_IDX(uint32_t); break;
+  case kU16: TTB_POOL_IDX(uint16_t); break;
+  default: setLastError("max_pool2d_with_indices: indices must be Int32, UInt32 or UInt16"); return TTB_ERR_UNSUPPORTED;
+  }
+#undef TTB_POOL_IDX
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_rotary_embedding_llama(const void *x, const void *cos_cache, const void *sin_cache, const void *trans_mat, void *y, int dtype,
+                               size_t rows, size_t head_dim, size_t cos_mod, size_t cos_div, void *stream) {
+  TTB_CHECK(x && cos_cache && sin_cache && trans_mat && y, "null tensor");
+  TTB_CHECK(head_dim > 0 && head_dim <= 256 && head_dim % 32 == 0, "head dimension must be a multiple of 32, at most 256");
+  TTB_CHECK(cos_mod > 0 && cos_div > 0, "bad cache row mapping");
+  if (rows == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("rotary_embedding_llama", 0, double(rows) * head_dim * 2 * dtypeSize(dtype), st);
+  const int grid = static_cast<int>(rows < static_cast<size_t>(smCount()) * 8 ? rows : static_cast<size_t>(smCount()) * 8);
+  TTB_DISPATCH_FLOAT(dtype, T,
+                     (rotaryLlamaKernel<T><<<grid, static_cast<unsigned>(head_dim < 64 ? 64 : head_dim), 0, st>>>(
+                         static_cast<const T *>(x), static_cast<const T *>(cos_cache), static_cast<const T *>(sin_cache),
+                         static_cast<const T *>(trans_mat), static_cast<T *>(y), rows, static_cast<int>(head_dim), cos_mod, cos_div)));
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_dropout(const void *x, void *y, int dtype, size_t n, float prob, float scale, uint32_t seed, uint32_t stream_id, void *stream) {
+  TTB_CHECK(x && y, "null tensor");
+  TTB_CHECK(prob >= 0.0f && prob <= 1.0f, "dropout probability outside [0, 1]");
+  if (n == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("dropout", 0, double(n) * 2 * dtypeSize(dtype), st);
+  TTB_DISPATCH_FLOAT(dtype, T,
+                     (dropoutKernel<T><<<gridFor((n + 3) / 4, 256), 256, 0, st>>>(static_cast<const T *>(x), static_cast<T *>(y), n, prob, scale,
+                                                                                 seed, stream_id)));
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_rand_uniform(void *y, int dtype, size_t n, float low, float high, uint32_t seed, uint32_t stream_id, void *stream) {
+  TTB_CHECK(y, "null tensor");
+  TTB_CHECK(low <= high, "rand: low above high");
+  if (n == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("rand", 0, double(n) * dtypeSize(dtype), st);
+  const int bitsUsed = dtype == kF32 ? 24 : (dtype == kBF16 ? 8 : 11);
+  TTB_DISPATCH_FLOAT(dtype, T,
+                     (randKernel<T><<<gridFor((n + 3) / 4, 256), 256, 0, st>>>(static_cast<T *>(y), n, low, high, seed, stream_id, bitsUsed)));
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;

@@ -13,7 +13,9 @@
 //     Fusion is off while debug hooks are registered, because callbacks may ask for any
 //     intermediate tensor;
 //   * tilize / untilize and memory-config changes are metadata only.
+#include <cstdio>
 #include <cstdlib>
+#include <fstream>
 #include <algorithm>
 #include <atomic>
 #include <cmath>
@@ -111,6 +113,114 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     IN1_OUT(GlobalAvgPool2dOp, in)
     IN1_OUT(PadOp, in)
 #undef IN1_OUT
+  case OpType::AssignOp: {
+    const auto *o = op->type_as_AssignOp();
+    pushRef(ins, o->input());
+    pushRef(outs, o->output());
+    break;
+  }
+  case OpType::EltwiseBinaryCompositeScalarOp: {
+    const auto *o = op->type_as_EltwiseBinaryCompositeScalarOp();
+    pushRef(ins, o->lhs());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::DumpTensorOp: pushRef(ins, op->type_as_DumpTensorOp()->in()); break;
+  case OpType::LoadTensorOp: pushRef(outs, op->type_as_LoadTensorOp()->out()); break;
+  case OpType::AnnotateOp: {
+    const auto *o = op->type_as_AnnotateOp();
+    pushRef(ins, o->operand());
+    pushRef(outs, o->result());
+    break;
+  }
+  case OpType::RegionStartOp: {
+    const auto *o = op->type_as_RegionStartOp();
+    pushRef(ins, o->operand());
+    pushRef(outs, o->result());
+    break;
+  }
+  case OpType::RegionEndOp: {
+    const auto *o = op->type_as_RegionEndOp();
+    pushRef(ins, o->operand());
+    pushRef(outs, o->result());
+    break;
+  }
+  case OpType::BreakpointOp: pushRef(ins, op->type_as_BreakpointOp()->operand()); break;
+  case OpType::PrintOp: pushRef(ins, op->type_as_PrintOp()->operand()); break;
+  case OpType::MemorySnapshotOp: pushRef(ins, op->type_as_MemorySnapshotOp()->operand()); break;
+  case OpType::AllReduceAsyncOp: {
+    const auto *o = op->type_as_AllReduceAsyncOp();
+    pushRef(ins, o->in());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::PointToPointOp: {
+    const auto *o = op->type_as_PointToPointOp();
+    pushRef(ins, o->in());
+    pushRef(ins, o->optional_output_tensor());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::PrepareConvTranspose2dWeightsOp: {
+    const auto *o = op->type_as_PrepareConvTranspose2dWeightsOp();
+    pushRef(ins, o->weight_tensor());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::PrepareConvTranspose2dBiasOp: {
+    const auto *o = op->type_as_PrepareConvTranspose2dBiasOp();
+    pushRef(ins, o->bias_tensor());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::NLPCreateQKVHeadsDecodeOp: {
+    const auto *o = op->type_as_NLPCreateQKVHeadsDecodeOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->batch_offset());
+    pushRef(outs, o->q_out());
+    pushRef(outs, o->k_out());
+    pushRef(outs, o->v_out());
+    break;
+  }
+  case OpType::NLPConcatHeadsDecodeOp: {
+    const auto *o = op->type_as_NLPConcatHeadsDecodeOp();
+    pushRef(ins, o->in());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::RotaryEmbeddingLlamaOp: {
+    const auto *o = op->type_as_RotaryEmbeddingLlamaOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->cos_cache());
+    pushRef(ins, o->sin_cache());
+    pushRef(ins, o->trans_mat());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::MaxPool2dWithIndicesOp: {
+    const auto *o = op->type_as_MaxPool2dWithIndicesOp();
+    pushRef(ins, o->in());
+    pushRef(outs, o->result());
+    pushRef(outs, o->result_indices());
+    break;
+  }
+  case OpType::DropoutOp: {
+    const auto *o = op->type_as_DropoutOp();
+    pushRef(ins, o->in());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::RandOp: pushRef(outs, op->type_as_RandOp()->out()); break;
+  case OpType::BatchNormTrainingOp: {
+    const auto *o = op->type_as_BatchNormTrainingOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->running_mean());
+    pushRef(ins, o->running_var());
+    pushRef(ins, o->weight());
+    pushRef(ins, o->bias());
+    pushRef(outs, o->out());
+    break;
+  }
   case OpType::GroupNormOp: {
     const auto *o = op->type_as_GroupNormOp();
     pushRef(ins, o->input());
@@ -601,6 +711,21 @@ private:
   void runArgMax(const fbt::ReductionArgMaxOp *op);
   void runCumSum(const fbt::CumSumOp *op);
   void runCumProd(const fbt::CumProdOp *op);
+  void runAssign(const fbt::AssignOp *op);
+  void runPowScalar(const fbt::EltwiseBinaryCompositeScalarOp *op);
+  void runDumpTensor(const fbt::DumpTensorOp *op);
+  void runLoadTensor(const fbt::LoadTensorOp *op);
+  void runAlias(const fbt::TensorRef *operand, const fbt::TensorRef *result);
+  void runMemorySnapshot(const fbt::MemorySnapshotOp *op);
+  void runAllReduceAsync(const fbt::AllReduceAsyncOp *op);
+  void runPointToPoint(const fbt::PointToPointOp *op);
+  void runNlpCreateQkvHeadsDecode(const fbt::NLPCreateQKVHeadsDecodeOp *op);
+  void runNlpConcatHeadsDecode(const fbt::NLPConcatHeadsDecodeOp *op);
+  void runRotaryEmbeddingLlama(const fbt::RotaryEmbeddingLlamaOp *op);
+  void runMaxPool2dWithIndices(const fbt::MaxPool2dWithIndicesOp *op);
+  void runDropout(const fbt::DropoutOp *op);
+  void runRand(const fbt::RandOp *op);
+  void runBatchNormTraining(const fbt::BatchNormTrainingOp *op);
   void runGroupNorm(const fbt::GroupNormOp *op);
   void runConvTranspose2d(const fbt::ConvTranspose2dOp *op);
   void runConv1d(const fbt::Conv1dOp *op);
@@ -953,6 +1078,43 @@ size_t Executor::runOp(size_t i) {
   case OpType::ReductionArgMaxOp: runArgMax(op->type_as_ReductionArgMaxOp()); break;
   case OpType::CumSumOp: runCumSum(op->type_as_CumSumOp()); break;
   case OpType::CumProdOp: runCumProd(op->type_as_CumProdOp()); break;
+  case OpType::AssignOp: runAssign(op->type_as_AssignOp()); break;
+  case OpType::EltwiseBinaryCompositeScalarOp: runPowScalar(op->type_as_EltwiseBinaryCompositeScalarOp()); break;
+  case OpType::DumpTensorOp: runDumpTensor(op->type_as_DumpTensorOp()); break;
+  case OpType::LoadTensorOp: runLoadTensor(op->type_as_LoadTensorOp()); break;
+  // Annotations and region markers hand their operand on (operations/debug/debug.cpp:18-24, 56-68).
+  case OpType::AnnotateOp: runAlias(op->type_as_AnnotateOp()->operand(), op->type_as_AnnotateOp()->result()); break;
+  case OpType::RegionStartOp: runAlias(op->type_as_RegionStartOp()->operand(), op->type_as_RegionStartOp()->result()); break;
+  case OpType::RegionEndOp: runAlias(op->type_as_RegionEndOp()->operand(), op->type_as_RegionEndOp()->result()); break;
+  case OpType::BreakpointOp:
+    // The reference drops into Python's pdb (debug.cpp:16,26-28); this runtime embeds no interpreter.
+    std::fprintf(stderr, "[ttb200] breakpoint op reached (no debugger is attached by this runtime)\n");
+    break;
+  case OpType::PrintOp: {
+    const auto *o = op->type_as_PrintOp();
+    std::fprintf(stderr, "%s\n", o->message() ? o->message()->c_str() : "");
+    break;
+  }
+  case OpType::MemorySnapshotOp: runMemorySnapshot(op->type_as_MemorySnapshotOp()); break;
+  case OpType::AllReduceAsyncOp: runAllReduceAsync(op->type_as_AllReduceAsyncOp()); break;
+  case OpType::PointToPointOp: runPointToPoint(op->type_as_PointToPointOp()); break;
+  case OpType::PrepareConvTranspose2dWeightsOp: {
+    const auto *o = op->type_as_PrepareConvTranspose2dWeightsOp();
+    runPrepareConv2d(o->weight_tensor(), o->out());
+    break;
+  }
+  case OpType::PrepareConvTranspose2dBiasOp: {
+    const auto *o = op->type_as_PrepareConvTranspose2dBiasOp();
+    runPrepareConv2d(o->bias_tensor(), o->out());
+    break;
+  }
+  case OpType::NLPCreateQKVHeadsDecodeOp: runNlpCreateQkvHeadsDecode(op->type_as_NLPCreateQKVHeadsDecodeOp()); break;
+  case OpType::NLPConcatHeadsDecodeOp: runNlpConcatHeadsDecode(op->type_as_NLPConcatHeadsDecodeOp()); break;
+  case OpType::RotaryEmbeddingLlamaOp: runRotaryEmbeddingLlama(op->type_as_RotaryEmbeddingLlamaOp()); break;
+  case OpType::MaxPool2dWithIndicesOp: runMaxPool2dWithIndices(op->type_as_MaxPool2dWithIndicesOp()); break;
+  case OpType::DropoutOp: runDropout(op->type_as_DropoutOp()); break;
+  case OpType::RandOp: runRand(op->type_as_RandOp()); break;
+  case OpType::BatchNormTrainingOp: runBatchNormTraining(op->type_as_BatchNormTrainingOp()); break;
   case OpType::GroupNormOp: runGroupNorm(op->type_as_GroupNormOp()); break;
   case OpType::ConvTranspose2dOp: runConvTranspose2d(op->type_as_ConvTranspose2dOp()); break;
   case OpType::Conv1dOp: runConv1d(op->type_as_Conv1dOp()); break;
@@ -2473,6 +2635,333 @@ void Executor::runReductionProd(const fbt::ReductionProdOp *op) {
 }
 
 // group_norm on channels-last [N, 1, H*W, C] (or [N, H, W, C]): operations/normalization/group_norm.cpp.
+// A second name for the same memory (annotate, region markers).
+void Executor::runAlias(const fbt::TensorRef *operand, const fbt::TensorRef *result) {
+  TensorPtr in = get(operand);
+  auto alias = std::make_shared<TensorImpl>();
+  alias->shape = in->shape;
+  alias->stride = in->stride;
+  alias->dtype = in->dtype;
+  alias->storage = in->storage;
+  alias->layout = in->layout;
+  alias->shards = in->shards;
+  alias->device = in->device;
+  alias->preparedFrom = in->preparedFrom;
+  put(result, alias);
+}
+
+// assign: a copy of the input, in the result's data type when one is given (operations/data_movement/assign.cpp).
+void Executor::runAssign(const fbt::AssignOp *op) {
+  TensorPtr in = getDevice(op->input());
+  DataType dt = op->output_dtype().value_or(in->dtype);
+  TensorPtr out = dt != in->dtype ? castOnDevice(in, dt) : stridedView(in, in->shape, denseStrides(in->shape), 0, in->dtype);
+  TTRT_ASSERT(out->volume() == prod(refShape(op->output()), 0, refShape(op->output()).size()), "assign changes the element count");
+  put(op->output(), out);
+}
+
+// pow(x, scalar) (operations/eltwise/binary/binary_composite_scalar.cpp; golden tools/golden/mapping.py:10447-10450).
+void Executor::runPowScalar(const fbt::EltwiseBinaryCompositeScalarOp *op) {
+  TTRT_ASSERT(op->type() == fbt::EltwiseBinaryCompositeScalarOpType::PowScalar, "unknown scalar composite op");
+  TensorPtr in = getDevice(op->lhs());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(out->volume() == in->volume(), "pow_scalar changes the element count");
+  TTRT_ASSERT(in->dtype == DataType::Float32 || in->dtype == DataType::BFloat16 || in->dtype == DataType::Float16,
+              "pow_scalar takes floating-point tensors");
+  const float e = numberValue(op->rhs_type(), op->rhs());
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_eltwise_unary(202, in->shards[i]->ptr, ttbDtype(in->dtype), out->shards[i]->ptr, ttbDtype(out->dtype), out->volume(), e,
+                               r.stream));
+  });
+  put(op->out(), out);
+}
+
+// dump_tensor / load_tensor (operations/tensor_serialization/{dump,load}_tensor.cpp).  The reference writes tt-metal's
+// tensor flatbuffer, a format of its own library; a file written here is read back here.  Layout: "TTB200T1", data type
+// (u32), rank (u32), dimensions (u32 each), shard count (u32), then per shard its index (u32), byte count (u64), bytes.
+static const char kTensorFileMagic[8] = {'T', 'T', 'B', '2', '0', '0', 'T', '1'};
+
+void Executor::runDumpTensor(const fbt::DumpTensorOp *op) {
+  refuseWhileRecording("dump_tensor");
+  TensorPtr t = get(op->in());
+  TensorPtr h = t->storage == Storage::Device ? toHostTensor(t, true) : t;
+  TTRT_ASSERT(op->file_path() != nullptr, "dump_tensor without a file path");
+  const std::string path = op->file_path()->str();
+  std::ofstream f(path, std::ios::binary | std::ios::trunc);
+  TTRT_ASSERT(f.is_open(), "dump_tensor cannot open ", path);
+  auto u32 = [&](uint32_t v) { f.write(reinterpret_cast<const char *>(&v), 4); };
+  f.write(kTensorFileMagic, 8);
+  u32(static_cast<uint32_t>(h->dtype));
+  u32(static_cast<uint32_t>(h->shape.size()));
+  for (uint32_t d : h->shape) u32(d);
+  u32(static_cast<uint32_t>(h->shards.size()));
+  for (size_t i = 0; i < h->shards.size(); ++i) {
+    const BufferPtr &b = h->shards[i];
+    const uint64_t n = b && b->ptr ? h->bytes() : 0;
+    u32(static_cast<uint32_t>(i));
+    f.write(reinterpret_cast<const char *>(&n), 8);
+    if (n) f.write(static_cast<const char *>(b->ptr), static_cast<std::streamsize>(n));
+  }
+  TTRT_ASSERT(f.good(), "dump_tensor failed writing ", path);
+}
+
+void Executor::runLoadTensor(const fbt::LoadTensorOp *op) {
+  refuseWhileRecording("load_tensor");
+  TTRT_ASSERT(op->file_path() != nullptr, "load_tensor without a file path");
+  const std::string path = op->file_path()->str();
+  std::ifstream f(path, std::ios::binary);
+  TTRT_ASSERT(f.is_open(), "load_tensor cannot open ", path);
+  char magic[8];
+  f.read(magic, 8);
+  TTRT_ASSERT(f.good() && std::memcmp(magic, kTensorFileMagic, 8) == 0, path, " is not a tensor file of this runtime");
+  auto u32 = [&]() {
+    uint32_t v = 0;
+    f.read(reinterpret_cast<char *>(&v), 4);
+    return v;
+  };
+  const DataType dt = static_cast<DataType>(u32());
+  const uint32_t rank = u32();
+  TTRT_ASSERT(f.good() && rank <= 8 && isSupportedDataType(dt), path, ": bad tensor header");
+  std::vector<uint32_t> shape(rank);
+  for (uint32_t &d : shape) d = u32();
+  const uint32_t nshards = u32();
+  TTRT_ASSERT(f.good() && nshards >= 1 && nshards <= 64, path, ": bad shard count");
+  TensorPtr h = makeHostTensor(shape, dt, nshards);
+  for (uint32_t k = 0; k < nshards; ++k) {
+    const uint32_t idx = u32();
+    uint64_t n = 0;
+    f.read(reinterpret_cast<char *>(&n), 8);
+    TTRT_ASSERT(f.good() && idx < nshards && (n == 0 || n == h->bytes()), path, ": bad shard record");
+    if (n) f.read(static_cast<char *>(h->shards[idx]->ptr), static_cast<std::streamsize>(n));
+    TTRT_ASSERT(f.good(), path, " is truncated");
+  }
+  TTRT_ASSERT(shape == refShape(op->out()) && dt == refDtype(op->out()), "the tensor in ", path, " does not have the op's result type");
+  h->layout = refLayout(op->out());
+  put(op->out(), op->device() && refOnDevice(op->out()) ? toDevice(h, dev, dt) : h);
+}
+
+// memory_snapshot (operations/debug/debug.cpp:34-54) writes the allocator's state per buffer type to a file.  There is
+// one kind of device memory here: the figures are those of each local GPU's default memory pool and of the device.
+void Executor::runMemorySnapshot(const fbt::MemorySnapshotOp *op) {
+  TTRT_ASSERT(op->file_path() != nullptr, "memory_snapshot without a file path");
+  const std::string path = op->file_path()->str();
+  std::ofstream f(path, std::ios::out | std::ios::trunc);
+  if (!f.is_open()) TTRT_FATAL("Failed to open file: ", path);
+  eachRank([&](size_t, const RankCtx &r) {
+    uint64_t reserved = 0, used = 0, high = 0;
+    TTB_CALL(ttb_mempool_stats(&reserved, &used, &high, 0));
+    int sms = 0, major = 0, minor = 0;
+    size_t total = 0;
+    TTB_CALL(ttb_device_info(r.cudaDevice, &sms, &total, &major, &minor));
+    f << "Device " << r.meshRank << " DRAM memory state: totalBytes=" << total << " poolReservedBytes=" << reserved
+      << " allocatedBytes=" << used << " peakAllocatedBytes=" << high << "\n";
+  });
+}
+
+void Executor::runAllReduceAsync(const fbt::AllReduceAsyncOp *op) {
+  TensorPtr in = getDevice(op->in());
+  if (meshAxisSize(op->cluster_axis()) == 1) {
+    put(op->out(), in);
+    return;
+  }
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(out->volume() == in->volume() && out->dtype == in->dtype, "all_reduce_async changes shape or type");
+  allReduce(in, nullptr, out, static_cast<int>(op->reduce_type()));
+  put(op->out(), out);
+}
+
+// point_to_point (operations/ccl/point_to_point.cpp): the result is the optional output tensor (or a copy of the input)
+// on every coordinate, except that the receiver's shard is the sender's shard of the input.
+void Executor::runPointToPoint(const fbt::PointToPointOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr base = op->optional_output_tensor() ? getDevice(op->optional_output_tensor()) : in;
+  TTRT_ASSERT(base->dtype == in->dtype && base->volume() == in->volume(), "point_to_point output tensor differs from the input's type");
+  auto linear = [&](const fb::Vector<uint32_t> *c, const char *what) {
+    TTRT_ASSERT(c && c->size() == 2, "point_to_point ", what, " must be a 2-D mesh coordinate");
+    TTRT_ASSERT(c->Get(0) < dev->meshShape[0] && c->Get(1) < dev->meshShape[1], "point_to_point ", what, " lies outside the mesh");
+    return c->Get(0) * dev->meshShape[1] + c->Get(1);
+  };
+  const uint32_t sender = linear(op->sender_coord(), "sender_coord"), receiver = linear(op->receiver_coord(), "receiver_coord");
+  TensorPtr out = stridedView(base, in->shape, denseStrides(in->shape), 0, in->dtype);
+  if (sender != receiver) {
+    refuseWhileRecording("a collective");
+    TTB_CALL(ttb_group_start());
+    eachRank([&](size_t i, const RankCtx &r) {
+      if (r.meshRank == sender) {
+        TTB_CALL(ttb_send(r.comm, in->shards[i]->ptr, in->volume(), ttbDtype(in->dtype), static_cast<int>(receiver), r.stream));
+      }
+      if (r.meshRank == receiver) {
+        TTB_CALL(ttb_recv(r.comm, out->shards[i]->ptr, in->volume(), ttbDtype(in->dtype), static_cast<int>(sender), r.stream));
+      }
+    });
+    TTB_CALL(ttb_group_end());
+  } else {
+    eachRank([&](size_t i, const RankCtx &r) {
+      if (r.meshRank == receiver && base != in) {
+        TTB_CALL(ttb_memcpy_d2d(out->shards[i]->ptr, in->shards[i]->ptr, in->bytes(), r.stream));
+      }
+    });
+  }
+  put(op->out(), out);
+}
+
+// nlp_create_qkv_heads_decode (operations/transformer/nlp_create_qkv_heads_decode.cpp): the fused projection of one
+// decode step, [1, 1, batch, (Hq + 2 Hkv) * D], split into q [1, batch, Hq, D], k and v [1, batch, Hkv, D].  With
+// `slice_size`, only the batch rows [batch_offset, batch_offset + slice_size) are taken.
+void Executor::runNlpCreateQkvHeadsDecode(const fbt::NLPCreateQKVHeadsDecodeOp *op) {
+  TensorPtr in = getDevice(op->input());
+  TTRT_ASSERT(in->shape.size() == 4 && in->shape[0] == 1 && in->shape[1] == 1, "nlp_create_qkv_heads_decode expects [1, 1, batch, hidden]");
+  const uint32_t B = in->shape[2], hidden = in->shape[3];
+  const uint32_t Hq = op->num_heads(), Hkv = op->num_kv_heads().value_or(Hq);
+  TTRT_ASSERT(Hq > 0 && Hkv > 0 && hidden % (Hq + 2 * Hkv) == 0, "hidden size ", hidden, " does not split into ", Hq, " + 2 x ", Hkv, " heads");
+  const uint32_t D = hidden / (Hq + 2 * Hkv);
+  uint32_t first = 0, count = B;
+  if (op->slice_size().has_value()) {
+    TTRT_ASSERT(op->batch_offset() != nullptr, "slice_size needs a batch_offset tensor");
+    refuseWhileRecording("reading batch_offset");
+    TensorPtr off = get(op->batch_offset());
+    TTRT_ASSERT(off->volume() >= 1 && dataTypeSize(off->dtype) == 4, "batch_offset must hold one 32-bit integer");
+    if (off->storage == Storage::Device) off = toHostTensor(off, true);
+    first = *static_cast<const uint32_t *>(off->shards[0]->ptr);
+    count = *op->slice_size();
+    TTRT_ASSERT(static_cast<uint64_t>(first) + count <= B, "batch slice [", first, ", ", first + count, ") exceeds the batch of ", B);
+  }
+  auto heads = [&](uint32_t colOff, uint32_t H) {
+    return stridedView(in, {1, count, H, D}, {0, static_cast<int64_t>(hidden), static_cast<int64_t>(D), 1},
+                       static_cast<int64_t>(first) * hidden + colOff, in->dtype);
+  };
+  TensorPtr q = heads(0, Hq), k = heads(Hq * D, Hkv), v = heads((Hq + Hkv) * D, Hkv);
+  TTRT_ASSERT(q->shape == refShape(op->q_out()) && k->shape == refShape(op->k_out()) && v->shape == refShape(op->v_out()),
+              "nlp_create_qkv_heads_decode result shapes differ from the op's result types");
+  put(op->q_out(), q);
+  put(op->k_out(), k);
+  put(op->v_out(), v);
+}
+
+// nlp_concat_heads_decode (operations/transformer/nlp_concat_heads_decode.cpp): [1, batch, padded heads, D] ->
+// [1, 1, batch, num_heads * D], dropping the heads beyond `num_heads`.
+void Executor::runNlpConcatHeadsDecode(const fbt::NLPConcatHeadsDecodeOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TTRT_ASSERT(in->shape.size() == 4 && in->shape[0] == 1, "nlp_concat_heads_decode expects [1, batch, heads, head_dim]");
+  const uint32_t B = in->shape[1], Hp = in->shape[2], D = in->shape[3], H = op->num_heads();
+  TTRT_ASSERT(H >= 1 && H <= Hp, "num_heads ", H, " exceeds the input's ", Hp, " heads");
+  TensorPtr t = stridedView(in, {B, H, D}, {static_cast<int64_t>(Hp) * D, static_cast<int64_t>(D), 1}, 0, in->dtype);
+  t->shape = {1, 1, B, H * D};
+  t->stride = denseStrides(t->shape);
+  TTRT_ASSERT(t->shape == refShape(op->out()), "nlp_concat_heads_decode result shape differs from the op's result type");
+  put(op->out(), t);
+}
+
+// rotary_embedding_llama (operations/transformer/rotary_embedding_llama.cpp).  Prefill: x [1, heads, seq, D] with caches
+// [1, 1, seq, D].  Decode: x [1, batch, heads, D] with caches [1, batch, 1 or heads, D].
+void Executor::runRotaryEmbeddingLlama(const fbt::RotaryEmbeddingLlamaOp *op) {
+  TensorPtr x = getDevice(op->input()), c = getDevice(op->cos_cache()), s = getDevice(op->sin_cache()), t = getDevice(op->trans_mat());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(x->shape.size() >= 2 && c->shape == s->shape, "rotary_embedding_llama: cos and sin caches must have the same shape");
+  const size_t rank = x->shape.size(), D = x->shape[rank - 1], inner = x->shape[rank - 2];
+  const size_t rows = x->volume() / std::max<size_t>(D, 1);
+  TTRT_ASSERT(t->volume() >= 1024 && t->shape.back() == 32, "the transformation matrix must be [1, 1, 32, 32]");
+  TTRT_ASSERT(c->shape.back() == D && c->volume() % D == 0, "cache rows must have the head dimension ", D);
+  TTRT_ASSERT(x->dtype == c->dtype && x->dtype == s->dtype && x->dtype == t->dtype && x->dtype == out->dtype && out->volume() == x->volume(),
+              "rotary_embedding_llama tensors must share one data type");
+  const size_t cacheRows = c->volume() / D;
+  size_t mod = cacheRows, div = 1;
+  if (op->is_decode_mode()) {
+    // rows are (batch, head): one cache row per batch entry, or one per (batch, head)
+    TTRT_ASSERT(cacheRows * inner == rows || cacheRows == rows, "decode caches must be [1, batch, 1, D] for x [1, batch, heads, D]");
+    div = cacheRows == rows ? 1 : inner;
+  } else {
+    TTRT_ASSERT(cacheRows >= inner, "prefill caches hold ", cacheRows, " positions, the input has ", inner);
+    mod = inner; // rows are (..., seq): position = row % seq
+  }
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_rotary_embedding_llama(x->shards[i]->ptr, c->shards[i]->ptr, s->shards[i]->ptr, t->shards[i]->ptr, out->shards[i]->ptr,
+                                        ttbDtype(x->dtype), rows, D, mod, div, r.stream));
+  });
+  put(op->out(), out);
+}
+
+void Executor::runMaxPool2dWithIndices(const fbt::MaxPool2dWithIndicesOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = allocOut(op->result()), idx = allocOut(op->result_indices());
+  const int n = static_cast<int>(op->batch_size()), h = static_cast<int>(op->input_height()), w = static_cast<int>(op->input_width()),
+            c = static_cast<int>(op->channels());
+  TTRT_ASSERT(in->volume() == size_t(n) * h * w * c, "max_pool2d_with_indices input has ", in->volume(), " elements, the op says ", n, "x",
+              h, "x", w, "x", c);
+  auto two = [](const fb::Vector<int32_t> *v, const char *what, int &a, int &b, int dflt) {
+    if (!v || v->size() == 0) {
+      a = b = dflt;
+      return;
+    }
+    TTRT_ASSERT(v->size() == 2 || v->size() == 4, what, " needs two entries");
+    a = v->Get(0);
+    b = v->Get(1);
+    if (v->size() == 4) TTRT_ASSERT(v->Get(2) == a && v->Get(3) == b, what, ": asymmetric padding is not supported with indices");
+  };
+  int kh, kw, sh, sw, ph, pw, dh, dw;
+  two(op->kernel_size(), "kernel_size", kh, kw, 1);
+  two(op->stride(), "stride", sh, sw, 1);
+  two(op->padding(), "padding", ph, pw, 0);
+  two(op->dilation(), "dilation", dh, dw, 1);
+  int ho = 0, wo = 0;
+  TTB_CALL(ttb_pool2d_out_shape(1, h, w, kh, kw, sh, sw, ph, pw, ph, pw, dh, dw, op->ceil_mode(), 0, &ho, &wo));
+  TTRT_ASSERT(out->volume() == size_t(n) * ho * wo * c && idx->volume() == out->volume(), "max_pool2d_with_indices results have ",
+              out->volume(), " elements, expected ", n, "x", ho, "x", wo, "x", c);
+  TTRT_ASSERT(out->dtype == in->dtype, "max_pool2d_with_indices changes the data type");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_max_pool2d_with_indices(in->shards[i]->ptr, out->shards[i]->ptr, idx->shards[i]->ptr, ttbDtype(in->dtype),
+                                         ttbDtype(idx->dtype), n, h, w, c, ho, wo, kh, kw, sh, sw, ph, pw, dh, dw, r.stream));
+  });
+  put(op->result(), out);
+  put(op->result_indices(), idx);
+}
+
+// dropout: with use_per_device_seed every mesh coordinate draws its own stream (operations/eltwise/unary/dropout.cpp).
+void Executor::runDropout(const fbt::DropoutOp *op) {
+  TensorPtr in = getDevice(op->in());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(out->dtype == in->dtype && out->volume() == in->volume(), "dropout changes shape or type");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_dropout(in->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(in->dtype), in->volume(), op->prob(), op->scale(), op->seed(),
+                         op->use_per_device_seed() ? r.meshRank : 0u, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// rand: uniform in [low, high), the same tensor on every mesh coordinate (golden mapping.py:4340-4362).
+void Executor::runRand(const fbt::RandOp *op) {
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(op->size() != nullptr, "rand without a size");
+  size_t n = 1;
+  for (int64_t d : *op->size()) n *= static_cast<size_t>(d);
+  TTRT_ASSERT(n == out->volume(), "rand size differs from the op's result type");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_rand_uniform(out->shards[i]->ptr, ttbDtype(out->dtype), n, op->low(), op->high(), op->seed(), 0u, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// Training batch norm over dim 1 of [N, C, ...]; running_mean / running_var are updated in place.
+void Executor::runBatchNormTraining(const fbt::BatchNormTrainingOp *op) {
+  TensorPtr x = getDevice(op->input()), mean = getDevice(op->running_mean()), var = getDevice(op->running_var());
+  TensorPtr w = op->weight() ? getDevice(op->weight()) : nullptr, b = op->bias() ? getDevice(op->bias()) : nullptr;
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(x->shape.size() >= 2, "batch_norm expects [N, C, ...]");
+  const size_t outer = x->shape[0], channels = x->shape[1], inner = prod(x->shape, 2, x->shape.size());
+  TTRT_ASSERT(mean->volume() == channels && var->volume() == channels && (!w || w->volume() == channels) && (!b || b->volume() == channels),
+              "batch_norm statistics and parameters must have one entry per channel (", channels, ")");
+  TTRT_ASSERT(mean->dtype == x->dtype && var->dtype == x->dtype && (!w || w->dtype == x->dtype) && (!b || b->dtype == x->dtype) &&
+                  out->dtype == x->dtype && out->volume() == x->volume(),
+              "batch_norm tensors must share one data type");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_batch_norm_training(x->shards[i]->ptr, mean->shards[i]->ptr, var->shards[i]->ptr, w ? w->shards[i]->ptr : nullptr,
+                                     b ? b->shards[i]->ptr : nullptr, out->shards[i]->ptr, ttbDtype(x->dtype), outer, channels, inner,
+                                     op->epsilon(), op->momentum(), r.stream));
+  });
+  mean->version = TensorImpl::nextTensorVersion();
+  var->version = TensorImpl::nextTensorVersion();
+  put(op->out(), out);
+}
+
 void Executor::runGroupNorm(const fbt::GroupNormOp *op) {
   TTRT_ASSERT(!op->input_mask(), "group_norm with an input mask (a Tenstorrent core-grid artefact) is not supported");
   TensorPtr x = getDevice(op->input());
@@ -2496,6 +2985,8 @@ void Executor::runGroupNorm(const fbt::GroupNormOp *op) {
 void Executor::runConvTranspose2d(const fbt::ConvTranspose2dOp *op) {
   TensorPtr x = getDevice(op->input()), w = getDevice(op->weight());
   TensorPtr bias = op->bias() ? getDevice(op->bias()) : nullptr;
+  if (w->preparedFrom) w = w->preparedFrom; // prepare_conv_transpose2d_weights handed the original on
+  if (bias && bias->preparedFrom) bias = bias->preparedFrom;
   TensorPtr out = allocOut(op->out());
   auto two = [](const fb::Vector<int32_t> *v, const char *what, int &a, int &b) {
     TTRT_ASSERT(v && (v->size() == 2 || v->size() == 4), "conv_transpose2d ", what, " must have 2 entries");

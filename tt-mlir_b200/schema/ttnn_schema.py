@@ -274,6 +274,62 @@ S.table("Conv1dOp", [
     ("compute_config", "DeviceComputeKernelConfig"), ("conv2d_slice_config", "opaque")])
 S.table("BitcastConvertOp", [("in", "TensorRef"), ("dtype", "DataType"), ("memcfg", "MemoryConfig"), ("out", "TensorRef")])
 S.table("NLPConcatHeadsOp", [("in", "TensorRef"), ("out", "TensorRef"), ("memcfg", "MemoryConfig")])
+S.table("AssignOp", [
+    ("input", "TensorRef"), ("output", "TensorRef"), ("output_memory_config", "MemoryConfig"),
+    ("output_dtype", "DataType", OPT)])
+S.enum("EltwiseBinaryCompositeScalarOpType", "u32", ["PowScalar"])
+S.table("EltwiseBinaryCompositeScalarOp", [
+    ("type", "EltwiseBinaryCompositeScalarOpType"), ("lhs", "TensorRef"), ("rhs", "NumberType"),
+    ("memory_config", "MemoryConfig"), ("out", "TensorRef")])
+S.table("DumpTensorOp", [("file_path", "string"), ("in", "TensorRef")])
+S.table("LoadTensorOp", [("file_path", "string"), ("device", "DeviceRef"), ("out", "TensorRef")])
+S.table("AnnotateOp", [("operand", "TensorRef"), ("result", "TensorRef"), ("annotation", "string")])
+S.table("BreakpointOp", [("operand", "TensorRef")])
+S.table("PrintOp", [("operand", "TensorRef"), ("message", "string")])
+S.table("MemorySnapshotOp", [("operand", "TensorRef"), ("file_path", "string")])
+S.table("RegionStartOp", [("operand", "TensorRef"), ("result", "TensorRef"), ("region_id", "string")])
+S.table("RegionEndOp", [("operand", "TensorRef"), ("result", "TensorRef"), ("region_id", "string")])
+S.table("PrepareConvTranspose2dWeightsOp", [
+    ("weight_tensor", "TensorRef"), ("out", "TensorRef"), ("input_memory_config", "MemoryConfig"),
+    ("input_tensor_layout", "TensorLayout"), ("weights_format", "string"), ("in_channels", "u32"),
+    ("out_channels", "u32"), ("batch_size", "u32"), ("input_height", "u32"), ("input_width", "u32"),
+    ("kernel_size", "[i32]"), ("stride", "[i32]"), ("padding", "[i32]"), ("output_padding", "[i32]"),
+    ("dilation", "[i32]"), ("has_bias", "bool"), ("groups", "u32"), ("device", "DeviceRef"),
+    ("input_dtype", "DataType"), ("output_dtype", "DataType", OPT), ("conv2d_config", "opaque"),
+    ("compute_config", "DeviceComputeKernelConfig"), ("conv2d_slice_config", "opaque"), ("mirror_kernel", "bool", True)])
+S.table("PrepareConvTranspose2dBiasOp", [
+    ("bias_tensor", "TensorRef"), ("out", "TensorRef"), ("input_memory_config", "MemoryConfig"),
+    ("input_tensor_layout", "TensorLayout"), ("in_channels", "u32"), ("out_channels", "u32"), ("batch_size", "u32"),
+    ("input_height", "u32"), ("input_width", "u32"), ("kernel_size", "[i32]"), ("stride", "[i32]"),
+    ("padding", "[i32]"), ("dilation", "[i32]"), ("groups", "u32"), ("device", "DeviceRef"),
+    ("input_dtype", "DataType"), ("output_dtype", "DataType", OPT), ("conv2d_config", "opaque"),
+    ("compute_config", "DeviceComputeKernelConfig"), ("conv2d_slice_config", "opaque")])
+S.table("NLPCreateQKVHeadsDecodeOp", [
+    ("input", "TensorRef"), ("q_out", "TensorRef"), ("k_out", "TensorRef"), ("v_out", "TensorRef"),
+    ("num_heads", "u32"), ("num_kv_heads", "u32", OPT), ("overlap_qk_coregrid", "bool", OPT),
+    ("batch_offset", "TensorRef"), ("slice_size", "u32", OPT), ("memcfg", "MemoryConfig")])
+S.table("NLPConcatHeadsDecodeOp", [
+    ("in", "TensorRef"), ("out", "TensorRef"), ("num_heads", "u32"), ("memcfg", "MemoryConfig")])
+S.table("RotaryEmbeddingLlamaOp", [
+    ("input", "TensorRef"), ("cos_cache", "TensorRef"), ("sin_cache", "TensorRef"), ("trans_mat", "TensorRef"),
+    ("is_decode_mode", "bool"), ("out", "TensorRef"), ("memcfg", "MemoryConfig"),
+    ("compute_config", "DeviceComputeKernelConfig")])
+S.table("MaxPool2dWithIndicesOp", [
+    ("in", "TensorRef"), ("result", "TensorRef"), ("result_indices", "TensorRef"), ("batch_size", "u32"),
+    ("input_height", "u32"), ("input_width", "u32"), ("channels", "u32"), ("kernel_size", "[i32]"),
+    ("stride", "[i32]"), ("padding", "[i32]"), ("dilation", "[i32]"), ("memory_config", "MemoryConfig"),
+    ("applied_shard_scheme", "TensorMemoryLayout", OPT), ("ceil_mode", "bool"),
+    ("reallocate_halo_output", "bool", True), ("config_tensors_in_dram", "bool")])
+S.table("DropoutOp", [
+    ("in", "TensorRef"), ("prob", "f32"), ("scale", "f32"), ("seed", "u32"), ("use_per_device_seed", "bool", True),
+    ("output_dtype", "DataType", OPT), ("memory_config", "MemoryConfig"), ("out", "TensorRef")])
+S.table("RandOp", [
+    ("device", "DeviceRef"), ("size", "[i64]"), ("low", "f32"), ("high", "f32"), ("seed", "u32"),
+    ("dtype", "DataType"), ("layout", "TensorLayout"), ("memcfg", "MemoryConfig"), ("out", "TensorRef")])
+S.table("BatchNormTrainingOp", [
+    ("input", "TensorRef"), ("running_mean", "TensorRef"), ("running_var", "TensorRef"), ("epsilon", "f32"),
+    ("momentum", "f32"), ("weight", "TensorRef"), ("bias", "TensorRef"), ("memory_config", "MemoryConfig"),
+    ("out", "TensorRef"), ("compute_config", "DeviceComputeKernelConfig")])
 S.table("UniformScale2D", [("scale", "i32")])
 S.table("NonUniformScale2D", [("scale", "[i32]")])
 S.union("Scale2D", ["UniformScale2D", "NonUniformScale2D"])
@@ -397,6 +453,13 @@ S.table("AllReduceOp", [
     ("in", "TensorRef"), ("out", "TensorRef"), ("reduce_type", "u32"), ("cluster_axis", "u32"),
     ("sub_device_id", "u8", OPT), ("memory_config", "MemoryConfig"), ("num_links", "u32", OPT),
     ("topology", "Topology", OPT)])
+S.table("AllReduceAsyncOp", [
+    ("in", "TensorRef"), ("out", "TensorRef"), ("reduce_type", "u32"), ("cluster_axis", "u32"),
+    ("sub_device_id", "u8", OPT), ("memory_config", "MemoryConfig"), ("num_links", "u32", OPT),
+    ("topology", "Topology", OPT)])
+S.table("PointToPointOp", [
+    ("in", "TensorRef"), ("out", "TensorRef"), ("sender_coord", "[u32]"), ("receiver_coord", "[u32]"),
+    ("optional_output_tensor", "TensorRef")])
 S.table("ReduceScatterOp", [
     ("in", "TensorRef"), ("out", "TensorRef"), ("scatter_dim", "i32"), ("reduce_type", "u32"),
     ("cluster_axis", "u32"), ("sub_device_id", "u8", OPT), ("memory_config", "MemoryConfig"),

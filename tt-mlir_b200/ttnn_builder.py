@@ -613,7 +613,7 @@ class ProgramBuilder:
     def conv_transpose2d(self, x: Value, w: Value, bias: Optional[Value], batch: int, height: int, width: int, stride=(1, 1),
                          padding=(0, 0), output_padding=(0, 0), dilation=(1, 1), groups: int = 1, loc=None) -> Value:
         """x is [1, 1, N*H*W, C] or [N, H, W, C]; w is [C, O/groups, kH, kW]; bias [1, 1, 1, O]."""
-        c, og, kh, kw = w.shape
+        c, og, kh, kw = getattr(w, "filter_shape", w.shape)
         o = og * groups
         ho = (height - 1) * stride[0] - 2 * padding[0] + dilation[0] * (kh - 1) + output_padding[0] + 1
         wo = (width - 1) * stride[1] - 2 * padding[1] + dilation[1] * (kw - 1) + output_padding[1] + 1
@@ -649,6 +649,156 @@ class ProgramBuilder:
         b, h, s_, d = x.shape
         out = self._value([b, 1, s_, h * d], x.dtype)
         self._emit("NLPConcatHeadsOp", {"in": x.ref, "out": out.ref, "memcfg": self._mc()}, [x], [out], loc)
+        return out
+
+    # ---- further ops of real model flatbuffers: copies, debug markers, decode-step head ops, random ops
+    def assign(self, x: Value, dtype: Optional[str] = None, loc=None) -> Value:
+        out = self._value(x.shape, dtype or x.dtype)
+        t = {"input": x.ref, "output": out.ref, "output_memory_config": self._mc()}
+        if dtype:
+            t["output_dtype"] = dtype
+        self._emit("AssignOp", t, [x], [out], loc)
+        return out
+
+    def pow_scalar(self, x: Value, exponent, loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        rhs = ("FP", {"value": float(exponent)}) if isinstance(exponent, float) else ("I32", {"value": int(exponent)})
+        self._emit("EltwiseBinaryCompositeScalarOp", {"type": "PowScalar", "lhs": x.ref, "rhs": rhs, "memory_config": self._mc(),
+                                                      "out": out.ref}, [x], [out], loc)
+        return out
+
+    def _marker(self, op_type: str, x: Value, key: str, text: str, loc=None) -> Value:
+        out = self._value(x.shape, x.dtype, x.on_device)
+        self._emit(op_type, {"operand": x.ref, "result": out.ref, key: text}, [x], [out], loc)
+        return out
+
+    def annotate(self, x: Value, annotation: str, loc=None) -> Value: return self._marker("AnnotateOp", x, "annotation", annotation, loc)
+    def region_start(self, x: Value, region_id: str, loc=None) -> Value: return self._marker("RegionStartOp", x, "region_id", region_id, loc)
+    def region_end(self, x: Value, region_id: str, loc=None) -> Value: return self._marker("RegionEndOp", x, "region_id", region_id, loc)
+
+    def breakpoint(self, x: Value, loc=None) -> None: self._emit("BreakpointOp", {"operand": x.ref}, [x], [], loc)
+    def print_message(self, x: Value, message: str, loc=None) -> None: self._emit("PrintOp", {"operand": x.ref, "message": message}, [x], [], loc)
+
+    def memory_snapshot(self, x: Value, file_path: str, loc=None) -> None:
+        self._emit("MemorySnapshotOp", {"operand": x.ref, "file_path": file_path}, [x], [], loc)
+
+    def dump_tensor(self, x: Value, file_path: str, loc=None) -> None:
+        self._emit("DumpTensorOp", {"file_path": file_path, "in": x.ref}, [x], [], loc)
+
+    def load_tensor(self, file_path: str, shape, dtype: str, on_device: bool = True, loc=None) -> Value:
+        out = self._value(shape, dtype, on_device)
+        t = {"file_path": file_path, "out": out.ref}
+        if on_device:
+            t["device"] = self.device_ref
+        self._emit("LoadTensorOp", t, [], [out], loc)
+        return out
+
+    def nlp_create_qkv_heads_decode(self, x: Value, num_heads: int, num_kv_heads: Optional[int] = None,
+                                    batch_offset: Optional[Value] = None, slice_size: Optional[int] = None, loc=None):
+        """x is [1, 1, batch, (num_heads + 2 * num_kv_heads) * head_dim]; q is [1, batch, num_heads, head_dim]."""
+        _, _, b, hidden = x.shape
+        hkv = num_kv_heads if num_kv_heads is not None else num_heads
+        d = hidden // (num_heads + 2 * hkv)
+        nb = slice_size if slice_size is not None else b
+        q, k, v = (self._value([1, nb, h, d], x.dtype) for h in (num_heads, hkv, hkv))
+        t = {"input": x.ref, "q_out": q.ref, "k_out": k.ref, "v_out": v.ref, "num_heads": num_heads, "memcfg": self._mc()}
+        if num_kv_heads is not None:
+            t["num_kv_heads"] = num_kv_heads
+        if slice_size is not None:
+            t["slice_size"] = slice_size
+            t["batch_offset"] = batch_offset.ref
+        self._emit("NLPCreateQKVHeadsDecodeOp", t, [x] + ([batch_offset] if batch_offset is not None else []), [q, k, v], loc)
+        return q, k, v
+
+    def nlp_concat_heads_decode(self, x: Value, num_heads: int, loc=None) -> Value:
+        _, b, _, d = x.shape
+        out = self._value([1, 1, b, num_heads * d], x.dtype)
+        self._emit("NLPConcatHeadsDecodeOp", {"in": x.ref, "out": out.ref, "num_heads": num_heads, "memcfg": self._mc()}, [x], [out], loc)
+        return out
+
+    def rotary_embedding_llama(self, x: Value, cos: Value, sin: Value, trans_mat: Value, is_decode_mode: bool = False, loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        self._emit("RotaryEmbeddingLlamaOp", {"input": x.ref, "cos_cache": cos.ref, "sin_cache": sin.ref, "trans_mat": trans_mat.ref,
+                                              "is_decode_mode": is_decode_mode, "out": out.ref, "memcfg": self._mc()},
+                   [x, cos, sin, trans_mat], [out], loc)
+        return out
+
+    def max_pool2d_with_indices(self, x: Value, batch: int, height: int, width: int, channels: int, kernel=(2, 2), stride=(2, 2),
+                                padding=(0, 0), dilation=(1, 1), ceil_mode: bool = False, index_dtype: str = "Int32", loc=None):
+        ho, wo = self.pool_out_hw("MaxPool2d", height, width, kernel, stride, padding, dilation, ceil_mode)
+        out = self._value([1, 1, batch * ho * wo, channels], x.dtype)
+        idx = self._value([1, 1, batch * ho * wo, channels], index_dtype)
+        self._emit("MaxPool2dWithIndicesOp", {
+            "in": x.ref, "result": out.ref, "result_indices": idx.ref, "batch_size": batch, "input_height": height,
+            "input_width": width, "channels": channels, "kernel_size": list(kernel), "stride": list(stride),
+            "padding": list(padding), "dilation": list(dilation), "memory_config": self._mc(), "ceil_mode": ceil_mode},
+            [x], [out, idx], loc)
+        return out, idx
+
+    def dropout(self, x: Value, prob: float, scale: Optional[float] = None, seed: int = 0, use_per_device_seed: bool = True,
+                loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        scale = 1.0 / (1.0 - prob) if scale is None else scale
+        self._emit("DropoutOp", {"in": x.ref, "prob": prob, "scale": scale, "seed": seed, "use_per_device_seed": use_per_device_seed,
+                                 "memory_config": self._mc(), "out": out.ref}, [x], [out], loc)
+        return out
+
+    def rand(self, shape, dtype: str, low: float = 0.0, high: float = 1.0, seed: int = 0, loc=None) -> Value:
+        out = self._value(shape, dtype)
+        self._emit("RandOp", {"device": self.device_ref, "size": list(shape), "low": low, "high": high, "seed": seed, "dtype": dtype,
+                              "layout": "Tile", "memcfg": self._mc(), "out": out.ref}, [], [out], loc)
+        return out
+
+    def batch_norm_training(self, x: Value, mean: Value, var: Value, weight: Optional[Value], bias: Optional[Value],
+                            epsilon: float = 1e-5, momentum: float = 0.1, loc=None) -> Value:
+        """x is [N, C, ...]; `mean` / `var` are the running statistics, updated in place."""
+        out = self._value(x.shape, x.dtype)
+        ins = [x, mean, var] + [t for t in (weight, bias) if t is not None]
+        self._emit("BatchNormTrainingOp", {
+            "input": x.ref, "running_mean": mean.ref, "running_var": var.ref, "epsilon": epsilon, "momentum": momentum,
+            "weight": weight.ref if weight else None, "bias": bias.ref if bias else None, "memory_config": self._mc(),
+            "out": out.ref}, ins, [out], loc)
+        return out
+
+    def all_reduce_async(self, x: Value, reduce_type: int = 0, cluster_axis: int = 1, loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        self._emit("AllReduceAsyncOp", {"in": x.ref, "out": out.ref, "reduce_type": reduce_type, "cluster_axis": cluster_axis,
+                                        "memory_config": self._mc()}, [x], [out], loc)
+        return out
+
+    def point_to_point(self, x: Value, sender_coord, receiver_coord, output: Optional[Value] = None, loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        t = {"in": x.ref, "out": out.ref, "sender_coord": list(sender_coord), "receiver_coord": list(receiver_coord)}
+        if output is not None:
+            t["optional_output_tensor"] = output.ref
+        self._emit("PointToPointOp", t, [x] + ([output] if output is not None else []), [out], loc)
+        return out
+
+    def prepare_conv_transpose2d_weights(self, w: Value, batch: int, height: int, width: int, stride=(1, 1), padding=(0, 0),
+                                         output_padding=(0, 0), dilation=(1, 1), groups: int = 1, has_bias: bool = True,
+                                         loc=None) -> Value:
+        """Like prepare_conv2d_weights, for [C_in, C_out / groups, kH, kW] filters."""
+        c, og, kh, kw = w.shape
+        up = lambda v: (v + 31) // 32 * 32
+        out = self._value([1, 1, up(kh * kw * c), up(og * groups)], w.dtype)
+        out.filter_shape = list(w.shape)
+        self._emit("PrepareConvTranspose2dWeightsOp", {
+            "weight_tensor": w.ref, "out": out.ref, "input_memory_config": self._mc(), "input_tensor_layout": "Tile",
+            "weights_format": "IOHW", "in_channels": c, "out_channels": og * groups, "batch_size": batch, "input_height": height,
+            "input_width": width, "kernel_size": [kh, kw], "stride": list(stride), "padding": list(padding),
+            "output_padding": list(output_padding), "dilation": list(dilation), "has_bias": has_bias, "groups": groups,
+            "device": self.device_ref, "input_dtype": w.dtype}, [w], [out], loc)
+        return out
+
+    def prepare_conv_transpose2d_bias(self, bias: Value, in_channels: int, batch: int, height: int, width: int, kernel=(1, 1),
+                                      stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups: int = 1, loc=None) -> Value:
+        o = bias.shape[-1]
+        out = self._value([1, 1, 1, (o + 31) // 32 * 32], bias.dtype)
+        self._emit("PrepareConvTranspose2dBiasOp", {
+            "bias_tensor": bias.ref, "out": out.ref, "input_memory_config": self._mc(), "input_tensor_layout": "Tile",
+            "in_channels": in_channels, "out_channels": o, "batch_size": batch, "input_height": height, "input_width": width,
+            "kernel_size": list(kernel), "stride": list(stride), "padding": list(padding), "dilation": list(dilation),
+            "groups": groups, "device": self.device_ref, "input_dtype": bias.dtype}, [bias], [out], loc)
         return out
 
     def prepare_conv2d_weights(self, w: Value, batch: int, height: int, width: int, stride=(1, 1), padding=(0, 0, 0, 0),

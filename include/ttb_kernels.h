@@ -183,6 +183,26 @@ TTB_API int ttb_rms_norm(const void *in, const void *weight, const void *bias, v
 TTB_API int ttb_add_rms_norm(const void *a, const void *b, const void *weight, void *sum_out,
                              void *out, int dtype, size_t rows, size_t cols, float eps,
                              void *stream);
+/* Split normalisations (hidden dimension sharded over the mesh).  ttb_norm_row_stats reduces each row of x (+ residual)
+ * into the reference's tile-layout statistics: mode 0 (::ttnn::rms_norm_pre_all_gather,
+ * operations/normalization/rms_norm_pre_all_gather.cpp) writes [rows, 32] with mean(x^2) in column 0; mode 1
+ * (::ttnn::layer_norm_pre_all_gather) writes [rows, 64] with sum(x^2) in column 0 and sum(x) in column 32; mode 2 writes
+ * the plain f32 sum of squares per row (the exchange buffer of distributed_rms_norm).  Other columns are zero. */
+TTB_API int ttb_norm_row_stats(const void *x, const void *residual, void *stats, int dtype, int stats_dtype, size_t rows,
+                               size_t cols, int mode, void *stream);
+/* y = act(rms_norm(x + residual) * weight + bias) over the last dimension (::ttnn::experimental::dit_rms_norm_unary_fused,
+ * operations/normalization/dit_rms_norm_unary_fused.cpp), and the local half of ::ttnn::fused_rms_minimal
+ * (distributed_rms_norm.cpp) when `row_sumsq` gives each row's sum of squares over all `total_cols` columns of the
+ * distributed row.  residual, weight, bias, row_sumsq nullable.  act: 0 none, 1 relu, 2 relu6, 3 silu, 4 mish,
+ * 5 sigmoid, 6 hardsigmoid, 7 tanh, 8 log, 9 softplus, 10 gelu, 11 sqrt. */
+TTB_API int ttb_rms_norm_apply(const void *x, const void *residual, const void *weight, const void *bias, const float *row_sumsq,
+                               void *y, int dtype, size_t rows, size_t cols, size_t total_cols, float eps, int act, void *stream);
+/* ::ttnn::layer_norm_post_all_gather (operations/normalization/layer_norm_post_all_gather.cpp): `stats` is
+ * [rows, 64 * blocks], one mode-1 block per device; mean and variance of the whole row of cols * blocks elements
+ * normalise the local `cols` columns. */
+TTB_API int ttb_layer_norm_post_all_gather(const void *x, const void *stats, const void *weight, const void *bias, void *y,
+                                           int dtype, int stats_dtype, size_t rows, size_t cols, size_t blocks, float eps,
+                                           void *stream);
 /* op: 0 sum, 1 mean, 2 max, 3 min (ReductionOpType, operations/reduction.fbs:6-11). */
 TTB_API int ttb_reduce(int op, const void *in, void *out, int dtype, size_t outer, size_t len,
                        size_t inner, void *stream);

@@ -361,6 +361,28 @@ class OracleBuilder:
         return OValue(ops.mesh_shard_shard_to_full(x.t, shard_dim))
 
     def all_reduce(self, x, reduce_type=0, cluster_axis=1, loc=None): return OValue(ops.all_reduce(x.t, reduce_type))
+    def dit_rms_norm_unary_fused(self, x, weight=None, bias=None, residual=None, epsilon=1e-5, activation=None, loc=None):
+        return _map(lambda t, w, b, r: ops.dit_rms_norm_unary_fused(t, w, b, r, epsilon, activation), x, weight, bias, residual)
+
+    def distributed_rms_norm(self, x, weight=None, residual=None, cluster_axis=1, epsilon=1e-5, loc=None):
+        if not isinstance(x.t, list):
+            return OValue(ops.distributed_rms_norm([x.t], [weight.t] if weight is not None else None,
+                                                   [residual.t] if residual is not None else None, epsilon)[0])
+        per = lambda v: (v.t if isinstance(v.t, list) else [v.t] * len(x.t)) if v is not None else None
+        return OValue(ops.distributed_rms_norm(x.t, per(weight), per(residual), epsilon))
+
+    def rms_norm_pre_all_gather(self, x, residual=None, dtype=None, loc=None):
+        return _map(lambda t, r: ops.rms_norm_pre_all_gather(t, r, TORCH_DTYPE[dtype] if dtype else t.dtype), x, residual)
+
+    def layer_norm_pre_all_gather(self, x, residual=None, dtype=None, loc=None):
+        return _map(lambda t, r: ops.layer_norm_pre_all_gather(t, r, TORCH_DTYPE[dtype] if dtype else t.dtype), x, residual)
+
+    def layer_norm_post_all_gather(self, x, stats, weight=None, bias=None, epsilon=1e-12, loc=None):
+        return _map(lambda t, st, w, b: ops.layer_norm_post_all_gather(t, st, w, b, epsilon), x, stats, weight, bias)
+
+    def create_global_semaphore(self, initial_value=0, loc=None): return None
+    def reset_global_semaphore(self, value=0, loc=None): return None
+
     def all_reduce_async(self, x, reduce_type=0, cluster_axis=1, loc=None): return OValue(ops.all_reduce(x.t, reduce_type))
 
     def point_to_point(self, x, sender_coord, receiver_coord, output=None, loc=None):

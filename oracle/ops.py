@@ -676,3 +676,75 @@ def nlp_create_qkv_heads_decode(x, num_heads, num_kv_heads, batch_offset=0, slic
 def nlp_concat_heads_decode(x, num_heads):
     """::ttnn::experimental::nlp_concat_heads_decode: [1, B, padded heads, D] -> [1, 1, B, num_heads * D]."""
     return x[:, :, :num_heads, :].reshape(1, 1, x.shape[1], num_heads * x.shape[3]).contiguous()
+
+
+FUSED_ACTIVATIONS = {
+    "relu": torch.nn.functional.relu, "relu6": torch.nn.functional.relu6, "silu": torch.nn.functional.silu,
+    "mish": torch.nn.functional.mish, "sigmoid": torch.sigmoid, "hardsigmoid": torch.nn.functional.hardsigmoid,
+    "tanh": torch.tanh, "log": torch.log, "softplus": torch.nn.functional.softplus, "gelu": torch.nn.functional.gelu,
+    "sqrt": torch.sqrt,
+}
+
+
+def dit_rms_norm_unary_fused(x, weight, bias, residual, eps: float, activation):
+    """tools/golden/mapping.py:1291-1326: act(rms_norm(x + residual, weight) + bias), f32 throughout, one rounding."""
+    xf = x.float() if residual is None else x.float() + residual.float()
+    y = xf * torch.rsqrt(xf.square().mean(dim=-1, keepdim=True) + eps)
+    if weight is not None:
+        y = y * weight.float().reshape(-1)
+    if bias is not None:
+        y = y + bias.float().reshape(-1)
+    if activation:
+        name = activation[:-7] if activation.endswith("_approx") else activation
+        y = FUSED_ACTIVATIONS[name](y)
+    return y.to(x.dtype)
+
+
+def distributed_rms_norm(shards, weights, residuals, eps: float):
+    """tools/golden/mapping.py:1329-1415: the shards are slices of the last dimension; the RMS statistics are those
+    of the concatenated rows, weight slices apply locally, each device keeps its slice of the result."""
+    xs = [s.float() if residuals is None else s.float() + r.float() for s, r in zip(shards, residuals or shards)]
+    total = sum(x.square().sum(dim=-1, keepdim=True) for x in xs)
+    n = sum(x.shape[-1] for x in xs)
+    scale = torch.rsqrt(total / n + eps)
+    out = []
+    for i, x in enumerate(xs):
+        y = x * scale
+        if weights is not None:
+            y = y * weights[i].float().reshape(-1)
+        out.append(y.to(shards[i].dtype))
+    return out
+
+
+def rms_norm_pre_all_gather(x, residual, dtype):
+    """tools/golden/mapping.py:7800-7826: [..., 32] with E(x^2) of the local row in column 0."""
+    xf = x.float() if residual is None else x.float() + residual.float()
+    out = torch.zeros(list(x.shape[:-1]) + [32])
+    out[..., :1] = xf.square().mean(dim=-1, keepdim=True)
+    return out.to(dtype)
+
+
+def layer_norm_pre_all_gather(x, residual, dtype):
+    """tools/golden/mapping.py:7852-7888: [..., 64] with sum(x^2) in column 0 and sum(x) in column 32."""
+    xf = x.float() if residual is None else x.float() + residual.float()
+    out = torch.zeros(list(x.shape[:-1]) + [64])
+    out[..., :1] = xf.square().sum(dim=-1, keepdim=True)
+    out[..., 32:33] = xf.sum(dim=-1, keepdim=True)
+    return out.to(dtype)
+
+
+def layer_norm_post_all_gather(x, stats, weight, bias, eps: float):
+    """::ttnn::layer_norm_post_all_gather: mean and variance of the whole distributed row rebuilt from the gathered
+    [..., 64 * devices] statistics normalise the local slice.  With one device this is the reference golden
+    (tools/golden/mapping.py:7891-7921, layer_norm of the shard)."""
+    blocks = stats.shape[-1] // 64
+    st = stats.float().reshape(*stats.shape[:-1], blocks, 64)
+    n = x.shape[-1] * blocks
+    mean = st[..., 32].sum(dim=-1, keepdim=True) / n
+    var = (st[..., 0].sum(dim=-1, keepdim=True) / n - mean * mean).clamp_min(0.0)
+    y = (x.float() - mean) * torch.rsqrt(var + eps)
+    if weight is not None:
+        y = y * weight.float().reshape(-1)
+    if bias is not None:
+        y = y + bias.float().reshape(-1)
+    return y.to(x.dtype)

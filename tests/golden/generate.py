@@ -466,6 +466,21 @@ def main():
         store(out, f"map/max_pool_indices/{name}", one(v))
         store(out, f"map/max_pool_indices/{name}_idx", one(ix).to(torch.int32))
 
+    # --- split normalisations (mapping.py:1291-1415, 7800-7921)
+    nx, nres = rnd(6, 96), rnd(6, 96) * 0.5
+    nw, nb = rnd(96) * 0.5 + 1.0, rnd(96) * 0.2
+    for n, t in (("x", nx), ("residual", nres), ("weight", nw), ("bias", nb)):
+        store(out, f"map/split_norm/{n}", t)
+    store(out, "map/split_norm/dit_silu", one(ref.dit_rms_norm_unary_fused_golden(gmt(nx), gmt(nw), gmt(nb), gmt(nres), None, 1e-5, "silu")))
+    store(out, "map/split_norm/dit_plain", one(ref.dit_rms_norm_unary_fused_golden(gmt(nx), gmt(nw), None, None, None, 1e-6, None)))
+    store(out, "map/split_norm/rms_pre", one(ref.ttnn_rms_norm_pre_all_gather_golden(gmt(nx), gmt(nres), S.F32Type())))
+    store(out, "map/split_norm/ln_pre", one(ref.ttnn_layer_norm_pre_all_gather_golden(gmt(nx), None, None, S.F32Type())))
+    store(out, "map/split_norm/ln_post_1dev", one(ref.ttnn_layer_norm_post_all_gather_golden(
+        gmt(nx), gmt(torch.zeros(6, 64)), gmt(nw), gmt(nb), S.FloatAttr(1e-5), S.F32Type())))
+    xsh, rsh, wsh = sharded(nx, (1, 4), [-1, 1]), sharded(nres, (1, 4), [-1, 1]), sharded(nw, (1, 4), [-1, 0])
+    store_shards("map/split_norm/dist_rms_1x4", ref.ttir_distributed_rms_norm_golden(xsh, wsh, rsh, S.IntegerAttr(1), S.FloatAttr(1e-5),
+                                                                                     S.F32Type()))
+
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ttir_cpu_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes")

@@ -74,6 +74,25 @@ def test_all_reduce_all_gather_reduce_scatter(rt, mesh2):
     assert torch.equal(got[1], x) and torch.equal(got[4], x)
 
 
+def test_norms_with_the_hidden_dimension_split_over_the_mesh(rt, mesh2):
+    torch.manual_seed(21)
+    x, res = torch.randn(48, 512), torch.randn(48, 512) * 0.5
+    w, bias = torch.rand(512) + 0.5, torch.randn(512) * 0.1
+
+    def body(b, xv, rv, wv, bv):
+        xs, rs, ws, bs = b.distribute(xv, 1), b.distribute(rv, 1), b.distribute(wv, 0), b.distribute(bv, 0)
+        rms = b.aggregate(b.distributed_rms_norm(xs, ws, rs), 1)
+        stats = b.all_gather(b.layer_norm_pre_all_gather(xs, dtype="Float32"), 1)
+        ln = b.aggregate(b.layer_norm_post_all_gather(xs, stats, ws, bs, 1e-5), 1)
+        return rms, ln
+    got, want = run_mesh(rt, mesh2, body, [x, res, w, bias])
+    xr = x + res
+    assert torch.allclose(got[0], xr * torch.rsqrt(xr.square().mean(-1, keepdim=True) + 1e-5) * w, rtol=1e-5, atol=1e-5)
+    assert torch.allclose(got[1], torch.nn.functional.layer_norm(x, [512], w, bias, 1e-5), rtol=1e-4, atol=1e-4)
+    for g, w_ in zip(got, want):
+        assert torch.allclose(g, w_, rtol=1e-4, atol=1e-4)
+
+
 def test_point_to_point_and_all_reduce_async(rt, mesh2):
     x = torch.randn(4, 6, 16)
     y = torch.randn(4, 6, 16)

@@ -212,3 +212,40 @@ def test_prepared_conv_transpose_weights_run_like_the_raw_ones(rt, device, golde
         return b.conv_transpose2d(xv, pw, pb, 2, 5, 6, stride=(2, 2), padding=(1, 1), output_padding=(1, 1))
     got, want = run_body(rt, device, body, [x, w, b_])
     assert torch.allclose(got[0], golden["map/conv_transpose/s2_p1_op1"], rtol=1e-5, atol=1e-5) and torch.allclose(got[0], want[0], rtol=1e-5, atol=1e-5)
+
+
+def test_split_normalisations_match_the_reference_goldens(rt, device, golden):
+    x, res, w, b_ = (golden[f"map/split_norm/{n}"] for n in ("x", "residual", "weight", "bias"))
+    got, want = run_body(rt, device, lambda b, xv, rv, wv, bv: (
+        b.dit_rms_norm_unary_fused(xv, wv, bv, rv, 1e-5, "silu"), b.dit_rms_norm_unary_fused(xv, wv, epsilon=1e-6),
+        b.rms_norm_pre_all_gather(xv, rv), b.layer_norm_pre_all_gather(xv),
+        b.layer_norm_post_all_gather(xv, b.layer_norm_pre_all_gather(xv), wv, bv, 1e-5),
+        b.distributed_rms_norm(xv, wv, rv)), [x, res, w, b_])
+    names = ("dit_silu", "dit_plain", "rms_pre", "ln_pre", "ln_post_1dev")
+    for g, w_, name in zip(got, want, names):
+        assert torch.allclose(g, golden[f"map/split_norm/{name}"], rtol=1e-5, atol=2e-6), name
+        assert torch.allclose(g, w_, rtol=1e-5, atol=2e-6), name
+    # one device: the distributed form is the plain rms norm of x + residual
+    xr = x + res
+    assert torch.allclose(got[5], xr * torch.rsqrt(xr.square().mean(-1, keepdim=True) + 1e-5) * w, rtol=1e-5, atol=2e-6)
+    assert got[2].shape == (6, 32) and int((got[2][:, 1:] != 0).sum()) == 0 and got[3].shape == (6, 64)
+    bf = torch.bfloat16
+    torch.manual_seed(9)
+    xb, rb, wb = torch.randn(64, 4096).to(bf), torch.randn(64, 4096).to(bf), (torch.rand(4096) + 0.5).to(bf)
+    for act in (None, "gelu", "relu6", "softplus", "tanh_approx"):
+        got, want = run_body(rt, device, lambda b, xv, rv, wv: b.dit_rms_norm_unary_fused(xv, wv, None, rv, 1e-5, act), [xb, rb, wb])
+        assert_matches(got[0], want[0], f"dit rms norm bf16 {act}", (0.9999, 1e-2, 2.0 ** -7))
+    got, want = run_body(rt, device, lambda b, xv: b.layer_norm_pre_all_gather(xv, dtype="Float32"), [xb])
+    assert torch.allclose(got[0], want[0], rtol=1e-5, atol=1e-3)
+
+
+def test_global_semaphore_ops_are_accepted(rt, device):
+    x = torch.randn(3, 32)
+
+    def body(b, v):
+        b.create_global_semaphore(0)
+        y = b.unary("Neg", v)
+        b.reset_global_semaphore(0)
+        return y
+    got, _ = run_body(rt, device, body, [x])
+    assert torch.equal(got[0], -x)

@@ -316,6 +316,28 @@ def test_decode_head_ops_and_llama_rotary():
     assert torch.allclose(y[..., 0::2], a * c - b * s_, atol=1e-6) and torch.allclose(y[..., 1::2], b * c + a * s_, atol=1e-6)
 
 
+def test_split_normalisations(golden):
+    """Restatements against the reference's goldens (tools/golden/mapping.py:1291-1415, 7800-7921)."""
+    x, res, w, b = (golden[f"map/split_norm/{n}"] for n in ("x", "residual", "weight", "bias"))
+    assert torch.allclose(ops.dit_rms_norm_unary_fused(x, w, b, res, 1e-5, "silu"), golden["map/split_norm/dit_silu"], rtol=1e-6, atol=1e-6)
+    assert torch.allclose(ops.dit_rms_norm_unary_fused(x, w, None, None, 1e-6, None), golden["map/split_norm/dit_plain"], rtol=1e-6, atol=1e-6)
+    assert torch.allclose(ops.rms_norm_pre_all_gather(x, res, torch.float32), golden["map/split_norm/rms_pre"], rtol=1e-6, atol=0)
+    pre = ops.layer_norm_pre_all_gather(x, None, torch.float32)
+    assert torch.allclose(pre, golden["map/split_norm/ln_pre"], rtol=1e-6, atol=1e-6)
+    # one device: the statistics rebuild the shard's own layer norm, which is what the golden computes
+    assert torch.allclose(ops.layer_norm_post_all_gather(x, pre, w, b, 1e-5), golden["map/split_norm/ln_post_1dev"], rtol=1e-5, atol=2e-6)
+    # four devices: pre -> gather -> post equals the layer norm of the whole row
+    xs = list(torch.chunk(x, 4, dim=-1))
+    stats = torch.cat([ops.layer_norm_pre_all_gather(t, None, torch.float32) for t in xs], dim=-1)
+    whole = torch.nn.functional.layer_norm(x, [96], w, b, 1e-5)
+    for i, t in enumerate(xs):
+        got = ops.layer_norm_post_all_gather(t, stats, w[24 * i: 24 * i + 24], b[24 * i: 24 * i + 24], 1e-5)
+        assert torch.allclose(got, whole[:, 24 * i: 24 * i + 24], rtol=1e-5, atol=2e-6)
+    got = ops.distributed_rms_norm(xs, list(torch.chunk(w, 4)), list(torch.chunk(res, 4, dim=-1)), 1e-5)
+    for i, g in enumerate(got):
+        assert torch.allclose(g, golden[f"map/split_norm/dist_rms_1x4/{i}"], rtol=1e-6, atol=1e-6)
+
+
 def test_layer_norm(golden):
     x, w, b = golden["ln/x"], golden["ln/w"], golden["ln/b"]
     assert same(ops.layer_norm(x), golden["ln/plain"])

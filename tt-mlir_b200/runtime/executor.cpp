@@ -113,6 +113,51 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     IN1_OUT(GlobalAvgPool2dOp, in)
     IN1_OUT(PadOp, in)
 #undef IN1_OUT
+  case OpType::DitRMSNormUnaryFusedOp: {
+    const auto *o = op->type_as_DitRMSNormUnaryFusedOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->weight());
+    pushRef(ins, o->bias());
+    pushRef(ins, o->residual_input());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::DistributedRMSNormOp: {
+    const auto *o = op->type_as_DistributedRMSNormOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->weight());
+    pushRef(ins, o->residual());
+    pushRef(ins, o->stats());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::RMSNormPreAllGatherOp: {
+    const auto *o = op->type_as_RMSNormPreAllGatherOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->residual());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::LayerNormPreAllGatherOp: {
+    const auto *o = op->type_as_LayerNormPreAllGatherOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->residual_input());
+    pushRef(ins, o->recip());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::LayerNormPostAllGatherOp: {
+    const auto *o = op->type_as_LayerNormPostAllGatherOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->stats());
+    pushRef(ins, o->weight());
+    pushRef(ins, o->bias());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::CreateGlobalSemaphoreOp:
+  case OpType::ResetGlobalSemaphoreOp:
+  case OpType::AllocateMoeComputeSemaphoreOp: break; // no tensors
   case OpType::AssignOp: {
     const auto *o = op->type_as_AssignOp();
     pushRef(ins, o->input());
@@ -711,6 +756,10 @@ private:
   void runArgMax(const fbt::ReductionArgMaxOp *op);
   void runCumSum(const fbt::CumSumOp *op);
   void runCumProd(const fbt::CumProdOp *op);
+  void runDitRmsNorm(const fbt::DitRMSNormUnaryFusedOp *op);
+  void runDistributedRmsNorm(const fbt::DistributedRMSNormOp *op);
+  void runNormPreAllGather(const fbt::TensorRef *in, const fbt::TensorRef *residual, const fbt::TensorRef *out, int mode);
+  void runLayerNormPostAllGather(const fbt::LayerNormPostAllGatherOp *op);
   void runAssign(const fbt::AssignOp *op);
   void runPowScalar(const fbt::EltwiseBinaryCompositeScalarOp *op);
   void runDumpTensor(const fbt::DumpTensorOp *op);
@@ -1078,6 +1127,24 @@ size_t Executor::runOp(size_t i) {
   case OpType::ReductionArgMaxOp: runArgMax(op->type_as_ReductionArgMaxOp()); break;
   case OpType::CumSumOp: runCumSum(op->type_as_CumSumOp()); break;
   case OpType::CumProdOp: runCumProd(op->type_as_CumProdOp()); break;
+  case OpType::DitRMSNormUnaryFusedOp: runDitRmsNorm(op->type_as_DitRMSNormUnaryFusedOp()); break;
+  case OpType::DistributedRMSNormOp: runDistributedRmsNorm(op->type_as_DistributedRMSNormOp()); break;
+  case OpType::RMSNormPreAllGatherOp: {
+    const auto *o = op->type_as_RMSNormPreAllGatherOp();
+    runNormPreAllGather(o->input(), o->residual(), o->out(), 0);
+    break;
+  }
+  case OpType::LayerNormPreAllGatherOp: {
+    const auto *o = op->type_as_LayerNormPreAllGatherOp();
+    runNormPreAllGather(o->input(), o->residual_input(), o->out(), 1); // `recip` is a lookup table of the Tensix kernel
+    break;
+  }
+  case OpType::LayerNormPostAllGatherOp: runLayerNormPostAllGather(op->type_as_LayerNormPostAllGatherOp()); break;
+  // Global semaphores synchronise Tensix cores of the reference's collectives (operations/global_semaphore/); the
+  // collectives here order themselves on the stream, so the ops have nothing to create or reset.
+  case OpType::CreateGlobalSemaphoreOp:
+  case OpType::ResetGlobalSemaphoreOp:
+  case OpType::AllocateMoeComputeSemaphoreOp: break;
   case OpType::AssignOp: runAssign(op->type_as_AssignOp()); break;
   case OpType::EltwiseBinaryCompositeScalarOp: runPowScalar(op->type_as_EltwiseBinaryCompositeScalarOp()); break;
   case OpType::DumpTensorOp: runDumpTensor(op->type_as_DumpTensorOp()); break;
@@ -2635,6 +2702,106 @@ void Executor::runReductionProd(const fbt::ReductionProdOp *op) {
 }
 
 // group_norm on channels-last [N, 1, H*W, C] (or [N, H, W, C]): operations/normalization/group_norm.cpp.
+static int fusedActivationCode(const fb::String *s) {
+  if (!s || s->size() == 0) return 0;
+  std::string name = s->str();
+  if (name.size() > 7 && name.compare(name.size() - 7, 7, "_approx") == 0) name.resize(name.size() - 7);
+  static const char *names[] = {"", "relu", "relu6", "silu", "mish", "sigmoid", "hardsigmoid", "tanh", "log", "softplus", "gelu", "sqrt"};
+  for (int i = 1; i < 12; ++i) {
+    if (name == names[i]) return i;
+  }
+  TTRT_FATAL("unsupported fused activation '", s->str(), "'");
+}
+
+// act(rms_norm(input + residual) * weight + bias) in one pass, the sum kept in f32 (tools/golden/mapping.py:1291-1326).
+void Executor::runDitRmsNorm(const fbt::DitRMSNormUnaryFusedOp *op) {
+  TensorPtr x = getDevice(op->input());
+  TensorPtr w = op->weight() ? getDevice(op->weight()) : nullptr, b = op->bias() ? getDevice(op->bias()) : nullptr;
+  TensorPtr res = op->residual_input() ? getDevice(op->residual_input()) : nullptr;
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(!x->shape.empty(), "rms norm of a scalar");
+  const size_t cols = x->shape.back(), rows = x->volume() / std::max<size_t>(cols, 1);
+  TTRT_ASSERT((!w || (w->volume() == cols && w->dtype == x->dtype)) && (!b || (b->volume() == cols && b->dtype == x->dtype)) &&
+                  (!res || (res->volume() == x->volume() && res->dtype == x->dtype)) && out->dtype == x->dtype &&
+                  out->volume() == x->volume(),
+              "dit_rms_norm_unary_fused operands must match the input's last dimension and data type");
+  const int act = fusedActivationCode(op->activation());
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_rms_norm_apply(x->shards[i]->ptr, res ? res->shards[i]->ptr : nullptr, w ? w->shards[i]->ptr : nullptr,
+                                b ? b->shards[i]->ptr : nullptr, nullptr, out->shards[i]->ptr, ttbDtype(x->dtype), rows, cols, cols,
+                                op->epsilon(), act, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// RMS norm of rows whose columns are split over a mesh axis: local sums of squares, one all-reduce of 4 bytes per
+// row, local normalisation with the weight slice (tools/golden/mapping.py:1329-1415).  The op's `stats` scratch
+// tensor and its semaphore belong to the Tensix implementation and are not touched.
+void Executor::runDistributedRmsNorm(const fbt::DistributedRMSNormOp *op) {
+  TensorPtr x = getDevice(op->input());
+  TensorPtr w = op->weight() ? getDevice(op->weight()) : nullptr, res = op->residual() ? getDevice(op->residual()) : nullptr;
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(!x->shape.empty(), "rms norm of a scalar");
+  const size_t cols = x->shape.back(), rows = x->volume() / std::max<size_t>(cols, 1);
+  TTRT_ASSERT((!w || (w->volume() == cols && w->dtype == x->dtype)) && (!res || (res->volume() == x->volume() && res->dtype == x->dtype)) &&
+                  out->dtype == x->dtype && out->volume() == x->volume(),
+              "distributed_rms_norm operands must match the input's local width and data type");
+  const uint32_t n = meshAxisSize(op->cluster_axis());
+  TensorPtr local = makeDeviceTensor(dev, {static_cast<uint32_t>(rows)}, DataType::Float32);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_norm_row_stats(x->shards[i]->ptr, res ? res->shards[i]->ptr : nullptr, local->shards[i]->ptr, ttbDtype(x->dtype),
+                                ttbDtype(DataType::Float32), rows, cols, 2, r.stream));
+  });
+  TensorPtr total = local;
+  if (n > 1) {
+    total = makeDeviceTensor(dev, {static_cast<uint32_t>(rows)}, DataType::Float32);
+    allReduce(local, nullptr, total, 0);
+  }
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_rms_norm_apply(x->shards[i]->ptr, res ? res->shards[i]->ptr : nullptr, w ? w->shards[i]->ptr : nullptr, nullptr,
+                                static_cast<const float *>(total->shards[i]->ptr), out->shards[i]->ptr, ttbDtype(x->dtype), rows, cols,
+                                cols * n, op->epsilon(), 0, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// rms_norm_pre_all_gather (mode 0) and layer_norm_pre_all_gather (mode 1): per-row statistics in tile layout.
+void Executor::runNormPreAllGather(const fbt::TensorRef *inRef, const fbt::TensorRef *resRef, const fbt::TensorRef *outRef, int mode) {
+  TensorPtr x = getDevice(inRef);
+  TensorPtr res = resRef ? getDevice(resRef) : nullptr;
+  TensorPtr out = allocOut(outRef);
+  TTRT_ASSERT(!x->shape.empty(), "norm statistics of a scalar");
+  const size_t cols = x->shape.back(), rows = x->volume() / std::max<size_t>(cols, 1);
+  const size_t width = mode == 0 ? 32 : 64;
+  TTRT_ASSERT(!res || (res->volume() == x->volume() && res->dtype == x->dtype), "the residual must have the input's shape and data type");
+  TTRT_ASSERT(out->volume() == rows * width && out->shape.back() == width, "the statistics tensor must be [..., ", width, "]");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_norm_row_stats(x->shards[i]->ptr, res ? res->shards[i]->ptr : nullptr, out->shards[i]->ptr, ttbDtype(x->dtype),
+                                ttbDtype(out->dtype), rows, cols, mode, r.stream));
+  });
+  put(outRef, out);
+}
+
+void Executor::runLayerNormPostAllGather(const fbt::LayerNormPostAllGatherOp *op) {
+  TensorPtr x = getDevice(op->input()), stats = getDevice(op->stats());
+  TensorPtr w = op->weight() ? getDevice(op->weight()) : nullptr, b = op->bias() ? getDevice(op->bias()) : nullptr;
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(!x->shape.empty() && !stats->shape.empty(), "layer norm of a scalar");
+  const size_t cols = x->shape.back(), rows = x->volume() / std::max<size_t>(cols, 1);
+  TTRT_ASSERT(stats->shape.back() % 64 == 0 && stats->volume() == rows * stats->shape.back(),
+              "the gathered statistics must be [..., 64 x devices] with the input's rows");
+  const size_t blocks = stats->shape.back() / 64;
+  TTRT_ASSERT((!w || (w->volume() == cols && w->dtype == x->dtype)) && (!b || (b->volume() == cols && b->dtype == x->dtype)) &&
+                  out->dtype == x->dtype && out->volume() == x->volume(),
+              "layer_norm_post_all_gather operands must match the input's local width and data type");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_layer_norm_post_all_gather(x->shards[i]->ptr, stats->shards[i]->ptr, w ? w->shards[i]->ptr : nullptr,
+                                            b ? b->shards[i]->ptr : nullptr, out->shards[i]->ptr, ttbDtype(x->dtype),
+                                            ttbDtype(stats->dtype), rows, cols, blocks, op->epsilon(), r.stream));
+  });
+  put(op->out(), out);
+}
+
 // A second name for the same memory (annotate, region markers).
 void Executor::runAlias(const fbt::TensorRef *operand, const fbt::TensorRef *result) {
   TensorPtr in = get(operand);

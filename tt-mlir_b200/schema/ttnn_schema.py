@@ -330,6 +330,32 @@ S.table("BatchNormTrainingOp", [
     ("input", "TensorRef"), ("running_mean", "TensorRef"), ("running_var", "TensorRef"), ("epsilon", "f32"),
     ("momentum", "f32"), ("weight", "TensorRef"), ("bias", "TensorRef"), ("memory_config", "MemoryConfig"),
     ("out", "TensorRef"), ("compute_config", "DeviceComputeKernelConfig")])
+S.table("DitRMSNormUnaryFusedOp", [
+    ("input", "TensorRef"), ("weight", "TensorRef"), ("bias", "TensorRef"), ("residual_input", "TensorRef"),
+    ("epsilon", "f32"), ("activation", "string"), ("memory_config", "MemoryConfig"),
+    ("compute_config", "DeviceComputeKernelConfig"), ("out", "TensorRef")])
+S.table("DistributedRMSNormOp", [
+    ("input", "TensorRef"), ("weight", "TensorRef"), ("residual", "TensorRef"), ("cluster_axis", "u32"), ("epsilon", "f32"),
+    ("sub_device_id", "u8", OPT), ("memory_config", "MemoryConfig"), ("num_links", "u32", OPT), ("topology", "Topology", OPT),
+    ("compute_config", "DeviceComputeKernelConfig"), ("stats", "TensorRef"), ("program_config", "opaque"),
+    ("out", "TensorRef"), ("semaphore", "GlobalSemaphoreRef")])
+S.table("RMSNormPreAllGatherOp", [
+    ("input", "TensorRef"), ("dtype", "DataType"), ("residual", "TensorRef"), ("memory_config", "MemoryConfig"),
+    ("compute_config", "DeviceComputeKernelConfig"), ("program_config", "opaque"), ("use_2d_core_grid", "bool"),
+    ("out", "TensorRef")])
+S.table("LayerNormPreAllGatherOp", [
+    ("input", "TensorRef"), ("residual_input", "TensorRef"), ("recip", "TensorRef"), ("dtype", "DataType", "BFloat16"),
+    ("memory_config", "MemoryConfig"), ("compute_config", "DeviceComputeKernelConfig"), ("program_config", "opaque"),
+    ("out", "TensorRef")])
+S.table("LayerNormPostAllGatherOp", [
+    ("input", "TensorRef"), ("stats", "TensorRef"), ("weight", "TensorRef"), ("bias", "TensorRef"), ("epsilon", "f32", 1e-12),
+    ("dtype", "DataType", OPT), ("memory_config", "MemoryConfig"), ("compute_config", "DeviceComputeKernelConfig"),
+    ("program_config", "opaque"), ("out", "TensorRef")])
+S.table("CreateGlobalSemaphoreOp", [("core_range_set", "opaque"), ("initial_value", "u32", OPT), ("out", "GlobalSemaphoreRef")])
+S.table("ResetGlobalSemaphoreOp", [("semaphore", "GlobalSemaphoreRef"), ("value", "u32")])
+S.table("AllocateMoeComputeSemaphoreOp", [
+    ("core_range_set", "opaque"), ("output_height_shard_dim", "u32"), ("hidden_size", "u32"), ("initial_value", "u32", OPT),
+    ("out", "GlobalSemaphoreRef")])
 S.table("UniformScale2D", [("scale", "i32")])
 S.table("NonUniformScale2D", [("scale", "[i32]")])
 S.union("Scale2D", ["UniformScale2D", "NonUniformScale2D"])

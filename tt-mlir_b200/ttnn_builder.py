@@ -760,6 +760,57 @@ class ProgramBuilder:
             "out": out.ref}, ins, [out], loc)
         return out
 
+    def dit_rms_norm_unary_fused(self, x: Value, weight: Optional[Value] = None, bias: Optional[Value] = None,
+                                 residual: Optional[Value] = None, epsilon: float = 1e-5, activation: Optional[str] = None,
+                                 loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        opt = lambda v: v.ref if v is not None else None
+        self._emit("DitRMSNormUnaryFusedOp", {
+            "input": x.ref, "weight": opt(weight), "bias": opt(bias), "residual_input": opt(residual), "epsilon": epsilon,
+            "activation": activation, "memory_config": self._mc(), "out": out.ref},
+            [x] + [t for t in (weight, bias, residual) if t is not None], [out], loc)
+        return out
+
+    def distributed_rms_norm(self, x: Value, weight: Optional[Value] = None, residual: Optional[Value] = None,
+                             cluster_axis: int = 1, epsilon: float = 1e-5, loc=None) -> Value:
+        """x holds this device's slice of the normalised (last) dimension; weight its slice of gamma."""
+        out = self._value(x.shape, x.dtype)
+        opt = lambda v: v.ref if v is not None else None
+        self._emit("DistributedRMSNormOp", {
+            "input": x.ref, "weight": opt(weight), "residual": opt(residual), "cluster_axis": cluster_axis, "epsilon": epsilon,
+            "memory_config": self._mc(), "out": out.ref, "semaphore": {"global_id": 0}},
+            [x] + [t for t in (weight, residual) if t is not None], [out], loc)
+        return out
+
+    def rms_norm_pre_all_gather(self, x: Value, residual: Optional[Value] = None, dtype: Optional[str] = None, loc=None) -> Value:
+        out = self._value(list(x.shape[:-1]) + [32], dtype or x.dtype)
+        self._emit("RMSNormPreAllGatherOp", {"input": x.ref, "dtype": dtype or x.dtype, "residual": residual.ref if residual else None,
+                                             "memory_config": self._mc(), "out": out.ref},
+                   [x] + ([residual] if residual else []), [out], loc)
+        return out
+
+    def layer_norm_pre_all_gather(self, x: Value, residual: Optional[Value] = None, dtype: Optional[str] = None, loc=None) -> Value:
+        out = self._value(list(x.shape[:-1]) + [64], dtype or x.dtype)
+        self._emit("LayerNormPreAllGatherOp", {"input": x.ref, "residual_input": residual.ref if residual else None,
+                                               "dtype": dtype or x.dtype, "memory_config": self._mc(), "out": out.ref},
+                   [x] + ([residual] if residual else []), [out], loc)
+        return out
+
+    def layer_norm_post_all_gather(self, x: Value, stats: Value, weight: Optional[Value] = None, bias: Optional[Value] = None,
+                                   epsilon: float = 1e-12, loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        opt = lambda v: v.ref if v is not None else None
+        self._emit("LayerNormPostAllGatherOp", {
+            "input": x.ref, "stats": stats.ref, "weight": opt(weight), "bias": opt(bias), "epsilon": epsilon,
+            "memory_config": self._mc(), "out": out.ref}, [x, stats] + [t for t in (weight, bias) if t is not None], [out], loc)
+        return out
+
+    def create_global_semaphore(self, initial_value: int = 0, loc=None) -> None:
+        self._emit("CreateGlobalSemaphoreOp", {"initial_value": initial_value, "out": {"global_id": 0}}, [], [], loc)
+
+    def reset_global_semaphore(self, value: int = 0, loc=None) -> None:
+        self._emit("ResetGlobalSemaphoreOp", {"semaphore": {"global_id": 0}, "value": value}, [], [], loc)
+
     def all_reduce_async(self, x: Value, reduce_type: int = 0, cluster_axis: int = 1, loc=None) -> Value:
         out = self._value(x.shape, x.dtype)
         self._emit("AllReduceAsyncOp", {"in": x.ref, "out": out.ref, "reduce_type": reduce_type, "cluster_axis": cluster_axis,

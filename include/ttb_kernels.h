@@ -612,6 +612,31 @@ TTB_API int ttb_reduce_scatter(void *comm, const void *in, void *out, size_t rec
                                int reduce_type, void *stream);
 TTB_API int ttb_broadcast(void *comm, const void *in, void *out, size_t count, int dtype, int root,
                           void *stream);
+/* ---- mixture of experts (operations/ccl/all_to_all_dispatch.cpp, all_to_all_combine.cpp, moe_expert_token_remap.cpp;
+ * operations/matmul/matmul.cpp ::ttnn::sparse_matmul).  `mapping` is the [experts, devices] one-hot ownership table as
+ * Int32; a device numbers its own experts in ascending global order.
+ * ttb_moe_local_index: local_idx[e] = this device's number for expert e, or -1.
+ * ttb_moe_dispatch_mask: clears the rows of the gathered [rows, hidden] token buffer none of whose k experts
+ *   (indices [rows, k], Int32) lives on this device -- the local half of ::ttnn::all_to_all_dispatch.
+ * ttb_moe_combine_partial: partial[p, slot, b, s, :] = expert_out[local expert, token(p, b, s), :] when the expert in
+ *   metadata[token, slot] lives here, else 0; summing the partials of all devices (one owner per expert) gives
+ *   destination p's ::ttnn::all_to_all_combine result [k, batch, seq, hidden].  Tokens of destination p are its
+ *   batch rows (seq_sharded = 0) or its sequence positions (seq_sharded = 1) of the global token grid.
+ * ttb_moe_expert_token_remap: mapping[t, le] = topk[t, e] for the selected experts that live here (0 elsewhere),
+ *   reduced[block, le] = 1 when a token of the block of `reduction` tokens selected local expert le.
+ * ttb_sparse_matmul: c[i] = a[a_per_entry ? i : i / experts] (m x k) * b[i % experts] (k x n) for the `entries`
+ *   whose sparsity[i] is non-zero; the others are cleared.  bf16 / f16, f32 accumulation, one rounding. */
+TTB_API int ttb_moe_local_index(const int32_t *mapping, int32_t *local_idx, int experts, int devices, int device, void *stream);
+TTB_API int ttb_moe_dispatch_mask(void *tokens, const int32_t *indices, const int32_t *local_idx, int dtype, size_t rows,
+                                  size_t hidden, int k, int experts, void *stream);
+TTB_API int ttb_moe_combine_partial(const void *expert_out, const int32_t *metadata, const int32_t *local_idx, void *partial,
+                                    int dtype, int devices, int k, int batch, int seq, size_t hidden, int experts,
+                                    int local_experts, int seq_sharded, void *stream);
+TTB_API int ttb_moe_expert_token_remap(const void *topk, const int32_t *metadata, const int32_t *local_idx, void *mapping,
+                                       void *reduced, int dtype, int reduced_dtype, size_t tokens, int k, int experts,
+                                       int local_experts, int reduction, void *stream);
+TTB_API int ttb_sparse_matmul(const void *a, const void *b, const void *sparsity, void *c, int dtype, int sparsity_dtype,
+                              int64_t entries, int64_t experts, int a_per_entry, int64_t m, int64_t n, int64_t k, void *stream);
 /* ::ttnn::point_to_point (operations/ccl/point_to_point.cpp): the sender's half and the receiver's half of one copy. */
 TTB_API int ttb_send(void *comm, const void *in, size_t count, int dtype, int peer, void *stream);
 TTB_API int ttb_recv(void *comm, void *out, size_t count, int dtype, int peer, void *stream);

@@ -383,6 +383,33 @@ class OracleBuilder:
     def create_global_semaphore(self, initial_value=0, loc=None): return None
     def reset_global_semaphore(self, value=0, loc=None): return None
 
+    def all_to_all_dispatch(self, x, expert_indices, expert_mapping, cluster_axis=1, loc=None):
+        per = lambda v: v.t if isinstance(v.t, list) else [v.t]
+        mp = expert_mapping.first
+        disp, meta = ops.all_to_all_dispatch(per(x), per(expert_indices), mp)
+        return (OValue(disp), OValue(meta)) if isinstance(x.t, list) else (OValue(disp[0]), OValue(meta[0]))
+
+    def all_to_all_combine(self, x, expert_metadata, expert_mapping, num_experts_per_tok, cluster_axis=1, output_shard_dim=1, loc=None):
+        per = lambda v: v.t if isinstance(v.t, list) else [v.t]
+        md = expert_metadata.t if isinstance(expert_metadata.t, list) else expert_metadata.t
+        outs = ops.all_to_all_combine(per(x), md, expert_mapping.first, num_experts_per_tok, seq_sharded=output_shard_dim == 2 and len(per(x)) > 1)
+        return OValue(outs) if isinstance(x.t, list) else OValue(outs[0])
+
+    def moe_expert_token_remap(self, topk, expert_mapping, expert_metadata, reduction_size=32, reduced_dtype=None, loc=None):
+        def fn(i, t, md):
+            m, r = ops.moe_expert_token_remap(t, expert_mapping.first, md, i, reduction_size)
+            return m, r.to(TORCH_DTYPE[reduced_dtype] if reduced_dtype else t.dtype)
+        if isinstance(topk.t, list) or isinstance(expert_metadata.t, list):
+            n = len(topk.t) if isinstance(topk.t, list) else len(expert_metadata.t)
+            pick = lambda v, i: v.t[i] if isinstance(v.t, list) else v.t
+            res = [fn(i, pick(topk, i), pick(expert_metadata, i)) for i in range(n)]
+            return OValue([r[0] for r in res]), OValue([r[1] for r in res])
+        m, r = fn(0, topk.t, expert_metadata.t)
+        return OValue(m), OValue(r)
+
+    def sparse_matmul(self, a, b, sparsity, is_input_a_sparse=False, is_input_b_sparse=True, nnz=None, loc=None):
+        return _map(lambda x, w, sp: ops.sparse_matmul(x, w, sp, is_input_a_sparse), a, b, sparsity)
+
     def all_reduce_async(self, x, reduce_type=0, cluster_axis=1, loc=None): return OValue(ops.all_reduce(x.t, reduce_type))
 
     def point_to_point(self, x, sender_coord, receiver_coord, output=None, loc=None):

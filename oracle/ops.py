@@ -748,3 +748,86 @@ def layer_norm_post_all_gather(x, stats, weight, bias, eps: float):
     if bias is not None:
         y = y + bias.float().reshape(-1)
     return y.to(x.dtype)
+
+
+# ---- mixture of experts (mapping.py:1596-1760, 2030-2186; ::ttnn::all_to_all_dispatch / all_to_all_combine /
+# moe_expert_token_remap / sparse_matmul).  expert_mapping is the [1, 1, E, D] one-hot ownership table; a device numbers
+# its experts in ascending global order.
+def _local_experts(mapping, device):
+    m = mapping.reshape(mapping.shape[-2], mapping.shape[-1])
+    return [e for e in range(m.shape[0]) if int(m[e, device]) != 0]
+
+
+def all_to_all_dispatch(xs, indices, mapping):
+    """Per device: the global token grid (devices concatenated along the batch) with the rows that selected none of
+    the device's experts cleared, and everybody's expert indices.  Routed rows are what
+    ttir_all_to_all_dispatch_metadata_golden (mapping.py:1656-1760) places."""
+    to_grid = lambda t: t.permute(1, 0, 2, 3) if t.shape[1] == 1 else t.permute(2, 0, 1, 3)
+    full = torch.cat([to_grid(x) for x in xs], dim=1)
+    meta = torch.cat([to_grid(i) for i in indices], dim=1)
+    out = []
+    for d in range(len(xs)):
+        mine = torch.tensor(_local_experts(mapping, d), dtype=torch.int64)
+        routed = torch.isin(meta.to(torch.int64), mine).any(dim=-1, keepdim=True)
+        out.append(torch.where(routed, full, torch.zeros_like(full)))
+    return out, [meta.clone() for _ in xs]
+
+
+def all_to_all_combine(xs, metadata, mapping, k, seq_sharded=False):
+    """Per destination device p: out[slot, b, s, :] = the row of the expert named by metadata[token, slot], taken from
+    the device that owns it (mapping.py:2030-2150; the token is the destination's own one of the global grid)."""
+    n = len(xs)
+    owners = {}
+    for d in range(n):
+        for le, e in enumerate(_local_experts(mapping, d)):
+            owners[e] = (d, le)
+    _, bg, sg, h = xs[0].shape
+    b, s_ = (bg, sg // n) if seq_sharded else (bg // n, sg)
+    outs = []
+    for p in range(n):
+        md = metadata[p] if isinstance(metadata, list) else metadata
+        out = torch.zeros(k, b, s_, h, dtype=xs[0].dtype)
+        for bi in range(b):
+            for si in range(s_):
+                gb, gs = (bi, p * s_ + si) if seq_sharded else (p * b + bi, si)
+                for slot in range(k):
+                    e = int(md[0, gb, gs, slot])
+                    if e in owners:
+                        d, le = owners[e]
+                        out[slot, bi, si] = xs[d][le, gb, gs]
+        outs.append(out)
+    return outs
+
+
+def moe_expert_token_remap(topk, mapping, metadata, device, reduction_size):
+    """mapping[t, le] = topk[t, e] for the experts in metadata[t] that `device` owns; reduced[block, le] = 1 when a
+    token of the block of `reduction_size` tokens selected local expert le (::ttnn::moe_expert_token_remap; the
+    reference golden, mapping.py:2153-2186, only fixes the shapes)."""
+    mine = _local_experts(mapping, device)
+    e_total = topk.shape[-1]
+    tk = topk.reshape(-1, e_total)
+    md = metadata.reshape(tk.shape[0], -1)
+    out = torch.zeros(tk.shape[0], len(mine), dtype=topk.dtype)
+    for t in range(tk.shape[0]):
+        for e in md[t].tolist():
+            if e in mine:
+                out[t, mine.index(e)] = tk[t, e]
+    blocks = (tk.shape[0] + reduction_size - 1) // reduction_size
+    red = torch.zeros(blocks, len(mine))
+    for blk in range(blocks):
+        rows = md[blk * reduction_size: (blk + 1) * reduction_size]
+        for le, e in enumerate(mine):
+            red[blk, le] = float((rows == e).any())
+    return out.reshape(*topk.shape[:-1], len(mine)), red.reshape(1, 1, blocks, len(mine))
+
+
+def sparse_matmul(a, b, sparsity, a_sparse: bool):
+    """tools/golden/mapping.py:1596-1624 (dense products) with the skipped blocks cleared; f32 accumulation, one rounding."""
+    af, bf = a.float(), b.float()
+    if a_sparse:
+        out = torch.matmul(af, bf)                                           # [A, E, M, N]
+        mask = sparsity.reshape(a.shape[0], b.shape[1], 1, 1)
+    else:
+        out = torch.einsum("abmk,xekn->abxemn", af, bf)                      # [A, B, 1, E, M, N]
+        mask = sparsity.reshape(a.shape[0], a.shape[1], 1, b.shape[1], 1, 1)
+    return torch.where(mask.float() != 0, out, torch.zeros_like(out)).to(a.dtype)

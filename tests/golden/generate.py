@@ -481,6 +481,39 @@ def main():
     store_shards("map/split_norm/dist_rms_1x4", ref.ttir_distributed_rms_norm_golden(xsh, wsh, rsh, S.IntegerAttr(1), S.FloatAttr(1e-5),
                                                                                      S.F32Type()))
 
+    # --- mixture of experts (mapping.py:1596-1760, 2030-2150)
+    sa, sb = rnd(2, 3, 32, 48).to(torch.bfloat16), (rnd(1, 4, 48, 40) * 0.2).to(torch.bfloat16)
+    store(out, "map/moe/spmm_a", sa)
+    store(out, "map/moe/spmm_b", sb)
+    store(out, "map/moe/spmm_b_sparse", one(ref.ttir_sparse_matmul_golden(gmt(sa), gmt(sb), None, S.BoolAttr(False), S.BoolAttr(True), None,
+                                                                          S.BF16Type())))
+    sa2 = rnd(3, 4, 32, 48).to(torch.bfloat16)
+    store(out, "map/moe/spmm_a2", sa2)
+    store(out, "map/moe/spmm_a_sparse", one(ref.ttir_sparse_matmul_golden(gmt(sa2), gmt(sb), None, S.BoolAttr(True), S.BoolAttr(False), None,
+                                                                          S.BF16Type())))
+    # dispatch on a 1x4 mesh: 6 tokens per device, hidden 16, 2 of 8 experts per token, experts 2d and 2d+1 on device d
+    D, Mt, Hh, Kk, Ee = 4, 6, 16, 2, 8
+    tok = rnd(D * Mt, Hh)
+    sel = torch.stack([torch.randperm(Ee, generator=g)[:Kk] for _ in range(D * Mt)]).to(torch.int32)
+    scr = torch.rand(D * Mt, Kk, generator=g)
+    store(out, "map/moe/tokens", tok)
+    store(out, "map/moe/selected", sel)
+    shard4 = lambda t: ref.GoldenMapTensor({d: t[d * Mt:(d + 1) * Mt].reshape(1, 1, Mt, -1).clone() for d in range(D)}, (1, D))
+    owner = (torch.arange(Ee) // 2).to(torch.int32).reshape(1, 1, 1, Ee).repeat(1, 1, D, 1)        # entry [d, e] = owning device
+    disp, idx_all, _ = ref.ttir_all_to_all_dispatch_metadata_golden(
+        shard4(tok), shard4(sel), shard4(scr), ref.GoldenMapTensor({d: owner.clone() for d in range(D)}, (1, D)),
+        S.IntegerAttr(D), S.IntegerAttr(1), S.F32Type(), S.IntegerType(32), S.F32Type())
+    store_shards("map/moe/dispatched_1x4", disp)
+    store(out, "map/moe/indices_gathered", idx_all.shard_at(0))
+    # combine on one device: 4 experts, all local; 3 x 5 tokens, 2 slots
+    cin = rnd(4, 3, 5, 16)
+    cmeta = torch.stack([torch.randperm(4, generator=g)[:2] for _ in range(15)]).to(torch.int32).reshape(1, 3, 5, 2)
+    store(out, "map/moe/combine_in", cin)
+    store(out, "map/moe/combine_meta", cmeta)
+    store(out, "map/moe/combine_out", one(ref.ttir_all_to_all_combine_golden(
+        gmt(cin), gmt(cmeta), gmt(torch.ones(1, 1, 4, 1, dtype=torch.int32)), S.IntegerAttr(1), S.IntegerAttr(1), S.IntegerAttr(2),
+        S.F32Type())))
+
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ttir_cpu_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes")

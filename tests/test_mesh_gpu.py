@@ -74,6 +74,39 @@ def test_all_reduce_all_gather_reduce_scatter(rt, mesh2):
     assert torch.equal(got[1], x) and torch.equal(got[4], x)
 
 
+def test_moe_dispatch_expert_layer_combine(rt, mesh2):
+    """Tokens sharded over the mesh go to the devices of their experts and come back: dispatch, remap, one expert
+    matrix per local expert through sparse_matmul, combine; against the oracle and against the experts applied densely."""
+    torch.manual_seed(31)
+    bf = torch.bfloat16
+    B, S, H, E, K = 32, 2, 64, 4, 2                       # per device: 16 x 2 tokens; experts 0, 1 on device 0 and 2, 3 on device 1
+    x = torch.randn(B, 1, S, H).to(bf)
+    sel = torch.stack([torch.randperm(E)[:K] for _ in range(B * S)]).to(torch.int32).reshape(B, 1, S, K)
+    mapping = torch.zeros(1, 1, E, 2, dtype=torch.int32)
+    for e in range(E):
+        mapping[0, 0, e, e // 2] = 1
+    w = (torch.randn(E, H, H) * 0.2).to(bf)                 # expert e: x @ w[e]
+
+    def body(b, xv, sv, mv, wv):
+        xs, ss = b.distribute(xv, 0), b.distribute(sv, 0)
+        mp = b.distribute(mv, None)
+        ws = b.reshape(b.distribute(wv, 0), [1, E // 2, H, H])          # each device holds its two experts' weights
+        disp, meta = b.all_to_all_dispatch(xs, ss, mp)                  # [1, 32, 2, 64], [1, 32, 2, 2]
+        blocks = b.reshape(disp, [2, 1, 32, H])                         # two blocks of 32 tokens
+        act = b.full([2, 1, 1, E // 2], 1.0, "BFloat16")                # every block is active for every local expert
+        y = b.sparse_matmul(blocks, ws, act)                            # [2, 1, 1, 2, 32, 64]
+        y = b.reshape(b.permute(b.reshape(y, [2, 2, 32, H]), [1, 0, 2, 3]), [2, B, S, H])     # [E_local, tokens..., H]
+        out = b.all_to_all_combine(y, meta, mp, K)                      # [K, 16, 2, 64] per device
+        return b.aggregate(out, 1), b.aggregate(disp, 0), b.aggregate(meta, 0)
+    got, want = run_mesh(rt, mesh2, body, [x, sel, mapping, w])
+    for i, (g, w_) in enumerate(zip(got, want)):
+        assert_matches(g.float(), w_.float(), f"moe output {i}", (0.9999, 2e-2, 2.0 ** -6))
+    dense = torch.einsum("bsh,ehf->ebsf", x.reshape(B, S, H).float(), w.float())       # every expert on every token
+    ref = torch.stack([torch.gather(dense, 0, sel.reshape(1, B, S, K)[..., k:k + 1].expand(1, B, S, H).long())[0] for k in range(K)])
+    assert_matches(got[0].float(), ref, "moe layer against the experts applied densely", (0.999, 3e-2, 2.0 ** -5))
+    assert torch.equal(got[2][0], sel.reshape(1, B, S, K)[0]) and torch.equal(got[2][0], got[2][1])
+
+
 def test_norms_with_the_hidden_dimension_split_over_the_mesh(rt, mesh2):
     torch.manual_seed(21)
     x, res = torch.randn(48, 512), torch.randn(48, 512) * 0.5

@@ -249,3 +249,50 @@ def test_global_semaphore_ops_are_accepted(rt, device):
         return y
     got, _ = run_body(rt, device, body, [x])
     assert torch.equal(got[0], -x)
+
+
+def test_sparse_matmul_matches_the_reference_goldens(rt, device, golden):
+    a, b_ = golden["map/moe/spmm_a"], golden["map/moe/spmm_b"]
+    bf = torch.bfloat16
+    got, want = run_body(rt, device, lambda b, av, bv, sv: b.sparse_matmul(av, bv, sv), [a, b_, torch.ones(2, 3, 1, 4).to(bf)])
+    assert got[0].shape == golden["map/moe/spmm_b_sparse"].shape
+    assert_matches(got[0], golden["map/moe/spmm_b_sparse"], "sparse_matmul, b sparse, all blocks", (0.9999, 1e-2, 2.0 ** -7))
+    sp = (torch.arange(24).reshape(2, 3, 1, 4) % 3 != 0).to(bf)
+    got, want = run_body(rt, device, lambda b, av, bv, sv: b.sparse_matmul(av, bv, sv, nnz=16), [a, b_, sp])
+    assert_matches(got[0], want[0], "sparse_matmul with skipped blocks", (0.9999, 1e-2, 2.0 ** -7))
+    keep = sp.reshape(2, 3, 1, 4, 1, 1).bool().expand_as(got[0])
+    assert int(got[0][~keep].float().abs().sum()) == 0
+    a2 = golden["map/moe/spmm_a2"]
+    got, want = run_body(rt, device, lambda b, av, bv, sv: b.sparse_matmul(av, bv, sv, is_input_a_sparse=True, is_input_b_sparse=False),
+                         [a2, b_, torch.ones(1, 1, 3, 4).to(bf)])
+    assert_matches(got[0], golden["map/moe/spmm_a_sparse"], "sparse_matmul, a sparse", (0.9999, 1e-2, 2.0 ** -7))
+    # an expert layer's shapes: 2 blocks of 32 tokens, 8 experts, 512 -> 1024, ragged n and k
+    torch.manual_seed(12)
+    xa, wb = torch.randn(2, 1, 32, 520).to(bf), (torch.randn(1, 8, 520, 1000) * 0.05).to(bf)
+    mask = (torch.rand(2, 1, 1, 8) < 0.4).to(bf)
+    got, want = run_body(rt, device, lambda b, av, bv, sv: b.sparse_matmul(av, bv, sv), [xa, wb, mask])
+    assert_matches(got[0], want[0], "sparse_matmul at expert shapes", (0.9999, 2e-2, 2.0 ** -6))
+    xh, wh = xa.to(torch.float16), wb.to(torch.float16)
+    got, want = run_body(rt, device, lambda b, av, bv, sv: b.sparse_matmul(av, bv, sv), [xh, wh, mask.to(torch.float16)])
+    assert_matches(got[0], want[0], "sparse_matmul f16", (0.9999, 1e-2, 2.0 ** -9))
+
+
+def test_moe_routing_ops_on_one_device(rt, device, golden):
+    cin, cmeta = golden["map/moe/combine_in"], golden["map/moe/combine_meta"]
+    ones = torch.ones(1, 1, 4, 1, dtype=torch.int32)
+    got, want = run_body(rt, device, lambda b, xv, mv, pv: b.all_to_all_combine(xv, mv, pv, 2), [cin, cmeta, ones])
+    assert torch.equal(got[0], golden["map/moe/combine_out"]) and torch.equal(want[0], got[0])
+    torch.manual_seed(13)
+    x = torch.randn(6, 1, 5, 64).to(torch.bfloat16)
+    sel = torch.stack([torch.randperm(4)[:2] for _ in range(30)]).to(torch.int32).reshape(6, 1, 5, 2)
+    half = torch.tensor([[1, 0], [0, 1], [1, 0], [0, 1]], dtype=torch.int32).reshape(1, 1, 4, 2)   # this device owns experts 0 and 2
+    got, want = run_body(rt, device, lambda b, xv, iv, pv: b.all_to_all_dispatch(xv, iv, pv), [x, sel, half])
+    assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1]) and got[0].shape == (1, 6, 5, 64)
+    routed = ((sel == 0) | (sel == 2)).any(-1).reshape(1, 6, 5, 1)
+    assert torch.equal(got[0], torch.where(routed, x.reshape(1, 6, 5, 64), torch.zeros(1, 6, 5, 64).to(torch.bfloat16)))
+    topk = torch.rand(1, 6, 5, 4).to(torch.bfloat16)
+    for rdt in (None, "UInt16"):
+        got, want = run_body(rt, device, lambda b, tv, pv, mv: b.moe_expert_token_remap(tv, pv, mv, 8, reduced_dtype=rdt),
+                             [topk, half, sel.reshape(1, 6, 5, 2)])
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1].float(), want[1].float())
+        assert got[0].shape == (1, 6, 5, 2) and got[1].shape == (1, 1, 4, 2)

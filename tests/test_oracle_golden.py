@@ -338,6 +338,40 @@ def test_split_normalisations(golden):
         assert torch.allclose(g, golden[f"map/split_norm/dist_rms_1x4/{i}"], rtol=1e-6, atol=1e-6)
 
 
+def test_mixture_of_experts_ops(golden):
+    """Restatements against the reference's goldens (tools/golden/mapping.py:1596-1760, 2030-2150)."""
+    a, b = golden["map/moe/spmm_a"], golden["map/moe/spmm_b"]
+    ones = torch.ones(2, 3, 1, 4)
+    assert torch.equal(ops.sparse_matmul(a, b, ones, False), golden["map/moe/spmm_b_sparse"])
+    sp = (torch.arange(24).reshape(2, 3, 1, 4) % 3 != 0).float()
+    got = ops.sparse_matmul(a, b, sp, False)
+    keep = sp.reshape(2, 3, 1, 4, 1, 1).bool().expand_as(got)
+    assert torch.equal(got[keep], golden["map/moe/spmm_b_sparse"][keep]) and int(got[~keep].abs().sum()) == 0
+    assert torch.equal(ops.sparse_matmul(golden["map/moe/spmm_a2"], b, torch.ones(1, 1, 3, 4), True), golden["map/moe/spmm_a_sparse"])
+    # dispatch: 4 devices, experts 2d and 2d + 1 on device d
+    tok, sel = golden["map/moe/tokens"], golden["map/moe/selected"]
+    mapping = torch.zeros(1, 1, 8, 4, dtype=torch.int32)
+    for e in range(8):
+        mapping[0, 0, e, e // 2] = 1
+    xs = [tok[6 * d: 6 * d + 6].reshape(6, 1, 1, 16) for d in range(4)]
+    idx = [sel[6 * d: 6 * d + 6].reshape(6, 1, 1, 2) for d in range(4)]
+    disp, meta = ops.all_to_all_dispatch(xs, idx, mapping)
+    for d in range(4):
+        assert torch.equal(disp[d].reshape(1, 24, 16), golden[f"map/moe/dispatched_1x4/{d}"])
+        assert torch.equal(meta[d].reshape(1, 24, 2), golden["map/moe/indices_gathered"])
+    cin, cmeta = golden["map/moe/combine_in"], golden["map/moe/combine_meta"]
+    got = ops.all_to_all_combine([cin], cmeta, torch.ones(1, 1, 4, 1, dtype=torch.int32), 2)
+    assert torch.equal(got[0], golden["map/moe/combine_out"])
+    # dispatch -> identity experts -> combine hands every token back once per selected expert
+    expert_out = [torch.stack([disp[d].reshape(24, 1, 16)] * 2) for d in range(4)]     # [E_local = 2, 24, 1, 16]
+    back = ops.all_to_all_combine(expert_out, meta[0].reshape(1, 24, 1, 2), mapping, 2)
+    for d in range(4):
+        assert torch.equal(back[d], torch.stack([tok[6 * d: 6 * d + 6].reshape(6, 1, 16)] * 2))
+    m, red = ops.moe_expert_token_remap(torch.rand(1, 24, 1, 8), mapping, meta[0].reshape(1, 24, 1, 2), 1, 8)
+    assert m.shape == (1, 24, 1, 2) and red.shape == (1, 1, 3, 2)
+    assert ((m != 0).reshape(24, 2) == torch.stack([(sel == 2).any(1), (sel == 3).any(1)], dim=1)).all()
+
+
 def test_layer_norm(golden):
     x, w, b = golden["ln/x"], golden["ln/w"], golden["ln/b"]
     assert same(ops.layer_norm(x), golden["ln/plain"])

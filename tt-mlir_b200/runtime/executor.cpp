@@ -113,6 +113,40 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     IN1_OUT(GlobalAvgPool2dOp, in)
     IN1_OUT(PadOp, in)
 #undef IN1_OUT
+  case OpType::AllToAllDispatchOp: {
+    const auto *o = op->type_as_AllToAllDispatchOp();
+    pushRef(ins, o->input_tensor());
+    pushRef(ins, o->expert_indices());
+    pushRef(ins, o->expert_mapping());
+    pushRef(outs, o->dispatched());
+    pushRef(outs, o->metadata());
+    break;
+  }
+  case OpType::AllToAllCombineOp: {
+    const auto *o = op->type_as_AllToAllCombineOp();
+    pushRef(ins, o->input_tensor());
+    pushRef(ins, o->expert_metadata());
+    pushRef(ins, o->expert_mapping());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::MoeExpertTokenRemapOp: {
+    const auto *o = op->type_as_MoeExpertTokenRemapOp();
+    pushRef(ins, o->topk_tensor());
+    pushRef(ins, o->expert_mapping());
+    pushRef(ins, o->expert_metadata());
+    pushRef(outs, o->mapping());
+    pushRef(outs, o->reduced());
+    break;
+  }
+  case OpType::SparseMatmulOp: {
+    const auto *o = op->type_as_SparseMatmulOp();
+    pushRef(ins, o->a());
+    pushRef(ins, o->b());
+    pushRef(ins, o->sparsity());
+    pushRef(outs, o->out());
+    break;
+  }
   case OpType::DitRMSNormUnaryFusedOp: {
     const auto *o = op->type_as_DitRMSNormUnaryFusedOp();
     pushRef(ins, o->input());
@@ -756,6 +790,12 @@ private:
   void runArgMax(const fbt::ReductionArgMaxOp *op);
   void runCumSum(const fbt::CumSumOp *op);
   void runCumProd(const fbt::CumProdOp *op);
+  // expert ownership of this process's mesh coordinates: localIdx tensors (Int32 [experts]) from a [1, 1, E, D] mapping
+  TensorPtr moeLocalIndex(const TensorPtr &mapping, uint32_t &experts, uint32_t &devices);
+  void runAllToAllDispatch(const fbt::AllToAllDispatchOp *op);
+  void runAllToAllCombine(const fbt::AllToAllCombineOp *op);
+  void runMoeExpertTokenRemap(const fbt::MoeExpertTokenRemapOp *op);
+  void runSparseMatmul(const fbt::SparseMatmulOp *op);
   void runDitRmsNorm(const fbt::DitRMSNormUnaryFusedOp *op);
   void runDistributedRmsNorm(const fbt::DistributedRMSNormOp *op);
   void runNormPreAllGather(const fbt::TensorRef *in, const fbt::TensorRef *residual, const fbt::TensorRef *out, int mode);
@@ -1127,6 +1167,10 @@ size_t Executor::runOp(size_t i) {
   case OpType::ReductionArgMaxOp: runArgMax(op->type_as_ReductionArgMaxOp()); break;
   case OpType::CumSumOp: runCumSum(op->type_as_CumSumOp()); break;
   case OpType::CumProdOp: runCumProd(op->type_as_CumProdOp()); break;
+  case OpType::AllToAllDispatchOp: runAllToAllDispatch(op->type_as_AllToAllDispatchOp()); break;
+  case OpType::AllToAllCombineOp: runAllToAllCombine(op->type_as_AllToAllCombineOp()); break;
+  case OpType::MoeExpertTokenRemapOp: runMoeExpertTokenRemap(op->type_as_MoeExpertTokenRemapOp()); break;
+  case OpType::SparseMatmulOp: runSparseMatmul(op->type_as_SparseMatmulOp()); break;
   case OpType::DitRMSNormUnaryFusedOp: runDitRmsNorm(op->type_as_DitRMSNormUnaryFusedOp()); break;
   case OpType::DistributedRMSNormOp: runDistributedRmsNorm(op->type_as_DistributedRMSNormOp()); break;
   case OpType::RMSNormPreAllGatherOp: {
@@ -2702,6 +2746,170 @@ void Executor::runReductionProd(const fbt::ReductionProdOp *op) {
 }
 
 // group_norm on channels-last [N, 1, H*W, C] (or [N, H, W, C]): operations/normalization/group_norm.cpp.
+// ---- mixture of experts ---------------------------------------------------------------------------
+TensorPtr Executor::moeLocalIndex(const TensorPtr &mappingIn, uint32_t &experts, uint32_t &devices) {
+  TTRT_ASSERT(mappingIn->shape.size() >= 2, "expert_mapping must be [1, 1, experts, devices]");
+  experts = mappingIn->shape[mappingIn->shape.size() - 2];
+  devices = mappingIn->shape.back();
+  TTRT_ASSERT(mappingIn->volume() == static_cast<size_t>(experts) * devices, "expert_mapping has leading dimensions other than 1");
+  TTRT_ASSERT(devices == dev->worldSize || dev->worldSize == 1, "expert_mapping covers ", devices, " devices, the mesh has ", dev->worldSize);
+  TensorPtr mapping = castOnDevice(mappingIn, DataType::Int32);
+  TensorPtr local = makeDeviceTensor(dev, {experts}, DataType::Int32);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_moe_local_index(static_cast<const int32_t *>(mapping->shards[i]->ptr), static_cast<int32_t *>(local->shards[i]->ptr),
+                                 static_cast<int>(experts), static_cast<int>(devices), static_cast<int>(r.meshRank % devices), r.stream));
+  });
+  return local;
+}
+
+// all_to_all_dispatch: every device ends up with the global token grid [1, D*B, S, H] (or [1, B, D*S, H]) holding the
+// tokens that selected one of its experts (other rows cleared) and with everybody's expert indices.  The exchange is
+// an all-gather of both tensors; the mask is local.
+void Executor::runAllToAllDispatch(const fbt::AllToAllDispatchOp *op) {
+  TensorPtr x = getDevice(op->input_tensor()), idxIn = getDevice(op->expert_indices());
+  uint32_t experts = 0, devices = 0;
+  TensorPtr local = moeLocalIndex(getDevice(op->expert_mapping()), experts, devices);
+  TensorPtr out = allocOut(op->dispatched()), meta = allocOut(op->metadata());
+  const uint32_t n = meshAxisSize(op->cluster_axis());
+  const size_t hidden = x->shape.back(), k = idxIn->shape.back();
+  const size_t rows = x->volume() / std::max<size_t>(hidden, 1);
+  TTRT_ASSERT(idxIn->volume() == rows * k, "expert_indices must have one row of ", k, " experts per token");
+  TTRT_ASSERT(out->volume() == x->volume() * n && out->dtype == x->dtype && meta->volume() == idxIn->volume() * n && meta->dtype == idxIn->dtype,
+              "all_to_all_dispatch results must hold the tokens and indices of all ", n, " devices");
+  // Device-major order is the result itself when the devices' tokens are concatenated along the batch; along the
+  // sequence each batch row interleaves the devices.
+  TTRT_ASSERT(out->shape.size() == 4 && x->shape.size() == 4, "all_to_all_dispatch expects 4-D tokens");
+  const size_t batch = x->shape[0], seq = rows / std::max<size_t>(batch, 1);
+  const bool seqConcat = n > 1 && out->shape[1] == batch && out->shape[2] == seq * n && batch > 1;
+  TensorPtr stagedX = seqConcat ? makeDeviceTensor(dev, {n, static_cast<uint32_t>(x->volume())}, x->dtype) : out;
+  TensorPtr stagedI = seqConcat ? makeDeviceTensor(dev, {n, static_cast<uint32_t>(idxIn->volume())}, idxIn->dtype) : meta;
+  if (n > 1) {
+    refuseWhileRecording("a collective");
+    TTB_CALL(ttb_group_start());
+    eachRank([&](size_t i, const RankCtx &r) {
+      TTB_CALL(ttb_all_gather(r.comm, x->shards[i]->ptr, stagedX->shards[i]->ptr, x->volume(), ttbDtype(x->dtype), r.stream));
+      TTB_CALL(ttb_all_gather(r.comm, idxIn->shards[i]->ptr, stagedI->shards[i]->ptr, idxIn->volume(), ttbDtype(idxIn->dtype), r.stream));
+    });
+    TTB_CALL(ttb_group_end());
+  } else {
+    eachRank([&](size_t i, const RankCtx &r) {
+      TTB_CALL(ttb_memcpy_d2d(out->shards[i]->ptr, x->shards[i]->ptr, x->bytes(), r.stream));
+      TTB_CALL(ttb_memcpy_d2d(meta->shards[i]->ptr, idxIn->shards[i]->ptr, idxIn->bytes(), r.stream));
+    });
+  }
+  if (seqConcat) {
+    // staged [n, batch, seq, w] -> [batch, n, seq, w]
+    auto interleave = [&](const TensorPtr &src, const TensorPtr &dst, size_t width) {
+      std::vector<int64_t> shape = {static_cast<int64_t>(batch), static_cast<int64_t>(n), static_cast<int64_t>(seq * width)};
+      std::vector<int64_t> strides = {static_cast<int64_t>(seq * width), static_cast<int64_t>(batch * seq * width), 1};
+      eachRank([&](size_t i, const RankCtx &r) {
+        TTB_CALL(ttb_strided_copy(src->shards[i]->ptr, dst->shards[i]->ptr, static_cast<int>(dataTypeSize(src->dtype)), 3, shape.data(),
+                                  strides.data(), 0, r.stream));
+      });
+    };
+    interleave(stagedX, out, hidden);
+    interleave(stagedI, meta, k);
+  }
+  TensorPtr idx32 = castOnDevice(meta, DataType::Int32);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_moe_dispatch_mask(out->shards[i]->ptr, static_cast<const int32_t *>(idx32->shards[i]->ptr),
+                                   static_cast<const int32_t *>(local->shards[i]->ptr), ttbDtype(out->dtype), rows * n, hidden,
+                                   static_cast<int>(k), static_cast<int>(experts), r.stream));
+  });
+  put(op->dispatched(), out);
+  put(op->metadata(), meta);
+}
+
+// all_to_all_combine: expert outputs [E_local, global tokens, H] go back to the devices their tokens came from,
+// out[slot, b, s, :] = the output of the expert in metadata[token, slot].  Every device writes, for every destination,
+// the rows it owns (zeros elsewhere); a sum reduce-scatter delivers them (one owner per row, so the sum is exact).
+void Executor::runAllToAllCombine(const fbt::AllToAllCombineOp *op) {
+  TensorPtr x = getDevice(op->input_tensor());
+  uint32_t experts = 0, devices = 0;
+  TensorPtr local = moeLocalIndex(getDevice(op->expert_mapping()), experts, devices);
+  TensorPtr meta = castOnDevice(getDevice(op->expert_metadata()), DataType::Int32);
+  TensorPtr out = allocOut(op->out());
+  const uint32_t n = meshAxisSize(op->cluster_axis());
+  TTRT_ASSERT(x->shape.size() == 4 && out->shape.size() == 4 && meta->shape.size() == 4, "all_to_all_combine expects 4-D tensors");
+  const uint32_t localExperts = x->shape[0], gBatch = x->shape[1], gSeq = x->shape[2], hidden = x->shape[3];
+  const uint32_t k = out->shape[0], batch = out->shape[1], seq = out->shape[2];
+  TTRT_ASSERT(k == op->num_experts_per_tok() && meta->shape[3] >= k && meta->shape[1] == gBatch && meta->shape[2] == gSeq,
+              "expert_metadata must be [1, ", gBatch, ", ", gSeq, ", >= ", k, "]");
+  TTRT_ASSERT(meta->shape[3] == k, "expert_metadata with more slots than num_experts_per_tok is not supported");
+  const bool seqSharded = op->output_shard_dim() == 2 && n > 1;
+  TTRT_ASSERT(out->shape[3] == hidden && out->dtype == x->dtype &&
+                  (seqSharded ? (batch == gBatch && seq * n == gSeq) : (batch * n == gBatch && seq == gSeq)),
+              "all_to_all_combine result must be this device's share of the ", gBatch, " x ", gSeq, " tokens");
+  TensorPtr partial = n > 1 ? makeDeviceTensor(dev, {n, k, batch, seq, hidden}, x->dtype) : out;
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_moe_combine_partial(x->shards[i]->ptr, static_cast<const int32_t *>(meta->shards[i]->ptr),
+                                     static_cast<const int32_t *>(local->shards[i]->ptr), partial->shards[i]->ptr, ttbDtype(x->dtype),
+                                     static_cast<int>(n), static_cast<int>(k), static_cast<int>(batch), static_cast<int>(seq), hidden,
+                                     static_cast<int>(experts), static_cast<int>(localExperts), seqSharded ? 1 : 0, r.stream));
+  });
+  if (n > 1) {
+    refuseWhileRecording("a collective");
+    TTB_CALL(ttb_group_start());
+    eachRank([&](size_t i, const RankCtx &r) {
+      TTB_CALL(ttb_reduce_scatter(r.comm, partial->shards[i]->ptr, out->shards[i]->ptr, out->volume(), ttbDtype(x->dtype), 0, r.stream));
+    });
+    TTB_CALL(ttb_group_end());
+  }
+  put(op->out(), out);
+}
+
+void Executor::runMoeExpertTokenRemap(const fbt::MoeExpertTokenRemapOp *op) {
+  TensorPtr topk = getDevice(op->topk_tensor());
+  uint32_t experts = 0, devices = 0;
+  TensorPtr local = moeLocalIndex(getDevice(op->expert_mapping()), experts, devices);
+  TensorPtr meta = castOnDevice(getDevice(op->expert_metadata()), DataType::Int32);
+  TensorPtr mapping = allocOut(op->mapping()), reduced = allocOut(op->reduced());
+  TTRT_ASSERT(topk->shape.back() == experts, "topk_tensor must have one column per expert (", experts, ")");
+  const size_t tokens = topk->volume() / experts, k = meta->shape.back();
+  TTRT_ASSERT(meta->volume() == tokens * k, "expert_metadata must have one row per token");
+  const uint32_t localExperts = mapping->shape.back(), reduction = op->reduction_size();
+  TTRT_ASSERT(reduction > 0 && mapping->volume() == tokens * localExperts && mapping->dtype == topk->dtype &&
+                  reduced->volume() == (tokens + reduction - 1) / reduction * localExperts,
+              "moe_expert_token_remap results must be [tokens, local experts] and [ceil(tokens / ", reduction, "), local experts]");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_moe_expert_token_remap(topk->shards[i]->ptr, static_cast<const int32_t *>(meta->shards[i]->ptr),
+                                        static_cast<const int32_t *>(local->shards[i]->ptr), mapping->shards[i]->ptr, reduced->shards[i]->ptr,
+                                        ttbDtype(topk->dtype), ttbDtype(reduced->dtype), tokens, static_cast<int>(k),
+                                        static_cast<int>(experts), static_cast<int>(localExperts), static_cast<int>(reduction), r.stream));
+  });
+  put(op->mapping(), mapping);
+  put(op->reduced(), reduced);
+}
+
+// sparse_matmul: token blocks against expert weights, only where the sparsity tensor is non-zero.
+//   b sparse:    a [A, B, M, K], b [1, E, K, N], sparsity [A, B, 1, E] -> [A, B, 1, E, M, N]
+//   a sparse:    a [A, E, M, K], b [1, E, K, N], sparsity [1, 1, A, E] -> [A, E, M, N]
+//   both sparse: a [1, E, M, K], b [1, E, K, N], sparsity [1, 1, 1, E] -> [1, E, M, N]
+void Executor::runSparseMatmul(const fbt::SparseMatmulOp *op) {
+  TensorPtr a = getDevice(op->a()), b = getDevice(op->b()), sp = getDevice(op->sparsity());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(a->shape.size() == 4 && b->shape.size() == 4 && b->shape[0] == 1, "sparse_matmul expects a [.., .., M, K] and b [1, E, K, N]");
+  const int64_t E = b->shape[1], K = b->shape[2], N = b->shape[3], M = a->shape[2];
+  TTRT_ASSERT(a->shape[3] == K, "inner dimensions differ: ", a->shape[3], " vs ", K);
+  const bool aSparse = op->is_input_a_sparse();
+  TTRT_ASSERT(aSparse || op->is_input_b_sparse(), "sparse_matmul needs at least one sparse operand");
+  int64_t entries;
+  if (aSparse) {
+    TTRT_ASSERT(a->shape[1] == E, "a must have one block per expert (", E, ")");
+    entries = static_cast<int64_t>(a->shape[0]) * E;
+  } else {
+    entries = static_cast<int64_t>(a->shape[0]) * a->shape[1] * E;
+  }
+  TTRT_ASSERT(static_cast<int64_t>(sp->volume()) == entries, "the sparsity tensor must have ", entries, " entries");
+  TTRT_ASSERT(static_cast<int64_t>(out->volume()) == entries * M * N && out->dtype == a->dtype && b->dtype == a->dtype,
+              "sparse_matmul result must be [entries, M, N] in the operands' data type");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_sparse_matmul(a->shards[i]->ptr, b->shards[i]->ptr, sp->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(a->dtype),
+                               ttbDtype(sp->dtype), entries, E, aSparse ? 1 : 0, M, N, K, r.stream));
+  });
+  put(op->out(), out);
+}
+
 static int fusedActivationCode(const fb::String *s) {
   if (!s || s->size() == 0) return 0;
   std::string name = s->str();

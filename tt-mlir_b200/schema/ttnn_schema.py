@@ -486,6 +486,21 @@ S.table("AllReduceAsyncOp", [
 S.table("PointToPointOp", [
     ("in", "TensorRef"), ("out", "TensorRef"), ("sender_coord", "[u32]"), ("receiver_coord", "[u32]"),
     ("optional_output_tensor", "TensorRef")])
+S.table("AllToAllDispatchOp", [
+    ("input_tensor", "TensorRef"), ("expert_indices", "TensorRef"), ("expert_mapping", "TensorRef"),
+    ("dispatched", "TensorRef"), ("metadata", "TensorRef"), ("num_devices", "u32"), ("cluster_axis", "u32"),
+    ("memory_config", "MemoryConfig")])
+S.table("AllToAllCombineOp", [
+    ("input_tensor", "TensorRef"), ("expert_metadata", "TensorRef"), ("expert_mapping", "TensorRef"), ("out", "TensorRef"),
+    ("num_devices", "u32"), ("cluster_axis", "u32"), ("num_experts_per_tok", "u32"), ("output_shard_dim", "u32", 2),
+    ("memory_config", "MemoryConfig")])
+S.table("MoeExpertTokenRemapOp", [
+    ("topk_tensor", "TensorRef"), ("expert_mapping", "TensorRef"), ("expert_metadata", "TensorRef"), ("mapping", "TensorRef"),
+    ("reduced", "TensorRef"), ("reduction_size", "u32"), ("memory_config", "MemoryConfig")])
+S.table("SparseMatmulOp", [
+    ("a", "TensorRef"), ("b", "TensorRef"), ("sparsity", "TensorRef"), ("out", "TensorRef"), ("is_input_a_sparse", "bool"),
+    ("is_input_b_sparse", "bool"), ("nnz", "i64", OPT), ("program_config", "opaque"), ("memory_config", "MemoryConfig"),
+    ("dtype", "DataType"), ("compute_config", "DeviceComputeKernelConfig")])
 S.table("ReduceScatterOp", [
     ("in", "TensorRef"), ("out", "TensorRef"), ("scatter_dim", "i32"), ("reduce_type", "u32"),
     ("cluster_axis", "u32"), ("sub_device_id", "u8", OPT), ("memory_config", "MemoryConfig"),

@@ -811,6 +811,63 @@ class ProgramBuilder:
     def reset_global_semaphore(self, value: int = 0, loc=None) -> None:
         self._emit("ResetGlobalSemaphoreOp", {"semaphore": {"global_id": 0}, "value": value}, [], [], loc)
 
+    # ---- mixture of experts (generic flow: dispatch -> remap -> sparse matmuls -> combine)
+    def all_to_all_dispatch(self, x: Value, expert_indices: Value, expert_mapping: Value, cluster_axis: int = 1, loc=None):
+        """x [B, 1, S, H] and expert_indices [B, 1, S, K] hold this device's tokens; expert_mapping is the replicated
+        [1, 1, E, D] one-hot table.  Returns dispatched [1, B*D, S, H] and metadata [1, B*D, S, K]."""
+        n = self._axis_size(cluster_axis)
+        b, _, s_, h = x.shape
+        k = expert_indices.shape[-1]
+        disp = self._value([1, b * n, s_, h], x.dtype)
+        meta = self._value([1, b * n, s_, k], expert_indices.dtype)
+        self._emit("AllToAllDispatchOp", {
+            "input_tensor": x.ref, "expert_indices": expert_indices.ref, "expert_mapping": expert_mapping.ref,
+            "dispatched": disp.ref, "metadata": meta.ref, "num_devices": n, "cluster_axis": cluster_axis,
+            "memory_config": self._mc()}, [x, expert_indices, expert_mapping], [disp, meta], loc)
+        return disp, meta
+
+    def all_to_all_combine(self, x: Value, expert_metadata: Value, expert_mapping: Value, num_experts_per_tok: int,
+                           cluster_axis: int = 1, output_shard_dim: int = 1, loc=None) -> Value:
+        """x [E_local, B*D, S, H] -> [K, B, S, H] (this device's tokens, one slice per selected expert)."""
+        n = self._axis_size(cluster_axis)
+        _, bg, sg, h = x.shape
+        shape = [num_experts_per_tok, bg // n, sg, h] if output_shard_dim == 1 else [num_experts_per_tok, bg, sg // n, h]
+        out = self._value(shape, x.dtype)
+        self._emit("AllToAllCombineOp", {
+            "input_tensor": x.ref, "expert_metadata": expert_metadata.ref, "expert_mapping": expert_mapping.ref, "out": out.ref,
+            "num_devices": n, "cluster_axis": cluster_axis, "num_experts_per_tok": num_experts_per_tok,
+            "output_shard_dim": output_shard_dim, "memory_config": self._mc()}, [x, expert_metadata, expert_mapping], [out], loc)
+        return out
+
+    def moe_expert_token_remap(self, topk: Value, expert_mapping: Value, expert_metadata: Value, reduction_size: int = 32,
+                               reduced_dtype: Optional[str] = None, loc=None):
+        """topk [1, T_b, S, E] -> mapping [1, T_b, S, E_local], reduced [1, 1, ceil(T_b*S / reduction_size), E_local]."""
+        _, tb, s_, e = topk.shape
+        d = expert_mapping.shape[-1]
+        el = e // d
+        mapping = self._value([1, tb, s_, el], topk.dtype)
+        reduced = self._value([1, 1, (tb * s_ + reduction_size - 1) // reduction_size, el], reduced_dtype or topk.dtype)
+        self._emit("MoeExpertTokenRemapOp", {
+            "topk_tensor": topk.ref, "expert_mapping": expert_mapping.ref, "expert_metadata": expert_metadata.ref,
+            "mapping": mapping.ref, "reduced": reduced.ref, "reduction_size": reduction_size, "memory_config": self._mc()},
+            [topk, expert_mapping, expert_metadata], [mapping, reduced], loc)
+        return mapping, reduced
+
+    def sparse_matmul(self, a: Value, b: Value, sparsity: Value, is_input_a_sparse: bool = False, is_input_b_sparse: bool = True,
+                      nnz: Optional[int] = None, loc=None) -> Value:
+        _, e, _, n = b.shape
+        if is_input_a_sparse:
+            shape = [a.shape[0], e, a.shape[2], n]
+        else:
+            shape = [a.shape[0], a.shape[1], 1, e, a.shape[2], n]
+        out = self._value(shape, a.dtype)
+        t = {"a": a.ref, "b": b.ref, "sparsity": sparsity.ref, "out": out.ref, "is_input_a_sparse": is_input_a_sparse,
+             "is_input_b_sparse": is_input_b_sparse, "memory_config": self._mc(), "dtype": a.dtype}
+        if nnz is not None:
+            t["nnz"] = nnz
+        self._emit("SparseMatmulOp", t, [a, b, sparsity], [out], loc)
+        return out
+
     def all_reduce_async(self, x: Value, reduce_type: int = 0, cluster_axis: int = 1, loc=None) -> Value:
         out = self._value(x.shape, x.dtype)
         self._emit("AllReduceAsyncOp", {"in": x.ref, "out": out.ref, "reduce_type": reduce_type, "cluster_axis": cluster_axis,

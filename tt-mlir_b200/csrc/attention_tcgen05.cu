@@ -559,17 +559,19 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       tcWaitLd();
       tcFenceBefore();
       mbarArrive(sEmpty + 8 * (hd * 2 + buf)); // the score buffer can take the tile after next
-      float mx = -INFINITY;
+      // Four independent chains: a single running maximum is 64 dependent instructions.
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         if (needMask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, c * 32 + i <= lastRel ? __uint_as_float(sc[c][i]) : -INFINITY);
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], c * 32 + i <= lastRel ? __uint_as_float(sc[c][i]) : -INFINITY);
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sc[c][i]));
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sc[c][i]));
         }
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       float corr = 1.0f;
       if (j == 0) {
         m = mx == -INFINITY ? 0.0f : mx;
@@ -577,7 +579,27 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         corr = fastExp2((m - mx) * sl2);
         m = mx;
       }
-      // P's buffer is free, and O holds every earlier tile, once P V_{j-1} has completed.
+      // The probabilities are computed into registers first: P's buffer and O are only touched once P V_{j-1}
+      // has completed, and that contraction runs while these exponentials do.
+      const float negM = -m * sl2;
+      float sum = 0.0f, sum2 = 0.0f;
+      uint32_t w[2][16];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float a = fastExp2(fmaf(__uint_as_float(sc[c][i]), sl2, negM));
+          float bb = fastExp2(fmaf(__uint_as_float(sc[c][i + 1]), sl2, negM));
+          if (needMask) {
+            a = c * 32 + i <= lastRel ? a : 0.0f;
+            bb = c * 32 + i + 1 <= lastRel ? bb : 0.0f;
+          }
+          sum += a;
+          sum2 += bb;
+          w[c][i >> 1] = packPair<T>(a, bb);
+        }
+      }
+      sum += sum2;
       if (!__all_sync(0xffffffffu, mbarWait(pEmpty + 8 * hd, (j & 1) ^ 1, abortP, 10))) { ok = false; break; }
       if (__any_sync(0xffffffffu, corr != 1.0f)) {
         tcFenceAfter();
@@ -593,28 +615,14 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         }
         tcWaitSt();
       }
-      const float negM = -m * sl2;
-      float sum = 0.0f;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t w[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float a = fastExp2(fmaf(__uint_as_float(sc[c][i]), sl2, negM));
-          float bb = fastExp2(fmaf(__uint_as_float(sc[c][i + 1]), sl2, negM));
-          if (needMask) {
-            a = c * 32 + i <= lastRel ? a : 0.0f;
-            bb = c * 32 + i + 1 <= lastRel ? bb : 0.0f;
-          }
-          sum += a + bb;
-          w[i >> 1] = packPair<T>(a, bb);
-        }
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           const uint32_t chunk = static_cast<uint32_t>(c * 4 + q4);
           const uint32_t addr = pRow + ((chunk ^ swz) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[q4 * 4]), "r"(w[q4 * 4 + 1]),
-                       "r"(w[q4 * 4 + 2]), "r"(w[q4 * 4 + 3]) : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[c][q4 * 4]), "r"(w[c][q4 * 4 + 1]),
+                       "r"(w[c][q4 * 4 + 2]), "r"(w[c][q4 * 4 + 3]) : "memory");
         }
       }
       l += sum;

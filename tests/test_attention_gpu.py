@@ -88,6 +88,22 @@ def test_sdpa_large_scores_and_scale(kh):
     assert_matches(got, want, "sdpa large scores")
 
 
+def test_sdpa_two_heads_per_cta_with_frequent_rescales(kh):
+    # Enough CTAs for the two-heads-per-CTA kernel, and keys whose magnitude grows along the sequence, so that rows
+    # raise their running maximum (and rescale O) at different tiles: the softmax warps of a head drift apart, which is
+    # what their barrier protocol has to survive.
+    torch.manual_seed(17)
+    B, Hq, Hkv, S = 2, 16, 4, 2048
+    q = (torch.randn(B, Hq, S, 128) * 2).to(torch.bfloat16)
+    growth = (1.0 + 6.0 * torch.arange(S) / S).reshape(1, 1, S, 1) * (torch.rand(B, Hkv, S, 1) > 0.5)
+    k = (torch.randn(B, Hkv, S, 128) * growth).to(torch.bfloat16)
+    v = torch.randn(B, Hkv, S, 128).to(torch.bfloat16)
+    for causal in (True, False):
+        got = run_sdpa(kh, q, k, v, causal, scale=0.2)
+        want = O.sdpa(q, k, v, is_causal=causal, scale=0.2)
+        assert_matches(got, want, f"sdpa with growing scores, causal={causal}")
+
+
 def test_sdpa_kernels_agree(kh, monkeypatch):
     # Two calls in a row give the same bits (no state carried between launches).
     torch.manual_seed(9)

@@ -382,18 +382,20 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
 // at the decoder shape).  This one gives a CTA the same 128 query rows of TWO heads of a group:
 // every K/V tile (64 keys, four-stage rings) is loaded once and used by both heads, which halves
 // that traffic, and each head has its own softmax warp group, score buffers (two per head) and
-// output accumulator in TMEM, so the two heads' softmax and contractions interleave.
-//   TMEM: S(head, buffer) at 64 * (2 head + buffer), O(head) at 256 + 128 head.
-//   Shared memory: Q_A | Q_B (32 KiB each) | K x4 | V x4 (16 KiB each) | P_A | P_B (16 KiB each) | barriers.
-// What bounds both kernels (clock stamps of the MMA thread, and a stand-alone issue loop):
-// an M = 128 contraction with both operands in shared memory reads 128 bytes per clock, all an SM
-// has, so the contractions slow down to half speed while the softmax warps store P and TMA
-// writes K/V into the same shared memory.
+// output accumulator in TMEM, so the two heads' softmax and contractions interleave.  The probabilities never touch
+// shared memory: a softmax thread packs its row's 64 values to 16 bits and writes them over the first 32 columns of
+// the score buffer they came from, and O += P V reads them from there as the tensor-memory A operand.
+//   TMEM: S(head, buffer) at 64 * (2 head + buffer) (P over its first 32 columns), O(head) at 256 + 128 head.
+//   Shared memory: Q_A | Q_B (32 KiB each) | K x4 | V x4 (16 KiB each) | barriers.
+// Measured with parts of the kernel switched off (decoder shape, 58 us whole): without the exponentials 59 us,
+// without the score loads 58 us, without P V 50 us, without Q K^T 48 us, without any contraction 44 us.  So
+// neither the special-function unit nor the tensor pipe nor shared-memory bandwidth (P in shared memory cost
+// 1 us more) is what the launch waits for: three quarters of it is the per-tile hand-over between the softmax
+// warps, the issuing thread and the TMA ring, plus the tail of the 1.7 waves of unequal (causal) CTAs.
 constexpr int AP_BN = 64;
 constexpr int AP_STAGES = 4;
 constexpr int AP_KV = AP_BN * AT_D * 2;  // bytes of a K or V tile
-constexpr int AP_P = AT_BM * AP_BN * 2;  // bytes of a P tile
-constexpr int AP_SMEM = 2 * AT_TILE + 2 * AP_STAGES * AP_KV + 2 * AP_P + 1024 + 256;
+constexpr int AP_SMEM = 2 * AT_TILE + 2 * AP_STAGES * AP_KV + 1024 + 256;
 
 template <typename T>
 __global__ void __launch_bounds__(AT_THREADS, 1)
@@ -404,8 +406,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   __shared__ int abortFlag;
 
   const uint32_t base = (smemU32(smemRaw) + 1023u) & ~1023u;
-  const uint32_t sQ = base, sK = base + 2 * AT_TILE, sV = sK + AP_STAGES * AP_KV, sP = sV + AP_STAGES * AP_KV;
-  const uint32_t bars = sP + 2 * AP_P;
+  const uint32_t sQ = base, sK = base + 2 * AT_TILE, sV = sK + AP_STAGES * AP_KV;
+  const uint32_t bars = sV + AP_STAGES * AP_KV;
   const uint32_t qFull = bars, kFull = bars + 8, kEmpty = kFull + 8 * AP_STAGES, vFull = kEmpty + 8 * AP_STAGES,
                  vEmpty = vFull + 8 * AP_STAGES, sFull = vEmpty + 8 * AP_STAGES, sEmpty = sFull + 32, pReady = sEmpty + 32,
                  pEmpty = pReady + 16;
@@ -436,10 +438,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     }
     for (int i = 0; i < 4; ++i) {
       mbarInit(sFull + 8 * i, 1);
-      mbarInit(sEmpty + 8 * i, 128);
+      mbarInit(sEmpty + 8 * i, 4); // one arrival per softmax warp (its lane 0, after the warp has synchronised)
     }
     for (int i = 0; i < 2; ++i) {
-      mbarInit(pReady + 8 * i, 128);
+      mbarInit(pReady + 8 * i, 4);
       mbarInit(pEmpty + 8 * i, 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -513,13 +515,15 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         for (int hd = 0; hd < 2 && fine; ++hd) {
           if (!mbarWait(pReady + 8 * hd, j & 1, abortP, 7)) { fine = false; break; }
           tcFenceAfter();
-          // O_hd += P_hd V_j: four steps of 16 keys.  P is K-major (one 128-byte row per query
-          // row); V is MN-major: 128-byte rows of 64 d values, one row per key, the second 64 d
-          // values half a tile further on.
+          // O_hd += P_hd V_j: four steps of 16 keys.  P is read from tensor memory, where the softmax warps wrote
+          // it over the first 32 columns of the score buffer it came from (row i in lane i, keys 2c and 2c + 1 in
+          // column c); V is MN-major: 128-byte rows of 64 d values, one row per key, the second 64 d values half a
+          // tile further on.  The next scores for this buffer, S_{j+2}, are issued after these products and the
+          // tensor pipe runs one thread's contractions in issue order, so P is consumed before it is overwritten.
 #pragma unroll
           for (int ks = 0; ks < AP_BN / 16; ++ks) {
-            tcMma(tmemBase + 4 * AP_BN + hd * AT_D, smemDescSw128(sP + hd * AP_P + ks * 32, 0, 1024),
-                  smemDescSw128(vb + ks * 2048, AP_KV / 2, 1024), idPV, (j | ks) > 0);
+            tcMmaTmemA(tmemBase + 4 * AP_BN + hd * AT_D, tmemBase + (hd * 2 + (j & 1)) * AP_BN + ks * 8,
+                       smemDescSw128(vb + ks * 2048, AP_KV / 2, 1024), idPV, (j | ks) > 0);
           }
           tcCommit(pEmpty + 8 * hd);
         }
@@ -538,8 +542,6 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     constexpr float kLazy = 8.0f; // see the single-head kernel
     float m = 0.0f, l = 0.0f;
     const uint32_t oAddr = laneAddr + 4 * AP_BN + hd * AT_D;
-    const uint32_t pRow = sP + hd * AP_P + row * 128;
-    const uint32_t swz = static_cast<uint32_t>(row & 7);
     bool ok = true;
     for (int j = 0; j < nT; ++j) {
       const int buf = j & 1, bph = (j >> 1) & 1;
@@ -558,7 +560,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       tcLoad32(sAddr + 32, sc[1]);
       tcWaitLd();
       tcFenceBefore();
-      mbarArrive(sEmpty + 8 * (hd * 2 + buf)); // the score buffer can take the tile after next
+      __syncwarp();
+      if (lane == 0) mbarArrive(sEmpty + 8 * (hd * 2 + buf)); // the score buffer can take the tile after next
       // Four independent chains: a single running maximum is 64 dependent instructions.
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -583,7 +586,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       // has completed, and that contraction runs while these exponentials do.
       const float negM = -m * sl2;
       float sum = 0.0f, sum2 = 0.0f;
-      uint32_t w[2][16];
+      uint32_t w[32];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
 #pragma unroll
@@ -596,10 +599,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
           }
           sum += a;
           sum2 += bb;
-          w[c][i >> 1] = packPair<T>(a, bb);
+          w[c * 16 + (i >> 1)] = packPair<T>(a, bb);
         }
       }
       sum += sum2;
+      // O may only be rescaled once P V_{j-1} has completed (P itself goes into this tile's own score buffer and
+      // would not need the wait).  Every warp waits, rescale or not: a warp that ran ahead would arrive on pReady
+      // for tile j + 1 while slower warps still owe their arrival for tile j, and the barrier would count it as theirs.
       if (!__all_sync(0xffffffffu, mbarWait(pEmpty + 8 * hd, (j & 1) ^ 1, abortP, 10))) { ok = false; break; }
       if (__any_sync(0xffffffffu, corr != 1.0f)) {
         tcFenceAfter();
@@ -613,21 +619,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
           for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
           tcStore32(oAddr + c * 32, r);
         }
-        tcWaitSt();
       }
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const uint32_t chunk = static_cast<uint32_t>(c * 4 + q4);
-          const uint32_t addr = pRow + ((chunk ^ swz) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[c][q4 * 4]), "r"(w[c][q4 * 4 + 1]),
-                       "r"(w[c][q4 * 4 + 2]), "r"(w[c][q4 * 4 + 3]) : "memory");
-        }
-      }
+      tcStore32(sAddr, w);
+      tcWaitSt();
+      tcFenceBefore();
       l += sum;
-      fenceProxyAsyncShared();
-      mbarArrive(pReady + 8 * hd);
+      __syncwarp();
+      if (lane == 0) mbarArrive(pReady + 8 * hd);
     }
     if (ok && nT > 0 && !__all_sync(0xffffffffu, mbarWait(pEmpty + 8 * hd, (nT & 1) ^ 1, abortP, 11))) ok = false;
     if (ok) {

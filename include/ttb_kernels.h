@@ -627,6 +627,8 @@ TTB_API int ttb_broadcast(void *comm, const void *in, void *out, size_t count, i
  * ttb_sparse_matmul: c[i] = a[a_per_entry ? i : i / experts] (m x k) * b[i % experts] (k x n) for the `entries`
  *   whose sparsity[i] is non-zero; the others are cleared.  bf16 / f16, f32 accumulation, one rounding. */
 TTB_API int ttb_moe_local_index(const int32_t *mapping, int32_t *local_idx, int experts, int devices, int device, void *stream);
+/* ... from a table of owners instead (owner[e] = mesh coordinate of expert e; ::ttnn::all_to_all_dispatch_metadata). */
+TTB_API int ttb_moe_local_index_owner(const int32_t *owner, int32_t *local_idx, int experts, int device, void *stream);
 TTB_API int ttb_moe_dispatch_mask(void *tokens, const int32_t *indices, const int32_t *local_idx, int dtype, size_t rows,
                                   size_t hidden, int k, int experts, void *stream);
 TTB_API int ttb_moe_combine_partial(const void *expert_out, const int32_t *metadata, const int32_t *local_idx, void *partial,

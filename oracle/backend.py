@@ -389,6 +389,18 @@ class OracleBuilder:
         disp, meta = ops.all_to_all_dispatch(per(x), per(expert_indices), mp)
         return (OValue(disp), OValue(meta)) if isinstance(x.t, list) else (OValue(disp[0]), OValue(meta[0]))
 
+    def all_to_all_dispatch_metadata(self, x, expert_indices, expert_scores, expert_mapping, cluster_axis=1, loc=None):
+        per = lambda v: v.t if isinstance(v.t, list) else [v.t]
+        d, i, s_ = ops.all_to_all_dispatch_metadata(per(x), per(expert_indices), per(expert_scores), expert_mapping.first)
+        pack = (lambda v: OValue(v)) if isinstance(x.t, list) else (lambda v: OValue(v[0]))
+        return pack(d), pack(i), pack(s_)
+
+    def topk_router_gpt(self, x, weight, bias, k, index_dtype="UInt16", loc=None):
+        def fn(t, w, b):
+            idx, wts = ops.topk_router_gpt(t, w, b, k)
+            return idx.to(TORCH_DTYPE[index_dtype]), wts
+        return _map(fn, x, weight, bias)
+
     def all_to_all_combine(self, x, expert_metadata, expert_mapping, num_experts_per_tok, cluster_axis=1, output_shard_dim=1, loc=None):
         per = lambda v: v.t if isinstance(v.t, list) else [v.t]
         md = expert_metadata.t if isinstance(expert_metadata.t, list) else expert_metadata.t

@@ -831,3 +831,27 @@ def sparse_matmul(a, b, sparsity, a_sparse: bool):
         out = torch.einsum("abmk,xekn->abxemn", af, bf)                      # [A, B, 1, E, M, N]
         mask = sparsity.reshape(a.shape[0], a.shape[1], 1, b.shape[1], 1, 1)
     return torch.where(mask.float() != 0, out, torch.zeros_like(out)).to(a.dtype)
+
+
+def all_to_all_dispatch_metadata(xs, indices, scores, owner):
+    """tools/golden/mapping.py:1656-1760: per device the global token list [1, T, H] with the rows routed to it (an
+    expert of the token lives there; owner[e] = device of expert e), and everybody's indices and scores."""
+    h, k = xs[0].shape[-1], indices[0].shape[-1]
+    full = torch.cat([x.reshape(-1, h) for x in xs])
+    idx = torch.cat([i.reshape(-1, k) for i in indices])
+    scr = torch.cat([s_.reshape(-1, k) for s_ in scores])
+    own = owner.reshape(-1, owner.shape[-1])[0].to(torch.int64)
+    target = own[idx.to(torch.int64)]                                          # [T, K] device per selected expert
+    outs = []
+    for d in range(len(xs)):
+        routed = (target == d).any(dim=-1, keepdim=True)
+        outs.append(torch.where(routed, full, torch.zeros_like(full)).reshape(1, -1, h))
+    return outs, [idx.reshape(1, -1, k).clone() for _ in xs], [scr.reshape(1, -1, k).clone() for _ in xs]
+
+
+def topk_router_gpt(x, weight, bias, k):
+    """tools/golden/mapping.py:5960-5992: logits = x @ weight (in the input's 16-bit type) + bias, the k largest per
+    row in descending order, softmax over those k."""
+    logits = torch.matmul(x.float(), weight.float()).to(x.dtype) + bias
+    values, idx = torch.topk(logits, k=k, dim=-1, largest=True, sorted=True)
+    return idx, torch.softmax(values.float(), dim=-1).to(x.dtype)

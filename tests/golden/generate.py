@@ -500,7 +500,7 @@ def main():
     store(out, "map/moe/selected", sel)
     shard4 = lambda t: ref.GoldenMapTensor({d: t[d * Mt:(d + 1) * Mt].reshape(1, 1, Mt, -1).clone() for d in range(D)}, (1, D))
     owner = (torch.arange(Ee) // 2).to(torch.int32).reshape(1, 1, 1, Ee).repeat(1, 1, D, 1)        # entry [d, e] = owning device
-    disp, idx_all, _ = ref.ttir_all_to_all_dispatch_metadata_golden(
+    disp, idx_all, scr_all = ref.ttir_all_to_all_dispatch_metadata_golden(
         shard4(tok), shard4(sel), shard4(scr), ref.GoldenMapTensor({d: owner.clone() for d in range(D)}, (1, D)),
         S.IntegerAttr(D), S.IntegerAttr(1), S.F32Type(), S.IntegerType(32), S.F32Type())
     store_shards("map/moe/dispatched_1x4", disp)
@@ -513,6 +513,16 @@ def main():
     store(out, "map/moe/combine_out", one(ref.ttir_all_to_all_combine_golden(
         gmt(cin), gmt(cmeta), gmt(torch.ones(1, 1, 4, 1, dtype=torch.int32)), S.IntegerAttr(1), S.IntegerAttr(1), S.IntegerAttr(2),
         S.F32Type())))
+
+    # --- GPT-OSS router (mapping.py:5960-5992): 32 tokens, hidden 64, 16 experts, top 4
+    rx, rw, rb = rnd(32, 64).to(torch.bfloat16), (rnd(64, 16) * 0.3).to(torch.bfloat16), (rnd(32, 16) * 0.1).to(torch.bfloat16)
+    for n, t in (("x", rx), ("w", rw), ("b", rb)):
+        store(out, f"map/router/{n}", t)
+    ridx, rwts = ref.ttir_topk_router_gpt_golden(gmt(rx), gmt(rw), gmt(rb), S.IntegerAttr(4), S.IntegerAttr(16), S.BF16Type())
+    store(out, "map/router/indices", one(ridx).to(torch.int32))
+    store(out, "map/router/weights", one(rwts))
+    store(out, "map/moe/scores", scr)
+    store(out, "map/moe/scores_gathered", scr_all.shard_at(0))
 
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ttir_cpu_golden.npz")
     np.savez_compressed(path, **out)

@@ -107,6 +107,25 @@ def test_moe_dispatch_expert_layer_combine(rt, mesh2):
     assert torch.equal(got[2][0], sel.reshape(1, B, S, K)[0]) and torch.equal(got[2][0], got[2][1])
 
 
+def test_all_to_all_dispatch_metadata_on_the_mesh(rt, mesh2):
+    torch.manual_seed(33)
+    x = torch.randn(1, 1, 48, 64).to(torch.bfloat16)                    # 24 tokens per device
+    sel = torch.stack([torch.randperm(8)[:2] for _ in range(48)]).to(torch.int32).reshape(1, 1, 48, 2)
+    scr = torch.rand(1, 1, 48, 2).to(torch.bfloat16)
+    owner = (torch.arange(8) // 4).to(torch.int32).reshape(1, 1, 1, 8).repeat(1, 1, 2, 1)
+
+    def body(b, xv, iv, sv, ov):
+        d, i, s_ = b.all_to_all_dispatch_metadata(b.distribute(xv, 2), b.distribute(iv, 2), b.distribute(sv, 2), b.distribute(ov, None))
+        return b.aggregate(d, 0), b.aggregate(i, 0), b.aggregate(s_, 0)
+    got, want = run_mesh(rt, mesh2, body, [x, sel, scr, owner])
+    for g, w_ in zip(got, want):
+        assert torch.equal(g, w_)
+    for d in range(2):
+        routed = (sel.reshape(48, 2) // 4 == d).any(-1).reshape(48, 1)
+        assert torch.equal(got[0][d], torch.where(routed, x.reshape(48, 64), torch.zeros(48, 64).to(torch.bfloat16)))
+        assert torch.equal(got[1][d], sel.reshape(48, 2)) and torch.equal(got[2][d], scr.reshape(48, 2))
+
+
 def test_norms_with_the_hidden_dimension_split_over_the_mesh(rt, mesh2):
     torch.manual_seed(21)
     x, res = torch.randn(48, 512), torch.randn(48, 512) * 0.5

@@ -296,3 +296,36 @@ def test_moe_routing_ops_on_one_device(rt, device, golden):
                              [topk, half, sel.reshape(1, 6, 5, 2)])
         assert torch.equal(got[0], want[0]) and torch.equal(got[1].float(), want[1].float())
         assert got[0].shape == (1, 6, 5, 2) and got[1].shape == (1, 1, 4, 2)
+
+
+def test_topk_router_gpt_matches_the_reference_golden(rt, device, golden):
+    # The contraction's summation order differs from torch's, so a logit can land on the other side of a bf16 rounding
+    # boundary and two near-equal experts swap places: the selections must agree on almost every token, and the
+    # weights wherever they do.
+    def check(got, idx, wts, what, tol):
+        same = (got[0].to(torch.int32) == idx.to(torch.int32)).all(dim=-1)
+        assert same.float().mean() >= 0.9, f"{what}: only {int(same.sum())} of {same.numel()} selections agree"
+        assert_matches(got[1][same], wts[same], what, tol)
+        assert got[0].dtype == torch.uint16 and torch.allclose(got[1].float().sum(-1), torch.ones(got[1].shape[0]), atol=2e-2)
+    x, w, b_ = (golden[f"map/router/{n}"] for n in ("x", "w", "b"))
+    got, want = run_body(rt, device, lambda b, xv, wv, bv: b.topk_router_gpt(xv, wv, bv, 4), [x, w, b_])
+    check(got, golden["map/router/indices"], golden["map/router/weights"], "router against the reference golden", (0.999, 1e-2, 2.0 ** -7))
+    check(got, want[0], want[1], "router against the oracle", (0.999, 1e-2, 2.0 ** -7))
+    torch.manual_seed(14)
+    xb = torch.randn(32, 2880).to(torch.bfloat16)                   # the GPT-OSS router's own shape: 128 experts, top 4
+    wb, bb = (torch.randn(2880, 128) * 0.02).to(torch.bfloat16), torch.randn(32, 128).to(torch.bfloat16)
+    got, want = run_body(rt, device, lambda b, xv, wv, bv: b.topk_router_gpt(xv, wv, bv, 4), [xb, wb, bb])
+    check(got, want[0], want[1], "router at scale", (0.999, 2e-2, 2.0 ** -6))
+
+
+def test_all_to_all_dispatch_metadata_on_one_device(rt, device):
+    torch.manual_seed(15)
+    x = torch.randn(1, 1, 24, 64).to(torch.bfloat16)
+    sel = torch.stack([torch.randperm(8)[:2] for _ in range(24)]).to(torch.int32).reshape(1, 1, 24, 2)
+    scr = torch.rand(1, 1, 24, 2).to(torch.bfloat16)
+    owner = (torch.arange(8) % 2).to(torch.int32).reshape(1, 1, 1, 8)      # even experts here, odd ones on a device that is not in this mesh
+    got, want = run_body(rt, device, lambda b, xv, iv, sv, ov: b.all_to_all_dispatch_metadata(xv, iv, sv, ov), [x, sel, scr, owner])
+    for g, w_ in zip(got, want):
+        assert torch.equal(g, w_)
+    routed = (sel % 2 == 0).any(-1).reshape(1, 24, 1)
+    assert torch.equal(got[0], torch.where(routed, x.reshape(1, 24, 64), torch.zeros(1, 24, 64).to(torch.bfloat16)))

@@ -372,6 +372,20 @@ def test_mixture_of_experts_ops(golden):
     assert ((m != 0).reshape(24, 2) == torch.stack([(sel == 2).any(1), (sel == 3).any(1)], dim=1)).all()
 
 
+def test_dispatch_metadata_and_router(golden):
+    """Restatements against the reference's goldens (tools/golden/mapping.py:1656-1760, 5960-5992)."""
+    tok, sel, scr = golden["map/moe/tokens"], golden["map/moe/selected"], golden["map/moe/scores"]
+    owner = (torch.arange(8) // 2).to(torch.int32).reshape(1, 1, 1, 8).repeat(1, 1, 4, 1)
+    part = lambda t: [t[6 * d: 6 * d + 6].reshape(1, 1, 6, -1) for d in range(4)]
+    disp, idx, sc = ops.all_to_all_dispatch_metadata(part(tok), part(sel), part(scr), owner)
+    for d in range(4):
+        assert torch.equal(disp[d], golden[f"map/moe/dispatched_1x4/{d}"])
+        assert torch.equal(idx[d], golden["map/moe/indices_gathered"]) and torch.equal(sc[d], golden["map/moe/scores_gathered"])
+    x, w, b = (golden[f"map/router/{n}"] for n in ("x", "w", "b"))
+    ridx, rw = ops.topk_router_gpt(x, w, b, 4)
+    assert torch.equal(ridx.to(torch.int32), golden["map/router/indices"]) and torch.equal(rw, golden["map/router/weights"])
+
+
 def test_layer_norm(golden):
     x, w, b = golden["ln/x"], golden["ln/w"], golden["ln/b"]
     assert same(ops.layer_norm(x), golden["ln/plain"])

@@ -28,6 +28,14 @@ __global__ void moeLocalIndexKernel(const int32_t *__restrict__ mapping, int32_t
   }
 }
 
+// The same from a table of owners (owner[e] = mesh coordinate of expert e), the format all_to_all_dispatch_metadata takes.
+__global__ void moeLocalIndexOwnerKernel(const int32_t *__restrict__ owner, int32_t *__restrict__ localIdx, int experts, int me) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int next = 0;
+    for (int e = 0; e < experts; ++e) localIdx[e] = owner[e] == me ? next++ : -1;
+  }
+}
+
 // Rows of the gathered token buffer [T, H] that none of whose K experts lives here are cleared.
 template <typename T>
 __global__ void __launch_bounds__(256) moeDispatchMaskKernel(T *__restrict__ tokens, const int32_t *__restrict__ indices,
@@ -225,6 +233,15 @@ int ttb_moe_local_index(const int32_t *mapping, int32_t *local_idx, int experts,
   TTB_CHECK(mapping && local_idx, "null tensor");
   TTB_CHECK(experts > 0 && devices > 0 && device >= 0 && device < devices, "bad expert mapping geometry");
   moeLocalIndexKernel<<<1, 32, 0, asStream(stream)>>>(mapping, local_idx, experts, devices, device);
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_moe_local_index_owner(const int32_t *owner, int32_t *local_idx, int experts, int device, void *stream) {
+  TTB_CHECK(owner && local_idx, "null tensor");
+  TTB_CHECK(experts > 0 && device >= 0, "bad expert mapping geometry");
+  moeLocalIndexOwnerKernel<<<1, 32, 0, asStream(stream)>>>(owner, local_idx, experts, device);
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;

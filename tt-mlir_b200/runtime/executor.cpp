@@ -122,6 +122,29 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     pushRef(outs, o->metadata());
     break;
   }
+  case OpType::AllToAllDispatchMetadataOp: {
+    const auto *o = op->type_as_AllToAllDispatchMetadataOp();
+    pushRef(ins, o->input_tensor());
+    pushRef(ins, o->expert_indices());
+    pushRef(ins, o->expert_scores());
+    pushRef(ins, o->expert_mapping());
+    pushRef(ins, o->dispatched_buffer());
+    pushRef(ins, o->indices_buffer());
+    pushRef(ins, o->scores_buffer());
+    pushRef(outs, o->dispatched());
+    pushRef(outs, o->indices());
+    pushRef(outs, o->scores());
+    break;
+  }
+  case OpType::TopKRouterGptOp: {
+    const auto *o = op->type_as_TopKRouterGptOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->weight());
+    pushRef(ins, o->bias());
+    pushRef(outs, o->expert_indices());
+    pushRef(outs, o->expert_weights());
+    break;
+  }
   case OpType::AllToAllCombineOp: {
     const auto *o = op->type_as_AllToAllCombineOp();
     pushRef(ins, o->input_tensor());
@@ -793,6 +816,8 @@ private:
   // expert ownership of this process's mesh coordinates: localIdx tensors (Int32 [experts]) from a [1, 1, E, D] mapping
   TensorPtr moeLocalIndex(const TensorPtr &mapping, uint32_t &experts, uint32_t &devices);
   void runAllToAllDispatch(const fbt::AllToAllDispatchOp *op);
+  void runAllToAllDispatchMetadata(const fbt::AllToAllDispatchMetadataOp *op);
+  void runTopKRouterGpt(const fbt::TopKRouterGptOp *op);
   void runAllToAllCombine(const fbt::AllToAllCombineOp *op);
   void runMoeExpertTokenRemap(const fbt::MoeExpertTokenRemapOp *op);
   void runSparseMatmul(const fbt::SparseMatmulOp *op);
@@ -1168,6 +1193,8 @@ size_t Executor::runOp(size_t i) {
   case OpType::CumSumOp: runCumSum(op->type_as_CumSumOp()); break;
   case OpType::CumProdOp: runCumProd(op->type_as_CumProdOp()); break;
   case OpType::AllToAllDispatchOp: runAllToAllDispatch(op->type_as_AllToAllDispatchOp()); break;
+  case OpType::AllToAllDispatchMetadataOp: runAllToAllDispatchMetadata(op->type_as_AllToAllDispatchMetadataOp()); break;
+  case OpType::TopKRouterGptOp: runTopKRouterGpt(op->type_as_TopKRouterGptOp()); break;
   case OpType::AllToAllCombineOp: runAllToAllCombine(op->type_as_AllToAllCombineOp()); break;
   case OpType::MoeExpertTokenRemapOp: runMoeExpertTokenRemap(op->type_as_MoeExpertTokenRemapOp()); break;
   case OpType::SparseMatmulOp: runSparseMatmul(op->type_as_SparseMatmulOp()); break;
@@ -2818,6 +2845,91 @@ void Executor::runAllToAllDispatch(const fbt::AllToAllDispatchOp *op) {
   });
   put(op->dispatched(), out);
   put(op->metadata(), meta);
+}
+
+// all_to_all_dispatch_metadata (operations/ccl/all_to_all_dispatch_metadata.cpp; golden tools/golden/mapping.py:1656-1760):
+// per device [1, 1, M, H] tokens with [1, 1, M, K] expert indices and scores; every device gets [1, D*M, H] holding the
+// tokens routed to it (zeros elsewhere) and the indices and scores of all devices.  expert_mapping is [.., D, E] with
+// entry [d, e] = the mesh coordinate that owns expert e.  The persistent buffers and the semaphore of the Tensix
+// implementation are not used.
+void Executor::runAllToAllDispatchMetadata(const fbt::AllToAllDispatchMetadataOp *op) {
+  TensorPtr x = getDevice(op->input_tensor()), idxIn = getDevice(op->expert_indices()), scrIn = getDevice(op->expert_scores());
+  TensorPtr owner = castOnDevice(getDevice(op->expert_mapping()), DataType::Int32);
+  TTRT_ASSERT(!owner->shape.empty(), "expert_mapping must be [devices, experts]");
+  const uint32_t experts = owner->shape.back();
+  TensorPtr local = makeDeviceTensor(dev, {experts}, DataType::Int32);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_moe_local_index_owner(static_cast<const int32_t *>(owner->shards[i]->ptr), static_cast<int32_t *>(local->shards[i]->ptr),
+                                       static_cast<int>(experts), static_cast<int>(r.meshRank), r.stream));
+  });
+  TensorPtr out = allocOut(op->dispatched()), idxOut = allocOut(op->indices()), scrOut = allocOut(op->scores());
+  const uint32_t n = meshAxisSize(op->cluster_axis());
+  const size_t hidden = x->shape.back(), k = idxIn->shape.back(), rows = x->volume() / std::max<size_t>(hidden, 1);
+  TTRT_ASSERT(idxIn->volume() == rows * k && scrIn->volume() == rows * k, "expert_indices / expert_scores must be [tokens, ", k, "]");
+  TTRT_ASSERT(out->volume() == x->volume() * n && out->dtype == x->dtype && idxOut->volume() == idxIn->volume() * n &&
+                  idxOut->dtype == idxIn->dtype && scrOut->volume() == scrIn->volume() * n && scrOut->dtype == scrIn->dtype,
+              "all_to_all_dispatch_metadata results must hold the tokens, indices and scores of all ", n, " devices");
+  if (n > 1) {
+    refuseWhileRecording("a collective");
+    TTB_CALL(ttb_group_start());
+    eachRank([&](size_t i, const RankCtx &r) {
+      TTB_CALL(ttb_all_gather(r.comm, x->shards[i]->ptr, out->shards[i]->ptr, x->volume(), ttbDtype(x->dtype), r.stream));
+      TTB_CALL(ttb_all_gather(r.comm, idxIn->shards[i]->ptr, idxOut->shards[i]->ptr, idxIn->volume(), ttbDtype(idxIn->dtype), r.stream));
+      TTB_CALL(ttb_all_gather(r.comm, scrIn->shards[i]->ptr, scrOut->shards[i]->ptr, scrIn->volume(), ttbDtype(scrIn->dtype), r.stream));
+    });
+    TTB_CALL(ttb_group_end());
+  } else {
+    eachRank([&](size_t i, const RankCtx &r) {
+      TTB_CALL(ttb_memcpy_d2d(out->shards[i]->ptr, x->shards[i]->ptr, x->bytes(), r.stream));
+      TTB_CALL(ttb_memcpy_d2d(idxOut->shards[i]->ptr, idxIn->shards[i]->ptr, idxIn->bytes(), r.stream));
+      TTB_CALL(ttb_memcpy_d2d(scrOut->shards[i]->ptr, scrIn->shards[i]->ptr, scrIn->bytes(), r.stream));
+    });
+  }
+  TensorPtr idx32 = castOnDevice(idxOut, DataType::Int32);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_moe_dispatch_mask(out->shards[i]->ptr, static_cast<const int32_t *>(idx32->shards[i]->ptr),
+                                   static_cast<const int32_t *>(local->shards[i]->ptr), ttbDtype(out->dtype), rows * n, hidden,
+                                   static_cast<int>(k), static_cast<int>(experts), r.stream));
+  });
+  put(op->dispatched(), out);
+  put(op->indices(), idxOut);
+  put(op->scores(), scrOut);
+}
+
+// topk_router_gpt (operations/reduction/topk_router_gpt.cpp; golden tools/golden/mapping.py:5960-5992): router logits
+// = input @ weight (rounded to the input type) + bias (rounded), the k largest per token in descending order, and the
+// softmax over those k values.
+void Executor::runTopKRouterGpt(const fbt::TopKRouterGptOp *op) {
+  TensorPtr x = getDevice(op->input()), w = getDevice(op->weight()), bias = getDevice(op->bias());
+  TTRT_ASSERT(x->shape.size() == 2 && w->shape.size() == 2 && w->shape[0] == x->shape[1], "topk_router_gpt expects input [B, H] and weight [H, E]");
+  const int64_t B = x->shape[0], H = x->shape[1], E = w->shape[1];
+  const size_t k = static_cast<size_t>(op->k());
+  TTRT_ASSERT(bias->volume() == static_cast<size_t>(B * E) && bias->dtype == x->dtype && w->dtype == x->dtype,
+              "topk_router_gpt bias must be [B, E] in the input's data type");
+  TTRT_ASSERT(k >= 1 && static_cast<int64_t>(k) <= E, "k outside [1, experts]");
+  TensorPtr logits = makeDeviceTensor(dev, {static_cast<uint32_t>(B), static_cast<uint32_t>(E)}, x->dtype);
+  int64_t shape[2] = {B, E}, strides[2] = {E, 1};
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_gemm(x->shards[i]->ptr, w->shards[i]->ptr, nullptr, logits->shards[i]->ptr, ttbDtype(x->dtype), 0, ttbDtype(x->dtype), 1, B, E,
+                      H, 0, 0, 0, 0, TTB_ACT_NONE, 1, r.stream));
+    TTB_CALL(ttb_eltwise_binary(static_cast<int>(fbt::EltwiseBinaryOpType::Add), logits->shards[i]->ptr, ttbDtype(x->dtype),
+                                bias->shards[i]->ptr, ttbDtype(x->dtype), logits->shards[i]->ptr, ttbDtype(x->dtype), 2, shape, strides,
+                                strides, r.stream));
+  });
+  TensorPtr indices = allocOut(op->expert_indices()), weights = allocOut(op->expert_weights());
+  TTRT_ASSERT(indices->volume() == static_cast<size_t>(B) * k && weights->volume() == static_cast<size_t>(B) * k,
+              "topk_router_gpt results must be [B, k]");
+  TensorPtr top = makeDeviceTensor(dev, {static_cast<uint32_t>(B), static_cast<uint32_t>(k)}, x->dtype);
+  const size_t wsBytes = ttb_sort_workspace_bytes(static_cast<size_t>(B), static_cast<size_t>(E));
+  TensorPtr ws = makeDeviceTensor(dev, {static_cast<uint32_t>((wsBytes + 3) / 4)}, DataType::UInt32);
+  TensorPtr soft = weights->dtype == x->dtype ? weights : makeDeviceTensor(dev, top->shape, x->dtype);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_sort(logits->shards[i]->ptr, top->shards[i]->ptr, indices->shards[i]->ptr, ttbDtype(x->dtype), ttbDtype(indices->dtype),
+                      static_cast<size_t>(B), static_cast<size_t>(E), k, 1, ws->shards[i]->ptr, wsBytes, r.stream));
+    TTB_CALL(ttb_softmax(top->shards[i]->ptr, soft->shards[i]->ptr, ttbDtype(x->dtype), static_cast<size_t>(B), k, 1, r.stream));
+  });
+  put(op->expert_indices(), indices);
+  put(op->expert_weights(), soft == weights ? weights : castOnDevice(soft, weights->dtype));
 }
 
 // all_to_all_combine: expert outputs [E_local, global tokens, H] go back to the devices their tokens came from,

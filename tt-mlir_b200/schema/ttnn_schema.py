@@ -501,6 +501,15 @@ S.table("SparseMatmulOp", [
     ("a", "TensorRef"), ("b", "TensorRef"), ("sparsity", "TensorRef"), ("out", "TensorRef"), ("is_input_a_sparse", "bool"),
     ("is_input_b_sparse", "bool"), ("nnz", "i64", OPT), ("program_config", "opaque"), ("memory_config", "MemoryConfig"),
     ("dtype", "DataType"), ("compute_config", "DeviceComputeKernelConfig")])
+S.table("AllToAllDispatchMetadataOp", [
+    ("input_tensor", "TensorRef"), ("expert_indices", "TensorRef"), ("expert_scores", "TensorRef"),
+    ("expert_mapping", "TensorRef"), ("dispatched", "TensorRef"), ("indices", "TensorRef"), ("scores", "TensorRef"),
+    ("num_devices", "u32"), ("cluster_axis", "u32"), ("memory_config", "MemoryConfig"),
+    ("dispatched_buffer", "TensorRef"), ("indices_buffer", "TensorRef"), ("scores_buffer", "TensorRef"),
+    ("cross_device_semaphore", "GlobalSemaphoreRef")])
+S.table("TopKRouterGptOp", [
+    ("input", "TensorRef"), ("weight", "TensorRef"), ("bias", "TensorRef"), ("k", "i32"), ("num_experts", "i32"),
+    ("expert_indices", "TensorRef"), ("expert_weights", "TensorRef")])
 S.table("ReduceScatterOp", [
     ("in", "TensorRef"), ("out", "TensorRef"), ("scatter_dim", "i32"), ("reduce_type", "u32"),
     ("cluster_axis", "u32"), ("sub_device_id", "u8", OPT), ("memory_config", "MemoryConfig"),

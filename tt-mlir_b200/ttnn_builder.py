@@ -826,6 +826,31 @@ class ProgramBuilder:
             "memory_config": self._mc()}, [x, expert_indices, expert_mapping], [disp, meta], loc)
         return disp, meta
 
+    def all_to_all_dispatch_metadata(self, x: Value, expert_indices: Value, expert_scores: Value, expert_mapping: Value,
+                                     cluster_axis: int = 1, loc=None):
+        """x [1, 1, M, H], expert_indices / expert_scores [1, 1, M, K]; expert_mapping [1, 1, D, E] holds the owning
+        device of every expert.  Returns dispatched [1, D*M, H], indices [1, D*M, K], scores [1, D*M, K]."""
+        n = self._axis_size(cluster_axis)
+        m, h, k = x.shape[-2], x.shape[-1], expert_indices.shape[-1]
+        disp = self._value([1, n * m, h], x.dtype)
+        idx = self._value([1, n * m, k], expert_indices.dtype)
+        scr = self._value([1, n * m, k], expert_scores.dtype)
+        self._emit("AllToAllDispatchMetadataOp", {
+            "input_tensor": x.ref, "expert_indices": expert_indices.ref, "expert_scores": expert_scores.ref,
+            "expert_mapping": expert_mapping.ref, "dispatched": disp.ref, "indices": idx.ref, "scores": scr.ref,
+            "num_devices": n, "cluster_axis": cluster_axis, "memory_config": self._mc(),
+            "cross_device_semaphore": {"global_id": 0}}, [x, expert_indices, expert_scores, expert_mapping], [disp, idx, scr], loc)
+        return disp, idx, scr
+
+    def topk_router_gpt(self, x: Value, weight: Value, bias: Value, k: int, index_dtype: str = "UInt16", loc=None):
+        """x [B, H], weight [H, E], bias [B, E] -> expert_indices [B, k], expert_weights [B, k]."""
+        b, e = x.shape[0], weight.shape[1]
+        idx = self._value([b, k], index_dtype)
+        wts = self._value([b, k], x.dtype)
+        self._emit("TopKRouterGptOp", {"input": x.ref, "weight": weight.ref, "bias": bias.ref, "k": k, "num_experts": e,
+                                       "expert_indices": idx.ref, "expert_weights": wts.ref}, [x, weight, bias], [idx, wts], loc)
+        return idx, wts
+
     def all_to_all_combine(self, x: Value, expert_metadata: Value, expert_mapping: Value, num_experts_per_tok: int,
                            cluster_axis: int = 1, output_shard_dim: int = 1, loc=None) -> Value:
         """x [E_local, B*D, S, H] -> [K, B, S, H] (this device's tokens, one slice per selected expert)."""

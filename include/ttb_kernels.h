@@ -268,6 +268,25 @@ TTB_API int ttb_dropout(const void *x, void *y, int dtype, size_t n, float prob,
                         void *stream);
 /* ::ttnn::rand (operations/rand/rand.cpp): uniform values in [low, high). */
 TTB_API int ttb_rand_uniform(void *y, int dtype, size_t n, float low, float high, uint32_t seed, uint32_t stream_id, void *stream);
+/* ::ttnn::experimental::conv3d (operations/conv/conv3d.cpp): NDHWC input [n, d, h, w, c], NDHWC output, symmetric
+ * padding (zeros, or the edge value when `replicate`), no dilation.  `weight_strides5` are the weight's element strides
+ * over (out channel, in channel within the group, kd, kh, kw): [O, C/g, kD, kH, kW] tensors and TTNN's prepared
+ * [kD*kH*kW*C/g, O] matrices are both read in place.  bias [o], nullable.  A CUDA-core kernel. */
+TTB_API int ttb_conv3d(const void *x, const void *weight, const void *bias, void *y, int dtype, int n, int d, int h, int w, int c,
+                       int o, int kd, int kh, int kw, int sd, int sh, int sw, int pd, int ph, int pw, int groups, int replicate,
+                       const int64_t *weight_strides5, void *stream);
+/* ::ttnn::experimental::gelu_bw (operations/eltwise/binary/experimental_binary_backward.cpp): grad * gelu'(x). */
+TTB_API int ttb_gelu_backward(const void *grad, const void *x, void *y, int dtype, size_t n, int tanh_approx, void *stream);
+/* ::ttnn::embedding_bw (operations/embedding/embedding_backward.cpp): out[v, :] = sum of grad rows whose index is v
+ * ([vocab, dim]; f32 accumulation in `workspace`, one rounding). */
+TTB_API size_t ttb_embedding_backward_workspace_bytes(size_t vocab, size_t dim);
+TTB_API int ttb_embedding_backward(const void *indices, const void *grad, void *out, int index_dtype, int dtype, size_t rows,
+                                   size_t vocab, size_t dim, void *workspace, void *stream);
+/* ttml::metal::adamw (operations/ttml/adamw.cpp), in place on param, exp_avg, exp_avg_sq and (amsgrad, nullable)
+ * max_exp_avg_sq.  beta*_pow are beta^step.  Stochastic rounding applies to bf16 parameters. */
+TTB_API int ttb_adamw(void *param, const void *grad, void *exp_avg, void *exp_avg_sq, void *max_exp_avg_sq, int param_dtype,
+                      int grad_dtype, int moment_dtype, size_t n, float lr, float beta1, float beta2, float beta1_pow, float beta2_pow,
+                      float eps, float weight_decay, int stochastic_rounding, uint32_t seed, void *stream);
 /* ::ttnn::cumsum (operations/cumsum/cumsum.cpp): running sum along the middle dimension. */
 TTB_API int ttb_cumsum(const void *in, void *out, int dtype, size_t outer, size_t len, size_t inner,
                        void *stream);

@@ -389,6 +389,22 @@ class OracleBuilder:
         disp, meta = ops.all_to_all_dispatch(per(x), per(expert_indices), mp)
         return (OValue(disp), OValue(meta)) if isinstance(x.t, list) else (OValue(disp[0]), OValue(meta[0]))
 
+    def conv3d(self, x, w, bias, batch, depth, height, width, stride=(1, 1, 1), padding=(0, 0, 0), groups=1, padding_mode="zeros", loc=None):
+        return _map(lambda t, wt, b: ops.conv3d(t, wt, b, batch, depth, height, width, stride, padding, groups, padding_mode), x, w, bias)
+
+    def prepare_conv3d_weights(self, w, *a, **k): return w
+    def gelu_backward(self, grad, x, approximate="none", loc=None): return _map(lambda g, t: ops.gelu_backward(g, t, approximate), grad, x)
+    def embedding_backward(self, indices, weight, in_grad, loc=None):
+        return _map(lambda i, w, g: ops.embedding_backward(i, list(w.shape), g), indices, weight, in_grad)
+
+    def adamw(self, param, grad, exp_avg, exp_avg_sq, max_exp_avg_sq=None, lr=1e-3, beta1=0.9, beta2=0.999, beta1_pow=0.9, beta2_pow=0.999,
+              epsilon=1e-8, weight_decay=0.0, stochastic_rounding=False, loc=None):
+        res = ops.adamw(param.t, grad.t, exp_avg.t, exp_avg_sq.t, max_exp_avg_sq.t if max_exp_avg_sq is not None else None, lr, beta1, beta2,
+                        beta1_pow, beta2_pow, epsilon, weight_decay)
+        param.t, exp_avg.t, exp_avg_sq.t = res[0], res[1], res[2]              # updated in place
+        if max_exp_avg_sq is not None:
+            max_exp_avg_sq.t = res[3]
+
     def all_to_all_dispatch_metadata(self, x, expert_indices, expert_scores, expert_mapping, cluster_axis=1, loc=None):
         per = lambda v: v.t if isinstance(v.t, list) else [v.t]
         d, i, s_ = ops.all_to_all_dispatch_metadata(per(x), per(expert_indices), per(expert_scores), expert_mapping.first)

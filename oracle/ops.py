@@ -855,3 +855,43 @@ def topk_router_gpt(x, weight, bias, k):
     logits = torch.matmul(x.float(), weight.float()).to(x.dtype) + bias
     values, idx = torch.topk(logits, k=k, dim=-1, largest=True, sorted=True)
     return idx, torch.softmax(values.float(), dim=-1).to(x.dtype)
+
+
+def conv3d(x, w, bias, batch, depth, height, width, stride, padding, groups, padding_mode="zeros"):
+    """tools/golden/mapping.py:714-801: torch conv3d on the NCDHW view of NDHWC data, symmetric padding; "replicate"
+    repeats the edge values.  f32, one rounding; the result keeps the input's flattened / 5-D form."""
+    c = x.numel() // (batch * depth * height * width)
+    t = x.reshape(batch, depth, height, width, c).permute(0, 4, 1, 2, 3).float()
+    if padding_mode == "replicate" and any(padding):
+        t = torch.nn.functional.pad(t, (padding[2], padding[2], padding[1], padding[1], padding[0], padding[0]), mode="replicate")
+        padding = (0, 0, 0)
+    y = torch.nn.functional.conv3d(t, w.float(), bias.float().reshape(-1) if bias is not None else None, stride=tuple(stride),
+                                   padding=tuple(padding), groups=groups)
+    y = y.permute(0, 2, 3, 4, 1).contiguous()
+    return (y.reshape(1, 1, -1, y.shape[-1]) if x.ndim == 4 else y).to(x.dtype)
+
+
+def gelu_backward(grad, x, approximate="none"):
+    """tools/golden/mapping.py:4379-4383 (aten.gelu_backward), evaluated in f32, one rounding."""
+    return torch.ops.aten.gelu_backward(grad.float(), x.float(), approximate=approximate).to(x.dtype)
+
+
+def embedding_backward(indices, weight_shape, in_grad):
+    """tools/golden/mapping.py:5875-5912: index_add_ of the gradient rows into a zero table; accumulated in f32 here."""
+    vocab, dim = weight_shape[-2], weight_shape[-1]
+    acc = torch.zeros(vocab, dim)
+    acc.index_add_(0, indices.to(torch.int64).flatten(), in_grad.float().reshape(-1, dim))
+    return acc.reshape(list(weight_shape)).to(in_grad.dtype)
+
+
+def adamw(param, grad, exp_avg, exp_avg_sq, max_exp_avg_sq, lr, beta1, beta2, beta1_pow, beta2_pow, eps, weight_decay):
+    """tools/golden/mapping.py:1155-1218 (tt-train's CPUAdamW).  Returns (param, exp_avg, exp_avg_sq[, max_exp_avg_sq])."""
+    g = grad.float()
+    m = exp_avg.float() * beta1 + g * (1.0 - beta1)
+    v = exp_avg_sq.float() * beta2 + (g * g) * (1.0 - beta2)
+    vv = torch.maximum(max_exp_avg_sq.float(), v) if max_exp_avg_sq is not None else v
+    denom = torch.sqrt(vv / (1.0 - beta2_pow)) + eps
+    p = param.float()
+    r = (p - (m / (1.0 - beta1_pow)) / denom * lr) - p * (lr * weight_decay)
+    out = (r.to(param.dtype), m.to(exp_avg.dtype), v.to(exp_avg_sq.dtype))
+    return out + ((vv.to(max_exp_avg_sq.dtype),) if max_exp_avg_sq is not None else ())

@@ -524,6 +524,34 @@ def main():
     store(out, "map/moe/scores", scr)
     store(out, "map/moe/scores_gathered", scr_all.shard_at(0))
 
+    # --- conv3d, gelu backward, embedding backward, adamw (mapping.py:714-801, 4379-4383, 5875-5912, 1155-1218)
+    vx = rnd(2, 4, 5, 6, 8)                                     # NDHWC
+    vw, vb = rnd(6, 4, 2, 3, 3) * 0.3, rnd(1, 1, 1, 1, 6) * 0.1  # groups 2: [O, C/2, kD, kH, kW]
+    for n, t in (("x", vx), ("w", vw), ("b", vb)):
+        store(out, f"map/conv3d/{n}", t)
+    ndhwc = (S.IntegerAttr(0), S.IntegerAttr(1), S.IntegerAttr(2), S.IntegerAttr(3), S.IntegerAttr(4))
+    store(out, "map/conv3d/s1x2x1_p1_g2", one(ref.conv3d_golden(gmt(vx), gmt(vw), gmt(vb), S.DenseI32ArrayAttr([1, 2, 1]),
+                                                                S.DenseI32ArrayAttr([1, 1, 1]), S.IntegerAttr(2), *ndhwc, S.StringAttr("zeros"))))
+    gg, gx = rnd(5, 40), rnd(5, 40) * 2
+    store(out, "map/gelu_bw/grad", gg)
+    store(out, "map/gelu_bw/x", gx)
+    for ap in ("none", "tanh"):
+        store(out, f"map/gelu_bw/{ap}", one(ref.ttir_gelu_backward_golden(gmt(gg), gmt(gx), approximate=ap)))
+    ei = torch.randint(0, 10, (3, 7), generator=g, dtype=torch.int32)
+    eg = rnd(3, 7, 16)
+    store(out, "map/embedding_bw/indices", ei)
+    store(out, "map/embedding_bw/grad", eg)
+    store(out, "map/embedding_bw/out", one(ref.ttir_embedding_backward_golden(gmt(ei), gmt(torch.zeros(10, 16)), gmt(eg), S.F32Type())))
+    ap_, ag = rnd(6, 50), rnd(6, 50).to(torch.bfloat16)
+    am, av, amax = rnd(6, 50) * 0.1, torch.rand(6, 50, generator=g) * 0.01, torch.rand(6, 50, generator=g) * 0.01
+    for n, t in (("param", ap_), ("grad", ag), ("m", am), ("v", av), ("vmax", amax)):
+        store(out, f"map/adamw/{n}", t)
+    for tag, vm in (("plain", None), ("amsgrad", amax)):
+        res = ref.adamw_golden(gmt(ap_), gmt(ag), gmt(am), gmt(av), gmt(vm) if vm is not None else None, lr=1e-2, beta1=0.9, beta2=0.99,
+                               beta1_pow=0.9 ** 3, beta2_pow=0.99 ** 3, epsilon=1e-8, weight_decay=0.1)
+        for n, t in zip(("param", "m", "v", "vmax"), res):
+            store(out, f"map/adamw/{tag}/{n}", one(t))
+
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ttir_cpu_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes")

@@ -329,3 +329,79 @@ def test_all_to_all_dispatch_metadata_on_one_device(rt, device):
         assert torch.equal(g, w_)
     routed = (sel % 2 == 0).any(-1).reshape(1, 24, 1)
     assert torch.equal(got[0], torch.where(routed, x.reshape(1, 24, 64), torch.zeros(1, 24, 64).to(torch.bfloat16)))
+
+
+def test_conv3d_matches_the_reference_golden(rt, device, golden):
+    x, w, b_ = (golden[f"map/conv3d/{n}"] for n in ("x", "w", "b"))
+    kw = dict(stride=(1, 2, 1), padding=(1, 1, 1), groups=2)
+    got, want = run_body(rt, device, lambda b, xv, wv, bv: b.conv3d(xv, wv, bv, 2, 4, 5, 6, **kw), [x, w, b_])
+    ref = golden["map/conv3d/s1x2x1_p1_g2"]
+    assert got[0].shape == ref.shape and torch.allclose(got[0], ref, rtol=1e-5, atol=1e-5) and torch.allclose(got[0], want[0], rtol=1e-5, atol=1e-5)
+    # flattened activations, prepared weights (carried through unchanged), replicate padding, bf16
+    bf = torch.bfloat16
+    xf = x.reshape(1, 1, -1, 8).to(bf)
+    got, want = run_body(rt, device, lambda b, xv, wv, bv: b.conv3d(xv, b.prepare_conv3d_weights(wv, groups=2), bv, 2, 4, 5, 6,
+                                                                   padding=(1, 1, 1), groups=2, padding_mode="replicate"),
+                         [xf, w.to(bf), b_.to(bf)])
+    assert list(got[0].shape) == [1, 1, 2 * 5 * 5 * 6, 6]
+    assert_matches(got[0], want[0], "conv3d bf16 replicate", (0.9999, 2e-2, 2.0 ** -6))
+    # TTNN's prepared weight matrix [kD*kH*kW*C, O] handed to conv3d directly (groups 1)
+    w1 = (torch.randn(6, 8, 2, 3, 3, generator=torch.Generator().manual_seed(3)) * 0.2)
+    prepared = w1.permute(2, 3, 4, 1, 0).reshape(2 * 3 * 3 * 8, 6).contiguous()
+
+    def body(b, xv, wv):
+        wv.filter_shape = [6, 8, 2, 3, 3]
+        return b.conv3d(xv, wv, None, 2, 4, 5, 6, padding=(0, 1, 1))
+    got = run_gpu(rt, device, body, [x, prepared])
+    import oracle.ops as O
+    assert torch.allclose(got[0], O.conv3d(x, w1, None, 2, 4, 5, 6, (1, 1, 1), (0, 1, 1), 1), rtol=1e-5, atol=1e-5)
+
+
+def test_gelu_backward_and_embedding_backward(rt, device, golden):
+    gg, gx = golden["map/gelu_bw/grad"], golden["map/gelu_bw/x"]
+    got, want = run_body(rt, device, lambda b, g, x: (b.gelu_backward(g, x), b.gelu_backward(g, x, "tanh")), [gg, gx])
+    for g, name in zip(got, ("none", "tanh")):
+        assert torch.allclose(g, golden[f"map/gelu_bw/{name}"], rtol=2e-5, atol=2e-6), name
+    got, want = run_body(rt, device, lambda b, g, x: b.gelu_backward(g, x), [gg.to(torch.bfloat16), gx.to(torch.bfloat16)])
+    assert_matches(got[0], want[0], "gelu_bw bf16", (0.9999, 1e-2, 2.0 ** -7))
+    ei, eg = golden["map/embedding_bw/indices"], golden["map/embedding_bw/grad"]
+    table = torch.zeros(10, 16)
+    got, want = run_body(rt, device, lambda b, i, w, g: b.embedding_backward(i, w, g), [ei, table, eg])
+    assert torch.allclose(got[0], golden["map/embedding_bw/out"], rtol=1e-5, atol=1e-6) and torch.allclose(got[0], want[0], rtol=1e-5, atol=1e-6)
+    torch.manual_seed(16)
+    big_i = torch.randint(0, 1000, (4, 512), dtype=torch.int32)
+    big_g = torch.randn(4, 512, 128).to(torch.bfloat16)
+    got, want = run_body(rt, device, lambda b, i, w, g: b.embedding_backward(i, w, g), [big_i, torch.zeros(1000, 128).to(torch.bfloat16), big_g])
+    assert_matches(got[0], want[0], "embedding_bw bf16", (0.9999, 2e-2, 2.0 ** -6))
+
+
+def test_adamw_matches_the_reference_golden(rt, device, golden):
+    p, g, m, v, vmax = (golden[f"map/adamw/{n}"] for n in ("param", "grad", "m", "v", "vmax"))
+    hp = dict(lr=1e-2, beta1=0.9, beta2=0.99, beta1_pow=0.9 ** 3, beta2_pow=0.99 ** 3, epsilon=1e-8, weight_decay=0.1)
+
+    def plain(b, pv, gv, mv, vv):
+        b.adamw(pv, gv, mv, vv, **hp)
+        return b.assign(pv), b.assign(mv), b.assign(vv)
+
+    def ams(b, pv, gv, mv, vv, xv):
+        b.adamw(pv, gv, mv, vv, xv, **hp)
+        return b.assign(pv), b.assign(mv), b.assign(vv), b.assign(xv)
+    got, want = run_body(rt, device, plain, [p, g, m, v])
+    for t, w_, n in zip(got, want, ("param", "m", "v")):
+        assert torch.allclose(t, golden[f"map/adamw/plain/{n}"], rtol=1e-5, atol=1e-7) and torch.allclose(t, w_, rtol=1e-5, atol=1e-7), n
+    got, want = run_body(rt, device, ams, [p, g, m, v, vmax])
+    for t, n in zip(got, ("param", "m", "v", "vmax")):
+        assert torch.allclose(t, golden[f"map/adamw/amsgrad/{n}"], rtol=1e-5, atol=1e-7), n
+    # bf16 parameters: round to nearest, then stochastic rounding (unbiased: the mean of many draws approaches the f32 value)
+    bf = torch.bfloat16
+    pb = torch.full((64, 1024), 1.0).to(bf)
+    gb = torch.full((64, 1024), 0.37).to(bf)
+    zeros = torch.zeros(64, 1024)
+
+    def step(b, pv, gv, mv, vv, stochastic):
+        b.adamw(pv, gv, mv, vv, lr=1e-3, beta1=0.9, beta2=0.999, beta1_pow=0.9, beta2_pow=0.999, stochastic_rounding=stochastic)
+        return b.assign(pv)
+    near = run_gpu(rt, device, lambda b, *v: step(b, *v, False), [pb, gb, zeros, zeros.clone()])[0]
+    assert torch.equal(near, torch.full((64, 1024), 0.999).to(bf))       # 1 - 1e-3 rounds to the nearest bf16 (0.99609375 or 1.0)
+    rnd = run_gpu(rt, device, lambda b, *v: step(b, *v, True), [pb, gb, zeros, zeros.clone()])[0].float()
+    assert set(rnd.unique().tolist()) <= {0.99609375, 1.0} and abs(rnd.mean().item() - 0.999) < 2e-4

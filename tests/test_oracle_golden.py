@@ -386,6 +386,26 @@ def test_dispatch_metadata_and_router(golden):
     assert torch.equal(ridx.to(torch.int32), golden["map/router/indices"]) and torch.equal(rw, golden["map/router/weights"])
 
 
+def test_conv3d_gelu_backward_embedding_backward_adamw(golden):
+    """Restatements against the reference's goldens (tools/golden/mapping.py:714-801, 4379-4383, 5875-5912, 1155-1218)."""
+    x, w, b = (golden[f"map/conv3d/{n}"] for n in ("x", "w", "b"))
+    got = ops.conv3d(x, w, b, 2, 4, 5, 6, (1, 2, 1), (1, 1, 1), 2)
+    assert torch.allclose(got, golden["map/conv3d/s1x2x1_p1_g2"], rtol=1e-5, atol=1e-5) and got.shape == golden["map/conv3d/s1x2x1_p1_g2"].shape
+    rep = ops.conv3d(x, w, b, 2, 4, 5, 6, (1, 1, 1), (1, 1, 1), 2, "replicate")
+    padded = torch.nn.functional.pad(x.permute(0, 4, 1, 2, 3), (1,) * 6, mode="replicate").permute(0, 2, 3, 4, 1).contiguous()
+    assert torch.allclose(rep, ops.conv3d(padded, w, b, 2, 6, 7, 8, (1, 1, 1), (0, 0, 0), 2), rtol=1e-6, atol=1e-6)
+    gg, gx = golden["map/gelu_bw/grad"], golden["map/gelu_bw/x"]
+    for ap in ("none", "tanh"):
+        assert torch.equal(ops.gelu_backward(gg, gx, ap), golden[f"map/gelu_bw/{ap}"])
+    assert torch.allclose(ops.embedding_backward(golden["map/embedding_bw/indices"], [10, 16], golden["map/embedding_bw/grad"]),
+                          golden["map/embedding_bw/out"], rtol=1e-6, atol=1e-6)
+    p, g, m, v, vmax = (golden[f"map/adamw/{n}"] for n in ("param", "grad", "m", "v", "vmax"))
+    for tag, vm in (("plain", None), ("amsgrad", vmax)):
+        res = ops.adamw(p, g, m, v, vm, 1e-2, 0.9, 0.99, 0.9 ** 3, 0.99 ** 3, 1e-8, 0.1)
+        for n, t in zip(("param", "m", "v", "vmax"), res):
+            assert torch.allclose(t, golden[f"map/adamw/{tag}/{n}"], rtol=1e-6, atol=1e-7), (tag, n)
+
+
 def test_layer_norm(golden):
     x, w, b = golden["ln/x"], golden["ln/w"], golden["ln/b"]
     assert same(ops.layer_norm(x), golden["ln/plain"])

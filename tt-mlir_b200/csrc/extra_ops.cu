@@ -354,6 +354,131 @@ __global__ void __launch_bounds__(256) randKernel(T *__restrict__ y, size_t n, f
   }
 }
 
+
+// conv3d on NDHWC activations (::ttnn::experimental::conv3d, operations/conv/conv3d.cpp; golden
+// tools/golden/mapping.py:714-801, torch conv3d with symmetric padding, "zeros" or "replicate").  The weight is read
+// through element strides over (o, c, kd, kh, kw), so both the framework layout [O, C/g, kD, kH, kW] and TTNN's
+// prepared [kD*kH*kW*C/g, O] matrix are taken as they are.  One thread per output value, f32 accumulation, one
+// rounding.  A CUDA-core kernel: the op is rare in the graphs this runtime is measured on.
+struct Conv3dGeom {
+  int n, d, h, w, c, o, kd, kh, kw, sd, sh, sw, pd, ph, pw, od, oh, ow, groups, replicate;
+  long long wo, wc, wkd, wkh, wkw; // weight strides in elements
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) conv3dKernel(const T *__restrict__ x, const T *__restrict__ wgt, const T *__restrict__ bias,
+                                                    T *__restrict__ y, Conv3dGeom g) {
+  const size_t total = static_cast<size_t>(g.n) * g.od * g.oh * g.ow * g.o;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  const int cg = g.c / g.groups, og = g.o / g.groups;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int oc = static_cast<int>(i % g.o);
+    size_t p = i / g.o;
+    const int ox = static_cast<int>(p % g.ow);
+    p /= g.ow;
+    const int oy = static_cast<int>(p % g.oh);
+    p /= g.oh;
+    const int oz = static_cast<int>(p % g.od);
+    const int img = static_cast<int>(p / g.od);
+    const int c0 = (oc / og) * cg;
+    float acc = bias ? toF32(bias[oc]) : 0.0f;
+    for (int kz = 0; kz < g.kd; ++kz) {
+      int iz = oz * g.sd - g.pd + kz;
+      if (g.replicate) iz = min(max(iz, 0), g.d - 1);
+      if (iz < 0 || iz >= g.d) continue;
+      for (int ky = 0; ky < g.kh; ++ky) {
+        int iy = oy * g.sh - g.ph + ky;
+        if (g.replicate) iy = min(max(iy, 0), g.h - 1);
+        if (iy < 0 || iy >= g.h) continue;
+        for (int kx = 0; kx < g.kw; ++kx) {
+          int ix = ox * g.sw - g.pw + kx;
+          if (g.replicate) ix = min(max(ix, 0), g.w - 1);
+          if (ix < 0 || ix >= g.w) continue;
+          const T *xp = x + (((static_cast<size_t>(img) * g.d + iz) * g.h + iy) * g.w + ix) * g.c + c0;
+          const T *wp = wgt + oc * g.wo + kz * g.wkd + ky * g.wkh + kx * g.wkw;
+          for (int c = 0; c < cg; ++c) acc = fmaf(toF32(xp[c]), toF32(wp[c * g.wc]), acc);
+        }
+      }
+    }
+    y[i] = fromF32<T>(acc);
+  }
+}
+
+// gelu_bw (::ttnn::experimental::gelu_bw, operations/eltwise/binary/experimental_binary_backward.cpp; golden
+// mapping.py:4379-4383, aten.gelu_backward): grad * d/dx gelu(x), exact (erf) or the tanh approximation.
+template <typename T>
+__global__ void __launch_bounds__(256) geluBackwardKernel(const T *__restrict__ grad, const T *__restrict__ x, T *__restrict__ y, size_t n,
+                                                          int tanhApprox) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float v = toF32(x[i]);
+    float d;
+    if (tanhApprox) {
+      const float kBeta = 0.79788456080286535588f * 0.044715f, kAlpha = 0.79788456080286535588f; // sqrt(2 / pi)
+      const float inner = kAlpha * v + kBeta * v * v * v;
+      const float t = tanhf(inner);
+      d = 0.5f * (1.0f + t) + 0.5f * v * (1.0f - t * t) * (kAlpha + 3.0f * kBeta * v * v);
+    } else {
+      const float cdf = 0.5f * (1.0f + erff(v * 0.70710678118654752440f));
+      const float pdf = 0.39894228040143267794f * expf(-0.5f * v * v);
+      d = cdf + v * pdf;
+    }
+    y[i] = fromF32<T>(toF32(grad[i]) * d);
+  }
+}
+
+// embedding_bw (::ttnn::embedding_bw, operations/embedding/embedding_backward.cpp; golden mapping.py:5875-5912,
+// index_add_ of the gradient rows into a zero table): rows are accumulated in f32 (atomics, so the order of equal
+// indices is not fixed) and rounded to the result type once.
+template <typename T, typename I>
+__global__ void __launch_bounds__(256) embeddingBackwardAccumulate(const I *__restrict__ idx, const T *__restrict__ grad, float *__restrict__ acc,
+                                                                   size_t rows, size_t dim, size_t vocab) {
+  const size_t total = rows * dim, stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long r = static_cast<long long>(idx[i / dim]);
+    if (r < 0 || static_cast<size_t>(r) >= vocab) continue;
+    atomicAdd(acc + static_cast<size_t>(r) * dim + i % dim, toF32(grad[i]));
+  }
+}
+template <typename T> __global__ void __launch_bounds__(256) roundFromF32Kernel(const float *__restrict__ in, T *__restrict__ out, size_t n) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = fromF32<T>(in[i]);
+}
+
+// adamw (ttml::metal::adamw, operations/ttml/adamw.cpp; golden mapping.py:1155-1218, tt-train's CPUAdamW), in place:
+//   m = b1 m + (1 - b1) g;  v = b2 v + (1 - b2) g^2;  [vmax = max(vmax, v)]
+//   p = p - lr (m / (1 - b1^t)) / (sqrt(v / (1 - b2^t)) + eps) - lr wd p
+// f32 arithmetic; the parameter is stored with round-to-nearest or, with stochastic rounding, by adding 16 random bits
+// below a bf16's last place and truncating (Philox keyed by seed and element).
+template <typename P, typename G, typename M>
+__global__ void __launch_bounds__(256) adamwKernel(P *__restrict__ param, const G *__restrict__ grad, M *__restrict__ m, M *__restrict__ v,
+                                                   M *__restrict__ vmax, size_t n, float lr, float b1, float b2, float b1pow, float b2pow,
+                                                   float eps, float wd, int stochastic, uint32_t seed) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  const float c1 = 1.0f - b1pow, c2 = 1.0f - b2pow;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float g = toF32(grad[i]), p = toF32(param[i]);
+    const float mi = toF32(m[i]) * b1 + g * (1.0f - b1);
+    const float vi = toF32(v[i]) * b2 + (g * g) * (1.0f - b2);
+    m[i] = fromF32<M>(mi);
+    v[i] = fromF32<M>(vi);
+    float vv = vi;
+    if (vmax) {
+      vv = fmaxf(toF32(vmax[i]), vi);
+      vmax[i] = fromF32<M>(vv);
+    }
+    const float denom = sqrtf(vv / c2) + eps;
+    const float r = (p - (mi / c1) / denom * lr) - p * (lr * wd);
+    if (stochastic && std::is_same<P, __nv_bfloat16>::value) {
+      const uint4 rnd = philox4x32(make_uint4(static_cast<uint32_t>(i), static_cast<uint32_t>(i >> 32), 0, 0), make_uint2(seed, 0x6164616Du));
+      const uint32_t bits = __float_as_uint(r) + (rnd.x & 0xffffu);
+      param[i] = fromF32<P>(__uint_as_float(bits & 0xffff0000u));
+    } else {
+      param[i] = fromF32<P>(r);
+    }
+  }
+}
+
 } // namespace ttb
 
 using namespace ttb;
@@ -589,6 +714,99 @@ int ttb_rand_uniform(void *y, int dtype, size_t n, float low, float high, uint32
   const int bitsUsed = dtype == kF32 ? 24 : (dtype == kBF16 ? 8 : 11);
   TTB_DISPATCH_FLOAT(dtype, T,
                      (randKernel<T><<<gridFor((n + 3) / 4, 256), 256, 0, st>>>(static_cast<T *>(y), n, low, high, seed, stream_id, bitsUsed)));
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_conv3d(const void *x, const void *weight, const void *bias, void *y, int dtype, int n, int d, int h, int w, int c, int o, int kd,
+               int kh, int kw, int sd, int sh, int sw, int pd, int ph, int pw, int groups, int replicate, const int64_t *weight_strides5,
+               void *stream) {
+  TTB_CHECK(x && weight && y && weight_strides5, "null tensor");
+  TTB_CHECK(kd > 0 && kh > 0 && kw > 0 && sd > 0 && sh > 0 && sw > 0 && pd >= 0 && ph >= 0 && pw >= 0, "bad convolution window");
+  TTB_CHECK(groups > 0 && c % groups == 0 && o % groups == 0, "channels do not divide into the groups");
+  Conv3dGeom g;
+  g.n = n; g.d = d; g.h = h; g.w = w; g.c = c; g.o = o; g.kd = kd; g.kh = kh; g.kw = kw; g.sd = sd; g.sh = sh; g.sw = sw;
+  g.pd = pd; g.ph = ph; g.pw = pw; g.groups = groups; g.replicate = replicate;
+  g.od = (d + 2 * pd - kd) / sd + 1;
+  g.oh = (h + 2 * ph - kh) / sh + 1;
+  g.ow = (w + 2 * pw - kw) / sw + 1;
+  TTB_CHECK(g.od > 0 && g.oh > 0 && g.ow > 0, "the kernel does not fit the padded input");
+  g.wo = weight_strides5[0]; g.wc = weight_strides5[1]; g.wkd = weight_strides5[2]; g.wkh = weight_strides5[3]; g.wkw = weight_strides5[4];
+  const size_t total = static_cast<size_t>(n) * g.od * g.oh * g.ow * o;
+  if (total == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("conv3d", 2.0 * double(total) * kd * kh * kw * (c / groups), double(total) * dtypeSize(dtype), st);
+  TTB_DISPATCH_FLOAT(dtype, T,
+                     (conv3dKernel<T><<<gridFor(total, 256), 256, 0, st>>>(static_cast<const T *>(x), static_cast<const T *>(weight),
+                                                                          static_cast<const T *>(bias), static_cast<T *>(y), g)));
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_gelu_backward(const void *grad, const void *x, void *y, int dtype, size_t n, int tanh_approx, void *stream) {
+  TTB_CHECK(grad && x && y, "null tensor");
+  if (n == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("gelu_backward", 0, double(n) * 3 * dtypeSize(dtype), st);
+  TTB_DISPATCH_FLOAT(dtype, T,
+                     (geluBackwardKernel<T><<<gridFor(n, 256), 256, 0, st>>>(static_cast<const T *>(grad), static_cast<const T *>(x),
+                                                                            static_cast<T *>(y), n, tanh_approx)));
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+size_t ttb_embedding_backward_workspace_bytes(size_t vocab, size_t dim) { return vocab * dim * sizeof(float); }
+
+int ttb_embedding_backward(const void *indices, const void *grad, void *out, int index_dtype, int dtype, size_t rows, size_t vocab,
+                           size_t dim, void *workspace, void *stream) {
+  TTB_CHECK(indices && grad && out && workspace, "null tensor");
+  if (vocab * dim == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("embedding_backward", 0, double(rows) * dim * dtypeSize(dtype) + double(vocab) * dim * (8 + dtypeSize(dtype)), st);
+  float *acc = static_cast<float *>(workspace);
+  TTB_CUDA(cudaMemsetAsync(acc, 0, vocab * dim * sizeof(float), st));
+  if (rows != 0 && dim != 0) {
+#define TTB_EMB_BW(I)                                                                                                        \
+    TTB_DISPATCH_FLOAT(dtype, T,                                                                                             \
+                       (embeddingBackwardAccumulate<T, I><<<gridFor(rows * dim, 256), 256, 0, st>>>(                         \
+                           static_cast<const I *>(indices), static_cast<const T *>(grad), acc, rows, dim, vocab)))
+    switch (index_dtype) {
+    case kI32: TTB_EMB_BW(int32_t); break;
+    case kU32: TTB_EMB_BW(uint32_t); break;
+    case kU16: TTB_EMB_BW(uint16_t); break;
+    default: setLastError("embedding_backward: indices must be Int32, UInt32 or UInt16"); return TTB_ERR_UNSUPPORTED;
+    }
+#undef TTB_EMB_BW
+    countLaunch();
+  }
+  TTB_DISPATCH_FLOAT(dtype, T, (roundFromF32Kernel<T><<<gridFor(vocab * dim, 256), 256, 0, st>>>(acc, static_cast<T *>(out), vocab * dim)));
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+int ttb_adamw(void *param, const void *grad, void *exp_avg, void *exp_avg_sq, void *max_exp_avg_sq, int param_dtype, int grad_dtype,
+              int moment_dtype, size_t n, float lr, float beta1, float beta2, float beta1_pow, float beta2_pow, float eps,
+              float weight_decay, int stochastic_rounding, uint32_t seed, void *stream) {
+  TTB_CHECK(param && grad && exp_avg && exp_avg_sq, "null tensor");
+  TTB_CHECK(beta1_pow != 1.0f && beta2_pow != 1.0f, "bias corrections of step 0 divide by zero");
+  if (n == 0) return TTB_OK;
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("adamw", 0, double(n) * (2 * dtypeSize(param_dtype) + dtypeSize(grad_dtype) + 4 * dtypeSize(moment_dtype)), st);
+  const int grid = gridFor(n, 256);
+#define TTB_ADAMW(P, G, M)                                                                                                   \
+  adamwKernel<P, G, M><<<grid, 256, 0, st>>>(static_cast<P *>(param), static_cast<const G *>(grad), static_cast<M *>(exp_avg),        \
+                                             static_cast<M *>(exp_avg_sq), static_cast<M *>(max_exp_avg_sq), n, lr, beta1, beta2,    \
+                                             beta1_pow, beta2_pow, eps, weight_decay, stochastic_rounding, seed)
+  if (param_dtype == kBF16 && grad_dtype == kBF16 && moment_dtype == kF32) TTB_ADAMW(__nv_bfloat16, __nv_bfloat16, float);
+  else if (param_dtype == kBF16 && grad_dtype == kBF16 && moment_dtype == kBF16) TTB_ADAMW(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+  else if (param_dtype == kF32 && grad_dtype == kF32 && moment_dtype == kF32) TTB_ADAMW(float, float, float);
+  else if (param_dtype == kF32 && grad_dtype == kBF16 && moment_dtype == kF32) TTB_ADAMW(float, __nv_bfloat16, float);
+  else { setLastError("adamw: unsupported combination of parameter / gradient / moment types"); return TTB_ERR_UNSUPPORTED; }
+#undef TTB_ADAMW
   countLaunch();
   TTB_LAUNCH_CHECK();
   return TTB_OK;

@@ -122,6 +122,44 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     pushRef(outs, o->metadata());
     break;
   }
+  case OpType::Conv3dOp: {
+    const auto *o = op->type_as_Conv3dOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->weight());
+    pushRef(ins, o->bias());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::PrepareConv3dWeightsOp: {
+    const auto *o = op->type_as_PrepareConv3dWeightsOp();
+    pushRef(ins, o->weight_tensor());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::ExperimentalEltwiseBinaryBackwardOp: {
+    const auto *o = op->type_as_ExperimentalEltwiseBinaryBackwardOp();
+    pushRef(ins, o->grad());
+    pushRef(ins, o->input());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::EmbeddingBackwardOp: {
+    const auto *o = op->type_as_EmbeddingBackwardOp();
+    pushRef(ins, o->input());
+    pushRef(ins, o->weight());
+    pushRef(ins, o->in_grad());
+    pushRef(outs, o->out());
+    break;
+  }
+  case OpType::AdamWOp: {
+    const auto *o = op->type_as_AdamWOp();
+    pushRef(ins, o->param());
+    pushRef(ins, o->grad());
+    pushRef(ins, o->exp_avg());
+    pushRef(ins, o->exp_avg_sq());
+    pushRef(ins, o->max_exp_avg_sq());
+    break;
+  }
   case OpType::AllToAllDispatchMetadataOp: {
     const auto *o = op->type_as_AllToAllDispatchMetadataOp();
     pushRef(ins, o->input_tensor());
@@ -816,6 +854,10 @@ private:
   // expert ownership of this process's mesh coordinates: localIdx tensors (Int32 [experts]) from a [1, 1, E, D] mapping
   TensorPtr moeLocalIndex(const TensorPtr &mapping, uint32_t &experts, uint32_t &devices);
   void runAllToAllDispatch(const fbt::AllToAllDispatchOp *op);
+  void runConv3d(const fbt::Conv3dOp *op);
+  void runGeluBackward(const fbt::ExperimentalEltwiseBinaryBackwardOp *op);
+  void runEmbeddingBackward(const fbt::EmbeddingBackwardOp *op);
+  void runAdamW(const fbt::AdamWOp *op);
   void runAllToAllDispatchMetadata(const fbt::AllToAllDispatchMetadataOp *op);
   void runTopKRouterGpt(const fbt::TopKRouterGptOp *op);
   void runAllToAllCombine(const fbt::AllToAllCombineOp *op);
@@ -1193,6 +1235,15 @@ size_t Executor::runOp(size_t i) {
   case OpType::CumSumOp: runCumSum(op->type_as_CumSumOp()); break;
   case OpType::CumProdOp: runCumProd(op->type_as_CumProdOp()); break;
   case OpType::AllToAllDispatchOp: runAllToAllDispatch(op->type_as_AllToAllDispatchOp()); break;
+  case OpType::Conv3dOp: runConv3d(op->type_as_Conv3dOp()); break;
+  case OpType::PrepareConv3dWeightsOp: {
+    const auto *o = op->type_as_PrepareConv3dWeightsOp();
+    runPrepareConv2d(o->weight_tensor(), o->out());
+    break;
+  }
+  case OpType::ExperimentalEltwiseBinaryBackwardOp: runGeluBackward(op->type_as_ExperimentalEltwiseBinaryBackwardOp()); break;
+  case OpType::EmbeddingBackwardOp: runEmbeddingBackward(op->type_as_EmbeddingBackwardOp()); break;
+  case OpType::AdamWOp: runAdamW(op->type_as_AdamWOp()); break;
   case OpType::AllToAllDispatchMetadataOp: runAllToAllDispatchMetadata(op->type_as_AllToAllDispatchMetadataOp()); break;
   case OpType::TopKRouterGptOp: runTopKRouterGpt(op->type_as_TopKRouterGptOp()); break;
   case OpType::AllToAllCombineOp: runAllToAllCombine(op->type_as_AllToAllCombineOp()); break;
@@ -2773,6 +2824,100 @@ void Executor::runReductionProd(const fbt::ReductionProdOp *op) {
 }
 
 // group_norm on channels-last [N, 1, H*W, C] (or [N, H, W, C]): operations/normalization/group_norm.cpp.
+// conv3d over flattened NDHWC activations.  The weight is either the framework's [O, C/g, kD, kH, kW] (also what a
+// prepare_conv3d_weights result carries) or TTNN's prepared matrix [kD*kH*kW*C/g, O].
+void Executor::runConv3d(const fbt::Conv3dOp *op) {
+  TensorPtr x = getDevice(op->input()), w = getDevice(op->weight());
+  TensorPtr bias = op->bias() ? getDevice(op->bias()) : nullptr;
+  if (w->preparedFrom) w = w->preparedFrom;
+  TensorPtr out = allocOut(op->out());
+  auto three = [](const fb::Vector<int32_t> *v, const char *what, int (&r)[3]) {
+    TTRT_ASSERT(v && v->size() == 3, "conv3d ", what, " must have 3 entries");
+    for (int i = 0; i < 3; ++i) r[i] = v->Get(i);
+  };
+  int k[3], st[3], pd[3];
+  three(op->kernel_size(), "kernel_size", k);
+  three(op->stride(), "stride", st);
+  three(op->padding(), "padding", pd);
+  const int N = static_cast<int>(op->batch_size()), D = static_cast<int>(op->input_depth()), H = static_cast<int>(op->input_height()),
+            W = static_cast<int>(op->input_width()), C = static_cast<int>(op->in_channels()), O = static_cast<int>(op->out_channels());
+  const int groups = static_cast<int>(op->groups()), cg = C / std::max(groups, 1);
+  TTRT_ASSERT(x->volume() == static_cast<size_t>(N) * D * H * W * C, "conv3d input has ", x->volume(), " elements, the op says ", N, "x", D,
+              "x", H, "x", W, "x", C);
+  TTRT_ASSERT(x->dtype == w->dtype && x->dtype == out->dtype && (!bias || (bias->dtype == x->dtype && bias->volume() == static_cast<size_t>(O))),
+              "conv3d tensors must share one data type");
+  const std::string mode = op->padding_mode() ? op->padding_mode()->str() : "zeros";
+  TTRT_ASSERT(mode == "zeros" || mode == "replicate", "conv3d padding mode ", mode, " is not supported");
+  const size_t taps = static_cast<size_t>(k[0]) * k[1] * k[2];
+  TTRT_ASSERT(w->volume() == taps * cg * O, "conv3d weight has ", w->volume(), " elements, expected ", taps * cg * O);
+  int64_t ws[5];
+  if (w->shape.size() == 5) { // [O, C/g, kD, kH, kW]
+    ws[0] = static_cast<int64_t>(cg) * taps; ws[1] = static_cast<int64_t>(taps); ws[2] = k[1] * k[2]; ws[3] = k[2]; ws[4] = 1;
+  } else {                    // [kD*kH*kW*C/g, O]
+    ws[0] = 1; ws[1] = O; ws[2] = static_cast<int64_t>(k[1]) * k[2] * cg * O; ws[3] = static_cast<int64_t>(k[2]) * cg * O; ws[4] = static_cast<int64_t>(cg) * O;
+  }
+  const int od = (D + 2 * pd[0] - k[0]) / st[0] + 1, oh = (H + 2 * pd[1] - k[1]) / st[1] + 1, ow = (W + 2 * pd[2] - k[2]) / st[2] + 1;
+  TTRT_ASSERT(out->volume() == static_cast<size_t>(N) * od * oh * ow * O, "conv3d result has ", out->volume(), " elements, expected ", N, "x",
+              od, "x", oh, "x", ow, "x", O);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_conv3d(x->shards[i]->ptr, w->shards[i]->ptr, bias ? bias->shards[i]->ptr : nullptr, out->shards[i]->ptr, ttbDtype(x->dtype), N,
+                        D, H, W, C, O, k[0], k[1], k[2], st[0], st[1], st[2], pd[0], pd[1], pd[2], groups, mode == "replicate" ? 1 : 0, ws,
+                        r.stream));
+  });
+  put(op->out(), out);
+}
+
+void Executor::runGeluBackward(const fbt::ExperimentalEltwiseBinaryBackwardOp *op) {
+  TTRT_ASSERT(op->type() == fbt::ExperimentalEltwiseBinaryBackwardOpType::GeluBW, "unknown backward op");
+  TensorPtr grad = getDevice(op->grad()), x = getDevice(op->input());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(grad->volume() == x->volume() && out->volume() == x->volume() && grad->dtype == x->dtype && out->dtype == x->dtype,
+              "gelu_bw operands must have one shape and data type");
+  const std::string approx = op->approximate() ? op->approximate()->str() : "none";
+  TTRT_ASSERT(approx == "none" || approx == "tanh", "gelu_bw approximation ", approx, " is not supported");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_gelu_backward(grad->shards[i]->ptr, x->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(x->dtype), x->volume(),
+                               approx == "tanh" ? 1 : 0, r.stream));
+  });
+  put(op->out(), out);
+}
+
+void Executor::runEmbeddingBackward(const fbt::EmbeddingBackwardOp *op) {
+  TensorPtr idx = getDevice(op->input()), grad = getDevice(op->in_grad());
+  TensorPtr out = allocOut(op->out());
+  std::vector<uint32_t> ws = refShape(op->weight()); // only the table's shape matters
+  TTRT_ASSERT(ws.size() >= 2, "embedding table needs two dimensions");
+  const size_t dim = ws.back(), vocab = ws[ws.size() - 2], rows = idx->volume();
+  TTRT_ASSERT(grad->volume() == rows * dim && out->volume() == vocab * dim && out->dtype == grad->dtype,
+              "embedding_bw: the gradient must be [indices, ", dim, "] and the result [", vocab, ", ", dim, "]");
+  const size_t wsBytes = ttb_embedding_backward_workspace_bytes(vocab, dim);
+  TensorPtr scratch = makeDeviceTensor(dev, {static_cast<uint32_t>(vocab), static_cast<uint32_t>(dim)}, DataType::Float32);
+  (void)wsBytes;
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_embedding_backward(idx->shards[i]->ptr, grad->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(idx->dtype), ttbDtype(grad->dtype),
+                                    rows, vocab, dim, scratch->shards[i]->ptr, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// adamw updates the parameter and the moments in place (operations/ttml/adamw.cpp); the op has no result.
+void Executor::runAdamW(const fbt::AdamWOp *op) {
+  TensorPtr p = getDevice(op->param()), g = getDevice(op->grad()), m = getDevice(op->exp_avg()), v = getDevice(op->exp_avg_sq());
+  TensorPtr vmax = op->max_exp_avg_sq() ? getDevice(op->max_exp_avg_sq()) : nullptr;
+  const size_t n = p->volume();
+  TTRT_ASSERT(g->volume() == n && m->volume() == n && v->volume() == n && (!vmax || vmax->volume() == n) && v->dtype == m->dtype &&
+                  (!vmax || vmax->dtype == m->dtype),
+              "adamw tensors must have the parameter's shape and the moments one data type");
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_adamw(p->shards[i]->ptr, g->shards[i]->ptr, m->shards[i]->ptr, v->shards[i]->ptr, vmax ? vmax->shards[i]->ptr : nullptr,
+                       ttbDtype(p->dtype), ttbDtype(g->dtype), ttbDtype(m->dtype), n, op->lr(), op->beta1(), op->beta2(), op->beta1_pow(),
+                       op->beta2_pow(), op->epsilon(), op->weight_decay(), op->stochastic_rounding() ? 1 : 0,
+                       static_cast<uint32_t>(curOp) * 2654435761u + r.meshRank, r.stream));
+  });
+  for (const TensorPtr &t : {p, m, v}) t->version = TensorImpl::nextTensorVersion();
+  if (vmax) vmax->version = TensorImpl::nextTensorVersion();
+}
+
 // ---- mixture of experts ---------------------------------------------------------------------------
 TensorPtr Executor::moeLocalIndex(const TensorPtr &mappingIn, uint32_t &experts, uint32_t &devices) {
   TTRT_ASSERT(mappingIn->shape.size() >= 2, "expert_mapping must be [1, 1, experts, devices]");

@@ -356,6 +356,26 @@ S.table("ResetGlobalSemaphoreOp", [("semaphore", "GlobalSemaphoreRef"), ("value"
 S.table("AllocateMoeComputeSemaphoreOp", [
     ("core_range_set", "opaque"), ("output_height_shard_dim", "u32"), ("hidden_size", "u32"), ("initial_value", "u32", OPT),
     ("out", "GlobalSemaphoreRef")])
+S.table("Conv3dOp", [
+    ("input", "TensorRef"), ("weight", "TensorRef"), ("bias", "TensorRef"), ("out", "TensorRef"), ("device", "DeviceRef"),
+    ("in_channels", "u32"), ("out_channels", "u32"), ("batch_size", "u32"), ("input_depth", "u32"), ("input_height", "u32"),
+    ("input_width", "u32"), ("kernel_size", "[i32]"), ("stride", "[i32]"), ("padding", "[i32]"), ("padding_mode", "string"),
+    ("groups", "u32"), ("output_dtype", "DataType", OPT), ("conv3d_config", "opaque"),
+    ("compute_config", "DeviceComputeKernelConfig"), ("memory_config", "MemoryConfig")])
+S.table("PrepareConv3dWeightsOp", [
+    ("weight_tensor", "TensorRef"), ("out", "TensorRef"), ("groups", "u32"), ("c_in_block", "u32"), ("alignment", "u32"),
+    ("device", "DeviceRef")])
+S.enum("ExperimentalEltwiseBinaryBackwardOpType", "u32", ["GeluBW"])
+S.table("ExperimentalEltwiseBinaryBackwardOp", [
+    ("type", "ExperimentalEltwiseBinaryBackwardOpType"), ("grad", "TensorRef"), ("input", "TensorRef"), ("approximate", "string"),
+    ("output_dtype", "DataType", OPT), ("memory_config", "MemoryConfig"), ("out", "TensorRef")])
+S.table("EmbeddingBackwardOp", [
+    ("input", "TensorRef"), ("weight", "TensorRef"), ("in_grad", "TensorRef"), ("dtype", "DataType", OPT), ("memcfg", "MemoryConfig"),
+    ("out", "TensorRef")])
+S.table("AdamWOp", [
+    ("param", "TensorRef"), ("grad", "TensorRef"), ("exp_avg", "TensorRef"), ("exp_avg_sq", "TensorRef"),
+    ("max_exp_avg_sq", "TensorRef"), ("lr", "f32"), ("beta1", "f32"), ("beta2", "f32"), ("beta1_pow", "f32"), ("beta2_pow", "f32"),
+    ("epsilon", "f32"), ("weight_decay", "f32"), ("stochastic_rounding", "bool")])
 S.table("UniformScale2D", [("scale", "i32")])
 S.table("NonUniformScale2D", [("scale", "[i32]")])
 S.union("Scale2D", ["UniformScale2D", "NonUniformScale2D"])

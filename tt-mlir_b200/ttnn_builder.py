@@ -811,6 +811,52 @@ class ProgramBuilder:
     def reset_global_semaphore(self, value: int = 0, loc=None) -> None:
         self._emit("ResetGlobalSemaphoreOp", {"semaphore": {"global_id": 0}, "value": value}, [], [], loc)
 
+    def conv3d(self, x: Value, w: Value, bias: Optional[Value], batch: int, depth: int, height: int, width: int, stride=(1, 1, 1),
+               padding=(0, 0, 0), groups: int = 1, padding_mode: str = "zeros", loc=None) -> Value:
+        """x is [1, 1, N*D*H*W, C] or [N, D, H, W, C]; w is [O, C/groups, kD, kH, kW]; bias [1, 1, 1, 1, O]."""
+        o, cg, kd, kh, kw = getattr(w, "filter_shape", w.shape)
+        od, oh, ow = ((s + 2 * p - k) // st + 1 for s, p, k, st in zip((depth, height, width), padding, (kd, kh, kw), stride))
+        flat = len(x.shape) == 4
+        out = self._value([1, 1, batch * od * oh * ow, o] if flat else [batch, od, oh, ow, o], x.dtype)
+        self._emit("Conv3dOp", {
+            "input": x.ref, "weight": w.ref, "bias": bias.ref if bias else None, "out": out.ref, "device": self.device_ref,
+            "in_channels": cg * groups, "out_channels": o, "batch_size": batch, "input_depth": depth, "input_height": height,
+            "input_width": width, "kernel_size": [kd, kh, kw], "stride": list(stride), "padding": list(padding),
+            "padding_mode": padding_mode, "groups": groups, "output_dtype": x.dtype, "memory_config": self._mc()},
+            [x, w] + ([bias] if bias else []), [out], loc)
+        return out
+
+    def prepare_conv3d_weights(self, w: Value, groups: int = 1, c_in_block: int = 32, alignment: int = 32, loc=None) -> Value:
+        o, cg, kd, kh, kw = w.shape
+        out = self._value([kd * kh * kw * cg, o], w.dtype)
+        out.filter_shape = list(w.shape)
+        self._emit("PrepareConv3dWeightsOp", {"weight_tensor": w.ref, "out": out.ref, "groups": groups, "c_in_block": c_in_block,
+                                              "alignment": alignment, "device": self.device_ref}, [w], [out], loc)
+        return out
+
+    def gelu_backward(self, grad: Value, x: Value, approximate: str = "none", loc=None) -> Value:
+        out = self._value(x.shape, x.dtype)
+        self._emit("ExperimentalEltwiseBinaryBackwardOp", {"type": "GeluBW", "grad": grad.ref, "input": x.ref, "approximate": approximate,
+                                                           "memory_config": self._mc(), "out": out.ref}, [grad, x], [out], loc)
+        return out
+
+    def embedding_backward(self, indices: Value, weight: Value, in_grad: Value, loc=None) -> Value:
+        out = self._value(weight.shape, in_grad.dtype)
+        self._emit("EmbeddingBackwardOp", {"input": indices.ref, "weight": weight.ref, "in_grad": in_grad.ref, "memcfg": self._mc(),
+                                           "out": out.ref}, [indices, weight, in_grad], [out], loc)
+        return out
+
+    def adamw(self, param: Value, grad: Value, exp_avg: Value, exp_avg_sq: Value, max_exp_avg_sq: Optional[Value] = None,
+              lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999, beta1_pow: float = 0.9, beta2_pow: float = 0.999,
+              epsilon: float = 1e-8, weight_decay: float = 0.0, stochastic_rounding: bool = False, loc=None) -> None:
+        """Updates param, exp_avg, exp_avg_sq (and max_exp_avg_sq) in place."""
+        ins = [param, grad, exp_avg, exp_avg_sq] + ([max_exp_avg_sq] if max_exp_avg_sq is not None else [])
+        self._emit("AdamWOp", {
+            "param": param.ref, "grad": grad.ref, "exp_avg": exp_avg.ref, "exp_avg_sq": exp_avg_sq.ref,
+            "max_exp_avg_sq": max_exp_avg_sq.ref if max_exp_avg_sq is not None else None, "lr": lr, "beta1": beta1, "beta2": beta2,
+            "beta1_pow": beta1_pow, "beta2_pow": beta2_pow, "epsilon": epsilon, "weight_decay": weight_decay,
+            "stochastic_rounding": stochastic_rounding}, ins, [], loc)
+
     # ---- mixture of experts (generic flow: dispatch -> remap -> sparse matmuls -> combine)
     def all_to_all_dispatch(self, x: Value, expert_indices: Value, expert_mapping: Value, cluster_axis: int = 1, loc=None):
         """x [B, 1, S, H] and expert_indices [B, 1, S, K] hold this device's tokens; expert_mapping is the replicated

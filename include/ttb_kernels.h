@@ -584,6 +584,20 @@ TTB_API int ttb_sdpa(const void *q, const void *k, const void *v, const void *ma
                      int dtype, int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seq_q,
                      int64_t seq_kv, int64_t head_dim, int64_t mask_batch, int64_t mask_heads,
                      int is_causal, float scale, void *stream);
+/* Causal attention of a prefill chunk that starts at position `offset`: query row r sees keys 0 .. r + offset
+ * (::ttnn::transformer::chunked_scaled_dot_product_attention once its paged keys and values are gathered,
+ * operations/transformer/chunked_scaled_dot_product_attention.cpp; golden tools/golden/mapping.py:8847-8912).  The
+ * tensor-core kernel applies the offset itself; other problems build an additive mask in `workspace`
+ * (ttb_sdpa_causal_offset_workspace_bytes) and take the general path. */
+TTB_API size_t ttb_sdpa_causal_offset_workspace_bytes(int dtype, int64_t seq_q, int64_t seq_kv);
+TTB_API int ttb_sdpa_causal_offset(const void *q, const void *k, const void *v, void *out, int dtype, int64_t batch,
+                                   int64_t heads_q, int64_t heads_kv, int64_t seq_q, int64_t seq_kv, int64_t head_dim,
+                                   int64_t offset, float scale, void *workspace, void *stream);
+/* out[u, h, t, :] = cache[page_table[u, t / block_size], h, t % block_size, :]: the paged cache
+ * [num_blocks, heads, block_size, head_dim] of every user as one sequence of max_blocks * block_size positions. */
+TTB_API int ttb_paged_gather(const void *cache, const void *page_table, void *out, int dtype, int table_dtype, int64_t users,
+                             int64_t heads, int64_t block_size, int64_t max_blocks, int64_t head_dim, int64_t num_blocks,
+                             void *stream);
 /* ttb_sdpa without a mask tensor, with every operand addressed as [batch, heads, seq, head_dim]
  * through element strides {batch, head, seq} (head_dim contiguous, strides multiples of 16 bytes).
  * Lets the caller skip the head split of q/k/v and the head merge of the output

@@ -389,6 +389,10 @@ class OracleBuilder:
         disp, meta = ops.all_to_all_dispatch(per(x), per(expert_indices), mp)
         return (OValue(disp), OValue(meta)) if isinstance(x.t, list) else (OValue(disp[0]), OValue(meta[0]))
 
+    def chunked_scaled_dot_product_attention(self, q, k_cache, v_cache, page_table, chunk_start_idx, scale=None, loc=None):
+        start = int(chunk_start_idx.first.reshape(-1)[0])
+        return _map(lambda t, kc, vc, pt: ops.chunked_sdpa(t, kc, vc, pt, start, scale), q, k_cache, v_cache, page_table)
+
     def conv3d(self, x, w, bias, batch, depth, height, width, stride=(1, 1, 1), padding=(0, 0, 0), groups=1, padding_mode="zeros", loc=None):
         return _map(lambda t, wt, b: ops.conv3d(t, wt, b, batch, depth, height, width, stride, padding, groups, padding_mode), x, w, bias)
 

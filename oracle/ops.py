@@ -895,3 +895,20 @@ def adamw(param, grad, exp_avg, exp_avg_sq, max_exp_avg_sq, lr, beta1, beta2, be
     r = (p - (m / (1.0 - beta1_pow)) / denom * lr) - p * (lr * weight_decay)
     out = (r.to(param.dtype), m.to(exp_avg.dtype), v.to(exp_avg_sq.dtype))
     return out + ((vv.to(max_exp_avg_sq.dtype),) if max_exp_avg_sq is not None else ())
+
+
+def chunked_sdpa(q, k_cache, v_cache, page_table, chunk_start, scale=None):
+    """tools/golden/mapping.py:8847-8912: un-page K and V through the page table, expand grouped heads, row j of the
+    chunk (absolute position chunk_start + j) sees keys 0 .. chunk_start + j; f32 softmax, one rounding."""
+    b, nh, sq, d = q.shape
+    nblocks, nkv, bs, _ = k_cache.shape
+    per_user = page_table.shape[-1]
+    pt = page_table.to(torch.int64).reshape(-1).clamp(0, nblocks - 1)
+    unpage = lambda c: c[pt].reshape(b, per_user, nkv, bs, d).transpose(1, 2).reshape(b, nkv, per_user * bs, d).float()
+    k, v = unpage(k_cache), unpage(v_cache)
+    if nh // nkv > 1:
+        k, v = k.repeat_interleave(nh // nkv, dim=1), v.repeat_interleave(nh // nkv, dim=1)
+    seq = per_user * bs
+    allowed = torch.arange(seq).view(1, seq) <= (chunk_start + torch.arange(sq)).view(sq, 1)
+    mask = torch.zeros(1, 1, sq, seq).masked_fill_(~allowed.view(1, 1, sq, seq), torch.finfo(torch.float32).min)
+    return torch.nn.functional.scaled_dot_product_attention(q.float(), k, v, attn_mask=mask, scale=scale).to(q.dtype)

@@ -552,6 +552,16 @@ def main():
         for n, t in zip(("param", "m", "v", "vmax"), res):
             store(out, f"map/adamw/{tag}/{n}", one(t))
 
+    # --- chunked prefill attention over a paged cache (mapping.py:8847-8912): 2 users, 4 q / 2 kv heads, block 16, 5 blocks each
+    cq = rnd(2, 4, 24, 32)
+    ck, cv = rnd(12, 2, 16, 32), rnd(12, 2, 16, 32)
+    cpt = torch.stack([torch.randperm(12, generator=g)[:5] for _ in range(2)]).to(torch.int32)
+    for n, t in (("q", cq), ("k", ck), ("v", cv), ("page_table", cpt)):
+        store(out, f"map/chunked_sdpa/{n}", t)
+    for start in (0, 40):
+        store(out, f"map/chunked_sdpa/start{start}", one(ref.ttir_chunked_scaled_dot_product_attention_golden(
+            gmt(cq), gmt(ck), gmt(cv), gmt(cpt), gmt(torch.tensor([start], dtype=torch.int32)), None, S.FloatAttr(0.2), S.F32Type())))
+
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ttir_cpu_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes")

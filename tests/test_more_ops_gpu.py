@@ -405,3 +405,29 @@ def test_adamw_matches_the_reference_golden(rt, device, golden):
     assert torch.equal(near, torch.full((64, 1024), 0.999).to(bf))       # 1 - 1e-3 rounds to the nearest bf16 (0.99609375 or 1.0)
     rnd = run_gpu(rt, device, lambda b, *v: step(b, *v, True), [pb, gb, zeros, zeros.clone()])[0].float()
     assert set(rnd.unique().tolist()) <= {0.99609375, 1.0} and abs(rnd.mean().item() - 0.999) < 2e-4
+
+
+def test_chunked_prefill_attention(rt, device, golden):
+    q, k, v, pt = (golden[f"map/chunked_sdpa/{n}"] for n in ("q", "k", "v", "page_table"))
+    for start in (0, 40):                                        # head_dim 32, f32: the general kernel with a built mask
+        st = torch.tensor([start], dtype=torch.int32)
+        got, want = run_body(rt, device, lambda b, *t: b.chunked_scaled_dot_product_attention(*t, scale=0.2), [q, k, v, pt, st])
+        assert torch.allclose(got[0], golden[f"map/chunked_sdpa/start{start}"], rtol=1e-4, atol=1e-5), start
+        assert torch.allclose(got[0], want[0], rtol=1e-4, atol=1e-5)
+    # the tensor-core kernel: head_dim 128, bf16, grouped heads, chunks of a 2048-token prefill over 64-token pages
+    torch.manual_seed(18)
+    bf = torch.bfloat16
+    B, Hq, Hkv, D, bs, per_user = 2, 8, 2, 128, 64, 32
+    kc, vc = torch.randn(80, Hkv, bs, D).to(bf), torch.randn(80, Hkv, bs, D).to(bf)
+    table = torch.stack([torch.randperm(80)[:per_user] for _ in range(B)]).to(torch.int32)
+    for start, sq in ((0, 256), (512, 384), (1792, 256), (1000, 200)):
+        qc = torch.randn(B, Hq, sq, D).to(bf)
+        st = torch.tensor([start], dtype=torch.int32)
+        got, want = run_body(rt, device, lambda b, *t: b.chunked_scaled_dot_product_attention(*t), [qc, kc, vc, table, st])
+        assert_matches(got[0], want[0], f"chunked attention, chunk [{start}, {start + sq})")
+    # enough heads for the two-heads-per-CTA kernel
+    qc = torch.randn(B, 32, 1024, D).to(bf)
+    kc8, vc8 = torch.randn(80, 8, bs, D).to(bf), torch.randn(80, 8, bs, D).to(bf)
+    got, want = run_body(rt, device, lambda b, *t: b.chunked_scaled_dot_product_attention(*t),
+                         [qc, kc8, vc8, table, torch.tensor([960], dtype=torch.int32)])
+    assert_matches(got[0], want[0], "chunked attention, 32 heads")

@@ -406,6 +406,13 @@ def test_conv3d_gelu_backward_embedding_backward_adamw(golden):
             assert torch.allclose(t, golden[f"map/adamw/{tag}/{n}"], rtol=1e-6, atol=1e-7), (tag, n)
 
 
+def test_chunked_prefill_attention(golden):
+    """Restatement against the reference's golden (tools/golden/mapping.py:8847-8912)."""
+    q, k, v, pt = (golden[f"map/chunked_sdpa/{n}"] for n in ("q", "k", "v", "page_table"))
+    for start in (0, 40):
+        assert torch.allclose(ops.chunked_sdpa(q, k, v, pt, start, 0.2), golden[f"map/chunked_sdpa/start{start}"], rtol=1e-6, atol=1e-6)
+
+
 def test_layer_norm(golden):
     x, w, b = golden["ln/x"], golden["ln/w"], golden["ln/b"]
     assert same(ops.layer_norm(x), golden["ln/plain"])

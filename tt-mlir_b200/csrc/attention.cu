@@ -315,7 +315,7 @@ __global__ void __launch_bounds__(128)
 namespace ttb {
 int sdpaTcgen05Try(const void *q, const void *k, const void *v, void *out, int dtype, int64_t batch, int64_t hq,
                    int64_t hkv, int64_t sq, int64_t skv, int64_t headDim, const int64_t *qs, const int64_t *ks,
-                   const int64_t *vs, const int64_t *os, int causal, float scale, cudaStream_t st);
+                   const int64_t *vs, const int64_t *os, int causal, float scale, cudaStream_t st, int64_t causalOff = 0);
 static bool sdpaLegacy() {
   static const bool legacy = [] {
     const char *e = std::getenv("TTB_SDPA_MMA_SYNC");
@@ -326,6 +326,93 @@ static bool sdpaLegacy() {
 }
 
 using namespace ttb;
+
+// Additive mask of a prefill chunk: row r sees keys 0 .. r + offset.  Only for problems the tensor-core kernel,
+// which applies the offset itself, does not take.
+template <typename T>
+__global__ void __launch_bounds__(256) causalOffsetMaskKernel(T *__restrict__ mask, int64_t seqQ, int64_t seqKv, int64_t offset) {
+  const size_t total = static_cast<size_t>(seqQ) * seqKv, stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t r = static_cast<int64_t>(i / seqKv), c = static_cast<int64_t>(i % seqKv);
+    mask[i] = fromF32<T>(c <= r + offset ? 0.0f : -INFINITY);
+  }
+}
+
+// out[u, h, t, :] = cache[table[u, t / block], h, t % block, :]: a user's paged keys or values as one sequence.
+template <typename I>
+__global__ void __launch_bounds__(256) pagedGatherKernel(const uint4 *__restrict__ cache, const I *__restrict__ table, uint4 *__restrict__ out,
+                                                         int64_t users, int64_t heads, int64_t blockSize, int64_t maxBlocks,
+                                                         int64_t vecPerRow, int64_t numBlocks) {
+  const int64_t seq = maxBlocks * blockSize;
+  const size_t total = static_cast<size_t>(users) * heads * seq * vecPerRow, stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t v = static_cast<int64_t>(i % vecPerRow);
+    size_t q = i / vecPerRow;
+    const int64_t t = static_cast<int64_t>(q % seq);
+    q /= seq;
+    const int64_t h = static_cast<int64_t>(q % heads), u = static_cast<int64_t>(q / heads);
+    int64_t blk = static_cast<int64_t>(table[u * maxBlocks + t / blockSize]);
+    blk = blk < 0 ? 0 : (blk >= numBlocks ? numBlocks - 1 : blk); // a table entry outside the cache reads a valid block
+    out[i] = cache[((blk * heads + h) * blockSize + t % blockSize) * vecPerRow + v];
+  }
+}
+
+extern "C" int ttb_paged_gather(const void *cache, const void *page_table, void *out, int dtype, int table_dtype, int64_t users,
+                                int64_t heads, int64_t block_size, int64_t max_blocks, int64_t head_dim, int64_t num_blocks,
+                                void *stream) {
+  TTB_CHECK(cache && page_table && out, "null tensor");
+  TTB_CHECK(users > 0 && heads > 0 && block_size > 0 && max_blocks > 0 && head_dim > 0 && num_blocks > 0, "empty paged cache");
+  const int64_t rowBytes = head_dim * static_cast<int64_t>(dtypeSize(dtype));
+  TTB_CHECK(rowBytes % 16 == 0 && aligned16(cache) && aligned16(out), "cache rows must be multiples of 16 bytes");
+  cudaStream_t st = asStream(stream);
+  const size_t total = static_cast<size_t>(users) * heads * max_blocks * block_size * (rowBytes / 16);
+  ProfScope prof("paged_gather", 0, double(total) * 32, st);
+  const int grid = gridFor(total, 256);
+  switch (table_dtype) {
+  case kI32:
+    pagedGatherKernel<int32_t><<<grid, 256, 0, st>>>(static_cast<const uint4 *>(cache), static_cast<const int32_t *>(page_table),
+                                                     static_cast<uint4 *>(out), users, heads, block_size, max_blocks, rowBytes / 16, num_blocks);
+    break;
+  case kU32:
+    pagedGatherKernel<uint32_t><<<grid, 256, 0, st>>>(static_cast<const uint4 *>(cache), static_cast<const uint32_t *>(page_table),
+                                                      static_cast<uint4 *>(out), users, heads, block_size, max_blocks, rowBytes / 16, num_blocks);
+    break;
+  default: setLastError("paged_gather: the page table must be Int32 or UInt32"); return TTB_ERR_UNSUPPORTED;
+  }
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
+extern "C" int ttb_sdpa(const void *q, const void *k, const void *v, const void *mask, void *out, int dtype, int64_t batch,
+                        int64_t heads_q, int64_t heads_kv, int64_t seq_q, int64_t seq_kv, int64_t head_dim, int64_t mask_batch,
+                        int64_t mask_heads, int is_causal, float scale, void *stream);
+
+extern "C" size_t ttb_sdpa_causal_offset_workspace_bytes(int dtype, int64_t seq_q, int64_t seq_kv) {
+  return static_cast<size_t>(seq_q) * static_cast<size_t>(seq_kv) * dtypeSize(dtype);
+}
+
+extern "C" int ttb_sdpa_causal_offset(const void *q, const void *k, const void *v, void *out, int dtype, int64_t batch, int64_t heads_q,
+                                      int64_t heads_kv, int64_t seq_q, int64_t seq_kv, int64_t head_dim, int64_t offset, float scale,
+                                      void *workspace, void *stream) {
+  TTB_CHECK(q && k && v && out, "null tensor");
+  TTB_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0, "bad head configuration");
+  TTB_CHECK(seq_q > 0 && seq_kv > 0 && head_dim > 0 && offset >= 0, "empty attention problem");
+  cudaStream_t st = asStream(stream);
+  if (!sdpaLegacy()) {
+    int64_t qs[3] = {heads_q * seq_q * head_dim, seq_q * head_dim, head_dim};
+    int64_t ks[3] = {heads_kv * seq_kv * head_dim, seq_kv * head_dim, head_dim};
+    int rc = sdpaTcgen05Try(q, k, v, out, dtype, batch, heads_q, heads_kv, seq_q, seq_kv, head_dim, qs, ks, ks, qs, 1, scale, st, offset);
+    if (rc >= 0) return rc;
+  }
+  TTB_CHECK(workspace != nullptr, "this problem needs the mask workspace");
+  TTB_DISPATCH_FLOAT(dtype, T,
+                     (causalOffsetMaskKernel<T><<<gridFor(static_cast<size_t>(seq_q) * seq_kv, 256), 256, 0, st>>>(
+                         static_cast<T *>(workspace), seq_q, seq_kv, offset)));
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return ttb_sdpa(q, k, v, workspace, out, dtype, batch, heads_q, heads_kv, seq_q, seq_kv, head_dim, 1, 1, 0, scale, stream);
+}
 
 extern "C" int ttb_sdpa(const void *q, const void *k, const void *v, const void *mask, void *out, int dtype,
                         int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seq_q, int64_t seq_kv,

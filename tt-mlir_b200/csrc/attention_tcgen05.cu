@@ -43,6 +43,7 @@ struct AtParams {
   int64_t Hq, Hkv, Sq, Skv;
   int64_t ob, oh, os; // element strides of out over batch, head, query row
   int causal;
+  int causalOff; // under a causal mask, query row r sees keys 0 .. r + causalOff (a prefill chunk that starts at causalOff)
   int fmt; // 1 bf16, 0 f16
   float scaleLog2;
   // Split mode (few heads: fewer query blocks than SMs, and a causal block's work grows with its
@@ -136,7 +137,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   const int q0 = qb * AT_BM;
   int nAll = static_cast<int>((p.Skv + AT_BN - 1) / AT_BN); // key tiles this query block sees
   if (p.causal) {
-    int lim = q0 / AT_BN + 1;
+    int lim = (q0 + AT_BM - 1 + p.causalOff) / AT_BN + 1;
     nAll = nAll < lim ? nAll : lim;
   }
   // this CTA's tiles: [t0, t0 + nT)
@@ -274,10 +275,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       tcFenceAfter();
       const uint32_t sAddr = laneAddr + s * AT_BN + wg * HALF;
       const int key0 = (t0 + j) * AT_BN + wg * HALF;
-      const bool needMask = (p.causal && key0 + HALF - 1 > q0) || key0 + HALF > p.Skv;
+      const bool needMask = (p.causal && key0 + HALF - 1 > q0 + p.causalOff) || key0 + HALF > p.Skv;
       // Last visible key of this row inside this half tile (relative, may be negative or >= 64).
       int64_t lastKey = p.Skv - 1;
-      if (p.causal && qrow < lastKey) lastKey = qrow;
+      if (p.causal && qrow + p.causalOff < lastKey) lastKey = qrow + p.causalOff;
       const int lastRel = static_cast<int>(lastKey - key0 < HALF ? lastKey - key0 : HALF);
       // This thread's 64 scores are read from TMEM once (both loads in flight together) and stay
       // in registers for the maximum and for the exponentials.
@@ -453,7 +454,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   const int q0 = qb * AT_BM;
   int nT = static_cast<int>((p.Skv + AP_BN - 1) / AP_BN);
   if (p.causal) {
-    int lim = q0 / AP_BN + AT_BM / AP_BN;
+    int lim = (q0 + AT_BM - 1 + p.causalOff) / AP_BN + 1;
     nT = nT < lim ? nT : lim;
   }
 
@@ -579,9 +580,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       tcFenceAfter();
       const uint32_t sAddr = laneAddr + (hd * 2 + buf) * AP_BN;
       const int key0 = j * AP_BN;
-      const bool needMask = (p.causal && key0 + AP_BN - 1 > q0) || key0 + AP_BN > p.Skv;
+      const bool needMask = (p.causal && key0 + AP_BN - 1 > q0 + p.causalOff) || key0 + AP_BN > p.Skv;
       int64_t lastKey = p.Skv - 1;
-      if (p.causal && qrow < lastKey) lastKey = qrow;
+      if (p.causal && qrow + p.causalOff < lastKey) lastKey = qrow + p.causalOff;
       const int lastRel = static_cast<int>(lastKey - key0 < AP_BN ? lastKey - key0 : AP_BN);
       // This thread's 64 scores are read from TMEM once (both loads in flight together) and stay
       // in registers for the maximum and for the exponentials.
@@ -792,8 +793,9 @@ static int launchAt(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensor
 // kernel), otherwise a TTB status.
 int sdpaTcgen05Try(const void *q, const void *k, const void *v, void *out, int dtype, int64_t batch, int64_t hq,
                    int64_t hkv, int64_t sq, int64_t skv, int64_t headDim, const int64_t *qs, const int64_t *ks,
-                   const int64_t *vs, const int64_t *os, int causal, float scale, cudaStream_t st) {
+                   const int64_t *vs, const int64_t *os, int causal, float scale, cudaStream_t st, int64_t causalOff) {
   if (headDim != AT_D || (dtype != kBF16 && dtype != kF16)) return -1;
+  if (causalOff < 0 || causalOff > 0x3fffffff) return -1;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return -1;
   if (sq > 0x7fffff00 || skv > 0x7fffff00) return -1;
   for (int i = 0; i < 3; ++i) {
@@ -818,6 +820,7 @@ int sdpaTcgen05Try(const void *q, const void *k, const void *v, void *out, int d
   p.Hq = hq; p.Hkv = hkv; p.Sq = sq; p.Skv = skv;
   p.ob = os[0]; p.oh = os[1]; p.os = os[2];
   p.causal = causal ? 1 : 0;
+  p.causalOff = causal ? static_cast<int>(causalOff) : 0;
   p.fmt = dtype == kBF16 ? 1 : 0;
   p.scaleLog2 = scale * 1.4426950408889634f;
   p.splitLen = 0;
@@ -847,7 +850,7 @@ int sdpaTcgen05Try(const void *q, const void *k, const void *v, void *out, int d
   unsigned grid = static_cast<unsigned>(ctas);
   const int64_t tilesAll = (skv + AT_BN - 1) / AT_BN;
   if (!noSplit && causal && nQ <= 64 && ctas < smCount() && tilesAll >= 4) {
-    auto tilesOf = [&](int64_t qb) { return std::min<int64_t>(tilesAll, qb * AT_BM / AT_BN + 1); };
+    auto tilesOf = [&](int64_t qb) { return std::min<int64_t>(tilesAll, (qb * AT_BM + AT_BM - 1 + causalOff) / AT_BN + 1); };
     const int64_t unsplit = (tilesOf(nQ - 1) + 6) * ((ctas + smCount() - 1) / smCount());
     int64_t bestCost = unsplit * 6 / 10;
     int bestL = 0;

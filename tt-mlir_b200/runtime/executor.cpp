@@ -122,6 +122,16 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     pushRef(outs, o->metadata());
     break;
   }
+  case OpType::ChunkedScaledDotProductAttentionOp: {
+    const auto *o = op->type_as_ChunkedScaledDotProductAttentionOp();
+    pushRef(ins, o->query());
+    pushRef(ins, o->key());
+    pushRef(ins, o->value());
+    pushRef(ins, o->page_table());
+    pushRef(ins, o->chunk_start_idx());
+    pushRef(outs, o->out());
+    break;
+  }
   case OpType::Conv3dOp: {
     const auto *o = op->type_as_Conv3dOp();
     pushRef(ins, o->input());
@@ -854,6 +864,7 @@ private:
   // expert ownership of this process's mesh coordinates: localIdx tensors (Int32 [experts]) from a [1, 1, E, D] mapping
   TensorPtr moeLocalIndex(const TensorPtr &mapping, uint32_t &experts, uint32_t &devices);
   void runAllToAllDispatch(const fbt::AllToAllDispatchOp *op);
+  void runChunkedSdpa(const fbt::ChunkedScaledDotProductAttentionOp *op);
   void runConv3d(const fbt::Conv3dOp *op);
   void runGeluBackward(const fbt::ExperimentalEltwiseBinaryBackwardOp *op);
   void runEmbeddingBackward(const fbt::EmbeddingBackwardOp *op);
@@ -1235,6 +1246,7 @@ size_t Executor::runOp(size_t i) {
   case OpType::CumSumOp: runCumSum(op->type_as_CumSumOp()); break;
   case OpType::CumProdOp: runCumProd(op->type_as_CumProdOp()); break;
   case OpType::AllToAllDispatchOp: runAllToAllDispatch(op->type_as_AllToAllDispatchOp()); break;
+  case OpType::ChunkedScaledDotProductAttentionOp: runChunkedSdpa(op->type_as_ChunkedScaledDotProductAttentionOp()); break;
   case OpType::Conv3dOp: runConv3d(op->type_as_Conv3dOp()); break;
   case OpType::PrepareConv3dWeightsOp: {
     const auto *o = op->type_as_PrepareConv3dWeightsOp();
@@ -2824,6 +2836,53 @@ void Executor::runReductionProd(const fbt::ReductionProdOp *op) {
 }
 
 // group_norm on channels-last [N, 1, H*W, C] (or [N, H, W, C]): operations/normalization/group_norm.cpp.
+// chunked_scaled_dot_product_attention (operations/transformer/chunked_scaled_dot_product_attention.cpp; golden
+// tools/golden/mapping.py:8847-8912): one chunk of a long prefill.  query [B, H, Sq, D] holds positions
+// chunk_start .. chunk_start + Sq - 1; keys and values live in a paged cache [blocks, Hkv, block, D] addressed through
+// page_table [B, blocks per user]; row r sees keys 0 .. chunk_start + r.  The pages of every user are gathered into
+// one sequence (one pass over K and V, small beside the Sq x Skv products), then the causal kernel runs with the
+// chunk's offset.  chunk_start_idx is read on the host: it decides how many key tiles the launch covers.
+void Executor::runChunkedSdpa(const fbt::ChunkedScaledDotProductAttentionOp *op) {
+  TensorPtr q = getDevice(op->query()), kc = getDevice(op->key()), vc = getDevice(op->value());
+  TensorPtr table = getDevice(op->page_table());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(q->shape.size() == 4 && kc->shape.size() == 4 && vc->shape == kc->shape && table->shape.size() == 2,
+              "chunked attention expects query [B, H, S, D], caches [blocks, Hkv, block, D] and page_table [B, blocks per user]");
+  const int64_t B = q->shape[0], Hq = q->shape[1], Sq = q->shape[2], D = q->shape[3];
+  const int64_t numBlocks = kc->shape[0], Hkv = kc->shape[1], blockSize = kc->shape[2], perUser = table->shape[1];
+  TTRT_ASSERT(kc->shape[3] == D && table->shape[0] == B && Hkv > 0 && Hq % Hkv == 0, "chunked attention operands do not fit together");
+  TTRT_ASSERT(kc->dtype == q->dtype && vc->dtype == q->dtype && out->dtype == q->dtype && out->volume() == q->volume(),
+              "chunked attention tensors must share one data type");
+  refuseWhileRecording("reading chunk_start_idx");
+  TensorPtr startT = get(op->chunk_start_idx());
+  TTRT_ASSERT(startT->volume() >= 1 && dataTypeSize(startT->dtype) == 4, "chunk_start_idx must hold one 32-bit integer");
+  if (startT->storage == Storage::Device) startT = toHostTensor(startT, true);
+  const int64_t start = *static_cast<const int32_t *>(startT->shards[0]->ptr);
+  const int64_t Skv = perUser * blockSize;
+  TTRT_ASSERT(start >= 0 && start + Sq <= Skv, "the chunk [", start, ", ", start + Sq, ") lies outside the ", Skv, " cached positions");
+  TensorPtr tbl = table->dtype == DataType::Int32 || table->dtype == DataType::UInt32 ? table : castOnDevice(table, DataType::Int32);
+  // Keys beyond the chunk's last row are never visible: gather and attend to the blocks that are.
+  const int64_t usedBlocks = (start + Sq + blockSize - 1) / blockSize, used = usedBlocks * blockSize;
+  std::vector<uint32_t> seqShape = {static_cast<uint32_t>(B), static_cast<uint32_t>(Hkv), static_cast<uint32_t>(used), static_cast<uint32_t>(D)};
+  TensorPtr k = makeDeviceTensor(dev, seqShape, q->dtype), v = makeDeviceTensor(dev, seqShape, q->dtype);
+  // the table is read with its own row length; only the first usedBlocks entries of a row are touched
+  TensorPtr tblUsed = perUser == usedBlocks ? tbl : stridedView(tbl, {static_cast<uint32_t>(B), static_cast<uint32_t>(usedBlocks)}, {perUser, 1}, 0, tbl->dtype);
+  const float scale = op->scale().value_or(1.0f / std::sqrt(static_cast<float>(D)));
+  const size_t wsBytes = ttb_sdpa_causal_offset_workspace_bytes(ttbDtype(q->dtype), Sq, used);
+  const bool tensorCore = D == 128 && (q->dtype == DataType::BFloat16 || q->dtype == DataType::Float16);
+  // small masks are always provided, so that a build or an environment that keeps the tensor-core kernel out still runs
+  TensorPtr ws = (tensorCore && wsBytes > (64u << 20)) ? nullptr : makeDeviceTensor(dev, {static_cast<uint32_t>((wsBytes + 3) / 4)}, DataType::UInt32);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_paged_gather(kc->shards[i]->ptr, tblUsed->shards[i]->ptr, k->shards[i]->ptr, ttbDtype(q->dtype), ttbDtype(tblUsed->dtype), B,
+                              Hkv, blockSize, usedBlocks, D, numBlocks, r.stream));
+    TTB_CALL(ttb_paged_gather(vc->shards[i]->ptr, tblUsed->shards[i]->ptr, v->shards[i]->ptr, ttbDtype(q->dtype), ttbDtype(tblUsed->dtype), B,
+                              Hkv, blockSize, usedBlocks, D, numBlocks, r.stream));
+    TTB_CALL(ttb_sdpa_causal_offset(q->shards[i]->ptr, k->shards[i]->ptr, v->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(q->dtype), B, Hq,
+                                    Hkv, Sq, used, D, start, scale, ws ? ws->shards[i]->ptr : nullptr, r.stream));
+  });
+  put(op->out(), out);
+}
+
 // conv3d over flattened NDHWC activations.  The weight is either the framework's [O, C/g, kD, kH, kW] (also what a
 // prepare_conv3d_weights result carries) or TTNN's prepared matrix [kD*kH*kW*C/g, O].
 void Executor::runConv3d(const fbt::Conv3dOp *op) {

@@ -376,6 +376,10 @@ S.table("AdamWOp", [
     ("param", "TensorRef"), ("grad", "TensorRef"), ("exp_avg", "TensorRef"), ("exp_avg_sq", "TensorRef"),
     ("max_exp_avg_sq", "TensorRef"), ("lr", "f32"), ("beta1", "f32"), ("beta2", "f32"), ("beta1_pow", "f32"), ("beta2_pow", "f32"),
     ("epsilon", "f32"), ("weight_decay", "f32"), ("stochastic_rounding", "bool")])
+S.table("ChunkedScaledDotProductAttentionOp", [
+    ("query", "TensorRef"), ("key", "TensorRef"), ("value", "TensorRef"), ("page_table", "TensorRef"),
+    ("chunk_start_idx", "TensorRef"), ("scale", "f32", OPT), ("out", "TensorRef"), ("memcfg", "MemoryConfig"),
+    ("program_config", "opaque")])
 S.table("UniformScale2D", [("scale", "i32")])
 S.table("NonUniformScale2D", [("scale", "[i32]")])
 S.union("Scale2D", ["UniformScale2D", "NonUniformScale2D"])

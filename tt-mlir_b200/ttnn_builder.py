@@ -811,6 +811,17 @@ class ProgramBuilder:
     def reset_global_semaphore(self, value: int = 0, loc=None) -> None:
         self._emit("ResetGlobalSemaphoreOp", {"semaphore": {"global_id": 0}, "value": value}, [], [], loc)
 
+    def chunked_scaled_dot_product_attention(self, q: Value, k_cache: Value, v_cache: Value, page_table: Value, chunk_start_idx: Value,
+                                             scale: Optional[float] = None, loc=None) -> Value:
+        """q [B, H, Sq, D] (positions chunk_start ..), caches [blocks, Hkv, block, D], page_table [B, blocks per user]."""
+        out = self._value(q.shape, q.dtype)
+        t = {"query": q.ref, "key": k_cache.ref, "value": v_cache.ref, "page_table": page_table.ref,
+             "chunk_start_idx": chunk_start_idx.ref, "out": out.ref, "memcfg": self._mc()}
+        if scale is not None:
+            t["scale"] = scale
+        self._emit("ChunkedScaledDotProductAttentionOp", t, [q, k_cache, v_cache, page_table, chunk_start_idx], [out], loc)
+        return out
+
     def conv3d(self, x: Value, w: Value, bias: Optional[Value], batch: int, depth: int, height: int, width: int, stride=(1, 1, 1),
                padding=(0, 0, 0), groups: int = 1, padding_mode: str = "zeros", loc=None) -> Value:
         """x is [1, 1, N*D*H*W, C] or [N, D, H, W, C]; w is [O, C/groups, kD, kH, kW]; bias [1, 1, 1, 1, O]."""

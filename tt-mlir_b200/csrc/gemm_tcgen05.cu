@@ -178,7 +178,7 @@ struct PushMaps {
   CUtensorMap m[8];
 };
 
-template <int BN, typename TC, bool PLAIN, bool PAIR>
+template <int BN, typename TC, bool PLAIN, bool PAIR, bool I8>
 __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     gemmTcgen05Kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                       const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapE,
@@ -215,8 +215,11 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     n0 = static_cast<int>(nt - (seg == 0 ? 0 : p.segCum[seg - 1])) * (p.dual ? BN / 2 : BN);
     return seg;
   };
-  const int kBlocks1 = static_cast<int>((p.K + p.kElems - 1) / p.kElems);
-  const int kBlocks = kBlocks1 + (p.dualA ? static_cast<int>((p.K2 + p.kElems - 1) / p.kElems) : 0);
+  // Elements in the 128 bytes of a k-block.  The 8-bit integer form is a template parameter, not a launch parameter: as
+  // runtime branches, its issue path and its dequantizing epilogue cost the 16-bit kernels 12 % (measured).
+  constexpr int K_ELEMS = I8 ? 128 : TC_BK;
+  const int kBlocks1 = static_cast<int>((p.K + K_ELEMS - 1) / K_ELEMS);
+  const int kBlocks = kBlocks1 + (p.dualA ? static_cast<int>((p.K2 + K_ELEMS - 1) / K_ELEMS) : 0);
   const uint32_t accCols = p.dualA ? 2u * BN : static_cast<uint32_t>(BN); // TMEM columns of one accumulator buffer
 
   if (threadIdx.x == 0) {
@@ -364,7 +367,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
             const uint32_t bar = mapToCta(fullBar(s), 0);
             if (leader) mbarArriveExpectTx(fullBar(s), 2 * Cfg::kStageBytes);
             const bool second = p.dualA && kb >= kBlocks1; // k-blocks of the second product
-            const int kc = (second ? kb - kBlocks1 : kb) * p.kElems;
+            const int kc = (second ? kb - kBlocks1 : kb) * K_ELEMS;
             tmaLoad2dPair(sa, second ? &mapE : &mapA, bar, kc, m0);
             if (p.dual) tmaLoad2dPair(sb, leader ? &mapB : &mapB1, bar, kc, n0);
             else tmaLoad2dPair(sb, second ? &mapB1 : mb, bar, kc, n0 + static_cast<int>(ctaRank) * (BN / 2));
@@ -376,17 +379,17 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
             const int tap = kb / cb, ky = tap / p.ckw, kx = tap - ky * p.ckw;
             tmaLoad4d(sa, &mapA, fullBar(s), (kb - tap * cb) * TC_BK, ox0 + kx * p.cdw - p.cpl, oy0 + ky * p.cdh - p.cpt, img);
           } else if (p.dualA && kb >= kBlocks1) {
-            tmaLoad2d(sa, &mapE, fullBar(s), (kb - kBlocks1) * p.kElems, m0);
+            tmaLoad2d(sa, &mapE, fullBar(s), (kb - kBlocks1) * K_ELEMS, m0);
           } else {
-            tmaLoad2d(sa, &mapA, fullBar(s), kb * p.kElems, m0);
+            tmaLoad2d(sa, &mapA, fullBar(s), kb * K_ELEMS, m0);
           }
           if (p.dual) {
             tmaLoad2d(sb, &mapB, fullBar(s), kb * TC_BK, n0);
             tmaLoad2d(sb + (BN / 2) * TC_BK * 2, &mapB1, fullBar(s), kb * TC_BK, n0);
           } else if (p.dualA && kb >= kBlocks1) {
-            tmaLoad2d(sb, &mapB1, fullBar(s), (kb - kBlocks1) * p.kElems, n0);
+            tmaLoad2d(sb, &mapB1, fullBar(s), (kb - kBlocks1) * K_ELEMS, n0);
           } else {
-            tmaLoad2d(sb, mb, fullBar(s), kb * p.kElems, n0);
+            tmaLoad2d(sb, mb, fullBar(s), kb * K_ELEMS, n0);
           }
         }
       }
@@ -394,7 +397,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0 && leader) {
-      const bool ints = p.fmt == 2;
+      constexpr bool ints = I8;
       const uint32_t idesc = ints ? instrDescI8(p.aSigned, p.bSigned, TILE_M, BN) : instrDesc(p.fmt, TILE_M, BN);
       uint32_t it = 0, accIt = 0;
       bool alive = true;
@@ -418,10 +421,10 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
           for (int k = 0; k < TC_BK / 16; ++k) {
             // +32 bytes per k-step (16 two-byte or 32 one-byte elements) = +2 in the descriptor's 16-byte address units
             if constexpr (PAIR) {
-              if (ints) tcMmaPairI8(tmemD, da + 2u * k, db + 2u * k, idesc, (kbIn | k) != 0 ? 1u : 0u);
+              if constexpr (ints) tcMmaPairI8(tmemD, da + 2u * k, db + 2u * k, idesc, (kbIn | k) != 0 ? 1u : 0u);
               else tcMmaPair(tmemD, da + 2u * k, db + 2u * k, idesc, (kbIn | k) != 0 ? 1u : 0u);
             } else {
-              if (ints) tcMmaI8(tmemD, da + 2u * k, db + 2u * k, idesc, (kbIn | k) != 0 ? 1u : 0u);
+              if constexpr (ints) tcMmaI8(tmemD, da + 2u * k, db + 2u * k, idesc, (kbIn | k) != 0 ? 1u : 0u);
               else tcMma(tmemD, da + 2u * k, db + 2u * k, idesc, (kbIn | k) != 0 ? 1u : 0u);
             }
           }
@@ -757,14 +760,16 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
             }
           }
           if constexpr (!PLAIN) {
-            if (p.deq) {
-              // quantized contraction followed by dequantize: float(accumulator) * scale, one rounding
-              float sc = p.deqScalar;
-              if (p.deq == 2) sc = colH + lane < p.N ? p.deqScale[colH + lane] : 0.0f;
+            if constexpr (I8) {
+              if (p.deq) {
+                // quantized contraction followed by dequantize: float(accumulator) * scale, one rounding
+                float sc = p.deqScalar;
+                if (p.deq == 2) sc = colH + lane < p.N ? p.deqScale[colH + lane] : 0.0f;
 #pragma unroll
-              for (int e = 0; e < HW; ++e) {
-                const float se = p.deq == 2 ? __shfl_sync(0xffffffffu, sc, e) : sc;
-                r[e] = __float_as_uint(__fmul_rn(__int2float_rn(static_cast<int>(r[e])), se));
+                for (int e = 0; e < HW; ++e) {
+                  const float se = p.deq == 2 ? __shfl_sync(0xffffffffu, sc, e) : sc;
+                  r[e] = __float_as_uint(__fmul_rn(__int2float_rn(static_cast<int>(r[e])), se));
+                }
               }
             }
             // One straight-line pass per case: runtime flags inside the unrolled loop would put
@@ -999,7 +1004,7 @@ static bool pairMmaWanted(int64_t m, int64_t k) {
   return !off && m >= 2 * TC_BM && k >= minK && smCount() >= 2;
 }
 
-template <int BN, typename TC, bool PLAIN, bool PAIR = false>
+template <int BN, typename TC, bool PLAIN, bool PAIR = false, bool I8 = false>
 static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &me, void *c, const TcParams &p,
                     cudaStream_t st, const CUtensorMap *more = nullptr /* mapB1, mapC1, mapB2, mapC2 of a grouped launch */,
                     const PushMaps *push = nullptr) {
@@ -1009,7 +1014,7 @@ static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensor
   int dev = 0;
   TTB_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attrSet[dev]) {
-    TTB_CUDA(cudaFuncSetAttribute(gemmTcgen05Kernel<BN, TC, PLAIN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+    TTB_CUDA(cudaFuncSetAttribute(gemmTcgen05Kernel<BN, TC, PLAIN, PAIR, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
     attrSet[dev] = true;
   }
   const int64_t tileM = PAIR ? 2 * TC_BM : TC_BM;
@@ -1037,7 +1042,7 @@ static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensor
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  TTB_CUDA(cudaLaunchKernelEx(&cfg, gemmTcgen05Kernel<BN, TC, PLAIN, PAIR>, ma, mb, mc, me, more ? more[0] : mb, more ? more[1] : mc,
+  TTB_CUDA(cudaLaunchKernelEx(&cfg, gemmTcgen05Kernel<BN, TC, PLAIN, PAIR, I8>, ma, mb, mc, me, more ? more[0] : mb, more ? more[1] : mc,
                               more ? more[2] : mb, more ? more[3] : mc, push ? *push : PushMaps{{mc, mc, mc, mc, mc, mc, mc, mc}},
                               static_cast<TC *>(c), p));
   countLaunch();
@@ -1279,8 +1284,8 @@ int gemmTcgen05I8Try(const void *a, const void *b, void *c, int aDtype, int bDty
   ProfScope prof("gemm_tcgen05_i8", 2.0 * double(m) * double(n) * double(k),
                  double(m) * k + double(n) * k + double(m) * n * dtypeSize(cDtype), stream);
 #define TTB_TCI(BNv, TCv, PLAINv)                                                        \
-  if (pair) return launchTc<BNv, TCv, PLAINv, true>(ma, mb, mc, mc, c, p, stream);       \
-  return launchTc<BNv, TCv, PLAINv>(ma, mb, mc, mc, c, p, stream)
+  if (pair) return launchTc<BNv, TCv, PLAINv, true, true>(ma, mb, mc, mc, c, p, stream); \
+  return launchTc<BNv, TCv, PLAINv, false, true>(ma, mb, mc, mc, c, p, stream)
 #define TTB_TCI_BN(TCv, PLAINv)                                                          \
   switch (bn) {                                                                          \
   case 256: TTB_TCI(256, TCv, PLAINv);                                                   \

@@ -178,7 +178,7 @@ struct PushMaps {
   CUtensorMap m[8];
 };
 
-template <int BN, typename TC, bool PLAIN, bool PAIR, bool I8>
+template <int BN, typename TC, bool PLAIN, bool PAIR, bool I8, bool DUALA>
 __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
     gemmTcgen05Kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                       const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapE,
@@ -217,10 +217,10 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
   };
   // Elements in the 128 bytes of a k-block.  The 8-bit integer form is a template parameter, not a launch parameter: as
   // runtime branches, its issue path and its dequantizing epilogue cost the 16-bit kernels 12 % (measured).
-  constexpr int K_ELEMS = I8 ? 128 : TC_BK;
+  constexpr int K_ELEMS = I8 ? 128 : TC_BK; // (the two-product mode, DUALA, is a template parameter for the same reason: 1-2 %)
   const int kBlocks1 = static_cast<int>((p.K + K_ELEMS - 1) / K_ELEMS);
-  const int kBlocks = kBlocks1 + (p.dualA ? static_cast<int>((p.K2 + K_ELEMS - 1) / K_ELEMS) : 0);
-  const uint32_t accCols = p.dualA ? 2u * BN : static_cast<uint32_t>(BN); // TMEM columns of one accumulator buffer
+  const int kBlocks = kBlocks1 + (DUALA ? static_cast<int>((p.K2 + K_ELEMS - 1) / K_ELEMS) : 0);
+  const uint32_t accCols = DUALA ? 2u * BN : static_cast<uint32_t>(BN); // TMEM columns of one accumulator buffer
 
   if (threadIdx.x == 0) {
     abortFlagS = 0;
@@ -366,7 +366,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
             // rows and rank 1 the up rows of the same output columns).
             const uint32_t bar = mapToCta(fullBar(s), 0);
             if (leader) mbarArriveExpectTx(fullBar(s), 2 * Cfg::kStageBytes);
-            const bool second = p.dualA && kb >= kBlocks1; // k-blocks of the second product
+            const bool second = DUALA && kb >= kBlocks1; // k-blocks of the second product
             const int kc = (second ? kb - kBlocks1 : kb) * K_ELEMS;
             tmaLoad2dPair(sa, second ? &mapE : &mapA, bar, kc, m0);
             if (p.dual) tmaLoad2dPair(sb, leader ? &mapB : &mapB1, bar, kc, n0);
@@ -378,7 +378,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
             // the input patch of this filter tap; coordinates left of / above the image read zeros
             const int tap = kb / cb, ky = tap / p.ckw, kx = tap - ky * p.ckw;
             tmaLoad4d(sa, &mapA, fullBar(s), (kb - tap * cb) * TC_BK, ox0 + kx * p.cdw - p.cpl, oy0 + ky * p.cdh - p.cpt, img);
-          } else if (p.dualA && kb >= kBlocks1) {
+          } else if (DUALA && kb >= kBlocks1) {
             tmaLoad2d(sa, &mapE, fullBar(s), (kb - kBlocks1) * K_ELEMS, m0);
           } else {
             tmaLoad2d(sa, &mapA, fullBar(s), kb * K_ELEMS, m0);
@@ -386,7 +386,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
           if (p.dual) {
             tmaLoad2d(sb, &mapB, fullBar(s), kb * TC_BK, n0);
             tmaLoad2d(sb + (BN / 2) * TC_BK * 2, &mapB1, fullBar(s), kb * TC_BK, n0);
-          } else if (p.dualA && kb >= kBlocks1) {
+          } else if (DUALA && kb >= kBlocks1) {
             tmaLoad2d(sb, &mapB1, fullBar(s), (kb - kBlocks1) * K_ELEMS, n0);
           } else {
             tmaLoad2d(sb, mb, fullBar(s), kb * K_ELEMS, n0);
@@ -408,7 +408,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
         tcFenceAfter();
         const uint32_t tmemD0 = tmemBase + static_cast<uint32_t>(acc) * accCols;
         for (int kb = 0; kb < kBlocks; ++kb, ++it) {
-          const bool second = p.dualA && kb >= kBlocks1;
+          const bool second = DUALA && kb >= kBlocks1;
           const uint32_t tmemD = tmemD0 + (second ? static_cast<uint32_t>(BN) : 0u);
           const int kbIn = second ? kb - kBlocks1 : kb; // the first MMA of a product overwrites the accumulator
           const int s = it % STAGES;
@@ -574,7 +574,7 @@ __global__ void __launch_bounds__(PLAIN ? TC_THREADS : TC_THREADS_EPI8, 1)
         }
       }
       if constexpr (!PLAIN && sizeof(TC) == 2 && BN <= 128) {
-        if (p.dualA) {
+        if constexpr (DUALA) {
           // Two products: columns [0, BN) and [BN, 2 BN) of the buffer; each gets its bias and its own rounding, the
           // sum is rounded again, relu (if any) commutes with that rounding and is applied to the packed pairs.
           dualDone = true;
@@ -1004,7 +1004,7 @@ static bool pairMmaWanted(int64_t m, int64_t k) {
   return !off && m >= 2 * TC_BM && k >= minK && smCount() >= 2;
 }
 
-template <int BN, typename TC, bool PLAIN, bool PAIR = false, bool I8 = false>
+template <int BN, typename TC, bool PLAIN, bool PAIR = false, bool I8 = false, bool DUALA = false>
 static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &me, void *c, const TcParams &p,
                     cudaStream_t st, const CUtensorMap *more = nullptr /* mapB1, mapC1, mapB2, mapC2 of a grouped launch */,
                     const PushMaps *push = nullptr) {
@@ -1014,7 +1014,7 @@ static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensor
   int dev = 0;
   TTB_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attrSet[dev]) {
-    TTB_CUDA(cudaFuncSetAttribute(gemmTcgen05Kernel<BN, TC, PLAIN, PAIR, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+    TTB_CUDA(cudaFuncSetAttribute(gemmTcgen05Kernel<BN, TC, PLAIN, PAIR, I8, DUALA>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
     attrSet[dev] = true;
   }
   const int64_t tileM = PAIR ? 2 * TC_BM : TC_BM;
@@ -1042,7 +1042,7 @@ static int launchTc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensor
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  TTB_CUDA(cudaLaunchKernelEx(&cfg, gemmTcgen05Kernel<BN, TC, PLAIN, PAIR, I8>, ma, mb, mc, me, more ? more[0] : mb, more ? more[1] : mc,
+  TTB_CUDA(cudaLaunchKernelEx(&cfg, gemmTcgen05Kernel<BN, TC, PLAIN, PAIR, I8, DUALA>, ma, mb, mc, me, more ? more[0] : mb, more ? more[1] : mc,
                               more ? more[2] : mb, more ? more[3] : mc, push ? *push : PushMaps{{mc, mc, mc, mc, mc, mc, mc, mc}},
                               static_cast<TC *>(c), p));
   countLaunch();
@@ -1236,8 +1236,8 @@ int gemmTcgen05DualTry(const void *a1, const void *b1, const void *bias1, const 
                  (double(m) * (k1 + k2) + double(n) * (k1 + k2) + double(m) * n) * 2, stream);
   const CUtensorMap more[4] = {mb2, mc, mb2, mc};
 #define TTB_TCD(BNv, TCv)                                                                \
-  if (pair) return launchTc<BNv, TCv, false, true>(ma1, mb1, mc, ma2, out, p, stream, more); \
-  return launchTc<BNv, TCv, false>(ma1, mb1, mc, ma2, out, p, stream, more)
+  if (pair) return launchTc<BNv, TCv, false, true, false, true>(ma1, mb1, mc, ma2, out, p, stream, more); \
+  return launchTc<BNv, TCv, false, false, false, true>(ma1, mb1, mc, ma2, out, p, stream, more)
   if (bn == 128) {
     if (dtype == kBF16) { TTB_TCD(128, __nv_bfloat16); }
     TTB_TCD(128, __half);

@@ -1,7 +1,7 @@
 """The caller-facing boundary without a GPU: the system descriptor in the reference's wire format,
 goldens embedded in a binary, perf::Env, and the stand-in for ttrt's extension module
 (tt-mlir_b200/ttrt_backend/_ttmlir_runtime).  Where a checkout of tenstorrent/tt-mlir is present
-(TT_MLIR_ROOT, or /root/reference), its own `ttrt` Python sources are laid over the stand-in and driven
+(TT_MLIR_ROOT, or a `reference` directory beside this repository), its own `ttrt` Python sources are laid over the stand-in and driven
 unchanged."""
 
 import importlib.util
@@ -18,7 +18,7 @@ from ttmlir_b200 import graphs
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SHIM = os.path.join(ROOT, "tt-mlir_b200", "ttrt_backend", "_ttmlir_runtime")
-REFERENCE = os.environ.get("TT_MLIR_ROOT", "/root/reference")
+REFERENCE = os.environ.get("TT_MLIR_ROOT", os.path.join(os.path.dirname(ROOT), "reference"))
 
 # Every name tools/ttrt/runtime/__init__.py and tools/ttrt/binary/__init__.py import from the extension module.
 RUNTIME_NAMES = """Device Event Tensor TensorRef TensorDesc MemoryBufferType DataType DeviceRuntime HostRuntime DispatchCoreType

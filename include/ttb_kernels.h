@@ -584,6 +584,13 @@ TTB_API int ttb_sdpa(const void *q, const void *k, const void *v, const void *ma
                      int dtype, int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seq_q,
                      int64_t seq_kv, int64_t head_dim, int64_t mask_batch, int64_t mask_heads,
                      int is_causal, float scale, void *stream);
+/* ::ttnn::transformer::flash_mla_prefill (operations/transformer/flash_mla_prefill.cpp; golden
+ * tools/golden/mapping.py:8662-8692): q [B, Hq, Sq, Dqk], k [B, Hkv, Skv, Dqk], v [B, Hkv, Skv, Dv] or null (then the first
+ * Dv columns of k), optional additive mask [B or 1, Hq or 1, Sq, Skv], out [B, Hq, Sq, Dv].  A CUDA-core kernel. */
+TTB_API int ttb_flash_mla_prefill(const void *q, const void *k, const void *v, const void *mask, void *out, int dtype,
+                                  int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seq_q, int64_t seq_kv,
+                                  int64_t head_dim_qk, int64_t head_dim_v, int64_t mask_batch, int64_t mask_heads,
+                                  int is_causal, float scale, void *stream);
 /* Causal attention of a prefill chunk that starts at position `offset`: query row r sees keys 0 .. r + offset
  * (::ttnn::transformer::chunked_scaled_dot_product_attention once its paged keys and values are gathered,
  * operations/transformer/chunked_scaled_dot_product_attention.cpp; golden tools/golden/mapping.py:8847-8912).  The

@@ -389,6 +389,9 @@ class OracleBuilder:
         disp, meta = ops.all_to_all_dispatch(per(x), per(expert_indices), mp)
         return (OValue(disp), OValue(meta)) if isinstance(x.t, list) else (OValue(disp[0]), OValue(meta[0]))
 
+    def flash_mla_prefill(self, q, k, head_dim_v, v=None, mask=None, is_causal=True, scale=None, loc=None):
+        return _map(lambda qt, kt, vt, mt: ops.flash_mla_prefill(qt, kt, vt, mt, head_dim_v, is_causal, scale), q, k, v, mask)
+
     def chunked_scaled_dot_product_attention(self, q, k_cache, v_cache, page_table, chunk_start_idx, scale=None, loc=None):
         start = int(chunk_start_idx.first.reshape(-1)[0])
         return _map(lambda t, kc, vc, pt: ops.chunked_sdpa(t, kc, vc, pt, start, scale), q, k_cache, v_cache, page_table)

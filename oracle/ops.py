@@ -912,3 +912,15 @@ def chunked_sdpa(q, k_cache, v_cache, page_table, chunk_start, scale=None):
     allowed = torch.arange(seq).view(1, seq) <= (chunk_start + torch.arange(sq)).view(sq, 1)
     mask = torch.zeros(1, 1, sq, seq).masked_fill_(~allowed.view(1, 1, sq, seq), torch.finfo(torch.float32).min)
     return torch.nn.functional.scaled_dot_product_attention(q.float(), k, v, attn_mask=mask, scale=scale).to(q.dtype)
+
+
+def flash_mla_prefill(q, k, v, mask, head_dim_v, is_causal, scale=None):
+    """tools/golden/mapping.py:8662-8692: attention whose values are the first head_dim_v key columns unless given;
+    a mask switches the causal flag off; f32, one rounding."""
+    vt = k[..., :head_dim_v] if v is None else v
+    kf, vf = k.float(), vt.float()
+    rep = q.shape[1] // k.shape[1]
+    if rep > 1:
+        kf, vf = kf.repeat_interleave(rep, dim=1), vf.repeat_interleave(rep, dim=1)
+    return torch.nn.functional.scaled_dot_product_attention(
+        q.float(), kf, vf, attn_mask=mask.float() if mask is not None else None, is_causal=is_causal and mask is None, scale=scale).to(q.dtype)

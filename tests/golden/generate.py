@@ -562,6 +562,18 @@ def main():
         store(out, f"map/chunked_sdpa/start{start}", one(ref.ttir_chunked_scaled_dot_product_attention_golden(
             gmt(cq), gmt(ck), gmt(cv), gmt(cpt), gmt(torch.tensor([start], dtype=torch.int32)), None, S.FloatAttr(0.2), S.F32Type())))
 
+    # --- multi-latent attention prefill (mapping.py:8662-8692): 4 q / 1 kv heads, 24 tokens, 48-wide keys, 32-wide values
+    lq, lk = rnd(2, 4, 24, 48), rnd(2, 1, 24, 48)
+    lmask = torch.where(torch.rand(1, 1, 24, 24, generator=g) < 0.3, torch.tensor(float("-inf")), torch.tensor(0.0))
+    lmask[..., 0] = 0.0                                        # no fully masked row
+    for n, t in (("q", lq), ("k", lk), ("mask", lmask)):
+        store(out, f"map/mla/{n}", t)
+    store(out, "map/mla/causal", one(ref.flash_mla_prefill_golden(gmt(lq), gmt(lk), None, None, 32, True, None)))
+    store(out, "map/mla/masked", one(ref.flash_mla_prefill_golden(gmt(lq), gmt(lk), None, gmt(lmask), 32, True, 0.2)))
+    lv = rnd(2, 1, 24, 16)
+    store(out, "map/mla/v", lv)
+    store(out, "map/mla/own_values", one(ref.flash_mla_prefill_golden(gmt(lq), gmt(lk), gmt(lv), None, 16, False, None)))
+
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ttir_cpu_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes")

@@ -431,3 +431,21 @@ def test_chunked_prefill_attention(rt, device, golden):
     got, want = run_body(rt, device, lambda b, *t: b.chunked_scaled_dot_product_attention(*t),
                          [qc, kc8, vc8, table, torch.tensor([960], dtype=torch.int32)])
     assert_matches(got[0], want[0], "chunked attention, 32 heads")
+
+
+def test_flash_mla_prefill_matches_the_reference_goldens(rt, device, golden):
+    q, k, mask, v = (golden[f"map/mla/{n}"] for n in ("q", "k", "mask", "v"))
+    got, want = run_body(rt, device, lambda b, qv, kv: b.flash_mla_prefill(qv, kv, 32), [q, k])
+    assert got[0].shape == (2, 4, 24, 32) and torch.allclose(got[0], golden["map/mla/causal"], rtol=1e-4, atol=1e-5)
+    assert torch.allclose(got[0], want[0], rtol=1e-4, atol=1e-5)
+    got, _ = run_body(rt, device, lambda b, qv, kv, mv: b.flash_mla_prefill(qv, kv, 32, mask=mv, scale=0.2), [q, k, mask])
+    assert torch.allclose(got[0], golden["map/mla/masked"], rtol=1e-4, atol=1e-5)
+    got, _ = run_body(rt, device, lambda b, qv, kv, vv: b.flash_mla_prefill(qv, kv, 16, v=vv, is_causal=False), [q, k, v])
+    assert torch.allclose(got[0], golden["map/mla/own_values"], rtol=1e-4, atol=1e-5)
+    # the latent widths of a DeepSeek-style layer: 576-wide keys (512 latent + 64 rotary), 512-wide values, one kv head
+    torch.manual_seed(19)
+    bf = torch.bfloat16
+    qb, kb = (torch.randn(1, 8, 160, 576) * 0.3).to(bf), (torch.randn(1, 1, 160, 576) * 0.3).to(bf)
+    got, want = run_body(rt, device, lambda b, qv, kv: b.flash_mla_prefill(qv, kv, 512), [qb, kb])
+    assert got[0].shape == (1, 8, 160, 512)
+    assert_matches(got[0], want[0], "flash_mla_prefill bf16, 576 / 512")

@@ -413,6 +413,14 @@ def test_chunked_prefill_attention(golden):
         assert torch.allclose(ops.chunked_sdpa(q, k, v, pt, start, 0.2), golden[f"map/chunked_sdpa/start{start}"], rtol=1e-6, atol=1e-6)
 
 
+def test_multi_latent_attention_prefill(golden):
+    """Restatement against the reference's golden (tools/golden/mapping.py:8662-8692)."""
+    q, k, mask, v = (golden[f"map/mla/{n}"] for n in ("q", "k", "mask", "v"))
+    assert torch.allclose(ops.flash_mla_prefill(q, k, None, None, 32, True), golden["map/mla/causal"], rtol=1e-6, atol=1e-6)
+    assert torch.allclose(ops.flash_mla_prefill(q, k, None, mask, 32, True, 0.2), golden["map/mla/masked"], rtol=1e-6, atol=1e-6)
+    assert torch.allclose(ops.flash_mla_prefill(q, k, v, None, 16, False), golden["map/mla/own_values"], rtol=1e-6, atol=1e-6)
+
+
 def test_layer_norm(golden):
     x, w, b = golden["ln/x"], golden["ln/w"], golden["ln/b"]
     assert same(ops.layer_norm(x), golden["ln/plain"])

@@ -327,6 +327,92 @@ static bool sdpaLegacy() {
 
 using namespace ttb;
 
+// Multi-latent attention prefill (::ttnn::transformer::flash_mla_prefill, operations/transformer/flash_mla_prefill.cpp;
+// golden tools/golden/mapping.py:8662-8692): queries and keys have Dqk columns, values the first Dv columns of the keys
+// (or their own tensor), the result has Dv columns.  One CTA per (batch, head, query row), the row's scores in shared
+// memory, f32 throughout, one rounding: the general kernel above with its own value width and row stride.  A CUDA-core
+// path: the tensor-core attention kernels take head_dim 128 on both sides only.
+template <typename T>
+__global__ void __launch_bounds__(128)
+    mlaPrefillKernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v, const T *__restrict__ mask,
+                     T *__restrict__ out, int64_t Hq, int64_t Hkv, int64_t Sq, int64_t Skv, int64_t Dqk, int64_t Dv, int64_t vRow,
+                     int64_t maskB, int64_t maskH, int causal, float scale) {
+  extern __shared__ float sc[]; // Skv scores + 33 scratch
+  float *scratch = sc + Skv;
+  const int64_t row = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int64_t kvHead = head / (Hq / Hkv);
+  const T *qr = q + (((batch * Hq + head) * Sq) + row) * Dqk;
+  const T *kg = k + ((batch * Hkv + kvHead) * Skv) * Dqk;
+  const T *vg = v + ((batch * Hkv + kvHead) * Skv) * vRow;
+  const T *mr = mask ? mask + ((((maskB > 1 ? batch : 0) * maskH + (maskH > 1 ? head : 0)) * Sq) + row) * Skv : nullptr;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  float mx = -INFINITY;
+  for (int64_t j = warp; j < Skv; j += nwarp) {
+    float acc = 0.0f;
+    for (int64_t d = lane; d < Dqk; d += 32) acc = fmaf(toF32(qr[d]), toF32(kg[j * Dqk + d]), acc);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    float s = acc * scale;
+    if (causal && j > row) s = -INFINITY;
+    if (mr) s += toF32(mr[j]);
+    if (lane == 0) sc[j] = s;
+    mx = fmaxf(mx, s);
+  }
+  if (lane == 0) scratch[warp] = mx;
+  __syncthreads();
+  mx = -INFINITY;
+  for (int w = 0; w < nwarp; ++w) mx = fmaxf(mx, scratch[w]);
+  __syncthreads();
+  float sum = 0.0f;
+  for (int64_t j = threadIdx.x; j < Skv; j += blockDim.x) {
+    const float p = mx == -INFINITY ? 0.0f : expf(sc[j] - mx);
+    sc[j] = p;
+    sum += p;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane == 0) scratch[warp] = sum;
+  __syncthreads();
+  sum = 0.0f;
+  for (int w = 0; w < nwarp; ++w) sum += scratch[w];
+  const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+  T *orow = out + (((batch * Hq + head) * Sq) + row) * Dv;
+  for (int64_t d = threadIdx.x; d < Dv; d += blockDim.x) {
+    float acc = 0.0f;
+    for (int64_t j = 0; j < Skv; ++j) acc = fmaf(sc[j], toF32(vg[j * vRow + d]), acc);
+    orow[d] = fromF32<T>(acc * inv);
+  }
+}
+
+extern "C" int ttb_flash_mla_prefill(const void *q, const void *k, const void *v, const void *mask, void *out, int dtype, int64_t batch,
+                                     int64_t heads_q, int64_t heads_kv, int64_t seq_q, int64_t seq_kv, int64_t head_dim_qk,
+                                     int64_t head_dim_v, int64_t mask_batch, int64_t mask_heads, int is_causal, float scale,
+                                     void *stream) {
+  TTB_CHECK(q && k && out, "null tensor");
+  TTB_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0, "bad head configuration");
+  TTB_CHECK(seq_q > 0 && seq_kv > 0 && head_dim_qk > 0 && head_dim_v > 0, "empty attention problem");
+  TTB_CHECK(v != nullptr || head_dim_v <= head_dim_qk, "values taken from the keys cannot be wider than the keys");
+  TTB_CHECK(batch <= 65535 && heads_q <= 65535 && seq_q <= 2147483647, "grid too large");
+  const size_t smem = (static_cast<size_t>(seq_kv) + 40) * sizeof(float);
+  TTB_CHECK(smem <= 200 * 1024, "sequence too long for the multi-latent attention kernel");
+  cudaStream_t st = asStream(stream);
+  ProfScope prof("flash_mla_prefill", 2.0 * double(batch) * heads_q * seq_q * seq_kv * (head_dim_qk + head_dim_v), 0, st);
+  dim3 grid(static_cast<unsigned>(seq_q), static_cast<unsigned>(heads_q), static_cast<unsigned>(batch));
+  const void *vals = v ? v : k;
+  const int64_t vRow = v ? head_dim_v : head_dim_qk;
+  TTB_DISPATCH_FLOAT(dtype, T, {
+    if (smem > 48 * 1024) {
+      TTB_CUDA(cudaFuncSetAttribute(mlaPrefillKernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    }
+    mlaPrefillKernel<T><<<grid, 128, smem, st>>>(static_cast<const T *>(q), static_cast<const T *>(k), static_cast<const T *>(vals),
+                                                 static_cast<const T *>(mask), static_cast<T *>(out), heads_q, heads_kv, seq_q, seq_kv,
+                                                 head_dim_qk, head_dim_v, vRow, mask_batch, mask_heads, is_causal, scale);
+  });
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
 // Additive mask of a prefill chunk: row r sees keys 0 .. r + offset.  Only for problems the tensor-core kernel,
 // which applies the offset itself, does not take.
 template <typename T>

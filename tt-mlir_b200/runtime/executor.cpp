@@ -122,6 +122,15 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     pushRef(outs, o->metadata());
     break;
   }
+  case OpType::FlashMlaPrefillOp: {
+    const auto *o = op->type_as_FlashMlaPrefillOp();
+    pushRef(ins, o->query());
+    pushRef(ins, o->key());
+    pushRef(ins, o->value());
+    pushRef(ins, o->attention_mask());
+    pushRef(outs, o->out());
+    break;
+  }
   case OpType::ChunkedScaledDotProductAttentionOp: {
     const auto *o = op->type_as_ChunkedScaledDotProductAttentionOp();
     pushRef(ins, o->query());
@@ -864,6 +873,7 @@ private:
   // expert ownership of this process's mesh coordinates: localIdx tensors (Int32 [experts]) from a [1, 1, E, D] mapping
   TensorPtr moeLocalIndex(const TensorPtr &mapping, uint32_t &experts, uint32_t &devices);
   void runAllToAllDispatch(const fbt::AllToAllDispatchOp *op);
+  void runFlashMlaPrefill(const fbt::FlashMlaPrefillOp *op);
   void runChunkedSdpa(const fbt::ChunkedScaledDotProductAttentionOp *op);
   void runConv3d(const fbt::Conv3dOp *op);
   void runGeluBackward(const fbt::ExperimentalEltwiseBinaryBackwardOp *op);
@@ -1246,6 +1256,7 @@ size_t Executor::runOp(size_t i) {
   case OpType::CumSumOp: runCumSum(op->type_as_CumSumOp()); break;
   case OpType::CumProdOp: runCumProd(op->type_as_CumProdOp()); break;
   case OpType::AllToAllDispatchOp: runAllToAllDispatch(op->type_as_AllToAllDispatchOp()); break;
+  case OpType::FlashMlaPrefillOp: runFlashMlaPrefill(op->type_as_FlashMlaPrefillOp()); break;
   case OpType::ChunkedScaledDotProductAttentionOp: runChunkedSdpa(op->type_as_ChunkedScaledDotProductAttentionOp()); break;
   case OpType::Conv3dOp: runConv3d(op->type_as_Conv3dOp()); break;
   case OpType::PrepareConv3dWeightsOp: {
@@ -2836,6 +2847,39 @@ void Executor::runReductionProd(const fbt::ReductionProdOp *op) {
 }
 
 // group_norm on channels-last [N, 1, H*W, C] (or [N, H, W, C]): operations/normalization/group_norm.cpp.
+// flash_mla_prefill: attention whose values are the first head_dim_v columns of the keys (the shared latent of
+// multi-latent attention) unless a value tensor is given; a mask tensor switches the causal flag off, as in the golden.
+void Executor::runFlashMlaPrefill(const fbt::FlashMlaPrefillOp *op) {
+  TensorPtr q = getDevice(op->query()), k = getDevice(op->key());
+  TensorPtr v = op->value() ? getDevice(op->value()) : nullptr, mask = op->attention_mask() ? getDevice(op->attention_mask()) : nullptr;
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(q->shape.size() == 4 && k->shape.size() == 4 && q->shape[0] == k->shape[0] && q->shape[3] == k->shape[3],
+              "flash_mla_prefill expects query [B, H, S, D] and key [B, Hkv, Skv, D]");
+  const int64_t B = q->shape[0], Hq = q->shape[1], Sq = q->shape[2], D = q->shape[3], Hkv = k->shape[1], Skv = k->shape[2];
+  const int64_t Dv = op->head_dim_v();
+  TTRT_ASSERT(Hkv > 0 && Hq % Hkv == 0, "query heads must be a multiple of key heads");
+  TTRT_ASSERT(!v || (v->shape.size() == 4 && v->shape[0] == B && v->shape[1] == Hkv && v->shape[2] == Skv && v->shape[3] == Dv),
+              "flash_mla_prefill value must be [B, Hkv, Skv, head_dim_v]");
+  TTRT_ASSERT(k->dtype == q->dtype && (!v || v->dtype == q->dtype) && out->dtype == q->dtype && (!mask || mask->dtype == q->dtype),
+              "flash_mla_prefill tensors must share one data type");
+  TTRT_ASSERT(out->volume() == static_cast<size_t>(B * Hq * Sq * Dv), "flash_mla_prefill result must be [B, H, S, head_dim_v]");
+  int64_t maskB = 1, maskH = 1;
+  if (mask) {
+    TTRT_ASSERT(mask->shape.size() == 4 && mask->shape[2] == Sq && mask->shape[3] == Skv && (mask->shape[0] == 1 || mask->shape[0] == B) &&
+                    (mask->shape[1] == 1 || mask->shape[1] == Hq),
+                "attention_mask must be [B or 1, H or 1, S, Skv]");
+    maskB = mask->shape[0];
+    maskH = mask->shape[1];
+  }
+  const float scale = op->scale().value_or(1.0f / std::sqrt(static_cast<float>(D)));
+  const int causal = op->is_causal() && !mask ? 1 : 0;
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_flash_mla_prefill(q->shards[i]->ptr, k->shards[i]->ptr, v ? v->shards[i]->ptr : nullptr, mask ? mask->shards[i]->ptr : nullptr,
+                                   out->shards[i]->ptr, ttbDtype(q->dtype), B, Hq, Hkv, Sq, Skv, D, Dv, maskB, maskH, causal, scale, r.stream));
+  });
+  put(op->out(), out);
+}
+
 // chunked_scaled_dot_product_attention (operations/transformer/chunked_scaled_dot_product_attention.cpp; golden
 // tools/golden/mapping.py:8847-8912): one chunk of a long prefill.  query [B, H, Sq, D] holds positions
 // chunk_start .. chunk_start + Sq - 1; keys and values live in a paged cache [blocks, Hkv, block, D] addressed through

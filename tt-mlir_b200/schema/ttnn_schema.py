@@ -380,6 +380,9 @@ S.table("ChunkedScaledDotProductAttentionOp", [
     ("query", "TensorRef"), ("key", "TensorRef"), ("value", "TensorRef"), ("page_table", "TensorRef"),
     ("chunk_start_idx", "TensorRef"), ("scale", "f32", OPT), ("out", "TensorRef"), ("memcfg", "MemoryConfig"),
     ("program_config", "opaque")])
+S.table("FlashMlaPrefillOp", [
+    ("query", "TensorRef"), ("key", "TensorRef"), ("value", "TensorRef"), ("attention_mask", "TensorRef"),
+    ("head_dim_v", "u32"), ("is_causal", "bool"), ("scale", "f32", OPT), ("out", "TensorRef"), ("memcfg", "MemoryConfig")])
 S.table("UniformScale2D", [("scale", "i32")])
 S.table("NonUniformScale2D", [("scale", "[i32]")])
 S.union("Scale2D", ["UniformScale2D", "NonUniformScale2D"])

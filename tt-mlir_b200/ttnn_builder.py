@@ -811,6 +811,18 @@ class ProgramBuilder:
     def reset_global_semaphore(self, value: int = 0, loc=None) -> None:
         self._emit("ResetGlobalSemaphoreOp", {"semaphore": {"global_id": 0}, "value": value}, [], [], loc)
 
+    def flash_mla_prefill(self, q: Value, k: Value, head_dim_v: int, v: Optional[Value] = None, mask: Optional[Value] = None,
+                          is_causal: bool = True, scale: Optional[float] = None, loc=None) -> Value:
+        """q [B, H, S, Dqk], k [B, Hkv, Skv, Dqk]; values are k[..., :head_dim_v] unless `v` is given."""
+        out = self._value(list(q.shape[:3]) + [head_dim_v], q.dtype)
+        t = {"query": q.ref, "key": k.ref, "value": v.ref if v is not None else None,
+             "attention_mask": mask.ref if mask is not None else None, "head_dim_v": head_dim_v, "is_causal": is_causal,
+             "out": out.ref, "memcfg": self._mc()}
+        if scale is not None:
+            t["scale"] = scale
+        self._emit("FlashMlaPrefillOp", t, [q, k] + [x for x in (v, mask) if x is not None], [out], loc)
+        return out
+
     def chunked_scaled_dot_product_attention(self, q: Value, k_cache: Value, v_cache: Value, page_table: Value, chunk_start_idx: Value,
                                              scale: Optional[float] = None, loc=None) -> Value:
         """q [B, H, Sq, D] (positions chunk_start ..), caches [blocks, Hkv, block, D], page_table [B, blocks per user]."""

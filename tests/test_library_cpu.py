@@ -148,7 +148,58 @@ def _close(a, b, path="$"):
         assert a == b, f"{path}: {a!r} vs {b!r}"
 
 
-@pytest.mark.parametrize("which", ["decoder", "quant", "traced", "pool"])
+def _wide_ops_graph(b):
+    """One op of every family that widens the op coverage: their tables go through the writer, the C++ reader /
+    verifier and the generated JSON printers without a GPU."""
+    bf = "BFloat16"
+    x = b.input([2, 6, 6, 8], bf)
+    v = b.input([4, 16], "Float32")
+    outs = [b.cumprod(v, 1), b.prod(v, 1), b.upsample(x, 2), b.group_norm(b.reshape(x, [2, 1, 36, 8]), None, None, 2),
+            b.bitcast_convert(v, "Int32"), b.assign(v, bf), b.pow_scalar(v, 2.0), b.dropout(v, 0.1, seed=3), b.rand([4, 4], "Float32"),
+            b.region_end(b.region_start(b.annotate(v, "note"), "r"), "r")]
+    b.print_message(v, "hello")
+    b.breakpoint(v)
+    b.memory_snapshot(v, "snapshot.txt")
+    b.dump_tensor(v, "t.bin")
+    outs.append(b.load_tensor("t.bin", [4, 16], "Float32"))
+    mean, var = b.input([6], bf), b.input([6], bf)
+    nchw = b.input([2, 6, 4, 4], bf)
+    outs += [b.batch_norm_inference(nchw, mean, var, None, None), b.batch_norm_training(nchw, mean, var, None, None)]
+    w = b.input([8, 4, 3, 3], bf)
+    outs.append(b.conv_transpose2d(x, b.prepare_conv_transpose2d_weights(w, 2, 6, 6), None, 2, 6, 6))
+    outs.append(b.conv1d(b.input([2, 10, 8], bf), b.input([4, 8, 3], bf), None, 2, 10))
+    outs.append(b.conv3d(b.input([1, 1, 2 * 3 * 4 * 4, 8], bf), b.prepare_conv3d_weights(b.input([4, 8, 2, 2, 2], bf)), None, 2, 3, 4, 4))
+    pooled, idx = b.max_pool2d_with_indices(b.reshape(x, [1, 1, 72, 8]), 2, 6, 6, 8)
+    outs += [pooled, idx]
+    q, k, vv = b.nlp_create_qkv_heads_decode(b.input([1, 1, 4, (2 + 2) * 32], bf), 2, 1)
+    outs += [b.nlp_concat_heads_decode(q, 2), k, vv, b.nlp_concat_heads(b.input([1, 2, 4, 32], bf))]
+    rx = b.input([1, 2, 32, 64], bf)
+    outs.append(b.rotary_embedding_llama(rx, b.input([1, 1, 32, 64], bf), b.input([1, 1, 32, 64], bf), b.input([1, 1, 32, 32], bf)))
+    nx = b.input([4, 64], bf)
+    outs += [b.dit_rms_norm_unary_fused(nx, activation="silu"), b.distributed_rms_norm(nx), b.rms_norm_pre_all_gather(nx),
+             b.layer_norm_post_all_gather(nx, b.layer_norm_pre_all_gather(nx))]
+    b.create_global_semaphore(0)
+    b.reset_global_semaphore(0)
+    tok, sel = b.input([4, 1, 2, 16], bf), b.input([4, 1, 2, 2], "Int32")
+    mp = b.input([1, 1, 4, 1], "Int32")
+    disp, meta = b.all_to_all_dispatch(tok, sel, mp)
+    mapping, reduced = b.moe_expert_token_remap(b.input([1, 4, 2, 4], bf), mp, meta, 8)
+    sm = b.sparse_matmul(b.input([1, 1, 32, 16], bf), b.input([1, 4, 16, 16], bf), b.input([1, 1, 1, 4], bf), nnz=2)
+    outs += [disp, mapping, reduced, sm, b.all_to_all_combine(b.input([4, 4, 2, 16], bf), meta, mp, 2)]
+    d3, i3, s3 = b.all_to_all_dispatch_metadata(b.input([1, 1, 8, 16], bf), b.input([1, 1, 8, 2], "Int32"), b.input([1, 1, 8, 2], bf),
+                                               b.input([1, 1, 1, 4], "Int32"))
+    ri, rw = b.topk_router_gpt(b.input([32, 64], bf), b.input([64, 16], bf), b.input([32, 16], bf), 4)
+    outs += [d3, i3, s3, ri, rw, b.all_reduce_async(nx), b.point_to_point(nx, [0, 0], [0, 0])]
+    outs += [b.gelu_backward(nx, nx, "tanh"), b.embedding_backward(b.input([2, 3], "Int32"), b.input([10, 64], bf), b.input([2, 3, 64], bf))]
+    b.adamw(b.input([8], "Float32"), b.input([8], "Float32"), b.input([8], "Float32"), b.input([8], "Float32"))
+    qc = b.input([1, 2, 16, 32], bf)
+    outs.append(b.chunked_scaled_dot_product_attention(qc, b.input([4, 1, 16, 32], bf), b.input([4, 1, 16, 32], bf),
+                                                       b.input([1, 2], "Int32"), b.input([1], "Int32"), scale=0.2))
+    outs.append(b.flash_mla_prefill(b.input([1, 2, 8, 48], bf), b.input([1, 1, 8, 48], bf), 32))
+    b.output(*outs)
+
+
+@pytest.mark.parametrize("which", ["decoder", "quant", "traced", "pool", "wide"])
 def test_json_views_print_every_declared_field(rt, which):
     """Binary::asJson / getProgramOpsAsJson (the generated printers) against the independent Python
     reader of the same buffer: every table, union, struct, enum and optional scalar of every op."""
@@ -161,6 +212,8 @@ def test_json_views_print_every_declared_field(rt, which):
         buf = graphs.build_binary(graphs.quant_chain_graph, rows=8, cols=8, keep_intermediates=True)
     elif which == "traced":
         buf = graphs.mlp_traced_binary(batch=4, d_in=8, d_hidden=8, d_out=4)
+    elif which == "wide":
+        buf = graphs.build_binary(_wide_ops_graph)
     else:
         def g(b):
             x = b.input([1, 1, 2 * 9 * 11, 8], "BFloat16")

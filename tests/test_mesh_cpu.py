@@ -55,6 +55,75 @@ def test_collective_semantics_with_gloo_ranks():
         assert dict(ret) == {0: True, 1: True}
 
 
+def _moe_worker(rank, world, port, ret):
+    """The exchange the runtime performs for the mixture-of-experts ops, replayed with real collectives: dispatch =
+    all-gather of tokens and expert indices + a local mask; combine = every rank writes, for every destination, the rows
+    of the experts it owns (zeros elsewhere) and a sum reduce-scatter delivers them; the split normalisations exchange one
+    statistic per row.  Each against the oracle's per-device results."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(11)
+        B, S, H, E, K = 4, 3, 8, 4, 2                           # per rank; experts 2r and 2r + 1 live on rank r
+        tokens = [torch.randn(B, 1, S, H, generator=g) for _ in range(world)]
+        select = [torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(B * S)]).to(torch.int32).reshape(B, 1, S, K)
+                  for _ in range(world)]
+        mapping = torch.zeros(1, 1, E, world, dtype=torch.int32)
+        for e in range(E):
+            mapping[0, 0, e, e // 2] = 1
+        want_disp, want_meta = ops.all_to_all_dispatch(tokens, select, mapping)
+        # dispatch
+        parts = [torch.empty(B, 1, S, H) for _ in range(world)]
+        dist.all_gather(parts, tokens[rank])
+        idx = [torch.empty(B, 1, S, K, dtype=torch.int32) for _ in range(world)]
+        dist.all_gather(idx, select[rank])
+        full, meta = torch.cat(parts, 0).reshape(1, world * B, S, H), torch.cat(idx, 0).reshape(1, world * B, S, K)
+        mine = [e for e in range(E) if int(mapping[0, 0, e, rank])]
+        routed = torch.isin(meta, torch.tensor(mine, dtype=torch.int32)).any(-1, keepdim=True)
+        disp = torch.where(routed, full, torch.zeros_like(full))
+        ok = torch.equal(disp, want_disp[rank]) and torch.equal(meta, want_meta[rank])
+        # identity experts: local expert le hands every dispatched row back
+        expert_out = torch.stack([disp[0]] * len(mine))           # [E_local, world * B, S, H]
+        want_back = ops.all_to_all_combine([torch.stack([d[0]] * 2) for d in want_disp], meta, mapping, K)
+        partial = torch.zeros(world, K, B, S, H)
+        for p in range(world):
+            for slot in range(K):
+                for b in range(B):
+                    for s_ in range(S):
+                        e = int(meta[0, p * B + b, s_, slot])
+                        if e in mine:
+                            partial[p, slot, b, s_] = expert_out[mine.index(e), p * B + b, s_]
+        dist.all_reduce(partial)                                # gloo has no reduce_scatter: reduce everything, keep the own block
+        back = partial[rank]
+        ok = ok and torch.equal(back, want_back[rank]) and torch.equal(back, torch.stack([tokens[rank].reshape(B, S, H)] * K))
+        # distributed rms norm: local sums of squares, one all-reduce of a float per row, local normalisation
+        x = [torch.randn(5, 16, generator=g) for _ in range(world)]
+        w = [torch.rand(16, generator=g) + 0.5 for _ in range(world)]
+        ss = x[rank].square().sum(-1, keepdim=True)
+        dist.all_reduce(ss)
+        got = x[rank] * torch.rsqrt(ss / (16 * world) + 1e-5) * w[rank]
+        ok = ok and torch.allclose(got, ops.distributed_rms_norm(x, w, None, 1e-5)[rank], rtol=1e-6, atol=1e-6)
+        # layer norm: pre statistics, all-gather along the last dimension, post
+        stats = [torch.empty(5, 64) for _ in range(world)]
+        dist.all_gather(stats, ops.layer_norm_pre_all_gather(x[rank], None, torch.float32))
+        post = ops.layer_norm_post_all_gather(x[rank], torch.cat(stats, -1), w[rank], None, 1e-5)
+        whole = torch.nn.functional.layer_norm(torch.cat(x, -1), [16 * world], torch.cat(w), None, 1e-5)
+        ok = ok and torch.allclose(post, whole[:, 16 * rank: 16 * rank + 16], rtol=1e-5, atol=1e-5)
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_moe_exchange_and_split_norms_with_gloo_ranks():
+    world = 2
+    port = 31500 + (os.getpid() % 2000)
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_moe_worker, args=(world, port, ret), nprocs=world, join=True)
+        assert dict(ret) == {0: True, 1: True}
+
+
 def test_tensor_parallel_sharding_covers_every_weight_once():
     kw = dict(seq=64, hidden=128, n_heads=4, n_kv_heads=2, head_dim=32, ffn=256)
     ins = graphs.decoder_block_inputs(**kw)

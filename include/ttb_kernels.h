@@ -591,6 +591,9 @@ TTB_API int ttb_flash_mla_prefill(const void *q, const void *k, const void *v, c
                                   int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seq_q, int64_t seq_kv,
                                   int64_t head_dim_qk, int64_t head_dim_v, int64_t mask_batch, int64_t mask_heads,
                                   int is_causal, float scale, void *stream);
+/* mask[u, 0, 0, j] = 0 for j <= cur_pos[u], -inf beyond: the additive mask of one decode step per user
+ * (::ttnn::transformer::paged_flash_multi_latent_attention_decode builds the same from its cur_pos tensor). */
+TTB_API int ttb_cur_pos_mask(void *mask, const int32_t *cur_pos, int dtype, int64_t users, int64_t seq_kv, void *stream);
 /* Causal attention of a prefill chunk that starts at position `offset`: query row r sees keys 0 .. r + offset
  * (::ttnn::transformer::chunked_scaled_dot_product_attention once its paged keys and values are gathered,
  * operations/transformer/chunked_scaled_dot_product_attention.cpp; golden tools/golden/mapping.py:8847-8912).  The

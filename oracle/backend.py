@@ -392,6 +392,11 @@ class OracleBuilder:
     def flash_mla_prefill(self, q, k, head_dim_v, v=None, mask=None, is_causal=True, scale=None, loc=None):
         return _map(lambda qt, kt, vt, mt: ops.flash_mla_prefill(qt, kt, vt, mt, head_dim_v, is_causal, scale), q, k, v, mask)
 
+    def paged_flash_multi_latent_attention_decode(self, q, k_cache, head_dim_v, page_table, v_cache=None, cur_pos=None, mask=None,
+                                                  is_causal=True, scale=None, loc=None):
+        return _map(lambda qt, kc, pt, vc, cp, mt: ops.paged_mla_decode(qt, kc, vc, pt, cp, mt, head_dim_v, is_causal, scale),
+                    q, k_cache, page_table, v_cache, cur_pos, mask)
+
     def chunked_scaled_dot_product_attention(self, q, k_cache, v_cache, page_table, chunk_start_idx, scale=None, loc=None):
         start = int(chunk_start_idx.first.reshape(-1)[0])
         return _map(lambda t, kc, vc, pt: ops.chunked_sdpa(t, kc, vc, pt, start, scale), q, k_cache, v_cache, page_table)

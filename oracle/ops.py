@@ -924,3 +924,28 @@ def flash_mla_prefill(q, k, v, mask, head_dim_v, is_causal, scale=None):
         kf, vf = kf.repeat_interleave(rep, dim=1), vf.repeat_interleave(rep, dim=1)
     return torch.nn.functional.scaled_dot_product_attention(
         q.float(), kf, vf, attn_mask=mask.float() if mask is not None else None, is_causal=is_causal and mask is None, scale=scale).to(q.dtype)
+
+
+def paged_mla_decode(q, k_cache, v_cache, page_table, cur_pos, mask, head_dim_v, is_causal=True, scale=None):
+    """tools/golden/mapping.py:8275-8365: q [1, B, H, D]; the latent cache is un-paged through the page table, values are
+    its first head_dim_v columns unless a value cache is given, user b sees keys 0 .. cur_pos[b]; scale defaults to 1."""
+    qf = q.permute(1, 2, 0, 3).float()
+    b, nh, _, d = qf.shape
+    nblocks, nkv, bs, _ = k_cache.shape
+    per_user = page_table.shape[-1]
+    pt = page_table.to(torch.int64).reshape(-1)
+    seq = per_user * bs
+    unpage = lambda c: c[pt].reshape(b, per_user, nkv, bs, c.shape[-1]).transpose(1, 2).reshape(b, nkv, seq, c.shape[-1]).float()
+    k = unpage(k_cache)
+    v = unpage(v_cache) if v_cache is not None else k[..., :head_dim_v]
+    rep = nh // nkv
+    k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
+    am = None
+    if mask is not None:
+        am = mask.float()
+    elif is_causal and cur_pos is not None:
+        am = torch.zeros(b, nh, 1, seq)
+        for i in range(b):
+            am[i, :, :, int(cur_pos[i]) + 1:] = torch.finfo(torch.float32).min
+    out = torch.nn.functional.scaled_dot_product_attention(qf, k, v, attn_mask=am, scale=1.0 if scale is None else scale)
+    return out.permute(2, 0, 1, 3).to(q.dtype)

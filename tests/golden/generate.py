@@ -574,6 +574,19 @@ def main():
     store(out, "map/mla/v", lv)
     store(out, "map/mla/own_values", one(ref.flash_mla_prefill_golden(gmt(lq), gmt(lk), gmt(lv), None, 16, False, None)))
 
+    # --- paged multi-latent decode attention (mapping.py:8275-8365): 3 users, 4 heads on one latent head, block 8, 4 blocks each
+    dq, dk = rnd(1, 3, 4, 48) * 0.5, rnd(14, 1, 8, 48) * 0.5
+    dpt = torch.stack([torch.randperm(14, generator=g)[:4] for _ in range(3)]).to(torch.int32)
+    dpos = torch.tensor([5, 31, 17], dtype=torch.int32)
+    for n, t in (("q", dq), ("k", dk), ("page_table", dpt), ("cur_pos", dpos)):
+        store(out, f"map/mla_decode/{n}", t)
+    store(out, "map/mla_decode/latent", one(ref.ttir_paged_flash_multi_latent_attention_decode_golden(
+        gmt(dq), gmt(dk), None, gmt(dpt), None, gmt(dpos), None, S.IntegerAttr(32), S.BoolAttr(True), None, S.F32Type())))
+    dv = rnd(14, 1, 8, 16)
+    store(out, "map/mla_decode/v", dv)
+    store(out, "map/mla_decode/own_values", one(ref.ttir_paged_flash_multi_latent_attention_decode_golden(
+        gmt(dq), gmt(dk), gmt(dv), gmt(dpt), None, gmt(dpos), None, S.IntegerAttr(16), S.BoolAttr(True), S.FloatAttr(0.15), S.F32Type())))
+
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ttir_cpu_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes")

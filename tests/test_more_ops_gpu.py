@@ -449,3 +449,26 @@ def test_flash_mla_prefill_matches_the_reference_goldens(rt, device, golden):
     got, want = run_body(rt, device, lambda b, qv, kv: b.flash_mla_prefill(qv, kv, 512), [qb, kb])
     assert got[0].shape == (1, 8, 160, 512)
     assert_matches(got[0], want[0], "flash_mla_prefill bf16, 576 / 512")
+
+
+def test_paged_multi_latent_decode_attention_matches_the_reference_goldens(rt, device, golden):
+    q, k, pt, pos, v = (golden[f"map/mla_decode/{n}"] for n in ("q", "k", "page_table", "cur_pos", "v"))
+    got, want = run_body(rt, device, lambda b, qv, kv, tv, pv: b.paged_flash_multi_latent_attention_decode(qv, kv, 32, tv, cur_pos=pv),
+                         [q, k, pt, pos])
+    assert got[0].shape == (1, 3, 4, 32) and torch.allclose(got[0], golden["map/mla_decode/latent"], rtol=1e-4, atol=1e-5)
+    assert torch.allclose(got[0], want[0], rtol=1e-4, atol=1e-5)
+    got, _ = run_body(rt, device, lambda b, qv, kv, tv, pv, vv: b.paged_flash_multi_latent_attention_decode(qv, kv, 16, tv, v_cache=vv,
+                                                                                                          cur_pos=pv, scale=0.15),
+                      [q, k, pt, pos, v])
+    assert torch.allclose(got[0], golden["map/mla_decode/own_values"], rtol=1e-4, atol=1e-5)
+    # latent widths of a DeepSeek-style layer, bf16: 32 users x 16 heads on one 576-wide latent head, 512-wide values
+    torch.manual_seed(20)
+    bf = torch.bfloat16
+    qb = (torch.randn(1, 32, 16, 576) * 0.1).to(bf)
+    kb = (torch.randn(160, 1, 32, 576) * 0.1).to(bf)
+    table = torch.stack([torch.randperm(160)[:4] for _ in range(32)]).to(torch.int32)
+    cur = torch.randint(0, 128, (32,), dtype=torch.int32)
+    got, want = run_body(rt, device, lambda b, qv, kv, tv, pv: b.paged_flash_multi_latent_attention_decode(qv, kv, 512, tv, cur_pos=pv, scale=0.05),
+                         [qb, kb, table, cur])
+    assert got[0].shape == (1, 32, 16, 512)
+    assert_matches(got[0], want[0], "paged MLA decode bf16, 576 / 512")

@@ -421,6 +421,13 @@ def test_multi_latent_attention_prefill(golden):
     assert torch.allclose(ops.flash_mla_prefill(q, k, v, None, 16, False), golden["map/mla/own_values"], rtol=1e-6, atol=1e-6)
 
 
+def test_paged_multi_latent_decode_attention(golden):
+    """Restatement against the reference's golden (tools/golden/mapping.py:8275-8365)."""
+    q, k, pt, pos, v = (golden[f"map/mla_decode/{n}"] for n in ("q", "k", "page_table", "cur_pos", "v"))
+    assert torch.allclose(ops.paged_mla_decode(q, k, None, pt, pos, None, 32), golden["map/mla_decode/latent"], rtol=1e-6, atol=1e-6)
+    assert torch.allclose(ops.paged_mla_decode(q, k, v, pt, pos, None, 16, True, 0.15), golden["map/mla_decode/own_values"], rtol=1e-6, atol=1e-6)
+
+
 def test_layer_norm(golden):
     x, w, b = golden["ln/x"], golden["ln/w"], golden["ln/b"]
     assert same(ops.layer_norm(x), golden["ln/plain"])

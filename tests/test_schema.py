@@ -89,6 +89,6 @@ def test_executor_dispatches_every_declared_op():
     assert declared <= dispatched, f"declared but not dispatched: {sorted(declared - dispatched)}"
     assert set(UNDECLARED_OPS) == {
         "GenericOp", "IndexerScoreDsaOp", "MoeGptOp", "PrepareMoEComputeW0W1WeightsOp", "PrepareMoEComputeW2WeightsOp", "MoeComputeOp",
-        "PagedFlashMultiLatentAttentionDecodeOp", "SDPAForwardOp", "SDPABackwardOp", "SelectiveReduceCombineOp"}
+        "SDPAForwardOp", "SDPABackwardOp", "SelectiveReduceCombineOp"}
     assert not (set(UNDECLARED_OPS) & dispatched)
     assert len(OP_TYPE_MEMBERS) == 131

@@ -413,6 +413,28 @@ extern "C" int ttb_flash_mla_prefill(const void *q, const void *k, const void *v
   return TTB_OK;
 }
 
+// Additive mask of a decode step: user u sees keys 0 .. cur_pos[u] ([users, 1, 1, seq_kv], 0 or -inf).
+template <typename T>
+__global__ void __launch_bounds__(256) curPosMaskKernel(T *__restrict__ mask, const int32_t *__restrict__ curPos, int64_t users, int64_t seqKv) {
+  const size_t total = static_cast<size_t>(users) * seqKv, stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t u = static_cast<int64_t>(i / seqKv), c = static_cast<int64_t>(i % seqKv);
+    mask[i] = fromF32<T>(c <= static_cast<int64_t>(curPos[u]) ? 0.0f : -INFINITY);
+  }
+}
+
+extern "C" int ttb_cur_pos_mask(void *mask, const int32_t *cur_pos, int dtype, int64_t users, int64_t seq_kv, void *stream) {
+  TTB_CHECK(mask && cur_pos, "null tensor");
+  TTB_CHECK(users > 0 && seq_kv > 0, "empty mask");
+  cudaStream_t st = asStream(stream);
+  TTB_DISPATCH_FLOAT(dtype, T,
+                     (curPosMaskKernel<T><<<gridFor(static_cast<size_t>(users) * seq_kv, 256), 256, 0, st>>>(static_cast<T *>(mask), cur_pos,
+                                                                                                          users, seq_kv)));
+  countLaunch();
+  TTB_LAUNCH_CHECK();
+  return TTB_OK;
+}
+
 // Additive mask of a prefill chunk: row r sees keys 0 .. r + offset.  Only for problems the tensor-core kernel,
 // which applies the offset itself, does not take.
 template <typename T>

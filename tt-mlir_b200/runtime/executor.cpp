@@ -122,6 +122,18 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     pushRef(outs, o->metadata());
     break;
   }
+  case OpType::PagedFlashMultiLatentAttentionDecodeOp: {
+    const auto *o = op->type_as_PagedFlashMultiLatentAttentionDecodeOp();
+    pushRef(ins, o->query());
+    pushRef(ins, o->key());
+    pushRef(ins, o->value());
+    pushRef(ins, o->page_table());
+    pushRef(ins, o->attention_mask());
+    pushRef(ins, o->cur_pos_tensor());
+    pushRef(ins, o->attention_sink());
+    pushRef(outs, o->out());
+    break;
+  }
   case OpType::FlashMlaPrefillOp: {
     const auto *o = op->type_as_FlashMlaPrefillOp();
     pushRef(ins, o->query());
@@ -873,6 +885,7 @@ private:
   // expert ownership of this process's mesh coordinates: localIdx tensors (Int32 [experts]) from a [1, 1, E, D] mapping
   TensorPtr moeLocalIndex(const TensorPtr &mapping, uint32_t &experts, uint32_t &devices);
   void runAllToAllDispatch(const fbt::AllToAllDispatchOp *op);
+  void runPagedMlaDecode(const fbt::PagedFlashMultiLatentAttentionDecodeOp *op);
   void runFlashMlaPrefill(const fbt::FlashMlaPrefillOp *op);
   void runChunkedSdpa(const fbt::ChunkedScaledDotProductAttentionOp *op);
   void runConv3d(const fbt::Conv3dOp *op);
@@ -1256,6 +1269,7 @@ size_t Executor::runOp(size_t i) {
   case OpType::CumSumOp: runCumSum(op->type_as_CumSumOp()); break;
   case OpType::CumProdOp: runCumProd(op->type_as_CumProdOp()); break;
   case OpType::AllToAllDispatchOp: runAllToAllDispatch(op->type_as_AllToAllDispatchOp()); break;
+  case OpType::PagedFlashMultiLatentAttentionDecodeOp: runPagedMlaDecode(op->type_as_PagedFlashMultiLatentAttentionDecodeOp()); break;
   case OpType::FlashMlaPrefillOp: runFlashMlaPrefill(op->type_as_FlashMlaPrefillOp()); break;
   case OpType::ChunkedScaledDotProductAttentionOp: runChunkedSdpa(op->type_as_ChunkedScaledDotProductAttentionOp()); break;
   case OpType::Conv3dOp: runConv3d(op->type_as_Conv3dOp()); break;
@@ -2847,6 +2861,65 @@ void Executor::runReductionProd(const fbt::ReductionProdOp *op) {
 }
 
 // group_norm on channels-last [N, 1, H*W, C] (or [N, H, W, C]): operations/normalization/group_norm.cpp.
+// paged_flash_multi_latent_attention_decode (operations/transformer/paged_flash_multi_latent_attention_decode.cpp;
+// golden tools/golden/mapping.py:8275-8365): one query token per user, [1, B, H, D], against a paged latent cache
+// [blocks, Hkv, block, D]; values are the first head_dim_v columns of the keys unless a paged value cache is given;
+// user u sees keys 0 .. cur_pos[u]; the scale defaults to 1, as in the golden.  The user's pages are gathered into one
+// sequence and the multi-latent attention kernel runs with one query row per (user, head).
+void Executor::runPagedMlaDecode(const fbt::PagedFlashMultiLatentAttentionDecodeOp *op) {
+  TTRT_ASSERT(!op->attention_sink(), "attention sinks are not supported");
+  TensorPtr q = getDevice(op->query()), kc = getDevice(op->key()), table = getDevice(op->page_table());
+  TensorPtr vc = op->value() ? getDevice(op->value()) : nullptr;
+  TensorPtr maskIn = op->attention_mask() ? getDevice(op->attention_mask()) : nullptr;
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(q->shape.size() == 4 && q->shape[0] == 1 && kc->shape.size() == 4 && table->shape.size() == 2,
+              "paged MLA decode expects query [1, B, H, D], a cache [blocks, Hkv, block, D] and page_table [B, blocks per user]");
+  const int64_t B = q->shape[1], Hq = q->shape[2], D = q->shape[3];
+  const int64_t numBlocks = kc->shape[0], Hkv = kc->shape[1], blockSize = kc->shape[2], perUser = table->shape[1];
+  const int64_t Dv = op->head_dim_v(), Skv = perUser * blockSize;
+  TTRT_ASSERT(kc->shape[3] == D && table->shape[0] == B && Hkv > 0 && Hq % Hkv == 0, "paged MLA decode operands do not fit together");
+  TTRT_ASSERT(!vc || (vc->shape.size() == 4 && vc->shape[0] == numBlocks && vc->shape[1] == Hkv && vc->shape[2] == blockSize && vc->shape[3] == Dv),
+              "the value cache must be [blocks, Hkv, block, head_dim_v]");
+  TTRT_ASSERT(kc->dtype == q->dtype && (!vc || vc->dtype == q->dtype) && out->dtype == q->dtype && (!maskIn || maskIn->dtype == q->dtype) &&
+                  out->volume() == static_cast<size_t>(B * Hq * Dv),
+              "paged MLA decode tensors must share one data type and the result must be [1, B, H, head_dim_v]");
+  TensorPtr tbl = table->dtype == DataType::Int32 || table->dtype == DataType::UInt32 ? table : castOnDevice(table, DataType::Int32);
+  TensorPtr k = makeDeviceTensor(dev, {static_cast<uint32_t>(B), static_cast<uint32_t>(Hkv), static_cast<uint32_t>(Skv), static_cast<uint32_t>(D)}, q->dtype);
+  TensorPtr v = vc ? makeDeviceTensor(dev, {static_cast<uint32_t>(B), static_cast<uint32_t>(Hkv), static_cast<uint32_t>(Skv), static_cast<uint32_t>(Dv)}, q->dtype)
+                   : nullptr;
+  TensorPtr mask = maskIn;
+  int64_t maskB = 1, maskH = 1;
+  TensorPtr pos;
+  if (maskIn) {
+    TTRT_ASSERT(maskIn->shape.size() == 4 && maskIn->shape[3] == Skv && maskIn->volume() == static_cast<size_t>(maskIn->shape[0]) * maskIn->shape[1] * Skv &&
+                    (maskIn->shape[0] == 1 || maskIn->shape[0] == B) && (maskIn->shape[1] == 1 || maskIn->shape[1] == Hq),
+                "attention_mask must be [B or 1, H or 1, 1, keys]");
+    maskB = maskIn->shape[0];
+    maskH = maskIn->shape[1];
+  } else if (op->is_causal() && op->cur_pos_tensor()) {
+    pos = castOnDevice(getDevice(op->cur_pos_tensor()), DataType::Int32);
+    TTRT_ASSERT(pos->volume() == static_cast<size_t>(B), "cur_pos_tensor must have one position per user");
+    mask = makeDeviceTensor(dev, {static_cast<uint32_t>(B), 1, 1, static_cast<uint32_t>(Skv)}, q->dtype);
+    maskB = B;
+  }
+  const float scale = op->scale().value_or(1.0f);
+  eachRank([&](size_t i, const RankCtx &r) {
+    TTB_CALL(ttb_paged_gather(kc->shards[i]->ptr, tbl->shards[i]->ptr, k->shards[i]->ptr, ttbDtype(q->dtype), ttbDtype(tbl->dtype), B, Hkv,
+                              blockSize, perUser, D, numBlocks, r.stream));
+    if (vc) {
+      TTB_CALL(ttb_paged_gather(vc->shards[i]->ptr, tbl->shards[i]->ptr, v->shards[i]->ptr, ttbDtype(q->dtype), ttbDtype(tbl->dtype), B, Hkv,
+                                blockSize, perUser, Dv, numBlocks, r.stream));
+    }
+    if (pos) {
+      TTB_CALL(ttb_cur_pos_mask(mask->shards[i]->ptr, static_cast<const int32_t *>(pos->shards[i]->ptr), ttbDtype(q->dtype), B, Skv, r.stream));
+    }
+    // [1, B, H, D] is [B, H, 1, D] in memory: one query row per (user, head)
+    TTB_CALL(ttb_flash_mla_prefill(q->shards[i]->ptr, k->shards[i]->ptr, v ? v->shards[i]->ptr : nullptr, mask ? mask->shards[i]->ptr : nullptr,
+                                   out->shards[i]->ptr, ttbDtype(q->dtype), B, Hq, Hkv, 1, Skv, D, Dv, maskB, maskH, 0, scale, r.stream));
+  });
+  put(op->out(), out);
+}
+
 // flash_mla_prefill: attention whose values are the first head_dim_v columns of the keys (the shared latent of
 // multi-latent attention) unless a value tensor is given; a mask tensor switches the causal flag off, as in the golden.
 void Executor::runFlashMlaPrefill(const fbt::FlashMlaPrefillOp *op) {

@@ -383,6 +383,10 @@ S.table("ChunkedScaledDotProductAttentionOp", [
 S.table("FlashMlaPrefillOp", [
     ("query", "TensorRef"), ("key", "TensorRef"), ("value", "TensorRef"), ("attention_mask", "TensorRef"),
     ("head_dim_v", "u32"), ("is_causal", "bool"), ("scale", "f32", OPT), ("out", "TensorRef"), ("memcfg", "MemoryConfig")])
+S.table("PagedFlashMultiLatentAttentionDecodeOp", [
+    ("query", "TensorRef"), ("key", "TensorRef"), ("value", "TensorRef"), ("head_dim_v", "u32"), ("page_table", "TensorRef"),
+    ("is_causal", "bool"), ("attention_mask", "TensorRef"), ("cur_pos_tensor", "TensorRef"), ("attention_sink", "TensorRef"),
+    ("scale", "f32", OPT), ("out", "TensorRef"), ("memcfg", "MemoryConfig")])
 S.table("UniformScale2D", [("scale", "i32")])
 S.table("NonUniformScale2D", [("scale", "[i32]")])
 S.union("Scale2D", ["UniformScale2D", "NonUniformScale2D"])

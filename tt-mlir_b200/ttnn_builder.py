@@ -823,6 +823,21 @@ class ProgramBuilder:
         self._emit("FlashMlaPrefillOp", t, [q, k] + [x for x in (v, mask) if x is not None], [out], loc)
         return out
 
+    def paged_flash_multi_latent_attention_decode(self, q: Value, k_cache: Value, head_dim_v: int, page_table: Value,
+                                                  v_cache: Optional[Value] = None, cur_pos: Optional[Value] = None,
+                                                  mask: Optional[Value] = None, is_causal: bool = True,
+                                                  scale: Optional[float] = None, loc=None) -> Value:
+        """q [1, B, H, D], k_cache [blocks, Hkv, block, D], page_table [B, blocks per user], cur_pos [B]."""
+        out = self._value(list(q.shape[:3]) + [head_dim_v], q.dtype)
+        opt = lambda x: x.ref if x is not None else None
+        t = {"query": q.ref, "key": k_cache.ref, "value": opt(v_cache), "head_dim_v": head_dim_v, "page_table": page_table.ref,
+             "is_causal": is_causal, "attention_mask": opt(mask), "cur_pos_tensor": opt(cur_pos), "out": out.ref, "memcfg": self._mc()}
+        if scale is not None:
+            t["scale"] = scale
+        self._emit("PagedFlashMultiLatentAttentionDecodeOp", t,
+                   [q, k_cache, page_table] + [x for x in (v_cache, cur_pos, mask) if x is not None], [out], loc)
+        return out
+
     def chunked_scaled_dot_product_attention(self, q: Value, k_cache: Value, v_cache: Value, page_table: Value, chunk_start_idx: Value,
                                              scale: Optional[float] = None, loc=None) -> Value:
         """q [B, H, Sq, D] (positions chunk_start ..), caches [blocks, Hkv, block, D], page_table [B, blocks per user]."""

@@ -594,6 +594,13 @@ TTB_API int ttb_flash_mla_prefill(const void *q, const void *k, const void *v, c
 /* mask[u, 0, 0, j] = 0 for j <= cur_pos[u], -inf beyond: the additive mask of one decode step per user
  * (::ttnn::transformer::paged_flash_multi_latent_attention_decode builds the same from its cur_pos tensor). */
 TTB_API int ttb_cur_pos_mask(void *mask, const int32_t *cur_pos, int dtype, int64_t users, int64_t seq_kv, void *stream);
+/* ::ttnn::experimental::indexer_score_dsa (operations/transformer/indexer_score_dsa.cpp; golden
+ * tools/golden/mapping.py:8695-8742): out[b, 0, s, t] = sum_h relu(q[b, h, s, :] . k[b, 0, t, :]) * weights[b, h, s, 0]
+ * for keys t <= offset + s, -inf for later ones.  q [batch, heads, seq_q, head_dim], k [batch, 1, seq_kv, head_dim],
+ * weights [batch, heads, seq_q, 1], out [batch, 1, seq_q, seq_kv]; bf16 or f16, f32 accumulation, one rounding.
+ * `offset` is chunk_start_idx plus, on a mesh, the sequence positions held by the devices before this one. */
+TTB_API int ttb_indexer_score_dsa(const void *q, const void *k, const void *weights, void *out, int dtype, int64_t batch,
+                                  int64_t heads, int64_t seq_q, int64_t seq_kv, int64_t head_dim, int64_t offset, void *stream);
 /* Causal attention of a prefill chunk that starts at position `offset`: query row r sees keys 0 .. r + offset
  * (::ttnn::transformer::chunked_scaled_dot_product_attention once its paged keys and values are gathered,
  * operations/transformer/chunked_scaled_dot_product_attention.cpp; golden tools/golden/mapping.py:8847-8912).  The

@@ -392,6 +392,16 @@ class OracleBuilder:
     def flash_mla_prefill(self, q, k, head_dim_v, v=None, mask=None, is_causal=True, scale=None, loc=None):
         return _map(lambda qt, kt, vt, mt: ops.flash_mla_prefill(qt, kt, vt, mt, head_dim_v, is_causal, scale), q, k, v, mask)
 
+    def indexer_score_dsa(self, q, k, weights, chunk_start_idx=0, cluster_axis=None, loc=None):
+        """Every device's causal window starts behind the query rows of the devices before it along the axis that
+        carries the sequence (all devices in row-major order when no axis is named)."""
+        sq = q.first.shape[2]
+        if not isinstance(q.t, list):
+            return OValue(ops.indexer_score_dsa(q.t, k.first, weights.first, chunk_start_idx))
+        per = lambda v, i: v.t[i] if isinstance(v.t, list) else v.t
+        coord = lambda i: i if cluster_axis is None else (i // self.mesh_shape[1] if cluster_axis == 0 else i % self.mesh_shape[1])
+        return OValue([ops.indexer_score_dsa(q.t[i], per(k, i), per(weights, i), chunk_start_idx + coord(i) * sq) for i in range(len(q.t))])
+
     def paged_flash_multi_latent_attention_decode(self, q, k_cache, head_dim_v, page_table, v_cache=None, cur_pos=None, mask=None,
                                                   is_causal=True, scale=None, loc=None):
         return _map(lambda qt, kc, pt, vc, cp, mt: ops.paged_mla_decode(qt, kc, vc, pt, cp, mt, head_dim_v, is_causal, scale),

@@ -926,6 +926,16 @@ def flash_mla_prefill(q, k, v, mask, head_dim_v, is_causal, scale=None):
         q.float(), kf, vf, attn_mask=mask.float() if mask is not None else None, is_causal=is_causal and mask is None, scale=scale).to(q.dtype)
 
 
+def indexer_score_dsa(q, k, weights, offset):
+    """tools/golden/mapping.py:8695-8742: score[b, 0, s, t] = sum_h relu(q[b, h, s] . k[b, 0, t]) * weights[b, h, s, 0] in f32,
+    -inf for keys t > offset + s, one rounding to the query's type."""
+    qk = torch.relu(torch.einsum("bhsd,btd->bhst", q.float(), k.float()[:, 0]))
+    score = (qk * weights.float()).sum(dim=1, keepdim=True)
+    sq, t = q.shape[2], k.shape[2]
+    visible = (torch.arange(sq).view(1, 1, sq, 1) + offset) >= torch.arange(t).view(1, 1, 1, t)
+    return score.masked_fill(~visible, float("-inf")).to(q.dtype)
+
+
 def paged_mla_decode(q, k_cache, v_cache, page_table, cur_pos, mask, head_dim_v, is_causal=True, scale=None):
     """tools/golden/mapping.py:8275-8365: q [1, B, H, D]; the latent cache is un-paged through the page table, values are
     its first head_dim_v columns unless a value cache is given, user b sees keys 0 .. cur_pos[b]; scale defaults to 1."""

@@ -587,6 +587,19 @@ def main():
     store(out, "map/mla_decode/own_values", one(ref.ttir_paged_flash_multi_latent_attention_decode_golden(
         gmt(dq), gmt(dk), gmt(dv), gmt(dpt), None, gmt(dpos), None, S.IntegerAttr(16), S.BoolAttr(True), S.FloatAttr(0.15), S.F32Type())))
 
+    # --- lightning-indexer scores of DeepSeek sparse attention (mapping.py:8695-8742): the shapes of the reference's own
+    # test (test/python/golden/test_stablehlo_ops.py:2560-2596), dense and as the last chunk of a longer history, plus a
+    # ragged case (5 heads, 19 queries, 75 keys) that fills no tile
+    iq, ik, iw = (rnd(1, 8, 64, 128) * 0.3).to(torch.bfloat16), (rnd(1, 1, 128, 128) * 0.3).to(torch.bfloat16), rnd(1, 8, 64, 1).to(torch.bfloat16)
+    for n, t in (("q", iq), ("k", ik), ("w", iw)):
+        store(out, f"map/indexer/{n}", t)
+    store(out, "map/indexer/dense", one(ref.indexer_score_dsa_golden(gmt(iq), gmt(ik), gmt(iw), 0)))
+    store(out, "map/indexer/chunked", one(ref.indexer_score_dsa_golden(gmt(iq), gmt(ik), gmt(iw), 64)))
+    rq, rk, rw = (rnd(2, 5, 19, 40) * 0.3).to(torch.bfloat16), (rnd(2, 1, 75, 40) * 0.3).to(torch.bfloat16), rnd(2, 5, 19, 1).to(torch.bfloat16)
+    for n, t in (("q", rq), ("k", rk), ("w", rw)):
+        store(out, f"map/indexer/ragged_{n}", t)
+    store(out, "map/indexer/ragged", one(ref.indexer_score_dsa_golden(gmt(rq), gmt(rk), gmt(rw), 30)))
+
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ttir_cpu_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes")

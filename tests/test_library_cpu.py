@@ -196,6 +196,7 @@ def _wide_ops_graph(b):
     outs.append(b.chunked_scaled_dot_product_attention(qc, b.input([4, 1, 16, 32], bf), b.input([4, 1, 16, 32], bf),
                                                        b.input([1, 2], "Int32"), b.input([1], "Int32"), scale=0.2))
     outs.append(b.flash_mla_prefill(b.input([1, 2, 8, 48], bf), b.input([1, 1, 8, 48], bf), 32))
+    outs.append(b.indexer_score_dsa(b.input([1, 4, 8, 32], bf), b.input([1, 1, 16, 32], bf), b.input([1, 4, 8, 1], bf), 8, cluster_axis=1))
     b.output(*outs)
 
 

@@ -451,6 +451,33 @@ def test_flash_mla_prefill_matches_the_reference_goldens(rt, device, golden):
     assert_matches(got[0], want[0], "flash_mla_prefill bf16, 576 / 512")
 
 
+def _same_scores(got, want, what):
+    """Masked keys agree exactly; the sums agree to one bf16 / f16 step (f32 sums taken in another order, one rounding)."""
+    assert got.shape == want.shape and got.dtype == want.dtype, what
+    assert torch.equal(torch.isneginf(got), torch.isneginf(want)), what
+    seen = torch.isfinite(want)
+    assert torch.isfinite(got[seen]).all(), what
+    assert torch.allclose(got[seen].float(), want[seen].float(), rtol=2.0 ** -7, atol=1e-3), what
+
+
+def test_indexer_score_dsa_matches_the_reference_goldens(rt, device, golden):
+    q, k, w = (golden[f"map/indexer/{n}"] for n in ("q", "k", "w"))
+    for start, name in ((0, "dense"), (64, "chunked")):
+        got, want = run_body(rt, device, lambda b, qv, kv, wv: b.indexer_score_dsa(qv, kv, wv, start), [q, k, w])
+        _same_scores(got[0], golden[f"map/indexer/{name}"], name)
+        assert torch.equal(want[0], golden[f"map/indexer/{name}"])
+    q, k, w = (golden[f"map/indexer/ragged_{n}"] for n in ("q", "k", "w"))
+    got, _ = run_body(rt, device, lambda b, qv, kv, wv: b.indexer_score_dsa(qv, kv, wv, 30), [q, k, w])
+    _same_scores(got[0], golden["map/indexer/ragged"], "5 heads, 19 queries, 75 keys of 40")
+    # the indexer of a DeepSeek-style layer: 64 heads of 128, the last 200 positions of a 1000-token history, f16 too
+    torch.manual_seed(21)
+    for dt in (torch.bfloat16, torch.float16):
+        qb, kb = (torch.randn(1, 64, 200, 128) * 0.2).to(dt), (torch.randn(1, 1, 1000, 128) * 0.2).to(dt)
+        wb = torch.randn(1, 64, 200, 1).to(dt)
+        got, want = run_body(rt, device, lambda b, qv, kv, wv: b.indexer_score_dsa(qv, kv, wv, 800), [qb, kb, wb])
+        _same_scores(got[0], want[0], f"64 heads, {dt}")
+
+
 def test_paged_multi_latent_decode_attention_matches_the_reference_goldens(rt, device, golden):
     q, k, pt, pos, v = (golden[f"map/mla_decode/{n}"] for n in ("q", "k", "page_table", "cur_pos", "v"))
     got, want = run_body(rt, device, lambda b, qv, kv, tv, pv: b.paged_flash_multi_latent_attention_decode(qv, kv, 32, tv, cur_pos=pv),

@@ -421,6 +421,16 @@ def test_multi_latent_attention_prefill(golden):
     assert torch.allclose(ops.flash_mla_prefill(q, k, v, None, 16, False), golden["map/mla/own_values"], rtol=1e-6, atol=1e-6)
 
 
+def test_indexer_score_dsa(golden):
+    """Restatement against the reference's golden (tools/golden/mapping.py:8695-8742)."""
+    q, k, w = (golden[f"map/indexer/{n}"] for n in ("q", "k", "w"))
+    assert torch.equal(ops.indexer_score_dsa(q, k, w, 0), golden["map/indexer/dense"])
+    assert torch.equal(ops.indexer_score_dsa(q, k, w, 64), golden["map/indexer/chunked"])
+    q, k, w = (golden[f"map/indexer/ragged_{n}"] for n in ("q", "k", "w"))
+    assert torch.equal(ops.indexer_score_dsa(q, k, w, 30), golden["map/indexer/ragged"])
+    assert torch.isneginf(golden["map/indexer/dense"][0, 0, 0, 1:]).all() and torch.isfinite(golden["map/indexer/chunked"][0, 0, 0, :65]).all()
+
+
 def test_paged_multi_latent_decode_attention(golden):
     """Restatement against the reference's golden (tools/golden/mapping.py:8275-8365)."""
     q, k, pt, pos, v = (golden[f"map/mla_decode/{n}"] for n in ("q", "k", "page_table", "cur_pos", "v"))

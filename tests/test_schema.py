@@ -88,7 +88,7 @@ def test_executor_dispatches_every_declared_op():
     declared = set(OP_TYPE_MEMBERS) - set(UNDECLARED_OPS)
     assert declared <= dispatched, f"declared but not dispatched: {sorted(declared - dispatched)}"
     assert set(UNDECLARED_OPS) == {
-        "GenericOp", "IndexerScoreDsaOp", "MoeGptOp", "PrepareMoEComputeW0W1WeightsOp", "PrepareMoEComputeW2WeightsOp", "MoeComputeOp",
+        "GenericOp", "MoeGptOp", "PrepareMoEComputeW0W1WeightsOp", "PrepareMoEComputeW2WeightsOp", "MoeComputeOp",
         "SDPAForwardOp", "SDPABackwardOp", "SelectiveReduceCombineOp"}
     assert not (set(UNDECLARED_OPS) & dispatched)
     assert len(OP_TYPE_MEMBERS) == 131

@@ -134,6 +134,14 @@ void collectOpRefs(const fbt::Operation *op, std::vector<const fbt::TensorRef *>
     pushRef(outs, o->out());
     break;
   }
+  case OpType::IndexerScoreDsaOp: {
+    const auto *o = op->type_as_IndexerScoreDsaOp();
+    pushRef(ins, o->query());
+    pushRef(ins, o->key());
+    pushRef(ins, o->weights());
+    pushRef(outs, o->out());
+    break;
+  }
   case OpType::FlashMlaPrefillOp: {
     const auto *o = op->type_as_FlashMlaPrefillOp();
     pushRef(ins, o->query());
@@ -887,6 +895,7 @@ private:
   void runAllToAllDispatch(const fbt::AllToAllDispatchOp *op);
   void runPagedMlaDecode(const fbt::PagedFlashMultiLatentAttentionDecodeOp *op);
   void runFlashMlaPrefill(const fbt::FlashMlaPrefillOp *op);
+  void runIndexerScoreDsa(const fbt::IndexerScoreDsaOp *op);
   void runChunkedSdpa(const fbt::ChunkedScaledDotProductAttentionOp *op);
   void runConv3d(const fbt::Conv3dOp *op);
   void runGeluBackward(const fbt::ExperimentalEltwiseBinaryBackwardOp *op);
@@ -1271,6 +1280,7 @@ size_t Executor::runOp(size_t i) {
   case OpType::AllToAllDispatchOp: runAllToAllDispatch(op->type_as_AllToAllDispatchOp()); break;
   case OpType::PagedFlashMultiLatentAttentionDecodeOp: runPagedMlaDecode(op->type_as_PagedFlashMultiLatentAttentionDecodeOp()); break;
   case OpType::FlashMlaPrefillOp: runFlashMlaPrefill(op->type_as_FlashMlaPrefillOp()); break;
+  case OpType::IndexerScoreDsaOp: runIndexerScoreDsa(op->type_as_IndexerScoreDsaOp()); break;
   case OpType::ChunkedScaledDotProductAttentionOp: runChunkedSdpa(op->type_as_ChunkedScaledDotProductAttentionOp()); break;
   case OpType::Conv3dOp: runConv3d(op->type_as_Conv3dOp()); break;
   case OpType::PrepareConv3dWeightsOp: {
@@ -2949,6 +2959,30 @@ void Executor::runFlashMlaPrefill(const fbt::FlashMlaPrefillOp *op) {
   eachRank([&](size_t i, const RankCtx &r) {
     TTB_CALL(ttb_flash_mla_prefill(q->shards[i]->ptr, k->shards[i]->ptr, v ? v->shards[i]->ptr : nullptr, mask ? mask->shards[i]->ptr : nullptr,
                                    out->shards[i]->ptr, ttbDtype(q->dtype), B, Hq, Hkv, Sq, Skv, D, Dv, maskB, maskH, causal, scale, r.stream));
+  });
+  put(op->out(), out);
+}
+
+// indexer_score_dsa (operations/transformer/indexer_score_dsa.cpp; golden tools/golden/mapping.py:8695-8742): the
+// lightning-indexer scores of DeepSeek sparse attention.  On a mesh every device holds a slice of the query sequence;
+// its causal window starts behind the rows of the devices before it along cluster_axis, or before it in row-major
+// order over the whole mesh when no axis is named (the reference passes the same choice on as its sequence-shard axes).
+void Executor::runIndexerScoreDsa(const fbt::IndexerScoreDsaOp *op) {
+  TensorPtr q = getDevice(op->query()), k = getDevice(op->key()), w = getDevice(op->weights());
+  TensorPtr out = allocOut(op->out());
+  TTRT_ASSERT(q->shape.size() == 4 && k->shape.size() == 4 && w->shape.size() == 4, "indexer_score_dsa expects rank-4 tensors");
+  const int64_t B = q->shape[0], H = q->shape[1], Sq = q->shape[2], D = q->shape[3], T = k->shape[2];
+  TTRT_ASSERT(k->shape[0] == B && k->shape[1] == 1 && k->shape[3] == D, "indexer_score_dsa key must be [B, 1, T, D]");
+  TTRT_ASSERT(w->shape[0] == B && w->shape[1] == H && w->shape[2] == Sq && w->shape[3] == 1, "indexer_score_dsa weights must be [B, Hi, Sq, 1]");
+  TTRT_ASSERT(k->dtype == q->dtype && w->dtype == q->dtype && out->dtype == q->dtype, "indexer_score_dsa tensors must share one data type");
+  TTRT_ASSERT(out->volume() == static_cast<size_t>(B * Sq * T), "indexer_score_dsa result must be [B, 1, Sq, T]");
+  const bool named = op->cluster_axis().has_value();
+  TTRT_ASSERT(!named || *op->cluster_axis() < 2, "cluster_axis must be 0 or 1");
+  const uint32_t cols = std::max<uint32_t>(dev->meshShape[1], 1);
+  eachRank([&](size_t i, const RankCtx &r) {
+    const uint32_t before = !named ? r.meshRank : (*op->cluster_axis() == 0 ? r.meshRank / cols : r.meshRank % cols);
+    TTB_CALL(ttb_indexer_score_dsa(q->shards[i]->ptr, k->shards[i]->ptr, w->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(q->dtype), B, H, Sq,
+                                   T, D, static_cast<int64_t>(op->chunk_start_idx()) + static_cast<int64_t>(before) * Sq, r.stream));
   });
   put(op->out(), out);
 }

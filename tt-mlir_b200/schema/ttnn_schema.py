@@ -383,6 +383,9 @@ S.table("ChunkedScaledDotProductAttentionOp", [
 S.table("FlashMlaPrefillOp", [
     ("query", "TensorRef"), ("key", "TensorRef"), ("value", "TensorRef"), ("attention_mask", "TensorRef"),
     ("head_dim_v", "u32"), ("is_causal", "bool"), ("scale", "f32", OPT), ("out", "TensorRef"), ("memcfg", "MemoryConfig")])
+S.table("IndexerScoreDsaOp", [
+    ("query", "TensorRef"), ("key", "TensorRef"), ("weights", "TensorRef"), ("chunk_start_idx", "u32"), ("out", "TensorRef"),
+    ("cluster_axis", "u32", OPT)])
 S.table("PagedFlashMultiLatentAttentionDecodeOp", [
     ("query", "TensorRef"), ("key", "TensorRef"), ("value", "TensorRef"), ("head_dim_v", "u32"), ("page_table", "TensorRef"),
     ("is_causal", "bool"), ("attention_mask", "TensorRef"), ("cur_pos_tensor", "TensorRef"), ("attention_sink", "TensorRef"),

@@ -823,6 +823,16 @@ class ProgramBuilder:
         self._emit("FlashMlaPrefillOp", t, [q, k] + [x for x in (v, mask) if x is not None], [out], loc)
         return out
 
+    def indexer_score_dsa(self, q: Value, k: Value, weights: Value, chunk_start_idx: int = 0, cluster_axis: Optional[int] = None,
+                          loc=None) -> Value:
+        """q [B, Hi, Sq, D], k [B, 1, T, D], weights [B, Hi, Sq, 1] -> scores [B, 1, Sq, T]."""
+        out = self._value([q.shape[0], 1, q.shape[2], k.shape[2]], q.dtype)
+        t = {"query": q.ref, "key": k.ref, "weights": weights.ref, "chunk_start_idx": chunk_start_idx, "out": out.ref}
+        if cluster_axis is not None:
+            t["cluster_axis"] = cluster_axis
+        self._emit("IndexerScoreDsaOp", t, [q, k, weights], [out], loc)
+        return out
+
     def paged_flash_multi_latent_attention_decode(self, q: Value, k_cache: Value, head_dim_v: int, page_table: Value,
                                                   v_cache: Optional[Value] = None, cur_pos: Optional[Value] = None,
                                                   mask: Optional[Value] = None, is_causal: bool = True,

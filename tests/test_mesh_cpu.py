@@ -185,3 +185,28 @@ def test_sequence_sharded_io_program_shape():
     buf = graphs.build_binary(graphs.decoder_block_graph, mesh_shape=(1, 2), tp=2, presharded=True, **kw)
     prog = Reader(S, buf).root("TTNNBinary")["programs"][0]
     assert prog["inputs"][0]["desc"]["shape"] == [1, 64, 128] and prog["outputs"][0]["desc"]["shape"] == [1, 64, 128]
+
+
+def test_sequence_sharded_indexer_scores_equal_the_single_device_scores():
+    """indexer_score_dsa with the query sequence split over a mesh axis: every device's causal window starts behind the
+    rows of the devices before it (the op's description, include/ttmlir/Dialect/TTNN/IR/TTNNOps.td:4378-4385), so the
+    gathered scores are those of one device holding the whole sequence."""
+    from oracle.backend import OracleBuilder
+    torch.manual_seed(23)
+    bf = torch.bfloat16
+    q, k, w = (torch.randn(1, 4, 32, 64) * 0.3).to(bf), (torch.randn(1, 1, 48, 64) * 0.3).to(bf), torch.randn(1, 4, 32, 1).to(bf)
+
+    def body(b, shard):
+        qv, kv, wv = b.input(list(q.shape), "BFloat16"), b.input(list(k.shape), "BFloat16"), b.input(list(w.shape), "BFloat16")
+        if not shard:
+            return b.output(b.indexer_score_dsa(qv, kv, wv, 16))
+        qs, ws = b.distribute(qv, 2), b.distribute(wv, 2)
+        b.output(b.aggregate(b.indexer_score_dsa(qs, kv, ws, 16, cluster_axis=1), 2))
+    whole = OracleBuilder([q, k, w])
+    body(whole, False)
+    split = OracleBuilder([q, k, w], mesh_shape=(1, 4))
+    body(split, True)
+    assert torch.equal(whole.results()[0], split.results()[0])
+    assert torch.isneginf(whole.results()[0][0, 0, 0, 17:]).all() and torch.isfinite(whole.results()[0][0, 0, 31]).all()
+    buf = graphs.build_binary(lambda b: body(b, True), mesh_shape=(1, 4))       # the same program as a flatbuffer
+    assert len(buf) > 0

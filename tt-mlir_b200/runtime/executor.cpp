@@ -2870,7 +2870,6 @@ void Executor::runReductionProd(const fbt::ReductionProdOp *op) {
   put(op->out(), out);
 }
 
-// group_norm on channels-last [N, 1, H*W, C] (or [N, H, W, C]): operations/normalization/group_norm.cpp.
 // paged_flash_multi_latent_attention_decode (operations/transformer/paged_flash_multi_latent_attention_decode.cpp;
 // golden tools/golden/mapping.py:8275-8365): one query token per user, [1, B, H, D], against a paged latent cache
 // [blocks, Hkv, block, D]; values are the first head_dim_v columns of the keys unless a paged value cache is given;
@@ -3100,9 +3099,8 @@ void Executor::runEmbeddingBackward(const fbt::EmbeddingBackwardOp *op) {
   const size_t dim = ws.back(), vocab = ws[ws.size() - 2], rows = idx->volume();
   TTRT_ASSERT(grad->volume() == rows * dim && out->volume() == vocab * dim && out->dtype == grad->dtype,
               "embedding_bw: the gradient must be [indices, ", dim, "] and the result [", vocab, ", ", dim, "]");
-  const size_t wsBytes = ttb_embedding_backward_workspace_bytes(vocab, dim);
   TensorPtr scratch = makeDeviceTensor(dev, {static_cast<uint32_t>(vocab), static_cast<uint32_t>(dim)}, DataType::Float32);
-  (void)wsBytes;
+  TTRT_ASSERT(scratch->bytes() >= ttb_embedding_backward_workspace_bytes(vocab, dim), "embedding_bw workspace is too small");
   eachRank([&](size_t i, const RankCtx &r) {
     TTB_CALL(ttb_embedding_backward(idx->shards[i]->ptr, grad->shards[i]->ptr, out->shards[i]->ptr, ttbDtype(idx->dtype), ttbDtype(grad->dtype),
                                     rows, vocab, dim, scratch->shards[i]->ptr, r.stream));
@@ -3804,6 +3802,7 @@ void Executor::runBatchNormTraining(const fbt::BatchNormTrainingOp *op) {
   put(op->out(), out);
 }
 
+// group_norm on channels-last [N, 1, H*W, C] (or [N, H, W, C]): operations/normalization/group_norm.cpp.
 void Executor::runGroupNorm(const fbt::GroupNormOp *op) {
   TTRT_ASSERT(!op->input_mask(), "group_norm with an input mask (a Tenstorrent core-grid artefact) is not supported");
   TensorPtr x = getDevice(op->input());

@@ -16,6 +16,10 @@ small seeded inputs:
   bindings; ttmlir_standin.py supplies attribute and type classes in their place, so the golden
   bodies that run are the reference's own text.
 
+A third source, for the one op whose golden lives in a test file that cannot be imported (it needs the compiler's
+builder): test/python/golden/ttir_ops/fusing/test_rope_fusing.py -- its `rotate_half` and `torch_rope` functions are
+compiled from that file's own syntax tree (lift_functions), nothing else of the file runs.
+
 Nothing in this script restates a golden.  The fixture travels with the repo; the reference tree
 does not.  Two things have no golden to call and are recorded from torch directly, marked below:
 per-axis quantization (torch.quantize_per_channel) and nothing else.
@@ -39,6 +43,22 @@ def load_ttir_cpu(root):
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     return mod
+
+
+def lift_functions(path, names):
+    """Compiles the named top-level functions of a Python file from its own syntax tree and returns them; the rest of
+    the file (imports of the compiler's builder, test bodies) is not executed."""
+    import ast
+    with open(path) as f:
+        tree = ast.parse(f.read(), path)
+    ns = {"torch": torch}
+    for node in tree.body:
+        if isinstance(node, ast.FunctionDef) and node.name in names:
+            exec(compile(ast.Module([node], []), path, "exec"), ns)
+    missing = [n for n in names if n not in ns]
+    if missing:
+        raise SystemExit(f"{path} no longer defines {missing}")
+    return [ns[n] for n in names]
 
 
 def store(out, name, t):
@@ -599,6 +619,19 @@ def main():
     for n, t in (("q", rq), ("k", rk), ("w", rw)):
         store(out, f"map/indexer/ragged_{n}", t)
     store(out, "map/indexer/ragged", one(ref.indexer_score_dsa_golden(gmt(rq), gmt(rk), gmt(rw), 30)))
+
+    # --- rotary embedding: the golden of the reference's fusing test (test_rope_fusing.py:23-33), cos / sin [1, S, D]
+    # reshaped to [1, 1, S, D] and broadcast over batch and heads as the test's builder does; f32, and bf16 operands
+    # evaluated in f32 with one rounding (the fused op's arithmetic)
+    (torch_rope,) = lift_functions(os.path.join(root, "test/python/golden/ttir_ops/fusing/test_rope_fusing.py"), ["rotate_half", "torch_rope"])[1:]
+    px = rnd(2, 4, 24, 64)
+    ang = torch.arange(24, dtype=torch.float32).view(24, 1) * torch.pow(10000.0, -torch.arange(32, dtype=torch.float32) / 32).view(1, 32)
+    pcos, psin = torch.cos(torch.cat([ang, ang], dim=-1)).view(1, 24, 64), torch.sin(torch.cat([ang, ang], dim=-1)).view(1, 24, 64)
+    for n, t in (("x", px), ("cos", pcos), ("sin", psin)):
+        store(out, f"rope/{n}", t)
+    store(out, "rope/f32", torch_rope(px, pcos.view(1, 1, 24, 64), psin.view(1, 1, 24, 64)))
+    bx, bc, bs = px.to(torch.bfloat16), pcos.to(torch.bfloat16), psin.to(torch.bfloat16)
+    store(out, "rope/bf16_operands", torch_rope(bx.float(), bc.float().view(1, 1, 24, 64), bs.float().view(1, 1, 24, 64)).to(torch.bfloat16))
 
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ttir_cpu_golden.npz")
     np.savez_compressed(path, **out)

@@ -203,6 +203,16 @@ def test_rotary_embedding(rt, device):
     assert_matches(got[0], want[0], "rope")
 
 
+def test_rotary_embedding_matches_the_golden_of_the_fusing_test(rt, device, golden):
+    """The fixture is what torch_rope of test/python/golden/ttir_ops/fusing/test_rope_fusing.py returns (f32 evaluation
+    of bf16 operands, one rounding), cos / sin broadcast over batch and heads."""
+    bf = torch.bfloat16
+    x, cos, sin = golden["rope/x"].to(bf), golden["rope/cos"].to(bf).reshape(1, 1, 24, 64), golden["rope/sin"].to(bf).reshape(1, 1, 24, 64)
+    got, want = run_body(rt, device, lambda b, xx, c, s: b.rotary_embedding(xx, c, s), [x, cos, sin])
+    assert_matches(got[0], golden["rope/bf16_operands"], "rope against the reference's golden")
+    assert torch.equal(want[0], golden["rope/bf16_operands"])
+
+
 def test_data_movement(rt, device):
     x = torch.randn(3, 4, 5, 6)
 

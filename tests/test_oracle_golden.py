@@ -421,6 +421,16 @@ def test_multi_latent_attention_prefill(golden):
     assert torch.allclose(ops.flash_mla_prefill(q, k, v, None, 16, False), golden["map/mla/own_values"], rtol=1e-6, atol=1e-6)
 
 
+def test_rotary_embedding_against_the_golden_of_the_fusing_test(golden):
+    """The reference's own definition of the fused op's result (test/python/golden/ttir_ops/fusing/test_rope_fusing.py:23-33,
+    lifted from the file by the fixture generator): bit for bit in f32, and for bf16 operands the f32 evaluation with
+    one rounding."""
+    x, cos, sin = golden["rope/x"], golden["rope/cos"], golden["rope/sin"]
+    assert torch.equal(ops.rotary_embedding(x, cos, sin), golden["rope/f32"])
+    bf = torch.bfloat16
+    assert torch.equal(ops.rotary_embedding(x.to(bf), cos.to(bf), sin.to(bf)), golden["rope/bf16_operands"])
+
+
 def test_indexer_score_dsa(golden):
     """Restatement against the reference's golden (tools/golden/mapping.py:8695-8742)."""
     q, k, w = (golden[f"map/indexer/{n}"] for n in ("q", "k", "w"))
